@@ -1,0 +1,602 @@
+"""Tensor-level ops of the framework.
+
+Each op has two implementations with identical semantics:
+
+* ``*_ref``: plain PyTorch (fp32 math), used on CPU tensors and as the numerical oracle in
+  tests;
+* the sm_100a kernel from ``libab2_kernels.so`` for CUDA tensors (bf16 activations), wrapped
+  in ``torch.autograd.Function`` where the op is differentiable.
+
+Public entry points dispatch on ``tensor.is_cuda`` only: CPU -> reference, CUDA -> kernel
+(raising if the library cannot be loaded; there is no silent CUDA fallback).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import lib as _lib
+
+EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_BF16_RESID = 0, 1, 2, 3
+
+
+def _L():
+    return _lib.get_lib()
+
+
+def _s():
+    return _lib.stream_ptr()
+
+
+# ----------------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, epi: int = EPI_BF16, resid: Optional[torch.Tensor] = None,
+         bn: int = 0) -> torch.Tensor:
+    """``C = op(A) @ op(B)`` on tcgen05 tensor cores (bf16 in, fp32 accumulate).
+
+    ``a``: ``[M,K]`` (or ``[K,M]`` when ``a_mn``); ``b``: ``[N,K]`` (or ``[K,N]`` when
+    ``b_mn``). ``epi``: EPI_BF16 store, EPI_F32 store, EPI_F32_ACC accumulate into ``out``,
+    EPI_BF16_RESID store of ``acc + resid``.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and a.dim() == 2 and b.dim() == 2
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    assert K == Kb, f"inner dims differ: {K} vs {Kb}"
+    if out is None:
+        assert epi != EPI_F32_ACC
+        out = torch.empty(M, N, device=a.device, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    if not a.is_cuda:
+        A = (a.t() if a_mn else a).float()
+        B = (b if b_mn else b.t()).float()
+        acc = A @ B
+        if epi == EPI_F32_ACC:
+            out += acc
+        elif epi == EPI_BF16_RESID:
+            out.copy_((acc + resid.float()).to(out.dtype))
+        else:
+            out.copy_(acc.to(out.dtype))
+        return out
+    if epi == EPI_BF16_RESID:
+        assert resid is not None and resid.shape == out.shape and resid.stride() == out.stride()
+    rc = _L().ab2_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(resid), M, N, K, a.stride(0),
+                            b.stride(0), out.stride(0), int(a_mn), int(b_mn), epi, bn, _s())
+    _lib.check(rc, "ab2_gemm_bf16")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x @ W^T (+ residual). Weight gradients accumulate in fp32 into ``w.main_grad``
+    when the parameter carries one (flat-shard training), else are returned in bf16."""
+
+    @staticmethod
+    def forward(ctx, x, w, resid):
+        ctx.save_for_backward(x, w)
+        ctx.has_resid = resid is not None
+        x2 = x.reshape(-1, x.shape[-1])
+        if resid is not None:
+            y = gemm(x2, w, epi=EPI_BF16_RESID, resid=resid.reshape(-1, w.shape[0]))
+        else:
+            y = gemm(x2, w)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, epi=EPI_F32_ACC)
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+        return dx, dw, (dy if ctx.has_resid else None)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if not x.is_cuda:
+        y = F.linear(x, w)
+        return y + resid if resid is not None else y
+    return _Linear.apply(x, w, resid)
+
+
+# ----------------------------------------------------------------------------- RMSNorm
+def rmsnorm_ref(x, w, eps, resid=None):
+    if resid is not None:
+        x = (x.float() + resid.float()).to(x.dtype)
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    return y.to(x.dtype), x
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, resid, eps):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        if resid is not None:
+            r2 = resid.reshape(-1, H)
+            new_res = torch.empty_like(x2)
+            rc = _L().ab2_rmsnorm_fwd(x2.data_ptr(), r2.data_ptr(), w.data_ptr(), y.data_ptr(), new_res.data_ptr(),
+                                      rstd.data_ptr(), rows, H, eps, _s())
+            saved_x = new_res
+        else:
+            rc = _L().ab2_rmsnorm_fwd(x2.data_ptr(), None, w.data_ptr(), y.data_ptr(), None, rstd.data_ptr(), rows, H,
+                                      eps, _s())
+            new_res = x2
+            saved_x = x2
+        _lib.check(rc, "ab2_rmsnorm_fwd")
+        ctx.save_for_backward(saved_x, w, rstd)
+        ctx.has_resid = resid is not None
+        ctx.shape = x.shape
+        return y.view(x.shape), new_res.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x2, w, rstd = ctx.saved_tensors
+        rows, H = x2.shape
+        dy2 = dy.reshape(rows, H).contiguous()
+        dr2 = dres.reshape(rows, H).contiguous() if dres is not None else None
+        dx = torch.empty_like(x2)
+        mg = getattr(w, "main_grad", None)
+        dw32 = mg if mg is not None else torch.zeros(H, device=x2.device, dtype=torch.float32)
+        rc = _L().ab2_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), _lib.ptr(dr2), rstd.data_ptr(),
+                                  dx.data_ptr(), dw32.data_ptr(), rows, H, _s())
+        _lib.check(rc, "ab2_rmsnorm_bwd")
+        dxv = dx.view(ctx.shape)
+        return dxv, (None if mg is not None else dw32.to(w.dtype)), (dxv if ctx.has_resid else None), None
+
+
+def rmsnorm(x, w, eps: float = 1e-6, resid=None):
+    """Returns ``(normed, residual_stream)`` where ``residual_stream = x (+ resid)``."""
+    if not x.is_cuda:
+        return rmsnorm_ref(x, w, eps, resid)
+    return _RMSNorm.apply(x.contiguous(), w, None if resid is None else resid.contiguous(), eps)
+
+
+# ----------------------------------------------------------------------------- RoPE
+def rope_tables(max_pos: int, dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
+    ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+def rope_ref(x, pos, cos, sin, backward=False):
+    # x: [T, h, D]; rotate-half convention (HF Qwen/Llama)
+    D = x.shape[-1]
+    c = cos[pos][:, None, :]
+    s = sin[pos][:, None, :]
+    if backward:
+        s = -s
+    xf = x.float()
+    a, b = xf[..., : D // 2], xf[..., D // 2:]
+    return torch.cat([a * c - b * s, b * c + a * s], dim=-1).to(x.dtype)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pos, cos, sin):
+        ctx.save_for_backward(pos, cos, sin)
+        y = x.clone() if x.is_contiguous() else x.contiguous()
+        T, h, D = y.shape
+        rc = _L().ab2_rope(y.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, h, D, y.stride(0), 0, _s())
+        _lib.check(rc, "ab2_rope")
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        pos, cos, sin = ctx.saved_tensors
+        g = dy.clone() if dy.is_contiguous() else dy.contiguous()
+        T, h, D = g.shape
+        rc = _L().ab2_rope(g.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, h, D, g.stride(0), 1, _s())
+        _lib.check(rc, "ab2_rope")
+        return g, None, None, None
+
+
+def rope(x, pos, cos, sin):
+    """x: [T, heads, D] bf16; pos: [T] int32; cos/sin: [max_pos, D/2] fp32."""
+    if not x.is_cuda:
+        return rope_ref(x, pos.long(), cos, sin)
+    return _Rope.apply(x, pos, cos, sin)
+
+
+def rope_inplace_(x, pos, cos, sin):
+    """In-place rotary embedding on a (possibly strided) ``[T, heads, D]`` view. No autograd."""
+    if not x.is_cuda:
+        x.copy_(rope_ref(x, pos.long(), cos, sin))
+        return x
+    T, h, D = x.shape
+    assert x.stride(2) == 1 and x.stride(1) == D
+    rc = _L().ab2_rope(x.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, h, D, x.stride(0), 0, _s())
+    _lib.check(rc, "ab2_rope")
+    return x
+
+
+# ----------------------------------------------------------------------------- SwiGLU
+def swiglu_ref(gu):
+    I = gu.shape[-1] // 2
+    g, u = gu[..., :I].float(), gu[..., I:].float()
+    return (F.silu(g) * u).to(gu.dtype)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        I = gu.shape[-1] // 2
+        g2 = gu.reshape(-1, 2 * I)
+        out = torch.empty(g2.shape[0], I, device=gu.device, dtype=gu.dtype)
+        _lib.check(_L().ab2_swiglu_fwd(g2.data_ptr(), out.data_ptr(), g2.shape[0], I, _s()), "ab2_swiglu_fwd")
+        return out.view(*gu.shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        I = gu.shape[-1] // 2
+        g2 = gu.reshape(-1, 2 * I)
+        d2 = dout.reshape(-1, I).contiguous()
+        dgu = torch.empty_like(g2)
+        _lib.check(_L().ab2_swiglu_bwd(g2.data_ptr(), d2.data_ptr(), dgu.data_ptr(), g2.shape[0], I, _s()),
+                   "ab2_swiglu_bwd")
+        return dgu.view_as(gu)
+
+
+def swiglu(gu):
+    """``silu(gu[..., :I]) * gu[..., I:]``."""
+    if not gu.is_cuda:
+        return swiglu_ref(gu)
+    return _SwiGLU.apply(gu.contiguous())
+
+
+# ----------------------------------------------------------------------------- embedding
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, W):
+        ctx.save_for_backward(ids)
+        ctx.W = W
+        T = ids.numel()
+        V, H = W.shape
+        out = torch.empty(T, H, device=W.device, dtype=W.dtype)
+        _lib.check(_L().ab2_embed_fwd(W.data_ptr(), ids.data_ptr(), out.data_ptr(), T, H, V, _s()), "ab2_embed_fwd")
+        return out.view(*ids.shape, H)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        W = ctx.W
+        V, H = W.shape
+        d2 = dy.reshape(-1, H).contiguous()
+        mg = getattr(W, "main_grad", None)
+        dW = mg if mg is not None else torch.zeros(V, H, device=W.device, dtype=torch.float32)
+        _lib.check(_L().ab2_embed_bwd(d2.data_ptr(), ids.data_ptr(), dW.data_ptr(), d2.shape[0], H, V, _s()),
+                   "ab2_embed_bwd")
+        return None, (None if mg is not None else dW.to(W.dtype))
+
+
+def embedding(ids, W):
+    if not W.is_cuda:
+        return F.embedding(ids.long(), W)
+    return _Embedding.apply(ids.to(torch.int32).contiguous(), W)
+
+
+# ----------------------------------------------------------------------------- attention
+def attention_ref(q, k, v, cu_seqlens, causal=True, scale=None):
+    """Packed varlen attention, fp32 math. q: [T,Hq,D], k/v: [T,Hkv,D]. Returns (o, lse[Hq,T])."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    o = torch.zeros_like(q, dtype=torch.float32)
+    lse = torch.zeros(Hq, T, dtype=torch.float32, device=q.device)
+    cu = cu_seqlens.tolist()
+    rep = Hq // Hkv
+    for i in range(len(cu) - 1):
+        a, b = cu[i], cu[i + 1]
+        if b <= a:
+            continue
+        qi = q[a:b].float().transpose(0, 1)  # [Hq, L, D]
+        ki = k[a:b].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        vi = v[a:b].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        s = qi @ ki.transpose(1, 2) * scale
+        if causal:
+            L = b - a
+            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            s = s.masked_fill(~mask, float("-inf"))
+        lse[:, a:b] = torch.logsumexp(s, dim=-1)
+        o[a:b] = (torch.softmax(s, dim=-1) @ vi).transpose(0, 1)
+    return o.to(q.dtype), lse
+
+
+def attn_tile_table(cu_seqlens: torch.Tensor, total_tokens: int, tile: int = 128) -> torch.Tensor:
+    """Device-side (sync-free) table ``[n,2]`` of (sequence index | -1, query block) for the
+    attention kernels; ``n = ceil(T/tile) + num_seqs`` is an upper bound on the tile count."""
+    B = cu_seqlens.numel() - 1
+    n = (total_tokens + tile - 1) // tile + B
+    lens = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
+    blocks = (lens + tile - 1) // tile
+    ends = torch.cumsum(blocks, 0)
+    starts = ends - blocks
+    idx = torch.arange(n, device=cu_seqlens.device)
+    seq = torch.searchsorted(ends, idx, right=True)
+    valid = seq < B
+    seqc = seq.clamp(max=B - 1)
+    qb = idx - starts[seqc]
+    # heaviest (latest) query blocks first: better tail behaviour under causal masking
+    info = torch.stack([torch.where(valid, seqc, torch.full_like(seqc, -1)), qb], dim=1)
+    order = torch.argsort(torch.where(valid, qb, torch.full_like(qb, -1)), descending=True, stable=True)
+    return info[order].to(torch.int32).contiguous()
+
+
+def attention_fwd(q, k, v, cu_seqlens, causal=True, scale=None, tile_info=None, out=None):
+    """Kernel forward; returns (o, lse). q/k/v may be strided slices of a fused projection."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        return attention_ref(q, k, v, cu_seqlens, causal, scale)
+    for t in (q, k, v):
+        assert t.stride(2) == 1 and t.stride(1) == D and t.dtype == torch.bfloat16
+    if tile_info is None:
+        tile_info = attn_tile_table(cu_seqlens, T)
+    o = out if out is not None else torch.empty(T, Hq, D, device=q.device, dtype=q.dtype)
+    lse = torch.empty(Hq, T, device=q.device, dtype=torch.float32)
+    cu = cu_seqlens.to(torch.int32)
+    rc = _L().ab2_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), cu.data_ptr(),
+                           tile_info.data_ptr(), tile_info.shape[0], T, Hq, Hkv, D, q.stride(0), k.stride(0),
+                           v.stride(0), o.stride(0), scale, int(causal), _s())
+    _lib.check(rc, "ab2_attn_fwd")
+    return o, lse
+
+
+def attention_bwd_ref(q, k, v, o, lse, do, cu_seqlens, causal, scale):
+    """Reference backward (recomputes probabilities from lse), fp32 math, per sequence."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    rep = Hq // Hkv
+    dq = torch.zeros_like(q, dtype=torch.float32)
+    dk = torch.zeros_like(k, dtype=torch.float32)
+    dv = torch.zeros_like(v, dtype=torch.float32)
+    cu = cu_seqlens.tolist()
+    for i in range(len(cu) - 1):
+        a, b = cu[i], cu[i + 1]
+        if b <= a:
+            continue
+        L = b - a
+        qi = q[a:b].float().transpose(0, 1)
+        ki = k[a:b].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        vi = v[a:b].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        doi = do[a:b].float().transpose(0, 1)
+        oi = o[a:b].float().transpose(0, 1)
+        s = qi @ ki.transpose(1, 2) * scale
+        if causal:
+            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            s = s.masked_fill(~mask, float("-inf"))
+        p = torch.exp(s - lse[:, a:b].unsqueeze(-1))
+        dvi = p.transpose(1, 2) @ doi
+        dp = doi @ vi.transpose(1, 2)
+        delta = (doi * oi).sum(-1, keepdim=True)
+        ds = p * (dp - delta) * scale
+        dq[a:b] = (ds @ ki).transpose(0, 1)
+        dki = ds.transpose(1, 2) @ qi
+        dk[a:b] = dki.view(Hkv, rep, L, D).sum(1).transpose(0, 1)
+        dv[a:b] = dvi.view(Hkv, rep, L, D).sum(1).transpose(0, 1)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
+_ATTN_BWD_IMPL = None  # installed by areal_b200.ops.attention_bwd once the kernel is loaded
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, causal, scale, tile_info):
+        o, lse = attention_fwd(q, k, v, cu_seqlens, causal, scale, tile_info)
+        ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
+        ctx.causal, ctx.scale, ctx.tile_info = causal, scale, tile_info
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, cu = ctx.saved_tensors
+        do = do.contiguous()
+        if _ATTN_BWD_IMPL is not None:
+            dq, dk, dv = _ATTN_BWD_IMPL(q, k, v, o, lse, do, cu, ctx.causal, ctx.scale, ctx.tile_info)
+        else:
+            dq, dk, dv = attention_bwd_ref(q, k, v, o, lse, do, cu, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None, None, None
+
+
+def attention(q, k, v, cu_seqlens, causal=True, scale=None, tile_info=None):
+    """Differentiable packed varlen attention. q: [T,Hq,D]; k,v: [T,Hkv,D]."""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        # autograd through the reference math
+        T, Hq, _ = q.shape
+        Hkv = k.shape[1]
+        rep = Hq // Hkv
+        outs = []
+        cu = cu_seqlens.tolist()
+        for i in range(len(cu) - 1):
+            a, b = cu[i], cu[i + 1]
+            if b <= a:
+                continue
+            qi = q[a:b].transpose(0, 1)
+            ki = k[a:b].transpose(0, 1).repeat_interleave(rep, dim=0)
+            vi = v[a:b].transpose(0, 1).repeat_interleave(rep, dim=0)
+            oi = F.scaled_dot_product_attention(qi[None], ki[None], vi[None], is_causal=causal, scale=scale)[0]
+            outs.append(oi.transpose(0, 1))
+        return torch.cat(outs, dim=0) if outs else torch.zeros_like(q)
+    return _Attention.apply(q, k, v, cu_seqlens, causal, scale, tile_info)
+
+
+# ----------------------------------------------------------------------------- logprob / entropy
+def logprob_entropy_ref(logits, labels, temperature=1.0):
+    z = logits.float() / temperature
+    lp = torch.log_softmax(z, dim=-1)
+    logp = lp.gather(-1, labels.long().unsqueeze(-1)).squeeze(-1)
+    ent = -(lp.exp() * lp).sum(-1)
+    return logp, ent
+
+
+def logprob_entropy_from_logits(logits: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
+    """(logp, entropy, lse) per row from fp32 logits; no autograd."""
+    if not logits.is_cuda:
+        logp, ent = logprob_entropy_ref(logits, labels, temperature)
+        return logp, ent, torch.logsumexp(logits.float() / temperature, -1)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    rows, V = logits.shape
+    logp = torch.empty(rows, device=logits.device, dtype=torch.float32)
+    ent = torch.empty_like(logp)
+    lse = torch.empty_like(logp)
+    lab = labels.to(torch.int32).contiguous()
+    rc = _L().ab2_logprob_fwd(logits.data_ptr(), lab.data_ptr(), logp.data_ptr(), ent.data_ptr(), lse.data_ptr(), None,
+                              rows, V, logits.stride(0), temperature, 0, 0, _s())
+    _lib.check(rc, "ab2_logprob_fwd")
+    return logp, ent, lse
+
+
+class _LMHeadLogprob(torch.autograd.Function):
+    """Chunked LM head + log-softmax gather + entropy without keeping ``[T, V]`` alive.
+
+    Forward: per chunk of rows, logits = h @ W^T (fp32 out) -> per-row (logp, entropy, lse).
+    Backward: logits are recomputed per chunk, turned in one pass into bf16 dlogits, and fed
+    to the dgrad / wgrad GEMMs (wgrad accumulates in fp32)."""
+
+    @staticmethod
+    def forward(ctx, h, W, labels, temperature, chunk):
+        T, H = h.shape
+        V = W.shape[0]
+        logp = torch.empty(T, device=h.device, dtype=torch.float32)
+        ent = torch.empty_like(logp)
+        lse = torch.empty_like(logp)
+        lab = labels.to(torch.int32).contiguous()
+        Vp = (V + 3) // 4 * 4
+        buf = torch.empty(min(chunk, T), Vp, device=h.device, dtype=torch.float32)
+        for a in range(0, T, chunk):
+            b = min(T, a + chunk)
+            lg = buf[: b - a, :V] if Vp == V else buf[: b - a]
+            out = buf[: b - a].as_strided((b - a, V), (Vp, 1))
+            gemm(h[a:b], W, out=out, epi=EPI_F32)
+            rc = _L().ab2_logprob_fwd(out.data_ptr(), lab[a:b].data_ptr(), logp[a:b].data_ptr(), ent[a:b].data_ptr(),
+                                      lse[a:b].data_ptr(), None, b - a, V, Vp, temperature, 0, 0, _s())
+            _lib.check(rc, "ab2_logprob_fwd")
+        ctx.save_for_backward(h, W, lab, lse, ent)
+        ctx.temperature, ctx.chunk = temperature, chunk
+        return logp, ent
+
+    @staticmethod
+    def backward(ctx, g_logp, g_ent):
+        h, W, lab, lse, ent = ctx.saved_tensors
+        T, H = h.shape
+        V = W.shape[0]
+        chunk = ctx.chunk
+        Vp = (V + 7) // 8 * 8
+        buf = torch.empty(min(chunk, T), Vp, device=h.device, dtype=torch.float32)
+        dbuf = torch.zeros(min(chunk, T), Vp, device=h.device, dtype=torch.bfloat16)
+        g_logp = g_logp.contiguous().float() if g_logp is not None else None
+        g_ent = g_ent.contiguous().float() if g_ent is not None else None
+        dh = torch.empty_like(h) if ctx.needs_input_grad[0] else None
+        mg = getattr(W, "main_grad", None)
+        dW = None
+        if ctx.needs_input_grad[1]:
+            dW = mg if mg is not None else torch.zeros(V, H, device=h.device, dtype=torch.float32)
+        for a in range(0, T, chunk):
+            b = min(T, a + chunk)
+            n = b - a
+            out = buf[:n].as_strided((n, V), (Vp, 1))
+            gemm(h[a:b], W, out=out, epi=EPI_F32)
+            dl = dbuf[:n].as_strided((n, V), (Vp, 1))
+            rc = _L().ab2_logprob_bwd(out.data_ptr(), lab[a:b].data_ptr(), lse[a:b].data_ptr(), ent[a:b].data_ptr(),
+                                      _lib.ptr(g_logp[a:b]) if g_logp is not None else None,
+                                      _lib.ptr(g_ent[a:b]) if g_ent is not None else None, dl.data_ptr(), n, V, Vp,
+                                      Vp, ctx.temperature, 0, _s())
+            _lib.check(rc, "ab2_logprob_bwd")
+            if dh is not None:
+                gemm(dl, W, b_mn=True, out=dh[a:b])
+            if dW is not None:
+                gemm(dl, h[a:b], a_mn=True, b_mn=True, out=dW, epi=EPI_F32_ACC)
+        if dW is not None and mg is None:
+            dW = dW.to(W.dtype)
+        elif mg is not None:
+            dW = None
+        return dh, dW, None, None, None
+
+
+def lm_head_logprob(h: torch.Tensor, W: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                    chunk: int = 2048):
+    """Per-token ``(logp[label], entropy)`` of ``softmax(h @ W^T / temperature)``.
+
+    Mirrors the chunked ``gather_logprobs_entropy`` of the reference
+    (areal/utils/functional/vocab_parallel.py:16-82) but folds the LM-head GEMM in, so the
+    full ``[T, V]`` logits never exist."""
+    if not h.is_cuda:
+        outs_lp, outs_e = [], []
+        for a in range(0, h.shape[0], chunk):
+            lg = F.linear(h[a:a + chunk], W)
+            lp, e = logprob_entropy_ref(lg, labels[a:a + chunk], temperature)
+            outs_lp.append(lp)
+            outs_e.append(e)
+        return torch.cat(outs_lp), torch.cat(outs_e)
+    return _LMHeadLogprob.apply(h.contiguous(), W, labels, float(temperature), int(chunk))
+
+
+# ----------------------------------------------------------------------------- optimizer pieces
+def sqnorm_accumulate_(x: torch.Tensor, state: torch.Tensor) -> None:
+    """state[0] += sum(x^2) for a flat fp32 tensor (device-side, no sync)."""
+    if not x.is_cuda:
+        state[0] += x.float().pow(2).sum()
+        return
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _lib.check(_L().ab2_sqnorm_f32(x.data_ptr(), x.numel(), state.data_ptr(), _s()), "ab2_sqnorm_f32")
+
+
+def clip_coef_(state: torch.Tensor, max_norm: float, inv_scale: float = 1.0) -> None:
+    """From state[0] = sum of squares: state[1] = grad multiplier, state[2] = finite flag,
+    state[3] = norm."""
+    if not state.is_cuda:
+        norm = math.sqrt(float(state[0])) * inv_scale if math.isfinite(float(state[0])) else float("nan")
+        finite = math.isfinite(norm)
+        coef = inv_scale
+        if max_norm > 0 and finite and norm > max_norm:
+            coef = inv_scale * max_norm / (norm + 1e-6)
+        state[1] = coef if finite else 0.0
+        state[2] = 1.0 if finite else 0.0
+        state[3] = norm
+        return
+    _lib.check(_L().ab2_clip_coef(state.data_ptr(), max_norm, inv_scale, _s()), "ab2_clip_coef")
+
+
+def adamw_step_(p32, m, v, g, p_bf16, state, lr, beta1, beta2, eps, wd, step) -> None:
+    """Fused decoupled-weight-decay Adam on flat buffers; reads the clip coefficient and the
+    skip flag from ``state`` on the device; also refreshes the bf16 compute copy."""
+    if not p32.is_cuda:
+        coef = float(state[1]) if state is not None else 1.0
+        go = (float(state[2]) != 0.0) if state is not None else True
+        if not go:
+            return
+        gi = g.float() * coef
+        m.mul_(beta1).add_(gi, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(gi, gi, value=1 - beta2)
+        bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
+        p32.mul_(1 - lr * wd)
+        p32.addcdiv_(m / bc1, (v / bc2).sqrt() + eps, value=-lr)
+        if p_bf16 is not None:
+            p_bf16.copy_(p32.to(p_bf16.dtype))
+        return
+    assert p32.is_contiguous() and m.is_contiguous() and v.is_contiguous() and g.is_contiguous()
+    rc = _L().ab2_adamw(p32.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), int(g.dtype == torch.bfloat16),
+                        _lib.ptr(p_bf16), _lib.ptr(state), p32.numel(), lr, beta1, beta2, eps, wd, int(step), _s())
+    _lib.check(rc, "ab2_adamw")

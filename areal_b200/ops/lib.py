@@ -1,0 +1,118 @@
+"""ctypes binding of the in-tree sm_100a kernel library (``libab2_kernels.so``).
+
+The library has a plain C ABI (raw device pointers + a CUDA stream handle). It is built
+by :mod:`areal_b200.ops.build`. On a machine with a GPU a missing or unloadable library is
+a hard error: no op silently falls back to PyTorch on CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+_LIB_PATH = Path(__file__).resolve().parent / "libab2_kernels.so"
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+
+_SIGS = {
+    "ab2_kernel_error": ([], c_int),
+    "ab2_runtime_init": ([], c_int),
+    "ab2_num_sms": ([], c_int),
+    "ab2_gemm_bf16": ([c_void_p] * 4 + [c_int] * 10 + [c_void_p], c_int),
+    "ab2_rmsnorm_fwd": ([c_void_p] * 6 + [c_int, c_int, c_float, c_void_p], c_int),
+    "ab2_rmsnorm_bwd": ([c_void_p] * 7 + [c_int, c_int, c_void_p], c_int),
+    "ab2_rope": ([c_void_p] * 4 + [c_int, c_int, c_int, c_ll, c_int, c_void_p], c_int),
+    "ab2_swiglu_fwd": ([c_void_p, c_void_p, c_ll, c_int, c_void_p], c_int),
+    "ab2_swiglu_bwd": ([c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p], c_int),
+    "ab2_embed_fwd": ([c_void_p] * 3 + [c_int] * 3 + [c_void_p], c_int),
+    "ab2_embed_bwd": ([c_void_p] * 3 + [c_int] * 3 + [c_void_p], c_int),
+    "ab2_sqnorm_f32": ([c_void_p, c_ll, c_void_p, c_void_p], c_int),
+    "ab2_clip_coef": ([c_void_p, c_float, c_float, c_void_p], c_int),
+    "ab2_adamw": ([c_void_p] * 4 + [c_int, c_void_p, c_void_p, c_ll] + [c_float] * 5 + [c_int, c_void_p], c_int),
+    "ab2_logprob_fwd": ([c_void_p] * 6 + [c_int, c_int, c_ll, c_float, c_int, c_int, c_void_p], c_int),
+    "ab2_logprob_bwd": ([c_void_p] * 7 + [c_int, c_int, c_ll, c_ll, c_float, c_int, c_void_p], c_int),
+    "ab2_logprob_combine": ([c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "ab2_attn_fwd": ([c_void_p] * 7 + [c_int] * 5 + [c_ll] * 4 + [c_float, c_int, c_void_p], c_int),
+}
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    """True when CUDA is usable and the kernel library can be loaded."""
+    if not torch.cuda.is_available():
+        return False
+    try:
+        get_lib()
+        return True
+    except KernelLibraryError:
+        return False
+
+
+def get_lib():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        if not _LIB_PATH.exists():
+            try:
+                from . import build as _build
+
+                _build.build()
+            except Exception as e:  # pragma: no cover - build environment specific
+                raise KernelLibraryError(f"kernel library missing and build failed: {e}") from e
+        try:
+            lib = ctypes.CDLL(str(_LIB_PATH))
+        except OSError as e:
+            raise KernelLibraryError(f"cannot load {_LIB_PATH}: {e}") from e
+        for name, (args, res) in _SIGS.items():
+            try:
+                fn = getattr(lib, name)
+            except AttributeError:
+                continue  # optional symbol from a newer source file; checked at call time
+            fn.argtypes = args
+            fn.restype = res
+        _LIB = lib
+    return _LIB
+
+
+def declare(name: str, argtypes, restype=c_int) -> None:
+    """Registers the signature of an additional exported symbol."""
+    _SIGS[name] = (argtypes, restype)
+    if _LIB is not None and hasattr(_LIB, name):
+        fn = getattr(_LIB, name)
+        fn.argtypes, fn.restype = argtypes, restype
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelLibraryError(f"{what} failed with code {rc}")
+
+
+def kernel_error() -> int:
+    """Synchronises and returns (then clears) the device-side error word: 0 means every
+    bounded wait completed; non-zero identifies the wait that gave up."""
+    return int(get_lib().ab2_kernel_error())

@@ -1,0 +1,204 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+from areal_b200.ops import functional as OF
+from areal_b200.ops import lib as oplib
+
+pytestmark = pytest.mark.gpu
+
+
+def _no_kernel_error():
+    assert oplib.kernel_error() == 0
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 200, 136), (1024, 4096, 1024), (64, 6144, 4096)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need the contiguous dim to be a multiple of 8")
+    torch.manual_seed(0)
+    dev = "cuda"
+    A = torch.randn(M, K, device=dev).bfloat16()
+    B = torch.randn(N, K, device=dev).bfloat16()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    ref = A.float() @ B.float().t()
+    out = OF.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    _no_kernel_error()
+    assert _rel_err(out, ref) < 1e-2
+    out32 = OF.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=OF.EPI_F32)
+    assert _rel_err(out32, ref) < 2e-3
+    acc = torch.ones(M, N, device=dev)
+    OF.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, epi=OF.EPI_F32_ACC)
+    assert _rel_err(acc, ref + 1) < 2e-3
+    R = torch.randn(M, N, device=dev).bfloat16()
+    outr = OF.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=OF.EPI_BF16_RESID, resid=R)
+    assert _rel_err(outr, ref + R.float()) < 1e-2
+    _no_kernel_error()
+
+
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+def test_gemm_tile_widths(bn):
+    torch.manual_seed(1)
+    A = torch.randn(384, 512, device="cuda").bfloat16()
+    B = torch.randn(640, 512, device="cuda").bfloat16()
+    out = OF.gemm(A, B, bn=bn)
+    _no_kernel_error()
+    assert _rel_err(out, A.float() @ B.float().t()) < 1e-2
+
+
+def test_linear_autograd():
+    torch.manual_seed(2)
+    x = torch.randn(512, 256, device="cuda").bfloat16().requires_grad_()
+    w = torch.randn(384, 256, device="cuda").bfloat16().requires_grad_()
+    y = OF.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    (xr @ wr.t()).backward(g.float())
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+    _no_kernel_error()
+
+
+@pytest.mark.parametrize("H", [128, 1536, 4096, 8192])
+def test_rmsnorm(H):
+    torch.manual_seed(3)
+    x = torch.randn(300, H, device="cuda").bfloat16().requires_grad_()
+    r = torch.randn(300, H, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_()
+    y, res = OF.rmsnorm(x, w, 1e-6, r)
+    gy, gr = torch.randn_like(y), torch.randn_like(res)
+    (y.float() * gy.float()).sum().add((res.float() * gr.float()).sum()).backward()
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    s = (xr + rr).bfloat16().float() + (xr + rr - (xr + rr).detach())  # bf16-rounded stream, fp32 grads
+    yr = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    ((yr * gy.float()).sum() + (s * gr.float()).sum()).backward()
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+    assert _rel_err(r.grad, rr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+def test_rope_roundtrip_and_ref():
+    torch.manual_seed(4)
+    T, h, D = 257, 6, 128
+    x = torch.randn(T, h, D, device="cuda").bfloat16()
+    pos = torch.randint(0, 1000, (T,), device="cuda", dtype=torch.int32)
+    cos, sin = OF.rope_tables(1024, D, 1e6, "cuda")
+    y = OF.rope(x, pos, cos, sin)
+    assert _rel_err(y, OF.rope_ref(x, pos.long(), cos, sin)) < 1e-2
+    xg = x.clone().requires_grad_()
+    OF.rope(xg, pos, cos, sin).backward(y)
+    assert _rel_err(xg.grad, x) < 2e-2  # inverse rotation recovers the input
+
+
+def test_swiglu():
+    torch.manual_seed(5)
+    gu = torch.randn(333, 2 * 688, device="cuda").bfloat16().requires_grad_()
+    o = OF.swiglu(gu)
+    g = torch.randn_like(o)
+    o.backward(g)
+    gr = gu.detach().float().requires_grad_()
+    I = 688
+    orf = torch.nn.functional.silu(gr[:, :I]) * gr[:, I:]
+    orf.backward(g.float())
+    assert _rel_err(o, orf) < 1e-2
+    assert _rel_err(gu.grad, gr.grad) < 1e-2
+
+
+def test_embedding():
+    torch.manual_seed(6)
+    W = torch.randn(1000, 256, device="cuda").bfloat16().requires_grad_()
+    ids = torch.randint(0, 1000, (777,), device="cuda")
+    o = OF.embedding(ids, W)
+    assert torch.equal(o, W.detach()[ids])
+    g = torch.randn_like(o)
+    o.backward(g)
+    ref = torch.zeros(1000, 256, device="cuda").index_add_(0, ids, g.float())
+    assert _rel_err(W.grad, ref) < 1e-2
+
+
+def test_adamw_and_clip():
+    torch.manual_seed(7)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda") * 3
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr = p.clone().requires_grad_()
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    state = torch.zeros(4, device="cuda")
+    for step in range(1, 4):
+        state.zero_()
+        OF.sqnorm_accumulate_(g, state)
+        OF.clip_coef_(state, 1.0)
+        OF.adamw_step_(p, m, v, g, pb, state, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+        pr.grad = g.clone()
+        torch.nn.utils.clip_grad_norm_([pr], 1.0)
+        opt.step()
+    assert abs(state[3].item() - g.norm().item()) / g.norm().item() < 1e-4
+    assert _rel_err(p, pr.detach()) < 1e-5
+    assert _rel_err(pb, pr.detach()) < 1e-2
+
+
+@pytest.mark.parametrize("V", [1024, 151936, 1001])
+def test_logprob_entropy(V):
+    torch.manual_seed(8)
+    T = 37
+    logits = torch.randn(T, V, device="cuda") * 3
+    labels = torch.randint(0, V, (T,), device="cuda")
+    if V % 4:
+        pytest.skip("row stride must be a multiple of 4 floats")
+    lp, ent, lse = OF.logprob_entropy_from_logits(logits, labels, 0.7)
+    lpr, entr = OF.logprob_entropy_ref(logits, labels, 0.7)
+    assert (lp - lpr).abs().max().item() < 1e-3
+    assert (ent - entr).abs().max().item() < 1e-3
+
+
+def test_lm_head_logprob_autograd():
+    torch.manual_seed(9)
+    T, H, V = 300, 256, 1024
+    h = (torch.randn(T, H, device="cuda") * 0.5).bfloat16().requires_grad_()
+    W = (torch.randn(V, H, device="cuda") * 0.1).bfloat16().requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    lp, ent = OF.lm_head_logprob(h, W, labels, 1.0, chunk=128)
+    gl, ge = torch.randn(T, device="cuda"), torch.randn(T, device="cuda") * 0.1
+    ((lp * gl).sum() + (ent * ge).sum()).backward()
+    hr, Wr = h.detach().float().requires_grad_(), W.detach().float().requires_grad_()
+    lpr, entr = OF.logprob_entropy_ref(hr @ Wr.t(), labels, 1.0)
+    ((lpr * gl).sum() + (entr * ge).sum()).backward()
+    assert (lp - lpr).abs().max().item() < 2e-2
+    assert (ent - entr).abs().max().item() < 2e-2
+    assert _rel_err(h.grad, hr.grad) < 3e-2
+    assert _rel_err(W.grad, Wr.grad) < 3e-2
+    _no_kernel_error()
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_fwd(D, causal):
+    torch.manual_seed(10)
+    lens = [1, 130, 257, 128, 515, 64]
+    T = sum(lens)
+    Hq, Hkv = 4, 2
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D: (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    o, lse = OF.attention_fwd(q, k, v, cu, causal)
+    _no_kernel_error()
+    orf, lser = OF.attention_ref(q, k, v, cu, causal)
+    assert _rel_err(o, orf) < 2e-2
+    assert (lse - lser).abs().max().item() < 2e-2
