@@ -1,0 +1,621 @@
+"""The training engine: a :class:`~areal_b200.models.decoder.CausalLM` on packed micro-batches
+with ZeRO-style sharded optimisation over data-parallel (and Ulysses sequence-parallel)
+ranks, implementing the :class:`~areal_b200.api.engine_api.TrainEngine` contract.
+
+Call flow of ``train_batch`` (reference: ``areal/engine/fsdp_engine.py:774``,
+``_prepare_mb_list`` :1883, ``_compute_logprobs_and_loss`` :2147, ``optimizer_step`` :696):
+
+  split by token budget -> pad to pages -> global loss weight (all-reduce) ->
+  per micro-batch: forward, fused LM-head logprob/entropy, user loss, scaled backward
+  (weight gradients accumulate in fp32 ``main_grad``) ->
+  gradient reduce-scatter -> global norm / clip -> sharded AdamW -> parameter all-gather.
+
+Algorithm-specific engines (PPO actor / critic, SFT, RW, DPO) are thin mix-ins at the bottom,
+mirroring ``FSDPPPOActor`` etc. (fsdp_engine.py:2257-2476).
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+from datetime import timedelta
+from typing import Any, Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..api.alloc_mode import FSDPParallelStrategy, ModelAllocation, ParallelStrategy
+from ..api.cli_args import MicroBatchSpec, TrainEngineConfig
+from ..api.engine_api import InferenceEngine, TrainEngine
+from ..api.io_struct import FinetuneSpec, SaveLoadMeta, WeightUpdateMeta
+from ..models import hf_io
+from ..models.config import ModelConfig, preset
+from ..models.decoder import CausalLM, PackedBatch, build_model
+from ..utils import data as D
+from ..utils import logging as alog
+from ..utils import stats_tracker
+from .flat_params import FlatParamStore
+from .optimizer import ShardedAdamW
+
+logger = alog.getLogger("train_engine")
+
+DIST_TIMEOUT_S = 7200
+
+
+def _dtype_of(name: str):
+    return {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[name]
+
+
+class B200TrainEngine(TrainEngine):
+    def __init__(self, config: TrainEngineConfig):
+        self.config = config
+        self.model: Optional[CausalLM] = None
+        self.model_config: Optional[ModelConfig] = None
+        self.store: Optional[FlatParamStore] = None
+        self.optimizer: Optional[ShardedAdamW] = None
+        self.parallel: Optional[ParallelStrategy] = None
+        self.device = torch.device("cpu")
+        self.rank = 0
+        self.world_size = 1
+        self._version = 0
+        self._dp_group = None
+        self._sp_group = None
+        self._cpu_group = None
+        self._own_pg = False
+        self.rollout_engine: Optional[InferenceEngine] = None
+        self.weight_update_meta: Optional[WeightUpdateMeta] = None
+        self._initialized = False
+        self._weight_pusher = None
+        self._grad_reducer = None
+        self.last_step_stats: dict = {}
+
+    # ------------------------------------------------------------------ process groups
+    def create_process_group(self, parallel_strategy: Optional[ParallelStrategy] = None):
+        use_cuda = torch.cuda.is_available() and os.environ.get("AREAL_FORCE_CPU", "0") != "1"
+        if parallel_strategy is None and self.config.backend:
+            parallel_strategy = ModelAllocation.from_str(self.config.backend).parallel
+        self.parallel = parallel_strategy or FSDPParallelStrategy()
+        env_world = int(os.environ.get("WORLD_SIZE", "1"))
+        if not dist.is_initialized() and env_world > 1:
+            backend = "nccl" if use_cuda else "gloo"
+            if use_cuda:
+                torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+            dist.init_process_group(backend=backend, timeout=timedelta(seconds=DIST_TIMEOUT_S))
+            self._own_pg = True
+        if dist.is_initialized():
+            self.rank, self.world_size = dist.get_rank(), dist.get_world_size()
+        if use_cuda:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        p = self.parallel
+        if getattr(self, "_train_ranks", None) is None:
+            self._train_ranks = list(range(self.world_size))
+        n = len(self._train_ranks)
+        if p.world_size != n:
+            if p.world_size == 1 and n > 1:  # bare config: everything data-parallel
+                self.parallel = p = FSDPParallelStrategy(data_parallel_size=n)
+            else:
+                raise ValueError(f"parallel strategy {p} needs {p.world_size} ranks, engine has {n}")
+        if p.tp_size > 1 or p.pp_size > 1:
+            raise NotImplementedError("tensor/pipeline parallel training is provided by parallel.tp / parallel.pp")
+        self.sp_size, self.dp_size = p.cp_size, p.dp_size
+        self.local_index = self._train_ranks.index(self.rank) if self.rank in self._train_ranks else -1
+        self.sp_rank = self.local_index % self.sp_size
+        self.dp_rank = self.local_index // self.sp_size
+        if dist.is_initialized() and n > 1:
+            self._shard_group = dist.new_group(self._train_ranks) if n != self.world_size else dist.group.WORLD
+            # sp groups: consecutive ranks; dp groups: strided
+            for d in range(self.dp_size):
+                ranks = [self._train_ranks[d * self.sp_size + s] for s in range(self.sp_size)]
+                g = dist.new_group(ranks) if self.sp_size > 1 else None
+                if d == self.dp_rank:
+                    self._sp_group = g
+            for s in range(self.sp_size):
+                ranks = [self._train_ranks[d * self.sp_size + s] for d in range(self.dp_size)]
+                g = dist.new_group(ranks) if self.dp_size > 1 else None
+                if s == self.sp_rank:
+                    self._dp_group = g
+            self._cpu_group = dist.new_group(self._train_ranks, backend="gloo") if use_cuda else self._shard_group
+            # warm the groups up so the first real collective does not pay connection setup
+            t = torch.zeros(1, device=self.device)
+            dist.all_reduce(t, group=self._shard_group)
+        else:
+            self._shard_group = None
+        return self
+
+    def set_train_ranks(self, ranks: list[int]):
+        """Restricts the engine to a subset of the global ranks (trainer/rollout split)."""
+        self._train_ranks = list(ranks)
+
+    # ------------------------------------------------------------------ init
+    def initialize(self, addr: Optional[str] = None, ft_spec: Optional[FinetuneSpec] = None,
+                   model_config: Optional[ModelConfig] = None, **kwargs):
+        cfg = self.config
+        if self.parallel is None:
+            self.create_process_group()
+        dtype = _dtype_of(cfg.dtype)
+        if not self.device.type == "cuda" and dtype != torch.float32:
+            dtype = torch.float32  # CPU reference path computes in fp32
+        if model_config is None:
+            if cfg.model_config:
+                mc = dict(cfg.model_config)
+                model_config = preset(mc.pop("preset"), **mc) if "preset" in mc else ModelConfig(**mc)
+            elif cfg.path and os.path.isdir(cfg.path):
+                model_config = ModelConfig.from_pretrained(cfg.path)
+            else:
+                raise ValueError("no model architecture: give model_config, config.model_config or a checkpoint path")
+        if cfg.is_critic:
+            model_config.is_critic = True
+            model_config.tie_word_embeddings = False
+        self.model_config = model_config
+        seed = kwargs.get("seed", 1)
+        t0 = time.time()
+        self.model = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
+        self.model.gradient_checkpointing = cfg.gradient_checkpointing
+        if not cfg.init_from_scratch and cfg.path and os.path.isdir(cfg.path) and \
+                any(f.endswith(".safetensors") for f in os.listdir(cfg.path)):
+            hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
+        n_shards = len(self._train_ranks) if self._shard_group is not None else 1
+        shard_rank = self.local_index if n_shards > 1 else 0
+        alloc = self._symmetric_alloc if (n_shards > 1 and self.device.type == "cuda" and cfg.fsdp.fuse_reduce_scatter_adamw) else None
+        self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc, alloc_grad=alloc,
+                                    with_grads=cfg.optimizer is not None)
+        if n_shards > 1:
+            # identical initial weights everywhere (rank 0 of the trainer group is the source)
+            dist.broadcast(self.store.flat_param, src=self._train_ranks[0], group=self._shard_group)
+        if cfg.optimizer is not None:
+            total = ft_spec.total_train_steps if ft_spec is not None else 1
+            self.optimizer = ShardedAdamW(self.store, cfg.optimizer, total_steps=total, group=self._shard_group)
+        if self.sp_size > 1:
+            from ..parallel.ulysses import install_ulysses
+
+            install_ulysses(self.model, self._sp_group, self.sp_size, self.sp_rank)
+        if alloc is not None:
+            from ..parallel.fused_zero import FusedGradReducer
+
+            self._grad_reducer = FusedGradReducer(self.store, self._shard_group, self._symm_handles)
+        self._initialized = True
+        logger.info("initialised %s: %.2fB params, dtype %s, dp=%d sp=%d, %.1fs", model_config.arch,
+                    model_config.num_params() / 1e9, dtype, self.dp_size, self.sp_size, time.time() - t0)
+        return self
+
+    _symm_handles: dict = {}
+
+    def _symmetric_alloc(self, n: int, dtype, device):
+        """Allocates a buffer every trainer rank can address (peer pointers) for the fused
+        reduce-scatter / parameter write-back kernels."""
+        from ..parallel.symm import symm_empty
+
+        t, hdl = symm_empty(n, dtype, device, self._shard_group)
+        t.zero_()
+        self._symm_handles = dict(self._symm_handles)
+        self._symm_handles[t.data_ptr()] = hdl
+        return t
+
+    def destroy(self):
+        self.model = None
+        self.store = None
+        self.optimizer = None
+        if self._own_pg and dist.is_initialized():
+            try:
+                dist.destroy_process_group()
+            except Exception:
+                pass
+        self._initialized = False
+
+    # ------------------------------------------------------------------ topology
+    @property
+    def data_parallel_group(self):
+        return self._dp_group
+
+    @property
+    def data_parallel_rank(self) -> int:
+        return self.dp_rank
+
+    @property
+    def data_parallel_world_size(self) -> int:
+        return self.dp_size
+
+    def current_data_parallel_head(self) -> int:
+        return self._train_ranks[self.dp_rank * self.sp_size]
+
+    def is_data_parallel_head(self) -> bool:
+        return self.sp_rank == 0
+
+    @property
+    def context_and_model_parallel_group(self):
+        return self._sp_group
+
+    @property
+    def cpu_group(self):
+        return self._cpu_group
+
+    # ------------------------------------------------------------------ modes / versions
+    def train(self, mode: bool = True):
+        self.model.train(mode)
+        return self
+
+    def set_version(self, version: int):
+        self._version = version
+
+    def get_version(self) -> int:
+        return self._version
+
+    # ------------------------------------------------------------------ micro-batches
+    def _align(self) -> int:
+        base = D.N_TOKENS_PER_PAGE if self.device.type == "cuda" else 1
+        return base * self.sp_size if self.sp_size > 1 and base % self.sp_size else max(base, self.sp_size)
+
+    def _prepare_mb_list(self, input_: dict[str, Any]) -> D.MicroBatchList:
+        assert "attention_mask" in input_ and "input_ids" in input_, "expected a padded batch"
+        input_ = D.amend_position_ids(dict(input_))
+        mbl = D.split_padded_tensor_dict_into_mb_list(input_, self.config.mb_spec, group=self._cpu_group if self.dp_size > 1 else None)
+        D.pad_mb_list(mbl, pad_to_maximum=self.config.pad_to_maximum, max_tokens=self.config.mb_spec.max_tokens_per_mb,
+                      align=self._align())
+        return mbl
+
+    def _mb_to_device(self, mb: dict[str, Any]) -> dict[str, Any]:
+        out = {}
+        for k, v in mb.items():
+            if torch.is_tensor(v):
+                if v.device != self.device:
+                    v = v.pin_memory() if (self.device.type == "cuda" and not v.is_pinned() and v.numel() > 0) else v
+                    v = v.to(self.device, non_blocking=True)
+                out[k] = v
+            else:
+                out[k] = v
+        return out
+
+    def _forward_mb(self, mb: dict[str, Any]):
+        """Runs the model on one padded packed micro-batch (already on the device). Returns
+        hidden states for the local sequence-parallel slice plus the matching labels."""
+        ids = mb["input_ids"].to(torch.int32) if self.device.type == "cuda" else mb["input_ids"].long()
+        cu = mb["cu_seqlens"]
+        T = ids.shape[0]
+        pos = mb.get("position_ids")
+        if pos is None or pos.shape[0] != T:
+            pos = D.positions_from_cu_seqlens(cu, T)
+        labels = torch.roll(ids, shifts=-1, dims=0)
+        pb = PackedBatch(cu, pos, T, int(mb.get("max_seqlen", 0)))
+        if self.sp_size > 1:
+            chunk = T // self.sp_size
+            sl = slice(self.sp_rank * chunk, (self.sp_rank + 1) * chunk)
+            pb_local = PackedBatch(cu, pos[sl], T, pb.max_seqlen)
+            pb_local.tile_info = pb.tile_info
+            hidden = self.model.forward_hidden(ids[sl], pb_local)
+            return hidden, labels[sl], sl
+        hidden = self.model.forward_hidden(ids, pb)
+        return hidden, labels, slice(0, T)
+
+    # ------------------------------------------------------------------ train / eval / forward
+    def optimizer_zero_grad(self):
+        self.store.zero_grad()
+
+    def forward_backward_batch(self, mb_list: D.MicroBatchList, process_output_fn: Callable, forward_only: bool = False):
+        """Runs every micro-batch; ``process_output_fn(hidden, labels, mb, pad_len, sl)`` returns a
+        loss (training) or an output (forward only)."""
+        outs = []
+        for mb, pad in zip(mb_list.padded_mbs, mb_list.padding_lengths):
+            mbd = self._mb_to_device(mb)
+            if forward_only:
+                with torch.no_grad():
+                    hidden, labels, sl = self._forward_mb(mbd)
+                    outs.append(process_output_fn(hidden, labels, mbd, pad, sl))
+            else:
+                hidden, labels, sl = self._forward_mb(mbd)
+                loss = process_output_fn(hidden, labels, mbd, pad, sl)
+                aux = self.model.aux_loss()
+                if aux is not None:
+                    loss = loss + aux
+                loss.backward()
+                outs.append(loss.detach())
+        return outs
+
+    def _slice_mb(self, mb: dict[str, Any], sl: slice, pad: int) -> dict[str, Any]:
+        """Per-token fields restricted to the local sequence-parallel slice."""
+        T = mb["input_ids"].shape[0]
+        out = {}
+        for k, v in mb.items():
+            if torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == T and k != "cu_seqlens":
+                out[k] = v[sl]
+            else:
+                out[k] = v
+        return out
+
+    def _actor_outputs(self, hidden, labels, temperature=None):
+        t = self.config.temperature if temperature is None else temperature
+        return self.model.logprobs_entropy(hidden, labels, t, chunk=max(256, self.config.logprobs_chunk_size))
+
+    def train_batch(self, input_: dict[str, Any], loss_fn: Callable[..., torch.Tensor],
+                    loss_weight_fn: Callable[[dict[str, Any]], torch.Tensor]) -> dict[str, float]:
+        assert self.optimizer is not None, "engine was initialised without an optimizer"
+        self.model.train()
+        self.optimizer_zero_grad()
+        mbl = self._prepare_mb_list(input_)
+        weights = [float(loss_weight_fn(mb)) for mb in mbl.mbs]
+        total_w = torch.tensor([sum(weights)], dtype=torch.float64)
+        if self.dp_size > 1:
+            tw = total_w.to(self.device) if self.device.type == "cuda" and dist.get_backend(self._dp_group) == "nccl" else total_w
+            dist.all_reduce(tw, group=self._dp_group)
+            total_w = tw.cpu()
+        total_weight = float(total_w[0])
+        if total_weight <= 0:
+            raise ValueError("total loss weight is zero: nothing to train on")
+        it = iter(weights)
+
+        def process(hidden, labels, mb, pad, sl):
+            w = next(it)
+            mb_local = self._slice_mb(mb, sl, pad)
+            if self.sp_size > 1:
+                # loss_fn normalises by the *local* token count, so weight by it
+                w = float(loss_weight_fn(mb_local))
+            if self.config.is_critic:
+                loss = loss_fn(self.model.values(hidden), mb_local)
+            else:
+                logp, ent = self._actor_outputs(hidden, labels)
+                loss = loss_fn(logp, ent, mb_local)
+            # sum over ranks of (w_mb / W_total) * mean-loss_mb == global weighted mean;
+            # sequence-parallel ranks each hold a slice of the same micro-batch
+            return loss * (w / total_weight)
+
+        losses = self.forward_backward_batch(mbl, process)
+        stats = self.optimizer_step()
+        stats["loss"] = float(torch.stack(losses).sum()) if losses else 0.0
+        return stats
+
+    def optimizer_step(self) -> dict[str, float]:
+        self.store.fold_autograd_grads()
+        opt = self.optimizer
+        if self._shard_group is not None:
+            if self._grad_reducer is not None:
+                gshard = self._grad_reducer.reduce_scatter()
+            else:
+                if dist.get_backend(self._shard_group) == "nccl":
+                    gshard = torch.empty_like(self.store.grad_shard)
+                    dist.reduce_scatter_tensor(gshard, self.store.flat_grad, group=self._shard_group)
+                else:
+                    dist.all_reduce(self.store.flat_grad, group=self._shard_group)
+                    gshard = self.store.grad_shard
+        else:
+            gshard = self.store.grad_shard
+        res = opt.step(gshard)
+        if self._shard_group is not None:
+            if self._grad_reducer is not None:
+                self._grad_reducer.all_gather_params()
+            else:
+                dist.all_gather_into_tensor(self.store.flat_param, self.store.param_shard.clone(), group=self._shard_group)
+        st = res["state"].tolist()
+        self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
+        return dict(self.last_step_stats)
+
+    def lr_scheduler_step(self):
+        if self.optimizer is not None:
+            self.optimizer.lr_scheduler_step()
+
+    @torch.no_grad()
+    def eval_batch(self, input_: dict[str, Any], loss_fn: Callable, loss_weight_fn: Callable) -> Optional[torch.Tensor]:
+        self.model.eval()
+        mbl = self._prepare_mb_list(input_)
+        weights = [float(loss_weight_fn(mb)) for mb in mbl.mbs]
+        it = iter(weights)
+
+        def process(hidden, labels, mb, pad, sl):
+            w = next(it)
+            mb_local = self._slice_mb(mb, sl, pad)
+            if self.config.is_critic:
+                return loss_fn(self.model.values(hidden), mb_local) * w
+            logp, ent = self._actor_outputs(hidden, labels)
+            return loss_fn(logp, ent, mb_local) * w
+
+        outs = self.forward_backward_batch(mbl, process, forward_only=True)
+        tot = torch.stack([o.float().cpu() for o in outs]).sum().reshape(1).double()
+        w = torch.tensor([sum(weights)], dtype=torch.float64)
+        if self.dp_size > 1 and self._cpu_group is not None:
+            both = torch.cat([tot, w])
+            dist.all_reduce(both, group=self._cpu_group)
+            tot, w = both[:1], both[1:]
+        return (tot / w.clamp(min=1e-12)).float().squeeze(0)
+
+    @torch.no_grad()
+    def forward_batch(self, input_: dict[str, Any], output_seqlens: Optional[list[int]] = None,
+                      aggregate_fn: Callable = torch.cat, output: str = "logprobs", temperature: Optional[float] = None):
+        """Per-token outputs for a padded batch, returned as a padded ``[B, L]`` tensor in the
+        input order. ``output``: logprobs | entropy | values | logprobs_entropy."""
+        self.model.eval()
+        mbl = self._prepare_mb_list(input_)
+        B, L = input_["attention_mask"].shape
+
+        def process(hidden, labels, mb, pad, sl):
+            if self.config.is_critic or output == "values":
+                v = self.model.values(hidden)
+                res = (v,)
+            else:
+                logp, ent = self._actor_outputs(hidden, labels, temperature)
+                res = (logp, ent) if output == "logprobs_entropy" else ((ent,) if output == "entropy" else (logp,))
+            if self.sp_size > 1:
+                full = []
+                for r in res:
+                    parts = [torch.empty_like(r) for _ in range(self.sp_size)]
+                    dist.all_gather(parts, r.contiguous(), group=self._sp_group)
+                    full.append(torch.cat(parts))
+                res = tuple(full)
+            return tuple(D.unpad_logits(r, pad).float().cpu() for r in res)
+
+        outs = self.forward_backward_batch(mbl, process, forward_only=True)
+        n_out = len(outs[0]) if outs else 1
+        results = []
+        for j in range(n_out):
+            padded = torch.zeros(B, L, dtype=torch.float32)
+            for g, o, mb in zip(mbl.groups, outs, mbl.mbs):
+                cu = mb["cu_seqlens"].tolist()
+                for k, i in enumerate(g):
+                    n = cu[k + 1] - cu[k]
+                    padded[i, :n] = o[j][cu[k]:cu[k + 1]]
+            results.append(padded)
+        return results[0] if n_out == 1 else tuple(results)
+
+    # ------------------------------------------------------------------ save / load
+    def save(self, meta: SaveLoadMeta):
+        os.makedirs(meta.path, exist_ok=True)
+        head = self.local_index <= 0
+        if meta.weight_format == "hf":
+            if head:
+                hf_io.save_model_hf(self.model, meta.path)
+                if meta.tokenizer is not None:
+                    meta.tokenizer.save_pretrained(meta.path)
+        else:
+            from ..ckpt.sharded import save_sharded
+
+            save_sharded(self, meta.path, with_optim=meta.with_optim)
+            return
+        if meta.with_optim and self.optimizer is not None:
+            torch.save(self.optimizer.state_dict(), os.path.join(meta.path, f"optim_rank{max(self.local_index, 0)}.pt"))
+        if self._cpu_group is not None:
+            dist.barrier(group=self._cpu_group)
+
+    def load(self, meta: SaveLoadMeta):
+        if meta.weight_format == "hf":
+            hf_io.load_model_hf(self.model, meta.path, strict=not self.config.is_critic)
+        else:
+            from ..ckpt.sharded import load_sharded
+
+            load_sharded(self, meta.path, with_optim=meta.with_optim)
+            return
+        if self.optimizer is not None:
+            self.optimizer.resync_master()
+            p = os.path.join(meta.path, f"optim_rank{max(self.local_index, 0)}.pt")
+            if meta.with_optim and os.path.exists(p):
+                self.optimizer.load_state_dict(torch.load(p, map_location="cpu", weights_only=False))
+
+    # ------------------------------------------------------------------ rollout coupling
+    def connect_engine(self, engine: InferenceEngine, meta: WeightUpdateMeta):
+        self.rollout_engine = engine
+        self.weight_update_meta = meta
+        from ..wsync.service import make_weight_pusher
+
+        self._weight_pusher = make_weight_pusher(self, engine, meta)
+
+    def update_weights(self, meta: Optional[WeightUpdateMeta] = None):
+        meta = meta or self.weight_update_meta
+        if self._weight_pusher is None:
+            raise RuntimeError("connect_engine must be called before update_weights")
+        return self._weight_pusher.push(meta)
+
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None):
+        return self.rollout_engine.rollout_batch(data, workflow=workflow, workflow_kwargs=workflow_kwargs,
+                                                 should_accept_fn=should_accept_fn)
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None, dynamic_bs=False):
+        return self.rollout_engine.prepare_batch(dataloader, workflow=workflow, workflow_kwargs=workflow_kwargs,
+                                                 should_accept_fn=should_accept_fn, dynamic_bs=dynamic_bs)
+
+    # ------------------------------------------------------------------ memory
+    def offload(self):
+        """Moves parameters / optimizer state to pinned host memory (time-sliced colocation)."""
+        if self.device.type != "cuda" or getattr(self, "_offloaded", None):
+            return
+        self._offloaded = {}
+        for name in ("master", "exp_avg", "exp_avg_sq"):
+            if self.optimizer is not None:
+                t = getattr(self.optimizer, name)
+                self._offloaded[name] = t.to("cpu", non_blocking=False).pin_memory()
+                setattr(self.optimizer, name, torch.empty(0, device=self.device))
+        if self.store.flat_grad is not None:
+            self._offloaded["grad_shape"] = self.store.flat_grad.numel()
+        torch.cuda.empty_cache()
+
+    def onload(self):
+        off = getattr(self, "_offloaded", None)
+        if not off:
+            return
+        for name in ("master", "exp_avg", "exp_avg_sq"):
+            if name in off:
+                setattr(self.optimizer, name, off[name].to(self.device, non_blocking=True))
+        self._offloaded = None
+
+    def export_stats(self) -> dict[str, float]:
+        return stats_tracker.export_all(reduce_group=self._cpu_group)
+
+
+FSDPEngine = B200TrainEngine  # the role FSDPEngine plays in the reference
+
+
+# --------------------------------------------------------------------------- algorithm mix-ins
+class B200PPOActor(B200TrainEngine):
+    def __init__(self, config):
+        super().__init__(config)
+        from ..trainer.ppo.actor import PPOActor
+
+        self.actor = PPOActor(config, self)
+
+    @torch.no_grad()
+    def compute_logp(self, *a, **k):
+        return self.actor.compute_logp(*a, **k)
+
+    @torch.no_grad()
+    def compute_advantages(self, *a, **k):
+        return self.actor.compute_advantages(*a, **k)
+
+    def ppo_update(self, *a, **k):
+        return self.actor.ppo_update(*a, **k)
+
+
+class B200PPOCritic(B200TrainEngine):
+    def __init__(self, config):
+        super().__init__(config)
+        from ..trainer.ppo.critic import PPOCritic
+
+        self.critic = PPOCritic(config, self)
+
+    @torch.no_grad()
+    def compute_values(self, *a, **k):
+        return self.critic.compute_values(*a, **k)
+
+    def ppo_update(self, *a, **k):
+        return self.critic.ppo_update(*a, **k)
+
+
+class B200LMEngine(B200TrainEngine):
+    def __init__(self, config):
+        super().__init__(config)
+        from ..trainer.sft.lm_engine import LMEngine
+
+        self.lm_engine = LMEngine(self)
+
+    def train_lm(self, data):
+        return self.lm_engine.train_lm(data)
+
+    def evaluate_lm(self, data):
+        return self.lm_engine.evaluate_lm(data)
+
+
+class B200RWEngine(B200TrainEngine):
+    def __init__(self, config):
+        config.is_critic = True
+        super().__init__(config)
+        from ..trainer.rw.rw_engine import RWEngine
+
+        self.rw_engine = RWEngine(self)
+
+    def train_rw(self, data):
+        return self.rw_engine.train_rw(data)
+
+    def evaluate_rw(self, data):
+        return self.rw_engine.evaluate_rw(data)
+
+
+class B200DPOEngine(B200TrainEngine):
+    def __init__(self, config, beta: float = 0.1, loss_type: str = "sigmoid"):
+        super().__init__(config)
+        from ..trainer.dpo.dpo_engine import DPOEngine
+
+        self.dpo_engine = DPOEngine(self, beta=beta, loss_type=loss_type)
+
+    def train_dpo(self, data):
+        return self.dpo_engine.train_dpo(data)
+
+    def evaluate_dpo(self, data):
+        return self.dpo_engine.evaluate_dpo(data)
+
+
+FSDPPPOActor, FSDPPPOCritic, FSDPLMEngine, FSDPRWEngine, FSDPDPOEngine = (
+    B200PPOActor, B200PPOCritic, B200LMEngine, B200RWEngine, B200DPOEngine)

@@ -1,0 +1,165 @@
+"""Architecture description of the supported decoder families (Qwen2 / Qwen2.5, Qwen3,
+Qwen3-MoE) and conversion from / to Hugging Face ``config.json``.
+
+Reference model zoo: ``areal/experimental/models/archon/{qwen2,qwen3}/model/args.py`` and
+the HF path of ``areal/engine/fsdp_engine.py:375-560``.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Optional
+
+
+@dataclass
+class ModelConfig:
+    arch: str = "qwen2"                 # qwen2 | qwen3 | qwen3_moe
+    vocab_size: int = 151936
+    hidden_size: int = 1536
+    num_layers: int = 28
+    num_heads: int = 12
+    num_kv_heads: int = 2
+    head_dim: int = 128
+    intermediate_size: int = 8960
+    rope_theta: float = 1e6
+    rms_norm_eps: float = 1e-6
+    tie_word_embeddings: bool = True
+    attention_bias: bool = True         # Qwen2: bias on q/k/v projections
+    qk_norm: bool = False               # Qwen3: RMSNorm on q and k per head
+    max_position_embeddings: int = 32768
+    # MoE (Qwen3-MoE)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    decoder_sparse_step: int = 1
+    mlp_only_layers: list[int] = field(default_factory=list)
+    # critic / reward heads
+    is_critic: bool = False
+
+    @property
+    def q_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i not in self.mlp_only_layers and (i + 1) % max(1, self.decoder_sparse_step) == 0
+
+    def num_params(self) -> int:
+        H, V, L = self.hidden_size, self.vocab_size, self.num_layers
+        attn = H * (self.q_size + 2 * self.kv_size) + self.q_size * H
+        if self.attention_bias:
+            attn += self.q_size + 2 * self.kv_size
+        if self.qk_norm:
+            attn += 2 * self.head_dim
+        dense_mlp = 3 * H * self.intermediate_size
+        moe_mlp = self.num_experts * 3 * H * self.moe_intermediate_size + H * self.num_experts
+        total = V * H * (1 if self.tie_word_embeddings else 2) + H
+        for i in range(L):
+            total += attn + 2 * H + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
+        return total
+
+    def flops_per_token(self, seq_len: int = 0, backward: bool = True) -> float:
+        """Approximate training FLOPs per token (matmuls + causal attention)."""
+        H, L = self.hidden_size, self.num_layers
+        attn_proj = 2 * H * (self.q_size + 2 * self.kv_size) + 2 * self.q_size * H
+        mlp = 0.0
+        for i in range(L):
+            if self.layer_is_moe(i):
+                mlp += 6 * H * self.moe_intermediate_size * self.num_experts_per_tok + 2 * H * self.num_experts
+            else:
+                mlp += 6 * H * self.intermediate_size
+        attn_core = L * 4 * self.q_size * (seq_len / 2)
+        fwd = L * attn_proj + mlp + attn_core + 2 * H * self.vocab_size
+        return fwd * (3 if backward else 1)
+
+    # ------------------------------------------------------------------ HF interop
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        mt = d.get("model_type", "qwen2")
+        arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "llama": "qwen2"}.get(mt)
+        if arch is None:
+            raise ValueError(f"unsupported model_type '{mt}'")
+        heads = d["num_attention_heads"]
+        hd = d.get("head_dim") or d["hidden_size"] // heads
+        return cls(
+            arch=arch, vocab_size=d["vocab_size"], hidden_size=d["hidden_size"], num_layers=d["num_hidden_layers"],
+            num_heads=heads, num_kv_heads=d.get("num_key_value_heads", heads), head_dim=hd,
+            intermediate_size=d.get("intermediate_size", 0), rope_theta=float(d.get("rope_theta", 1e4)),
+            rms_norm_eps=float(d.get("rms_norm_eps", 1e-6)), tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
+            attention_bias=bool(d.get("attention_bias", mt == "qwen2")), qk_norm=(mt in ("qwen3", "qwen3_moe")),
+            max_position_embeddings=d.get("max_position_embeddings", 32768),
+            num_experts=d.get("num_experts", 0) or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
+            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0, norm_topk_prob=bool(d.get("norm_topk_prob", True)),
+            router_aux_loss_coef=float(d.get("router_aux_loss_coef", 0.0) or 0.0),
+            decoder_sparse_step=d.get("decoder_sparse_step", 1) or 1, mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
+        )
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_hf_dict(json.load(f))
+
+    def to_hf_dict(self) -> dict:
+        mt = self.arch
+        d = dict(
+            model_type=mt, architectures=[{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+                                           "qwen3_moe": "Qwen3MoeForCausalLM"}[mt]],
+            vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_layers,
+            num_attention_heads=self.num_heads, num_key_value_heads=self.num_kv_heads, head_dim=self.head_dim,
+            intermediate_size=self.intermediate_size, rope_theta=self.rope_theta, rms_norm_eps=self.rms_norm_eps,
+            tie_word_embeddings=self.tie_word_embeddings, attention_bias=self.attention_bias,
+            max_position_embeddings=self.max_position_embeddings, hidden_act="silu", torch_dtype="bfloat16",
+        )
+        if self.is_moe:
+            d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
+                     router_aux_loss_coef=self.router_aux_loss_coef, decoder_sparse_step=self.decoder_sparse_step,
+                     mlp_only_layers=self.mlp_only_layers)
+        return d
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as f:
+            json.dump(self.to_hf_dict(), f, indent=2)
+
+
+# named presets used by benchmarks and tests (random-init experiments)
+PRESETS = {
+    "tiny-qwen2": dict(arch="qwen2", vocab_size=1024, hidden_size=256, num_layers=4, num_heads=4, num_kv_heads=2,
+                       head_dim=64, intermediate_size=688, rope_theta=1e4, tie_word_embeddings=True, attention_bias=True),
+    "tiny-qwen3": dict(arch="qwen3", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                       head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False,
+                       attention_bias=False, qk_norm=True),
+    "tiny-qwen3-moe": dict(arch="qwen3_moe", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                           head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False,
+                           attention_bias=False, qk_norm=True, num_experts=8, num_experts_per_tok=2,
+                           moe_intermediate_size=128),
+    "qwen2.5-1.5b": dict(arch="qwen2", vocab_size=151936, hidden_size=1536, num_layers=28, num_heads=12, num_kv_heads=2,
+                         head_dim=128, intermediate_size=8960, rope_theta=1e6, tie_word_embeddings=True,
+                         attention_bias=True),
+    "qwen3-8b": dict(arch="qwen3", vocab_size=151936, hidden_size=4096, num_layers=36, num_heads=32, num_kv_heads=8,
+                     head_dim=128, intermediate_size=12288, rope_theta=1e6, tie_word_embeddings=False,
+                     attention_bias=False, qk_norm=True, max_position_embeddings=40960),
+    "qwen3-30b-a3b": dict(arch="qwen3_moe", vocab_size=151936, hidden_size=2048, num_layers=48, num_heads=32,
+                          num_kv_heads=4, head_dim=128, intermediate_size=6144, rope_theta=1e6,
+                          tie_word_embeddings=False, attention_bias=False, qk_norm=True, num_experts=128,
+                          num_experts_per_tok=8, moe_intermediate_size=768, max_position_embeddings=40960),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    if name not in PRESETS:
+        raise KeyError(f"unknown model preset '{name}' (have {sorted(PRESETS)})")
+    d = dict(PRESETS[name])
+    d.update(overrides)
+    return ModelConfig(**d)

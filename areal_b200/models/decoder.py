@@ -1,0 +1,277 @@
+"""Decoder-only transformer (Qwen2 / Qwen2.5 / Qwen3 / Qwen3-MoE) on packed variable-length
+batches, written against :mod:`areal_b200.ops.functional` so every hot op runs on the
+sm_100a kernels on CUDA tensors and on the fp32 reference on CPU tensors.
+
+Layout choices (differ from HF, converted by :mod:`areal_b200.models.hf_io`):
+
+* ``qkv_proj.weight``   ``[(Hq + 2*Hkv) * D, H]``   q rows | k rows | v rows
+* ``gate_up_proj.weight`` ``[2 * I, H]``            gate rows | up rows
+* experts: ``w_gate_up [E, 2*Im, H]``, ``w_down [E, H, Im]``
+
+The residual stream is carried separately from the sublayer output and added inside the
+next RMSNorm kernel (one read-modify-write instead of two).
+
+Reference behaviour: ``areal/experimental/models/archon/qwen2/model/model.py``,
+``qwen3/model/model.py`` (RMSNorm in fp32, rotate-half RoPE, SwiGLU, QK-norm, GQA, tied
+embeddings) and ``archon/moe/{router,moe,grouped_experts}.py``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from ..ops import functional as OF
+from .config import ModelConfig
+
+
+class PackedBatch:
+    """Per-forward metadata of a packed batch (built once, shared by all layers)."""
+
+    def __init__(self, cu_seqlens: torch.Tensor, position_ids: torch.Tensor, total_tokens: int, max_seqlen: int = 0):
+        self.cu_seqlens = cu_seqlens.to(torch.int32)
+        self.position_ids = position_ids.to(torch.int32)
+        self.total_tokens = total_tokens
+        self.max_seqlen = max_seqlen
+        self.tile_info = OF.attn_tile_table(self.cu_seqlens, total_tokens) if cu_seqlens.is_cuda else None
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        H, D = cfg.hidden_size, cfg.head_dim
+        self.nq, self.nkv, self.D = cfg.num_heads, cfg.num_kv_heads, D
+        qkv_out = (self.nq + 2 * self.nkv) * D
+        self.qkv_proj = nn.Parameter(torch.empty(qkv_out, H, dtype=dtype, device=device))
+        self.qkv_bias = nn.Parameter(torch.zeros(qkv_out, dtype=dtype, device=device)) if cfg.attention_bias else None
+        self.o_proj = nn.Parameter(torch.empty(H, self.nq * D, dtype=dtype, device=device))
+        if cfg.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
+            self.k_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
+        else:
+            self.q_norm = self.k_norm = None
+
+    def project_qkv(self, x: torch.Tensor, pb_positions: torch.Tensor, cos, sin):
+        """Returns q [T,nq,D], k [T,nkv,D], v [T,nkv,D] with QK-norm and RoPE applied."""
+        T = x.shape[0]
+        D, nq, nkv = self.D, self.nq, self.nkv
+        qkv = OF.linear(x, self.qkv_proj)
+        if self.qkv_bias is not None:
+            qkv = qkv + self.qkv_bias
+        q = qkv[:, : nq * D].view(T, nq, D)
+        k = qkv[:, nq * D: (nq + nkv) * D].view(T, nkv, D)
+        v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+        if self.q_norm is not None:
+            q, _ = OF.rmsnorm(q.reshape(T * nq, D), self.q_norm, self.cfg.rms_norm_eps)
+            k, _ = OF.rmsnorm(k.reshape(T * nkv, D), self.k_norm, self.cfg.rms_norm_eps)
+            q, k = q.view(T, nq, D), k.view(T, nkv, D)
+        q = OF.rope(q, pb_positions, cos, sin)
+        k = OF.rope(k, pb_positions, cos, sin)
+        return q, k, v
+
+    def forward(self, x: torch.Tensor, pb: PackedBatch, cos, sin, attn_fn=None) -> torch.Tensor:
+        T = x.shape[0]
+        q, k, v = self.project_qkv(x, pb.position_ids, cos, sin)
+        if attn_fn is not None:
+            o = attn_fn(q, k, v)
+        else:
+            o = OF.attention(q, k.contiguous() if not k.is_cuda else k, v.contiguous() if not v.is_cuda else v,
+                             pb.cu_seqlens, True, 1.0 / math.sqrt(self.D), pb.tile_info)
+        return OF.linear(o.reshape(T, self.nq * self.D), self.o_proj)
+
+
+class DenseMLP(nn.Module):
+    def __init__(self, hidden: int, inter: int, dtype, device):
+        super().__init__()
+        self.gate_up_proj = nn.Parameter(torch.empty(2 * inter, hidden, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(hidden, inter, dtype=dtype, device=device))
+
+    def forward(self, x):
+        return OF.linear(OF.swiglu(OF.linear(x, self.gate_up_proj)), self.down_proj)
+
+
+class MoEMLP(nn.Module):
+    """Token-choice top-k routed experts (softmax router in fp32, optional renormalisation of
+    the top-k weights). Tokens are sorted by expert and each expert's slice goes through the
+    dense GEMM kernel; expert parallelism re-homes the slices (see ``parallel/ep.py``)."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        E, H, Im = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
+        self.router = nn.Parameter(torch.empty(E, H, dtype=dtype, device=device))
+        self.w_gate_up = nn.Parameter(torch.empty(E, 2 * Im, H, dtype=dtype, device=device))
+        self.w_down = nn.Parameter(torch.empty(E, H, Im, dtype=dtype, device=device))
+        self.ep_dispatcher = None  # set by parallel.ep.ExpertParallel
+        self.last_aux_loss: Optional[torch.Tensor] = None
+        self.last_routed_experts: Optional[torch.Tensor] = None
+
+    def route(self, x):
+        logits = F.linear(x.float(), self.router.float())
+        probs = torch.softmax(logits, dim=-1)
+        topw, tope = torch.topk(probs, self.cfg.num_experts_per_tok, dim=-1)
+        if self.cfg.norm_topk_prob:
+            topw = topw / topw.sum(-1, keepdim=True).clamp(min=1e-20)
+        if self.cfg.router_aux_loss_coef > 0 and self.training:
+            E = self.cfg.num_experts
+            frac = torch.zeros(E, device=x.device).scatter_add_(0, tope.reshape(-1), torch.ones(tope.numel(), device=x.device))
+            frac = frac / tope.numel()
+            self.last_aux_loss = E * (frac * probs.mean(0)).sum() * self.cfg.router_aux_loss_coef
+        self.last_routed_experts = tope
+        return topw, tope
+
+    def experts_forward(self, xs: torch.Tensor, counts: list[int], first_expert: int = 0) -> torch.Tensor:
+        """xs: tokens sorted by (local) expert; counts[e] tokens for expert first_expert+e."""
+        outs = []
+        off = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            xe = xs[off:off + n]
+            ge = first_expert + e
+            outs.append(OF.linear(OF.swiglu(OF.linear(xe, self.w_gate_up[ge])), self.w_down[ge]))
+            off += n
+        if not outs:
+            return xs.new_zeros(0, self.cfg.hidden_size)
+        return torch.cat(outs, dim=0)
+
+    def forward(self, x):
+        T, H = x.shape
+        k = self.cfg.num_experts_per_tok
+        topw, tope = self.route(x)
+        flat_e = tope.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        token_of = order // k
+        xs = x[token_of]
+        if self.ep_dispatcher is not None:
+            ys = self.ep_dispatcher(self, xs, flat_e[order])
+        else:
+            counts = torch.bincount(flat_e, minlength=self.cfg.num_experts).tolist()
+            ys = self.experts_forward(xs, counts)
+        w = topw.reshape(-1)[order].to(ys.dtype).unsqueeze(-1)
+        out = torch.zeros(T, H, dtype=ys.dtype, device=x.device)
+        out.index_add_(0, token_of, ys * w)
+        return out
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        H = cfg.hidden_size
+        self.input_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
+        self.post_attention_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
+        self.self_attn = Attention(cfg, dtype, device)
+        self.mlp = MoEMLP(cfg, dtype, device) if cfg.layer_is_moe(idx) else DenseMLP(H, cfg.intermediate_size, dtype, device)
+
+    def forward(self, h, resid, pb: PackedBatch, cos, sin, attn_fn=None):
+        x, resid = OF.rmsnorm(h, self.input_layernorm, self.cfg.rms_norm_eps, resid)
+        h = self.self_attn(x, pb, cos, sin, attn_fn)
+        x, resid = OF.rmsnorm(h, self.post_attention_layernorm, self.cfg.rms_norm_eps, resid)
+        h = self.mlp(x)
+        return h, resid
+
+
+class CausalLM(nn.Module):
+    """Embedding -> N decoder layers -> final norm -> (LM head | value head)."""
+
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", init_std: float = 0.02, seed: Optional[int] = None):
+        super().__init__()
+        self.cfg = cfg
+        self.dtype = dtype
+        H = cfg.hidden_size
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, dtype, device) for i in range(cfg.num_layers)])
+        self.norm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
+        if cfg.is_critic:
+            self.value_head = nn.Parameter(torch.zeros(1, H, dtype=dtype, device=device))
+            self.lm_head = None
+        else:
+            self.value_head = None
+            self.lm_head = None if cfg.tie_word_embeddings else nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
+        self.gradient_checkpointing = False
+        self._rope_cache: dict = {}
+        self.reset_parameters(init_std, seed)
+
+    @torch.no_grad()
+    def reset_parameters(self, std: float = 0.02, seed: Optional[int] = None):
+        gen = None
+        if seed is not None:
+            gen = torch.Generator(device=self.embed_tokens.device)
+            gen.manual_seed(seed)
+        for name, p in self.named_parameters():
+            if name.endswith("layernorm") or name.endswith("norm") or name.endswith("q_norm") or name.endswith("k_norm"):
+                p.fill_(1.0)
+            elif name.endswith("bias") or name.endswith("value_head"):
+                p.zero_()
+            else:
+                # draw in fp32 chunks to keep peak memory small for multi-GB tensors
+                flat = p.view(-1)
+                step = 1 << 26
+                for a in range(0, flat.numel(), step):
+                    b = min(flat.numel(), a + step)
+                    flat[a:b] = (torch.randn(b - a, device=p.device, dtype=torch.float32, generator=gen) * std).to(p.dtype)
+
+    @property
+    def output_weight(self) -> torch.Tensor:
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    def rope(self, device, max_pos: Optional[int] = None):
+        max_pos = max_pos or self.cfg.max_position_embeddings
+        key = (str(device), max_pos)
+        if key not in self._rope_cache:
+            self._rope_cache = {key: OF.rope_tables(max_pos, self.cfg.head_dim, self.cfg.rope_theta, device)}
+        return self._rope_cache[key]
+
+    def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None) -> torch.Tensor:
+        """input_ids: [T] -> final normed hidden states [T, H]."""
+        cos, sin = self.rope(input_ids.device, max(self.cfg.max_position_embeddings, pb.max_seqlen + 1))
+        h = OF.embedding(input_ids, self.embed_tokens)
+        resid = None
+        for i, layer in enumerate(self.layers):
+            fn = attn_fns[i] if attn_fns is not None else None
+            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+                h, resid = checkpoint(layer, h, resid, pb, cos, sin, fn, use_reentrant=False)
+            else:
+                h, resid = layer(h, resid, pb, cos, sin, fn)
+        x, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
+        return x
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Full fp32 logits (small batches / sampling only)."""
+        if hidden.is_cuda:
+            return OF.gemm(hidden.contiguous(), self.output_weight, epi=OF.EPI_F32)
+        return F.linear(hidden, self.output_weight).float()
+
+    def logprobs_entropy(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0, chunk: int = 2048):
+        return OF.lm_head_logprob(hidden, self.output_weight, labels, temperature, chunk)
+
+    def values(self, hidden: torch.Tensor) -> torch.Tensor:
+        return F.linear(hidden.float(), self.value_head.float()).squeeze(-1)
+
+    def aux_loss(self) -> Optional[torch.Tensor]:
+        tot = None
+        for layer in self.layers:
+            al = getattr(layer.mlp, "last_aux_loss", None)
+            if al is not None:
+                tot = al if tot is None else tot + al
+                layer.mlp.last_aux_loss = None
+        return tot
+
+    def forward(self, input_ids, cu_seqlens, position_ids=None, max_seqlen: int = 0):
+        from ..utils.data import positions_from_cu_seqlens
+
+        T = input_ids.shape[0]
+        if position_ids is None:
+            position_ids = positions_from_cu_seqlens(cu_seqlens, T)
+        pb = PackedBatch(cu_seqlens, position_ids, T, max_seqlen)
+        return self.forward_hidden(input_ids, pb)
+
+
+def build_model(cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None) -> CausalLM:
+    return CausalLM(cfg, dtype=dtype, device=device, seed=seed)

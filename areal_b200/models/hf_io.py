@@ -1,0 +1,171 @@
+"""Hugging Face checkpoint interop: name mapping between this framework's fused parameter
+layout and HF's per-projection names, sharded safetensors reading and writing
+(``model-0000i-of-0000N.safetensors`` + ``model.safetensors.index.json``).
+
+Reference behaviour: HF save/load in ``areal/engine/fsdp_engine.py:1787-1818`` and the
+state-dict adapters ``areal/experimental/models/archon/qwen*/model/state_dict_adapter.py``,
+``archon/moe_weight_converter.py`` (per-expert <-> grouped expert tensors).
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from typing import Iterable, Iterator, Optional
+
+import torch
+
+from .config import ModelConfig
+
+
+# --------------------------------------------------------------------------- name mapping
+def hf_to_native_plan(cfg: ModelConfig) -> dict[str, list[tuple[str, Optional[tuple[int, int]], Optional[int]]]]:
+    """native name -> list of (hf name, row range in the native tensor or None, expert idx or None)."""
+    D, nq, nkv = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    plan: dict = {"embed_tokens": [("model.embed_tokens.weight", None, None)], "norm": [("model.norm.weight", None, None)]}
+    if cfg.is_critic:
+        plan["value_head"] = [("score.weight", None, None)]
+    elif not cfg.tie_word_embeddings:
+        plan["lm_head"] = [("lm_head.weight", None, None)]
+    for i in range(cfg.num_layers):
+        p, h = f"layers.{i}.", f"model.layers.{i}."
+        plan[p + "input_layernorm"] = [(h + "input_layernorm.weight", None, None)]
+        plan[p + "post_attention_layernorm"] = [(h + "post_attention_layernorm.weight", None, None)]
+        q_rows, k_rows = nq * D, nkv * D
+        plan[p + "self_attn.qkv_proj"] = [
+            (h + "self_attn.q_proj.weight", (0, q_rows), None),
+            (h + "self_attn.k_proj.weight", (q_rows, q_rows + k_rows), None),
+            (h + "self_attn.v_proj.weight", (q_rows + k_rows, q_rows + 2 * k_rows), None),
+        ]
+        if cfg.attention_bias:
+            plan[p + "self_attn.qkv_bias"] = [
+                (h + "self_attn.q_proj.bias", (0, q_rows), None),
+                (h + "self_attn.k_proj.bias", (q_rows, q_rows + k_rows), None),
+                (h + "self_attn.v_proj.bias", (q_rows + k_rows, q_rows + 2 * k_rows), None),
+            ]
+        plan[p + "self_attn.o_proj"] = [(h + "self_attn.o_proj.weight", None, None)]
+        if cfg.qk_norm:
+            plan[p + "self_attn.q_norm"] = [(h + "self_attn.q_norm.weight", None, None)]
+            plan[p + "self_attn.k_norm"] = [(h + "self_attn.k_norm.weight", None, None)]
+        if cfg.layer_is_moe(i):
+            Im = cfg.moe_intermediate_size
+            plan[p + "mlp.router"] = [(h + "mlp.gate.weight", None, None)]
+            gu, dn = [], []
+            for e in range(cfg.num_experts):
+                gu.append((h + f"mlp.experts.{e}.gate_proj.weight", (0, Im), e))
+                gu.append((h + f"mlp.experts.{e}.up_proj.weight", (Im, 2 * Im), e))
+                dn.append((h + f"mlp.experts.{e}.down_proj.weight", None, e))
+            plan[p + "mlp.w_gate_up"] = gu
+            plan[p + "mlp.w_down"] = dn
+        else:
+            I = cfg.intermediate_size
+            plan[p + "mlp.gate_up_proj"] = [(h + "mlp.gate_proj.weight", (0, I), None),
+                                            (h + "mlp.up_proj.weight", (I, 2 * I), None)]
+            plan[p + "mlp.down_proj"] = [(h + "mlp.down_proj.weight", None, None)]
+    return plan
+
+
+def native_to_hf_tensors(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor]]) -> Iterator[tuple[str, torch.Tensor]]:
+    """Splits native (fused) tensors into HF-named tensors (views; no copies)."""
+    plan = hf_to_native_plan(cfg)
+    for name, t in named:
+        if name not in plan:
+            raise KeyError(f"no HF mapping for parameter '{name}'")
+        for hf_name, rows, expert in plan[name]:
+            src = t if expert is None else t[expert]
+            yield hf_name, (src if rows is None else src[rows[0]:rows[1]])
+
+
+@torch.no_grad()
+def load_hf_tensors_into(cfg: ModelConfig, params: dict[str, torch.Tensor], hf_tensors: Iterable[tuple[str, torch.Tensor]],
+                         strict: bool = True) -> set[str]:
+    """Copies HF-named tensors into native parameters. Returns the set of HF names consumed."""
+    plan = hf_to_native_plan(cfg)
+    inverse: dict[str, tuple[str, Optional[tuple[int, int]], Optional[int]]] = {}
+    for native, parts in plan.items():
+        for hf_name, rows, expert in parts:
+            inverse[hf_name] = (native, rows, expert)
+    seen = set()
+    for hf_name, t in hf_tensors:
+        if hf_name not in inverse:
+            if hf_name == "lm_head.weight" and cfg.tie_word_embeddings:
+                continue
+            if strict:
+                raise KeyError(f"unexpected tensor '{hf_name}' in checkpoint")
+            continue
+        native, rows, expert = inverse[hf_name]
+        dst = params[native]
+        dst = dst if expert is None else dst[expert]
+        dst = dst if rows is None else dst[rows[0]:rows[1]]
+        if dst.shape != t.shape:
+            raise ValueError(f"shape mismatch for {hf_name}: checkpoint {tuple(t.shape)} vs model {tuple(dst.shape)}")
+        dst.copy_(t.to(dst.dtype))
+        seen.add(hf_name)
+    if strict:
+        missing = set(inverse) - seen
+        if missing:
+            raise KeyError(f"{len(missing)} tensors missing from checkpoint, e.g. {sorted(missing)[:3]}")
+    return seen
+
+
+# --------------------------------------------------------------------------- safetensors IO
+def iter_safetensors(path: str, device: str = "cpu") -> Iterator[tuple[str, torch.Tensor]]:
+    from safetensors import safe_open
+
+    files = sorted(f for f in os.listdir(path) if f.endswith(".safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors files under {path}")
+    for fn in files:
+        with safe_open(os.path.join(path, fn), framework="pt", device=device) as f:
+            for k in f.keys():
+                yield k, f.get_tensor(k)
+
+
+def save_hf_sharded(path: str, cfg: ModelConfig, hf_named: Iterable[tuple[str, torch.Tensor]],
+                    max_shard_bytes: int = 5 * 1024 ** 3, shard_prefix: str = "model", rank_tag: Optional[str] = None,
+                    write_index: bool = True) -> dict[str, str]:
+    """Writes HF-layout safetensors shards; returns the tensor -> file map. ``rank_tag``
+    lets several ranks write disjoint tensors into the same directory (the caller merges the
+    maps and writes the index once)."""
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    shards: list[dict[str, torch.Tensor]] = [{}]
+    size = 0
+    for name, t in hf_named:
+        nbytes = t.numel() * t.element_size()
+        if size + nbytes > max_shard_bytes and shards[-1]:
+            shards.append({})
+            size = 0
+        shards[-1][name] = t.detach().to("cpu").contiguous()
+        size += nbytes
+    n = len(shards)
+    weight_map = {}
+    total = 0
+    for i, sh in enumerate(shards):
+        tag = f"{shard_prefix}-{rank_tag}-" if rank_tag else f"{shard_prefix}-"
+        fn = f"{tag}{i + 1:05d}-of-{n:05d}.safetensors" if (n > 1 or rank_tag) else f"{shard_prefix}.safetensors"
+        save_file(sh, os.path.join(path, fn), metadata={"format": "pt"})
+        for k, t in sh.items():
+            weight_map[k] = fn
+            total += t.numel() * t.element_size()
+    if write_index:
+        write_hf_index(path, weight_map, total)
+        cfg.save_pretrained(path)
+    return weight_map
+
+
+def write_hf_index(path: str, weight_map: dict[str, str], total_size: int) -> None:
+    if len(set(weight_map.values())) > 1:
+        with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": total_size}, "weight_map": dict(sorted(weight_map.items()))}, f, indent=2)
+
+
+def save_model_hf(model, path: str, max_shard_bytes: int = 5 * 1024 ** 3) -> None:
+    named = [(n, p.detach()) for n, p in model.named_parameters()]
+    save_hf_sharded(path, model.cfg, native_to_hf_tensors(model.cfg, named), max_shard_bytes)
+
+
+def load_model_hf(model, path: str, strict: bool = True) -> None:
+    params = {n: p.data for n, p in model.named_parameters()}
+    load_hf_tensors_into(model.cfg, params, iter_safetensors(path), strict=strict)

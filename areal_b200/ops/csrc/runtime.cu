@@ -21,6 +21,16 @@ static void load_encode() {
     g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
 }
 
+// Driver entry points need a context bound to the calling thread; threads that have only
+// seen the runtime API lazily (e.g. autograd worker threads) may not have one yet.
+static void bind_context_once() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(0);
+    bound = true;
+  }
+}
+
 static CUtensorMapDataType dtype_of(int code) {
   switch (code) {
     case 0: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -36,6 +46,7 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t 
                    uint32_t box_outer, bool swizzle128, int dtype_code) {
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return -1;
+  bind_context_once();
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -53,6 +64,7 @@ int encode_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t 
                    uint32_t b1, uint32_t b2, bool swizzle128, int dtype_code) {
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return -1;
+  bind_context_once();
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {b0, b1, b2};

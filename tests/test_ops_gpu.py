@@ -80,7 +80,7 @@ def test_rmsnorm(H):
     gy, gr = torch.randn_like(y), torch.randn_like(res)
     (y.float() * gy.float()).sum().add((res.float() * gr.float()).sum()).backward()
     xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
-    s = (xr + rr).bfloat16().float() + (xr + rr - (xr + rr).detach())  # bf16-rounded stream, fp32 grads
+    s = (xr + rr).bfloat16().float().detach() + (xr + rr - (xr + rr).detach())  # bf16-rounded stream, fp32 grads
     yr = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
     ((yr * gy.float()).sum() + (s * gr.float()).sum()).backward()
     assert _rel_err(y, yr) < 1e-2
