@@ -376,6 +376,8 @@ class NativeInferConfig:
     use_cuda_graph: bool = True
     weight_dtype: str = "bfloat16"  # or float8_e4m3fn (block-scaled)
     random_seed: int = 1
+    share_trainer_weights: bool = True  # colocated mode: read the trainer's parameters in place
+    num_pages: Optional[int] = None     # fixed KV page count (default: sized from free memory)
 
 
 @dataclass

@@ -1,0 +1,659 @@
+"""The rollout (inference) engine of this framework: continuous batching over a paged KV
+cache, prefill with the varlen flash-attention kernel, decode with the paged-attention kernel
+under CUDA graphs, fused sampling that returns per-token log-probs, abort / pause / resume
+for weight hot-swap, and per-token weight-version tagging.
+
+It implements :class:`~areal_b200.api.engine_api.InferenceEngine` in-process (one engine per
+GPU / process) and takes the place of the SGLang / vLLM servers plus HTTP clients of the
+reference (``areal/engine/sglang_remote.py``, ``areal/infra/remote_inf_engine.py``).
+Interruptible generation follows ``remote_inf_engine.py:912-1083``: the client loop pins the
+weight version before every (re)submission, an aborted request returns its partial output,
+and the prefix (prompt + tokens so far) is prefetched again under the new weights.
+
+On CPU tensors (tests, tiny models) the engine recomputes the full prefix every step with the
+reference ops instead of using the paged cache; semantics are identical.
+"""
+from __future__ import annotations
+
+import asyncio
+import collections
+import math
+import threading
+import time
+import zlib
+from concurrent.futures import Future
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from ..api.cli_args import InferenceEngineConfig, NativeInferConfig
+from ..api.engine_api import InferenceEngine
+from ..api.io_struct import ModelRequest, ModelResponse, ParamSpec, WeightUpdateMeta
+from ..models.config import ModelConfig
+from ..models.decoder import CausalLM, PackedBatch, build_model
+from ..ops import functional as OF
+from ..ops import lib as oplib
+from ..utils import logging as alog
+
+logger = alog.getLogger("infer_engine")
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+
+
+@dataclass
+class _Seq:
+    rid: str
+    tokens: list[int]                      # prompt + generated so far
+    prompt_len: int
+    max_new: int
+    min_new: int
+    temperature: float
+    greedy: bool
+    stop_ids: set
+    ignore_eos: bool
+    seed: int
+    future: Any = None                     # (loop, asyncio future)
+    out_tokens: list[int] = field(default_factory=list)
+    out_logprobs: list[float] = field(default_factory=list)
+    pages: list[int] = field(default_factory=list)
+    cached: int = 0                        # tokens whose KV is in the cache
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    aborted: bool = False
+    top_p: float = 1.0
+    top_k: int = 0
+
+
+class PagedKVCache:
+    """K and V pages for all layers: ``[layers, 2, num_pages * page_size, Hkv, D]``."""
+
+    def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int, device, dtype):
+        self.page_size, self.num_pages = page_size, num_pages
+        self.data = torch.zeros(cfg.num_layers, 2, num_pages * page_size, cfg.num_kv_heads, cfg.head_dim,
+                                device=device, dtype=dtype)
+        self.free = list(range(num_pages - 1, -1, -1))
+
+    def alloc(self, n: int) -> Optional[list[int]]:
+        if len(self.free) < n:
+            return None
+        out = self.free[-n:]
+        del self.free[-n:]
+        return out
+
+    def release(self, pages: list[int]) -> None:
+        self.free.extend(pages)
+
+    def pages_needed(self, tokens: int) -> int:
+        return (tokens + self.page_size - 1) // self.page_size
+
+
+class NativeInferenceEngine(InferenceEngine):
+    def __init__(self, config: Optional[InferenceEngineConfig] = None, infer_config: Optional[NativeInferConfig] = None,
+                 model_config: Optional[ModelConfig] = None, model: Optional[CausalLM] = None, eos_token_id: Optional[int] = None):
+        self.config = config or InferenceEngineConfig()
+        self.icfg = infer_config or NativeInferConfig()
+        self.model_config = model_config or (model.cfg if model is not None else None)
+        self.model = model
+        self.eos_token_id = eos_token_id
+        self._version = 0
+        self._lock = threading.Lock()
+        self._waiting: collections.deque[_Seq] = collections.deque()
+        self._running: list[_Seq] = []
+        self._gen_paused = threading.Event()
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self._executor = None
+        self._graphs: dict[int, Any] = {}
+        self._step = 0
+        self._exc: Optional[BaseException] = None
+        self._idle = threading.Event()
+        self._idle.set()
+        self.stats = collections.Counter()
+        self.device = torch.device("cpu")
+        self.cache: Optional[PagedKVCache] = None
+
+    # ------------------------------------------------------------------ lifecycle
+    def initialize(self, device=None, seed: int = 1, train_data_parallel_size: int = 1, model_path: Optional[str] = None,
+                   start_executor: bool = True, **kwargs):
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        if self.model is None:
+            if self.model_config is None:
+                if not model_path:
+                    raise ValueError("inference engine needs a model, a model_config or a model_path")
+                self.model_config = ModelConfig.from_pretrained(model_path)
+            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            self.model = build_model(self.model_config, dtype=dtype, device=self.device, seed=seed)
+            if model_path:
+                from ..models import hf_io
+
+                hf_io.load_model_hf(self.model, model_path)
+        self.shared_model = kwargs.get("shared_model", False)
+        if not self.shared_model:
+            self.model.eval()
+            for p in self.model.parameters():
+                p.requires_grad_(False)
+        if self.device.type == "cuda":
+            self._init_cuda_state()
+        self._thread = threading.Thread(target=self._engine_main, name="infer-engine", daemon=True)
+        self._thread.start()
+        if start_executor:
+            from ..rollout.executor import WorkflowExecutor
+
+            self._executor = WorkflowExecutor(self.config, self, dp_world_size=train_data_parallel_size).initialize()
+        return self
+
+    def _init_cuda_state(self):
+        cfg, ic = self.model_config, self.icfg
+        free, total = torch.cuda.mem_get_info()
+        per_page = cfg.num_layers * 2 * ic.page_size * cfg.num_kv_heads * cfg.head_dim * 2
+        budget = int(free * ic.mem_fraction_static) - (2 << 30)
+        want = ic.max_running_requests * (ic.context_length // ic.page_size + 1)
+        n_pages = max(16, min(want, budget // per_page))
+        if getattr(ic, "num_pages", None):
+            n_pages = ic.num_pages
+        self.cache = PagedKVCache(cfg, n_pages, ic.page_size, self.device, torch.bfloat16)
+        self.max_pages_per_seq = ic.context_length // ic.page_size + 1
+        B = max(b for b in DECODE_BUCKETS if b <= max(1, ic.max_running_requests)) if ic.max_running_requests >= 1 else 1
+        self.max_batch = B
+        dev = self.device
+        self.s_tokens = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.s_pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.s_slots = torch.full((B,), -1, dtype=torch.int32, device=dev)
+        self.s_lens = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.s_pt = torch.zeros(B, self.max_pages_per_seq, dtype=torch.int32, device=dev)
+        self.s_inv_temp = torch.ones(B, dtype=torch.float32, device=dev)
+        self.s_greedy = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.s_seeds = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.s_out_tok = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.s_out_lp = torch.zeros(B, dtype=torch.float32, device=dev)
+        self.n_splits = 4
+        self.s_part_o = torch.zeros(B * cfg.num_heads * self.n_splits * cfg.head_dim, dtype=torch.float32, device=dev)
+        self.s_part_ml = torch.zeros(B * cfg.num_heads * self.n_splits * 2, dtype=torch.float32, device=dev)
+        self.stream = torch.cuda.Stream(device=dev)
+        oplib.get_lib().ab2_runtime_init()
+        logger.info("KV cache: %d pages x %d tokens (%.1f GB)", n_pages, ic.page_size, n_pages * per_page / 2 ** 30)
+
+    def destroy(self):
+        self._stop.set()
+        if self._executor is not None:
+            self._executor.destroy()
+            self._executor = None
+        if self._thread is not None:
+            self._thread.join(timeout=10)
+            self._thread = None
+        self._graphs.clear()
+        self.cache = None
+
+    # ------------------------------------------------------------------ versions / weights
+    def set_version(self, version: int) -> None:
+        self._version = version
+
+    def get_version(self) -> int:
+        return self._version
+
+    def pause_generation(self):
+        """Aborts in-flight requests (they return their partial output) and holds the engine
+        loop until ``continue_generation``."""
+        self._gen_paused.set()
+        self._idle.wait(timeout=60)
+
+    def continue_generation(self):
+        self._gen_paused.clear()
+
+    def pause(self):
+        if self._executor is not None:
+            self._executor.pause()
+
+    def resume(self):
+        if self._executor is not None:
+            self._executor.resume()
+
+    def is_paused(self) -> bool:
+        return self._executor.is_paused() if self._executor is not None else False
+
+    @torch.no_grad()
+    def update_weights_from_tensors(self, named_tensors, meta: Optional[WeightUpdateMeta] = None) -> Future:
+        """Copies native-named tensors into the model (device-to-device or host-to-device)."""
+        fut: Future = Future()
+        params = dict(self.model.named_parameters())
+        for name, t in named_tensors:
+            params[name].data.copy_(t.to(params[name].dtype), non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        if meta is not None and meta.version is not None:
+            self.set_version(meta.version)
+        fut.set_result(True)
+        return fut
+
+    def update_weights_from_disk(self, meta: WeightUpdateMeta) -> Future:
+        from ..models import hf_io
+
+        fut: Future = Future()
+        hf_io.load_model_hf(self.model, meta.path)
+        if meta.version is not None:
+            self.set_version(meta.version)
+        fut.set_result(True)
+        return fut
+
+    def init_weights_update_group(self, meta: WeightUpdateMeta) -> Future:
+        fut: Future = Future()
+        fut.set_result(True)
+        return fut
+
+    def update_weights_from_distributed(self, meta: WeightUpdateMeta, param_specs: list[ParamSpec]) -> Future:
+        from ..wsync.service import receive_broadcast
+
+        fut: Future = Future()
+        receive_broadcast(self, meta, param_specs)
+        fut.set_result(True)
+        return fut
+
+    def offload(self, tags=None):
+        """Drops the KV cache (and CUDA graphs that point into it); weights stay."""
+        self.pause_generation()
+        self._graphs.clear()
+        if self.cache is not None:
+            self._saved_cache_shape = (self.cache.num_pages, self.cache.page_size)
+            self.cache = None
+            torch.cuda.empty_cache()
+
+    def onload(self, tags=None):
+        if self.cache is None and self.device.type == "cuda":
+            n, ps = self._saved_cache_shape
+            self.cache = PagedKVCache(self.model_config, n, ps, self.device, torch.bfloat16)
+        self.continue_generation()
+
+    # ------------------------------------------------------------------ request API
+    async def agenerate(self, req: ModelRequest) -> ModelResponse:
+        """Interruptible generation: loops over engine submissions until the request stops for
+        a real reason; every segment is tagged with the weight version it ran under."""
+        g = req.gconfig
+        prompt = list(req.input_ids)
+        budget = min(g.max_tokens - len(prompt), g.max_new_tokens)
+        if budget <= 0:
+            raise ValueError(f"prompt of {len(prompt)} tokens leaves no room under max_tokens={g.max_tokens}")
+        out_tok: list[int] = []
+        out_lp: list[float] = []
+        out_ver: list[int] = []
+        stop_reason = "abort"
+        t0 = time.perf_counter()
+        ttft = float("inf")
+        tokens = prompt
+        remaining = budget
+        loop = asyncio.get_running_loop()
+        while stop_reason not in ("stop", "tool_calls", "length") and len(out_tok) < budget:
+            while self._gen_paused.is_set():
+                await asyncio.sleep(0.002)
+            version = self.get_version()
+            fut = loop.create_future()
+            seq = _Seq(rid=req.rid, tokens=list(tokens), prompt_len=len(tokens), max_new=remaining,
+                       min_new=max(0, g.min_new_tokens - len(out_tok)), temperature=0.0 if g.greedy else g.temperature,
+                       greedy=bool(g.greedy) or g.temperature == 0.0,
+                       stop_ids=set(g.stop_token_ids or []), ignore_eos=g.ignore_eos,
+                       seed=(g.seed if g.seed is not None else zlib.crc32(req.rid.encode())) & 0x7FFFFFFF, future=(loop, fut),
+                       t_submit=time.perf_counter(), top_p=g.top_p, top_k=0 if g.top_k >= 10 ** 7 else int(g.top_k))
+            with self._lock:
+                self._waiting.append(seq)
+            seg_tokens, seg_lps, stop_reason, t_first = await fut
+            if seg_tokens and ttft == float("inf"):
+                ttft = t_first - t0
+            out_tok += seg_tokens
+            out_lp += seg_lps
+            out_ver += [version] * len(seg_tokens)
+            tokens = tokens + seg_tokens
+            remaining -= len(seg_tokens)
+        if stop_reason == "abort":
+            stop_reason = "length"
+        assert len(out_tok) == len(out_lp) == len(out_ver), "token / logprob / version streams diverged"
+        lat = time.perf_counter() - t0
+        return ModelResponse(input_tokens=prompt, output_tokens=out_tok, output_logprobs=out_lp, output_versions=out_ver,
+                             stop_reason=stop_reason, latency=lat, ttft=ttft, tokenizer=req.tokenizer,
+                             itl=[(lat - ttft) / max(1, len(out_tok) - 1)] if out_tok else [])
+
+    def submit(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, task_id=None, is_eval=False) -> int:
+        return self._executor.submit(data, workflow, workflow_kwargs, should_accept_fn, task_id, is_eval)
+
+    def wait(self, count, timeout=None, raise_timeout=True):
+        return self._executor.wait(count, timeout, raise_timeout)
+
+    def wait_for_task(self, task_id, timeout=None, raise_timeout=True):
+        return self._executor.wait_for_task(task_id, timeout, raise_timeout)
+
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None):
+        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn)
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None, dynamic_bs=False):
+        return self._executor.prepare_batch(dataloader, workflow, workflow_kwargs, should_accept_fn, dynamic_bs)
+
+    @property
+    def workflow_executor(self):
+        return self._executor
+
+    # ------------------------------------------------------------------ engine loop
+    def _engine_main(self):
+        try:
+            if self.device.type == "cuda":
+                torch.cuda.set_device(self.device)
+            while not self._stop.is_set():
+                if self._gen_paused.is_set():
+                    self._abort_all()
+                    self._idle.set()
+                    time.sleep(0.001)
+                    continue
+                with self._lock:
+                    has_work = bool(self._waiting) or bool(self._running)
+                if not has_work:
+                    self._idle.set()
+                    time.sleep(0.0005)
+                    continue
+                self._idle.clear()
+                if self.device.type == "cuda":
+                    with torch.cuda.stream(self.stream), torch.no_grad():
+                        self._step_cuda()
+                else:
+                    with torch.no_grad():
+                        self._step_cpu()
+        except BaseException as e:  # surface to waiting clients
+            logger.error("inference engine loop failed: %r", e)
+            self._exc = e
+            self._fail_all(e)
+        finally:
+            self._idle.set()
+
+    def _resolve(self, seq: _Seq, reason: str):
+        loop, fut = seq.future
+        res = (seq.out_tokens, seq.out_logprobs, reason, seq.t_first)
+        if self.cache is not None and seq.pages:
+            self.cache.release(seq.pages)
+            seq.pages = []
+
+        def _set():
+            if not fut.done():
+                fut.set_result(res)
+        loop.call_soon_threadsafe(_set)
+
+    def _fail_all(self, e):
+        with self._lock:
+            seqs = list(self._waiting) + self._running
+            self._waiting.clear()
+            self._running = []
+        for s in seqs:
+            loop, fut = s.future
+            loop.call_soon_threadsafe(lambda f=fut: (not f.done()) and f.set_exception(RuntimeError(f"engine failed: {e!r}")))
+
+    def _abort_all(self):
+        with self._lock:
+            seqs = list(self._waiting) + self._running
+            self._waiting.clear()
+            self._running = []
+        for s in seqs:
+            self.stats["aborted"] += 1
+            self._resolve(s, "abort")
+
+    def _finish_check(self, s: _Seq, tok: int) -> Optional[str]:
+        n = len(s.out_tokens)
+        if n >= s.min_new:
+            if tok in s.stop_ids:
+                return "stop"
+            if not s.ignore_eos and self.eos_token_id is not None and tok == self.eos_token_id:
+                return "stop"
+        if n >= s.max_new:
+            return "length"
+        if len(s.tokens) >= self.icfg.context_length:
+            return "length"
+        return None
+
+    # ---------------------------------------------------------------- CPU reference path
+    def _step_cpu(self):
+        with self._lock:
+            while self._waiting and len(self._running) < self.icfg.max_running_requests:
+                self._running.append(self._waiting.popleft())
+            batch = list(self._running)
+        if not batch:
+            return
+        lens = [len(s.tokens) for s in batch]
+        ids = torch.tensor([t for s in batch for t in s.tokens], dtype=torch.long)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        hidden = self.model(ids, cu, max_seqlen=max(lens))
+        last = hidden[(cu[1:] - 1).long()]
+        logits = self.model.logits(last)
+        self._step += 1
+        done = []
+        for i, s in enumerate(batch):
+            tok, lp = self._sample_cpu(logits[i], s)
+            self._accept_token(s, tok, lp, done)
+        self._retire(done)
+
+    def _sample_cpu(self, logits: torch.Tensor, s: _Seq):
+        if s.greedy:
+            lp_all = torch.log_softmax(logits.float(), -1)
+            tok = int(torch.argmax(lp_all))
+            return tok, float(lp_all[tok])
+        z = logits.float() / max(s.temperature, 1e-6)
+        z = _apply_top_k_top_p(z, s.top_k, s.top_p)
+        lp_all = torch.log_softmax(z, -1)
+        gen = torch.Generator().manual_seed((s.seed * 1000003 + len(s.tokens)) & 0x7FFFFFFF)
+        tok = int(torch.multinomial(lp_all.exp(), 1, generator=gen))
+        return tok, float(lp_all[tok])
+
+    def _accept_token(self, s: _Seq, tok: int, lp: float, done: list):
+        if not s.out_tokens:
+            s.t_first = time.perf_counter()
+        s.out_tokens.append(tok)
+        s.out_logprobs.append(lp)
+        s.tokens.append(tok)
+        self.stats["generated_tokens"] += 1
+        reason = self._finish_check(s, tok)
+        if reason is not None:
+            done.append((s, reason))
+
+    def _retire(self, done):
+        if not done:
+            return
+        gone = {id(s) for s, _ in done}
+        with self._lock:
+            self._running = [s for s in self._running if id(s) not in gone]
+        for s, reason in done:
+            self._resolve(s, reason)
+
+    # ---------------------------------------------------------------- CUDA path
+    def _step_cuda(self):
+        cache = self.cache
+        # ---- admission + prefill
+        admitted: list[_Seq] = []
+        budget = self.icfg.max_prefill_tokens
+        with self._lock:
+            while self._waiting and len(self._running) + len(admitted) < self.max_batch:
+                s = self._waiting[0]
+                need = cache.pages_needed(min(len(s.tokens) + s.max_new, self.icfg.context_length))
+                if len(s.tokens) > budget and admitted:
+                    break
+                pages = cache.alloc(need)
+                if pages is None:
+                    break
+                self._waiting.popleft()
+                s.pages = pages
+                admitted.append(s)
+                budget -= len(s.tokens)
+        done: list = []
+        if admitted:
+            self._prefill(admitted, done)
+            with self._lock:
+                self._running.extend(s for s in admitted if all(s is not d for d, _ in done))
+        with self._lock:
+            batch = list(self._running)
+        batch = [s for s in batch if all(s is not d for d, _ in done)]
+        fresh = {id(s) for s in admitted}
+        decode_batch = [s for s in batch if id(s) not in fresh]
+        if decode_batch:
+            self._decode(decode_batch, done)
+        self._retire(done)
+
+    def _layer_attn_fns(self, mode: str, **kw):
+        cfg = self.model_config
+        fns = []
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        L = oplib.get_lib()
+        for li in range(cfg.num_layers):
+            kc, vc = self.cache.data[li, 0], self.cache.data[li, 1]
+
+            def fn(q, k, v, kc=kc, vc=vc):
+                n = q.shape[0]
+                rc = L.ab2_kv_append(k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), kw["slots"].data_ptr(), n,
+                                     cfg.num_kv_heads, cfg.head_dim, k.stride(0), v.stride(0), oplib.stream_ptr())
+                oplib.check(rc, "ab2_kv_append")
+                if mode == "prefill":
+                    o, _ = OF.attention_fwd(q, k, v, kw["cu"], True, scale, kw["tile_info"])
+                    return o
+                o = torch.empty_like(q)
+                rc = L.ab2_paged_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), kw["pt"].data_ptr(),
+                                        kw["lens"].data_ptr(), self.s_part_o.data_ptr(), self.s_part_ml.data_ptr(),
+                                        o.data_ptr(), n, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim,
+                                        self.cache.page_size, self.max_pages_per_seq, self.n_splits, scale,
+                                        oplib.stream_ptr())
+                oplib.check(rc, "ab2_paged_decode")
+                return o
+            fns.append(fn)
+        return fns
+
+    def _slot_of(self, s: _Seq, pos: int) -> int:
+        ps = self.cache.page_size
+        return s.pages[pos // ps] * ps + pos % ps
+
+    def _prefill(self, seqs: list[_Seq], done: list):
+        dev = self.device
+        lens = [len(s.tokens) for s in seqs]
+        T = sum(lens)
+        Tp = (T + 127) // 128 * 128
+        ids = torch.zeros(Tp, dtype=torch.int32)
+        pos = torch.zeros(Tp, dtype=torch.int32)
+        slots = torch.full((Tp,), -1, dtype=torch.int32)
+        off = 0
+        for s, n in zip(seqs, lens):
+            ids[off:off + n] = torch.tensor(s.tokens, dtype=torch.int32)
+            pos[off:off + n] = torch.arange(n, dtype=torch.int32)
+            ps = self.cache.page_size
+            pg = torch.tensor(s.pages, dtype=torch.int32)
+            ar = torch.arange(n, dtype=torch.int32)
+            slots[off:off + n] = pg[(ar // ps).long()] * ps + ar % ps
+            off += n
+        cu_list = [0] + list(torch.tensor(lens).cumsum(0).tolist())
+        if Tp > T:
+            cu_list.append(Tp)
+        cu = torch.tensor(cu_list, dtype=torch.int32)
+        ids, pos, slots, cu = (t.pin_memory().to(dev, non_blocking=True) for t in (ids, pos, slots, cu))
+        pb = PackedBatch(cu, pos, Tp, max(lens))
+        fns = self._layer_attn_fns("prefill", slots=slots, cu=cu, tile_info=pb.tile_info)
+        hidden = self.model.forward_hidden(ids, pb, attn_fns=fns)
+        last_idx = torch.tensor([c - 1 for c in cu_list[1:len(seqs) + 1]], dtype=torch.long, device=dev)
+        logits = self.model.logits(hidden[last_idx].contiguous())
+        toks, lps = self._sample_cuda(logits, seqs)
+        self.stats["prefill_tokens"] += T
+        for s, n, tok, lp in zip(seqs, lens, toks, lps):
+            s.cached = n
+            self._accept_token(s, tok, lp, done)
+
+    def _sample_cuda(self, logits: torch.Tensor, seqs: list[_Seq]):
+        n = len(seqs)
+        plain = all(s.top_p >= 1.0 and s.top_k <= 0 for s in seqs)
+        self._step += 1
+        if not plain:
+            out_t, out_l = [], []
+            lg = logits.float().cpu()
+            for i, s in enumerate(seqs):
+                t, l = self._sample_cpu(lg[i], s)
+                out_t.append(t)
+                out_l.append(l)
+            return out_t, out_l
+        inv_t = torch.tensor([1.0 if s.greedy else 1.0 / max(s.temperature, 1e-6) for s in seqs], dtype=torch.float32)
+        gr = torch.tensor([int(s.greedy) for s in seqs], dtype=torch.int32)
+        sd = torch.tensor([s.seed & 0x7FFFFFFF for s in seqs], dtype=torch.int32)
+        self.s_inv_temp[:n].copy_(inv_t, non_blocking=True)
+        self.s_greedy[:n].copy_(gr, non_blocking=True)
+        self.s_seeds[:n].copy_(sd, non_blocking=True)
+        rc = oplib.get_lib().ab2_sample(logits.data_ptr(), logits.stride(0), n, logits.shape[1], self.s_inv_temp.data_ptr(),
+                                        self.s_greedy.data_ptr(), self.s_seeds.data_ptr(), self._step & 0x7FFFFFFF,
+                                        self.s_out_tok.data_ptr(), self.s_out_lp.data_ptr(), oplib.stream_ptr())
+        oplib.check(rc, "ab2_sample")
+        toks = self.s_out_tok[:n].tolist()
+        lps = self.s_out_lp[:n].tolist()
+        return toks, lps
+
+    def _decode_forward(self, B: int) -> torch.Tensor:
+        """One decode step over the static buffers (first B rows). Returns fp32 logits [B, V]."""
+        pb = PackedBatch.__new__(PackedBatch)
+        pb.cu_seqlens = None
+        pb.position_ids = self.s_pos[:B]
+        pb.total_tokens, pb.max_seqlen, pb.tile_info = B, 1, None
+        fns = self._layer_attn_fns("decode", slots=self.s_slots[:B], pt=self.s_pt[:B], lens=self.s_lens[:B])
+        hidden = self.model.forward_hidden(self.s_tokens[:B], pb, attn_fns=fns)
+        return self.model.logits(hidden)
+
+    def _decode(self, seqs: list[_Seq], done: list):
+        n = len(seqs)
+        B = next(b for b in DECODE_BUCKETS if b >= n)
+        B = min(B, self.max_batch)
+        toks = torch.zeros(B, dtype=torch.int32)
+        pos = torch.zeros(B, dtype=torch.int32)
+        slots = torch.full((B,), -1, dtype=torch.int32)
+        lens = torch.zeros(B, dtype=torch.int32)
+        pt = torch.zeros(B, self.max_pages_per_seq, dtype=torch.int32)
+        for i, s in enumerate(seqs):
+            p = len(s.tokens) - 1          # position of the token being fed
+            toks[i] = s.tokens[-1]
+            pos[i] = p
+            slots[i] = self._slot_of(s, p)
+            lens[i] = p + 1
+            pt[i, :len(s.pages)] = torch.tensor(s.pages, dtype=torch.int32)
+        self.s_tokens[:B].copy_(toks, non_blocking=True)
+        self.s_pos[:B].copy_(pos, non_blocking=True)
+        self.s_slots[:B].copy_(slots, non_blocking=True)
+        self.s_lens[:B].copy_(lens, non_blocking=True)
+        self.s_pt[:B].copy_(pt, non_blocking=True)
+        if self.icfg.use_cuda_graph:
+            g = self._graphs.get(B)
+            if g is None:
+                g = self._capture(B)
+            graph, logits, n_kernels = g
+            graph.replay()
+            oplib.LAUNCHES["count"] += n_kernels
+        else:
+            logits = self._decode_forward(B)
+        out_t, out_l = self._sample_cuda(logits[:n], seqs)
+        self.stats["decode_steps"] += 1
+        for s, tok, lp in zip(seqs, out_t, out_l):
+            self._accept_token(s, tok, lp, done)
+
+    def _capture(self, B: int):
+        # warm-up outside capture (sets kernel attributes, allocates the error word)
+        for _ in range(2):
+            self._decode_forward(B)
+        self.stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = oplib.launch_count()
+        with torch.cuda.graph(graph, stream=self.stream):
+            logits = self._decode_forward(B)
+        n_kernels = oplib.launch_count() - n0
+        oplib.LAUNCHES["count"] = n0  # capture itself executes nothing
+        self._graphs[B] = (graph, logits, n_kernels)
+        return self._graphs[B]
+
+    def export_stats(self) -> dict[str, float]:
+        return {f"infer/{k}": float(v) for k, v in self.stats.items()}
+
+
+def _apply_top_k_top_p(z: torch.Tensor, top_k: int, top_p: float) -> torch.Tensor:
+    if top_k and top_k > 0 and top_k < z.numel():
+        kth = torch.topk(z, top_k).values[-1]
+        z = torch.where(z < kth, torch.full_like(z, float("-inf")), z)
+    if top_p < 1.0:
+        sz, idx = torch.sort(z, descending=True)
+        probs = torch.softmax(sz, -1)
+        cum = torch.cumsum(probs, -1)
+        remove = cum - probs > top_p
+        sz = torch.where(remove, torch.full_like(sz, float("-inf")), sz)
+        z = torch.full_like(z, float("-inf")).scatter(0, idx, sz)
+    return z

@@ -101,7 +101,14 @@ class B200TrainEngine(TrainEngine):
         self.local_index = self._train_ranks.index(self.rank) if self.rank in self._train_ranks else -1
         self.sp_rank = self.local_index % self.sp_size
         self.dp_rank = self.local_index // self.sp_size
-        if dist.is_initialized() and n > 1:
+        preset = getattr(self, "_preset_groups", None)
+        if preset is not None:
+            # groups were created collectively by every rank of a trainer / rollout split
+            self._shard_group = preset.get("shard") if n > 1 else None
+            self._sp_group = preset.get("sp")
+            self._dp_group = preset.get("dp")
+            self._cpu_group = preset.get("cpu") if n > 1 else None
+        elif dist.is_initialized() and n > 1:
             self._shard_group = dist.new_group(self._train_ranks) if n != self.world_size else dist.group.WORLD
             # sp groups: consecutive ranks; dp groups: strided
             for d in range(self.dp_size):
@@ -122,9 +129,11 @@ class B200TrainEngine(TrainEngine):
             self._shard_group = None
         return self
 
-    def set_train_ranks(self, ranks: list[int]):
-        """Restricts the engine to a subset of the global ranks (trainer/rollout split)."""
+    def set_train_ranks(self, ranks: list[int], groups: Optional[dict] = None):
+        """Restricts the engine to a subset of the global ranks (trainer / rollout split).
+        ``groups``: process groups created collectively by all ranks (keys shard, dp, sp, cpu)."""
         self._train_ranks = list(ranks)
+        self._preset_groups = groups
 
     # ------------------------------------------------------------------ init
     def initialize(self, addr: Optional[str] = None, ft_spec: Optional[FinetuneSpec] = None,
@@ -156,8 +165,18 @@ class B200TrainEngine(TrainEngine):
             hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
         n_shards = len(self._train_ranks) if self._shard_group is not None else 1
         shard_rank = self.local_index if n_shards > 1 else 0
-        alloc = self._symmetric_alloc if (n_shards > 1 and self.device.type == "cuda" and cfg.fsdp.fuse_reduce_scatter_adamw) else None
-        self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc, alloc_grad=alloc,
+        on_gpu = self.device.type == "cuda"
+        fused = n_shards > 1 and on_gpu and cfg.fsdp.fuse_reduce_scatter_adamw
+        # the parameter buffer may be peer-mapped over a wider group (trainer + rollout ranks)
+        psg = kwargs.get("param_symm_group")
+        psg_ranks = kwargs.get("param_symm_ranks")
+        alloc_g = (lambda n, dt, d: self._symmetric_alloc(n, dt, d, self._shard_group, self._train_ranks)) if fused else None
+        if psg is not None and on_gpu:
+            alloc_p = lambda n, dt, d: self._symmetric_alloc(n, dt, d, psg, psg_ranks)
+        else:
+            alloc_p = alloc_g
+        alloc = alloc_g
+        self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
                                     with_grads=cfg.optimizer is not None)
         if n_shards > 1:
             # identical initial weights everywhere (rank 0 of the trainer group is the source)
@@ -172,7 +191,9 @@ class B200TrainEngine(TrainEngine):
         if alloc is not None:
             from ..parallel.fused_zero import FusedGradReducer
 
-            self._grad_reducer = FusedGradReducer(self.store, self._shard_group, self._symm_handles)
+            self._grad_reducer = FusedGradReducer(self.store, self._shard_group,
+                                                  self.peer_ptrs(self.store.flat_grad, self._train_ranks),
+                                                  self.peer_ptrs(self.store.flat_param, self._train_ranks))
         self._initialized = True
         logger.info("initialised %s: %.2fB params, dtype %s, dp=%d sp=%d, %.1fs", model_config.arch,
                     model_config.num_params() / 1e9, dtype, self.dp_size, self.sp_size, time.time() - t0)
@@ -180,16 +201,22 @@ class B200TrainEngine(TrainEngine):
 
     _symm_handles: dict = {}
 
-    def _symmetric_alloc(self, n: int, dtype, device):
-        """Allocates a buffer every trainer rank can address (peer pointers) for the fused
-        reduce-scatter / parameter write-back kernels."""
+    def _symmetric_alloc(self, n: int, dtype, device, group, group_ranks):
+        """Allocates a buffer that every rank of ``group`` can address (peer pointers) for the
+        fused reduce-scatter / parameter write-back / weight-push kernels."""
         from ..parallel.symm import symm_empty
 
-        t, hdl = symm_empty(n, dtype, device, self._shard_group)
+        t, hdl = symm_empty(n, dtype, device, group)
         t.zero_()
         self._symm_handles = dict(self._symm_handles)
-        self._symm_handles[t.data_ptr()] = hdl
+        self._symm_handles[t.data_ptr()] = (hdl, list(group_ranks))
         return t
+
+    def peer_ptrs(self, tensor: torch.Tensor, global_ranks: list[int]) -> list[int]:
+        """Addresses (in this process) of the peers' copies of a symmetric buffer."""
+        hdl, ranks = self._symm_handles[tensor.data_ptr()]
+        ptrs = list(hdl.buffer_ptrs)
+        return [ptrs[ranks.index(r)] for r in global_ranks]
 
     def destroy(self):
         self.model = None
@@ -363,10 +390,16 @@ class B200TrainEngine(TrainEngine):
         return stats
 
     def optimizer_step(self) -> dict[str, float]:
+        hook = getattr(self, "before_optimizer_step", None)
+        if hook is not None:
+            hook()
         self.store.fold_autograd_grads()
         opt = self.optimizer
+        fused = self._grad_reducer is not None and not opt.sgd
         if self._shard_group is not None:
-            if self._grad_reducer is not None:
+            if fused:
+                gshard = self._grad_reducer.reduce_scatter(opt.state)
+            elif self._grad_reducer is not None:
                 gshard = self._grad_reducer.reduce_scatter()
             else:
                 if dist.get_backend(self._shard_group) == "nccl":
@@ -377,12 +410,21 @@ class B200TrainEngine(TrainEngine):
                     gshard = self.store.grad_shard
         else:
             gshard = self.store.grad_shard
-        res = opt.step(gshard)
-        if self._shard_group is not None:
-            if self._grad_reducer is not None:
-                self._grad_reducer.all_gather_params()
-            else:
-                dist.all_gather_into_tensor(self.store.flat_param, self.store.param_shard.clone(), group=self._shard_group)
+        if fused:
+            from ..ops import functional as OF
+
+            OF.clip_coef_(opt.state, float(opt.cfg.gradient_clipping or 0.0), 1.0)
+            opt.step_count += 1
+            lr = opt.current_lr()
+            self._grad_reducer.adamw_and_all_gather(opt, opt.state, lr)
+            res = {"state": opt.state, "lr": lr}
+        else:
+            res = opt.step(gshard)
+            if self._shard_group is not None:
+                if self._grad_reducer is not None:
+                    self._grad_reducer.all_gather_params()
+                else:
+                    dist.all_gather_into_tensor(self.store.flat_param, self.store.param_shard.clone(), group=self._shard_group)
         st = res["state"].tolist()
         self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
         return dict(self.last_step_stats)

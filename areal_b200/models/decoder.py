@@ -79,6 +79,10 @@ class Attention(nn.Module):
         q, k, v = self.project_qkv(x, pb.position_ids, cos, sin)
         if attn_fn is not None:
             o = attn_fn(q, k, v)
+        elif getattr(self, "sp_size", 1) > 1:
+            from ..parallel.ulysses import ulysses_attention
+
+            o = ulysses_attention(self, q, k, v, pb.cu_seqlens, True, 1.0 / math.sqrt(self.D), pb.tile_info, OF.attention)
         else:
             o = OF.attention(q, k.contiguous() if not k.is_cuda else k, v.contiguous() if not v.is_cuda else v,
                              pb.cu_seqlens, True, 1.0 / math.sqrt(self.D), pb.tile_info)
@@ -129,12 +133,19 @@ class MoEMLP(nn.Module):
         """xs: tokens sorted by (local) expert; counts[e] tokens for expert first_expert+e."""
         outs = []
         off = 0
+        mg_gu = getattr(self.w_gate_up, "main_grad", None)
+        mg_dn = getattr(self.w_down, "main_grad", None)
+        direct = xs.is_cuda and mg_gu is not None and mg_dn is not None and torch.is_grad_enabled()
         for e, n in enumerate(counts):
             if n == 0:
                 continue
             xe = xs[off:off + n]
             ge = first_expert + e
-            outs.append(OF.linear(OF.swiglu(OF.linear(xe, self.w_gate_up[ge])), self.w_down[ge]))
+            if direct:  # weight gradients accumulate straight into the fp32 buffers of expert ge
+                h = OF.linear(xe, self.w_gate_up.detach()[ge], None, mg_gu[ge])
+                outs.append(OF.linear(OF.swiglu(h), self.w_down.detach()[ge], None, mg_dn[ge]))
+            else:
+                outs.append(OF.linear(OF.swiglu(OF.linear(xe, self.w_gate_up[ge])), self.w_down[ge]))
             off += n
         if not outs:
             return xs.new_zeros(0, self.cfg.hidden_size)

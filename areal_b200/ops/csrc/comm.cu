@@ -1,0 +1,295 @@
+// Kernels that fuse compute with cross-GPU data movement over NVLink peer memory.
+// Every rank maps every peer's symmetric buffers, so a kernel can load from / store to a
+// peer with plain ld/st (no TMA multicast, no library collective in between).
+//
+//   signal_barrier     all-to-all flag exchange with a bounded wait (error status, no trap)
+//   rs_sumsq           gradient reduce-scatter by peer loads + squared-norm partial of the shard
+//   norm_allreduce     exchanges the per-shard partials through peer stores -> global sum
+//   adamw_push         sharded AdamW whose bf16 result is written straight into every
+//                      destination buffer (trainer peers = parameter all-gather, rollout
+//                      replicas = weight update)
+//   push_copy          shard-direct copy of a bf16 range to several destinations (weight push)
+//   push_cast_fp8      same, with an in-kernel block-scaled (1x128) e4m3 cast
+//
+// These replace: FSDP2's NCCL reduce-scatter / all-gather (areal/engine/fsdp_utils/parallel.py:388),
+// the grad-norm all-reduces of areal/engine/fsdp_utils/grad.py:112-190, and the all-gather +
+// NCCL broadcast weight update of areal/engine/fsdp_engine.py:1596-1692.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace ab2 {
+
+static constexpr int MAX_PEERS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_PEERS];
+};
+
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// One CTA. Thread r publishes `epoch` into slot [channel][my_rank] of rank r's signal pad and
+// then waits until slot [channel][r] of the local pad reaches `epoch`. The wait is bounded.
+__global__ void signal_barrier_kernel(PeerPtrs pads, int my_rank, int world, int channel, int epoch,
+                                      long long limit_cycles, int* err) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    int* remote = reinterpret_cast<int*>(pads.p[r]) + channel * MAX_PEERS + my_rank;
+    st_release_sys(remote, epoch);
+    const int* local = reinterpret_cast<const int*>(pads.p[my_rank]) + channel * MAX_PEERS + r;
+    const long long t0 = clock64();
+    while (ld_acquire_sys(local) < epoch) {
+      if (clock64() - t0 > limit_cycles) {
+        set_error(err, ERR_WAIT_PEER_FLAG);
+        break;
+      }
+    }
+  }
+}
+
+// out[i] = sum_r grads[r][lo + i] for i in [0, n); state[0] += sum(out^2).
+__global__ void rs_sumsq_kernel(PeerPtrs grads, int world, long long lo, long long n, float* __restrict__ out,
+                                float* __restrict__ state, float scale) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    reinterpret_cast<float4*>(out)[i] = s;
+    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  acc = warp_sum(acc);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = acc;
+  __syncthreads();
+  if (w == 0) {
+    float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+    t = warp_sum(t);
+    if (l == 0) atomicAdd(state, t);
+  }
+}
+
+// Every rank writes its partial (state[0]) into slot my_rank of every peer's float pad, raises
+// the flag, waits (bounded) for all peers and replaces state[0] by the global sum.
+__global__ void norm_allreduce_kernel(PeerPtrs pads, PeerPtrs fpads, int my_rank, int world, int channel, int epoch,
+                                      float* __restrict__ state, long long limit_cycles, int* err) {
+  __shared__ float vals[MAX_PEERS];
+  const int r = threadIdx.x;
+  if (r < world) {
+    const float mine = state[0];
+    float* rf = reinterpret_cast<float*>(fpads.p[r]) + my_rank;
+    *reinterpret_cast<volatile float*>(rf) = mine;
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(pads.p[r]) + channel * MAX_PEERS + my_rank, epoch);
+    const int* local = reinterpret_cast<const int*>(pads.p[my_rank]) + channel * MAX_PEERS + r;
+    const long long t0 = clock64();
+    bool ok = true;
+    while (ld_acquire_sys(local) < epoch) {
+      if (clock64() - t0 > limit_cycles) { set_error(err, ERR_WAIT_PEER_FLAG); ok = false; break; }
+    }
+    vals[r] = ok ? *reinterpret_cast<volatile float*>(reinterpret_cast<float*>(fpads.p[my_rank]) + r) : 0.f;
+  }
+  __syncthreads();
+  if (r == 0) {
+    float s = 0.f;
+    for (int i = 0; i < world; ++i) s += vals[i];
+    state[0] = s;
+  }
+}
+
+// AdamW on the local shard; the refreshed bf16 values go to dst[k] + lo for every k < ndst.
+__global__ void adamw_push_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                                  const float* __restrict__ g, PeerPtrs dst, int ndst, long long lo,
+                                  const float* __restrict__ state, long long n, float lr, float beta1, float beta2,
+                                  float eps, float wd, float bc1, float bc2) {
+  const float coef = state[1];
+  const bool go = state[2] != 0.f;
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 pv = reinterpret_cast<float4*>(p)[i];
+    if (go) {
+      const float4 gv = reinterpret_cast<const float4*>(g)[i];
+      float4 mv = reinterpret_cast<float4*>(m)[i], vv = reinterpret_cast<float4*>(v)[i];
+      float* pp = reinterpret_cast<float*>(&pv);
+      float* mm = reinterpret_cast<float*>(&mv);
+      float* vq = reinterpret_cast<float*>(&vv);
+      const float* gg = reinterpret_cast<const float*>(&gv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float gi = gg[e] * coef;
+        mm[e] = beta1 * mm[e] + (1.f - beta1) * gi;
+        vq[e] = beta2 * vq[e] + (1.f - beta2) * gi * gi;
+        float x = pp[e];
+        x -= lr * wd * x;
+        x -= lr * (mm[e] / bc1) / (sqrtf(vq[e] / bc2) + eps);
+        pp[e] = x;
+      }
+      reinterpret_cast<float4*>(p)[i] = pv;
+      reinterpret_cast<float4*>(m)[i] = mv;
+      reinterpret_cast<float4*>(v)[i] = vv;
+    }
+    uint2 pk;
+    pk.x = pack_bf16(pv.x, pv.y);
+    pk.y = pack_bf16(pv.z, pv.w);
+    for (int k = 0; k < ndst; ++k)
+      reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(dst.p[k]) + lo)[i] = pk;
+  }
+}
+
+// dst[k][dst_off + i] = src[i] for a bf16 range (16-byte vectors).
+__global__ void push_copy_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, int ndst, long long dst_off,
+                                 long long n) {
+  const long long n8 = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = reinterpret_cast<const uint4*>(src)[i];
+    for (int k = 0; k < ndst; ++k) reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[k]) + dst_off)[i] = v;
+  }
+}
+
+// 2-D strided copy: rows x cols bf16 from a row-major source (ld_src) into destination k at
+// element offset dst_off[k] with leading dimension ld_dst (tensor-parallel re-sharding: a
+// row or column slice of a weight lands in the replica's TP-local tensor).
+__global__ void push_copy2d_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src, PeerPtrs dst, int ndst,
+                                   long long dst_off, long long ld_dst, int rows, int cols) {
+  const int c8 = cols >> 3;
+  const long long total = (long long)rows * c8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / c8), c = (int)(i - (long long)r * c8);
+    const uint4 v = reinterpret_cast<const uint4*>(src + (size_t)r * ld_src)[c];
+    for (int k = 0; k < ndst; ++k)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[k]) + dst_off + (size_t)r * ld_dst)[c] = v;
+  }
+}
+
+// Block-scaled fp8 cast fused into the push: one warp per 128-element block of the source
+// range; amax -> scale (optionally rounded up to a power of two, UE8M0 style) -> e4m3 values
+// to dstq[k] + off and the fp32 scale to dsts[k] + off / 128.
+__global__ void push_cast_fp8_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dstq, PeerPtrs dsts, int ndst,
+                                     long long dst_off, long long n_blocks, int pow2) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long b = warp; b < n_blocks; b += nwarps) {
+    const uint2 raw = reinterpret_cast<const uint2*>(src + b * 128)[lane];
+    const float2 a = unpack_bf16(raw.x), c = unpack_bf16(raw.y);
+    float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(c.x), fabsf(c.y)));
+    amax = warp_max(amax);
+    float scale = fmaxf(amax, 1e-12f) / 448.f;
+    if (pow2) scale = exp2f(ceilf(log2f(scale)));
+    const float inv = 1.f / scale;
+    __nv_fp8x4_e4m3 q(make_float4(a.x * inv, a.y * inv, c.x * inv, c.y * inv));
+    for (int k = 0; k < ndst; ++k) {
+      reinterpret_cast<__nv_fp8x4_e4m3*>(reinterpret_cast<uint8_t*>(dstq.p[k]) + dst_off + b * 128)[lane] = q;
+      if (lane == 0) reinterpret_cast<float*>(dsts.p[k])[dst_off / 128 + b] = scale;
+    }
+  }
+}
+
+static int grid_of(long long work) {
+  long long b = (work + 255) / 256;
+  if (b > 148 * 8) b = 148 * 8;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+}  // namespace ab2
+
+extern "C" {
+using namespace ab2;
+
+static PeerPtrs make_ptrs(void* const* ptrs, int n) {
+  PeerPtrs pp;
+  for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < n ? ptrs[i] : nullptr;
+  return pp;
+}
+
+// pads: device pointers of every rank's signal pad (int32[channels][16]), indexed by rank.
+// timeout_ms bounds the wait; on expiry the kernel records ERR_WAIT_PEER_FLAG and returns.
+int ab2_signal_barrier(void* const* pads, int my_rank, int world, int channel, int epoch, int timeout_ms,
+                       void* stream) {
+  if (world > MAX_PEERS) return 10;
+  int* err = ab2host::error_flag();
+  if (!err) return 301;
+  const long long limit = (long long)timeout_ms * 1900000LL;
+  signal_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_ptrs(pads, world), my_rank, world, channel, epoch,
+                                                            limit, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+int ab2_rs_sumsq(void* const* grads, int world, long long lo, long long n, float* out, float* state, float scale,
+                 void* stream) {
+  if (world > MAX_PEERS || (n & 3) || (lo & 3)) return 10;
+  if (n <= 0) return 0;
+  rs_sumsq_kernel<<<grid_of(n / 4), 256, 0, (cudaStream_t)stream>>>(make_ptrs(grads, world), world, lo, n, out, state,
+                                                                    scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+int ab2_norm_allreduce(void* const* pads, void* const* fpads, int my_rank, int world, int channel, int epoch,
+                       float* state, int timeout_ms, void* stream) {
+  if (world > MAX_PEERS) return 10;
+  int* err = ab2host::error_flag();
+  if (!err) return 301;
+  norm_allreduce_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_ptrs(pads, world), make_ptrs(fpads, world), my_rank,
+                                                            world, channel, epoch, state,
+                                                            (long long)timeout_ms * 1900000LL, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+int ab2_adamw_push(float* p, float* m, float* v, const float* g, void* const* dst, int ndst, long long lo,
+                   const float* state, long long n, float lr, float beta1, float beta2, float eps, float wd, int step,
+                   void* stream) {
+  if (ndst > MAX_PEERS || (n & 3) || (lo & 3)) return 10;
+  if (n <= 0) return 0;
+  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
+  adamw_push_kernel<<<grid_of(n / 4), 256, 0, (cudaStream_t)stream>>>(p, m, v, g, make_ptrs(dst, ndst), ndst, lo, state,
+                                                                      n, lr, beta1, beta2, eps, wd, bc1, bc2);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+int ab2_push_copy(const void* src, void* const* dst, int ndst, long long dst_off, long long n, void* stream) {
+  if (ndst > MAX_PEERS || (n & 7) || (dst_off & 7)) return 10;
+  if (n <= 0 || ndst <= 0) return 0;
+  push_copy_kernel<<<grid_of(n / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, make_ptrs(dst, ndst),
+                                                                     ndst, dst_off, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+int ab2_push_copy2d(const void* src, long long ld_src, void* const* dst, int ndst, long long dst_off, long long ld_dst,
+                    int rows, int cols, void* stream) {
+  if (ndst > MAX_PEERS || (cols & 7) || (dst_off & 7) || (ld_src & 7) || (ld_dst & 7)) return 10;
+  if (rows <= 0 || cols <= 0 || ndst <= 0) return 0;
+  push_copy2d_kernel<<<grid_of((long long)rows * (cols / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)src, ld_src, make_ptrs(dst, ndst), ndst, dst_off, ld_dst, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+// n must be a multiple of 128. dst_off is in elements for the fp8 buffers (scales at off/128).
+int ab2_push_cast_fp8(const void* src, void* const* dstq, void* const* dsts, int ndst, long long dst_off, long long n,
+                      int pow2_scales, void* stream) {
+  if (ndst > MAX_PEERS || (n & 127) || (dst_off & 127)) return 10;
+  if (n <= 0 || ndst <= 0) return 0;
+  const long long nb = n / 128;
+  push_cast_fp8_kernel<<<grid_of(nb * 32), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src,
+                                                                           make_ptrs(dstq, ndst), make_ptrs(dsts, ndst),
+                                                                           ndst, dst_off, nb, pow2_scales);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+}

@@ -1,0 +1,299 @@
+// Rollout-engine kernels: paged KV-cache append, paged decode attention (split-KV with a
+// combine pass), and fused temperature / Gumbel-max sampling that also returns the
+// log-probability of the sampled token.
+//
+// These take the place of the SGLang / vLLM (FlashInfer, sgl_kernel) kernels that the
+// reference reaches through areal/engine/sglang_remote.py and areal/engine/vllm_remote.py.
+#include "common.cuh"
+
+namespace ab2 {
+
+// ------------------------------------------------------------------ KV append
+// k, v: [n, Hkv, D] (token stride given) -> cache[slot[n]] where the cache is
+// [num_slots, Hkv, D] (slot = page * page_size + offset). slot < 0 skips the token.
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                 __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
+                                 const int* __restrict__ slots, int n, int row_elems, long long k_stride,
+                                 long long v_stride) {
+  const int vec = row_elems >> 3;
+  const long long total = (long long)n * vec;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / vec), c = (int)(i - (long long)t * vec);
+    const int s = slots[t];
+    if (s < 0) continue;
+    reinterpret_cast<uint4*>(kc + (size_t)s * row_elems)[c] = reinterpret_cast<const uint4*>(k + (size_t)t * k_stride)[c];
+    reinterpret_cast<uint4*>(vc + (size_t)s * row_elems)[c] = reinterpret_cast<const uint4*>(v + (size_t)t * v_stride)[c];
+  }
+}
+
+// ------------------------------------------------------------------ paged decode attention
+// One CTA = (sequence b, kv head h, split s). 128 threads = 16 groups of 8 lanes; a group
+// handles one cached token at a time (8 lanes x 16 dims = D 128; for D 64 each lane holds 8).
+// Every group keeps an online-softmax state for the G = Hq/Hkv query heads that share the
+// kv head; groups are merged through shared memory; the CTA writes an (m, l, o) partial.
+template <int D, int G>
+__global__ void __launch_bounds__(128)
+paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ page_table,
+                    const int* __restrict__ seq_lens, float* __restrict__ part_o, float* __restrict__ part_ml,
+                    int Hq, int Hkv, int page_size, int max_pages, int num_splits, float scale) {
+  constexpr int EPL = D / 8;  // elements per lane
+  const int b = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
+  const int len = seq_lens[b];
+  const int per = (len + num_splits - 1) / num_splits;
+  const int t0 = sp * per, t1 = min(len, t0 + per);
+  const int grp = threadIdx.x >> 3, lg = threadIdx.x & 7;
+  const float sl2 = scale * 1.4426950408889634f;
+
+  float qr[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const __nv_bfloat16* qp = q + ((size_t)b * Hq + (size_t)h * G + g) * D + lg * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; e += 2) {
+      const float2 f = unpack_bf16(*reinterpret_cast<const uint32_t*>(qp + e));
+      qr[g][e] = f.x * sl2;
+      qr[g][e + 1] = f.y * sl2;
+    }
+  }
+  float m[G], l[G], o[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) o[g][e] = 0.f;
+  }
+  const int* pt = page_table + (size_t)b * max_pages;
+  for (int t = t0 + grp; t < t1; t += 16) {
+    const int page = pt[t / page_size];
+    const size_t slot = (size_t)page * page_size + (t % page_size);
+    const __nv_bfloat16* kp = kc + (slot * Hkv + h) * D + lg * EPL;
+    const __nv_bfloat16* vp = vc + (slot * Hkv + h) * D + lg * EPL;
+    float kf[EPL], vf[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; e += 8) {
+      const uint4 kk = *reinterpret_cast<const uint4*>(kp + e);
+      const uint4 vv = *reinterpret_cast<const uint4*>(vp + e);
+      const uint32_t ka[4] = {kk.x, kk.y, kk.z, kk.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack_bf16(ka[j]), c = unpack_bf16(va[j]);
+        kf[e + 2 * j] = a.x; kf[e + 2 * j + 1] = a.y;
+        vf[e + 2 * j] = c.x; vf[e + 2 * j + 1] = c.y;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) s += qr[g][e] * kf[e];
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      const float mn = fmaxf(m[g], s);
+      const float a = fast_exp2(m[g] - mn), p = fast_exp2(s - mn);
+      l[g] = l[g] * a + p;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) o[g][e] = o[g][e] * a + p * vf[e];
+      m[g] = mn;
+    }
+  }
+  // merge the 16 groups, one query head at a time (keeps shared memory at 8 KB)
+  __shared__ float sm_m[16][G], sm_l[16][G];
+  __shared__ float sm_o[16][D];
+  if (lg == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) { sm_m[grp][g] = m[g]; sm_l[grp][g] = l[g]; }
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sm_o[grp][lg * EPL + e] = o[g][e];
+    __syncthreads();
+    if (threadIdx.x < D) {
+      const int d = threadIdx.x;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) mm = fmaxf(mm, sm_m[r][g]);
+      float ll = 0.f, oo = 0.f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const float w = (sm_m[r][g] == -INFINITY) ? 0.f : fast_exp2(sm_m[r][g] - mm);
+        ll += sm_l[r][g] * w;
+        oo += sm_o[r][d] * w;
+      }
+      const size_t pidx = ((size_t)b * Hq + (size_t)h * G + g) * num_splits + sp;
+      part_o[pidx * D + d] = oo;
+      if (d == 0) {
+        part_ml[pidx * 2] = mm;
+        part_ml[pidx * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+// out[b, hq, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
+template <int D>
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      __nv_bfloat16* __restrict__ out, int num_splits) {
+  const size_t row = blockIdx.x;  // b * Hq + hq
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
+  float L = 0.f, acc = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float ms = part_ml[(row * num_splits + s) * 2];
+    const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+    L += part_ml[(row * num_splits + s) * 2 + 1] * w;
+    acc += part_o[(row * num_splits + s) * D + d] * w;
+  }
+  out[row * D + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+}
+
+// ------------------------------------------------------------------ sampling
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ float uniform01(uint32_t seed, uint32_t row, uint32_t idx, uint32_t step) {
+  uint32_t h = mix32(seed ^ 0x9e3779b9U);
+  h = mix32(h ^ (row * 0x85ebca6bU + 0x165667b1U));
+  h = mix32(h ^ (step * 0xc2b2ae35U + 0x27d4eb2fU));
+  h = mix32(h ^ idx);
+  return ((h >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0, 1)
+}
+
+struct SampleState {
+  float m, s;      // online max / sum-exp of z
+  float best;      // best perturbed score
+  int best_idx;
+  float best_z;
+};
+__device__ __forceinline__ void sample_merge(SampleState& a, const SampleState& b) {
+  const float mm = fmaxf(a.m, b.m);
+  const float ra = (a.m == -INFINITY) ? 0.f : __expf(a.m - mm);
+  const float rb = (b.m == -INFINITY) ? 0.f : __expf(b.m - mm);
+  a.s = a.s * ra + b.s * rb;
+  a.m = mm;
+  if (b.best > a.best || (b.best == a.best && b.best_idx < a.best_idx && b.best_idx >= 0)) {
+    a.best = b.best; a.best_idx = b.best_idx; a.best_z = b.best_z;
+  }
+}
+
+// One CTA per row. z = logits * inv_temp[row]; token = argmax(z + Gumbel) (argmax z when
+// greedy[row]); logprob = z_token - logsumexp(z). Per-row temperature / seed / greedy flags.
+__global__ void sample_kernel(const float* __restrict__ logits, long long ld, int V,
+                              const float* __restrict__ inv_temp, const int* __restrict__ greedy,
+                              const unsigned int* __restrict__ seeds, unsigned int step,
+                              int* __restrict__ out_tok, float* __restrict__ out_logp) {
+  __shared__ SampleState red[32];
+  const int row = blockIdx.x;
+  const float it = inv_temp[row];
+  const bool gr = greedy[row] != 0;
+  const uint32_t seed = seeds[row];
+  const float* z = logits + (size_t)row * ld;
+  SampleState st;
+  st.m = -INFINITY; st.s = 0.f; st.best = -INFINITY; st.best_idx = -1; st.best_z = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float zi = z[i] * it;
+    if (zi > st.m) { st.s = st.s * __expf(st.m - zi) + 1.f; st.m = zi; } else { st.s += __expf(zi - st.m); }
+    float score = zi;
+    if (!gr) {
+      const float u = uniform01(seed, (uint32_t)row, (uint32_t)i, step);
+      score = zi - __logf(-__logf(u));
+    }
+    if (score > st.best) { st.best = score; st.best_idx = i; st.best_z = zi; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    SampleState y;
+    y.m = __shfl_xor_sync(0xffffffffu, st.m, o);
+    y.s = __shfl_xor_sync(0xffffffffu, st.s, o);
+    y.best = __shfl_xor_sync(0xffffffffu, st.best, o);
+    y.best_idx = __shfl_xor_sync(0xffffffffu, st.best_idx, o);
+    y.best_z = __shfl_xor_sync(0xffffffffu, st.best_z, o);
+    sample_merge(st, y);
+  }
+  const int w = threadIdx.x >> 5, ln = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (ln == 0) red[w] = st;
+  __syncthreads();
+  if (w == 0) {
+    SampleState t;
+    t.m = -INFINITY; t.s = 0.f; t.best = -INFINITY; t.best_idx = -1; t.best_z = 0.f;
+    if (ln < nw) t = red[ln];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      SampleState y;
+      y.m = __shfl_xor_sync(0xffffffffu, t.m, o);
+      y.s = __shfl_xor_sync(0xffffffffu, t.s, o);
+      y.best = __shfl_xor_sync(0xffffffffu, t.best, o);
+      y.best_idx = __shfl_xor_sync(0xffffffffu, t.best_idx, o);
+      y.best_z = __shfl_xor_sync(0xffffffffu, t.best_z, o);
+      sample_merge(t, y);
+    }
+    if (ln == 0) {
+      out_tok[row] = t.best_idx;
+      out_logp[row] = t.best_z - (t.m + __logf(t.s));
+    }
+  }
+}
+
+template <int D, int G>
+static int launch_decode(const void* q, const void* kc, const void* vc, const int* pt, const int* lens,
+                         float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int page_size,
+                         int max_pages, int splits, float scale, cudaStream_t s) {
+  dim3 grid(B, Hkv, splits);
+  paged_decode_kernel<D, G><<<grid, 128, 0, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
+                                                 (const __nv_bfloat16*)vc, pt, lens, part_o, part_ml, Hq, Hkv,
+                                                 page_size, max_pages, splits, scale);
+  decode_combine_kernel<D><<<B * Hq, D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+}  // namespace ab2
+
+extern "C" {
+using namespace ab2;
+
+int ab2_kv_append(const void* k, const void* v, void* kc, void* vc, const int* slots, int n, int Hkv, int D,
+                  long long k_stride, long long v_stride, void* stream) {
+  if (n <= 0) return 0;
+  const int row = Hkv * D;
+  if (row % 8) return 10;
+  long long work = (long long)n * (row / 8);
+  int grid = (int)((work + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  kv_append_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                                                           (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slots, n, row,
+                                                           k_stride, v_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+// Workspace sizes (floats) for ab2_paged_decode: part_o = B*Hq*splits*D, part_ml = B*Hq*splits*2.
+int ab2_paged_decode(const void* q, const void* kc, const void* vc, const int* page_table, const int* seq_lens,
+                     float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int page_size,
+                     int max_pages, int num_splits, float scale, void* stream) {
+  if (B <= 0) return 0;
+  if (Hq % Hkv || num_splits < 1) return 10;
+  const int G = Hq / Hkv;
+  cudaStream_t s = (cudaStream_t)stream;
+#define AB2_DEC(DD, GG)                                                                                   \
+  if (D == DD && G == GG)                                                                                 \
+    return launch_decode<DD, GG>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv,       \
+                                 page_size, max_pages, num_splits, scale, s);
+  AB2_DEC(128, 1) AB2_DEC(128, 2) AB2_DEC(128, 4) AB2_DEC(128, 6) AB2_DEC(128, 8)
+  AB2_DEC(64, 1) AB2_DEC(64, 2) AB2_DEC(64, 4) AB2_DEC(64, 8)
+#undef AB2_DEC
+  return 11;
+}
+
+int ab2_sample(const float* logits, long long ld, int B, int V, const float* inv_temp, const int* greedy,
+               const unsigned int* seeds, unsigned int step, int* out_tok, float* out_logp, void* stream) {
+  if (B <= 0) return 0;
+  sample_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(logits, ld, V, inv_temp, greedy, seeds, step, out_tok, out_logp);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+}

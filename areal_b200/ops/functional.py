@@ -74,9 +74,10 @@ class _Linear(torch.autograd.Function):
     when the parameter carries one (flat-shard training), else are returned in bf16."""
 
     @staticmethod
-    def forward(ctx, x, w, resid):
+    def forward(ctx, x, w, resid, grad_buf=None):
         ctx.save_for_backward(x, w)
         ctx.has_resid = resid is not None
+        ctx.grad_buf = grad_buf
         x2 = x.reshape(-1, x.shape[-1])
         if resid is not None:
             y = gemm(x2, w, epi=EPI_BF16_RESID, resid=resid.reshape(-1, w.shape[0]))
@@ -94,21 +95,26 @@ class _Linear(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).view_as(x)
-        if ctx.needs_input_grad[1]:
+        if ctx.grad_buf is not None:
+            gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.grad_buf, epi=EPI_F32_ACC)
+        elif ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
             if mg is not None:
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, epi=EPI_F32_ACC)
                 dw = None
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
-        return dx, dw, (dy if ctx.has_resid else None)
+        return dx, dw, (dy if ctx.has_resid else None), None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = None,
+           grad_buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w^T (+ resid)``. ``grad_buf`` (fp32, shape of ``w``): the weight gradient is
+    accumulated there even when ``w`` is a detached view (slices of stacked expert weights)."""
     if not x.is_cuda:
         y = F.linear(x, w)
         return y + resid if resid is not None else y
-    return _Linear.apply(x, w, resid)
+    return _Linear.apply(x, w, resid, grad_buf)
 
 
 # ----------------------------------------------------------------------------- RMSNorm
@@ -137,12 +143,14 @@ class _RMSNorm(torch.autograd.Function):
         else:
             rc = _L().ab2_rmsnorm_fwd(x2.data_ptr(), None, w.data_ptr(), y.data_ptr(), None, rstd.data_ptr(), rows, H,
                                       eps, _s())
-            new_res = x2
+            new_res = None
             saved_x = x2
         _lib.check(rc, "ab2_rmsnorm_fwd")
         ctx.save_for_backward(saved_x, w, rstd)
         ctx.has_resid = resid is not None
         ctx.shape = x.shape
+        if new_res is None:  # the residual stream is the input itself; the caller keeps using it
+            return y.view(x.shape), x2.new_empty(0)
         return y.view(x.shape), new_res.view(x.shape)
 
     @staticmethod
@@ -150,7 +158,7 @@ class _RMSNorm(torch.autograd.Function):
         x2, w, rstd = ctx.saved_tensors
         rows, H = x2.shape
         dy2 = dy.reshape(rows, H).contiguous()
-        dr2 = dres.reshape(rows, H).contiguous() if dres is not None else None
+        dr2 = dres.reshape(rows, H).contiguous() if (dres is not None and ctx.has_resid) else None
         dx = torch.empty_like(x2)
         mg = getattr(w, "main_grad", None)
         dw32 = mg if mg is not None else torch.zeros(H, device=x2.device, dtype=torch.float32)
@@ -165,7 +173,11 @@ def rmsnorm(x, w, eps: float = 1e-6, resid=None):
     """Returns ``(normed, residual_stream)`` where ``residual_stream = x (+ resid)``."""
     if not x.is_cuda:
         return rmsnorm_ref(x, w, eps, resid)
-    return _RMSNorm.apply(x.contiguous(), w, None if resid is None else resid.contiguous(), eps)
+    x = x.contiguous()
+    if resid is None:
+        y, _ = _RMSNorm.apply(x, w, None, eps)
+        return y, x
+    return _RMSNorm.apply(x, w, resid.contiguous(), eps)
 
 
 # ----------------------------------------------------------------------------- RoPE

@@ -39,6 +39,9 @@ _SIGS = {
     "ab2_logprob_fwd": ([c_void_p] * 6 + [c_int, c_int, c_ll, c_float, c_int, c_int, c_void_p], c_int),
     "ab2_logprob_bwd": ([c_void_p] * 7 + [c_int, c_int, c_ll, c_ll, c_float, c_int, c_void_p], c_int),
     "ab2_logprob_combine": ([c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "ab2_kv_append": ([c_void_p] * 5 + [c_int, c_int, c_int, c_ll, c_ll, c_void_p], c_int),
+    "ab2_paged_decode": ([c_void_p] * 8 + [c_int] * 7 + [c_float, c_void_p], c_int),
+    "ab2_sample": ([c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint, c_void_p, c_void_p, c_void_p], c_int),
     "ab2_attn_fwd": ([c_void_p] * 7 + [c_int] * 5 + [c_ll] * 4 + [c_float, c_int, c_void_p], c_int),
 }
 
@@ -87,15 +90,48 @@ def get_lib():
                 continue  # optional symbol from a newer source file; checked at call time
             fn.argtypes = args
             fn.restype = res
-        _LIB = lib
+        _LIB = _CountingLib(lib)
     return _LIB
+
+
+# Number of kernels each exported launcher enqueues (used for launch accounting).
+_KERNELS_PER_CALL = {"ab2_paged_decode": 2, "ab2_kernel_error": 0, "ab2_runtime_init": 0, "ab2_num_sms": 0}
+LAUNCHES = {"count": 0}
+
+
+class _CountingLib:
+    """Proxy over the CDLL that counts kernel launches issued through it."""
+
+    def __init__(self, lib):
+        object.__setattr__(self, "_lib", lib)
+        object.__setattr__(self, "_cache", {})
+
+    def __getattr__(self, name):
+        c = self._cache
+        if name in c:
+            return c[name]
+        fn = getattr(self._lib, name)
+        n = _KERNELS_PER_CALL.get(name, 1)
+        if n == 0:
+            c[name] = fn
+            return fn
+
+        def call(*a, _fn=fn, _n=n):
+            LAUNCHES["count"] += _n
+            return _fn(*a)
+        c[name] = call
+        return call
+
+
+def launch_count() -> int:
+    return LAUNCHES["count"]
 
 
 def declare(name: str, argtypes, restype=c_int) -> None:
     """Registers the signature of an additional exported symbol."""
     _SIGS[name] = (argtypes, restype)
-    if _LIB is not None and hasattr(_LIB, name):
-        fn = getattr(_LIB, name)
+    if _LIB is not None and hasattr(_LIB._lib, name):
+        fn = getattr(_LIB._lib, name)
         fn.argtypes, fn.restype = argtypes, restype
 
 

@@ -1,0 +1,214 @@
+"""Trainer -> rollout weight push over NVLink peer memory.
+
+Every trainer rank owns a contiguous shard of the flat bf16 parameter space. On an update it
+writes exactly that shard into the parameter buffers of every rollout replica with one kernel
+(:func:`ab2_push_copy`, or :func:`ab2_push_cast_fp8` for block-scaled fp8 rollout weights), so
+all trainer GPUs push concurrently, nothing is gathered to rank 0 and no tensor is touched
+twice. For tensor-parallel rollout replicas the plan below cuts every parameter into the row /
+column slices each TP rank owns and emits 1-D or 2-D strided copies
+(:func:`ab2_push_copy2d`).
+
+Compared with the reference's ``xccl`` path (``areal/engine/fsdp_engine.py:1596-1692``: full
+``full_tensor()`` all-gather on every trainer rank, then per-tensor NCCL broadcast from rank 0
+in 1 GiB buckets with an HTTP round-trip per bucket) the bytes crossing NVLink drop from
+``(world-1)/world * P`` (gather) ``+ P`` per replica from one source port to ``P / n_train``
+per trainer per replica, spread over all ports. The NCCL broadcast path is kept as
+:class:`BroadcastWeightPusher` for baseline measurements.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..api.io_struct import WeightUpdateMeta
+from ..ops import lib as oplib
+from ..utils import logging as alog
+from .symm import ptr_array
+
+logger = alog.getLogger("weight_push")
+
+
+# --------------------------------------------------------------------------- reshard plan
+@dataclass
+class CopyOp:
+    src_off: int        # element offset in the trainer's flat buffer
+    dst_tp: int         # destination TP rank inside a replica
+    dst_off: int        # element offset in that TP rank's flat buffer
+    rows: int
+    cols: int
+    ld_src: int
+    ld_dst: int
+
+    @property
+    def contiguous(self) -> bool:
+        return self.rows == 1 or (self.cols == self.ld_src and self.cols == self.ld_dst)
+
+
+def tp_layout_of(cfg, name: str, shape: tuple, tp: int):
+    """How a native parameter is split for tensor-parallel inference.
+
+    Returns a list (one entry per TP rank) of lists of ``(row0, row1, col0, col1)`` source
+    blocks that are concatenated (along rows) into the rank-local tensor."""
+    if tp == 1 or len(shape) == 1 and not name.endswith("qkv_bias"):
+        return [[(0, shape[0], 0, shape[1] if len(shape) > 1 else 1)] for _ in range(tp)]
+    D, nq, nkv = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    R = shape[0]
+    C = shape[1] if len(shape) > 1 else 1
+    out = []
+    for j in range(tp):
+        if name.endswith("qkv_proj") or name.endswith("qkv_bias"):
+            qr, kr = nq * D, nkv * D
+            q0, q1 = j * qr // tp, (j + 1) * qr // tp
+            k0, k1 = j * kr // tp, (j + 1) * kr // tp
+            out.append([(q0, q1, 0, C), (qr + k0, qr + k1, 0, C), (qr + kr + k0, qr + kr + k1, 0, C)])
+        elif name.endswith("gate_up_proj"):
+            I = R // 2
+            a, b = j * I // tp, (j + 1) * I // tp
+            out.append([(a, b, 0, C), (I + a, I + b, 0, C)])
+        elif name.endswith("o_proj") or name.endswith("down_proj"):
+            a, b = j * C // tp, (j + 1) * C // tp
+            out.append([(0, R, a, b)])
+        elif name in ("embed_tokens", "lm_head"):
+            a, b = j * R // tp, (j + 1) * R // tp
+            out.append([(a, b, 0, C)])
+        else:
+            out.append([(0, R, 0, C)])
+    return out
+
+
+def build_push_plan(cfg, names, offsets, shapes, shard_range, tp: int, dst_offsets: list[dict]) -> list[CopyOp]:
+    """Copy operations that move the part of ``[shard_range)`` of the trainer's flat buffer that
+    each TP rank needs. ``dst_offsets[j][name]`` is the element offset of ``name`` in TP rank
+    j's flat buffer."""
+    lo, hi = shard_range
+    ops: list[CopyOp] = []
+    for name, off, shape in zip(names, offsets, shapes):
+        numel = 1
+        for s in shape:
+            numel *= s
+        if off + numel <= lo or off >= hi:
+            continue
+        C = shape[1] if len(shape) > 1 else 1
+        if len(shape) > 2:  # stacked experts: treat as [E*rows, cols]
+            C = shape[-1]
+        R = numel // C
+        layout = tp_layout_of(cfg, name, (R, C), tp) if len(shape) <= 2 else [[(0, R, 0, C)] for _ in range(tp)]
+        for j, blocks in enumerate(layout):
+            drow = 0
+            ldd = None
+            for (r0, r1, c0, c1) in blocks:
+                w = c1 - c0
+                ldd = w
+                # rows of this block that intersect the shard (a row is cut at most at its ends)
+                for r in _row_segments(off, C, r0, r1, c0, c1, lo, hi):
+                    (ra, rb, ca, cb) = r
+                    src = off + ra * C + ca
+                    dst = dst_offsets[j][name] + (drow + ra - r0) * w + (ca - c0)
+                    ops.append(CopyOp(src, j, dst, rb - ra, cb - ca, C, w))
+                drow += r1 - r0
+    return ops
+
+
+def _row_segments(off, C, r0, r1, c0, c1, lo, hi):
+    """Splits block rows [r0,r1) x cols [c0,c1) of a tensor at flat offset ``off`` (row width
+    ``C``) into pieces fully inside the flat range [lo, hi): at most one partial row before and
+    one after a run of full rows. Returns ``(row_a, row_b, col_a, col_b)`` tuples."""
+    def ceil_div(a, b):
+        return -((-a) // b)
+
+    full_a = max(r0, ceil_div(lo - off - c0, C))
+    full_b = min(r1, (hi - off - c1) // C + 1)
+    out = []
+    cand = set()
+    if full_a < full_b:
+        cand.update((full_a - 1, full_b))
+    else:
+        base = max(r0, (max(lo, off) - off) // C - 1)
+        cand.update(range(base, min(r1, base + 4)))
+    pre, post = [], []
+    for r in sorted(cand):
+        if r < r0 or r >= r1 or (full_a < full_b and full_a <= r < full_b):
+            continue
+        a, b = max(off + r * C + c0, lo), min(off + r * C + c1, hi)
+        if a < b:
+            seg = (r, r + 1, a - off - r * C, b - off - r * C)
+            (pre if (full_a >= full_b or r < full_a) else post).append(seg)
+    out += pre
+    if full_a < full_b:
+        out.append((full_a, full_b, c0, c1))
+    out += post
+    return out
+
+
+# --------------------------------------------------------------------------- pushers
+class DistributedWeightPusher:
+    """Shard-direct push from every trainer rank into every rollout rank (replicas with the
+    trainer's flat layout; TP = 1)."""
+
+    def __init__(self, train_engine, rollout_client, meta: WeightUpdateMeta):
+        self.train, self.client, self.meta = train_engine, rollout_client, meta
+        self.bus = rollout_client.bus
+        self.split = rollout_client.split
+        if train_engine.store.flat_param.data_ptr() not in train_engine._symm_handles:
+            raise RuntimeError("the trainer's parameter buffer is not in symmetric memory; cannot push peer to peer")
+        self.dst_ptrs = train_engine.peer_ptrs(train_engine.store.flat_param, self.split.rollout_ranks)
+        self.seq = 0
+        self.last_ms = 0.0
+        self.last_gbps = 0.0
+
+    def push(self, meta: Optional[WeightUpdateMeta] = None) -> float:
+        meta = meta or self.meta
+        eng = self.train
+        head = eng.local_index == 0
+        t0 = time.perf_counter()
+        if head:
+            self.bus.put(f"wu/{self.seq}/pause", 1)
+        for r in self.split.rollout_ranks:
+            self.bus.get(f"wu/{self.seq}/ack/{r}")
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        sh = eng.store.param_shard
+        rc = oplib.get_lib().ab2_push_copy(sh.data_ptr(), ptr_array(self.dst_ptrs), len(self.dst_ptrs),
+                                           eng.store.shard_range[0], sh.numel(), oplib.stream_ptr())
+        oplib.check(rc, "ab2_push_copy")
+        ev1.record()
+        torch.cuda.current_stream().synchronize()
+        dev_ms = ev0.elapsed_time(ev1)
+        if eng.cpu_group is not None:
+            dist.barrier(group=eng.cpu_group)
+        if head:
+            self.bus.put(f"wu/{self.seq}/done", {"version": meta.version if meta.version is not None else eng.get_version() + 1})
+        self.seq += 1
+        self.last_ms = (time.perf_counter() - t0) * 1e3
+        self.last_dev_ms = dev_ms
+        self.last_gbps = sh.numel() * 2 * len(self.dst_ptrs) / max(dev_ms, 1e-6) / 1e6
+        return self.last_ms
+
+
+class BroadcastWeightPusher:
+    """NCCL baseline: rank-0-rooted broadcast of the whole flat buffer to the rollout ranks in
+    buckets (the data movement of the reference's xccl path, minus its HTTP round trips)."""
+
+    def __init__(self, train_engine, rollout_client, group, bucket_mb: int = 1024):
+        self.train, self.client, self.group, self.bucket = train_engine, rollout_client, group, bucket_mb * 1024 * 1024 // 2
+        self.bus, self.split, self.seq = rollout_client.bus, rollout_client.split, 0
+
+    def push(self, meta: Optional[WeightUpdateMeta] = None) -> float:
+        eng = self.train
+        t0 = time.perf_counter()
+        if eng.local_index == 0:
+            self.bus.put(f"wu/{self.seq}/pause", 1)
+        for r in self.split.rollout_ranks:
+            self.bus.get(f"wu/{self.seq}/ack/{r}")
+        flat = eng.store.flat_param
+        if eng.local_index == 0:
+            for a in range(0, flat.numel(), self.bucket):
+                dist.broadcast(flat[a:a + self.bucket], src=self.split.train_ranks[0], group=self.group)
+            torch.cuda.current_stream().synchronize()
+            self.bus.put(f"wu/{self.seq}/done", {"version": (meta.version if meta and meta.version is not None else eng.get_version() + 1)})
+        self.seq += 1
+        return (time.perf_counter() - t0) * 1e3

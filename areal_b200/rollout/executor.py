@@ -1,0 +1,308 @@
+"""Streaming rollout executor: staleness-gated admission of workflow episodes, asynchronous
+execution, ordered collection of finished trajectories into training batches.
+
+Semantics follow the reference's ``areal/infra/workflow_executor.py`` (BatchTaskDispatcher
+:284-770: producer admits tasks only while ``not paused and capacity > 0``; ``wait`` drains
+all finished results, orders them by creation time (task id in deterministic mode), returns
+the first ``count`` shuffled and keeps the rest; ``pause/resume`` gate admission only.
+WorkflowExecutor :772-1492: workflow resolution, accept filter, trajectory format check,
+``submit`` :1277, ``wait`` :1307, ``rollout_batch`` :1358, ``prepare_batch`` :1393).
+"""
+from __future__ import annotations
+
+import collections
+import inspect
+import json
+import os
+import random
+import threading
+import time
+from typing import Any, Callable, Optional
+
+import torch
+
+from ..api.cli_args import InferenceEngineConfig
+from ..api.workflow_api import AgentWorkflow, RolloutWorkflow
+from ..utils import data as D
+from ..utils import logging as alog
+from ..utils.dynamic_import import import_from_string
+from .staleness import StalenessManager
+from .task_runner import AsyncTaskRunner, TaskQueueFullError, TaskResult
+
+logger = alog.getLogger("rollout_executor")
+
+ROLLOUT_POLL_S = 0.05
+REQUIRED_KEYS = ("input_ids", "attention_mask")
+
+
+def check_trajectory_format(traj: Any, expected_keys: Optional[set] = None) -> bool:
+    """Validates a trajectory: dict of tensors with a shared ``[n, L]`` leading shape,
+    ``input_ids`` and ``attention_mask`` present. Raises ``ValueError`` on mismatch."""
+    if traj is None:
+        return True
+    if not isinstance(traj, dict):
+        raise ValueError(f"trajectory must be a dict or None, got {type(traj).__name__}")
+    for k in REQUIRED_KEYS:
+        if k not in traj:
+            raise ValueError(f"trajectory lacks required key '{k}'")
+    ids = traj["input_ids"]
+    if not torch.is_tensor(ids) or ids.dim() != 2:
+        raise ValueError("input_ids must be a 2-D tensor [n, L]")
+    n, L = ids.shape
+    for k, v in traj.items():
+        if torch.is_tensor(v):
+            if v.shape[0] != n:
+                raise ValueError(f"'{k}' batch dim {v.shape[0]} != {n}")
+            if v.dim() >= 2 and v.shape[1] != L and k not in ("rewards",):
+                raise ValueError(f"'{k}' sequence dim {v.shape[1]} != {L}")
+    if expected_keys is not None and set(traj.keys()) != expected_keys:
+        raise ValueError(f"trajectory keys {sorted(traj)} differ from the first trajectory's {sorted(expected_keys)}")
+    return True
+
+
+class WorkflowExecutor:
+    def __init__(self, config: InferenceEngineConfig, inference_engine, staleness_manager: Optional[StalenessManager] = None,
+                 dp_world_size: int = 1):
+        self.config = config
+        self.engine = inference_engine
+        self.dp_world_size = max(1, dp_world_size)
+        mc = config.max_concurrent_rollouts or config.consumer_batch_size
+        self.max_concurrent = max(1, mc // self.dp_world_size)
+        self.consumer_bs = max(1, config.consumer_batch_size // self.dp_world_size)
+        qsize = config.queue_size or self.max_concurrent * 16
+        self.staleness = staleness_manager or StalenessManager(inference_engine, self.max_concurrent, self.consumer_bs,
+                                                               config.max_head_offpolicyness)
+        self.runner = AsyncTaskRunner(max_queue_size=qsize)
+        self._pending: collections.deque = collections.deque()
+        self._pending_lock = threading.Lock()
+        self._results: list[TaskResult] = []
+        self._results_lock = threading.Lock()
+        self._task_results: dict[int, Any] = {}
+        self._paused = threading.Event()
+        self._stop = threading.Event()
+        self._threads: list[threading.Thread] = []
+        self._exc: Optional[BaseException] = None
+        self._expected_keys: Optional[set] = None
+        self._data_gen = None
+        self._dump_fh = None
+        self.queue_size = qsize
+        self.rejected_count = 0
+
+    # ------------------------------------------------------------------ lifecycle
+    def initialize(self):
+        self.runner.initialize()
+        for fn, name in ((self._commit_loop, "rollout-commit"), (self._fetch_loop, "rollout-fetch")):
+            t = threading.Thread(target=self._guard(fn), name=name, daemon=True)
+            t.start()
+            self._threads.append(t)
+        return self
+
+    def destroy(self):
+        self._stop.set()
+        for t in self._threads:
+            t.join(timeout=5)
+        self._threads.clear()
+        self.runner.destroy()
+        if self._dump_fh:
+            self._dump_fh.close()
+
+    def _guard(self, fn):
+        def run():
+            try:
+                fn()
+            except BaseException as e:  # fail fast: surfaced by the next public call
+                logger.error("rollout thread failed: %r", e)
+                self._exc = e
+        return run
+
+    def _check(self):
+        if self._exc is not None:
+            raise RuntimeError("rollout executor thread failed") from self._exc
+        self.runner.check_health()
+
+    # ------------------------------------------------------------------ producer / consumer
+    def _commit_loop(self):
+        while not self._stop.is_set():
+            moved = False
+            if not self._paused.is_set():
+                while self.staleness.get_capacity() > 0:
+                    with self._pending_lock:
+                        if not self._pending:
+                            break
+                        tid, factory = self._pending.popleft()
+                    try:
+                        self.runner.submit(factory, task_id=tid)
+                    except TaskQueueFullError:
+                        with self._pending_lock:
+                            self._pending.appendleft((tid, factory))
+                        break
+                    self.staleness.on_rollout_submitted()
+                    moved = True
+            if not moved:
+                time.sleep(0.002)
+
+    def _fetch_loop(self):
+        while not self._stop.is_set():
+            r = self.runner.poll(timeout=ROLLOUT_POLL_S)
+            if r is None:
+                continue
+            if r.error is not None:
+                self.staleness.on_rollout_rejected()
+                raise RuntimeError(f"workflow episode {r.task_id} failed") from r.error
+            traj, accepted = r.data
+            if accepted:
+                self.staleness.on_rollout_accepted()
+                with self._results_lock:
+                    self._results.append(TaskResult(r.task_id, traj, r.create_time))
+                    self._task_results[r.task_id] = traj
+            else:
+                self.staleness.on_rollout_rejected()
+                self.rejected_count += 1
+                with self._results_lock:
+                    self._task_results[r.task_id] = None
+
+    # ------------------------------------------------------------------ workflow resolution
+    def _resolve_workflow(self, workflow, workflow_kwargs) -> RolloutWorkflow:
+        kw = workflow_kwargs or {}
+        if isinstance(workflow, str):
+            workflow = import_from_string(workflow)
+        if inspect.isclass(workflow):
+            workflow = workflow(**kw)
+        if isinstance(workflow, RolloutWorkflow):
+            return workflow
+        if isinstance(workflow, AgentWorkflow) or hasattr(workflow, "run"):
+            from .workflows.agent import AgentRolloutAdapter
+
+            return AgentRolloutAdapter(workflow, self.config)
+        raise TypeError(f"cannot use {workflow!r} as a rollout workflow")
+
+    def _make_task(self, data, workflow: RolloutWorkflow, should_accept_fn, is_eval: bool, task_id: int):
+        async def run():
+            from . import workflow_context as wctx
+
+            with wctx.scoped(is_eval=is_eval, task_id=task_id):
+                traj = await workflow.arun_episode(self.engine, data)
+            if traj is None:
+                return None, False
+            if self.config.check_trajectory_format:
+                check_trajectory_format(traj, self._expected_keys)
+                if self._expected_keys is None and isinstance(traj, dict):
+                    self._expected_keys = set(traj.keys())
+            ok = True if should_accept_fn is None else bool(should_accept_fn(traj))
+            if ok and self.config.dump_to_file:
+                self._dump(traj, task_id)
+            return traj, ok
+        return run
+
+    def _dump(self, traj, task_id):
+        root = os.path.join(self.config.fileroot or "/tmp/areal", "rollout_dump")
+        os.makedirs(root, exist_ok=True)
+        if self._dump_fh is None:
+            self._dump_fh = open(os.path.join(root, f"v{self.engine.get_version()}_{os.getpid()}.jsonl"), "a")
+        rec = {"task_id": task_id, "version": self.engine.get_version()}
+        for k, v in traj.items():
+            if torch.is_tensor(v):
+                rec[k] = v.tolist()
+        self._dump_fh.write(json.dumps(rec) + "\n")
+        self._dump_fh.flush()
+
+    # ------------------------------------------------------------------ public API
+    def submit(self, data: dict[str, Any], workflow=None, workflow_kwargs=None, should_accept_fn=None,
+               task_id: Optional[int] = None, is_eval: bool = False) -> int:
+        self._check()
+        wf = self._resolve_workflow(workflow, workflow_kwargs)
+        if isinstance(should_accept_fn, str):
+            should_accept_fn = import_from_string(should_accept_fn)
+        tid = task_id if task_id is not None else self.runner.new_task_id()
+        with self._pending_lock:
+            if len(self._pending) >= self.queue_size:
+                raise TaskQueueFullError("pending rollout queue is full")
+            self._pending.append((tid, self._make_task(data, wf, should_accept_fn, is_eval, tid)))
+        self.staleness.on_rollout_enqueued()
+        return tid
+
+    def wait(self, count: int, timeout: Optional[float] = None, raise_timeout: bool = True) -> list:
+        """Blocks until ``count`` accepted trajectories exist; returns them (oldest first,
+        shuffled unless deterministic) and keeps the surplus for the next call."""
+        deadline = None if timeout is None else time.monotonic() + timeout
+        while True:
+            self._check()
+            with self._results_lock:
+                if len(self._results) >= count:
+                    key = (lambda r: r.task_id) if self.config.deterministic_sampling else (lambda r: r.create_time)
+                    self._results.sort(key=key)
+                    take, self._results = self._results[:count], self._results[count:]
+                    break
+            if deadline is not None and time.monotonic() > deadline:
+                if raise_timeout:
+                    raise TimeoutError(f"timed out waiting for {count} rollouts")
+                return []
+            time.sleep(0.005)
+        if not self.config.deterministic_sampling:
+            random.shuffle(take)
+        return [r.data for r in take]
+
+    def wait_for_task(self, task_id: int, timeout: Optional[float] = None, raise_timeout: bool = True):
+        deadline = None if timeout is None else time.monotonic() + timeout
+        while True:
+            self._check()
+            with self._results_lock:
+                if task_id in self._task_results:
+                    traj = self._task_results.pop(task_id)
+                    self._results = [r for r in self._results if r.task_id != task_id]
+                    return traj
+            if deadline is not None and time.monotonic() > deadline:
+                if raise_timeout:
+                    raise TimeoutError(f"timed out waiting for task {task_id}")
+                return None
+            time.sleep(0.005)
+
+    def rollout_batch(self, data: list[dict[str, Any]], workflow=None, workflow_kwargs=None, should_accept_fn=None
+                      ) -> dict[str, Any]:
+        for item in data:
+            self.submit(item, workflow, workflow_kwargs, should_accept_fn)
+        trajs = self.wait(len(data))
+        return D.concat_padded_tensors([t for t in trajs if t])
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,
+                      dynamic_bs: bool = False) -> dict[str, Any]:
+        """Keeps the pipeline fed from ``dataloader`` and returns one training batch of
+        ``dataloader.batch_size`` accepted trajectories (``dynamic_bs``: returns once accepted
+        plus rejected reaches the batch size)."""
+        if self._data_gen is None:
+            self._data_gen = D.cycle_dataloader(dataloader)
+        bs = getattr(dataloader, "batch_size", None) or self.consumer_bs
+        bs = max(1, bs // self.dp_world_size) if self.dp_world_size > 1 else bs
+        rej0 = self.rejected_count
+        while True:
+            self._check()
+            with self._pending_lock:
+                npending = len(self._pending)
+            room = min(self.staleness.get_pending_limit() - npending,
+                       self.queue_size - (self.runner.input_queue_size() + npending + bs))
+            fed = 0
+            while fed < room:
+                items = next(self._data_gen)
+                items = items if isinstance(items, list) else [items]
+                for it in items:
+                    self.submit(it, workflow, workflow_kwargs, should_accept_fn)
+                    fed += 1
+            with self._results_lock:
+                have = len(self._results)
+            if have >= bs or (dynamic_bs and have + (self.rejected_count - rej0) >= bs and have > 0):
+                n = min(have, bs)
+                return D.concat_padded_tensors(self.wait(n, timeout=1.0))
+            time.sleep(0.01)
+
+    def pause(self):
+        """Stops admitting new episodes; running ones continue."""
+        self._paused.set()
+
+    def resume(self):
+        self._paused.clear()
+
+    def is_paused(self) -> bool:
+        return self._paused.is_set()
+
+    def get_capacity(self) -> int:
+        return self.staleness.get_capacity()

