@@ -119,6 +119,8 @@ class NativeInferenceEngine(InferenceEngine):
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         if self.model is None:
             if self.model_config is None:
                 if not model_path:
@@ -287,6 +289,8 @@ class NativeInferenceEngine(InferenceEngine):
         while stop_reason not in ("stop", "tool_calls", "length") and len(out_tok) < budget:
             while self._gen_paused.is_set():
                 await asyncio.sleep(0.002)
+            if self._exc is not None:
+                raise RuntimeError("inference engine is dead") from self._exc
             version = self.get_version()
             fut = loop.create_future()
             seq = _Seq(rid=req.rid, tokens=list(tokens), prompt_len=len(tokens), max_new=remaining,
@@ -357,9 +361,16 @@ class NativeInferenceEngine(InferenceEngine):
                     with torch.no_grad():
                         self._step_cpu()
         except BaseException as e:  # surface to waiting clients
-            logger.error("inference engine loop failed: %r", e)
+            import traceback
+
+            logger.error("inference engine loop failed: %r\n%s", e, traceback.format_exc())
             self._exc = e
             self._fail_all(e)
+            self._idle.set()
+            # keep rejecting requests that were queued after the failure so no client hangs
+            while not self._stop.is_set():
+                self._fail_all(e)
+                time.sleep(0.01)
         finally:
             self._idle.set()
 
@@ -634,7 +645,8 @@ class NativeInferenceEngine(InferenceEngine):
         self.stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         n0 = oplib.launch_count()
-        with torch.cuda.graph(graph, stream=self.stream):
+        # thread_local: other threads (the colocated trainer) keep issuing CUDA work meanwhile
+        with torch.cuda.graph(graph, stream=self.stream, capture_error_mode="thread_local"):
             logits = self._decode_forward(B)
         n_kernels = oplib.launch_count() - n0
         oplib.LAUNCHES["count"] = n0  # capture itself executes nothing

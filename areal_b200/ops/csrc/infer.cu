@@ -45,6 +45,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int t0 = sp * per, t1 = min(len, t0 + per);
   const int grp = threadIdx.x >> 3, lg = threadIdx.x & 7;
   const float sl2 = scale * 1.4426950408889634f;
+  const unsigned gmask = 0xFFu << ((threadIdx.x & 31) & ~7);
 
   float qr[G][EPL];
 #pragma unroll
@@ -89,9 +90,11 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       float s = 0.f;
 #pragma unroll
       for (int e = 0; e < EPL; ++e) s += qr[g][e] * kf[e];
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      // only the 8 lanes of this group take part: groups of one warp may run different
+      // numbers of iterations, so a full-warp mask would wait for lanes that never arrive
+      s += __shfl_xor_sync(gmask, s, 1);
+      s += __shfl_xor_sync(gmask, s, 2);
+      s += __shfl_xor_sync(gmask, s, 4);
       const float mn = fmaxf(m[g], s);
       const float a = fast_exp2(m[g] - mn), p = fast_exp2(s - mn);
       l[g] = l[g] * a + p;
