@@ -98,8 +98,13 @@ class RandomTokenDataset(Dataset):
         return dict(input_ids=self.prompts[i].tolist(), max_new_tokens=self.lens[i], reward=self.rewards[i], idx=i)
 
 
-def bernoulli_reward_fn(prompt, completion, prompt_ids, completion_ids, reward=0.0, **kwargs) -> float:
-    return float(reward)
+def bernoulli_reward_fn(prompt, completion, prompt_ids, completion_ids, reward=0.0, idx=0, **kwargs) -> float:
+    """Bernoulli(0.5) reward that is deterministic in (prompt index, sampled completion), so
+    the samples of one group differ and group-normalised advantages are non-zero."""
+    import zlib
+
+    h = zlib.crc32(bytes(int(t) & 0xFF for t in completion_ids[:64])) ^ (int(idx) * 2654435761 & 0xFFFFFFFF)
+    return float((h >> 7) & 1)
 
 
 def _load_records(path: str) -> list[dict]:
