@@ -4,6 +4,9 @@
 //
 // These take the place of the SGLang / vLLM (FlashInfer, sgl_kernel) kernels that the
 // reference reaches through areal/engine/sglang_remote.py and areal/engine/vllm_remote.py.
+#include <mutex>
+
+#include "ab2_noalloc.h"
 #include "common.cuh"
 
 namespace ab2 {
@@ -299,4 +302,41 @@ int ab2_sample(const float* logits, long long ld, int B, int V, const float* inv
   sample_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(logits, ld, V, inv_temp, greedy, seeds, step, out_tok, out_logp);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
+}
+
+// ------------------------------------------------------------------ allocation-free variant
+// Workspace of ab2_paged_decode_noalloc(): partial outputs first, then the (max, sum) pairs.
+// In host code this name is only a stand-in for the symbol, not a device address; the address
+// each device uses is resolved with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_scratch[AB2_NOALLOC_MAX_ROWS * (128 + 2)];
+
+static float* g_noalloc_ptr[64] = {nullptr};
+static std::mutex g_noalloc_mu;
+
+// Resolves (once per device, with that device current) where the built-in workspace lives.
+static float* noalloc_workspace() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess) return nullptr;
+    g_noalloc_ptr[dev] = p;
+  }
+  return g_noalloc_ptr[dev];
+}
+
+extern "C" int ab2_paged_decode_noalloc(const void* q, const void* kc, const void* vc, const int* page_table,
+                                        const int* seq_lens, void* out, int B, int Hq, int Hkv, int D,
+                                        int page_size, int max_pages, int num_splits, float scale, void* stream) {
+  if (B <= 0) return 0;
+  if (num_splits < 1 || Hkv <= 0 || Hq % Hkv) return 10;
+  const long long rows = (long long)B * Hq * num_splits;
+  if (rows > AB2_NOALLOC_MAX_ROWS || D > 128) return 20;  // beyond the built-in workspace
+  float* ws = noalloc_workspace();
+  if (!ws) return 21;
+  float* part_o = ws;
+  float* part_ml = ws + (size_t)AB2_NOALLOC_MAX_ROWS * 128;
+  return ab2_paged_decode(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, D, page_size,
+                          max_pages, num_splits, scale, stream);
 }
