@@ -239,4 +239,4 @@ class InferenceEngine(abc.ABC):
     def export_stats(self) -> dict[str, float]:
         from ..utils import stats_tracker
 
-        return stats_tracker.export_all()
+        return stats_tracker.export_all(distributed=False)

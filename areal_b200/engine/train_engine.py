@@ -575,7 +575,8 @@ class B200TrainEngine(TrainEngine):
         self._offloaded = None
 
     def export_stats(self) -> dict[str, float]:
-        return stats_tracker.export_all(reduce_group=self._cpu_group)
+        # reduce over the trainer ranks only (rollout ranks of a split world do not take part)
+        return stats_tracker.export_all(reduce_group=self._cpu_group, distributed=self._cpu_group is not None)
 
 
 FSDPEngine = B200TrainEngine  # the role FSDPEngine plays in the reference

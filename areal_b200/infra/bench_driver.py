@@ -115,65 +115,25 @@ def run_async_grpo_bench(args, clock_sampler_cls) -> Optional[dict]:
         return _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, parallelism="colocated-1gpu")
 
     # ---------------------------------------------------------------- split world
-    from .spmd import MessageBus, RemoteRolloutClient, RolloutWorker, SplitWorld, build_split_groups
+    from .spmd import init_split_world, make_split_trainer, run_rollout_rank
 
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
     n_train = world // 2
-    split = SplitWorld(n_train, world - n_train, rank)
-    groups = build_split_groups(split, sp_size=1)
-    bus = MessageBus(rank, world)
-    world_ranks = list(range(world))
+    split, groups, bus = init_split_world(n_train, dev)
     cfg = _make_config(args, n_train, max_running=args.prompts_per_gpu_pair * args.group_size, fileroot=fileroot)
     if split.is_trainer:
-        from ..engine.train_engine import B200PPOActor
-
-        actor = B200PPOActor(cfg.actor)
-        actor.set_train_ranks(split.train_ranks, groups)
-        actor.create_process_group()
-        from ..api.io_struct import FinetuneSpec
-
-        actor.initialize(ft_spec=FinetuneSpec(1000, 4096, cfg.train_dataset.batch_size), model_config=model_cfg, seed=1,
-                         param_symm_group=dist.group.WORLD, param_symm_ranks=world_ranks)
-        _instrument_transfers(actor)
-        client = RemoteRolloutClient(bus, split, rank)
         ds = _dataset(args, model_cfg, seed=1)  # only sizes the trainer's bookkeeping
-        trainer = PPOTrainer(cfg, ds, model_config=model_cfg, rollout_engine=client, actor_engine=actor)
-        # initial weights to the rollout replicas, then start
-        actor.update_weights(trainer.weight_update_meta.with_version(0))
+        trainer = make_split_trainer(cfg, model_cfg, split, groups, bus, ds, seed=1)
+        _instrument_transfers(trainer.actor)
         res = _timed_loop(args, trainer, None, clock_sampler_cls, world, rank, model_cfg,
                           parallelism=f"train:dp{n_train}+rollout:dp{world - n_train}", groups=groups)
         if rank == 0:
             bus.put("exit", 1)
         dist.barrier(group=groups["world_cpu"])
         return res if rank == 0 else None
-    # ---- rollout rank
-    from ..engine.flat_params import FlatParamStore
-    from ..engine.infer_engine import NativeInferenceEngine
-    from ..models.decoder import build_model
-    from ..parallel.symm import symm_empty
-
-    dev = torch.device("cuda", local_rank)
-    model = build_model(model_cfg, dtype=torch.bfloat16, device=dev, seed=1)
-    handles = {}
-
-    def alloc(n, dt, d):
-        t, h = symm_empty(n, dt, d, dist.group.WORLD)
-        t.zero_()
-        handles[t.data_ptr()] = h
-        return t
-
-    FlatParamStore(model, n_train, 0, alloc_param=alloc, with_grads=False)
-    engine = NativeInferenceEngine(cfg.rollout, cfg.native_infer, model=model)
-    engine.initialize(device=dev, seed=1)
     ds = _dataset(args, model_cfg, seed=1000 + rank)
-    from torch.utils.data import DataLoader
-
-    dl = DataLoader(ds, batch_size=cfg.train_dataset.batch_size, shuffle=True, drop_last=True, collate_fn=list,
-                    generator=torch.Generator().manual_seed(rank))
     wf = RLVRWorkflow(bernoulli_reward_fn, cfg.gconfig, reward_in_process=True)
-    worker = RolloutWorker(engine, bus, split, dl, wf)
-    worker.run()
-    engine.destroy()
+    run_rollout_rank(cfg, model_cfg, split, groups, bus, ds, wf, dev, seed=1)
     dist.barrier(group=groups["world_cpu"])
     return None
 

@@ -65,6 +65,8 @@ def build_split_groups(split: SplitWorld, sp_size: int = 1, use_cuda: bool = Tru
     if n > 1:
         out["shard"] = dist.new_group(tr)
         out["cpu"] = dist.new_group(tr, backend="gloo") if use_cuda else out["shard"]
+    # weight-update broadcast group (baseline / CPU path): trainer head + every rollout rank
+    out["wu"] = dist.new_group([tr[0]] + split.rollout_ranks)
     dp_size = n // sp_size
     me = split.rank
     for d in range(dp_size):
@@ -126,8 +128,9 @@ class RemoteRolloutClient(InferenceEngine):
     """Trainer-side handle of the rollout ranks: receives ready-made training batches and
     drives the weight-update handshake."""
 
-    def __init__(self, bus: MessageBus, split: SplitWorld, train_rank: int):
+    def __init__(self, bus: MessageBus, split: SplitWorld, train_rank: int, wu_group=None):
         self.bus, self.split, self.train_rank = bus, split, train_rank
+        self.wu_group = wu_group
         self.remote_ranks = split.rollout_ranks
         self.my_rollout_ranks = split.rollout_peers_of(train_rank)
         self._seq = {r: 0 for r in self.my_rollout_ranks}
@@ -176,8 +179,10 @@ class RemoteRolloutClient(InferenceEngine):
 class RolloutWorker:
     """Main loop of a rollout rank."""
 
-    def __init__(self, engine, bus: MessageBus, split: SplitWorld, dataloader, workflow, workflow_kwargs=None):
+    def __init__(self, engine, bus: MessageBus, split: SplitWorld, dataloader, workflow, workflow_kwargs=None,
+                 flat_param: Optional[torch.Tensor] = None, wu_group=None):
         self.engine, self.bus, self.split = engine, bus, split
+        self.flat_param, self.wu_group = flat_param, wu_group
         self.dataloader, self.workflow, self.workflow_kwargs = dataloader, workflow, workflow_kwargs
         self.rank = split.rank
         self._stop = threading.Event()
@@ -198,6 +203,10 @@ class RolloutWorker:
             if self.engine.device.type == "cuda":
                 torch.cuda.synchronize(self.engine.device)
             self.bus.put(f"wu/{self.push_seq}/ack/{self.rank}", 1)
+            if isinstance(cmd, dict) and cmd.get("mode") == "broadcast":
+                flat = self.flat_param
+                for a in range(0, flat.numel(), cmd["bucket"]):
+                    dist.broadcast(flat[a:a + cmd["bucket"]], src=cmd["src"], group=self.wu_group)
             done = self.bus.get(f"wu/{self.push_seq}/done")
             if self.engine.device.type == "cuda":
                 torch.cuda.synchronize(self.engine.device)
@@ -237,3 +246,78 @@ class RolloutWorker:
         if "e" in holder:
             raise holder["e"]
         return holder["b"]
+
+
+# --------------------------------------------------------------------------- launch helpers
+def init_split_world(n_train: int, device: Optional[torch.device] = None):
+    """Initialises ``torch.distributed`` (NCCL on CUDA, gloo on CPU) from the torchrun-style
+    environment and returns ``(split, groups, bus)``."""
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    use_cuda = device is not None and device.type == "cuda"
+    if not dist.is_initialized():
+        if use_cuda:
+            dist.init_process_group("nccl", device_id=device)
+        else:
+            dist.init_process_group("gloo")
+    split = SplitWorld(n_train, world - n_train, rank)
+    groups = build_split_groups(split, sp_size=1, use_cuda=use_cuda)
+    bus = MessageBus(rank, world)
+    return split, groups, bus
+
+
+def make_split_trainer(cfg, model_cfg, split: SplitWorld, groups: dict, bus: MessageBus, dataset, seed: int = 1,
+                       symmetric: bool = True):
+    """Trainer-rank side: builds the actor engine on the trainer sub-world, the remote rollout
+    client and the :class:`PPOTrainer`, and pushes the initial weights."""
+    from ..api.io_struct import FinetuneSpec
+    from ..engine.train_engine import B200PPOActor
+    from ..trainer.rl_trainer import PPOTrainer
+
+    actor = B200PPOActor(cfg.actor)
+    actor.set_train_ranks(split.train_ranks, groups)
+    actor.create_process_group()
+    kw = {}
+    if symmetric and actor.device.type == "cuda":
+        kw = dict(param_symm_group=dist.group.WORLD, param_symm_ranks=list(range(split.world)))
+    ft = FinetuneSpec(cfg.total_train_epochs, len(dataset), cfg.train_dataset.batch_size)
+    actor.initialize(ft_spec=ft, model_config=model_cfg, seed=seed, **kw)
+    client = RemoteRolloutClient(bus, split, split.rank, wu_group=groups.get("wu"))
+    trainer = PPOTrainer(cfg, dataset, model_config=model_cfg, rollout_engine=client, actor_engine=actor)
+    actor.update_weights(trainer.weight_update_meta.with_version(0))
+    return trainer
+
+
+def run_rollout_rank(cfg, model_cfg, split: SplitWorld, groups: dict, bus: MessageBus, dataset, workflow,
+                     device: torch.device, seed: int = 1, symmetric: bool = True, eos_token_id=None,
+                     max_batches: Optional[int] = None):
+    """Rollout-rank side: builds the engine over a flat parameter buffer laid out like the
+    trainer's (peer-mapped when ``symmetric``), then produces batches until told to exit."""
+    from torch.utils.data import DataLoader
+
+    from ..engine.flat_params import FlatParamStore
+    from ..engine.infer_engine import NativeInferenceEngine
+    from ..models.decoder import build_model
+
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    model = build_model(model_cfg, dtype=dtype, device=device, seed=seed)
+    alloc = None
+    if symmetric and device.type == "cuda":
+        from ..parallel.symm import symm_empty
+
+        def alloc(n, dt, d):
+            t, _ = symm_empty(n, dt, d, dist.group.WORLD)
+            t.zero_()
+            return t
+    n_shards = split.n_train if split.n_train > 1 else 1
+    store = FlatParamStore(model, n_shards, 0, alloc_param=alloc, with_grads=False)
+    engine = NativeInferenceEngine(cfg.rollout, cfg.native_infer, model=model, eos_token_id=eos_token_id)
+    engine.initialize(device=device, seed=seed)
+    dl = DataLoader(dataset, batch_size=cfg.train_dataset.batch_size, shuffle=True, drop_last=True, collate_fn=list,
+                    generator=torch.Generator().manual_seed(seed + split.rank))
+    worker = RolloutWorker(engine, bus, split, dl, workflow, flat_param=store.flat_param, wu_group=groups.get("wu"))
+    try:
+        worker.run(max_batches=max_batches)
+    finally:
+        engine.destroy()
+    return worker

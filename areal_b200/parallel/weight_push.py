@@ -190,25 +190,36 @@ class DistributedWeightPusher:
 
 
 class BroadcastWeightPusher:
-    """NCCL baseline: rank-0-rooted broadcast of the whole flat buffer to the rollout ranks in
-    buckets (the data movement of the reference's xccl path, minus its HTTP round trips)."""
+    """Collective baseline: the trainer head broadcasts the whole flat parameter buffer to the
+    rollout ranks in buckets (the data movement of the reference's xccl path, minus its HTTP
+    round trips). Works on NCCL and on gloo (CPU deployments)."""
 
     def __init__(self, train_engine, rollout_client, group, bucket_mb: int = 1024):
-        self.train, self.client, self.group, self.bucket = train_engine, rollout_client, group, bucket_mb * 1024 * 1024 // 2
+        self.train, self.client, self.group = train_engine, rollout_client, group
+        self.bucket = bucket_mb * 1024 * 1024 // max(1, train_engine.store.flat_param.element_size())
         self.bus, self.split, self.seq = rollout_client.bus, rollout_client.split, 0
+        self.last_ms = 0.0
 
     def push(self, meta: Optional[WeightUpdateMeta] = None) -> float:
         eng = self.train
+        head = eng.local_index <= 0
         t0 = time.perf_counter()
-        if eng.local_index == 0:
-            self.bus.put(f"wu/{self.seq}/pause", 1)
+        src = self.split.train_ranks[0]
+        if head:
+            self.bus.put(f"wu/{self.seq}/pause", {"mode": "broadcast", "bucket": self.bucket, "src": src})
         for r in self.split.rollout_ranks:
             self.bus.get(f"wu/{self.seq}/ack/{r}")
         flat = eng.store.flat_param
-        if eng.local_index == 0:
+        if head:
             for a in range(0, flat.numel(), self.bucket):
-                dist.broadcast(flat[a:a + self.bucket], src=self.split.train_ranks[0], group=self.group)
-            torch.cuda.current_stream().synchronize()
-            self.bus.put(f"wu/{self.seq}/done", {"version": (meta.version if meta and meta.version is not None else eng.get_version() + 1)})
+                dist.broadcast(flat[a:a + self.bucket], src=src, group=self.group)
+            if flat.is_cuda:
+                torch.cuda.current_stream().synchronize()
+        if eng.cpu_group is not None:
+            dist.barrier(group=eng.cpu_group)
+        if head:
+            version = meta.version if meta is not None and meta.version is not None else eng.get_version() + 1
+            self.bus.put(f"wu/{self.seq}/done", {"version": version})
         self.seq += 1
-        return (time.perf_counter() - t0) * 1e3
+        self.last_ms = (time.perf_counter() - t0) * 1e3
+        return self.last_ms

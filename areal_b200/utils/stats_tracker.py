@@ -84,9 +84,15 @@ class DistributedStatsTracker:
             self._reduce[name] = ReduceType.SCALAR
 
     # ------------------------------------------------------------------ export
-    def export(self, key: Optional[str] = None, reduce_group=None, reset: bool = True) -> dict[str, float]:
+    def export(self, key: Optional[str] = None, reduce_group=None, reset: bool = True,
+               distributed: Optional[bool] = None) -> dict[str, float]:
+        """``distributed``: force (True) or forbid (False) the cross-rank reduction; by default
+        statistics are reduced over ``reduce_group`` (the default group when None) whenever
+        ``torch.distributed`` is initialised with more than one rank."""
         out: dict[str, float] = {}
         use_dist = dist.is_initialized() and (reduce_group is not None or dist.get_world_size() > 1)
+        if distributed is not None:
+            use_dist = bool(distributed) and dist.is_initialized()
         keys = sorted(set(self._denoms) | set(self._stats) | set(self._scalars))
         if use_dist:
             gathered = [None] * dist.get_world_size(reduce_group)
@@ -187,8 +193,8 @@ def get(name: str = "") -> DistributedStatsTracker:
     return _TRACKERS[name]
 
 
-def export_all(reduce_group=None, reset: bool = True) -> dict[str, float]:
-    out = DEFAULT_TRACKER.export(reduce_group=reduce_group, reset=reset)
+def export_all(reduce_group=None, reset: bool = True, distributed: Optional[bool] = None) -> dict[str, float]:
+    out = DEFAULT_TRACKER.export(reduce_group=reduce_group, reset=reset, distributed=distributed)
     for name in sorted(_TRACKERS):
-        out.update(_TRACKERS[name].export(reduce_group=reduce_group, reset=reset))
+        out.update(_TRACKERS[name].export(reduce_group=reduce_group, reset=reset, distributed=distributed))
     return out

@@ -82,8 +82,12 @@ def make_weight_pusher(train_engine, infer_engine, meta: WeightUpdateMeta):
     if meta.type == "disk":
         return DiskPusher(train_engine, infer_engine)
     if meta.type in ("p2p", "xccl", "awex") and hasattr(infer_engine, "remote_ranks"):
-        from ..parallel.weight_push import DistributedWeightPusher
+        from ..parallel.weight_push import BroadcastWeightPusher, DistributedWeightPusher
 
+        symmetric = train_engine.store.flat_param.data_ptr() in train_engine._symm_handles
+        if meta.type == "xccl" or not symmetric:
+            return BroadcastWeightPusher(train_engine, infer_engine, infer_engine.wu_group,
+                                         bucket_mb=meta.weight_chunked_mem_mb)
         return DistributedWeightPusher(train_engine, infer_engine, meta)
     return InProcessPusher(train_engine, infer_engine)
 
