@@ -408,7 +408,32 @@ def attention_bwd_ref(q, k, v, o, lse, do, cu_seqlens, causal, scale):
     return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
 
-_ATTN_BWD_IMPL = None  # installed by areal_b200.ops.attention_bwd once the kernel is loaded
+def attention_bwd(q, k, v, o, lse, do, cu_seqlens, causal, scale, tile_info=None):
+    """Kernel backward: returns (dq, dk, dv) in the dtype of q. ``lse``: [Hq, T] from the forward."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    for t in (q, k, v, o, do):
+        assert t.stride(2) == 1 and t.stride(1) == D and t.dtype == torch.bfloat16
+    if tile_info is None:
+        tile_info = attn_tile_table(cu_seqlens, T)
+    # heaviest key blocks (most query blocks to visit under causal masking) first
+    tiles_bwd = tile_info.flip(0).contiguous()
+    cu = cu_seqlens.to(torch.int32)
+    delta = torch.empty(Hq, T, device=q.device, dtype=torch.float32)
+    _lib.check(_L().ab2_attn_delta(o.data_ptr(), do.data_ptr(), delta.data_ptr(), T, Hq, D, o.stride(0), do.stride(0), _s()),
+               "ab2_attn_delta")
+    dq32 = torch.zeros(T, Hq, D, device=q.device, dtype=torch.float32)
+    dk = torch.zeros(T, Hkv, D, device=q.device, dtype=q.dtype)
+    dv = torch.zeros(T, Hkv, D, device=q.device, dtype=q.dtype)
+    rc = _L().ab2_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                           dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr(), tiles_bwd.data_ptr(),
+                           tiles_bwd.shape[0], T, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0), do.stride(0),
+                           dk.stride(0), dv.stride(0), scale, int(causal), _s())
+    _lib.check(rc, "ab2_attn_bwd")
+    return dq32.to(q.dtype), dk, dv
+
+
+_ATTN_BWD_IMPL = attention_bwd  # set to None to fall back to the fp32 reference backward
 
 
 class _Attention(torch.autograd.Function):
@@ -423,6 +448,8 @@ class _Attention(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, lse, cu = ctx.saved_tensors
         do = do.contiguous()
+        if not o.is_contiguous():
+            o = o.contiguous()
         if _ATTN_BWD_IMPL is not None:
             dq, dk, dv = _ATTN_BWD_IMPL(q, k, v, o, lse, do, cu, ctx.causal, ctx.scale, ctx.tile_info)
         else:

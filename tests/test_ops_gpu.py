@@ -202,3 +202,50 @@ def test_attention_fwd(D, causal):
     orf, lser = OF.attention_ref(q, k, v, cu, causal)
     assert _rel_err(o, orf) < 2e-2
     assert (lse - lser).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_bwd(D, causal):
+    torch.manual_seed(11)
+    lens = [1, 130, 257, 128, 515, 64]
+    T = sum(lens)
+    Hq, Hkv = 4, 2
+    qkv = (torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda") * 0.7).bfloat16()
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D: (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    o, lse = OF.attention_fwd(q, k, v, cu, causal)
+    do = torch.randn_like(o)
+    scale = D ** -0.5
+    dq, dk, dv = OF.attention_bwd(q, k, v, o, lse, do, cu, causal, scale)
+    _no_kernel_error()
+    orf, lser = OF.attention_ref(q, k, v, cu, causal)
+    dqr, dkr, dvr = OF.attention_bwd_ref(q, k, v, orf, lser, do, cu, causal, scale)
+    assert _rel_err(dq, dqr) < 3e-2
+    assert _rel_err(dk, dkr) < 3e-2
+    assert _rel_err(dv, dvr) < 3e-2
+
+
+def test_attention_autograd_matches_reference_path():
+    torch.manual_seed(12)
+    T, Hq, Hkv, D = 700, 8, 2, 128
+    q = torch.randn(T, Hq, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(T, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(T, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    cu = torch.tensor([0, 300, 700], device="cuda", dtype=torch.int32)
+    g = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    OF.attention(q, k, v, cu, True).backward(g)
+    got = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    saved = OF._ATTN_BWD_IMPL
+    OF._ATTN_BWD_IMPL = None
+    try:
+        OF.attention(q, k, v, cu, True).backward(g)
+    finally:
+        OF._ATTN_BWD_IMPL = saved
+    for a, t in zip(got, (q, k, v)):
+        assert _rel_err(a, t.grad) < 3e-2
+    _no_kernel_error()
