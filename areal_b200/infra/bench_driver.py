@@ -187,6 +187,11 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
     else:
         h2d, d2h = float(stats[4]), float(stats[5])
     push_ms = getattr(getattr(trainer.actor, "_weight_pusher", None), "last_ms", None)
+    phases = {}
+    for h in hist_a:
+        for k_, v_ in h.items():
+            if k_.startswith("timeperf/"):
+                phases[k_[9:]] = phases.get(k_[9:], 0.0) + float(v_) / max(1, len(hist_a))
     trainer.close()
     if rank != 0:
         return None
@@ -202,7 +207,8 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
                    "seq_len": seq_len, "prompt_len": args.prompt_len, "response_median": args.median_len,
                    "response_cap": args.max_len, "group_size": args.group_size, "parallelism": parallelism,
                    "max_staleness": args.staleness, "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
-                   "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms},
+                   "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms,
+                   "phase_seconds_per_step": {k_: round(v_, 4) for k_, v_ in sorted(phases.items())}},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d / K, "d2h_bytes_per_step": d2h / K},
         "gpu_launches": int(launches),

@@ -63,7 +63,8 @@ class StatsLogger:
         logger.info("epoch %d step %d (global %d/%d) %.1fs since start", epoch + 1, step + 1, global_step + 1, total,
                     time.perf_counter() - self.start)
         keys = sorted(merged)
-        show = [k for k in keys if not k.endswith(("/min", "/max"))][:40]
+        show = [k for k in keys if k.startswith("timeperf/")] + \
+               [k for k in keys if not k.endswith(("/min", "/max")) and not k.startswith("timeperf/")][:40]
         logger.info("stats: " + ", ".join(f"{k}={merged[k]:.4g}" for k in show))
         if self._fh:
             self._fh.write(json.dumps(dict(epoch=epoch, step=step, global_step=global_step, **merged)) + "\n")
