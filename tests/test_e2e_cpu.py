@@ -1,0 +1,190 @@
+"""End-to-end slices on CPU: colocated async GRPO, trainer/rollout split over gloo, HF
+checkpoint round trip, recover, weight-push plan."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from areal_b200.api.cli_args import (ClusterSpecConfig, DatasetConfig, GenerationHyperparameters, GRPOConfig,
+                                     InferenceEngineConfig, MicroBatchSpec, NormConfig, OptimizerConfig, PPOActorConfig,
+                                     RecoverConfig, SaverConfig, StatsLoggerConfig)
+from areal_b200.api.io_struct import SaveLoadMeta
+from areal_b200.dataset import ArithmeticDataset, CharTokenizer
+from areal_b200.engine.flat_params import FlatParamStore
+from areal_b200.engine.train_engine import B200PPOActor
+from areal_b200.models import hf_io
+from areal_b200.models.config import ModelConfig, preset
+from areal_b200.models.decoder import build_model
+from areal_b200.parallel.weight_push import build_push_plan, tp_layout_of
+from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
+from areal_b200.trainer.rl_trainer import PPOTrainer
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def digit_reward(prompt, completion, prompt_ids, completion_ids, **kw):
+    """Shaped reward that a random-init model can climb: fraction of generated ids < 10."""
+    return sum(1 for t in completion_ids if t < 10) / max(1, len(completion_ids))
+
+
+def _cfg(root, steps=None, recover="disabled"):
+    return GRPOConfig(
+        experiment_name="e2e", trial_name="t0", total_train_epochs=1, total_train_steps=steps, seed=1,
+        cluster=ClusterSpecConfig(fileroot=root), train_dataset=DatasetConfig(batch_size=8),
+        gconfig=GenerationHyperparameters(n_samples=4, max_new_tokens=8, max_tokens=64),
+        rollout=InferenceEngineConfig(max_concurrent_rollouts=16, consumer_batch_size=8, max_head_offpolicyness=1,
+                                      check_trajectory_format=True),
+        actor=PPOActorConfig(init_from_scratch=True, dtype="float32", optimizer=OptimizerConfig(lr=3e-3),
+                             mb_spec=MicroBatchSpec(max_tokens_per_mb=512), use_decoupled_loss=True, recompute_logprob=True,
+                             kl_ctl=0.0, ppo_n_minibatches=1,
+                             reward_norm=NormConfig(mean_level="group", std_level="group", group_size=4)),
+        saver=SaverConfig(fileroot=root, experiment_name="e2e", trial_name="t0"),
+        recover=RecoverConfig(mode=recover, fileroot=root, experiment_name="e2e", trial_name="t0", freq_steps=1),
+        stats_logger=StatsLoggerConfig(fileroot=root, experiment_name="e2e", trial_name="t0"))
+
+
+def test_colocated_async_grpo_learns_shaped_reward(tmp_path):
+    cfg = _cfg(str(tmp_path), steps=12)
+    mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+    tok = CharTokenizer()
+    with PPOTrainer(cfg, ArithmeticDataset(size=128), tokenizer=None, model_config=mc) as tr:
+        wf = RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True)
+        hist = tr.train(workflow=wf)
+    assert len(hist) == 12
+    r = [h["ppo_actor/task_reward/avg"] for h in hist]
+    assert all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
+    assert max(h.get("ppo_actor/update/staleness/avg", 0) for h in hist) <= 1.0 + 1e-6      # max_head_offpolicyness respected
+    assert sum(r[-3:]) / 3 > sum(r[:3]) / 3 + 0.05, r                                       # the policy improved
+    assert os.path.exists(os.path.join(str(tmp_path), "logs"))
+
+
+def test_recover_resumes_from_checkpoint(tmp_path):
+    mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+    cfg = _cfg(str(tmp_path), steps=2, recover="auto")
+    with PPOTrainer(cfg, ArithmeticDataset(size=64), model_config=mc) as tr:
+        tr.train(workflow=RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True))
+        w_end = tr.actor.store.flat_param.clone()
+    cfg2 = _cfg(str(tmp_path), steps=3, recover="auto")
+    with PPOTrainer(cfg2, ArithmeticDataset(size=64), model_config=mc) as tr2:
+        assert tr2.start_step == 2 and tr2.actor.get_version() == 2 and tr2.rollout.get_version() == 2
+        assert torch.equal(tr2.actor.store.flat_param, w_end)
+        assert tr2.actor.optimizer.step_count == 2
+        hist = tr2.train(workflow=RLVRWorkflow(digit_reward, cfg2.gconfig, reward_in_process=True))
+        assert len(hist) == 1
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-qwen3", "tiny-qwen3-moe"])
+def test_hf_checkpoint_roundtrip_and_names(tmp_path, name):
+    cfg = preset(name)
+    m = build_model(cfg, dtype=torch.float32, seed=2)
+    hf_io.save_model_hf(m, str(tmp_path), max_shard_bytes=2_000_000)
+    files = os.listdir(tmp_path)
+    assert "config.json" in files and any(f.endswith(".safetensors") for f in files)
+    names = {k for k, _ in hf_io.iter_safetensors(str(tmp_path))}
+    assert "model.layers.0.self_attn.q_proj.weight" in names and "model.embed_tokens.weight" in names
+    if cfg.is_moe:
+        assert "model.layers.0.mlp.experts.3.up_proj.weight" in names and "model.layers.0.mlp.gate.weight" in names
+    m2 = build_model(ModelConfig.from_pretrained(str(tmp_path)), dtype=torch.float32, seed=99)
+    hf_io.load_model_hf(m2, str(tmp_path))
+    for (n, a), (_, b) in zip(m.named_parameters(), m2.named_parameters()):
+        assert torch.equal(a, b), n
+
+
+def test_engine_save_load_hf_and_sharded(tmp_path):
+    cfg = PPOActorConfig(init_from_scratch=True, dtype="float32", optimizer=OptimizerConfig(lr=1e-3))
+    e = B200PPOActor(cfg); e.create_process_group(); e.initialize(model_config=preset("tiny-qwen3"), seed=4)
+    e.optimizer.exp_avg.fill_(0.25); e.optimizer.step_count = 5; e.set_version(9)
+    e.save(SaveLoadMeta(path=str(tmp_path / "hf"), weight_format="hf", with_optim=True))
+    e.save(SaveLoadMeta(path=str(tmp_path / "sh"), weight_format="sharded", with_optim=True))
+    f = B200PPOActor(cfg); f.create_process_group(); f.initialize(model_config=preset("tiny-qwen3"), seed=5)
+    assert not torch.equal(f.store.flat_param, e.store.flat_param)
+    f.load(SaveLoadMeta(path=str(tmp_path / "sh"), weight_format="sharded", with_optim=True))
+    assert torch.equal(f.store.flat_param, e.store.flat_param) and f.optimizer.step_count == 5 and f.get_version() == 9
+    assert float(f.optimizer.exp_avg[0]) == 0.25
+    g = B200PPOActor(cfg); g.create_process_group(); g.initialize(model_config=preset("tiny-qwen3"), seed=6)
+    g.load(SaveLoadMeta(path=str(tmp_path / "hf"), weight_format="hf", with_optim=True))
+    assert torch.equal(g.store.flat_param[: g.store.numel], e.store.flat_param[: e.store.numel])
+
+
+@pytest.mark.parametrize("tp,world", [(1, 3), (2, 4), (4, 2)])
+def test_weight_push_plan_covers_every_tp_slice(tp, world):
+    cfg = preset("tiny-qwen2", num_heads=4, num_kv_heads=4)
+    stores = [FlatParamStore(build_model(cfg, dtype=torch.float32, seed=0), world, r, with_grads=False) for r in range(world)]
+    st = stores[0]
+    shapes = [tuple(p.shape) for p in st.params]
+    dst_offsets, sizes = [], []
+    for j in range(tp):
+        d, o = {}, 0
+        for n, sh in zip(st.names, shapes):
+            d[n] = o
+            C = sh[1] if len(sh) > 1 else 1
+            R = int(torch.tensor(sh).prod()) // C
+            o += sum((b[1] - b[0]) * (b[3] - b[2]) for b in tp_layout_of(cfg, n, (R, C), tp)[j])
+        dst_offsets.append(d); sizes.append(o)
+    dst = [torch.full((s,), float("nan")) for s in sizes]
+    for r in range(world):
+        for op in build_push_plan(cfg, st.names, st.offsets, shapes, stores[r].shard_range, tp, dst_offsets):
+            for rr in range(op.rows):
+                a, b = op.dst_off + rr * op.ld_dst, op.src_off + rr * op.ld_src
+                assert torch.isnan(dst[op.dst_tp][a:a + op.cols]).all(), "element written twice"
+                dst[op.dst_tp][a:a + op.cols] = st.flat_param[b:b + op.cols]
+    for j in range(tp):
+        for n, sh, p in zip(st.names, shapes, st.params):
+            C = sh[1] if len(sh) > 1 else 1
+            t = p.data.reshape(-1, C)
+            exp = torch.cat([t[b[0]:b[1], b[2]:b[3]].reshape(-1) for b in tp_layout_of(cfg, n, (t.shape[0], C), tp)[j]])
+            got = dst[j][dst_offsets[j][n]: dst_offsets[j][n] + exp.numel()]
+            assert torch.equal(got, exp), (tp, j, n)
+
+
+SPLIT_SCRIPT = r'''
+import faulthandler, os, sys
+faulthandler.dump_traceback_later(150, exit=True)
+sys.path.insert(0, %(root)r)
+os.environ["AREAL_FORCE_CPU"] = "1"
+import torch, torch.distributed as dist
+from tests.test_e2e_cpu import _cfg, digit_reward
+from areal_b200.dataset import ArithmeticDataset
+from areal_b200.models.config import preset
+from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
+from areal_b200.infra.spmd import init_split_world, make_split_trainer, run_rollout_rank
+cfg = _cfg(%(tmp)r)
+mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+split, groups, bus = init_split_world(int(os.environ["N_TRAIN"]), None)
+ds = ArithmeticDataset(size=128)
+if split.is_trainer:
+    tr = make_split_trainer(cfg, mc, split, groups, bus, ds)
+    h = tr.train(max_steps=3)
+    assert len(h) == 3 and all(x["ppo_actor/update/update_successful"] == 1.0 for x in h)
+    assert max(x.get("ppo_actor/update/staleness/avg", 0) for x in h) <= 1.0 + 1e-6
+    ref = tr.actor.store.flat_param.clone()
+    if groups["shard"] is not None:
+        dist.broadcast(ref, src=0, group=groups["shard"])
+        assert torch.equal(ref, tr.actor.store.flat_param), "trainer replicas diverged"
+    if split.rank == 0:
+        bus.put("final_sum", float(tr.actor.store.flat_param.double().sum()))
+        bus.put("exit", 1)
+    tr.close()
+else:
+    wf = RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True)
+    w = run_rollout_rank(cfg, mc, split, groups, bus, ds, wf, torch.device("cpu"))
+    assert w.engine.get_version() == 3, w.engine.get_version()
+    got = float(w.flat_param.double().sum())
+    assert abs(got - bus.get("final_sum")) < 1e-6, "rollout replica does not hold the trainer's final weights"
+dist.barrier(group=groups["world_cpu"])
+print("SPLIT_OK", split.rank, flush=True)
+'''
+
+
+@pytest.mark.parametrize("n_train,world,port", [(1, 2, 29811), (2, 4, 29821)])
+def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port):
+    script = tmp_path / "split.py"
+    script.write_text(SPLIT_SCRIPT % dict(root=ROOT, tmp=str(tmp_path)))
+    env = dict(os.environ, N_TRAIN=str(n_train), OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("SPLIT_OK") == world
