@@ -65,7 +65,7 @@ def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOCon
         train_dataset=DatasetConfig(batch_size=bs, shuffle=True, drop_last=True),
         gconfig=GenerationHyperparameters(n_samples=args.group_size, max_new_tokens=args.max_len,
                                           max_tokens=args.prompt_len + args.max_len + 8, temperature=1.0, ignore_eos=True),
-        rollout=InferenceEngineConfig(max_concurrent_rollouts=max(bs * 2, 4), consumer_batch_size=bs,
+        rollout=InferenceEngineConfig(max_concurrent_rollouts=bs * (args.staleness + 1), consumer_batch_size=bs,
                                       max_head_offpolicyness=args.staleness),
         native_infer=NativeInferConfig(max_running_requests=max_running, page_size=64,
                                        context_length=args.prompt_len + args.max_len + 64, mem_fraction_static=0.35 if n_pairs == 1 and int(os.environ.get('WORLD_SIZE', '1')) == 1 else 0.6,
@@ -107,7 +107,7 @@ def run_async_grpo_bench(args, clock_sampler_cls) -> Optional[dict]:
     W, K = args.warmup, args.steps
 
     if world == 1:
-        cfg = _make_config(args, 1, max_running=args.prompts_per_gpu_pair * args.group_size, fileroot=fileroot)
+        cfg = _make_config(args, 1, max_running=256, fileroot=fileroot)
         ds = _dataset(args, model_cfg, seed=1)
         trainer = PPOTrainer(cfg, ds, model_config=model_cfg)
         _instrument_transfers(trainer.actor)
@@ -120,7 +120,7 @@ def run_async_grpo_bench(args, clock_sampler_cls) -> Optional[dict]:
     dev = torch.device("cuda", local_rank)
     n_train = world // 2
     split, groups, bus = init_split_world(n_train, dev)
-    cfg = _make_config(args, n_train, max_running=args.prompts_per_gpu_pair * args.group_size, fileroot=fileroot)
+    cfg = _make_config(args, n_train, max_running=256, fileroot=fileroot)
     if split.is_trainer:
         ds = _dataset(args, model_cfg, seed=1)  # only sizes the trainer's bookkeeping
         trainer = make_split_trainer(cfg, model_cfg, split, groups, bus, ds, seed=1)

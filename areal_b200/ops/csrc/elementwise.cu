@@ -34,14 +34,18 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                    int rows, int H, float eps) {
   __shared__ float red[32];
   const int nvec = H >> 3;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  // TPR == 32: every warp of the CTA owns its own row (blockDim.x / 32 rows per CTA step)
+  const int rows_per_cta = (TPR == 32) ? (blockDim.x >> 5) : 1;
+  const int sub = (TPR == 32) ? (threadIdx.x >> 5) : 0;
+  const int tid = (TPR == 32) ? (threadIdx.x & 31) : threadIdx.x;
+  for (int row = blockIdx.x * rows_per_cta + sub; row < rows; row += gridDim.x * rows_per_cta) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
     const uint4* rr = resid ? reinterpret_cast<const uint4*>(resid + (size_t)row * H) : nullptr;
     float v[VPT][8];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int idx = threadIdx.x + i * TPR;
+      const int idx = tid + i * TPR;
       if (idx < nvec) {
         uint4 a = xr[idx];
         const uint32_t aa[4] = {a.x, a.y, a.z, a.w};
@@ -70,12 +74,12 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
     }
     ss = (TPR == 32) ? warp_sum(ss) : block_sum(ss, red);
     const float rstd = rsqrtf(ss / (float)H + eps);
-    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    if (tid == 0 && rstd_out) rstd_out[row] = rstd;
     const uint4* wr = reinterpret_cast<const uint4*>(w);
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int idx = threadIdx.x + i * TPR;
+      const int idx = tid + i * TPR;
       if (idx < nvec) {
         const uint4 ww = wr[idx];
         const uint32_t wa[4] = {ww.x, ww.y, ww.z, ww.w};
@@ -103,12 +107,15 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
                                    float* __restrict__ dw, int rows, int H) {
   __shared__ float red[32];
   const int nvec = H >> 3;
+  const int rows_per_cta = (TPR == 32) ? (blockDim.x >> 5) : 1;
+  const int sub = (TPR == 32) ? (threadIdx.x >> 5) : 0;
+  const int tid = (TPR == 32) ? (threadIdx.x & 31) : threadIdx.x;
   float dwacc[VPT][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
 #pragma unroll
     for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  for (int row = blockIdx.x * rows_per_cta + sub; row < rows; row += gridDim.x * rows_per_cta) {
     const float rstd = rstd_in[row];
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
@@ -117,7 +124,7 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int idx = threadIdx.x + i * TPR;
+      const int idx = tid + i * TPR;
       if (idx < nvec) {
         const uint4 a = xr[idx], g = gr[idx], ww = wr[idx];
         const uint32_t aa[4] = {a.x, a.y, a.z, a.w}, ga[4] = {g.x, g.y, g.z, g.w},
@@ -139,7 +146,7 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
     const uint4* drr = dresid ? reinterpret_cast<const uint4*>(dresid + (size_t)row * H) : nullptr;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int idx = threadIdx.x + i * TPR;
+      const int idx = tid + i * TPR;
       if (idx < nvec) {
         uint32_t o[4];
         uint32_t da[4] = {0, 0, 0, 0};
@@ -163,7 +170,7 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int idx = threadIdx.x + i * TPR;
+    const int idx = tid + i * TPR;
     if (idx < nvec) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) atomicAdd(dw + idx * 8 + e, dwacc[i][e]);
@@ -361,7 +368,7 @@ int ab2_rmsnorm_fwd(const void* x, const void* resid, const void* w, void* y, vo
   if (rows <= 0) return 0;
   auto X = (const __nv_bfloat16*)x; auto R = (const __nv_bfloat16*)resid; auto W = (const __nv_bfloat16*)w;
   auto Y = (__nv_bfloat16*)y; auto RO = (__nv_bfloat16*)resid_out;
-  if (H <= 256) rmsnorm_fwd_kernel<32, 1><<<grid, 32, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
+  if (H <= 256) rmsnorm_fwd_kernel<32, 1><<<(rows + 7) / 8 < 148 * 16 ? (rows + 7) / 8 : 148 * 16, 256, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
   else if (H <= 2048) rmsnorm_fwd_kernel<128, 2><<<grid, 128, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
   else if (H <= 4096) rmsnorm_fwd_kernel<128, 4><<<grid, 128, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
   else rmsnorm_fwd_kernel<256, 4><<<grid, 256, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
@@ -377,7 +384,7 @@ int ab2_rmsnorm_bwd(const void* x, const void* w, const void* dy, const void* dr
   const int grid = rows < 148 * 4 ? rows : 148 * 4;
   auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w; auto DY = (const __nv_bfloat16*)dy;
   auto DR = (const __nv_bfloat16*)dresid; auto DX = (__nv_bfloat16*)dx;
-  if (H <= 256) rmsnorm_bwd_kernel<32, 1><<<grid, 32, 0, s>>>(X, W, DY, DR, rstd, DX, dw, rows, H);
+  if (H <= 256) rmsnorm_bwd_kernel<32, 1><<<(rows + 7) / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8, 256, 0, s>>>(X, W, DY, DR, rstd, DX, dw, rows, H);
   else if (H <= 2048) rmsnorm_bwd_kernel<128, 2><<<grid, 128, 0, s>>>(X, W, DY, DR, rstd, DX, dw, rows, H);
   else if (H <= 4096) rmsnorm_bwd_kernel<128, 4><<<grid, 128, 0, s>>>(X, W, DY, DR, rstd, DX, dw, rows, H);
   else rmsnorm_bwd_kernel<256, 4><<<grid, 256, 0, s>>>(X, W, DY, DR, rstd, DX, dw, rows, H);

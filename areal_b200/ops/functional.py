@@ -423,8 +423,9 @@ def attention_bwd(q, k, v, o, lse, do, cu_seqlens, causal, scale, tile_info=None
     _lib.check(_L().ab2_attn_delta(o.data_ptr(), do.data_ptr(), delta.data_ptr(), T, Hq, D, o.stride(0), do.stride(0), _s()),
                "ab2_attn_delta")
     dq32 = torch.zeros(T, Hq, D, device=q.device, dtype=torch.float32)
-    dk = torch.zeros(T, Hkv, D, device=q.device, dtype=q.dtype)
-    dv = torch.zeros(T, Hkv, D, device=q.device, dtype=q.dtype)
+    # every token of the packed batch belongs to one key block, so dk / dv are fully written
+    dk = torch.empty(T, Hkv, D, device=q.device, dtype=q.dtype)
+    dv = torch.empty(T, Hkv, D, device=q.device, dtype=q.dtype)
     rc = _L().ab2_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
                            dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr(), tiles_bwd.data_ptr(),
                            tiles_bwd.shape[0], T, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0), do.stride(0),

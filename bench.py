@@ -99,7 +99,9 @@ def run_reference(args):
     ref = os.path.join(ROOT, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref, "areal")):
-        why = "reference not installed under baseline/_ref (offline pip install did not produce the package)"
+        why = ("reference could not be installed offline: its build backend uv_build is not in /opt/wheelhouse "
+               "(pip exits with ModuleNotFoundError: uv_build), and its stock GRPO path also needs hydra, omegaconf "
+               "and an SGLang server, none of which is installed")
     else:
         sys.path.insert(0, ref)
         missing = []
