@@ -1,0 +1,199 @@
+"""Micro-benchmarks of the individual sm_100a kernels (CUDA-event timing, L2 flushed between
+iterations) with achieved throughput and the fraction of the measured device peaks.
+
+    python -m areal_b200.ops.bench_kernels gemm --m 8192 --n 8192 --k 8192
+    python -m areal_b200.ops.bench_kernels attn_fwd --seqlen 4096 --batch 4
+    python -m areal_b200.ops.bench_kernels attn_bwd --seqlen 4096 --batch 4
+    python -m areal_b200.ops.bench_kernels decode --batch 128 --ctx 1024
+    python -m areal_b200.ops.bench_kernels rmsnorm | swiglu | adamw | logprob
+
+The same entry points are what the profiler summaries under ``profiles/`` were captured from
+(small cases: one kernel, a few launches).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from . import functional as OF
+from . import lib as oplib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+_flush_buf = None
+
+
+def flush_l2():
+    global _flush_buf
+    if _flush_buf is None:
+        _flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")  # > 126 MB L2
+    _flush_buf.zero_()
+
+
+def timeit(fn, iters: int = 10, warmup: int = 3, flush: bool = True) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def report(name: str, ms: float, flops: float = 0.0, bytes_: float = 0.0, **extra) -> dict:
+    pk = peaks()
+    out = {"kernel": name, "ms": round(ms, 4), **extra}
+    if flops:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out[f"frac_of_{pk['source']}_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)
+    if bytes_:
+        out["gbs"] = round(bytes_ / ms / 1e6, 1)
+        out[f"frac_of_{pk['source']}_hbm_peak"] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+    out["kernel_error"] = oplib.kernel_error()
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def bench_gemm(a):
+    A = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    B = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    a_mn, b_mn = a.layout[0] == "t", a.layout[1] == "n"
+    Aop = A.t().contiguous() if a_mn else A
+    Bop = B.t().contiguous() if b_mn else B
+    C = torch.empty(a.m, a.n, device="cuda", dtype=torch.float32 if a.epi in (1, 2) else torch.bfloat16)
+    if a.epi == 2:
+        C.zero_()
+    ms = timeit(lambda: OF.gemm(Aop, Bop, a_mn=a_mn, b_mn=b_mn, out=C, epi=a.epi, bn=a.bn), a.iters, a.warmup)
+    fl = 2.0 * a.m * a.n * a.k
+    by = 2.0 * (a.m * a.k + a.n * a.k) + C.element_size() * a.m * a.n
+    res = report("gemm_bf16_tcgen05", ms, fl, by, m=a.m, n=a.n, k=a.k, layout=a.layout, epi=a.epi)
+    if a.compare:
+        ref = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        ms2 = timeit(lambda: torch.matmul(A, B.t(), out=ref), a.iters, a.warmup)
+        report("cublas_bf16 (library baseline)", ms2, fl, by)
+    return res
+
+
+def _attn_inputs(a):
+    T = a.seqlen * a.batch
+    q = torch.randn(T, a.heads, a.dim, device="cuda").bfloat16()
+    k = torch.randn(T, a.kv_heads, a.dim, device="cuda").bfloat16()
+    v = torch.randn(T, a.kv_heads, a.dim, device="cuda").bfloat16()
+    cu = torch.arange(0, T + 1, a.seqlen, device="cuda", dtype=torch.int32)
+    return q, k, v, cu, OF.attn_tile_table(cu, T)
+
+
+def bench_attn_fwd(a):
+    q, k, v, cu, ti = _attn_inputs(a)
+    ms = timeit(lambda: OF.attention_fwd(q, k, v, cu, True, None, ti), a.iters, a.warmup)
+    fl = 4.0 * a.batch * a.heads * a.seqlen * a.seqlen * a.dim / 2
+    return report("attn_fwd_tcgen05", ms, fl, seqlen=a.seqlen, batch=a.batch, heads=a.heads, kv_heads=a.kv_heads)
+
+
+def bench_attn_bwd(a):
+    q, k, v, cu, ti = _attn_inputs(a)
+    o, lse = OF.attention_fwd(q, k, v, cu, True, None, ti)
+    do = torch.randn_like(o)
+    ms = timeit(lambda: OF.attention_bwd(q, k, v, o, lse, do, cu, True, a.dim ** -0.5, ti), a.iters, a.warmup)
+    fl = 2.5 * 4.0 * a.batch * a.heads * a.seqlen * a.seqlen * a.dim / 2
+    return report("attn_bwd_tcgen05 (+delta, dq cast)", ms, fl, seqlen=a.seqlen, batch=a.batch, heads=a.heads)
+
+
+def bench_decode(a):
+    ps = 64
+    pages_per = (a.ctx + ps - 1) // ps
+    n_pages = a.batch * pages_per
+    kc = torch.randn(n_pages * ps, a.kv_heads, a.dim, device="cuda").bfloat16()
+    vc = torch.randn(n_pages * ps, a.kv_heads, a.dim, device="cuda").bfloat16()
+    q = torch.randn(a.batch, a.heads, a.dim, device="cuda").bfloat16()
+    pt = torch.randperm(n_pages, device="cuda").int().view(a.batch, pages_per).contiguous()
+    lens = torch.full((a.batch,), a.ctx, device="cuda", dtype=torch.int32)
+    splits = a.splits
+    po = torch.empty(a.batch * a.heads * splits * a.dim, device="cuda")
+    pml = torch.empty(a.batch * a.heads * splits * 2, device="cuda")
+    out = torch.empty_like(q)
+    L = oplib.get_lib()
+
+    def run():
+        oplib.check(L.ab2_paged_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pt.data_ptr(), lens.data_ptr(),
+                                       po.data_ptr(), pml.data_ptr(), out.data_ptr(), a.batch, a.heads, a.kv_heads, a.dim,
+                                       ps, pages_per, splits, a.dim ** -0.5, oplib.stream_ptr()), "decode")
+    ms = timeit(run, a.iters, a.warmup)
+    by = 2.0 * 2 * a.batch * a.ctx * a.kv_heads * a.dim
+    return report("paged_decode_attention", ms, 0.0, by, batch=a.batch, ctx=a.ctx)
+
+
+def bench_rmsnorm(a):
+    x = torch.randn(a.rows, a.hidden, device="cuda").bfloat16()
+    r = torch.randn_like(x)
+    w = torch.ones(a.hidden, device="cuda").bfloat16()
+    ms = timeit(lambda: OF.rmsnorm(x, w, 1e-6, r), a.iters, a.warmup)
+    return report("rmsnorm_fwd(+residual)", ms, 0.0, 2.0 * 4 * a.rows * a.hidden, rows=a.rows, hidden=a.hidden)
+
+
+def bench_swiglu(a):
+    gu = torch.randn(a.rows, 2 * a.inter, device="cuda").bfloat16()
+    ms = timeit(lambda: OF.swiglu(gu), a.iters, a.warmup)
+    return report("swiglu_fwd", ms, 0.0, 2.0 * 3 * a.rows * a.inter, rows=a.rows, inter=a.inter)
+
+
+def bench_adamw(a):
+    n = a.numel
+    p, m, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+    v.abs_()
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    st = torch.tensor([1.0, 1.0, 1.0, 1.0], device="cuda")
+    ms = timeit(lambda: OF.adamw_step_(p, m, v, g, pb, st, 1e-5, 0.9, 0.95, 1e-8, 0.01, 3), a.iters, a.warmup)
+    return report("adamw_fused(+bf16 copy)", ms, 0.0, n * (4 * 4 + 3 * 4 + 2), numel=n)
+
+
+def bench_logprob(a):
+    logits = torch.randn(a.rows, a.vocab, device="cuda")
+    labels = torch.randint(0, a.vocab, (a.rows,), device="cuda")
+    ms = timeit(lambda: OF.logprob_entropy_from_logits(logits, labels, 1.0), a.iters, a.warmup)
+    return report("logprob_entropy_fwd", ms, 0.0, 4.0 * a.rows * a.vocab, rows=a.rows, vocab=a.vocab)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob"])
+    ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--layout", type=str, default="nt", help="A major n|t, B major t|n: nt = x@W^T, nn = dy@W, tn = dy^T@x")
+    ap.add_argument("--epi", type=int, default=0); ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--seqlen", type=int, default=4096); ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--dim", type=int, default=128)
+    ap.add_argument("--ctx", type=int, default=1024); ap.add_argument("--splits", type=int, default=4)
+    ap.add_argument("--rows", type=int, default=32768); ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--inter", type=int, default=12288); ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--iters", type=int, default=10); ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args(argv)
+    if a.kernel == "logprob" and a.rows > 4096:
+        a.rows = 2048
+    return {"gemm": bench_gemm, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
+            "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob}[a.kernel](a)
+
+
+if __name__ == "__main__":
+    main()
