@@ -20,7 +20,7 @@ def compute_packed_sft_loss(logprobs: torch.Tensor, entropy: torch.Tensor, input
     loss = sft_loss_fn(logprobs, loss_mask)
     with torch.no_grad():
         stats_tracker.denominator(n_valid_tokens=loss_mask)
-        stats_tracker.stat(loss=-logprobs.detach(), ppl_logp=logprobs.detach(), denominator="n_valid_tokens")
+        stats_tracker.stat(nll=-logprobs.detach(), denominator="n_valid_tokens")
     return loss
 
 
