@@ -107,6 +107,12 @@ def bernoulli_reward_fn(prompt, completion, prompt_ids, completion_ids, reward=0
     return float((h >> 7) & 1)
 
 
+def small_id_fraction_reward_fn(prompt, completion, prompt_ids, completion_ids, threshold: int = 10, **kwargs) -> float:
+    """Shaped synthetic reward a random-init model can climb within a few steps: the fraction
+    of generated token ids below ``threshold``."""
+    return sum(1 for t in completion_ids if t < threshold) / max(1, len(completion_ids))
+
+
 def _load_records(path: str) -> list[dict]:
     if os.path.isdir(path):
         files = sorted(os.path.join(path, f) for f in os.listdir(path) if f.endswith((".jsonl", ".json", ".parquet")))

@@ -221,6 +221,8 @@ class NativeInferenceEngine(InferenceEngine):
         """Copies native-named tensors into the model (device-to-device or host-to-device)."""
         fut: Future = Future()
         params = dict(self.model.named_parameters())
+        if isinstance(named_tensors, dict):
+            named_tensors = named_tensors.items()
         for name, t in named_tensors:
             params[name].data.copy_(t.to(params[name].dtype), non_blocking=True)
         if self.device.type == "cuda":
@@ -229,6 +231,11 @@ class NativeInferenceEngine(InferenceEngine):
             self.set_version(meta.version)
         fut.set_result(True)
         return fut
+
+    @torch.no_grad()
+    def export_weights(self) -> dict[str, torch.Tensor]:
+        """Host copies of the parameters currently served (diagnostics, weight-sync checks)."""
+        return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters()}
 
     def update_weights_from_disk(self, meta: WeightUpdateMeta) -> Future:
         from ..models import hf_io

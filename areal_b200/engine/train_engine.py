@@ -574,6 +574,12 @@ class B200TrainEngine(TrainEngine):
                 setattr(self.optimizer, name, off[name].to(self.device, non_blocking=True))
         self._offloaded = None
 
+    @torch.no_grad()
+    def export_weights(self) -> dict[str, torch.Tensor]:
+        """Host copies of the (replicated) parameters under their native names: the payload of
+        the controller-mediated weight update for small models and CPU runs."""
+        return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters()}
+
     def export_stats(self) -> dict[str, float]:
         # reduce over the trainer ranks only (rollout ranks of a split world do not take part)
         return stats_tracker.export_all(reduce_group=self._cpu_group, distributed=self._cpu_group is not None)

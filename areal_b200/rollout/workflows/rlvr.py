@@ -39,6 +39,14 @@ class RLVRWorkflow(RolloutWorkflow):
     def __init__(self, reward_fn: Callable[..., float], gconfig: GenerationHyperparameters, tokenizer=None,
                  enable_thinking: bool = False, get_input_ids_fn: Callable = default_get_input_ids,
                  reward_in_process: bool = False, reward_timeout: float = 15.0):
+        if isinstance(reward_fn, str):  # import path: how a workflow is described to a remote worker
+            from ...utils.dynamic_import import import_from_string
+
+            reward_fn = import_from_string(reward_fn)
+        if isinstance(get_input_ids_fn, str):
+            from ...utils.dynamic_import import import_from_string
+
+            get_input_ids_fn = import_from_string(get_input_ids_fn)
         self.gconfig = gconfig
         self.tokenizer = tokenizer
         self.enable_thinking = enable_thinking
