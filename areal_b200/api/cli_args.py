@@ -378,6 +378,10 @@ class NativeInferConfig:
     random_seed: int = 1
     share_trainer_weights: bool = True  # colocated mode: read the trainer's parameters in place
     num_pages: Optional[int] = None     # fixed KV page count (default: sized from free memory)
+    # In-flight weight updates: False = running requests are interrupted and re-prefilled under
+    # the new weights (what a server that flushes its cache does); True = they keep their KV
+    # cache and simply continue, every token tagged with the version that sampled it.
+    retain_kv_on_weight_update: bool = False
 
 
 @dataclass

@@ -25,6 +25,7 @@ from concurrent.futures import Future
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
+import numpy as np
 import torch
 
 from ..api.cli_args import InferenceEngineConfig, NativeInferConfig
@@ -56,6 +57,8 @@ class _Seq:
     future: Any = None                     # (loop, asyncio future)
     out_tokens: list[int] = field(default_factory=list)
     out_logprobs: list[float] = field(default_factory=list)
+    out_versions: list[int] = field(default_factory=list)
+    row: int = -1                          # row of the static decode buffers while running
     pages: list[int] = field(default_factory=list)
     cached: int = 0                        # tokens whose KV is in the cache
     t_submit: float = 0.0
@@ -171,6 +174,24 @@ class NativeInferenceEngine(InferenceEngine):
         self.s_seeds = torch.zeros(B, dtype=torch.int32, device=dev)
         self.s_out_tok = torch.zeros(B, dtype=torch.int32, device=dev)
         self.s_out_lp = torch.zeros(B, dtype=torch.float32, device=dev)
+        # Host mirrors of the per-row decode state, packed in ONE pinned buffer so a decode
+        # step costs one host-to-device copy: columns tokens|pos|slots|lens|greedy|seeds|
+        # inv_temp(bits)|page table. Rows are stable while a sequence runs.
+        self._ncol = 7 + self.max_pages_per_seq
+        self.h_state = torch.zeros(B, self._ncol, dtype=torch.int32).pin_memory()
+        self.d_state = torch.zeros(B, self._ncol, dtype=torch.int32, device=dev)
+        hs = self.h_state.numpy()
+        self.hn_tokens, self.hn_pos, self.hn_slots, self.hn_lens = hs[:, 0], hs[:, 1], hs[:, 2], hs[:, 3]
+        self.hn_greedy, self.hn_seeds = hs[:, 4], hs[:, 5]
+        self.hn_inv_temp = hs[:, 6].view(np.float32)
+        self.hn_pt = hs[:, 7:]
+        self.hn_slots[:] = -1
+        self.hn_inv_temp[:] = 1.0
+        self.h_out = torch.zeros(2, B, dtype=torch.int32).pin_memory()
+        self.hn_out_tok = self.h_out.numpy()[0]
+        self.hn_out_lp = self.h_out.numpy()[1].view(np.float32)
+        self._row_seq: list = [None] * B
+        self._rows_free = list(range(B - 1, -1, -1))   # pop() gives the lowest free row
         self.n_splits = 4
         self.s_part_o = torch.zeros(B * cfg.num_heads * self.n_splits * cfg.head_dim, dtype=torch.float32, device=dev)
         self.s_part_ml = torch.zeros(B * cfg.num_heads * self.n_splits * 2, dtype=torch.float32, device=dev)
@@ -308,12 +329,12 @@ class NativeInferenceEngine(InferenceEngine):
                        t_submit=time.perf_counter(), top_p=g.top_p, top_k=0 if g.top_k >= 10 ** 7 else int(g.top_k))
             with self._lock:
                 self._waiting.append(seq)
-            seg_tokens, seg_lps, stop_reason, t_first = await fut
+            seg_tokens, seg_lps, seg_vers, stop_reason, t_first = await fut
             if seg_tokens and ttft == float("inf"):
                 ttft = t_first - t0
             out_tok += seg_tokens
             out_lp += seg_lps
-            out_ver += [version] * len(seg_tokens)
+            out_ver += seg_vers
             tokens = tokens + seg_tokens
             remaining -= len(seg_tokens)
         if stop_reason == "abort":
@@ -350,7 +371,8 @@ class NativeInferenceEngine(InferenceEngine):
                 torch.cuda.set_device(self.device)
             while not self._stop.is_set():
                 if self._gen_paused.is_set():
-                    self._abort_all()
+                    if not getattr(self.icfg, "retain_kv_on_weight_update", False):
+                        self._abort_all()
                     self._idle.set()
                     time.sleep(0.001)
                     continue
@@ -383,10 +405,12 @@ class NativeInferenceEngine(InferenceEngine):
 
     def _resolve(self, seq: _Seq, reason: str):
         loop, fut = seq.future
-        res = (seq.out_tokens, seq.out_logprobs, reason, seq.t_first)
+        res = (seq.out_tokens, seq.out_logprobs, seq.out_versions, reason, seq.t_first)
         if self.cache is not None and seq.pages:
             self.cache.release(seq.pages)
             seq.pages = []
+        if seq.row >= 0:
+            self._free_row(seq)
 
         def _set():
             if not fut.done():
@@ -462,6 +486,7 @@ class NativeInferenceEngine(InferenceEngine):
             s.t_first = time.perf_counter()
         s.out_tokens.append(tok)
         s.out_logprobs.append(lp)
+        s.out_versions.append(self._version)
         s.tokens.append(tok)
         self.stats["generated_tokens"] += 1
         reason = self._finish_check(s, tok)
@@ -499,15 +524,16 @@ class NativeInferenceEngine(InferenceEngine):
         done: list = []
         if admitted:
             self._prefill(admitted, done)
+            keep = [s for s in admitted if all(s is not d for d, _ in done)]
+            for s in keep:
+                self._assign_row(s)
             with self._lock:
-                self._running.extend(s for s in admitted if all(s is not d for d, _ in done))
+                self._running.extend(keep)
         with self._lock:
             batch = list(self._running)
-        batch = [s for s in batch if all(s is not d for d, _ in done)]
-        fresh = {id(s) for s in admitted}
-        decode_batch = [s for s in batch if id(s) not in fresh]
-        if decode_batch:
-            self._decode(decode_batch, done)
+        if batch:
+            # freshly prefilled sequences already hold their first token: they decode at once
+            self._decode(batch, done)
         self._retire(done)
 
     def _layer_attn_fns(self, mode: str, **kw):
@@ -574,11 +600,28 @@ class NativeInferenceEngine(InferenceEngine):
             s.cached = n
             self._accept_token(s, tok, lp, done)
 
+    def _sample_rows(self, logits: torch.Tensor, n: int, inv_temp, greedy, seeds):
+        """Launches the sampling kernel for ``n`` rows of ``logits`` with per-row parameters
+        that already live on the device; results land in ``s_out_tok`` / ``s_out_lp``."""
+        self._step += 1
+        rc = oplib.get_lib().ab2_sample(logits.data_ptr(), logits.stride(0), n, logits.shape[1], inv_temp.data_ptr(),
+                                        greedy.data_ptr(), seeds.data_ptr(), self._step & 0x7FFFFFFF,
+                                        self.s_out_tok.data_ptr(), self.s_out_lp.data_ptr(), oplib.stream_ptr())
+        oplib.check(rc, "ab2_sample")
+
+    def _fetch_samples(self, n: int):
+        """One device-to-host copy of the sampled tokens and logprobs (pinned), one sync."""
+        self.h_out[0, :n].copy_(self.s_out_tok[:n], non_blocking=True)
+        self.h_out[1, :n].copy_(self.s_out_lp[:n].view(torch.int32), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.hn_out_tok[:n].tolist(), self.hn_out_lp[:n].tolist()
+
     def _sample_cuda(self, logits: torch.Tensor, seqs: list[_Seq]):
+        """Sampling for an ad-hoc list of sequences (prefill path)."""
         n = len(seqs)
         plain = all(s.top_p >= 1.0 and s.top_k <= 0 for s in seqs)
-        self._step += 1
         if not plain:
+            self._step += 1
             out_t, out_l = [], []
             lg = logits.float().cpu()
             for i, s in enumerate(seqs):
@@ -592,45 +635,70 @@ class NativeInferenceEngine(InferenceEngine):
         self.s_inv_temp[:n].copy_(inv_t, non_blocking=True)
         self.s_greedy[:n].copy_(gr, non_blocking=True)
         self.s_seeds[:n].copy_(sd, non_blocking=True)
-        rc = oplib.get_lib().ab2_sample(logits.data_ptr(), logits.stride(0), n, logits.shape[1], self.s_inv_temp.data_ptr(),
-                                        self.s_greedy.data_ptr(), self.s_seeds.data_ptr(), self._step & 0x7FFFFFFF,
-                                        self.s_out_tok.data_ptr(), self.s_out_lp.data_ptr(), oplib.stream_ptr())
-        oplib.check(rc, "ab2_sample")
-        toks = self.s_out_tok[:n].tolist()
-        lps = self.s_out_lp[:n].tolist()
-        return toks, lps
+        self._sample_rows(logits, n, self.s_inv_temp, self.s_greedy, self.s_seeds)
+        return self._fetch_samples(n)
+
+    # ---- stable rows of the static decode buffers
+    def _assign_row(self, s: _Seq):
+        r = self._rows_free.pop()
+        s.row = r
+        self._row_seq[r] = s
+        self.hn_pt[r, :] = 0
+        self.hn_pt[r, :len(s.pages)] = s.pages
+        self.hn_greedy[r] = int(s.greedy)
+        self.hn_seeds[r] = s.seed & 0x7FFFFFFF
+        self.hn_inv_temp[r] = 1.0 if s.greedy else 1.0 / max(s.temperature, 1e-6)
+        p = len(s.tokens) - 1              # position of the token the next decode step feeds
+        self.hn_tokens[r] = s.tokens[-1]
+        self.hn_pos[r] = p
+        self.hn_lens[r] = p + 1
+
+    def _free_row(self, s: _Seq):
+        r = s.row
+        s.row = -1
+        if r < 0 or self._row_seq[r] is not s:
+            return
+        self._row_seq[r] = None
+        self.hn_lens[r] = 0
+        self.hn_slots[r] = -1
+        self.hn_tokens[r] = 0
+        self.hn_pos[r] = 0
+        # keep the free list sorted descending so pop() returns the lowest row
+        import bisect
+
+        keys = [-x for x in self._rows_free]
+        self._rows_free.insert(bisect.bisect_left(keys, -r), r)
 
     def _decode_forward(self, B: int) -> torch.Tensor:
         """One decode step over the static buffers (first B rows). Returns fp32 logits [B, V]."""
+        st = self.d_state
         pb = PackedBatch.__new__(PackedBatch)
         pb.cu_seqlens = None
-        pb.position_ids = self.s_pos[:B]
+        pb.position_ids = st[:B, 1]
         pb.total_tokens, pb.max_seqlen, pb.tile_info = B, 1, None
         fns = self._layer_attn_fns("decode", slots=self.s_slots[:B], pt=self.s_pt[:B], lens=self.s_lens[:B])
+        # strided columns of the packed state -> the contiguous buffers the kernels read
+        self.s_tokens[:B].copy_(st[:B, 0])
+        self.s_pos[:B].copy_(st[:B, 1])
+        self.s_slots[:B].copy_(st[:B, 2])
+        self.s_lens[:B].copy_(st[:B, 3])
+        self.s_pt[:B].copy_(st[:B, 7:])
+        pb.position_ids = self.s_pos[:B]
         hidden = self.model.forward_hidden(self.s_tokens[:B], pb, attn_fns=fns)
         return self.model.logits(hidden)
 
     def _decode(self, seqs: list[_Seq], done: list):
-        n = len(seqs)
-        B = next(b for b in DECODE_BUCKETS if b >= n)
-        B = min(B, self.max_batch)
-        toks = torch.zeros(B, dtype=torch.int32)
-        pos = torch.zeros(B, dtype=torch.int32)
-        slots = torch.full((B,), -1, dtype=torch.int32)
-        lens = torch.zeros(B, dtype=torch.int32)
-        pt = torch.zeros(B, self.max_pages_per_seq, dtype=torch.int32)
-        for i, s in enumerate(seqs):
-            p = len(s.tokens) - 1          # position of the token being fed
-            toks[i] = s.tokens[-1]
-            pos[i] = p
-            slots[i] = self._slot_of(s, p)
-            lens[i] = p + 1
-            pt[i, :len(s.pages)] = torch.tensor(s.pages, dtype=torch.int32)
-        self.s_tokens[:B].copy_(toks, non_blocking=True)
-        self.s_pos[:B].copy_(pos, non_blocking=True)
-        self.s_slots[:B].copy_(slots, non_blocking=True)
-        self.s_lens[:B].copy_(lens, non_blocking=True)
-        self.s_pt[:B].copy_(pt, non_blocking=True)
+        """One decode step for every running row. Host work is vectorised over rows (numpy on
+        the pinned mirror) and the step costs one H2D copy, one graph replay, the sampling
+        launch and one D2H copy."""
+        hi = max(s.row for s in seqs) + 1
+        B = min(next(b for b in DECODE_BUCKETS if b >= hi), self.max_batch)
+        ps = self.cache.page_size
+        pos = self.hn_pos[:B]
+        active = self.hn_lens[:B] > 0
+        page = self.hn_pt[np.arange(B), np.minimum(pos // ps, self.max_pages_per_seq - 1)]
+        self.hn_slots[:B] = np.where(active, page * ps + pos % ps, -1)
+        self.d_state[:B].copy_(self.h_state[:B], non_blocking=True)
         if self.icfg.use_cuda_graph:
             g = self._graphs.get(B)
             if g is None:
@@ -640,10 +708,28 @@ class NativeInferenceEngine(InferenceEngine):
             oplib.LAUNCHES["count"] += n_kernels
         else:
             logits = self._decode_forward(B)
-        out_t, out_l = self._sample_cuda(logits[:n], seqs)
+        plain = all(s.top_p >= 1.0 and s.top_k <= 0 for s in seqs)
+        if plain:
+            st = self.d_state
+            self.s_greedy[:B].copy_(st[:B, 4])
+            self.s_seeds[:B].copy_(st[:B, 5])
+            self.s_inv_temp[:B].copy_(st[:B, 6].view(torch.float32))
+            self._sample_rows(logits, B, self.s_inv_temp, self.s_greedy, self.s_seeds)
+            toks, lps = self._fetch_samples(B)
+        else:
+            self._step += 1
+            lg = logits[:B].float().cpu()
+            toks, lps = [0] * B, [0.0] * B
+            for s in seqs:
+                toks[s.row], lps[s.row] = self._sample_cpu(lg[s.row], s)
         self.stats["decode_steps"] += 1
-        for s, tok, lp in zip(seqs, out_t, out_l):
-            self._accept_token(s, tok, lp, done)
+        # advance the mirrors for the next step (vectorised), then per-sequence bookkeeping
+        self.hn_tokens[:B] = np.where(active, np.asarray(toks, dtype=np.int32), 0)
+        self.hn_pos[:B] += active
+        self.hn_lens[:B] += active
+        for s in seqs:
+            r = s.row
+            self._accept_token(s, toks[r], lps[r], done)
 
     def _capture(self, B: int):
         # warm-up outside capture (sets kernel attributes, allocates the error word)

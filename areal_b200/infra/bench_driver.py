@@ -69,7 +69,8 @@ def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOCon
                                       max_head_offpolicyness=args.staleness),
         native_infer=NativeInferConfig(max_running_requests=max_running, page_size=64,
                                        context_length=args.prompt_len + args.max_len + 64, mem_fraction_static=0.35 if n_pairs == 1 and int(os.environ.get('WORLD_SIZE', '1')) == 1 else 0.6,
-                                       max_prefill_tokens=16384),
+                                       max_prefill_tokens=16384,
+                                       retain_kv_on_weight_update=bool(getattr(args, "retain_kv", 1))),
         actor=PPOActorConfig(init_from_scratch=True, dtype="bfloat16", gradient_checkpointing=True,
                              optimizer=OptimizerConfig(lr=1e-6, weight_decay=0.01, gradient_clipping=1.0),
                              mb_spec=MicroBatchSpec(max_tokens_per_mb=args.max_tokens_per_mb),
@@ -206,7 +207,9 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
         "config": {"model": args.model, "global_batch": args.prompts_per_gpu_pair * args.group_size * n_train,
                    "seq_len": seq_len, "prompt_len": args.prompt_len, "response_median": args.median_len,
                    "response_cap": args.max_len, "group_size": args.group_size, "parallelism": parallelism,
-                   "max_staleness": args.staleness, "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
+                   "max_staleness": args.staleness,
+                   "inflight_weight_update": "running requests keep their KV cache" if getattr(args, "retain_kv", 1) else "running requests are re-prefilled",
+                   "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
                    "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms,
                    "phase_seconds_per_step": {k_: round(v_, 4) for k_, v_ in sorted(phases.items())}},
         "clocks": clocks,

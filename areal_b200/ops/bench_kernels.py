@@ -174,9 +174,52 @@ def bench_logprob(a):
     return report("logprob_entropy_fwd", ms, 0.0, 4.0 * a.rows * a.vocab, rows=a.rows, vocab=a.vocab)
 
 
+def bench_engine_decode(a):
+    """Decode throughput of the rollout engine itself (continuous batching, CUDA graphs):
+    ``--batch`` concurrent requests of ``--ctx`` prompt tokens generating ``--new`` tokens."""
+    import asyncio
+    import time
+
+    from ..api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeInferConfig
+    from ..api.io_struct import ModelRequest
+    from ..engine.infer_engine import NativeInferenceEngine
+    from ..models.config import preset
+
+    mc = preset(a.model) if not a.layers else preset(a.model, num_layers=a.layers)
+    eng = NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=a.batch, context_length=a.ctx + a.new + 64,
+                                                                           mem_fraction_static=0.5), model_config=mc)
+    eng.initialize(start_executor=False)
+    g = GenerationHyperparameters(max_new_tokens=a.new, max_tokens=a.ctx + a.new + 8, ignore_eos=True)
+    gen = torch.Generator().manual_seed(0)
+
+    async def run():
+        reqs = [ModelRequest(input_ids=torch.randint(0, mc.vocab_size, (a.ctx,), generator=gen).tolist(), gconfig=g) for _ in range(a.batch)]
+        return await asyncio.gather(*[eng.agenerate(r) for r in reqs])
+    asyncio.run(run())          # warm-up: captures the graphs
+    torch.cuda.synchronize()
+    s0 = dict(eng.stats)
+    t0 = time.perf_counter()
+    out = asyncio.run(run())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    steps = eng.stats["decode_steps"] - s0.get("decode_steps", 0)
+    ntok = sum(r.output_len for r in out)
+    wbytes = 2.0 * mc.num_params()
+    res = {"kernel": "engine_decode (end to end, host included)", "model": a.model, "layers": mc.num_layers, "batch": a.batch, "ctx": a.ctx,
+           "new": a.new, "seconds": round(dt, 3), "decode_steps": int(steps), "tokens_per_s": round(ntok / dt, 1),
+           "ms_per_step_incl_prefill": round(1e3 * dt / max(1, steps), 3),
+           "weight_stream_frac_of_hbm_peak": round(wbytes * steps / dt / 1e9 / peaks()["hbm_gbs"], 3), "kernel_error": oplib.kernel_error()}
+    print(json.dumps(res), flush=True)
+    eng.destroy()
+    return res
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob"])
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
+                                           "engine_decode"])
+    ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--layout", type=str, default="nt", help="A major n|t, B major t|n: nt = x@W^T, nn = dy@W, tn = dy^T@x")
     ap.add_argument("--epi", type=int, default=0); ap.add_argument("--bn", type=int, default=0)
@@ -192,7 +235,8 @@ def main(argv=None):
     if a.kernel == "logprob" and a.rows > 4096:
         a.rows = 2048
     return {"gemm": bench_gemm, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
-            "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob}[a.kernel](a)
+            "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
+            "engine_decode": bench_engine_decode}[a.kernel](a)
 
 
 if __name__ == "__main__":

@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument("--max-len", type=int, default=768)
     ap.add_argument("--max-tokens-per-mb", type=int, default=16384)
     ap.add_argument("--staleness", type=int, default=2)
+    ap.add_argument("--retain-kv", type=int, default=1, help="1: requests in flight keep their KV cache across a weight update; "
+                    "0: they are interrupted and re-prefilled under the new weights")
     return ap.parse_args()
 
 

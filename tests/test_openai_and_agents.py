@@ -1,0 +1,202 @@
+"""OpenAI-compatible client, interaction cache, HTTP proxy, agent adapter, multi-turn workflow
+(CPU, scripted engine)."""
+import asyncio
+import json
+import urllib.request
+
+import pytest
+import torch
+
+from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig
+from areal_b200.api.io_struct import ModelResponse
+from areal_b200.openai import ArealOpenAI
+from areal_b200.openai.proxy import OpenAIProxyServer, anthropic_to_openai
+from areal_b200.openai.tool_call_parser import parse_tool_calls, split_reasoning
+from areal_b200.rollout.workflows.agent import AgentRolloutAdapter
+from areal_b200.rollout.workflows.multi_turn import MultiTurnWorkflow
+
+
+class ByteTok:
+    eos_token_id = 0
+    pad_token_id = 0
+
+    def encode(self, text):
+        return list(text.encode())
+
+    def decode(self, ids):
+        return bytes(int(i) for i in ids if int(i) != 0).decode(errors="replace")
+
+
+class ScriptedEngine:
+    """Answers with the next scripted string; records the requests it saw."""
+
+    def __init__(self, answers, version=3):
+        self.answers, self.k, self.version, self.requests = list(answers), 0, version, []
+
+    def get_version(self):
+        return self.version
+
+    async def agenerate(self, req):
+        self.requests.append(req)
+        text = self.answers[min(self.k, len(self.answers) - 1)]
+        self.k += 1
+        out = list(text.encode())[: req.gconfig.max_new_tokens - 1] + [0]
+        return ModelResponse(input_tokens=list(req.input_ids), output_tokens=out, output_logprobs=[-0.5] * len(out),
+                             output_versions=[self.version] * len(out), stop_reason="stop")
+
+
+def test_client_records_tokens_rewards_and_exports_individual():
+    eng, tok = ScriptedEngine(["four", "five"]), ByteTok()
+    cl = ArealOpenAI(eng, tok, gconfig=GenerationHyperparameters(max_new_tokens=32))
+
+    async def go():
+        m = [{"role": "user", "content": "2+2?"}]
+        c1 = await cl.chat.completions.create(messages=m, temperature=0.7, max_completion_tokens=16)
+        m += [{"role": "assistant", "content": c1.choices[0].message.content}, {"role": "user", "content": "again"}]
+        c2 = await cl.chat.completions.create(messages=m)
+        return c1, c2
+    c1, c2 = asyncio.run(go())
+    assert c1.choices[0].message.content == "four" and c1.usage.completion_tokens == 5
+    assert eng.requests[0].gconfig.temperature == 0.7 and eng.requests[0].gconfig.max_new_tokens == 16
+    cl.set_reward(c1.id, 0.5)
+    cl.set_last_reward(1.0)
+    cl.apply_reward_discount(0.5)
+    with pytest.raises(RuntimeError):
+        cl.apply_reward_discount(0.5)
+    inter = cl.export_interactions("individual")
+    assert list(inter) == [c1.id, c2.id]
+    assert inter[c2.id].reward == 1.0 and inter[c1.id].reward == pytest.approx(0.5 + 0.5 * 1.0)
+    td = inter[c1.id].to_tensor_dict()
+    n_in = len(eng.requests[0].input_ids)
+    assert td["input_ids"].shape == (1, n_in + 5) and td["loss_mask"][0].tolist() == [0] * n_in + [1] * 5
+    assert td["versions"][0, -1] == 3 and td["versions"][0, 0] == -1 and td["logprobs"][0, -1] == -0.5
+    batch = cl.to_trajectory("individual")
+    assert batch["input_ids"].shape[0] == 2 and batch["rewards"].tolist() == [1.0, 1.0]
+    with pytest.raises(ValueError):   # hf template type cannot be exported as a token-exact tree
+        cl.export_interactions("concat")
+
+
+def test_concat_export_builds_prefix_tree():
+    eng, tok = ScriptedEngine(["a1", "a2", "b2"]), ByteTok()
+    cl = ArealOpenAI(eng, tok, chat_template_type="concat", gconfig=GenerationHyperparameters(max_new_tokens=8))
+
+    async def go():
+        root = [{"role": "user", "content": "q"}]
+        c1 = await cl.chat.completions.create(messages=root)
+        h = root + [{"role": "assistant", "content": c1.choices[0].message.content}]
+        c2 = await cl.chat.completions.create(messages=h + [{"role": "user", "content": "x"}])
+        c3 = await cl.chat.completions.create(messages=h + [{"role": "user", "content": "y"}])
+        return c1, c2, c3
+    c1, c2, c3 = asyncio.run(go())
+    for c in (c2, c3):
+        assert cl.get_interaction(c.id).parent is cl.get_interaction(c1.id)
+    cl.set_reward(c2.id, 1.0)
+    cl.set_reward(c3.id, 0.0)
+    leaves = cl.export_interactions("concat")
+    assert set(leaves) == {c2.id, c3.id}
+    td = leaves[c2.id].to_tensor_dict()
+    p = cl.get_interaction(c1.id).to_tensor_dict()
+    n1 = p["input_ids"].shape[1]
+    assert td["input_ids"][0, :n1].tolist() == p["input_ids"][0].tolist()       # the parent's tokens are the prefix
+    assert td["loss_mask"][0, :n1].tolist() == p["loss_mask"][0].tolist()       # ... and stay trainable
+    assert td["loss_mask"][0].sum() == 3 + 3                                    # "a1"+eos and "a2"+eos
+    # the second request was built from the parent's exact tokens
+    assert eng.requests[1].input_ids[:n1] == p["input_ids"][0].tolist()
+
+
+def test_tool_calls_and_reasoning_parsing():
+    tools = [{"type": "function", "function": {"name": "calc", "parameters": {}}}]
+    text = 'let me see <tool_call>{"name": "calc", "arguments": {"x": 1}}</tool_call>'
+    rest, calls = parse_tool_calls(text, tools)
+    assert rest == "let me see" and calls[0].function.name == "calc" and json.loads(calls[0].function.arguments) == {"x": 1}
+    rest, calls = parse_tool_calls('<tool_call>{"name": "other", "arguments": {}}</tool_call>', tools)
+    assert not calls and "tool_call" in rest
+    rest, calls = parse_tool_calls("<tool_call>{broken</tool_call>", tools)
+    assert not calls
+    assert split_reasoning("<think>hmm</think>answer") == ("hmm", "answer")
+    eng = ScriptedEngine(['<think>t</think><tool_call>{"name": "calc", "arguments": {"x": 2}}</tool_call>'])
+    cl = ArealOpenAI(eng, ByteTok(), gconfig=GenerationHyperparameters(max_new_tokens=128))
+    c = asyncio.run(cl.chat.completions.create(messages=[{"role": "user", "content": "?"}], tools=tools))
+    assert c.choices[0].finish_reason == "tool_calls" and c.choices[0].message.tool_calls[0].function.name == "calc"
+    assert c.choices[0].message.reasoning_content == "t"
+
+
+def _post(url, body, key=None):
+    req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json",
+                                 **({"Authorization": f"Bearer {key}"} if key else {})})
+    try:
+        with urllib.request.urlopen(req, timeout=30) as r:
+            return r.status, json.loads(r.read())
+    except urllib.error.HTTPError as e:
+        return e.code, json.loads(e.read())
+
+
+def test_http_proxy_sessions_rewards_export_and_anthropic_route():
+    eng = ScriptedEngine(["hello", "world"])
+    px = OpenAIProxyServer(eng, ByteTok(), GenerationHyperparameters(max_new_tokens=16), admin_key="adm").start()
+    try:
+        root = px.base_url[:-3]
+        assert _post(f"{root}/rl/start_session", {})[0] == 401
+        code, s = _post(f"{root}/rl/start_session", {}, "adm")
+        key = s["api_key"]
+        assert _post(f"{px.base_url}/chat/completions", {"messages": [{"role": "user", "content": "hi"}]}, "sk-bad")[0] == 401
+        code, c = _post(f"{px.base_url}/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 8}, key)
+        assert code == 200 and c["choices"][0]["message"]["content"] == "hello" and c["usage"]["completion_tokens"] == 6
+        code, a = _post(f"{root}/v1/messages", {"system": "s", "max_tokens": 8, "messages": [
+            {"role": "user", "content": [{"type": "text", "text": "hi"}]}]}, key)
+        assert code == 200 and a["content"][0]["text"] == "world" and a["stop_reason"] == "end_turn"
+        assert _post(f"{root}/rl/set_reward", {"reward": 2.0}, key)[0] == 200
+        assert _post(f"{root}/rl/end_session", {}, key)[0] == 200
+        assert _post(f"{px.base_url}/chat/completions", {"messages": []}, key)[0] == 401   # ended
+        code, ex = _post(f"{root}/rl/export_trajectories", {"api_key": key, "discount": 1.0}, "adm")
+        assert code == 200 and len(ex["interactions"]) == 2
+        assert all(v["rewards"] == [2.0] for v in ex["interactions"].values())
+    finally:
+        px.stop()
+    o = anthropic_to_openai({"messages": [{"role": "user", "content": [{"type": "tool_result", "tool_use_id": "t1", "content": "42"}]}],
+                             "tools": [{"name": "calc", "input_schema": {"type": "object"}}]})
+    assert o["messages"][0] == {"role": "tool", "tool_call_id": "t1", "content": "42"} and o["tools"][0]["function"]["name"] == "calc"
+
+
+class EchoAgent:
+    tokenizer = ByteTok()
+    gconfig = GenerationHyperparameters(max_new_tokens=8)
+
+    async def run(self, data, client):
+        c1 = await client.chat.completions.create(messages=[{"role": "user", "content": data["q"]}])
+        c2 = await client.chat.completions.create(messages=[{"role": "user", "content": data["q"] + "!"}])
+        return {c1.id: 0.25, c2.id: 1.0} if data.get("per_call") else (None if data.get("reject") else 1.0)
+
+
+def test_agent_adapter_and_executor_resolution():
+    from areal_b200.rollout.executor import WorkflowExecutor
+
+    eng = ScriptedEngine(["x", "y"])
+    ad = AgentRolloutAdapter(EchoAgent(), turn_discount=0.5)
+    traj = asyncio.run(ad.arun_episode(eng, {"q": "a"}))
+    assert traj["input_ids"].shape[0] == 2 and traj["rewards"].tolist() == [0.5, 1.0]
+    traj = asyncio.run(AgentRolloutAdapter(EchoAgent()).arun_episode(ScriptedEngine(["x"]), {"q": "a", "per_call": True}))
+    assert traj["rewards"].tolist() == [1.25, 1.0]
+    assert asyncio.run(AgentRolloutAdapter(EchoAgent()).arun_episode(ScriptedEngine(["x"]), {"q": "a", "reject": True})) is None
+    ex = WorkflowExecutor(InferenceEngineConfig(consumer_batch_size=1, max_concurrent_rollouts=2), eng)
+    assert isinstance(ex._resolve_workflow(EchoAgent(), None), AgentRolloutAdapter)
+
+
+def test_multi_turn_retries_with_discount_and_masks_feedback():
+    tok = ByteTok()
+
+    def reward(prompt, completion, pids, cids, **kw):
+        return 1.0 if "right" in completion else 0.0
+    g = GenerationHyperparameters(max_new_tokens=16, max_tokens=512)
+    wf = MultiTurnWorkflow(reward, g, tok, max_turns=3, turn_discount=0.5, reward_in_process=True)
+    eng = ScriptedEngine(["wrong", "right"])
+    t = asyncio.run(wf.arun_episode(eng, {"input_ids": tok.encode("q?")}))
+    assert t["rewards"].item() == 0.5 and len(eng.requests) == 2
+    fb = len(wf._encode_feedback())
+    assert int(t["loss_mask"].sum()) == 6 + 6                    # two answers (+eos), feedback and prompt masked out
+    assert t["input_ids"].shape[1] == 2 + 6 + fb + 6
+    assert eng.requests[1].input_ids == t["input_ids"][0, : 2 + 6 + fb].tolist()
+    t = asyncio.run(wf.arun_episode(ScriptedEngine(["no", "no", "no"]), {"input_ids": tok.encode("q?")}))
+    assert t["rewards"].item() == 0.0
+    t = asyncio.run(wf.arun_episode(ScriptedEngine(["right"]), {"input_ids": tok.encode("q?")}))
+    assert t["rewards"].item() == 1.0
