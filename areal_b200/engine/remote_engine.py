@@ -1,0 +1,333 @@
+"""Client-side inference engine for rollout servers reached over HTTP.
+
+Implements the ``InferenceEngine`` contract against one or more servers (this framework's own
+``areal_b200.engine.server`` or any server speaking the same routes): server discovery
+through ``name_resolve`` or explicit addresses, round-robin scheduling with request-id
+affinity, interruptible ``agenerate`` (a generation aborted by a weight update is resubmitted
+with the tokens produced so far; every token keeps the version that sampled it), weight-update
+fan-out, pause / continue, and the workflow executor on top. Reference:
+``areal/infra/remote_inf_engine.py:434-1695`` and ``areal/engine/sglang_remote.py``.
+"""
+from __future__ import annotations
+
+import asyncio
+import os
+import subprocess
+import sys
+import threading
+import time
+import uuid
+from concurrent.futures import Future, ThreadPoolExecutor
+from typing import Any, Optional
+
+from ..api.cli_args import InferenceEngineConfig
+from ..api.engine_api import InferenceEngine
+from ..api.io_struct import ModelRequest, ModelResponse, ParamSpec, WeightUpdateMeta
+from ..utils import logging as alog
+from ..utils import name_resolve, names
+
+logger = alog.getLogger("remote_engine")
+
+
+async def arequest_with_retry(session, addr: str, endpoint: str, payload: Optional[dict] = None, method: str = "POST",
+                              max_retries: int = 3, timeout: float = 3600.0, retry_delay: float = 0.5) -> dict:
+    """One JSON request with bounded retries on connection errors and 5xx answers."""
+    import aiohttp
+
+    last: Optional[BaseException] = None
+    url = f"http://{addr}{endpoint}"
+    for attempt in range(max_retries):
+        try:
+            async with session.request(method, url, json=payload, timeout=aiohttp.ClientTimeout(total=timeout)) as r:
+                if r.status >= 500:
+                    raise RuntimeError(f"{url} -> HTTP {r.status}: {(await r.text())[:500]}")
+                r.raise_for_status()
+                return await r.json()
+        except (aiohttp.ClientConnectionError, asyncio.TimeoutError, RuntimeError) as e:
+            last = e
+            if attempt + 1 < max_retries:
+                await asyncio.sleep(retry_delay * (attempt + 1))
+    raise RuntimeError(f"request to {url} failed after {max_retries} attempts: {last!r}")
+
+
+class RemoteInfEngine(InferenceEngine):
+    def __init__(self, config: InferenceEngineConfig, addresses: Optional[list[str]] = None):
+        self.config = config
+        self.addresses: list[str] = list(addresses or [])
+        self._version = 0
+        self._rr = 0
+        self._rid_to_addr: dict[str, str] = {}
+        self._rid_order: list[str] = []
+        self._lock = threading.Lock()
+        self._executor = None
+        self._paused = threading.Event()
+        self._pool = ThreadPoolExecutor(max_workers=8, thread_name_prefix="remote-engine")
+        self._sessions: dict[int, Any] = {}
+        self._server_procs: list[subprocess.Popen] = []
+        self._initialized = False
+
+    # ------------------------------------------------------------------ lifecycle
+    def initialize(self, addr: Optional[Any] = None, train_data_parallel_size: int = 1, start_executor: bool = True, **kwargs):
+        if addr:
+            self.addresses = [addr] if isinstance(addr, str) else list(addr)
+        if not self.addresses and os.environ.get("AREAL_LLM_SERVER_ADDRS"):
+            self.addresses = os.environ["AREAL_LLM_SERVER_ADDRS"].split(",")
+        if not self.addresses:
+            key = names.gen_servers(self.config.experiment_name or "", self.config.trial_name or "")
+            deadline = time.monotonic() + self.config.setup_timeout
+            while time.monotonic() < deadline:
+                self.addresses = sorted(set(name_resolve.get_subtree(key)))
+                if self.addresses:
+                    break
+                time.sleep(0.5)
+        if not self.addresses:
+            raise RuntimeError("no inference server address (argument, AREAL_LLM_SERVER_ADDRS or name_resolve)")
+        self._wait_healthy()
+        if start_executor:
+            from ..rollout.executor import WorkflowExecutor
+
+            self._executor = WorkflowExecutor(self.config, self, dp_world_size=train_data_parallel_size).initialize()
+        self._initialized = True
+        return self
+
+    @property
+    def initialized(self) -> bool:
+        return self._initialized
+
+    def _wait_healthy(self):
+        import urllib.request
+
+        deadline = time.monotonic() + self.config.setup_timeout
+        for a in self.addresses:
+            while True:
+                try:
+                    with urllib.request.urlopen(f"http://{a}/health", timeout=2) as r:
+                        if r.status == 200:
+                            break
+                except OSError:
+                    pass
+                if time.monotonic() > deadline:
+                    raise TimeoutError(f"inference server {a} not healthy after {self.config.setup_timeout}s")
+                time.sleep(0.2)
+
+    def destroy(self):
+        if self._executor is not None:
+            self._executor.destroy()
+            self._executor = None
+        self.teardown_server()
+        self._pool.shutdown(wait=False)
+        self._initialized = False
+
+    def launch_server(self, server_args: dict[str, Any]) -> str:
+        """Starts a local server process (``python -m areal_b200.engine.server``) and returns
+        its address once it reports ready."""
+        cmd = [sys.executable, "-m", "areal_b200.engine.server"]
+        for k, v in server_args.items():
+            cmd += [f"--{k.replace('_', '-')}", str(v)]
+        p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True)
+        self._server_procs.append(p)
+        deadline = time.monotonic() + self.config.setup_timeout
+        addr = None
+        while time.monotonic() < deadline:
+            line = p.stdout.readline()
+            if not line:
+                if p.poll() is not None:
+                    raise RuntimeError(f"inference server exited with code {p.returncode}")
+                continue
+            if line.startswith("INFER_SERVER_READY"):
+                addr = line.split()[1]
+                break
+        if addr is None:
+            raise TimeoutError("inference server did not become ready")
+        threading.Thread(target=lambda: [None for _ in p.stdout], daemon=True).start()  # keep draining the pipe
+        self.addresses.append(addr)
+        return addr
+
+    def teardown_server(self):
+        for p in self._server_procs:
+            if p.poll() is None:
+                p.terminate()
+                try:
+                    p.wait(timeout=10)
+                except subprocess.TimeoutExpired:
+                    p.kill()
+        self._server_procs.clear()
+
+    # ------------------------------------------------------------------ scheduling
+    def choose_server(self, rid: Optional[str] = None) -> str:
+        with self._lock:
+            if rid is not None and rid in self._rid_to_addr:
+                return self._rid_to_addr[rid]          # KV-cache affinity for resumed / multi-turn requests
+            a = self.addresses[self._rr % len(self.addresses)]
+            self._rr += 1
+            if rid is not None:
+                self._rid_to_addr[rid] = a
+                self._rid_order.append(rid)
+                if len(self._rid_order) > 1 << 16:
+                    for old in self._rid_order[: 1 << 15]:
+                        self._rid_to_addr.pop(old, None)
+                    del self._rid_order[: 1 << 15]
+            return a
+
+    async def _session(self):
+        import aiohttp
+
+        loop = asyncio.get_running_loop()
+        s = self._sessions.get(id(loop))
+        if s is None or s.closed:
+            s = aiohttp.ClientSession(connector=aiohttp.TCPConnector(limit=0))
+            self._sessions[id(loop)] = s
+        return s
+
+    # ------------------------------------------------------------------ generation
+    async def agenerate(self, req: ModelRequest) -> ModelResponse:
+        g = req.gconfig
+        if g.n_samples != 1:
+            raise ValueError("agenerate serves one sample per request; workflows fan out n_samples themselves")
+        prompt = list(req.input_ids)
+        budget = min(g.max_new_tokens, g.max_tokens - len(prompt))
+        if budget <= 0:
+            raise ValueError(f"prompt of {len(prompt)} tokens leaves no room under max_tokens={g.max_tokens}")
+        out_tok: list[int] = []
+        out_lp: list[float] = []
+        out_ver: list[int] = []
+        stop = "abort"
+        t0 = time.perf_counter()
+        ttft = float("inf")
+        addr = self.choose_server(req.rid)
+        session = await self._session()
+        while stop not in ("stop", "length", "tool_calls") and len(out_tok) < budget:
+            while self._paused.is_set():
+                await asyncio.sleep(0.01)
+            payload = {"rid": req.rid, "input_ids": prompt + out_tok, "return_logprob": True,
+                       "sampling_params": {"max_new_tokens": budget - len(out_tok), "min_new_tokens": max(0, g.min_new_tokens - len(out_tok)),
+                                           "temperature": 0.0 if g.greedy else g.temperature, "top_p": g.top_p,
+                                           "top_k": -1 if g.top_k >= 10 ** 7 else g.top_k, "stop_token_ids": g.stop_token_ids,
+                                           "ignore_eos": g.ignore_eos, "seed": g.seed}}
+            r = await arequest_with_retry(session, addr, "/generate", payload, max_retries=self.config.request_retries,
+                                          timeout=self.config.request_timeout)
+            seg = r.get("output_ids", [])
+            if seg and ttft == float("inf"):
+                ttft = time.perf_counter() - t0
+            vers = r.get("output_versions") or [self._version] * len(seg)
+            out_tok += seg
+            out_lp += r.get("output_logprobs", [0.0] * len(seg))
+            out_ver += vers
+            stop = r["meta_info"]["finish_reason"]["type"]
+            if stop == "abort" and not seg:
+                await asyncio.sleep(0.02)     # server is paused for a weight update
+        if stop == "abort":
+            stop = "length"
+        lat = time.perf_counter() - t0
+        return ModelResponse(input_tokens=prompt, output_tokens=out_tok, output_logprobs=out_lp, output_versions=out_ver,
+                             stop_reason=stop, latency=lat, ttft=ttft, tokenizer=req.tokenizer)
+
+    # ------------------------------------------------------------------ control fan-out
+    def _fanout(self, endpoint: str, payload: Optional[dict] = None, timeout: float = 3600.0) -> list[dict]:
+        import json
+        import urllib.request
+
+        def one(a):
+            req = urllib.request.Request(f"http://{a}{endpoint}", data=json.dumps(payload or {}).encode(),
+                                         headers={"Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=timeout) as r:
+                return json.loads(r.read())
+        return list(self._pool.map(one, self.addresses))
+
+    def _fanout_future(self, endpoint: str, payload_fn, after=None) -> Future:
+        fut: Future = Future()
+
+        def run():
+            try:
+                import json
+                import urllib.request
+
+                def one(ia):
+                    i, a = ia
+                    req = urllib.request.Request(f"http://{a}{endpoint}", data=json.dumps(payload_fn(i)).encode(),
+                                                 headers={"Content-Type": "application/json"})
+                    with urllib.request.urlopen(req, timeout=self.config.request_timeout) as r:
+                        return json.loads(r.read())
+                res = list(self._pool.map(one, enumerate(self.addresses)))
+                if after:
+                    after()
+                fut.set_result(res)
+            except BaseException as e:
+                fut.set_exception(e)
+        threading.Thread(target=run, daemon=True).start()
+        return fut
+
+    def set_version(self, version: int) -> None:
+        self._version = version
+        self._fanout("/set_version", {"version": version})
+
+    def get_version(self) -> int:
+        return self._version
+
+    def pause_generation(self):
+        self._paused.set()
+        self._fanout("/pause_generation")
+
+    def continue_generation(self):
+        self._fanout("/continue_generation")
+        self._paused.clear()
+
+    def update_weights_from_disk(self, meta: WeightUpdateMeta) -> Future:
+        def done():
+            if meta.version is not None:
+                self._version = meta.version
+        return self._fanout_future("/update_weights_from_disk", lambda i: {"model_path": meta.path, "version": meta.version}, done)
+
+    def init_weights_update_group(self, meta: WeightUpdateMeta) -> Future:
+        n = len(self.addresses)
+        return self._fanout_future("/init_weights_update_group", lambda i: {
+            "master_address": meta.nccl_master_address, "master_port": meta.nccl_master_port, "rank_offset": 1 + i,
+            "world_size": n + 1, "group_name": meta.nccl_group_name})
+
+    def update_weights_from_distributed(self, meta: WeightUpdateMeta, param_specs: list[ParamSpec]) -> Future:
+        body = {"names": [p.name for p in param_specs], "dtypes": [p.dtype for p in param_specs],
+                "shapes": [list(p.shape) for p in param_specs], "group_name": meta.nccl_group_name, "version": meta.version}
+
+        def done():
+            if meta.version is not None:
+                self._version = meta.version
+        return self._fanout_future("/update_weights_from_distributed", lambda i: body, done)
+
+    def update_weights_from_tensors(self, named_tensors, meta: Optional[WeightUpdateMeta] = None) -> Future:
+        raise NotImplementedError("tensors cannot be handed to another process; use disk, xccl or p2p weight updates")
+
+    def offload(self, tags: Optional[list[str]] = None):
+        self._fanout("/release_memory_occupation", {"tags": tags})
+
+    def onload(self, tags: Optional[list[str]] = None):
+        self._fanout("/resume_memory_occupation", {"tags": tags})
+
+    # ------------------------------------------------------------------ executor passthrough
+    def submit(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, task_id=None, is_eval=False) -> int:
+        return self._executor.submit(data, workflow, workflow_kwargs, should_accept_fn, task_id, is_eval)
+
+    def wait(self, count, timeout=None, raise_timeout=True):
+        return self._executor.wait(count, timeout, raise_timeout)
+
+    def wait_for_task(self, task_id, timeout=None, raise_timeout=True):
+        return self._executor.wait_for_task(task_id, timeout, raise_timeout)
+
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None):
+        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn)
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None, dynamic_bs=False):
+        return self._executor.prepare_batch(dataloader, workflow, workflow_kwargs, should_accept_fn, dynamic_bs)
+
+    def pause(self):
+        if self._executor is not None:
+            self._executor.pause()
+
+    def resume(self):
+        if self._executor is not None:
+            self._executor.resume()
+
+    def export_stats(self) -> dict[str, float]:
+        return {}
+
+
+RemoteNativeEngine = RemoteInfEngine

@@ -69,6 +69,48 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+SKINNY_MAX_TOKENS = 256
+_skinny_ws: dict = {}
+
+
+def _skinny_workspace(device, n_out: int):
+    """Zeroed split-K workspace and tile counters, one set per (device, stream): launches on
+    one stream are ordered, launches on different streams must not share them. The kernel
+    leaves both zeroed."""
+    key = (device.index, _s())
+    ent = _skinny_ws.get(key)
+    need = SKINNY_MAX_TOKENS * n_out
+    if ent is None or ent[0].numel() < need:
+        ws = torch.zeros(max(need, SKINNY_MAX_TOKENS * 32768), device=device, dtype=torch.float32)
+        cnt = torch.zeros(4096, device=device, dtype=torch.int32)
+        ent = _skinny_ws[key] = (ws, cnt)
+    return ent
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+                split_k: int = 0) -> torch.Tensor:
+    """``x @ w^T (+ resid)`` for at most 256 rows of ``x``: the decode-shaped product, bound
+    by streaming ``w`` once (swap-AB tcgen05 tiles, split-K reduced in L2)."""
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.shape[0] <= SKINNY_MAX_TOKENS
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    M, K = x.shape
+    N = w.shape[0]
+    if not x.is_cuda:
+        y = x.float() @ w.float().t()
+        if resid is not None:
+            y = y + resid.float()
+        return y.to(out_dtype)
+    y = torch.empty(M, N, device=x.device, dtype=out_dtype)
+    if resid is not None:
+        assert resid.shape == y.shape and resid.stride() == y.stride() and resid.dtype == torch.bfloat16
+    ws, cnt = _skinny_workspace(x.device, N) if N <= 65536 else (None, None)
+    rc = _L().ab2_gemm_skinny(x.data_ptr(), w.data_ptr(), y.data_ptr(), _lib.ptr(resid), _lib.ptr(ws), _lib.ptr(cnt), M, N, K,
+                              x.stride(0), w.stride(0), y.stride(0), int(out_dtype == torch.float32),
+                              split_k if ws is not None else 1, _s())
+    _lib.check(rc, "ab2_gemm_skinny")
+    return y
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ W^T (+ residual). Weight gradients accumulate in fp32 into ``w.main_grad``
     when the parameter carries one (flat-shard training), else are returned in bf16."""
@@ -114,6 +156,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = Non
     if not x.is_cuda:
         y = F.linear(x, w)
         return y + resid if resid is not None else y
+    if (x.dim() == 2 and x.shape[0] <= SKINNY_MAX_TOKENS and not torch.is_grad_enabled() and x.stride(1) == 1
+            and (x.stride(0) & 7) == 0 and (resid is None or resid.is_contiguous())):
+        return gemm_skinny(x, w, resid)
     return _Linear.apply(x, w, resid, grad_buf)
 
 

@@ -26,6 +26,7 @@ _SIGS = {
     "ab2_runtime_init": ([], c_int),
     "ab2_num_sms": ([], c_int),
     "ab2_gemm_bf16": ([c_void_p] * 4 + [c_int] * 10 + [c_void_p], c_int),
+    "ab2_gemm_skinny": ([c_void_p] * 6 + [c_int] * 8 + [c_void_p], c_int),
     "ab2_rmsnorm_fwd": ([c_void_p] * 6 + [c_int, c_int, c_float, c_void_p], c_int),
     "ab2_rmsnorm_bwd": ([c_void_p] * 7 + [c_int, c_int, c_void_p], c_int),
     "ab2_rope": ([c_void_p] * 4 + [c_int, c_int, c_int, c_ll, c_int, c_void_p], c_int),
