@@ -204,7 +204,14 @@ def main(argv=None):
     ap.add_argument("--port", type=int, required=True)
     ap.add_argument("--role", default="worker")
     ap.add_argument("--index", type=int, default=0)
+    ap.add_argument("--announce", default="", help="name_resolve key prefix under which '<prefix>/<index>' -> host:port is published")
     a = ap.parse_args(argv)
+    if a.port == 0:
+        a.port = find_free_ports(1)[0]
+    if a.announce:
+        from ...utils import name_resolve
+
+        name_resolve.add(f"{a.announce}/{a.index}", f"{a.host}:{a.port}", replace=True)
     serve(a.host, a.port)
     os._exit(0)
 

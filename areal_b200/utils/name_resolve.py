@@ -198,7 +198,10 @@ class NfsNameRecordRepository(NameRecordRepository):
                 pass
 
 
-_DEFAULT: NameRecordRepository = MemoryNameRecordRepository()
+# Processes started by a scheduler / launcher inherit the rendezvous location through the
+# environment: AREAL_NAME_RESOLVE_ROOT selects the shared-filesystem backend.
+_DEFAULT: NameRecordRepository = (NfsNameRecordRepository(os.environ["AREAL_NAME_RESOLVE_ROOT"])
+                                  if os.environ.get("AREAL_NAME_RESOLVE_ROOT") else MemoryNameRecordRepository())
 
 
 def reconfigure(config=None, **kwargs) -> NameRecordRepository:

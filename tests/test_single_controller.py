@@ -175,3 +175,116 @@ def test_controllers_run_grpo_over_local_scheduler(tmp_path):
         rollout.destroy()
         actor.destroy()
         sched.delete_workers()
+
+
+def test_slurm_scheduler_against_mocked_commands(tmp_path, monkeypatch):
+    """sbatch / squeue / scancel are faked; worker discovery goes through the NFS name store."""
+    from areal_b200.api.cli_args import SchedulingSpec
+    from areal_b200.api.scheduler_api import Job
+    from areal_b200.infra.scheduler import slurm as S
+    from areal_b200.infra.scheduler.exceptions import WorkerCreationError, WorkerFailedError
+    from areal_b200.utils import name_resolve, names
+
+    name_resolve.reconfigure(type="nfs", record_root=str(tmp_path / "nr"))
+    calls, state = [], {"squeue": "RUNNING"}
+
+    def fake_run(self, cmd):
+        calls.append(cmd)
+        if cmd[0] == "sbatch":
+            return "Submitted batch job 4242\n"
+        if cmd[0] == "squeue":
+            return state["squeue"] + "\n"
+        if cmd[0] == "scancel":
+            return ""
+        raise AssertionError(cmd)
+    monkeypatch.setattr(S.SlurmScheduler, "_run", fake_run)
+    sch = S.SlurmScheduler("exp", "t0", str(tmp_path), n_gpus_per_node=8, startup_timeout=5)
+    job = Job(replicas=2, tasks=[SchedulingSpec(gpu=1, cpu=4, mem=16, partition="gpu", env_vars={"A": "b c"},
+                                                additional_bash_cmds=["module load cuda"])], role="actor")
+    ids = sch.create_workers(job)
+    assert ids == ["actor/0", "actor/1"]
+    script = open(tmp_path / "logs/exp/t0/slurm/actor.sbatch").read()
+    assert "#SBATCH --ntasks=2" in script and "#SBATCH --partition=gpu" in script and "--gpus-per-task=1" in script
+    assert "export A='b c'" in script and "module load cuda" in script and "areal_b200.infra.rpc.rpc_server" in script
+    assert "--announce areal/exp/t0/workers/actor" in script
+    with pytest.raises(WorkerCreationError):
+        sch.create_workers(job)
+    # a failed job surfaces as WorkerFailedError; a live one resolves the published addresses
+    state["squeue"] = "FAILED"
+    with pytest.raises(WorkerFailedError):
+        sch.get_workers("actor")
+    state["squeue"] = "RUNNING"
+    from http.server import ThreadingHTTPServer
+
+    servers = []
+    for i in range(2):
+        port = find_free_ports(1)[0]
+        srv = ThreadingHTTPServer(("127.0.0.1", port), make_handler(EngineHost(f"127.0.0.1:{port}"), threading.Event()))
+        threading.Thread(target=srv.serve_forever, daemon=True).start()
+        servers.append(srv)
+        name_resolve.add(names.worker_discovery("exp", "t0", "actor", i), f"127.0.0.1:{port}", replace=True)
+    ws = sch.get_workers("actor")
+    assert [w.id for w in ws] == ids and all(w.worker_ports for w in ws)
+    sch.create_engine("actor/0", "tests.test_single_controller._Echo", name="actor", scale=2)
+    assert sch.call_engine("actor/0", "scale", engine_name="actor") == 2
+    sch.delete_workers()
+    assert ["scancel", "4242"] in calls
+    for s in servers:
+        s.shutdown()
+    name_resolve.reconfigure(type="memory")
+
+
+def test_ray_scheduler_against_fake_ray(tmp_path):
+    """A stand-in ``ray`` module: actors run in-process, placement groups are records."""
+    import types
+
+    from areal_b200.api.cli_args import SchedulingSpec
+    from areal_b200.api.scheduler_api import Job
+    from areal_b200.infra.scheduler.ray import RayScheduler
+
+    killed, removed = [], []
+
+    class _Ref:
+        def __init__(self, v):
+            self.v = v
+
+    class _Method:
+        def __init__(self, fn):
+            self.fn = fn
+
+        def remote(self, *a, **k):
+            return _Ref(self.fn(*a, **k))
+
+    class _Handle:
+        def __init__(self, obj):
+            self._obj = obj
+
+        def __getattr__(self, n):
+            return _Method(getattr(self._obj, n))
+
+    class _ActorCls:
+        def __init__(self, cls):
+            self.cls, self.opts = cls, {}
+
+        def options(self, **kw):
+            self.opts = kw
+            return self
+
+        def remote(self, *a, **k):
+            return _Handle(self.cls(*a, **k))
+
+    fake = types.SimpleNamespace(
+        is_initialized=lambda: True, init=lambda **k: None, remote=lambda cls: _ActorCls(cls),
+        get=lambda refs, timeout=None: [r.v for r in refs] if isinstance(refs, list) else refs.v,
+        kill=lambda a: killed.append(a),
+        util=types.SimpleNamespace(placement_group=lambda bundles, strategy: types.SimpleNamespace(bundles=bundles, ready=lambda: _Ref(True)),
+                                   remove_placement_group=lambda pg: removed.append(pg)))
+    sch = RayScheduler(ray_module=fake, log_dir=str(tmp_path), startup_timeout=20)
+    ids = sch.create_workers(Job(replicas=2, tasks=[SchedulingSpec(gpu=0, cpu=1)], role="rollout"))
+    ws = sch.get_workers("rollout")
+    assert len(ws) == 2 and ids == ["rollout/0", "rollout/1"] and sch._pgs["rollout"].bundles == [{"CPU": 1}, {"CPU": 1}]
+    sch.create_engine("rollout/1", "tests.test_single_controller._Echo", name="rollout", scale=5)
+    assert sch.call_engine("rollout/1", "scale", engine_name="rollout") == 5
+    assert sch.fork_workers("ref", "rollout") == ["ref/0", "ref/1"]
+    sch.delete_workers()
+    assert len(killed) == 2 and len(removed) == 1
