@@ -94,6 +94,23 @@ def bench_gemm(a):
     return res
 
 
+def bench_gemm_skinny(a):
+    """Decode-shaped product: --m tokens (<= 256) against an [--n, --k] weight; --split 0 = automatic."""
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    w = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    fl = 2.0 * a.m * a.n * a.k
+    by = 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n)
+    ms = timeit(lambda: OF.gemm_skinny(x, w, split_k=a.split), a.iters, a.warmup)
+    res = report("gemm_skinny_tcgen05", ms, fl, by, m=a.m, n=a.n, k=a.k, split=a.split)
+    if a.compare:
+        out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        ms1 = timeit(lambda: OF.gemm(x, w, out=out), a.iters, a.warmup)
+        report("gemm_bf16_tcgen05 (general kernel)", ms1, fl, by)
+        ms2 = timeit(lambda: torch.matmul(x, w.t(), out=out), a.iters, a.warmup)
+        report("cublas_bf16 (library baseline)", ms2, fl, by)
+    return res
+
+
 def _attn_inputs(a):
     T = a.seqlen * a.batch
     q = torch.randn(T, a.heads, a.dim, device="cuda").bfloat16()
@@ -216,14 +233,14 @@ def bench_engine_decode(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
+    ap.add_argument("kernel", choices=["gemm", "gemm_skinny", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
                                            "engine_decode"])
     ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--layout", type=str, default="nt", help="A major n|t, B major t|n: nt = x@W^T, nn = dy@W, tn = dy^T@x")
     ap.add_argument("--epi", type=int, default=0); ap.add_argument("--bn", type=int, default=0)
-    ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--compare", action="store_true"); ap.add_argument("--split", type=int, default=0)
     ap.add_argument("--seqlen", type=int, default=4096); ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--dim", type=int, default=128)
     ap.add_argument("--ctx", type=int, default=1024); ap.add_argument("--splits", type=int, default=4)
@@ -234,7 +251,7 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.kernel == "logprob" and a.rows > 4096:
         a.rows = 2048
-    return {"gemm": bench_gemm, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
+    return {"gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
             "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
             "engine_decode": bench_engine_decode}[a.kernel](a)
 

@@ -32,7 +32,8 @@ struct SkinnyCfg {
   static constexpr int A_BYTES = SK_BM * SK_BK * 2;
   static constexpr int B_BYTES = MT * SK_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES_RAW = (98 * 1024) / STAGE_BYTES;
+  // up to 128 tokens: <= 98 KB so two CTAs share an SM; 256 tokens: one CTA with 4 stages
+  static constexpr int STAGES_RAW = (MT > 128 ? 196 * 1024 : 98 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 6 ? 6 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
   static constexpr int TMEM_COLS = MT < 32 ? 32 : MT;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 128;
@@ -181,17 +182,55 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (s_last) {
       __threadfence();
       const int rows = min(SK_BM, N_out - n0);
-      for (int idx = threadIdx.x; idx < M_tok * SK_BM; idx += blockDim.x) {
-        const int tok = idx / SK_BM;
-        const int nn = idx - tok * SK_BM;
-        if (nn < rows) {
-          float* p = ws + (size_t)tok * N_out + n0 + nn;
-          float v = __ldcg(p);
-          __stcg(p, 0.f);
-          const size_t o = (size_t)tok * ldy + n0 + nn;
-          if (Rptr) v += __bfloat162float(Rptr[o]);
-          if (out_f32) reinterpret_cast<float*>(Yptr)[o] = v;
-          else reinterpret_cast<__nv_bfloat16*>(Yptr)[o] = __float2bfloat16(v);
+      const bool vec_ok = rows == SK_BM && (N_out & 3) == 0 && (ldy & 3) == 0;
+      if (vec_ok) {
+        // 4 features per thread and 4 independent loads in flight: the tile sits in L2 and
+        // this loop would otherwise pay one L2 round trip per element
+        const int items = M_tok * (SK_BM / 4);
+        for (int base = threadIdx.x; base < items; base += blockDim.x * 4) {
+          float4 v[4];
+          int idxs[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            idxs[u] = base + u * blockDim.x;
+            if (idxs[u] < items) {
+              const int tok = idxs[u] / (SK_BM / 4);
+              const int nn = (idxs[u] - tok * (SK_BM / 4)) * 4;
+              v[u] = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)tok * N_out + n0 + nn));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (idxs[u] < items) {
+              const int tok = idxs[u] / (SK_BM / 4);
+              const int nn = (idxs[u] - tok * (SK_BM / 4)) * 4;
+              __stcg(reinterpret_cast<float4*>(ws + (size_t)tok * N_out + n0 + nn), make_float4(0.f, 0.f, 0.f, 0.f));
+              const size_t o = (size_t)tok * ldy + n0 + nn;
+              float4 a = v[u];
+              if (Rptr) {
+                const uint2 rr = *reinterpret_cast<const uint2*>(Rptr + o);
+                const float2 r0 = unpack_bf16(rr.x), r1 = unpack_bf16(rr.y);
+                a.x += r0.x; a.y += r0.y; a.z += r1.x; a.w += r1.y;
+              }
+              if (out_f32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(Yptr) + o) = a;
+              else *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Yptr) + o) =
+                  make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+            }
+          }
+        }
+      } else {
+        for (int idx = threadIdx.x; idx < M_tok * SK_BM; idx += blockDim.x) {
+          const int tok = idx / SK_BM;
+          const int nn = idx - tok * SK_BM;
+          if (nn < rows) {
+            float* p = ws + (size_t)tok * N_out + n0 + nn;
+            float v = __ldcg(p);
+            __stcg(p, 0.f);
+            const size_t o = (size_t)tok * ldy + n0 + nn;
+            if (Rptr) v += __bfloat162float(Rptr[o]);
+            if (out_f32) reinterpret_cast<float*>(Yptr)[o] = v;
+            else reinterpret_cast<__nv_bfloat16*>(Yptr)[o] = __float2bfloat16(v);
+          }
         }
       }
       if (threadIdx.x == 0) counters[tile_n] = 0;

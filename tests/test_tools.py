@@ -1,0 +1,40 @@
+import json
+import os
+
+from areal_b200.tools import perf_trace_converter as ptc
+from areal_b200.tools import validate_installation as vi
+
+
+def test_trace_converter_merges_ranks_and_sessions(tmp_path):
+    d = tmp_path / "perf_tracer"
+    d.mkdir()
+    for r in range(2):
+        with open(d / f"traces-r{r}.jsonl", "w") as f:
+            f.write(json.dumps(dict(name="train.ppo_update", cat="compute", ph="X", ts=1000.0 + r, dur=500.0, pid=r, tid=1, args={})) + "\n")
+            f.write("not json\n")
+            f.write(json.dumps(dict(name="mark", cat="misc", ph="i", ts=1700.0, pid=r, tid=1, args={})) + "\n")
+    with open(d / "sessions.jsonl", "w") as f:
+        f.write(json.dumps(dict(session_id=3, task_id=7, rank=0, submit_ts=10.0, status="accepted", end_ts=11.0,
+                                phases=[dict(name="generate", start=10.1, end=10.6), dict(name="reward", start=10.6, end=10.7)])) + "\n")
+    out = tmp_path / "trace.json"
+    ptc.main([str(tmp_path), "-o", str(out), "--summary"])
+    tr = json.load(open(out))
+    ev = tr["traceEvents"]
+    assert tr["otherData"] == {"ranks": [0, 1], "sessions": 1, "source_files": 3}
+    assert sum(e.get("ph") == "M" for e in ev) == 3
+    x = [e for e in ev if e.get("ph") == "X" and e["name"] == "train.ppo_update"]
+    assert len(x) == 2 and min(e["ts"] for e in x) == 0.0
+    gen = next(e for e in ev if e["name"] == "generate")
+    assert abs(gen["dur"] - 0.5e6) < 1 and gen["pid"] == 2 and gen["tid"] == 3 and gen["args"]["task_id"] == 7
+    s = ptc.summarize(tr)
+    assert s["train.ppo_update"]["count"] == 2 and abs(s["train.ppo_update"]["total_ms"] - 1.0) < 1e-9
+
+
+def test_validate_installation_cpu_mode(capsys):
+    rc = vi.main(["--no-gpu"])
+    outp = capsys.readouterr().out
+    assert rc == 0 and "import torch" in outp and "import areal_b200" in outp
+    r = vi.Report()
+    r.run("bad", lambda: 1 / 0, required=True)
+    r.run("opt", lambda: 1 / 0, required=False)
+    assert not r.ok and [s for _, s, _ in r.rows] == ["FAIL", "missing"]
