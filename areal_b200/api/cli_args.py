@@ -780,12 +780,14 @@ def _coerce(value, tp, path: str):
     return value
 
 
-def _merge_into_dataclass(cls, data: dict, path: str = ""):
+def _merge_into_dataclass(cls, data: dict, path: str = "", strict: bool = True):
     hints = get_type_hints(cls)
     known = {f.name: f for f in fields(cls)}
     kwargs = {}
     for key, val in data.items():
         if key not in known:
+            if not strict:
+                continue
             raise ConfigError(f"unknown config key '{path + '.' if path else ''}{key}' for {cls.__name__}")
         kwargs[key] = _coerce(val, hints[key], f"{path + '.' if path else ''}{key}")
     try:
@@ -794,10 +796,11 @@ def _merge_into_dataclass(cls, data: dict, path: str = ""):
         raise ConfigError(f"{path or cls.__name__}: {e}") from e
 
 
-def to_structured_cfg(raw: dict, config_cls):
-    """Resolves ``${...}`` references and builds the typed dataclass tree."""
+def to_structured_cfg(raw: dict, config_cls, strict: bool = True):
+    """Resolves ``${...}`` references and builds the typed dataclass tree. ``strict=False``
+    ignores unknown TOP-LEVEL keys (a launcher reads the shared part of any experiment config)."""
     resolved = _resolve(raw, raw)
-    return _merge_into_dataclass(config_cls, resolved)
+    return _merge_into_dataclass(config_cls, resolved, strict=strict)
 
 
 def parse_cli_args(argv: list[str]):

@@ -256,8 +256,6 @@ class CausalLM(nn.Module):
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Full fp32 logits (small batches / sampling only)."""
         if hidden.is_cuda:
-            if hidden.shape[0] <= OF.SKINNY_MAX_TOKENS:
-                return OF.gemm_skinny(hidden.contiguous(), self.output_weight, out_dtype=torch.float32)
             return OF.gemm(hidden.contiguous(), self.output_weight, epi=OF.EPI_F32)
         return F.linear(hidden, self.output_weight).float()
 

@@ -73,7 +73,7 @@ def test_gemm_skinny_matches_fp32(M, N, K, split):
     yr = OF.gemm_skinny(x, w, resid=r, split_k=split)
     assert _rel_err(yr, ref + r.float()) < 1e-2
     with torch.no_grad():
-        assert _rel_err(OF.linear(x, w, r), ref + r.float()) < 1e-2      # inference-shaped linear takes this path
+        assert _rel_err(OF.linear(x, w, r), ref + r.float()) < 1e-2      # inference-shaped linear may take this path
     _no_kernel_error()
 
 

@@ -38,3 +38,37 @@ def test_validate_installation_cpu_mode(capsys):
     r.run("bad", lambda: 1 / 0, required=True)
     r.run("opt", lambda: 1 / 0, required=False)
     assert not r.ok and [s for _, s, _ in r.rows] == ["FAIL", "missing"]
+
+
+def test_local_launcher_restarts_failed_job(tmp_path):
+    """The trainer script fails on its first run and succeeds on the recover run."""
+    import sys
+
+    from areal_b200.api.cli_args import BaseExperimentConfig, ClusterSpecConfig, RecoverConfig
+    from areal_b200.infra.launcher.local import JobFailed, LocalLauncher, launch
+
+    script = tmp_path / "train.py"
+    marker = tmp_path / "ran_once"
+    script.write_text(
+        "import os, sys\n"
+        f"m = {str(marker)!r}\n"
+        "if os.environ.get('RANK') == '0' and not os.path.exists(m):\n"
+        "    open(m, 'w').write(os.environ['AREAL_RECOVER_RUN']); sys.exit(3)\n"
+        "assert os.environ['WORLD_SIZE'] == '2'\n"
+        f"open(os.path.join({str(tmp_path)!r}, 'done_' + os.environ['RANK']), 'w').write(os.environ['AREAL_RECOVER_RUN'])\n")
+    cfg = BaseExperimentConfig(experiment_name="l", trial_name="t", cluster=ClusterSpecConfig(fileroot=str(tmp_path)),
+                               allocation_mode="d2", recover=RecoverConfig(mode="auto", retries=2))
+    assert launch(str(script), [], cfg, n_gpus=0) == 0
+    assert marker.read_text() == "0" and (tmp_path / "done_0").read_text() == "1" and (tmp_path / "done_1").exists()
+    # with recovery disabled the failure is final
+    marker.unlink()
+    cfg.recover.mode = "disabled"
+    assert launch(str(script), [], cfg, n_gpus=0) != 0
+    la = LocalLauncher("l", "t", str(tmp_path), n_gpus=0)
+    la.submit("bad", [sys.executable, "-c", "import sys; sys.exit(5)"])
+    try:
+        la.wait()
+        raise AssertionError("expected JobFailed")
+    except JobFailed as e:
+        assert e.code == 5 and e.name == "bad"
+    la.stop_all()
