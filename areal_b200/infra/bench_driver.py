@@ -59,6 +59,18 @@ def _instrument_transfers(engine):
 
 def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOConfig:
     bs = args.prompts_per_gpu_pair
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    # Activation memory policy: one trainer GPU that also holds the whole optimizer state
+    # (colocated, or 1 trainer + 1 rollout) has ~30 GB left, so it recomputes activations
+    # (colocated) or uses small micro-batches; from 2 trainer ranks on the optimizer state is
+    # sharded and full activations of 8k-token micro-batches fit.
+    ckpt = getattr(args, "grad_ckpt", -1)
+    if ckpt < 0:
+        ckpt = 1 if world == 1 else 0
+    mb_tokens = args.max_tokens_per_mb
+    if mb_tokens <= 0:
+        mb_tokens = 16384 if ckpt else (4096 if n_pairs == 1 else 8192)
+    args._resolved = {"gradient_checkpointing": bool(ckpt), "max_tokens_per_mb": mb_tokens}
     return GRPOConfig(
         experiment_name="bench-async-grpo", trial_name="t0", total_train_epochs=1000, seed=1,
         cluster=ClusterSpecConfig(fileroot=fileroot),
@@ -71,10 +83,11 @@ def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOCon
                                        context_length=args.prompt_len + args.max_len + 64, mem_fraction_static=0.35 if n_pairs == 1 and int(os.environ.get('WORLD_SIZE', '1')) == 1 else 0.6,
                                        max_prefill_tokens=16384,
                                        retain_kv_on_weight_update=bool(getattr(args, "retain_kv", 1))),
-        actor=PPOActorConfig(init_from_scratch=True, dtype="bfloat16", gradient_checkpointing=True,
+        actor=PPOActorConfig(init_from_scratch=True, dtype="bfloat16", gradient_checkpointing=bool(ckpt),
                              optimizer=OptimizerConfig(lr=1e-6, weight_decay=0.01, gradient_clipping=1.0),
-                             mb_spec=MicroBatchSpec(max_tokens_per_mb=args.max_tokens_per_mb),
+                             mb_spec=MicroBatchSpec(max_tokens_per_mb=mb_tokens),
                              use_decoupled_loss=True, recompute_logprob=True, kl_ctl=0.0, ppo_n_minibatches=1,
+                             prox_logp_method=args.prox_logp_method,
                              eps_clip=0.2, rejection_sampling=RejectionSamplingConfig(upper=5.0),
                              reward_norm=NormConfig(mean_level="group", std_level="group", group_size=args.group_size),
                              weight_update_mode="p2p", logprobs_chunk_size=2048),
@@ -207,7 +220,7 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
         "config": {"model": args.model, "global_batch": args.prompts_per_gpu_pair * args.group_size * n_train,
                    "seq_len": seq_len, "prompt_len": args.prompt_len, "response_median": args.median_len,
                    "response_cap": args.max_len, "group_size": args.group_size, "parallelism": parallelism,
-                   "max_staleness": args.staleness,
+                   "max_staleness": args.staleness, "prox_logp_method": args.prox_logp_method, **getattr(args, "_resolved", {}),
                    "inflight_weight_update": "running requests keep their KV cache" if getattr(args, "retain_kv", 1) else "running requests are re-prefilled",
                    "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
                    "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms,

@@ -39,7 +39,11 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=256)
     ap.add_argument("--median-len", type=int, default=256)
     ap.add_argument("--max-len", type=int, default=768)
-    ap.add_argument("--max-tokens-per-mb", type=int, default=16384)
+    ap.add_argument("--max-tokens-per-mb", type=int, default=0, help="0: chosen from the activation-memory policy")
+    ap.add_argument("--grad-ckpt", type=int, default=-1, help="-1: automatic (recompute activations only when one GPU holds "
+                    "the whole optimizer state and the rollout engine), 0 / 1: force")
+    ap.add_argument("--prox-logp-method", type=str, default="reuse_train_logp",
+                    help="reuse_train_logp (single minibatch: the update forward's log-probs ARE the proximal ones) | recompute")
     ap.add_argument("--staleness", type=int, default=2)
     ap.add_argument("--retain-kv", type=int, default=1, help="1: requests in flight keep their KV cache across a weight update; "
                     "0: they are interrupted and re-prefilled under the new weights")
