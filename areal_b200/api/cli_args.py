@@ -292,6 +292,9 @@ class PPOActorConfig(TrainEngineConfig):
             raise ValueError("choose at most one of SAPO / CISPO")
         if self.prox_logp_method not in ("recompute", "loglinear", "linear", "reuse_train_logp"):
             raise ValueError(f"unknown prox_logp_method {self.prox_logp_method}")
+        if self.prox_logp_method == "reuse_train_logp" and self.ppo_n_minibatches != 1:
+            raise ValueError("prox_logp_method='reuse_train_logp' requires ppo_n_minibatches=1: only then are the update "
+                             "forward's log-probs those of the policy before the update")
         if self.kl_estimator not in ("k1", "k2", "k3"):
             raise ValueError("kl_estimator must be k1|k2|k3")
 
