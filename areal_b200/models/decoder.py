@@ -63,6 +63,10 @@ class Attention(nn.Module):
         qkv = OF.linear(x, self.qkv_proj)
         if self.qkv_bias is not None:
             qkv = qkv + self.qkv_bias
+        if qkv.is_cuda and not torch.is_grad_enabled() and D in (64, 128):
+            # inference: one fused kernel for norm + rotation; v stays a strided view
+            qk, _ = OF.qknorm_rope_fwd(qkv, self.q_norm, self.k_norm, pb_positions, cos, sin, nq, nkv, D, self.cfg.rms_norm_eps)
+            return qk[:, :nq].contiguous(), qk[:, nq:], qkv[:, (nq + nkv) * D:].view(T, nkv, D)
         q = qkv[:, : nq * D].view(T, nq, D)
         k = qkv[:, nq * D: (nq + nkv) * D].view(T, nkv, D)
         v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
@@ -76,6 +80,13 @@ class Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, pb: PackedBatch, cos, sin, attn_fn=None) -> torch.Tensor:
         T = x.shape[0]
+        if attn_fn is None and getattr(self, "sp_size", 1) == 1 and x.is_cuda and self.D in (64, 128):
+            qkv = OF.linear(x, self.qkv_proj)
+            if self.qkv_bias is not None:
+                qkv = qkv + self.qkv_bias
+            o = OF.qknorm_rope_attention(qkv, self.q_norm, self.k_norm, pb.position_ids, cos, sin, pb.cu_seqlens, self.nq,
+                                         self.nkv, self.D, self.cfg.rms_norm_eps, 1.0 / math.sqrt(self.D), pb.tile_info)
+            return OF.linear(o.reshape(T, self.nq * self.D), self.o_proj)
         q, k, v = self.project_qkv(x, pb.position_ids, cos, sin)
         if attn_fn is not None:
             o = attn_fn(q, k, v)
@@ -180,11 +191,23 @@ class DecoderLayer(nn.Module):
         self.self_attn = Attention(cfg, dtype, device)
         self.mlp = MoEMLP(cfg, dtype, device) if cfg.layer_is_moe(idx) else DenseMLP(H, cfg.intermediate_size, dtype, device)
 
+    tp_group = None  # set by parallel.tp.install_tp
+
     def forward(self, h, resid, pb: PackedBatch, cos, sin, attn_fn=None):
         x, resid = OF.rmsnorm(h, self.input_layernorm, self.cfg.rms_norm_eps, resid)
-        h = self.self_attn(x, pb, cos, sin, attn_fn)
+        g = self.tp_group
+        if g is None:
+            h = self.self_attn(x, pb, cos, sin, attn_fn)
+            x, resid = OF.rmsnorm(h, self.post_attention_layernorm, self.cfg.rms_norm_eps, resid)
+            h = self.mlp(x)
+            return h, resid
+        # tensor parallel: this rank holds a slice of the heads / MLP columns; partial block
+        # outputs are summed over the group
+        from ..parallel.tp import copy_to_tp, reduce_from_tp
+
+        h = reduce_from_tp(self.self_attn(copy_to_tp(x, g), pb, cos, sin, attn_fn), g)
         x, resid = OF.rmsnorm(h, self.post_attention_layernorm, self.cfg.rms_norm_eps, resid)
-        h = self.mlp(x)
+        h = reduce_from_tp(self.mlp(copy_to_tp(x, g)), g)
         return h, resid
 
 

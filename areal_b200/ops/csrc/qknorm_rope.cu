@@ -1,0 +1,279 @@
+// Fused per-head RMSNorm (Qwen3 QK-norm) + rotary embedding for the q and k heads of a fused
+// QKV projection, forward and backward, reading and writing the projection buffer's layout
+// directly:
+//
+//   forward : qkv [T, (nq + 2 nkv) * D] bf16  ->  qk [T, (nq + nkv), D] bf16 (normed, rotated)
+//             (+ rstd [T, nq + nkv] fp32 when norm weights are given); v is consumed in place
+//             by the attention kernel through its row stride.
+//   backward: dq fp32 [T, nq, D] (the attention backward's reduction buffer) and dk bf16 already
+//             sitting in the k region of dqkv  ->  dqkv q / k regions bf16 (un-rotated, norm
+//             backward applied), dw_q / dw_k accumulated in fp32.
+//
+// One warp per (token, head) row, every lane holds D / 32 contiguous elements, the rotate-half
+// partner lives in lane ^ 16. Rows are processed four at a time so that four independent
+// loads are in flight per warp. Weight gradients are reduced in registers, then across the
+// CTA in shared memory, and reach global memory as one atomic per column per CTA.
+//
+// Replaces the separate slice / RMSNorm / RoPE launches (and their backward slice-copies) of
+// the reference's attention block (areal/experimental/models/archon/qwen3/model/model.py,
+// apply_rotary_emb in areal/experimental/models/archon/qwen2/model/rope.py).
+#include "common.cuh"
+
+namespace ab2 {
+
+template <int VEC>
+__device__ __forceinline__ void load_bf16_vec(const __nv_bfloat16* p, float* out) {
+  if (VEC == 4) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y);
+    out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+  } else {
+    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(p));
+    out[0] = a.x; out[1] = a.y;
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void store_bf16_vec(__nv_bfloat16* p, const float* v) {
+  if (VEC == 4) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+  } else {
+    *reinterpret_cast<uint32_t*>(p) = pack_bf16(v[0], v[1]);
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void load_f32_vec(const float* p, float* out) {
+  if (VEC == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  } else {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    out[0] = v.x; out[1] = v.y;
+  }
+}
+
+constexpr int QK_UNROLL = 4;
+
+// D = 32 * VEC. wq / wk may be null (no norm: rotation only).
+template <int VEC>
+__global__ void __launch_bounds__(256)
+qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq,
+                       const __nv_bfloat16* __restrict__ wk, const int* __restrict__ pos,
+                       const float* __restrict__ cosb, const float* __restrict__ sinb,
+                       __nv_bfloat16* __restrict__ qk, float* __restrict__ rstd_out, int T, int nq, int nkv,
+                       long long qkv_stride, float eps) {
+  constexpr int D = 32 * VEC;
+  constexpr int HALF = D / 2;
+  const int lane = threadIdx.x & 31;
+  const int heads = nq + nkv;
+  const long long rows = (long long)T * heads;
+  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const int e0 = lane * VEC;               // first element of this lane
+  const int f0 = e0 & (HALF - 1);          // frequency index of that element
+  const bool upper = lane >= 16;
+  float wqv[VEC], wkv[VEC];
+  const bool has_norm = wq != nullptr;
+  if (has_norm) {
+    load_bf16_vec<VEC>(wq + e0, wqv);
+    load_bf16_vec<VEC>(wk + e0, wkv);
+  }
+  for (long long r0 = warp0 * QK_UNROLL; r0 < rows; r0 += nwarps * QK_UNROLL) {
+    float x[QK_UNROLL][VEC];
+    int tok[QK_UNROLL], head[QK_UNROLL];
+#pragma unroll
+    for (int u = 0; u < QK_UNROLL; ++u) {
+      const long long r = r0 + u;
+      if (r < rows) {
+        tok[u] = (int)(r / heads);
+        head[u] = (int)(r - (long long)tok[u] * heads);
+        load_bf16_vec<VEC>(qkv + (size_t)tok[u] * qkv_stride + (size_t)head[u] * D + e0, x[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < QK_UNROLL; ++u) {
+      const long long r = r0 + u;
+      if (r >= rows) break;
+      float y[VEC];
+      if (has_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss += x[u][e] * x[u][e];
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / (float)D + eps);
+        if (lane == 0) rstd_out[r] = rstd;
+        const float* w = head[u] < nq ? wqv : wkv;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          // the normalised value is rounded to bf16 like the unfused op's output
+          y[e] = __bfloat162float(__float2bfloat16(x[u][e] * rstd * w[e]));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) y[e] = x[u][e];
+      }
+      const int p = pos[tok[u]];
+      float c[VEC], s[VEC], o[VEC];
+      load_f32_vec<VEC>(cosb + (size_t)p * HALF + f0, c);
+      load_f32_vec<VEC>(sinb + (size_t)p * HALF + f0, s);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float partner = __shfl_xor_sync(0xffffffffu, y[e], 16);
+        o[e] = upper ? (y[e] * c[e] + partner * s[e]) : (y[e] * c[e] - partner * s[e]);
+      }
+      store_bf16_vec<VEC>(qk + (size_t)r * D + e0, o);
+    }
+  }
+}
+
+// dq32: [T, nq, D] fp32. dqkv: [T, (nq + 2 nkv) * D] bf16 whose k region holds dk on entry; q and
+// k regions are overwritten with the gradient w.r.t. the projection output.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq,
+                       const __nv_bfloat16* __restrict__ wk, const int* __restrict__ pos,
+                       const float* __restrict__ cosb, const float* __restrict__ sinb,
+                       const float* __restrict__ rstd_in, const float* __restrict__ dq32,
+                       __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dwq, float* __restrict__ dwk, int T,
+                       int nq, int nkv, long long qkv_stride, long long dqkv_stride) {
+  constexpr int D = 32 * VEC;
+  constexpr int HALF = D / 2;
+  __shared__ float red[2][8][D];
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int heads = nq + nkv;
+  const long long rows = (long long)T * heads;
+  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + wib;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const int e0 = lane * VEC;
+  const int f0 = e0 & (HALF - 1);
+  const bool upper = lane >= 16;
+  const bool has_norm = wq != nullptr;
+  float wqv[VEC], wkv[VEC], aq[VEC], ak[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) { aq[e] = 0.f; ak[e] = 0.f; wqv[e] = 1.f; wkv[e] = 1.f; }
+  if (has_norm) {
+    load_bf16_vec<VEC>(wq + e0, wqv);
+    load_bf16_vec<VEC>(wk + e0, wkv);
+  }
+  for (long long r0 = warp0 * QK_UNROLL; r0 < rows; r0 += nwarps * QK_UNROLL) {
+    float g[QK_UNROLL][VEC], x[QK_UNROLL][VEC];
+    int tok[QK_UNROLL], head[QK_UNROLL];
+#pragma unroll
+    for (int u = 0; u < QK_UNROLL; ++u) {
+      const long long r = r0 + u;
+      if (r < rows) {
+        tok[u] = (int)(r / heads);
+        head[u] = (int)(r - (long long)tok[u] * heads);
+        if (head[u] < nq) load_f32_vec<VEC>(dq32 + ((size_t)tok[u] * nq + head[u]) * D + e0, g[u]);
+        else load_bf16_vec<VEC>(dqkv + (size_t)tok[u] * dqkv_stride + (size_t)head[u] * D + e0, g[u]);
+        if (has_norm) load_bf16_vec<VEC>(qkv + (size_t)tok[u] * qkv_stride + (size_t)head[u] * D + e0, x[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < QK_UNROLL; ++u) {
+      const long long r = r0 + u;
+      if (r >= rows) break;
+      const int p = pos[tok[u]];
+      float c[VEC], s[VEC], gy[VEC];
+      load_f32_vec<VEC>(cosb + (size_t)p * HALF + f0, c);
+      load_f32_vec<VEC>(sinb + (size_t)p * HALF + f0, s);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        // transpose of the rotation: gy_lo = g_lo c + g_hi s ; gy_hi = g_hi c - g_lo s
+        const float partner = __shfl_xor_sync(0xffffffffu, g[u][e], 16);
+        gy[e] = upper ? (g[u][e] * c[e] - partner * s[e]) : (g[u][e] * c[e] + partner * s[e]);
+      }
+      float dx[VEC];
+      if (has_norm) {
+        const float rstd = rstd_in[r];
+        const bool isq = head[u] < nq;
+        const float* w = isq ? wqv : wkv;
+        float xh[VEC], gw[VEC];
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          xh[e] = x[u][e] * rstd;
+          gw[e] = gy[e] * w[e];
+          dot += gw[e] * xh[e];
+          if (isq) aq[e] += gy[e] * xh[e]; else ak[e] += gy[e] * xh[e];
+        }
+        dot = warp_sum(dot) / (float)D;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) dx[e] = rstd * (gw[e] - xh[e] * dot);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) dx[e] = gy[e];
+      }
+      store_bf16_vec<VEC>(dqkv + (size_t)tok[u] * dqkv_stride + (size_t)head[u] * D + e0, dx);
+    }
+  }
+  if (has_norm) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      red[0][wib][e0 + e] = aq[e];
+      red[1][wib][e0 + e] = ak[e];
+    }
+    __syncthreads();
+    const int nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+      const int which = i / D, col = i - which * D;
+      float sum = 0.f;
+      for (int w = 0; w < nw; ++w) sum += red[which][w][col];
+      atomicAdd((which ? dwk : dwq) + col, sum);
+    }
+  }
+}
+
+}  // namespace ab2
+
+extern "C" {
+
+// Forward. qkv: [T, qkv_stride] bf16 (q heads, then k heads, then v heads, D each); qk: contiguous
+// [T, nq + nkv, D] bf16; rstd: [T * (nq + nkv)] fp32 (written only with norm weights).
+// wq / wk: [D] bf16 or null together. D must be 64 or 128.
+int ab2_qknorm_rope_fwd(const void* qkv, const void* wq, const void* wk, const int* pos, const float* cosb,
+                        const float* sinb, void* qk, float* rstd, int T, int nq, int nkv, int D,
+                        long long qkv_stride, float eps, void* stream) {
+  if (T <= 0) return 0;
+  if (D != 64 && D != 128) return 10;
+  if ((wq == nullptr) != (wk == nullptr)) return 11;
+  if (qkv_stride & 3) return 12;
+  const long long rows = (long long)T * (nq + nkv);
+  long long want = (rows + 8 * ab2::QK_UNROLL - 1) / (8 * ab2::QK_UNROLL);
+  const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+  auto s = (cudaStream_t)stream;
+  if (D == 128)
+    ab2::qknorm_rope_fwd_kernel<4><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
+                                                        (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk,
+                                                        rstd, T, nq, nkv, qkv_stride, eps);
+  else
+    ab2::qknorm_rope_fwd_kernel<2><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
+                                                        (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk,
+                                                        rstd, T, nq, nkv, qkv_stride, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+// Backward (see the kernel comment for the buffer contract). dwq / dwk: [D] fp32, accumulated.
+int ab2_qknorm_rope_bwd(const void* qkv, const void* wq, const void* wk, const int* pos, const float* cosb,
+                        const float* sinb, const float* rstd, const float* dq32, void* dqkv, float* dwq, float* dwk,
+                        int T, int nq, int nkv, int D, long long qkv_stride, long long dqkv_stride, void* stream) {
+  if (T <= 0) return 0;
+  if (D != 64 && D != 128) return 10;
+  if ((wq == nullptr) != (wk == nullptr)) return 11;
+  if ((qkv_stride | dqkv_stride) & 3) return 12;
+  if (wq && (!dwq || !dwk || !rstd)) return 13;
+  const long long rows = (long long)T * (nq + nkv);
+  long long want = (rows + 8 * ab2::QK_UNROLL - 1) / (8 * ab2::QK_UNROLL);
+  const int grid = (int)(want < 148 * 4 ? want : 148 * 4);
+  auto s = (cudaStream_t)stream;
+  if (D == 128)
+    ab2::qknorm_rope_bwd_kernel<4><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
+                                                        (const __nv_bfloat16*)wk, pos, cosb, sinb, rstd, dq32,
+                                                        (__nv_bfloat16*)dqkv, dwq, dwk, T, nq, nkv, qkv_stride, dqkv_stride);
+  else
+    ab2::qknorm_rope_bwd_kernel<2><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
+                                                        (const __nv_bfloat16*)wk, pos, cosb, sinb, rstd, dq32,
+                                                        (__nv_bfloat16*)dqkv, dwq, dwk, T, nq, nkv, qkv_stride, dqkv_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+}

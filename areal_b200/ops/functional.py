@@ -457,6 +457,30 @@ def attention_bwd_ref(q, k, v, o, lse, do, cu_seqlens, causal, scale):
     return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
 
+def attention_bwd_into(q, k, v, o, lse, do, cu_seqlens, causal, scale, tile_info, dk, dv):
+    """Kernel backward writing dk / dv into caller-provided (possibly strided) ``[T, Hkv, D]``
+    views; returns the fp32 dq reduction buffer ``[T, Hq, D]``."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    for t in (q, k, v, o, do, dk, dv):
+        assert t.stride(2) == 1 and t.stride(1) == D and t.dtype == torch.bfloat16
+    if tile_info is None:
+        tile_info = attn_tile_table(cu_seqlens, T)
+    # heaviest key blocks (most query blocks to visit under causal masking) first
+    tiles_bwd = tile_info.flip(0).contiguous()
+    cu = cu_seqlens.to(torch.int32)
+    delta = torch.empty(Hq, T, device=q.device, dtype=torch.float32)
+    _lib.check(_L().ab2_attn_delta(o.data_ptr(), do.data_ptr(), delta.data_ptr(), T, Hq, D, o.stride(0), do.stride(0), _s()),
+               "ab2_attn_delta")
+    dq32 = torch.zeros(T, Hq, D, device=q.device, dtype=torch.float32)
+    rc = _L().ab2_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                           dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr(), tiles_bwd.data_ptr(),
+                           tiles_bwd.shape[0], T, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0), do.stride(0),
+                           dk.stride(0), dv.stride(0), scale, int(causal), _s())
+    _lib.check(rc, "ab2_attn_bwd")
+    return dq32
+
+
 def attention_bwd(q, k, v, o, lse, do, cu_seqlens, causal, scale, tile_info=None):
     """Kernel backward: returns (dq, dk, dv) in the dtype of q. ``lse``: [Hq, T] from the forward."""
     T, Hq, D = q.shape
@@ -529,6 +553,82 @@ def attention(q, k, v, cu_seqlens, causal=True, scale=None, tile_info=None):
             outs.append(oi.transpose(0, 1))
         return torch.cat(outs, dim=0) if outs else torch.zeros_like(q)
     return _Attention.apply(q, k, v, cu_seqlens, causal, scale, tile_info)
+
+
+# ----------------------------------------------------------------------------- fused attention block
+def qknorm_rope_fwd(qkv: torch.Tensor, wq, wk, pos, cos, sin, nq: int, nkv: int, D: int, eps: float):
+    """q/k heads of a fused projection -> normalised (optional) and rotated ``[T, nq+nkv, D]``
+    plus the per-row rstd (``None`` without norm). No autograd."""
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.dtype == torch.bfloat16
+    qk = torch.empty(T, nq + nkv, D, device=qkv.device, dtype=qkv.dtype)
+    rstd = torch.empty(T * (nq + nkv), device=qkv.device, dtype=torch.float32) if wq is not None else None
+    rc = _L().ab2_qknorm_rope_fwd(qkv.data_ptr(), _lib.ptr(wq), _lib.ptr(wk), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                  qk.data_ptr(), _lib.ptr(rstd), T, nq, nkv, D, qkv.stride(0), eps, _s())
+    _lib.check(rc, "ab2_qknorm_rope_fwd")
+    return qk, rstd
+
+
+class _QKNormRopeAttention(torch.autograd.Function):
+    """QK-norm + RoPE + varlen causal attention on a fused QKV projection: the forward reads q/k
+    heads straight from the projection output and v through its row stride; the backward has
+    the attention kernel write dk / dv into the projection-gradient buffer and finishes dq / dk
+    in place (inverse rotation + norm backward), so no slice, copy or zero-fill op runs."""
+
+    @staticmethod
+    def forward(ctx, qkv, wq, wk, pos, cos, sin, cu_seqlens, scale, tile_info, nq, nkv, D, eps):
+        T = qkv.shape[0]
+        qk, rstd = qknorm_rope_fwd(qkv, wq, wk, pos, cos, sin, nq, nkv, D, eps)
+        q, k = qk[:, :nq], qk[:, nq:]
+        v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+        o, lse = attention_fwd(q, k, v, cu_seqlens, True, scale, tile_info)
+        ctx.save_for_backward(qkv, qk, rstd, o, lse, wq, wk, pos, cos, sin, cu_seqlens)
+        ctx.meta = (scale, tile_info, nq, nkv, D)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, qk, rstd, o, lse, wq, wk, pos, cos, sin, cu = ctx.saved_tensors
+        scale, tile_info, nq, nkv, D = ctx.meta
+        T = qkv.shape[0]
+        do = do.contiguous()
+        dqkv = torch.empty(T, (nq + 2 * nkv) * D, device=qkv.device, dtype=qkv.dtype)
+        dk = dqkv[:, nq * D:(nq + nkv) * D].view(T, nkv, D)
+        dv = dqkv[:, (nq + nkv) * D:].view(T, nkv, D)
+        v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+        dq32 = attention_bwd_into(qk[:, :nq], qk[:, nq:], v, o, lse, do, cu, True, scale, tile_info, dk, dv)
+        dwq = dwk = None
+        ret_q = ret_k = None
+        if wq is not None:
+            mq, mk = getattr(wq, "main_grad", None), getattr(wk, "main_grad", None)
+            dwq = mq if mq is not None else torch.zeros(D, device=qkv.device, dtype=torch.float32)
+            dwk = mk if mk is not None else torch.zeros(D, device=qkv.device, dtype=torch.float32)
+        rc = _L().ab2_qknorm_rope_bwd(qkv.data_ptr(), _lib.ptr(wq), _lib.ptr(wk), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                      _lib.ptr(rstd), dq32.data_ptr(), dqkv.data_ptr(), _lib.ptr(dwq), _lib.ptr(dwk), T, nq, nkv,
+                                      D, qkv.stride(0), dqkv.stride(0), _s())
+        _lib.check(rc, "ab2_qknorm_rope_bwd")
+        if wq is not None:
+            ret_q = None if getattr(wq, "main_grad", None) is not None else dwq.to(wq.dtype)
+            ret_k = None if getattr(wk, "main_grad", None) is not None else dwk.to(wk.dtype)
+        return dqkv, ret_q, ret_k, None, None, None, None, None, None, None, None, None, None
+
+
+def qknorm_rope_attention(qkv, wq, wk, pos, cos, sin, cu_seqlens, nq: int, nkv: int, D: int, eps: float, scale=None,
+                          tile_info=None):
+    """``attention(rope(norm(q)), rope(norm(k)), v)`` for ``qkv = [q heads | k heads | v heads]``
+    (``[T, (nq + 2 nkv) D]``). CUDA: fused kernels; CPU: the unfused reference ops."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    T = qkv.shape[0]
+    if qkv.is_cuda and D in (64, 128):
+        return _QKNormRopeAttention.apply(qkv, wq, wk, pos, cos, sin, cu_seqlens, scale, tile_info, nq, nkv, D, eps)
+    q = qkv[:, : nq * D].view(T, nq, D)
+    k = qkv[:, nq * D: (nq + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+    if wq is not None:
+        q = rmsnorm(q.reshape(T * nq, D), wq, eps)[0].view(T, nq, D)
+        k = rmsnorm(k.reshape(T * nkv, D), wk, eps)[0].view(T, nkv, D)
+    q, k = rope(q, pos, cos, sin), rope(k, pos, cos, sin)
+    return attention(q, k.contiguous(), v.contiguous(), cu_seqlens, True, scale, tile_info)
 
 
 # ----------------------------------------------------------------------------- logprob / entropy

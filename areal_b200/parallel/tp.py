@@ -1,0 +1,175 @@
+"""Tensor parallelism for the decoder (training and inference).
+
+Every rank builds the SAME model code with a rank-local architecture (heads / kv heads /
+intermediate width divided by ``tp``): q/k/v/gate/up projections are split by output features
+(column parallel), o/down projections by input features (row parallel), so each block needs
+one sum over the TP group after the row-parallel product (forward) and one before the
+column-parallel product (backward) — the conjugate pair ``copy_to_tp`` / ``reduce_from_tp``.
+Norm weights, embeddings and the LM head stay replicated; their gradients are summed over the
+group by :func:`allreduce_replicated_grads`.
+
+The sums use NCCL here (the measured baseline); ``parallel/tp_fused.py`` replaces the
+row-parallel product + sum by one GEMM kernel that writes its partial tiles straight into the
+peers' buffers. Reference: ``areal/engine/fsdp_utils/parallel.py:227-385`` (Colwise / Rowwise
+plans), ``areal/experimental/models/archon/qwen3/infra/parallelize.py:180``.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.config import ModelConfig
+from .weight_push import tp_layout_of
+
+
+def local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+    """Architecture of one TP rank."""
+    if tp == 1:
+        return cfg
+    if cfg.num_heads % tp:
+        raise ValueError(f"num_heads={cfg.num_heads} is not divisible by tp={tp}")
+    if cfg.num_kv_heads % tp:
+        raise ValueError(f"num_kv_heads={cfg.num_kv_heads} is not divisible by tp={tp} (kv-head replication is not supported)")
+    if cfg.intermediate_size % tp or (cfg.num_experts and cfg.moe_intermediate_size % tp):
+        raise ValueError("MLP width is not divisible by tp")
+    kw = dict(num_heads=cfg.num_heads // tp, num_kv_heads=cfg.num_kv_heads // tp, intermediate_size=cfg.intermediate_size // tp)
+    if cfg.num_experts:
+        kw["moe_intermediate_size"] = cfg.moe_intermediate_size // tp
+    return dataclasses.replace(cfg, **kw)
+
+
+def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+    """Rank-local slice of a full (native-named) parameter."""
+    if tp == 1:
+        return full
+    leaf = name.rsplit(".", 1)[-1]
+    if leaf in ("embed_tokens", "lm_head"):       # replicated here (vocab parallelism is separate)
+        return full
+    if full.dim() == 3:                             # stacked experts [E, rows, cols]
+        if leaf == "w_gate_up":
+            I = full.shape[1] // 2
+            a, b = rank * I // tp, (rank + 1) * I // tp
+            return torch.cat([full[:, a:b], full[:, I + a:I + b]], dim=1).contiguous()
+        if leaf == "w_down":
+            C = full.shape[2]
+            return full[:, :, rank * C // tp:(rank + 1) * C // tp].contiguous()
+        return full
+    shape = tuple(full.shape) if full.dim() == 2 else (full.shape[0],)
+    blocks = tp_layout_of(cfg, leaf, shape, tp)[rank]
+    if full.dim() == 1:
+        return torch.cat([full[r0:r1] for (r0, r1, _, _) in blocks]).contiguous()
+    return torch.cat([full[r0:r1, c0:c1] for (r0, r1, c0, c1) in blocks], dim=0).contiguous()
+
+
+def unshard_tensors(cfg: ModelConfig, name: str, parts: list[torch.Tensor]) -> torch.Tensor:
+    """Inverse of :func:`shard_tensor` (checkpoint export, weight push to a TP=1 consumer)."""
+    tp = len(parts)
+    if tp == 1:
+        return parts[0]
+    leaf = name.rsplit(".", 1)[-1]
+    p0 = parts[0]
+    if leaf in ("embed_tokens", "lm_head") or (p0.dim() == 1 and leaf != "qkv_bias") or leaf in ("router",):
+        return p0
+    if p0.dim() == 3:
+        if leaf == "w_gate_up":
+            h = p0.shape[1] // 2
+            return torch.cat([p[:, :h] for p in parts] + [p[:, h:] for p in parts], dim=1)
+        if leaf == "w_down":
+            return torch.cat(parts, dim=2)
+        return p0
+    if leaf in ("o_proj", "down_proj"):
+        return torch.cat(parts, dim=1)
+    if leaf == "gate_up_proj":
+        h = p0.shape[0] // 2
+        return torch.cat([p[:h] for p in parts] + [p[h:] for p in parts], dim=0)
+    if leaf in ("qkv_proj", "qkv_bias"):
+        D = cfg.head_dim
+        nq, nkv = cfg.num_heads // tp * D, cfg.num_kv_heads // tp * D
+        return torch.cat([p[:nq] for p in parts] + [p[nq:nq + nkv] for p in parts] + [p[nq + nkv:] for p in parts], dim=0)
+    return p0
+
+
+class _CopyToTP(torch.autograd.Function):
+    """Identity forward, sum over the TP group backward (input of a column-parallel product)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """Sum over the TP group forward, identity backward (output of a row-parallel product)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def copy_to_tp(x, group):
+    return _CopyToTP.apply(x, group) if group is not None else x
+
+
+def reduce_from_tp(x, group):
+    return _ReduceFromTP.apply(x, group) if group is not None else x
+
+
+def install_tp(model, group, tp_size: int, tp_rank: int):
+    """Marks every decoder layer of a rank-local model as tensor parallel (the layer's forward
+    then brackets attention and MLP with the conjugate pair)."""
+    for layer in model.layers:
+        layer.tp_group = group if tp_size > 1 else None
+    model.tp_group, model.tp_size, model.tp_rank = (group if tp_size > 1 else None), tp_size, tp_rank
+    return model
+
+
+def replicated_parameter_names(model) -> list[str]:
+    """Parameters every TP rank holds in full (their gradients must be summed over the group)."""
+    out = []
+    for n, p in model.named_parameters():
+        leaf = n.rsplit(".", 1)[-1]
+        if p.dim() == 1 and leaf != "qkv_bias" or leaf in ("embed_tokens", "lm_head", "router", "value_head"):
+            out.append(n)
+    return out
+
+
+@torch.no_grad()
+def allreduce_replicated_grads(model, group, grad_of=lambda p: getattr(p, "main_grad", None) if getattr(p, "main_grad", None) is not None else p.grad):
+    """Sums the gradients of replicated parameters over the TP group (each rank saw only its
+    heads' / columns' contribution to them ... except norms applied to full activations, which
+    already hold the full gradient: those are averaged consistently by using SUM of 1/tp-scaled
+    copies). Replicated weights consumed by full (unsharded) activations receive identical
+    gradients on every rank, so they are left alone; per-head norms (q_norm / k_norm) see only
+    local heads and are summed."""
+    if group is None:
+        return
+    params = dict(model.named_parameters())
+    for n in replicated_parameter_names(model):
+        leaf = n.rsplit(".", 1)[-1]
+        if leaf in ("q_norm", "k_norm", "router"):
+            g = grad_of(params[n])
+            if g is not None:
+                dist.all_reduce(g, group=group)
+
+
+def load_sharded_from_full(model, cfg: ModelConfig, full_state: dict, tp: int, rank: int):
+    """Copies the rank-local slices of a full state dict into a rank-local model."""
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.copy_(shard_tensor(cfg, n, full_state[n], tp, rank).to(p.dtype))
+    return model

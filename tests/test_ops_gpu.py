@@ -271,3 +271,63 @@ def test_attention_autograd_matches_reference_path():
     for a, t in zip(got, (q, k, v)):
         assert _rel_err(a, t.grad) < 3e-2
     _no_kernel_error()
+
+
+@pytest.mark.parametrize("D,nq,nkv,norm", [(128, 8, 2, True), (128, 4, 4, False), (64, 6, 2, True)])
+def test_fused_qknorm_rope_attention_matches_fp32(D, nq, nkv, norm):
+    """Fused QK-norm + RoPE + attention block (forward, dqkv, norm-weight grads) against plain
+    PyTorch fp32 math with autograd."""
+    import math
+
+    torch.manual_seed(5)
+    dev = "cuda"
+    lens = [130, 257, 64, 61]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=dev, dtype=torch.int32)
+    pos = torch.cat([torch.arange(n) for n in lens]).to(dev).int()
+    W = (nq + 2 * nkv) * D
+    qkv = torch.randn(T, W, device=dev).bfloat16().requires_grad_()
+    wq = (1 + 0.1 * torch.randn(D, device=dev)).bfloat16().requires_grad_() if norm else None
+    wk = (1 + 0.1 * torch.randn(D, device=dev)).bfloat16().requires_grad_() if norm else None
+    cos, sin = OF.rope_tables(512, D, 1e4, dev)
+    eps = 1e-6
+    o = OF.qknorm_rope_attention(qkv, wq, wk, pos, cos, sin, cu, nq, nkv, D, eps)
+    g = torch.randn_like(o)
+    o.backward(g)
+    _no_kernel_error()
+
+    # ---- fp32 oracle
+    x = qkv.detach().float().requires_grad_()
+    wq32 = wq.detach().float().requires_grad_() if norm else None
+    wk32 = wk.detach().float().requires_grad_() if norm else None
+    q = x[:, : nq * D].view(T, nq, D)
+    k = x[:, nq * D:(nq + nkv) * D].view(T, nkv, D)
+    v = x[:, (nq + nkv) * D:].view(T, nkv, D)
+
+    def nrm(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    def rot(t):
+        c, s_ = cos[pos.long()][:, None, :], sin[pos.long()][:, None, :]
+        a, b = t[..., : D // 2], t[..., D // 2:]
+        return torch.cat([a * c - b * s_, b * c + a * s_], -1)
+    if norm:
+        q, k = nrm(q, wq32), nrm(k, wk32)
+    q, k = rot(q), rot(k)
+    outs = []
+    rep = nq // nkv
+    b = 0
+    for n in lens:
+        qi = q[b:b + n].transpose(0, 1)
+        ki = k[b:b + n].transpose(0, 1).repeat_interleave(rep, 0)
+        vi = v[b:b + n].transpose(0, 1).repeat_interleave(rep, 0)
+        sc = (qi @ ki.transpose(1, 2)) / math.sqrt(D)
+        sc = sc.masked_fill(~torch.tril(torch.ones(n, n, device=dev, dtype=torch.bool)), float("-inf"))
+        outs.append((torch.softmax(sc, -1) @ vi).transpose(0, 1))
+        b += n
+    ref = torch.cat(outs, 0)
+    ref.backward(g.float())
+    assert _rel_err(o, ref) < 2e-2
+    assert _rel_err(qkv.grad, x.grad) < 3e-2
+    if norm:
+        assert _rel_err(wq.grad, wq32.grad) < 3e-2 and _rel_err(wk.grad, wk32.grad) < 3e-2

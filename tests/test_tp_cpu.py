@@ -1,0 +1,42 @@
+"""Tensor parallelism: shard layout helpers and 2-rank gloo parity run."""
+import os
+import subprocess
+import sys
+
+import torch
+
+from areal_b200.models.config import preset
+from areal_b200.parallel import tp as TP
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_local_config_and_shard_roundtrip():
+    cfg = preset("tiny-qwen3")
+    l2 = TP.local_config(cfg, 2)
+    assert l2.num_heads == cfg.num_heads // 2 and l2.num_kv_heads == cfg.num_kv_heads // 2 and l2.intermediate_size == cfg.intermediate_size // 2
+    assert TP.local_config(cfg, 1) is cfg
+    D = cfg.head_dim
+    qkv = torch.arange((cfg.num_heads + 2 * cfg.num_kv_heads) * D * 8, dtype=torch.float32).view(-1, 8)
+    parts = [TP.shard_tensor(cfg, "layers.0.self_attn.qkv_proj", qkv, 2, r) for r in range(2)]
+    assert parts[0].shape[0] == qkv.shape[0] // 2
+    # rank 0 holds the first half of the q heads, k heads and v heads
+    assert torch.equal(parts[0][: cfg.num_heads * D // 2], qkv[: cfg.num_heads * D // 2])
+    assert torch.equal(TP.unshard_tensors(cfg, "layers.0.self_attn.qkv_proj", parts), qkv)
+    gu = torch.randn(2 * cfg.intermediate_size, 16)
+    parts = [TP.shard_tensor(cfg, "layers.0.mlp.gate_up_proj", gu, 2, r) for r in range(2)]
+    assert torch.equal(TP.unshard_tensors(cfg, "layers.0.mlp.gate_up_proj", parts), gu)
+    dn = torch.randn(16, cfg.intermediate_size)
+    parts = [TP.shard_tensor(cfg, "layers.0.mlp.down_proj", dn, 2, r) for r in range(2)]
+    assert parts[0].shape == (16, cfg.intermediate_size // 2) and torch.equal(TP.unshard_tensors(cfg, "x.down_proj", parts), dn)
+    norm = torch.randn(cfg.hidden_size)
+    assert TP.shard_tensor(cfg, "layers.0.input_layernorm", norm, 2, 1) is norm or torch.equal(TP.shard_tensor(cfg, "layers.0.input_layernorm", norm, 2, 1), norm)
+
+
+def test_tensor_parallel_matches_unsharded_model_gloo():
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29871", os.path.join(ROOT, "tests", "dist_scripts", "run_tp.py")], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_OK") == 2
