@@ -59,14 +59,19 @@ class ShardedAdamW:
         self.sched_step += 1
 
     # ------------------------------------------------------------------ step
-    def step(self, grad_shard: torch.Tensor, inv_scale: float = 1.0, norm_already_global: bool = False) -> dict:
+    def step(self, grad_shard: torch.Tensor, inv_scale: float = 1.0, norm_already_global: bool = False,
+             precomputed_sumsq: Optional[torch.Tensor] = None) -> dict:
         """``grad_shard``: reduced fp32 gradient of this rank's shard. Returns the statistics
-        tensor (device): [sumsq, coef, finite, norm]."""
+        tensor (device): [sumsq, coef, finite, norm]. ``precomputed_sumsq``: global squared norm
+        worked out by the caller (tensor parallelism de-duplicates replicated parameters)."""
         st = self.state
         st.zero_()
-        OF.sqnorm_accumulate_(grad_shard, st)
-        if not norm_already_global and self.group is not None and dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            dist.all_reduce(st[0:1], group=self.group)
+        if precomputed_sumsq is not None:
+            st[0:1].copy_(precomputed_sumsq.to(st.dtype))
+        else:
+            OF.sqnorm_accumulate_(grad_shard, st)
+            if not norm_already_global and self.group is not None and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+                dist.all_reduce(st[0:1], group=self.group)
         OF.clip_coef_(st, float(self.cfg.gradient_clipping or 0.0), inv_scale)
         self.step_count += 1
         lr = self.current_lr()

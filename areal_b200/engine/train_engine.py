@@ -95,12 +95,23 @@ class B200TrainEngine(TrainEngine):
                 self.parallel = p = FSDPParallelStrategy(data_parallel_size=n)
             else:
                 raise ValueError(f"parallel strategy {p} needs {p.world_size} ranks, engine has {n}")
-        if p.tp_size > 1 or p.pp_size > 1:
-            raise NotImplementedError("tensor/pipeline parallel training is provided by parallel.tp / parallel.pp")
-        self.sp_size, self.dp_size = p.cp_size, p.dp_size
+        if p.pp_size > 1:
+            raise NotImplementedError("pipeline-parallel training is provided by parallel.pp (PipelineRunner), not by this engine")
+        self.sp_size, self.dp_size, self.tp_size = p.cp_size, p.dp_size, p.tp_size
+        sp, tp, dp = self.sp_size, self.tp_size, self.dp_size
+        # rank layout inside the trainer ranks: index = (d * sp + s) * tp + t  (tp fastest)
         self.local_index = self._train_ranks.index(self.rank) if self.rank in self._train_ranks else -1
-        self.sp_rank = self.local_index % self.sp_size
-        self.dp_rank = self.local_index // self.sp_size
+        li = max(self.local_index, 0)
+        self.tp_rank = li % tp
+        self.sp_rank = (li // tp) % sp
+        self.dp_rank = li // (tp * sp)
+        self._tp_group = None
+        self._mp_group = None      # context + tensor parallel peers of one data-parallel rank
+        self._all_train_group = None
+        tr = self._train_ranks
+
+        def gid(d, s_, t):
+            return tr[(d * sp + s_) * tp + t]
         preset = getattr(self, "_preset_groups", None)
         if preset is not None:
             # groups were created collectively by every rank of a trainer / rollout split
@@ -108,25 +119,63 @@ class B200TrainEngine(TrainEngine):
             self._sp_group = preset.get("sp")
             self._dp_group = preset.get("dp")
             self._cpu_group = preset.get("cpu") if n > 1 else None
+            self._tp_group = preset.get("tp")
+            self._mp_group = preset.get("mp", self._sp_group)
+            self._all_train_group = self._shard_group
         elif dist.is_initialized() and n > 1:
-            self._shard_group = dist.new_group(self._train_ranks) if n != self.world_size else dist.group.WORLD
-            # sp groups: consecutive ranks; dp groups: strided
-            for d in range(self.dp_size):
-                ranks = [self._train_ranks[d * self.sp_size + s] for s in range(self.sp_size)]
-                g = dist.new_group(ranks) if self.sp_size > 1 else None
-                if d == self.dp_rank:
-                    self._sp_group = g
-            for s in range(self.sp_size):
-                ranks = [self._train_ranks[d * self.sp_size + s] for d in range(self.dp_size)]
-                g = dist.new_group(ranks) if self.dp_size > 1 else None
-                if s == self.sp_rank:
-                    self._dp_group = g
-            self._cpu_group = dist.new_group(self._train_ranks, backend="gloo") if use_cuda else self._shard_group
+            whole = n == self.world_size
+            self._all_train_group = dist.group.WORLD if whole else dist.new_group(tr)
+            # shard groups: ranks that hold the same tensor-parallel slice
+            if tp == 1:
+                self._shard_group = self._all_train_group
+            else:
+                for t in range(tp):
+                    ranks = [gid(d, s_, t) for d in range(dp) for s_ in range(sp)]
+                    g = dist.new_group(ranks) if len(ranks) > 1 else None
+                    if t == self.tp_rank:
+                        self._shard_group = g
+            for d in range(dp):
+                for t in range(tp):
+                    ranks = [gid(d, s_, t) for s_ in range(sp)]
+                    g = dist.new_group(ranks) if sp > 1 else None
+                    if d == self.dp_rank and t == self.tp_rank:
+                        self._sp_group = g
+            for s_ in range(sp):
+                for t in range(tp):
+                    ranks = [gid(d, s_, t) for d in range(dp)]
+                    g = dist.new_group(ranks) if dp > 1 else None
+                    if s_ == self.sp_rank and t == self.tp_rank:
+                        self._dp_group = g
+            for d in range(dp):
+                for s_ in range(sp):
+                    ranks = [gid(d, s_, t) for t in range(tp)]
+                    g = dist.new_group(ranks) if tp > 1 else None
+                    if d == self.dp_rank and s_ == self.sp_rank:
+                        self._tp_group = g
+            if tp > 1 and sp > 1:
+                for d in range(dp):
+                    ranks = [gid(d, s_, t) for s_ in range(sp) for t in range(tp)]
+                    g = dist.new_group(ranks)
+                    if d == self.dp_rank:
+                        self._mp_group = g
+            else:
+                self._mp_group = self._tp_group if tp > 1 else self._sp_group
+            self._cpu_group = dist.new_group(tr, backend="gloo") if use_cuda else self._all_train_group
+            # statistics are reduced over ranks that saw different tokens only
+            self._stats_group = self._cpu_group
+            if tp > 1:
+                for t in range(tp):
+                    ranks = [gid(d, s_, t) for d in range(dp) for s_ in range(sp)]
+                    g = dist.new_group(ranks, backend="gloo") if len(ranks) > 1 else None
+                    if t == self.tp_rank:
+                        self._stats_group = g
             # warm the groups up so the first real collective does not pay connection setup
-            t = torch.zeros(1, device=self.device)
-            dist.all_reduce(t, group=self._shard_group)
+            t_ = torch.zeros(1, device=self.device)
+            dist.all_reduce(t_, group=self._all_train_group)
         else:
             self._shard_group = None
+        if not hasattr(self, "_stats_group"):
+            self._stats_group = self._cpu_group
         return self
 
     def set_train_ranks(self, ranks: list[int], groups: Optional[dict] = None):
@@ -158,19 +207,42 @@ class B200TrainEngine(TrainEngine):
         self.model_config = model_config
         seed = kwargs.get("seed", 1)
         t0 = time.time()
-        self.model = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
+        tp = getattr(self, "tp_size", 1)
+        has_ckpt = (not cfg.init_from_scratch and cfg.path and os.path.isdir(cfg.path)
+                    and any(f.endswith(".safetensors") for f in os.listdir(cfg.path)))
+        if tp > 1:
+            # every rank materialises the full weights once (same seed / same checkpoint), keeps
+            # its slice and drops the rest
+            from ..parallel import tp as TP
+
+            full = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
+            if has_ckpt:
+                hf_io.load_model_hf(full, cfg.path, strict=not cfg.is_critic)
+            self.local_model_config = TP.local_config(model_config, tp)
+            self.model = build_model(self.local_model_config, dtype=dtype, device=self.device, seed=seed)
+            TP.load_sharded_from_full(self.model, model_config, {n_: p_.detach() for n_, p_ in full.named_parameters()}, tp, self.tp_rank)
+            TP.install_tp(self.model, self._tp_group, tp, self.tp_rank)
+            del full
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+        else:
+            self.local_model_config = model_config
+            self.model = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
+            if has_ckpt:
+                hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
         self.model.gradient_checkpointing = cfg.gradient_checkpointing
-        if not cfg.init_from_scratch and cfg.path and os.path.isdir(cfg.path) and \
-                any(f.endswith(".safetensors") for f in os.listdir(cfg.path)):
-            hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
-        n_shards = len(self._train_ranks) if self._shard_group is not None else 1
-        shard_rank = self.local_index if n_shards > 1 else 0
+        sp = self.sp_size
+        # ranks that hold the same tensor-parallel slice shard its optimizer state (ZeRO)
+        self._shard_ranks = [self._train_ranks[(d * sp + s_) * tp + self.tp_rank] for d in range(self.dp_size) for s_ in range(sp)] \
+            if self.local_index >= 0 else list(self._train_ranks)
+        n_shards = len(self._shard_ranks) if self._shard_group is not None else 1
+        shard_rank = (self.dp_rank * sp + self.sp_rank) if n_shards > 1 else 0
         on_gpu = self.device.type == "cuda"
         fused = n_shards > 1 and on_gpu and cfg.fsdp.fuse_reduce_scatter_adamw
         # the parameter buffer may be peer-mapped over a wider group (trainer + rollout ranks)
         psg = kwargs.get("param_symm_group")
         psg_ranks = kwargs.get("param_symm_ranks")
-        alloc_g = (lambda n, dt, d: self._symmetric_alloc(n, dt, d, self._shard_group, self._train_ranks)) if fused else None
+        alloc_g = (lambda n, dt, d: self._symmetric_alloc(n, dt, d, self._shard_group, self._shard_ranks)) if fused else None
         if psg is not None and on_gpu:
             alloc_p = lambda n, dt, d: self._symmetric_alloc(n, dt, d, psg, psg_ranks)
         else:
@@ -179,8 +251,10 @@ class B200TrainEngine(TrainEngine):
         self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
                                     with_grads=cfg.optimizer is not None)
         if n_shards > 1:
-            # identical initial weights everywhere (rank 0 of the trainer group is the source)
-            dist.broadcast(self.store.flat_param, src=self._train_ranks[0], group=self._shard_group)
+            # identical initial weights on every rank of the shard group
+            dist.broadcast(self.store.flat_param, src=self._shard_ranks[0], group=self._shard_group)
+        if tp > 1 and cfg.optimizer is not None:
+            self._replicated_ranges = self._find_replicated_ranges()
         if cfg.optimizer is not None:
             total = ft_spec.total_train_steps if ft_spec is not None else 1
             self.optimizer = ShardedAdamW(self.store, cfg.optimizer, total_steps=total, group=self._shard_group)
@@ -192,12 +266,26 @@ class B200TrainEngine(TrainEngine):
             from ..parallel.fused_zero import FusedGradReducer
 
             self._grad_reducer = FusedGradReducer(self.store, self._shard_group,
-                                                  self.peer_ptrs(self.store.flat_grad, self._train_ranks),
-                                                  self.peer_ptrs(self.store.flat_param, self._train_ranks))
+                                                  self.peer_ptrs(self.store.flat_grad, self._shard_ranks),
+                                                  self.peer_ptrs(self.store.flat_param, self._shard_ranks))
         self._initialized = True
         logger.info("initialised %s: %.2fB params, dtype %s, dp=%d sp=%d, %.1fs", model_config.arch,
                     model_config.num_params() / 1e9, dtype, self.dp_size, self.sp_size, time.time() - t0)
         return self
+
+    def _find_replicated_ranges(self) -> list[tuple[int, int]]:
+        """Ranges (relative to this rank's gradient shard) that belong to parameters every
+        tensor-parallel rank holds in full: they count once in the global gradient norm."""
+        from ..parallel.tp import replicated_parameter_names
+
+        lo, hi = self.store.shard_range
+        out = []
+        for name in replicated_parameter_names(self.model):
+            off, numel = self.store.locate(name)
+            a, b = max(off, lo), min(off + numel, hi)
+            if a < b:
+                out.append((a - lo, b - lo))
+        return out
 
     _symm_handles: dict = {}
 
@@ -243,14 +331,18 @@ class B200TrainEngine(TrainEngine):
         return self.dp_size
 
     def current_data_parallel_head(self) -> int:
-        return self._train_ranks[self.dp_rank * self.sp_size]
+        return self._train_ranks[self.dp_rank * self.sp_size * getattr(self, "tp_size", 1)]
 
     def is_data_parallel_head(self) -> bool:
-        return self.sp_rank == 0
+        return self.sp_rank == 0 and getattr(self, "tp_rank", 0) == 0
 
     @property
     def context_and_model_parallel_group(self):
-        return self._sp_group
+        return self._mp_group if getattr(self, "_mp_group", None) is not None else self._sp_group
+
+    @property
+    def tensor_parallel_group(self):
+        return getattr(self, "_tp_group", None)
 
     @property
     def cpu_group(self):
@@ -395,7 +487,12 @@ class B200TrainEngine(TrainEngine):
             hook()
         self.store.fold_autograd_grads()
         opt = self.optimizer
-        fused = self._grad_reducer is not None and not opt.sgd
+        tp = getattr(self, "tp_size", 1)
+        if tp > 1:
+            from ..parallel.tp import allreduce_replicated_grads
+
+            allreduce_replicated_grads(self.model, self._tp_group)
+        fused = self._grad_reducer is not None and not opt.sgd and tp == 1
         if self._shard_group is not None:
             if fused:
                 gshard = self._grad_reducer.reduce_scatter(opt.state)
@@ -419,7 +516,17 @@ class B200TrainEngine(TrainEngine):
             self._grad_reducer.adamw_and_all_gather(opt, opt.state, lr)
             res = {"state": opt.state, "lr": lr}
         else:
-            res = opt.step(gshard)
+            pre = None
+            if tp > 1:
+                # global norm^2 = sum over TP ranks of the sliced parameters' part + the replicated
+                # parameters' part counted once
+                pre = torch.zeros(1, dtype=torch.float32, device=self.device)
+                g32 = gshard.float()
+                tot = g32.pow(2).sum()
+                rep = sum((g32[a:b].pow(2).sum() for a, b in self._replicated_ranges), torch.zeros((), device=self.device))
+                pre[0] = tot - rep + rep / tp
+                dist.all_reduce(pre, group=self._all_train_group)
+            res = opt.step(gshard, precomputed_sumsq=pre)
             if self._shard_group is not None:
                 if self._grad_reducer is not None:
                     self._grad_reducer.all_gather_params()
@@ -500,10 +607,20 @@ class B200TrainEngine(TrainEngine):
         os.makedirs(meta.path, exist_ok=True)
         head = self.local_index <= 0
         if meta.weight_format == "hf":
-            if head:
+            if getattr(self, "tp_size", 1) > 1:
+                # every tensor-parallel rank of the first data-parallel replica takes part in
+                # the gather; the head writes full tensors one by one
+                if self.dp_rank == 0 and self.sp_rank == 0:
+                    named = self._gathered_full_tensors()
+                    if head:
+                        hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named))
+                    else:
+                        for _ in named:
+                            pass
+            elif head:
                 hf_io.save_model_hf(self.model, meta.path)
-                if meta.tokenizer is not None:
-                    meta.tokenizer.save_pretrained(meta.path)
+            if head and meta.tokenizer is not None:
+                meta.tokenizer.save_pretrained(meta.path)
         else:
             from ..ckpt.sharded import save_sharded
 
@@ -514,9 +631,27 @@ class B200TrainEngine(TrainEngine):
         if self._cpu_group is not None:
             dist.barrier(group=self._cpu_group)
 
+    def _gathered_full_tensors(self):
+        """Yields (name, full tensor) for a tensor-parallel model; a collective over the TP group."""
+        from ..parallel import tp as TP
+
+        for n_, p_ in self.model.named_parameters():
+            parts = [torch.empty_like(p_) for _ in range(self.tp_size)]
+            dist.all_gather(parts, p_.detach().contiguous(), group=self._tp_group)
+            yield n_, TP.unshard_tensors(self.model_config, n_, parts)
+
     def load(self, meta: SaveLoadMeta):
         if meta.weight_format == "hf":
-            hf_io.load_model_hf(self.model, meta.path, strict=not self.config.is_critic)
+            if getattr(self, "tp_size", 1) > 1:
+                from ..parallel import tp as TP
+
+                full = build_model(self.model_config, dtype=self.model.dtype, device=self.device, seed=0)
+                hf_io.load_model_hf(full, meta.path, strict=not self.config.is_critic)
+                TP.load_sharded_from_full(self.model, self.model_config, {n_: p_.detach() for n_, p_ in full.named_parameters()},
+                                          self.tp_size, self.tp_rank)
+                del full
+            else:
+                hf_io.load_model_hf(self.model, meta.path, strict=not self.config.is_critic)
         else:
             from ..ckpt.sharded import load_sharded
 
@@ -542,13 +677,22 @@ class B200TrainEngine(TrainEngine):
             raise RuntimeError("connect_engine must be called before update_weights")
         return self._weight_pusher.push(meta)
 
+    def _rollout_source(self):
+        """The rollout engine itself, or (with context / tensor parallel peers that must see the
+        same tokens) a coordinator that lets the data-parallel head roll out and broadcasts."""
+        if self.sp_size * getattr(self, "tp_size", 1) > 1 and dist.is_initialized():
+            from ..rollout.dist_rollout import DistRolloutCoordinator
+
+            return DistRolloutCoordinator(self.rollout_engine, self, redistribute=False)
+        return self.rollout_engine
+
     def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None):
-        return self.rollout_engine.rollout_batch(data, workflow=workflow, workflow_kwargs=workflow_kwargs,
-                                                 should_accept_fn=should_accept_fn)
+        return self._rollout_source().rollout_batch(data, workflow=workflow, workflow_kwargs=workflow_kwargs,
+                                                    should_accept_fn=should_accept_fn)
 
     def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None, dynamic_bs=False):
-        return self.rollout_engine.prepare_batch(dataloader, workflow=workflow, workflow_kwargs=workflow_kwargs,
-                                                 should_accept_fn=should_accept_fn, dynamic_bs=dynamic_bs)
+        return self._rollout_source().prepare_batch(dataloader, workflow=workflow, workflow_kwargs=workflow_kwargs,
+                                                    should_accept_fn=should_accept_fn, dynamic_bs=dynamic_bs)
 
     # ------------------------------------------------------------------ memory
     def offload(self):
@@ -582,7 +726,8 @@ class B200TrainEngine(TrainEngine):
 
     def export_stats(self) -> dict[str, float]:
         # reduce over the trainer ranks only (rollout ranks of a split world do not take part)
-        return stats_tracker.export_all(reduce_group=self._cpu_group, distributed=self._cpu_group is not None)
+        g = getattr(self, "_stats_group", self._cpu_group)
+        return stats_tracker.export_all(reduce_group=g, distributed=g is not None)
 
 
 FSDPEngine = B200TrainEngine  # the role FSDPEngine plays in the reference
