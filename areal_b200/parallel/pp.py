@@ -1,0 +1,243 @@
+"""Pipeline parallelism: the decoder's layers are split into contiguous stages, activations
+``[tokens, hidden]`` travel between neighbouring stages with point-to-point sends, and
+micro-batches follow the 1F1B (one-forward-one-backward) or GPipe schedule.
+
+Every pipeline rank receives the same micro-batch list (token ids, packing metadata), so
+shapes are known everywhere and only the hidden state crosses stage boundaries: the stage
+boundary folds the residual stream into one tensor (``h + resid``), halving the traffic.
+Activations stay on NCCL p2p (the transfers are small next to a stage's compute and overlap
+with it). Tied embeddings live on the first and last stage and their gradients are summed
+between the two. Reference: ``areal/experimental/engine/archon/pipeline_parallel.py`` (stage
+split by FQN :80, schedules from ``torch.distributed.pipelining``), Megatron schedules in
+``areal/engine/megatron_engine.py:1112-1329``.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..models.config import ModelConfig
+from ..models.decoder import CausalLM, PackedBatch, build_model
+from ..ops import functional as OF
+
+
+def split_layers(n_layers: int, n_stages: int, first_extra: int = 0, last_extra: int = 0) -> list[range]:
+    """Contiguous, near-equal layer ranges. ``first_extra`` / ``last_extra`` count the embedding
+    and the LM head as that many layers' worth of work when balancing."""
+    if n_stages > n_layers:
+        raise ValueError(f"{n_stages} pipeline stages for {n_layers} layers")
+    total = n_layers + first_extra + last_extra
+    out, start = [], 0
+    for s in range(n_stages):
+        want = (total * (s + 1)) // n_stages - (total * s) // n_stages
+        if s == 0:
+            want -= first_extra
+        if s == n_stages - 1:
+            want = n_layers - start
+        want = max(1, min(want, n_layers - start - (n_stages - 1 - s)))
+        out.append(range(start, start + want))
+        start += want
+    return out
+
+
+class PipelineStage(nn.Module):
+    """The slice of a :class:`CausalLM` one pipeline rank owns."""
+
+    def __init__(self, cfg: ModelConfig, stage: int, n_stages: int, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None,
+                 layer_ranges: Optional[list[range]] = None):
+        super().__init__()
+        self.cfg, self.stage, self.n_stages = cfg, stage, n_stages
+        self.is_first, self.is_last = stage == 0, stage == n_stages - 1
+        ranges = layer_ranges or split_layers(cfg.num_layers, n_stages)
+        self.layer_range = ranges[stage]
+        # build the full model once (same seed on every rank => consistent weights), keep a slice
+        full = build_model(cfg, dtype=dtype, device=device, seed=seed)
+        self.layers = nn.ModuleList([full.layers[i] for i in self.layer_range])
+        self.embed_tokens = full.embed_tokens if (self.is_first or (self.is_last and cfg.tie_word_embeddings and not cfg.is_critic)) else None
+        self.norm = full.norm if self.is_last else None
+        self.lm_head = full.lm_head if self.is_last else None
+        self.value_head = full.value_head if self.is_last else None
+        self._rope = full.rope
+        self._full_ref = full if False else None
+        self.gradient_checkpointing = False
+
+    @property
+    def output_weight(self):
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    def native_name(self, local_name: str) -> str:
+        """Name of a stage parameter in the full model (checkpoints, weight updates)."""
+        if local_name.startswith("layers."):
+            i, rest = local_name[len("layers."):].split(".", 1)
+            return f"layers.{self.layer_range[int(i)]}.{rest}"
+        return local_name
+
+    def forward(self, x: torch.Tensor, pb: PackedBatch) -> torch.Tensor:
+        """First stage: ``x`` = token ids [T]; other stages: hidden state [T, H]. Returns the
+        hidden state handed to the next stage, or the final normed hidden state."""
+        cos, sin = self._rope(x.device, max(self.cfg.max_position_embeddings, pb.max_seqlen + 1))
+        h = OF.embedding(x, self.embed_tokens) if self.is_first else x
+        resid = None
+        for layer in self.layers:
+            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+
+                h, resid = checkpoint(layer, h, resid, pb, cos, sin, None, use_reentrant=False)
+            else:
+                h, resid = layer(h, resid, pb, cos, sin, None)
+        if self.is_last:
+            out, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
+            return out
+        return h + resid if resid is not None else h
+
+    def logprobs_entropy(self, hidden, labels, temperature: float = 1.0, chunk: int = 2048):
+        return OF.lm_head_logprob(hidden, self.output_weight, labels, temperature, chunk)
+
+
+class PipelineRunner:
+    """Runs micro-batches through the stages of ONE pipeline (a process group whose ranks are
+    the stages in order)."""
+
+    def __init__(self, stage_module: PipelineStage, group, schedule: str = "1F1B"):
+        self.m = stage_module
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.n = dist.get_world_size(group)
+        assert self.rank == stage_module.stage and self.n == stage_module.n_stages
+        ranks = dist.get_process_group_ranks(group)
+        self.prev = ranks[self.rank - 1] if self.rank > 0 else None
+        self.next = ranks[self.rank + 1] if self.rank < self.n - 1 else None
+        self.first_rank, self.last_rank = ranks[0], ranks[-1]
+        if schedule not in ("1F1B", "GPipe"):
+            raise ValueError("schedule must be 1F1B or GPipe (interleaved / zero-bubble variants need virtual stages)")
+        self.schedule = schedule
+        p = next(stage_module.parameters())
+        self.device, self.dtype = p.device, p.dtype
+        self.H = stage_module.cfg.hidden_size
+
+    # ---- p2p: every exchange is ONE batch of sends and receives, so a stage that sends forward
+    # while its neighbour sends backward cannot block the other (NCCL groups the batch)
+    def _p2p(self, send_next=None, recv_prev_T: Optional[int] = None, send_prev=None, recv_next_T: Optional[int] = None):
+        ops, from_prev, from_next = [], None, None
+        keep = []
+        if send_prev is not None and self.prev is not None:
+            t = send_prev.contiguous()
+            keep.append(t)
+            ops.append(dist.P2POp(dist.isend, t, self.prev, self.group))
+        if recv_prev_T is not None and self.prev is not None:
+            from_prev = torch.empty(recv_prev_T, self.H, device=self.device, dtype=self.dtype)
+            ops.append(dist.P2POp(dist.irecv, from_prev, self.prev, self.group))
+        if send_next is not None and self.next is not None:
+            t = send_next.contiguous()
+            keep.append(t)
+            ops.append(dist.P2POp(dist.isend, t, self.next, self.group))
+        if recv_next_T is not None and self.next is not None:
+            from_next = torch.empty(recv_next_T, self.H, device=self.device, dtype=self.dtype)
+            ops.append(dist.P2POp(dist.irecv, from_next, self.next, self.group))
+        if ops:
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+        return from_prev, from_next
+
+    # ---- compute of one micro-batch
+    def _forward(self, mb, x_in, loss_fn, forward_only: bool):
+        if self.m.is_first:
+            y = self.m(mb["input_ids"], mb["pb"])
+        else:
+            if not forward_only:
+                x_in.requires_grad_(True)
+            y = self.m(x_in, mb["pb"])
+        if self.m.is_last:
+            return loss_fn(y, mb)
+        return y
+
+    def _backward(self, x_in, y, dy):
+        if self.m.is_last:
+            y.backward()
+        else:
+            y.backward(dy)
+        return None if self.m.is_first else x_in.grad
+
+    def run(self, microbatches: list[dict[str, Any]], loss_fn: Optional[Callable] = None, forward_only: bool = False) -> list:
+        """``microbatches``: dicts with ``input_ids`` [T] and ``pb`` (PackedBatch) plus whatever
+        ``loss_fn(hidden, mb)`` needs; identical on every stage. Returns the per-micro-batch
+        losses (training) or outputs (forward only) on the last stage and ``[]`` elsewhere."""
+        M = len(microbatches)
+        Ts = [mb["input_ids"].shape[0] for mb in microbatches]
+        results: list = []
+        if forward_only:
+            with torch.no_grad():
+                for i, mb in enumerate(microbatches):
+                    x, _ = self._p2p(recv_prev_T=Ts[i])
+                    y = self._forward(mb, x, loss_fn, True)
+                    if self.m.is_last:
+                        results.append(y)
+                    else:
+                        self._p2p(send_next=y)
+            return results
+        warm = M if self.schedule == "GPipe" else min(M, self.n - self.rank - 1)
+        rest = M - warm
+        inputs, outputs = [], []
+        for i in range(warm):                              # warm-up forwards
+            x, _ = self._p2p(recv_prev_T=Ts[i])
+            y = self._forward(microbatches[i], x, loss_fn, False)
+            self._p2p(send_next=None if self.m.is_last else y.detach())
+            inputs.append(x)
+            outputs.append(y)
+        x = None
+        if rest > 0:
+            x, _ = self._p2p(recv_prev_T=Ts[warm])
+        for k in range(rest):                              # steady state: one forward, one backward
+            i = warm + k
+            y = self._forward(microbatches[i], x, loss_fn, False)
+            inputs.append(x)
+            outputs.append(y)
+            j = len(results)                               # oldest micro-batch still waiting for its backward
+            _, dy = self._p2p(send_next=None if self.m.is_last else y.detach(), recv_next_T=Ts[j])
+            xb, yb = inputs.pop(0), outputs.pop(0)
+            if self.m.is_last:
+                results.append(yb.detach())
+            else:
+                results.append(None)
+            dx = self._backward(xb, yb, dy)
+            if k == rest - 1:
+                self._p2p(send_prev=dx)
+                x = None
+            else:
+                x, _ = self._p2p(send_prev=dx, recv_prev_T=Ts[i + 1])
+        while inputs:                                      # cool-down backwards
+            j = len(results)
+            _, dy = self._p2p(recv_next_T=Ts[j])
+            xb, yb = inputs.pop(0), outputs.pop(0)
+            results.append(yb.detach() if self.m.is_last else None)
+            dx = self._backward(xb, yb, dy)
+            self._p2p(send_prev=dx)
+        self.sync_tied_embedding_grads()
+        return results if self.m.is_last else []
+
+    def sync_tied_embedding_grads(self):
+        """Tied input / output embeddings exist on the first and last stage: sum their grads."""
+        m = self.m
+        if self.n == 1 or not m.cfg.tie_word_embeddings or m.cfg.is_critic or not (m.is_first or m.is_last):
+            return
+        g = getattr(m.embed_tokens, "main_grad", None)
+        if g is None:
+            g = m.embed_tokens.grad
+        if g is None:
+            g = torch.zeros_like(m.embed_tokens)
+            m.embed_tokens.grad = g
+        peer = self.last_rank if m.is_first else self.first_rank
+        other = torch.empty_like(g)
+        mine = g.contiguous().clone()
+        for r in dist.batch_isend_irecv([dist.P2POp(dist.isend, mine, peer, self.group), dist.P2POp(dist.irecv, other, peer, self.group)]):
+            r.wait()
+        g.add_(other)
+
+    def broadcast_loss(self, loss: Optional[torch.Tensor]) -> torch.Tensor:
+        """The last stage's scalar (statistics, early stopping) made known to every stage."""
+        t = loss.detach().float().reshape(1).to(self.device) if self.m.is_last else torch.zeros(1, device=self.device)
+        dist.broadcast(t, src=self.last_rank, group=self.group)
+        return t[0]

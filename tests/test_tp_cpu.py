@@ -40,3 +40,12 @@ def test_tensor_parallel_matches_unsharded_model_gloo():
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("TP_OK") == 2
+
+
+def test_train_engine_dp2_tp2_matches_single_rank(tmp_path):
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", TP_SAVE_DIR=str(tmp_path / "hf"))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+                        "--master-port", "29873", os.path.join(ROOT, "tests", "dist_scripts", "run_engine_tp.py")], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ENGINE_TP_OK") == 4
