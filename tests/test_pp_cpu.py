@@ -16,3 +16,12 @@ def test_pipeline_matches_unsplit_model(stages, port):
                        env=env, capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("PP_OK") == stages
+
+
+def test_expert_parallel_matches_unsplit_moe():
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29887", os.path.join(ROOT, "tests", "dist_scripts", "run_ep.py")], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("EP_OK") == 2
