@@ -256,10 +256,11 @@ def init_split_world(n_train: int, device: Optional[torch.device] = None):
     rank = int(os.environ["RANK"])
     use_cuda = device is not None and device.type == "cuda"
     if not dist.is_initialized():
+        to = timedelta(seconds=float(os.environ.get("AREAL_DIST_TIMEOUT_S", "600")))
         if use_cuda:
-            dist.init_process_group("nccl", device_id=device)
+            dist.init_process_group("nccl", device_id=device, timeout=to)
         else:
-            dist.init_process_group("gloo")
+            dist.init_process_group("gloo", timeout=to)
     split = SplitWorld(n_train, world - n_train, rank)
     groups = build_split_groups(split, sp_size=1, use_cuda=use_cuda)
     bus = MessageBus(rank, world)

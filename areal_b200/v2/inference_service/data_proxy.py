@@ -1,0 +1,153 @@
+"""Data proxy: one per inference worker. Owns the RL sessions that run on that worker: every
+session is an :class:`ArealOpenAI` client over the worker's engine; chat completions are
+recorded token by token, rewards are attached, finished sessions are exported as training
+trajectories. Also forwards pause / continue / version / memory control to the engine.
+Reference: ``areal/v2/inference_service/data_proxy/{app.py, session.py}``."""
+from __future__ import annotations
+
+import asyncio
+import secrets
+import threading
+import time
+from typing import Any, Optional
+
+from ...api.cli_args import GenerationHyperparameters
+from ...openai.client import ArealOpenAI
+from ..common import HTTPError, JsonService
+
+
+class Session:
+    def __init__(self, client: ArealOpenAI, task_id: Optional[str]):
+        self.client, self.task_id = client, task_id
+        self.created = self.last_used = time.time()
+        self.finished = False
+
+
+class DataProxy:
+    def __init__(self, engine, tokenizer, gconfig: Optional[GenerationHyperparameters] = None, host: str = "127.0.0.1",
+                 port: Optional[int] = None, session_timeout: float = 3600.0, chat_template_type: str = "hf"):
+        self.engine, self.tokenizer, self.gconfig = engine, tokenizer, gconfig or GenerationHyperparameters()
+        self.chat_template_type = chat_template_type
+        self.session_timeout = session_timeout
+        self.sessions: dict[str, Session] = {}
+        self.ready: list[tuple[str, Session]] = []          # finished sessions waiting for export
+        self._lock = threading.Lock()
+        self._loop = asyncio.new_event_loop()
+        threading.Thread(target=self._loop.run_forever, daemon=True, name="data-proxy-loop").start()
+        self.svc = JsonService("data_proxy", host, port)
+        self._install()
+
+    # ------------------------------------------------------------------ helpers
+    def _get(self, key: Optional[str]) -> Session:
+        with self._lock:
+            s = self.sessions.get(key or "")
+        if s is None:
+            raise HTTPError(401, "unknown session key")
+        if s.finished:
+            raise HTTPError(409, "session already finished")
+        s.last_used = time.time()
+        return s
+
+    def _run(self, coro):
+        return asyncio.run_coroutine_threadsafe(coro, self._loop).result()
+
+    def gc(self) -> int:
+        """Drops sessions idle for longer than the timeout."""
+        now = time.time()
+        with self._lock:
+            dead = [k for k, s in self.sessions.items() if now - s.last_used > self.session_timeout]
+            for k in dead:
+                del self.sessions[k]
+        return len(dead)
+
+    # ------------------------------------------------------------------ routes
+    def _install(self):
+        svc = self.svc
+
+        @svc.route("GET", "/health")
+        def health(body, ctx):
+            return {"status": "ok", "sessions": len(self.sessions), "ready": len(self.ready), "version": self.engine.get_version()}
+
+        @svc.route("POST", "/rl/start_session")
+        def start(body, ctx):
+            key = "sk-sess-" + secrets.token_hex(16)
+            cl = ArealOpenAI(self.engine, self.tokenizer, gconfig=self.gconfig, chat_template_type=self.chat_template_type)
+            with self._lock:
+                self.sessions[key] = Session(cl, body.get("task_id"))
+            return {"session_id": key, "api_key": key}
+
+        @svc.route("POST", "/v1/chat/completions")
+        @svc.route("POST", "/chat/completions")
+        def chat(body, ctx):
+            s = self._get(ctx.api_key)
+            kw = {k: body[k] for k in ("messages", "model", "temperature", "top_p", "max_tokens", "max_completion_tokens", "stop",
+                                        "tools", "tool_choice", "frequency_penalty", "extra_body", "metadata") if k in body}
+            return self._run(s.client.chat.completions.create(**kw)).to_dict()
+
+        @svc.route("POST", "/rl/set_reward")
+        def set_reward(body, ctx):
+            s = self._get(ctx.api_key)
+            if body.get("interaction_id"):
+                s.client.set_reward(body["interaction_id"], float(body["reward"]))
+            else:
+                s.client.set_last_reward(float(body["reward"]))
+            return {"ok": True}
+
+        @svc.route("POST", "/rl/end_session")
+        def end(body, ctx):
+            s = self._get(ctx.api_key)
+            s.finished = True
+            with self._lock:
+                self.sessions.pop(ctx.api_key, None)
+                self.ready.append((ctx.api_key, s))
+            return {"ok": True, "interactions": len(s.client._cache)}
+
+        @svc.route("POST", "/export_trajectories")
+        def export(body, ctx):
+            style, discount = body.get("style", "individual"), body.get("discount", 1.0)
+            with self._lock:
+                take, self.ready = self.ready[: int(body.get("max_sessions", 1 << 30))], self.ready[int(body.get("max_sessions", 1 << 30)):]
+            out = []
+            for key, s in take:
+                inter = s.client.export_interactions(style, discount)
+                tds = [v.to_tensor_dict() for v in inter.values() if v.has_tensor_data]
+                out.append({"session_id": key, "task_id": s.task_id,
+                            "trajectories": [{k: (t[0].tolist() if t.dim() == 2 else t.tolist()) for k, t in td.items()} for td in tds]})
+            return {"sessions": out}
+
+        @svc.route("POST", "/pause_generation")
+        def pause(body, ctx):
+            self.engine.pause_generation()
+            return {"ok": True}
+
+        @svc.route("POST", "/continue_generation")
+        def cont(body, ctx):
+            self.engine.continue_generation()
+            return {"ok": True}
+
+        @svc.route("POST", "/set_version")
+        def set_version(body, ctx):
+            self.engine.set_version(int(body["version"]))
+            return {"ok": True}
+
+        @svc.route("POST", "/release_memory")
+        def release(body, ctx):
+            self.engine.offload(body.get("tags"))
+            return {"ok": True}
+
+        @svc.route("POST", "/resume_memory")
+        def resume(body, ctx):
+            self.engine.onload(body.get("tags"))
+            return {"ok": True}
+
+    def start(self):
+        self.svc.start()
+        return self
+
+    def stop(self):
+        self.svc.stop()
+        self._loop.call_soon_threadsafe(self._loop.stop)
+
+    @property
+    def address(self) -> str:
+        return self.svc.address

@@ -130,10 +130,18 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    import faulthandler
+
     import torch
     import torch.distributed as dist
 
     from areal_b200.infra.bench_driver import run_async_grpo_bench
+
+    # a rank that stops making progress prints every thread's stack and exits instead of
+    # holding the other ranks (and the GPUs) until an outer limit
+    wd = float(os.environ.get("AREAL_BENCH_WATCHDOG_S", "0") or 0)
+    if wd > 0:
+        faulthandler.dump_traceback_later(wd, exit=True)
 
     result = run_async_grpo_bench(args, ClockSampler)
     if result is not None:
