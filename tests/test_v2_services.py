@@ -1,0 +1,197 @@
+"""v2 microservices with in-process servers: gateway / router / data proxies, training
+service with a fake engine, weight-update gateway, CLI state."""
+import json
+import os
+
+import pytest
+import torch
+
+from areal_b200.api.cli_args import GenerationHyperparameters
+from areal_b200.v2 import cli
+from areal_b200.v2.common import HTTPError, JsonService, call
+from areal_b200.v2.inference_service.controller import InferenceServiceController
+from areal_b200.v2.training_service.controller import TrainingServiceClient
+from areal_b200.v2.training_service.worker import TrainingWorker
+from areal_b200.v2.weight_update.gateway import WeightUpdateGateway
+from tests.test_openai_and_agents import ByteTok, ScriptedEngine
+
+
+class CtlEngine(ScriptedEngine):
+    def __init__(self, answers):
+        super().__init__(answers, version=0)
+        self.events = []
+
+    def pause_generation(self):
+        self.events.append("pause")
+
+    def continue_generation(self):
+        self.events.append("continue")
+
+    def set_version(self, v):
+        self.version = v
+        self.events.append(("version", v))
+
+
+def test_json_service_routing_and_errors():
+    svc = JsonService("t")
+
+    @svc.route("POST", "/a/{x}/b")
+    def h(body, ctx):
+        if body.get("boom"):
+            raise HTTPError(418, "teapot")
+        return {"x": ctx.params["x"], "key": ctx.api_key, "n": body.get("n", 0) + 1}
+    svc.start()
+    try:
+        assert call(f"{svc.url}/a/7/b", {"n": 1}, api_key="k") == {"x": "7", "key": "k", "n": 2}
+        with pytest.raises(HTTPError) as e:
+            call(f"{svc.url}/a/7/b", {"boom": True})
+        assert e.value.status == 418 and e.value.message == "teapot"
+        with pytest.raises(HTTPError) as e:
+            call(f"{svc.url}/nope", {})
+        assert e.value.status == 404
+    finally:
+        svc.stop()
+    with pytest.raises(HTTPError) as e:
+        call(f"{svc.url}/a/7/b", {}, timeout=1)
+    assert e.value.status == 503
+
+
+def test_inference_service_sessions_affinity_export_and_control():
+    engines = [CtlEngine(["alpha", "beta"]), CtlEngine(["gamma", "delta"])]
+    ctl = InferenceServiceController(admin_key="adm").start(engines, ByteTok(), GenerationHyperparameters(max_new_tokens=16))
+    try:
+        with pytest.raises(HTTPError) as e:
+            call(f"{ctl.gateway.svc.url}/rl/start_session", {}, api_key="wrong")
+        assert e.value.status == 401
+        s1, s2 = ctl.start_session("t1"), ctl.start_session("t2")
+        assert s1["base_url"] == ctl.base_url
+        owners = {call(f"http://{ctl.router.address}/route/lookup", {"session_id": s["api_key"]})["address"] for s in (s1, s2)}
+        assert len(owners) == 2                                         # least-loaded placement spreads the two sessions
+        for s in (s1, s2):
+            for turn in range(2):                                        # both turns of a session hit the same engine
+                c = call(f"{ctl.base_url}/chat/completions", {"messages": [{"role": "user", "content": f"q{turn}"}]}, api_key=s["api_key"])
+                assert c["choices"][0]["message"]["content"] in ("alpha", "beta", "gamma", "delta")
+            call(f"{ctl.gateway.svc.url}/rl/set_reward", {"reward": 1.5}, api_key=s["api_key"])
+            call(f"{ctl.gateway.svc.url}/rl/end_session", {}, api_key=s["api_key"])
+        assert [len(e.requests) for e in engines] == [2, 2]
+        with pytest.raises(HTTPError):                                   # ended sessions are gone
+            call(f"{ctl.base_url}/chat/completions", {"messages": []}, api_key=s1["api_key"])
+        batch = ctl.export_batch(style="individual", discount=0.5)
+        assert batch["input_ids"].shape[0] == 4 and sorted(batch["rewards"].tolist()) == [0.75, 0.75, 1.5, 1.5]
+        assert ctl.export_batch() is None
+        ctl.pause_generation()
+        ctl.set_version(3)
+        ctl.continue_generation()
+        assert all(e.events == ["pause", ("version", 3), "continue"] for e in engines)
+        assert call(f"http://{ctl.router.address}/health_check", {})["workers"][ctl.proxies[0].address]["healthy"]
+    finally:
+        ctl.stop()
+
+
+class FakeTrainEngine:
+    """CPU stand-in for a train engine: deterministic functions of the batch."""
+
+    def __init__(self):
+        self.version, self.saved, self.lr_steps = 0, [], 0
+
+    def get_version(self):
+        return self.version
+
+    def set_version(self, v):
+        self.version = v
+
+    def step_lr_scheduler(self):
+        self.lr_steps += 1
+
+    def compute_logp(self, batch):
+        return batch["input_ids"].float() * -0.5
+
+    def compute_advantages(self, batch, group_sizes=None):
+        batch["advantages"] = batch["rewards"][:, None].expand_as(batch["input_ids"]).float() * batch["attention_mask"]
+        return batch
+
+    def ppo_update(self, batch):
+        return [{"n_seqs": float(batch["input_ids"].shape[0])}]
+
+    def train_lm(self, batch):
+        return {"nll": 1.0}
+
+    def save(self, meta):
+        os.makedirs(meta.path, exist_ok=True)
+        open(os.path.join(meta.path, "model.safetensors"), "w").write("x")
+        self.saved.append(meta.path)
+
+    def export_stats(self):
+        return {"k": 1.0}
+
+
+def test_training_service_dispatch_and_merge():
+    engs = [FakeTrainEngine(), FakeTrainEngine()]
+    workers = [TrainingWorker(e).start() for e in engs]
+    try:
+        cl = TrainingServiceClient([w.address for w in workers], group_size=2)
+        lens = torch.tensor([9, 3, 5, 7, 2, 8, 6, 4])
+        am = torch.arange(9)[None] < lens[:, None]
+        batch = {"attention_mask": am, "input_ids": torch.randint(1, 9, (8, 9)) * am, "rewards": torch.arange(8).float()}
+        lp = cl.compute_logp(batch)
+        assert torch.equal(lp, batch["input_ids"].float() * -0.5)
+        out = cl.compute_advantages(batch)
+        assert out is batch and torch.equal(batch["advantages"], batch["rewards"][:, None].expand(8, 9) * am)
+        assert cl.ppo_update(batch) == [{"n_seqs": 4.0}]
+        assert cl.train_lm(batch) == {"nll": 1.0}
+        cl.set_version(5)
+        cl.step_lr_scheduler()
+        assert [e.version for e in engs] == [5, 5] and [e.lr_steps for e in engs] == [1, 1]
+        assert cl.export_stats() == {"k": 1.0} and all(h["status"] == "ok" for h in cl.health())
+        with pytest.raises(HTTPError) as e:
+            cl._batch_call("/rw/train", batch)
+        assert e.value.status == 404
+    finally:
+        for w in workers:
+            w.stop()
+
+
+def test_weight_update_gateway_disk_flow(tmp_path):
+    eng = FakeTrainEngine()
+    tw = TrainingWorker(eng).start()
+    infer = JsonService("fake_infer")
+    log = []
+    for name in ("pause_generation", "continue_generation", "update_weights_from_disk"):
+        infer.route("POST", f"/{name}")(lambda body, ctx, name=name: log.append((name, body.get("model_path"), body.get("version"))) or {"success": True})
+    infer.start()
+    gw = WeightUpdateGateway().start()
+    try:
+        with pytest.raises(HTTPError):
+            call(f"{gw.svc.url}/connect", {"pair": "p", "train_workers": [], "infer_workers": [], "mode": "disk"})
+        call(f"{gw.svc.url}/connect", {"pair": "p", "train_workers": [tw.address], "infer_workers": [infer.address], "mode": "disk",
+                                       "path": str(tmp_path)})
+        r = call(f"{gw.svc.url}/update_weights", {"pair": "p", "version": 2})
+        assert r["ok"] and r["version"] == 2
+        ck = os.path.join(str(tmp_path), "v2")
+        assert eng.saved == [ck] and eng.version == 2
+        assert log == [("pause_generation", None, None), ("update_weights_from_disk", ck, 2), ("continue_generation", None, None)]
+        assert call(f"{gw.svc.url}/weight_meta/p/version") == {"version": 2}
+        assert call(f"{gw.svc.url}/weight_meta/p/last_checkpoint") == {"last_checkpoint": ck}
+        call(f"{gw.svc.url}/disconnect", {"pair": "p"})
+        with pytest.raises(HTTPError) as e:
+            call(f"{gw.svc.url}/update_weights", {"pair": "p", "version": 3})
+        assert e.value.status == 404
+    finally:
+        gw.stop(); infer.stop(); tw.stop()
+
+
+def test_cli_state_roundtrip(tmp_path, monkeypatch, capsys):
+    monkeypatch.setattr(cli, "STATE", str(tmp_path / "st.json"))
+    svc = JsonService("x")
+    svc.route("GET", "/health")(lambda b, c: {"status": "ok"})
+    svc.start()
+    try:
+        cli.record("inference", svc.address, preset="tiny")
+        cli.record("inference", "127.0.0.1:9", preset="dead")
+        assert cli.main(["inference", "status"]) == 1
+        out = capsys.readouterr().out
+        assert "ok" in out and "DOWN" in out
+        assert len(json.load(open(tmp_path / "st.json"))["services"]) == 2
+        assert cli.main(["state", "clear"]) == 0 and cli.load_state() == {"services": []}
+    finally:
+        svc.stop()
