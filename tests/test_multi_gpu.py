@@ -43,3 +43,12 @@ def test_split_async_grpo_two_gpus():
                          "--median-len", "64", "--max-len", "128"])
     assert r.returncode == 0
     assert '"metric"' in r.stdout
+
+
+def test_fused_tp_gemm_collectives_two_gpus():
+    """all-gather->GEMM and GEMM->reduce-scatter kernels (peer TMA loads / peer reductions)
+    against fp32 math on gathered operands."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_tp_fused.py"), 2, 29731, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("TP_FUSED_OK") == 2
