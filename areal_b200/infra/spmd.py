@@ -263,7 +263,9 @@ def init_split_world(n_train: int, device: Optional[torch.device] = None):
             dist.init_process_group("gloo", timeout=to)
     split = SplitWorld(n_train, world - n_train, rank)
     groups = build_split_groups(split, sp_size=1, use_cuda=use_cuda)
+    logger.info("rank %d: process groups ready", rank)
     bus = MessageBus(rank, world)
+    logger.info("rank %d: message bus connected", rank)
     return split, groups, bus
 
 
@@ -301,7 +303,9 @@ def run_rollout_rank(cfg, model_cfg, split: SplitWorld, groups: dict, bus: Messa
     from ..models.decoder import build_model
 
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    logger.info("rollout rank %d: building the model", split.rank)
     model = build_model(model_cfg, dtype=dtype, device=device, seed=seed)
+    logger.info("rollout rank %d: model built, mapping the parameter buffer", split.rank)
     alloc = None
     if symmetric and device.type == "cuda":
         from ..parallel.symm import symm_empty
@@ -312,6 +316,7 @@ def run_rollout_rank(cfg, model_cfg, split: SplitWorld, groups: dict, bus: Messa
             return t
     n_shards = split.n_train if split.n_train > 1 else 1
     store = FlatParamStore(model, n_shards, 0, alloc_param=alloc, with_grads=False)
+    logger.info("rollout rank %d: parameter buffer ready (%d elements)", split.rank, store.padded)
     engine = NativeInferenceEngine(cfg.rollout, cfg.native_infer, model=model, eos_token_id=eos_token_id)
     engine.initialize(device=device, seed=seed)
     dl = DataLoader(dataset, batch_size=cfg.train_dataset.batch_size, shuffle=True, drop_last=True, collate_fn=list,
