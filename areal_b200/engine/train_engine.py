@@ -231,6 +231,13 @@ class B200TrainEngine(TrainEngine):
             if has_ckpt:
                 hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
         self.model.gradient_checkpointing = cfg.gradient_checkpointing
+        self.use_lora = bool(cfg.use_lora) and cfg.optimizer is not None
+        if self.use_lora:
+            if tp > 1:
+                raise NotImplementedError("LoRA with tensor parallelism")
+            from ..models.lora import apply_lora
+
+            apply_lora(self.model, cfg.lora_rank, cfg.lora_alpha, cfg.target_modules or None, seed=seed)
         sp = self.sp_size
         # ranks that hold the same tensor-parallel slice shard its optimizer state (ZeRO)
         self._shard_ranks = [self._train_ranks[(d * sp + s_) * tp + self.tp_rank] for d in range(self.dp_size) for s_ in range(sp)] \
@@ -249,7 +256,7 @@ class B200TrainEngine(TrainEngine):
             alloc_p = alloc_g
         alloc = alloc_g
         self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
-                                    with_grads=cfg.optimizer is not None)
+                                    with_grads=cfg.optimizer is not None, only_trainable=self.use_lora)
         if n_shards > 1:
             # identical initial weights on every rank of the shard group
             dist.broadcast(self.store.flat_param, src=self._shard_ranks[0], group=self._shard_group)
@@ -617,6 +624,15 @@ class B200TrainEngine(TrainEngine):
                     else:
                         for _ in named:
                             pass
+            elif head and getattr(self, "use_lora", False):
+                from ..models.lora import merge_lora_, save_adapter, unmerge_lora_
+
+                save_adapter(self.model, os.path.join(meta.path, "adapter"), base_model_name_or_path=self.config.path)
+                merge_lora_(self.model)       # the served checkpoint carries the adapters folded in
+                try:
+                    hf_io.save_model_hf(self.model, meta.path, skip=lambda n: "_lora_" in n)
+                finally:
+                    unmerge_lora_(self.model)
             elif head:
                 hf_io.save_model_hf(self.model, meta.path)
             if head and meta.tokenizer is not None:
@@ -722,6 +738,14 @@ class B200TrainEngine(TrainEngine):
     def export_weights(self) -> dict[str, torch.Tensor]:
         """Host copies of the (replicated) parameters under their native names: the payload of
         the controller-mediated weight update for small models and CPU runs."""
+        if getattr(self, "use_lora", False):
+            from ..models.lora import merge_lora_, unmerge_lora_
+
+            merge_lora_(self.model)
+            try:
+                return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters() if "_lora_" not in n}
+            finally:
+                unmerge_lora_(self.model)
         return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters()}
 
     def export_stats(self) -> dict[str, float]:

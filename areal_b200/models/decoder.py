@@ -40,6 +40,16 @@ class PackedBatch:
         self.tile_info = OF.attn_tile_table(self.cu_seqlens, total_tokens) if cu_seqlens.is_cuda else None
 
 
+def _lin(mod, name: str, x: torch.Tensor, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ W^T (+ resid)`` for ``W = mod.<name>`` plus its low-rank adapter when one is attached
+    (and not merged into ``W``)."""
+    y = OF.linear(x, getattr(mod, name), resid)
+    st = getattr(mod, "lora", None)
+    if st is not None and not st.merged and name in getattr(mod, "lora_targets", ()):
+        y = y + st.scale * OF.linear(OF.linear(x, getattr(mod, name + "_lora_A")), getattr(mod, name + "_lora_B"))
+    return y
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device):
         super().__init__()
@@ -60,7 +70,7 @@ class Attention(nn.Module):
         """Returns q [T,nq,D], k [T,nkv,D], v [T,nkv,D] with QK-norm and RoPE applied."""
         T = x.shape[0]
         D, nq, nkv = self.D, self.nq, self.nkv
-        qkv = OF.linear(x, self.qkv_proj)
+        qkv = _lin(self, "qkv_proj", x)
         if self.qkv_bias is not None:
             qkv = qkv + self.qkv_bias
         if qkv.is_cuda and not torch.is_grad_enabled() and D in (64, 128):
@@ -81,12 +91,12 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, pb: PackedBatch, cos, sin, attn_fn=None) -> torch.Tensor:
         T = x.shape[0]
         if attn_fn is None and getattr(self, "sp_size", 1) == 1 and x.is_cuda and self.D in (64, 128):
-            qkv = OF.linear(x, self.qkv_proj)
+            qkv = _lin(self, "qkv_proj", x)
             if self.qkv_bias is not None:
                 qkv = qkv + self.qkv_bias
             o = OF.qknorm_rope_attention(qkv, self.q_norm, self.k_norm, pb.position_ids, cos, sin, pb.cu_seqlens, self.nq,
                                          self.nkv, self.D, self.cfg.rms_norm_eps, 1.0 / math.sqrt(self.D), pb.tile_info)
-            return OF.linear(o.reshape(T, self.nq * self.D), self.o_proj)
+            return _lin(self, "o_proj", o.reshape(T, self.nq * self.D))
         q, k, v = self.project_qkv(x, pb.position_ids, cos, sin)
         if attn_fn is not None:
             o = attn_fn(q, k, v)
@@ -97,7 +107,7 @@ class Attention(nn.Module):
         else:
             o = OF.attention(q, k.contiguous() if not k.is_cuda else k, v.contiguous() if not v.is_cuda else v,
                              pb.cu_seqlens, True, 1.0 / math.sqrt(self.D), pb.tile_info)
-        return OF.linear(o.reshape(T, self.nq * self.D), self.o_proj)
+        return _lin(self, "o_proj", o.reshape(T, self.nq * self.D))
 
 
 class DenseMLP(nn.Module):
@@ -107,7 +117,7 @@ class DenseMLP(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(hidden, inter, dtype=dtype, device=device))
 
     def forward(self, x):
-        return OF.linear(OF.swiglu(OF.linear(x, self.gate_up_proj)), self.down_proj)
+        return _lin(self, "down_proj", OF.swiglu(_lin(self, "gate_up_proj", x)))
 
 
 class MoEMLP(nn.Module):

@@ -161,8 +161,8 @@ def write_hf_index(path: str, weight_map: dict[str, str], total_size: int) -> No
             json.dump({"metadata": {"total_size": total_size}, "weight_map": dict(sorted(weight_map.items()))}, f, indent=2)
 
 
-def save_model_hf(model, path: str, max_shard_bytes: int = 5 * 1024 ** 3) -> None:
-    named = [(n, p.detach()) for n, p in model.named_parameters()]
+def save_model_hf(model, path: str, max_shard_bytes: int = 5 * 1024 ** 3, skip=None) -> None:
+    named = [(n, p.detach()) for n, p in model.named_parameters() if skip is None or not skip(n)]
     save_hf_sharded(path, model.cfg, native_to_hf_tensors(model.cfg, named), max_shard_bytes)
 
 
