@@ -238,6 +238,12 @@ class PPOTrainer:
         return stats
 
     def close(self):
+        try:
+            self.saver.wait()
+        except Exception as e:  # an export that failed must not mask the shutdown
+            import logging as _l
+
+            _l.getLogger("areal_b200.trainer").error("pending checkpoint export failed: %r", e)
         for e in (self.rollout, self.eval_rollout):
             if e is not None:
                 e.destroy()

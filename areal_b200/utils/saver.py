@@ -39,13 +39,39 @@ class Saver:
         c = self.config
         path = self.get_model_save_path(c.experiment_name, c.trial_name, c.fileroot, epoch, step, global_step, name)
         fmt = "sharded" if self.for_recover else "hf"
+        mode = getattr(c, "mode", "auto")
+        use_async = (mode == "async" or (mode == "auto" and getattr(getattr(engine, "device", None), "type", "cpu") == "cuda")) \
+            and not self.for_recover and hasattr(engine, "model") and getattr(engine, "tp_size", 1) == 1 \
+            and not getattr(engine, "use_lora", False) and getattr(engine, "local_index", 0) <= 0
+        if use_async:
+            from ..models import hf_io
+            from .async_checkpoint import AsyncCheckpointWriter
+
+            if self._async is None:
+                self._async = AsyncCheckpointWriter(getattr(c, "max_pinned_gb", 17.5))
+            cfg_m = engine.model.cfg
+            named = [(n, p.detach()) for n, p in engine.model.named_parameters()]
+
+            def write(host_named, path=path, cfg_m=cfg_m, tokenizer=tokenizer):
+                hf_io.save_hf_sharded(path, cfg_m, hf_io.native_to_hf_tensors(cfg_m, host_named))
+                if tokenizer is not None and hasattr(tokenizer, "save_pretrained"):
+                    tokenizer.save_pretrained(path)
+            self._async.save(named, write, path)
+            return path
         engine.save(SaveLoadMeta(path=path, weight_format=fmt, with_optim=self.for_recover, tokenizer=tokenizer,
                                  processor=processor, base_model_path=base_model_path))
         return path
 
     def maybe_wait_for_staging(self):
+        """Called before the optimizer rewrites the weights: the device->host copy of an
+        asynchronous export must be complete by then."""
         if self._async is not None:
             self._async.wait_staging()
+
+    def wait(self):
+        """Blocks until an export in flight is on disk (end of training, before loading it)."""
+        if self._async is not None:
+            self._async.wait()
 
     def state_dict(self):
         return self.freq_ctl.state_dict()

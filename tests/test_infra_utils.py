@@ -75,3 +75,88 @@ def test_frequency_controls_and_schedules():
     e2.load_state_dict(sd)
     assert ValueScheduler("linear", 1.0, 10, 0.0).get(5) == pytest.approx(0.5)
     assert ValueScheduler("cosine", 1.0, 10, 0.0).get(10) == pytest.approx(0.0, abs=1e-9)
+
+
+def test_async_checkpoint_writer_and_saver_async_mode(tmp_path):
+    import threading
+    import time as _time
+
+    import torch as _torch
+
+    from areal_b200.api.cli_args import SaverConfig
+    from areal_b200.models import hf_io
+    from areal_b200.models.config import preset
+    from areal_b200.models.decoder import build_model
+    from areal_b200.utils.async_checkpoint import AsyncCheckpointWriter
+    from areal_b200.utils.saver import Saver
+
+    w = AsyncCheckpointWriter(max_pinned_gb=0.001)
+    t = _torch.arange(10.0)
+    gate, seen = threading.Event(), {}
+
+    def write(host):
+        gate.wait(5)
+        seen.update({n: x.clone() for n, x in host})
+    w.save([("a", t)], write, "p")
+    t.zero_()                                   # the source may change right after staging
+    assert w.busy
+    gate.set()
+    w.wait()
+    assert _torch.equal(seen["a"], _torch.arange(10.0)) and not w.busy
+    w.save([("a", t)], lambda host: (_ for _ in ()).throw(IOError("disk full")), "p")
+    try:
+        w.wait()
+        raise AssertionError("expected the writer's error")
+    except RuntimeError as e:
+        assert "failed" in str(e)
+
+    class Eng:
+        device = _torch.device("cpu")
+        local_index = 0
+
+        def __init__(self):
+            self.model = build_model(preset("tiny-qwen2"), dtype=_torch.float32, device="cpu", seed=1)
+    eng = Eng()
+    sv = Saver(SaverConfig(fileroot=str(tmp_path), experiment_name="e", trial_name="t", freq_steps=1, mode="async"))
+    path = sv.save(eng, 0, 0, 0)
+    sv.maybe_wait_for_staging()
+    sv.wait()
+    m2 = build_model(preset("tiny-qwen2"), dtype=_torch.float32, device="cpu", seed=2)
+    hf_io.load_model_hf(m2, path)
+    a, b = dict(eng.model.named_parameters()), dict(m2.named_parameters())
+    assert all(_torch.equal(a[k], b[k]) for k in a)
+
+
+def test_delta_weight_transfer_exact_and_predicted():
+    import torch as _torch
+
+    from areal_b200.wsync.delta import DeltaPusher, changed_blocks, predict_changed_blocks
+
+    _torch.manual_seed(0)
+    n, blk = 10_000, 256
+    master = _torch.randn(n) * 0.05
+    old = master.to(_torch.bfloat16)
+    m, v = _torch.randn(n) * 1e-3, _torch.rand(n) * 1e-6 + 1e-8
+    lr, b1, b2, eps, wd, step = 1e-6, 0.9, 0.95, 1e-8, 0.0, 10
+    m[:512] *= 5000                                          # a region with large updates
+    upd = lr * ((m / (1 - b1 ** step)) / ((v / (1 - b2 ** step)).sqrt() + eps) + wd * master)
+    new_master = master - upd
+    new = new_master.to(_torch.bfloat16)
+    exact = changed_blocks(new, old, blk)
+    assert exact[:2].all() and exact.float().mean() < 0.9
+    pred = predict_changed_blocks(new_master, m, v, lr, b1, b2, eps, wd, step, blk, safety=2.0)
+    assert bool((pred | ~exact).all()), "prediction must be a superset of the exact set"
+    # pusher: the receiver ends up identical while only changed runs travel
+    dst = _torch.zeros(n, dtype=_torch.bfloat16)
+    src = old.clone()
+    copies = []
+
+    def copy(off, ln):
+        copies.append((off, ln))
+        dst[off:off + ln] = src[off:off + ln]
+    p = DeltaPusher(src, copy, block=blk)
+    assert p.push() == 1.0 and _torch.equal(dst, src)
+    src.copy_(new)
+    frac = p.push()
+    assert _torch.equal(dst, src) and 0 < frac < 1.0 and abs(frac - exact.float().mean().item()) < 0.05
+    assert p.push() == 0.0 and len(copies) < 2 + exact.sum().item() + 1
