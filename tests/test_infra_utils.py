@@ -137,8 +137,8 @@ def test_delta_weight_transfer_exact_and_predicted():
     master = _torch.randn(n) * 0.05
     old = master.to(_torch.bfloat16)
     m, v = _torch.randn(n) * 1e-3, _torch.rand(n) * 1e-6 + 1e-8
-    lr, b1, b2, eps, wd, step = 1e-6, 0.9, 0.95, 1e-8, 0.0, 10
-    m[:512] *= 5000                                          # a region with large updates
+    lr, b1, b2, eps, wd, step = 1e-7, 0.9, 0.95, 1e-8, 0.0, 10
+    m[:512] *= 50000                                          # a region with large updates
     upd = lr * ((m / (1 - b1 ** step)) / ((v / (1 - b2 ** step)).sqrt() + eps) + wd * master)
     new_master = master - upd
     new = new_master.to(_torch.bfloat16)
