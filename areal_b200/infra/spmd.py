@@ -258,7 +258,11 @@ def init_split_world(n_train: int, device: Optional[torch.device] = None):
     if not dist.is_initialized():
         to = timedelta(seconds=float(os.environ.get("AREAL_DIST_TIMEOUT_S", "600")))
         if use_cuda:
-            dist.init_process_group("nccl", device_id=device, timeout=to)
+            # No ``device_id`` here: binding the default group to a device makes every later
+            # ``new_group`` call an NCCL communicator split on the NON-member ranks, also for gloo
+            # sub-groups whose members never join that split; with trainer-only gloo groups
+            # (2+ trainer ranks) the rollout ranks then wait in the split forever.
+            dist.init_process_group("nccl", timeout=to)
         else:
             dist.init_process_group("gloo", timeout=to)
     split = SplitWorld(n_train, world - n_train, rank)

@@ -40,7 +40,7 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    dist.init_process_group("nccl")
     big = os.environ.get("TP_FUSED_BENCH", "0") == "1"
     rows, K, N = (4096, 4096, 6144) if big else (256, 512, 768)
     tp = FusedTPLinear(dist.group.WORLD, dev, max_rows_per_rank=rows, max_k=max(K, N), max_n=max(K, N))
