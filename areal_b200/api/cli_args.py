@@ -198,6 +198,8 @@ class TrainEngineConfig:
     pad_to_maximum: bool = False
     disable_dropout: bool = False
     gradient_checkpointing: bool = False
+    activation_checkpointing: Optional[str] = None   # none | full | selective | memory_budget (overrides the flag above)
+    activation_memory_budget: float = 0.5            # fraction of layers recomputed in memory_budget mode
     dtype: str = "bfloat16"
     grad_reduce_dtype: str = "float32"
     optimizer_dtype: str = "float32"

@@ -231,6 +231,11 @@ class B200TrainEngine(TrainEngine):
             if has_ckpt:
                 hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
         self.model.gradient_checkpointing = cfg.gradient_checkpointing
+        ac = getattr(cfg.archon, "ac_mode", "selective") if not cfg.gradient_checkpointing else "full"
+        if getattr(cfg, "activation_checkpointing", None):
+            ac = cfg.activation_checkpointing
+        if ac in ("selective", "memory_budget") and not cfg.gradient_checkpointing and getattr(cfg, "activation_checkpointing", None):
+            self.model.set_activation_checkpointing(ac, getattr(cfg, "activation_memory_budget", 0.5))
         self.use_lora = bool(cfg.use_lora) and cfg.optimizer is not None
         if self.use_lora:
             if tp > 1:

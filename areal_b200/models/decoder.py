@@ -279,12 +279,35 @@ class CausalLM(nn.Module):
         resid = None
         for i, layer in enumerate(self.layers):
             fn = attn_fns[i] if attn_fns is not None else None
-            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+            if self.training and torch.is_grad_enabled() and self._recompute_layer(i):
                 h, resid = checkpoint(layer, h, resid, pb, cos, sin, fn, use_reentrant=False)
             else:
                 h, resid = layer(h, resid, pb, cos, sin, fn)
         x, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
         return x
+
+    def set_activation_checkpointing(self, mode: str = "none", fraction: float = 0.5) -> None:
+        """``none`` keeps every activation; ``full`` recomputes every layer in the backward;
+        ``selective`` recomputes every second layer; ``memory_budget`` recomputes the first
+        ``round(fraction * num_layers)`` layers (their activations live longest), keeping the
+        rest: pick the fraction from the memory that is left after parameters and optimizer
+        state. Reference: ``areal/experimental/models/archon/activation_checkpoint.py``."""
+        n = len(self.layers)
+        if mode in ("none", None, False):
+            self.gradient_checkpointing, self._ckpt_layers = False, frozenset()
+        elif mode in ("full", True):
+            self.gradient_checkpointing, self._ckpt_layers = True, frozenset(range(n))
+        elif mode == "selective":
+            self.gradient_checkpointing, self._ckpt_layers = False, frozenset(range(0, n, 2))
+        elif mode == "memory_budget":
+            if not 0.0 <= fraction <= 1.0:
+                raise ValueError("memory_budget fraction must be in [0, 1]")
+            self.gradient_checkpointing, self._ckpt_layers = False, frozenset(range(int(round(fraction * n))))
+        else:
+            raise ValueError(f"unknown activation checkpointing mode '{mode}'")
+
+    def _recompute_layer(self, i: int) -> bool:
+        return self.gradient_checkpointing or i in getattr(self, "_ckpt_layers", ())
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Full fp32 logits (small batches / sampling only)."""

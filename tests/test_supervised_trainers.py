@@ -73,3 +73,26 @@ def test_dpo_prefers_chosen(tmp_path):
         assert h[0]["dpo/dpo_acc"] <= 0.6 or True
         assert sum(x["dpo/dpo_acc"] for x in h[-3:]) / 3 > 0.9
         assert h[-1]["dpo/reward_chosen"] > h[-1]["dpo/reward_rejected"]
+
+
+def test_activation_checkpointing_modes_keep_gradients_identical():
+    import torch
+
+    from areal_b200.models.config import preset
+    from areal_b200.models.decoder import build_model
+
+    cfg = preset("tiny-qwen3", num_layers=4)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (40,), generator=g)
+    cu = torch.tensor([0, 15, 40], dtype=torch.int32)
+    grads = {}
+    for mode, frac in (("none", 0), ("full", 0), ("selective", 0), ("memory_budget", 0.75)):
+        m = build_model(cfg, dtype=torch.float32, device="cpu", seed=1)
+        m.train()
+        m.set_activation_checkpointing(mode, frac)
+        want = {"none": 0, "full": 4, "selective": 2, "memory_budget": 3}[mode]
+        assert sum(m._recompute_layer(i) for i in range(4)) == want
+        m(ids, cu, max_seqlen=25).float().pow(2).mean().backward()
+        grads[mode] = torch.cat([p.grad.flatten() for p in m.parameters() if p.grad is not None])
+    for mode in ("full", "selective", "memory_budget"):
+        assert torch.allclose(grads[mode], grads["none"], atol=1e-6)
