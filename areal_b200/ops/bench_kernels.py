@@ -136,6 +136,35 @@ def bench_attn_bwd(a):
     return report("attn_bwd_tcgen05 (+delta, dq cast)", ms, fl, seqlen=a.seqlen, batch=a.batch, heads=a.heads)
 
 
+def bench_qknorm_rope(a):
+    """Fused QK-norm + RoPE forward and backward on the layout of a fused QKV projection."""
+    T = a.seqlen * a.batch
+    nq, nkv, D = a.heads, a.kv_heads, a.dim
+    W = (nq + 2 * nkv) * D
+    qkv = torch.randn(T, W, device="cuda").bfloat16()
+    wq = torch.ones(D, device="cuda").bfloat16()
+    wk = torch.ones(D, device="cuda").bfloat16()
+    pos = (torch.arange(T, device="cuda") % a.seqlen).int()
+    cos, sin = OF.rope_tables(a.seqlen, D, 1e6, "cuda")
+    ms = timeit(lambda: OF.qknorm_rope_fwd(qkv, wq, wk, pos, cos, sin, nq, nkv, D, 1e-6), a.iters, a.warmup)
+    by = 2.0 * T * (nq + nkv) * D * 2
+    report("qknorm_rope_fwd", ms, 0.0, by, tokens=T, heads=nq, kv_heads=nkv)
+    qk, rstd = OF.qknorm_rope_fwd(qkv, wq, wk, pos, cos, sin, nq, nkv, D, 1e-6)
+    dq32 = torch.randn(T, nq, D, device="cuda")
+    dqkv = torch.randn(T, W, device="cuda").bfloat16()
+    dwq, dwk = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    L = oplib.get_lib()
+
+    def bwd():
+        oplib.check(L.ab2_qknorm_rope_bwd(qkv.data_ptr(), wq.data_ptr(), wk.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                          rstd.data_ptr(), dq32.data_ptr(), dqkv.data_ptr(), dwq.data_ptr(), dwk.data_ptr(), T, nq, nkv, D,
+                                          W, W, oplib.stream_ptr()), "qknorm_rope_bwd")
+    ms = timeit(bwd, a.iters, a.warmup)
+    # reads: x (bf16), dq (fp32), dk (bf16); writes: dq/dk region (bf16)
+    by = T * D * (nq * (2 + 4 + 2) + nkv * (2 + 2 + 2))
+    return report("qknorm_rope_bwd", ms, 0.0, by, tokens=T, heads=nq, kv_heads=nkv)
+
+
 def bench_decode(a):
     ps = 64
     pages_per = (a.ctx + ps - 1) // ps
@@ -233,7 +262,7 @@ def bench_engine_decode(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_skinny", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
+    ap.add_argument("kernel", choices=["gemm", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
                                            "engine_decode"])
     ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--new", type=int, default=128)
@@ -251,7 +280,7 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.kernel == "logprob" and a.rows > 4096:
         a.rows = 2048
-    return {"gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
+    return {"gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
             "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
             "engine_decode": bench_engine_decode}[a.kernel](a)
 
