@@ -196,7 +196,9 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM, group=cpu_group)
         ms_a, wall_b = float(mx[0]), float(mx[2])
-        tok_a, tok_b = float(sm[1]), float(sm[3])
+        # ``ppo_actor/n_tokens`` is exported after a reduction over the trainer ranks, so every
+        # rank already holds the GLOBAL token count of a step: take it once, do not sum it again
+        tok_a, tok_b = float(mx[1]), float(mx[3])
         h2d, d2h, launches = float(sm[4]), float(sm[5]), int(sm[6])
     else:
         h2d, d2h = float(stats[4]), float(stats[5])
