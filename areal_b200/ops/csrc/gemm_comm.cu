@@ -13,6 +13,15 @@
 //       the peer pointer; the transfer of tile i overlaps the math of tile i+1 (two TMEM
 //       accumulators). Remote owners are visited first.
 //
+//   all-gather -> GEMM, copy-once form (MODE 2): a few CTAs of the same kernel copy each remote
+//       row block into a local gathered buffer exactly once (so A crosses NVLink once instead
+//       of once per output-tile column) and publish a per-block flag; the GEMM CTAs take local
+//       tiles first and wait (bounded) on the flag of a remote block before its first TMA load.
+//       All CTAs are co-resident (grid <= number of SMs), so the wait cannot starve.
+//
+//   GEMM -> reduce-scatter with bf16 payload (RED_BF16): the epilogue packs to bf16x2 and uses
+//       red.global.add.noftz.v4.bf16x2, halving the NVLink bytes (for small groups).
+//
 // Operand layouts: A K-major ([rows, K]); B K-major ([N, K], the weight layout) or MN-major
 // ([K, N]). The pipeline (TMA -> 128B-swizzled smem -> tcgen05.mma -> TMEM -> epilogue warps)
 // is the one of gemm.cu. Callers bracket the kernels with the bounded device barrier
@@ -34,8 +43,26 @@ struct TmapArray {
   CUtensorMap m[GC_MAX_PEERS];
 };
 struct OutPtrs {
-  float* p[GC_MAX_PEERS];
+  void* p[GC_MAX_PEERS];
 };
+struct GatherArgs {
+  const __nv_bfloat16* peer_a[GC_MAX_PEERS];  // every rank's [rows_per_rank, K] block as mapped here
+  __nv_bfloat16* gathered;                    // local [M, K] buffer (remote blocks land here)
+  int* flags;                                 // one per 128-row block: == epoch when the block is complete
+  int epoch;
+  int n_copy;                                 // CTAs [0, n_copy) copy, the rest compute
+  int lda;
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 template <int BN>
 struct GcCfg {
@@ -56,12 +83,14 @@ __device__ __forceinline__ void gc_tile(int tile, int m_blocks, int n_blocks, in
   mb = (m_lin + first_owner * blocks_per_rank) % m_blocks;
 }
 
-// MODE 0: gathered A, local bf16 output. MODE 1: local A, fp32 reduction into the row owners.
-template <int BN, bool B_MN, int MODE>
+// MODE 0: A gathered by remote TMA loads, local bf16 output. MODE 1: local A, reduction into the
+// row owners (fp32, or bf16x2 with RED_BF16). MODE 2: A gathered by copy CTAs (each remote block
+// crosses NVLink once), local bf16 output.
+template <int BN, bool B_MN, int MODE, bool RED_BF16>
 __global__ void __launch_bounds__(192, 1)
 gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUtensorMap tmB,
-                 __nv_bfloat16* __restrict__ Cloc, const __grid_constant__ OutPtrs outs, int M, int N, int K, int ldc, int rows_per_rank,
-                 int my_rank, int P, int* err) {
+                 __nv_bfloat16* __restrict__ Cloc, const __grid_constant__ OutPtrs outs, const __grid_constant__ GatherArgs ga,
+                 int M, int N, int K, int ldc, int rows_per_rank, int my_rank, int P, int* err) {
   using Cfg = GcCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -81,10 +110,50 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
   const int num_kb = (K + GC_BK - 1) / GC_BK;
   const int blocks_per_rank = rows_per_rank / GC_BM;
   // gather: start with the local rows; reduce: start with the next rank's rows (remote first)
-  const int first_owner = MODE == 0 ? my_rank : (my_rank + 1) % P;
+  const int first_owner = MODE == 1 ? (my_rank + 1) % P : my_rank;
+  const int n_copy = MODE == 2 ? ga.n_copy : 0;
+  const int n_compute = gridDim.x - n_copy;
+
+  if (MODE == 2 && (int)blockIdx.x < n_copy) {
+    // ------------------------------------------------ copy CTA: remote row blocks -> local buffer, once
+    const int remote_blocks = m_blocks - blocks_per_rank;
+    const int vec_per_row = K >> 3;  // 8 bf16 per 16-byte vector
+    for (int i = blockIdx.x; i < remote_blocks; i += n_copy) {
+      // i-th remote block in the order the compute CTAs will want them
+      const int mb = ((my_rank + 1) * blocks_per_rank + i) % m_blocks;
+      const int m0 = mb * GC_BM;
+      const int owner = m0 / rows_per_rank;
+      const uint4* src = reinterpret_cast<const uint4*>(ga.peer_a[owner] + (size_t)(m0 - owner * rows_per_rank) * ga.lda);
+      uint4* dst = reinterpret_cast<uint4*>(ga.gathered + (size_t)m0 * K);
+      const int rows = min(GC_BM, M - m0);
+      const int total = rows * vec_per_row;
+      const int src_ld = ga.lda >> 3;
+      for (int v = threadIdx.x; v < total; v += 4 * blockDim.x) {
+        uint4 t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int w = v + u * blockDim.x;
+          if (w < total) {
+            const int r = w / vec_per_row, c = w - r * vec_per_row;
+            t[u] = src[(size_t)r * src_ld + c];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int w = v + u * blockDim.x;
+          if (w < total) dst[w] = t[u];
+        }
+      }
+      __threadfence();
+      fence_proxy_async_global();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_gpu(ga.flags + mb, ga.epoch);
+    }
+    return;  // copy CTAs own no TMEM and no barriers
+  }
 
   if (threadIdx.x == 0) {
-    for (int r = 0; r < (MODE == 0 ? P : 1); ++r) prefetch_tmap(&tmA.m[r]);
+    for (int r = 0; r < (MODE == 0 ? P : (MODE == 2 ? 2 : 1)); ++r) prefetch_tmap(&tmA.m[r]);
     prefetch_tmap(&tmB);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -112,12 +181,29 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       int issued = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x - n_copy; tile < num_tiles && ok; tile += n_compute) {
         int mb, nb;
         gc_tile(tile, m_blocks, n_blocks, blocks_per_rank, first_owner, P, mb, nb);
         const int m0 = mb * GC_BM, n0 = nb * BN;
-        const int owner = MODE == 0 ? m0 / rows_per_rank : 0;
-        const int a_row = MODE == 0 ? m0 - owner * rows_per_rank : m0;
+        int owner = 0, a_row = m0;
+        if (MODE == 0) {
+          owner = m0 / rows_per_rank;
+          a_row = m0 - owner * rows_per_rank;
+        } else if (MODE == 2) {
+          if (m0 / rows_per_rank == my_rank) {
+            owner = 0;                       // map 0: this rank's own block
+            a_row = m0 - my_rank * rows_per_rank;
+          } else {
+            owner = 1;                       // map 1: the gathered buffer, filled by the copy CTAs
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(ga.flags + mb) != ga.epoch) {
+              if (clock64() - t0 > WAIT_LIMIT_CYCLES) { set_error(err, ERR_WAIT_PEER_FLAG); ok = false; break; }
+              __nanosleep(64);
+            }
+            if (!ok) break;
+            fence_proxy_async_global();
+          }
+        }
         const CUtensorMap* ta = &tmA.m[owner];
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, err, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -151,7 +237,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x - n_copy; tile < num_tiles && ok; tile += n_compute, ++local) {
         const int buf = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1);
         if (!mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u, err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
@@ -181,7 +267,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
     const int row_in_tile = q * 32 + lane;
     bool ok = true;
     int local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x - n_copy; tile < num_tiles && ok; tile += n_compute, ++local) {
       int mb, nb;
       gc_tile(tile, m_blocks, n_blocks, blocks_per_rank, first_owner, P, mb, nb);
       const int m0 = mb * GC_BM, n0 = nb * BN;
@@ -192,9 +278,12 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
       const int row = m0 + row_in_tile;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       float* red_row = nullptr;
+      __nv_bfloat16* red_row_h = nullptr;
       if (MODE == 1 && row < M) {
         const int owner = row / rows_per_rank;
-        red_row = outs.p[owner] + (size_t)(row - owner * rows_per_rank) * ldc;
+        const size_t off = (size_t)(row - owner * rows_per_rank) * ldc;
+        if (RED_BF16) red_row_h = reinterpret_cast<__nv_bfloat16*>(outs.p[owner]) + off;
+        else red_row = reinterpret_cast<float*>(outs.p[owner]) + off;
       }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -204,7 +293,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
         const int col = n0 + c * 32;
         if (row < M && col < N) {
           const bool full = (col + 32 <= N);
-          if (MODE == 0) {
+          if (MODE != 1) {
             __nv_bfloat16* C = Cloc + (size_t)row * ldc + col;
             if (full) {
               uint4* C4 = reinterpret_cast<uint4*>(C);
@@ -217,6 +306,30 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
             } else {
               for (int j = 0; j < 32; ++j)
                 if (col + j < N) C[j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          } else if (RED_BF16) {
+            __nv_bfloat16* dst = red_row_h + col;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst + 8 * j),
+                             "r"(pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]))),
+                             "r"(pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]))),
+                             "r"(pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]))),
+                             "r"(pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])))
+                             : "memory");
+              }
+            } else {
+              for (int j = 0; j + 1 < 32; j += 2) {
+                if (col + j + 1 < N) {
+                  asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + j),
+                               "r"(pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1])))
+                               : "memory");
+                } else if (col + j < N) {
+                  asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + j), "r"(pack_bf16(__uint_as_float(r[j]), 0.f))
+                               : "memory");
+                }
+              }
             }
           } else {
             float* dst = red_row + col;
@@ -249,17 +362,34 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
   }
 }
 
-template <int BN, bool B_MN, int MODE>
-static int launch_gc(void* const* a_ptrs, const void* B, void* C, float* const* out_ptrs, int M, int N, int K, int lda, int ldb,
-                     int ldc, int rows_per_rank, int my_rank, int P, cudaStream_t stream) {
+template <int BN, bool B_MN, int MODE, bool RED_BF16>
+static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* out_ptrs, int M, int N, int K, int lda, int ldb,
+                     int ldc, int rows_per_rank, int my_rank, int P, void* gathered, int* flags, int epoch, cudaStream_t stream) {
   using Cfg = GcCfg<BN>;
   TmapArray ta;
+  GatherArgs ga = {};
   int rc;
-  const int nA = MODE == 0 ? P : 1;
-  const uint64_t a_rows = MODE == 0 ? (uint64_t)rows_per_rank : (uint64_t)M;
-  for (int r = 0; r < nA; ++r) {
-    rc = ab2host::encode_tmap_2d(&ta.m[r], a_ptrs[r], 2, (uint64_t)K, a_rows, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
+  int nA = 1;
+  if (MODE == 0) {
+    nA = P;
+    for (int r = 0; r < P; ++r) {
+      rc = ab2host::encode_tmap_2d(&ta.m[r], a_ptrs[r], 2, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
+      if (rc) return 100 + rc;
+    }
+  } else if (MODE == 1) {
+    rc = ab2host::encode_tmap_2d(&ta.m[0], a_ptrs[0], 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
     if (rc) return 100 + rc;
+  } else {
+    nA = 2;
+    rc = ab2host::encode_tmap_2d(&ta.m[0], a_ptrs[my_rank], 2, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
+    if (rc) return 100 + rc;
+    rc = ab2host::encode_tmap_2d(&ta.m[1], gathered, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, GC_BK, GC_BM, true, 0);
+    if (rc) return 110 + rc;
+    for (int r = 0; r < GC_MAX_PEERS; ++r) ga.peer_a[r] = r < P ? reinterpret_cast<const __nv_bfloat16*>(a_ptrs[r]) : nullptr;
+    ga.gathered = reinterpret_cast<__nv_bfloat16*>(gathered);
+    ga.flags = flags;
+    ga.epoch = epoch;
+    ga.lda = lda;
   }
   for (int r = nA; r < GC_MAX_PEERS; ++r) ta.m[r] = ta.m[0];
   CUtensorMap tmB;
@@ -270,7 +400,7 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, float* const* 
   if (rc) return 200 + rc;
   OutPtrs op;
   for (int r = 0; r < GC_MAX_PEERS; ++r) op.p[r] = (MODE == 1 && r < P) ? out_ptrs[r] : nullptr;
-  auto kern = gemm_comm_kernel<BN, B_MN, MODE>;
+  auto kern = gemm_comm_kernel<BN, B_MN, MODE, RED_BF16>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 300;
@@ -283,23 +413,30 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, float* const* 
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int tiles = ((M + GC_BM - 1) / GC_BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < num_sms ? tiles : num_sms;
+  int grid = tiles < num_sms ? tiles : num_sms;
+  if (MODE == 2) {
+    // copy CTAs and compute CTAs must all be resident at once: the compute side waits on flags
+    // that the copy side sets
+    ga.n_copy = P > 1 ? (num_sms >= 64 ? 12 : 2) : 0;
+    grid = num_sms;
+    if (tiles + ga.n_copy < grid) grid = tiles + ga.n_copy;
+  }
   int* err = ab2host::error_flag();
   if (!err) return 301;
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(ta, tmB, reinterpret_cast<__nv_bfloat16*>(C), op, M, N, K, ldc, rows_per_rank,
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(ta, tmB, reinterpret_cast<__nv_bfloat16*>(C), op, ga, M, N, K, ldc, rows_per_rank,
                                                my_rank, P, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 302;
 }
 
-template <int MODE>
-static int dispatch_gc(int bn, int b_mn, void* const* a_ptrs, const void* B, void* C, float* const* out_ptrs, int M, int N, int K,
-                       int lda, int ldb, int ldc, int rpr, int me, int P, cudaStream_t s) {
+template <int MODE, bool RED_BF16>
+static int dispatch_gc(int bn, int b_mn, void* const* a_ptrs, const void* B, void* C, void* const* out_ptrs, int M, int N, int K,
+                       int lda, int ldb, int ldc, int rpr, int me, int P, void* gathered, int* flags, int epoch, cudaStream_t s) {
   if (bn == 256) {
-    return b_mn ? launch_gc<256, true, MODE>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, s)
-                : launch_gc<256, false, MODE>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, s);
+    return b_mn ? launch_gc<256, true, MODE, RED_BF16>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, gathered, flags, epoch, s)
+                : launch_gc<256, false, MODE, RED_BF16>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, gathered, flags, epoch, s);
   }
-  return b_mn ? launch_gc<128, true, MODE>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, s)
-              : launch_gc<128, false, MODE>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, s);
+  return b_mn ? launch_gc<128, true, MODE, RED_BF16>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, gathered, flags, epoch, s)
+              : launch_gc<128, false, MODE, RED_BF16>(a_ptrs, B, C, out_ptrs, M, N, K, lda, ldb, ldc, rpr, me, P, gathered, flags, epoch, s);
 }
 
 }  // namespace ab2
@@ -309,31 +446,44 @@ extern "C" {
 // C[M, N] (bf16, local) = concat_r(A_r)[M, K] * op(B). a_ptrs[r]: rank r's [M/P, K] block (lda
 // elements per row) as mapped into this process; rows_per_rank = M / P must be a multiple of
 // 128. b_mn = 0: B is [N, K]; 1: B is [K, N].
+// gathered == null: remote tiles are loaded by TMA straight from the owner's memory (every
+// output-tile column re-reads them over NVLink). gathered != null (local [M, K] bf16) with
+// flags (int32 per 128-row block) and a per-call epoch that differs from every earlier one:
+// copy CTAs bring each remote block over once and the tiles read the local copy.
 int ab2_allgather_gemm(void* const* a_ptrs, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int b_mn,
-                       int my_rank, int world, void* stream) {
+                       int my_rank, int world, void* gathered, void* flags, int epoch, void* stream) {
   using namespace ab2;
   if (world < 1 || world > GC_MAX_PEERS) return 10;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M % world || (M / world) % GC_BM) return 11;
-  if ((lda & 7) || (ldb & 7) || (ldc & 7)) return 12;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (K & 7)) return 12;
   const int bn = (N % 256 == 0 && ((M + 127) / 128) * (N / 256) >= 120) ? 256 : 128;
-  return dispatch_gc<0>(bn, b_mn, a_ptrs, B, C, nullptr, M, N, K, lda, ldb, ldc, M / world, my_rank, world,
-                        reinterpret_cast<cudaStream_t>(stream));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (gathered != nullptr) {
+    if (!flags) return 13;
+    return dispatch_gc<2, false>(bn, b_mn, a_ptrs, B, C, nullptr, M, N, K, lda, ldb, ldc, M / world, my_rank, world, gathered,
+                                 reinterpret_cast<int*>(flags), epoch, s);
+  }
+  return dispatch_gc<0, false>(bn, b_mn, a_ptrs, B, C, nullptr, M, N, K, lda, ldb, ldc, M / world, my_rank, world, nullptr, nullptr, 0, s);
 }
 
-// out_r[M/P, N] (fp32, rank r's buffer as mapped here, ldc elements per row) += rows r of A * op(B).
-// All buffers must be zero (or hold the value to add to) and visible before any rank launches;
-// results are complete after a barrier that follows every rank's kernel.
+// out_r[M/P, N] (rank r's buffer as mapped here, ldc elements per row) += rows r of A * op(B).
+// out_bf16 = 0: fp32 buffers and fp32 reductions; 1: bf16 buffers, bf16x2 reductions (half the
+// NVLink bytes; every add rounds to bf16, meant for small groups). All buffers must be zero (or
+// hold the value to add to) and visible before any rank launches; results are complete after
+// a barrier that follows every rank's kernel.
 int ab2_gemm_reduce_scatter(const void* A, const void* B, void* const* out_ptrs, int M, int N, int K, int lda, int ldb, int ldc,
-                            int b_mn, int my_rank, int world, void* stream) {
+                            int b_mn, int my_rank, int world, int out_bf16, void* stream) {
   using namespace ab2;
   if (world < 1 || world > GC_MAX_PEERS) return 10;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M % world || (M / world) % GC_BM) return 11;
-  if ((lda & 7) || (ldb & 7) || (ldc & 3)) return 12;
+  if ((lda & 7) || (ldb & 7) || (ldc & (out_bf16 ? 7 : 3))) return 12;
   const int bn = (N % 256 == 0 && ((M + 127) / 128) * (N / 256) >= 120) ? 256 : 128;
   void* a1[1] = {const_cast<void*>(A)};
-  return dispatch_gc<1>(bn, b_mn, a1, B, nullptr, reinterpret_cast<float* const*>(out_ptrs), M, N, K, lda, ldb, ldc, M / world,
-                        my_rank, world, reinterpret_cast<cudaStream_t>(stream));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (out_bf16)
+    return dispatch_gc<1, true>(bn, b_mn, a1, B, nullptr, out_ptrs, M, N, K, lda, ldb, ldc, M / world, my_rank, world, nullptr, nullptr, 0, s);
+  return dispatch_gc<1, false>(bn, b_mn, a1, B, nullptr, out_ptrs, M, N, K, lda, ldb, ldc, M / world, my_rank, world, nullptr, nullptr, 0, s);
 }
 }

@@ -27,8 +27,9 @@ from ..ops import functional as OF
 from ..ops import lib as oplib
 from .symm import SymmComm, ptr_array, symm_empty
 
-oplib.declare("ab2_allgather_gemm", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 9 + [ctypes.c_void_p])
-oplib.declare("ab2_gemm_reduce_scatter", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 9 + [ctypes.c_void_p])
+oplib.declare("ab2_allgather_gemm", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 9 +
+              [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p])
+oplib.declare("ab2_gemm_reduce_scatter", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 10 + [ctypes.c_void_p])
 
 
 class FusedTPLinear:
@@ -42,14 +43,21 @@ class FusedTPLinear:
         # staging: this rank's activation rows (bf16) and its reduce-scatter target (fp32)
         self.x_buf, self.x_hdl = symm_empty(max_rows_per_rank * max_k, torch.bfloat16, device, self.group)
         self.o_buf, self.o_hdl = symm_empty(max_rows_per_rank * max_n, torch.float32, device, self.group)
+        self.oh_buf, self.oh_hdl = symm_empty(max_rows_per_rank * max_n, torch.bfloat16, device, self.group)
         self.x_ptrs = list(self.x_hdl.buffer_ptrs)
         self.o_ptrs = list(self.o_hdl.buffer_ptrs)
+        self.oh_ptrs = list(self.oh_hdl.buffer_ptrs)
         self.max_rows, self.max_k, self.max_n = max_rows_per_rank, max_k, max_n
+        # copy-once gather: local landing buffer for the peers' rows + one ready flag per 128 rows
+        self.gathered = torch.empty(max_rows_per_rank * self.world * max_k, dtype=torch.bfloat16, device=device)
+        self.flags = torch.zeros(max_rows_per_rank * self.world // 128 + 1, dtype=torch.int32, device=device)
+        self._epoch = 0
 
     # ------------------------------------------------------------------ fused
-    def allgather_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False) -> torch.Tensor:
+    def allgather_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, copy_once: bool = True) -> torch.Tensor:
         """``concat_ranks(x_local) @ w^T`` (``b_mn``: ``@ w``). x_local: [T/P, K] bf16 with T/P a
-        multiple of 128."""
+        multiple of 128. ``copy_once``: remote rows are brought over NVLink once by copy CTAs of
+        the same kernel (default); otherwise every output tile loads them from the owner."""
         rows, K = x_local.shape
         N = w.shape[1] if b_mn else w.shape[0]
         assert rows % 128 == 0 and rows <= self.max_rows and K <= self.max_k and x_local.dtype == torch.bfloat16
@@ -58,24 +66,31 @@ class FusedTPLinear:
         self.comm.barrier(0)                               # every rank's rows are in place
         M = rows * self.world
         y = torch.empty(M, N, device=self.device, dtype=torch.bfloat16)
+        self._epoch += 1
         rc = oplib.get_lib().ab2_allgather_gemm(ptr_array(self.x_ptrs), w.data_ptr(), y.data_ptr(), M, N, K, K, w.stride(0),
-                                                y.stride(0), int(b_mn), self.rank, self.world, oplib.stream_ptr())
+                                                y.stride(0), int(b_mn), self.rank, self.world,
+                                                self.gathered.data_ptr() if copy_once else None,
+                                                self.flags.data_ptr() if copy_once else None, self._epoch, oplib.stream_ptr())
         oplib.check(rc, "ab2_allgather_gemm")
         self.comm.barrier(1)                               # peers finished reading before the stage is reused
         return y
 
-    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, b_mn: bool = False, out_dtype=torch.bfloat16) -> torch.Tensor:
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, b_mn: bool = False, out_dtype=torch.bfloat16,
+                            reduce_dtype=torch.float32) -> torch.Tensor:
         """This rank's rows of ``sum_ranks(x_r @ w_r^T)``. x: [T, K_local] bf16, T/P a multiple
-        of 128. Returns [T/P, N]."""
+        of 128. Returns [T/P, N]. ``reduce_dtype=torch.bfloat16`` halves the NVLink bytes (every
+        add rounds to bf16)."""
         M, K = x.shape
         N = w.shape[1] if b_mn else w.shape[0]
         rows = M // self.world
         assert M % self.world == 0 and rows % 128 == 0 and rows <= self.max_rows and N <= self.max_n
-        out = self.o_buf[: rows * N].view(rows, N)
+        half = reduce_dtype == torch.bfloat16
+        out = (self.oh_buf if half else self.o_buf)[: rows * N].view(rows, N)
         out.zero_()
         self.comm.barrier(2)                               # every target is zeroed
-        rc = oplib.get_lib().ab2_gemm_reduce_scatter(x.data_ptr(), w.data_ptr(), ptr_array(self.o_ptrs), M, N, K, x.stride(0),
-                                                     w.stride(0), N, int(b_mn), self.rank, self.world, oplib.stream_ptr())
+        rc = oplib.get_lib().ab2_gemm_reduce_scatter(x.data_ptr(), w.data_ptr(), ptr_array(self.oh_ptrs if half else self.o_ptrs), M, N,
+                                                     K, x.stride(0), w.stride(0), N, int(b_mn), self.rank, self.world, int(half),
+                                                     oplib.stream_ptr())
         oplib.check(rc, "ab2_gemm_reduce_scatter")
         self.comm.barrier(3)                               # every rank's reductions have landed
         return out.to(out_dtype)
@@ -85,6 +100,11 @@ class FusedTPLinear:
         full = torch.empty(x_local.shape[0] * self.world, x_local.shape[1], device=self.device, dtype=x_local.dtype)
         dist.all_gather_into_tensor(full, x_local.contiguous(), group=self.group)
         return OF.gemm(full, w, b_mn=b_mn)
+
+    def baseline_gemm_only(self, x_local, w):
+        """The local product alone (no communication): the floor for the fused forms."""
+        full = self.gathered[: x_local.shape[0] * self.world * x_local.shape[1]].view(-1, x_local.shape[1])
+        return OF.gemm(full, w)
 
     def baseline_gemm_reduce_scatter(self, x, w, b_mn: bool = False, out_dtype=torch.bfloat16):
         part = OF.gemm(x, w, b_mn=b_mn, epi=OF.EPI_F32)

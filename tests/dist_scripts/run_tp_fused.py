@@ -53,9 +53,10 @@ def main():
     x_full = torch.cat(xs, 0)
     for b_mn in (False, True):
         w = w_col.t().contiguous() if b_mn else w_col
-        y = tp.allgather_gemm(x_loc, w, b_mn=b_mn)
         ref = x_full.float() @ w_col.float().t()
-        assert rel(y, ref) < 1e-2, ("ag_gemm", b_mn, rel(y, ref))
+        for copy_once in (True, False, True):
+            y = tp.allgather_gemm(x_loc, w, b_mn=b_mn, copy_once=copy_once)
+            assert rel(y, ref) < 1e-2, ("ag_gemm", b_mn, copy_once, rel(y, ref))
         assert rel(tp.baseline_allgather_gemm(x_loc, w, b_mn=b_mn), ref) < 1e-2
     # ---- GEMM -> reduce-scatter (row parallel forward): full rows, K split over ranks
     x_row = torch.randn(rows * world, K // world, device=dev, generator=g).bfloat16()
@@ -68,15 +69,20 @@ def main():
         for _ in range(2):                                  # twice: the target buffer is reused
             o = tp.gemm_reduce_scatter(x_row, w, b_mn=b_mn, out_dtype=torch.float32)
             assert rel(o, mine) < 1e-2, ("gemm_rs", b_mn, rel(o, mine))
+            o = tp.gemm_reduce_scatter(x_row, w, b_mn=b_mn, out_dtype=torch.float32, reduce_dtype=torch.bfloat16)
+            assert rel(o, mine) < 2e-2, ("gemm_rs_bf16", b_mn, rel(o, mine))
         assert rel(tp.baseline_gemm_reduce_scatter(x_row, w, b_mn=b_mn, out_dtype=torch.float32), mine) < 1e-2
     torch.cuda.synchronize()
     assert oplib.kernel_error() == 0, oplib.kernel_error()
     if big:
         res = {
             "shape": {"rows_per_rank": rows, "K": K, "N": N, "world": world},
-            "allgather_gemm_ms": timed(lambda: tp.allgather_gemm(x_loc, w_col)),
+            "allgather_gemm_copy_once_ms": timed(lambda: tp.allgather_gemm(x_loc, w_col)),
+            "allgather_gemm_remote_tma_ms": timed(lambda: tp.allgather_gemm(x_loc, w_col, copy_once=False)),
             "nccl_allgather_then_gemm_ms": timed(lambda: tp.baseline_allgather_gemm(x_loc, w_col)),
             "gemm_reduce_scatter_ms": timed(lambda: tp.gemm_reduce_scatter(x_row, w_row)),
+            "gemm_reduce_scatter_bf16_ms": timed(lambda: tp.gemm_reduce_scatter(x_row, w_row, reduce_dtype=torch.bfloat16)),
+            "gemm_only_ms": timed(lambda: tp.baseline_gemm_only(x_loc, w_col)),
             "gemm_then_nccl_reduce_scatter_ms": timed(lambda: tp.baseline_gemm_reduce_scatter(x_row, w_row)),
         }
         if rank == 0:
