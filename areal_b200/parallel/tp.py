@@ -173,3 +173,91 @@ def load_sharded_from_full(model, cfg: ModelConfig, full_state: dict, tp: int, r
         for n, p in model.named_parameters():
             p.copy_(shard_tensor(cfg, n, full_state[n], tp, rank).to(p.dtype))
     return model
+
+
+# --------------------------------------------------------------------------- sequence-parallel TP
+# Megatron-style sequence parallelism: between blocks, activations are sharded by rows
+# ([T/P, H] per rank). A column-parallel product starts with an all-gather of the rows, a
+# row-parallel product ends with a reduce-scatter; forward and input-gradient of both are
+# exactly the two fused primitives of ``parallel/tp_fused.py`` (weight gradients gather once
+# more with the library collective).
+def _ag_rows(x, group):
+    P = dist.get_world_size(group)
+    out = x.new_empty((x.shape[0] * P,) + tuple(x.shape[1:]))
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+    else:
+        dist.all_gather(list(out.chunk(P, 0)), x.contiguous(), group=group)
+    return out
+
+
+def _rs_rows(x, group):
+    P, r = dist.get_world_size(group), dist.get_rank(group)
+    if dist.get_backend(group) == "nccl":
+        out = x.new_empty((x.shape[0] // P,) + tuple(x.shape[1:]))
+        dist.reduce_scatter_tensor(out, x.contiguous(), group=group)
+        return out
+    x = x.contiguous().clone()
+    dist.all_reduce(x, group=group)
+    return x.chunk(P, 0)[r].clone()
+
+
+class _ColumnParallelSP(torch.autograd.Function):
+    """``y[T, N/P] = gather_rows(x[T/P, K]) @ W[N/P, K]^T``."""
+
+    @staticmethod
+    def forward(ctx, x, w, group, fused):
+        ctx.group, ctx.fused = group, fused
+        ctx.save_for_backward(x, w)
+        if fused is not None and x.is_cuda:
+            return fused.allgather_gemm(x, w)
+        return _ag_rows(x, group) @ w.t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        g, fused = ctx.group, ctx.fused
+        dy = dy.contiguous()
+        if fused is not None and dy.is_cuda:
+            dx = fused.gemm_reduce_scatter(dy, w, b_mn=True)           # rows of dy @ W that this rank owns
+        else:
+            dx = _rs_rows(dy @ w, g)
+        dw = dy.t() @ _ag_rows(x, g) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None
+
+
+class _RowParallelSP(torch.autograd.Function):
+    """``y[T/P, N] = reduce_scatter_rows(x[T, K/P] @ W[N, K/P]^T)``."""
+
+    @staticmethod
+    def forward(ctx, x, w, group, fused):
+        ctx.group, ctx.fused = group, fused
+        ctx.save_for_backward(x, w)
+        if fused is not None and x.is_cuda:
+            return fused.gemm_reduce_scatter(x, w)
+        return _rs_rows(x @ w.t(), group)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        g, fused = ctx.group, ctx.fused
+        dy = dy.contiguous()
+        if fused is not None and dy.is_cuda:
+            dx = fused.allgather_gemm(dy, w, b_mn=True)                # gather_rows(dy) @ W
+            dy_full = None
+        else:
+            dy_full = _ag_rows(dy, g)
+            dx = dy_full @ w
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dy_full = dy_full if dy_full is not None else _ag_rows(dy, g)
+            dw = dy_full.t() @ x
+        return dx, dw, None, None
+
+
+def column_parallel_sp(x_rows: torch.Tensor, w_local: torch.Tensor, group, fused=None) -> torch.Tensor:
+    return _ColumnParallelSP.apply(x_rows, w_local, group, fused)
+
+
+def row_parallel_sp(x_full: torch.Tensor, w_local: torch.Tensor, group, fused=None) -> torch.Tensor:
+    return _RowParallelSP.apply(x_full, w_local, group, fused)

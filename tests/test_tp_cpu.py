@@ -58,3 +58,12 @@ def test_vocab_parallel_lm_head_matches_full_softmax():
                        capture_output=True, text=True, timeout=200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("VP_OK") == 2
+
+
+def test_sequence_parallel_tp_linear_pair_gloo():
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29879", os.path.join(ROOT, "tests", "dist_scripts", "run_tp_sp.py")], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=200)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_SP_OK") == 2
