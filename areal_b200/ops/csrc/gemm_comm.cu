@@ -89,7 +89,7 @@ __device__ __forceinline__ void gc_tile(int tile, int m_blocks, int n_blocks, in
 template <int BN, bool B_MN, int MODE, bool RED_BF16>
 __global__ void __launch_bounds__(192, 1)
 gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUtensorMap tmB,
-                 __nv_bfloat16* __restrict__ Cloc, const __grid_constant__ OutPtrs outs, const __grid_constant__ GatherArgs ga,
+                 const __grid_constant__ CUtensorMap tmG, __nv_bfloat16* __restrict__ Cloc, const __grid_constant__ OutPtrs outs, const __grid_constant__ GatherArgs ga,
                  int M, int N, int K, int ldc, int rows_per_rank, int my_rank, int P, int* err) {
   using Cfg = GcCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -115,45 +115,65 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
   const int n_compute = gridDim.x - n_copy;
 
   if (MODE == 2 && (int)blockIdx.x < n_copy) {
-    // ------------------------------------------------ copy CTA: remote row blocks -> local buffer, once
-    const int remote_blocks = m_blocks - blocks_per_rank;
-    const int vec_per_row = K >> 3;  // 8 bf16 per 16-byte vector
-    for (int i = blockIdx.x; i < remote_blocks; i += n_copy) {
-      // i-th remote block in the order the compute CTAs will want them
-      const int mb = ((my_rank + 1) * blocks_per_rank + i) % m_blocks;
-      const int m0 = mb * GC_BM;
-      const int owner = m0 / rows_per_rank;
-      const uint4* src = reinterpret_cast<const uint4*>(ga.peer_a[owner] + (size_t)(m0 - owner * rows_per_rank) * ga.lda);
-      uint4* dst = reinterpret_cast<uint4*>(ga.gathered + (size_t)m0 * K);
-      const int rows = min(GC_BM, M - m0);
-      const int total = rows * vec_per_row;
-      const int src_ld = ga.lda >> 3;
-      for (int v = threadIdx.x; v < total; v += 4 * blockDim.x) {
-        uint4 t[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int w = v + u * blockDim.x;
-          if (w < total) {
-            const int r = w / vec_per_row, c = w - r * vec_per_row;
-            t[u] = src[(size_t)r * src_ld + c];
+    // ------------------------------------------------ copy CTA: remote row blocks -> local buffer, once.
+    // One elected thread drives a TMA pipeline: 128x64 boxes are loaded from the owner's
+    // memory into shared memory (two groups of GROUP stages, so one group's loads are in
+    // flight while the other group's stores drain) and stored to the local gathered buffer.
+    constexpr int GROUP = 6;
+    constexpr int BOX_BYTES = GC_BM * GC_BK * 2;
+    if (threadIdx.x == 0) {
+      const uint32_t gbar0 = smem_base + 2 * GROUP * BOX_BYTES;  // two 8-byte barriers after the boxes
+      mbar_init(gbar0, 1);
+      mbar_init(gbar0 + 8, 1);
+      fence_mbar_init();
+      for (int r = 0; r < P; ++r) prefetch_tmap(&tmA.m[r]);
+      prefetch_tmap(&tmG);
+      const int remote_blocks = m_blocks - blocks_per_rank;
+      bool ok = true;
+      uint32_t ph[2] = {0u, 0u};
+      for (int i = blockIdx.x; i < remote_blocks && ok; i += n_copy) {
+        // i-th remote block in the order the compute CTAs will want them
+        const int mb = ((my_rank + 1) * blocks_per_rank + i) % m_blocks;
+        const int m0 = mb * GC_BM;
+        const int owner = m0 / rows_per_rank;
+        const int src_row = m0 - owner * rows_per_rank;
+        const CUtensorMap* ts = &tmA.m[owner];
+        const int n_batches = (num_kb + GROUP - 1) / GROUP;
+        auto issue_loads = [&](int batch) {
+          const int g = batch & 1;
+          const int kb_lo = batch * GROUP;
+          const int n = min(GROUP, num_kb - kb_lo);
+          mbar_expect_tx(gbar0 + 8 * g, n * BOX_BYTES);
+          for (int j = 0; j < n; ++j)
+            tma_load_2d(smem_base + (g * GROUP + j) * BOX_BYTES, ts, gbar0 + 8 * g, (kb_lo + j) * GC_BK, src_row);
+        };
+        issue_loads(0);
+        if (n_batches > 1) issue_loads(1);
+        for (int batch = 0; batch < n_batches; ++batch) {
+          const int g = batch & 1;
+          if (!mbar_wait(gbar0 + 8 * g, ph[g], err, ERR_WAIT_FULL)) { ok = false; break; }
+          ph[g] ^= 1u;
+          const int kb_lo = batch * GROUP;
+          const int n = min(GROUP, num_kb - kb_lo);
+          for (int j = 0; j < n; ++j) tma_store_2d(&tmG, smem_base + (g * GROUP + j) * BOX_BYTES, (kb_lo + j) * GC_BK, m0);
+          tma_store_commit();
+          if (batch + 2 < n_batches) {
+            tma_store_wait_read<0>();  // this group's boxes have been read out: refill them
+            issue_loads(batch + 2);
           }
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int w = v + u * blockDim.x;
-          if (w < total) dst[w] = t[u];
-        }
+        tma_store_wait<0>();           // the whole block is in local memory
+        fence_proxy_async_global();
+        __threadfence();
+        if (ok) st_release_gpu(ga.flags + mb, ga.epoch);
       }
-      __threadfence();
-      fence_proxy_async_global();
-      __syncthreads();
-      if (threadIdx.x == 0) st_release_gpu(ga.flags + mb, ga.epoch);
     }
-    return;  // copy CTAs own no TMEM and no barriers
+    return;  // copy CTAs own no TMEM
   }
 
   if (threadIdx.x == 0) {
-    for (int r = 0; r < (MODE == 0 ? P : (MODE == 2 ? 2 : 1)); ++r) prefetch_tmap(&tmA.m[r]);
+    for (int r = 0; r < (MODE == 1 ? 1 : P); ++r) prefetch_tmap(&tmA.m[r]);
+    if (MODE == 2) prefetch_tmap(&tmG);
     prefetch_tmap(&tmB);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -191,10 +211,10 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
           a_row = m0 - owner * rows_per_rank;
         } else if (MODE == 2) {
           if (m0 / rows_per_rank == my_rank) {
-            owner = 0;                       // map 0: this rank's own block
+            owner = my_rank;                 // this rank's own block
             a_row = m0 - my_rank * rows_per_rank;
           } else {
-            owner = 1;                       // map 1: the gathered buffer, filled by the copy CTAs
+            owner = -1;                      // the gathered buffer, filled by the copy CTAs
             const long long t0 = clock64();
             while (ld_acquire_gpu(ga.flags + mb) != ga.epoch) {
               if (clock64() - t0 > WAIT_LIMIT_CYCLES) { set_error(err, ERR_WAIT_PEER_FLAG); ok = false; break; }
@@ -204,7 +224,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
             fence_proxy_async_global();
           }
         }
-        const CUtensorMap* ta = &tmA.m[owner];
+        const CUtensorMap* ta = owner < 0 ? &tmG : &tmA.m[owner];
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, err, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
@@ -367,6 +387,7 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
                      int ldc, int rows_per_rank, int my_rank, int P, void* gathered, int* flags, int epoch, cudaStream_t stream) {
   using Cfg = GcCfg<BN>;
   TmapArray ta;
+  CUtensorMap tmG;
   GatherArgs ga = {};
   int rc;
   int nA = 1;
@@ -380,10 +401,12 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
     rc = ab2host::encode_tmap_2d(&ta.m[0], a_ptrs[0], 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
     if (rc) return 100 + rc;
   } else {
-    nA = 2;
-    rc = ab2host::encode_tmap_2d(&ta.m[0], a_ptrs[my_rank], 2, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
-    if (rc) return 100 + rc;
-    rc = ab2host::encode_tmap_2d(&ta.m[1], gathered, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, GC_BK, GC_BM, true, 0);
+    nA = P;
+    for (int r = 0; r < P; ++r) {
+      rc = ab2host::encode_tmap_2d(&ta.m[r], a_ptrs[r], 2, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
+      if (rc) return 100 + rc;
+    }
+    rc = ab2host::encode_tmap_2d(&tmG, gathered, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, GC_BK, GC_BM, true, 0);
     if (rc) return 110 + rc;
     for (int r = 0; r < GC_MAX_PEERS; ++r) ga.peer_a[r] = r < P ? reinterpret_cast<const __nv_bfloat16*>(a_ptrs[r]) : nullptr;
     ga.gathered = reinterpret_cast<__nv_bfloat16*>(gathered);
@@ -392,6 +415,7 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
     ga.lda = lda;
   }
   for (int r = nA; r < GC_MAX_PEERS; ++r) ta.m[r] = ta.m[0];
+  if (MODE != 2) tmG = ta.m[0];
   CUtensorMap tmB;
   if (!B_MN)
     rc = ab2host::encode_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, GC_BK, BN, true, 0);
@@ -417,13 +441,13 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
   if (MODE == 2) {
     // copy CTAs and compute CTAs must all be resident at once: the compute side waits on flags
     // that the copy side sets
-    ga.n_copy = P > 1 ? (num_sms >= 64 ? 12 : 2) : 0;
+    ga.n_copy = P > 1 ? (num_sms >= 64 ? 8 : 2) : 0;
     grid = num_sms;
     if (tiles + ga.n_copy < grid) grid = tiles + ga.n_copy;
   }
   int* err = ab2host::error_flag();
   if (!err) return 301;
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(ta, tmB, reinterpret_cast<__nv_bfloat16*>(C), op, ga, M, N, K, ldc, rows_per_rank,
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(ta, tmB, tmG, reinterpret_cast<__nv_bfloat16*>(C), op, ga, M, N, K, ldc, rows_per_rank,
                                                my_rank, P, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 302;
 }
