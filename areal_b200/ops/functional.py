@@ -156,13 +156,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = Non
     if not x.is_cuda:
         y = F.linear(x, w)
         return y + resid if resid is not None else y
-    # The swap-AB split-K kernel wins over the general one only for few tokens against a large
-    # weight (measured on B200: <= 64 tokens and >= ~20M weight elements); elsewhere the
-    # general kernel's vectorised epilogue is faster.
-    if (x.dim() == 2 and x.shape[0] <= 64 and w.shape[0] * w.shape[1] >= 20_000_000 and w.shape[0] <= 65536
-            and not torch.is_grad_enabled() and x.stride(1) == 1 and (x.stride(0) & 7) == 0
-            and (resid is None or resid.is_contiguous())):
-        return gemm_skinny(x, w, resid)
+    # The swap-AB split-K kernel (gemm_skinny) is NOT routed here: in isolation (L2 flushed) it
+    # beats the general kernel for <= 64 tokens on three of the four decode shapes of an 8B
+    # model, but inside the decode CUDA graph the whole step came out slower (13.2 ms vs 10.1 ms
+    # per step at 64 sequences), so decode keeps the general kernel; callers can use
+    # gemm_skinny() explicitly.
     return _Linear.apply(x, w, resid, grad_buf)
 
 
