@@ -9,9 +9,10 @@
 //             sitting in the k region of dqkv  ->  dqkv q / k regions bf16 (un-rotated, norm
 //             backward applied), dw_q / dw_k accumulated in fp32.
 //
-// One warp per (token, head) row, every lane holds D / 32 contiguous elements, the rotate-half
-// partner lives in lane ^ 16. Rows are processed four at a time so that four independent
-// loads are in flight per warp. Weight gradients are reduced in registers, then across the
+// One warp per token at a time (its heads share the position, so cos / sin are fetched once per
+// token), one (token, head) row per step with every lane holding D / 32 contiguous elements,
+// the rotate-half partner lives in lane ^ 16. Rows are processed four at a time so that four
+// independent loads are in flight per warp. Weight gradients are reduced in registers, then across the
 // CTA in shared memory, and reach global memory as one atomic per column per CTA.
 //
 // Replaces the separate slice / RMSNorm / RoPE launches (and their backward slice-copies) of
@@ -52,6 +53,7 @@ __device__ __forceinline__ void load_f32_vec(const float* p, float* out) {
 }
 
 constexpr int QK_UNROLL = 4;
+constexpr int QK_UNROLL_BWD = 2;  // the backward keeps three vectors per row live: two rows keep it at 3+ CTAs per SM
 
 // D = 32 * VEC. wq / wk may be null (no norm: rotation only).
 template <int VEC>
@@ -65,9 +67,8 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   constexpr int HALF = D / 2;
   const int lane = threadIdx.x & 31;
   const int heads = nq + nkv;
-  const long long rows = (long long)T * heads;
-  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const int warp0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
   const int e0 = lane * VEC;               // first element of this lane
   const int f0 = e0 & (HALF - 1);          // frequency index of that element
   const bool upper = lane >= 16;
@@ -77,50 +78,50 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     load_bf16_vec<VEC>(wq + e0, wqv);
     load_bf16_vec<VEC>(wk + e0, wkv);
   }
-  for (long long r0 = warp0 * QK_UNROLL; r0 < rows; r0 += nwarps * QK_UNROLL) {
-    float x[QK_UNROLL][VEC];
-    int tok[QK_UNROLL], head[QK_UNROLL];
+  // One token per warp at a time: its heads share the position, so cos / sin are fetched once
+  // per token and the per-row work is a single independent load -> reduce -> store chain.
+  for (int tok = warp0; tok < T; tok += nwarps) {
+    const int p = pos[tok];
+    float c[VEC], s[VEC];
+    load_f32_vec<VEC>(cosb + (size_t)p * HALF + f0, c);
+    load_f32_vec<VEC>(sinb + (size_t)p * HALF + f0, s);
+    const __nv_bfloat16* src = qkv + (size_t)tok * qkv_stride + e0;
+    __nv_bfloat16* dst = qk + (size_t)tok * heads * D + e0;
+    for (int h0 = 0; h0 < heads; h0 += QK_UNROLL) {
+      float x[QK_UNROLL][VEC];
 #pragma unroll
-    for (int u = 0; u < QK_UNROLL; ++u) {
-      const long long r = r0 + u;
-      if (r < rows) {
-        tok[u] = (int)(r / heads);
-        head[u] = (int)(r - (long long)tok[u] * heads);
-        load_bf16_vec<VEC>(qkv + (size_t)tok[u] * qkv_stride + (size_t)head[u] * D + e0, x[u]);
-      }
-    }
+      for (int u = 0; u < QK_UNROLL; ++u)
+        if (h0 + u < heads) load_bf16_vec<VEC>(src + (size_t)(h0 + u) * D, x[u]);
 #pragma unroll
-    for (int u = 0; u < QK_UNROLL; ++u) {
-      const long long r = r0 + u;
-      if (r >= rows) break;
-      float y[VEC];
-      if (has_norm) {
-        float ss = 0.f;
+      for (int u = 0; u < QK_UNROLL; ++u) {
+        const int h = h0 + u;
+        if (h >= heads) break;
+        float y[VEC];
+        if (has_norm) {
+          float ss = 0.f;
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) ss += x[u][e] * x[u][e];
-        ss = warp_sum(ss);
-        const float rstd = rsqrtf(ss / (float)D + eps);
-        if (lane == 0) rstd_out[r] = rstd;
-        const float* w = head[u] < nq ? wqv : wkv;
+          for (int e = 0; e < VEC; ++e) ss += x[u][e] * x[u][e];
+          ss = warp_sum(ss);
+          const float rstd = rsqrtf(ss / (float)D + eps);
+          if (lane == 0) rstd_out[(size_t)tok * heads + h] = rstd;
+          const bool isq = h < nq;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            // the normalised value is rounded to bf16 like the unfused op's output
+            y[e] = __bfloat162float(__float2bfloat16(x[u][e] * rstd * (isq ? wqv[e] : wkv[e])));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y[e] = x[u][e];
+        }
+        float o[VEC];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          // the normalised value is rounded to bf16 like the unfused op's output
-          y[e] = __bfloat162float(__float2bfloat16(x[u][e] * rstd * w[e]));
+          const float partner = __shfl_xor_sync(0xffffffffu, y[e], 16);
+          o[e] = upper ? (y[e] * c[e] + partner * s[e]) : (y[e] * c[e] - partner * s[e]);
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) y[e] = x[u][e];
+        store_bf16_vec<VEC>(dst + (size_t)h * D, o);
       }
-      const int p = pos[tok[u]];
-      float c[VEC], s[VEC], o[VEC];
-      load_f32_vec<VEC>(cosb + (size_t)p * HALF + f0, c);
-      load_f32_vec<VEC>(sinb + (size_t)p * HALF + f0, s);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        const float partner = __shfl_xor_sync(0xffffffffu, y[e], 16);
-        o[e] = upper ? (y[e] * c[e] + partner * s[e]) : (y[e] * c[e] - partner * s[e]);
-      }
-      store_bf16_vec<VEC>(qk + (size_t)r * D + e0, o);
     }
   }
 }
@@ -141,9 +142,8 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
   const int heads = nq + nkv;
-  const long long rows = (long long)T * heads;
-  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + wib;
-  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const int warp0 = blockIdx.x * (blockDim.x >> 5) + wib;
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
   const int e0 = lane * VEC;
   const int f0 = e0 & (HALF - 1);
   const bool upper = lane >= 16;
@@ -155,56 +155,61 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     load_bf16_vec<VEC>(wq + e0, wqv);
     load_bf16_vec<VEC>(wk + e0, wkv);
   }
-  for (long long r0 = warp0 * QK_UNROLL; r0 < rows; r0 += nwarps * QK_UNROLL) {
-    float g[QK_UNROLL][VEC], x[QK_UNROLL][VEC];
-    int tok[QK_UNROLL], head[QK_UNROLL];
+  for (int tok = warp0; tok < T; tok += nwarps) {
+    const int p = pos[tok];
+    float c[VEC], s[VEC];
+    load_f32_vec<VEC>(cosb + (size_t)p * HALF + f0, c);
+    load_f32_vec<VEC>(sinb + (size_t)p * HALF + f0, s);
+    const __nv_bfloat16* xsrc = qkv + (size_t)tok * qkv_stride + e0;
+    __nv_bfloat16* gdst = dqkv + (size_t)tok * dqkv_stride + e0;
+    const float* qsrc = dq32 + (size_t)tok * nq * D + e0;
+    const float* rs = rstd_in + (size_t)tok * heads;
+    for (int h0 = 0; h0 < heads; h0 += QK_UNROLL_BWD) {
+      float g[QK_UNROLL_BWD][VEC], x[QK_UNROLL_BWD][VEC], rstd[QK_UNROLL_BWD];
 #pragma unroll
-    for (int u = 0; u < QK_UNROLL; ++u) {
-      const long long r = r0 + u;
-      if (r < rows) {
-        tok[u] = (int)(r / heads);
-        head[u] = (int)(r - (long long)tok[u] * heads);
-        if (head[u] < nq) load_f32_vec<VEC>(dq32 + ((size_t)tok[u] * nq + head[u]) * D + e0, g[u]);
-        else load_bf16_vec<VEC>(dqkv + (size_t)tok[u] * dqkv_stride + (size_t)head[u] * D + e0, g[u]);
-        if (has_norm) load_bf16_vec<VEC>(qkv + (size_t)tok[u] * qkv_stride + (size_t)head[u] * D + e0, x[u]);
+      for (int u = 0; u < QK_UNROLL_BWD; ++u) {
+        const int h = h0 + u;
+        if (h < heads) {
+          if (h < nq) load_f32_vec<VEC>(qsrc + (size_t)h * D, g[u]);
+          else load_bf16_vec<VEC>(gdst + (size_t)h * D, g[u]);
+          if (has_norm) {
+            load_bf16_vec<VEC>(xsrc + (size_t)h * D, x[u]);
+            rstd[u] = rs[h];
+          }
+        }
       }
-    }
 #pragma unroll
-    for (int u = 0; u < QK_UNROLL; ++u) {
-      const long long r = r0 + u;
-      if (r >= rows) break;
-      const int p = pos[tok[u]];
-      float c[VEC], s[VEC], gy[VEC];
-      load_f32_vec<VEC>(cosb + (size_t)p * HALF + f0, c);
-      load_f32_vec<VEC>(sinb + (size_t)p * HALF + f0, s);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        // transpose of the rotation: gy_lo = g_lo c + g_hi s ; gy_hi = g_hi c - g_lo s
-        const float partner = __shfl_xor_sync(0xffffffffu, g[u][e], 16);
-        gy[e] = upper ? (g[u][e] * c[e] - partner * s[e]) : (g[u][e] * c[e] + partner * s[e]);
-      }
-      float dx[VEC];
-      if (has_norm) {
-        const float rstd = rstd_in[r];
-        const bool isq = head[u] < nq;
-        const float* w = isq ? wqv : wkv;
-        float xh[VEC], gw[VEC];
-        float dot = 0.f;
+      for (int u = 0; u < QK_UNROLL_BWD; ++u) {
+        const int h = h0 + u;
+        if (h >= heads) break;
+        float gy[VEC];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          xh[e] = x[u][e] * rstd;
-          gw[e] = gy[e] * w[e];
-          dot += gw[e] * xh[e];
-          if (isq) aq[e] += gy[e] * xh[e]; else ak[e] += gy[e] * xh[e];
+          // transpose of the rotation: gy_lo = g_lo c + g_hi s ; gy_hi = g_hi c - g_lo s
+          const float partner = __shfl_xor_sync(0xffffffffu, g[u][e], 16);
+          gy[e] = upper ? (g[u][e] * c[e] - partner * s[e]) : (g[u][e] * c[e] + partner * s[e]);
         }
-        dot = warp_sum(dot) / (float)D;
+        float dx[VEC];
+        if (has_norm) {
+          const bool isq = h < nq;
+          float xh[VEC], gw[VEC];
+          float dot = 0.f;
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) dx[e] = rstd * (gw[e] - xh[e] * dot);
-      } else {
+          for (int e = 0; e < VEC; ++e) {
+            xh[e] = x[u][e] * rstd[u];
+            gw[e] = gy[e] * (isq ? wqv[e] : wkv[e]);
+            dot += gw[e] * xh[e];
+            if (isq) aq[e] += gy[e] * xh[e]; else ak[e] += gy[e] * xh[e];
+          }
+          dot = warp_sum(dot) / (float)D;
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) dx[e] = gy[e];
+          for (int e = 0; e < VEC; ++e) dx[e] = rstd[u] * (gw[e] - xh[e] * dot);
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) dx[e] = gy[e];
+        }
+        store_bf16_vec<VEC>(gdst + (size_t)h * D, dx);
       }
-      store_bf16_vec<VEC>(dqkv + (size_t)tok[u] * dqkv_stride + (size_t)head[u] * D + e0, dx);
     }
   }
   if (has_norm) {
@@ -238,8 +243,7 @@ int ab2_qknorm_rope_fwd(const void* qkv, const void* wq, const void* wk, const i
   if (D != 64 && D != 128) return 10;
   if ((wq == nullptr) != (wk == nullptr)) return 11;
   if (qkv_stride & 3) return 12;
-  const long long rows = (long long)T * (nq + nkv);
-  long long want = (rows + 8 * ab2::QK_UNROLL - 1) / (8 * ab2::QK_UNROLL);
+  const long long want = ((long long)T + 7) / 8;   // 8 warps per CTA, one token per warp step
   const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
   auto s = (cudaStream_t)stream;
   if (D == 128)
@@ -262,8 +266,7 @@ int ab2_qknorm_rope_bwd(const void* qkv, const void* wq, const void* wk, const i
   if ((wq == nullptr) != (wk == nullptr)) return 11;
   if ((qkv_stride | dqkv_stride) & 3) return 12;
   if (wq && (!dwq || !dwk || !rstd)) return 13;
-  const long long rows = (long long)T * (nq + nkv);
-  long long want = (rows + 8 * ab2::QK_UNROLL - 1) / (8 * ab2::QK_UNROLL);
+  const long long want = ((long long)T + 7) / 8;
   const int grid = (int)(want < 148 * 4 ? want : 148 * 4);
   auto s = (cudaStream_t)stream;
   if (D == 128)
