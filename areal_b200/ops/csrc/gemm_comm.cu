@@ -19,6 +19,17 @@
 //       tiles first and wait (bounded) on the flag of a remote block before its first TMA load.
 //       All CTAs are co-resident (grid <= number of SMs), so the wait cannot starve.
 //
+//   GEMM -> all-to-all by columns (MODE 3, Ulysses seq->heads after the QKV projection): the
+//       epilogue stores every tile straight into the buffer of the rank that owns those output
+//       columns (heads), at this rank's row offset: [T_local, N] -> [P * T_local, N / P] on
+//       every owner, plain 16-byte peer stores, no separate all-to-all.
+//
+//   all-to-all by columns -> GEMM (MODE 4, Ulysses heads->seq before the output projection):
+//       the K dimension of A is spread over the ranks ([P * T_local, K / P] each); copy CTAs
+//       pull this rank's rows of every remote panel once (TMA load/store pipeline) into a
+//       local [T_local, K] buffer, the GEMM starts with the local panel's k-blocks and waits
+//       (bounded) per (row block, owner) flag.
+//
 //   GEMM -> reduce-scatter with bf16 payload (RED_BF16): the epilogue packs to bf16x2 and uses
 //       red.global.add.noftz.v4.bf16x2, halving the NVLink bytes (for small groups).
 //
@@ -108,11 +119,67 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
   const int n_blocks = (N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (K + GC_BK - 1) / GC_BK;
-  const int blocks_per_rank = rows_per_rank / GC_BM;
+  const int blocks_per_rank = (MODE == 3 || MODE == 4) ? 0 : rows_per_rank / GC_BM;
   // gather: start with the local rows; reduce: start with the next rank's rows (remote first)
-  const int first_owner = MODE == 1 ? (my_rank + 1) % P : my_rank;
-  const int n_copy = MODE == 2 ? ga.n_copy : 0;
+  const int first_owner = MODE == 1 ? (my_rank + 1) % P : ((MODE == 3 || MODE == 4) ? 0 : my_rank);
+  const int n_copy = (MODE == 2 || MODE == 4) ? ga.n_copy : 0;
+  const int kb_per_rank = MODE == 4 ? (rows_per_rank / GC_BK) : 0;  // MODE 4: rows_per_rank carries K / P
   const int n_compute = gridDim.x - n_copy;
+
+  if (MODE == 4 && (int)blockIdx.x < n_copy) {
+    // ------------------------------------------------ copy CTA (column panels): this rank's rows of
+    // every remote rank's [T_full, K / P] panel -> local [T_local, K] buffer, once.
+    constexpr int GROUP = 6;
+    constexpr int BOX_BYTES = GC_BM * GC_BK * 2;
+    if (threadIdx.x == 0) {
+      const uint32_t gbar0 = smem_base + 2 * GROUP * BOX_BYTES;
+      mbar_init(gbar0, 1);
+      mbar_init(gbar0 + 8, 1);
+      fence_mbar_init();
+      for (int r = 0; r < P; ++r) prefetch_tmap(&tmA.m[r]);
+      prefetch_tmap(&tmG);
+      const int pairs = m_blocks * (P - 1);
+      bool ok = true;
+      uint32_t ph[2] = {0u, 0u};
+      for (int i = blockIdx.x; i < pairs && ok; i += n_copy) {
+        const int mb = i / (P - 1);
+        const int owner = (my_rank + 1 + (i - mb * (P - 1))) % P;
+        const int m0 = mb * GC_BM;
+        const int src_row = my_rank * M + m0;             // my rows inside the owner's [P * M, K / P] panel
+        const CUtensorMap* ts = &tmA.m[owner];
+        const int n_batches = (kb_per_rank + GROUP - 1) / GROUP;
+        auto issue_loads = [&](int batch) {
+          const int g = batch & 1;
+          const int kb_lo = batch * GROUP;
+          const int n = min(GROUP, kb_per_rank - kb_lo);
+          mbar_expect_tx(gbar0 + 8 * g, n * BOX_BYTES);
+          for (int j = 0; j < n; ++j)
+            tma_load_2d(smem_base + (g * GROUP + j) * BOX_BYTES, ts, gbar0 + 8 * g, (kb_lo + j) * GC_BK, src_row);
+        };
+        issue_loads(0);
+        if (n_batches > 1) issue_loads(1);
+        for (int batch = 0; batch < n_batches; ++batch) {
+          const int g = batch & 1;
+          if (!mbar_wait(gbar0 + 8 * g, ph[g], err, ERR_WAIT_FULL)) { ok = false; break; }
+          ph[g] ^= 1u;
+          const int kb_lo = batch * GROUP;
+          const int n = min(GROUP, kb_per_rank - kb_lo);
+          for (int j = 0; j < n; ++j)
+            tma_store_2d(&tmG, smem_base + (g * GROUP + j) * BOX_BYTES, (owner * kb_per_rank + kb_lo + j) * GC_BK, m0);
+          tma_store_commit();
+          if (batch + 2 < n_batches) {
+            tma_store_wait_read<0>();
+            issue_loads(batch + 2);
+          }
+        }
+        tma_store_wait<0>();
+        fence_proxy_async_global();
+        __threadfence();
+        if (ok) st_release_gpu(ga.flags + mb * P + owner, ga.epoch);
+      }
+    }
+    return;
+  }
 
   if (MODE == 2 && (int)blockIdx.x < n_copy) {
     // ------------------------------------------------ copy CTA: remote row blocks -> local buffer, once.
@@ -173,7 +240,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < (MODE == 1 ? 1 : P); ++r) prefetch_tmap(&tmA.m[r]);
-    if (MODE == 2) prefetch_tmap(&tmG);
+    if (MODE == 2 || MODE == 4) prefetch_tmap(&tmG);
     prefetch_tmap(&tmB);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -225,12 +292,36 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
           }
         }
         const CUtensorMap* ta = owner < 0 ? &tmG : &tmA.m[owner];
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int it = 0; it < num_kb; ++it) {
+          int kb = it;                     // k-block this iteration loads (MODE 4 starts with the local panel)
+          int a_col = it * GC_BK;
+          if constexpr (MODE == 4) {
+            kb = (it + my_rank * kb_per_rank) % num_kb;
+            const int k_owner = kb / kb_per_rank;
+            if (k_owner == my_rank) {
+              ta = &tmA.m[my_rank];
+              a_col = (kb - my_rank * kb_per_rank) * GC_BK;
+              a_row = my_rank * M + m0;
+            } else {
+              if (kb == k_owner * kb_per_rank || it == 0) {   // first block of a remote panel: wait for its copy
+                const long long t0 = clock64();
+                while (ld_acquire_gpu(ga.flags + mb * P + k_owner) != ga.epoch) {
+                  if (clock64() - t0 > WAIT_LIMIT_CYCLES) { set_error(err, ERR_WAIT_PEER_FLAG); ok = false; break; }
+                  __nanosleep(64);
+                }
+                if (!ok) break;
+                fence_proxy_async_global();
+              }
+              ta = &tmG;
+              a_col = kb * GC_BK;
+              a_row = m0;
+            }
+          }
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, err, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
           mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
-          tma_load_2d(sA, ta, full_bar(stage), kb * GC_BK, a_row);
+          tma_load_2d(sA, ta, full_bar(stage), a_col, a_row);
           if (!B_MN) {
             tma_load_2d(sB, &tmB, full_bar(stage), kb * GC_BK, n0);
           } else {
@@ -313,7 +404,24 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
         const int col = n0 + c * 32;
         if (row < M && col < N) {
           const bool full = (col + 32 <= N);
-          if (MODE != 1) {
+          if (MODE == 3) {
+            // columns -> owner (rows_per_rank carries N / P); rows land at this rank's offset
+            const int c_owner = col / rows_per_rank;
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(outs.p[c_owner]) + (size_t)(my_rank * M + row) * ldc +
+                               (col - c_owner * rows_per_rank);
+            if (full) {
+              uint4* C4 = reinterpret_cast<uint4*>(C);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                C4[j] = make_uint4(pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                                   pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                                   pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                                   pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col + j < N) C[j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          } else if (MODE != 1) {
             __nv_bfloat16* C = Cloc + (size_t)row * ldc + col;
             if (full) {
               uint4* C4 = reinterpret_cast<uint4*>(C);
@@ -371,7 +479,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(tempty_bar(buf));
     }
-    if (MODE == 1) __threadfence_system();  // reductions on peer memory ordered before the closing barrier
+    if (MODE == 1 || MODE == 3) __threadfence_system();  // peer writes ordered before the closing barrier
   }
 
   tc_fence_before();
@@ -397,9 +505,22 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
       rc = ab2host::encode_tmap_2d(&ta.m[r], a_ptrs[r], 2, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
       if (rc) return 100 + rc;
     }
-  } else if (MODE == 1) {
+  } else if (MODE == 1 || MODE == 3) {
     rc = ab2host::encode_tmap_2d(&ta.m[0], a_ptrs[0], 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
     if (rc) return 100 + rc;
+  } else if (MODE == 4) {
+    // rows_per_rank carries K / P: every rank holds a [P * M, K / P] column panel
+    nA = P;
+    for (int r = 0; r < P; ++r) {
+      rc = ab2host::encode_tmap_2d(&ta.m[r], a_ptrs[r], 2, (uint64_t)rows_per_rank, (uint64_t)P * M, (uint64_t)lda * 2, GC_BK, GC_BM, true, 0);
+      if (rc) return 100 + rc;
+    }
+    rc = ab2host::encode_tmap_2d(&tmG, gathered, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, GC_BK, GC_BM, true, 0);
+    if (rc) return 110 + rc;
+    ga.gathered = reinterpret_cast<__nv_bfloat16*>(gathered);
+    ga.flags = flags;
+    ga.epoch = epoch;
+    ga.lda = lda;
   } else {
     nA = P;
     for (int r = 0; r < P; ++r) {
@@ -415,7 +536,7 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
     ga.lda = lda;
   }
   for (int r = nA; r < GC_MAX_PEERS; ++r) ta.m[r] = ta.m[0];
-  if (MODE != 2) tmG = ta.m[0];
+  if (MODE != 2 && MODE != 4) tmG = ta.m[0];
   CUtensorMap tmB;
   if (!B_MN)
     rc = ab2host::encode_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, GC_BK, BN, true, 0);
@@ -423,7 +544,7 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
     rc = ab2host::encode_tmap_2d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, GC_BK, true, 0);
   if (rc) return 200 + rc;
   OutPtrs op;
-  for (int r = 0; r < GC_MAX_PEERS; ++r) op.p[r] = (MODE == 1 && r < P) ? out_ptrs[r] : nullptr;
+  for (int r = 0; r < GC_MAX_PEERS; ++r) op.p[r] = ((MODE == 1 || MODE == 3) && r < P) ? out_ptrs[r] : nullptr;
   auto kern = gemm_comm_kernel<BN, B_MN, MODE, RED_BF16>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -438,7 +559,7 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
   }
   const int tiles = ((M + GC_BM - 1) / GC_BM) * ((N + BN - 1) / BN);
   int grid = tiles < num_sms ? tiles : num_sms;
-  if (MODE == 2) {
+  if (MODE == 2 || MODE == 4) {
     // copy CTAs and compute CTAs must all be resident at once: the compute side waits on flags
     // that the copy side sets
     ga.n_copy = P > 1 ? (num_sms >= 64 ? 8 : 2) : 0;
@@ -496,6 +617,40 @@ int ab2_allgather_gemm(void* const* a_ptrs, const void* B, void* C, int M, int N
 // NVLink bytes; every add rounds to bf16, meant for small groups). All buffers must be zero (or
 // hold the value to add to) and visible before any rank launches; results are complete after
 // a barrier that follows every rank's kernel.
+// Ulysses seq->heads fused into the projection: Y = A[M, K] * op(B) (N columns) is never stored
+// locally; columns [r * N/P, (r+1) * N/P) go to rank r's buffer out_ptrs[r] ([P * M, N / P] bf16,
+// ld_out elements per row) at rows [my_rank * M, (my_rank + 1) * M). N / P must be a multiple of 32.
+int ab2_gemm_scatter_cols(const void* A, const void* B, void* const* out_ptrs, int M, int N, int K, int lda, int ldb, int ld_out,
+                          int b_mn, int my_rank, int world, void* stream) {
+  using namespace ab2;
+  if (world < 1 || world > GC_MAX_PEERS) return 10;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (N % world || (N / world) % 32) return 11;
+  if ((lda & 7) || (ldb & 7) || (ld_out & 7)) return 12;
+  const int bn = (N % 256 == 0 && ((M + 127) / 128) * (N / 256) >= 120) ? 256 : 128;
+  void* a1[1] = {const_cast<void*>(A)};
+  return dispatch_gc<3, false>(bn, b_mn, a1, B, nullptr, out_ptrs, M, N, K, lda, ldb, ld_out, N / world, my_rank, world, nullptr, nullptr,
+                               0, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Ulysses heads->seq fused into the output projection: C[M, N] (bf16, local) = A * op(B) where
+// A[M, K] is this rank's M rows of every rank's column panel: a_ptrs[r] is rank r's
+// [P * M, K / P] buffer (lda elements per row) as mapped here; this rank's rows start at
+// my_rank * M. K / P must be a multiple of 64, M of 128. gathered: local [M, K] bf16 scratch;
+// flags: int32[(M / 128) * P]; epoch: differs from every earlier call on these flags.
+int ab2_gather_cols_gemm(void* const* a_ptrs, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int b_mn,
+                         int my_rank, int world, void* gathered, void* flags, int epoch, void* stream) {
+  using namespace ab2;
+  if (world < 1 || world > GC_MAX_PEERS) return 10;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % world || (K / world) % GC_BK || M % GC_BM) return 11;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7)) return 12;
+  if (!gathered || !flags) return 13;
+  const int bn = (N % 256 == 0 && ((M + 127) / 128) * (N / 256) >= 120) ? 256 : 128;
+  return dispatch_gc<4, false>(bn, b_mn, a_ptrs, B, C, nullptr, M, N, K, lda, ldb, ldc, K / world, my_rank, world, gathered,
+                               reinterpret_cast<int*>(flags), epoch, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int ab2_gemm_reduce_scatter(const void* A, const void* B, void* const* out_ptrs, int M, int N, int K, int lda, int ldb, int ldc,
                             int b_mn, int my_rank, int world, int out_bf16, void* stream) {
   using namespace ab2;

@@ -52,3 +52,12 @@ def test_fused_tp_gemm_collectives_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_tp_fused.py"), 2, 29731, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("TP_FUSED_OK") == 2
+
+
+def test_fused_ulysses_projections_two_gpus():
+    """QKV projection + seq->heads scatter and heads->seq gather + output projection, each one
+    kernel over peer memory, against fp32 math on gathered operands."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_ulysses_fused.py"), 2, 29751, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("ULYSSES_FUSED_OK") == 2
