@@ -85,3 +85,100 @@ def ulysses_attention(attn_module, q, k, v, full_cu_seqlens, causal, scale, tile
     vf = SeqToHead.apply(v.contiguous(), group, n)
     o = attention_fn(qf, kf, vf, full_cu_seqlens, causal, scale, tile_info)
     return HeadToSeq.apply(o, group, n)
+
+
+# --------------------------------------------------------------------------- fused exchanges (CUDA)
+class _ProjectScatter(torch.autograd.Function):
+    """``x_local[T/P, K] @ w[N, K]^T`` landing as ``[T, N/P]`` on the column owners (one kernel).
+    Backward: ``dx_local = gather_cols(dy) @ w`` (one kernel); ``dw`` is non-zero only in the
+    rows (output columns) this rank owns: ``dy^T @ gather_rows(x)``."""
+
+    @staticmethod
+    def forward(ctx, x, w, fused):
+        ctx.fused = fused
+        ctx.save_for_backward(x, w)
+        return fused.project_scatter(x, w).clone()
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import functional as OF
+
+        x, w = ctx.saved_tensors
+        f = ctx.fused
+        dy = dy.contiguous()
+        dx = f.gather_project(dy, w, b_mn=True)                     # [T/P, K]
+        dw = None
+        if ctx.needs_input_grad[1]:
+            P, r = f.world, f.rank
+            xf = x.new_empty(x.shape[0] * P, x.shape[1])
+            dist.all_gather_into_tensor(xf, x.contiguous(), group=f.group)
+            cpr = w.shape[0] // P
+            dw = torch.zeros_like(w)
+            dw[r * cpr:(r + 1) * cpr] = OF.gemm(dy, xf, a_mn=True, b_mn=True)
+        return dx, dw, None
+
+
+class _GatherProject(torch.autograd.Function):
+    """``gather_cols(o_full[T, K/P])[T/P, K] @ w[N, K]^T`` (one kernel). Backward:
+    ``do_full = scatter_cols(dy @ w)`` (one kernel), ``dw = dy^T @ gathered``."""
+
+    @staticmethod
+    def forward(ctx, o_full, w, fused):
+        ctx.fused = fused
+        y = fused.gather_project(o_full, w)
+        M, K = y.shape[0], o_full.shape[1] * fused.world
+        ctx.save_for_backward(fused.gathered[: M * K].view(M, K).clone(), w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import functional as OF
+
+        a, w = ctx.saved_tensors
+        f = ctx.fused
+        dy = dy.contiguous()
+        do = f.project_scatter(dy, w, b_mn=True).clone()            # [T, K/P]
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                OF.gemm(dy, a, a_mn=True, b_mn=True, out=mg, epi=OF.EPI_F32_ACC)
+            else:
+                dw = OF.gemm(dy, a, a_mn=True, b_mn=True)
+        return do, dw, None
+
+
+def head_owner_permutation(nq: int, nkv: int, D: int, P: int, device) -> torch.Tensor:
+    """Row order of a fused QKV weight such that rank r's column slice is ``[q heads of r | k
+    heads of r | v heads of r]``."""
+    nql, nkl = nq // P, nkv // P
+    q = torch.arange(nq * D, device=device).view(P, nql * D)
+    k = (nq * D + torch.arange(nkv * D, device=device)).view(P, nkl * D)
+    v = ((nq + nkv) * D + torch.arange(nkv * D, device=device)).view(P, nkl * D)
+    return torch.cat([q, k, v], dim=1).reshape(-1)
+
+
+def fused_ulysses_attention_block(attn_module, x: torch.Tensor, pb, cos, sin, fused) -> torch.Tensor:
+    """Whole attention block under Ulysses SP with both exchanges inside the projection
+    kernels: x_local [T/P, H] -> y_local [T/P, H]. The QKV weight rows are re-ordered by head
+    owner (one gather of the weight per call), so one projection kernel scatters every rank its
+    ``[q | k | v]`` head group for all tokens, which the fused QK-norm + RoPE + attention kernels
+    consume in place; the output projection pulls the other ranks' head outputs as it runs."""
+    import math
+
+    from ..ops import functional as OF
+
+    a = attn_module
+    P = fused.world
+    D, nq, nkv = a.D, a.nq, a.nkv
+    if nq % P or nkv % P or a.qkv_bias is not None:
+        raise ValueError("the fused Ulysses block needs q and kv heads divisible by the group size and no QKV bias")
+    nql, nkl = nq // P, nkv // P
+    perm = getattr(a, "_sp_perm", None)
+    if perm is None or perm.device != x.device:
+        perm = a._sp_perm = head_owner_permutation(nq, nkv, D, P, x.device)
+    w_perm = a.qkv_proj.index_select(0, perm)
+    qkv = _ProjectScatter.apply(x, w_perm, fused)                    # [T, (nql + 2 nkl) D]: all tokens, my heads
+    o = OF.qknorm_rope_attention(qkv, a.q_norm, a.k_norm, pb.position_ids, cos, sin, pb.cu_seqlens, nql, nkl, D, a.cfg.rms_norm_eps,
+                                 1.0 / math.sqrt(D), pb.tile_info)
+    return _GatherProject.apply(o.reshape(o.shape[0], nql * D), a.o_proj, fused)
