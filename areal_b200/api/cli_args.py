@@ -127,6 +127,9 @@ class FSDPEngineConfig:
     fuse_reduce_scatter_adamw: bool = True   # fused RS + cast/scale + sharded AdamW kernel
     fuse_allgather_gemm: bool = True         # param all-gather fused into the consuming GEMM
     bucket_mb: int = 256
+    per_layer_optim_step: bool = False        # accepted for compatibility (the flat sharded optimizer steps once)
+    optim_step_prefetch_layers: int = 1
+    shard_vision_across_sp: bool = False
 
 
 @dataclass
@@ -147,6 +150,8 @@ class ArchonEngineConfig:
     pp_schedule: str = "1F1B"
     fp8: FP8Config = field(default_factory=FP8Config)
     offload_params: bool = False
+    extra: dict = field(default_factory=dict)   # backend-specific keys of the reference, accepted and kept
+    __allow_extra__ = True
 
 
 @dataclass
@@ -158,6 +163,8 @@ class MegatronEngineConfig:
     moe_token_dispatcher_type: str = "alltoall"
     moe_enable_deepep: bool = False
     fp8: FP8Config = field(default_factory=FP8Config)
+    extra: dict = field(default_factory=dict)   # backend-specific keys of the reference, accepted and kept
+    __allow_extra__ = True
 
 
 @dataclass
@@ -175,6 +182,12 @@ class SchedulingSpec:
     partition: Optional[str] = None
     time_limit: Optional[str] = None
     additional_bash_cmds: Optional[list[str]] = None
+    srun_additional_args: str = ""
+    container_type: str = "none"
+    mount: str = ""
+    reservation: Optional[str] = None
+    exclusive: bool = False
+    ray_placement_strategy: str = "PACK"
 
 
 @dataclass
@@ -200,6 +213,14 @@ class TrainEngineConfig:
     gradient_checkpointing: bool = False
     activation_checkpointing: Optional[str] = None   # none | full | selective | memory_budget (overrides the flag above)
     activation_memory_budget: float = 0.5            # fraction of layers recomputed in memory_budget mode
+    use_kernels: bool = True                          # accepted for compatibility: the sm_100a kernels are always used
+    weight_update_delta_method: str = "none"          # none | exact | adamw_inversion (see wsync/delta.py)
+    weight_update_anchor_interval: int = 0            # full (non-delta) push every k updates; 0 = never forced
+    admin_api_key: str = "areal-admin-key"
+    log_level: str = "info"
+    request_timeout: float = 3600.0
+    setup_timeout: float = 300.0
+    workers_ready_timeout: float = 600.0
     dtype: str = "bfloat16"
     grad_reduce_dtype: str = "float32"
     optimizer_dtype: str = "float32"
@@ -262,6 +283,7 @@ class PPOActorConfig(TrainEngineConfig):
     mask_no_eos_with_zero: bool = False
     discount: float = 1.0
     gae_lambda: float = 1.0
+    gae_lambda_kwargs: dict = field(default_factory=dict)   # parameters of a lambda schedule (see algo/advantages.py)
     gae_timestep_unit: str = "token"  # token | turn
     adv_norm: Optional[NormConfig] = None
     kl_ctl: float = 0.1
@@ -316,6 +338,9 @@ class PPOCriticConfig(TrainEngineConfig):
 class TeacherConfig(TrainEngineConfig):
     rl_loss_weight: float = 1.0
     distill_loss_weight: float = 0.005
+    engine_type: str = "train"                # train: forward with a train engine; rollout: score through an inference engine
+    rollout: Optional[dict] = None
+    train: Optional[dict] = None
 
 
 @dataclass
@@ -338,6 +363,8 @@ class vLLMConfig:
     uvicorn_log_level: str = "warning"
     enable_lora: bool = False
     max_lora_rank: int = 16
+    extra: dict = field(default_factory=dict)   # server flags of the reference's backend, accepted and kept
+    __allow_extra__ = True
 
 
 @dataclass
@@ -366,6 +393,8 @@ class SGLangConfig:
     enable_return_routed_experts: bool = False
     enable_lora: Optional[bool] = None
     max_lora_rank: Optional[int] = None
+    extra: dict = field(default_factory=dict)   # server flags of the reference's backend, accepted and kept
+    __allow_extra__ = True
 
 
 @dataclass
@@ -425,6 +454,14 @@ class InferenceEngineConfig:
     setup_timeout: float = 300.0
     request_timeout: float = 3600.0
     request_retries: int = 3
+    serialize_group_samples: bool = False
+    workers_ready_timeout: float = 600.0
+    lora_name: str = ""
+    model: str = "default"
+    poll_interval: float = 0.05
+    admin_api_key: str = "areal-admin-key"
+    api_url: str = ""
+    provider_api_key: str = ""
     pause_grace_period: float = 0.0
     scheduling_spec: list[SchedulingSpec] = field(default_factory=lambda: [SchedulingSpec(gpu=1)])
     scheduling_strategy: SchedulingStrategy = field(default_factory=SchedulingStrategy)
@@ -448,7 +485,7 @@ class _Timer:
 
 @dataclass
 class EvaluatorConfig(_Timer):
-    pass
+    eval_before_train: bool = False
 
 
 @dataclass
@@ -593,6 +630,7 @@ class LauncherConfig:
 
 @dataclass
 class BaseExperimentConfig:
+    post_exit_hook: Optional[str] = None      # import path of a callable run after training ends
     experiment_name: str = "default-experiment"
     trial_name: str = "trial0"
     cluster: ClusterSpecConfig = field(default_factory=ClusterSpecConfig)
@@ -789,12 +827,19 @@ def _merge_into_dataclass(cls, data: dict, path: str = "", strict: bool = True):
     hints = get_type_hints(cls)
     known = {f.name: f for f in fields(cls)}
     kwargs = {}
+    extra_ok = getattr(cls, "__allow_extra__", False) and "extra" in known
+    extra: dict = {}
     for key, val in data.items():
         if key not in known:
+            if extra_ok:      # tunables of a backend this framework replaces: kept, not interpreted
+                extra[key] = val
+                continue
             if not strict:
                 continue
             raise ConfigError(f"unknown config key '{path + '.' if path else ''}{key}' for {cls.__name__}")
         kwargs[key] = _coerce(val, hints[key], f"{path + '.' if path else ''}{key}")
+    if extra:
+        kwargs["extra"] = {**kwargs.get("extra", {}), **extra}
     try:
         return cls(**kwargs)
     except (TypeError, ValueError) as e:

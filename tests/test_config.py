@@ -94,3 +94,25 @@ def test_rejection_sampling_config_validation():
         C.RejectionSamplingConfig(upper=None, lower=None)
     with pytest.raises(ValueError):
         C.PPOActorConfig(use_sapo_loss=True, use_decoupled_loss=True)
+
+
+def test_example_configs_parse_and_backend_extras_are_kept():
+    import glob
+    import os
+
+    from areal_b200.api.cli_args import GRPOConfig, PPOConfig, SFTConfig, parse_cli_args, to_structured_cfg
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "examples", "**", "*.yaml"), recursive=True))
+    assert len(files) >= 5
+    for f in files:
+        cls = SFTConfig if "sft" in os.path.basename(f) else (PPOConfig if "ppo" in os.path.basename(f) else GRPOConfig)
+        raw, _ = parse_cli_args(["--config", f])
+        cfg = to_structured_cfg(raw, cls)
+        assert cfg.experiment_name
+    # keys that configure a backend of the reference (SGLang server flags, Megatron switches) are accepted and kept
+    raw, _ = parse_cli_args(["--config", files[0], "+sglang.enable_dp_attention=true", "+actor.megatron.recompute_method=uniform",
+                             "+actor.use_kernels=false", "+rollout.poll_interval=0.1"])
+    cfg = to_structured_cfg(raw, GRPOConfig)
+    assert cfg.sglang.extra == {"enable_dp_attention": True} and cfg.actor.megatron.extra == {"recompute_method": "uniform"}
+    assert cfg.actor.use_kernels is False and cfg.rollout.poll_interval == 0.1
