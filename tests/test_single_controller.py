@@ -288,3 +288,31 @@ def test_ray_scheduler_against_fake_ray(tmp_path):
     assert sch.fork_workers("ref", "rollout") == ["ref/0", "ref/1"]
     sch.delete_workers()
     assert len(killed) == 2 and len(removed) == 1
+
+
+def test_worker_death_is_reported_as_worker_failed(tmp_path):
+    """Failure injected on the host: the worker process exits between calls; the scheduler
+    reports which worker died (with its exit code) instead of timing out."""
+    import os
+    import signal
+
+    from areal_b200.api.cli_args import SchedulingSpec
+    from areal_b200.api.scheduler_api import Job
+    from areal_b200.infra.scheduler.exceptions import WorkerFailedError
+
+    sched = LocalScheduler(gpu_devices=[], log_dir=str(tmp_path))
+    try:
+        sched.create_workers(Job(replicas=2, tasks=[SchedulingSpec(gpu=0)], role="w"))
+        ws = sched.get_workers("w")
+        for w in ws:
+            sched.create_engine(w.id, "tests.test_single_controller._Echo", name="w", scale=2)
+        assert sched.call_engine(ws[1].id, "scale", engine_name="w") == 2
+        victim = sched._find(ws[0].id).process
+        os.kill(victim.pid, signal.SIGKILL)                   # exact pid of the child this test started
+        victim.wait(timeout=10)
+        with pytest.raises(WorkerFailedError) as e:
+            sched.call_engine(ws[0].id, "scale", engine_name="w")
+        assert e.value.worker_id == "w/0" and e.value.exit_code == -signal.SIGKILL
+        assert sched.call_engine(ws[1].id, "scale", engine_name="w") == 2     # the survivor still answers
+    finally:
+        sched.delete_workers()
