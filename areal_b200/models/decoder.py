@@ -152,6 +152,13 @@ class MoEMLP(nn.Module):
 
     def experts_forward(self, xs: torch.Tensor, counts: list[int], first_expert: int = 0) -> torch.Tensor:
         """xs: tokens sorted by (local) expert; counts[e] tokens for expert first_expert+e."""
+        if xs.is_cuda and xs.shape[0] > 0 and getattr(self, "use_grouped_gemm", True):
+            # one grouped kernel per projection instead of a launch per expert
+            E_local = self.w_gate_up.shape[0]
+            cnt = [0] * first_expert + [int(c) for c in counts]
+            cnt += [0] * (E_local - len(cnt))
+            h = OF.grouped_linear(xs, self.w_gate_up, cnt)
+            return OF.grouped_linear(OF.swiglu(h), self.w_down, cnt)
         outs = []
         off = 0
         mg_gu = getattr(self.w_gate_up, "main_grad", None)

@@ -69,6 +69,96 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+# ----------------------------------------------------------------------------- grouped (expert) GEMM
+def grouped_tile_table(counts, n_cols: int, bn: int, device) -> torch.Tensor:
+    """int32 [num_tiles, 4] = (expert, first row, valid rows, n-block) for row groups of sizes
+    ``counts`` (rows sorted by expert)."""
+    rows = []
+    off = 0
+    nb = (n_cols + bn - 1) // bn
+    for e, n in enumerate(counts):
+        n = int(n)
+        for r0 in range(0, n, 128):
+            valid = min(128, n - r0)
+            for b in range(nb):
+                rows.append((e, off + r0, valid, b))
+        off += n
+    if not rows:
+        return torch.zeros(0, 4, dtype=torch.int32, device=device)
+    return torch.tensor(rows, dtype=torch.int32).to(device, non_blocking=True)
+
+
+def grouped_gemm_ref(x, w, counts, b_mn: bool = False):
+    outs, off = [], 0
+    for e, n in enumerate(counts):
+        n = int(n)
+        if n:
+            we = w[e].float()
+            outs.append(x[off:off + n].float() @ (we if b_mn else we.t()))
+        off += n
+    n_out = w.shape[2] if b_mn else w.shape[1]
+    return (torch.cat(outs, 0) if outs else x.new_zeros(0, n_out)).to(x.dtype)
+
+
+def grouped_gemm(x: torch.Tensor, w: torch.Tensor, counts, b_mn: bool = False, tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows of ``x`` [R, K] are grouped by expert (``counts[e]`` rows each, in order); returns
+    ``y`` [R, N] with ``y[group e] = x[group e] @ w[e]^T`` (``w``: [E, N, K]) or ``@ w[e]``
+    (``b_mn``; ``w``: [E, K, N]). One persistent kernel for all experts."""
+    if not x.is_cuda:
+        return grouped_gemm_ref(x, w, counts, b_mn)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()
+    R, K = x.shape
+    E = w.shape[0]
+    N = w.shape[2] if b_mn else w.shape[1]
+    assert (w.shape[1] if b_mn else w.shape[2]) == K and sum(int(c) for c in counts) == R
+    bn = 256 if N % 256 == 0 else 128
+    if tiles is None:
+        tiles = grouped_tile_table(counts, N, bn, x.device)
+    y = torch.empty(R, N, device=x.device, dtype=torch.bfloat16)
+    if tiles.shape[0]:
+        rc = _L().ab2_gemm_grouped(x.data_ptr(), w.data_ptr(), y.data_ptr(), tiles.data_ptr(), tiles.shape[0], R, N, K, E, x.stride(0),
+                                   y.stride(0), int(b_mn), bn, _s())
+        _lib.check(rc, "ab2_gemm_grouped")
+    return y
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """``y[group e] = x[group e] @ W[e]^T`` for stacked expert weights ``W`` [E, N, K]. Forward and
+    input gradient are one grouped kernel each; weight gradients accumulate per expert in fp32
+    (into ``W.main_grad`` when present)."""
+
+    @staticmethod
+    def forward(ctx, x, w, counts):
+        ctx.counts = [int(c) for c in counts]
+        ctx.save_for_backward(x, w)
+        return grouped_gemm(x, w, ctx.counts)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        counts = ctx.counts
+        dy = dy.contiguous()
+        dx = grouped_gemm(dy, w, counts, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            acc = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+            off = 0
+            for e, n in enumerate(counts):
+                if n:
+                    if x.is_cuda:
+                        gemm(dy[off:off + n], x[off:off + n], a_mn=True, b_mn=True, out=acc[e], epi=EPI_F32_ACC)
+                    else:
+                        acc[e] += dy[off:off + n].float().t() @ x[off:off + n].float()
+                off += n
+            dw = None if mg is not None else acc.to(w.dtype)
+        return dx, dw, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts) -> torch.Tensor:
+    return _GroupedLinear.apply(x, w, counts)
+
+
 SKINNY_MAX_TOKENS = 256
 _skinny_ws: dict = {}
 

@@ -331,3 +331,27 @@ def test_fused_qknorm_rope_attention_matches_fp32(D, nq, nkv, norm):
     assert _rel_err(qkv.grad, x.grad) < 3e-2
     if norm:
         assert _rel_err(wq.grad, wq32.grad) < 3e-2 and _rel_err(wk.grad, wk32.grad) < 3e-2
+
+
+@pytest.mark.parametrize("counts", [[130, 0, 77, 256, 1], [5, 5, 5, 5], [0, 0, 300]])
+def test_grouped_gemm_matches_fp32(counts):
+    """Grouped expert GEMM (variable row groups, 3-D tensor map over the expert stack) forward,
+    input gradient and weight gradient against per-expert fp32 matmuls."""
+    torch.manual_seed(6)
+    E, K, N = len(counts), 256, 384
+    R = sum(counts)
+    x = torch.randn(R, K, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(E, N, K, device="cuda") / K ** 0.5).bfloat16().requires_grad_()
+    y = OF.grouped_linear(x, w, counts)
+    g = torch.randn_like(y)
+    y.backward(g)
+    _no_kernel_error()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    outs, off = [], 0
+    for e, n in enumerate(counts):
+        if n:
+            outs.append(xr[off:off + n] @ wr[e].t())
+        off += n
+    ref = torch.cat(outs, 0)
+    ref.backward(g.float())
+    assert _rel_err(y, ref) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(w.grad, wr.grad) < 1e-2
