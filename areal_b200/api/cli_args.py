@@ -126,6 +126,7 @@ class FSDPEngineConfig:
     reshard_after_forward: bool = True
     fuse_reduce_scatter_adamw: bool = True   # fused RS + cast/scale + sharded AdamW kernel
     fuse_allgather_gemm: bool = True         # param all-gather fused into the consuming GEMM
+    fuse_ulysses_projections: bool = True    # sequence-parallel all-to-alls folded into the QKV / output projection kernels
     bucket_mb: int = 256
     per_layer_optim_step: bool = False        # accepted for compatibility (the flat sharded optimizer steps once)
     optim_step_prefetch_layers: int = 1

@@ -274,6 +274,19 @@ class B200TrainEngine(TrainEngine):
             from ..parallel.ulysses import install_ulysses
 
             install_ulysses(self.model, self._sp_group, self.sp_size, self.sp_rank)
+            self._sp_fused = None
+            mc = model_config
+            if (on_gpu and cfg.fsdp.fuse_ulysses_projections and not self.use_lora and tp == 1 and self.sp_size <= 8
+                    and mc.num_heads % sp == 0 and mc.num_kv_heads % sp == 0 and not mc.attention_bias and mc.head_dim in (64, 128)
+                    and ((mc.num_heads + 2 * mc.num_kv_heads) // sp * mc.head_dim) % 64 == 0):
+                from ..parallel.tp_fused import FusedUlyssesLinear
+                from ..parallel.ulysses import install_fused_ulysses
+
+                unit = 128 * sp
+                max_t = (max(int(cfg.mb_spec.max_tokens_per_mb or 0), unit) + unit - 1) // unit * unit
+                cols = max(mc.hidden_size, (mc.num_heads + 2 * mc.num_kv_heads) * mc.head_dim)
+                self._sp_fused = FusedUlyssesLinear(self._sp_group, self.device, max_t // sp, cols)
+                install_fused_ulysses(self.model, self._sp_fused)
         if alloc is not None:
             from ..parallel.fused_zero import FusedGradReducer
 
@@ -374,6 +387,8 @@ class B200TrainEngine(TrainEngine):
     # ------------------------------------------------------------------ micro-batches
     def _align(self) -> int:
         base = D.N_TOKENS_PER_PAGE if self.device.type == "cuda" else 1
+        if getattr(self, "_sp_fused", None) is not None:
+            return max(base, 128 * self.sp_size)   # the fused projections work on 128-row blocks per rank
         return base * self.sp_size if self.sp_size > 1 and base % self.sp_size else max(base, self.sp_size)
 
     def _prepare_mb_list(self, input_: dict[str, Any]) -> D.MicroBatchList:
@@ -412,6 +427,7 @@ class B200TrainEngine(TrainEngine):
             sl = slice(self.sp_rank * chunk, (self.sp_rank + 1) * chunk)
             pb_local = PackedBatch(cu, pos[sl], T, pb.max_seqlen)
             pb_local.tile_info = pb.tile_info
+            pb_local.full_position_ids = pb.position_ids
             hidden = self.model.forward_hidden(ids[sl], pb_local)
             return hidden, labels[sl], sl
         hidden = self.model.forward_hidden(ids, pb)

@@ -97,6 +97,10 @@ class Attention(nn.Module):
             o = OF.qknorm_rope_attention(qkv, self.q_norm, self.k_norm, pb.position_ids, cos, sin, pb.cu_seqlens, self.nq,
                                          self.nkv, self.D, self.cfg.rms_norm_eps, 1.0 / math.sqrt(self.D), pb.tile_info)
             return _lin(self, "o_proj", o.reshape(T, self.nq * self.D))
+        if attn_fn is None and getattr(self, "sp_fused", None) is not None and x.is_cuda:
+            from ..parallel.ulysses import fused_ulysses_attention_block
+
+            return fused_ulysses_attention_block(self, x, pb, cos, sin, self.sp_fused)
         q, k, v = self.project_qkv(x, pb.position_ids, cos, sin)
         if attn_fn is not None:
             o = attn_fn(q, k, v)

@@ -70,6 +70,13 @@ def install_ulysses(model, group, sp_size: int, sp_rank: int) -> None:
         a.sp_group, a.sp_size, a.sp_rank = group, sp_size, sp_rank
 
 
+def install_fused_ulysses(model, fused) -> None:
+    """Routes every attention block of a sequence-parallel model through
+    :func:`fused_ulysses_attention_block`; ``fused`` (one ``FusedUlyssesLinear``) is shared by all layers."""
+    for layer in model.layers:
+        layer.self_attn.sp_fused = fused
+
+
 def ulysses_attention(attn_module, q, k, v, full_cu_seqlens, causal, scale, tile_info, attention_fn):
     """q/k/v: local slices ``[T/n, heads, D]``; returns the local slice of the output."""
     n, group = attn_module.sp_size, attn_module.sp_group
@@ -89,33 +96,42 @@ def ulysses_attention(attn_module, q, k, v, full_cu_seqlens, causal, scale, tile
 
 # --------------------------------------------------------------------------- fused exchanges (CUDA)
 class _ProjectScatter(torch.autograd.Function):
-    """``x_local[T/P, K] @ w[N, K]^T`` landing as ``[T, N/P]`` on the column owners (one kernel).
-    Backward: ``dx_local = gather_cols(dy) @ w`` (one kernel); ``dw`` is non-zero only in the
-    rows (output columns) this rank owns: ``dy^T @ gather_rows(x)``."""
+    """``x_local[T/P, K] @ w[perm][N, K]^T`` landing as ``[T, N/P]`` on the column owners (one
+    kernel). ``perm`` orders the weight rows (output columns) by owner. Backward:
+    ``dx_local = gather_cols(dy) @ w[perm]`` (one kernel); ``dw`` is non-zero only in the rows this
+    rank owns, ``dy^T @ gather_rows(x)``, and goes straight into ``w.main_grad`` when present."""
 
     @staticmethod
-    def forward(ctx, x, w, fused):
+    def forward(ctx, x, w, fused, perm):
         ctx.fused = fused
-        ctx.save_for_backward(x, w)
-        return fused.project_scatter(x, w).clone()
+        w_perm = w if perm is None else w.index_select(0, perm)
+        ctx.save_for_backward(x, w, perm)
+        return fused.project_scatter(x, w_perm).clone()
 
     @staticmethod
     def backward(ctx, dy):
         from ..ops import functional as OF
 
-        x, w = ctx.saved_tensors
+        x, w, perm = ctx.saved_tensors
         f = ctx.fused
         dy = dy.contiguous()
-        dx = f.gather_project(dy, w, b_mn=True)                     # [T/P, K]
+        w_perm = w if perm is None else w.index_select(0, perm)
+        dx = f.gather_project(dy, w_perm, b_mn=True)                # [T/P, K]
         dw = None
         if ctx.needs_input_grad[1]:
             P, r = f.world, f.rank
             xf = x.new_empty(x.shape[0] * P, x.shape[1])
             dist.all_gather_into_tensor(xf, x.contiguous(), group=f.group)
             cpr = w.shape[0] // P
-            dw = torch.zeros_like(w)
-            dw[r * cpr:(r + 1) * cpr] = OF.gemm(dy, xf, a_mn=True, b_mn=True)
-        return dx, dw, None
+            own = OF.gemm(dy, xf, a_mn=True, b_mn=True)             # [N/P, K]: the rows this rank owns
+            rows = torch.arange(r * cpr, (r + 1) * cpr, device=w.device) if perm is None else perm[r * cpr:(r + 1) * cpr]
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                mg.index_add_(0, rows, own.to(mg.dtype))
+            else:
+                dw = torch.zeros_like(w)
+                dw.index_copy_(0, rows, own)
+        return dx, dw, None, None
 
 
 class _GatherProject(torch.autograd.Function):
@@ -126,8 +142,13 @@ class _GatherProject(torch.autograd.Function):
     def forward(ctx, o_full, w, fused):
         ctx.fused = fused
         y = fused.gather_project(o_full, w)
-        M, K = y.shape[0], o_full.shape[1] * fused.world
-        ctx.save_for_backward(fused.gathered[: M * K].view(M, K).clone(), w)
+        Kl = o_full.shape[1]
+        M, K = y.shape[0], Kl * fused.world
+        # the kernel's scratch holds the peers' panels; this rank's own panel is read in place
+        a = fused.gathered[: M * K].view(M, K).clone()
+        r = fused.rank
+        a[:, r * Kl:(r + 1) * Kl] = o_full[r * M:(r + 1) * M]
+        ctx.save_for_backward(a, w)
         return y
 
     @staticmethod
@@ -177,8 +198,10 @@ def fused_ulysses_attention_block(attn_module, x: torch.Tensor, pb, cos, sin, fu
     perm = getattr(a, "_sp_perm", None)
     if perm is None or perm.device != x.device:
         perm = a._sp_perm = head_owner_permutation(nq, nkv, D, P, x.device)
-    w_perm = a.qkv_proj.index_select(0, perm)
-    qkv = _ProjectScatter.apply(x, w_perm, fused)                    # [T, (nql + 2 nkl) D]: all tokens, my heads
-    o = OF.qknorm_rope_attention(qkv, a.q_norm, a.k_norm, pb.position_ids, cos, sin, pb.cu_seqlens, nql, nkl, D, a.cfg.rms_norm_eps,
+    qkv = _ProjectScatter.apply(x, a.qkv_proj, fused, perm)                  # [T, (nql + 2 nkl) D]: all tokens, my heads
+    pos = getattr(pb, "full_position_ids", None)
+    if pos is None:
+        pos = pb.position_ids
+    o = OF.qknorm_rope_attention(qkv, a.q_norm, a.k_norm, pos, cos, sin, pb.cu_seqlens, nql, nkl, D, a.cfg.rms_norm_eps,
                                  1.0 / math.sqrt(D), pb.tile_info)
     return _GatherProject.apply(o.reshape(o.shape[0], nql * D), a.o_proj, fused)

@@ -61,3 +61,12 @@ def test_fused_ulysses_projections_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_ulysses_fused.py"), 2, 29751, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("ULYSSES_FUSED_OK") == 2
+
+
+def test_sequence_parallel_engine_fused_projections_two_gpus():
+    """Train engine with sp=2: attention blocks on the fused projection + exchange kernels
+    against the same engine on NCCL all-to-alls (loss, gradient norm, weights after two steps)."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_sp_fused.py"), 2, 29761, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("ENGINE_SP_FUSED_OK") == 2
