@@ -560,6 +560,12 @@ class B200TrainEngine(TrainEngine):
                     self._grad_reducer.all_gather_params()
                 else:
                     dist.all_gather_into_tensor(self.store.flat_param, self.store.param_shard.clone(), group=self._shard_group)
+        if self.model.cfg.is_moe and self.model.cfg.router_bias_update_rate > 0:
+            # auxiliary-loss-free balancing: selection biases follow the expert load of this step
+            for layer in self.model.layers:
+                upd = getattr(layer.mlp, "update_expert_bias", None)
+                if upd is not None:
+                    upd(self._shard_group)
         st = res["state"].tolist()
         self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
         return dict(self.last_step_stats)

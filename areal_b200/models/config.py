@@ -34,6 +34,11 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     router_aux_loss_coef: float = 0.0
+    router_score_func: str = "softmax"      # softmax | sigmoid (DeepSeek-V3 style gates)
+    router_scale: float = 1.0               # multiplies the selected gate weights
+    num_expert_groups: int = 0              # > 0: group-limited routing (experts chosen inside the best groups only)
+    num_limited_groups: int = 0
+    router_bias_update_rate: float = 0.0    # > 0: auxiliary-loss-free balancing (selection bias nudged against expert load)
     decoder_sparse_step: int = 1
     mlp_only_layers: list[int] = field(default_factory=list)
     # critic / reward heads
@@ -101,6 +106,11 @@ class ModelConfig:
             num_experts=d.get("num_experts", 0) or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0, norm_topk_prob=bool(d.get("norm_topk_prob", True)),
             router_aux_loss_coef=float(d.get("router_aux_loss_coef", 0.0) or 0.0),
+            router_score_func=d.get("scoring_func", d.get("router_score_func", "softmax")) or "softmax",
+            router_scale=float(d.get("routed_scaling_factor", d.get("router_scale", 1.0)) or 1.0),
+            num_expert_groups=int(d.get("n_group", d.get("num_expert_groups", 0)) or 0),
+            num_limited_groups=int(d.get("topk_group", d.get("num_limited_groups", 0)) or 0),
+            router_bias_update_rate=float(d.get("router_bias_update_rate", 0.0) or 0.0),
             decoder_sparse_step=d.get("decoder_sparse_step", 1) or 1, mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
         )
 
@@ -125,6 +135,9 @@ class ModelConfig:
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
                      router_aux_loss_coef=self.router_aux_loss_coef, decoder_sparse_step=self.decoder_sparse_step,
                      mlp_only_layers=self.mlp_only_layers)
+            if self.router_score_func != "softmax" or self.num_expert_groups or self.router_scale != 1.0 or self.router_bias_update_rate:
+                d.update(scoring_func=self.router_score_func, routed_scaling_factor=self.router_scale, n_group=self.num_expert_groups,
+                         topk_group=self.num_limited_groups, router_bias_update_rate=self.router_bias_update_rate)
         return d
 
     def save_pretrained(self, path: str) -> None:

@@ -137,22 +137,62 @@ class MoEMLP(nn.Module):
         self.w_gate_up = nn.Parameter(torch.empty(E, 2 * Im, H, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(E, H, Im, dtype=dtype, device=device))
         self.ep_dispatcher = None  # set by parallel.ep.ExpertParallel
+        if cfg.router_bias_update_rate > 0:
+            self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device), persistent=True)
+            self.register_buffer("tokens_per_expert", torch.zeros(E, dtype=torch.float32, device=device), persistent=False)
+        else:
+            self.expert_bias = None
         self.last_aux_loss: Optional[torch.Tensor] = None
         self.last_routed_experts: Optional[torch.Tensor] = None
 
     def route(self, x):
+        """Gate weights and expert ids per token (fp32). Scores are softmax or sigmoid gates; the
+        *choice* of experts may add a balancing bias and be limited to the best expert groups,
+        while the returned weights are always the unbiased scores of the chosen experts
+        (reference: areal/experimental/models/archon/moe/router.py:234-297)."""
+        cfg = self.cfg
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
         logits = F.linear(x.float(), self.router.float())
-        probs = torch.softmax(logits, dim=-1)
-        topw, tope = torch.topk(probs, self.cfg.num_experts_per_tok, dim=-1)
-        if self.cfg.norm_topk_prob:
+        probs = torch.sigmoid(logits) if cfg.router_score_func == "sigmoid" else torch.softmax(logits, dim=-1)
+        choice = probs if self.expert_bias is None else probs + self.expert_bias
+        if cfg.num_expert_groups > 0:
+            ng, keep = cfg.num_expert_groups, max(1, cfg.num_limited_groups)
+            per = E // ng
+            grouped = choice.view(-1, ng, per)
+            # a group's score: its two best experts when a bias is in play (DeepSeek-V3), else its best expert
+            gscore = grouped.topk(min(2, per), dim=-1).values.sum(-1) if self.expert_bias is not None else grouped.max(-1).values
+            gidx = gscore.topk(keep, dim=-1).indices
+            gmask = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, gidx, True)
+            choice = grouped.masked_fill(~gmask.unsqueeze(-1), float("-inf")).view(-1, E)
+        tope = torch.topk(choice, k, dim=-1).indices
+        topw = probs.gather(1, tope)
+        if cfg.norm_topk_prob:
             topw = topw / topw.sum(-1, keepdim=True).clamp(min=1e-20)
-        if self.cfg.router_aux_loss_coef > 0 and self.training:
-            E = self.cfg.num_experts
-            frac = torch.zeros(E, device=x.device).scatter_add_(0, tope.reshape(-1), torch.ones(tope.numel(), device=x.device))
-            frac = frac / tope.numel()
-            self.last_aux_loss = E * (frac * probs.mean(0)).sum() * self.cfg.router_aux_loss_coef
+        if cfg.router_scale != 1.0:
+            topw = topw * cfg.router_scale
+        if self.training and (cfg.router_aux_loss_coef > 0 or self.expert_bias is not None):
+            load = torch.zeros(E, device=x.device).scatter_add_(0, tope.reshape(-1), torch.ones(tope.numel(), device=x.device))
+            if self.expert_bias is not None:
+                self.tokens_per_expert.add_(load)
+            if cfg.router_aux_loss_coef > 0:
+                mean_p = probs.mean(0) if cfg.router_score_func != "sigmoid" else (probs / probs.sum(-1, keepdim=True).clamp(min=1e-20)).mean(0)
+                self.last_aux_loss = E * (load / tope.numel() * mean_p).sum() * cfg.router_aux_loss_coef
         self.last_routed_experts = tope
         return topw, tope
+
+    @torch.no_grad()
+    def update_expert_bias(self, group=None) -> None:
+        """Auxiliary-loss-free balancing: after an optimizer step, move each expert's selection bias
+        by ``router_bias_update_rate`` against its load since the last call (summed over ``group``)
+        (reference: areal/experimental/models/archon/moe/moe.py:119-146, DeepSeek-V3 sec. 2.1.2)."""
+        if self.expert_bias is None:
+            return
+        load = self.tokens_per_expert
+        if group is not None and torch.distributed.is_initialized():
+            torch.distributed.all_reduce(load, group=group)
+        self.expert_bias.add_(self.cfg.router_bias_update_rate * torch.sign(load.mean() - load))
+        self.expert_bias.sub_(self.expert_bias.mean())
+        load.zero_()
 
     def experts_forward(self, xs: torch.Tensor, counts: list[int], first_expert: int = 0) -> torch.Tensor:
         """xs: tokens sorted by (local) expert; counts[e] tokens for expert first_expert+e."""

@@ -31,114 +31,243 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv
 }
 
 // ------------------------------------------------------------------ paged decode attention
-// One CTA = (sequence b, kv head h, split s). 128 threads = 16 groups of 8 lanes; a group
-// handles one cached token at a time (8 lanes x 16 dims = D 128; for D 64 each lane holds 8).
-// Every group keeps an online-softmax state for the G = Hq/Hkv query heads that share the
-// kv head; groups are merged through shared memory; the CTA writes an (m, l, o) partial.
+// One CTA = (sequence b, kv head h, split s), 128 threads. The split's tokens are walked in chunks
+// of 64: the chunk's K and V rows are brought into shared memory with 16-byte asynchronous copies
+// (two stages, so one chunk is in flight while the other is consumed; three CTAs per SM keep about
+// 100 KB of loads in flight), then every warp works on its own 16 rows of the chunk:
+//   scores:  8 lanes per token, each lane 2 x 8 dims (conflict-free 128-byte reads of a row), the
+//            query heads of the group in registers four at a time;
+//   softmax: running (max, sum) per warp and query head, no block-wide exchange;
+//   output:  lane = D/32 dims, probabilities broadcast from shared memory.
+// The four warps' states are merged once at the end and the CTA writes an (m, l, o) partial.
+constexpr int DEC_CHUNK = 64;
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int D, int G>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                     const __nv_bfloat16* __restrict__ vc, const int* __restrict__ page_table,
                     const int* __restrict__ seq_lens, float* __restrict__ part_o, float* __restrict__ part_ml,
                     int Hq, int Hkv, int page_size, int max_pages, int num_splits, float scale) {
-  constexpr int EPL = D / 8;  // elements per lane
-  const int b = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
+  constexpr int NC = D / 64;            // 8-dim pieces per lane in the score phase
+  constexpr int DPL = D / 32;           // dims per lane in the output phase
+  constexpr int GH = G < 4 ? G : 4;     // query heads held in registers at a time
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int STAGE_BYTES = 2 * DEC_CHUNK * ROW_BYTES;   // K rows then V rows
+  constexpr int PIECES = DEC_CHUNK * ROW_BYTES / 16;       // 16-byte pieces per operand and chunk
+  extern __shared__ __align__(128) unsigned char dsm[];
+  float* sq = reinterpret_cast<float*>(dsm + 2 * STAGE_BYTES);      // [G][D] scaled queries
+  float* sp = sq + G * D;                                           // [DEC_CHUNK][G] probabilities
+  const int b = blockIdx.x, h = blockIdx.y, spl = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = tid >> 3, lg = tid & 7;
   const int len = seq_lens[b];
   const int per = (len + num_splits - 1) / num_splits;
-  const int t0 = sp * per, t1 = min(len, t0 + per);
-  const int grp = threadIdx.x >> 3, lg = threadIdx.x & 7;
-  const float sl2 = scale * 1.4426950408889634f;
-  const unsigned gmask = 0xFFu << ((threadIdx.x & 31) & ~7);
-
-  float qr[G][EPL];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = q + ((size_t)b * Hq + (size_t)h * G + g) * D + lg * EPL;
-#pragma unroll
-    for (int e = 0; e < EPL; e += 2) {
-      const float2 f = unpack_bf16(*reinterpret_cast<const uint32_t*>(qp + e));
-      qr[g][e] = f.x * sl2;
-      qr[g][e + 1] = f.y * sl2;
-    }
-  }
-  float m[G], l[G], o[G][EPL];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) o[g][e] = 0.f;
-  }
+  const int t0 = spl * per, t1 = min(len, t0 + per);
+  const int n_chunks = t1 > t0 ? (t1 - t0 + DEC_CHUNK - 1) / DEC_CHUNK : 0;
   const int* pt = page_table + (size_t)b * max_pages;
-  for (int t = t0 + grp; t < t1; t += 16) {
-    const int page = pt[t / page_size];
-    const size_t slot = (size_t)page * page_size + (t % page_size);
-    const __nv_bfloat16* kp = kc + (slot * Hkv + h) * D + lg * EPL;
-    const __nv_bfloat16* vp = vc + (slot * Hkv + h) * D + lg * EPL;
-    float kf[EPL], vf[EPL];
+  const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(dsm);
+  const float sl2 = scale * 1.4426950408889634f;
+
+  auto issue = [&](int c, int stage) {
+    const int base = t0 + c * DEC_CHUNK;
 #pragma unroll
-    for (int e = 0; e < EPL; e += 8) {
-      const uint4 kk = *reinterpret_cast<const uint4*>(kp + e);
-      const uint4 vv = *reinterpret_cast<const uint4*>(vp + e);
-      const uint32_t ka[4] = {kk.x, kk.y, kk.z, kk.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+    for (int i = 0; i < PIECES / 128; ++i) {
+      const int idx = tid + i * 128;
+      const int row = idx / (ROW_BYTES / 16), piece = idx % (ROW_BYTES / 16);
+      const int t = base + row;
+      const bool ok = t < t1;
+      size_t off = 0;
+      if (ok) {
+        const int page = pt[t / page_size];
+        off = (((size_t)page * page_size + (t % page_size)) * Hkv + h) * D + piece * 8;
+      }
+      const uint32_t dst = smem0 + stage * STAGE_BYTES + row * ROW_BYTES + piece * 16;
+      cp_async16(dst, kc + off, ok);
+      cp_async16(dst + DEC_CHUNK * ROW_BYTES, vc + off, ok);
+    }
+    cp_async_commit();
+  };
+
+  if (n_chunks > 0) issue(0, 0);
+  for (int i = tid; i < G * D; i += 128)
+    sq[i] = __bfloat162float(q[((size_t)b * Hq + (size_t)h * G) * D + i]) * sl2;
+  __syncthreads();
+
+  float m_run[G], l_run[G], o[G][DPL];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 a = unpack_bf16(ka[j]), c = unpack_bf16(va[j]);
-        kf[e + 2 * j] = a.x; kf[e + 2 * j + 1] = a.y;
-        vf[e + 2 * j] = c.x; vf[e + 2 * j + 1] = c.y;
+  for (int g = 0; g < G; ++g) {
+    m_run[g] = -INFINITY;
+    l_run[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) o[g][e] = 0.f;
+  }
+  float qr[GH][NC * 8];
+  if constexpr (G <= 4) {
+#pragma unroll
+    for (int g = 0; g < GH; ++g)
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qr[g][c * 8 + e] = sq[g * D + c * 64 + lg * 8 + e];
+  }
+
+  for (int c = 0; c < n_chunks; ++c) {
+    const int stage = c & 1;
+    if (c + 1 < n_chunks) {
+      issue(c + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const unsigned char* ks = dsm + stage * STAGE_BYTES;
+    const unsigned char* vs = ks + DEC_CHUNK * ROW_BYTES;
+    const int base = t0 + c * DEC_CHUNK;
+    // ---- scores of this warp's 16 rows: row = grp + 16 * i (grp = 4 * warp + 0..3)
+    float sc[4][G];
+#pragma unroll
+    for (int g0 = 0; g0 < G; g0 += GH) {
+      if constexpr (G > 4) {
+#pragma unroll
+        for (int g = 0; g < GH; ++g)
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) qr[g][cc * 8 + e] = sq[(g0 + g) * D + cc * 64 + lg * 8 + e];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = grp + 16 * i;
+        float kf[NC * 8];
+#pragma unroll
+        for (int cc = 0; cc < NC; ++cc) {
+          const uint4 kk = *reinterpret_cast<const uint4*>(ks + row * ROW_BYTES + cc * 128 + lg * 16);
+          const uint32_t ka[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 a = unpack_bf16(ka[j]);
+            kf[cc * 8 + 2 * j] = a.x;
+            kf[cc * 8 + 2 * j + 1] = a.y;
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < GH; ++g) {
+          float s = 0.f;
+#pragma unroll
+          for (int e = 0; e < NC * 8; ++e) s += qr[g][e] * kf[e];
+          s += __shfl_xor_sync(0xffffffffu, s, 1);
+          s += __shfl_xor_sync(0xffffffffu, s, 2);
+          s += __shfl_xor_sync(0xffffffffu, s, 4);
+          sc[i][g0 + g] = (base + row < t1) ? s : -INFINITY;
+        }
       }
     }
+    // ---- running max per warp, probabilities to shared memory, partial sums per group
+    float alpha[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      float s = 0.f;
+      float mx = fmaxf(fmaxf(sc[0][g], sc[1][g]), fmaxf(sc[2][g], sc[3][g]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float mn = fmaxf(m_run[g], mx);
+      const float mref = (mn == -INFINITY) ? 0.f : mn;
+      alpha[g] = fast_exp2(m_run[g] - mref);
+      m_run[g] = mn;
+      float ps = 0.f;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) s += qr[g][e] * kf[e];
-      // only the 8 lanes of this group take part: groups of one warp may run different
-      // numbers of iterations, so a full-warp mask would wait for lanes that never arrive
-      s += __shfl_xor_sync(gmask, s, 1);
-      s += __shfl_xor_sync(gmask, s, 2);
-      s += __shfl_xor_sync(gmask, s, 4);
-      const float mn = fmaxf(m[g], s);
-      const float a = fast_exp2(m[g] - mn), p = fast_exp2(s - mn);
-      l[g] = l[g] * a + p;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) o[g][e] = o[g][e] * a + p * vf[e];
-      m[g] = mn;
+      for (int i = 0; i < 4; ++i) {
+        const float p = fast_exp2(sc[i][g] - mref);
+        sc[i][g] = p;
+        ps += p;
+      }
+      l_run[g] = l_run[g] * alpha[g] + ps;     // the group's rows (same value in its 8 lanes)
     }
-  }
-  // merge the 16 groups, one query head at a time (keeps shared memory at 8 KB)
-  __shared__ float sm_m[16][G], sm_l[16][G];
-  __shared__ float sm_o[16][D];
-  if (lg == 0) {
+    if (lg == 0) {
 #pragma unroll
-    for (int g = 0; g < G; ++g) { sm_m[grp][g] = m[g]; sm_l[grp][g] = l[g]; }
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int g = 0; g < G; ++g) sp[(grp + 16 * i) * G + g] = sc[i][g];
+    }
+    __syncwarp();
+    // ---- output: the same 16 rows, lane = DPL dims
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) o[g][e] *= alpha[g];
+#pragma unroll 4
+    for (int j = 0; j < 16; ++j) {
+      const int row = 4 * warp + (j & 3) + 16 * (j >> 2);
+      float vf[DPL];
+      if constexpr (DPL == 4) {
+        const uint2 vv = *reinterpret_cast<const uint2*>(vs + row * ROW_BYTES + lane * 8);
+        const float2 a = unpack_bf16(vv.x), c2 = unpack_bf16(vv.y);
+        vf[0] = a.x; vf[1] = a.y; vf[2] = c2.x; vf[3] = c2.y;
+      } else {
+        const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(vs + row * ROW_BYTES + lane * 4));
+        vf[0] = a.x; vf[1] = a.y;
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float p = sp[row * G + g];
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) o[g][e] += p * vf[e];
+      }
+    }
+    __syncthreads();   // every warp is done with this stage before the next copies land in it
   }
+
+  // ---- merge the four warps (stage memory is free now)
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    __syncthreads();
+    l_run[g] += __shfl_xor_sync(0xffffffffu, l_run[g], 8);
+    l_run[g] += __shfl_xor_sync(0xffffffffu, l_run[g], 16);
+  }
+  float* mo = reinterpret_cast<float*>(dsm);          // [4][G][D]
+  float* mm = mo + 4 * G * D;                         // [4][G]
+  float* ml = mm + 4 * G;                             // [4][G]
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) sm_o[grp][lg * EPL + e] = o[g][e];
-    __syncthreads();
-    if (threadIdx.x < D) {
-      const int d = threadIdx.x;
-      float mm = -INFINITY;
+  for (int g = 0; g < G; ++g) {
 #pragma unroll
-      for (int r = 0; r < 16; ++r) mm = fmaxf(mm, sm_m[r][g]);
-      float ll = 0.f, oo = 0.f;
-#pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        const float w = (sm_m[r][g] == -INFINITY) ? 0.f : fast_exp2(sm_m[r][g] - mm);
-        ll += sm_l[r][g] * w;
-        oo += sm_o[r][d] * w;
-      }
-      const size_t pidx = ((size_t)b * Hq + (size_t)h * G + g) * num_splits + sp;
-      part_o[pidx * D + d] = oo;
-      if (d == 0) {
-        part_ml[pidx * 2] = mm;
-        part_ml[pidx * 2 + 1] = ll;
-      }
+    for (int e = 0; e < DPL; ++e) mo[(warp * G + g) * D + lane * DPL + e] = o[g][e];
+    if (lane == 0) {
+      mm[warp * G + g] = m_run[g];
+      ml[warp * G + g] = l_run[g];
     }
   }
+  __syncthreads();
+  for (int i = tid; i < G * D; i += 128) {
+    const int g = i / D, d = i - g * D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mm[w * G + g]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mm[w * G + g];
+      const float wt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mx);
+      ll += ml[w * G + g] * wt;
+      oo += mo[(w * G + g) * D + d] * wt;
+    }
+    const size_t pidx = ((size_t)b * Hq + (size_t)h * G + g) * num_splits + spl;
+    part_o[pidx * D + d] = oo;
+    if (d == 0) {
+      part_ml[pidx * 2] = mx;
+      part_ml[pidx * 2 + 1] = ll;
+    }
+  }
+}
+
+template <int D, int G>
+constexpr int decode_smem_bytes() {
+  return 2 * (2 * DEC_CHUNK * D * 2) + (G * D + DEC_CHUNK * G) * 4;
 }
 
 // out[b, hq, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
@@ -252,9 +381,16 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
                          float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int page_size,
                          int max_pages, int splits, float scale, cudaStream_t s) {
   dim3 grid(B, Hkv, splits);
-  paged_decode_kernel<D, G><<<grid, 128, 0, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
-                                                 (const __nv_bfloat16*)vc, pt, lens, part_o, part_ml, Hq, Hkv,
-                                                 page_size, max_pages, splits, scale);
+  constexpr int SMEM = decode_smem_bytes<D, G>();
+  static_assert(SMEM >= (4 * G * D + 8 * G) * 4, "the merge buffers alias the stage memory");
+  auto kern = paged_decode_kernel<D, G>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 2;
+    attr_set = true;
+  }
+  kern<<<grid, 128, SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens, part_o, part_ml,
+                               Hq, Hkv, page_size, max_pages, splits, scale);
   decode_combine_kernel<D><<<B * Hq, D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

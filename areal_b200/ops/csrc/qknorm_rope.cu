@@ -62,7 +62,7 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        const __nv_bfloat16* __restrict__ wk, const int* __restrict__ pos,
                        const float* __restrict__ cosb, const float* __restrict__ sinb,
                        __nv_bfloat16* __restrict__ qk, float* __restrict__ rstd_out, int T, int nq, int nkv,
-                       long long qkv_stride, float eps) {
+                       long long qkv_stride, float eps, int hsplit) {
   constexpr int D = 32 * VEC;
   constexpr int HALF = D / 2;
   const int lane = threadIdx.x & 31;
@@ -80,22 +80,28 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   }
   // One token per warp at a time: its heads share the position, so cos / sin are fetched once
   // per token and the per-row work is a single independent load -> reduce -> store chain.
-  for (int tok = warp0; tok < T; tok += nwarps) {
+  // With few tokens (decode) a token's heads are split over ``hsplit`` warps so the launch is
+  // not one long serial walk per token.
+  const int hps = ((heads + hsplit - 1) / hsplit + QK_UNROLL - 1) / QK_UNROLL * QK_UNROLL;
+  for (long long w = warp0; w < (long long)T * hsplit; w += nwarps) {
+    const int tok = (int)(w / hsplit);
+    const int hbeg = (int)(w - (long long)tok * hsplit) * hps;
+    const int hend = min(heads, hbeg + hps);
     const int p = pos[tok];
     float c[VEC], s[VEC];
     load_f32_vec<VEC>(cosb + (size_t)p * HALF + f0, c);
     load_f32_vec<VEC>(sinb + (size_t)p * HALF + f0, s);
     const __nv_bfloat16* src = qkv + (size_t)tok * qkv_stride + e0;
     __nv_bfloat16* dst = qk + (size_t)tok * heads * D + e0;
-    for (int h0 = 0; h0 < heads; h0 += QK_UNROLL) {
+    for (int h0 = hbeg; h0 < hend; h0 += QK_UNROLL) {
       float x[QK_UNROLL][VEC];
 #pragma unroll
       for (int u = 0; u < QK_UNROLL; ++u)
-        if (h0 + u < heads) load_bf16_vec<VEC>(src + (size_t)(h0 + u) * D, x[u]);
+        if (h0 + u < hend) load_bf16_vec<VEC>(src + (size_t)(h0 + u) * D, x[u]);
 #pragma unroll
       for (int u = 0; u < QK_UNROLL; ++u) {
         const int h = h0 + u;
-        if (h >= heads) break;
+        if (h >= hend) break;
         float y[VEC];
         if (has_norm) {
           float ss = 0.f;
@@ -243,17 +249,25 @@ int ab2_qknorm_rope_fwd(const void* qkv, const void* wq, const void* wk, const i
   if (D != 64 && D != 128) return 10;
   if ((wq == nullptr) != (wk == nullptr)) return 11;
   if (qkv_stride & 3) return 12;
-  const long long want = ((long long)T + 7) / 8;   // 8 warps per CTA, one token per warp step
+  // few tokens (decode): split each token's heads over several warps until the GPU is covered
+  const int max_split = (nq + nkv + ab2::QK_UNROLL - 1) / ab2::QK_UNROLL;
+  int hsplit = 1;
+  if ((long long)T < 148 * 8) {
+    hsplit = (int)((148 * 8 * 2) / (long long)T);
+    if (hsplit > max_split) hsplit = max_split;
+    if (hsplit < 1) hsplit = 1;
+  }
+  const long long want = ((long long)T * hsplit + 7) / 8;   // 8 warps per CTA, one (token, head range) per warp step
   const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
   auto s = (cudaStream_t)stream;
   if (D == 128)
     ab2::qknorm_rope_fwd_kernel<4><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
                                                         (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk,
-                                                        rstd, T, nq, nkv, qkv_stride, eps);
+                                                        rstd, T, nq, nkv, qkv_stride, eps, hsplit);
   else
     ab2::qknorm_rope_fwd_kernel<2><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
                                                         (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk,
-                                                        rstd, T, nq, nkv, qkv_stride, eps);
+                                                        rstd, T, nq, nkv, qkv_stride, eps, hsplit);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

@@ -188,3 +188,49 @@ def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port):
                        capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("SPLIT_OK") == world
+
+
+def test_moe_router_variants():
+    """Sigmoid gates, group-limited choice, scaling, and the auxiliary-loss-free balancing bias."""
+    import torch
+
+    from areal_b200.models.config import preset
+    from areal_b200.models.decoder import MoEMLP
+
+    torch.manual_seed(0)
+    cfg = preset("tiny-qwen3-moe", router_score_func="sigmoid", num_expert_groups=4, num_limited_groups=2, router_scale=2.5,
+                 router_bias_update_rate=0.01, norm_topk_prob=True)
+    m = MoEMLP(cfg, torch.float32, "cpu")
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    m.train()
+    x = torch.randn(64, cfg.hidden_size)
+    w, e = m.route(x)
+    assert w.shape == (64, 2) and e.shape == (64, 2)
+    # weights: normalised sigmoid gates of the chosen experts times the scale
+    probs = torch.sigmoid(x @ m.router.t())
+    chosen = probs.gather(1, e)
+    assert torch.allclose(w, chosen / chosen.sum(-1, keepdim=True) * 2.5, atol=1e-6)
+    # group-limited: 8 experts in 4 groups of 2, both experts of a token come from at most 2 groups
+    assert ((e // 2)[:, 0:1] != (e // 2)).sum(-1).max() <= 1
+    best_groups = probs.view(64, 4, 2).sum(-1).topk(2, dim=-1).indices   # with a bias: groups ranked by their two best experts
+    assert all(int(g) in best_groups[i].tolist() for i in range(64) for g in (e[i] // 2))
+    # balancing: the load was recorded; the update moves the bias against it and keeps it centred
+    assert m.tokens_per_expert.sum() == 128
+    load = m.tokens_per_expert.clone()
+    m.update_expert_bias()
+    assert m.tokens_per_expert.sum() == 0 and abs(float(m.expert_bias.sum())) < 1e-6
+    over, under = load.argmax(), load.argmin()
+    if load[over] > load.mean() > load[under]:
+        assert m.expert_bias[over] < m.expert_bias[under]
+    # the bias changes the choice only, not the weights
+    m.expert_bias[:] = 0
+    m.expert_bias[3] = 10.0
+    w2, e2 = m.route(x)
+    assert (e2 == 3).any(dim=-1).float().mean() > 0.4   # expert 3 is picked whenever its group is among the chosen ones
+    p2 = probs.gather(1, e2)
+    assert torch.allclose(w2, p2 / p2.sum(-1, keepdim=True) * 2.5, atol=1e-6)
+    y = m(x)
+    assert y.shape == x.shape and torch.isfinite(y).all()
+    y.sum().backward()
+    assert m.router.grad is not None and torch.isfinite(m.router.grad).all()

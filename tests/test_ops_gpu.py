@@ -355,3 +355,43 @@ def test_grouped_gemm_matches_fp32(counts):
     ref = torch.cat(outs, 0)
     ref.backward(g.float())
     assert _rel_err(y, ref) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(w.grad, wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,page_size,splits", [(128, 32, 8, 64, 4), (128, 8, 1, 16, 3), (128, 12, 2, 64, 1), (64, 4, 2, 16, 4),
+                                                       (64, 16, 2, 32, 2)])
+def test_paged_decode_attention_matches_fp32(D, Hq, Hkv, page_size, splits):
+    """Split-KV paged decode attention (K/V chunks staged in shared memory) against fp32 softmax
+    attention over each row's gathered cache; rows of length 0 (idle slots) and 1 included."""
+    g = torch.Generator(device="cuda").manual_seed(D + Hq + page_size)
+    B, max_len = 9, 700
+    lens = torch.randint(2, max_len + 1, (B,), device="cuda", generator=g).int()
+    lens[0], lens[1], lens[2] = 0, 1, max_len
+    max_pages = (max_len + page_size - 1) // page_size
+    n_pages = B * max_pages + 5
+    kc = torch.randn(n_pages * page_size, Hkv, D, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(n_pages * page_size, Hkv, D, device="cuda", generator=g).bfloat16()
+    q = torch.randn(B, Hq, D, device="cuda", generator=g).bfloat16()
+    pt = torch.randperm(n_pages, device="cuda", generator=g)[: B * max_pages].int().view(B, max_pages).contiguous()
+    po = torch.empty(B * Hq * splits * D, device="cuda")
+    pml = torch.empty(B * Hq * splits * 2, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    rc = oplib.get_lib().ab2_paged_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pt.data_ptr(), lens.data_ptr(), po.data_ptr(),
+                                          pml.data_ptr(), out.data_ptr(), B, Hq, Hkv, D, page_size, max_pages, splits, D ** -0.5,
+                                          oplib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert oplib.kernel_error() == 0
+    G = Hq // Hkv
+    for b in range(B):
+        n = int(lens[b])
+        if n == 0:
+            assert (out[b].float() == 0).all()
+            continue
+        t = torch.arange(n, device="cuda")
+        slots = pt[b, t // page_size].long() * page_size + t % page_size
+        k = kc[slots].float().repeat_interleave(G, dim=1)          # [n, Hq, D]
+        v = vc[slots].float().repeat_interleave(G, dim=1)
+        s = torch.einsum("hd,nhd->hn", q[b].float(), k) * D ** -0.5
+        ref = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), v)
+        err = ((out[b].float() - ref).norm() / ref.norm()).item()
+        assert err < 1e-2, f"row {b} (len {n}): relative error {err}"
