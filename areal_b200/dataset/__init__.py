@@ -6,7 +6,7 @@ from __future__ import annotations
 import json
 import os
 import random
-from typing import Any, Callable, Optional
+from typing import Sequence, Any, Callable, Optional
 
 import torch
 from torch.utils.data import Dataset
@@ -113,6 +113,60 @@ def small_id_fraction_reward_fn(prompt, completion, prompt_ids, completion_ids, 
     return sum(1 for t in completion_ids if t < threshold) / max(1, len(completion_ids))
 
 
+class CountShapesDataset(Dataset):
+    """Procedural vision-language task (offline stand-in for clevr_count_70k): a picture with
+    ``k`` bright squares on a dark canvas; the question asks for ``k``. Items carry ``images``
+    (PIL), ``input_ids`` (``[bos, vision_start, image, question tokens...]``) and ``answer``."""
+
+    def __init__(self, size: int = 1024, seed: int = 1, image_size: int = 112, max_shapes: int = 6, image_token_id: int = 1000,
+                 vision_start_token_id: int = 1002, question_ids: Sequence[int] = (11, 12, 13)):
+        self.size, self.seed, self.image_size, self.max_shapes = size, seed, image_size, max_shapes
+        self.prefix = [5, vision_start_token_id, image_token_id] + list(question_ids)
+
+    def __len__(self):
+        return self.size
+
+    def __getitem__(self, i):
+        import numpy as np
+        from PIL import Image
+
+        rng = np.random.default_rng(self.seed * 1000003 + i)
+        k = int(rng.integers(1, self.max_shapes + 1))
+        S = self.image_size
+        img = np.full((S, S, 3), 16, dtype=np.uint8)
+        cell = S // 4
+        for c in rng.choice(16, size=k, replace=False):
+            y, x = (c // 4) * cell + cell // 4, (c % 4) * cell + cell // 4
+            img[y:y + cell // 2, x:x + cell // 2] = rng.integers(160, 255, 3)
+        return dict(images=[Image.fromarray(img)], input_ids=list(self.prefix), answer=k, idx=i)
+
+
+def count_shapes_reward_fn(prompt, completion, prompt_ids, completion_ids, answer=None, **kwargs) -> float:
+    """1 when the first generated token id equals ``20 + answer`` (digit tokens of the toy vocabulary)."""
+    return float(bool(completion_ids) and int(completion_ids[0]) == 20 + int(answer))
+
+
+def _record_images(r: dict) -> list:
+    """Images of a record in the layouts of geometry3k / clevr_count (``images`` as a list of
+    ``{"bytes": ...}`` / bytes / paths, or a single ``image``)."""
+    from ..utils.image import load_image
+
+    raw = r.get("images")
+    if raw is None and r.get("image") is not None:
+        raw = [r["image"]]
+    out = []
+    for im in raw or []:
+        if isinstance(im, dict):
+            im = im.get("bytes") or im.get("path")
+        if isinstance(im, str) and os.path.exists(im):
+            from PIL import Image
+
+            out.append(Image.open(im).convert("RGB"))
+        else:
+            out.append(load_image(im))
+    return out
+
+
 def _load_records(path: str) -> list[dict]:
     if os.path.isdir(path):
         files = sorted(os.path.join(path, f) for f in os.listdir(path) if f.endswith((".jsonl", ".json", ".parquet")))
@@ -158,6 +212,10 @@ def get_custom_dataset(path: str, type: str = "rl", split: str = "train", tokeni
         return RandomTokenDataset(kwargs.get("size", 4096), kwargs.get("prompt_len", 512), kwargs.get("vocab_size", 151936),
                                   seed=kwargs.get("seed", 1), median_len=kwargs.get("median_len", 1024),
                                   max_len=kwargs.get("max_len", 4096))
+    if path.startswith("synthetic/count_shapes"):
+        return CountShapesDataset(size=kwargs.get("size", 1024), seed=kwargs.get("seed", 1), image_size=kwargs.get("image_size", 112),
+                                  image_token_id=kwargs.get("image_token_id", 1000),
+                                  vision_start_token_id=kwargs.get("vision_start_token_id", 1002))
     if not os.path.exists(path):
         raise FileNotFoundError(f"dataset '{path}' not found locally (no network access to fetch it)")
     recs = _load_records(os.path.join(path, split) if os.path.isdir(os.path.join(path, split)) else path)
@@ -182,8 +240,18 @@ def get_custom_dataset(path: str, type: str = "rl", split: str = "train", tokeni
     def rw_transform(r):
         return dict(chosen_ids=tokenizer.encode(r["chosen"])[:max_length], rejected_ids=tokenizer.encode(r["rejected"])[:max_length])
 
-    tf = {"rl": rl_transform, "sft": sft_transform, "rw": rw_transform, "dpo": rw_transform}.get(type)
-    ds = RecordDataset(recs, tf if (tokenizer is not None or type == "rl") else None)
+    def vl_rl_transform(r):
+        # geometry3k / clevr_count style: question text + pictures; the chat template gets one image slot per picture
+        q = r.get("problem") or r.get("question") or r.get("prompt") or ""
+        images = _record_images(r)
+        content = [{"type": "image"} for _ in images] + [{"type": "text", "text": q.replace("<image>", "")}]
+        out = {k: v for k, v in r.items() if k not in ("images", "image")}
+        out["messages"] = [{"role": "user", "content": content}]
+        out["images"] = images
+        return out
+
+    tf = {"rl": rl_transform, "sft": sft_transform, "rw": rw_transform, "dpo": rw_transform, "vl_rl": vl_rl_transform}.get(type)
+    ds = RecordDataset(recs, tf if (tokenizer is not None or type in ("rl", "vl_rl")) else None)
     if max_length and type == "rl" and tokenizer is not None:
         keep = [i for i in range(len(ds)) if len(ds[i]["input_ids"]) <= max_length]
         ds = RecordDataset([recs[i] for i in keep], tf)

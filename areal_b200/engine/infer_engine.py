@@ -66,6 +66,8 @@ class _Seq:
     aborted: bool = False
     top_p: float = 1.0
     top_k: int = 0
+    mm: Any = None                         # vision-language request: {"pixel_values", "image_grid_thw"}
+    rope_delta: int = 0                    # M-RoPE: rotary position of token i (after the prompt) = i + rope_delta
 
 
 class PagedKVCache:
@@ -297,6 +299,26 @@ class NativeInferenceEngine(InferenceEngine):
         self.continue_generation()
 
     # ------------------------------------------------------------------ request API
+    def _prepare_multi_modal(self, req: ModelRequest, prompt: list[int]):
+        """Images of a vision-language request -> patches for the tower plus the M-RoPE offset of
+        the tokens generated after the prompt. ``image_data`` entries may be PIL images, uint8
+        arrays, raw bytes or base64 strings (optionally ``data:`` URLs); the prompt must already
+        hold one placeholder token per merged patch (what the HF processor produces)."""
+        images = getattr(req, "image_data", None)
+        if not images or not getattr(self.model.cfg, "is_vlm", False):
+            return None, 0
+        from ..models.vision import mrope_position_ids, preprocess_images
+        from ..utils.image import load_image
+
+        pre = getattr(req, "metadata", None) or {}
+        if isinstance(pre, dict) and pre.get("pixel_values") is not None:
+            px, grid = torch.as_tensor(pre["pixel_values"]), torch.as_tensor(pre["image_grid_thw"]).view(-1, 3).long()
+        else:
+            px, grid = preprocess_images([load_image(im) for im in images], self.model.vcfg)
+        cfg = self.model.cfg
+        _, delta = mrope_position_ids(torch.tensor(prompt), grid, cfg.image_token_id, self.model.vcfg.spatial_merge_size, cfg.video_token_id)
+        return {"pixel_values": px, "image_grid_thw": grid}, int(delta)
+
     async def agenerate(self, req: ModelRequest) -> ModelResponse:
         """Interruptible generation: loops over engine submissions until the request stops for
         a real reason; every segment is tagged with the weight version it ran under."""
@@ -314,6 +336,7 @@ class NativeInferenceEngine(InferenceEngine):
         tokens = prompt
         remaining = budget
         loop = asyncio.get_running_loop()
+        mm, rope_delta = self._prepare_multi_modal(req, prompt)
         while stop_reason not in ("stop", "tool_calls", "length") and len(out_tok) < budget:
             while self._gen_paused.is_set():
                 await asyncio.sleep(0.002)
@@ -326,7 +349,8 @@ class NativeInferenceEngine(InferenceEngine):
                        greedy=bool(g.greedy) or g.temperature == 0.0,
                        stop_ids=set(g.stop_token_ids or []), ignore_eos=g.ignore_eos,
                        seed=(g.seed if g.seed is not None else zlib.crc32(req.rid.encode())) & 0x7FFFFFFF, future=(loop, fut),
-                       t_submit=time.perf_counter(), top_p=g.top_p, top_k=0 if g.top_k >= 10 ** 7 else int(g.top_k))
+                       t_submit=time.perf_counter(), top_p=g.top_p, top_k=0 if g.top_k >= 10 ** 7 else int(g.top_k),
+                       mm=mm, rope_delta=rope_delta)
             with self._lock:
                 self._waiting.append(seq)
             seg_tokens, seg_lps, seg_vers, stop_reason, t_first = await fut
@@ -459,7 +483,12 @@ class NativeInferenceEngine(InferenceEngine):
         lens = [len(s.tokens) for s in batch]
         ids = torch.tensor([t for s in batch for t in s.tokens], dtype=torch.long)
         cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
-        hidden = self.model(ids, cu, max_seqlen=max(lens))
+        if any(s.mm is not None for s in batch):
+            from ..models.vlm import collect_multi_modal
+
+            hidden = self.model(ids, cu, max_seqlen=max(lens), mm=collect_multi_modal([s.mm for s in batch]))
+        else:
+            hidden = self.model(ids, cu, max_seqlen=max(lens))
         last = hidden[(cu[1:] - 1).long()]
         logits = self.model.logits(last)
         self._step += 1
@@ -591,7 +620,14 @@ class NativeInferenceEngine(InferenceEngine):
         ids, pos, slots, cu = (t.pin_memory().to(dev, non_blocking=True) for t in (ids, pos, slots, cu))
         pb = PackedBatch(cu, pos, Tp, max(lens))
         fns = self._layer_attn_fns("prefill", slots=slots, cu=cu, tile_info=pb.tile_info)
-        hidden = self.model.forward_hidden(ids, pb, attn_fns=fns)
+        if any(s.mm is not None for s in seqs):
+            from ..models.vlm import collect_multi_modal
+
+            mm = collect_multi_modal([s.mm for s in seqs])
+            mm = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in mm.items()}
+            hidden = self.model.forward_hidden(ids, pb, attn_fns=fns, mm=mm)
+        else:
+            hidden = self.model.forward_hidden(ids, pb, attn_fns=fns)
         last_idx = torch.tensor([c - 1 for c in cu_list[1:len(seqs) + 1]], dtype=torch.long, device=dev)
         logits = self.model.logits(hidden[last_idx].contiguous())
         toks, lps = self._sample_cuda(logits, seqs)
@@ -650,7 +686,7 @@ class NativeInferenceEngine(InferenceEngine):
         self.hn_inv_temp[r] = 1.0 if s.greedy else 1.0 / max(s.temperature, 1e-6)
         p = len(s.tokens) - 1              # position of the token the next decode step feeds
         self.hn_tokens[r] = s.tokens[-1]
-        self.hn_pos[r] = p
+        self.hn_pos[r] = p + s.rope_delta  # rotary position; the cache slot comes from hn_lens
         self.hn_lens[r] = p + 1
 
     def _free_row(self, s: _Seq):
@@ -694,8 +730,8 @@ class NativeInferenceEngine(InferenceEngine):
         hi = max(s.row for s in seqs) + 1
         B = min(next(b for b in DECODE_BUCKETS if b >= hi), self.max_batch)
         ps = self.cache.page_size
-        pos = self.hn_pos[:B]
         active = self.hn_lens[:B] > 0
+        pos = np.maximum(self.hn_lens[:B] - 1, 0)   # index of the fed token inside its sequence
         page = self.hn_pt[np.arange(B), np.minimum(pos // ps, self.max_pages_per_seq - 1)]
         self.hn_slots[:B] = np.where(active, page * ps + pos % ps, -1)
         self.d_state[:B].copy_(self.h_state[:B], non_blocking=True)

@@ -270,6 +270,8 @@ class B200TrainEngine(TrainEngine):
         if cfg.optimizer is not None:
             total = ft_spec.total_train_steps if ft_spec is not None else 1
             self.optimizer = ShardedAdamW(self.store, cfg.optimizer, total_steps=total, group=self._shard_group)
+        if self.sp_size * tp > 1 and model_config.is_vlm:
+            raise NotImplementedError("vision-language models run data-parallel only (no sequence / tensor parallelism yet)")
         if self.sp_size > 1:
             from ..parallel.ulysses import install_ulysses
 
@@ -430,7 +432,15 @@ class B200TrainEngine(TrainEngine):
             pb_local.full_position_ids = pb.position_ids
             hidden = self.model.forward_hidden(ids[sl], pb_local)
             return hidden, labels[sl], sl
-        hidden = self.model.forward_hidden(ids, pb)
+        if getattr(self.model.cfg, "is_vlm", False):
+            from ..models.vlm import collect_multi_modal
+
+            mm = collect_multi_modal(mb.get("multi_modal_input"))
+            if mm is not None:
+                mm = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mm.items()}
+            hidden = self.model.forward_hidden(ids, pb, mm=mm)
+        else:
+            hidden = self.model.forward_hidden(ids, pb)
         return hidden, labels, slice(0, T)
 
     # ------------------------------------------------------------------ train / eval / forward

@@ -43,6 +43,21 @@ class ModelConfig:
     mlp_only_layers: list[int] = field(default_factory=list)
     # critic / reward heads
     is_critic: bool = False
+    # vision-language models (Qwen2-VL / Qwen2.5-VL): HF ``vision_config`` dict, placeholder ids, M-RoPE sections
+    vision: Optional[dict] = None
+    image_token_id: int = 151655
+    video_token_id: int = 151656
+    vision_start_token_id: int = 151652
+    mrope_section: list[int] = field(default_factory=list)
+
+    @property
+    def is_vlm(self) -> bool:
+        return self.vision is not None
+
+    def vision_config(self):
+        from .vision import VisionConfig
+
+        return VisionConfig.from_hf_dict(self.vision, self.hidden_size, self.vision.get("model_type", "qwen2_vl"))
 
     @property
     def q_size(self) -> int:
@@ -91,6 +106,20 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "qwen2")
+        vl = None
+        if mt in ("qwen2_vl", "qwen2_5_vl"):
+            # text fields sit at the top level (older checkpoints) or under ``text_config``
+            vl = dict(d.get("vision_config") or {})
+            vl["model_type"] = mt
+            top = d
+            d = dict(d.get("text_config") or {})
+            for k, v in top.items():
+                if k not in ("text_config", "vision_config"):
+                    d.setdefault(k, v)
+            rs = d.get("rope_scaling") or d.get("rope_parameters") or {}
+            d["_mrope_section"] = list(rs.get("mrope_section", [16, 24, 24]))
+            d["attention_bias"] = True
+            mt = "qwen2"
         arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "llama": "qwen2"}.get(mt)
         if arch is None:
             raise ValueError(f"unsupported model_type '{mt}'")
@@ -112,6 +141,9 @@ class ModelConfig:
             num_limited_groups=int(d.get("topk_group", d.get("num_limited_groups", 0)) or 0),
             router_bias_update_rate=float(d.get("router_bias_update_rate", 0.0) or 0.0),
             decoder_sparse_step=d.get("decoder_sparse_step", 1) or 1, mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
+            vision=vl, mrope_section=list(d.get("_mrope_section", [])),
+            image_token_id=int(d.get("image_token_id", 151655)), video_token_id=int(d.get("video_token_id", 151656)),
+            vision_start_token_id=int(d.get("vision_start_token_id", 151652)),
         )
 
     @classmethod
@@ -130,6 +162,13 @@ class ModelConfig:
             tie_word_embeddings=self.tie_word_embeddings, attention_bias=self.attention_bias,
             max_position_embeddings=self.max_position_embeddings, hidden_act="silu", torch_dtype="bfloat16",
         )
+        if self.is_vlm:
+            vmt = self.vision.get("model_type", "qwen2_vl")
+            d.update(model_type=vmt, architectures=[{"qwen2_vl": "Qwen2VLForConditionalGeneration",
+                                                     "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration"}[vmt]],
+                     vision_config=dict(self.vision), image_token_id=self.image_token_id, video_token_id=self.video_token_id,
+                     vision_start_token_id=self.vision_start_token_id,
+                     rope_scaling=dict(type="mrope", mrope_section=list(self.mrope_section)))
         if self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
@@ -157,6 +196,23 @@ PRESETS = {
                            head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False,
                            attention_bias=False, qk_norm=True, num_experts=8, num_experts_per_tok=2,
                            moe_intermediate_size=128),
+    "tiny-qwen2-vl": dict(arch="qwen2", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                          head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False, attention_bias=True,
+                          image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, mrope_section=[8, 12, 12],
+                          vision=dict(model_type="qwen2_vl", depth=2, embed_dim=64, num_heads=4, mlp_ratio=2, in_chans=3, patch_size=14,
+                                      temporal_patch_size=2, spatial_merge_size=2, hidden_size=256)),
+    "tiny-qwen2.5-vl": dict(arch="qwen2", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                            head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False, attention_bias=True,
+                            image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, mrope_section=[8, 12, 12],
+                            vision=dict(model_type="qwen2_5_vl", depth=2, hidden_size=64, intermediate_size=96, num_heads=4, in_chans=3,
+                                        patch_size=14, temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=256, window_size=56,
+                                        fullatt_block_indexes=[1])),
+    "qwen2.5-vl-7b": dict(arch="qwen2", vocab_size=152064, hidden_size=3584, num_layers=28, num_heads=28, num_kv_heads=4,
+                          head_dim=128, intermediate_size=18944, rope_theta=1e6, tie_word_embeddings=False, attention_bias=True,
+                          max_position_embeddings=128000, mrope_section=[16, 24, 24],
+                          vision=dict(model_type="qwen2_5_vl", depth=32, hidden_size=1280, intermediate_size=3420, num_heads=16, in_chans=3,
+                                      patch_size=14, temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=3584, window_size=112,
+                                      fullatt_block_indexes=[7, 15, 23, 31])),
     "qwen2.5-1.5b": dict(arch="qwen2", vocab_size=151936, hidden_size=1536, num_layers=28, num_heads=12, num_kv_heads=2,
                          head_dim=128, intermediate_size=8960, rope_theta=1e6, tie_word_embeddings=True,
                          attention_bias=True),

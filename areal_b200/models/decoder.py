@@ -323,10 +323,13 @@ class CausalLM(nn.Module):
             self._rope_cache = {key: OF.rope_tables(max_pos, self.cfg.head_dim, self.cfg.rope_theta, device)}
         return self._rope_cache[key]
 
-    def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None) -> torch.Tensor:
-        """input_ids: [T] -> final normed hidden states [T, H]."""
-        cos, sin = self.rope(input_ids.device, max(self.cfg.max_position_embeddings, pb.max_seqlen + 1))
-        h = OF.embedding(input_ids, self.embed_tokens)
+    def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None, inputs_embeds: Optional[torch.Tensor] = None,
+                       rope: Optional[tuple] = None) -> torch.Tensor:
+        """input_ids: [T] -> final normed hidden states [T, H]. ``inputs_embeds`` replaces the
+        embedding lookup; ``rope = (cos, sin)`` replaces the position tables (rows are then
+        selected by ``pb.position_ids`` exactly like the default tables)."""
+        cos, sin = rope if rope is not None else self.rope(input_ids.device, max(self.cfg.max_position_embeddings, pb.max_seqlen + 1))
+        h = inputs_embeds if inputs_embeds is not None else OF.embedding(input_ids, self.embed_tokens)
         resid = None
         for i, layer in enumerate(self.layers):
             fn = attn_fns[i] if attn_fns is not None else None
@@ -381,15 +384,19 @@ class CausalLM(nn.Module):
                 layer.mlp.last_aux_loss = None
         return tot
 
-    def forward(self, input_ids, cu_seqlens, position_ids=None, max_seqlen: int = 0):
+    def forward(self, input_ids, cu_seqlens, position_ids=None, max_seqlen: int = 0, **kw):
         from ..utils.data import positions_from_cu_seqlens
 
         T = input_ids.shape[0]
         if position_ids is None:
             position_ids = positions_from_cu_seqlens(cu_seqlens, T)
         pb = PackedBatch(cu_seqlens, position_ids, T, max_seqlen)
-        return self.forward_hidden(input_ids, pb)
+        return self.forward_hidden(input_ids, pb, **kw)
 
 
 def build_model(cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None) -> CausalLM:
+    if cfg.is_vlm:
+        from .vlm import VisionLanguageModel
+
+        return VisionLanguageModel(cfg, dtype=dtype, device=device, seed=seed)
     return CausalLM(cfg, dtype=dtype, device=device, seed=seed)

@@ -27,6 +27,11 @@ def hf_to_native_plan(cfg: ModelConfig) -> dict[str, list[tuple[str, Optional[tu
         plan["value_head"] = [("score.weight", None, None)]
     elif not cfg.tie_word_embeddings:
         plan["lm_head"] = [("lm_head.weight", None, None)]
+    if cfg.is_vlm:
+        from .vision import vision_param_names
+
+        for n in vision_param_names(cfg.vision_config()):
+            plan["visual." + n] = [("visual." + n, None, None)]
     for i in range(cfg.num_layers):
         p, h = f"layers.{i}.", f"model.layers.{i}."
         plan[p + "input_layernorm"] = [(h + "input_layernorm.weight", None, None)]
@@ -87,6 +92,11 @@ def load_hf_tensors_into(cfg: ModelConfig, params: dict[str, torch.Tensor], hf_t
             inverse[hf_name] = (native, rows, expert)
     seen = set()
     for hf_name, t in hf_tensors:
+        # newer VLM checkpoints nest the decoder and the tower under ``model.``
+        if hf_name.startswith("model.language_model."):
+            hf_name = "model." + hf_name[len("model.language_model."):]
+        elif hf_name.startswith("model.visual."):
+            hf_name = hf_name[len("model."):]
         if hf_name not in inverse:
             if hf_name == "lm_head.weight" and cfg.tie_word_embeddings:
                 continue

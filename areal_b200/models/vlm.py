@@ -1,0 +1,107 @@
+"""Vision-language causal LM: the decoder of ``decoder.py`` plus the image tower of
+``vision.py``. Image features replace the embeddings of the image placeholder tokens and the
+rotary tables are built per token from the three M-RoPE position streams.
+
+Reference behaviour: ``areal/engine/fsdp_engine.py:1997-2056`` (multi-modal inputs gathered per
+micro-batch, position ids from the model's ``get_rope_index``) and
+``areal/models/transformers/qwen2_vl.py``.
+"""
+from __future__ import annotations
+
+import copy
+from typing import Any, Optional
+
+import torch
+
+from ..ops import functional as OF
+from .config import ModelConfig
+from .decoder import CausalLM, PackedBatch
+from .vision import VisionTower, mrope_position_ids, mrope_tables, num_image_tokens
+
+
+def collect_multi_modal(mm_list: Optional[list]) -> Optional[dict[str, Any]]:
+    """Per-sequence ``multi_modal_input`` entries (dicts with ``pixel_values`` / ``image_grid_thw``,
+    or ``None`` for text-only samples) -> one dict for the packed batch, images in sequence order;
+    ``images_per_seq`` says how many grids each sequence owns."""
+    if not mm_list:
+        return None
+    px, grids, per_seq = [], [], []
+    for m in mm_list:
+        if not m or m.get("pixel_values") is None:
+            per_seq.append(0)
+            continue
+        g = torch.as_tensor(m["image_grid_thw"]).view(-1, 3).long()
+        px.append(torch.as_tensor(m["pixel_values"]))
+        grids.append(g)
+        per_seq.append(g.shape[0])
+    if not px:
+        return None
+    return {"pixel_values": torch.cat(px, 0), "image_grid_thw": torch.cat(grids, 0), "images_per_seq": per_seq}
+
+
+class VisionLanguageModel(CausalLM):
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", init_std: float = 0.02, seed: Optional[int] = None):
+        super().__init__(cfg, dtype=dtype, device=device, init_std=init_std, seed=seed)
+        self.vcfg = cfg.vision_config()
+        self.visual = VisionTower(self.vcfg, dtype=dtype, device=device, init_std=init_std, seed=seed)
+
+    def packed_mrope(self, ids_cpu: torch.Tensor, cu: list[int], grid_thw: Optional[torch.Tensor],
+                     images_per_seq: Optional[list[int]] = None) -> tuple[torch.Tensor, list[int], torch.Tensor]:
+        """M-RoPE streams ``[3, T]`` for a packed batch, the per-sequence deltas, and the token
+        indices that hold image features. Images are consumed in order; a sequence owns
+        ``images_per_seq[i]`` grids (without that list: as many as its placeholder tokens account for)."""
+        cfg = self.cfg
+        m = self.vcfg.spatial_merge_size
+        T = ids_cpu.shape[0]
+        pos = torch.zeros(3, T, dtype=torch.long)
+        per_image = num_image_tokens(grid_thw, m) if grid_thw is not None else []
+        img, deltas, where = 0, [], []
+        for si, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+            seq = ids_cpu[a:b]
+            if images_per_seq is not None:
+                k = images_per_seq[si] if si < len(images_per_seq) else 0
+            else:
+                want = int(((seq == cfg.image_token_id) | (seq == cfg.video_token_id)).sum())
+                k = 0
+                while want > 0 and img + k < len(per_image):
+                    want -= per_image[img + k]
+                    k += 1
+                if want != 0:
+                    raise ValueError("image placeholder tokens do not match the image grids of this sequence")
+            g = grid_thw[img:img + k] if k else None
+            local: list[int] = []
+            p, d = mrope_position_ids(seq, g, cfg.image_token_id, m, cfg.video_token_id, image_positions=local)
+            if len(local) != sum(per_image[img:img + k]):
+                raise ValueError(f"sequence {si}: {len(local)} placeholder tokens for {sum(per_image[img:img + k])} image features")
+            pos[:, a:b] = p
+            deltas.append(d)
+            where += [a + x for x in local]
+            img += k
+        return pos, deltas, torch.tensor(where, dtype=torch.long)
+
+    def embed_multimodal(self, input_ids: torch.Tensor, mm: dict[str, Any], positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+        feats = self.visual(mm["pixel_values"].to(self.embed_tokens.dtype), mm["image_grid_thw"])
+        h = OF.embedding(input_ids, self.embed_tokens)
+        if positions is None:
+            mask = (input_ids == self.cfg.image_token_id) | (input_ids == self.cfg.video_token_id)
+            positions = mask.nonzero(as_tuple=True)[0]
+        positions = positions.to(input_ids.device)
+        if positions.numel() != feats.shape[0]:
+            raise ValueError(f"{positions.numel()} placeholder tokens for {feats.shape[0]} image features")
+        return h.index_copy(0, positions, feats.to(h.dtype))
+
+    def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None, mm: Optional[dict[str, Any]] = None, **kw) -> torch.Tensor:
+        if mm is None or mm.get("pixel_values") is None or mm["pixel_values"].numel() == 0:
+            # text only: the three streams coincide and M-RoPE is ordinary RoPE
+            return super().forward_hidden(input_ids, pb, attn_fns, **kw)
+        T = input_ids.shape[0]
+        pos3, where = mm.get("mrope_position_ids"), mm.get("image_positions")
+        if pos3 is None:
+            cu = pb.cu_seqlens.tolist()
+            pos3, _, where = self.packed_mrope(input_ids.cpu().long(), cu, mm["image_grid_thw"].cpu().long(), mm.get("images_per_seq"))
+        sections = self.cfg.mrope_section or [self.cfg.head_dim // 2, 0, 0]
+        cos, sin = mrope_tables(pos3, self.cfg.head_dim, self.cfg.rope_theta, sections, input_ids.device)
+        pb2 = copy.copy(pb)
+        pb2.position_ids = torch.arange(T, dtype=torch.int32, device=input_ids.device)   # row t of the per-token tables
+        embeds = self.embed_multimodal(input_ids, mm, where)
+        return super().forward_hidden(input_ids, pb2, attn_fns, inputs_embeds=embeds, rope=(cos, sin))
