@@ -25,3 +25,14 @@ def test_expert_parallel_matches_unsplit_moe():
                        env=env, capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("EP_OK") == 2
+
+
+@pytest.mark.parametrize("ranks,port", [(2, 29917), (4, 29919)])
+def test_zigzag_context_parallel_attention(ranks, port):
+    """Zig-zag split / gather round trip and attention against gathered K/V (forward + gradients)."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr",
+                        "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "dist_scripts", "run_cp.py")], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("CP_OK") == ranks
