@@ -95,13 +95,16 @@ class B200TrainEngine(TrainEngine):
                 self.parallel = p = FSDPParallelStrategy(data_parallel_size=n)
             else:
                 raise ValueError(f"parallel strategy {p} needs {p.world_size} ranks, engine has {n}")
-        if p.pp_size > 1:
-            raise NotImplementedError("pipeline-parallel training is provided by parallel.pp (PipelineRunner), not by this engine")
+        self.pp_size = p.pp_size
+        self.pp_rank = 0
+        self._pp_group = self._pp_cpu_group = None
         self.sp_size, self.dp_size, self.tp_size = p.cp_size, p.dp_size, p.tp_size
         sp, tp, dp = self.sp_size, self.tp_size, self.dp_size
         # rank layout inside the trainer ranks: index = (d * sp + s) * tp + t  (tp fastest)
         self.local_index = self._train_ranks.index(self.rank) if self.rank in self._train_ranks else -1
         li = max(self.local_index, 0)
+        if self.pp_size > 1:
+            return self._create_pp_groups(li, use_cuda)
         self.tp_rank = li % tp
         self.sp_rank = (li // tp) % sp
         self.dp_rank = li // (tp * sp)
@@ -178,6 +181,41 @@ class B200TrainEngine(TrainEngine):
             self._stats_group = self._cpu_group
         return self
 
+    def _create_pp_groups(self, li: int, use_cuda: bool):
+        """Pipeline x data parallel layout: index = stage * dp + d (stages outermost). Every stage
+        shards its optimizer state over its own data-parallel ranks; the ranks of one pipeline see
+        the same data (they are each other's model-parallel peers)."""
+        pp, dp, tr = self.pp_size, self.dp_size, self._train_ranks
+        if self.sp_size * self.tp_size > 1:
+            raise NotImplementedError("pipeline parallelism combines with data parallelism only (no tp / sp inside a stage yet)")
+        if getattr(self, "_preset_groups", None) is not None:
+            raise NotImplementedError("pipeline parallelism inside a trainer / rollout split")
+        self.pp_rank, self.dp_rank = li // dp, li % dp
+        self.tp_rank = self.sp_rank = 0
+        self._tp_group = self._sp_group = None
+        self._all_train_group = dist.group.WORLD if len(tr) == self.world_size else dist.new_group(tr)
+        self._shard_group = self._dp_group = None
+        for s_ in range(pp):
+            ranks = [tr[s_ * dp + d] for d in range(dp)]
+            g = dist.new_group(ranks) if dp > 1 else None
+            if s_ == self.pp_rank:
+                self._shard_group = self._dp_group = g
+        for d in range(dp):
+            ranks = [tr[s_ * dp + d] for s_ in range(pp)]
+            g = dist.new_group(ranks)
+            gc = dist.new_group(ranks, backend="gloo") if use_cuda else g
+            if d == self.dp_rank:
+                self._pp_group, self._pp_cpu_group = g, gc
+        self._mp_group = self._pp_group
+        self._cpu_group = dist.new_group(tr, backend="gloo") if use_cuda else self._all_train_group
+        # losses and statistics exist on the last stage only
+        last = [tr[(pp - 1) * dp + d] for d in range(dp)]
+        g = dist.new_group(last, backend="gloo") if dp > 1 else None
+        self._stats_group = g if self.pp_rank == pp - 1 else None
+        t_ = torch.zeros(1, device=self.device)
+        dist.all_reduce(t_, group=self._all_train_group)
+        return self
+
     def set_train_ranks(self, ranks: list[int], groups: Optional[dict] = None):
         """Restricts the engine to a subset of the global ranks (trainer / rollout split).
         ``groups``: process groups created collectively by all ranks (keys shard, dp, sp, cpu)."""
@@ -210,7 +248,19 @@ class B200TrainEngine(TrainEngine):
         tp = getattr(self, "tp_size", 1)
         has_ckpt = (not cfg.init_from_scratch and cfg.path and os.path.isdir(cfg.path)
                     and any(f.endswith(".safetensors") for f in os.listdir(cfg.path)))
-        if tp > 1:
+        if getattr(self, "pp_size", 1) > 1:
+            from ..parallel.pp import PipelineRunner, PipelineStage
+
+            if model_config.is_vlm or cfg.use_lora:
+                raise NotImplementedError("pipeline parallelism with vision-language models / LoRA")
+            loader = (lambda full: hf_io.load_model_hf(full, cfg.path, strict=not cfg.is_critic)) if has_ckpt else None
+            self.local_model_config = model_config
+            self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader)
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+            sched = {"1f1b": "1F1B", "gpipe": "GPipe"}.get(str(getattr(cfg.archon, "pp_schedule", "1F1B")).lower(), "1F1B")
+            self._pp_runner = PipelineRunner(self.model, self._pp_group, schedule=sched)
+        elif tp > 1:
             # every rank materialises the full weights once (same seed / same checkpoint), keeps
             # its slice and drops the rest
             from ..parallel import tp as TP
@@ -234,7 +284,8 @@ class B200TrainEngine(TrainEngine):
         ac = getattr(cfg.archon, "ac_mode", "selective") if not cfg.gradient_checkpointing else "full"
         if getattr(cfg, "activation_checkpointing", None):
             ac = cfg.activation_checkpointing
-        if ac in ("selective", "memory_budget") and not cfg.gradient_checkpointing and getattr(cfg, "activation_checkpointing", None):
+        if ac in ("selective", "memory_budget") and not cfg.gradient_checkpointing and getattr(cfg, "activation_checkpointing", None) \
+                and getattr(self, "pp_size", 1) == 1:
             self.model.set_activation_checkpointing(ac, getattr(cfg, "activation_memory_budget", 0.5))
         self.use_lora = bool(cfg.use_lora) and cfg.optimizer is not None
         if self.use_lora:
@@ -247,6 +298,8 @@ class B200TrainEngine(TrainEngine):
         # ranks that hold the same tensor-parallel slice shard its optimizer state (ZeRO)
         self._shard_ranks = [self._train_ranks[(d * sp + s_) * tp + self.tp_rank] for d in range(self.dp_size) for s_ in range(sp)] \
             if self.local_index >= 0 else list(self._train_ranks)
+        if getattr(self, "pp_size", 1) > 1:
+            self._shard_ranks = [self._train_ranks[self.pp_rank * self.dp_size + d] for d in range(self.dp_size)]
         n_shards = len(self._shard_ranks) if self._shard_group is not None else 1
         shard_rank = (self.dp_rank * sp + self.sp_rank) if n_shards > 1 else 0
         on_gpu = self.device.type == "cuda"
@@ -267,6 +320,16 @@ class B200TrainEngine(TrainEngine):
             dist.broadcast(self.store.flat_param, src=self._shard_ranks[0], group=self._shard_group)
         if tp > 1 and cfg.optimizer is not None:
             self._replicated_ranges = self._find_replicated_ranges()
+        if getattr(self, "pp_size", 1) > 1 and cfg.optimizer is not None:
+            # the last stage's copy of a tied embedding must not count twice in the global norm
+            self._replicated_ranges = []
+            m = self.model
+            if m.is_last and not m.is_first and m.embed_tokens is not None and m.lm_head is None and not model_config.is_critic:
+                lo, hi = self.store.shard_range
+                off, numel = self.store.locate("embed_tokens")
+                a, b = max(off, lo), min(off + numel, hi)
+                if a < b:
+                    self._replicated_ranges.append((a - lo, b - lo))
         if cfg.optimizer is not None:
             total = ft_spec.total_train_steps if ft_spec is not None else 1
             self.optimizer = ShardedAdamW(self.store, cfg.optimizer, total_steps=total, group=self._shard_group)
@@ -358,10 +421,19 @@ class B200TrainEngine(TrainEngine):
         return self.dp_size
 
     def current_data_parallel_head(self) -> int:
+        if getattr(self, "pp_size", 1) > 1:
+            return self._train_ranks[self.dp_rank]          # first stage of this rank's pipeline
         return self._train_ranks[self.dp_rank * self.sp_size * getattr(self, "tp_size", 1)]
 
     def is_data_parallel_head(self) -> bool:
-        return self.sp_rank == 0 and getattr(self, "tp_rank", 0) == 0
+        return self.sp_rank == 0 and getattr(self, "tp_rank", 0) == 0 and getattr(self, "pp_rank", 0) == 0
+
+    @property
+    def pipeline_parallel_group(self):
+        return getattr(self, "_pp_group", None)
+
+    def is_pipeline_last_stage(self) -> bool:
+        return getattr(self, "pp_size", 1) == 1 or self.pp_rank == self.pp_size - 1
 
     @property
     def context_and_model_parallel_group(self):
@@ -450,6 +522,8 @@ class B200TrainEngine(TrainEngine):
     def forward_backward_batch(self, mb_list: D.MicroBatchList, process_output_fn: Callable, forward_only: bool = False):
         """Runs every micro-batch; ``process_output_fn(hidden, labels, mb, pad_len, sl)`` returns a
         loss (training) or an output (forward only)."""
+        if getattr(self, "pp_size", 1) > 1:
+            return self._pp_forward_backward(mb_list, process_output_fn, forward_only)
         outs = []
         for mb, pad in zip(mb_list.padded_mbs, mb_list.padding_lengths):
             mbd = self._mb_to_device(mb)
@@ -466,6 +540,39 @@ class B200TrainEngine(TrainEngine):
                 loss.backward()
                 outs.append(loss.detach())
         return outs
+
+    def _pp_forward_backward(self, mb_list: D.MicroBatchList, process_output_fn: Callable, forward_only: bool):
+        """Micro-batches through this rank's pipeline (every stage holds the same micro-batches).
+        Losses / outputs exist on the last stage; the other stages return ``[]``."""
+        mbs = []
+        for mb, pad in zip(mb_list.padded_mbs, mb_list.padding_lengths):
+            mbd = self._mb_to_device(mb)
+            ids = mbd["input_ids"].to(torch.int32) if self.device.type == "cuda" else mbd["input_ids"].long()
+            T = ids.shape[0]
+            pos = mbd.get("position_ids")
+            if pos is None or pos.shape[0] != T:
+                pos = D.positions_from_cu_seqlens(mbd["cu_seqlens"], T)
+            mbs.append(dict(input_ids=ids, pb=PackedBatch(mbd["cu_seqlens"], pos, T, int(mbd.get("max_seqlen", 0))),
+                            labels=torch.roll(ids, shifts=-1, dims=0), mbd=mbd, pad=pad))
+
+        def last_stage(hidden, mb):
+            out = process_output_fn(hidden, mb["labels"], mb["mbd"], mb["pad"], slice(0, mb["input_ids"].shape[0]))
+            if not forward_only:
+                aux = self.model.aux_loss()
+                if aux is not None:
+                    out = out + aux
+            return out
+
+        return self._pp_runner.run(mbs, last_stage, forward_only=forward_only)
+
+    def _pp_share(self, outs: list):
+        """Results of the last pipeline stage made known to every stage of this pipeline."""
+        if getattr(self, "pp_size", 1) == 1:
+            return outs
+        box = [outs if self.is_pipeline_last_stage() else None]
+        src = self._train_ranks[(self.pp_size - 1) * self.dp_size + self.dp_rank]
+        dist.broadcast_object_list(box, src=src, group=self._pp_cpu_group)
+        return box[0]
 
     def _slice_mb(self, mb: dict[str, Any], sl: slice, pad: int) -> dict[str, Any]:
         """Per-token fields restricted to the local sequence-parallel slice."""
@@ -517,6 +624,8 @@ class B200TrainEngine(TrainEngine):
         losses = self.forward_backward_batch(mbl, process)
         stats = self.optimizer_step()
         stats["loss"] = float(torch.stack(losses).sum()) if losses else 0.0
+        if getattr(self, "pp_size", 1) > 1:
+            stats["loss"] = float(self._pp_runner.broadcast_loss(torch.tensor(stats["loss"])))
         return stats
 
     def optimizer_step(self) -> dict[str, float]:
@@ -530,7 +639,8 @@ class B200TrainEngine(TrainEngine):
             from ..parallel.tp import allreduce_replicated_grads
 
             allreduce_replicated_grads(self.model, self._tp_group)
-        fused = self._grad_reducer is not None and not opt.sgd and tp == 1
+        pp = getattr(self, "pp_size", 1)
+        fused = self._grad_reducer is not None and not opt.sgd and tp == 1 and pp == 1
         if self._shard_group is not None:
             if fused:
                 gshard = self._grad_reducer.reduce_scatter(opt.state)
@@ -555,7 +665,13 @@ class B200TrainEngine(TrainEngine):
             res = {"state": opt.state, "lr": lr}
         else:
             pre = None
-            if tp > 1:
+            if pp > 1:
+                # global norm^2 = sum over every stage's shards; a tied embedding's second copy is left out
+                pre = torch.zeros(1, dtype=torch.float32, device=self.device)
+                g32 = gshard.float()
+                pre[0] = g32.pow(2).sum() - sum((g32[a:b].pow(2).sum() for a, b in self._replicated_ranges), torch.zeros((), device=self.device))
+                dist.all_reduce(pre, group=self._all_train_group)
+            elif tp > 1:
                 # global norm^2 = sum over TP ranks of the sliced parameters' part + the replicated
                 # parameters' part counted once
                 pre = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -599,7 +715,7 @@ class B200TrainEngine(TrainEngine):
             logp, ent = self._actor_outputs(hidden, labels)
             return loss_fn(logp, ent, mb_local) * w
 
-        outs = self.forward_backward_batch(mbl, process, forward_only=True)
+        outs = self._pp_share([o.float().cpu() for o in self.forward_backward_batch(mbl, process, forward_only=True)])
         tot = torch.stack([o.float().cpu() for o in outs]).sum().reshape(1).double()
         w = torch.tensor([sum(weights)], dtype=torch.float64)
         if self.dp_size > 1 and self._cpu_group is not None:
@@ -633,7 +749,7 @@ class B200TrainEngine(TrainEngine):
                 res = tuple(full)
             return tuple(D.unpad_logits(r, pad).float().cpu() for r in res)
 
-        outs = self.forward_backward_batch(mbl, process, forward_only=True)
+        outs = self._pp_share(self.forward_backward_batch(mbl, process, forward_only=True))
         n_out = len(outs[0]) if outs else 1
         results = []
         for j in range(n_out):
@@ -650,7 +766,24 @@ class B200TrainEngine(TrainEngine):
     def save(self, meta: SaveLoadMeta):
         os.makedirs(meta.path, exist_ok=True)
         head = self.local_index <= 0
-        if meta.weight_format == "hf":
+        if meta.weight_format == "hf" and getattr(self, "pp_size", 1) > 1:
+            # the stages of the first pipeline write their own tensors; the head merges the index
+            maps = [None] * self.pp_size
+            if self.dp_rank == 0:
+                named = [(n, p.detach()) for n, p in self.model.named_native_parameters()]
+                mine = hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named),
+                                             rank_tag=f"pp{self.pp_rank}", write_index=False)
+                dist.all_gather_object(maps, mine, group=self._pp_cpu_group)
+            if head:
+                merged = {}
+                for m_ in maps:
+                    merged.update(m_)
+                total = sum(os.path.getsize(os.path.join(meta.path, f)) for f in set(merged.values()))
+                hf_io.write_hf_index(meta.path, merged, total)
+                self.model_config.save_pretrained(meta.path)
+                if meta.tokenizer is not None:
+                    meta.tokenizer.save_pretrained(meta.path)
+        elif meta.weight_format == "hf":
             if getattr(self, "tp_size", 1) > 1:
                 # every tensor-parallel rank of the first data-parallel replica takes part in
                 # the gather; the head writes full tensors one by one
@@ -694,7 +827,13 @@ class B200TrainEngine(TrainEngine):
             yield n_, TP.unshard_tensors(self.model_config, n_, parts)
 
     def load(self, meta: SaveLoadMeta):
-        if meta.weight_format == "hf":
+        if meta.weight_format == "hf" and getattr(self, "pp_size", 1) > 1:
+            mine = {n: p for n, p in self.model.named_native_parameters(skip_tied_copy=False)}
+            plan = hf_io.hf_to_native_plan(self.model_config)
+            wanted = {hf for n in mine for hf, _, _ in plan[n]}
+            hf_io.load_hf_tensors_into(self.model_config, {n: p.data for n, p in mine.items()},
+                                       ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
+        elif meta.weight_format == "hf":
             if getattr(self, "tp_size", 1) > 1:
                 from ..parallel import tp as TP
 
@@ -733,7 +872,7 @@ class B200TrainEngine(TrainEngine):
     def _rollout_source(self):
         """The rollout engine itself, or (with context / tensor parallel peers that must see the
         same tokens) a coordinator that lets the data-parallel head roll out and broadcasts."""
-        if self.sp_size * getattr(self, "tp_size", 1) > 1 and dist.is_initialized():
+        if self.sp_size * getattr(self, "tp_size", 1) * getattr(self, "pp_size", 1) > 1 and dist.is_initialized():
             from ..rollout.dist_rollout import DistRolloutCoordinator
 
             return DistRolloutCoordinator(self.rollout_engine, self, redistribute=False)
@@ -783,6 +922,15 @@ class B200TrainEngine(TrainEngine):
                 return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters() if "_lora_" not in n}
             finally:
                 unmerge_lora_(self.model)
+        if getattr(self, "pp_size", 1) > 1:
+            # every stage contributes its own tensors; all stages end up with the full dictionary
+            parts = [None] * self.pp_size
+            mine = {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_native_parameters()}
+            dist.all_gather_object(parts, mine, group=self._pp_cpu_group)
+            out = {}
+            for d_ in parts:
+                out.update(d_)
+            return out
         return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters()}
 
     def export_stats(self) -> dict[str, float]:

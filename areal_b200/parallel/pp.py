@@ -47,14 +47,18 @@ class PipelineStage(nn.Module):
     """The slice of a :class:`CausalLM` one pipeline rank owns."""
 
     def __init__(self, cfg: ModelConfig, stage: int, n_stages: int, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None,
-                 layer_ranges: Optional[list[range]] = None):
+                 layer_ranges: Optional[list[range]] = None, init_full: Optional[Callable] = None):
         super().__init__()
         self.cfg, self.stage, self.n_stages = cfg, stage, n_stages
+        self.dtype = dtype
         self.is_first, self.is_last = stage == 0, stage == n_stages - 1
         ranges = layer_ranges or split_layers(cfg.num_layers, n_stages)
         self.layer_range = ranges[stage]
-        # build the full model once (same seed on every rank => consistent weights), keep a slice
+        # build the full model once (same seed on every rank => consistent weights), keep a slice;
+        # ``init_full(model)`` may load a checkpoint into it first
         full = build_model(cfg, dtype=dtype, device=device, seed=seed)
+        if init_full is not None:
+            init_full(full)
         self.layers = nn.ModuleList([full.layers[i] for i in self.layer_range])
         self.embed_tokens = full.embed_tokens if (self.is_first or (self.is_last and cfg.tie_word_embeddings and not cfg.is_critic)) else None
         self.norm = full.norm if self.is_last else None
@@ -96,6 +100,27 @@ class PipelineStage(nn.Module):
     def logprobs_entropy(self, hidden, labels, temperature: float = 1.0, chunk: int = 2048):
         return OF.lm_head_logprob(hidden, self.output_weight, labels, temperature, chunk)
 
+    def values(self, hidden: torch.Tensor) -> torch.Tensor:
+        return torch.nn.functional.linear(hidden.float(), self.value_head.float()).squeeze(-1)
+
+    def aux_loss(self) -> Optional[torch.Tensor]:
+        """Router balancing loss of this stage's MoE layers (each stage adds its own to its backward)."""
+        tot = None
+        for layer in self.layers:
+            al = getattr(layer.mlp, "last_aux_loss", None)
+            if al is not None:
+                tot = al if tot is None else tot + al
+                layer.mlp.last_aux_loss = None
+        return tot
+
+    def named_native_parameters(self, skip_tied_copy: bool = True):
+        """(name in the full model, parameter); the last stage's copy of a tied embedding is left
+        out so that the stages' name sets are disjoint."""
+        for n, p in self.named_parameters():
+            if skip_tied_copy and n == "embed_tokens" and self.is_last and not self.is_first:
+                continue
+            yield self.native_name(n), p
+
 
 class PipelineRunner:
     """Runs micro-batches through the stages of ONE pipeline (a process group whose ranks are
@@ -117,6 +142,7 @@ class PipelineRunner:
         p = next(stage_module.parameters())
         self.device, self.dtype = p.device, p.dtype
         self.H = stage_module.cfg.hidden_size
+        self._aux: dict[int, torch.Tensor] = {}
 
     # ---- p2p: every exchange is ONE batch of sends and receives, so a stage that sends forward
     # while its neighbour sends backward cannot block the other (NCCL groups the batch)
@@ -152,13 +178,21 @@ class PipelineRunner:
             y = self.m(x_in, mb["pb"])
         if self.m.is_last:
             return loss_fn(y, mb)
+        if not forward_only:
+            aux = self.m.aux_loss()      # MoE balancing loss of this stage: joins this stage's backward
+            if aux is not None:
+                self._aux[id(y)] = aux
         return y
 
     def _backward(self, x_in, y, dy):
         if self.m.is_last:
             y.backward()
         else:
-            y.backward(dy)
+            aux = self._aux.pop(id(y), None)
+            if aux is not None:
+                torch.autograd.backward([y, aux], [dy, torch.ones_like(aux)])
+            else:
+                y.backward(dy)
         return None if self.m.is_first else x_in.grad
 
     def run(self, microbatches: list[dict[str, Any]], loss_fn: Optional[Callable] = None, forward_only: bool = False) -> list:
@@ -224,6 +258,10 @@ class PipelineRunner:
         if self.n == 1 or not m.cfg.tie_word_embeddings or m.cfg.is_critic or not (m.is_first or m.is_last):
             return
         g = getattr(m.embed_tokens, "main_grad", None)
+        if g is not None and m.embed_tokens.grad is not None:
+            # the lookup's gradient arrives through autograd, the head's through the fp32 buffer: one sum
+            g.add_(m.embed_tokens.grad.to(g.dtype))
+            m.embed_tokens.grad = None
         if g is None:
             g = m.embed_tokens.grad
         if g is None:

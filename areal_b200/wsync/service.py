@@ -31,6 +31,26 @@ from ..utils import logging as alog
 logger = alog.getLogger("wsync")
 
 
+class GatheredPusher:
+    """Pipeline-parallel trainer + engine in the same process: the stages exchange their tensors
+    (host side) and every rank loads the full set into its engine."""
+
+    def __init__(self, train_engine, infer_engine):
+        self.train, self.infer = train_engine, infer_engine
+        self.last_ms = 0.0
+
+    def push(self, meta: Optional[WeightUpdateMeta] = None):
+        t0 = time.perf_counter()
+        weights = self.train.export_weights()
+        self.infer.pause_generation()
+        try:
+            self.infer.update_weights_from_tensors(iter(weights.items()), meta)
+        finally:
+            self.infer.continue_generation()
+        self.last_ms = (time.perf_counter() - t0) * 1e3
+        return self.last_ms
+
+
 class InProcessPusher:
     """Trainer and engine share the process: copy parameters tensor by tensor (device copy)."""
 
@@ -61,7 +81,11 @@ class DiskPusher:
     def push(self, meta: WeightUpdateMeta):
         t0 = time.perf_counter()
         path = meta.path
-        if self.train.local_index <= 0:
+        if getattr(self.train, "pp_size", 1) * getattr(self.train, "tp_size", 1) > 1:
+            from ..api.io_struct import SaveLoadMeta
+
+            self.train.save(SaveLoadMeta(path=path, weight_format="hf", with_optim=False))   # collective: gathers slices / stages
+        elif self.train.local_index <= 0:
             hf_io.save_model_hf(self.train.model, path)
         if self.train.cpu_group is not None:
             dist.barrier(group=self.train.cpu_group)
@@ -89,6 +113,8 @@ def make_weight_pusher(train_engine, infer_engine, meta: WeightUpdateMeta):
             return BroadcastWeightPusher(train_engine, infer_engine, infer_engine.wu_group,
                                          bucket_mb=meta.weight_chunked_mem_mb)
         return DistributedWeightPusher(train_engine, infer_engine, meta)
+    if getattr(train_engine, "pp_size", 1) > 1:
+        return GatheredPusher(train_engine, infer_engine)
     return InProcessPusher(train_engine, infer_engine)
 
 

@@ -36,3 +36,15 @@ def test_zigzag_context_parallel_attention(ranks, port):
                        env=env, capture_output=True, text=True, timeout=180)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("CP_OK") == ranks
+
+
+def test_train_engine_pipeline_x_data_parallel(tmp_path):
+    """dp2 x pp2 engine (ZeRO inside each stage, 1F1B over micro-batches) against one rank:
+    gradient norms, weights after two steps, forward-only outputs on every stage, HF export /
+    reload, complete weight dictionary; untied and tied embeddings."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", PP_SAVE_DIR=str(tmp_path))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+                        "127.0.0.1", "--master-port", "29931", os.path.join(ROOT, "tests", "dist_scripts", "run_engine_pp.py")], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ENGINE_PP_OK") == 4
