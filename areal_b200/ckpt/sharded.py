@@ -26,6 +26,13 @@ def save_sharded(engine, path: str, with_optim: bool = True) -> None:
     if with_optim and opt is not None:
         tensors.update(master=opt.master.cpu(), exp_avg=opt.exp_avg.cpu(), exp_avg_sq=opt.exp_avg_sq.cpu())
         meta.update(step_count=opt.step_count, sched_step=opt.sched_step)
+    es, eo = getattr(engine, "expert_store", None), getattr(engine, "expert_optimizer", None)
+    if es is not None:
+        # expert parallelism: the experts' own flat space (sharded over the replicas of the same experts)
+        tensors["expert_param_shard"] = es.param_shard.detach().cpu().contiguous()
+        meta["expert"] = dict(padded=es.padded, world_size=es.world_size, shard_range=list(es.shard_range), names=es.names)
+        if with_optim and eo is not None:
+            tensors.update(expert_master=eo.master.cpu(), expert_exp_avg=eo.exp_avg.cpu(), expert_exp_avg_sq=eo.exp_avg_sq.cpu())
     save_file(tensors, os.path.join(path, f"shard-{r:05d}-of-{st.world_size:05d}.safetensors"))
     with open(os.path.join(path, f"shard-{r:05d}.json"), "w") as f:
         json.dump(meta, f)
@@ -57,4 +64,20 @@ def load_sharded(engine, path: str, with_optim: bool = True) -> None:
             opt.step_count, opt.sched_step = int(meta.get("step_count", 0)), int(meta.get("sched_step", 0))
         else:
             opt.resync_master()
+    es, eo = getattr(engine, "expert_store", None), getattr(engine, "expert_optimizer", None)
+    if es is not None:
+        em = meta.get("expert")
+        if em is None or em["world_size"] != es.world_size or em["padded"] != es.padded:
+            raise ValueError("sharded checkpoint has no matching expert-parallel section")
+        es.param_shard.copy_(tensors["expert_param_shard"].to(es.dtype))
+        if es.world_size > 1:
+            dist.all_gather_into_tensor(es.flat_param, es.param_shard.clone(), group=engine._edp_group)
+        if eo is not None:
+            if with_optim and "expert_master" in tensors:
+                eo.master.copy_(tensors["expert_master"])
+                eo.exp_avg.copy_(tensors["expert_exp_avg"])
+                eo.exp_avg_sq.copy_(tensors["expert_exp_avg_sq"])
+                eo.step_count, eo.sched_step = int(meta.get("step_count", 0)), int(meta.get("sched_step", 0))
+            else:
+                eo.resync_master()
     engine.set_version(int(meta.get("version", 0)))

@@ -27,8 +27,9 @@ class FlatParamStore:
     def __init__(self, model: nn.Module, world_size: int = 1, rank: int = 0, grad_dtype=torch.float32,
                  alloc_param: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None,
                  alloc_grad: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None,
-                 with_grads: bool = True, only_trainable: bool = False):
-        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad or not only_trainable]
+                 with_grads: bool = True, only_trainable: bool = False, include: Optional[Callable[[str], bool]] = None):
+        params = [(n, p) for n, p in model.named_parameters()
+                  if (p.requires_grad or not only_trainable) and (include is None or include(n))]
         if not params:
             raise ValueError("model has no parameters")
         self.names = [n for n, _ in params]

@@ -179,6 +179,22 @@ class B200TrainEngine(TrainEngine):
             self._shard_group = None
         if not hasattr(self, "_stats_group"):
             self._stats_group = self._cpu_group
+        self.ep_size = getattr(p, "ep_size", 1) or 1
+        self.ep_rank, self._ep_group, self._edp_group = 0, None, None
+        if self.ep_size > 1:
+            ep = self.ep_size
+            if sp * tp > 1 or dp % ep or preset is not None:
+                raise NotImplementedError("expert parallelism folds into plain data parallelism (ep must divide dp; no tp / sp, no trainer-rollout split)")
+            self.ep_rank = self.dp_rank % ep
+            for blk in range(dp // ep):                       # experts are spread over consecutive data-parallel ranks
+                g = dist.new_group([tr[blk * ep + e] for e in range(ep)])
+                if blk == self.dp_rank // ep:
+                    self._ep_group = g
+            for e in range(ep):                               # replicas of the same experts: their gradients are summed
+                ranks = [tr[blk * ep + e] for blk in range(dp // ep)]
+                g = dist.new_group(ranks) if len(ranks) > 1 else None
+                if e == self.ep_rank:
+                    self._edp_group = g
         return self
 
     def _create_pp_groups(self, li: int, use_cuda: bool):
@@ -280,6 +296,13 @@ class B200TrainEngine(TrainEngine):
             self.model = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
             if has_ckpt:
                 hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
+        self._expert_param_names: list[str] = []
+        if getattr(self, "ep_size", 1) > 1:
+            from ..parallel.ep import shard_experts
+
+            if not model_config.is_moe:
+                raise ValueError("expert parallelism needs a mixture-of-experts model")
+            self._expert_param_names = shard_experts(self.model, self.ep_rank, self.ep_size, self._ep_group)
         self.model.gradient_checkpointing = cfg.gradient_checkpointing
         ac = getattr(cfg.archon, "ac_mode", "selective") if not cfg.gradient_checkpointing else "full"
         if getattr(cfg, "activation_checkpointing", None):
@@ -313,8 +336,19 @@ class B200TrainEngine(TrainEngine):
         else:
             alloc_p = alloc_g
         alloc = alloc_g
+        self.expert_store = self.expert_optimizer = None
+        if self._expert_param_names:
+            # experts differ between the ranks of an EP group: their own flat space, sharded over
+            # the ranks that hold the SAME experts; everything else is sharded over all ranks
+            fused, alloc_g, alloc_p, alloc = False, None, None, None
+            expert = set(self._expert_param_names)
+            n_edp = self.dp_size // self.ep_size
+            self.expert_store = FlatParamStore(self.model, n_edp, self.dp_rank // self.ep_size, torch.float32,
+                                               with_grads=cfg.optimizer is not None, include=lambda n: n in expert)
+        _expert_set = frozenset(self._expert_param_names)
+        dense_only = (lambda n: n not in _expert_set) if _expert_set else None
         self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
-                                    with_grads=cfg.optimizer is not None, only_trainable=self.use_lora)
+                                    with_grads=cfg.optimizer is not None, only_trainable=self.use_lora, include=dense_only)
         if n_shards > 1:
             # identical initial weights on every rank of the shard group
             dist.broadcast(self.store.flat_param, src=self._shard_ranks[0], group=self._shard_group)
@@ -333,6 +367,8 @@ class B200TrainEngine(TrainEngine):
         if cfg.optimizer is not None:
             total = ft_spec.total_train_steps if ft_spec is not None else 1
             self.optimizer = ShardedAdamW(self.store, cfg.optimizer, total_steps=total, group=self._shard_group)
+            if self.expert_store is not None:
+                self.expert_optimizer = ShardedAdamW(self.expert_store, cfg.optimizer, total_steps=total, group=self._edp_group)
         if self.sp_size * tp > 1 and model_config.is_vlm:
             raise NotImplementedError("vision-language models run data-parallel only (no sequence / tensor parallelism yet)")
         if self.sp_size > 1:
@@ -518,6 +554,8 @@ class B200TrainEngine(TrainEngine):
     # ------------------------------------------------------------------ train / eval / forward
     def optimizer_zero_grad(self):
         self.store.zero_grad()
+        if getattr(self, "expert_store", None) is not None:
+            self.expert_store.zero_grad()
 
     def forward_backward_batch(self, mb_list: D.MicroBatchList, process_output_fn: Callable, forward_only: bool = False):
         """Runs every micro-batch; ``process_output_fn(hidden, labels, mb, pad_len, sl)`` returns a
@@ -633,6 +671,8 @@ class B200TrainEngine(TrainEngine):
         if hook is not None:
             hook()
         self.store.fold_autograd_grads()
+        if getattr(self, "expert_store", None) is not None:
+            return self._ep_optimizer_step()
         opt = self.optimizer
         tp = getattr(self, "tp_size", 1)
         if tp > 1:
@@ -696,9 +736,50 @@ class B200TrainEngine(TrainEngine):
         self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
         return dict(self.last_step_stats)
 
+    def _reduce_scatter_flat(self, store, group):
+        """Sum of ``store.flat_grad`` over ``group``; returns this rank's shard."""
+        if group is None or dist.get_world_size(group) == 1:
+            return store.grad_shard
+        if dist.get_backend(group) == "nccl":
+            out = torch.empty_like(store.grad_shard)
+            dist.reduce_scatter_tensor(out, store.flat_grad, group=group)
+            return out
+        dist.all_reduce(store.flat_grad, group=group)
+        return store.grad_shard
+
+    @staticmethod
+    def _all_gather_flat(store, group):
+        if group is not None and dist.get_world_size(group) > 1:
+            dist.all_gather_into_tensor(store.flat_param, store.param_shard.clone(), group=group)
+
+    def _ep_optimizer_step(self) -> dict[str, float]:
+        """Expert parallelism: the dense parameters' gradients are summed over all ranks, the
+        experts' over the replicas of the same experts; one global norm clips both."""
+        es = self.expert_store
+        es.fold_autograd_grads()
+        g_dense = self._reduce_scatter_flat(self.store, self._shard_group)
+        g_exp = self._reduce_scatter_flat(es, self._edp_group)
+        pre = (g_dense.float().pow(2).sum() + g_exp.float().pow(2).sum()).reshape(1)
+        if self._all_train_group is not None:
+            dist.all_reduce(pre, group=self._all_train_group)     # every shard of either kind lives on exactly one rank
+        res = self.optimizer.step(g_dense, precomputed_sumsq=pre)
+        self.expert_optimizer.step(g_exp, precomputed_sumsq=pre)
+        self._all_gather_flat(self.store, self._shard_group)
+        self._all_gather_flat(es, self._edp_group)
+        if self.model.cfg.router_bias_update_rate > 0:
+            for layer in self.model.layers:
+                upd = getattr(layer.mlp, "update_expert_bias", None)
+                if upd is not None:
+                    upd(self._shard_group)
+        st = res["state"].tolist()
+        self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
+        return dict(self.last_step_stats)
+
     def lr_scheduler_step(self):
         if self.optimizer is not None:
             self.optimizer.lr_scheduler_step()
+        if getattr(self, "expert_optimizer", None) is not None:
+            self.expert_optimizer.lr_scheduler_step()
 
     @torch.no_grad()
     def eval_batch(self, input_: dict[str, Any], loss_fn: Callable, loss_weight_fn: Callable) -> Optional[torch.Tensor]:
@@ -783,6 +864,16 @@ class B200TrainEngine(TrainEngine):
                 self.model_config.save_pretrained(meta.path)
                 if meta.tokenizer is not None:
                     meta.tokenizer.save_pretrained(meta.path)
+        elif meta.weight_format == "hf" and getattr(self, "ep_size", 1) > 1:
+            if self.dp_rank < self.ep_size:                   # the first EP group gathers its experts; its head writes
+                named = self._ep_full_named_tensors()
+                if head:
+                    hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named))
+                    if meta.tokenizer is not None:
+                        meta.tokenizer.save_pretrained(meta.path)
+                else:
+                    for _ in named:
+                        pass
         elif meta.weight_format == "hf":
             if getattr(self, "tp_size", 1) > 1:
                 # every tensor-parallel rank of the first data-parallel replica takes part in
@@ -814,8 +905,21 @@ class B200TrainEngine(TrainEngine):
             return
         if meta.with_optim and self.optimizer is not None:
             torch.save(self.optimizer.state_dict(), os.path.join(meta.path, f"optim_rank{max(self.local_index, 0)}.pt"))
+            if getattr(self, "expert_optimizer", None) is not None:
+                torch.save(self.expert_optimizer.state_dict(), os.path.join(meta.path, f"optim_expert_rank{max(self.local_index, 0)}.pt"))
         if self._cpu_group is not None:
             dist.barrier(group=self._cpu_group)
+
+    def _ep_full_named_tensors(self, to_cpu: bool = False):
+        """(name, tensor) with every expert stack gathered over the EP group (a collective of that group)."""
+        expert = set(self._expert_param_names)
+        for n_, p_ in self.model.named_parameters():
+            t = p_.detach()
+            if n_ in expert:
+                parts = [torch.empty_like(t) for _ in range(self.ep_size)]
+                dist.all_gather(parts, t.contiguous(), group=self._ep_group)
+                t = torch.cat(parts, dim=0)
+            yield n_, (t.to("cpu", copy=True) if to_cpu else t)
 
     def _gathered_full_tensors(self):
         """Yields (name, full tensor) for a tensor-parallel model; a collective over the TP group."""
@@ -833,6 +937,16 @@ class B200TrainEngine(TrainEngine):
             wanted = {hf for n in mine for hf, _, _ in plan[n]}
             hf_io.load_hf_tensors_into(self.model_config, {n: p.data for n, p in mine.items()},
                                        ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
+        elif meta.weight_format == "hf" and getattr(self, "ep_size", 1) > 1:
+            full = build_model(self.model_config, dtype=self.model.dtype, device=self.device, seed=0)
+            hf_io.load_model_hf(full, meta.path, strict=not self.config.is_critic)
+            src = dict(full.named_parameters())
+            El = self.model_config.num_experts // self.ep_size
+            with torch.no_grad():
+                for n_, p_ in self.model.named_parameters():
+                    t = src[n_].detach()
+                    p_.copy_(t[self.ep_rank * El:(self.ep_rank + 1) * El] if n_ in set(self._expert_param_names) else t)
+            del full, src
         elif meta.weight_format == "hf":
             if getattr(self, "tp_size", 1) > 1:
                 from ..parallel import tp as TP
@@ -849,6 +963,11 @@ class B200TrainEngine(TrainEngine):
 
             load_sharded(self, meta.path, with_optim=meta.with_optim)
             return
+        if getattr(self, "expert_optimizer", None) is not None:
+            self.expert_optimizer.resync_master()
+            pe = os.path.join(meta.path, f"optim_expert_rank{max(self.local_index, 0)}.pt")
+            if meta.with_optim and os.path.exists(pe):
+                self.expert_optimizer.load_state_dict(torch.load(pe, map_location="cpu", weights_only=False))
         if self.optimizer is not None:
             self.optimizer.resync_master()
             p = os.path.join(meta.path, f"optim_rank{max(self.local_index, 0)}.pt")
@@ -922,6 +1041,8 @@ class B200TrainEngine(TrainEngine):
                 return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters() if "_lora_" not in n}
             finally:
                 unmerge_lora_(self.model)
+        if getattr(self, "ep_size", 1) > 1:
+            return dict(self._ep_full_named_tensors(to_cpu=True))
         if getattr(self, "pp_size", 1) > 1:
             # every stage contributes its own tensors; all stages end up with the full dictionary
             parts = [None] * self.pp_size

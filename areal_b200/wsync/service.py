@@ -32,8 +32,8 @@ logger = alog.getLogger("wsync")
 
 
 class GatheredPusher:
-    """Pipeline-parallel trainer + engine in the same process: the stages exchange their tensors
-    (host side) and every rank loads the full set into its engine."""
+    """Pipeline- or expert-parallel trainer + engine in the same process: the ranks exchange the
+    tensors they own and every rank loads the full set into its engine."""
 
     def __init__(self, train_engine, infer_engine):
         self.train, self.infer = train_engine, infer_engine
@@ -81,7 +81,7 @@ class DiskPusher:
     def push(self, meta: WeightUpdateMeta):
         t0 = time.perf_counter()
         path = meta.path
-        if getattr(self.train, "pp_size", 1) * getattr(self.train, "tp_size", 1) > 1:
+        if getattr(self.train, "pp_size", 1) * getattr(self.train, "tp_size", 1) * getattr(self.train, "ep_size", 1) > 1:
             from ..api.io_struct import SaveLoadMeta
 
             self.train.save(SaveLoadMeta(path=path, weight_format="hf", with_optim=False))   # collective: gathers slices / stages
@@ -113,7 +113,7 @@ def make_weight_pusher(train_engine, infer_engine, meta: WeightUpdateMeta):
             return BroadcastWeightPusher(train_engine, infer_engine, infer_engine.wu_group,
                                          bucket_mb=meta.weight_chunked_mem_mb)
         return DistributedWeightPusher(train_engine, infer_engine, meta)
-    if getattr(train_engine, "pp_size", 1) > 1:
+    if getattr(train_engine, "pp_size", 1) > 1 or getattr(train_engine, "ep_size", 1) > 1:
         return GatheredPusher(train_engine, infer_engine)
     return InProcessPusher(train_engine, infer_engine)
 

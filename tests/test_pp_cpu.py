@@ -48,3 +48,16 @@ def test_train_engine_pipeline_x_data_parallel(tmp_path):
                        env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("ENGINE_PP_OK") == 4
+
+
+@pytest.mark.parametrize("ranks,port", [(2, 29941), (4, 29943)])
+def test_train_engine_expert_parallel(tmp_path, ranks, port):
+    """d{N}e2 engine on a tiny MoE model (dense parameters sharded over all ranks, experts over the
+    replicas of the same experts, one global norm) against one rank; HF export / reload, sharded
+    recovery checkpoint with both optimizers."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", EP_SAVE_DIR=str(tmp_path))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr",
+                        "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "dist_scripts", "run_engine_ep.py")], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ENGINE_EP_OK") == ranks
