@@ -296,6 +296,11 @@ class B200TrainEngine(TrainEngine):
             self.model = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
             if has_ckpt:
                 hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
+        f8 = cfg.archon.fp8 if cfg.archon.fp8.enabled else cfg.megatron.fp8
+        if f8.enabled and f8.include_dense and hasattr(self.model, "set_fp8"):
+            if tp > 1:
+                raise NotImplementedError("fp8 projections with tensor parallelism")
+            self.model.set_fp8(True)
         self._expert_param_names: list[str] = []
         if getattr(self, "ep_size", 1) > 1:
             from ..parallel.ep import shard_experts

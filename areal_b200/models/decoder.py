@@ -43,7 +43,13 @@ class PackedBatch:
 def _lin(mod, name: str, x: torch.Tensor, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ W^T (+ resid)`` for ``W = mod.<name>`` plus its low-rank adapter when one is attached
     (and not merged into ``W``)."""
-    y = OF.linear(x, getattr(mod, name), resid)
+    if getattr(mod, "use_fp8", False):
+        # block-scaled e4m3 operands in forward and input gradient, fp32 accumulation
+        y = OF.fp8_linear(x, getattr(mod, name))
+        if resid is not None:
+            y = y + resid
+    else:
+        y = OF.linear(x, getattr(mod, name), resid)
     st = getattr(mod, "lora", None)
     if st is not None and not st.merged and name in getattr(mod, "lora_targets", ()):
         y = y + st.scale * OF.linear(OF.linear(x, getattr(mod, name + "_lora_A")), getattr(mod, name + "_lora_B"))
@@ -339,6 +345,17 @@ class CausalLM(nn.Module):
                 h, resid = layer(h, resid, pb, cos, sin, fn)
         x, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
         return x
+
+    def set_fp8(self, dense: bool = True) -> int:
+        """Routes the dense projections (attention QKV / output, dense MLP) through the
+        block-scaled fp8 GEMM. Returns the number of modules switched."""
+        n = 0
+        for layer in self.layers:
+            mods = [layer.self_attn] + ([layer.mlp] if isinstance(layer.mlp, DenseMLP) else [])
+            for m in mods:
+                m.use_fp8 = bool(dense)
+                n += 1
+        return n
 
     def set_activation_checkpointing(self, mode: str = "none", fraction: float = 0.5) -> None:
         """``none`` keeps every activation; ``full`` recomputes every layer in the backward;

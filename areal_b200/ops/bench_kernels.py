@@ -94,6 +94,23 @@ def bench_gemm(a):
     return res
 
 
+def bench_gemm_fp8(a):
+    """e4m3 GEMM (``--split 1``: block-wise scales, 0: row-wise), operands quantised once outside the timed region."""
+    block = bool(a.split)
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.05).bfloat16()
+    am, bm = (OF.FP8_BLOCK_1x128, OF.FP8_BLOCK_128x128) if block else (OF.FP8_ROW, OF.FP8_ROW)
+    xq, xs = OF.quant_fp8(x, am)
+    wq, ws = OF.quant_fp8(w, bm)
+    ms = timeit(lambda: OF.gemm_fp8(xq, xs, wq, ws, block), a.iters, a.warmup)
+    res = report("gemm_fp8_tcgen05" + ("_blockscaled" if block else "_rowscaled"), ms, 2.0 * a.m * a.n * a.k,
+                 1.0 * (a.m * a.k + a.n * a.k) + 2.0 * a.m * a.n, m=a.m, n=a.n, k=a.k)
+    if a.compare:
+        ms_q = timeit(lambda: OF.quant_fp8(x, am), a.iters, a.warmup)
+        report("quant_fp8" + ("_1x128" if block else "_row"), ms_q, 0.0, 3.0 * a.m * a.k, m=a.m, k=a.k)
+    return res
+
+
 def bench_gemm_skinny(a):
     """Decode-shaped product: --m tokens (<= 256) against an [--n, --k] weight; --split 0 = automatic."""
     x = torch.randn(a.m, a.k, device="cuda").bfloat16()
@@ -262,7 +279,7 @@ def bench_engine_decode(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
                                            "engine_decode"])
     ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--new", type=int, default=128)
@@ -280,7 +297,7 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.kernel == "logprob" and a.rows > 4096:
         a.rows = 2048
-    return {"gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
+    return {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
             "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
             "engine_decode": bench_engine_decode}[a.kernel](a)
 

@@ -443,6 +443,123 @@ def embedding(ids, W):
 
 
 # ----------------------------------------------------------------------------- attention
+# --------------------------------------------------------------------------- fp8 (e4m3) GEMM
+FP8_MAX = 448.0
+FP8_ROW, FP8_BLOCK_1x128, FP8_BLOCK_128x128 = 0, 1, 2
+
+
+def quant_fp8_ref(x: torch.Tensor, mode: int, pow2: bool = False):
+    """Plain PyTorch statement of :func:`quant_fp8` (any device): returns (e4m3 tensor, fp32 scales)."""
+    R, K = x.shape
+    xf = x.float()
+    kb = (K + 127) // 128
+    if mode == FP8_ROW:
+        amax = xf.abs().amax(1)
+    elif mode == FP8_BLOCK_1x128:
+        pad = torch.zeros(R, kb * 128, device=x.device)
+        pad[:, :K] = xf.abs()
+        amax = pad.view(R, kb, 128).amax(-1).t().contiguous()              # [kb, R]
+    else:
+        rb = (R + 127) // 128
+        pad = torch.zeros(rb * 128, kb * 128, device=x.device)
+        pad[:R, :K] = xf.abs()
+        amax = pad.view(rb, 128, kb, 128).amax((1, 3))                      # [rb, kb]
+    s = amax.clamp(min=1e-12) / FP8_MAX
+    if pow2:
+        s = torch.exp2(torch.ceil(torch.log2(s)))
+    if mode == FP8_ROW:
+        full = s[:, None]
+    elif mode == FP8_BLOCK_1x128:
+        full = s.t().repeat_interleave(128, dim=1)[:, :K]
+    else:
+        full = s.repeat_interleave(128, 0).repeat_interleave(128, 1)[:R, :K]
+    q = (xf / full).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, s.float()
+
+
+def quant_fp8(x: torch.Tensor, mode: int = FP8_BLOCK_1x128, pow2: bool = False):
+    """bf16 ``[R, K]`` -> (e4m3 ``[R, K]``, fp32 scales). ``mode``: ``FP8_ROW`` one scale per row
+    (``[R]``); ``FP8_BLOCK_1x128`` one per row and 128-wide K block (``[ceil(K/128), R]``, the
+    activation layout); ``FP8_BLOCK_128x128`` one per 128 x 128 block (``[ceil(R/128), ceil(K/128)]``,
+    the weight layout). ``x = q * scale`` up to rounding; ``pow2`` rounds scales up to powers of two."""
+    if not x.is_cuda:
+        return quant_fp8_ref(x, mode, pow2)
+    R, K = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    q = torch.empty(R, K, dtype=torch.float8_e4m3fn, device=x.device)
+    kb = (K + 127) // 128
+    shape = (R,) if mode == FP8_ROW else ((kb, R) if mode == FP8_BLOCK_1x128 else ((R + 127) // 128, kb))
+    s = torch.empty(shape, dtype=torch.float32, device=x.device)
+    rc = _L().ab2_quant_fp8(x.data_ptr(), q.data_ptr(), s.data_ptr(), R, K, x.stride(0), q.stride(0), mode, int(pow2), _s())
+    _lib.check(rc, "ab2_quant_fp8")
+    return q, s
+
+
+def dequant_fp8(q: torch.Tensor, s: torch.Tensor, mode: int) -> torch.Tensor:
+    R, K = q.shape
+    if mode == FP8_ROW:
+        full = s[:, None]
+    elif mode == FP8_BLOCK_1x128:
+        full = s.t().repeat_interleave(128, dim=1)[:, :K]
+    else:
+        full = s.repeat_interleave(128, 0).repeat_interleave(128, 1)[:R, :K]
+    return q.float() * full
+
+
+def gemm_fp8(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, block_scaled: bool = True,
+             out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``[M, K] x [N, K]^T`` on e4m3 operands with fp32 accumulation. Block-scaled: ``a_s``
+    ``[ceil(K/128), M]`` and ``b_s`` ``[ceil(N/128), ceil(K/128)]``; otherwise row scales ``[M]`` / ``[N]``."""
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    if not a_q.is_cuda:
+        am = FP8_BLOCK_1x128 if block_scaled else FP8_ROW
+        bm = FP8_BLOCK_128x128 if block_scaled else FP8_ROW
+        return (dequant_fp8(a_q, a_s, am) @ dequant_fp8(b_q, b_s, bm).t()).to(out_dtype)
+    assert a_q.stride(1) == 1 and b_q.stride(1) == 1 and a_s.is_contiguous() and b_s.is_contiguous()
+    c = torch.empty(M, N, dtype=out_dtype, device=a_q.device)
+    rc = _L().ab2_gemm_fp8(a_q.data_ptr(), b_q.data_ptr(), c.data_ptr(), a_s.data_ptr(), b_s.data_ptr(), M, N, K, a_q.stride(0),
+                           b_q.stride(0), c.stride(0), int(block_scaled), int(out_dtype == torch.float32), _s())
+    _lib.check(rc, "ab2_gemm_fp8")
+    return c
+
+
+class _Fp8Linear(torch.autograd.Function):
+    """``y = x @ W^T`` with block-scaled fp8 operands in the forward and in the input gradient
+    (activations 1 x 128, weights 128 x 128 blocks, scales recomputed from the current values);
+    the weight gradient stays in bf16 / fp32 (it accumulates over micro-batches)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        xq, xs = quant_fp8(x.contiguous(), FP8_BLOCK_1x128)
+        wq, ws = quant_fp8(w, FP8_BLOCK_128x128)
+        ctx.save_for_backward(x, w)
+        return gemm_fp8(xq, xs, wq, ws, True, x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            # dx = dy @ W: contraction over the output features, so W is needed K-major in that dimension
+            dq, ds = quant_fp8(dy, FP8_BLOCK_1x128)
+            wtq, wts = quant_fp8(w.t().contiguous(), FP8_BLOCK_128x128)
+            dx = gemm_fp8(dq, ds, wtq, wts, True, x.dtype)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and x.is_cuda:
+                gemm(dy, x, a_mn=True, b_mn=True, out=mg, epi=EPI_F32_ACC)
+            else:
+                dw = (dy.float().t() @ x.float()).to(w.dtype)
+        return dx, dw
+
+
+def fp8_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return _Fp8Linear.apply(x, w)
+
+
 def attention_ref(q, k, v, cu_seqlens, causal=True, scale=None):
     """Packed varlen attention, fp32 math. q: [T,Hq,D], k/v: [T,Hkv,D]. Returns (o, lse[Hq,T])."""
     T, Hq, D = q.shape

@@ -395,3 +395,57 @@ def test_paged_decode_attention_matches_fp32(D, Hq, Hkv, page_size, splits):
         ref = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), v)
         err = ((out[b].float() - ref).norm() / ref.norm()).item()
         assert err < 1e-2, f"row {b} (len {n}): relative error {err}"
+
+
+@pytest.mark.parametrize("mode", [OF.FP8_ROW, OF.FP8_BLOCK_1x128, OF.FP8_BLOCK_128x128])
+@pytest.mark.parametrize("pow2", [False, True])
+def test_fp8_quantisation_kernels(mode, pow2):
+    """Scales equal the PyTorch statement; de-quantised values are within one e4m3 step."""
+    torch.manual_seed(mode)
+    x = (torch.randn(300, 576, device="cuda") * torch.rand(300, 1, device="cuda") * 3).bfloat16()
+    q, s = OF.quant_fp8(x, mode, pow2)
+    qr, sr = OF.quant_fp8_ref(x, mode, pow2)
+    assert s.shape == sr.shape and torch.allclose(s, sr, rtol=1e-6, atol=0)
+    d, dr = OF.dequant_fp8(q, s, mode), OF.dequant_fp8(qr, sr, mode)
+    assert (d - x.float()).abs().max() <= 0.0626 * x.float().abs().max()
+    # same rounding as the reference cast except at exact ties
+    assert (q.view(torch.uint8) != qr.view(torch.uint8)).float().mean().item() < 2e-3
+    assert oplib.kernel_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 512), (300, 384, 576), (4096, 1024, 2048), (64, 6144, 4096)])
+@pytest.mark.parametrize("block", [False, True])
+def test_fp8_gemm_matches_fp32_on_the_same_operands(M, N, K, block):
+    """tcgen05 kind::f8f6f4 GEMM with row-wise / block-wise scales against an fp32 matmul of the
+    de-quantised operands (so only the accumulation order differs)."""
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    am, bm = (OF.FP8_BLOCK_1x128, OF.FP8_BLOCK_128x128) if block else (OF.FP8_ROW, OF.FP8_ROW)
+    aq, sa = OF.quant_fp8(a, am)
+    bq, sb = OF.quant_fp8(b, bm)
+    ref = OF.dequant_fp8(aq, sa, am) @ OF.dequant_fp8(bq, sb, bm).t()
+    for dt, tol in ((torch.float32, 2e-4), (torch.bfloat16, 6e-3)):
+        c = OF.gemm_fp8(aq, sa, bq, sb, block, dt)
+        torch.cuda.synchronize()
+        assert oplib.kernel_error() == 0
+        err = ((c.float() - ref).norm() / ref.norm()).item()
+        assert err < tol, f"{dt}: relative error {err}"
+    # and the quantised product is close to the bf16 one
+    full = a.float() @ b.float().t()
+    assert ((ref - full).norm() / full.norm()).item() < 0.06
+
+
+def test_fp8_linear_gradients_close_to_bf16():
+    torch.manual_seed(0)
+    x = torch.randn(512, 1024, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(768, 1024, device="cuda") * 0.03).bfloat16().requires_grad_(True)
+    dy = torch.randn(512, 768, device="cuda").bfloat16()
+    y = OF.fp8_linear(x, w)
+    y.backward(dy)
+    yr = x.detach().float() @ w.detach().float().t()
+    assert ((y.float() - yr).norm() / yr.norm()).item() < 0.06
+    dxr = dy.float() @ w.detach().float()
+    dwr = dy.float().t() @ x.detach().float()
+    assert ((x.grad.float() - dxr).norm() / dxr.norm()).item() < 0.06
+    assert ((w.grad.float() - dwr).norm() / dwr.norm()).item() < 1e-2
