@@ -1048,6 +1048,8 @@ class B200TrainEngine(TrainEngine):
                 unmerge_lora_(self.model)
         if getattr(self, "ep_size", 1) > 1:
             return dict(self._ep_full_named_tensors(to_cpu=True))
+        if getattr(self, "tp_size", 1) > 1:
+            return {n: t.to("cpu", copy=True) for n, t in self._gathered_full_tensors()}
         if getattr(self, "pp_size", 1) > 1:
             # every stage contributes its own tensors; all stages end up with the full dictionary
             parts = [None] * self.pp_size

@@ -226,7 +226,10 @@ class MoEMLP(nn.Module):
                 outs.append(OF.linear(OF.swiglu(OF.linear(xe, self.w_gate_up[ge])), self.w_down[ge]))
             off += n
         if not outs:
-            return xs.new_zeros(0, self.cfg.hidden_size)
+            # no token reached this rank's experts: keep the (empty) result attached to ``xs`` so that
+            # the backward of the surrounding all-to-alls still runs here. Peers that did send tokens
+            # wait for this rank in those collectives; autograd would otherwise prune them.
+            return xs[:0] * 0.0
         return torch.cat(outs, dim=0)
 
     def forward(self, x):

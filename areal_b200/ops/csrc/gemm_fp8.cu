@@ -25,22 +25,33 @@
 namespace ab2 {
 
 static constexpr int F8_BM = 128;
-static constexpr int F8_BN = 128;
 static constexpr int F8_BK = 128;      // one 128-byte swizzle row of fp8
 static constexpr int F8_UMMA_K = 32;
-static constexpr int F8_STAGES = 6;
 static constexpr int F8_A_BYTES = F8_BM * F8_BK;
-static constexpr int F8_B_BYTES = F8_BN * F8_BK;
-static constexpr int F8_STAGE_BYTES = F8_A_BYTES + F8_B_BYTES;
-static constexpr int F8_SMEM_BYTES = F8_STAGES * F8_STAGE_BYTES + 1024 + 256;
-static constexpr int F8_TMEM_COLS = 2 * F8_BN;
+
+// BN = 128 for the block-wise recipe (the weight scale blocks are 128 wide and the promoted
+// accumulators live in registers); 256 for row-wise scales, where a wider tile halves the
+// shared-memory traffic per flop.
+template <int BN>
+struct F8Cfg {
+  static constexpr int B_BYTES = BN * F8_BK;
+  static constexpr int STAGE_BYTES = F8_A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
 
 // sa: row-wise: [M]; block-wise: [ceil(K / 128)][M] (K-block major, so a warp reads consecutive rows).
 // sb: row-wise: [N]; block-wise: [ceil(N / 128)][ceil(K / 128)].
-template <bool BLOCK_SCALED>
+template <bool BLOCK_SCALED, int F8_BN>
 __global__ void __launch_bounds__(192, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cptr,
                 const float* __restrict__ sa, const float* __restrict__ sb, int M, int N, int K, int ldc, int out_f32, int* err) {
+  using Cfg = F8Cfg<F8_BN>;
+  constexpr int F8_STAGES = Cfg::STAGES;
+  constexpr int F8_STAGE_BYTES = Cfg::STAGE_BYTES;
+  constexpr int F8_TMEM_COLS = Cfg::TMEM_COLS;
+  static_assert(!BLOCK_SCALED || F8_BN == 128, "block-wise scales: one weight scale block per tile column");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + F8_STAGES * F8_STAGE_BYTES;
@@ -237,7 +248,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
-template <bool BLOCK_SCALED>
+template <bool BLOCK_SCALED, int F8_BN>
 static int launch_fp8(const void* A, const void* B, void* C, const float* sa, const float* sb, int M, int N, int K, int lda, int ldb,
                       int ldc, int out_f32, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
@@ -245,7 +256,9 @@ static int launch_fp8(const void* A, const void* B, void* C, const float* sa, co
   if (rc) return 100 + rc;
   rc = ab2host::encode_tmap_2d(&tmB, B, 1, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, F8_BK, F8_BN, true, 2);
   if (rc) return 200 + rc;
-  auto kern = gemm_fp8_kernel<BLOCK_SCALED>;
+  using Cfg = F8Cfg<F8_BN>;
+  constexpr int F8_SMEM_BYTES = Cfg::SMEM_BYTES;
+  auto kern = gemm_fp8_kernel<BLOCK_SCALED, F8_BN>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES) != cudaSuccess) return 300;
@@ -395,8 +408,11 @@ int ab2_gemm_fp8(const void* A, const void* B, void* C, const float* sa, const f
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return 11;
   if (!sa || !sb) return 12;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return block_scaled ? launch_fp8<true>(A, B, C, sa, sb, M, N, K, lda, ldb, ldc, out_f32, s)
-                      : launch_fp8<false>(A, B, C, sa, sb, M, N, K, lda, ldb, ldc, out_f32, s);
+  if (block_scaled) return launch_fp8<true, 128>(A, B, C, sa, sb, M, N, K, lda, ldb, ldc, out_f32, s);
+  // wide tiles when they still fill the machine
+  const long long tiles256 = (long long)((M + F8_BM - 1) / F8_BM) * ((N + 255) / 256);
+  if (N % 256 == 0 && tiles256 >= 120) return launch_fp8<false, 256>(A, B, C, sa, sb, M, N, K, lda, ldb, ldc, out_f32, s);
+  return launch_fp8<false, 128>(A, B, C, sa, sb, M, N, K, lda, ldb, ldc, out_f32, s);
 }
 
 // x [rows, K] bf16 -> e4m3 + scales. mode 0: one scale per row ([rows]); mode 1: one per (row,

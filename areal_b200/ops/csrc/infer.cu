@@ -137,11 +137,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int g0 = 0; g0 < G; g0 += GH) {
       if constexpr (G > 4) {
 #pragma unroll
-        for (int g = 0; g < GH; ++g)
+        for (int g = 0; g < GH; ++g) {
+          if (g0 + g >= G) break;            // G need not be a multiple of GH (e.g. 6 query heads per kv head)
 #pragma unroll
           for (int cc = 0; cc < NC; ++cc)
 #pragma unroll
             for (int e = 0; e < 8; ++e) qr[g][cc * 8 + e] = sq[(g0 + g) * D + cc * 64 + lg * 8 + e];
+        }
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -160,6 +162,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         }
 #pragma unroll
         for (int g = 0; g < GH; ++g) {
+          if (g0 + g >= G) break;
           float s = 0.f;
 #pragma unroll
           for (int e = 0; e < NC * 8; ++e) s += qr[g][e] * kf[e];

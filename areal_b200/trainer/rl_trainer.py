@@ -115,7 +115,10 @@ class PPOTrainer:
 
         c = self.config
         eos = getattr(self.tokenizer, "eos_token_id", None)
-        share = self.actor.device.type == "cuda" and getattr(c.native_infer, "share_trainer_weights", True)
+        # a trainer rank that holds only part of the model (pipeline stage, expert or tensor slice)
+        # cannot lend its parameters to the engine: the engine keeps a full copy, fed by gathers
+        partial = any(getattr(self.actor, a, 1) > 1 for a in ("pp_size", "ep_size", "tp_size"))
+        share = self.actor.device.type == "cuda" and getattr(c.native_infer, "share_trainer_weights", True) and not partial
         if share:
             # colocated on one GPU: the rollout engine reads the trainer's bf16 parameters in
             # place (no second copy in HBM); generation is interrupted while the optimizer
@@ -128,7 +131,10 @@ class PPOTrainer:
         eng = NativeInferenceEngine(c.rollout, c.native_infer, model_config=self.actor.model_config, eos_token_id=eos)
         eng.initialize(device=self.actor.device, seed=c.seed, train_data_parallel_size=self.actor.data_parallel_world_size)
         # start from the trainer's weights
-        eng.update_weights_from_tensors(((n, p.data) for n, p in self.actor.model.named_parameters()))
+        if partial:
+            eng.update_weights_from_tensors(iter(self.actor.export_weights().items()))
+        else:
+            eng.update_weights_from_tensors(((n, p.data) for n, p in self.actor.model.named_parameters()))
         return eng
 
     def _choose_weight_update_meta(self) -> WeightUpdateMeta:

@@ -113,7 +113,7 @@ def make_weight_pusher(train_engine, infer_engine, meta: WeightUpdateMeta):
             return BroadcastWeightPusher(train_engine, infer_engine, infer_engine.wu_group,
                                          bucket_mb=meta.weight_chunked_mem_mb)
         return DistributedWeightPusher(train_engine, infer_engine, meta)
-    if getattr(train_engine, "pp_size", 1) > 1 or getattr(train_engine, "ep_size", 1) > 1:
+    if any(getattr(train_engine, a, 1) > 1 for a in ("pp_size", "ep_size", "tp_size")):
         return GatheredPusher(train_engine, infer_engine)
     return InProcessPusher(train_engine, infer_engine)
 

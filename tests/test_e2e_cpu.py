@@ -234,3 +234,47 @@ def test_moe_router_variants():
     assert y.shape == x.shape and torch.isfinite(y).all()
     y.sum().backward()
     assert m.router.grad is not None and torch.isfinite(m.router.grad).all()
+
+
+PARALLEL_TRAINER_SCRIPT = r'''
+import faulthandler, os, sys
+faulthandler.dump_traceback_later(200, exit=True)
+sys.path.insert(0, %(root)r)
+os.environ["AREAL_FORCE_CPU"] = "1"
+import torch, torch.distributed as dist
+from tests.test_e2e_cpu import _cfg, digit_reward
+from areal_b200.dataset import ArithmeticDataset
+from areal_b200.models.config import preset
+from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
+from areal_b200.trainer.rl_trainer import PPOTrainer
+dist.init_process_group("gloo")
+cfg = _cfg(%(tmp)r, steps=4)
+cfg.actor.backend = %(backend)r
+mc = preset(%(model)r, vocab_size=64, num_layers=2)
+with PPOTrainer(cfg, ArithmeticDataset(size=128), tokenizer=None, model_config=mc) as tr:
+    hist = tr.train(workflow=RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True))
+    # the rollout engine holds exactly the trainer's (gathered) weights
+    want = tr.actor.export_weights()
+    got = dict(tr.rollout.model.named_parameters())
+    assert set(want) == set(got)
+    for n, t in want.items():
+        assert torch.equal(t, got[n].detach().cpu()), n
+assert len(hist) == 4
+print("PARALLEL_TRAINER_OK", dist.get_rank(), flush=True)
+dist.barrier()
+'''
+
+
+@pytest.mark.parametrize("backend,model,port", [("native:d1p2", "tiny-qwen2", 29955), ("native:d2e2", "tiny-qwen3-moe", 29953),
+                                                ("d1t2", "tiny-qwen2", 29957)])
+def test_ppo_trainer_with_model_parallel_actor(tmp_path, backend, model, port):
+    """Whole GRPO loop on 2 gloo ranks with a pipeline- / expert- / tensor-parallel actor: every rank's
+    rollout engine keeps a full model that the trainer feeds with gathered weights."""
+    script = tmp_path / "par.py"
+    script.write_text(PARALLEL_TRAINER_SCRIPT % dict(root=ROOT, tmp=str(tmp_path), backend=backend, model=model))
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("PARALLEL_TRAINER_OK") == 2
