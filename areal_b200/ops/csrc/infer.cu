@@ -4,6 +4,7 @@
 //
 // These take the place of the SGLang / vLLM (FlashInfer, sgl_kernel) kernels that the
 // reference reaches through areal/engine/sglang_remote.py and areal/engine/vllm_remote.py.
+#include <cstdlib>
 #include <mutex>
 
 #include "ab2_noalloc.h"
@@ -268,6 +269,228 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 }
 
+// ------------------------------------------------------------------ paged decode attention, tensor-core form
+// Same decomposition as above (CTA = sequence x kv head x split, 64-token chunks staged by
+// asynchronous copies, one warp per 16 tokens of the chunk), but the two products run on
+// mma.sync m16n8k16 (bf16 in, fp32 out): the G query heads of the group are the rows of a
+// 16-row tile (rows >= G are zero), S = Q K^T takes D/16 steps per 8 tokens, and the
+// probabilities feed O += P V straight from the accumulator registers. About eight times fewer
+// issued instructions than the scalar form, so the kernel follows the memory system instead of
+// the issue slots. Rows of K / V / Q in shared memory are padded by 16 bytes so that the 8 x 8
+// matrix loads touch distinct banks.
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int D>
+struct DecodeMmaCfg {
+  static constexpr int STRIDE = D * 2 + 16;                       // bytes per staged row
+  static constexpr int OPERAND_BYTES = DEC_CHUNK * STRIDE;
+  static constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;           // K rows then V rows
+  static constexpr int Q_BYTES = 16 * STRIDE;
+  static constexpr int SMEM_BYTES = 2 * STAGE_BYTES + Q_BYTES;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128, 3)
+paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                        const __nv_bfloat16* __restrict__ vc, const int* __restrict__ page_table,
+                        const int* __restrict__ seq_lens, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int Hq, int Hkv, int G, int page_size, int max_pages, int num_splits, float scale) {
+  using Cfg = DecodeMmaCfg<D>;
+  constexpr int STRIDE = Cfg::STRIDE;
+  constexpr int KS = D / 16;                 // k-steps of S = Q K^T; also 16-dim column pairs of O
+  constexpr int PIECES = DEC_CHUNK * D * 2 / 16;
+  extern __shared__ __align__(128) unsigned char dsm[];
+  const int b = blockIdx.x, h = blockIdx.y, spl = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;    // row group / column pair inside a fragment
+  const int len = seq_lens[b];
+  const int per = (len + num_splits - 1) / num_splits;
+  const int t0 = spl * per, t1 = min(len, t0 + per);
+  const int n_chunks = t1 > t0 ? (t1 - t0 + DEC_CHUNK - 1) / DEC_CHUNK : 0;
+  const int* pt = page_table + (size_t)b * max_pages;
+  const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(dsm);
+  const uint32_t sq_addr = smem0 + 2 * Cfg::STAGE_BYTES;
+  const float sl2 = scale * 1.4426950408889634f;
+
+  auto issue = [&](int c, int stage) {
+    const int base = t0 + c * DEC_CHUNK;
+#pragma unroll
+    for (int i = 0; i < PIECES / 128; ++i) {
+      const int idx = tid + i * 128;
+      const int row = idx / (D / 8), piece = idx % (D / 8);
+      const int t = base + row;
+      const bool ok = t < t1;
+      size_t off = 0;
+      if (ok) {
+        const int page = pt[t / page_size];
+        off = (((size_t)page * page_size + (t % page_size)) * Hkv + h) * D + piece * 8;
+      }
+      const uint32_t dst = smem0 + stage * Cfg::STAGE_BYTES + row * STRIDE + piece * 16;
+      cp_async16(dst, kc + off, ok);
+      cp_async16(dst + Cfg::OPERAND_BYTES, vc + off, ok);
+    }
+    cp_async_commit();
+  };
+
+  if (n_chunks > 0) issue(0, 0);
+  // queries of the group as a 16-row tile (rows >= G zero)
+  for (int i = tid; i < 16 * (D / 8); i += 128) {
+    const int row = i / (D / 8), piece = i % (D / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)b * Hq + (size_t)h * G + row) * D + piece * 8);
+    *reinterpret_cast<uint4*>(dsm + 2 * Cfg::STAGE_BYTES + row * STRIDE + piece * 16) = v;
+  }
+  __syncthreads();
+  uint32_t qa[KS][4];
+  {
+    const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+      ldsm_x4(sq_addr + ((mat & 1) * 8 + r) * STRIDE + (ks * 16 + (mat >> 1) * 8) * 2, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};     // rows gq and gq + 8
+
+  for (int c = 0; c < n_chunks; ++c) {
+    const int stage = c & 1;
+    if (c + 1 < n_chunks) {
+      issue(c + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t ks_addr = smem0 + stage * Cfg::STAGE_BYTES + (warp * 16) * STRIDE;   // this warp's 16 tokens
+    const uint32_t vs_addr = ks_addr + Cfg::OPERAND_BYTES;
+    const int mat = lane >> 3, r = lane & 7;
+    // ---- S[16 heads, 16 tokens] = Q K^T
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t b0, b1, b2, b3;   // tokens 0-7: dims lo / hi; tokens 8-15: dims lo / hi
+      ldsm_x4(ks_addr + ((mat >> 1) * 8 + r) * STRIDE + (ks * 16 + (mat & 1) * 8) * 2, b0, b1, b2, b3);
+      mma_bf16_16816(s0, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      mma_bf16_16816(s1, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+    }
+    // ---- mask, running max per row over this warp's tokens
+    const int tok = t0 + c * DEC_CHUNK + warp * 16 + 2 * tq;
+    const bool v00 = tok < t1, v01 = tok + 1 < t1, v10 = tok + 8 < t1, v11 = tok + 9 < t1;
+    s0[0] = v00 ? s0[0] * sl2 : -INFINITY; s0[1] = v01 ? s0[1] * sl2 : -INFINITY;
+    s0[2] = v00 ? s0[2] * sl2 : -INFINITY; s0[3] = v01 ? s0[3] * sl2 : -INFINITY;
+    s1[0] = v10 ? s1[0] * sl2 : -INFINITY; s1[1] = v11 ? s1[1] * sl2 : -INFINITY;
+    s1[2] = v10 ? s1[2] * sl2 : -INFINITY; s1[3] = v11 ? s1[3] * sl2 : -INFINITY;
+    float alpha[2];
+    uint32_t pa[4];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {           // hh = 0: row gq (elements 0, 1); 1: row gq + 8 (elements 2, 3)
+      float mx = fmaxf(fmaxf(s0[2 * hh], s0[2 * hh + 1]), fmaxf(s1[2 * hh], s1[2 * hh + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float mn = fmaxf(m_run[hh], mx);
+      const float mref = (mn == -INFINITY) ? 0.f : mn;
+      alpha[hh] = fast_exp2(m_run[hh] - mref);
+      m_run[hh] = mn;
+      const float p00 = fast_exp2(s0[2 * hh] - mref), p01 = fast_exp2(s0[2 * hh + 1] - mref);
+      const float p10 = fast_exp2(s1[2 * hh] - mref), p11 = fast_exp2(s1[2 * hh + 1] - mref);
+      l_run[hh] = l_run[hh] * alpha[hh] + (p00 + p01 + p10 + p11);   // this thread's columns; summed over the quad at the end
+      pa[hh] = pack_bf16(p00, p01);            // A fragment: tokens 0-7
+      pa[2 + hh] = pack_bf16(p10, p11);        //             tokens 8-15
+    }
+    // ---- O[16 heads, D] = O * alpha + P V
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int jj = 0; jj < KS; ++jj) {          // 16 output dims per step
+      uint32_t b0, b1, b2, b3;   // dims lo: tokens 0-7 / 8-15; dims hi: tokens 0-7 / 8-15
+      ldsm_x4_trans(vs_addr + ((mat & 1) * 8 + r) * STRIDE + (jj * 16 + (mat >> 1) * 8) * 2, b0, b1, b2, b3);
+      mma_bf16_16816(o[2 * jj], pa[0], pa[1], pa[2], pa[3], b0, b1);
+      mma_bf16_16816(o[2 * jj + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
+    }
+    __syncthreads();   // every warp is done with this stage before the next copies land in it
+  }
+
+  // ---- merge the four warps (stage memory is free now): mo [4][16][D], mm / ml [4][16]
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
+    l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
+  }
+  float* mo = reinterpret_cast<float*>(dsm);
+  float* mm = mo + 4 * 16 * D;
+  float* ml = mm + 4 * 16;
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) {
+    const int col = j * 8 + 2 * tq;
+    *reinterpret_cast<float2*>(mo + ((warp * 16 + gq) * D + col)) = make_float2(o[j][0], o[j][1]);
+    *reinterpret_cast<float2*>(mo + ((warp * 16 + gq + 8) * D + col)) = make_float2(o[j][2], o[j][3]);
+  }
+  if (tq == 0) {
+    mm[warp * 16 + gq] = m_run[0]; mm[warp * 16 + gq + 8] = m_run[1];
+    ml[warp * 16 + gq] = l_run[0]; ml[warp * 16 + gq + 8] = l_run[1];
+  }
+  __syncthreads();
+  for (int i = tid; i < G * D; i += 128) {
+    const int g = i / D, d = i - g * D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mm[w * 16 + g]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mm[w * 16 + g];
+      const float wt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mx);
+      ll += ml[w * 16 + g] * wt;
+      oo += mo[(w * 16 + g) * D + d] * wt;
+    }
+    const size_t pidx = ((size_t)b * Hq + (size_t)h * G + g) * num_splits + spl;
+    part_o[pidx * D + d] = oo;
+    if (d == 0) {
+      part_ml[pidx * 2] = mx;
+      part_ml[pidx * 2 + 1] = ll;
+    }
+  }
+}
+
+template <int D>
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      __nv_bfloat16* __restrict__ out, int num_splits);
+
+template <int D>
+static int launch_decode_mma(const void* q, const void* kc, const void* vc, const int* pt, const int* lens,
+                             float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int page_size,
+                             int max_pages, int splits, float scale, cudaStream_t s) {
+  using Cfg = DecodeMmaCfg<D>;
+  static_assert(2 * Cfg::STAGE_BYTES >= (4 * 16 * D + 8 * 16) * 4, "the merge buffers alias the stage memory");
+  dim3 grid(B, Hkv, splits);
+  auto kern = paged_decode_mma_kernel<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 2;
+    attr_set = true;
+  }
+  kern<<<grid, 128, Cfg::SMEM_BYTES, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens, part_o,
+                                          part_ml, Hq, Hkv, Hq / Hkv, page_size, max_pages, splits, scale);
+  decode_combine_kernel<D><<<B * Hq, D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
 template <int D, int G>
 constexpr int decode_smem_bytes() {
   return 2 * (2 * DEC_CHUNK * D * 2) + (G * D + DEC_CHUNK * G) * 4;
@@ -425,6 +648,12 @@ int ab2_paged_decode(const void* q, const void* kc, const void* vc, const int* p
   if (Hq % Hkv || num_splits < 1) return 10;
   const int G = Hq / Hkv;
   cudaStream_t s = (cudaStream_t)stream;
+  // tensor-core form for every group size up to 16; AB2_DECODE_SIMT=1 selects the scalar form
+  static const bool simt = [] { const char* e = getenv("AB2_DECODE_SIMT"); return e && e[0] == '1'; }();
+  if (!simt && G <= 16 && (D == 64 || D == 128)) {
+    if (D == 128) return launch_decode_mma<128>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, page_size, max_pages, num_splits, scale, s);
+    return launch_decode_mma<64>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, page_size, max_pages, num_splits, scale, s);
+  }
 #define AB2_DEC(DD, GG)                                                                                   \
   if (D == DD && G == GG)                                                                                 \
     return launch_decode<DD, GG>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv,       \
