@@ -113,6 +113,31 @@ def small_id_fraction_reward_fn(prompt, completion, prompt_ids, completion_ids, 
     return sum(1 for t in completion_ids if t < threshold) / max(1, len(completion_ids))
 
 
+class CountdownDataset(Dataset):
+    """Procedural Countdown problems (offline stand-in for the reference's ``examples/countdown``
+    data): ``numbers`` and a reachable ``target``; items carry a ``prompt`` / ``messages`` pair."""
+
+    def __init__(self, size: int = 4096, seed: int = 1, n_numbers: int = 3, max_number: int = 50, tokenizer=None):
+        self.size, self.seed, self.n, self.max_number, self.tokenizer = size, seed, n_numbers, max_number, tokenizer
+
+    def __len__(self):
+        return self.size
+
+    def __getitem__(self, i):
+        rng = random.Random(self.seed * 7919 + i)
+        nums = [rng.randint(1, self.max_number) for _ in range(self.n)]
+        val = nums[0]
+        for x in nums[1:]:
+            op = rng.choice("+-*")
+            val = val + x if op == "+" else (val - x if op == "-" else val * x)
+        q = (f"Using the numbers {nums}, create an equation that equals {val}. Use each number exactly once with + - * /. "
+             "Put the equation inside <answer> </answer>.")
+        item = dict(prompt=q, messages=[{"role": "user", "content": q}], numbers=nums, target=val, idx=i)
+        if self.tokenizer is not None:
+            item["input_ids"] = list(self.tokenizer.encode(q))
+        return item
+
+
 class CountShapesDataset(Dataset):
     """Procedural vision-language task (offline stand-in for clevr_count_70k): a picture with
     ``k`` bright squares on a dark canvas; the question asks for ``k``. Items carry ``images``
@@ -212,6 +237,9 @@ def get_custom_dataset(path: str, type: str = "rl", split: str = "train", tokeni
         return RandomTokenDataset(kwargs.get("size", 4096), kwargs.get("prompt_len", 512), kwargs.get("vocab_size", 151936),
                                   seed=kwargs.get("seed", 1), median_len=kwargs.get("median_len", 1024),
                                   max_len=kwargs.get("max_len", 4096))
+    if path.startswith("synthetic/countdown"):
+        return CountdownDataset(size=kwargs.get("size", 4096), seed=kwargs.get("seed", 1), n_numbers=kwargs.get("n_numbers", 3),
+                                tokenizer=tokenizer)
     if path.startswith("synthetic/count_shapes"):
         return CountShapesDataset(size=kwargs.get("size", 1024), seed=kwargs.get("seed", 1), image_size=kwargs.get("image_size", 112),
                                   image_token_id=kwargs.get("image_token_id", 1000),

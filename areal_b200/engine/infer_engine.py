@@ -66,6 +66,9 @@ class _Seq:
     aborted: bool = False
     top_p: float = 1.0
     top_k: int = 0
+    stop_strs: tuple = ()                  # stop strings (need the request's tokenizer)
+    tokenizer: Any = None
+    stop_window: int = 16                  # tokens decoded per check
     mm: Any = None                         # vision-language request: {"pixel_values", "image_grid_thw"}
     rope_delta: int = 0                    # M-RoPE: rotary position of token i (after the prompt) = i + rope_delta
 
@@ -350,7 +353,8 @@ class NativeInferenceEngine(InferenceEngine):
                        stop_ids=set(g.stop_token_ids or []), ignore_eos=g.ignore_eos,
                        seed=(g.seed if g.seed is not None else zlib.crc32(req.rid.encode())) & 0x7FFFFFFF, future=(loop, fut),
                        t_submit=time.perf_counter(), top_p=g.top_p, top_k=0 if g.top_k >= 10 ** 7 else int(g.top_k),
-                       mm=mm, rope_delta=rope_delta)
+                       mm=mm, rope_delta=rope_delta, stop_strs=tuple(g.stop or ()), tokenizer=getattr(req, "tokenizer", None),
+                       stop_window=max(8, 2 * max((len(x) for x in (g.stop or [""])), default=0)))
             with self._lock:
                 self._waiting.append(seq)
             seg_tokens, seg_lps, seg_vers, stop_reason, t_first = await fut
@@ -466,6 +470,11 @@ class NativeInferenceEngine(InferenceEngine):
                 return "stop"
             if not s.ignore_eos and self.eos_token_id is not None and tok == self.eos_token_id:
                 return "stop"
+            if s.stop_strs and s.tokenizer is not None:
+                # stop strings are matched on the decoded tail (a string may span several tokens)
+                tail = s.tokenizer.decode(s.out_tokens[-s.stop_window:])
+                if any(st in tail for st in s.stop_strs):
+                    return "stop"
         if n >= s.max_new:
             return "length"
         if len(s.tokens) >= self.icfg.context_length:

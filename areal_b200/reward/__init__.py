@@ -41,3 +41,30 @@ def gsm8k_reward_fn(prompt, completions, prompt_ids, completion_ids, answer=None
 
 
 math_verify_reward_fn = gsm8k_reward_fn
+
+
+def countdown_reward_fn(prompt, completions, prompt_ids, completion_ids, numbers=None, target=None, **kwargs) -> float:
+    """Countdown: the completion's last equation (``<answer>...</answer>`` if present, else the last
+    line with digits) must use exactly the given numbers once each with + - * / and evaluate to
+    ``target``. 1.0 for a correct equation, 0.1 for a well-formed one with the wrong value, else 0."""
+    import ast
+    import re
+
+    text = completions or ""
+    m = re.findall(r"<answer>(.*?)</answer>", text, re.S)
+    expr = m[-1] if m else next((l for l in reversed(text.strip().splitlines()) if re.search(r"\d", l)), "")
+    expr = expr.split("=")[0].strip()
+    if not expr or not re.fullmatch(r"[\d\s+\-*/().]+", expr):
+        return 0.0
+    used = sorted(int(x) for x in re.findall(r"\d+", expr))
+    if numbers is None or used != sorted(int(x) for x in numbers):
+        return 0.0
+    try:
+        tree = ast.parse(expr, mode="eval")
+        ok_nodes = (ast.Expression, ast.BinOp, ast.UnaryOp, ast.Constant, ast.Add, ast.Sub, ast.Mult, ast.Div, ast.USub)
+        if not all(isinstance(n, ok_nodes) for n in ast.walk(tree)):
+            return 0.0
+        val = eval(compile(tree, "<countdown>", "eval"), {"__builtins__": {}}, {})
+    except Exception:
+        return 0.0
+    return 1.0 if target is not None and abs(val - float(target)) < 1e-6 else 0.1

@@ -200,3 +200,82 @@ def test_multi_turn_retries_with_discount_and_masks_feedback():
     assert t["rewards"].item() == 0.0
     t = asyncio.run(wf.arun_episode(ScriptedEngine(["right"]), {"input_ids": tok.encode("q?")}))
     assert t["rewards"].item() == 1.0
+
+
+class _ByteTokenizer:
+    vocab_size = 256
+    eos_token_id = 0
+
+    def encode(self, text):
+        return list(text.encode())
+
+    def decode(self, ids):
+        return bytes(int(i) for i in ids).decode(errors="replace")
+
+
+def test_tir_workflow_runs_code_and_masks_tool_output():
+    """Tool-integrated reasoning: a scripted engine writes a python block, the sandbox runs it,
+    the output block is appended with loss mask 0, and generation continues to the answer."""
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters
+    from areal_b200.api.io_struct import ModelResponse
+    from areal_b200.rollout.workflows.tir import TIRWorkflow
+
+    tok = _ByteTokenizer()
+    scripted = ["Let me compute.\n```python\nprint(6*7)\n```\n", "So the answer is 42."]
+    seen_prompts = []
+
+    class Engine:
+        def get_version(self):
+            return 3
+
+        async def agenerate(self, req):
+            seen_prompts.append(tok.decode(req.input_ids))
+            assert req.gconfig.stop == ["```\n"]
+            text = scripted[len(seen_prompts) - 1]
+            ids = tok.encode(text)
+            return ModelResponse(input_tokens=list(req.input_ids), output_tokens=ids, output_logprobs=[-0.5] * len(ids),
+                                 output_versions=[3] * len(ids), stop_reason="stop")
+
+    def reward(prompt, completion, prompt_ids, completion_ids, answer=None, **kw):
+        return float(completion.strip().endswith(str(answer) + "."))
+
+    wf = TIRWorkflow(reward, GenerationHyperparameters(max_new_tokens=200, max_tokens=600), tok, max_tool_calls=2)
+    out = asyncio.run(wf.arun_episode(Engine(), {"input_ids": tok.encode("What is 6*7? "), "answer": 42}))
+    assert len(seen_prompts) == 2 and "```output\n42\n```" in seen_prompts[1]
+    ids, lm = out["input_ids"][0].tolist(), out["loss_mask"][0].tolist()
+    text = tok.decode(ids)
+    assert text.endswith("So the answer is 42.") and out["rewards"].item() == 1.0
+    tool = "\n```output\n42\n```\n"
+    a = text.index(tool)
+    assert all(m == 0 for m in lm[a:a + len(tool)])                      # tool text is not trained on
+    n_prompt = len(tok.encode("What is 6*7? "))
+    assert all(m == 0 for m in lm[:n_prompt]) and sum(lm) == len(tok.encode(scripted[0])) + len(tok.encode(scripted[1]))
+    assert out["versions"][0][a].item() == -1 and out["versions"][0][-1].item() == 3
+    assert TIRWorkflow.pending_code("text ```python\nx=1\n```") == "x=1" and TIRWorkflow.pending_code("no code") is None
+
+
+def test_engine_stops_on_stop_strings():
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeInferConfig
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.engine.infer_engine import NativeInferenceEngine
+    from areal_b200.models.config import preset
+
+    tok = _ByteTokenizer()
+    eng = NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=2, context_length=128),
+                                model_config=preset("tiny-qwen2", vocab_size=tok.vocab_size, num_layers=1))
+    eng.initialize(device="cpu", start_executor=False)
+    try:
+        g = GenerationHyperparameters(max_new_tokens=40, max_tokens=100, greedy=True, ignore_eos=True)
+        free = asyncio.run(eng.agenerate(ModelRequest(rid="a", input_ids=tok.encode("12+3="), gconfig=g, tokenizer=tok)))
+        text = tok.decode(free.output_tokens)
+        assert len(free.output_tokens) == 40
+        stop = text[5:7]                                   # a two-character string the greedy continuation is known to contain
+        r = asyncio.run(eng.agenerate(ModelRequest(rid="b", input_ids=tok.encode("12+3="), gconfig=g.new(stop=[stop]), tokenizer=tok)))
+        got = tok.decode(r.output_tokens)
+        assert r.stop_reason == "stop" and got.endswith(stop) and len(r.output_tokens) == text.index(stop) + 2
+    finally:
+        eng.destroy()
