@@ -590,13 +590,15 @@ class NativeInferenceEngine(InferenceEngine):
                 if mode == "prefill":
                     o, _ = OF.attention_fwd(q, k, v, kw["cu"], True, scale, kw["tile_info"])
                     return o
-                o = torch.empty_like(q)
-                rc = L.ab2_paged_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), kw["pt"].data_ptr(),
-                                        kw["lens"].data_ptr(), self.s_part_o.data_ptr(), self.s_part_ml.data_ptr(),
-                                        o.data_ptr(), n, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim,
-                                        self.cache.page_size, self.max_pages_per_seq, self.n_splits, scale,
-                                        oplib.stream_ptr())
-                oplib.check(rc, "ab2_paged_decode")
+                # q may be the query part of the fused [q | k] buffer: rows q.stride(0) apart, heads dense
+                assert q.stride(2) == 1 and q.stride(1) == cfg.head_dim
+                o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+                rc = L.ab2_paged_decode_strided(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), kw["pt"].data_ptr(),
+                                                kw["lens"].data_ptr(), self.s_part_o.data_ptr(), self.s_part_ml.data_ptr(),
+                                                o.data_ptr(), n, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim,
+                                                self.cache.page_size, self.max_pages_per_seq, self.n_splits, scale,
+                                                q.stride(0), oplib.stream_ptr())
+                oplib.check(rc, "ab2_paged_decode_strided")
                 return o
             fns.append(fn)
         return fns

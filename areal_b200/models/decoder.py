@@ -82,7 +82,7 @@ class Attention(nn.Module):
         if qkv.is_cuda and not torch.is_grad_enabled() and D in (64, 128):
             # inference: one fused kernel for norm + rotation; v stays a strided view
             qk, _ = OF.qknorm_rope_fwd(qkv, self.q_norm, self.k_norm, pb_positions, cos, sin, nq, nkv, D, self.cfg.rms_norm_eps)
-            return qk[:, :nq].contiguous(), qk[:, nq:], qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+            return qk[:, :nq], qk[:, nq:], qkv[:, (nq + nkv) * D:].view(T, nkv, D)   # strided views: no copies
         q = qkv[:, : nq * D].view(T, nq, D)
         k = qkv[:, nq * D: (nq + nkv) * D].view(T, nkv, D)
         v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)

@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(128, 3)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                     const __nv_bfloat16* __restrict__ vc, const int* __restrict__ page_table,
                     const int* __restrict__ seq_lens, float* __restrict__ part_o, float* __restrict__ part_ml,
-                    int Hq, int Hkv, int page_size, int max_pages, int num_splits, float scale) {
+                    int Hq, int Hkv, int page_size, int max_pages, int num_splits, float scale, long long q_stride) {
   constexpr int NC = D / 64;            // 8-dim pieces per lane in the score phase
   constexpr int DPL = D / 32;           // dims per lane in the output phase
   constexpr int GH = G < 4 ? G : 4;     // query heads held in registers at a time
@@ -99,7 +99,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
   if (n_chunks > 0) issue(0, 0);
   for (int i = tid; i < G * D; i += 128)
-    sq[i] = __bfloat162float(q[((size_t)b * Hq + (size_t)h * G) * D + i]) * sl2;
+    sq[i] = __bfloat162float(q[(size_t)b * q_stride + (size_t)h * G * D + i]) * sl2;
   __syncthreads();
 
   float m_run[G], l_run[G], o[G][DPL];
@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(128, 3)
 paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                         const __nv_bfloat16* __restrict__ vc, const int* __restrict__ page_table,
                         const int* __restrict__ seq_lens, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int Hq, int Hkv, int G, int page_size, int max_pages, int num_splits, float scale) {
+                        int Hq, int Hkv, int G, int page_size, int max_pages, int num_splits, float scale, long long q_stride) {
   using Cfg = DecodeMmaCfg<D>;
   constexpr int STRIDE = Cfg::STRIDE;
   constexpr int KS = D / 16;                 // k-steps of S = Q K^T; also 16-dim column pairs of O
@@ -348,7 +348,7 @@ paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   for (int i = tid; i < 16 * (D / 8); i += 128) {
     const int row = i / (D / 8), piece = i % (D / 8);
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)b * Hq + (size_t)h * G + row) * D + piece * 8);
+    if (row < G) v = *reinterpret_cast<const uint4*>(q + (size_t)b * q_stride + ((size_t)h * G + row) * D + piece * 8);
     *reinterpret_cast<uint4*>(dsm + 2 * Cfg::STAGE_BYTES + row * STRIDE + piece * 16) = v;
   }
   __syncthreads();
@@ -475,7 +475,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 template <int D>
 static int launch_decode_mma(const void* q, const void* kc, const void* vc, const int* pt, const int* lens,
                              float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int page_size,
-                             int max_pages, int splits, float scale, cudaStream_t s) {
+                             int max_pages, int splits, float scale, long long q_stride, cudaStream_t s) {
   using Cfg = DecodeMmaCfg<D>;
   static_assert(2 * Cfg::STAGE_BYTES >= (4 * 16 * D + 8 * 16) * 4, "the merge buffers alias the stage memory");
   dim3 grid(B, Hkv, splits);
@@ -486,7 +486,7 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
     attr_set = true;
   }
   kern<<<grid, 128, Cfg::SMEM_BYTES, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens, part_o,
-                                          part_ml, Hq, Hkv, Hq / Hkv, page_size, max_pages, splits, scale);
+                                          part_ml, Hq, Hkv, Hq / Hkv, page_size, max_pages, splits, scale, q_stride);
   decode_combine_kernel<D><<<B * Hq, D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
@@ -605,7 +605,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, in
 template <int D, int G>
 static int launch_decode(const void* q, const void* kc, const void* vc, const int* pt, const int* lens,
                          float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int page_size,
-                         int max_pages, int splits, float scale, cudaStream_t s) {
+                         int max_pages, int splits, float scale, long long q_stride, cudaStream_t s) {
   dim3 grid(B, Hkv, splits);
   constexpr int SMEM = decode_smem_bytes<D, G>();
   static_assert(SMEM >= (4 * G * D + 8 * G) * 4, "the merge buffers alias the stage memory");
@@ -616,7 +616,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
     attr_set = true;
   }
   kern<<<grid, 128, SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens, part_o, part_ml,
-                               Hq, Hkv, page_size, max_pages, splits, scale);
+                               Hq, Hkv, page_size, max_pages, splits, scale, q_stride);
   decode_combine_kernel<D><<<B * Hq, D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
@@ -641,27 +641,36 @@ int ab2_kv_append(const void* k, const void* v, void* kc, void* vc, const int* s
 }
 
 // Workspace sizes (floats) for ab2_paged_decode: part_o = B*Hq*splits*D, part_ml = B*Hq*splits*2.
-int ab2_paged_decode(const void* q, const void* kc, const void* vc, const int* page_table, const int* seq_lens,
-                     float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int page_size,
-                     int max_pages, int num_splits, float scale, void* stream) {
+// q_stride: elements between consecutive rows of q (Hq * D when q is dense; larger when q is the query part
+// of a fused [q | k] buffer). out is dense [B, Hq, D].
+int ab2_paged_decode_strided(const void* q, const void* kc, const void* vc, const int* page_table, const int* seq_lens,
+                             float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int page_size,
+                             int max_pages, int num_splits, float scale, long long q_stride, void* stream) {
   if (B <= 0) return 0;
-  if (Hq % Hkv || num_splits < 1) return 10;
+  if (Hq % Hkv || num_splits < 1 || (q_stride & 7)) return 10;
   const int G = Hq / Hkv;
   cudaStream_t s = (cudaStream_t)stream;
   // tensor-core form for every group size up to 16; AB2_DECODE_SIMT=1 selects the scalar form
   static const bool simt = [] { const char* e = getenv("AB2_DECODE_SIMT"); return e && e[0] == '1'; }();
   if (!simt && G <= 16 && (D == 64 || D == 128)) {
-    if (D == 128) return launch_decode_mma<128>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, page_size, max_pages, num_splits, scale, s);
-    return launch_decode_mma<64>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, page_size, max_pages, num_splits, scale, s);
+    if (D == 128) return launch_decode_mma<128>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, page_size, max_pages, num_splits, scale, q_stride, s);
+    return launch_decode_mma<64>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, page_size, max_pages, num_splits, scale, q_stride, s);
   }
 #define AB2_DEC(DD, GG)                                                                                   \
   if (D == DD && G == GG)                                                                                 \
     return launch_decode<DD, GG>(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv,       \
-                                 page_size, max_pages, num_splits, scale, s);
+                                 page_size, max_pages, num_splits, scale, q_stride, s);
   AB2_DEC(128, 1) AB2_DEC(128, 2) AB2_DEC(128, 4) AB2_DEC(128, 6) AB2_DEC(128, 8)
   AB2_DEC(64, 1) AB2_DEC(64, 2) AB2_DEC(64, 4) AB2_DEC(64, 8)
 #undef AB2_DEC
   return 11;
+}
+
+int ab2_paged_decode(const void* q, const void* kc, const void* vc, const int* page_table, const int* seq_lens,
+                     float* part_o, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int page_size,
+                     int max_pages, int num_splits, float scale, void* stream) {
+  return ab2_paged_decode_strided(q, kc, vc, page_table, seq_lens, part_o, part_ml, out, B, Hq, Hkv, D, page_size, max_pages,
+                                  num_splits, scale, (long long)Hq * D, stream);
 }
 
 int ab2_sample(const float* logits, long long ld, int B, int V, const float* inv_temp, const int* greedy,

@@ -47,6 +47,7 @@ _SIGS = {
     "ab2_logprob_combine": ([c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p], c_int),
     "ab2_kv_append": ([c_void_p] * 5 + [c_int, c_int, c_int, c_ll, c_ll, c_void_p], c_int),
     "ab2_paged_decode": ([c_void_p] * 8 + [c_int] * 7 + [c_float, c_void_p], c_int),
+    "ab2_paged_decode_strided": ([c_void_p] * 8 + [c_int] * 7 + [c_float, c_ll, c_void_p], c_int),
     "ab2_sample": ([c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint, c_void_p, c_void_p, c_void_p], c_int),
     "ab2_attn_delta": ([c_void_p] * 3 + [c_int] * 3 + [c_ll, c_ll, c_void_p], c_int),
     "ab2_attn_bwd": ([c_void_p] * 11 + [c_int] * 5 + [c_ll] * 6 + [c_float, c_int, c_void_p], c_int),
@@ -103,7 +104,7 @@ def get_lib():
 
 
 # Number of kernels each exported launcher enqueues (used for launch accounting).
-_KERNELS_PER_CALL = {"ab2_paged_decode": 2, "ab2_paged_decode_noalloc": 2, "ab2_kernel_error": 0, "ab2_runtime_init": 0, "ab2_num_sms": 0}
+_KERNELS_PER_CALL = {"ab2_paged_decode": 2, "ab2_paged_decode_strided": 2, "ab2_paged_decode_noalloc": 2, "ab2_kernel_error": 0, "ab2_runtime_init": 0, "ab2_num_sms": 0}
 LAUNCHES = {"count": 0}
 
 
