@@ -98,7 +98,19 @@ class PagedKVCache:
 
 class NativeInferenceEngine(InferenceEngine):
     def __init__(self, config: Optional[InferenceEngineConfig] = None, infer_config: Optional[NativeInferConfig] = None,
-                 model_config: Optional[ModelConfig] = None, model: Optional[CausalLM] = None, eos_token_id: Optional[int] = None):
+                 model_config: Optional[ModelConfig] = None, model: Optional[CausalLM] = None, eos_token_id: Optional[int] = None,
+                 tp_group=None, tp_control_group=None):
+        """``tp_group``: ranks that hold one tensor-parallel replica together (attention heads and
+        MLP columns split, embeddings replicated). Every rank of the group runs this engine; the
+        group's first rank is the leader and the only one that accepts requests. The ranks move in
+        lock-step: once per loop iteration they exchange a small control record (new requests,
+        pause / stop flags) over ``tp_control_group`` (a gloo group of the same ranks; defaults to
+        ``tp_group``), after which scheduling, paging and sampling are deterministic and identical
+        everywhere."""
+        self.tp_group, self.tp_control_group = tp_group, (tp_control_group if tp_control_group is not None else tp_group)
+        self.tp_size = torch.distributed.get_world_size(tp_group) if tp_group is not None else 1
+        self.tp_rank = torch.distributed.get_rank(tp_group) if tp_group is not None else 0
+        self._inbox: collections.deque = collections.deque()
         self.config = config or InferenceEngineConfig()
         self.icfg = infer_config or NativeInferConfig()
         self.model_config = model_config or (model.cfg if model is not None else None)
@@ -140,6 +152,8 @@ class NativeInferenceEngine(InferenceEngine):
                 from ..models import hf_io
 
                 hf_io.load_model_hf(self.model, model_path)
+            if self.tp_size > 1:
+                self._shard_model_for_tp(dtype, seed)
         self.shared_model = kwargs.get("shared_model", False)
         if not self.shared_model:
             self.model.eval()
@@ -154,6 +168,23 @@ class NativeInferenceEngine(InferenceEngine):
 
             self._executor = WorkflowExecutor(self.config, self, dp_world_size=train_data_parallel_size).initialize()
         return self
+
+    def _shard_model_for_tp(self, dtype, seed):
+        """Replaces the freshly built (or loaded) full model by this rank's tensor-parallel slice."""
+        from ..parallel import tp as TP
+
+        if self.model_config.is_vlm:
+            raise NotImplementedError("tensor-parallel rollout of vision-language models")
+        full, full_cfg = self.model, self.model_config
+        self.full_model_config = full_cfg
+        self.model_config = TP.local_config(full_cfg, self.tp_size)
+        self.model = build_model(self.model_config, dtype=dtype, device=self.device, seed=seed)
+        TP.load_sharded_from_full(self.model, full_cfg, {n: p.detach() for n, p in full.named_parameters()}, self.tp_size, self.tp_rank)
+        TP.install_tp(self.model, self.tp_group, self.tp_size, self.tp_rank)
+        del full
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+            self.icfg.use_cuda_graph = False   # decode steps contain collectives: replayed eagerly
 
     def _init_cuda_state(self):
         cfg, ic = self.model_config, self.icfg
@@ -250,6 +281,10 @@ class NativeInferenceEngine(InferenceEngine):
         if isinstance(named_tensors, dict):
             named_tensors = named_tensors.items()
         for name, t in named_tensors:
+            if self.tp_size > 1 and tuple(t.shape) != tuple(params[name].shape):
+                from ..parallel import tp as TP
+
+                t = TP.shard_tensor(self.full_model_config, name, t, self.tp_size, self.tp_rank)   # full tensor -> this rank's slice
             params[name].data.copy_(t.to(params[name].dtype), non_blocking=True)
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
@@ -267,7 +302,16 @@ class NativeInferenceEngine(InferenceEngine):
         from ..models import hf_io
 
         fut: Future = Future()
-        hf_io.load_model_hf(self.model, meta.path)
+        if self.tp_size > 1:
+            from ..parallel import tp as TP
+
+            full = build_model(self.full_model_config, dtype=self.model.dtype, device="cpu", seed=0)
+            hf_io.load_model_hf(full, meta.path)
+            TP.load_sharded_from_full(self.model, self.full_model_config, {n: p.detach() for n, p in full.named_parameters()},
+                                      self.tp_size, self.tp_rank)
+            del full
+        else:
+            hf_io.load_model_hf(self.model, meta.path)
         if meta.version is not None:
             self.set_version(meta.version)
         fut.set_result(True)
@@ -326,6 +370,11 @@ class NativeInferenceEngine(InferenceEngine):
         """Interruptible generation: loops over engine submissions until the request stops for
         a real reason; every segment is tagged with the weight version it ran under."""
         g = req.gconfig
+        if self.tp_size > 1:
+            if self.tp_rank != 0:
+                raise RuntimeError("requests go to the leader (first rank) of a tensor-parallel replica")
+            if g.stop:
+                raise NotImplementedError("stop strings with a tensor-parallel replica (use stop_token_ids)")
         prompt = list(req.input_ids)
         budget = min(g.max_tokens - len(prompt), g.max_new_tokens)
         if budget <= 0:
@@ -356,7 +405,7 @@ class NativeInferenceEngine(InferenceEngine):
                        mm=mm, rope_delta=rope_delta, stop_strs=tuple(g.stop or ()), tokenizer=getattr(req, "tokenizer", None),
                        stop_window=max(8, 2 * max((len(x) for x in (g.stop or [""])), default=0)))
             with self._lock:
-                self._waiting.append(seq)
+                (self._inbox if self.tp_size > 1 else self._waiting).append(seq)
             seg_tokens, seg_lps, seg_vers, stop_reason, t_first = await fut
             if seg_tokens and ttft == float("inf"):
                 ttft = t_first - t0
@@ -397,8 +446,13 @@ class NativeInferenceEngine(InferenceEngine):
         try:
             if self.device.type == "cuda":
                 torch.cuda.set_device(self.device)
-            while not self._stop.is_set():
-                if self._gen_paused.is_set():
+            while self.tp_size > 1 or not self._stop.is_set():      # a TP replica leaves the loop together (stop is exchanged)
+                paused = self._gen_paused.is_set()
+                if self.tp_size > 1:
+                    paused, stop = self._tp_sync_control(paused)
+                    if stop:
+                        break
+                if paused:
                     if not getattr(self.icfg, "retain_kv_on_weight_update", False):
                         self._abort_all()
                     self._idle.set()
@@ -431,14 +485,40 @@ class NativeInferenceEngine(InferenceEngine):
         finally:
             self._idle.set()
 
+    _SEQ_WIRE_FIELDS = ("rid", "tokens", "prompt_len", "max_new", "min_new", "temperature", "greedy", "stop_ids", "ignore_eos", "seed",
+                        "top_p", "top_k", "rope_delta")
+
+    def _tp_sync_control(self, paused: bool):
+        """One exchange per loop iteration of a tensor-parallel replica: every rank reports its
+        pause / stop flags, the leader adds the requests that arrived since the last exchange.
+        Afterwards all ranks hold the same waiting queue and take the same branch."""
+        import torch.distributed as dist
+
+        mine = {"paused": paused, "stop": self._stop.is_set(), "new": None}
+        fresh: list[_Seq] = []
+        if self.tp_rank == 0:
+            with self._lock:
+                while self._inbox:
+                    fresh.append(self._inbox.popleft())
+            mine["new"] = [{k: getattr(q, k) for k in self._SEQ_WIRE_FIELDS} for q in fresh]
+        box = [None] * self.tp_size
+        dist.all_gather_object(box, mine, group=self.tp_control_group)
+        arrivals = fresh if self.tp_rank == 0 else [_Seq(future=None, t_submit=time.perf_counter(), **d) for d in (box[0]["new"] or [])]
+        if arrivals:
+            with self._lock:
+                self._waiting.extend(arrivals)
+        return any(b["paused"] for b in box), any(b["stop"] for b in box)
+
     def _resolve(self, seq: _Seq, reason: str):
-        loop, fut = seq.future
         res = (seq.out_tokens, seq.out_logprobs, seq.out_versions, reason, seq.t_first)
         if self.cache is not None and seq.pages:
             self.cache.release(seq.pages)
             seq.pages = []
         if seq.row >= 0:
             self._free_row(seq)
+        if seq.future is None:          # follower of a tensor-parallel replica: the leader answers the client
+            return
+        loop, fut = seq.future
 
         def _set():
             if not fut.done():
@@ -451,6 +531,8 @@ class NativeInferenceEngine(InferenceEngine):
             self._waiting.clear()
             self._running = []
         for s in seqs:
+            if s.future is None:
+                continue
             loop, fut = s.future
             loop.call_soon_threadsafe(lambda f=fut: (not f.done()) and f.set_exception(RuntimeError(f"engine failed: {e!r}")))
 

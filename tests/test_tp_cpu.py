@@ -67,3 +67,14 @@ def test_sequence_parallel_tp_linear_pair_gloo():
                        capture_output=True, text=True, timeout=200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("TP_SP_OK") == 2
+
+
+def test_tensor_parallel_rollout_replica_gloo():
+    """Inference engine with tp=2 (leader + follower in lock-step) against a single-rank engine:
+    identical tokens and log-probs, weight update from full tensors, joint shutdown."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29981", os.path.join(ROOT, "tests", "dist_scripts", "run_infer_tp.py")], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("INFER_TP_OK") == 2
