@@ -61,6 +61,10 @@ class PPOTrainer:
         if config.ref is not None and config.actor.kl_ctl > 0:
             self.ref = self._create_train_engine(config.ref, "ref")
         self.teacher = self._create_train_engine(config.teacher, "teacher") if config.teacher is not None else None
+        # resumable loader; data-parallel ranks draw disjoint prompts (model-parallel peers share their head's batch)
+        dp_rank = int(getattr(self.actor, "data_parallel_rank", 0) or 0)
+        dp_world = int(getattr(self.actor, "data_parallel_world_size", 1) or 1)
+        self.train_dataloader = self._make_dataloader(train_dataset, config.train_dataset, dp_rank, dp_world)
         self.rollout = rollout_engine or self._init_rollout()
         self.eval_rollout = None
         self.weight_update_meta = self._choose_weight_update_meta()
@@ -88,12 +92,14 @@ class PPOTrainer:
         if c.gconfig.n_samples < 1:
             raise ValueError("gconfig.n_samples must be >= 1")
 
-    def _make_dataloader(self, dataset, dcfg):
+    def _make_dataloader(self, dataset, dcfg, rank: int = 0, world: int = 1):
         if dataset is None or dcfg is None:
             return None
-        g = torch.Generator().manual_seed(self.config.seed)
-        return DataLoader(dataset, batch_size=dcfg.batch_size, shuffle=dcfg.shuffle, drop_last=dcfg.drop_last,
-                          collate_fn=_collate_list, generator=g, num_workers=0)
+        from ..utils.dataloader import StatefulDataLoader
+
+        # every rank hands ``batch_size`` prompts per call to its own rollout executor
+        return StatefulDataLoader(dataset, dcfg.batch_size, shuffle=dcfg.shuffle, drop_last=dcfg.drop_last, collate_fn=_collate_list,
+                                  seed=self.config.seed, rank=rank, world_size=world)
 
     def _create_train_engine(self, ecfg, role: str):
         from ..engine.train_engine import B200PPOActor, B200PPOCritic

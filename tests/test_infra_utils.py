@@ -160,3 +160,83 @@ def test_delta_weight_transfer_exact_and_predicted():
     frac = p.push()
     assert _torch.equal(dst, src) and 0 < frac < 1.0 and abs(frac - exact.float().mean().item()) < 0.05
     assert p.push() == 0.0 and len(copies) < 2 + exact.sum().item() + 1
+
+
+def test_stateful_dataloader_resumes_and_partitions():
+    from areal_b200.utils.dataloader import StatefulDataLoader, create_dataloader
+
+    data = list(range(103))
+    loaders = [create_dataloader(data, 8, rank=r, world_size=2, seed=3) for r in range(2)]
+    assert all(len(l) == 51 // 4 for l in loaders)
+    e0 = [list(l) for l in loaders]
+    seen = [x for b in e0[0] for x in b] + [x for b in e0[1] for x in b]
+    assert len(seen) == len(set(seen)) == 2 * 12 * 4                     # ranks see disjoint samples
+    e1 = [x for b in loaders[0] for x in b]
+    assert e1 != [x for b in e0[0] for x in b]                           # next epoch: another permutation
+    # resume in the middle of an epoch
+    a = StatefulDataLoader(data, 5, seed=1)
+    it = iter(a)
+    first = [next(it) for _ in range(7)]
+    sd = a.state_dict()
+    rest = list(it)
+    b = StatefulDataLoader(data, 5, seed=1)
+    b.load_state_dict(sd)
+    assert list(b) == rest and sd["served"] == 7
+    assert first + rest == list(StatefulDataLoader(data, 5, seed=1))
+    # a finished epoch resumes at the start of the next one
+    c = StatefulDataLoader(data, 5, seed=1)
+    list(c)
+    d = StatefulDataLoader(data, 5, seed=1)
+    d.load_state_dict(c.state_dict())
+    assert d.epoch == 1 and list(d) == list(c)
+    # without drop_last every rank still gets the same number of batches
+    u = [StatefulDataLoader(data, 4, drop_last=False, rank=r, world_size=3, seed=0) for r in range(3)]
+    assert len({len(list(x)) for x in u}) == 1
+
+
+def test_slurm_and_ray_launcher_plans(tmp_path, capsys):
+    from areal_b200.api.cli_args import BaseExperimentConfig, ClusterSpecConfig
+    from areal_b200.infra.launcher import ray as ray_launcher
+    from areal_b200.infra.launcher import slurm as slurm_launcher
+
+    cfg = BaseExperimentConfig(experiment_name="e", trial_name="t", allocation_mode="native:d2+d12", cluster=ClusterSpecConfig(fileroot=str(tmp_path)))
+    jobs = slurm_launcher.plan_jobs("train.py", ["--config", "c.yaml"], cfg, gpus_per_node=8)
+    assert [j["name"] for j in jobs] == ["llm_server", "trainer"]
+    assert jobs[0]["nodes"] == 1 and jobs[0]["gpus_per_node"] == 2 and jobs[1]["nodes"] == 2 and jobs[1]["gpus_per_node"] == 8
+    assert "--nnodes=2 --nproc-per-node=8" in jobs[1]["command"] and "train.py --config c.yaml" in jobs[1]["command"]
+    assert slurm_launcher.launch("train.py", ["--config", "c.yaml"], cfg, dry_run=True) == 0
+    out = capsys.readouterr().out
+    assert out.count("#SBATCH --job-name=e_t:") == 2 and "--gres=gpu:8" in out and "srun" in out
+    tasks = ray_launcher.plan_tasks(cfg)
+    assert [t["role"] for t in tasks].count("server") == 2 and [t["role"] for t in tasks].count("trainer") == 12
+    assert tasks[-1]["rank"] == 11 and tasks[-1]["world"] == 12
+
+    # the Ray launcher against a stand-in module: servers are cancelled when the trainers return
+    calls = {"run": [], "cancel": 0}
+
+    class _Handle:
+        def __init__(self, fn, opts):
+            self.fn, self.opts = fn, opts
+
+        def options(self, **kw):
+            return _Handle(self.fn, kw)
+
+        def remote(self, *a):
+            calls["run"].append((self.opts.get("name"), a[0]))
+            return ("future", self.opts.get("name"))
+
+    class _Ray:
+        def is_initialized(self):
+            return True
+
+        def remote(self, fn):
+            return _Handle(fn, {})
+
+        def get(self, futs):
+            return [0 for _ in futs]
+
+        def cancel(self, f, force=False):
+            calls["cancel"] += 1
+
+    assert ray_launcher.launch("train.py", [], cfg, ray_module=_Ray()) == 0
+    assert calls["cancel"] == 2 and sum(1 for n, _ in calls["run"] if n.startswith("trainer_")) == 12
