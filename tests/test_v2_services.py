@@ -195,3 +195,60 @@ def test_cli_state_roundtrip(tmp_path, monkeypatch, capsys):
         assert cli.main(["state", "clear"]) == 0 and cli.load_state() == {"services": []}
     finally:
         svc.stop()
+
+
+def test_agent_service_runs_queues_and_ends_sessions():
+    import threading
+    import time
+
+    from areal_b200.v2.agent_service import AgentController
+    from areal_b200.v2.common import call
+
+    gate = threading.Event()
+    seen = []
+
+    def agent(message, session):
+        seen.append((session.session_key, message, len(session.history)))
+        if message == "slow":
+            gate.wait(5)
+        return {"text": f"echo:{message}", "n_history": len(session.history)}
+
+    ctl = AgentController(agent, n_workers=2)
+    try:
+        r = ctl.run("s1", "hello")
+        assert r["status"] == "ok" and r["result"]["text"] == "echo:hello"
+        r2 = ctl.run("s1", "again")
+        assert r2["result"]["n_history"] == 2                       # the session's history reached the agent
+        # while a run is active, messages queue; collect mode folds them into one follow-up turn
+        first = ctl.run("s2", "slow", wait=False)
+        q1 = ctl.run("s2", "a", wait=False)
+        q2 = ctl.run("s2", "b", wait=False)
+        assert q1["status"] == "queued" and q2["queued"] == 2 and q2["active_run_id"] == first["run_id"]
+        gate.set()
+        done = ctl.gateway.wait_run(first["run_id"])
+        follow = ctl.gateway.wait_run(done["followup_run_id"])
+        assert follow["message"] == "a\nb" and follow["result"]["text"] == "echo:a\nb"
+        # followup mode replays them one by one
+        gate.clear()
+        f0 = ctl.run("s3", "slow", wait=False)
+        ctl.run("s3", "x", queue_mode="followup", wait=False)
+        ctl.run("s3", "y", queue_mode="followup", wait=False)
+        gate.set()
+        d0 = ctl.gateway.wait_run(f0["run_id"])
+        d1 = ctl.gateway.wait_run(d0["followup_run_id"])
+        d2 = ctl.gateway.wait_run(d1["followup_run_id"])
+        assert (d1["message"], d2["message"]) == ("x", "y")
+        polled = call(f"http://{ctl.gateway.address}/agent/runs/{d2['run_id']}")
+        assert polled["status"] == "ok" and polled["result"]["text"] == "echo:y"
+        ended = call(f"http://{ctl.gateway.address}/agent/sessions/s1/end", {})
+        assert ended["turns"] == 2
+        try:
+            ctl.run("s1", "late")
+            raise AssertionError("an ended session accepted a run")
+        except Exception as e:
+            assert "409" in repr(e) or "ended" in repr(e)
+        # sessions stick to one worker; two workers share the sessions
+        assert sum(w.turns for w in ctl.workers) == len(seen) and all(w.turns > 0 for w in ctl.workers)
+    finally:
+        gate.set()
+        ctl.close()
