@@ -271,11 +271,23 @@ class B200TrainEngine(TrainEngine):
                 raise NotImplementedError("pipeline parallelism with vision-language models / LoRA")
             loader = (lambda full: hf_io.load_model_hf(full, cfg.path, strict=not cfg.is_critic)) if has_ckpt else None
             self.local_model_config = model_config
-            self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader)
+            vpp = max(int(getattr(self.parallel, "virtual_pipeline_parallel_size", 0) or 0), int(cfg.megatron.virtual_pipeline_parallel_size or 1), 1)
+            sched_name = str(getattr(cfg.archon, "pp_schedule", "1F1B"))
+            if vpp > 1 or sched_name.lower() == "interleaved1f1b":
+                # virtual stages: several model chunks per rank, interleaved 1F1B on the timetable runner
+                from ..parallel.pp import InterleavedStages, ScheduledPipelineRunner
+
+                vpp = max(vpp, 2)
+                self.model = InterleavedStages(model_config, self.pp_rank, self.pp_size, vpp, dtype=dtype, device=self.device, seed=seed,
+                                               init_full=loader)
+                self._pp_runner = ScheduledPipelineRunner(self.model, self._pp_group,
+                                                          "GPipe" if sched_name.lower() == "gpipe" else "Interleaved1F1B")
+            else:
+                self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader)
+                sched = {"1f1b": "1F1B", "gpipe": "GPipe"}.get(sched_name.lower(), "1F1B")
+                self._pp_runner = PipelineRunner(self.model, self._pp_group, schedule=sched)
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
-            sched = {"1f1b": "1F1B", "gpipe": "GPipe"}.get(str(getattr(cfg.archon, "pp_schedule", "1F1B")).lower(), "1F1B")
-            self._pp_runner = PipelineRunner(self.model, self._pp_group, schedule=sched)
         elif tp > 1:
             # every rank materialises the full weights once (same seed / same checkpoint), keeps
             # its slice and drops the rest
@@ -365,7 +377,8 @@ class B200TrainEngine(TrainEngine):
             m = self.model
             if m.is_last and not m.is_first and m.embed_tokens is not None and m.lm_head is None and not model_config.is_critic:
                 lo, hi = self.store.shard_range
-                off, numel = self.store.locate("embed_tokens")
+                tied = [n for n in self.store.names if n.endswith("embed_tokens")][-1]   # the last stage's copy
+                off, numel = self.store.locate(tied)
                 a, b = max(off, lo), min(off + numel, hi)
                 if a < b:
                     self._replicated_ranges.append((a - lo, b - lo))
@@ -509,7 +522,14 @@ class B200TrainEngine(TrainEngine):
     def _prepare_mb_list(self, input_: dict[str, Any]) -> D.MicroBatchList:
         assert "attention_mask" in input_ and "input_ids" in input_, "expected a padded batch"
         input_ = D.amend_position_ids(dict(input_))
-        mbl = D.split_padded_tensor_dict_into_mb_list(input_, self.config.mb_spec, group=self._cpu_group if self.dp_size > 1 else None)
+        spec = self.config.mb_spec
+        if getattr(self, "pp_size", 1) > 1 and getattr(self.model, "n_chunks", 1) > 1 and spec.n_mbs_divisor % self.pp_size:
+            import dataclasses
+            import math as _math
+
+            # interleaved 1F1B walks the micro-batches in groups of the pipeline size
+            spec = dataclasses.replace(spec, n_mbs_divisor=_math.lcm(max(1, spec.n_mbs_divisor), self.pp_size))
+        mbl = D.split_padded_tensor_dict_into_mb_list(input_, spec, group=self._cpu_group if self.dp_size > 1 else None)
         D.pad_mb_list(mbl, pad_to_maximum=self.config.pad_to_maximum, max_tokens=self.config.mb_spec.max_tokens_per_mb,
                       align=self._align())
         return mbl

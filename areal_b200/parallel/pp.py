@@ -279,3 +279,246 @@ class PipelineRunner:
         t = loss.detach().float().reshape(1).to(self.device) if self.m.is_last else torch.zeros(1, device=self.device)
         dist.broadcast(t, src=self.last_rank, group=self.group)
         return t[0]
+
+
+# --------------------------------------------------------------------------- virtual stages
+class InterleavedStages(nn.Module):
+    """``V`` model chunks of one pipeline rank (virtual pipeline): chunk ``v`` on rank ``r`` of
+    ``P`` is global stage ``v * P + r``. Presents the attributes the engine reads from a stage
+    (first / last flags, embedding, heads, native parameter names)."""
+
+    def __init__(self, cfg: ModelConfig, rank: int, n_ranks: int, n_chunks: int, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None,
+                 init_full: Optional[Callable] = None):
+        super().__init__()
+        self.cfg, self.dtype, self.stage, self.n_stages = cfg, dtype, rank, n_ranks
+        self.n_chunks = n_chunks
+        total = n_ranks * n_chunks
+        self.chunks = nn.ModuleList([PipelineStage(cfg, v * n_ranks + rank, total, dtype=dtype, device=device, seed=seed, init_full=init_full)
+                                     for v in range(n_chunks)])
+        self.is_first, self.is_last = rank == 0, rank == n_ranks - 1
+        self.gradient_checkpointing = False
+
+    @property
+    def layers(self):
+        return [l for c in self.chunks for l in c.layers]
+
+    @property
+    def embed_tokens(self):
+        return self.chunks[0].embed_tokens if self.is_first else (self.chunks[-1].embed_tokens if self.is_last else None)
+
+    @property
+    def lm_head(self):
+        return self.chunks[-1].lm_head
+
+    @property
+    def value_head(self):
+        return self.chunks[-1].value_head
+
+    @property
+    def output_weight(self):
+        return self.chunks[-1].output_weight
+
+    def logprobs_entropy(self, hidden, labels, temperature: float = 1.0, chunk: int = 2048):
+        return self.chunks[-1].logprobs_entropy(hidden, labels, temperature, chunk)
+
+    def values(self, hidden):
+        return self.chunks[-1].values(hidden)
+
+    def aux_loss(self):
+        return None   # each chunk's balancing loss joins that chunk's backward inside the runner
+
+    def named_native_parameters(self, skip_tied_copy: bool = True):
+        for c in self.chunks:
+            yield from c.named_native_parameters(skip_tied_copy)
+
+    def native_name(self, local_name: str) -> str:
+        v, rest = local_name[len("chunks."):].split(".", 1)
+        return self.chunks[int(v)].native_name(rest)
+
+
+def interleaved_order(n_ranks: int, n_chunks: int, n_micro: int, rank: int) -> list[tuple[str, int, int]]:
+    """Operation order ``[(F|B, micro-batch, chunk)]`` of one rank under interleaved 1F1B:
+    forwards run in groups of ``P`` micro-batches per chunk, backwards mirror them with the chunks
+    reversed, after a warm-up of ``2 (P - r - 1) + (V - 1) P`` forwards (``V = 1`` gives plain
+    1F1B). ``n_micro`` must be a multiple of ``P`` when ``V > 1``."""
+    P, V, M = n_ranks, n_chunks, n_micro
+    if V > 1 and M % P:
+        raise ValueError(f"interleaved schedule needs the number of micro-batches ({M}) to be a multiple of the pipeline size ({P})")
+    total = M * V
+
+    def fwd(k):
+        return ("F", (k // (P * V)) * P + k % P, (k // P) % V) if V > 1 else ("F", k, 0)
+
+    def bwd(k):
+        return ("B", (k // (P * V)) * P + k % P, V - 1 - (k // P) % V) if V > 1 else ("B", k, 0)
+    warm = min(total, (P - rank - 1) * 2 + (V - 1) * P) if V > 1 else min(total, P - rank - 1)
+    ops, f, b = [], 0, 0
+    for _ in range(warm):
+        ops.append(fwd(f)); f += 1
+    while f < total:
+        ops.append(fwd(f)); f += 1
+        ops.append(bwd(b)); b += 1
+    while b < total:
+        ops.append(bwd(b)); b += 1
+    return ops
+
+
+def build_timetable(n_ranks: int, n_chunks: int, n_micro: int, schedule: str = "Interleaved1F1B", forward_only: bool = False):
+    """Lock-step timetable every rank derives identically: per tick, the operation each rank runs
+    (or None) and the messages ``(src, dst, kind, micro-batch, destination stage)`` delivered at the
+    tick's start. An operation runs once its input has been delivered; a message is delivered the
+    tick after it was produced."""
+    P, V, M = n_ranks, n_chunks, n_micro
+    S = P * V
+    if forward_only or schedule == "GPipe":
+        orders = [[("F", m, v) for v in range(V) for m in range(M)] + ([] if forward_only else [("B", m, v) for v in reversed(range(V)) for m in range(M)])
+                  for _ in range(P)]
+    else:
+        orders = [interleaved_order(P, V, M, r) for r in range(P)]
+    ptr = [0] * P
+    have: set = set()                # (kind, micro-batch, stage) inputs present on their rank
+    done: set = set()
+    ticks = []
+    pending: list = []               # messages produced in the previous tick
+    while any(ptr[r] < len(orders[r]) for r in range(P)):
+        for m in pending:
+            have.add((m[2], m[3], m[4]))
+        delivered, pending = pending, []
+        row = []
+        for r in range(P):
+            op = orders[r][ptr[r]] if ptr[r] < len(orders[r]) else None
+            if op is not None:
+                kind, mb, v = op
+                s = v * P + r
+                ready = (s == 0 or ("act", mb, s) in have) if kind == "F" else \
+                    (("F", mb, s) in done and (s == S - 1 or ("grad", mb, s) in have))
+                if not ready:
+                    op = None
+            row.append(op)
+        if not delivered and all(o is None for o in row):
+            raise RuntimeError(f"pipeline schedule cannot make progress (P={P}, V={V}, M={M})")
+        for r, op in enumerate(row):
+            if op is None:
+                continue
+            kind, mb, v = op
+            s = v * P + r
+            ptr[r] += 1
+            done.add((kind, mb, s))
+            if kind == "F" and s < S - 1:
+                pending.append((r, (r + 1) % P, "act", mb, s + 1))
+            if kind == "B" and s > 0:
+                pending.append((r, (r - 1) % P, "grad", mb, s - 1))
+        ticks.append((row, delivered))
+    if pending:
+        ticks.append(([None] * P, pending))
+    return ticks
+
+
+class ScheduledPipelineRunner:
+    """Runs micro-batches through ``P`` ranks x ``V`` chunks following a timetable
+    (:func:`build_timetable`): every tick starts with ONE batch of sends and receives that both
+    sides derive from the same table, then each rank runs at most one forward or backward. Covers
+    GPipe, 1F1B (``V = 1``) and interleaved 1F1B."""
+
+    def __init__(self, stages, group, schedule: str = "Interleaved1F1B"):
+        self.m = stages
+        self.chunks = list(stages.chunks) if isinstance(stages, InterleavedStages) else [stages]
+        self.group = group
+        self.rank, self.n = dist.get_rank(group), dist.get_world_size(group)
+        self.V = len(self.chunks)
+        self.ranks = dist.get_process_group_ranks(group)
+        self.first_rank, self.last_rank = self.ranks[0], self.ranks[-1]
+        self.schedule = {"1f1b": "Interleaved1F1B", "interleaved1f1b": "Interleaved1F1B", "gpipe": "GPipe"}.get(schedule.lower())
+        if self.schedule is None:
+            raise ValueError(f"unknown pipeline schedule '{schedule}'")
+        p = next(self.chunks[0].parameters())
+        self.device, self.dtype, self.H = p.device, p.dtype, stages.cfg.hidden_size
+
+    def run(self, microbatches: list[dict[str, Any]], loss_fn: Optional[Callable] = None, forward_only: bool = False) -> list:
+        P, V, M = self.n, self.V, len(microbatches)
+        S = P * V
+        table = build_timetable(P, V, M, self.schedule, forward_only)
+        Ts = [mb["input_ids"].shape[0] for mb in microbatches]
+        inbox: dict = {}             # (kind, mb, stage) -> tensor
+        outbox: dict = {}
+        saved: dict = {}             # (mb, chunk) -> (x_in, y, aux)
+        results: list = [None] * M
+        for row, delivered in table:
+            ops, keep = [], []
+            for (src, dst, kind, mb, s) in delivered:
+                if src == self.rank:
+                    t = outbox.pop((kind, mb, s)).contiguous()
+                    keep.append(t)
+                    ops.append(dist.P2POp(dist.isend, t, self.ranks[dst], self.group))
+                if dst == self.rank:
+                    buf = torch.empty(Ts[mb], self.H, device=self.device, dtype=self.dtype)
+                    inbox[(kind, mb, s)] = buf
+                    ops.append(dist.P2POp(dist.irecv, buf, self.ranks[src], self.group))
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+            op = row[self.rank]
+            if op is None:
+                continue
+            kind, mb, v = op
+            s = v * P + self.rank
+            chunk, data = self.chunks[v], microbatches[mb]
+            if kind == "F":
+                with torch.set_grad_enabled(not forward_only):
+                    x = data["input_ids"] if s == 0 else inbox.pop(("act", mb, s))
+                    if s > 0 and not forward_only:
+                        x.requires_grad_(True)
+                    y = chunk(x, data["pb"])
+                    aux = None if forward_only else chunk.aux_loss()
+                    if s == S - 1:
+                        y = loss_fn(y, data)
+                        if forward_only:
+                            results[mb] = y
+                    else:
+                        outbox[("act", mb, s + 1)] = y.detach()
+                if not forward_only:
+                    saved[(mb, v)] = (x if s > 0 else None, y, aux)
+            else:
+                x, y, aux = saved.pop((mb, v))
+                if s == S - 1:
+                    (y if aux is None else y + aux).backward()
+                    results[mb] = y.detach()
+                else:
+                    dy = inbox.pop(("grad", mb, s))
+                    if aux is not None:
+                        torch.autograd.backward([y, aux], [dy, torch.ones_like(aux)])
+                    else:
+                        y.backward(dy)
+                if s > 0:
+                    outbox[("grad", mb, s - 1)] = x.grad
+        self.sync_tied_embedding_grads()
+        return results if self.rank == P - 1 else []
+
+    def sync_tied_embedding_grads(self):
+        cfg = self.m.cfg
+        if self.n * self.V == 1 or not cfg.tie_word_embeddings or cfg.is_critic or self.rank not in (0, self.n - 1):
+            return
+        emb = self.chunks[0].embed_tokens if self.rank == 0 else self.chunks[-1].embed_tokens
+        if self.n == 1:
+            # first and last chunk live on the same rank: the two copies are one gradient
+            a, b = self.chunks[0].embed_tokens, self.chunks[-1].embed_tokens
+            if a is b:
+                return
+        g = getattr(emb, "main_grad", None)
+        if g is not None and emb.grad is not None:
+            g.add_(emb.grad.to(g.dtype))
+            emb.grad = None
+        if g is None:
+            if emb.grad is None:
+                emb.grad = torch.zeros_like(emb)
+            g = emb.grad
+        peer = self.last_rank if self.rank == 0 else self.first_rank
+        other, mine = torch.empty_like(g), g.contiguous().clone()
+        for w in dist.batch_isend_irecv([dist.P2POp(dist.isend, mine, peer, self.group), dist.P2POp(dist.irecv, other, peer, self.group)]):
+            w.wait()
+        g.add_(other)
+
+    def broadcast_loss(self, loss: Optional[torch.Tensor]) -> torch.Tensor:
+        t = loss.detach().float().reshape(1).to(self.device) if self.rank == self.n - 1 else torch.zeros(1, device=self.device)
+        dist.broadcast(t, src=self.last_rank, group=self.group)
+        return t[0]
