@@ -12,6 +12,10 @@ import torch
 from torch.utils.data import Dataset
 
 
+VALID_DATASETS = ["gsm8k", "clevr_count_70k", "geometry3k", "virl39k", "hh-rlhf", "torl_data", "synthetic/arithmetic", "synthetic/random_tokens",
+                  "synthetic/countdown", "synthetic/count_shapes"]
+
+
 class CharTokenizer:
     """Character-level tokenizer over ``0-9 + = space`` plus pad / eos (ids stable)."""
 
@@ -278,8 +282,25 @@ def get_custom_dataset(path: str, type: str = "rl", split: str = "train", tokeni
         out["images"] = images
         return out
 
-    tf = {"rl": rl_transform, "sft": sft_transform, "rw": rw_transform, "dpo": rw_transform, "vl_rl": vl_rl_transform}.get(type)
-    ds = RecordDataset(recs, tf if (tokenizer is not None or type in ("rl", "vl_rl")) else None)
+    def torl_transform(r):
+        # torl_data / verl-style records: ``prompt`` is a message list, the answer sits in ``reward_model.ground_truth``
+        msgs = r.get("prompt") if isinstance(r.get("prompt"), list) else [{"role": "user", "content": str(r.get("prompt") or r.get("question") or "")}]
+        rm = r.get("reward_model") or {}
+        out = {k: v for k, v in r.items() if k not in ("prompt",)}
+        out["messages"] = list(msgs)
+        out["answer"] = rm.get("ground_truth", r.get("answer"))
+        if tokenizer is not None:
+            out["input_ids"] = list(tokenizer.apply_chat_template(out["messages"], tokenize=True, add_generation_prompt=True))
+        return out
+
+    # named sets of the reference keep their conventions: picture sets carry images, torl carries verl-style records
+    if type == "rl" and any(n in path for n in ("clevr_count_70k", "geometry3k", "virl39k")):
+        type = "vl_rl"
+    elif type == "rl" and "torl" in path:
+        type = "torl"
+    tf = {"rl": rl_transform, "sft": sft_transform, "rw": rw_transform, "dpo": rw_transform, "vl_rl": vl_rl_transform,
+          "torl": torl_transform}.get(type)
+    ds = RecordDataset(recs, tf if (tokenizer is not None or type in ("rl", "vl_rl", "torl")) else None)
     if max_length and type == "rl" and tokenizer is not None:
         keep = [i for i in range(len(ds)) if len(ds[i]["input_ids"]) <= max_length]
         ds = RecordDataset([recs[i] for i in keep], tf)
