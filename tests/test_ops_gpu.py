@@ -451,3 +451,31 @@ def test_fp8_linear_gradients_close_to_bf16():
     dwr = dy.float().t() @ x.detach().float()
     assert ((x.grad.float() - dxr).norm() / dxr.norm()).item() < 0.06
     assert ((w.grad.float() - dwr).norm() / dwr.norm()).item() < 1e-2
+
+
+def test_bounded_peer_wait_reports_instead_of_hanging():
+    """A flag that nothing sets: the device-side barrier gives up after its (short) limit, records
+    the failed wait in the error word and returns; the context stays usable. When the peer's flag
+    is there, the same barrier passes."""
+    import time
+
+    from areal_b200.parallel.symm import CHANNELS, MAX_PEERS, ptr_array
+
+    L = oplib.get_lib()
+    mine = torch.zeros(CHANNELS * MAX_PEERS, dtype=torch.int32, device="cuda")
+    absent_peer = torch.zeros(CHANNELS * MAX_PEERS, dtype=torch.int32, device="cuda")    # plays rank 1's pad; nobody runs rank 1
+    pads = ptr_array([mine.data_ptr(), absent_peer.data_ptr()])
+    assert oplib.kernel_error() == 0
+    t0 = time.perf_counter()
+    rc = L.ab2_signal_barrier(pads, 0, 2, 0, 1, 50, oplib.stream_ptr())                  # 50 ms limit
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert oplib.kernel_error() != 0                                                     # the wait that gave up was recorded
+    assert oplib.kernel_error() == 0                                                     # ... and reading cleared it
+    assert int(absent_peer[0]) == 1                                                      # this rank's own arrival was published
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0                       # the context still works
+    mine[1] = 2                                                                           # "rank 1" arrived for epoch 2
+    rc = L.ab2_signal_barrier(pads, 0, 2, 0, 2, 50, oplib.stream_ptr())
+    torch.cuda.synchronize()
+    assert rc == 0 and oplib.kernel_error() == 0 and int(absent_peer[0]) == 2
