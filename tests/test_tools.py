@@ -72,3 +72,54 @@ def test_local_launcher_restarts_failed_job(tmp_path):
     except JobFailed as e:
         assert e.code == 5 and e.name == "bad"
     la.stop_all()
+
+
+KILLED_RANK_SCRIPT = r'''
+import faulthandler, json, os, signal, sys
+faulthandler.dump_traceback_later(240, exit=True)
+sys.path.insert(0, %(root)r)
+os.environ["AREAL_FORCE_CPU"] = "1"
+import torch.distributed as dist
+from tests.test_e2e_cpu import _cfg, digit_reward
+from areal_b200.dataset import ArithmeticDataset
+from areal_b200.models.config import preset
+from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
+from areal_b200.trainer.rl_trainer import PPOTrainer
+dist.init_process_group("gloo")
+rank = dist.get_rank()
+first_run = os.environ["AREAL_RECOVER_RUN"] == "0"
+cfg = _cfg(%(tmp)r, steps=6, recover="auto")
+cfg.actor.backend = "d2"
+mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+with PPOTrainer(cfg, ArithmeticDataset(size=128), tokenizer=None, model_config=mc) as tr:
+    wf = RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True)
+    start = tr.start_step
+    if first_run:
+        hist = tr.train(workflow=wf, max_steps=3)
+        dist.barrier()
+        if rank == 1:
+            os.kill(os.getpid(), signal.SIGKILL)          # dies between steps, nothing of it in flight
+        hist += tr.train(workflow=wf)                      # the survivor walks into a collective with a dead peer
+    else:
+        hist = tr.train(workflow=wf)
+    json.dump({"start": start, "steps": len(hist), "version": tr.actor.get_version()}, open(os.path.join(%(tmp)r, f"result_{rank}.json"), "w"))
+dist.barrier()
+'''
+
+
+def test_killed_rank_restarts_job_which_resumes_from_recover_checkpoint(tmp_path):
+    """SIGKILL of one gloo trainer rank between steps: torchrun ends the job, the launcher starts it
+    again as a recover run, and training continues from the last recover checkpoint (step 3 of 6)."""
+    import json
+
+    from areal_b200.api.cli_args import BaseExperimentConfig, ClusterSpecConfig, RecoverConfig
+    from areal_b200.infra.launcher.local import launch
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "train.py"
+    script.write_text(KILLED_RANK_SCRIPT % dict(root=root, tmp=str(tmp_path)))
+    cfg = BaseExperimentConfig(experiment_name="e2e", trial_name="t0", cluster=ClusterSpecConfig(fileroot=str(tmp_path)),
+                               allocation_mode="d2", recover=RecoverConfig(mode="auto", retries=1))
+    assert launch(str(script), [], cfg, n_gpus=0) == 0
+    res = [json.load(open(tmp_path / f"result_{r}.json")) for r in range(2)]
+    assert all(r["start"] == 3 and r["steps"] == 3 and r["version"] == 6 for r in res), res

@@ -252,3 +252,75 @@ def test_agent_service_runs_queues_and_ends_sessions():
     finally:
         gate.set()
         ctl.close()
+
+
+def test_control_plane_fault_injection_5xx_drop_and_delay():
+    """HTTP faults on the control plane: 5xx answers and refused connections are retried with
+    back-off, 4xx answers are final, a slow answer beyond the caller's time-out counts as a fault."""
+    import asyncio
+    import time
+
+    import aiohttp
+
+    from areal_b200.engine.remote_engine import arequest_with_retry
+    from areal_b200.utils.network import find_free_ports
+    from areal_b200.v2.common import HTTPError, JsonService, call
+
+    hits = {"flaky": 0, "bad": 0, "slow": 0}
+    svc = JsonService("faulty")
+
+    @svc.route("POST", "/flaky")
+    def flaky(body, ctx):
+        hits["flaky"] += 1
+        if hits["flaky"] % 3:                       # two 5xx answers, then success
+            raise RuntimeError("injected failure")
+        return {"ok": True, "attempts": hits["flaky"]}
+
+    @svc.route("POST", "/bad")
+    def bad(body, ctx):
+        hits["bad"] += 1
+        raise HTTPError(422, "malformed")
+
+    @svc.route("POST", "/slow")
+    def slow(body, ctx):
+        hits["slow"] += 1
+        if hits["slow"] == 1:
+            time.sleep(1.0)                         # first answer comes too late for the caller
+        return {"ok": True}
+
+    svc.start()
+    try:
+        assert call(f"{svc.url}/flaky", {}, retries=3)["attempts"] == 3
+        try:
+            call(f"{svc.url}/flaky", {}, retries=2)                        # 5xx twice: gives up
+            raise AssertionError("expected a failure")
+        except HTTPError as e:
+            assert e.status == 500
+        try:
+            call(f"{svc.url}/bad", {}, retries=5)
+            raise AssertionError("expected a failure")
+        except HTTPError as e:
+            assert e.status == 422 and hits["bad"] == 1                     # client errors are not retried
+        dead = f"http://127.0.0.1:{find_free_ports(1)[0]}/x"
+        t0 = time.time()
+        try:
+            call(dead, {}, retries=2, timeout=1.0)
+            raise AssertionError("expected a failure")
+        except HTTPError as e:
+            assert e.status == 503 and time.time() - t0 < 5
+
+        async def go():
+            async with aiohttp.ClientSession() as s:
+                hits["flaky"] = 0
+                r = await arequest_with_retry(s, svc.address, "/flaky", {}, max_retries=3, retry_delay=0.01)
+                assert r["attempts"] == 3
+                r = await arequest_with_retry(s, svc.address, "/slow", {}, max_retries=2, timeout=0.3, retry_delay=0.01)
+                assert r["ok"] and hits["slow"] == 2                          # timed out once, then served
+                try:
+                    await arequest_with_retry(s, dead[7:].split("/")[0], "/x", {}, max_retries=2, retry_delay=0.01)
+                    raise AssertionError("expected a failure")
+                except RuntimeError as e:
+                    assert "failed after 2 attempts" in str(e)
+        asyncio.run(go())
+    finally:
+        svc.stop()
