@@ -36,6 +36,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl() may become resident while the
+// previous kernel of the stream is still running (its launch latency and prologue overlap that
+// kernel's tail). pdl_wait() blocks until every prerequisite grid has completed and its memory is
+// visible; it must precede the first global access other than reads of data no kernel writes
+// (weights). Without a programmatic dependency both calls return at once.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(
@@ -298,4 +306,28 @@ int encode_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t 
                    uint32_t b1, uint32_t b2, bool swizzle128, int dtype_code);
 // Device pointer of the current device's kernel error word (allocated on first use).
 int* error_flag();
+// True when AB2_PDL=1: kernels of the decode path are chained with programmatic dependent launch.
+bool pdl_enabled();
+}  // namespace ab2host
+
+namespace ab2 {
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (ab2host::pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+}  // namespace ab2
+
+namespace ab2host {
 }  // namespace ab2host

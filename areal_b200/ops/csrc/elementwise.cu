@@ -33,6 +33,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                    __nv_bfloat16* __restrict__ resid_out, float* __restrict__ rstd_out,
                                    int rows, int H, float eps) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
   const int nvec = H >> 3;
   // TPR == 32: every warp of the CTA owns its own row (blockDim.x / 32 rows per CTA step)
   const int rows_per_cta = (TPR == 32) ? (blockDim.x >> 5) : 1;
@@ -210,6 +212,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
 // gu: [T, 2I] (gate | up); out[T, I] = silu(gate) * up
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                   long long T, int I) {
+  pdl_wait();
+  pdl_trigger();
   const int vec_per_row = I >> 3;
   const long long total = T * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -260,6 +264,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
 // ------------------------------------------------------------------ embedding
 __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ W, const int* __restrict__ ids,
                                  __nv_bfloat16* __restrict__ out, int T, int H, int V) {
+  pdl_wait();
+  pdl_trigger();
   const int vec = H >> 3;
   const long long total = (long long)T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -368,10 +374,10 @@ int ab2_rmsnorm_fwd(const void* x, const void* resid, const void* w, void* y, vo
   if (rows <= 0) return 0;
   auto X = (const __nv_bfloat16*)x; auto R = (const __nv_bfloat16*)resid; auto W = (const __nv_bfloat16*)w;
   auto Y = (__nv_bfloat16*)y; auto RO = (__nv_bfloat16*)resid_out;
-  if (H <= 256) rmsnorm_fwd_kernel<32, 1><<<(rows + 7) / 8 < 148 * 16 ? (rows + 7) / 8 : 148 * 16, 256, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
-  else if (H <= 2048) rmsnorm_fwd_kernel<128, 2><<<grid, 128, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
-  else if (H <= 4096) rmsnorm_fwd_kernel<128, 4><<<grid, 128, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
-  else rmsnorm_fwd_kernel<256, 4><<<grid, 256, 0, s>>>(X, R, W, Y, RO, rstd, rows, H, eps);
+  if (H <= 256) launch_pdl(rmsnorm_fwd_kernel<32, 1>, dim3((rows + 7) / 8 < 148 * 16 ? (rows + 7) / 8 : 148 * 16), dim3(256), 0, s, X, R, W, Y, RO, rstd, rows, H, eps);
+  else if (H <= 2048) launch_pdl(rmsnorm_fwd_kernel<128, 2>, dim3(grid), dim3(128), 0, s, X, R, W, Y, RO, rstd, rows, H, eps);
+  else if (H <= 4096) launch_pdl(rmsnorm_fwd_kernel<128, 4>, dim3(grid), dim3(128), 0, s, X, R, W, Y, RO, rstd, rows, H, eps);
+  else launch_pdl(rmsnorm_fwd_kernel<256, 4>, dim3(grid), dim3(256), 0, s, X, R, W, Y, RO, rstd, rows, H, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
@@ -405,8 +411,8 @@ int ab2_rope(void* x, const int* pos, const float* cosb, const float* sinb, int 
 int ab2_swiglu_fwd(const void* gu, void* out, long long T, int I, void* stream) {
   if (I % 8) return 10;
   if (T <= 0) return 0;
-  swiglu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
+  launch_pdl(swiglu_fwd_kernel, dim3(grid_for(T * (I / 8), 256)), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)gu,
+             (__nv_bfloat16*)out, T, I);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 int ab2_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int I, void* stream) {
@@ -420,8 +426,8 @@ int ab2_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int
 int ab2_embed_fwd(const void* W, const int* ids, void* out, int T, int H, int V, void* stream) {
   if (H % 8) return 10;
   if (T <= 0) return 0;
-  embed_fwd_kernel<<<grid_for((long long)T * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)W, ids, (__nv_bfloat16*)out, T, H, V);
+  launch_pdl(embed_fwd_kernel, dim3(grid_for((long long)T * (H / 8), 256)), dim3(256), 0, (cudaStream_t)stream,
+             (const __nv_bfloat16*)W, ids, (__nv_bfloat16*)out, T, H, V);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 int ab2_embed_bwd(const void* dy, const int* ids, float* dW, int T, int H, int V, void* stream) {

@@ -102,6 +102,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  // barriers, tensor memory and descriptors are set up: from here on the kernel touches what the
+  // previous kernel of the stream may still be producing
+  pdl_wait();
+  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer
@@ -315,8 +319,8 @@ static int launch_gemm(int epi, const void* A, const void* B, void* C, const voi
   const int grid = tiles < num_sms ? tiles : num_sms;
   int* err = ab2host::error_flag();
   if (!err) return 301;
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, reinterpret_cast<const __nv_bfloat16*>(R),
-                                               M, N, K, ldc, epi, err);
+  launch_pdl(kern, dim3(grid), dim3(192), (size_t)Cfg::SMEM_BYTES, stream, tmA, tmB, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K,
+             ldc, epi, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 302;
 }
 

@@ -19,6 +19,8 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv
                                  __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
                                  const int* __restrict__ slots, int n, int row_elems, long long k_stride,
                                  long long v_stride) {
+  pdl_wait();
+  pdl_trigger();
   const int vec = row_elems >> 3;
   const long long total = (long long)n * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -309,6 +311,8 @@ paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   using Cfg = DecodeMmaCfg<D>;
   constexpr int STRIDE = Cfg::STRIDE;
   constexpr int KS = D / 16;                 // k-steps of S = Q K^T; also 16-dim column pairs of O
+  pdl_wait();
+  pdl_trigger();
   constexpr int PIECES = DEC_CHUNK * D * 2 / 16;
   extern __shared__ __align__(128) unsigned char dsm[];
   const int b = blockIdx.x, h = blockIdx.y, spl = blockIdx.z;
@@ -485,9 +489,9 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 2;
     attr_set = true;
   }
-  kern<<<grid, 128, Cfg::SMEM_BYTES, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens, part_o,
-                                          part_ml, Hq, Hkv, Hq / Hkv, page_size, max_pages, splits, scale, q_stride);
-  decode_combine_kernel<D><<<B * Hq, D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
+  launch_pdl(kern, grid, dim3(128), (size_t)Cfg::SMEM_BYTES, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens,
+             part_o, part_ml, Hq, Hkv, Hq / Hkv, page_size, max_pages, splits, scale, q_stride);
+  launch_pdl(decode_combine_kernel<D>, dim3(B * Hq), dim3(D), 0, s, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
@@ -500,6 +504,8 @@ constexpr int decode_smem_bytes() {
 template <int D>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       __nv_bfloat16* __restrict__ out, int num_splits) {
+  pdl_wait();
+  pdl_trigger();
   const size_t row = blockIdx.x;  // b * Hq + hq
   const int d = threadIdx.x;
   float M = -INFINITY;
@@ -551,6 +557,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, in
                               const unsigned int* __restrict__ seeds, unsigned int step,
                               int* __restrict__ out_tok, float* __restrict__ out_logp) {
   __shared__ SampleState red[32];
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const float it = inv_temp[row];
   const bool gr = greedy[row] != 0;
@@ -634,7 +642,7 @@ int ab2_kv_append(const void* k, const void* v, void* kc, void* vc, const int* s
   long long work = (long long)n * (row / 8);
   int grid = (int)((work + 255) / 256);
   if (grid > 148 * 8) grid = 148 * 8;
-  kv_append_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+  launch_pdl(kv_append_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
                                                            (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slots, n, row,
                                                            k_stride, v_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
@@ -676,7 +684,7 @@ int ab2_paged_decode(const void* q, const void* kc, const void* vc, const int* p
 int ab2_sample(const float* logits, long long ld, int B, int V, const float* inv_temp, const int* greedy,
                const unsigned int* seeds, unsigned int step, int* out_tok, float* out_logp, void* stream) {
   if (B <= 0) return 0;
-  sample_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(logits, ld, V, inv_temp, greedy, seeds, step, out_tok, out_logp);
+  launch_pdl(sample_kernel, dim3(B), dim3(1024), 0, (cudaStream_t)stream, logits, ld, V, inv_temp, greedy, seeds, step, out_tok, out_logp);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 }

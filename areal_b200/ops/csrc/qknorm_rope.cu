@@ -65,6 +65,8 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        long long qkv_stride, float eps, int hsplit) {
   constexpr int D = 32 * VEC;
   constexpr int HALF = D / 2;
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int heads = nq + nkv;
   const int warp0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -261,13 +263,11 @@ int ab2_qknorm_rope_fwd(const void* qkv, const void* wq, const void* wk, const i
   const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
   auto s = (cudaStream_t)stream;
   if (D == 128)
-    ab2::qknorm_rope_fwd_kernel<4><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
-                                                        (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk,
-                                                        rstd, T, nq, nkv, qkv_stride, eps, hsplit);
+    ab2::launch_pdl(ab2::qknorm_rope_fwd_kernel<4>, dim3(grid), dim3(256), 0, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
+                    (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk, rstd, T, nq, nkv, qkv_stride, eps, hsplit);
   else
-    ab2::qknorm_rope_fwd_kernel<2><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
-                                                        (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk,
-                                                        rstd, T, nq, nkv, qkv_stride, eps, hsplit);
+    ab2::launch_pdl(ab2::qknorm_rope_fwd_kernel<2>, dim3(grid), dim3(256), 0, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq,
+                    (const __nv_bfloat16*)wk, pos, cosb, sinb, (__nv_bfloat16*)qk, rstd, T, nq, nkv, qkv_stride, eps, hsplit);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

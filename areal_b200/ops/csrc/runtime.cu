@@ -1,6 +1,7 @@
 // Host-side runtime shared by all kernels of the library: per-device error word,
 // TMA tensor-map encoding through the driver entry point (no link-time libcuda
 // dependency), and a few exported C helpers.
+#include <cstdlib>
 #include <cudaTypedefs.h>
 #include <stdio.h>
 
@@ -92,6 +93,11 @@ int* error_flag() {
     g_err[dev] = p;
   }
   return g_err[dev];
+}
+
+bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("AB2_PDL"); return e && e[0] == '1'; }();
+  return on;
 }
 
 }  // namespace ab2host
