@@ -71,9 +71,10 @@ def test_unknown_key_and_type_errors(tmp_path):
 
 
 def test_reference_yaml_loads():
-    ref = "/root/reference/examples/math/gsm8k_grpo.yaml"
-    if not os.path.exists(ref):
-        pytest.skip("reference tree not mounted")
+    root = os.environ.get("AREAL_REFERENCE_ROOT", "")
+    ref = os.path.join(root, "examples", "math", "gsm8k_grpo.yaml")
+    if not root or not os.path.exists(ref):
+        pytest.skip("set AREAL_REFERENCE_ROOT to a checkout of the reference to check its stock YAML")
     raw, _ = C.parse_cli_args(["--config", ref])
     cfg = C.to_structured_cfg(raw, C.GRPOConfig)
     assert cfg.actor.use_decoupled_loss and cfg.actor.rejection_sampling.upper == 5.0
