@@ -94,6 +94,19 @@ def bench_gemm(a):
     return res
 
 
+def bench_gemm_decode(a):
+    """Decode-shaped ``x @ W^T``: split-K kernel pair against the general kernel (``--compare``)."""
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.05).bfloat16()
+    bn, splits = OF.decode_gemm_plan(a.m, a.n, a.k)
+    ms = timeit(lambda: OF.gemm_decode(x, w), a.iters, a.warmup)
+    res = report("gemm_decode_splitk", ms, 2.0 * a.m * a.n * a.k, 2.0 * (a.n * a.k + a.m * a.k + a.m * a.n), m=a.m, n=a.n, k=a.k, bn=bn, splits=splits)
+    if a.compare:
+        ms_g = timeit(lambda: OF.gemm(x, w), a.iters, a.warmup)
+        report("gemm_bf16_tcgen05 (same shape)", ms_g, 2.0 * a.m * a.n * a.k, 2.0 * (a.n * a.k + a.m * a.k + a.m * a.n), m=a.m, n=a.n, k=a.k)
+    return res
+
+
 def bench_gemm_fp8(a):
     """e4m3 GEMM (``--split 1``: block-wise scales, 0: row-wise), operands quantised once outside the timed region."""
     block = bool(a.split)
@@ -279,7 +292,7 @@ def bench_engine_decode(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
+    ap.add_argument("kernel", choices=["gemm", "gemm_decode", "gemm_fp8", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
                                            "engine_decode"])
     ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--new", type=int, default=128)
@@ -297,7 +310,7 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.kernel == "logprob" and a.rows > 4096:
         a.rows = 2048
-    return {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
+    return {"gemm": bench_gemm, "gemm_decode": bench_gemm_decode, "gemm_fp8": bench_gemm_fp8, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
             "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
             "engine_decode": bench_engine_decode}[a.kernel](a)
 

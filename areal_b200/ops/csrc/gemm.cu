@@ -56,11 +56,15 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
   nb = in_g / gsize;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// SPLITK: the K range is cut into `splits` pieces of `kb_per` k-blocks; a tile index also selects
+// the piece, and piece ks stores its fp32 partial product at Cptr + ks * M * ldc (the caller sums
+// the pieces). Used for decode-shaped products whose output alone has too few tiles to keep the
+// machine's load pipes busy.
+template <int BN, bool A_MN, bool B_MN, bool SPLITK = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  void* __restrict__ Cptr, const __nv_bfloat16* __restrict__ Rptr, int M, int N,
-                 int K, int ldc, const int EPI, int* err) {
+                 int K, int ldc, const int EPI, int* err, int splits, int kb_per) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -77,8 +81,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int m_blocks = (M + BM - 1) / BM;
   const int n_blocks = (N + BN - 1) / BN;
-  const int num_tiles = m_blocks * n_blocks;
-  const int num_kb = (K + BK - 1) / BK;
+  const int mn_tiles = m_blocks * n_blocks;
+  const int num_tiles = SPLITK ? mn_tiles * splits : mn_tiles;
+  const int num_kb_all = (K + BK - 1) / BK;
+  // k-block range of a tile: everything, or piece ks of the split
+  auto kb_begin = [&](int tile) { return SPLITK ? (tile / mn_tiles) * kb_per : 0; };
+  auto kb_end = [&](int tile) { return SPLITK ? min(num_kb_all, (tile / mn_tiles + 1) * kb_per) : num_kb_all; };
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
@@ -116,9 +124,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int issued = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mb, nb;
-        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        tile_coords(SPLITK ? tile % mn_tiles : tile, m_blocks, n_blocks, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin(tile); kb < kb_end(tile); ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, err, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
@@ -164,7 +172,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u, err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = kb_begin(tile);
+        for (int kb = kb0; kb < kb_end(tile); ++kb) {
           if (!mbar_wait(full_bar(stage), phase, err, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
@@ -177,7 +186,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // MN-major: +16 K-rows of 128 B.
             const uint64_t ad = adesc + (A_MN ? (uint64_t)(k * (UMMA_K * 128 >> 4)) : (uint64_t)(k * 2));
             const uint64_t bd = bdesc + (B_MN ? (uint64_t)(k * (UMMA_K * 128 >> 4)) : (uint64_t)(k * 2));
-            umma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -193,10 +202,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       int mb, nb;
-      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      tile_coords(SPLITK ? tile % mn_tiles : tile, m_blocks, n_blocks, mb, nb);
       const int m0 = mb * BM, n0 = nb * BN;
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
+      void* Cptr_t = SPLITK ? static_cast<void*>(reinterpret_cast<float*>(Cptr) + (size_t)(tile / mn_tiles) * M * ldc) : Cptr;
       if (!mbar_wait(tfull_bar(buf), use & 1u, err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + row_in_tile;
@@ -210,7 +220,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (row < M && col < N) {
           const bool full = (col + 32 <= N);
           if (EPI == EPI_BF16 || EPI == EPI_BF16_RESID) {
-            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cptr) + (size_t)row * ldc + col;
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cptr_t) + (size_t)row * ldc + col;
             if (full) {
               uint32_t p[16];
               if (EPI == EPI_BF16_RESID) {
@@ -246,7 +256,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           } else {
-            float* C = reinterpret_cast<float*>(Cptr) + (size_t)row * ldc + col;
+            float* C = reinterpret_cast<float*>(Cptr_t) + (size_t)row * ldc + col;
             if (full) {
               float4* C4 = reinterpret_cast<float4*>(C);
 #pragma unroll
@@ -320,8 +330,70 @@ static int launch_gemm(int epi, const void* A, const void* B, void* C, const voi
   int* err = ab2host::error_flag();
   if (!err) return 301;
   launch_pdl(kern, dim3(grid), dim3(192), (size_t)Cfg::SMEM_BYTES, stream, tmA, tmB, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K,
-             ldc, epi, err);
+             ldc, epi, err, 1, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : 302;
+}
+
+// Sum of the split-K pieces: out[i] = bf16(sum_s ws[s * MN + i] (+ resid[i])). MN is a multiple of 4.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out,
+                                     const __nv_bfloat16* __restrict__ resid, int splits, long long MN) {
+  pdl_wait();
+  pdl_trigger();
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < MN; i += (long long)gridDim.x * blockDim.x * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(ws + i);
+    for (int sp = 1; sp < splits; ++sp) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + (size_t)sp * MN + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (resid != nullptr) {
+      const uint2 r = *reinterpret_cast<const uint2*>(resid + i);
+      const float2 a = unpack_bf16(r.x), b = unpack_bf16(r.y);
+      acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+    }
+    *reinterpret_cast<uint2*>(out + i) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+  }
+}
+
+// Y[M, N] (bf16) = A[M, K] B[N, K]^T (+ R) with the K range split over `splits` CTAs per output tile:
+// pieces go to ws ([splits, M, N] fp32) with plain stores, a second kernel sums them.
+template <int BN>
+static int launch_splitk(const void* A, const void* B, void* Y, const void* R, float* ws, int M, int N, int K, int lda, int ldb,
+                         int splits, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc = ab2host::encode_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true, 0);
+  if (rc) return 100 + rc;
+  rc = ab2host::encode_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, true, 0);
+  if (rc) return 200 + rc;
+  auto kern = gemm_bf16_kernel<BN, false, false, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 300;
+    attr_set = true;
+  }
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int num_kb = (K + BK - 1) / BK;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;             // every piece owns at least one k-block
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  int* err = ab2host::error_flag();
+  if (!err) return 301;
+  if (launch_pdl(kern, dim3(grid), dim3(192), (size_t)Cfg::SMEM_BYTES, stream, tmA, tmB, (void*)ws, (const __nv_bfloat16*)nullptr, M, N, K, N,
+                 (int)EPI_F32, err, splits, kb_per) != cudaSuccess)
+    return 302;
+  const long long MN = (long long)M * N;
+  long long want = (MN / 4 + 255) / 256;
+  const int rgrid = (int)(want < 148 * 8 ? want : 148 * 8);
+  if (launch_pdl(splitk_reduce_kernel, dim3(rgrid), dim3(256), 0, stream, (const float*)ws, (__nv_bfloat16*)Y, (const __nv_bfloat16*)R, splits,
+                 MN) != cudaSuccess)
+    return 303;
+  return 0;
 }
 
 template <int BN>
@@ -367,6 +439,25 @@ int ab2_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, i
     case 128: return dispatch_major<128>(a_mn, b_mn, epi, A, B, C, R, M, N, K, lda, ldb, ldc, s);
     case 64: return dispatch_major<64>(a_mn, b_mn, epi, A, B, C, R, M, N, K, lda, ldb, ldc, s);
     case 32: return dispatch_major<32>(a_mn, b_mn, epi, A, B, C, R, M, N, K, lda, ldb, ldc, s);
+  }
+  return 12;
+}
+
+// Decode-shaped product: Y[M, N] (bf16, dense rows) = A[M, K] B[N, K]^T (+ R, Y's layout), K split over
+// `splits` CTAs per 128 x bn output tile. ws: fp32 workspace of at least splits * M * N elements (no
+// initialisation needed). N must be a multiple of 4; lda / ldb multiples of 8.
+int ab2_gemm_splitk(const void* A, const void* B, void* Y, const void* R, void* ws, int M, int N, int K, int lda, int ldb, int splits,
+                    int bn, void* stream) {
+  using namespace ab2;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (N & 3) || splits < 1 || !ws) return 10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(Y)) & 15) return 11;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  float* w = reinterpret_cast<float*>(ws);
+  switch (bn) {
+    case 256: return launch_splitk<256>(A, B, Y, R, w, M, N, K, lda, ldb, splits, s);
+    case 128: return launch_splitk<128>(A, B, Y, R, w, M, N, K, lda, ldb, splits, s);
+    case 64: return launch_splitk<64>(A, B, Y, R, w, M, N, K, lda, ldb, splits, s);
   }
   return 12;
 }

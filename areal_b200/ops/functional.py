@@ -13,6 +13,7 @@ Public entry points dispatch on ``tensor.is_cuda`` only: CPU -> reference, CUDA 
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -177,6 +178,55 @@ def _skinny_workspace(device, n_out: int):
     return ent
 
 
+_SPLITK_WS: dict = {}
+DECODE_SPLITK = os.environ.get("AB2_DECODE_SPLITK", "0") == "1"     # route decode-sized linear() calls through gemm_decode
+DECODE_GEMM_MAX_ROWS = 128
+
+
+def decode_gemm_plan(M: int, N: int, K: int, n_sms: int = 148) -> tuple[int, int]:
+    """(tile width, K splits) for a decode-shaped product: the widest tile whose count, times the
+    split, comes closest to one CTA per SM without exceeding it; at least 8 k-blocks per piece."""
+    best = (128, 1, 0.0)
+    for bn in (256, 128):
+        if N % bn and N > bn:
+            continue
+        tiles = -(-N // bn) * -(-M // 128)
+        max_split = max(1, (K // 64) // 8)
+        split = max(1, min(max_split, n_sms // tiles if tiles <= n_sms else 1))
+        fill = min(1.0, tiles * split / n_sms)
+        # wider tiles re-read the activations less often: prefer them at equal fill
+        score = fill + (0.05 if bn == 256 else 0.0)
+        if score > best[2]:
+            best = (bn, split, score)
+    return best[0], best[1]
+
+
+def gemm_decode(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w^T (+ resid)`` for a handful of rows (decode): output tiles alone cannot fill the
+    machine, so K is split over CTAs as well (fp32 pieces in a static workspace, one reduce
+    kernel). Falls back to :func:`gemm` when no split is worth it."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not x.is_cuda:
+        y = x.float() @ w.float().t()
+        return (y + resid.float() if resid is not None else y).to(x.dtype)
+    bn, splits = decode_gemm_plan(M, N, K)
+    if splits <= 1 or N % 4 or x.stride(1) != 1 or w.stride(1) != 1:
+        return gemm(x, w, epi=EPI_BF16_RESID, resid=resid) if resid is not None else gemm(x, w)
+    need = splits * M * N
+    key = (x.device.index, torch.cuda.current_stream(x.device).cuda_stream)
+    ws = _SPLITK_WS.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _SPLITK_WS[key] = torch.empty(max(need, 4 * DECODE_GEMM_MAX_ROWS * 32768), dtype=torch.float32, device=x.device)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if resid is not None:
+        assert resid.shape == y.shape and resid.is_contiguous() and resid.dtype == torch.bfloat16
+    rc = _L().ab2_gemm_splitk(x.data_ptr(), w.data_ptr(), y.data_ptr(), _lib.ptr(resid), ws.data_ptr(), M, N, K, x.stride(0), w.stride(0),
+                              splits, bn, _s())
+    _lib.check(rc, "ab2_gemm_splitk")
+    return y
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
                 split_k: int = 0) -> torch.Tensor:
     """``x @ w^T (+ resid)`` for at most 256 rows of ``x``: the decode-shaped product, bound
@@ -251,6 +301,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = Non
     # model, but inside the decode CUDA graph the whole step came out slower (13.2 ms vs 10.1 ms
     # per step at 64 sequences), so decode keeps the general kernel; callers can use
     # gemm_skinny() explicitly.
+    if DECODE_SPLITK and x.dim() == 2 and x.shape[0] <= DECODE_GEMM_MAX_ROWS and not torch.is_grad_enabled() and x.dtype == torch.bfloat16:
+        return gemm_decode(x, w, resid)      # decode: split K as well, the output alone has too few tiles
     return _Linear.apply(x, w, resid, grad_buf)
 
 

@@ -29,6 +29,7 @@ _SIGS = {
     "ab2_qknorm_rope_fwd": ([c_void_p] * 8 + [c_int] * 4 + [c_ll, c_float, c_void_p], c_int),
     "ab2_qknorm_rope_bwd": ([c_void_p] * 11 + [c_int] * 4 + [c_ll, c_ll, c_void_p], c_int),
     "ab2_gemm_grouped": ([c_void_p] * 4 + [c_int] * 9 + [c_void_p], c_int),
+    "ab2_gemm_splitk": ([c_void_p] * 5 + [c_int] * 7 + [c_void_p], c_int),
     "ab2_gemm_fp8": ([c_void_p] * 5 + [c_int] * 8 + [c_void_p], c_int),
     "ab2_quant_fp8": ([c_void_p] * 3 + [c_int, c_int, c_ll, c_ll, c_int, c_int, c_void_p], c_int),
     "ab2_gemm_skinny": ([c_void_p] * 6 + [c_int] * 8 + [c_void_p], c_int),
@@ -104,7 +105,7 @@ def get_lib():
 
 
 # Number of kernels each exported launcher enqueues (used for launch accounting).
-_KERNELS_PER_CALL = {"ab2_paged_decode": 2, "ab2_paged_decode_strided": 2, "ab2_paged_decode_noalloc": 2, "ab2_kernel_error": 0, "ab2_runtime_init": 0, "ab2_num_sms": 0}
+_KERNELS_PER_CALL = {"ab2_gemm_splitk": 2, "ab2_paged_decode": 2, "ab2_paged_decode_strided": 2, "ab2_paged_decode_noalloc": 2, "ab2_kernel_error": 0, "ab2_runtime_init": 0, "ab2_num_sms": 0}
 LAUNCHES = {"count": 0}
 
 

@@ -479,3 +479,20 @@ def test_bounded_peer_wait_reports_instead_of_hanging():
     rc = L.ab2_signal_barrier(pads, 0, 2, 0, 2, 50, oplib.stream_ptr())
     torch.cuda.synchronize()
     assert rc == 0 and oplib.kernel_error() == 0 and int(absent_peer[0]) == 2
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 6144, 4096), (64, 4096, 12288), (7, 4096, 4096), (128, 2048, 1024), (64, 24576, 4096)])
+@pytest.mark.parametrize("with_resid", [False, True])
+def test_decode_splitk_gemm_matches_fp32(M, N, K, with_resid):
+    \"\"\"Decode-shaped product with K split over CTAs (fp32 pieces + reduce kernel) against an fp32 matmul.\"\"\"
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16() if with_resid else None
+    y = OF.gemm_decode(x, w, r)
+    torch.cuda.synchronize()
+    assert oplib.kernel_error() == 0
+    ref = x.float() @ w.float().t() + (r.float() if with_resid else 0)
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 4e-3
+    y2 = OF.gemm_decode(x, w, r)                                    # the workspace is reusable without clearing
+    assert torch.equal(y, y2)
