@@ -484,7 +484,7 @@ def test_bounded_peer_wait_reports_instead_of_hanging():
 @pytest.mark.parametrize("M,N,K", [(64, 6144, 4096), (64, 4096, 12288), (7, 4096, 4096), (128, 2048, 1024), (64, 24576, 4096)])
 @pytest.mark.parametrize("with_resid", [False, True])
 def test_decode_splitk_gemm_matches_fp32(M, N, K, with_resid):
-    \"\"\"Decode-shaped product with K split over CTAs (fp32 pieces + reduce kernel) against an fp32 matmul.\"\"\"
+    """Decode-shaped product with K split over CTAs (fp32 pieces + reduce kernel) against an fp32 matmul."""
     torch.manual_seed(M + N)
     x = torch.randn(M, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
