@@ -299,7 +299,8 @@ struct DecodeMmaCfg {
   static constexpr int OPERAND_BYTES = DEC_CHUNK * STRIDE;
   static constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;           // K rows then V rows
   static constexpr int Q_BYTES = 16 * STRIDE;
-  static constexpr int SMEM_BYTES = 2 * STAGE_BYTES + Q_BYTES;
+  static constexpr int SLOT_BYTES = 2 * DEC_CHUNK * 8;               // row -> element offset of its K/V row, two chunks
+  static constexpr int SMEM_BYTES = 2 * STAGE_BYTES + Q_BYTES + SLOT_BYTES;
 };
 
 template <int D>
@@ -327,26 +328,38 @@ paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const uint32_t sq_addr = smem0 + 2 * Cfg::STAGE_BYTES;
   const float sl2 = scale * 1.4426950408889634f;
 
+  // Row offsets of a chunk are worked out once (64 threads, one row each: page lookup + the only
+  // integer divisions of the copy path) and kept in shared memory, one chunk ahead of the copies.
+  long long* s_off = reinterpret_cast<long long*>(dsm + 2 * Cfg::STAGE_BYTES + Cfg::Q_BYTES);   // [2][DEC_CHUNK], -1 = past the end
+  auto plan = [&](int c) {
+    if (tid < DEC_CHUNK) {
+      const int t = t0 + c * DEC_CHUNK + tid;
+      long long off = -1;
+      if (t < t1) {
+        const int page = pt[t / page_size];
+        off = (((long long)page * page_size + (t % page_size)) * Hkv + h) * D;
+      }
+      s_off[(c & 1) * DEC_CHUNK + tid] = off;
+    }
+  };
   auto issue = [&](int c, int stage) {
-    const int base = t0 + c * DEC_CHUNK;
 #pragma unroll
     for (int i = 0; i < PIECES / 128; ++i) {
       const int idx = tid + i * 128;
       const int row = idx / (D / 8), piece = idx % (D / 8);
-      const int t = base + row;
-      const bool ok = t < t1;
-      size_t off = 0;
-      if (ok) {
-        const int page = pt[t / page_size];
-        off = (((size_t)page * page_size + (t % page_size)) * Hkv + h) * D + piece * 8;
-      }
+      const long long off = s_off[(c & 1) * DEC_CHUNK + row];
+      const bool ok = off >= 0;
+      const size_t src = ok ? (size_t)off + piece * 8 : 0;
       const uint32_t dst = smem0 + stage * Cfg::STAGE_BYTES + row * STRIDE + piece * 16;
-      cp_async16(dst, kc + off, ok);
-      cp_async16(dst + Cfg::OPERAND_BYTES, vc + off, ok);
+      cp_async16(dst, kc + src, ok);
+      cp_async16(dst + Cfg::OPERAND_BYTES, vc + src, ok);
     }
     cp_async_commit();
   };
 
+  if (n_chunks > 0) plan(0);
+  if (n_chunks > 1) plan(1);
+  __syncthreads();
   if (n_chunks > 0) issue(0, 0);
   // queries of the group as a 16-row tile (rows >= G zero)
   for (int i = tid; i < 16 * (D / 8); i += 128) {
@@ -378,6 +391,7 @@ paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       cp_async_wait<0>();
     }
     __syncthreads();
+    if (c + 2 < n_chunks) plan(c + 2);      // table slot (c & 1) is free: chunk c's copies have been issued from it
     const uint32_t ks_addr = smem0 + stage * Cfg::STAGE_BYTES + (warp * 16) * STRIDE;   // this warp's 16 tokens
     const uint32_t vs_addr = ks_addr + Cfg::OPERAND_BYTES;
     const int mat = lane >> 3, r = lane & 7;
