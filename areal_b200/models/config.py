@@ -132,7 +132,7 @@ class ModelConfig:
             rms_norm_eps=float(d.get("rms_norm_eps", 1e-6)), tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
             attention_bias=bool(d.get("attention_bias", mt == "qwen2")), qk_norm=(mt in ("qwen3", "qwen3_moe")),
             max_position_embeddings=d.get("max_position_embeddings", 32768),
-            num_experts=d.get("num_experts", 0) or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
+            num_experts=d.get("num_experts") or d.get("num_local_experts") or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0, norm_topk_prob=bool(d.get("norm_topk_prob", True)),
             router_aux_loss_coef=float(d.get("router_aux_loss_coef", 0.0) or 0.0),
             router_score_func=d.get("scoring_func", d.get("router_score_func", "softmax")) or "softmax",
