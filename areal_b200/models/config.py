@@ -14,7 +14,7 @@ from typing import Optional
 
 @dataclass
 class ModelConfig:
-    arch: str = "qwen2"                 # qwen2 | qwen3 | qwen3_moe
+    arch: str = "qwen2"                 # qwen2 | qwen3 | qwen3_moe | qwen2_moe
     vocab_size: int = 151936
     hidden_size: int = 1536
     num_layers: int = 28
@@ -34,6 +34,7 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     router_aux_loss_coef: float = 0.0
+    shared_expert_intermediate_size: int = 0   # > 0: a dense expert every token visits, gated by sigmoid(w . x) (Qwen2-MoE)
     router_score_func: str = "softmax"      # softmax | sigmoid (DeepSeek-V3 style gates)
     router_scale: float = 1.0               # multiplies the selected gate weights
     num_expert_groups: int = 0              # > 0: group-limited routing (experts chosen inside the best groups only)
@@ -83,6 +84,8 @@ class ModelConfig:
             attn += 2 * self.head_dim
         dense_mlp = 3 * H * self.intermediate_size
         moe_mlp = self.num_experts * 3 * H * self.moe_intermediate_size + H * self.num_experts
+        if self.shared_expert_intermediate_size:
+            moe_mlp += 3 * H * self.shared_expert_intermediate_size + H
         total = V * H * (1 if self.tie_word_embeddings else 2) + H
         for i in range(L):
             total += attn + 2 * H + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
@@ -120,7 +123,7 @@ class ModelConfig:
             d["_mrope_section"] = list(rs.get("mrope_section", [16, 24, 24]))
             d["attention_bias"] = True
             mt = "qwen2"
-        arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "llama": "qwen2"}.get(mt)
+        arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "qwen2_moe": "qwen2_moe", "llama": "qwen2"}.get(mt)
         if arch is None:
             raise ValueError(f"unsupported model_type '{mt}'")
         heads = d["num_attention_heads"]
@@ -130,11 +133,12 @@ class ModelConfig:
             num_heads=heads, num_kv_heads=d.get("num_key_value_heads", heads), head_dim=hd,
             intermediate_size=d.get("intermediate_size", 0), rope_theta=float(d.get("rope_theta", 1e4)),
             rms_norm_eps=float(d.get("rms_norm_eps", 1e-6)), tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
-            attention_bias=bool(d.get("attention_bias", mt == "qwen2")), qk_norm=(mt in ("qwen3", "qwen3_moe")),
+            attention_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))), qk_norm=(mt in ("qwen3", "qwen3_moe")),
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             num_experts=d.get("num_experts") or d.get("num_local_experts") or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
-            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0, norm_topk_prob=bool(d.get("norm_topk_prob", True)),
+            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0, norm_topk_prob=bool(d.get("norm_topk_prob", mt != "qwen2_moe")),
             router_aux_loss_coef=float(d.get("router_aux_loss_coef", 0.0) or 0.0),
+            shared_expert_intermediate_size=int(d.get("shared_expert_intermediate_size", 0) or 0) if mt == "qwen2_moe" else 0,
             router_score_func=d.get("scoring_func", d.get("router_score_func", "softmax")) or "softmax",
             router_scale=float(d.get("routed_scaling_factor", d.get("router_scale", 1.0)) or 1.0),
             num_expert_groups=int(d.get("n_group", d.get("num_expert_groups", 0)) or 0),
@@ -155,7 +159,7 @@ class ModelConfig:
         mt = self.arch
         d = dict(
             model_type=mt, architectures=[{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                                           "qwen3_moe": "Qwen3MoeForCausalLM"}[mt]],
+                                           "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_moe": "Qwen2MoeForCausalLM"}[mt]],
             vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_layers,
             num_attention_heads=self.num_heads, num_key_value_heads=self.num_kv_heads, head_dim=self.head_dim,
             intermediate_size=self.intermediate_size, rope_theta=self.rope_theta, rms_norm_eps=self.rms_norm_eps,
@@ -174,6 +178,8 @@ class ModelConfig:
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
                      router_aux_loss_coef=self.router_aux_loss_coef, decoder_sparse_step=self.decoder_sparse_step,
                      mlp_only_layers=self.mlp_only_layers)
+            if self.shared_expert_intermediate_size:
+                d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
             if self.router_score_func != "softmax" or self.num_expert_groups or self.router_scale != 1.0 or self.router_bias_update_rate:
                 d.update(scoring_func=self.router_score_func, routed_scaling_factor=self.router_scale, n_group=self.num_expert_groups,
                          topk_group=self.num_limited_groups, router_bias_update_rate=self.router_bias_update_rate)
@@ -213,6 +219,10 @@ PRESETS = {
                           vision=dict(model_type="qwen2_5_vl", depth=32, hidden_size=1280, intermediate_size=3420, num_heads=16, in_chans=3,
                                       patch_size=14, temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=3584, window_size=112,
                                       fullatt_block_indexes=[7, 15, 23, 31])),
+    "tiny-qwen2-moe": dict(arch="qwen2_moe", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                           head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False, attention_bias=True,
+                           num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=256,
+                           norm_topk_prob=False),
     "qwen2.5-1.5b": dict(arch="qwen2", vocab_size=151936, hidden_size=1536, num_layers=28, num_heads=12, num_kv_heads=2,
                          head_dim=128, intermediate_size=8960, rope_theta=1e6, tie_word_embeddings=True,
                          attention_bias=True),

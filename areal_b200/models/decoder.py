@@ -143,6 +143,13 @@ class MoEMLP(nn.Module):
         self.w_gate_up = nn.Parameter(torch.empty(E, 2 * Im, H, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(E, H, Im, dtype=dtype, device=device))
         self.ep_dispatcher = None  # set by parallel.ep.ExpertParallel
+        if cfg.shared_expert_intermediate_size > 0:
+            Is = cfg.shared_expert_intermediate_size
+            self.shared_gate_up = nn.Parameter(torch.empty(2 * Is, H, dtype=dtype, device=device))
+            self.shared_down = nn.Parameter(torch.empty(H, Is, dtype=dtype, device=device))
+            self.shared_expert_gate = nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+        else:
+            self.shared_gate_up = None
         if cfg.router_bias_update_rate > 0:
             self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device), persistent=True)
             self.register_buffer("tokens_per_expert", torch.zeros(E, dtype=torch.float32, device=device), persistent=False)
@@ -248,6 +255,11 @@ class MoEMLP(nn.Module):
         w = topw.reshape(-1)[order].to(ys.dtype).unsqueeze(-1)
         out = torch.zeros(T, H, dtype=ys.dtype, device=x.device)
         out.index_add_(0, token_of, ys * w)
+        if self.shared_gate_up is not None:
+            # the shared expert sees every token; its output is scaled by a per-token sigmoid gate
+            sh = OF.linear(OF.swiglu(OF.linear(x, self.shared_gate_up)), self.shared_down)
+            gate = torch.sigmoid(F.linear(x.float(), self.shared_expert_gate.float())).to(sh.dtype)
+            out = out + gate * sh
         return out
 
 

@@ -62,6 +62,12 @@ def hf_to_native_plan(cfg: ModelConfig) -> dict[str, list[tuple[str, Optional[tu
                 dn.append((h + f"mlp.experts.{e}.down_proj.weight", None, e))
             plan[p + "mlp.w_gate_up"] = gu
             plan[p + "mlp.w_down"] = dn
+            if cfg.shared_expert_intermediate_size:
+                Is = cfg.shared_expert_intermediate_size
+                plan[p + "mlp.shared_gate_up"] = [(h + "mlp.shared_expert.gate_proj.weight", (0, Is), None),
+                                                  (h + "mlp.shared_expert.up_proj.weight", (Is, 2 * Is), None)]
+                plan[p + "mlp.shared_down"] = [(h + "mlp.shared_expert.down_proj.weight", None, None)]
+                plan[p + "mlp.shared_expert_gate"] = [(h + "mlp.shared_expert_gate.weight", None, None)]
         else:
             I = cfg.intermediate_size
             plan[p + "mlp.gate_up_proj"] = [(h + "mlp.gate_proj.weight", (0, I), None),

@@ -29,6 +29,8 @@ def local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
     """Architecture of one TP rank."""
     if tp == 1:
         return cfg
+    if getattr(cfg, "shared_expert_intermediate_size", 0):
+        raise NotImplementedError("tensor parallelism for models with a shared expert (use expert / data parallelism)")
     if cfg.num_heads % tp:
         raise ValueError(f"num_heads={cfg.num_heads} is not divisible by tp={tp}")
     if cfg.num_kv_heads % tp:

@@ -30,10 +30,16 @@ def _hf_model(family):
         cfg = tr.Qwen3MoeConfig(**COMMON, head_dim=64, tie_word_embeddings=False, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
                                 norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])
         return tr.Qwen3MoeForCausalLM(cfg)
+    if family == "qwen2_moe":
+        if not hasattr(tr, "Qwen2MoeForCausalLM"):
+            pytest.skip("transformers without Qwen2-MoE")
+        cfg = tr.Qwen2MoeConfig(**COMMON, tie_word_embeddings=False, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                                shared_expert_intermediate_size=96, norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[])
+        return tr.Qwen2MoeForCausalLM(cfg)
     raise ValueError(family)
 
 
-@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe"])
+@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "qwen2_moe"])
 def test_logits_match_hf(family):
     hf = _hf_model(family).float().eval()
     # make the parameters non-trivial where HF initialises constants (norm weights, biases)
