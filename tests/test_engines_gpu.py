@@ -167,3 +167,61 @@ def test_rollout_engine_sampling_logprobs_consistent_with_trainer():
         worst = max(worst, (got - ref).abs().max().item())
     assert oplib.kernel_error() == 0
     assert worst < 0.1, worst
+
+
+DECODE_SWITCH_SCRIPT = r'''
+import asyncio, json, sys
+sys.path.insert(0, %(root)r)
+import torch
+from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeInferConfig
+from areal_b200.api.io_struct import ModelRequest
+from areal_b200.engine.infer_engine import NativeInferenceEngine
+from areal_b200.models.config import preset
+from areal_b200.ops import lib as oplib
+mc = preset("qwen2.5-1.5b", num_layers=2, vocab_size=4096)
+eng = NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=8, context_length=256, mem_fraction_static=0.1), model_config=mc)
+eng.initialize(seed=11, start_executor=False)
+g = torch.Generator().manual_seed(0)
+reqs = [ModelRequest(rid=f"r{i}", input_ids=torch.randint(0, 4096, (24 + 5 * i,), generator=g).tolist(),
+                     gconfig=GenerationHyperparameters(max_new_tokens=12, max_tokens=200, greedy=True, ignore_eos=True)) for i in range(6)]
+async def run():
+    return await asyncio.gather(*[eng.agenerate(r) for r in reqs])
+out = asyncio.run(run())
+torch.cuda.synchronize()
+print("RESULT " + json.dumps({"tokens": [o.output_tokens for o in out], "logp": [o.output_logprobs for o in out], "err": oplib.kernel_error()}))
+eng.destroy()
+'''
+
+
+def test_decode_switches_agree_with_default(tmp_path):
+    """The optional decode paths (split-K GEMMs, programmatic dependent launch) generate what the
+    default path generates: same first-token log-probs, (almost) the same greedy tokens."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "gen.py"
+    script.write_text(DECODE_SWITCH_SCRIPT % dict(root=root))
+
+    def run(env_extra):
+        env = dict(os.environ)
+        env.update(env_extra)
+        r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=300, env=env, cwd=root)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+        line = next(l for l in r.stdout.splitlines() if l.startswith("RESULT "))
+        return json.loads(line[7:])
+
+    base = run({"AB2_DECODE_SPLITK": "0", "AB2_PDL": "0"})
+    assert base["err"] == 0
+    for extra in ({"AB2_PDL": "1"}, {"AB2_DECODE_SPLITK": "1"}, {"AB2_DECODE_SPLITK": "1", "AB2_PDL": "1"}):
+        got = run({"AB2_DECODE_SPLITK": "0", "AB2_PDL": "0", **extra})
+        assert got["err"] == 0
+        same = sum(int(a == b) for ta, tb in zip(base["tokens"], got["tokens"]) for a, b in zip(ta, tb))
+        total = sum(len(t) for t in base["tokens"])
+        assert same >= 0.9 * total, (extra, same, total)
+        first = max(abs(a[0] - b[0]) for a, b in zip(base["logp"], got["logp"]))
+        assert first < 0.05, (extra, first)
+        if extra == {"AB2_PDL": "1"}:                      # same arithmetic, only the launch differs
+            assert got["tokens"] == base["tokens"]
