@@ -123,3 +123,21 @@ def test_killed_rank_restarts_job_which_resumes_from_recover_checkpoint(tmp_path
     assert launch(str(script), [], cfg, n_gpus=0) == 0
     res = [json.load(open(tmp_path / f"result_{r}.json")) for r in range(2)]
     assert all(r["start"] == 3 and r["steps"] == 3 and r["version"] == 6 for r in res), res
+
+
+def test_plot_session_trace(tmp_path, capsys):
+    from areal_b200.tools import plot_session_trace as pst
+
+    d = tmp_path / "rank0"
+    d.mkdir()
+    rows = [dict(session_id=i, task_id=i, rank=0, submit_ts=100.0 + i, end_ts=103.0 + i, status="accepted" if i % 3 else "rejected",
+                 phases=[dict(name="generate", start=100.2 + i, end=102.0 + i), dict(name="reward", start=102.0 + i, end=102.5 + i)]) for i in range(5)]
+    (d / "sessions.jsonl").write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    out = tmp_path / "s.html"
+    assert pst.main([str(tmp_path), "-o", str(out)]) == 0
+    summ = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert summ["n_sessions"] == 5 and abs(summ["phase_seconds"]["generate"] - 9.0) < 1e-6 and summ["status"] == {"rejected": 2, "accepted": 3}
+    assert abs(summ["unattributed_seconds"] - 5 * 0.7) < 1e-6 and abs(summ["session_seconds"]["max"] - 3.0) < 1e-9
+    text = out.read_text()
+    assert text.count("<rect") >= 5 * 3 and "generate" in text and "<svg" in text
+    assert "no sessions" in pst.render_svg([])
