@@ -417,6 +417,9 @@ class NativeInferConfig:
     # the new weights (what a server that flushes its cache does); True = they keep their KV
     # cache and simply continue, every token tagged with the version that sampled it.
     retain_kv_on_weight_update: bool = False
+    # Requests with an identical prompt (the samples of a GRPO group, retries) share the prompt's full KV
+    # pages and the logits of its last token: the prompt is prefetched once per weight version.
+    enable_prefix_sharing: bool = False
 
 
 @dataclass

@@ -81,16 +81,28 @@ class PagedKVCache:
         self.data = torch.zeros(cfg.num_layers, 2, num_pages * page_size, cfg.num_kv_heads, cfg.head_dim,
                                 device=device, dtype=dtype)
         self.free = list(range(num_pages - 1, -1, -1))
+        self.ref = [0] * num_pages          # users of a page: its sequence, plus the prefix cache and other sequences when shared
 
     def alloc(self, n: int) -> Optional[list[int]]:
         if len(self.free) < n:
             return None
-        out = self.free[-n:]
-        del self.free[-n:]
+        out = self.free[-n:] if n else []
+        if n:
+            del self.free[-n:]
+        for p in out:
+            self.ref[p] = 1
         return out
 
+    def share(self, pages: list[int]) -> None:
+        for p in pages:
+            self.ref[p] += 1
+
     def release(self, pages: list[int]) -> None:
-        self.free.extend(pages)
+        for p in pages:
+            self.ref[p] -= 1
+            if self.ref[p] <= 0:
+                self.ref[p] = 0
+                self.free.append(p)
 
     def pages_needed(self, tokens: int) -> int:
         return (tokens + self.page_size - 1) // self.page_size
@@ -130,6 +142,7 @@ class NativeInferenceEngine(InferenceEngine):
         self._idle = threading.Event()
         self._idle.set()
         self.stats = collections.Counter()
+        self._prefix: collections.OrderedDict = collections.OrderedDict()     # prompt bytes -> shared pages + last-token logits
         self.device = torch.device("cpu")
         self.cache: Optional[PagedKVCache] = None
 
@@ -627,24 +640,43 @@ class NativeInferenceEngine(InferenceEngine):
         cache = self.cache
         # ---- admission + prefill
         admitted: list[_Seq] = []
+        reuse: list[tuple[_Seq, bytes]] = []       # sequences whose prompt is (or is about to be) in the prefix cache
+        pending: dict = {}                         # prompts that a sequence of THIS batch prefetches
+        sharing = bool(getattr(self.icfg, "enable_prefix_sharing", False))
         budget = self.icfg.max_prefill_tokens
+        ps = cache.page_size
         with self._lock:
-            while self._waiting and len(self._running) + len(admitted) < self.max_batch:
+            while self._waiting and len(self._running) + len(admitted) + len(reuse) < self.max_batch:
                 s = self._waiting[0]
                 need = cache.pages_needed(min(len(s.tokens) + s.max_new, self.icfg.context_length))
+                key = self._prefix_key(s) if sharing else None
+                hit = key is not None and (key in pending or self._prefix_lookup(key) is not None)
+                if hit:
+                    pages = self._alloc_pages(need - len(s.tokens) // ps)      # only the private part
+                    if pages is None:
+                        break
+                    self._waiting.popleft()
+                    s.pages = pages
+                    reuse.append((s, key))
+                    continue
                 if len(s.tokens) > budget and admitted:
                     break
-                pages = cache.alloc(need)
+                pages = self._alloc_pages(need)
                 if pages is None:
                     break
                 self._waiting.popleft()
                 s.pages = pages
                 admitted.append(s)
                 budget -= len(s.tokens)
+                if key is not None:
+                    pending[key] = s
         done: list = []
         if admitted:
-            self._prefill(admitted, done)
-            keep = [s for s in admitted if all(s is not d for d, _ in done)]
+            self._prefill(admitted, done, remember=pending if sharing else None)
+        if reuse:
+            self._start_from_prefix(reuse, done)
+        if admitted or reuse:
+            keep = [s for s in admitted + [s for s, _ in reuse] if all(s is not d for d, _ in done)]
             for s in keep:
                 self._assign_row(s)
             with self._lock:
@@ -689,7 +721,81 @@ class NativeInferenceEngine(InferenceEngine):
         ps = self.cache.page_size
         return s.pages[pos // ps] * ps + pos % ps
 
-    def _prefill(self, seqs: list[_Seq], done: list):
+    # ---- prefix sharing (identical prompts: GRPO groups, retries)
+    @staticmethod
+    def _prefix_key(s: _Seq) -> Optional[bytes]:
+        return None if s.mm is not None else np.asarray(s.tokens, dtype=np.int32).tobytes()
+
+    def _prefix_lookup(self, key: bytes):
+        ent = self._prefix.get(key)
+        if ent is None:
+            return None
+        if ent["version"] != self._version:            # computed under older weights
+            self._prefix_drop(key)
+            return None
+        self._prefix.move_to_end(key)
+        return ent
+
+    def _prefix_drop(self, key: bytes) -> None:
+        ent = self._prefix.pop(key, None)
+        if ent is not None:
+            self.cache.release(ent["pages"] + ([ent["tail_page"]] if ent["tail_page"] is not None else []))
+
+    def _alloc_pages(self, n: int):
+        """Page allocation that evicts least recently used prefix entries when the pool runs dry."""
+        pages = self.cache.alloc(n)
+        while pages is None and self._prefix:
+            self._prefix_drop(next(iter(self._prefix)))
+            pages = self.cache.alloc(n)
+        return pages
+
+    def _prefix_remember(self, key: bytes, s: _Seq, logits_row: torch.Tensor) -> None:
+        ps = self.cache.page_size
+        n = s.cached
+        n_full, tail = n // ps, n % ps
+        tail_page = None
+        if tail:
+            got = self.cache.alloc(1)
+            if got is None:
+                return
+            tail_page = got[0]
+            src = s.pages[n_full]
+            self.cache.data[:, :, tail_page * ps: tail_page * ps + tail] = self.cache.data[:, :, src * ps: src * ps + tail]
+        full = list(s.pages[:n_full])
+        self.cache.share(full)
+        self._prefix[key] = dict(pages=full, tail_page=tail_page, tail=tail, n=n, logits=logits_row.clone(), version=self._version)
+
+    def _start_from_prefix(self, reuse: list, done: list) -> None:
+        """Sequences whose whole prompt is cached: link the shared pages, copy the partial last page,
+        sample the first token from the stored logits. No forward pass."""
+        ps = self.cache.page_size
+        ready, rows = [], []
+        for s, key in reuse:
+            ent = self._prefix_lookup(key)
+            if ent is None:                            # the sequence that was to prefetch it did not get to (eviction, failure)
+                self.cache.release(s.pages)
+                s.pages = []
+                with self._lock:
+                    self._waiting.appendleft(s)
+                continue
+            private = s.pages
+            self.cache.share(ent["pages"])
+            s.pages = list(ent["pages"]) + private
+            if ent["tail"]:
+                dst, src = private[0], ent["tail_page"]
+                self.cache.data[:, :, dst * ps: dst * ps + ent["tail"]] = self.cache.data[:, :, src * ps: src * ps + ent["tail"]]
+            s.cached = ent["n"]
+            ready.append(s)
+            rows.append(ent["logits"])
+        if not ready:
+            return
+        toks, lps = self._sample_cuda(torch.stack(rows), ready)
+        self.stats["prefix_hits"] += len(ready)
+        self.stats["prefix_tokens_saved"] += sum(s.cached for s in ready)
+        for s, tok, lp in zip(ready, toks, lps):
+            self._accept_token(s, tok, lp, done)
+
+    def _prefill(self, seqs: list[_Seq], done: list, remember: Optional[dict] = None):
         dev = self.device
         lens = [len(s.tokens) for s in seqs]
         T = sum(lens)
@@ -725,8 +831,11 @@ class NativeInferenceEngine(InferenceEngine):
         logits = self.model.logits(hidden[last_idx].contiguous())
         toks, lps = self._sample_cuda(logits, seqs)
         self.stats["prefill_tokens"] += T
-        for s, n, tok, lp in zip(seqs, lens, toks, lps):
+        keys = {id(s): k for k, s in (remember or {}).items()}
+        for i, (s, n, tok, lp) in enumerate(zip(seqs, lens, toks, lps)):
             s.cached = n
+            if id(s) in keys:
+                self._prefix_remember(keys[id(s)], s, logits[i])      # before the first token is appended to s.tokens
             self._accept_token(s, tok, lp, done)
 
     def _sample_rows(self, logits: torch.Tensor, n: int, inv_temp, greedy, seeds):

@@ -225,3 +225,46 @@ def test_decode_switches_agree_with_default(tmp_path):
         assert first < 0.05, (extra, first)
         if extra == {"AB2_PDL": "1"}:                      # same arithmetic, only the launch differs
             assert got["tokens"] == base["tokens"]
+
+
+@pytest.mark.parametrize("prompt_len", [64, 75])       # whole pages only / a partial last page
+def test_prefix_sharing_reuses_prompt_pages_and_matches_plain_engine(prompt_len):
+    """Requests with the same prompt: one prefetch, shared full pages, first token sampled from the
+    stored logits; greedy outputs equal those of an engine without sharing, and every page returns
+    to the pool afterwards. A weight-version change invalidates the stored prompts."""
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=11)
+
+    def engine(share):
+        ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=512, enable_prefix_sharing=share)
+        ic.num_pages = 256
+        return NativeInferenceEngine(InferenceEngineConfig(), ic, model=model, eos_token_id=None).initialize(device="cuda", start_executor=False)
+
+    g = GenerationHyperparameters(max_new_tokens=20, max_tokens=400, greedy=True, ignore_eos=True)
+    shared = list(range(7, 7 + prompt_len))
+    other = list(range(100, 100 + prompt_len - 3))
+    prompts = [shared, shared, other, shared, shared]
+
+    async def run(e):
+        return await asyncio.gather(*[e.agenerate(ModelRequest(rid=f"r{i}", input_ids=p, gconfig=g)) for i, p in enumerate(prompts)])
+
+    plain = engine(False)
+    want = asyncio.run(run(plain))
+    plain.destroy()
+    eng = engine(True)
+    got = asyncio.run(run(eng))
+    assert oplib.kernel_error() == 0
+    for a, b in zip(want, got):
+        assert a.output_tokens == b.output_tokens
+        assert max(abs(x - y) for x, y in zip(a.output_logprobs, b.output_logprobs)) < 1e-3
+    assert eng.stats["prefix_hits"] == 3 and eng.stats["prefix_tokens_saved"] == 3 * prompt_len
+    assert eng.stats["prefill_tokens"] == prompt_len + len(other)
+    # only the cache's own references remain: the two prompts' full pages (+ a copy of each partial last page)
+    held = sum(len(e["pages"]) + (e["tail_page"] is not None) for e in eng._prefix.values())
+    assert len(eng.cache.free) == eng.cache.num_pages - held and held == 2 * (prompt_len // 16) + 2 * (prompt_len % 16 > 0)
+    again = asyncio.run(run(eng))                                   # now all five prompts are cached
+    assert [r.output_tokens for r in again] == [r.output_tokens for r in want] and eng.stats["prefix_hits"] == 8
+    eng.set_version(3)                                              # new weights: stored prompts are stale
+    asyncio.run(run(eng))
+    assert eng.stats["prefix_hits"] == 8 + 3 and all(e["version"] == 3 for e in eng._prefix.values())
+    eng.destroy()
