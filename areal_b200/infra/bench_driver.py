@@ -83,7 +83,7 @@ def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOCon
                                        context_length=args.prompt_len + args.max_len + 64, mem_fraction_static=0.35 if n_pairs == 1 and int(os.environ.get('WORLD_SIZE', '1')) == 1 else 0.6,
                                        max_prefill_tokens=16384,
                                        retain_kv_on_weight_update=bool(getattr(args, "retain_kv", 1)),
-                                       enable_prefix_sharing=bool(getattr(args, "prefix_sharing", 0))),
+                                       enable_prefix_sharing=bool(getattr(args, "prefix_sharing", 1))),
         actor=PPOActorConfig(init_from_scratch=True, dtype="bfloat16", gradient_checkpointing=bool(ckpt),
                              optimizer=OptimizerConfig(lr=1e-6, weight_decay=0.01, gradient_clipping=1.0),
                              mb_spec=MicroBatchSpec(max_tokens_per_mb=mb_tokens),
@@ -225,7 +225,7 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
                    "response_cap": args.max_len, "group_size": args.group_size, "parallelism": parallelism,
                    "max_staleness": args.staleness, "prox_logp_method": args.prox_logp_method, **getattr(args, "_resolved", {}),
                    "inflight_weight_update": "running requests keep their KV cache" if getattr(args, "retain_kv", 1) else "running requests are re-prefilled",
-                   "prefix_sharing": bool(getattr(args, "prefix_sharing", 0)),
+                   "prefix_sharing": bool(getattr(args, "prefix_sharing", 1)),
                    "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
                    "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms,
                    "phase_seconds_per_step": {k_: round(v_, 4) for k_, v_ in sorted(phases.items())}},

@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--staleness", type=int, default=2)
     ap.add_argument("--retain-kv", type=int, default=1, help="1: requests in flight keep their KV cache across a weight update; "
                     "0: they are interrupted and re-prefilled under the new weights")
-    ap.add_argument("--prefix-sharing", type=int, default=0, help="1: the samples of a group share the prompt's KV pages (one prefetch per prompt)")
+    ap.add_argument("--prefix-sharing", type=int, default=1, help="1: the samples of a group share the prompt's KV pages (one prefetch per prompt)")
     return ap.parse_args()
 
 
