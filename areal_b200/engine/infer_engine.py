@@ -753,6 +753,7 @@ class NativeInferenceEngine(InferenceEngine):
         ps = self.cache.page_size
         n = s.cached
         n_full, tail = n // ps, n % ps
+        self._prefix_drop(key)                  # a stale entry of the same prompt gives its pages back first
         tail_page = None
         if tail:
             got = self.cache.alloc(1)
