@@ -150,6 +150,7 @@ class ArchonEngineConfig:
     ac_mode: str = "selective"  # none | full | selective | memory_budget
     pp_schedule: str = "1F1B"
     fp8: FP8Config = field(default_factory=FP8Config)
+    fuse_ep_dispatch: bool = True     # expert-parallel dispatch / combine as peer-memory kernels instead of NCCL all-to-alls
     offload_params: bool = False
     extra: dict = field(default_factory=dict)   # backend-specific keys of the reference, accepted and kept
     __allow_extra__ = True

@@ -319,7 +319,10 @@ class B200TrainEngine(TrainEngine):
 
             if not model_config.is_moe:
                 raise ValueError("expert parallelism needs a mixture-of-experts model")
-            self._expert_param_names = shard_experts(self.model, self.ep_rank, self.ep_size, self._ep_group)
+            fused_ep = (self.device.type == "cuda" and (cfg.archon.fuse_ep_dispatch or cfg.megatron.moe_enable_deepep)
+                        and os.environ.get("AREAL_EP_FUSED", "1") != "0")
+            self._expert_param_names = shard_experts(self.model, self.ep_rank, self.ep_size, self._ep_group, fused=fused_ep,
+                                                     device=self.device)
         self.model.gradient_checkpointing = cfg.gradient_checkpointing
         ac = getattr(cfg.archon, "ac_mode", "selective") if not cfg.gradient_checkpointing else "full"
         if getattr(cfg, "activation_checkpointing", None):

@@ -226,6 +226,7 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
                    "max_staleness": args.staleness, "prox_logp_method": args.prox_logp_method, **getattr(args, "_resolved", {}),
                    "inflight_weight_update": "running requests keep their KV cache" if getattr(args, "retain_kv", 1) else "running requests are re-prefilled",
                    "prefix_sharing": bool(getattr(args, "prefix_sharing", 1)),
+                   "decode_switches": {k_: os.environ.get(k_, "0") for k_ in ("AB2_PDL", "AB2_DECODE_SPLITK")},
                    "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
                    "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms,
                    "phase_seconds_per_step": {k_: round(v_, 4) for k_, v_ in sorted(phases.items())}},

@@ -246,15 +246,20 @@ class MoEMLP(nn.Module):
         flat_e = tope.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         token_of = order // k
-        xs = x[token_of]
-        if self.ep_dispatcher is not None:
-            ys = self.ep_dispatcher(self, xs, flat_e[order])
-        else:
-            counts = torch.bincount(flat_e, minlength=self.cfg.num_experts).tolist()
-            ys = self.experts_forward(xs, counts)
-        w = topw.reshape(-1)[order].to(ys.dtype).unsqueeze(-1)
-        out = torch.zeros(T, H, dtype=ys.dtype, device=x.device)
-        out.index_add_(0, token_of, ys * w)
+        out = None
+        if x.is_cuda and hasattr(self.ep_dispatcher, "fused_forward"):
+            # dispatch and combine as one peer-memory kernel each (parallel/ep_fused.py)
+            out = self.ep_dispatcher.fused_forward(self, x, order, flat_e, topw)
+        if out is None:
+            xs = x[token_of]
+            if self.ep_dispatcher is not None:
+                ys = self.ep_dispatcher(self, xs, flat_e[order])
+            else:
+                counts = torch.bincount(flat_e, minlength=self.cfg.num_experts).tolist()
+                ys = self.experts_forward(xs, counts)
+            w = topw.reshape(-1)[order].to(ys.dtype).unsqueeze(-1)
+            out = torch.zeros(T, H, dtype=ys.dtype, device=x.device)
+            out.index_add_(0, token_of, ys * w)
         if self.shared_gate_up is not None:
             # the shared expert sees every token; its output is scaled by a per-token sigmoid gate
             sh = OF.linear(OF.swiglu(OF.linear(x, self.shared_gate_up)), self.shared_down)

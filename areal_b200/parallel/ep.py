@@ -4,8 +4,8 @@ Experts are partitioned over the EP group (rank r owns experts ``[r*E/ep, (r+1)*
 the router is replicated. Per layer: count exchange -> token dispatch all-to-all (variable
 splits) -> local regroup by expert -> expert GEMMs -> inverse regroup -> combine all-to-all.
 Both all-to-alls are differentiable (the backward of a dispatch is a combine with the splits
-swapped). This is the NCCL baseline; the fused dispatch/combine kernels over peer memory use
-the same split bookkeeping. Reference:
+swapped). This is the library path (and the CPU path); on GPUs ``parallel/ep_fused.py`` replaces both
+directions with one peer-memory kernel each. Reference:
 ``areal/experimental/models/archon/expert_parallel.py`` (count exchange :131, dispatch :163,
 combine :207).
 """
@@ -109,10 +109,12 @@ class ExpertParallelDispatcher:
         return all_to_all_tokens(back, recv_splits, send_splits, self.group)
 
 
-def shard_experts(model, ep_rank: int, ep_size: int, group) -> list[str]:
+def shard_experts(model, ep_rank: int, ep_size: int, group, fused: bool = False, device=None) -> list[str]:
     """Keeps only this rank's experts in every MoE layer and installs the dispatcher. Returns
     the names of the expert parameters (they are NOT replicated over the EP group: their
-    gradients are reduced over the expert-data-parallel replicas only)."""
+    gradients are reduced over the expert-data-parallel replicas only). ``fused`` wraps the
+    dispatchers with the peer-memory dispatch / combine kernels (CUDA only); the communicator
+    is kept as ``model.ep_fused_comm``."""
     expert_params = []
     for lname, layer in model.layers.named_children():
         mlp = layer.mlp
@@ -128,6 +130,10 @@ def shard_experts(model, ep_rank: int, ep_size: int, group) -> list[str]:
         mlp.ep_dispatcher = ExpertParallelDispatcher(group, ep_rank, ep_size)
         mlp.first_local_expert, mlp.num_local_experts = ep_rank * El, El
         expert_params += [f"layers.{lname}.mlp.w_gate_up", f"layers.{lname}.mlp.w_down"]
+    if fused and expert_params:
+        from .ep_fused import install_fused_dispatch
+
+        model.ep_fused_comm = install_fused_dispatch(model, group, ep_rank, ep_size, device)
     return expert_params
 
 
