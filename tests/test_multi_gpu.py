@@ -70,3 +70,12 @@ def test_sequence_parallel_engine_fused_projections_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_sp_fused.py"), 2, 29761, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("ENGINE_SP_FUSED_OK") == 2
+
+
+def test_fused_ep_dispatch_combine_two_gpus():
+    """Expert-parallel dispatch and combine as one peer-memory kernel each, against the NCCL
+    all-to-all dispatcher on the same model and tokens (hidden states, loss, all gradients)."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_ep_fused.py"), 2, 29771, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("EP_FUSED_OK") == 2
