@@ -172,8 +172,13 @@ class NativeInferenceEngine(InferenceEngine):
             self.model.eval()
             for p in self.model.parameters():
                 p.requires_grad_(False)
-        if self.device.type == "cuda":
+        # Layers with a recurrent state (gated delta rule) have no paged-cache decode kernel: such models
+        # generate by re-running the packed forward over every running sequence each step.
+        self._recompute_decode = bool(getattr(self.model_config, "is_hybrid", False))
+        if self.device.type == "cuda" and not self._recompute_decode:
             self._init_cuda_state()
+        elif self.device.type == "cuda":
+            self.stream = torch.cuda.Stream(device=self.device)
         self._thread = threading.Thread(target=self._engine_main, name="infer-engine", daemon=True)
         self._thread.start()
         if start_executor:
@@ -353,7 +358,7 @@ class NativeInferenceEngine(InferenceEngine):
             torch.cuda.empty_cache()
 
     def onload(self, tags=None):
-        if self.cache is None and self.device.type == "cuda":
+        if self.cache is None and self.device.type == "cuda" and not self._recompute_decode:
             n, ps = self._saved_cache_shape
             self.cache = PagedKVCache(self.model_config, n, ps, self.device, torch.bfloat16)
         self.continue_generation()
@@ -478,7 +483,10 @@ class NativeInferenceEngine(InferenceEngine):
                     time.sleep(0.0005)
                     continue
                 self._idle.clear()
-                if self.device.type == "cuda":
+                if self.device.type == "cuda" and self._recompute_decode:
+                    with torch.cuda.stream(self.stream), torch.no_grad():
+                        self._step_cpu()
+                elif self.device.type == "cuda":
                     with torch.cuda.stream(self.stream), torch.no_grad():
                         self._step_cuda()
                 else:
@@ -585,8 +593,8 @@ class NativeInferenceEngine(InferenceEngine):
         if not batch:
             return
         lens = [len(s.tokens) for s in batch]
-        ids = torch.tensor([t for s in batch for t in s.tokens], dtype=torch.long)
-        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        ids = torch.tensor([t for s in batch for t in s.tokens], dtype=torch.long).to(self.device)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32).to(self.device)
         if any(s.mm is not None for s in batch):
             from ..models.vlm import collect_multi_modal
 
@@ -594,7 +602,7 @@ class NativeInferenceEngine(InferenceEngine):
         else:
             hidden = self.model(ids, cu, max_seqlen=max(lens))
         last = hidden[(cu[1:] - 1).long()]
-        logits = self.model.logits(last)
+        logits = self.model.logits(last).float().cpu()
         self._step += 1
         done = []
         for i, s in enumerate(batch):

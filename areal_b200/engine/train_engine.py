@@ -262,6 +262,8 @@ class B200TrainEngine(TrainEngine):
         seed = kwargs.get("seed", 1)
         t0 = time.time()
         tp = getattr(self, "tp_size", 1)
+        if getattr(model_config, "is_hybrid", False) and (tp > 1 or getattr(self, "sp_size", 1) > 1 or getattr(self, "pp_size", 1) > 1):
+            raise NotImplementedError("linear-attention (hybrid) models train data-parallel only: no tensor / sequence / pipeline split yet")
         has_ckpt = (not cfg.init_from_scratch and cfg.path and os.path.isdir(cfg.path)
                     and any(f.endswith(".safetensors") for f in os.listdir(cfg.path)))
         if getattr(self, "pp_size", 1) > 1:

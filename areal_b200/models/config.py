@@ -50,6 +50,29 @@ class ModelConfig:
     video_token_id: int = 151656
     vision_start_token_id: int = 151652
     mrope_section: list[int] = field(default_factory=list)
+    # hybrid linear / full attention stacks (Qwen3.5): per-layer token mixer, gated-delta-rule dimensions,
+    # rotation of only the leading part of each head, sigmoid output gate on full attention, RMSNorm weights
+    # stored as offsets from one
+    layer_types: list[str] = field(default_factory=list)    # "linear_attention" | "full_attention" per layer; empty = all full
+    linear_conv_kernel_dim: int = 4
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
+    partial_rotary_factor: float = 1.0
+    attn_output_gate: bool = False
+    rms_norm_offset: bool = False
+
+    @property
+    def is_hybrid(self) -> bool:
+        return any(t == "linear_attention" for t in self.layer_types)
+
+    def layer_is_linear(self, i: int) -> bool:
+        return bool(self.layer_types) and self.layer_types[i] == "linear_attention"
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
 
     @property
     def is_vlm(self) -> bool:
@@ -86,9 +109,14 @@ class ModelConfig:
         moe_mlp = self.num_experts * 3 * H * self.moe_intermediate_size + H * self.num_experts
         if self.shared_expert_intermediate_size:
             moe_mlp += 3 * H * self.shared_expert_intermediate_size + H
+        if self.attn_output_gate:
+            attn += H * self.q_size
+        kd, vd = self.linear_num_key_heads * self.linear_key_head_dim, self.linear_num_value_heads * self.linear_value_head_dim
+        nv = self.linear_num_value_heads
+        linear = H * (2 * kd + 2 * vd + 2 * nv) + (2 * kd + vd) * self.linear_conv_kernel_dim + 2 * nv + self.linear_value_head_dim + vd * H
         total = V * H * (1 if self.tie_word_embeddings else 2) + H
         for i in range(L):
-            total += attn + 2 * H + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
+            total += (linear if self.layer_is_linear(i) else attn) + 2 * H + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
         return total
 
     def flops_per_token(self, seq_len: int = 0, backward: bool = True) -> float:
@@ -123,7 +151,29 @@ class ModelConfig:
             d["_mrope_section"] = list(rs.get("mrope_section", [16, 24, 24]))
             d["attention_bias"] = True
             mt = "qwen2"
-        arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "qwen2_moe": "qwen2_moe", "llama": "qwen2"}.get(mt)
+        hybrid = {}
+        if mt in ("qwen3_5", "qwen3_5_text"):
+            # text-only use of the hybrid stack: the decoder's fields sit under ``text_config`` in full checkpoints
+            if "text_config" in d:
+                top, d = d, dict(d["text_config"])
+                d.setdefault("tie_word_embeddings", top.get("tie_word_embeddings", False))
+            rp = d.get("rope_parameters") or d.get("rope_scaling") or {}
+            n_l = d["num_hidden_layers"]
+            lt = d.get("layer_types")
+            if not lt:
+                iv = int(d.get("full_attention_interval", 4))
+                lt = ["linear_attention" if (i + 1) % iv else "full_attention" for i in range(n_l)]
+            hybrid = dict(layer_types=list(lt), linear_conv_kernel_dim=int(d.get("linear_conv_kernel_dim", 4)),
+                          linear_key_head_dim=int(d.get("linear_key_head_dim", 128)), linear_value_head_dim=int(d.get("linear_value_head_dim", 128)),
+                          linear_num_key_heads=int(d.get("linear_num_key_heads", 16)), linear_num_value_heads=int(d.get("linear_num_value_heads", 32)),
+                          partial_rotary_factor=float(rp.get("partial_rotary_factor", d.get("partial_rotary_factor", 0.25))),
+                          attn_output_gate=True, rms_norm_offset=True)
+            d = dict(d)
+            d.setdefault("rope_theta", rp.get("rope_theta", 1e7))
+            d["attention_bias"] = bool(d.get("attention_bias", False))
+            mt = "qwen3_5"
+        arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "qwen2_moe": "qwen2_moe", "llama": "qwen2",
+                "qwen3_5": "qwen3_5"}.get(mt)
         if arch is None:
             raise ValueError(f"unsupported model_type '{mt}'")
         heads = d["num_attention_heads"]
@@ -133,7 +183,7 @@ class ModelConfig:
             num_heads=heads, num_kv_heads=d.get("num_key_value_heads", heads), head_dim=hd,
             intermediate_size=d.get("intermediate_size", 0), rope_theta=float(d.get("rope_theta", 1e4)),
             rms_norm_eps=float(d.get("rms_norm_eps", 1e-6)), tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
-            attention_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))), qk_norm=(mt in ("qwen3", "qwen3_moe")),
+            attention_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))), qk_norm=(mt in ("qwen3", "qwen3_moe", "qwen3_5")),
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             num_experts=d.get("num_experts") or d.get("num_local_experts") or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0, norm_topk_prob=bool(d.get("norm_topk_prob", mt != "qwen2_moe")),
@@ -147,7 +197,7 @@ class ModelConfig:
             decoder_sparse_step=d.get("decoder_sparse_step", 1) or 1, mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
             vision=vl, mrope_section=list(d.get("_mrope_section", [])),
             image_token_id=int(d.get("image_token_id", 151655)), video_token_id=int(d.get("video_token_id", 151656)),
-            vision_start_token_id=int(d.get("vision_start_token_id", 151652)),
+            vision_start_token_id=int(d.get("vision_start_token_id", 151652)), **hybrid,
         )
 
     @classmethod
@@ -158,7 +208,7 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         mt = self.arch
         d = dict(
-            model_type=mt, architectures=[{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+            model_type=mt, architectures=[{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
                                            "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_moe": "Qwen2MoeForCausalLM"}[mt]],
             vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_layers,
             num_attention_heads=self.num_heads, num_key_value_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -166,6 +216,12 @@ class ModelConfig:
             tie_word_embeddings=self.tie_word_embeddings, attention_bias=self.attention_bias,
             max_position_embeddings=self.max_position_embeddings, hidden_act="silu", torch_dtype="bfloat16",
         )
+        if self.arch == "qwen3_5":
+            d.update(model_type="qwen3_5_text", layer_types=list(self.layer_types), linear_conv_kernel_dim=self.linear_conv_kernel_dim,
+                     linear_key_head_dim=self.linear_key_head_dim, linear_value_head_dim=self.linear_value_head_dim,
+                     linear_num_key_heads=self.linear_num_key_heads, linear_num_value_heads=self.linear_num_value_heads,
+                     rope_parameters=dict(rope_type="default", rope_theta=self.rope_theta, partial_rotary_factor=self.partial_rotary_factor))
+            d.pop("rope_theta", None)
         if self.is_vlm:
             vmt = self.vision.get("model_type", "qwen2_vl")
             d.update(model_type=vmt, architectures=[{"qwen2_vl": "Qwen2VLForConditionalGeneration",
@@ -202,6 +258,16 @@ PRESETS = {
                            head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False,
                            attention_bias=False, qk_norm=True, num_experts=8, num_experts_per_tok=2,
                            moe_intermediate_size=128),
+    "tiny-qwen3.5": dict(arch="qwen3_5", vocab_size=1024, hidden_size=128, num_layers=4, num_heads=4, num_kv_heads=2, head_dim=32,
+                         intermediate_size=256, rope_theta=1e4, tie_word_embeddings=False, attention_bias=False, qk_norm=True,
+                         layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+                         linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
+                         linear_num_value_heads=4, partial_rotary_factor=0.25, attn_output_gate=True, rms_norm_offset=True),
+    "qwen3.5-9b": dict(arch="qwen3_5", vocab_size=248320, hidden_size=4096, num_layers=32, num_heads=16, num_kv_heads=4, head_dim=256,
+                       intermediate_size=12288, rope_theta=1e7, tie_word_embeddings=False, attention_bias=False, qk_norm=True,
+                       layer_types=[("linear_attention" if (i + 1) % 4 else "full_attention") for i in range(32)],
+                       linear_conv_kernel_dim=4, linear_key_head_dim=128, linear_value_head_dim=128, linear_num_key_heads=16,
+                       linear_num_value_heads=32, partial_rotary_factor=0.25, attn_output_gate=True, rms_norm_offset=True),
     "tiny-qwen2-vl": dict(arch="qwen2", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
                           head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False, attention_bias=True,
                           image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, mrope_section=[8, 12, 12],

@@ -307,7 +307,11 @@ class CausalLM(nn.Module):
         self.dtype = dtype
         H = cfg.hidden_size
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
-        self.layers = nn.ModuleList([DecoderLayer(cfg, i, dtype, device) for i in range(cfg.num_layers)])
+        if cfg.layer_types:
+            from .hybrid import HybridDecoderLayer as layer_cls   # linear / gated full attention per layer (Qwen3.5)
+        else:
+            layer_cls = DecoderLayer
+        self.layers = nn.ModuleList([layer_cls(cfg, i, dtype, device) for i in range(cfg.num_layers)])
         self.norm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
         if cfg.is_critic:
             self.value_head = nn.Parameter(torch.zeros(1, H, dtype=dtype, device=device))
@@ -337,6 +341,10 @@ class CausalLM(nn.Module):
                 for a in range(0, flat.numel(), step):
                     b = min(flat.numel(), a + step)
                     flat[a:b] = (torch.randn(b - a, device=p.device, dtype=torch.float32, generator=gen) * std).to(p.dtype)
+        if self.cfg.layer_types:
+            from .hybrid import init_hybrid_parameters
+
+            init_hybrid_parameters(self, gen)
 
     @property
     def output_weight(self) -> torch.Tensor:
@@ -346,7 +354,7 @@ class CausalLM(nn.Module):
         max_pos = max_pos or self.cfg.max_position_embeddings
         key = (str(device), max_pos)
         if key not in self._rope_cache:
-            self._rope_cache = {key: OF.rope_tables(max_pos, self.cfg.head_dim, self.cfg.rope_theta, device)}
+            self._rope_cache = {key: OF.rope_tables(max_pos, self.cfg.rotary_dim, self.cfg.rope_theta, device)}
         return self._rope_cache[key]
 
     def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None, inputs_embeds: Optional[torch.Tensor] = None,
@@ -363,7 +371,12 @@ class CausalLM(nn.Module):
                 h, resid = checkpoint(layer, h, resid, pb, cos, sin, fn, use_reentrant=False)
             else:
                 h, resid = layer(h, resid, pb, cos, sin, fn)
-        x, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
+        if self.cfg.rms_norm_offset:
+            from .hybrid import rmsnorm_offset
+
+            x, _ = rmsnorm_offset(h, self.norm, self.cfg.rms_norm_eps, resid)
+        else:
+            x, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
         return x
 
     def set_fp8(self, dense: bool = True) -> int:

@@ -37,6 +37,29 @@ def hf_to_native_plan(cfg: ModelConfig) -> dict[str, list[tuple[str, Optional[tu
         plan[p + "input_layernorm"] = [(h + "input_layernorm.weight", None, None)]
         plan[p + "post_attention_layernorm"] = [(h + "post_attention_layernorm.weight", None, None)]
         q_rows, k_rows = nq * D, nkv * D
+        if cfg.layer_types:
+            # hybrid stack: gated-delta-rule layers and gated full attention keep their own projections
+            I = cfg.intermediate_size
+            plan[p + "mlp.gate_up_proj"] = [(h + "mlp.gate_proj.weight", (0, I), None), (h + "mlp.up_proj.weight", (I, 2 * I), None)]
+            plan[p + "mlp.down_proj"] = [(h + "mlp.down_proj.weight", None, None)]
+            if cfg.layer_is_linear(i):
+                la, nv = h + "linear_attn.", cfg.linear_num_value_heads
+                plan[p + "linear_attn.in_proj_qkv"] = [(la + "in_proj_qkv.weight", None, None)]
+                plan[p + "linear_attn.in_proj_z"] = [(la + "in_proj_z.weight", None, None)]
+                plan[p + "linear_attn.in_proj_ba"] = [(la + "in_proj_b.weight", (0, nv), None), (la + "in_proj_a.weight", (nv, 2 * nv), None)]
+                plan[p + "linear_attn.conv1d"] = [(la + "conv1d.weight", None, None)]        # checkpoint shape [C, 1, K]
+                plan[p + "linear_attn.dt_bias"] = [(la + "dt_bias", None, None)]
+                plan[p + "linear_attn.A_log"] = [(la + "A_log", None, None)]
+                plan[p + "linear_attn.norm"] = [(la + "norm.weight", None, None)]
+                plan[p + "linear_attn.out_proj"] = [(la + "out_proj.weight", None, None)]
+            else:
+                plan[p + "self_attn.q_proj"] = [(h + "self_attn.q_proj.weight", None, None)]
+                plan[p + "self_attn.kv_proj"] = [(h + "self_attn.k_proj.weight", (0, k_rows), None),
+                                                 (h + "self_attn.v_proj.weight", (k_rows, 2 * k_rows), None)]
+                plan[p + "self_attn.o_proj"] = [(h + "self_attn.o_proj.weight", None, None)]
+                plan[p + "self_attn.q_norm"] = [(h + "self_attn.q_norm.weight", None, None)]
+                plan[p + "self_attn.k_norm"] = [(h + "self_attn.k_norm.weight", None, None)]
+            continue
         plan[p + "self_attn.qkv_proj"] = [
             (h + "self_attn.q_proj.weight", (0, q_rows), None),
             (h + "self_attn.k_proj.weight", (q_rows, q_rows + k_rows), None),
@@ -84,7 +107,8 @@ def native_to_hf_tensors(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tens
             raise KeyError(f"no HF mapping for parameter '{name}'")
         for hf_name, rows, expert in plan[name]:
             src = t if expert is None else t[expert]
-            yield hf_name, (src if rows is None else src[rows[0]:rows[1]])
+            src = src if rows is None else src[rows[0]:rows[1]]
+            yield hf_name, (src.unsqueeze(1) if hf_name.endswith("linear_attn.conv1d.weight") else src)
 
 
 @torch.no_grad()
@@ -110,6 +134,8 @@ def load_hf_tensors_into(cfg: ModelConfig, params: dict[str, torch.Tensor], hf_t
                 raise KeyError(f"unexpected tensor '{hf_name}' in checkpoint")
             continue
         native, rows, expert = inverse[hf_name]
+        if hf_name.endswith("linear_attn.conv1d.weight") and t.dim() == 3:
+            t = t.squeeze(1)
         dst = params[native]
         dst = dst if expert is None else dst[expert]
         dst = dst if rows is None else dst[rows[0]:rows[1]]

@@ -68,22 +68,51 @@ def main():
         loss.backward()
         return h.detach(), loss.detach()
 
+    # fp32 oracle on the CPU: the unsplit model with the same (bf16-rounded) weights on this rank's tokens.
+    # Replicated parameters get exactly that gradient; an expert slice gets the sum over all ranks' tokens.
+    oracle = build_model(cfg, dtype=torch.float32, device="cpu", seed=3)
+    full = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=3)      # same draws as the two GPU models
+    with torch.no_grad():
+        src = dict(full.named_parameters())
+        for n, p in oracle.named_parameters():
+            p.copy_(src[n].float().cpu())
+    del full, src
+    oracle.train()
+    ho = oracle(ids.cpu(), cu.cpu(), max_seqlen=max(lens))
+    lpo, _ = oracle.logprobs_entropy(ho, labels.cpu())
+    (-lpo.float().mean()).backward()
+    El = cfg.num_experts // world
+    want = {}
+    for n, p in oracle.named_parameters():
+        gr = p.grad.to(dev)
+        if n in names:
+            dist.all_reduce(gr)
+            gr = gr[rank * El:(rank + 1) * El]
+        want[n] = gr
+
     for it in range(2):                                       # second pass reuses the slabs with advanced phases
         h0, l0 = run(base)
         h1, l1 = run(fused)
         assert rel(h1, h0) < 2e-2, ("hidden", rel(h1, h0))
+        hf_, hb_ = rel(h1, ho.to(dev)), rel(h0, ho.to(dev))
+        assert hf_ < max(1.5 * hb_, 5e-2), ("hidden vs fp32 (fused, library)", hf_, hb_)
         assert abs(l0.item() - l1.item()) < 2e-2 * max(1.0, abs(l0.item())), (l0.item(), l1.item())
         gb = dict(base.named_parameters())
-        worst = ("", 0.0)
+        worst = ("", 0.0, 0.0)
+        bad = []
         for n, p in fused.named_parameters():
             a, b = p.grad, gb[n].grad
             assert (a is None) == (b is None), n
             if a is None:
                 continue
-            r = rel(a, b)
-            if r > worst[1]:
-                worst = (n, r)
-        assert worst[1] < 5e-2, worst
+            # both paths against fp32 math: the fused kernels (fp32 gate weighting and top-k sums) must be at
+            # least as close as the library path (bf16 products and sums), up to a small floor
+            ef, eb = rel(a, want[n]), rel(b, want[n])
+            if not ef < max(2.0 * eb, 5e-2):
+                bad.append((n, round(ef, 4), round(eb, 4)))
+            if ef > worst[1]:
+                worst = (n, ef, eb)
+        assert not bad, bad
     calls = sum(layer.mlp.ep_dispatcher.fused_calls for layer in fused.layers if hasattr(layer.mlp, "ep_dispatcher"))
     assert calls >= 2 * cfg.num_layers, calls                  # the fused path is what ran
     # forward-only (no_grad) path returns views of the slabs
@@ -92,7 +121,7 @@ def main():
         b = fused(ids, cu, max_seqlen=max(lens))
     assert rel(b, a) < 2e-2
     assert oplib.kernel_error() == 0
-    out = {"rank": rank, "hidden_rel": rel(h1, h0), "worst_grad": worst}
+    out = {"rank": rank, "hidden_rel": rel(h1, h0), "worst_grad_vs_fp32 (name, fused, library)": worst}
 
     if os.environ.get("EP_FUSED_BENCH", "0") == "1":
         big = preset("tiny-qwen3-moe", hidden_size=2048, num_layers=1, num_heads=16, num_kv_heads=4, head_dim=128,

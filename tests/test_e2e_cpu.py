@@ -1,5 +1,6 @@
 """End-to-end slices on CPU: colocated async GRPO, trainer/rollout split over gloo, HF
 checkpoint round trip, recover, weight-push plan."""
+import math
 import os
 import subprocess
 import sys
@@ -60,6 +61,19 @@ def test_colocated_async_grpo_learns_shaped_reward(tmp_path):
     assert os.path.exists(os.path.join(str(tmp_path), "logs"))
 
 
+def test_hybrid_linear_attention_actor_trains_and_rolls_out(tmp_path):
+    """The gated-delta-rule / gated-attention stack through the whole loop: rollout (recompute
+    path of the engine), log-prob recompute, PPO update, weight hand-over."""
+    cfg = _cfg(str(tmp_path), steps=3)
+    mc = preset("tiny-qwen3.5", vocab_size=64, num_layers=2, layer_types=["linear_attention", "full_attention"])
+    with PPOTrainer(cfg, ArithmeticDataset(size=64), tokenizer=None, model_config=mc) as tr:
+        hist = tr.train(workflow=RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True))
+        names = [n for n, _ in tr.actor.model.named_parameters()]
+    assert len(hist) == 3 and all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
+    assert all(math.isfinite(h["ppo_actor/update/grad_norm"]) for h in hist)
+    assert "layers.0.linear_attn.A_log" in names and "layers.1.self_attn.q_proj" in names
+
+
 def test_recover_resumes_from_checkpoint(tmp_path):
     mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
     cfg = _cfg(str(tmp_path), steps=2, recover="auto")
@@ -75,7 +89,7 @@ def test_recover_resumes_from_checkpoint(tmp_path):
         assert len(hist) == 1
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-qwen3", "tiny-qwen3-moe"])
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-qwen3", "tiny-qwen3-moe", "tiny-qwen3.5"])
 def test_hf_checkpoint_roundtrip_and_names(tmp_path, name):
     cfg = preset(name)
     m = build_model(cfg, dtype=torch.float32, seed=2)
@@ -83,7 +97,12 @@ def test_hf_checkpoint_roundtrip_and_names(tmp_path, name):
     files = os.listdir(tmp_path)
     assert "config.json" in files and any(f.endswith(".safetensors") for f in files)
     names = {k for k, _ in hf_io.iter_safetensors(str(tmp_path))}
-    assert "model.layers.0.self_attn.q_proj.weight" in names and "model.embed_tokens.weight" in names
+    if cfg.is_hybrid:
+        assert {"model.layers.0.linear_attn.in_proj_qkv.weight", "model.layers.0.linear_attn.in_proj_a.weight", "model.layers.0.linear_attn.A_log",
+                "model.layers.3.self_attn.q_proj.weight", "model.layers.3.self_attn.v_proj.weight"} <= names
+    else:
+        assert "model.layers.0.self_attn.q_proj.weight" in names
+    assert "model.embed_tokens.weight" in names
     if cfg.is_moe:
         assert "model.layers.0.mlp.experts.3.up_proj.weight" in names and "model.layers.0.mlp.gate.weight" in names
     m2 = build_model(ModelConfig.from_pretrained(str(tmp_path)), dtype=torch.float32, seed=99)

@@ -29,7 +29,7 @@ def _batch(B=6, L=300, V=1024, seed=0):
                 versions=torch.zeros(B, L, dtype=torch.int32), rewards=torch.randn(B, generator=g))
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-qwen3", "tiny-qwen3-moe"])
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-qwen3", "tiny-qwen3-moe", "tiny-qwen3.5"])
 def test_forward_logprob_parity_with_cpu(name):
     cfg = preset(name)
     ref = build_model(cfg, dtype=torch.float32, device="cpu", seed=3)
