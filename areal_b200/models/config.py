@@ -152,7 +152,8 @@ class ModelConfig:
             d["attention_bias"] = True
             mt = "qwen2"
         hybrid = {}
-        if mt in ("qwen3_5", "qwen3_5_text"):
+        if mt in ("qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text"):
+            moe5 = "moe" in mt
             # text-only use of the hybrid stack: the decoder's fields sit under ``text_config`` in full checkpoints
             if "text_config" in d:
                 top, d = d, dict(d["text_config"])
@@ -171,9 +172,11 @@ class ModelConfig:
             d = dict(d)
             d.setdefault("rope_theta", rp.get("rope_theta", 1e7))
             d["attention_bias"] = bool(d.get("attention_bias", False))
-            mt = "qwen3_5"
+            mt = "qwen3_5_moe" if moe5 else "qwen3_5"
+            if moe5:
+                d["norm_topk_prob"] = True
         arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "qwen2_moe": "qwen2_moe", "llama": "qwen2",
-                "qwen3_5": "qwen3_5"}.get(mt)
+                "qwen3_5": "qwen3_5", "qwen3_5_moe": "qwen3_5_moe"}.get(mt)
         if arch is None:
             raise ValueError(f"unsupported model_type '{mt}'")
         heads = d["num_attention_heads"]
@@ -183,12 +186,12 @@ class ModelConfig:
             num_heads=heads, num_kv_heads=d.get("num_key_value_heads", heads), head_dim=hd,
             intermediate_size=d.get("intermediate_size", 0), rope_theta=float(d.get("rope_theta", 1e4)),
             rms_norm_eps=float(d.get("rms_norm_eps", 1e-6)), tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
-            attention_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))), qk_norm=(mt in ("qwen3", "qwen3_moe", "qwen3_5")),
+            attention_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))), qk_norm=(mt in ("qwen3", "qwen3_moe", "qwen3_5", "qwen3_5_moe")),
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             num_experts=d.get("num_experts") or d.get("num_local_experts") or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0, norm_topk_prob=bool(d.get("norm_topk_prob", mt != "qwen2_moe")),
             router_aux_loss_coef=float(d.get("router_aux_loss_coef", 0.0) or 0.0),
-            shared_expert_intermediate_size=int(d.get("shared_expert_intermediate_size", 0) or 0) if mt == "qwen2_moe" else 0,
+            shared_expert_intermediate_size=int(d.get("shared_expert_intermediate_size", 0) or 0) if mt in ("qwen2_moe", "qwen3_5_moe") else 0,
             router_score_func=d.get("scoring_func", d.get("router_score_func", "softmax")) or "softmax",
             router_scale=float(d.get("routed_scaling_factor", d.get("router_scale", 1.0)) or 1.0),
             num_expert_groups=int(d.get("n_group", d.get("num_expert_groups", 0)) or 0),
@@ -208,7 +211,7 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         mt = self.arch
         d = dict(
-            model_type=mt, architectures=[{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
+            model_type=mt, architectures=[{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM", "qwen3_5_moe": "Qwen3_5MoeForCausalLM",
                                            "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_moe": "Qwen2MoeForCausalLM"}[mt]],
             vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_layers,
             num_attention_heads=self.num_heads, num_key_value_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -216,8 +219,8 @@ class ModelConfig:
             tie_word_embeddings=self.tie_word_embeddings, attention_bias=self.attention_bias,
             max_position_embeddings=self.max_position_embeddings, hidden_act="silu", torch_dtype="bfloat16",
         )
-        if self.arch == "qwen3_5":
-            d.update(model_type="qwen3_5_text", layer_types=list(self.layer_types), linear_conv_kernel_dim=self.linear_conv_kernel_dim,
+        if self.arch in ("qwen3_5", "qwen3_5_moe"):
+            d.update(model_type=self.arch + "_text", layer_types=list(self.layer_types), linear_conv_kernel_dim=self.linear_conv_kernel_dim,
                      linear_key_head_dim=self.linear_key_head_dim, linear_value_head_dim=self.linear_value_head_dim,
                      linear_num_key_heads=self.linear_num_key_heads, linear_num_value_heads=self.linear_num_value_heads,
                      rope_parameters=dict(rope_type="default", rope_theta=self.rope_theta, partial_rotary_factor=self.partial_rotary_factor))
@@ -263,6 +266,13 @@ PRESETS = {
                          layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
                          linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
                          linear_num_value_heads=4, partial_rotary_factor=0.25, attn_output_gate=True, rms_norm_offset=True),
+    "tiny-qwen3.5-moe": dict(arch="qwen3_5_moe", vocab_size=1024, hidden_size=128, num_layers=4, num_heads=4, num_kv_heads=2, head_dim=32,
+                             intermediate_size=0, rope_theta=1e4, tie_word_embeddings=False, attention_bias=False, qk_norm=True,
+                             layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+                             linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
+                             linear_num_value_heads=4, partial_rotary_factor=0.25, attn_output_gate=True, rms_norm_offset=True,
+                             num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
+                             norm_topk_prob=True),
     "qwen3.5-9b": dict(arch="qwen3_5", vocab_size=248320, hidden_size=4096, num_layers=32, num_heads=16, num_kv_heads=4, head_dim=256,
                        intermediate_size=12288, rope_theta=1e7, tie_word_embeddings=False, attention_bias=False, qk_norm=True,
                        layer_types=[("linear_attention" if (i + 1) % 4 else "full_attention") for i in range(32)],

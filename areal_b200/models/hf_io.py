@@ -39,9 +39,23 @@ def hf_to_native_plan(cfg: ModelConfig) -> dict[str, list[tuple[str, Optional[tu
         q_rows, k_rows = nq * D, nkv * D
         if cfg.layer_types:
             # hybrid stack: gated-delta-rule layers and gated full attention keep their own projections
-            I = cfg.intermediate_size
-            plan[p + "mlp.gate_up_proj"] = [(h + "mlp.gate_proj.weight", (0, I), None), (h + "mlp.up_proj.weight", (I, 2 * I), None)]
-            plan[p + "mlp.down_proj"] = [(h + "mlp.down_proj.weight", None, None)]
+            if cfg.layer_is_moe(i):
+                Is, Im = cfg.shared_expert_intermediate_size, cfg.moe_intermediate_size
+                plan[p + "mlp.router"] = [(h + "mlp.gate.weight", None, None)]
+                gu, dn = [], []
+                for e in range(cfg.num_experts):
+                    gu.append((h + f"mlp.experts.{e}.gate_proj.weight", (0, Im), e))
+                    gu.append((h + f"mlp.experts.{e}.up_proj.weight", (Im, 2 * Im), e))
+                    dn.append((h + f"mlp.experts.{e}.down_proj.weight", None, e))
+                plan[p + "mlp.w_gate_up"], plan[p + "mlp.w_down"] = gu, dn
+                plan[p + "mlp.shared_gate_up"] = [(h + "mlp.shared_expert.gate_proj.weight", (0, Is), None),
+                                                  (h + "mlp.shared_expert.up_proj.weight", (Is, 2 * Is), None)]
+                plan[p + "mlp.shared_down"] = [(h + "mlp.shared_expert.down_proj.weight", None, None)]
+                plan[p + "mlp.shared_expert_gate"] = [(h + "mlp.shared_expert_gate.weight", None, None)]
+            else:
+                I = cfg.intermediate_size
+                plan[p + "mlp.gate_up_proj"] = [(h + "mlp.gate_proj.weight", (0, I), None), (h + "mlp.up_proj.weight", (I, 2 * I), None)]
+                plan[p + "mlp.down_proj"] = [(h + "mlp.down_proj.weight", None, None)]
             if cfg.layer_is_linear(i):
                 la, nv = h + "linear_attn.", cfg.linear_num_value_heads
                 plan[p + "linear_attn.in_proj_qkv"] = [(la + "in_proj_qkv.weight", None, None)]

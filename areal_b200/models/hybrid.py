@@ -267,8 +267,11 @@ class HybridDecoderLayer(nn.Module):
         else:
             self.self_attn = GatedAttention(cfg, dtype, device)
         if cfg.layer_is_moe(idx):
-            raise NotImplementedError("mixture-of-experts MLPs in the hybrid stack")
-        self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device)
+            from .decoder import MoEMLP
+
+            self.mlp = MoEMLP(cfg, dtype, device)        # routed experts + sigmoid-gated shared expert (Qwen3.5-MoE)
+        else:
+            self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device)
 
     def forward(self, h, resid, pb, cos, sin, attn_fn=None):
         eps = self.cfg.rms_norm_eps

@@ -44,10 +44,20 @@ def _hf_model(family):
                                    linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=24, linear_num_key_heads=2,
                                    linear_num_value_heads=4)
         return tr.Qwen3_5ForCausalLM(cfg)
+    if family == "qwen3_5_moe":
+        if not hasattr(tr, "Qwen3_5MoeForCausalLM"):
+            pytest.skip("transformers without Qwen3.5-MoE")
+        c = {k: v for k, v in COMMON.items() if k != "intermediate_size"}
+        cfg = tr.Qwen3_5MoeTextConfig(**{**c, "num_hidden_layers": 4}, head_dim=32, tie_word_embeddings=False,
+                                      layer_types=["linear_attention", "full_attention", "linear_attention", "linear_attention"],
+                                      linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=24, linear_num_key_heads=2,
+                                      linear_num_value_heads=4, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                                      shared_expert_intermediate_size=96)
+        return tr.Qwen3_5MoeForCausalLM(cfg)
     raise ValueError(family)
 
 
-@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "qwen2_moe", "qwen3_5"])
+@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "qwen2_moe", "qwen3_5", "qwen3_5_moe"])
 def test_logits_match_hf(family):
     hf = _hf_model(family).float().eval()
     # make the parameters non-trivial where HF initialises constants (norm weights, biases)
