@@ -50,6 +50,7 @@ class ModelConfig:
     video_token_id: int = 151656
     vision_start_token_id: int = 151652
     mrope_section: list[int] = field(default_factory=list)
+    mrope_interleaved: bool = False         # Qwen3-VL: the three position streams alternate over the frequencies
     # hybrid linear / full attention stacks (Qwen3.5): per-layer token mixer, gated-delta-rule dimensions,
     # rotation of only the leading part of each head, sigmoid output gate on full attention, RMSNorm weights
     # stored as offsets from one
@@ -138,6 +139,20 @@ class ModelConfig:
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "qwen2")
         vl = None
+        if mt == "qwen3_vl":
+            vl = dict(d.get("vision_config") or {})
+            vl["model_type"] = mt
+            top = d
+            d = dict(d.get("text_config") or {})
+            for k in ("image_token_id", "video_token_id", "vision_start_token_id", "tie_word_embeddings"):
+                if k in top:
+                    d.setdefault(k, top[k])
+            rs = d.get("rope_parameters") or d.get("rope_scaling") or {}
+            d["_mrope_section"] = list(rs.get("mrope_section", [24, 20, 20]))
+            d["_mrope_interleaved"] = bool(rs.get("mrope_interleaved", True))
+            d.setdefault("rope_theta", rs.get("rope_theta", 5e6))
+            d["attention_bias"] = bool(d.get("attention_bias", False))
+            mt = "qwen3"
         if mt in ("qwen2_vl", "qwen2_5_vl"):
             # text fields sit at the top level (older checkpoints) or under ``text_config``
             vl = dict(d.get("vision_config") or {})
@@ -198,7 +213,7 @@ class ModelConfig:
             num_limited_groups=int(d.get("topk_group", d.get("num_limited_groups", 0)) or 0),
             router_bias_update_rate=float(d.get("router_bias_update_rate", 0.0) or 0.0),
             decoder_sparse_step=d.get("decoder_sparse_step", 1) or 1, mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
-            vision=vl, mrope_section=list(d.get("_mrope_section", [])),
+            vision=vl, mrope_section=list(d.get("_mrope_section", [])), mrope_interleaved=bool(d.get("_mrope_interleaved", False)),
             image_token_id=int(d.get("image_token_id", 151655)), video_token_id=int(d.get("video_token_id", 151656)),
             vision_start_token_id=int(d.get("vision_start_token_id", 151652)), **hybrid,
         )
@@ -225,6 +240,14 @@ class ModelConfig:
                      linear_num_key_heads=self.linear_num_key_heads, linear_num_value_heads=self.linear_num_value_heads,
                      rope_parameters=dict(rope_type="default", rope_theta=self.rope_theta, partial_rotary_factor=self.partial_rotary_factor))
             d.pop("rope_theta", None)
+        if self.is_vlm and self.vision.get("model_type") == "qwen3_vl":
+            text = {k: v for k, v in d.items() if k not in ("model_type", "architectures", "rope_theta")}
+            text.update(model_type="qwen3_vl_text", rope_parameters=dict(rope_type="default", rope_theta=self.rope_theta,
+                                                                         mrope_section=list(self.mrope_section), mrope_interleaved=True))
+            return dict(model_type="qwen3_vl", architectures=["Qwen3VLForConditionalGeneration"], text_config=text,
+                        vision_config=dict(self.vision), image_token_id=self.image_token_id, video_token_id=self.video_token_id,
+                        vision_start_token_id=self.vision_start_token_id, tie_word_embeddings=self.tie_word_embeddings,
+                        torch_dtype="bfloat16")
         if self.is_vlm:
             vmt = self.vision.get("model_type", "qwen2_vl")
             d.update(model_type=vmt, architectures=[{"qwen2_vl": "Qwen2VLForConditionalGeneration",
@@ -278,6 +301,13 @@ PRESETS = {
                        layer_types=[("linear_attention" if (i + 1) % 4 else "full_attention") for i in range(32)],
                        linear_conv_kernel_dim=4, linear_key_head_dim=128, linear_value_head_dim=128, linear_num_key_heads=16,
                        linear_num_value_heads=32, partial_rotary_factor=0.25, attn_output_gate=True, rms_norm_offset=True),
+    "tiny-qwen3-vl": dict(arch="qwen3", vocab_size=1024, hidden_size=256, num_layers=3, num_heads=4, num_kv_heads=2,
+                          head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False, attention_bias=False, qk_norm=True,
+                          image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, mrope_section=[12, 10, 10],
+                          mrope_interleaved=True,
+                          vision=dict(model_type="qwen3_vl", depth=3, hidden_size=64, num_heads=4, intermediate_size=128, in_channels=3,
+                                      patch_size=16, temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=256,
+                                      num_position_embeddings=64, deepstack_visual_indexes=[0, 1])),
     "tiny-qwen2-vl": dict(arch="qwen2", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
                           head_dim=64, intermediate_size=512, rope_theta=1e4, tie_word_embeddings=False, attention_bias=True,
                           image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, mrope_section=[8, 12, 12],

@@ -358,7 +358,7 @@ class CausalLM(nn.Module):
         return self._rope_cache[key]
 
     def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None, inputs_embeds: Optional[torch.Tensor] = None,
-                       rope: Optional[tuple] = None) -> torch.Tensor:
+                       rope: Optional[tuple] = None, deepstack: Optional[tuple] = None) -> torch.Tensor:
         """input_ids: [T] -> final normed hidden states [T, H]. ``inputs_embeds`` replaces the
         embedding lookup; ``rope = (cos, sin)`` replaces the position tables (rows are then
         selected by ``pb.position_ids`` exactly like the default tables)."""
@@ -371,6 +371,9 @@ class CausalLM(nn.Module):
                 h, resid = checkpoint(layer, h, resid, pb, cos, sin, fn, use_reentrant=False)
             else:
                 h, resid = layer(h, resid, pb, cos, sin, fn)
+            if deepstack is not None and i < len(deepstack[1]):
+                # deep-stack features of the image tower join the hidden state (= resid + h) after the first layers
+                h = h.index_add(0, deepstack[0], deepstack[1][i].to(h.dtype))
         if self.cfg.rms_norm_offset:
             from .hybrid import rmsnorm_offset
 

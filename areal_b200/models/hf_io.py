@@ -116,10 +116,15 @@ def hf_to_native_plan(cfg: ModelConfig) -> dict[str, list[tuple[str, Optional[tu
 def native_to_hf_tensors(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor]]) -> Iterator[tuple[str, torch.Tensor]]:
     """Splits native (fused) tensors into HF-named tensors (views; no copies)."""
     plan = hf_to_native_plan(cfg)
+    # checkpoints of the newer vision-language families nest the decoder and the tower under ``model.``
+    nested = cfg.is_vlm and cfg.vision.get("model_type") == "qwen3_vl"
     for name, t in named:
         if name not in plan:
             raise KeyError(f"no HF mapping for parameter '{name}'")
         for hf_name, rows, expert in plan[name]:
+            if nested:
+                hf_name = ("model." + hf_name if hf_name.startswith("visual.") else
+                           "model.language_model." + hf_name[len("model."):] if hf_name.startswith("model.") else hf_name)
             src = t if expert is None else t[expert]
             src = src if rows is None else src[rows[0]:rows[1]]
             yield hf_name, (src.unsqueeze(1) if hf_name.endswith("linear_attn.conv1d.weight") else src)

@@ -43,7 +43,7 @@ CLIP_STD = (0.26862954, 0.26130258, 0.27577711)
 
 @dataclass
 class VisionConfig:
-    arch: str = "qwen2_vl"              # qwen2_vl | qwen2_5_vl
+    arch: str = "qwen2_vl"              # qwen2_vl | qwen2_5_vl | qwen3_vl
     depth: int = 32
     embed_dim: int = 1280
     num_heads: int = 16
@@ -55,6 +55,11 @@ class VisionConfig:
     out_hidden_size: int = 3584
     window_size: int = 0                # pixels; 0 = full attention everywhere
     fullatt_block_indexes: list[int] = field(default_factory=list)
+    # qwen3_vl: learned position table (a square grid, bilinearly resampled to the image grid) and
+    # "deep stack" taps: the outputs of these blocks are merged and added to the hidden states of
+    # the first decoder layers at the image positions
+    num_position_embeddings: int = 0
+    deepstack_visual_indexes: list[int] = field(default_factory=list)
 
     @property
     def head_dim(self) -> int:
@@ -66,6 +71,13 @@ class VisionConfig:
 
     @classmethod
     def from_hf_dict(cls, d: dict, llm_hidden: int, arch: str) -> "VisionConfig":
+        if arch == "qwen3_vl":
+            return cls(arch=arch, depth=d.get("depth", 27), embed_dim=d.get("hidden_size", 1152), num_heads=d.get("num_heads", 16),
+                       mlp_hidden=d.get("intermediate_size", 4304), in_channels=d.get("in_channels", d.get("in_chans", 3)),
+                       patch_size=d.get("patch_size", 16), temporal_patch_size=d.get("temporal_patch_size", 2),
+                       spatial_merge_size=d.get("spatial_merge_size", 2), out_hidden_size=d.get("out_hidden_size", llm_hidden),
+                       num_position_embeddings=d.get("num_position_embeddings", 2304),
+                       deepstack_visual_indexes=list(d.get("deepstack_visual_indexes", [8, 16, 24])))
         if arch == "qwen2_5_vl":
             return cls(arch=arch, depth=d.get("depth", 32), embed_dim=d.get("hidden_size", 1280), num_heads=d.get("num_heads", 16),
                        mlp_hidden=d.get("intermediate_size", 3420), in_channels=d.get("in_chans", d.get("in_channels", 3)),
@@ -79,6 +91,12 @@ class VisionConfig:
                    spatial_merge_size=d.get("spatial_merge_size", 2), out_hidden_size=d.get("hidden_size", llm_hidden))
 
     def to_hf_dict(self) -> dict:
+        if self.arch == "qwen3_vl":
+            return dict(depth=self.depth, hidden_size=self.embed_dim, intermediate_size=self.mlp_hidden, num_heads=self.num_heads,
+                        in_channels=self.in_channels, patch_size=self.patch_size, temporal_patch_size=self.temporal_patch_size,
+                        spatial_merge_size=self.spatial_merge_size, out_hidden_size=self.out_hidden_size, hidden_act="gelu_pytorch_tanh",
+                        num_position_embeddings=self.num_position_embeddings, deepstack_visual_indexes=list(self.deepstack_visual_indexes),
+                        model_type="qwen3_vl")
         if self.arch == "qwen2_5_vl":
             return dict(depth=self.depth, hidden_size=self.embed_dim, intermediate_size=self.mlp_hidden, num_heads=self.num_heads,
                         in_chans=self.in_channels, patch_size=self.patch_size, temporal_patch_size=self.temporal_patch_size,
@@ -115,8 +133,9 @@ def preprocess_images(images: Sequence, cfg: Optional[VisionConfig] = None, min_
     merge-block order."""
     cfg = cfg or VisionConfig()
     P, m, Tp = cfg.patch_size, cfg.spatial_merge_size, cfg.temporal_patch_size
-    mean = np.asarray(CLIP_MEAN, dtype=np.float32).reshape(1, 1, 3)
-    std = np.asarray(CLIP_STD, dtype=np.float32).reshape(1, 1, 3)
+    # Qwen3-VL checkpoints were trained with 0.5 / 0.5 normalisation, the earlier families with the CLIP statistics
+    mean = np.asarray((0.5, 0.5, 0.5) if cfg.arch == "qwen3_vl" else CLIP_MEAN, dtype=np.float32).reshape(1, 1, 3)
+    std = np.asarray((0.5, 0.5, 0.5) if cfg.arch == "qwen3_vl" else CLIP_STD, dtype=np.float32).reshape(1, 1, 3)
     outs, grids = [], []
     for im in images:
         if not isinstance(im, np.ndarray):
@@ -189,14 +208,23 @@ def mrope_position_ids(input_ids: torch.Tensor, grid_thw: Optional[torch.Tensor]
     return pos, nxt - L
 
 
-def mrope_tables(pos3: torch.Tensor, head_dim: int, theta: float, sections: Sequence[int], device) -> tuple[torch.Tensor, torch.Tensor]:
+def mrope_tables(pos3: torch.Tensor, head_dim: int, theta: float, sections: Sequence[int], device,
+                 interleaved: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-token cos / sin rows ``[T, head_dim / 2]``: frequency ``f`` turns with the temporal,
-    height or width stream according to the section it falls in (``sum(sections) = head_dim / 2``)."""
+    height or width stream according to the section it falls in (``sum(sections) = head_dim / 2``).
+    ``interleaved`` (Qwen3-VL): the streams alternate t, h, w, t, h, w, ... over the first
+    ``3 * sections[1]`` (height) / ``3 * sections[2]`` (width) frequencies instead of forming three
+    contiguous runs; everything else turns with the temporal stream."""
     half = head_dim // 2
     if sum(sections) != half:
         raise ValueError(f"mrope sections {list(sections)} must sum to {half}")
     inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64, device=device) * 2 / head_dim))
-    which = torch.repeat_interleave(torch.arange(3, device=device), torch.tensor(list(sections), device=device))
+    if interleaved:
+        which = torch.zeros(half, dtype=torch.long, device=device)
+        which[1:3 * sections[1]:3] = 1
+        which[2:3 * sections[2]:3] = 2
+    else:
+        which = torch.repeat_interleave(torch.arange(3, device=device), torch.tensor(list(sections), device=device))
     p = pos3.to(device=device, dtype=torch.float64)[which]                        # [half, T]
     ang = (p * inv[:, None]).t()
     return ang.cos().float().contiguous(), ang.sin().float().contiguous()
@@ -239,9 +267,10 @@ class _PatchEmbed(nn.Module):
         self.proj = nn.Module()
         self.proj.weight = nn.Parameter(torch.empty(cfg.embed_dim, cfg.in_channels, cfg.temporal_patch_size, cfg.patch_size,
                                                     cfg.patch_size, dtype=dtype, device=device))
+        self.proj.bias = nn.Parameter(torch.zeros(cfg.embed_dim, dtype=dtype, device=device)) if cfg.arch == "qwen3_vl" else None
 
     def forward(self, x):
-        return F.linear(x.to(self.proj.weight.dtype), self.proj.weight.view(self.proj.weight.shape[0], -1))
+        return F.linear(x.to(self.proj.weight.dtype), self.proj.weight.view(self.proj.weight.shape[0], -1), self.proj.bias)
 
 
 class _VisionAttention(nn.Module):
@@ -272,7 +301,11 @@ class _VisionMLP(nn.Module):
     def __init__(self, cfg: VisionConfig, dtype, device):
         super().__init__()
         self.gated = cfg.arch == "qwen2_5_vl"
-        if self.gated:
+        self.tanh_gelu = cfg.arch == "qwen3_vl"
+        if self.tanh_gelu:
+            self.linear_fc1 = _Lin(cfg.embed_dim, cfg.mlp_hidden, dtype, device)
+            self.linear_fc2 = _Lin(cfg.mlp_hidden, cfg.embed_dim, dtype, device)
+        elif self.gated:
             self.gate_proj = _Lin(cfg.embed_dim, cfg.mlp_hidden, dtype, device)
             self.up_proj = _Lin(cfg.embed_dim, cfg.mlp_hidden, dtype, device)
             self.down_proj = _Lin(cfg.mlp_hidden, cfg.embed_dim, dtype, device)
@@ -281,6 +314,8 @@ class _VisionMLP(nn.Module):
             self.fc2 = _Lin(cfg.mlp_hidden, cfg.embed_dim, dtype, device)
 
     def forward(self, x):
+        if self.tanh_gelu:
+            return self.linear_fc2(F.gelu(self.linear_fc1(x), approximate="tanh"))
         if self.gated:
             return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
         h = self.fc1(x)
@@ -313,6 +348,23 @@ class _Merger(nn.Module):
         return self.mlp[2](self.mlp[1](self.mlp[0](x)))
 
 
+class _Merger3(nn.Module):
+    """Qwen3-VL merger: LayerNorm over one patch (main merger) or over the whole merge unit
+    (deep-stack mergers), then a two-layer GELU MLP on the unit."""
+
+    def __init__(self, cfg: VisionConfig, post_shuffle: bool, dtype, device):
+        super().__init__()
+        self.unit = cfg.embed_dim * cfg.spatial_merge_size ** 2
+        self.post_shuffle = post_shuffle
+        self.norm = _Norm(self.unit if post_shuffle else cfg.embed_dim, False, dtype, device)
+        self.linear_fc1 = _Lin(self.unit, self.unit, dtype, device)
+        self.linear_fc2 = _Lin(self.unit, cfg.out_hidden_size, dtype, device)
+
+    def forward(self, x):
+        x = self.norm(x.view(-1, self.unit) if self.post_shuffle else x).view(-1, self.unit)
+        return self.linear_fc2(F.gelu(self.linear_fc1(x)))
+
+
 class VisionTower(nn.Module):
     """``forward(pixel_values [N, patch_dim], grid_thw [n, 3]) -> [N / m^2, out_hidden_size]``."""
 
@@ -321,7 +373,13 @@ class VisionTower(nn.Module):
         self.cfg = cfg
         self.patch_embed = _PatchEmbed(cfg, dtype, device)
         self.blocks = nn.ModuleList([_VisionBlock(cfg, dtype, device) for _ in range(cfg.depth)])
-        self.merger = _Merger(cfg, dtype, device)
+        if cfg.arch == "qwen3_vl":
+            self.pos_embed = nn.Module()
+            self.pos_embed.weight = nn.Parameter(torch.empty(cfg.num_position_embeddings, cfg.embed_dim, dtype=dtype, device=device))
+            self.merger = _Merger3(cfg, False, dtype, device)
+            self.deepstack_merger_list = nn.ModuleList([_Merger3(cfg, True, dtype, device) for _ in cfg.deepstack_visual_indexes])
+        else:
+            self.merger = _Merger(cfg, dtype, device)
         gen = None
         if seed is not None:
             gen = torch.Generator(device=device)
@@ -330,7 +388,7 @@ class VisionTower(nn.Module):
             for n, p in self.named_parameters():
                 if n.endswith("bias"):
                     p.zero_()
-                elif "norm" in n or "ln_q" in n:
+                elif ("norm" in n or "ln_q" in n) and n.endswith("weight"):
                     p.fill_(1.0)
                 else:
                     p.copy_((torch.randn(p.shape, device=p.device, dtype=torch.float32, generator=gen) * init_std).to(p.dtype))
@@ -367,11 +425,33 @@ class VisionTower(nn.Module):
             base += t * lh * lw
         return torch.cat(order), bounds
 
-    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+    def _interpolated_pos_embed(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """Rows of the learned ``side x side`` position table resampled bilinearly to every image's
+        ``h x w`` patch grid (corners aligned), repeated per frame, in merge-block order: ``[N, E]``."""
+        cfg, m = self.cfg, self.cfg.spatial_merge_size
+        table = self.pos_embed.weight
+        side = int(cfg.num_position_embeddings ** 0.5)
+        out = []
+        for t, h, w in grid_thw.tolist():
+            hi, wi = torch.linspace(0, side - 1, h), torch.linspace(0, side - 1, w)
+            h0, w0 = hi.int(), wi.int()
+            h1, w1 = (h0 + 1).clip(max=side - 1), (w0 + 1).clip(max=side - 1)
+            dh, dw = (hi - h0)[:, None], (wi - w0)[None, :]
+            acc = 0
+            for hh, ww, wt in ((h0, w0, (1 - dh) * (1 - dw)), (h0, w1, (1 - dh) * dw), (h1, w0, dh * (1 - dw)), (h1, w1, dh * dw)):
+                idx = (hh[:, None] * side + ww[None, :]).reshape(-1).long().to(table.device)
+                acc = acc + table[idx] * wt.reshape(-1, 1).to(device=table.device, dtype=table.dtype)
+            pe = acc.repeat(t, 1).view(t, h // m, m, w // m, m, -1).permute(0, 1, 3, 2, 4, 5).reshape(t * h * w, -1)
+            out.append(pe)
+        return torch.cat(out, 0)
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor, return_deepstack: bool = False):
         cfg = self.cfg
         dev = self.patch_embed.proj.weight.device
         grid_thw = grid_thw.cpu().long()
         x = self.patch_embed(pixel_values.to(dev))
+        if cfg.arch == "qwen3_vl":
+            x = x + self._interpolated_pos_embed(grid_thw)
         N, m2 = x.shape[0], cfg.spatial_merge_size ** 2
         rp = self._rot_pos(grid_thw)
         quarter = cfg.head_dim // 4
@@ -390,26 +470,36 @@ class VisionTower(nn.Module):
             x = x.view(N // m2, m2, -1)[widx].reshape(N, -1)
             cos = cos.view(N // m2, m2, -1)[widx].reshape(N, -1)
             sin = sin.view(N // m2, m2, -1)[widx].reshape(N, -1)
+        taps = []
         for i, blk in enumerate(self.blocks):
             bounds = win_bounds if (windowed and i not in cfg.fullatt_block_indexes) else frame_bounds
             x = blk(x, cos, sin, bounds)
+            if i in cfg.deepstack_visual_indexes:
+                taps.append(self.deepstack_merger_list[cfg.deepstack_visual_indexes.index(i)](x))
         y = self.merger(x)
         if windowed:
             y = y[torch.argsort(widx)]
-        return y
+        return (y, taps) if return_deepstack else y
 
 
 def vision_param_names(cfg: VisionConfig) -> list[str]:
     """Parameter names of the tower (identical to the HF checkpoint names after ``visual.``)."""
     names = ["patch_embed.proj.weight"]
     rms = cfg.arch == "qwen2_5_vl"
+    v3 = cfg.arch == "qwen3_vl"
+    if v3:
+        names += ["patch_embed.proj.bias", "pos_embed.weight"]
     for i in range(cfg.depth):
         b = f"blocks.{i}."
         names += [b + "norm1.weight", b + "norm2.weight"] + ([] if rms else [b + "norm1.bias", b + "norm2.bias"])
         names += [b + "attn.qkv.weight", b + "attn.qkv.bias", b + "attn.proj.weight", b + "attn.proj.bias"]
-        mlp = ["gate_proj", "up_proj", "down_proj"] if rms else ["fc1", "fc2"]
+        mlp = ["linear_fc1", "linear_fc2"] if v3 else (["gate_proj", "up_proj", "down_proj"] if rms else ["fc1", "fc2"])
         for n in mlp:
             names += [b + f"mlp.{n}.weight", b + f"mlp.{n}.bias"]
+    if v3:
+        for pre in ["merger."] + [f"deepstack_merger_list.{j}." for j in range(len(cfg.deepstack_visual_indexes))]:
+            names += [pre + n for n in ("norm.weight", "norm.bias", "linear_fc1.weight", "linear_fc1.bias", "linear_fc2.weight", "linear_fc2.bias")]
+        return names
     names += ["merger.ln_q.weight"] + ([] if rms else ["merger.ln_q.bias"])
     names += ["merger.mlp.0.weight", "merger.mlp.0.bias", "merger.mlp.2.weight", "merger.mlp.2.bias"]
     return names

@@ -79,8 +79,13 @@ class VisionLanguageModel(CausalLM):
             img += k
         return pos, deltas, torch.tensor(where, dtype=torch.long)
 
-    def embed_multimodal(self, input_ids: torch.Tensor, mm: dict[str, Any], positions: Optional[torch.Tensor] = None) -> torch.Tensor:
-        feats = self.visual(mm["pixel_values"].to(self.embed_tokens.dtype), mm["image_grid_thw"])
+    def embed_multimodal(self, input_ids: torch.Tensor, mm: dict[str, Any], positions: Optional[torch.Tensor] = None,
+                         with_deepstack: bool = False):
+        taps = None
+        if self.vcfg.deepstack_visual_indexes:
+            feats, taps = self.visual(mm["pixel_values"].to(self.embed_tokens.dtype), mm["image_grid_thw"], return_deepstack=True)
+        else:
+            feats = self.visual(mm["pixel_values"].to(self.embed_tokens.dtype), mm["image_grid_thw"])
         h = OF.embedding(input_ids, self.embed_tokens)
         if positions is None:
             mask = (input_ids == self.cfg.image_token_id) | (input_ids == self.cfg.video_token_id)
@@ -88,7 +93,8 @@ class VisionLanguageModel(CausalLM):
         positions = positions.to(input_ids.device)
         if positions.numel() != feats.shape[0]:
             raise ValueError(f"{positions.numel()} placeholder tokens for {feats.shape[0]} image features")
-        return h.index_copy(0, positions, feats.to(h.dtype))
+        out = h.index_copy(0, positions, feats.to(h.dtype))
+        return (out, (positions, taps) if taps else None) if with_deepstack else out
 
     def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None, mm: Optional[dict[str, Any]] = None, **kw) -> torch.Tensor:
         if mm is None or mm.get("pixel_values") is None or mm["pixel_values"].numel() == 0:
@@ -100,8 +106,8 @@ class VisionLanguageModel(CausalLM):
             cu = pb.cu_seqlens.tolist()
             pos3, _, where = self.packed_mrope(input_ids.cpu().long(), cu, mm["image_grid_thw"].cpu().long(), mm.get("images_per_seq"))
         sections = self.cfg.mrope_section or [self.cfg.head_dim // 2, 0, 0]
-        cos, sin = mrope_tables(pos3, self.cfg.head_dim, self.cfg.rope_theta, sections, input_ids.device)
+        cos, sin = mrope_tables(pos3, self.cfg.head_dim, self.cfg.rope_theta, sections, input_ids.device, self.cfg.mrope_interleaved)
         pb2 = copy.copy(pb)
         pb2.position_ids = torch.arange(T, dtype=torch.int32, device=input_ids.device)   # row t of the per-token tables
-        embeds = self.embed_multimodal(input_ids, mm, where)
-        return super().forward_hidden(input_ids, pb2, attn_fns, inputs_embeds=embeds, rope=(cos, sin))
+        embeds, deep = self.embed_multimodal(input_ids, mm, where, with_deepstack=True)
+        return super().forward_hidden(input_ids, pb2, attn_fns, inputs_embeds=embeds, rope=(cos, sin), deepstack=deep)

@@ -192,3 +192,56 @@ def test_vision_rlvr_workflow_rollout_cpu():
         assert torch.equal(out["input_ids"][0], out["input_ids"][1])
     finally:
         eng.destroy()
+
+
+def test_qwen3_vl_matches_hf():
+    """Qwen3-VL: learned position table resampled to the patch grid, tanh-GELU tower, deep-stack
+    features added after the first decoder layers, interleaved M-RoPE."""
+    tr = pytest.importorskip("transformers")
+    if not hasattr(tr, "Qwen3VLForConditionalGeneration"):
+        pytest.skip("transformers without Qwen3-VL")
+    torch.manual_seed(0)
+    text = dict(vocab_size=1024, hidden_size=256, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                intermediate_size=512, max_position_embeddings=4096, rms_norm_eps=1e-6,
+                rope_parameters=dict(rope_type="default", rope_theta=1e4, mrope_section=[12, 10, 10], mrope_interleaved=True))
+    vis = dict(depth=3, hidden_size=64, num_heads=4, intermediate_size=128, in_channels=3, patch_size=16, temporal_patch_size=2,
+               spatial_merge_size=2, out_hidden_size=256, num_position_embeddings=64, deepstack_visual_indexes=[0, 2])
+    hf = tr.Qwen3VLForConditionalGeneration(tr.Qwen3VLConfig(text_config=text, vision_config=vis, tie_word_embeddings=False, **IDS)).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    with tempfile.TemporaryDirectory() as d:
+        hf.save_pretrained(d, safe_serialization=True)
+        mc = ModelConfig.from_pretrained(d)
+        assert mc.is_vlm and mc.mrope_interleaved and mc.qk_norm and mc.vision_config().deepstack_visual_indexes == [0, 2]
+        m = build_model(mc, dtype=torch.float32, device="cpu", seed=0)
+        hf_io.load_model_hf(m, d)
+        with tempfile.TemporaryDirectory() as d2:
+            hf_io.save_model_hf(m, d2)
+            mc.save_pretrained(d2)
+            back = tr.Qwen3VLForConditionalGeneration.from_pretrained(d2, torch_dtype=torch.float32)
+            ref_sd = hf.state_dict()
+            for k, v in back.state_dict().items():
+                assert torch.equal(ref_sd[k], v), k
+    m.eval()
+    px, grid = preprocess_images(_images(), m.vcfg, min_pixels=32 * 32, max_pixels=32 * 32 * 30)
+    nt = num_image_tokens(grid)
+    seq = [5, 6, 1002] + [1000] * nt[0] + [7, 8, 1002] + [1000] * nt[1] + [9, 10, 11]
+    ids = torch.tensor(seq)
+    with torch.no_grad():
+        pos3, _, where = m.packed_mrope(ids, [0, len(seq)], grid)
+        kw = dict(input_ids=ids[None], pixel_values=px, image_grid_thw=grid, attention_mask=torch.ones(1, len(seq), dtype=torch.long),
+                  position_ids=pos3[:, None, :])
+        try:
+            ref = hf(**kw, mm_token_type_ids=(ids == 1000).long()[None]).logits[0]
+        except TypeError:
+            ref = hf(**kw).logits[0]
+        pb = PackedBatch(torch.tensor([0, len(seq)], dtype=torch.int32), torch.arange(len(seq)), len(seq), len(seq))
+        out = m.logits(m.forward_hidden(ids, pb, mm={"pixel_values": px, "image_grid_thw": grid}))
+        # text only: the three streams coincide
+        t_ids = torch.tensor([5, 6, 7, 8, 9, 10])
+        ref_t = hf(input_ids=t_ids[None]).logits[0]
+        out_t = m.logits(m(t_ids, torch.tensor([0, 6], dtype=torch.int32), max_seqlen=6))
+    assert (out - ref).abs().max().item() < 1e-4, (out - ref).abs().max().item()
+    assert (out_t - ref_t).abs().max().item() < 1e-4
