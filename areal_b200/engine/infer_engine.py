@@ -71,6 +71,7 @@ class _Seq:
     stop_window: int = 16                  # tokens decoded per check
     mm: Any = None                         # vision-language request: {"pixel_values", "image_grid_thw"}
     rope_delta: int = 0                    # M-RoPE: rotary position of token i (after the prompt) = i + rope_delta
+    hstate: Any = None                     # recurrent-state models: models.hybrid.SequenceState once the prompt is absorbed
 
 
 class PagedKVCache:
@@ -173,7 +174,9 @@ class NativeInferenceEngine(InferenceEngine):
             for p in self.model.parameters():
                 p.requires_grad_(False)
         # Layers with a recurrent state (gated delta rule) have no paged-cache decode kernel: such models
-        # generate by re-running the packed forward over every running sequence each step.
+        # absorb a prompt with one packed forward that also returns the per-sequence state (rule state,
+        # convolution tail, keys / values of the full-attention layers) and then advance one token per
+        # step on that state (``_step_recurrent``).
         self._recompute_decode = bool(getattr(self.model_config, "is_hybrid", False))
         if self.device.type == "cuda" and not self._recompute_decode:
             self._init_cuda_state()
@@ -485,13 +488,13 @@ class NativeInferenceEngine(InferenceEngine):
                 self._idle.clear()
                 if self.device.type == "cuda" and self._recompute_decode:
                     with torch.cuda.stream(self.stream), torch.no_grad():
-                        self._step_cpu()
+                        self._step_recurrent()
                 elif self.device.type == "cuda":
                     with torch.cuda.stream(self.stream), torch.no_grad():
                         self._step_cuda()
                 else:
                     with torch.no_grad():
-                        self._step_cpu()
+                        self._step_recurrent() if self._recompute_decode else self._step_cpu()
         except BaseException as e:  # surface to waiting clients
             import traceback
 
@@ -608,6 +611,43 @@ class NativeInferenceEngine(InferenceEngine):
         for i, s in enumerate(batch):
             tok, lp = self._sample_cpu(logits[i], s)
             self._accept_token(s, tok, lp, done)
+        self._retire(done)
+
+    def _step_recurrent(self):
+        """Models with carried state: new sequences are absorbed by one packed forward, running ones
+        advance by one token on their state; both groups sample from the last position."""
+        from ..models.hybrid import decode_states, prefill_states
+
+        with self._lock:
+            while self._waiting and len(self._running) < self.icfg.max_running_requests:
+                self._running.append(self._waiting.popleft())
+            batch = list(self._running)
+        if not batch:
+            return
+        fresh = [s for s in batch if s.hstate is None]
+        going = [s for s in batch if s.hstate is not None]
+        rows, order = [], []
+        if fresh:
+            lens = [len(s.tokens) for s in fresh]
+            ids = torch.tensor([t for s in fresh for t in s.tokens], dtype=torch.long).to(self.device)
+            cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32).to(self.device)
+            hidden, states = prefill_states(self.model, ids, cu, max(lens))
+            for s, st in zip(fresh, states):
+                s.hstate = st
+            rows.append(hidden[(cu[1:] - 1).long()])
+            order += fresh
+        if going:
+            toks = torch.tensor([s.tokens[-1] for s in going], dtype=torch.long).to(self.device)
+            rows.append(decode_states(self.model, toks, [s.hstate for s in going]))
+            order += going
+        logits = self.model.logits(torch.cat(rows, 0)).float().cpu()
+        self._step += 1
+        done = []
+        for i, s in enumerate(order):
+            tok, lp = self._sample_cpu(logits[i], s)
+            self._accept_token(s, tok, lp, done)
+        for s, _ in done:
+            s.hstate = None
         self._retire(done)
 
     def _sample_cpu(self, logits: torch.Tensor, s: _Seq):

@@ -177,6 +177,33 @@ class GatedDeltaNet(nn.Module):
         self.norm = mk(self.dv)
         self.out_proj = mk(H, self.value_dim)
 
+    capture = None      # a list: forward() appends (pre-convolution projections [T, C], final states [B, nv, dk, dv])
+
+    def _inputs(self, x: torch.Tensor):
+        """Projections of ``x`` [T, H]: pre-convolution q|k|v, output gate z, write strength beta, log decay g."""
+        ba = F.linear(x, self.in_proj_ba).float()                 # 2 * nv columns: too narrow for the tiled GEMM
+        beta = ba[:, : self.nv].sigmoid()
+        g = -self.A_log.float().exp() * F.softplus(ba[:, self.nv:] + self.dt_bias.float())
+        return OF.linear(x, self.in_proj_qkv), OF.linear(x, self.in_proj_z), beta, g
+
+    def _heads(self, mixed: torch.Tensor):
+        """Post-convolution q|k|v [T, C] -> unit-norm q, k [T, nv, dk] and v [T, nv, dv] (fp32)."""
+        T = mixed.shape[0]
+        q, k, v = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        q = l2norm(q.reshape(T, self.nk, self.dk))
+        k = l2norm(k.reshape(T, self.nk, self.dk))
+        rep = self.nv // self.nk
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
+        return q, k, v.reshape(T, self.nv, self.dv).float()
+
+    def _output(self, o: torch.Tensor, z: torch.Tensor, dtype) -> torch.Tensor:
+        """Per-head RMSNorm of the rule's output [T, nv, dv] (fp32), gate by silu(z), project back."""
+        T = o.shape[0]
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps)
+        o = (self.norm.float() * o.to(dtype).float()) * F.silu(z.reshape(T, self.nv, self.dv).float())
+        return OF.linear(o.to(dtype).reshape(T, self.value_dim), self.out_proj)
+
     def forward(self, x: torch.Tensor, pb) -> torch.Tensor:
         T = x.shape[0]
         max_len = int(pb.max_seqlen) or int((pb.cu_seqlens[1:] - pb.cu_seqlens[:-1]).max())
@@ -186,27 +213,27 @@ class GatedDeltaNet(nn.Module):
             idx = (key, pad_index(pb.cu_seqlens, T, max_len))
             pb._pad_index = idx
         gather, scatter, pis = idx[1]
-        mixed = causal_conv_packed(OF.linear(x, self.in_proj_qkv), self.conv1d, pis)
-        z = OF.linear(x, self.in_proj_z)
-        ba = F.linear(x, self.in_proj_ba).float()                 # 2 * nv columns: too narrow for the tiled GEMM
-        beta = ba[:, : self.nv].sigmoid()
-        g = -self.A_log.float().exp() * F.softplus(ba[:, self.nv:] + self.dt_bias.float())
-        q, k, v = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
-        q = l2norm(q.reshape(T, self.nk, self.dk))
-        k = l2norm(k.reshape(T, self.nk, self.dk))
-        v = v.reshape(T, self.nv, self.dv).float()
-        rep = self.nv // self.nk
-        if rep > 1:
-            q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
+        pre, z, beta, g = self._inputs(x)
+        q, k, v = self._heads(causal_conv_packed(pre, self.conv1d, pis))
 
         def padded(t):                                            # [T, ...] -> [B, max_len, ...]
             zero = torch.zeros((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
             return torch.cat([t, zero], 0)[gather]
-        o, _ = gated_delta_rule_chunked(padded(q), padded(k), padded(v), padded(g), padded(beta))
-        o = o.reshape(-1, self.nv, self.dv)[scatter]              # back to [T, nv, dv], fp32
-        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps)
-        o = (self.norm.float() * o.to(x.dtype).float()) * F.silu(z.reshape(T, self.nv, self.dv).float())
-        return OF.linear(o.to(x.dtype).reshape(T, self.value_dim), self.out_proj)
+        # rows past a sequence's end carry k = 0 and beta = 0: they leave its state untouched
+        o, S = gated_delta_rule_chunked(padded(q), padded(k), padded(v), padded(g), padded(beta))
+        if self.capture is not None:
+            self.capture.append((pre, S))
+        return self._output(o.reshape(-1, self.nv, self.dv)[scatter], z, x.dtype)
+
+    def step(self, x: torch.Tensor, conv_state: torch.Tensor, S: torch.Tensor):
+        """One new token per sequence: x [B, H], conv_state [B, K-1, C] (the last pre-convolution
+        rows), S [B, nv, dk, dv]. Returns (y [B, H], new conv_state, new S)."""
+        pre, z, beta, g = self._inputs(x)
+        window = torch.cat([conv_state.to(pre.dtype), pre[:, None, :]], dim=1)                # [B, K, C]
+        mixed = F.silu((window.float() * self.conv1d.float().t()[None]).sum(1)).to(x.dtype)
+        q, k, v = self._heads(mixed)
+        o, S = gated_delta_rule_recurrent(q[:, None], k[:, None], v[:, None], g[:, None], beta[:, None], S)
+        return self._output(o[:, 0], z, x.dtype), window[:, 1:], S
 
 
 class GatedAttention(nn.Module):
@@ -224,7 +251,9 @@ class GatedAttention(nn.Module):
         self.q_norm = nn.Parameter(torch.zeros(D, dtype=dtype, device=device))
         self.k_norm = nn.Parameter(torch.zeros(D, dtype=dtype, device=device))
 
-    def forward(self, x: torch.Tensor, pb, cos, sin, attn_fn=None) -> torch.Tensor:
+    capture = None      # a list: forward() appends (k [T, nkv, D] after norm and rotation, v [T, nkv, D])
+
+    def _qkv(self, x: torch.Tensor, positions, cos, sin):
         T, D, nq, nkv, eps = x.shape[0], self.D, self.nq, self.nkv, self.cfg.rms_norm_eps
         qg = OF.linear(x, self.q_proj).view(T, nq, 2 * D)
         q, gate = qg[..., :D], qg[..., D:].reshape(T, nq * D)
@@ -233,8 +262,29 @@ class GatedAttention(nn.Module):
         q, _ = rmsnorm_offset(q, self.q_norm, eps)
         k, _ = rmsnorm_offset(k, self.k_norm, eps)
         rd = self.cfg.rotary_dim
-        q = partial_rope(q, pb.position_ids, cos, sin, rd).to(x.dtype)
-        k = partial_rope(k, pb.position_ids, cos, sin, rd).to(x.dtype)
+        q = partial_rope(q, positions, cos, sin, rd).to(x.dtype)
+        k = partial_rope(k, positions, cos, sin, rd).to(x.dtype)
+        return q, k, v, gate
+
+    def step(self, x: torch.Tensor, positions, cos, sin, ks: list, vs: list):
+        """One new token per sequence: x [B, H]; ``ks[i]`` / ``vs[i]`` [L_i, nkv, D] are sequence
+        i's cached keys / values. Returns (y [B, H], new keys [B, nkv, D], new values)."""
+        B, D, nq = x.shape[0], self.D, self.nq
+        q, k, v, gate = self._qkv(x, positions, cos, sin)
+        rep = nq // self.nkv
+        outs = []
+        for i in range(B):
+            K = torch.cat([ks[i], k[i:i + 1]], 0).transpose(0, 1).repeat_interleave(rep, dim=0)      # [nq, L+1, D]
+            V = torch.cat([vs[i], v[i:i + 1]], 0).transpose(0, 1).repeat_interleave(rep, dim=0)
+            outs.append(F.scaled_dot_product_attention(q[i][None, :, None, :], K[None], V[None], scale=1.0 / math.sqrt(D))[0, :, 0])
+        o = torch.stack(outs, 0).reshape(B, nq * D) * torch.sigmoid(gate.float()).to(x.dtype)
+        return OF.linear(o, self.o_proj), k, v
+
+    def forward(self, x: torch.Tensor, pb, cos, sin, attn_fn=None) -> torch.Tensor:
+        T, D, nq, nkv = x.shape[0], self.D, self.nq, self.nkv
+        q, k, v, gate = self._qkv(x, pb.position_ids, cos, sin)
+        if self.capture is not None:
+            self.capture.append((k, v))
         scale = 1.0 / math.sqrt(D)
         if attn_fn is not None:
             o = attn_fn(q, k, v)
@@ -294,3 +344,79 @@ def init_hybrid_parameters(model, gen: Optional[torch.Generator] = None) -> None
             p.copy_(a.clamp_min(1e-3).log().to(p.dtype))
         elif name.endswith("norm") or name.endswith("layernorm"):
             p.zero_()
+
+
+# ----------------------------------------------------------------------------- generation with carried state
+class SequenceState:
+    """What one sequence carries between decode steps: per linear layer the last ``K - 1``
+    pre-convolution rows and the ``nv x dk x dv`` rule state, per full-attention layer its keys and
+    values. ``length`` = tokens absorbed so far (the rotary position of the next token)."""
+
+    __slots__ = ("layers", "length")
+
+    def __init__(self, layers: list, length: int):
+        self.layers, self.length = layers, length
+
+
+@torch.no_grad()
+def prefill_states(model, input_ids: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int):
+    """One packed forward over whole sequences that also returns every sequence's carried state:
+    ``(hidden [T, H], [SequenceState])``."""
+    mixers = [(l.linear_attn if l.is_linear else l.self_attn) for l in model.layers]
+    for mx in mixers:
+        mx.capture = []
+    try:
+        hidden = model(input_ids, cu_seqlens, max_seqlen=max_seqlen)
+        caps = [mx.capture[0] for mx in mixers]
+    finally:
+        for mx in mixers:
+            mx.capture = None
+    cu = cu_seqlens.tolist()
+    states = []
+    for si, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+        per_layer = []
+        for layer, cap in zip(model.layers, caps):
+            if layer.is_linear:
+                pre, S = cap
+                keep = layer.linear_attn.conv1d.shape[1] - 1
+                tail = pre[max(a, b - keep):b]
+                if tail.shape[0] < keep:
+                    tail = torch.cat([tail.new_zeros(keep - tail.shape[0], tail.shape[1]), tail], 0)
+                per_layer.append((tail.clone(), S[si].clone()))
+            else:
+                k, v = cap
+                per_layer.append((k[a:b].clone(), v[a:b].clone()))
+        states.append(SequenceState(per_layer, b - a))
+    return hidden, states
+
+
+@torch.no_grad()
+def decode_states(model, tokens: torch.Tensor, states: list) -> torch.Tensor:
+    """Absorbs one new token per sequence (``tokens`` [B]) into ``states`` (updated in place) and
+    returns the final normed hidden states [B, H]: constant work per token in the linear layers, one
+    attention row in the full layers."""
+    cfg = model.cfg
+    dev = tokens.device
+    pos = torch.tensor([st.length for st in states], dtype=torch.int32, device=dev)
+    cos, sin = model.rope(dev, max(cfg.max_position_embeddings, int(pos.max()) + 2))
+    h = OF.embedding(tokens, model.embed_tokens)
+    resid = None
+    eps = cfg.rms_norm_eps
+    for li, layer in enumerate(model.layers):
+        x, resid = rmsnorm_offset(h, layer.input_layernorm, eps, resid)
+        if layer.is_linear:
+            conv = torch.stack([st.layers[li][0] for st in states], 0)
+            S = torch.stack([st.layers[li][1] for st in states], 0)
+            h, conv, S = layer.linear_attn.step(x, conv, S)
+            for i, st in enumerate(states):
+                st.layers[li] = (conv[i], S[i])
+        else:
+            h, k, v = layer.self_attn.step(x, pos, cos, sin, [st.layers[li][0] for st in states], [st.layers[li][1] for st in states])
+            for i, st in enumerate(states):
+                st.layers[li] = (torch.cat([st.layers[li][0], k[i:i + 1]], 0), torch.cat([st.layers[li][1], v[i:i + 1]], 0))
+        x, resid = rmsnorm_offset(h, layer.post_attention_layernorm, eps, resid)
+        h = layer.mlp(x)
+    for st in states:
+        st.length += 1
+    out, _ = rmsnorm_offset(h, model.norm, eps, resid)
+    return out

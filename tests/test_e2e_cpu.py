@@ -297,3 +297,33 @@ def test_ppo_trainer_with_model_parallel_actor(tmp_path, backend, model, port):
                        capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("PARALLEL_TRAINER_OK") == 2
+
+
+def test_hybrid_rollout_on_carried_state_matches_recompute():
+    """The rollout engine advances linear-attention models on per-sequence state (rule state,
+    convolution tail, keys / values of the full layers); greedy generations must equal those of
+    the path that re-runs the whole packed forward every step."""
+    import asyncio
+
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.api.cli_args import NativeInferConfig
+    from areal_b200.engine.infer_engine import NativeInferenceEngine
+
+    mc = preset("tiny-qwen3.5", vocab_size=64)
+    outs = {}
+    for mode in ("state", "recompute"):
+        eng = NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=3, context_length=128), model_config=mc)
+        if mode == "recompute":
+            eng._step_recurrent = eng._step_cpu
+        eng.initialize(device="cpu", start_executor=False, seed=5)
+        g = GenerationHyperparameters(n_samples=1, max_new_tokens=12, max_tokens=100, greedy=True, ignore_eos=True)
+
+        async def run():
+            reqs = [ModelRequest(rid=f"r{i}", input_ids=[3 + i, 7, 11 + i, 2, 5][: 2 + i], gconfig=g) for i in range(4)]
+            return await asyncio.gather(*[eng.agenerate(r) for r in reqs])
+        res = asyncio.run(run())
+        outs[mode] = [(r.output_tokens, r.output_logprobs) for r in res]
+        eng.destroy()
+    for (ta, la), (tb, lb) in zip(outs["state"], outs["recompute"]):
+        assert ta == tb
+        assert max(abs(x - y) for x, y in zip(la, lb)) < 1e-4
