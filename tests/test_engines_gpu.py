@@ -138,6 +138,39 @@ def test_rollout_engine_greedy_matches_cpu():
     assert agree >= 0.5 * total
 
 
+def test_hybrid_model_rolls_out_on_carried_state_on_gpu():
+    """Linear-attention stack on the GPU rollout engine: prompts absorbed by a packed forward, then one
+    token per step on per-sequence state; the first log-prob matches the fp32 CPU engine and the
+    generated log-probs match a packed forward of the finished sequences on the same GPU model."""
+    cfg = preset("tiny-qwen3.5")
+    gpu_model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=11)
+    cpu_model = build_model(cfg, dtype=torch.float32, device="cpu", seed=11)
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(gpu_model.named_parameters(), cpu_model.named_parameters()):
+            q.copy_(p.float().cpu())
+    mk = lambda m, dev: NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=3, context_length=256),  # noqa: E731
+                                              model=m, eos_token_id=None).initialize(device=dev, start_executor=False)
+    eg, ec = mk(gpu_model, "cuda"), mk(cpu_model, "cpu")
+    g = GenerationHyperparameters(max_new_tokens=10, max_tokens=200, greedy=True)
+    prompts = [list(range(5 + i, 20 + 9 * i)) for i in range(4)]
+
+    async def run(e):
+        return await asyncio.gather(*[e.agenerate(ModelRequest(input_ids=p, gconfig=g)) for p in prompts])
+
+    rg, rc = asyncio.run(run(eg)), asyncio.run(run(ec))
+    eg.destroy(); ec.destroy()
+    for p, a, b in zip(prompts, rg, rc):
+        assert len(a.output_tokens) == 10
+        assert abs(a.output_logprobs[0] - b.output_logprobs[0]) < 0.1
+        ids = torch.tensor(p + a.output_tokens, device="cuda")
+        cu = torch.tensor([0, ids.numel()], dtype=torch.int32, device="cuda")
+        with torch.no_grad():
+            lp, _ = gpu_model.logprobs_entropy(gpu_model(ids, cu, max_seqlen=ids.numel()), torch.roll(ids, -1))
+        got = torch.tensor(a.output_logprobs)
+        want = lp[len(p) - 1: len(p) - 1 + 10].float().cpu()
+        assert (got - want).abs().max().item() < 0.1, (got - want).abs().max().item()
+
+
 def test_rollout_engine_sampling_logprobs_consistent_with_trainer():
     """Behaviour log-probs reported by the rollout engine match a trainer-side recompute."""
     cfg = preset("tiny-qwen3")
