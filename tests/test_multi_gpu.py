@@ -79,3 +79,12 @@ def test_fused_ep_dispatch_combine_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_ep_fused.py"), 2, 29771, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("EP_FUSED_OK") == 2
+
+
+def test_engine_expert_parallel_fused_dispatch_two_gpus():
+    """``native:d2e2`` train engine in bf16: three optimizer steps through the fused dispatch / combine
+    kernels give the gradient norms of the NCCL all-to-all path."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_ep_gpu.py"), 2, 29781, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("ENGINE_EP_GPU_OK") == 2
