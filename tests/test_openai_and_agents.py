@@ -279,3 +279,41 @@ def test_engine_stops_on_stop_strings():
         assert r.stop_reason == "stop" and got.endswith(stop) and len(r.output_tokens) == text.index(stop) + 2
     finally:
         eng.destroy()
+
+
+def test_search_agent_example_calls_tool_then_answers():
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "search_agent", "train.py")
+    spec = importlib.util.spec_from_file_location("search_agent_example", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.LocalSearch().query("Danube sea")[0].startswith("The Danube")
+    assert mod.answer_reward("<answer>The Black Sea</answer>", "black sea") == 1.0 and mod.answer_reward("Black Sea", "black sea") == 0.0
+    eng = ScriptedEngine(['<tool_call>{"name": "search", "arguments": {"query": "Danube empties sea"}}</tool_call>',
+                          "<answer>Black Sea</answer>"])
+    ad = AgentRolloutAdapter(mod.SearchAgent(), tokenizer=ByteTok(), gconfig=GenerationHyperparameters(max_new_tokens=200), turn_discount=0.5)
+    traj = asyncio.run(ad.arun_episode(eng, mod.dataset(1)[0]))
+    assert traj["input_ids"].shape[0] == 2 and traj["rewards"].tolist() == [0.5, 1.0]
+    # the second request saw the retrieved passage as a tool message
+    second_prompt = ByteTok().decode(eng.requests[1].input_ids)
+    assert "Black Sea" in second_prompt and "Danube" in second_prompt
+
+
+def test_openai_agents_example_runs_a_function_call_round_trip():
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "openai_agents", "calculator_agent.py")
+    spec = importlib.util.spec_from_file_location("calculator_agent_example", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.safe_eval("(17+72)*2") == 178
+    with pytest.raises(Exception):
+        mod.safe_eval("__import__('os').getcwd()")
+    eng = ScriptedEngine(['<tool_call>{"name": "calculate", "arguments": {"expression": "17+72"}}</tool_call>', "Answer: 89"])
+    ad = AgentRolloutAdapter(mod.CalculatorAgent(), tokenizer=ByteTok(), gconfig=GenerationHyperparameters(max_new_tokens=200))
+    traj = asyncio.run(ad.arun_episode(eng, {"question": "What is 17+72?", "answer": 89}))
+    assert traj["input_ids"].shape[0] == 2 and traj["rewards"].tolist()[-1] == 1.0
+    assert "89" in ByteTok().decode(eng.requests[1].input_ids)            # the tool result reached the second call
