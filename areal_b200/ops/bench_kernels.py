@@ -290,10 +290,47 @@ def bench_engine_decode(a):
     return res
 
 
+def bench_ep(a):
+    """Expert-parallel dispatch and combine kernels on ONE GPU: the ranks' receive buffers are separate local
+    tensors (the kernels never wait on each other), so this measures the kernels against local HBM; over NVLink
+    the same launches are bound by the 770 GB/s peer path for the remote share of the rows."""
+    import types
+
+    from ..parallel import ep_fused as EF
+    from ..parallel.symm import ptr_array
+
+    dev = torch.device("cuda")
+    T, H, k, E, ep = a.rows, a.hidden, 8, 64, 2
+    g = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(T, H, device=dev, generator=g).bfloat16()
+    scores = torch.rand(T, E, device=dev, generator=g)
+    topw, tope = scores.topk(k, dim=-1)
+    flat_e = tope.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)
+    mine = torch.bincount(flat_e, minlength=E)
+    counts = torch.stack([mine, mine])                          # the other emulated rank routes the same way
+    plan = EF.build_plan(counts, order, flat_e[order], 0, k)
+    cap = plan.max_recv + 8
+    bufs = [torch.zeros(cap, H, dtype=torch.bfloat16, device=dev) for _ in range(ep)]
+    comm = types.SimpleNamespace(world=ep, hidden=H, capacity=cap, device=dev)
+    slab = (None, None, ptr_array([b.data_ptr() for b in bufs]))
+    w = topw.reshape(-1)[order].float().contiguous()
+    N = T * k
+    ms = timeit(lambda: EF._dispatch(comm, x, plan, slab), a.iters, a.warmup)
+    report("ep_dispatch", ms, bytes_=N * H * 2 + T * H * 2, rows=N, hidden=H, note="reads T rows (k-fold reuse from L2), writes T*k rows")
+    ms = timeit(lambda: EF._combine(comm, plan, slab, w=w), a.iters, a.warmup)
+    report("ep_combine", ms, bytes_=N * H * 2 + T * H * 2, rows=N, hidden=H, note="reads T*k rows, writes T rows")
+    ms = timeit(lambda: EF._combine(comm, plan, slab, w=w, save=True), a.iters, a.warmup)
+    report("ep_combine_save", ms, bytes_=2 * N * H * 2 + T * H * 2, rows=N, hidden=H, note="also keeps the pulled rows for the backward")
+    ys = torch.randn(N, H, device=dev, generator=g).bfloat16()
+    ms = timeit(lambda: EF._dispatch(comm, x, plan, slab, scale=w, ys=ys), a.iters, a.warmup)
+    return report("ep_dispatch_bwd", ms, bytes_=2 * N * H * 2 + T * H * 2, rows=N, hidden=H, note="scaled rows out + gate-weight gradients (reads the saved rows)")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_decode", "gemm_fp8", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
-                                           "engine_decode"])
+                                           "engine_decode", "ep"])
     ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
@@ -312,7 +349,7 @@ def main(argv=None):
         a.rows = 2048
     return {"gemm": bench_gemm, "gemm_decode": bench_gemm_decode, "gemm_fp8": bench_gemm_fp8, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
             "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
-            "engine_decode": bench_engine_decode}[a.kernel](a)
+            "engine_decode": bench_engine_decode, "ep": bench_ep}[a.kernel](a)
 
 
 if __name__ == "__main__":

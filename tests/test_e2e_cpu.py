@@ -170,7 +170,7 @@ from areal_b200.models.config import preset
 from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
 from areal_b200.infra.spmd import init_split_world, make_split_trainer, run_rollout_rank
 cfg = _cfg(%(tmp)r)
-mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+mc = preset(os.environ.get("SPLIT_MODEL", "tiny-qwen2"), vocab_size=64, num_layers=2, **({"layer_types": ["linear_attention", "full_attention"]} if "qwen3.5" in os.environ.get("SPLIT_MODEL", "") else {}))
 split, groups, bus = init_split_world(int(os.environ["N_TRAIN"]), None)
 ds = ArithmeticDataset(size=128)
 if split.is_trainer:
@@ -197,11 +197,11 @@ print("SPLIT_OK", split.rank, flush=True)
 '''
 
 
-@pytest.mark.parametrize("n_train,world,port", [(1, 2, 29811), (2, 4, 29821)])
-def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port):
+@pytest.mark.parametrize("n_train,world,port,model", [(1, 2, 29811, "tiny-qwen2"), (2, 4, 29821, "tiny-qwen2"), (1, 2, 29831, "tiny-qwen3.5")])
+def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port, model):
     script = tmp_path / "split.py"
     script.write_text(SPLIT_SCRIPT % dict(root=ROOT, tmp=str(tmp_path)))
-    env = dict(os.environ, N_TRAIN=str(n_train), OMP_NUM_THREADS="1")
+    env = dict(os.environ, N_TRAIN=str(n_train), OMP_NUM_THREADS="1", SPLIT_MODEL=model)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)], cwd=ROOT, env=env,
                        capture_output=True, text=True, timeout=400)
