@@ -286,7 +286,10 @@ class B200TrainEngine(TrainEngine):
                                                           "GPipe" if sched_name.lower() == "gpipe" else "Interleaved1F1B")
             else:
                 self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader)
-                sched = {"1f1b": "1F1B", "gpipe": "GPipe"}.get(sched_name.lower(), "1F1B")
+                # zero-bubble names of the reference map to the split-backward 1F1B (input gradients sent on first,
+                # weight gradients in the wait that follows); the V-shaped variant needs virtual stages and is not built
+                sched = {"1f1b": "1F1B", "gpipe": "GPipe", "zbh1": "ZBH1", "zerobubble": "ZBH1", "interleavedzerobubble": "ZBH1",
+                         "zbvzerobubble": "ZBH1"}.get(sched_name.lower(), "1F1B")
                 self._pp_runner = PipelineRunner(self.model, self._pp_group, schedule=sched)
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()

@@ -251,6 +251,72 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] 
     return y
 
 
+# ---- split backward (zero-bubble pipeline schedules): while a queue is installed, the backward of a
+# linear layer computes only the input gradient and appends its weight-gradient product to the queue;
+# the caller runs the queue later (after it has handed the input gradient to the previous stage).
+_WGRAD_QUEUE: Optional[list] = None
+SPLIT_BACKWARD = False          # set while a schedule that splits backward is running (selects the deferrable CPU path)
+
+
+class deferred_wgrad:
+    """``with deferred_wgrad() as q: loss.backward()`` leaves the weight-gradient work of every
+    ``linear`` in ``q``; ``flush_wgrad(q)`` performs it."""
+
+    def __enter__(self):
+        global _WGRAD_QUEUE
+        self.prev, self.queue = _WGRAD_QUEUE, []
+        _WGRAD_QUEUE = self.queue
+        return self.queue
+
+    def __exit__(self, *exc):
+        global _WGRAD_QUEUE
+        _WGRAD_QUEUE = self.prev
+        return False
+
+
+def flush_wgrad(queue: list) -> None:
+    with torch.no_grad():
+        for fn in queue:
+            fn()
+    queue.clear()
+
+
+def _accumulate_wgrad(w, g32):
+    mg = getattr(w, "main_grad", None)
+    if mg is not None:
+        mg.add_(g32.to(mg.dtype))
+    elif w.grad is None:
+        w.grad = g32.to(w.dtype)
+    else:
+        w.grad.add_(g32.to(w.dtype))
+
+
+class _LinearSplit(torch.autograd.Function):
+    """Plain-PyTorch linear whose weight gradient can be deferred (the CPU counterpart of ``_Linear``)."""
+
+    @staticmethod
+    def forward(ctx, x, w, resid):
+        ctx.save_for_backward(x, w)
+        ctx.has_resid = resid is not None
+        y = F.linear(x, w)
+        return y + resid if resid is not None else y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx = (dy @ w) if ctx.needs_input_grad[0] else None
+        if ctx.needs_input_grad[1]:
+            dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
+
+            def wgrad(dy2=dy2, x2=x2, w=w):
+                _accumulate_wgrad(w, dy2.float().t() @ x2.float())
+            if _WGRAD_QUEUE is not None:
+                _WGRAD_QUEUE.append(wgrad)
+            else:
+                wgrad()
+        return dx, None, (dy if ctx.has_resid else None)
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ W^T (+ residual). Weight gradients accumulate in fp32 into ``w.main_grad``
     when the parameter carries one (flat-shard training), else are returned in bf16."""
@@ -281,7 +347,15 @@ class _Linear(torch.autograd.Function):
             gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.grad_buf, epi=EPI_F32_ACC)
         elif ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
-            if mg is not None:
+            if _WGRAD_QUEUE is not None:
+                # split backward: the product runs when the caller flushes the queue
+                def wgrad(dy2=dy2, x2=x2, w=w, mg=mg):
+                    if mg is not None:
+                        gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, epi=EPI_F32_ACC)
+                    else:
+                        _accumulate_wgrad(w, gemm(dy2, x2, a_mn=True, b_mn=True, epi=EPI_F32))
+                _WGRAD_QUEUE.append(wgrad)
+            elif mg is not None:
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, epi=EPI_F32_ACC)
                 dw = None
             else:
@@ -294,6 +368,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor] = Non
     """``x @ w^T (+ resid)``. ``grad_buf`` (fp32, shape of ``w``): the weight gradient is
     accumulated there even when ``w`` is a detached view (slices of stacked expert weights)."""
     if not x.is_cuda:
+        if SPLIT_BACKWARD and torch.is_grad_enabled() and grad_buf is None:
+            return _LinearSplit.apply(x, w, resid)
         y = F.linear(x, w)
         return y + resid if resid is not None else y
     # The swap-AB split-K kernel (gemm_skinny) is NOT routed here: in isolation (L2 flushed) it

@@ -136,13 +136,14 @@ class PipelineRunner:
         self.prev = ranks[self.rank - 1] if self.rank > 0 else None
         self.next = ranks[self.rank + 1] if self.rank < self.n - 1 else None
         self.first_rank, self.last_rank = ranks[0], ranks[-1]
-        if schedule not in ("1F1B", "GPipe"):
-            raise ValueError("schedule must be 1F1B or GPipe (interleaved / zero-bubble variants need virtual stages)")
+        if schedule not in ("1F1B", "GPipe", "ZBH1"):
+            raise ValueError("schedule must be 1F1B, GPipe or ZBH1 (interleaved variants need virtual stages)")
         self.schedule = schedule
         p = next(stage_module.parameters())
         self.device, self.dtype = p.device, p.dtype
         self.H = stage_module.cfg.hidden_size
         self._aux: dict[int, torch.Tensor] = {}
+        self._pending_wgrad: Optional[list] = None
 
     # ---- p2p: every exchange is ONE batch of sends and receives, so a stage that sends forward
     # while its neighbour sends backward cannot block the other (NCCL groups the batch)
@@ -164,8 +165,17 @@ class PipelineRunner:
             from_next = torch.empty(recv_next_T, self.H, device=self.device, dtype=self.dtype)
             ops.append(dist.P2POp(dist.irecv, from_next, self.next, self.group))
         if ops:
-            for r in dist.batch_isend_irecv(ops):
+            works = dist.batch_isend_irecv(ops)
+            if self._pending_wgrad:
+                # zero-bubble step: the exchange is in flight (the previous stage already has its input
+                # gradient on the way) while this stage does the deferred weight-gradient products
+                q, self._pending_wgrad = self._pending_wgrad, None
+                OF.flush_wgrad(q)
+            for r in works:
                 r.wait()
+        elif self._pending_wgrad:
+            q, self._pending_wgrad = self._pending_wgrad, None
+            OF.flush_wgrad(q)
         return from_prev, from_next
 
     # ---- compute of one micro-batch
@@ -185,6 +195,17 @@ class PipelineRunner:
         return y
 
     def _backward(self, x_in, y, dy):
+        if self.schedule == "ZBH1":
+            # input gradients only; the weight-gradient products wait in a queue that the next exchange runs
+            # after it has posted this stage's send (``_p2p``)
+            with OF.deferred_wgrad() as q:
+                self._backward_now(y, dy)
+            self._pending_wgrad = q
+        else:
+            self._backward_now(y, dy)
+        return None if self.m.is_first else x_in.grad
+
+    def _backward_now(self, y, dy):
         if self.m.is_last:
             y.backward()
         else:
@@ -193,7 +214,6 @@ class PipelineRunner:
                 torch.autograd.backward([y, aux], [dy, torch.ones_like(aux)])
             else:
                 y.backward(dy)
-        return None if self.m.is_first else x_in.grad
 
     def run(self, microbatches: list[dict[str, Any]], loss_fn: Optional[Callable] = None, forward_only: bool = False) -> list:
         """``microbatches``: dicts with ``input_ids`` [T] and ``pb`` (PackedBatch) plus whatever
@@ -212,6 +232,15 @@ class PipelineRunner:
                     else:
                         self._p2p(send_next=y)
             return results
+        if self.schedule == "ZBH1":
+            OF.SPLIT_BACKWARD = True
+            try:
+                return self._run_train(microbatches, loss_fn, M, Ts, results)
+            finally:
+                OF.SPLIT_BACKWARD = False
+        return self._run_train(microbatches, loss_fn, M, Ts, results)
+
+    def _run_train(self, microbatches, loss_fn, M, Ts, results):
         warm = M if self.schedule == "GPipe" else min(M, self.n - self.rank - 1)
         rest = M - warm
         inputs, outputs = [], []
@@ -249,6 +278,9 @@ class PipelineRunner:
             results.append(yb.detach() if self.m.is_last else None)
             dx = self._backward(xb, yb, dy)
             self._p2p(send_prev=dx)
+        if self._pending_wgrad:
+            OF.flush_wgrad(self._pending_wgrad)
+            self._pending_wgrad = None
         self.sync_tied_embedding_grads()
         return results if self.m.is_last else []
 

@@ -38,17 +38,18 @@ def make_batch(vocab):
     return dict(input_ids=ids, attention_mask=am, loss_mask=lm.int())
 
 
-def cfg_of(backend, vpp=1):
+def cfg_of(backend, vpp=1, schedule="1F1B"):
     # several micro-batches per rank so that the 1F1B schedule has warm-up, steady and cool-down phases
     c = TrainEngineConfig(init_from_scratch=True, dtype="float32", backend=backend, optimizer=OptimizerConfig(lr=1e-2, gradient_clipping=0.5),
                           mb_spec=MicroBatchSpec(max_tokens_per_mb=32))
     c.megatron.virtual_pipeline_parallel_size = vpp
+    c.archon.pp_schedule = schedule
     return c
 
 
-def check(mc, tag, vpp=1):
+def check(mc, tag, vpp=1, schedule="1F1B"):
     rank = dist.get_rank()
-    eng = B200TrainEngine(cfg_of("native:d2p2", vpp))
+    eng = B200TrainEngine(cfg_of("native:d2p2", vpp, schedule))
     eng.create_process_group()
     eng.initialize(model_config=mc, seed=5)
     assert (eng.dp_size, eng.pp_size) == (2, 2) and eng.pp_rank == rank // 2 and eng.dp_rank == rank % 2
@@ -102,6 +103,7 @@ def main():
     dist.init_process_group("gloo")
     check(preset("tiny-qwen3"), "untied")
     check(preset("tiny-qwen3", tie_word_embeddings=True), "tied")
+    check(preset("tiny-qwen3", tie_word_embeddings=True), "zero-bubble-tied", schedule="ZBH1")   # split backward, weight gradients deferred
     check(preset("tiny-qwen3", num_layers=4), "interleaved", vpp=2)            # 2 ranks x 2 chunks, one layer each
     check(preset("tiny-qwen3", num_layers=4, tie_word_embeddings=True), "interleaved-tied", vpp=2)
     print("ENGINE_PP_OK", flush=True)

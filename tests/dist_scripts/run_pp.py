@@ -1,4 +1,4 @@
-"""Pipeline-parallel parity (gloo ranks on CPU): 1F1B and GPipe over 2 and 3 stages against the
+"""Pipeline-parallel parity (gloo ranks on CPU): 1F1B, GPipe and the split-backward ZBH1 schedule over 2 and 3 stages against the
 unsplit model. Prints PP_OK per rank."""
 import os
 import sys
@@ -36,7 +36,7 @@ def main():
                 lp, _ = model.logprobs_entropy(hidden, mb["labels"])
                 return -lp.float().mean() / len(mbs)
             return fn
-        for schedule in ("1F1B", "GPipe"):
+        for schedule in ("1F1B", "GPipe", "ZBH1"):
             stage.zero_grad(set_to_none=True)
             full.zero_grad(set_to_none=True)
             full.train(); stage.train()
