@@ -143,16 +143,24 @@ class _GroupedLinear(torch.autograd.Function):
         dw = None
         if ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
-            acc = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
-            off = 0
-            for e, n in enumerate(counts):
-                if n:
-                    if x.is_cuda:
-                        gemm(dy[off:off + n], x[off:off + n], a_mn=True, b_mn=True, out=acc[e], epi=EPI_F32_ACC)
-                    else:
-                        acc[e] += dy[off:off + n].float().t() @ x[off:off + n].float()
-                off += n
-            dw = None if mg is not None else acc.to(w.dtype)
+
+            def wgrad(acc):
+                off = 0
+                for e, n in enumerate(counts):
+                    if n:
+                        if x.is_cuda:
+                            gemm(dy[off:off + n], x[off:off + n], a_mn=True, b_mn=True, out=acc[e], epi=EPI_F32_ACC)
+                        else:
+                            acc[e] += dy[off:off + n].float().t() @ x[off:off + n].float()
+                    off += n
+                return acc
+            if _WGRAD_QUEUE is not None:
+                # split backward: per-expert products run when the caller flushes the queue
+                _WGRAD_QUEUE.append(lambda: wgrad(mg) if mg is not None else _accumulate_wgrad(
+                    w, wgrad(torch.zeros(w.shape, device=w.device, dtype=torch.float32))))
+            else:
+                acc = wgrad(mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32))
+                dw = None if mg is not None else acc.to(w.dtype)
         return dx, dw, None
 
 
