@@ -61,3 +61,46 @@ def test_train_engine_expert_parallel(tmp_path, ranks, port):
                        env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("ENGINE_EP_OK") == ranks
+
+
+def test_deferred_weight_gradients_match_plain_backward():
+    """Split backward used by the ZBH1 schedule: with a queue installed, ``linear`` / ``grouped_linear``
+    backward yields input gradients only; flushing the queue adds exactly the weight gradients."""
+    import torch
+
+    from areal_b200.ops import functional as OF
+
+    torch.manual_seed(0)
+    x = torch.randn(7, 8, requires_grad=True)
+    w1, w2 = torch.nn.Parameter(torch.randn(6, 8)), torch.nn.Parameter(torch.randn(3, 5, 6))
+    counts = [2, 0, 5]
+
+    def loss():
+        return OF.grouped_linear(torch.relu(OF.linear(x, w1)), w2, counts).square().sum()
+
+    loss().backward()
+    ref = [t.grad.clone() for t in (x, w1, w2)]
+    for t in (x, w1, w2):
+        t.grad = None
+    OF.SPLIT_BACKWARD = True
+    try:
+        y = loss()
+        with OF.deferred_wgrad() as q:
+            y.backward()
+        assert w1.grad is None and w2.grad is None and len(q) == 2
+        assert torch.allclose(x.grad, ref[0], atol=1e-5)
+        OF.flush_wgrad(q)
+    finally:
+        OF.SPLIT_BACKWARD = False
+    assert torch.allclose(w1.grad, ref[1], atol=1e-4) and torch.allclose(w2.grad, ref[2], atol=1e-4)
+    # with main_grad buffers (flat-shard training) the products accumulate there
+    w1.grad = None
+    w1.main_grad = torch.zeros(6, 8)
+    OF.SPLIT_BACKWARD = True
+    try:
+        with OF.deferred_wgrad() as q:
+            loss().backward()
+        OF.flush_wgrad(q)
+    finally:
+        OF.SPLIT_BACKWARD = False
+    assert w1.grad is None and torch.allclose(w1.main_grad, ref[1], atol=1e-4)
