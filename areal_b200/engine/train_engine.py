@@ -275,7 +275,7 @@ class B200TrainEngine(TrainEngine):
             self.local_model_config = model_config
             vpp = max(int(getattr(self.parallel, "virtual_pipeline_parallel_size", 0) or 0), int(cfg.megatron.virtual_pipeline_parallel_size or 1), 1)
             sched_name = str(getattr(cfg.archon, "pp_schedule", "1F1B"))
-            if vpp > 1 or sched_name.lower() == "interleaved1f1b":
+            if vpp > 1 or sched_name.lower() in ("interleaved1f1b", "interleavedzerobubble"):
                 # virtual stages: several model chunks per rank, interleaved 1F1B on the timetable runner
                 from ..parallel.pp import InterleavedStages, ScheduledPipelineRunner
 
@@ -283,13 +283,14 @@ class B200TrainEngine(TrainEngine):
                 self.model = InterleavedStages(model_config, self.pp_rank, self.pp_size, vpp, dtype=dtype, device=self.device, seed=seed,
                                                init_full=loader)
                 self._pp_runner = ScheduledPipelineRunner(self.model, self._pp_group,
-                                                          "GPipe" if sched_name.lower() == "gpipe" else "Interleaved1F1B")
+                                                          "GPipe" if sched_name.lower() == "gpipe" else
+                                                          "InterleavedZeroBubble" if "zero" in sched_name.lower() or sched_name.lower() == "zbh1"
+                                                          else "Interleaved1F1B")
             else:
                 self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader)
                 # zero-bubble names of the reference map to the split-backward 1F1B (input gradients sent on first,
                 # weight gradients in the wait that follows); the V-shaped variant needs virtual stages and is not built
-                sched = {"1f1b": "1F1B", "gpipe": "GPipe", "zbh1": "ZBH1", "zerobubble": "ZBH1", "interleavedzerobubble": "ZBH1",
-                         "zbvzerobubble": "ZBH1"}.get(sched_name.lower(), "1F1B")
+                sched = {"1f1b": "1F1B", "gpipe": "GPipe", "zbh1": "ZBH1", "zerobubble": "ZBH1", "zbvzerobubble": "ZBH1"}.get(sched_name.lower(), "1F1B")
                 self._pp_runner = PipelineRunner(self.model, self._pp_group, schedule=sched)
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()

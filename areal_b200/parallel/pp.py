@@ -460,9 +460,13 @@ class ScheduledPipelineRunner:
         self.V = len(self.chunks)
         self.ranks = dist.get_process_group_ranks(group)
         self.first_rank, self.last_rank = self.ranks[0], self.ranks[-1]
-        self.schedule = {"1f1b": "Interleaved1F1B", "interleaved1f1b": "Interleaved1F1B", "gpipe": "GPipe"}.get(schedule.lower())
+        self.schedule = {"1f1b": "Interleaved1F1B", "interleaved1f1b": "Interleaved1F1B", "gpipe": "GPipe",
+                         "interleavedzerobubble": "Interleaved1F1B", "zbh1": "Interleaved1F1B"}.get(schedule.lower())
         if self.schedule is None:
             raise ValueError(f"unknown pipeline schedule '{schedule}'")
+        # zero-bubble variant: same timetable, every backward leaves its weight-gradient products in a queue
+        # that runs while the next tick's exchange (which carries this backward's input gradient) is in flight
+        self.split_backward = schedule.lower() in ("interleavedzerobubble", "zbh1")
         p = next(self.chunks[0].parameters())
         self.device, self.dtype, self.H = p.device, p.dtype, stages.cfg.hidden_size
 
@@ -475,6 +479,16 @@ class ScheduledPipelineRunner:
         outbox: dict = {}
         saved: dict = {}             # (mb, chunk) -> (x_in, y, aux)
         results: list = [None] * M
+        pending: Optional[list] = None
+        OF.SPLIT_BACKWARD = self.split_backward and not forward_only
+        try:
+            return self._run_table(table, microbatches, loss_fn, forward_only, Ts, inbox, outbox, saved, results, pending)
+        finally:
+            OF.SPLIT_BACKWARD = False
+
+    def _run_table(self, table, microbatches, loss_fn, forward_only, Ts, inbox, outbox, saved, results, pending):
+        P, V = self.n, self.V
+        S = P * V
         for row, delivered in table:
             ops, keep = [], []
             for (src, dst, kind, mb, s) in delivered:
@@ -486,9 +500,12 @@ class ScheduledPipelineRunner:
                     buf = torch.empty(Ts[mb], self.H, device=self.device, dtype=self.dtype)
                     inbox[(kind, mb, s)] = buf
                     ops.append(dist.P2POp(dist.irecv, buf, self.ranks[src], self.group))
-            if ops:
-                for w in dist.batch_isend_irecv(ops):
-                    w.wait()
+            works = dist.batch_isend_irecv(ops) if ops else []
+            if pending:
+                OF.flush_wgrad(pending)
+                pending = None
+            for w in works:
+                w.wait()
             op = row[self.rank]
             if op is None:
                 continue
@@ -512,17 +529,27 @@ class ScheduledPipelineRunner:
                     saved[(mb, v)] = (x if s > 0 else None, y, aux)
             else:
                 x, y, aux = saved.pop((mb, v))
-                if s == S - 1:
-                    (y if aux is None else y + aux).backward()
-                    results[mb] = y.detach()
-                else:
-                    dy = inbox.pop(("grad", mb, s))
-                    if aux is not None:
-                        torch.autograd.backward([y, aux], [dy, torch.ones_like(aux)])
+                ctx = OF.deferred_wgrad() if self.split_backward else None
+                q = ctx.__enter__() if ctx is not None else None
+                try:
+                    if s == S - 1:
+                        (y if aux is None else y + aux).backward()
+                        results[mb] = y.detach()
                     else:
-                        y.backward(dy)
+                        dy = inbox.pop(("grad", mb, s))
+                        if aux is not None:
+                            torch.autograd.backward([y, aux], [dy, torch.ones_like(aux)])
+                        else:
+                            y.backward(dy)
+                finally:
+                    if ctx is not None:
+                        ctx.__exit__(None, None, None)
+                if q:
+                    pending = (pending or []) + q
                 if s > 0:
                     outbox[("grad", mb, s - 1)] = x.grad
+        if pending:
+            OF.flush_wgrad(pending)
         self.sync_tied_embedding_grads()
         return results if self.rank == P - 1 else []
 

@@ -61,7 +61,7 @@ def main():
         if cfg.num_layers % (2 * world) == 0 or cfg.num_layers >= 2 * world:
             inter = InterleavedStages(cfg, rank, world, 2, dtype=torch.float32, device="cpu", seed=3)
             mbs_i = (mbs * world)[: 2 * world]                     # a multiple of the pipeline size
-            for schedule in ("Interleaved1F1B", "GPipe"):
+            for schedule in ("Interleaved1F1B", "GPipe", "InterleavedZeroBubble"):
                 inter.zero_grad(set_to_none=True)
                 full.zero_grad(set_to_none=True)
                 inter.train()
