@@ -110,7 +110,8 @@ def test_vlm_matches_hf(family):
 
 
 def _vlm_batch(mc, vcfg):
-    px, grid = preprocess_images(_images(), vcfg, min_pixels=28 * 28, max_pixels=28 * 28 * 16)
+    unit = vcfg.patch_size * vcfg.spatial_merge_size
+    px, grid = preprocess_images(_images(), vcfg, min_pixels=unit * unit, max_pixels=unit * unit * 16)
     nt = num_image_tokens(grid)
     rows, mm = [], []
     g = torch.Generator().manual_seed(0)
@@ -137,11 +138,12 @@ def _vlm_batch(mc, vcfg):
     return dict(input_ids=ids, attention_mask=am, loss_mask=lm, multi_modal_input=mm)
 
 
-def test_train_engine_steps_a_vlm_and_tower_gets_gradients():
+@pytest.mark.parametrize("name", ["tiny-qwen2.5-vl", "tiny-qwen3-vl"])
+def test_train_engine_steps_a_vlm_and_tower_gets_gradients(name):
     from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, TrainEngineConfig
     from areal_b200.engine.train_engine import B200TrainEngine
 
-    mc = preset("tiny-qwen2.5-vl")
+    mc = preset(name)
     eng = B200TrainEngine(TrainEngineConfig(init_from_scratch=True, dtype="float32", optimizer=OptimizerConfig(lr=1e-2),
                                             mb_spec=MicroBatchSpec(max_tokens_per_mb=64)))
     eng.create_process_group()
@@ -156,18 +158,21 @@ def test_train_engine_steps_a_vlm_and_tower_gets_gradients():
     losses = [eng.train_batch(batch, loss_fn, lambda mb: mb["loss_mask"].count_nonzero())["loss"] for _ in range(4)]
     assert losses[-1] < losses[0]
     assert not torch.equal(before, eng.model.visual.blocks[0].attn.qkv.weight.detach())
+    if eng.model.vcfg.deepstack_visual_indexes:           # the deep-stack mergers train too
+        assert eng.model.visual.deepstack_merger_list[0].linear_fc1.weight.main_grad is not None
     lp = eng.forward_batch(batch)
     assert lp.shape == batch["input_ids"].shape and torch.isfinite(lp).all()
     eng.destroy()
 
 
-def test_vision_rlvr_workflow_rollout_cpu():
+@pytest.mark.parametrize("name", ["tiny-qwen2-vl", "tiny-qwen3-vl"])
+def test_vision_rlvr_workflow_rollout_cpu(name):
     from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeInferConfig
     from areal_b200.engine.infer_engine import NativeInferenceEngine
     from areal_b200.rollout.workflows.vision_rlvr import VisionRLVRWorkflow, expand_image_placeholders
 
     assert expand_image_placeholders([1, 1000, 2, 1000], [2, 3], 1000) == [1, 1000, 1000, 2, 1000, 1000, 1000]
-    mc = preset("tiny-qwen2-vl")
+    mc = preset(name)
     eng = NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=4, context_length=256), model_config=mc)
     eng.initialize(device="cpu", start_executor=False)
     try:
@@ -181,7 +186,7 @@ def test_vision_rlvr_workflow_rollout_cpu():
 
         pil = Image.fromarray(_images()[0])
         wf = VisionRLVRWorkflow(reward, GenerationHyperparameters(n_samples=2, max_new_tokens=5, max_tokens=200, greedy=True), vision_config=eng.model.vcfg,
-                                image_token_id=mc.image_token_id, reward_in_process=True, min_pixels=28 * 28, max_pixels=28 * 28 * 16)
+                                image_token_id=mc.image_token_id, reward_in_process=True, min_pixels=32 * 32, max_pixels=32 * 32 * 16)
         out = asyncio.run(wf.arun_episode(eng, {"input_ids": [5, 6, 1002, 1000, 7], "images": [pil]}))
         assert out["input_ids"].shape[0] == 2 and len(out["multi_modal_input"]) == 2
         grid = out["multi_modal_input"][0]["image_grid_thw"]
