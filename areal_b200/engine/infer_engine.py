@@ -721,10 +721,13 @@ class NativeInferenceEngine(InferenceEngine):
         done: list = []
         if admitted:
             self._prefill(admitted, done, remember=pending if sharing else None)
+        started: list[_Seq] = []
         if reuse:
-            self._start_from_prefix(reuse, done)
-        if admitted or reuse:
-            keep = [s for s in admitted + [s for s, _ in reuse] if all(s is not d for d, _ in done)]
+            # only the sequences that really started: one whose prefix entry was evicted meanwhile
+            # went back to the waiting queue and must not also get a decode row
+            started = self._start_from_prefix(reuse, done)
+        if admitted or started:
+            keep = [s for s in admitted + started if all(s is not d for d, _ in done)]
             for s in keep:
                 self._assign_row(s)
             with self._lock:
@@ -814,9 +817,10 @@ class NativeInferenceEngine(InferenceEngine):
         self.cache.share(full)
         self._prefix[key] = dict(pages=full, tail_page=tail_page, tail=tail, n=n, logits=logits_row.clone(), version=self._version)
 
-    def _start_from_prefix(self, reuse: list, done: list) -> None:
+    def _start_from_prefix(self, reuse: list, done: list) -> list:
         """Sequences whose whole prompt is cached: link the shared pages, copy the partial last page,
-        sample the first token from the stored logits. No forward pass."""
+        sample the first token from the stored logits. No forward pass. Returns the sequences that
+        started; the others (entry evicted since admission) are back at the head of the waiting queue."""
         ps = self.cache.page_size
         ready, rows = [], []
         for s, key in reuse:
@@ -837,12 +841,13 @@ class NativeInferenceEngine(InferenceEngine):
             ready.append(s)
             rows.append(ent["logits"])
         if not ready:
-            return
+            return ready
         toks, lps = self._sample_cuda(torch.stack(rows), ready)
         self.stats["prefix_hits"] += len(ready)
         self.stats["prefix_tokens_saved"] += sum(s.cached for s in ready)
         for s, tok, lp in zip(ready, toks, lps):
             self._accept_token(s, tok, lp, done)
+        return ready
 
     def _prefill(self, seqs: list[_Seq], done: list, remember: Optional[dict] = None):
         dev = self.device
@@ -927,6 +932,7 @@ class NativeInferenceEngine(InferenceEngine):
 
     # ---- stable rows of the static decode buffers
     def _assign_row(self, s: _Seq):
+        assert s.row < 0 and s.pages, "a sequence gets a decode row once, after its pages"
         r = self._rows_free.pop()
         s.row = r
         self._row_seq[r] = s

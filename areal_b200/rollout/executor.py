@@ -32,6 +32,9 @@ from .task_runner import AsyncTaskRunner, TaskQueueFullError, TaskResult
 logger = alog.getLogger("rollout_executor")
 
 ROLLOUT_POLL_S = 0.05
+# ``wait`` / ``wait_for_task`` without a timeout still end: a week, like the reference's
+# ``_DEFAULT_WAIT_TIMEOUT_SECONDS`` (areal/infra/workflow_executor.py:252)
+DEFAULT_WAIT_TIMEOUT_S = float(7 * 24 * 3600)
 REQUIRED_KEYS = ("input_ids", "attention_mask")
 
 
@@ -77,7 +80,8 @@ class WorkflowExecutor:
         self._pending_lock = threading.Lock()
         self._results: list[TaskResult] = []
         self._results_lock = threading.Lock()
-        self._task_results: dict[int, Any] = {}
+        self._task_results: dict[int, Any] = {}    # only for task ids somebody asked to wait on (``_tracked``)
+        self._tracked: set[int] = set()
         self._paused = threading.Event()
         self._stop = threading.Event()
         self._threads: list[threading.Thread] = []
@@ -117,7 +121,10 @@ class WorkflowExecutor:
 
     def _check(self):
         if self._exc is not None:
-            raise RuntimeError("rollout executor thread failed") from self._exc
+            root = self._exc
+            while root.__cause__ is not None:
+                root = root.__cause__
+            raise RuntimeError(f"rollout executor thread failed: {root!r}") from self._exc
         self.runner.check_health()
 
     # ------------------------------------------------------------------ producer / consumer
@@ -153,13 +160,16 @@ class WorkflowExecutor:
             if accepted:
                 self.staleness.on_rollout_accepted()
                 with self._results_lock:
-                    self._results.append(TaskResult(r.task_id, traj, r.create_time))
-                    self._task_results[r.task_id] = traj
+                    if r.task_id in self._tracked:      # handed out by ``wait_for_task`` only, never by ``wait``
+                        self._task_results[r.task_id] = traj
+                    else:
+                        self._results.append(TaskResult(r.task_id, traj, r.create_time))
             else:
                 self.staleness.on_rollout_rejected()
                 self.rejected_count += 1
                 with self._results_lock:
-                    self._task_results[r.task_id] = None
+                    if r.task_id in self._tracked:
+                        self._task_results[r.task_id] = None
 
     # ------------------------------------------------------------------ workflow resolution
     def _resolve_workflow(self, workflow, workflow_kwargs) -> RolloutWorkflow:
@@ -208,12 +218,17 @@ class WorkflowExecutor:
 
     # ------------------------------------------------------------------ public API
     def submit(self, data: dict[str, Any], workflow=None, workflow_kwargs=None, should_accept_fn=None,
-               task_id: Optional[int] = None, is_eval: bool = False) -> int:
+               task_id: Optional[int] = None, is_eval: bool = False, track: bool = False) -> int:
+        """Queues one episode. ``track=True`` keeps the episode's outcome (a trajectory, or ``None``
+        when it was rejected) for ``wait_for_task`` instead of the shared result pool of ``wait``."""
         self._check()
         wf = self._resolve_workflow(workflow, workflow_kwargs)
         if isinstance(should_accept_fn, str):
             should_accept_fn = import_from_string(should_accept_fn)
         tid = task_id if task_id is not None else self.runner.new_task_id()
+        if track:
+            with self._results_lock:
+                self._tracked.add(tid)
         with self._pending_lock:
             if len(self._pending) >= self.queue_size:
                 raise TaskQueueFullError("pending rollout queue is full")
@@ -224,7 +239,7 @@ class WorkflowExecutor:
     def wait(self, count: int, timeout: Optional[float] = None, raise_timeout: bool = True) -> list:
         """Blocks until ``count`` accepted trajectories exist; returns them (oldest first,
         shuffled unless deterministic) and keeps the surplus for the next call."""
-        deadline = None if timeout is None else time.monotonic() + timeout
+        deadline = time.monotonic() + (DEFAULT_WAIT_TIMEOUT_S if timeout is None else timeout)
         while True:
             self._check()
             with self._results_lock:
@@ -243,14 +258,20 @@ class WorkflowExecutor:
         return [r.data for r in take]
 
     def wait_for_task(self, task_id: int, timeout: Optional[float] = None, raise_timeout: bool = True):
-        deadline = None if timeout is None else time.monotonic() + timeout
+        """Outcome of one episode: its trajectory, or ``None`` if it was rejected. An id that was not
+        submitted with ``track=True`` is looked for in the shared pool (accepted episodes only)."""
+        deadline = time.monotonic() + (DEFAULT_WAIT_TIMEOUT_S if timeout is None else timeout)
         while True:
             self._check()
             with self._results_lock:
                 if task_id in self._task_results:
-                    traj = self._task_results.pop(task_id)
-                    self._results = [r for r in self._results if r.task_id != task_id]
-                    return traj
+                    self._tracked.discard(task_id)
+                    return self._task_results.pop(task_id)
+                if task_id not in self._tracked:
+                    hit = [r for r in self._results if r.task_id == task_id]
+                    if hit:
+                        self._results = [r for r in self._results if r.task_id != task_id]
+                        return hit[0].data
             if deadline is not None and time.monotonic() > deadline:
                 if raise_timeout:
                     raise TimeoutError(f"timed out waiting for task {task_id}")
@@ -259,10 +280,15 @@ class WorkflowExecutor:
 
     def rollout_batch(self, data: list[dict[str, Any]], workflow=None, workflow_kwargs=None, should_accept_fn=None
                       ) -> dict[str, Any]:
-        for item in data:
-            self.submit(item, workflow, workflow_kwargs, should_accept_fn)
-        trajs = self.wait(len(data))
-        return D.concat_padded_tensors([t for t in trajs if t])
+        """Synchronous helper: runs one episode per item and returns the accepted ones, concatenated.
+        Rejected episodes and episodes that returned ``None`` count as finished (reference:
+        areal/infra/workflow_executor.py:1358-1391 waits on completions and filters afterwards)."""
+        tids = [self.submit(item, workflow, workflow_kwargs, should_accept_fn, track=True) for item in data]
+        trajs = [self.wait_for_task(t) for t in tids]
+        trajs = [t for t in trajs if t]
+        if not trajs:
+            raise RuntimeError("every episode of the batch was rejected or returned no trajectory")
+        return D.concat_padded_tensors(trajs)
 
     def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,
                       dynamic_bs: bool = False) -> dict[str, Any]:

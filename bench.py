@@ -150,7 +150,23 @@ def main():
     if wd > 0:
         faulthandler.dump_traceback_later(wd, exit=True)
 
-    result = run_async_grpo_bench(args, ClockSampler)
+    try:
+        result = run_async_grpo_bench(args, ClockSampler)
+    except BaseException as e:
+        # the innermost cause goes out as the LAST stderr line and as a JSON line, so a failure
+        # deep inside an engine thread stays readable from the tail of a log
+        import traceback
+
+        traceback.print_exc()
+        root = e
+        while root.__cause__ is not None or (root.__context__ is not None and not root.__suppress_context__):
+            root = root.__cause__ or root.__context__
+        msg = f"{type(root).__name__}: {root}"
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "native", "error": msg[:2000]}))
+        sys.stdout.flush()
+        print(f"bench failed, root cause: {msg[:4000]}", file=sys.stderr, flush=True)
+        os._exit(1)
     if result is not None:
         print(json.dumps(result))
     return 0

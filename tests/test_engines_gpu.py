@@ -308,3 +308,40 @@ def test_prefix_sharing_reuses_prompt_pages_and_matches_plain_engine(prompt_len)
     asyncio.run(run(eng))
     assert eng.stats["prefix_hits"] == 8 + 3 and all(e["version"] == 3 for e in eng._prefix.values())
     eng.destroy()
+
+
+def test_prefix_eviction_under_page_pressure_keeps_rows_and_pages_consistent():
+    """A page pool too small for the stored prompts plus the running sequences: stored prompts get
+    evicted between the admission of a sequence that counted on them and its start. Such a sequence
+    goes back to the waiting queue and must not also take a decode row (it used to: every such
+    event leaked one row and left a page-less sequence in the decode batch). Many groups of
+    identical prompts run through such a pool; outputs equal those of a roomy engine and every row
+    and page is back afterwards."""
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=5)
+
+    def engine(num_pages, share=True):
+        ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=256, enable_prefix_sharing=share)
+        ic.num_pages = num_pages
+        return NativeInferenceEngine(InferenceEngineConfig(), ic, model=model, eos_token_id=None).initialize(device="cuda", start_executor=False)
+
+    g = GenerationHyperparameters(max_new_tokens=24, max_tokens=200, greedy=True, ignore_eos=True)
+    prompts = [[(7 * k + i) % 1000 + 3 for i in range(40 + k)] for k in range(12)]      # 12 different prompts
+    reqs = [(k, j) for k in range(12) for j in range(4)]                               # groups of 4
+
+    async def run(e):
+        return await asyncio.gather(*[e.agenerate(ModelRequest(rid=f"r{k}_{j}", input_ids=prompts[k], gconfig=g)) for k, j in reqs])
+
+    roomy = engine(512, share=False)
+    want = asyncio.run(run(roomy))
+    roomy.destroy()
+    # 8 running sequences need 8 * ceil((51 + 24) / 16) = 40 pages; 44 leaves next to nothing for stored prompts
+    tight = engine(44)
+    for _ in range(3):
+        got = asyncio.run(run(tight))
+        assert [r.output_tokens for r in got] == [r.output_tokens for r in want]
+    assert oplib.kernel_error() == 0
+    assert sorted(tight._rows_free) == list(range(tight.max_batch)) and all(s is None for s in tight._row_seq)
+    held = sum(len(e["pages"]) + (e["tail_page"] is not None) for e in tight._prefix.values())
+    assert len(tight.cache.free) == tight.cache.num_pages - held
+    tight.destroy()
