@@ -83,15 +83,21 @@ def arithmetic_reward_fn(prompt, completion, prompt_ids, completion_ids, answer=
 
 
 class RandomTokenDataset(Dataset):
-    """Uniform-random prompt token ids with a per-sample response budget drawn from a
-    log-normal (forced-length benchmarks); rewards are Bernoulli from the seed."""
+    """Uniform-random prompt token ids with forced response lengths drawn from a log-normal
+    (forced-length benchmarks); rewards are Bernoulli from the seed.
+
+    ``n_samples > 0``: every item carries ``max_new_tokens_per_sample`` -- one independent draw
+    per sample of the prompt's group (the samples of a group then finish at different times, as
+    they do with real generations). ``n_samples = 0``: one draw per prompt (``max_new_tokens``),
+    shared by the whole group."""
 
     def __init__(self, size: int, prompt_len: int, vocab_size: int, seed: int = 1, median_len: int = 1024,
-                 max_len: int = 4096, sigma: float = 0.6, min_len: int = 16):
+                 max_len: int = 4096, sigma: float = 0.6, min_len: int = 16, n_samples: int = 0):
         g = torch.Generator().manual_seed(seed)
         self.prompts = torch.randint(0, vocab_size, (size, prompt_len), generator=g, dtype=torch.int32)
-        z = torch.randn(size, generator=g)
+        z = torch.randn(size, max(1, n_samples), generator=g)
         lens = (median_len * torch.exp(sigma * z)).clamp(min_len, max_len).long()
+        self.per_sample = n_samples > 0
         self.lens = lens.tolist()
         self.rewards = (torch.rand(size, generator=g) < 0.5).float().tolist()
 
@@ -99,7 +105,12 @@ class RandomTokenDataset(Dataset):
         return self.prompts.shape[0]
 
     def __getitem__(self, i):
-        return dict(input_ids=self.prompts[i].tolist(), max_new_tokens=self.lens[i], reward=self.rewards[i], idx=i)
+        item = dict(input_ids=self.prompts[i].tolist(), reward=self.rewards[i], idx=i)
+        if self.per_sample:
+            item["max_new_tokens_per_sample"] = list(self.lens[i])
+        else:
+            item["max_new_tokens"] = self.lens[i][0]
+        return item
 
 
 def bernoulli_reward_fn(prompt, completion, prompt_ids, completion_ids, reward=0.0, idx=0, **kwargs) -> float:

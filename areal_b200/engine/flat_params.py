@@ -21,6 +21,21 @@ import torch
 import torch.nn as nn
 
 ALIGN = 256  # elements; keeps every shard 16-byte aligned for vector / TMA access
+TENSOR_ALIGN = 128  # elements: every tensor starts on a 128-element boundary, so 1 x 128 scaling blocks of a
+                    # row never straddle a shard boundary (in-kernel fp8 cast of the weight push) and all
+                    # vector / TMA accesses are 16-byte aligned
+
+
+def flat_layout(numels: list[int], world_size: int = 1) -> tuple[list[int], int]:
+    """(element offset of every tensor, padded total) of a flat buffer over tensors of ``numels``
+    elements, sharded over ``world_size`` ranks. Pure arithmetic: used to plan against a layout
+    that lives in another process."""
+    offs, total = [], 0
+    for n in numels:
+        offs.append(total)
+        total += (n + TENSOR_ALIGN - 1) // TENSOR_ALIGN * TENSOR_ALIGN
+    unit = ALIGN * world_size
+    return offs, (total + unit - 1) // unit * unit
 
 
 class FlatParamStore:
@@ -37,13 +52,8 @@ class FlatParamStore:
         dev, dtype = self.params[0].device, self.params[0].dtype
         self.device, self.dtype = dev, dtype
         self.world_size, self.rank = world_size, rank
-        offs, total = [], 0
-        for p in self.params:
-            offs.append(total)
-            total += (p.numel() + 7) // 8 * 8  # keep every tensor 16-byte aligned in bf16
-        unit = ALIGN * world_size
-        self.numel = total
-        self.padded = (total + unit - 1) // unit * unit
+        offs, self.padded = flat_layout([p.numel() for p in self.params], world_size)
+        self.numel = (offs[-1] + self.params[-1].numel()) if offs else 0
         self.offsets = offs
         self.shard_numel = self.padded // world_size
         alloc_param = alloc_param or (lambda n, dt, d: torch.zeros(n, dtype=dt, device=d))

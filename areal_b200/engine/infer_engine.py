@@ -168,6 +168,8 @@ class NativeInferenceEngine(InferenceEngine):
                 hf_io.load_model_hf(self.model, model_path)
             if self.tp_size > 1:
                 self._shard_model_for_tp(dtype, seed)
+        elif self.tp_size > 1 and not hasattr(self, "tp_exchange"):
+            self._setup_tp_exchange()          # a ready-made tensor-parallel slice was handed in
         self.shared_model = kwargs.get("shared_model", False)
         if not self.shared_model:
             self.model.eval()
@@ -205,7 +207,27 @@ class NativeInferenceEngine(InferenceEngine):
         del full
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
-            self.icfg.use_cuda_graph = False   # decode steps contain collectives: replayed eagerly
+        self._setup_tp_exchange()
+
+    def _setup_tp_exchange(self):
+        """Dense models on CUDA: the sums over the tensor-parallel ranks run inside this library's
+        own kernels over peer memory (``parallel/tp_decode.py``), so decode steps stay graph
+        captured. Otherwise (CPU, MoE layers, ``AREAL_TP_FUSED=0``) the sums are library
+        all-reduces and decode steps are replayed eagerly."""
+        import os
+
+        from ..parallel.tp_decode import TPDecodeExchange, install_tp_decode, supports_fused_tp
+
+        self.tp_exchange = None
+        if self.device.type != "cuda" or self.tp_size <= 1:
+            return
+        if os.environ.get("AREAL_TP_FUSED", "1") == "0" or not supports_fused_tp(self.model) or self.tp_size > 8:
+            self.icfg.use_cuda_graph = False
+            return
+        ic = self.icfg
+        max_rows = (max(ic.context_length, ic.max_prefill_tokens, ic.max_running_requests) + 255) // 128 * 128
+        self.tp_exchange = TPDecodeExchange(self.tp_group, self.device, self.model_config.hidden_size, max_rows)
+        install_tp_decode(self.model, self.tp_exchange)
 
     def _init_cuda_state(self):
         cfg, ic = self.model_config, self.icfg

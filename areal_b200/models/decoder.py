@@ -43,6 +43,11 @@ class PackedBatch:
 def _lin(mod, name: str, x: torch.Tensor, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ W^T (+ resid)`` for ``W = mod.<name>`` plus its low-rank adapter when one is attached
     (and not merged into ``W``)."""
+    ex = getattr(mod, "tp_exchange", None)
+    if ex is not None and name in ("o_proj", "down_proj") and x.is_cuda and not torch.is_grad_enabled() and resid is None:
+        # tensor-parallel inference: the partial product goes straight into every rank's receive
+        # slots from the GEMM epilogue; the caller gets a handle that the next norm kernel sums
+        return ex.linear_bcast(x if x.stride(-1) == 1 else x.contiguous(), getattr(mod, name))
     if getattr(mod, "use_fp8", False):
         # block-scaled e4m3 operands in forward and input gradient, fp32 accumulation
         y = OF.fp8_linear(x, getattr(mod, name))
@@ -268,6 +273,14 @@ class MoEMLP(nn.Module):
         return out
 
 
+def norm_or_reduce(h, w, eps, resid):
+    """``OF.rmsnorm`` for a tensor; for the handle of a tensor-parallel partial sum the fused
+    sum-over-ranks + residual + RMSNorm kernel."""
+    if hasattr(h, "set_idx"):
+        return h.ex.reduce_rmsnorm(h, w, eps, resid)
+    return OF.rmsnorm(h, w, eps, resid)
+
+
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
         super().__init__()
@@ -279,8 +292,16 @@ class DecoderLayer(nn.Module):
         self.mlp = MoEMLP(cfg, dtype, device) if cfg.layer_is_moe(idx) else DenseMLP(H, cfg.intermediate_size, dtype, device)
 
     tp_group = None  # set by parallel.tp.install_tp
+    tp_exchange = None  # set by parallel.tp_decode.install_tp_decode (inference: fused partial-sum exchange)
 
     def forward(self, h, resid, pb: PackedBatch, cos, sin, attn_fn=None):
+        if self.tp_exchange is not None and not torch.is_grad_enabled():
+            # the attention and MLP blocks return handles of partial sums; each norm kernel below
+            # waits for the peers' parts, sums them, adds the residual stream and normalises
+            x, resid = norm_or_reduce(h, self.input_layernorm, self.cfg.rms_norm_eps, resid)
+            h = self.self_attn(x, pb, cos, sin, attn_fn)
+            x, resid = norm_or_reduce(h, self.post_attention_layernorm, self.cfg.rms_norm_eps, resid)
+            return self.mlp(x), resid
         x, resid = OF.rmsnorm(h, self.input_layernorm, self.cfg.rms_norm_eps, resid)
         g = self.tp_group
         if g is None:
@@ -325,6 +346,8 @@ class CausalLM(nn.Module):
 
     @torch.no_grad()
     def reset_parameters(self, std: float = 0.02, seed: Optional[int] = None):
+        if self.embed_tokens.device.type == "meta":
+            return          # shapes only (layout planning): nothing to draw
         gen = None
         if seed is not None:
             gen = torch.Generator(device=self.embed_tokens.device)
@@ -379,7 +402,7 @@ class CausalLM(nn.Module):
 
             x, _ = rmsnorm_offset(h, self.norm, self.cfg.rms_norm_eps, resid)
         else:
-            x, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
+            x, _ = norm_or_reduce(h, self.norm, self.cfg.rms_norm_eps, resid)
         return x
 
     def set_fp8(self, dense: bool = True) -> int:

@@ -312,12 +312,10 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, void* o,
   if (ab2host::encode_tmap_2d(&tk, k, 2, (uint64_t)Hkv * HD, (uint64_t)T, (uint64_t)k_stride * 2, 64, KT, true, 0)) return 101;
   if (ab2host::encode_tmap_2d(&tv, v, 2, (uint64_t)Hkv * HD, (uint64_t)T, (uint64_t)v_stride * 2, 64, KT, true, 0)) return 102;
   auto kern = attn_fwd_kernel<HD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return 300;
-    attr_set = true;
-  }
+  static ab2host::DevState dev_state;
+  int num_sms = 0;
+  if (ab2host::prepare_launch(kern, Cfg::SMEM_BYTES, dev_state, &num_sms)) return 300;
+  (void)num_sms;
   int* err = ab2host::error_flag();
   if (!err) return 301;
   dim3 grid(num_tiles, Hq);

@@ -10,6 +10,8 @@
 //                      replicas = weight update)
 //   push_copy          shard-direct copy of a bf16 range to several destinations (weight push)
 //   push_cast_fp8      same, with an in-kernel block-scaled (1x128) e4m3 cast
+//   push_plan          a whole FSDP-shard -> tensor-parallel re-shard plan (row / column slices of
+//                      q/k/v/o, gate/up/down) in ONE launch, bf16 or cast to block-scaled e4m3
 //
 // These replace: FSDP2's NCCL reduce-scatter / all-gather (areal/engine/fsdp_utils/parallel.py:388),
 // the grad-norm all-reduces of areal/engine/fsdp_utils/grad.py:112-190, and the all-gather +
@@ -202,6 +204,104 @@ __global__ void push_cast_fp8_kernel(const __nv_bfloat16* __restrict__ src, Peer
   }
 }
 
+// One launch for a whole re-shard plan (tensor-parallel rollout replicas). Every op is a 2-D strided
+// copy of bf16 (rows x cols, 16-byte vectors) from this rank's flat parameter buffer into the flat
+// buffer of TP rank `dst` of EVERY replica: the source vector is loaded once and stored n_rep times.
+// Work is cut into chunks of PLAN_CHUNK vectors; chunk_start[] is the exclusive prefix sum of the
+// ops' chunk counts, so a CTA finds its op by bisection. With fp8 != 0 the copy casts instead:
+// 128-element blocks (16 consecutive threads, 8 values each) become e4m3 values plus
+// one fp32 scale per block, written to the q / s destination tables.
+struct PushOp {
+  long long src_off;   // elements, in the source flat buffer
+  long long dst_off;   // elements, in the destination flat buffer
+  int dst;             // TP rank inside a replica
+  int rows, cols;      // cols % 8 == 0
+  int ld_src, ld_dst;  // elements
+  int pad;
+};
+static constexpr int PLAN_CHUNK = 4096;  // 16-byte vectors per work item (64 KiB)
+
+__global__ void push_plan_kernel(const __nv_bfloat16* __restrict__ src, const PushOp* __restrict__ ops, int n_ops,
+                                 const int* __restrict__ chunk_start, int total_chunks,
+                                 void* const* __restrict__ dst_ptrs, int n_rep, int tp) {
+  for (int chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    int lo = 0, hi = n_ops - 1;
+    while (lo < hi) {              // last op whose first chunk is <= chunk
+      const int mid = (lo + hi + 1) >> 1;
+      if (chunk_start[mid] <= chunk) lo = mid; else hi = mid - 1;
+    }
+    const PushOp op = ops[lo];
+    const int c8 = op.cols >> 3;
+    const long long total = (long long)op.rows * c8;
+    const long long base = (long long)(chunk - chunk_start[lo]) * PLAN_CHUNK;
+    const long long end = min(total, base + PLAN_CHUNK);
+    for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
+      const int r = (int)(i / c8), c = (int)(i - (long long)r * c8);
+      const uint4 v = reinterpret_cast<const uint4*>(src + op.src_off + (size_t)r * op.ld_src)[c];
+      for (int k = 0; k < n_rep; ++k) {
+        __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(dst_ptrs[k * tp + op.dst]);
+        reinterpret_cast<uint4*>(d + op.dst_off + (size_t)r * op.ld_dst)[c] = v;
+      }
+    }
+  }
+}
+
+// Same plan, casting to block-scaled e4m3 on the way: every row of an op is cut into 1 x 128 blocks
+// (cols % 128 == 0, dst_off % 128 == 0, ld_dst % 128 == 0); 16 threads share a block (8 values each),
+// take its amax with shuffles inside their half-warp, and write 8 e4m3 bytes each plus one fp32 scale
+// per block at (element offset / 128) of the scale buffer.
+__global__ void push_plan_fp8_kernel(const __nv_bfloat16* __restrict__ src, const PushOp* __restrict__ ops, int n_ops,
+                                     const int* __restrict__ chunk_start, int total_chunks,
+                                     void* const* __restrict__ dstq, void* const* __restrict__ dsts, int n_rep, int tp,
+                                     int pow2) {
+  for (int chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    int lo = 0, hi = n_ops - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (chunk_start[mid] <= chunk) lo = mid; else hi = mid - 1;
+    }
+    const PushOp op = ops[lo];
+    const int c8 = op.cols >> 3;
+    const long long total = (long long)op.rows * c8;
+    const long long base = (long long)(chunk - chunk_start[lo]) * PLAN_CHUNK;
+    const long long end = min(total, base + PLAN_CHUNK);
+    // total and PLAN_CHUNK are multiples of 16 vectors, so the 16 threads of a block stay together
+    for (long long i0 = base; i0 < end; i0 += blockDim.x) {
+      const long long i = i0 + threadIdx.x;
+      const bool live = i < end;
+      const long long ii = live ? i : base;
+      const int r = (int)(ii / c8), c = (int)(ii - (long long)r * c8);
+      const uint4 v = reinterpret_cast<const uint4*>(src + op.src_off + (size_t)r * op.ld_src)[c];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      float f[8];
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 t = unpack_bf16(w[e]);
+        f[2 * e] = t.x; f[2 * e + 1] = t.y;
+        amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      float scale = fmaxf(amax, 1e-12f) / 448.f;
+      if (pow2) scale = exp2f(ceilf(log2f(scale)));
+      const float inv = 1.f / scale;
+      __nv_fp8x4_e4m3 q0(make_float4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv));
+      __nv_fp8x4_e4m3 q1(make_float4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv));
+      if (!live) continue;
+      const size_t e_off = (size_t)op.dst_off + (size_t)r * op.ld_dst + (size_t)c * 8;
+      for (int k = 0; k < n_rep; ++k) {
+        uint8_t* dq = reinterpret_cast<uint8_t*>(dstq[k * tp + op.dst]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&q0);
+        pk.y = *reinterpret_cast<uint32_t*>(&q1);
+        *reinterpret_cast<uint2*>(dq + e_off) = pk;
+        if ((c & 15) == 0) reinterpret_cast<float*>(dsts[k * tp + op.dst])[e_off >> 7] = scale;
+      }
+    }
+  }
+}
+
 static int grid_of(long long work) {
   long long b = (work + 255) / 256;
   if (b > 148 * 8) b = 148 * 8;
@@ -278,6 +378,30 @@ int ab2_push_copy2d(const void* src, long long ld_src, void* const* dst, int nds
   if (rows <= 0 || cols <= 0 || ndst <= 0) return 0;
   push_copy2d_kernel<<<grid_of((long long)rows * (cols / 8)), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)src, ld_src, make_ptrs(dst, ndst), ndst, dst_off, ld_dst, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+// Executes a re-shard plan in one launch. ops / chunk_start / dst tables live in device memory:
+// ops[n_ops] (PushOp, 40 bytes each), chunk_start[n_ops] (int32, exclusive prefix sum of
+// ceil(rows * cols / 8 / 4096)), dst_ptrs[n_rep * tp] (destination flat buffers, replica-major).
+// fp8 == 0: bf16 copy into dst_ptrs. fp8 != 0: block-scaled e4m3 cast into dst_ptrs (values) and
+// scale_ptrs (fp32, one per 128 elements); then every op needs cols, dst_off and ld_dst to be multiples of 128.
+int ab2_push_plan(const void* src, const void* ops, int n_ops, const void* chunk_start, int total_chunks,
+                  const void* dst_ptrs, const void* scale_ptrs, int n_rep, int tp, int fp8, int pow2_scales, void* stream) {
+  if (n_ops <= 0 || total_chunks <= 0 || n_rep <= 0) return 0;
+  if (tp <= 0 || !src || !ops || !chunk_start || !dst_ptrs) return 10;
+  const int grid = total_chunks < 148 * 8 ? total_chunks : 148 * 8;
+  if (fp8) {
+    if (!scale_ptrs) return 10;
+    push_plan_fp8_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, (const PushOp*)ops, n_ops,
+                                                                  (const int*)chunk_start, total_chunks,
+                                                                  (void* const*)dst_ptrs, (void* const*)scale_ptrs, n_rep,
+                                                                  tp, pow2_scales);
+  } else {
+    push_plan_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, (const PushOp*)ops, n_ops,
+                                                              (const int*)chunk_start, total_chunks,
+                                                              (void* const*)dst_ptrs, n_rep, tp);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

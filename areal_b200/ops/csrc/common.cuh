@@ -330,4 +330,23 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
 }  // namespace ab2
 
 namespace ab2host {
+// Per-device launch state of one kernel instantiation (keep one `static DevState` beside each
+// launch site): the opt-in dynamic shared-memory size has to be set once on EVERY device that
+// launches the kernel, and the SM count belongs to the device, not the process.
+struct DevState {
+  bool attr_set[64] = {};
+  int num_sms[64] = {};
+};
+template <typename K>
+static inline int prepare_launch(K kern, int smem_bytes, DevState& st, int* num_sms) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 300;
+  if (!st.attr_set[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return 300;
+    cudaDeviceGetAttribute(&st.num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    st.attr_set[dev] = true;
+  }
+  if (num_sms) *num_sms = st.num_sms[dev];
+  return 0;
+}
 }  // namespace ab2host

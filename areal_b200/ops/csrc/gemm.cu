@@ -29,7 +29,21 @@ enum Epilogue : int {
   EPI_BF16 = 0,       // C = bf16(acc)
   EPI_F32 = 1,        // C = acc
   EPI_F32_ACC = 2,    // C += acc                (fp32 gradient accumulation)
-  EPI_BF16_RESID = 3  // C = bf16(acc + R)       (residual add fused)
+  EPI_BF16_RESID = 3, // C = bf16(acc + R)       (residual add fused)
+  EPI_BF16_BCAST = 4  // bf16(acc) stored into the same place of SEVERAL buffers (this GPU's and its
+                      // peers'), then a release-add on each buffer's arrival counter: the product is
+                      // handed to every tensor-parallel rank from inside the epilogue
+};
+
+// Destinations of EPI_BF16_BCAST: `n` buffers with C's shape and ldc (peer-mapped symmetric memory)
+// and one 64-bit arrival counter per buffer. Every epilogue warp adds, per tile, the number of
+// (row, 32-column chunk) pieces it stored, so one product adds M * ceil(N / 32) to each counter
+// whatever the tile shape.
+static constexpr int BCAST_MAX = 8;
+struct BcastArgs {
+  void* dst[BCAST_MAX];
+  unsigned long long* counter[BCAST_MAX];
+  int n;
 };
 
 template <int BN>
@@ -64,7 +78,7 @@ template <int BN, bool A_MN, bool B_MN, bool SPLITK = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  void* __restrict__ Cptr, const __nv_bfloat16* __restrict__ Rptr, int M, int N,
-                 int K, int ldc, const int EPI, int* err, int splits, int kb_per) {
+                 int K, int ldc, const int EPI, int* err, int splits, int kb_per, const BcastArgs bc) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -207,10 +221,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       void* Cptr_t = SPLITK ? static_cast<void*>(reinterpret_cast<float*>(Cptr) + (size_t)(tile / mn_tiles) * M * ldc) : Cptr;
-      if (!mbar_wait(tfull_bar(buf), use & 1u, err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), use & 1u, err, ERR_WAIT_TMEM_FULL));   // the warp leaves together
+      if (!ok) break;
       tc_fence_after();
       const int row = m0 + row_in_tile;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      int pieces = 0;   // EPI_BF16_BCAST: (row, chunk) pieces this thread handed out
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -219,7 +235,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int col = n0 + c * 32;
         if (row < M && col < N) {
           const bool full = (col + 32 <= N);
-          if (EPI == EPI_BF16 || EPI == EPI_BF16_RESID) {
+          if (EPI == EPI_BF16_BCAST) {
+            uint32_t p[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) p[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            for (int d = 0; d < bc.n; ++d) {
+              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(bc.dst[d]) + (size_t)row * ldc + col;
+              if (full) {
+                uint4* C4 = reinterpret_cast<uint4*>(C);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) C4[j] = make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col + j < N) C[j] = __float2bfloat16(__uint_as_float(r[j]));
+              }
+            }
+            ++pieces;
+          } else if (EPI == EPI_BF16 || EPI == EPI_BF16_RESID) {
             __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(Cptr_t) + (size_t)row * ldc + col;
             if (full) {
               uint32_t p[16];
@@ -284,6 +316,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before();
       mbar_arrive(tempty_bar(buf));
+      if (EPI == EPI_BF16_BCAST) {
+        // the warp's stores of this tile become visible everywhere before its share of the count does
+        int total = pieces;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);   // also orders the lanes' stores before lane 0
+        if (lane == 0 && total > 0) {
+          __threadfence_system();
+          for (int d = 0; d < bc.n; ++d)
+            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(bc.counter[d]), "l"((unsigned long long)total) : "memory");
+        }
+      }
     }
   }
 
@@ -297,7 +340,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(int epi, const void* A, const void* B, void* C, const void* R, int M, int N,
-                       int K, int lda, int ldb, int ldc, cudaStream_t stream) {
+                       int K, int lda, int ldb, int ldc, cudaStream_t stream, const BcastArgs* bcast = nullptr) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -312,25 +355,16 @@ static int launch_gemm(int epi, const void* A, const void* B, void* C, const voi
     rc = ab2host::encode_tmap_2d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true, 0);
   if (rc) return 200 + rc;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) !=
-        cudaSuccess)
-      return 300;
-    attr_set = true;
-  }
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  static ab2host::DevState st;
+  int num_sms = 0;
+  if (int e = ab2host::prepare_launch(kern, Cfg::SMEM_BYTES, st, &num_sms)) return e;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   int* err = ab2host::error_flag();
   if (!err) return 301;
+  BcastArgs none = {};
   launch_pdl(kern, dim3(grid), dim3(192), (size_t)Cfg::SMEM_BYTES, stream, tmA, tmB, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K,
-             ldc, epi, err, 1, 0);
+             ldc, epi, err, 1, 0, bcast ? *bcast : none);
   return cudaGetLastError() == cudaSuccess ? 0 : 302;
 }
 
@@ -366,17 +400,9 @@ static int launch_splitk(const void* A, const void* B, void* Y, const void* R, f
   rc = ab2host::encode_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, true, 0);
   if (rc) return 200 + rc;
   auto kern = gemm_bf16_kernel<BN, false, false, true>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 300;
-    attr_set = true;
-  }
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  static ab2host::DevState st;
+  int num_sms = 0;
+  if (int e = ab2host::prepare_launch(kern, Cfg::SMEM_BYTES, st, &num_sms)) return e;
   const int num_kb = (K + BK - 1) / BK;
   const int kb_per = (num_kb + splits - 1) / splits;
   splits = (num_kb + kb_per - 1) / kb_per;             // every piece owns at least one k-block
@@ -385,7 +411,7 @@ static int launch_splitk(const void* A, const void* B, void* Y, const void* R, f
   int* err = ab2host::error_flag();
   if (!err) return 301;
   if (launch_pdl(kern, dim3(grid), dim3(192), (size_t)Cfg::SMEM_BYTES, stream, tmA, tmB, (void*)ws, (const __nv_bfloat16*)nullptr, M, N, K, N,
-                 (int)EPI_F32, err, splits, kb_per) != cudaSuccess)
+                 (int)EPI_F32, err, splits, kb_per, BcastArgs{}) != cudaSuccess)
     return 302;
   const long long MN = (long long)M * N;
   long long want = (MN / 4 + 255) / 256;
@@ -439,6 +465,40 @@ int ab2_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, i
     case 128: return dispatch_major<128>(a_mn, b_mn, epi, A, B, C, R, M, N, K, lda, ldb, ldc, s);
     case 64: return dispatch_major<64>(a_mn, b_mn, epi, A, B, C, R, M, N, K, lda, ldb, ldc, s);
     case 32: return dispatch_major<32>(a_mn, b_mn, epi, A, B, C, R, M, N, K, lda, ldb, ldc, s);
+  }
+  return 12;
+}
+
+// Y = A[M, K] B[N, K]^T in bf16, stored into `ndst` buffers at once (dst[i], all with leading dimension
+// ldc; peers' buffers are addressed through peer-mapped symmetric memory), followed by a release-add of
+// M * ceil(N / 32) on counters[i]. The row-parallel products of a tensor-parallel layer use it to hand
+// their partial result to every rank of the group from inside the GEMM epilogue; the consumer
+// (ab2_tp_reduce_rmsnorm) waits on its own counter and sums the partials.
+int ab2_gemm_bf16_bcast(const void* A, const void* B, void* const* dst, void* const* counters, int ndst, int M, int N, int K,
+                        int lda, int ldb, int ldc, int bn, void* stream) {
+  using namespace ab2;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (ndst < 1 || ndst > BCAST_MAX) return 13;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7)) return 10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) return 11;
+  BcastArgs bc = {};
+  bc.n = ndst;
+  for (int i = 0; i < ndst; ++i) {
+    if (!dst[i] || !counters[i] || (reinterpret_cast<uintptr_t>(dst[i]) & 15)) return 11;
+    bc.dst[i] = dst[i];
+    bc.counter[i] = reinterpret_cast<unsigned long long*>(counters[i]);
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 0) {
+    const int mblk = (M + BM - 1) / BM;
+    bn = 256;
+    while (bn > 32 && mblk * ((N + bn - 1) / bn) < 120) bn >>= 1;
+  }
+  switch (bn) {
+    case 256: return launch_gemm<256, false, false>(EPI_BF16_BCAST, A, B, dst[0], nullptr, M, N, K, lda, ldb, ldc, s, &bc);
+    case 128: return launch_gemm<128, false, false>(EPI_BF16_BCAST, A, B, dst[0], nullptr, M, N, K, lda, ldb, ldc, s, &bc);
+    case 64: return launch_gemm<64, false, false>(EPI_BF16_BCAST, A, B, dst[0], nullptr, M, N, K, lda, ldb, ldc, s, &bc);
+    case 32: return launch_gemm<32, false, false>(EPI_BF16_BCAST, A, B, dst[0], nullptr, M, N, K, lda, ldb, ldc, s, &bc);
   }
   return 12;
 }

@@ -546,17 +546,10 @@ static int launch_gc(void* const* a_ptrs, const void* B, void* C, void* const* o
   OutPtrs op;
   for (int r = 0; r < GC_MAX_PEERS; ++r) op.p[r] = ((MODE == 1 || MODE == 3) && r < P) ? out_ptrs[r] : nullptr;
   auto kern = gemm_comm_kernel<BN, B_MN, MODE, RED_BF16>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 300;
-    attr_set = true;
-  }
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  static ab2host::DevState dev_state;
+  int num_sms = 0;
+  if (ab2host::prepare_launch(kern, Cfg::SMEM_BYTES, dev_state, &num_sms)) return 300;
+  (void)num_sms;
   const int tiles = ((M + GC_BM - 1) / GC_BM) * ((N + BN - 1) / BN);
   int grid = tiles < num_sms ? tiles : num_sms;
   if (MODE == 2 || MODE == 4) {

@@ -259,17 +259,10 @@ static int launch_fp8(const void* A, const void* B, void* C, const float* sa, co
   using Cfg = F8Cfg<F8_BN>;
   constexpr int F8_SMEM_BYTES = Cfg::SMEM_BYTES;
   auto kern = gemm_fp8_kernel<BLOCK_SCALED, F8_BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES) != cudaSuccess) return 300;
-    attr_set = true;
-  }
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  static ab2host::DevState dev_state;
+  int num_sms = 0;
+  if (ab2host::prepare_launch(kern, F8_SMEM_BYTES, dev_state, &num_sms)) return 300;
+  (void)num_sms;
   const int tiles = ((M + F8_BM - 1) / F8_BM) * ((N + F8_BN - 1) / F8_BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   int* err = ab2host::error_flag();

@@ -218,17 +218,10 @@ static int launch_grouped(const void* A, const void* B, void* C, const void* til
     rc = ab2host::encode_tmap_3d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)E, (uint64_t)N * 2, (uint64_t)N * K * 2, 64, BK, 1, true, 0);
   if (rc) return 200 + rc;
   auto kern = gemm_grouped_kernel<BN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 300;
-    attr_set = true;
-  }
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  static ab2host::DevState dev_state;
+  int num_sms = 0;
+  if (ab2host::prepare_launch(kern, Cfg::SMEM_BYTES, dev_state, &num_sms)) return 300;
+  (void)num_sms;
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
   int* err = ab2host::error_flag();
   if (!err) return 301;

@@ -498,11 +498,10 @@ static int launch_decode_mma(const void* q, const void* kc, const void* vc, cons
   static_assert(2 * Cfg::STAGE_BYTES >= (4 * 16 * D + 8 * 16) * 4, "the merge buffers alias the stage memory");
   dim3 grid(B, Hkv, splits);
   auto kern = paged_decode_mma_kernel<D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 2;
-    attr_set = true;
-  }
+  static ab2host::DevState dev_state;
+  int num_sms = 0;
+  if (ab2host::prepare_launch(kern, Cfg::SMEM_BYTES, dev_state, &num_sms)) return 2;
+  (void)num_sms;
   launch_pdl(kern, grid, dim3(128), (size_t)Cfg::SMEM_BYTES, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens,
              part_o, part_ml, Hq, Hkv, Hq / Hkv, page_size, max_pages, splits, scale, q_stride);
   launch_pdl(decode_combine_kernel<D>, dim3(B * Hq), dim3(D), 0, s, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits);
@@ -632,11 +631,10 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
   constexpr int SMEM = decode_smem_bytes<D, G>();
   static_assert(SMEM >= (4 * G * D + 8 * G) * 4, "the merge buffers alias the stage memory");
   auto kern = paged_decode_kernel<D, G>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 2;
-    attr_set = true;
-  }
+  static ab2host::DevState dev_state;
+  int num_sms = 0;
+  if (ab2host::prepare_launch(kern, SMEM, dev_state, &num_sms)) return 2;
+  (void)num_sms;
   kern<<<grid, 128, SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pt, lens, part_o, part_ml,
                                Hq, Hkv, page_size, max_pages, splits, scale, q_stride);
   decode_combine_kernel<D><<<B * Hq, D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);

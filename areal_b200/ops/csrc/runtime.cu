@@ -115,6 +115,16 @@ int ab2_kernel_error() {
   return v;
 }
 
+// Enqueues on `stream` a copy of the current device's error word into `host_word` (pinned host
+// memory owned by the caller). The caller reads host_word after its next synchronisation of that
+// stream: a step loop that already synchronises once per step learns of a wait that gave up
+// without paying for a second synchronisation.
+int ab2_kernel_error_peek(int* host_word, void* stream) {
+  int* p = ab2host::error_flag();
+  if (!p || !host_word) return -1;
+  return cudaMemcpyAsync(host_word, p, sizeof(int), cudaMemcpyDeviceToHost, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? 0 : -2;
+}
+
 // Allocates the error word of the current device ahead of time (call once per device
 // before capturing CUDA graphs).
 int ab2_runtime_init() { return ab2host::error_flag() ? 0 : -1; }

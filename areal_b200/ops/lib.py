@@ -24,6 +24,10 @@ c_float = ctypes.c_float
 _SIGS = {
     "ab2_kernel_error": ([], c_int),
     "ab2_runtime_init": ([], c_int),
+    "ab2_kernel_error_peek": ([c_void_p, c_void_p], c_int),
+    "ab2_gemm_bf16_bcast": ([c_void_p] * 4 + [c_int] * 8 + [c_void_p], c_int),
+    "ab2_tp_reduce_rmsnorm": ([c_void_p, c_int, c_ll] + [c_void_p] * 4 + [c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "ab2_push_plan": ([c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "ab2_num_sms": ([], c_int),
     "ab2_gemm_bf16": ([c_void_p] * 4 + [c_int] * 10 + [c_void_p], c_int),
     "ab2_qknorm_rope_fwd": ([c_void_p] * 8 + [c_int] * 4 + [c_ll, c_float, c_void_p], c_int),
@@ -105,7 +109,7 @@ def get_lib():
 
 
 # Number of kernels each exported launcher enqueues (used for launch accounting).
-_KERNELS_PER_CALL = {"ab2_gemm_splitk": 2, "ab2_paged_decode": 2, "ab2_paged_decode_strided": 2, "ab2_paged_decode_noalloc": 2, "ab2_kernel_error": 0, "ab2_runtime_init": 0, "ab2_num_sms": 0}
+_KERNELS_PER_CALL = {"ab2_kernel_error_peek": 0, "ab2_gemm_splitk": 2, "ab2_paged_decode": 2, "ab2_paged_decode_strided": 2, "ab2_paged_decode_noalloc": 2, "ab2_kernel_error": 0, "ab2_runtime_init": 0, "ab2_num_sms": 0}
 LAUNCHES = {"count": 0}
 
 
@@ -162,3 +166,40 @@ def kernel_error() -> int:
     """Synchronises and returns (then clears) the device-side error word: 0 means every
     bounded wait completed; non-zero identifies the wait that gave up."""
     return int(get_lib().ab2_kernel_error())
+
+
+KERNEL_ERROR_NAMES = {1: "a TMA stage never landed", 2: "a pipeline stage was never released", 3: "an accumulator was never filled",
+                      4: "an accumulator was never drained", 5: "a peer GPU's signal never arrived", 6: "an index was out of bounds",
+                      7: "a device-side wait ran out"}
+
+
+class KernelWaitTimeout(KernelLibraryError):
+    """A bounded device-side wait gave up: the results of the step that saw it are not to be used."""
+
+
+class ErrorPoller:
+    """Polls the device error word without a synchronisation of its own: ``enqueue()`` puts a copy of
+    the word into a pinned host word behind the work already on the current stream, ``check()`` reads
+    that host word after the caller's own synchronisation and raises if a wait gave up. Step loops
+    (one optimizer step, one decode iteration) call the pair once per step."""
+
+    def __init__(self):
+        self.word = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.pending = False
+
+    def enqueue(self) -> None:
+        rc = get_lib().ab2_kernel_error_peek(self.word.data_ptr(), stream_ptr())
+        check(rc, "ab2_kernel_error_peek")
+        self.pending = True
+
+    def value(self) -> int:
+        """The word as of the last ``enqueue`` (valid after a synchronisation of that stream)."""
+        return int(self.word[0]) if self.pending else 0
+
+    def check(self, what: str = "step") -> None:
+        v = self.value()
+        self.pending = False
+        if v != 0:
+            kernel_error()          # clears the device word so the next step starts clean
+            self.word[0] = 0
+            raise KernelWaitTimeout(f"{what}: device-side wait gave up (code {v}: {KERNEL_ERROR_NAMES.get(v, 'unknown')})")

@@ -72,10 +72,7 @@ def tp_layout_of(cfg, name: str, shape: tuple, tp: int):
         elif name.endswith("o_proj") or name.endswith("down_proj"):
             a, b = j * C // tp, (j + 1) * C // tp
             out.append([(0, R, a, b)])
-        elif name in ("embed_tokens", "lm_head"):
-            a, b = j * R // tp, (j + 1) * R // tp
-            out.append([(a, b, 0, C)])
-        else:
+        else:       # norms, embeddings and the LM head are replicated on every TP rank (as in parallel.tp.shard_tensor)
             out.append([(0, R, 0, C)])
     return out
 
@@ -144,7 +141,138 @@ def _row_segments(off, C, r0, r1, c0, c1, lo, hi):
     return out
 
 
+class TPPushPlan:
+    """A re-shard plan in device memory, executed by ONE launch of ``ab2_push_plan`` per push: the
+    op table (``CopyOp`` rows), the prefix sum of the ops' work chunks and, per call, the table of
+    destination buffers (replica-major: entry ``k * tp + j`` is TP rank ``j`` of replica ``k``)."""
+
+    CHUNK = 4096          # 16-byte vectors per work item; must equal PLAN_CHUNK in ops/csrc/comm.cu
+
+    def __init__(self, ops: list, tp: int, device):
+        import numpy as np
+
+        self.ops, self.tp, self.device = list(ops), tp, torch.device(device)
+        rec = np.zeros(len(self.ops), dtype=[("src_off", "<i8"), ("dst_off", "<i8"), ("dst", "<i4"), ("rows", "<i4"), ("cols", "<i4"),
+                                             ("ld_src", "<i4"), ("ld_dst", "<i4"), ("pad", "<i4")])
+        starts, total = [], 0
+        for i, op in enumerate(self.ops):
+            if op.contiguous and op.rows * op.cols < 2 ** 31:      # one long row: 1-D tensors, whole row blocks
+                op = self.ops[i] = CopyOp(op.src_off, op.dst_tp, op.dst_off, 1, op.rows * op.cols, op.rows * op.cols, op.rows * op.cols)
+            if op.cols % 8 or op.src_off % 8 or op.dst_off % 8 or op.ld_src % 8 or op.ld_dst % 8:
+                raise ValueError(f"re-shard op {op} is not 16-byte aligned")
+            rec[i] = (op.src_off, op.dst_off, op.dst_tp, op.rows, op.cols, op.ld_src, op.ld_dst, 0)
+            starts.append(total)
+            total += -(-(op.rows * (op.cols // 8)) // self.CHUNK)
+        self.total_chunks = total
+        self.bytes = sum(op.rows * op.cols for op in self.ops) * 2
+        if self.device.type == "cuda" and self.ops:
+            self.d_ops = torch.from_numpy(rec.view(np.uint8).reshape(-1).copy()).to(self.device)
+            self.d_starts = torch.tensor(starts, dtype=torch.int32, device=self.device)
+        self._tables: dict = {}
+
+    @classmethod
+    def build(cls, cfg, store, tp: int, dst_offsets: list[dict], device=None) -> "TPPushPlan":
+        """Plan for the shard of ``store`` (a trainer's :class:`FlatParamStore`)."""
+        shapes = [tuple(p.shape) for p in store.params]
+        ops = build_push_plan(cfg, store.names, store.offsets, shapes, store.shard_range, tp, dst_offsets)
+        return cls(ops, tp, device if device is not None else store.device)
+
+    def _table(self, ptrs: list[int]) -> torch.Tensor:
+        key = tuple(ptrs)
+        t = self._tables.get(key)
+        if t is None:
+            t = self._tables[key] = torch.tensor(list(ptrs), dtype=torch.int64, device=self.device)
+        return t
+
+    def run(self, src_flat: torch.Tensor, dst_ptrs: list[int], n_rep: int, scale_ptrs: Optional[list[int]] = None,
+            pow2: bool = False) -> None:
+        """Copies (``scale_ptrs`` given: casts to block-scaled e4m3) on the current stream."""
+        if not self.ops:
+            return
+        assert len(dst_ptrs) == n_rep * self.tp
+        if self.device.type != "cuda":
+            raise RuntimeError("the plan kernel runs on CUDA; use apply_plan_reference on the CPU")
+        tab = self._table(dst_ptrs)
+        stab = self._table(scale_ptrs) if scale_ptrs is not None else None
+        rc = oplib.get_lib().ab2_push_plan(src_flat.data_ptr(), self.d_ops.data_ptr(), len(self.ops), self.d_starts.data_ptr(),
+                                           self.total_chunks, tab.data_ptr(), stab.data_ptr() if stab is not None else None, n_rep,
+                                           self.tp, int(scale_ptrs is not None), int(pow2), oplib.stream_ptr())
+        oplib.check(rc, "ab2_push_plan")
+
+
+def apply_plan_reference(ops: list, src_flat: torch.Tensor, dst_flats: list[torch.Tensor]) -> None:
+    """Plain PyTorch execution of a plan (CPU deployments and tests): ``dst_flats[j]`` is TP rank j's buffer."""
+    for op in ops:
+        src = torch.as_strided(src_flat, (op.rows, op.cols), (op.ld_src, 1), op.src_off)
+        torch.as_strided(dst_flats[op.dst_tp], (op.rows, op.cols), (op.ld_dst, 1), op.dst_off).copy_(src)
+
+
+def tp_dst_layout(model_cfg, tp: int, dtype=torch.bfloat16) -> list[dict]:
+    """``{name: element offset}`` of every parameter in the flat buffer of a TP rank (identical for
+    all ranks of a replica): the layout :class:`~areal_b200.engine.flat_params.FlatParamStore`
+    gives a rank-local model, computed from shapes alone."""
+    from ..engine.flat_params import flat_layout
+    from ..models.decoder import build_model
+    from . import tp as TP
+
+    local = build_model(TP.local_config(model_cfg, tp), dtype=dtype, device="meta")
+    names = [n for n, _ in local.named_parameters()]
+    offs, _ = flat_layout([p.numel() for _, p in local.named_parameters()], 1)
+    d = dict(zip(names, offs))
+    return [d for _ in range(tp)]
+
+
 # --------------------------------------------------------------------------- pushers
+class TPWeightPusher:
+    """Shard-direct push into tensor-parallel rollout replicas: every trainer rank re-shards ITS part
+    of the flat parameter space into the row / column slices each TP rank owns and writes them over
+    NVLink into every replica, all in one kernel launch (``ab2_push_plan``). Nothing is gathered on
+    the trainer side and no rollout rank receives bytes it does not keep (except the replicated
+    embeddings / norms, which every TP rank holds in full).
+
+    The rollout ranks' flat buffers are symmetric allocations of the world group (same size as the
+    trainer's); ``dst_layout[j]`` gives the element offset of each parameter inside TP rank j's buffer."""
+
+    def __init__(self, train_engine, rollout_client, meta: WeightUpdateMeta, tp: int):
+        self.train, self.client, self.meta, self.tp = train_engine, rollout_client, meta, tp
+        self.bus, self.split = rollout_client.bus, rollout_client.split
+        eng = train_engine
+        if eng.store.flat_param.data_ptr() not in eng._symm_handles:
+            raise RuntimeError("the trainer's parameter buffer is not in symmetric memory; cannot push peer to peer")
+        layout = tp_dst_layout(eng.model_config, tp, eng.store.dtype)
+        self.plan = TPPushPlan.build(eng.model_config, eng.store, tp, layout)
+        # replica-major table: replica k occupies rollout ranks [k * tp, (k + 1) * tp)
+        self.dst_ptrs = eng.peer_ptrs(eng.store.flat_param, self.split.rollout_ranks)
+        self.n_rep = len(self.split.rollout_ranks) // tp
+        self.seq = 0
+        self.last_ms = self.last_dev_ms = self.last_gbps = 0.0
+
+    def push(self, meta: Optional[WeightUpdateMeta] = None) -> float:
+        meta = meta or self.meta
+        eng = self.train
+        head = eng.local_index == 0
+        t0 = time.perf_counter()
+        if head:
+            self.bus.put(f"wu/{self.seq}/pause", 1)
+        for r in self.split.rollout_ranks:
+            self.bus.get(f"wu/{self.seq}/ack/{r}")
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        self.plan.run(eng.store.flat_param, self.dst_ptrs, self.n_rep)
+        ev1.record()
+        torch.cuda.current_stream().synchronize()
+        dev_ms = ev0.elapsed_time(ev1)
+        if eng.cpu_group is not None:
+            dist.barrier(group=eng.cpu_group)
+        if head:
+            self.bus.put(f"wu/{self.seq}/done", {"version": meta.version if meta.version is not None else eng.get_version() + 1})
+        self.seq += 1
+        self.last_ms = (time.perf_counter() - t0) * 1e3
+        self.last_dev_ms = dev_ms
+        self.last_gbps = self.plan.bytes * self.n_rep / max(dev_ms, 1e-6) / 1e6
+        return self.last_ms
+
+
 class DistributedWeightPusher:
     """Shard-direct push from every trainer rank into every rollout rank (replicas with the
     trainer's flat layout; TP = 1)."""

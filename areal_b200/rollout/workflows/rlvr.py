@@ -56,7 +56,7 @@ class RLVRWorkflow(RolloutWorkflow):
         self._areward = None if reward_in_process else AsyncRewardWrapper(reward_fn, timeout_seconds=reward_timeout)
 
     async def _reward(self, prompt_str, completion_str, prompt_ids, completion_ids, data):
-        kw = {k: v for k, v in data.items() if k not in ("input_ids", "messages", "prompt")}
+        kw = {k: v for k, v in data.items() if k not in ("input_ids", "messages", "prompt", "max_new_tokens_per_sample")}
         if self._reward_in_process:
             r = self.reward_fn(prompt_str, completion_str, prompt_ids, completion_ids, **kw)
             if asyncio.iscoroutine(r):
@@ -91,7 +91,9 @@ class RLVRWorkflow(RolloutWorkflow):
         g1 = self.gconfig.new(n_samples=1)
         if "max_new_tokens" in data:  # per-prompt response budget (forced-length experiments)
             g1 = g1.new(max_new_tokens=int(data["max_new_tokens"]))
-        samples = await asyncio.gather(*[self._one_sample(engine, input_ids, data, g1) for _ in range(n)])
+        per = data.get("max_new_tokens_per_sample")     # forced-length experiments: one budget per sample of the group
+        gs = [g1.new(max_new_tokens=int(per[i % len(per)])) if per else g1 for i in range(n)]
+        samples = await asyncio.gather(*[self._one_sample(engine, input_ids, data, gs[i]) for i in range(n)])
         return D.concat_padded_tensors(list(samples))
 
 
