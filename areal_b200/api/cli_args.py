@@ -408,6 +408,9 @@ class NativeInferConfig:
     max_prefill_tokens: int = 16384
     context_length: int = 32768
     mem_fraction_static: float = 0.85
+    # Colocated engines: size the KV pool as (free memory - reserve_free_gb) instead of a fraction, so
+    # the trainer sharing the GPU keeps a known amount for its activations. 0 = use the fraction.
+    reserve_free_gb: float = 0.0
     kv_cache_dtype: str = "bfloat16"
     use_cuda_graph: bool = True
     weight_dtype: str = "bfloat16"  # or float8_e4m3fn (block-scaled)

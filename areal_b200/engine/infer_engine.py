@@ -184,6 +184,7 @@ class NativeInferenceEngine(InferenceEngine):
             self._init_cuda_state()
         elif self.device.type == "cuda":
             self.stream = torch.cuda.Stream(device=self.device)
+        self._t_start = time.perf_counter()
         self._thread = threading.Thread(target=self._engine_main, name="infer-engine", daemon=True)
         self._thread.start()
         if start_executor:
@@ -233,7 +234,10 @@ class NativeInferenceEngine(InferenceEngine):
         cfg, ic = self.model_config, self.icfg
         free, total = torch.cuda.mem_get_info()
         per_page = cfg.num_layers * 2 * ic.page_size * cfg.num_kv_heads * cfg.head_dim * 2
-        budget = int(free * ic.mem_fraction_static) - (2 << 30)
+        if getattr(ic, "reserve_free_gb", 0.0) > 0:
+            budget = free - int(ic.reserve_free_gb * (1 << 30))
+        else:
+            budget = int(free * ic.mem_fraction_static) - (2 << 30)
         want = ic.max_running_requests * (ic.context_length // ic.page_size + 1)
         n_pages = max(16, min(want, budget // per_page))
         if getattr(ic, "num_pages", None):
@@ -274,7 +278,10 @@ class NativeInferenceEngine(InferenceEngine):
         self.n_splits = 4
         self.s_part_o = torch.zeros(B * cfg.num_heads * self.n_splits * cfg.head_dim, dtype=torch.float32, device=dev)
         self.s_part_ml = torch.zeros(B * cfg.num_heads * self.n_splits * 2, dtype=torch.float32, device=dev)
-        self.stream = torch.cuda.Stream(device=dev)
+        # higher priority than the default stream: when a trainer shares the GPU, the short decode
+        # kernels get the SMs that free up first instead of queueing behind its long ones
+        self.stream = torch.cuda.Stream(device=dev, priority=-1)
+        self._err_poll = oplib.ErrorPoller()
         oplib.get_lib().ab2_runtime_init()
         logger.info("KV cache: %d pages x %d tokens (%.1f GB)", n_pages, ic.page_size, n_pages * per_page / 2 ** 30)
 
@@ -508,6 +515,7 @@ class NativeInferenceEngine(InferenceEngine):
                     time.sleep(0.0005)
                     continue
                 self._idle.clear()
+                t_busy = time.perf_counter()
                 if self.device.type == "cuda" and self._recompute_decode:
                     with torch.cuda.stream(self.stream), torch.no_grad():
                         self._step_recurrent()
@@ -517,6 +525,7 @@ class NativeInferenceEngine(InferenceEngine):
                 else:
                     with torch.no_grad():
                         self._step_recurrent() if self._recompute_decode else self._step_cpu()
+                self.stats["busy_seconds"] += time.perf_counter() - t_busy
         except BaseException as e:  # surface to waiting clients
             import traceback
 
@@ -927,7 +936,9 @@ class NativeInferenceEngine(InferenceEngine):
         """One device-to-host copy of the sampled tokens and logprobs (pinned), one sync."""
         self.h_out[0, :n].copy_(self.s_out_tok[:n], non_blocking=True)
         self.h_out[1, :n].copy_(self.s_out_lp[:n].view(torch.int32), non_blocking=True)
+        self._err_poll.enqueue()            # the error word rides along with the step's only synchronisation
         torch.cuda.current_stream().synchronize()
+        self._err_poll.check("rollout engine step")
         return self.hn_out_tok[:n].tolist(), self.hn_out_lp[:n].tolist()
 
     def _sample_cuda(self, logits: torch.Tensor, seqs: list[_Seq]):
@@ -1062,7 +1073,9 @@ class NativeInferenceEngine(InferenceEngine):
         return self._graphs[B]
 
     def export_stats(self) -> dict[str, float]:
-        return {f"infer/{k}": float(v) for k, v in self.stats.items()}
+        out = {f"infer/{k}": float(v) for k, v in self.stats.items()}
+        out["infer/alive_seconds"] = time.perf_counter() - self._t_start
+        return out
 
 
 def _apply_top_k_top_p(z: torch.Tensor, top_k: int, top_p: float) -> torch.Tensor:

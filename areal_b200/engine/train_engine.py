@@ -68,6 +68,8 @@ class B200TrainEngine(TrainEngine):
         self._weight_pusher = None
         self._grad_reducer = None
         self.last_step_stats: dict = {}
+        self.d2h_bytes = 0          # bytes of results this engine read back from the device (losses, log-probs, optimizer status)
+        self._err_poll = None
 
     # ------------------------------------------------------------------ process groups
     def create_process_group(self, parallel_strategy: Optional[ParallelStrategy] = None):
@@ -696,6 +698,7 @@ class B200TrainEngine(TrainEngine):
         losses = self.forward_backward_batch(mbl, process)
         stats = self.optimizer_step()
         stats["loss"] = float(torch.stack(losses).sum()) if losses else 0.0
+        self.d2h_bytes += 4
         if getattr(self, "pp_size", 1) > 1:
             stats["loss"] = float(self._pp_runner.broadcast_loss(torch.tensor(stats["loss"])))
         return stats
@@ -766,9 +769,73 @@ class B200TrainEngine(TrainEngine):
                 upd = getattr(layer.mlp, "update_expert_bias", None)
                 if upd is not None:
                     upd(self._shard_group)
-        st = res["state"].tolist()
+        st = self._read_step_state(res["state"])
         self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
         return dict(self.last_step_stats)
+
+    def _read_step_state(self, state: torch.Tensor) -> list:
+        """The optimizer's 4-float status, read at the one host synchronisation of the step. The
+        device error word travels with it: a bounded wait that gave up anywhere in this step (a peer
+        that never signalled, a lost copy) means gradients or parameters may be incomplete. Every
+        trainer rank learns of it (MAX over the host group) and raises, so no rank carries on alone."""
+        poll = None
+        if self.device.type == "cuda":
+            if self._err_poll is None:
+                from ..ops import lib as oplib
+
+                self._err_poll = oplib.ErrorPoller()
+            poll = self._err_poll
+            poll.enqueue()
+        st = state.tolist()
+        self.d2h_bytes += state.numel() * state.element_size()
+        code = poll.value() if poll is not None else 0
+        if self._cpu_group is not None and os.environ.get("AREAL_SKIP_ERROR_EXCHANGE", "0") != "1":
+            t = torch.tensor([code], dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self._cpu_group)
+            code = max(code, int(t[0]))
+        if code != 0:
+            from ..ops import lib as oplib
+
+            if poll is not None:
+                poll.pending = False
+            oplib.kernel_error()        # clear the local word
+            raise oplib.KernelWaitTimeout(f"optimizer step: a device-side wait gave up on some trainer rank (code {code}: "
+                                          f"{oplib.KERNEL_ERROR_NAMES.get(code, 'unknown')}); the step's update must not be used")
+        if poll is not None:
+            poll.pending = False
+        return st
+
+    def use_library_collectives(self, on: bool = True) -> None:
+        """Switches this engine between its fused peer-memory kernels and the library-collective
+        path at a step boundary (all trainer ranks must switch at the same step): NCCL
+        reduce-scatter + all-gather around the optimizer, NCCL all-to-all around attention, NCCL
+        broadcast for the weight update. Used to measure the fused path against that baseline."""
+        if on:
+            if getattr(self, "_fused_saved", None) is None:
+                self._fused_saved = dict(reducer=self._grad_reducer, sp=getattr(self, "_sp_fused", None), pusher=self._weight_pusher)
+            self._grad_reducer = None
+            if getattr(self, "_sp_fused", None) is not None:
+                from ..parallel.ulysses import install_fused_ulysses
+
+                install_fused_ulysses(self.model, None)
+            if self._weight_pusher is not None and hasattr(self.rollout_engine, "remote_ranks"):
+                from ..parallel.weight_push import BroadcastWeightPusher
+
+                old = self._weight_pusher
+                new = BroadcastWeightPusher(self, self.rollout_engine, self.rollout_engine.wu_group)
+                new.seq = old.seq
+                self._weight_pusher = new
+        elif getattr(self, "_fused_saved", None) is not None:
+            sv = self._fused_saved
+            self._grad_reducer = sv["reducer"]
+            if sv["sp"] is not None:
+                from ..parallel.ulysses import install_fused_ulysses
+
+                install_fused_ulysses(self.model, sv["sp"])
+            if sv["pusher"] is not None:
+                sv["pusher"].seq = self._weight_pusher.seq
+                self._weight_pusher = sv["pusher"]
+            self._fused_saved = None
 
     def _reduce_scatter_flat(self, store, group):
         """Sum of ``store.flat_grad`` over ``group``; returns this rank's shard."""
@@ -805,7 +872,7 @@ class B200TrainEngine(TrainEngine):
                 upd = getattr(layer.mlp, "update_expert_bias", None)
                 if upd is not None:
                     upd(self._shard_group)
-        st = res["state"].tolist()
+        st = self._read_step_state(res["state"])
         self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
         return dict(self.last_step_stats)
 
@@ -862,7 +929,9 @@ class B200TrainEngine(TrainEngine):
                     dist.all_gather(parts, r.contiguous(), group=self._sp_group)
                     full.append(torch.cat(parts))
                 res = tuple(full)
-            return tuple(D.unpad_logits(r, pad).float().cpu() for r in res)
+            host = tuple(D.unpad_logits(r, pad).float().cpu() for r in res)
+            self.d2h_bytes += sum(h.numel() * 4 for h in host)
+            return host
 
         outs = self._pp_share(self.forward_backward_batch(mbl, process, forward_only=True))
         n_out = len(outs[0]) if outs else 1

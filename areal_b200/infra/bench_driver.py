@@ -1,17 +1,25 @@
 """Drives the asynchronous-GRPO throughput benchmark through the public trainer API.
 
 N = 1: trainer and rollout engine colocated on one GPU (shared bf16 weights, concurrent
-generation and training). N >= 2: trainer ranks ``[0, N/2)`` and rollout ranks ``[N/2, N)`` of
-one ``torch.distributed`` world; gradients are reduced and parameters refreshed by the fused
-peer-memory kernels, weights are pushed shard-direct over NVLink after every step.
+generation and training). N >= 2: trainer ranks ``[0, T)`` and rollout ranks ``[T, N)`` of one
+``torch.distributed`` world (``T = N / 2`` unless ``--train-gpus``): the trainers shard the
+optimizer state over all of them (ZeRO) and split every packed micro-batch over groups of
+``--sp`` ranks (Ulysses, projections fused with the exchanges); the rollout ranks form
+tensor-parallel replicas of ``--rollout-tp`` GPUs (partial sums exchanged from the GEMM epilogue,
+decode steps graph captured); weights are pushed shard-direct over NVLink after every step and
+re-sharded into the tensor-parallel layout in flight.
 
 Measured quantities (rank 0 reports):
 * ``value``: trained tokens per second over K steps, device-timed with CUDA events on the
   trainer ranks (barrier + synchronize on both sides, max over ranks);
 * ``e2e``: the same metric over K further steps, wall-clock around ``PPOTrainer.train`` (the
   user-facing call), which every step copies the step's inputs host->device from pinned memory
-  and reads the step's statistics back device->host; byte counts are accumulated from the
-  tensors actually copied.
+  and reads the step's results back device->host; byte counts are accumulated from the
+  tensors actually copied;
+* ``config.nccl_path_tokens_per_s`` (N >= 2): a few more steps of the SAME job with this
+  repository's library-collective path switched on (NCCL reduce-scatter + all-gather around the
+  optimizer, NCCL all-to-all around attention, NCCL broadcast weight update): the baseline that
+  the fused kernels are there to beat. It is not the reference implementation.
 """
 from __future__ import annotations
 
@@ -39,7 +47,8 @@ class _ByteCounter:
 
 
 def _instrument_transfers(engine):
-    """Counts host->device bytes of micro-batch inputs and device->host bytes of step results."""
+    """Counts host->device bytes of micro-batch inputs; device->host bytes are counted by the
+    engine itself wherever it reads results back (``engine.d2h_bytes``)."""
     orig = engine._mb_to_device
 
     def counted(mb):
@@ -48,29 +57,47 @@ def _instrument_transfers(engine):
                 _ByteCounter.h2d += v.numel() * v.element_size()
         return orig(mb)
     engine._mb_to_device = counted
-    orig_step = engine.optimizer_step
-
-    def counted_step():
-        out = orig_step()
-        _ByteCounter.d2h += 16  # the 4-float optimizer state read back per step
-        return out
-    engine.optimizer_step = counted_step
 
 
-def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOConfig:
-    bs = args.prompts_per_gpu_pair
+def resolve_layout(args, world: int) -> dict:
+    """GPU roles of an N-GPU job: one rule for every N."""
+    if world == 1:
+        return dict(n_train=1, n_rollout=1, sp=1, dp=1, rollout_tp=1, replicas=1, colocated=True)
+    n_train = args.train_gpus or world // 2
+    n_roll = world - n_train
+    if n_train < 1 or n_roll < 1:
+        raise SystemExit("--train-gpus must leave at least one trainer and one rollout GPU")
+    sp = args.sp or min(4, n_train)
+    while n_train % sp:
+        sp -= 1
+    tp = args.rollout_tp or (2 if n_roll >= 2 and n_roll % 2 == 0 else 1)
+    if n_roll % tp:
+        raise SystemExit(f"--rollout-tp {tp} does not divide the {n_roll} rollout GPUs")
+    return dict(n_train=n_train, n_rollout=n_roll, sp=sp, dp=n_train // sp, rollout_tp=tp, replicas=n_roll // tp, colocated=False)
+
+
+def _make_config(args, lay: dict, fileroot: str) -> GRPOConfig:
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    # Activation memory policy: one trainer GPU that also holds the whole optimizer state
-    # (colocated, or 1 trainer + 1 rollout) has ~30 GB left, so it recomputes activations
-    # (colocated) or uses small micro-batches; from 2 trainer ranks on the optimizer state is
-    # sharded and full activations of 8k-token micro-batches fit.
-    ckpt = getattr(args, "grad_ckpt", -1)
-    if ckpt < 0:
-        ckpt = 1 if world == 1 else 0
+    global_prompts = max(1, int(round(args.prompts_per_gpu * world)))
+    # batches travel leader -> head: a head merges the batches of its `feeders` leaders
+    feeders = max(1, lay["replicas"] // lay["dp"])
+    bs = max(1, -(-global_prompts // (lay["dp"] * feeders)))
+    global_prompts = bs * lay["dp"] * feeders
     mb_tokens = args.max_tokens_per_mb
     if mb_tokens <= 0:
-        mb_tokens = 16384 if ckpt else (4096 if n_pairs == 1 else 8192)
-    args._resolved = {"gradient_checkpointing": bool(ckpt), "max_tokens_per_mb": mb_tokens}
+        mb_tokens = 16384 if lay["colocated"] else 8192
+    elif lay["colocated"]:
+        # one GPU holds the whole optimizer state, the gradients AND the KV cache: half-size micro-batches
+        mb_tokens = min(mb_tokens, 16384)
+    ctx = args.prompt_len + args.max_len + 64
+    args._resolved = {"gradient_checkpointing": bool(args.grad_ckpt), "max_tokens_per_mb": mb_tokens,
+                      "prompts_per_step": global_prompts, "prompts_per_batch": bs}
+    if lay["colocated"]:
+        # what the trainer needs beside its resident state: activations of one recomputed micro-batch,
+        # layer-input checkpoints, LM-head chunks (about 0.75 MB per micro-batch token) plus allocator slack
+        infer = dict(reserve_free_gb=6.0 + mb_tokens * 0.75e-3, max_running_requests=256)
+    else:
+        infer = dict(mem_fraction_static=0.88, max_running_requests=512)
     return GRPOConfig(
         experiment_name="bench-async-grpo", trial_name="t0", total_train_epochs=1000, seed=1,
         cluster=ClusterSpecConfig(fileroot=fileroot),
@@ -79,12 +106,10 @@ def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOCon
                                           max_tokens=args.prompt_len + args.max_len + 8, temperature=1.0, ignore_eos=True),
         rollout=InferenceEngineConfig(max_concurrent_rollouts=bs * (args.staleness + 1), consumer_batch_size=bs,
                                       max_head_offpolicyness=args.staleness),
-        native_infer=NativeInferConfig(max_running_requests=max_running, page_size=64,
-                                       context_length=args.prompt_len + args.max_len + 64, mem_fraction_static=0.35 if n_pairs == 1 and int(os.environ.get('WORLD_SIZE', '1')) == 1 else 0.6,
-                                       max_prefill_tokens=16384,
-                                       retain_kv_on_weight_update=bool(getattr(args, "retain_kv", 1)),
-                                       enable_prefix_sharing=bool(getattr(args, "prefix_sharing", 1))),
-        actor=PPOActorConfig(init_from_scratch=True, dtype="bfloat16", gradient_checkpointing=bool(ckpt),
+        native_infer=NativeInferConfig(page_size=64, context_length=ctx, max_prefill_tokens=16384,
+                                       retain_kv_on_weight_update=bool(args.retain_kv),
+                                       enable_prefix_sharing=bool(args.prefix_sharing), **infer),
+        actor=PPOActorConfig(init_from_scratch=True, dtype="bfloat16", gradient_checkpointing=bool(args.grad_ckpt),
                              optimizer=OptimizerConfig(lr=1e-6, weight_decay=0.01, gradient_clipping=1.0),
                              mb_spec=MicroBatchSpec(max_tokens_per_mb=mb_tokens),
                              use_decoupled_loss=True, recompute_logprob=True, kl_ctl=0.0, ppo_n_minibatches=1,
@@ -99,11 +124,11 @@ def _make_config(args, n_pairs: int, max_running: int, fileroot: str) -> GRPOCon
 
 def _dataset(args, model_cfg, seed: int):
     return RandomTokenDataset(size=4096, prompt_len=args.prompt_len, vocab_size=model_cfg.vocab_size, seed=seed,
-                              median_len=args.median_len, max_len=args.max_len, min_len=16)
+                              median_len=args.median_len, max_len=args.max_len, min_len=16, n_samples=args.group_size)
 
 
-def _tokens_of(history) -> float:
-    return float(sum(h.get("ppo_actor/n_tokens", 0.0) for h in history))
+def _sum_of(history, key: str) -> float:
+    return float(sum(h.get(key, 0.0) for h in history))
 
 
 def run_async_grpo_bench(args, clock_sampler_cls) -> Optional[dict]:
@@ -119,44 +144,52 @@ def run_async_grpo_bench(args, clock_sampler_cls) -> Optional[dict]:
     torch.cuda.set_device(local_rank)
     model_cfg = preset(args.model)
     fileroot = f"/tmp/areal_bench_{os.getpid()}"
-    W, K = args.warmup, args.steps
+    lay = resolve_layout(args, world)
+    cfg = _make_config(args, lay, fileroot)
 
     if world == 1:
-        cfg = _make_config(args, 1, max_running=256, fileroot=fileroot)
         ds = _dataset(args, model_cfg, seed=1)
         trainer = PPOTrainer(cfg, ds, model_config=model_cfg)
         _instrument_transfers(trainer.actor)
         wf = RLVRWorkflow(bernoulli_reward_fn, cfg.gconfig, reward_in_process=True)
-        return _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, parallelism="colocated-1gpu")
+        return _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, lay, parallelism="colocated-1gpu")
 
     # ---------------------------------------------------------------- split world
     from .spmd import init_split_world, make_split_trainer, run_rollout_rank
 
     dev = torch.device("cuda", local_rank)
-    n_train = world // 2
-    split, groups, bus = init_split_world(n_train, dev)
-    cfg = _make_config(args, n_train, max_running=256, fileroot=fileroot)
+    split, groups, bus = init_split_world(lay["n_train"], dev, sp=lay["sp"], rollout_tp=lay["rollout_tp"])
+    par = (f"train:d{lay['dp']}s{lay['sp']} (ZeRO over {lay['n_train']})+rollout:{lay['replicas']}xtp{lay['rollout_tp']}")
     if split.is_trainer:
         ds = _dataset(args, model_cfg, seed=1)  # only sizes the trainer's bookkeeping
         trainer = make_split_trainer(cfg, model_cfg, split, groups, bus, ds, seed=1)
         _instrument_transfers(trainer.actor)
-        res = _timed_loop(args, trainer, None, clock_sampler_cls, world, rank, model_cfg,
-                          parallelism=f"train:dp{n_train}+rollout:dp{world - n_train}", groups=groups)
+        res = _timed_loop(args, trainer, None, clock_sampler_cls, world, rank, model_cfg, lay, parallelism=par, groups=groups)
         if rank == 0:
             bus.put("exit", 1)
         dist.barrier(group=groups["world_cpu"])
+        if rank == 0 and res is not None:
+            rs = [bus.poll(f"rollout_stats/{r}") for r in split.leaders]
+            rs = [x for x in rs if x]
+            if rs:
+                busy = [x.get("infer/busy_seconds", 0.0) / max(1e-9, x.get("infer/alive_seconds", 1.0)) for x in rs]
+                res["config"]["rollout_busy_fraction"] = round(sum(busy) / len(busy), 3)
+                res["config"]["rollout_decode_steps"] = int(sum(x.get("infer/decode_steps", 0) for x in rs))
+                res["config"]["rollout_generated_tokens"] = int(sum(x.get("infer/generated_tokens", 0) for x in rs))
         return res if rank == 0 else None
     ds = _dataset(args, model_cfg, seed=1000 + rank)
     wf = RLVRWorkflow(bernoulli_reward_fn, cfg.gconfig, reward_in_process=True)
-    run_rollout_rank(cfg, model_cfg, split, groups, bus, ds, wf, dev, seed=1)
+    worker = run_rollout_rank(cfg, model_cfg, split, groups, bus, ds, wf, dev, seed=1)
+    if split.is_leader(rank):
+        bus.put(f"rollout_stats/{rank}", worker.engine.export_stats())
     dist.barrier(group=groups["world_cpu"])
     return None
 
 
-def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, parallelism: str, groups=None):
+def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, lay, parallelism: str, groups=None):
     W, K = args.warmup, args.steps
-    n_train = max(1, world // 2) if world > 1 else 1
     cpu_group = groups["cpu"] if groups else None
+    actor = trainer.actor
 
     def sync():
         torch.cuda.synchronize()
@@ -180,57 +213,93 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, pa
     launches = oplib.launch_count() - launches0
     trainer.start_step += K
     ms_a = e0.elapsed_time(e1)
-    tok_a = _tokens_of(hist_a)
+    tok_a = _sum_of(hist_a, "ppo_actor/n_tokens")
+    resp_a = _sum_of(hist_a, "ppo_actor/n_valid_tokens")
     # ---- region B: end-to-end through the public API, wall clock
-    _ByteCounter.h2d = _ByteCounter.d2h = 0
+    _ByteCounter.h2d = 0
+    actor.d2h_bytes = 0
     sync()
     t0 = time.perf_counter()
     hist_b = trainer.train(workflow=wf, max_steps=K)
     sync()
     wall_b = time.perf_counter() - t0
-    tok_b = _tokens_of(hist_b)
-    stats = torch.tensor([ms_a, tok_a, wall_b, tok_b, float(_ByteCounter.h2d), float(_ByteCounter.d2h), float(launches)],
-                         dtype=torch.float64)
+    trainer.start_step += K
+    tok_b = _sum_of(hist_b, "ppo_actor/n_tokens")
+    h2d_b, d2h_b = float(_ByteCounter.h2d), float(actor.d2h_bytes)
+    push_ms = getattr(getattr(actor, "_weight_pusher", None), "last_ms", None)
+    push_dev_ms = getattr(getattr(actor, "_weight_pusher", None), "last_dev_ms", None)
+    # ---- region C: the same job on the library-collective path (NCCL), a few steps
+    Kc = args.nccl_steps if args.nccl_steps >= 0 else (max(2, K // 5) if world >= 2 else 0)
+    ms_c = tok_c = 0.0
+    if Kc > 0 and world >= 2:
+        actor.use_library_collectives(True)
+        trainer.train(workflow=wf, max_steps=1)          # NCCL communicators connect outside the timed steps
+        trainer.start_step += 1
+        sync()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        hist_c = trainer.train(workflow=wf, max_steps=Kc)
+        c1.record()
+        sync()
+        trainer.start_step += Kc
+        ms_c, tok_c = c0.elapsed_time(c1), _sum_of(hist_c, "ppo_actor/n_tokens")
+        push_ms_c = getattr(getattr(actor, "_weight_pusher", None), "last_ms", None)
+    stats = torch.tensor([ms_a, tok_a, wall_b, tok_b, h2d_b, d2h_b, float(launches), resp_a, ms_c, tok_c], dtype=torch.float64)
     if cpu_group is not None:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=cpu_group)
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM, group=cpu_group)
-        ms_a, wall_b = float(mx[0]), float(mx[2])
-        # ``ppo_actor/n_tokens`` is exported after a reduction over the trainer ranks, so every
-        # rank already holds the GLOBAL token count of a step: take it once, do not sum it again
-        tok_a, tok_b = float(mx[1]), float(mx[3])
-        h2d, d2h, launches = float(sm[4]), float(sm[5]), int(sm[6])
-    else:
-        h2d, d2h = float(stats[4]), float(stats[5])
-    push_ms = getattr(getattr(trainer.actor, "_weight_pusher", None), "last_ms", None)
+        ms_a, wall_b, ms_c = float(mx[0]), float(mx[2]), float(mx[8])
+        # ``ppo_actor/n_tokens`` is exported after a reduction over the trainer ranks that saw different
+        # tokens, so every rank already holds the GLOBAL count of a step: take it once, do not sum it again
+        tok_a, tok_b, resp_a, tok_c = float(mx[1]), float(mx[3]), float(mx[7]), float(mx[9])
+        h2d_b, d2h_b, launches = float(sm[4]), float(sm[5]), int(sm[6])
     phases = {}
     for h in hist_a:
         for k_, v_ in h.items():
             if k_.startswith("timeperf/"):
                 phases[k_[9:]] = phases.get(k_[9:], 0.0) + float(v_) / max(1, len(hist_a))
+    stale = [h.get("ppo_actor/update/staleness/avg") for h in hist_a if h.get("ppo_actor/update/staleness/avg") is not None]
+    stale_max = [h.get("ppo_actor/update/staleness/max") for h in hist_a if h.get("ppo_actor/update/staleness/max") is not None]
     trainer.close()
     if rank != 0:
         return None
     value = tok_a / (ms_a / 1e3)
     e2e = tok_b / wall_b
-    seq_len = args.prompt_len + args.median_len
+    step_s = max(1e-9, phases.get("step", ms_a / 1e3 / K))
+    cfgd = {"model": args.model, "preset": args.preset, "length_scale": args.length_scale,
+            "global_batch": args._resolved["prompts_per_step"] * args.group_size,
+            "prompts_per_step": args._resolved["prompts_per_step"], "group_size": args.group_size,
+            "seq_len": args.prompt_len + args.median_len, "prompt_len": args.prompt_len, "response_median": args.median_len,
+            "response_cap": args.max_len, "response_lengths": "log-normal per sample (sigma 0.6), forced",
+            "parallelism": parallelism, "trainer_gpus": lay["n_train"], "rollout_gpus": lay["n_rollout"] if world > 1 else 1,
+            "ulysses_sp": lay["sp"], "rollout_tp": lay["rollout_tp"], "rollout_replicas": lay["replicas"],
+            "max_staleness": args.staleness, "prox_logp_method": args.prox_logp_method, **args._resolved,
+            "loss": "decoupled PPO (GRPO advantages), fp32 master weights + AdamW moments",
+            "inflight_weight_update": "running requests keep their KV cache" if args.retain_kv else "running requests are re-prefilled",
+            "prefix_sharing": bool(args.prefix_sharing),
+            "decode_switches": {k_: os.environ.get(k_, "0") for k_ in ("AB2_PDL", "AB2_DECODE_SPLITK")},
+            "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
+            "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms, "weight_sync_device_ms": push_dev_ms,
+            "tokens_counted": "prompt + response tokens of the trained sequences",
+            "response_tokens_per_s": resp_a / (ms_a / 1e3),
+            "trainer_busy_fraction": round(1.0 - phases.get("rollout", 0.0) / step_s, 3),
+            "staleness_avg": round(sum(stale) / len(stale), 3) if stale else None,
+            "staleness_max": max(stale_max) if stale_max else None,
+            "phase_seconds_per_step": {k_: round(v_, 4) for k_, v_ in sorted(phases.items())}}
+    if ms_c > 0:
+        cfgd["nccl_path_tokens_per_s"] = tok_c / (ms_c / 1e3)
+        cfgd["nccl_path_steps"] = Kc
+        cfgd["nccl_path_weight_sync_ms"] = push_ms_c
+        cfgd["fused_over_nccl_path"] = round(value / max(1e-9, cfgd["nccl_path_tokens_per_s"]), 3)
+        cfgd["nccl_path_note"] = ("this repository's own library-collective path (NCCL reduce-scatter / all-gather / all-to-all / "
+                                  "broadcast), same job and step loop; not the reference implementation")
     return {
         "metric": "async GRPO trained tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms_a / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (uniform-random prompts, forced log-normal response lengths, Bernoulli rewards, random-init weights)",
-        "impl": "native",
-        "config": {"model": args.model, "global_batch": args.prompts_per_gpu_pair * args.group_size * n_train,
-                   "seq_len": seq_len, "prompt_len": args.prompt_len, "response_median": args.median_len,
-                   "response_cap": args.max_len, "group_size": args.group_size, "parallelism": parallelism,
-                   "max_staleness": args.staleness, "prox_logp_method": args.prox_logp_method, **getattr(args, "_resolved", {}),
-                   "inflight_weight_update": "running requests keep their KV cache" if getattr(args, "retain_kv", 1) else "running requests are re-prefilled",
-                   "prefix_sharing": bool(getattr(args, "prefix_sharing", 1)),
-                   "decode_switches": {k_: os.environ.get(k_, "0") for k_ in ("AB2_PDL", "AB2_DECODE_SPLITK")},
-                   "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
-                   "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms,
-                   "phase_seconds_per_step": {k_: round(v_, 4) for k_, v_ in sorted(phases.items())}},
-        "clocks": clocks,
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d / K, "d2h_bytes_per_step": d2h / K},
+        "impl": "native", "config": cfgd, "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d_b / K, "d2h_bytes_per_step": d2h_b / K},
         "gpu_launches": int(launches),
     }

@@ -32,35 +32,81 @@ logger = alog.getLogger("spmd")
 
 
 class SplitWorld:
-    """Rank bookkeeping of a trainer / rollout split."""
+    """Rank bookkeeping of a trainer / rollout split.
 
-    def __init__(self, n_train: int, n_rollout: int, rank: Optional[int] = None):
+    Trainer ranks ``[0, n_train)`` form ``dp = n_train / sp`` data-parallel replicas of ``sp``
+    sequence-parallel ranks each (rank ``d * sp + s``); the first rank of a replica is its head.
+    Rollout ranks ``[n_train, world)`` form ``n_rollout / rollout_tp`` tensor-parallel engine
+    replicas of consecutive ranks; the first rank of a replica is its leader (the only one that
+    takes requests and produces batches). Leaders feed trainer heads round-robin: with more
+    leaders than heads a head merges several leaders' batches, with fewer a leader deals its
+    batches to several heads in turn."""
+
+    def __init__(self, n_train: int, n_rollout: int, rank: Optional[int] = None, sp: int = 1, rollout_tp: int = 1):
+        if n_train % max(1, sp) or n_rollout % max(1, rollout_tp):
+            raise ValueError(f"sp={sp} must divide the {n_train} trainer ranks and rollout_tp={rollout_tp} the {n_rollout} rollout ranks")
         self.n_train, self.n_rollout = n_train, n_rollout
+        self.sp, self.rollout_tp = max(1, sp), max(1, rollout_tp)
+        self.dp = n_train // self.sp
+        self.n_replicas = n_rollout // self.rollout_tp
         self.world = n_train + n_rollout
         self.rank = int(os.environ.get("RANK", "0")) if rank is None else rank
         self.train_ranks = list(range(n_train))
         self.rollout_ranks = list(range(n_train, self.world))
+        self.heads = [d * self.sp for d in range(self.dp)]
+        self.leaders = [n_train + k * self.rollout_tp for k in range(self.n_replicas)]
+        if self.n_replicas >= self.dp:
+            if self.n_replicas % self.dp:
+                raise ValueError(f"{self.n_replicas} rollout replicas cannot be dealt evenly to {self.dp} trainer replicas")
+        elif self.dp % self.n_replicas:
+            raise ValueError(f"{self.dp} trainer replicas cannot share {self.n_replicas} rollout replicas evenly")
 
     @property
     def is_trainer(self) -> bool:
         return self.rank < self.n_train
 
+    # ---- rollout side
+    def replica_of(self, rollout_rank: int) -> int:
+        return (rollout_rank - self.n_train) // self.rollout_tp
+
+    def tp_rank_of(self, rollout_rank: int) -> int:
+        return (rollout_rank - self.n_train) % self.rollout_tp
+
+    def replica_ranks(self, k: int) -> list[int]:
+        return [self.n_train + k * self.rollout_tp + j for j in range(self.rollout_tp)]
+
+    def is_leader(self, rank: Optional[int] = None) -> bool:
+        return (self.rank if rank is None else rank) in self.leaders
+
+    def consumers_of(self, leader: int) -> list[int]:
+        """Trainer heads that a rollout leader produces batches for."""
+        k = self.leaders.index(leader)
+        if self.n_replicas >= self.dp:
+            return [self.heads[k % self.dp]]
+        return [h for i, h in enumerate(self.heads) if i % self.n_replicas == k]
+
+    # ---- trainer side
     def rollout_peers_of(self, train_rank: int) -> list[int]:
-        """Rollout ranks that feed ``train_rank`` (round-robin pairing)."""
-        return [r for i, r in enumerate(self.rollout_ranks) if i % self.n_train == train_rank]
+        """Rollout leaders whose batches ``train_rank`` consumes (empty unless it is a head)."""
+        if train_rank not in self.heads:
+            return []
+        return [l for l in self.leaders if train_rank in self.consumers_of(l)]
 
     def trainer_of(self, rollout_rank: int) -> int:
-        return (rollout_rank - self.n_train) % self.n_train
+        return self.consumers_of(self.leaders[self.replica_of(rollout_rank)])[0]
 
 
-def build_split_groups(split: SplitWorld, sp_size: int = 1, use_cuda: bool = True) -> dict:
-    """Creates, collectively on every rank of the world, the process groups of the trainer
-    side (``dist.new_group`` must be entered by all ranks in the same order). Returns the
-    groups this rank belongs to: ``shard`` (all trainers), ``cpu`` (gloo mirror), ``dp`` and
-    ``sp`` (this trainer's data- / sequence-parallel group) and ``world_cpu`` (gloo, all ranks)."""
+def build_split_groups(split: SplitWorld, sp_size: Optional[int] = None, use_cuda: bool = True) -> dict:
+    """Creates, collectively on every rank of the world, all process groups of the deployment
+    (``dist.new_group`` must be entered by all ranks in the same order). Returns the groups this
+    rank belongs to: ``shard`` (all trainers), ``cpu`` (its gloo mirror), ``dp`` / ``sp`` (this
+    trainer's data- / sequence-parallel group), ``wu`` (trainer head + every rollout rank: the
+    broadcast baseline of the weight update), ``rtp`` / ``rtp_cpu`` (this rollout rank's
+    tensor-parallel replica: data plane and gloo control plane) and ``world_cpu`` (gloo, all ranks)."""
+    sp_size = split.sp if sp_size is None else sp_size
     tr = split.train_ranks
     n = len(tr)
-    out: dict = {"shard": None, "cpu": None, "dp": None, "sp": None}
+    out: dict = {"shard": None, "cpu": None, "dp": None, "sp": None, "rtp": None, "rtp_cpu": None}
     out["world_cpu"] = dist.new_group(list(range(split.world)), backend="gloo")
     if n > 1:
         out["shard"] = dist.new_group(tr)
@@ -81,6 +127,13 @@ def build_split_groups(split: SplitWorld, sp_size: int = 1, use_cuda: bool = Tru
             g = dist.new_group(ranks)
             if me in ranks:
                 out["dp"] = g
+    if split.rollout_tp > 1:
+        for k in range(split.n_replicas):
+            ranks = split.replica_ranks(k)
+            g = dist.new_group(ranks)
+            gc = dist.new_group(ranks, backend="gloo") if use_cuda else dist.new_group(ranks)
+            if me in ranks:
+                out["rtp"], out["rtp_cpu"] = g, gc
     return out
 
 
@@ -142,7 +195,7 @@ class RemoteRolloutClient(InferenceEngine):
 
         parts = []
         for r in self.my_rollout_ranks:
-            key = f"traj/{r}/{self._seq[r]}"
+            key = f"traj/{r}/{self.train_rank}/{self._seq[r]}"
             parts.append(self.bus.get(key))
             self.bus.delete(key)
             self._seq[r] += 1
@@ -177,20 +230,33 @@ class RemoteRolloutClient(InferenceEngine):
 
 
 class RolloutWorker:
-    """Main loop of a rollout rank."""
+    """Main loop of a rollout rank. A replica leader produces batches and deals them to the trainer
+    heads it feeds; the other ranks of a tensor-parallel replica only take part in weight updates
+    (their engine follows the leader's schedule in lock-step). ``staging``: a full flat parameter
+    buffer in the trainer's layout for the broadcast path of a tensor-parallel replica (every rank
+    receives the whole buffer and keeps its slices)."""
 
     def __init__(self, engine, bus: MessageBus, split: SplitWorld, dataloader, workflow, workflow_kwargs=None,
-                 flat_param: Optional[torch.Tensor] = None, wu_group=None):
+                 flat_param: Optional[torch.Tensor] = None, wu_group=None, staging=None):
         self.engine, self.bus, self.split = engine, bus, split
-        self.flat_param, self.wu_group = flat_param, wu_group
+        self.flat_param, self.wu_group, self.staging = flat_param, wu_group, staging
         self.dataloader, self.workflow, self.workflow_kwargs = dataloader, workflow, workflow_kwargs
         self.rank = split.rank
+        self.consumers = split.consumers_of(self.rank) if split.is_leader(self.rank) else []
         self._stop = threading.Event()
         self._ctl = threading.Thread(target=self._control_loop, name="rollout-control", daemon=True)
+        self._ctl_exc: Optional[BaseException] = None
         self.push_seq = 0
         self.produced = 0
 
     def _control_loop(self):
+        try:
+            self._control_loop_inner()
+        except BaseException as e:          # surfaced by run()
+            self._ctl_exc = e
+            self._stop.set()
+
+    def _control_loop_inner(self):
         while not self._stop.is_set():
             cmd = self.bus.poll(f"wu/{self.push_seq}/pause")
             if cmd is None:
@@ -204,9 +270,13 @@ class RolloutWorker:
                 torch.cuda.synchronize(self.engine.device)
             self.bus.put(f"wu/{self.push_seq}/ack/{self.rank}", 1)
             if isinstance(cmd, dict) and cmd.get("mode") == "broadcast":
-                flat = self.flat_param
+                if self.staging is not None and self.staging.get("flat") is None:     # allocated on first use
+                    self.staging["flat"] = torch.zeros(self.staging["padded"], dtype=self.flat_param.dtype, device=self.flat_param.device)
+                flat = self.staging["flat"] if self.staging is not None else self.flat_param
                 for a in range(0, flat.numel(), cmd["bucket"]):
                     dist.broadcast(flat[a:a + cmd["bucket"]], src=cmd["src"], group=self.wu_group)
+                if self.staging is not None:
+                    self._reshard_from_staging()
             done = self.bus.get(f"wu/{self.push_seq}/done")
             if self.engine.device.type == "cuda":
                 torch.cuda.synchronize(self.engine.device)
@@ -214,20 +284,44 @@ class RolloutWorker:
             self.engine.continue_generation()
             self.push_seq += 1
 
+    @torch.no_grad()
+    def _reshard_from_staging(self):
+        """Broadcast path of a tensor-parallel replica: slices of the full tensors -> local parameters."""
+        from ..parallel import tp as TP
+
+        st, eng = self.staging, self.engine
+        params = dict(eng.model.named_parameters())
+        for name, off, shape in zip(st["names"], st["offsets"], st["shapes"]):
+            n = 1
+            for d in shape:
+                n *= d
+            full = st["flat"][off:off + n].view(shape)
+            params[name].data.copy_(TP.shard_tensor(st["cfg"], name, full, eng.tp_size, eng.tp_rank))
+
     def run(self, max_batches: Optional[int] = None):
         self._ctl.start()
         try:
-            while not self._stop.is_set() and (max_batches is None or self.produced < max_batches):
-                batch = self._next_batch()
-                if batch is None:
-                    break
-                self.bus.put(f"traj/{self.rank}/{self.produced}", batch)
-                self.produced += 1
+            if not self.consumers:                       # follower of a tensor-parallel replica
+                while not self._stop.is_set():
+                    time.sleep(0.01)
+            seqs = {c: 0 for c in self.consumers}
+            while self.consumers and not self._stop.is_set() and (max_batches is None or self.produced < max_batches):
+                for c in self.consumers:
+                    batch = self._next_batch()
+                    if batch is None:
+                        break
+                    self.bus.put(f"traj/{self.rank}/{c}/{seqs[c]}", batch)
+                    seqs[c] += 1
+                    self.produced += 1
+                else:
+                    continue
+                break
         finally:
             self._stop.set()
+        if self._ctl_exc is not None:
+            raise RuntimeError("rollout control loop failed") from self._ctl_exc
 
     def _next_batch(self):
-        ex = self.engine.workflow_executor
         holder: dict = {}
 
         def work():
@@ -249,9 +343,10 @@ class RolloutWorker:
 
 
 # --------------------------------------------------------------------------- launch helpers
-def init_split_world(n_train: int, device: Optional[torch.device] = None):
+def init_split_world(n_train: int, device: Optional[torch.device] = None, sp: int = 1, rollout_tp: int = 1):
     """Initialises ``torch.distributed`` (NCCL on CUDA, gloo on CPU) from the torchrun-style
-    environment and returns ``(split, groups, bus)``."""
+    environment and returns ``(split, groups, bus)``. ``sp``: Ulysses sequence-parallel degree of
+    the trainers; ``rollout_tp``: tensor-parallel degree of a rollout replica."""
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
     use_cuda = device is not None and device.type == "cuda"
@@ -265,8 +360,8 @@ def init_split_world(n_train: int, device: Optional[torch.device] = None):
             dist.init_process_group("nccl", timeout=to)
         else:
             dist.init_process_group("gloo", timeout=to)
-    split = SplitWorld(n_train, world - n_train, rank)
-    groups = build_split_groups(split, sp_size=1, use_cuda=use_cuda)
+    split = SplitWorld(n_train, world - n_train, rank, sp=sp, rollout_tp=rollout_tp)
+    groups = build_split_groups(split, use_cuda=use_cuda)
     logger.info("rank %d: process groups ready", rank)
     bus = MessageBus(rank, world)
     logger.info("rank %d: message bus connected", rank)
@@ -277,13 +372,15 @@ def make_split_trainer(cfg, model_cfg, split: SplitWorld, groups: dict, bus: Mes
                        symmetric: bool = True):
     """Trainer-rank side: builds the actor engine on the trainer sub-world, the remote rollout
     client and the :class:`PPOTrainer`, and pushes the initial weights."""
+    from ..api.alloc_mode import FSDPParallelStrategy
     from ..api.io_struct import FinetuneSpec
     from ..engine.train_engine import B200PPOActor
     from ..trainer.rl_trainer import PPOTrainer
 
     actor = B200PPOActor(cfg.actor)
     actor.set_train_ranks(split.train_ranks, groups)
-    actor.create_process_group()
+    actor.create_process_group(FSDPParallelStrategy(data_parallel_size=split.dp, context_parallel_size=split.sp)
+                               if split.sp > 1 else None)
     kw = {}
     if symmetric and actor.device.type == "cuda":
         kw = dict(param_symm_group=dist.group.WORLD, param_symm_ranks=list(range(split.world)))
@@ -298,34 +395,69 @@ def make_split_trainer(cfg, model_cfg, split: SplitWorld, groups: dict, bus: Mes
 def run_rollout_rank(cfg, model_cfg, split: SplitWorld, groups: dict, bus: MessageBus, dataset, workflow,
                      device: torch.device, seed: int = 1, symmetric: bool = True, eos_token_id=None,
                      max_batches: Optional[int] = None):
-    """Rollout-rank side: builds the engine over a flat parameter buffer laid out like the
-    trainer's (peer-mapped when ``symmetric``), then produces batches until told to exit."""
+    """Rollout-rank side: builds the engine over a flat parameter buffer (peer-mapped when
+    ``symmetric``; laid out like the trainer's for a single-GPU replica, like the rank-local
+    tensor-parallel slice otherwise), then produces batches until told to exit."""
+    import copy
+
     from torch.utils.data import DataLoader
 
-    from ..engine.flat_params import FlatParamStore
+    from ..engine.flat_params import FlatParamStore, flat_layout
     from ..engine.infer_engine import NativeInferenceEngine
     from ..models.decoder import build_model
 
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
-    logger.info("rollout rank %d: building the model", split.rank)
-    model = build_model(model_cfg, dtype=dtype, device=device, seed=seed)
-    logger.info("rollout rank %d: model built, mapping the parameter buffer", split.rank)
+    tp = split.rollout_tp
+    tp_rank = split.tp_rank_of(split.rank)
+    n_shards = split.n_train if split.n_train > 1 else 1
+    # size of the trainers' flat buffer: symmetric allocations of one group must agree on it
+    meta_full = build_model(model_cfg, dtype=dtype, device="meta")
+    full_names = [n for n, _ in meta_full.named_parameters()]
+    full_shapes = [tuple(p.shape) for _, p in meta_full.named_parameters()]
+    full_offsets, full_padded = flat_layout([p.numel() for _, p in meta_full.named_parameters()], n_shards)
+    logger.info("rollout rank %d: building the model (tp %d/%d)", split.rank, tp_rank, tp)
+    if tp > 1:
+        from ..parallel import tp as TP
+
+        local_cfg = TP.local_config(model_cfg, tp)
+        model = build_model(local_cfg, dtype=dtype, device=device, seed=seed)
+        TP.install_tp(model, groups["rtp"], tp, tp_rank)
+    else:
+        local_cfg = model_cfg
+        model = build_model(model_cfg, dtype=dtype, device=device, seed=seed)
     alloc = None
     if symmetric and device.type == "cuda":
         from ..parallel.symm import symm_empty
 
         def alloc(n, dt, d):
-            t, _ = symm_empty(n, dt, d, dist.group.WORLD)
+            t, _ = symm_empty(max(n, full_padded), dt, d, dist.group.WORLD)
             t.zero_()
-            return t
-    n_shards = split.n_train if split.n_train > 1 else 1
-    store = FlatParamStore(model, n_shards, 0, alloc_param=alloc, with_grads=False)
+            return t[:n]
+    store = FlatParamStore(model, n_shards if tp == 1 else 1, 0, alloc_param=alloc, with_grads=False)
     logger.info("rollout rank %d: parameter buffer ready (%d elements)", split.rank, store.padded)
-    engine = NativeInferenceEngine(cfg.rollout, cfg.native_infer, model=model, eos_token_id=eos_token_id)
-    engine.initialize(device=device, seed=seed)
+    staging = None
+    if tp > 1:
+        # broadcast path: the whole buffer arrives in the trainer's layout and is sliced locally
+        # (the buffer itself is allocated when the first broadcast update arrives)
+        staging = dict(flat=None, padded=full_padded, names=full_names, shapes=full_shapes, offsets=full_offsets, cfg=model_cfg)
+    rcfg = cfg.rollout
+    is_leader = split.is_leader(split.rank)
+    consumers = split.consumers_of(split.rank) if is_leader else []
+    if len(consumers) > 1:
+        # one version step consumes a batch for each of the heads this leader feeds
+        rcfg = copy.copy(rcfg)
+        rcfg.consumer_batch_size = cfg.rollout.consumer_batch_size * len(consumers)
+        if rcfg.max_concurrent_rollouts:
+            rcfg.max_concurrent_rollouts = rcfg.max_concurrent_rollouts * len(consumers)
+    engine = NativeInferenceEngine(rcfg, cfg.native_infer, model_config=local_cfg, model=model, eos_token_id=eos_token_id,
+                                   tp_group=groups.get("rtp") if tp > 1 else None,
+                                   tp_control_group=groups.get("rtp_cpu") if tp > 1 else None)
+    if tp > 1:
+        engine.full_model_config = model_cfg
+    engine.initialize(device=device, seed=seed, start_executor=is_leader)
     dl = DataLoader(dataset, batch_size=cfg.train_dataset.batch_size, shuffle=True, drop_last=True, collate_fn=list,
                     generator=torch.Generator().manual_seed(seed + split.rank))
-    worker = RolloutWorker(engine, bus, split, dl, workflow, flat_param=store.flat_param, wu_group=groups.get("wu"))
+    worker = RolloutWorker(engine, bus, split, dl, workflow, flat_param=store.flat_param, wu_group=groups.get("wu"), staging=staging)
     try:
         worker.run(max_batches=max_batches)
     finally:

@@ -106,12 +106,15 @@ def make_weight_pusher(train_engine, infer_engine, meta: WeightUpdateMeta):
     if meta.type == "disk":
         return DiskPusher(train_engine, infer_engine)
     if meta.type in ("p2p", "xccl", "awex") and hasattr(infer_engine, "remote_ranks"):
-        from ..parallel.weight_push import BroadcastWeightPusher, DistributedWeightPusher
+        from ..parallel.weight_push import BroadcastWeightPusher, DistributedWeightPusher, TPWeightPusher
 
         symmetric = train_engine.store.flat_param.data_ptr() in train_engine._symm_handles
         if meta.type == "xccl" or not symmetric:
             return BroadcastWeightPusher(train_engine, infer_engine, infer_engine.wu_group,
                                          bucket_mb=meta.weight_chunked_mem_mb)
+        rollout_tp = getattr(infer_engine.split, "rollout_tp", 1)
+        if rollout_tp > 1:
+            return TPWeightPusher(train_engine, infer_engine, meta, rollout_tp)
         return DistributedWeightPusher(train_engine, infer_engine, meta)
     if any(getattr(train_engine, a, 1) > 1 for a in ("pp_size", "ep_size", "tp_size")):
         return GatheredPusher(train_engine, infer_engine)

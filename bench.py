@@ -4,8 +4,14 @@
 of one node (for N > 1 launch under ``python -m torch.distributed.run --nproc-per-node N``):
 
 * N = 1: trainer and rollout engine share the GPU (colocated, concurrent);
-* N >= 2: ranks [0, N/2) train (ZeRO data parallel), ranks [N/2, N) generate, weights travel
-  trainer -> rollout over NVLink after every step.
+* N >= 2: ranks [0, N/2) train (ZeRO over all trainers, Ulysses sequence parallel in groups of up
+  to 4), ranks [N/2, N) generate (tensor-parallel replicas of 2 GPUs from N = 4 on), weights travel
+  trainer -> rollout over NVLink after every step, re-sharded in flight.
+
+The default workload is BASELINE.json's Qwen3-8B decoupled-PPO shape (``--preset baseline``) with
+all lengths scaled by 0.25 so that the 45 steps of a driver run finish inside its time limit on
+one GPU; ``--preset baseline`` runs the unscaled shape, ``--preset small`` the short-sequence
+workload of earlier measurements.
 
 Synthetic data (uniform-random prompt ids, forced log-normal response lengths, Bernoulli
 rewards) and random-init weights, bf16 compute. After W warm-up steps exactly K steps are
@@ -27,6 +33,19 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
+PRESETS = {
+    # BASELINE.json config 3 (Qwen3-8B decoupled PPO): 1,024-token prompts, log-normal responses with
+    # median 4,096 capped at 16,384, groups of 16, 32k-token packed micro-batches
+    "baseline": dict(prompt_len=1024, median_len=4096, max_len=16384, group_size=16, max_tokens_per_mb=32768, length_scale=1.0),
+    # the same shape with every length scaled by --length-scale (default 0.25): what fits the 45 steps of a
+    # driver run into its time limit on one GPU (see README "Benchmark workload")
+    "driver": dict(prompt_len=1024, median_len=4096, max_len=16384, group_size=16, max_tokens_per_mb=32768, length_scale=0.25),
+    # the short-sequence workload of earlier measurements (data-parallel trainers and rollout replicas)
+    "small": dict(prompt_len=256, median_len=256, max_len=768, group_size=8, max_tokens_per_mb=0, length_scale=1.0,
+                  sp=1, rollout_tp=1, staleness=2, prompts_per_gpu=4.0, prox_logp_method="reuse_train_logp"),
+}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -34,21 +53,52 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
     ap.add_argument("--model", type=str, default="qwen3-8b")
-    ap.add_argument("--prompts-per-gpu-pair", type=int, default=8, help="prompts per step per (trainer, rollout) pair")
-    ap.add_argument("--group-size", type=int, default=8)
-    ap.add_argument("--prompt-len", type=int, default=256)
-    ap.add_argument("--median-len", type=int, default=256)
-    ap.add_argument("--max-len", type=int, default=768)
-    ap.add_argument("--max-tokens-per-mb", type=int, default=0, help="0: chosen from the activation-memory policy")
-    ap.add_argument("--grad-ckpt", type=int, default=-1, help="-1: automatic (recompute activations only when one GPU holds "
-                    "the whole optimizer state and the rollout engine), 0 / 1: force")
-    ap.add_argument("--prox-logp-method", type=str, default="reuse_train_logp",
-                    help="reuse_train_logp (single minibatch: the update forward's log-probs ARE the proximal ones) | recompute")
-    ap.add_argument("--staleness", type=int, default=2)
+    ap.add_argument("--preset", type=str, default="driver", choices=sorted(PRESETS))
+    ap.add_argument("--length-scale", type=float, default=None, help="scales prompt / median / cap lengths of the preset")
+    ap.add_argument("--prompts-per-gpu", type=float, default=None,
+                    help="prompts (groups) per optimizer step per GPU of the job: the global batch grows with N (weak scaling)")
+    ap.add_argument("--group-size", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--median-len", type=int, default=None)
+    ap.add_argument("--max-len", type=int, default=None)
+    ap.add_argument("--max-tokens-per-mb", type=int, default=None, help="packed micro-batch size in tokens (0: from the memory policy)")
+    ap.add_argument("--grad-ckpt", type=int, default=1, help="1: activations are recomputed in backward (the same policy at every N), 0: kept")
+    ap.add_argument("--prox-logp-method", type=str, default=None,
+                    help="recompute (decoupled PPO's own forward pass for the proximal log-probs, the reference's default) | "
+                         "reuse_train_logp | loglinear")
+    ap.add_argument("--staleness", type=int, default=None, help="max_head_offpolicyness")
+    ap.add_argument("--train-gpus", type=int, default=0, help="trainer GPUs of an N >= 2 job (default N / 2)")
+    ap.add_argument("--sp", type=int, default=0, help="Ulysses sequence-parallel degree of the trainers (default min(4, trainer GPUs))")
+    ap.add_argument("--rollout-tp", type=int, default=0, help="tensor-parallel degree of a rollout replica (default 2 with >= 2 rollout GPUs)")
+    ap.add_argument("--nccl-steps", type=int, default=-1,
+                    help="steps of the same job re-run on the library-collective path (NCCL reduce-scatter / all-gather / "
+                         "all-to-all / broadcast instead of the fused kernels) for config.nccl_path_tokens_per_s; "
+                         "-1: max(2, steps / 5) when N >= 2, 0: skip")
     ap.add_argument("--retain-kv", type=int, default=1, help="1: requests in flight keep their KV cache across a weight update; "
                     "0: they are interrupted and re-prefilled under the new weights")
     ap.add_argument("--prefix-sharing", type=int, default=1, help="1: the samples of a group share the prompt's KV pages (one prefetch per prompt)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    pre = dict(PRESETS[args.preset])
+    scale = args.length_scale if args.length_scale is not None else pre["length_scale"]
+    args.length_scale = scale
+    for k in ("prompt_len", "median_len", "max_len"):
+        if getattr(args, k) is None:
+            setattr(args, k, max(16, int(round(pre[k] * scale / 16)) * 16))
+    if args.group_size is None:
+        args.group_size = pre["group_size"]
+    if args.max_tokens_per_mb is None:
+        args.max_tokens_per_mb = pre["max_tokens_per_mb"]
+    if args.staleness is None:
+        args.staleness = pre.get("staleness", 8)
+    if args.prompts_per_gpu is None:
+        args.prompts_per_gpu = pre.get("prompts_per_gpu", 1.0)
+    if args.prox_logp_method is None:
+        args.prox_logp_method = pre.get("prox_logp_method", "recompute")
+    if not args.sp and "sp" in pre:
+        args.sp = pre["sp"]
+    if not args.rollout_tp and "rollout_tp" in pre:
+        args.rollout_tp = pre["rollout_tp"]
+    return args
 
 
 class ClockSampler:

@@ -171,7 +171,7 @@ from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
 from areal_b200.infra.spmd import init_split_world, make_split_trainer, run_rollout_rank
 cfg = _cfg(%(tmp)r)
 mc = preset(os.environ.get("SPLIT_MODEL", "tiny-qwen2"), vocab_size=64, num_layers=2, **({"layer_types": ["linear_attention", "full_attention"]} if "qwen3.5" in os.environ.get("SPLIT_MODEL", "") else {}))
-split, groups, bus = init_split_world(int(os.environ["N_TRAIN"]), None)
+split, groups, bus = init_split_world(int(os.environ["N_TRAIN"]), None, sp=int(os.environ.get("SPLIT_SP", "1")), rollout_tp=int(os.environ.get("SPLIT_RTP", "1")))
 ds = ArithmeticDataset(size=128)
 if split.is_trainer:
     tr = make_split_trainer(cfg, mc, split, groups, bus, ds)
@@ -190,18 +190,32 @@ else:
     wf = RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True)
     w = run_rollout_rank(cfg, mc, split, groups, bus, ds, wf, torch.device("cpu"))
     assert w.engine.get_version() == 3, w.engine.get_version()
-    got = float(w.flat_param.double().sum())
-    assert abs(got - bus.get("final_sum")) < 1e-6, "rollout replica does not hold the trainer's final weights"
+    if split.rollout_tp == 1:
+        got = float(w.flat_param.double().sum())
+        assert abs(got - bus.get("final_sum")) < 1e-6, "rollout replica does not hold the trainer's final weights"
+    else:
+        # every rank of a tensor-parallel replica holds exactly its slices of the trainer's final weights
+        from areal_b200.parallel import tp as TP
+        st = w.staging
+        for name, off, shape in zip(st["names"], st["offsets"], st["shapes"]):
+            full = st["flat"][off:off + int(torch.tensor(shape).prod())].view(shape)
+            mine = dict(w.engine.model.named_parameters())[name].data
+            assert torch.equal(mine, TP.shard_tensor(mc, name, full, split.rollout_tp, split.tp_rank_of(split.rank))), name
+        assert abs(float(st["flat"].double().sum()) - bus.get("final_sum")) < 1e-6
 dist.barrier(group=groups["world_cpu"])
 print("SPLIT_OK", split.rank, flush=True)
 '''
 
 
-@pytest.mark.parametrize("n_train,world,port,model", [(1, 2, 29811, "tiny-qwen2"), (2, 4, 29821, "tiny-qwen2"), (1, 2, 29831, "tiny-qwen3.5")])
-def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port, model):
+@pytest.mark.parametrize("n_train,world,port,model,sp,rtp", [
+    (1, 2, 29811, "tiny-qwen2", 1, 1), (2, 4, 29821, "tiny-qwen2", 1, 1), (1, 2, 29831, "tiny-qwen3.5", 1, 1),
+    (2, 4, 29841, "tiny-qwen2", 2, 2),        # one Ulysses pair of trainers, one tensor-parallel rollout replica
+    (2, 4, 29851, "tiny-qwen2", 1, 2),        # two data-parallel trainers share one tensor-parallel replica
+    (1, 3, 29861, "tiny-qwen2", 1, 1)])       # one trainer merges the batches of two replicas
+def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port, model, sp, rtp):
     script = tmp_path / "split.py"
     script.write_text(SPLIT_SCRIPT % dict(root=ROOT, tmp=str(tmp_path)))
-    env = dict(os.environ, N_TRAIN=str(n_train), OMP_NUM_THREADS="1", SPLIT_MODEL=model)
+    env = dict(os.environ, N_TRAIN=str(n_train), OMP_NUM_THREADS="1", SPLIT_MODEL=model, SPLIT_SP=str(sp), SPLIT_RTP=str(rtp))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)], cwd=ROOT, env=env,
                        capture_output=True, text=True, timeout=400)
