@@ -99,7 +99,8 @@ class OptimizerConfig:
     lr_scheduler_type: str = "constant"  # constant | linear | cosine
     warmup_steps_proportion: float = 0.001
     warmup_steps: Optional[int] = None
-    offload: bool = False
+    offload: bool = False             # fp32 master weights + moments in pinned host memory, streamed through the GPU in chunks
+    offload_chunk_numel: int = 1 << 26  # elements per streamed chunk (three fp32 buffers of this size, double buffered)
     initial_loss_scale: float = 2 ** 32
     min_loss_scale: float = 1.0
     loss_scale_window: float = 5

@@ -46,6 +46,26 @@ def _dtype_of(name: str):
     return {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[name]
 
 
+class _GatherOverSP(torch.autograd.Function):
+    """Concatenates the sequence-parallel ranks' slices of a per-token tensor. Every rank then
+    evaluates the SAME loss on whole sequences; in backward a rank keeps only the gradient of its
+    own slice (the other slices are the other ranks' business), so the parameter gradients summed
+    over the group are those of the loss counted once. Role of ``_sp_all_gather`` in the reference
+    (areal/engine/fsdp_engine.py:2057-2142)."""
+
+    @staticmethod
+    def forward(ctx, x, group, rank, world):
+        ctx.rank, ctx.n = rank, x.shape[0]
+        x = x.contiguous()
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x, group=group)
+        return torch.cat(parts, dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g[ctx.rank * ctx.n:(ctx.rank + 1) * ctx.n].contiguous(), None, None, None
+
+
 class B200TrainEngine(TrainEngine):
     def __init__(self, config: TrainEngineConfig):
         self.config = config
@@ -181,6 +201,15 @@ class B200TrainEngine(TrainEngine):
             self._shard_group = None
         if not hasattr(self, "_stats_group"):
             self._stats_group = self._cpu_group
+        if sp > 1 and tp == 1:
+            # sequence-parallel peers evaluate the loss on the same whole micro-batches, so their
+            # statistics are copies: only the heads of the data-parallel replicas are reduced
+            if preset is not None:
+                self._stats_group = preset.get("stats") if self.sp_rank == 0 else None
+            elif dist.is_initialized() and n > 1:
+                heads = [gid(d, 0, 0) for d in range(dp)]
+                g = dist.new_group(heads, backend="gloo") if (dp > 1 and use_cuda) else (dist.new_group(heads) if dp > 1 else None)
+                self._stats_group = g if self.sp_rank == 0 else None
         self.ep_size = getattr(p, "ep_size", 1) or 1
         self.ep_rank, self._ep_group, self._edp_group = 0, None, None
         if self.ep_size > 1:
@@ -659,6 +688,11 @@ class B200TrainEngine(TrainEngine):
                 out[k] = v
         return out
 
+    def _sp_gather(self, t: torch.Tensor) -> torch.Tensor:
+        if self.sp_size <= 1:
+            return t
+        return _GatherOverSP.apply(t, self._sp_group, self.sp_rank, self.sp_size)
+
     def _actor_outputs(self, hidden, labels, temperature=None):
         t = self.config.temperature if temperature is None else temperature
         return self.model.logprobs_entropy(hidden, labels, t, chunk=max(256, self.config.logprobs_chunk_size))
@@ -682,17 +716,14 @@ class B200TrainEngine(TrainEngine):
 
         def process(hidden, labels, mb, pad, sl):
             w = next(it)
-            mb_local = self._slice_mb(mb, sl, pad)
-            if self.sp_size > 1:
-                # loss_fn normalises by the *local* token count, so weight by it
-                w = float(loss_weight_fn(mb_local))
+            # sequence-parallel ranks gather the per-token outputs and evaluate the loss on the WHOLE
+            # micro-batch (sequence-level losses, pair sums and sorts need whole sequences)
             if self.config.is_critic:
-                loss = loss_fn(self.model.values(hidden), mb_local)
+                loss = loss_fn(self._sp_gather(self.model.values(hidden)), mb)
             else:
                 logp, ent = self._actor_outputs(hidden, labels)
-                loss = loss_fn(logp, ent, mb_local)
-            # sum over ranks of (w_mb / W_total) * mean-loss_mb == global weighted mean;
-            # sequence-parallel ranks each hold a slice of the same micro-batch
+                loss = loss_fn(self._sp_gather(logp), self._sp_gather(ent), mb)
+            # sum over data-parallel ranks of (w_mb / W_total) * mean-loss_mb == global weighted mean
             return loss * (w / total_weight)
 
         losses = self.forward_backward_batch(mbl, process)
@@ -717,7 +748,8 @@ class B200TrainEngine(TrainEngine):
 
             allreduce_replicated_grads(self.model, self._tp_group)
         pp = getattr(self, "pp_size", 1)
-        fused = self._grad_reducer is not None and not opt.sgd and tp == 1 and pp == 1
+        fused = (self._grad_reducer is not None and not opt.sgd and not opt.bf16_state and not opt.offload
+                 and tp == 1 and pp == 1)
         if self._shard_group is not None:
             if fused:
                 gshard = self._grad_reducer.reduce_scatter(opt.state)
@@ -891,11 +923,10 @@ class B200TrainEngine(TrainEngine):
 
         def process(hidden, labels, mb, pad, sl):
             w = next(it)
-            mb_local = self._slice_mb(mb, sl, pad)
             if self.config.is_critic:
-                return loss_fn(self.model.values(hidden), mb_local) * w
+                return loss_fn(self._sp_gather(self.model.values(hidden)), mb) * w
             logp, ent = self._actor_outputs(hidden, labels)
-            return loss_fn(logp, ent, mb_local) * w
+            return loss_fn(self._sp_gather(logp), self._sp_gather(ent), mb) * w
 
         outs = self._pp_share([o.float().cpu() for o in self.forward_backward_batch(mbl, process, forward_only=True)])
         tot = torch.stack([o.float().cpu() for o in outs]).sum().reshape(1).double()

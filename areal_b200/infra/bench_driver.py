@@ -122,6 +122,26 @@ def _make_config(args, lay: dict, fileroot: str) -> GRPOConfig:
     )
 
 
+def _cap_micro_batch(args, actor) -> None:
+    """Caps the packed micro-batch size by what the trainer GPU has left once parameters, gradients
+    and optimizer state are resident: about 0.8 MB per micro-batch token (layer-input checkpoints,
+    one layer's activations and their gradients, LM-head chunks) plus 6 GB of slack."""
+    free, _ = torch.cuda.mem_get_info()
+    sp = max(1, getattr(actor, "sp_size", 1))
+    cap = int((free / 2 ** 30 - 6.0) / 0.8e-3) * sp // 1024 * 1024
+    if actor.cpu_group is not None:          # every trainer rank must split the batch the same way
+        t = torch.tensor([cap], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=actor.cpu_group)
+        cap = int(t[0])
+    mb = actor.config.mb_spec.max_tokens_per_mb
+    if cap < mb:
+        cap = max(4096, cap)
+        logger.info("micro-batches capped at %d tokens (%.1f GB free on the trainer GPU)", cap, free / 2 ** 30)
+        actor.config.mb_spec.max_tokens_per_mb = cap
+        args._resolved["max_tokens_per_mb"] = cap
+        args._resolved["max_tokens_per_mb_capped_by_memory"] = True
+
+
 def _dataset(args, model_cfg, seed: int):
     return RandomTokenDataset(size=4096, prompt_len=args.prompt_len, vocab_size=model_cfg.vocab_size, seed=seed,
                               median_len=args.median_len, max_len=args.max_len, min_len=16, n_samples=args.group_size)
@@ -164,6 +184,7 @@ def run_async_grpo_bench(args, clock_sampler_cls) -> Optional[dict]:
         ds = _dataset(args, model_cfg, seed=1)  # only sizes the trainer's bookkeeping
         trainer = make_split_trainer(cfg, model_cfg, split, groups, bus, ds, seed=1)
         _instrument_transfers(trainer.actor)
+        _cap_micro_batch(args, trainer.actor)
         res = _timed_loop(args, trainer, None, clock_sampler_cls, world, rank, model_cfg, lay, parallelism=par, groups=groups)
         if rank == 0:
             bus.put("exit", 1)

@@ -127,6 +127,11 @@ def build_split_groups(split: SplitWorld, sp_size: Optional[int] = None, use_cud
             g = dist.new_group(ranks)
             if me in ranks:
                 out["dp"] = g
+    out["stats"] = None
+    if sp_size > 1 and dp_size > 1:
+        g = dist.new_group([tr[h] for h in split.heads], backend="gloo")
+        if me in split.heads:
+            out["stats"] = g
     if split.rollout_tp > 1:
         for k in range(split.n_replicas):
             ranks = split.replica_ranks(k)

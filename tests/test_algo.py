@@ -186,3 +186,70 @@ def test_advantage_pipeline_grpo_shape_and_values():
     assert out["loss_mask"].tolist() == [[0, 1, 1, 1, 1, 0], [0, 1, 1, 0, 0, 0]]
     assert torch.allclose(out["advantages"][0, 1:5], torch.full((4,), 1.0))      # (1 - .5) * 2
     assert torch.allclose(out["advantages"][1, 1:3], torch.full((2,), -1.0))     # (0 - .5) * 2
+
+
+# --------------------------------------------------------------------------- optimizer variants
+def _opt_setup(kind, wd=0.1, **kw):
+    import torch.nn as nn
+
+    from areal_b200.api.cli_args import OptimizerConfig
+    from areal_b200.engine.flat_params import FlatParamStore
+    from areal_b200.engine.optimizer import ShardedAdamW
+
+    torch.manual_seed(0)
+    m = nn.Linear(64, 32, bias=True)
+    ref = nn.Linear(64, 32, bias=True)
+    ref.load_state_dict(m.state_dict())
+    store = FlatParamStore(m, 1, 0)
+    opt = ShardedAdamW(store, OptimizerConfig(type=kind, lr=1e-2, weight_decay=wd, gradient_clipping=0.0, warmup_steps=0, **kw))
+    return m, ref, store, opt
+
+
+def test_sgd_applies_weight_decay_like_torch():
+    m, ref, store, opt = _opt_setup("sgd")
+    topt = torch.optim.SGD(ref.parameters(), lr=1e-2, weight_decay=0.1)
+    for step in range(3):
+        g = torch.randn(store.padded)
+        store.flat_grad.copy_(g)
+        for p, off in zip(ref.parameters(), store.offsets):
+            p.grad = g[off:off + p.numel()].view(p.shape).clone()
+        opt.step(store.grad_shard)
+        topt.step()
+    for p, q in zip(m.parameters(), ref.parameters()):
+        assert torch.allclose(p, q, atol=1e-6)
+    # a non-finite gradient norm skips the step entirely, decay included
+    before = store.flat_param.clone()
+    store.flat_grad.fill_(float("nan"))
+    res = opt.step(store.grad_shard)
+    assert float(res["state"][2]) == 0.0 and torch.equal(store.flat_param, before)
+
+
+def test_adam_with_bf16_state_tracks_fp32_adamw():
+    """bf16 moments + Kahan-compensated bf16 weights stay close to fp32 AdamW over many small steps,
+    where plain bf16 weights would stall (updates below half a bf16 ulp are rounded away)."""
+    import torch.nn as nn
+
+    from areal_b200.api.cli_args import OptimizerConfig
+    from areal_b200.engine.flat_params import FlatParamStore
+    from areal_b200.engine.optimizer import ShardedAdamW
+
+    torch.manual_seed(1)
+    m = nn.Linear(48, 16, bias=False).to(torch.bfloat16)
+    w0 = m.weight.detach().float().clone()
+    store = FlatParamStore(m, 1, 0)
+    opt = ShardedAdamW(store, OptimizerConfig(type="adam_bf16", lr=1e-5, weight_decay=0.0, gradient_clipping=0.0, warmup_steps=0))
+    assert opt.exp_avg.dtype == torch.bfloat16 and opt.master.dtype == torch.bfloat16
+    ref = nn.Parameter(w0.clone())
+    topt = torch.optim.AdamW([ref], lr=1e-5, weight_decay=0.0)
+    g = torch.randn(store.padded).sign()                    # constant-sign gradient: every step moves each weight by about lr
+    for _ in range(200):
+        store.flat_grad.copy_(g)
+        ref.grad = g[:ref.numel()].view(ref.shape).clone()
+        opt.step(store.grad_shard)
+        topt.step()
+    moved = (m.weight.float() + opt.master[:ref.numel()].view(ref.shape).float()) - w0     # weights + carried low-order bits
+    want = ref.detach() - w0
+    assert (want.abs() > 1e-3).all()
+    assert float((moved - want).abs().max()) < 0.1 * float(want.abs().max())
+    stalled = (w0.to(torch.bfloat16).float() - w0).abs().max()          # scale of one bf16 rounding error, for reference
+    assert float((m.weight.float() - ref.detach()).abs().max()) <= 2 * float(stalled) + 1e-3

@@ -78,3 +78,15 @@ def test_tensor_parallel_rollout_replica_gloo():
                        env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("INFER_TP_OK") == 2
+
+
+def test_sequence_level_loss_under_ulysses_equals_single_rank():
+    """GSPO (sequence-level importance ratios need whole sequences) with two Ulysses ranks: the
+    per-token outputs are gathered over the group before the loss, so the gradient norm and the
+    parameter update equal the single-rank run."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29983", os.path.join(ROOT, "tests", "dist_scripts", "run_sp_gspo.py")], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("SP_GSPO_OK") == 2
