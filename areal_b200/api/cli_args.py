@@ -453,6 +453,12 @@ class InferenceEngineConfig:
     queue_size: Optional[int] = None
     consumer_batch_size: int = 1
     max_head_offpolicyness: int = 0
+    # The admission formula bounds how far rollout may run AHEAD of the trainer; an episode that
+    # finishes long after its cohort (a straggler) is still trained when it arrives, at whatever age
+    # it then has (the reference behaves the same). True: a training batch is not formed while an
+    # episode that would exceed the bound in the NEXT batch is still running, so no trained token is
+    # older than max_head_offpolicyness versions, at the price of waiting for stragglers.
+    strict_staleness: bool = False
     enable_rollout_tracing: bool = False
     deterministic_sampling: bool = False
     check_trajectory_format: bool = False

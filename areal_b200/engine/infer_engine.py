@@ -232,6 +232,9 @@ class NativeInferenceEngine(InferenceEngine):
 
     def _init_cuda_state(self):
         cfg, ic = self.model_config, self.icfg
+        # blocks the caching allocator holds but nobody uses (e.g. the parameters' first home before a
+        # trainer moved them into its flat buffer) would otherwise count as taken
+        torch.cuda.empty_cache()
         free, total = torch.cuda.mem_get_info()
         per_page = cfg.num_layers * 2 * ic.page_size * cfg.num_kv_heads * cfg.head_dim * 2
         if getattr(ic, "reserve_free_gb", 0.0) > 0:

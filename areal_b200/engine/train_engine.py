@@ -406,6 +406,8 @@ class B200TrainEngine(TrainEngine):
         dense_only = (lambda n: n not in _expert_set) if _expert_set else None
         self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
                                     with_grads=cfg.optimizer is not None, only_trainable=self.use_lora, include=dense_only)
+        if on_gpu:
+            torch.cuda.empty_cache()        # the parameters' first home (before the flat buffer) goes back to the driver
         if n_shards > 1:
             # identical initial weights on every rank of the shard group
             dist.broadcast(self.store.flat_param, src=self._shard_ranks[0], group=self._shard_group)

@@ -82,6 +82,7 @@ class WorkflowExecutor:
         self._results_lock = threading.Lock()
         self._task_results: dict[int, Any] = {}    # only for task ids somebody asked to wait on (``_tracked``)
         self._tracked: set[int] = set()
+        self._start_version: dict[int, int] = {}    # task id -> weight version when the episode started (running episodes only)
         self._paused = threading.Event()
         self._stop = threading.Event()
         self._threads: list[threading.Thread] = []
@@ -153,6 +154,7 @@ class WorkflowExecutor:
             r = self.runner.poll(timeout=ROLLOUT_POLL_S)
             if r is None:
                 continue
+            self._start_version.pop(r.task_id, None)
             if r.error is not None:
                 self.staleness.on_rollout_rejected()
                 raise RuntimeError(f"workflow episode {r.task_id} failed") from r.error
@@ -190,6 +192,7 @@ class WorkflowExecutor:
         async def run():
             from . import workflow_context as wctx
 
+            self._start_version[task_id] = self.engine.get_version()
             with wctx.scoped(is_eval=is_eval, task_id=task_id):
                 traj = await workflow.arun_episode(self.engine, data)
             if traj is None:
@@ -315,10 +318,22 @@ class WorkflowExecutor:
                     fed += 1
             with self._results_lock:
                 have = len(self._results)
+            if self._stragglers_due():
+                time.sleep(0.002)           # strict bound: the oldest running episodes must make this batch
+                continue
             if have >= bs or (dynamic_bs and have + (self.rejected_count - rej0) >= bs and have > 0):
                 n = min(have, bs)
                 return D.concat_padded_tensors(self.wait(n, timeout=1.0))
             time.sleep(0.01)
+
+    def _stragglers_due(self) -> bool:
+        """Strict staleness only: is an episode still running that started ``max_head_offpolicyness``
+        or more versions ago? It has to be part of the batch about to be formed (the batch after it
+        would train it one version too late), so the batch waits for it."""
+        if not getattr(self.config, "strict_staleness", False):
+            return False
+        limit = self.engine.get_version() - self.config.max_head_offpolicyness
+        return any(v <= limit for v in list(self._start_version.values()))
 
     def pause(self):
         """Stops admitting new episodes; running ones continue."""

@@ -341,3 +341,29 @@ def test_hybrid_rollout_on_carried_state_matches_recompute():
     for (ta, la), (tb, lb) in zip(outs["state"], outs["recompute"]):
         assert ta == tb
         assert max(abs(x - y) for x, y in zip(la, lb)) < 1e-4
+
+
+def test_colocated_loop_runs_a_hundred_steps_within_the_staleness_bound(tmp_path):
+    """The asynchronous loop left alone for 120 steps (several epochs of the dataset, per-sample
+    response budgets, strict staleness): every step succeeds, no trained token is older than the
+    configured bound although episodes finish out of order, the executor holds no finished
+    trajectory back and its bookkeeping does not grow."""
+    from areal_b200.dataset import RandomTokenDataset, small_id_fraction_reward_fn
+
+    cfg = _cfg(str(tmp_path), steps=120)
+    cfg.train_dataset.batch_size = 2
+    cfg.rollout.consumer_batch_size, cfg.rollout.max_concurrent_rollouts, cfg.rollout.max_head_offpolicyness = 2, 6, 2
+    cfg.rollout.strict_staleness = True
+    cfg.gconfig = GenerationHyperparameters(n_samples=4, max_new_tokens=12, max_tokens=64, ignore_eos=True)
+    mc = preset("tiny-qwen2", vocab_size=64, num_layers=1)
+    ds = RandomTokenDataset(size=16, prompt_len=8, vocab_size=64, seed=3, median_len=6, max_len=12, min_len=2, n_samples=4)
+    with PPOTrainer(cfg, ds, tokenizer=None, model_config=mc) as tr:
+        wf = RLVRWorkflow(small_id_fraction_reward_fn, cfg.gconfig, reward_in_process=True)
+        hist = tr.train(workflow=wf)
+        ex = tr.rollout.workflow_executor
+        assert len(ex._task_results) == 0 and len(ex._tracked) == 0
+        assert len(ex._results) <= cfg.rollout.max_concurrent_rollouts
+    assert len(hist) == 120 and all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
+    assert max(h["ppo_actor/update/staleness/max"] for h in hist) <= 2 + 1e-6
+    lens = {round(h["ppo_actor/seq_len/avg"], 2) for h in hist}
+    assert len(lens) > 5                                           # the samples of a group really have different lengths
