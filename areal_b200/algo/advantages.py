@@ -69,6 +69,10 @@ def token_level_gae(rewards: torch.Tensor, values: torch.Tensor, loss_mask: torc
         adv_body = torch.where(mask[:, : L - 1] > 0, suffix, nxt_loss_suffix)
         adv = torch.cat([adv_body, torch.zeros(B, 1, device=dev)], dim=1)
         return adv, adv + values.float()
+    if rewards.is_cuda:
+        from ..ops import functional as OF
+
+        return OF.gae_scan(rewards, values, loss_mask, seq_no_eos_mask, discount, gae_lambda)    # one thread per sequence
     gl = gae_lambda.float().to(dev) if torch.is_tensor(gae_lambda) else torch.full((B,), float(gae_lambda), device=dev)
     dl = discount * gl
     adv = torch.zeros(B, L, dtype=torch.float32, device=dev)

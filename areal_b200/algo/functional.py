@@ -193,6 +193,12 @@ def ppo_actor_loss_fn(logprobs: torch.Tensor, proximal_logprobs: torch.Tensor, o
     ``min(L, sign(A)*c*A)``; optional behaviour importance weight ``exp(prox - old)`` from
     rejection sampling. The denominator is the number of valid tokens *before* rejection so
     the loss weight stays consistent with the engine's global token count."""
+    if (logprobs.is_cuda and importance_sampling_level == "token" and _FUSED_LOSS
+            and (rejection_sampling is None or rejection_sampling.level == "token")):
+        if c_clip is not None and c_clip <= 1.0:
+            raise ValueError("c_clip must be > 1")
+        return _ppo_actor_loss_fused(logprobs, proximal_logprobs, old_logprobs, advantages, eps_clip, loss_mask, eps_clip_higher,
+                                     c_clip, rejection_sampling)
     loss_mask = loss_mask.bool()
     denom = loss_mask.count_nonzero().clamp(min=1)
     stat_mask = loss_mask
@@ -236,6 +242,40 @@ def ppo_actor_loss_fn(logprobs: torch.Tensor, proximal_logprobs: torch.Tensor, o
                 clip_mask=clip_mask & stat_mask, dual_clip_mask=dual_mask & stat_mask,
                 n_total_tokens=float(n_tot), n_valid_tokens=float(n_valid), n_masked_tokens=float(n_tot - n_valid),
                 masked_token_ratio=1.0 - n_valid / max(n_tot, 1))
+    return total, stat
+
+
+_FUSED_LOSS = __import__("os").environ.get("AREAL_FUSED_LOSS", "1") != "0"
+_RS_METRICS = {"ratio": 0, "kl_k1": 1, "kl_k2": 2, "kl_k3": 3, "binary_kl": 4}
+
+
+def _ppo_actor_loss_fused(logprobs, proximal_logprobs, old_logprobs, advantages, eps_clip, loss_mask, eps_clip_higher, c_clip,
+                          rs_cfg) -> tuple[torch.Tensor, dict]:
+    """The token-level loss, its gradient and all per-token statistics from one kernel pass
+    (``ops/csrc/rl_loss.cu``); same outputs as the eager statement above."""
+    from ..ops import functional as OF
+
+    shape = logprobs.shape
+    stat_mask = loss_mask.bool()
+    action = 0 if rs_cfg is None else (1 if rs_cfg.action == "mask" else 2)
+    if rs_cfg is not None and rs_cfg.metric not in _RS_METRICS:
+        raise ValueError(f"unknown rejection metric {rs_cfg.metric}")
+    total, loss_tok, ratio, behave_w, flags, sums = OF.ppo_token_loss(
+        logprobs, proximal_logprobs, old_logprobs, advantages, stat_mask, eps_clip, eps_clip_higher, c_clip, rs_action=action,
+        rs_metric=_RS_METRICS[rs_cfg.metric] if rs_cfg is not None else 0,
+        rs_lower=rs_cfg.lower if rs_cfg is not None else None, rs_upper=rs_cfg.upper if rs_cfg is not None else None)
+    flags = flags.view(shape)
+    stat: dict = dict(loss=loss_tok.view(shape), importance_weight=ratio.view(shape),
+                      approx_kl=(logprobs.detach() - proximal_logprobs.detach()),
+                      clip_mask=(flags & 1).bool(), dual_clip_mask=(flags & 2).bool())
+    if rs_cfg is not None:
+        bmask = (flags & 4).bool()
+        bkl = proximal_logprobs.detach() - old_logprobs.detach()
+        stat.update(behave_approx_kl=torch.where(bmask, bkl, torch.zeros_like(bkl)), behave_imp_weight=behave_w.view(shape),
+                    behave_mask=bmask, filtered_fraction=(sums[3] / sums[1].clamp(min=1.0)).float())
+    n_tot = stat_mask.numel()
+    stat.update(n_total_tokens=float(n_tot), n_valid_tokens=sums[1].float(), n_masked_tokens=(n_tot - sums[1]).float(),
+                masked_token_ratio=(1.0 - sums[1] / max(n_tot, 1)).float())
     return total, stat
 
 

@@ -422,6 +422,11 @@ class NativeInferConfig:
     # the new weights (what a server that flushes its cache does); True = they keep their KV
     # cache and simply continue, every token tagged with the version that sampled it.
     retain_kv_on_weight_update: bool = False
+    # KV pages of a request: False = taken as the sequence grows (a page at a time; when the pool runs
+    # dry the most recently admitted request is pre-empted: it returns what it has and its client
+    # resubmits it, so its prefix is prefetched again); True = all pages for prompt + max_new_tokens are
+    # reserved at admission (no pre-emption ever, but long budgets keep most of the pool idle).
+    reserve_full_length: bool = False
     # Requests with an identical prompt (the samples of a GRPO group, retries) share the prompt's full KV
     # pages and the logits of its last token: the prompt is prefetched once per weight version.
     enable_prefix_sharing: bool = False

@@ -727,14 +727,25 @@ class NativeInferenceEngine(InferenceEngine):
         sharing = bool(getattr(self.icfg, "enable_prefix_sharing", False))
         budget = self.icfg.max_prefill_tokens
         ps = cache.page_size
+        full = bool(getattr(self.icfg, "reserve_full_length", False))
         with self._lock:
             while self._waiting and len(self._running) + len(admitted) + len(reuse) < self.max_batch:
                 s = self._waiting[0]
-                need = cache.pages_needed(min(len(s.tokens) + s.max_new, self.icfg.context_length))
+                if full:
+                    need = cache.pages_needed(min(len(s.tokens) + s.max_new, self.icfg.context_length))
+                    headroom = 0
+                else:
+                    # pages for the prompt and the first generated token now, the rest as the sequence grows;
+                    # a page per running sequence stays free so that growth rarely has to pre-empt
+                    need = cache.pages_needed(min(len(s.tokens) + 1, self.icfg.context_length))
+                    headroom = len(self._running) + len(admitted) + len(reuse) + 1
                 key = self._prefix_key(s) if sharing else None
                 hit = key is not None and (key in pending or self._prefix_lookup(key) is not None)
                 if hit:
-                    pages = self._alloc_pages(need - len(s.tokens) // ps)      # only the private part
+                    private = need - len(s.tokens) // ps
+                    if not self._have_pages(private + headroom):
+                        break
+                    pages = self._alloc_pages(private)      # only the private part
                     if pages is None:
                         break
                     self._waiting.popleft()
@@ -742,6 +753,8 @@ class NativeInferenceEngine(InferenceEngine):
                     reuse.append((s, key))
                     continue
                 if len(s.tokens) > budget and admitted:
+                    break
+                if not self._have_pages(need + headroom):
                     break
                 pages = self._alloc_pages(need)
                 if pages is None:
@@ -833,6 +846,47 @@ class NativeInferenceEngine(InferenceEngine):
             self._prefix_drop(next(iter(self._prefix)))
             pages = self.cache.alloc(n)
         return pages
+
+    def _have_pages(self, n: int) -> bool:
+        """True when ``n`` pages are free, or can be made free by dropping stored prompts."""
+        if len(self.cache.free) >= n:
+            return True
+        spare = 0
+        for ent in self._prefix.values():
+            spare += sum(1 for p in ent["pages"] if self.cache.ref[p] == 1) + (ent["tail_page"] is not None)
+            if len(self.cache.free) + spare >= n:
+                return True
+        return False
+
+    def _grow_pages(self, seqs: list, done: list) -> list:
+        """Before a decode step every sequence needs a page for the token it is about to cache. Takes
+        them one at a time; when the pool is dry (stored prompts already dropped) the most recently
+        admitted sequence other than the one in need is pre-empted: it leaves with what it has
+        generated ("abort"), its client resubmits it and its prefix is prefetched again later."""
+        ps = self.cache.page_size
+        short = [s for s in seqs if len(s.pages) * ps < len(s.tokens)]
+        if not short:
+            return seqs
+        gone = set()
+        for s in short:
+            if id(s) in gone:
+                continue
+            while len(s.pages) * ps < len(s.tokens):
+                got = self._alloc_pages(1)
+                if got is None:
+                    victims = [v for v in seqs if id(v) not in gone and v is not s]
+                    if not victims:
+                        raise RuntimeError("KV page pool too small for a single sequence")
+                    v = max(victims, key=lambda q: (q.t_submit, q.rid))
+                    gone.add(id(v))
+                    self.stats["preempted"] += 1
+                    with self._lock:
+                        self._running = [q for q in self._running if q is not v]
+                    self._resolve(v, "abort")
+                    continue
+                s.pages.append(got[0])
+                self.hn_pt[s.row, len(s.pages) - 1] = got[0]
+        return [q for q in seqs if id(q) not in gone] if gone else seqs
 
     def _prefix_remember(self, key: bytes, s: _Seq, logits_row: torch.Tensor) -> None:
         ps = self.cache.page_size
@@ -1020,6 +1074,9 @@ class NativeInferenceEngine(InferenceEngine):
         """One decode step for every running row. Host work is vectorised over rows (numpy on
         the pinned mirror) and the step costs one H2D copy, one graph replay, the sampling
         launch and one D2H copy."""
+        seqs = self._grow_pages(seqs, done)
+        if not seqs:
+            return
         hi = max(s.row for s in seqs) + 1
         B = min(next(b for b in DECODE_BUCKETS if b >= hi), self.max_batch)
         ps = self.cache.page_size

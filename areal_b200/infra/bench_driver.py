@@ -97,7 +97,7 @@ def _make_config(args, lay: dict, fileroot: str) -> GRPOConfig:
         # layer-input checkpoints, LM-head chunks (about 0.75 MB per micro-batch token) plus allocator slack
         infer = dict(reserve_free_gb=6.0 + mb_tokens * 0.75e-3, max_running_requests=256)
     else:
-        infer = dict(mem_fraction_static=0.88, max_running_requests=512)
+        infer = dict(mem_fraction_static=0.8, max_running_requests=512)   # the rest: CUDA graphs' pools, the broadcast path's staging buffer
     return GRPOConfig(
         experiment_name="bench-async-grpo", trial_name="t0", total_train_epochs=1000, seed=1,
         cluster=ClusterSpecConfig(fileroot=fileroot),

@@ -1130,3 +1130,71 @@ def adamw_step_(p32, m, v, g, p_bf16, state, lr, beta1, beta2, eps, wd, step) ->
     rc = _L().ab2_adamw(p32.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), int(g.dtype == torch.bfloat16),
                         _lib.ptr(p_bf16), _lib.ptr(state), p32.numel(), lr, beta1, beta2, eps, wd, int(step), _s())
     _lib.check(rc, "ab2_adamw")
+
+
+# ----------------------------------------------------------------------------- RL losses
+class _PPOTokenLoss(torch.autograd.Function):
+    """``sum over kept tokens of the clipped surrogate / n_valid`` with the gradient taken from the
+    same kernel pass (the loss is an elementwise function of the new log-probs)."""
+
+    @staticmethod
+    def forward(ctx, logp, prox, old, adv, mask, params_bytes, prox_is_logp):
+        n = logp.numel()
+        dev = logp.device
+        dlogp = torch.empty(n, dtype=torch.float32, device=dev)
+        loss_tok = torch.empty(n, dtype=torch.float32, device=dev)
+        ratio = torch.empty(n, dtype=torch.float32, device=dev)
+        behave_w = torch.empty(n, dtype=torch.float32, device=dev)
+        flags = torch.empty(n, dtype=torch.uint8, device=dev)
+        sums = torch.zeros(8, dtype=torch.float64, device=dev)
+        rc = _L().ab2_ppo_token_loss(logp.data_ptr(), None if prox_is_logp else prox.data_ptr(), old.data_ptr(), adv.data_ptr(),
+                                     mask.data_ptr(), n, params_bytes, dlogp.data_ptr(), loss_tok.data_ptr(), ratio.data_ptr(),
+                                     behave_w.data_ptr(), flags.data_ptr(), sums.data_ptr(), _s())
+        _lib.check(rc, "ab2_ppo_token_loss")
+        denom = sums[1].clamp(min=1.0)
+        ctx.save_for_backward(dlogp, denom)
+        ctx.shape = logp.shape
+        ctx.mark_non_differentiable(loss_tok, ratio, behave_w, flags, sums)
+        return (sums[0] / denom).float(), loss_tok, ratio, behave_w, flags, sums
+
+    @staticmethod
+    def backward(ctx, g, *unused):
+        dlogp, denom = ctx.saved_tensors
+        return (dlogp * (g / denom).float()).view(ctx.shape), None, None, None, None, None, None
+
+
+def ppo_token_loss(logp: torch.Tensor, prox: Optional[torch.Tensor], old: torch.Tensor, adv: torch.Tensor, mask: torch.Tensor,
+                   eps_clip: float, eps_clip_higher: Optional[float] = None, c_clip: Optional[float] = None,
+                   rs_action: int = 0, rs_metric: int = 0, rs_lower: Optional[float] = None, rs_upper: Optional[float] = None):
+    """Token-level decoupled PPO loss with token-level rejection sampling in ONE kernel (CUDA, fp32
+    inputs of identical shape; ``prox=None``: the proximal policy is the current one). Returns
+    ``(loss, per_token_loss, ratio, behave_weight, flags, sums)``; ``flags`` bits: 1 clipped, 2 dual
+    clipped, 4 behaviour weight > 0, 8 kept after rejection; ``sums`` (fp64): loss, valid, kept,
+    filtered, clipped, dual clipped, behave tokens."""
+    import struct
+
+    assert logp.is_cuda and logp.dtype == torch.float32
+    hi = eps_clip if eps_clip_higher is None else eps_clip_higher
+    params = struct.pack("fffiiffiii", float(eps_clip), float(hi), float(c_clip or 0.0), int(rs_action), int(rs_metric),
+                         float(rs_lower or 0.0), float(rs_upper or 0.0), int(rs_lower is not None), int(rs_upper is not None),
+                         int(prox is None))
+    f = lambda t: t.detach().to(torch.float32).contiguous().reshape(-1)
+    m = mask.to(torch.uint8).contiguous().reshape(-1) if mask.dtype != torch.uint8 else mask.contiguous().reshape(-1)
+    lp = logp.contiguous()
+    out = _PPOTokenLoss.apply(lp.reshape(-1) if lp.dim() > 1 else lp, None if prox is None else f(prox), f(old), f(adv), m, params, prox is None)
+    return out
+
+
+def gae_scan(rewards: torch.Tensor, values: torch.Tensor, loss_mask: torch.Tensor, seq_no_eos_mask: torch.Tensor, discount: float,
+             gae_lambda) -> tuple[torch.Tensor, torch.Tensor]:
+    """Token-level GAE over ``[B, L]`` CUDA tensors: one thread per sequence walks its row backwards."""
+    B, L = rewards.shape
+    dev = rewards.device
+    lam = gae_lambda.float().to(dev).contiguous() if torch.is_tensor(gae_lambda) else torch.full((B,), float(gae_lambda), device=dev)
+    adv = torch.empty(B, L, dtype=torch.float32, device=dev)
+    ret = torch.empty(B, L, dtype=torch.float32, device=dev)
+    rc = _L().ab2_gae_scan(rewards.float().contiguous().data_ptr(), values.float().contiguous().data_ptr(),
+                           loss_mask.to(torch.uint8).contiguous().data_ptr(), seq_no_eos_mask.to(torch.uint8).contiguous().data_ptr(),
+                           lam.data_ptr(), float(discount), B, L, adv.data_ptr(), ret.data_ptr(), _s())
+    _lib.check(rc, "ab2_gae_scan")
+    return adv, ret

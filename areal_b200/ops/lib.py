@@ -27,6 +27,8 @@ _SIGS = {
     "ab2_kernel_error_peek": ([c_void_p, c_void_p], c_int),
     "ab2_gemm_bf16_bcast": ([c_void_p] * 4 + [c_int] * 8 + [c_void_p], c_int),
     "ab2_tp_reduce_rmsnorm": ([c_void_p, c_int, c_ll] + [c_void_p] * 4 + [c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "ab2_ppo_token_loss": ([c_void_p] * 5 + [c_ll] + [c_void_p] * 8, c_int),
+    "ab2_gae_scan": ([c_void_p] * 5 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p], c_int),
     "ab2_push_plan": ([c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "ab2_num_sms": ([], c_int),
     "ab2_gemm_bf16": ([c_void_p] * 4 + [c_int] * 10 + [c_void_p], c_int),

@@ -55,6 +55,14 @@ class PPOTrainer:
         self.ft_spec = FinetuneSpec(total_train_epochs=config.total_train_epochs, dataset_size=len(train_dataset),
                                     train_batch_size=bs)
         self.model_config = model_config
+        # Single-controller mode (the reference's default, areal/trainer/rl_trainer.py:131-141 and
+        # :1123-1177): with ``scheduler.type`` set and no torchrun environment this process only
+        # orchestrates; engines live in worker processes that a scheduler starts and are driven
+        # through TrainController / RolloutController over RPC.
+        self._scheduler = None
+        self._owned_controllers: list = []
+        if actor_engine is None and rollout_engine is None and self._wants_single_controller():
+            actor_engine, rollout_engine = self._init_single_controller()
         self.actor = actor_engine or self._create_train_engine(config.actor, "actor")
         self.critic = self._create_train_engine(config.critic, "critic") if config.critic is not None else None
         self.ref = None
@@ -91,6 +99,55 @@ class PPOTrainer:
             raise ValueError("max_head_offpolicyness must be >= 0")
         if c.gconfig.n_samples < 1:
             raise ValueError("gconfig.n_samples must be >= 1")
+
+    def _wants_single_controller(self) -> bool:
+        from ..utils.environ import is_single_controller
+
+        sc = getattr(self.config, "scheduler", None)
+        return sc is not None and getattr(sc, "type", None) in ("local", "ray", "slurm") and is_single_controller()
+
+    def _init_single_controller(self):
+        """Scheduler -> worker processes -> engines created over RPC. Worker counts come from the
+        allocation strings (``actor.backend`` e.g. ``native:d2``, ``rollout.backend`` e.g.
+        ``native:d2t1``); a worker gets a GPU when the node has one per worker."""
+        import torch
+
+        from ..api.alloc_mode import ModelAllocation
+        from ..infra.controller import RolloutController, TrainController
+
+        c = self.config
+        kind = c.scheduler.type
+        if kind == "local":
+            from ..infra.scheduler import LocalScheduler
+
+            n_gpu = torch.cuda.device_count() if torch.cuda.is_available() else 0
+            sched = LocalScheduler(gpu_devices=None if n_gpu else [])
+        elif kind == "ray":
+            from ..infra.scheduler import RayScheduler
+
+            sched = RayScheduler()
+        else:
+            from ..infra.scheduler import SlurmScheduler
+
+            sched = SlurmScheduler()
+        self._scheduler = sched
+        n_train = ModelAllocation.from_str(c.actor.backend).parallel.world_size if c.actor.backend else 1
+        ra = ModelAllocation.from_str(c.rollout.backend).parallel if c.rollout.backend else None
+        n_roll = ra.dp_size if ra is not None else 1
+        use_gpu = bool(torch.cuda.is_available() and torch.cuda.device_count() >= n_train + n_roll)
+        gpw = 1 if use_gpu else 0
+        actor = TrainController("areal_b200.engine.train_engine.B200PPOActor", c.actor, sched, role="actor")
+        rollout = RolloutController("areal_b200.engine.infer_engine.NativeInferenceEngine", c.rollout, sched, role="rollout")
+        self._owned_controllers = [rollout, actor]
+        mc = self.model_config
+        actor.initialize(ft_spec=self.ft_spec, model_config=mc, seed=c.seed, n_workers=n_train, gpus_per_worker=gpw,
+                         group_size=c.gconfig.n_samples)
+        if mc is None:
+            mc = actor.model_config() if hasattr(actor, "model_config") and callable(actor.model_config) else None
+        rollout.initialize(n_workers=n_roll, gpus_per_worker=gpw,
+                           engine_kwargs={"model_config": mc, "infer_config": c.native_infer} if mc is not None else {"infer_config": c.native_infer},
+                           init_kwargs={"seed": c.seed, **({"model_path": c.actor.path} if mc is None else {})})
+        return actor, rollout
 
     def _make_dataloader(self, dataset, dcfg, rank: int = 0, world: int = 1):
         if dataset is None or dcfg is None:
@@ -263,6 +320,12 @@ class PPOTrainer:
         for e in (self.actor, self.critic, self.ref, self.teacher):
             if e is not None:
                 e.destroy()
+        if self._scheduler is not None:
+            try:
+                self._scheduler.delete_workers()
+            except Exception:
+                pass
+            self._scheduler = None
 
     def __enter__(self):
         return self

@@ -41,7 +41,7 @@ async def run_all(eng, reqs):
     return await asyncio.gather(*[eng.agenerate(r) for r in reqs])
 
 
-def run_engine(fused: bool, mc, args, tp_group, ctl_group, rank):
+def run_engine(fused: bool, mc, args, tp_group, ctl_group, main_group, rank):
     os.environ["AREAL_TP_FUSED"] = "1" if fused else "0"
     ic = NativeInferConfig(max_running_requests=max(8, args.batch), context_length=args.prompt + args.new + 64, page_size=64,
                            max_prefill_tokens=8192, mem_fraction_static=0.5)
@@ -59,7 +59,7 @@ def run_engine(fused: bool, mc, args, tp_group, ctl_group, rank):
         secs = time.perf_counter() - t0
         steps = eng.stats["decode_steps"] - steps0
         secs = secs / max(1, steps)
-    dist.barrier(group=ctl_group)
+    dist.barrier(group=main_group)       # never the engine thread's control group: that thread uses it all the time
     eng.destroy()
     err = oplib.kernel_error()
     assert err == 0, f"kernel error word = {err}"
@@ -78,10 +78,14 @@ def main():
     dist.init_process_group("nccl")
     rank = dist.get_rank()
     mc = preset(args.model)
+    import faulthandler
+
+    faulthandler.dump_traceback_later(420, exit=True)      # a stuck run prints its stacks and leaves
     tp_group = dist.new_group([0, 1])
-    ctl_group = dist.new_group([0, 1], backend="gloo")
-    want, ms_lib = run_engine(False, mc, args, tp_group, ctl_group, rank)
-    got, ms_fused = run_engine(True, mc, args, tp_group, ctl_group, rank)
+    ctl_group = dist.new_group([0, 1], backend="gloo")      # the engine threads' control exchange
+    main_group = dist.new_group([0, 1], backend="gloo")     # this script's own barriers
+    want, ms_lib = run_engine(False, mc, args, tp_group, ctl_group, main_group, rank)
+    got, ms_fused = run_engine(True, mc, args, tp_group, ctl_group, main_group, rank)
     if rank == 0:
         for w, g_ in zip(want, got):
             assert w.output_tokens == g_.output_tokens, (w.output_tokens[:8], g_.output_tokens[:8])
@@ -91,7 +95,7 @@ def main():
                           "ms_per_step_fused_graph": round(ms_fused * 1e3, 3),
                           "speedup": round(ms_lib / max(ms_fused, 1e-9), 3)}), flush=True)
     print("INFER_TP_GPU_OK", flush=True)
-    dist.barrier(group=ctl_group)
+    dist.barrier(group=main_group)
     dist.destroy_process_group()
 
 

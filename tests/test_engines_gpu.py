@@ -310,7 +310,8 @@ def test_prefix_sharing_reuses_prompt_pages_and_matches_plain_engine(prompt_len)
     eng.destroy()
 
 
-def test_prefix_eviction_under_page_pressure_keeps_rows_and_pages_consistent():
+@pytest.mark.parametrize("reserve_full", [True, False])
+def test_prefix_eviction_under_page_pressure_keeps_rows_and_pages_consistent(reserve_full):
     """A page pool too small for the stored prompts plus the running sequences: stored prompts get
     evicted between the admission of a sequence that counted on them and its start. Such a sequence
     goes back to the waiting queue and must not also take a decode row (it used to: every such
@@ -321,7 +322,8 @@ def test_prefix_eviction_under_page_pressure_keeps_rows_and_pages_consistent():
     model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=5)
 
     def engine(num_pages, share=True):
-        ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=256, enable_prefix_sharing=share)
+        ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=256, enable_prefix_sharing=share,
+                               reserve_full_length=reserve_full)
         ic.num_pages = num_pages
         return NativeInferenceEngine(InferenceEngineConfig(), ic, model=model, eos_token_id=None).initialize(device="cuda", start_executor=False)
 
@@ -345,3 +347,118 @@ def test_prefix_eviction_under_page_pressure_keeps_rows_and_pages_consistent():
     held = sum(len(e["pages"]) + (e["tail_page"] is not None) for e in tight._prefix.values())
     assert len(tight.cache.free) == tight.cache.num_pages - held
     tight.destroy()
+
+
+def test_on_demand_pages_preempt_and_resume_when_the_pool_runs_dry():
+    """Pages are taken as sequences grow. A pool that cannot hold every running sequence at full
+    length forces pre-emptions: the victim returns its partial output, its client resubmits it and
+    the generation continues after a new prefetch. Every request still delivers exactly its budget
+    of tokens with finite log-probs, and all rows and pages are back afterwards."""
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=9)
+    ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=256, enable_prefix_sharing=False)
+    ic.num_pages = 30                       # 8 sequences x ceil((20 + 100) / 16) = 64 pages would be needed at full length
+    eng = NativeInferenceEngine(InferenceEngineConfig(), ic, model=model, eos_token_id=None).initialize(device="cuda", start_executor=False)
+    g = GenerationHyperparameters(max_new_tokens=100, max_tokens=200, greedy=False, temperature=1.0, ignore_eos=True)
+
+    async def run():
+        return await asyncio.gather(*[eng.agenerate(ModelRequest(rid=f"p{i}", input_ids=[(11 * i + j) % 900 + 5 for j in range(20)], gconfig=g))
+                                      for i in range(12)])
+
+    outs = asyncio.run(run())
+    assert oplib.kernel_error() == 0
+    assert eng.stats["preempted"] > 0
+    for o in outs:
+        assert len(o.output_tokens) == 100 and len(o.output_logprobs) == 100 and o.stop_reason == "length"
+        assert all(lp <= 0 and lp > -50 for lp in o.output_logprobs)
+    assert sorted(eng._rows_free) == list(range(eng.max_batch)) and len(eng.cache.free) == eng.cache.num_pages
+    eng.destroy()
+
+
+def _tiny_actor(**opt_kw):
+    cfg = PPOActorConfig(init_from_scratch=True, dtype="bfloat16", optimizer=OptimizerConfig(lr=1e-4, **opt_kw),
+                         mb_spec=MicroBatchSpec(max_tokens_per_mb=1024), use_decoupled_loss=True, recompute_logprob=True,
+                         kl_ctl=0.0, ppo_n_minibatches=1)
+    eng = B200PPOActor(cfg)
+    eng.create_process_group()
+    eng.initialize(model_config=preset("tiny-qwen3"), seed=1)
+    return eng
+
+
+def test_optimizer_step_raises_when_a_device_wait_gave_up():
+    """A bounded wait that ran out anywhere before the optimizer step (here: a tensor-parallel
+    consumer whose peer never produced, limit 50 ms) must not be silent: the step reads the device
+    error word with its own status read and raises; the next step is clean again."""
+    from areal_b200.parallel.tp_decode import TPDecodeExchange
+
+    eng = _tiny_actor()
+    data = _batch()
+    data["prox_logp"] = eng.compute_logp(data)
+    eng.compute_advantages(data)
+    eng.ppo_update(data)                                     # a normal step first
+    exs = TPDecodeExchange.emulated(2, "cuda", 256, 64, timeout_ms=50)
+    x = torch.randn(16, 128, device="cuda").bfloat16()
+    w = torch.randn(256, 128, device="cuda").bfloat16()
+    p0 = exs[0].linear_bcast(x, w)                           # the second rank never produces
+    exs[0].reduce_rmsnorm(p0, torch.ones(256, device="cuda").bfloat16(), 1e-6, torch.zeros(16, 256, device="cuda").bfloat16())
+    with pytest.raises(oplib.KernelWaitTimeout):
+        eng.ppo_update(data)
+    stats = eng.ppo_update(data)                             # the word was cleared: training continues
+    assert stats[0]["update_successful"] == 1.0
+    eng.destroy()
+
+
+def test_offloaded_and_bf16_state_optimizers_follow_the_default_on_gpu():
+    """Host-resident optimizer state streamed through the GPU in (tiny, so several) chunks gives the
+    same parameters as the resident fused AdamW; bf16 moments with compensated weights stay close."""
+    data = _batch()
+    outs = {}
+    for name, kw in (("resident", {}), ("offload", dict(offload=True, offload_chunk_numel=1 << 16)), ("bf16", dict(type="adam_bf16"))):
+        eng = _tiny_actor(**kw)
+        d = dict(data)
+        d["prox_logp"] = eng.compute_logp(d)
+        eng.compute_advantages(d)
+        for _ in range(3):
+            st = eng.ppo_update(d)
+            assert st[0]["update_successful"] == 1.0
+        outs[name] = eng.store.flat_param.float().clone()
+        if name == "offload":
+            assert eng.optimizer.master.device.type == "cpu" and eng.optimizer.master.is_pinned()
+        eng.destroy()
+    assert torch.equal(outs["resident"], outs["offload"])
+    assert float((outs["resident"] - outs["bf16"]).abs().max()) < 3e-3
+    assert oplib.kernel_error() == 0
+
+
+def test_colocated_loop_runs_sixty_steps_on_gpu(tmp_path):
+    """Trainer and rollout engine sharing one GPU (shared weights, CUDA graphs, prefix sharing, pages
+    on demand in a small pool) for 60 steps: the configuration whose long runs used to die."""
+    from areal_b200.api.cli_args import (ClusterSpecConfig, DatasetConfig, GRPOConfig, NormConfig, SaverConfig, StatsLoggerConfig)
+    from areal_b200.dataset import RandomTokenDataset, bernoulli_reward_fn
+    from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
+    from areal_b200.trainer.rl_trainer import PPOTrainer
+
+    root = str(tmp_path)
+    ic = NativeInferConfig(max_running_requests=32, page_size=16, context_length=256, retain_kv_on_weight_update=True,
+                           enable_prefix_sharing=True)
+    ic.num_pages = 160
+    cfg = GRPOConfig(
+        experiment_name="gpu-loop", trial_name="t0", total_train_epochs=100, seed=1, cluster=ClusterSpecConfig(fileroot=root),
+        train_dataset=DatasetConfig(batch_size=2, shuffle=True, drop_last=True),
+        gconfig=GenerationHyperparameters(n_samples=8, max_new_tokens=96, max_tokens=200, temperature=1.0, ignore_eos=True),
+        rollout=InferenceEngineConfig(max_concurrent_rollouts=6, consumer_batch_size=2, max_head_offpolicyness=2),
+        native_infer=ic,
+        actor=PPOActorConfig(init_from_scratch=True, dtype="bfloat16", gradient_checkpointing=True,
+                             optimizer=OptimizerConfig(lr=1e-5), mb_spec=MicroBatchSpec(max_tokens_per_mb=2048),
+                             use_decoupled_loss=True, recompute_logprob=True, kl_ctl=0.0, ppo_n_minibatches=1,
+                             reward_norm=NormConfig(mean_level="group", std_level="group", group_size=8)),
+        saver=SaverConfig(fileroot=root, experiment_name="gpu-loop", trial_name="t0"),
+        stats_logger=StatsLoggerConfig(fileroot=root, experiment_name="gpu-loop", trial_name="t0", jsonl=False))
+    mc = preset("tiny-qwen3")
+    ds = RandomTokenDataset(size=64, prompt_len=40, vocab_size=mc.vocab_size, seed=2, median_len=40, max_len=96, min_len=4, n_samples=8)
+    with PPOTrainer(cfg, ds, model_config=mc) as tr:
+        hist = tr.train(workflow=RLVRWorkflow(bernoulli_reward_fn, cfg.gconfig, reward_in_process=True), max_steps=60)
+        eng = tr.rollout
+        assert eng._exc is None
+    assert len(hist) == 60 and all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
+    assert oplib.kernel_error() == 0

@@ -496,3 +496,66 @@ def test_decode_splitk_gemm_matches_fp32(M, N, K, with_resid):
     assert ((y.float() - ref).norm() / ref.norm()).item() < 4e-3
     y2 = OF.gemm_decode(x, w, r)                                    # the workspace is reusable without clearing
     assert torch.equal(y, y2)
+
+
+# --------------------------------------------------------------------------- RL losses
+@pytest.mark.parametrize("rs", [None, ("mask", "ratio", None, 5.0), ("clamp", "ratio", 0.5, 2.0), ("mask", "kl_k3", None, 0.05),
+                                ("mask", "binary_kl", None, 0.02), ("mask", "kl_k2", None, 0.02)])
+@pytest.mark.parametrize("c_clip,hi", [(None, None), (3.0, 0.28)])
+def test_fused_ppo_token_loss_matches_eager_statement(rs, c_clip, hi):
+    """Loss value, gradient with respect to the new log-probs and every logged per-token statistic
+    of the one-kernel loss against the eager PyTorch statement of the same math (fp32)."""
+    from areal_b200.algo import functional as AF
+    from areal_b200.api.cli_args import RejectionSamplingConfig
+
+    torch.manual_seed(3)
+    n = 5000
+    old = (-torch.rand(n, device="cuda") * 6).requires_grad_(False)
+    prox = old + 0.3 * torch.randn(n, device="cuda")
+    logp0 = prox + 0.25 * torch.randn(n, device="cuda")
+    adv = torch.randn(n, device="cuda")
+    adv[::7] = 0.0
+    mask = torch.rand(n, device="cuda") < 0.8
+    cfg = None
+    if rs is not None:
+        cfg = RejectionSamplingConfig(level="token", action=rs[0], metric=rs[1], lower=rs[2], upper=rs[3])
+    outs = []
+    for fused in (False, True):
+        AF._FUSED_LOSS = fused
+        lp = logp0.clone().requires_grad_(True)
+        loss, stat = AF.ppo_actor_loss_fn(lp, prox, old, adv, 0.2, mask, hi, c_clip, cfg, "token", None)
+        loss.backward()
+        outs.append((loss.detach(), lp.grad.clone(), stat))
+    AF._FUSED_LOSS = True
+    (l0, g0, s0), (l1, g1, s1) = outs
+    assert torch.allclose(l0, l1, rtol=1e-5, atol=1e-7), (float(l0), float(l1))
+    assert torch.allclose(g0, g1, rtol=1e-4, atol=1e-9)
+    assert torch.equal(s0["clip_mask"], s1["clip_mask"]) and torch.equal(s0["dual_clip_mask"], s1["dual_clip_mask"])
+    assert torch.allclose(s0["importance_weight"], s1["importance_weight"], rtol=1e-5)
+    assert torch.allclose(torch.where(mask, s0["loss"], torch.zeros_like(s0["loss"])), torch.where(mask, s1["loss"], torch.zeros_like(s1["loss"])),
+                          rtol=1e-4, atol=1e-7)
+    if rs is not None:
+        assert torch.equal(s0["behave_mask"], s1["behave_mask"])
+        assert torch.allclose(s0["behave_imp_weight"], s1["behave_imp_weight"], rtol=1e-5)
+        assert abs(float(s0["filtered_fraction"]) - float(s1["filtered_fraction"])) < 1e-6
+    assert float(s1["n_valid_tokens"]) == float(mask.sum())
+
+
+@pytest.mark.parametrize("lam", [0.95, "per_sequence"])
+def test_gae_scan_kernel_matches_the_loop(lam):
+    from areal_b200.algo.advantages import token_level_gae
+
+    torch.manual_seed(4)
+    B, L = 37, 301
+    rewards = torch.randn(B, L, device="cuda") * 0.1
+    values = torch.randn(B, L, device="cuda")
+    lm = (torch.rand(B, L, device="cuda") < 0.7).int()
+    lm[:, :20] = 0
+    no_eos = torch.rand(B, device="cuda") < 0.3
+    gl = 0.95 if lam == 0.95 else torch.rand(B, device="cuda") * 0.2 + 0.8
+    want_adv, want_ret = token_level_gae(rewards.cpu(), values.cpu(), lm.cpu(), no_eos.cpu(), 0.99, gl if lam == 0.95 else gl.cpu())
+    adv, ret = OF.gae_scan(rewards, values, lm, no_eos, 0.99, gl)
+    assert torch.allclose(adv.cpu(), want_adv, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ret.cpu(), want_ret, rtol=1e-4, atol=1e-5)
+    got_adv, _ = token_level_gae(rewards, values, lm, no_eos, 0.99, gl)      # CUDA inputs take the kernel
+    assert torch.allclose(got_adv, adv)

@@ -316,3 +316,32 @@ def test_worker_death_is_reported_as_worker_failed(tmp_path):
         assert sched.call_engine(ws[1].id, "scale", engine_name="w") == 2     # the survivor still answers
     finally:
         sched.delete_workers()
+
+
+def test_ppo_trainer_builds_its_own_controllers_when_a_scheduler_is_configured(tmp_path, monkeypatch):
+    """``scheduler.type: local`` and no torchrun environment: PPOTrainer itself starts worker
+    processes through the scheduler, creates the engines in them and runs the loop through the
+    controllers (two trainer workers from ``actor.backend``, one rollout worker)."""
+    from areal_b200.dataset import ArithmeticDataset
+    from areal_b200.infra.controller import RolloutController, TrainController
+    from areal_b200.trainer.rl_trainer import PPOTrainer
+
+    for k in ("RANK", "WORLD_SIZE", "AREAL_SPMD_MODE"):
+        monkeypatch.delenv(k, raising=False)
+    cfg = _grpo_cfg(str(tmp_path))
+    cfg.scheduler.type = "local"
+    cfg.actor.backend = "native:d2"
+    cfg.actor.model_config = {"preset": "tiny-qwen2", "vocab_size": 64, "num_layers": 2}
+    mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+    with PPOTrainer(cfg, ArithmeticDataset(size=64), model_config=mc) as tr:
+        assert isinstance(tr.actor, TrainController) and isinstance(tr.rollout, RolloutController)
+        assert tr.actor.dp_size == 2 and len(tr.rollout.workers) == 1
+        hist = tr.train(workflow="areal_b200.rollout.workflows.rlvr.RLVRWorkflow",
+                        workflow_kwargs={"reward_fn": "areal_b200.dataset.small_id_fraction_reward_fn", "gconfig": cfg.gconfig,
+                                         "reward_in_process": True})
+        assert len(hist) == 3 and all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
+        assert tr.rollout.get_version() == 3
+        sched = tr._scheduler
+    assert tr._scheduler is None                    # the trainer tore down what it started
+    with pytest.raises(WorkerNotFoundError):
+        sched.get_workers("actor")
