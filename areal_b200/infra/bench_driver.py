@@ -85,17 +85,22 @@ def _make_config(args, lay: dict, fileroot: str) -> GRPOConfig:
     global_prompts = bs * lay["dp"] * feeders
     mb_tokens = args.max_tokens_per_mb
     if mb_tokens <= 0:
-        mb_tokens = 16384 if lay["colocated"] else 8192
+        mb_tokens = 8192
     elif lay["colocated"]:
-        # one GPU holds the whole optimizer state, the gradients AND the KV cache: half-size micro-batches
-        mb_tokens = min(mb_tokens, 16384)
+        # one GPU holds the whole optimizer state, the gradients AND the KV cache: quarter-size micro-batches,
+        # so that most of what is left can hold KV pages
+        mb_tokens = min(mb_tokens, 8192)
     ctx = args.prompt_len + args.max_len + 64
-    args._resolved = {"gradient_checkpointing": bool(args.grad_ckpt), "max_tokens_per_mb": mb_tokens,
+    args._resolved = {"gradient_checkpointing": bool(args.grad_ckpt) if not (args.grad_ckpt < 0 and lay["colocated"]) else "memory_budget: all layers recomputed (colocated: the KV cache takes the rest)",
+                      "max_tokens_per_mb": mb_tokens,
                       "prompts_per_step": global_prompts, "prompts_per_batch": bs}
     if lay["colocated"]:
-        # what the trainer needs beside its resident state: activations of one recomputed micro-batch,
-        # layer-input checkpoints, LM-head chunks (about 0.75 MB per micro-batch token) plus allocator slack
-        infer = dict(reserve_free_gb=6.0 + mb_tokens * 0.75e-3, max_running_requests=256)
+        # what trainer and engine need beside the resident state and the KV pool. Measured peak with 8k-token
+        # micro-batches and every layer recomputed: 19.5 GB (layer-input checkpoints, one layer's activations and
+        # gradients, LM-head chunks, prefill activations of up to 16k tokens); the decode graphs of the larger
+        # buckets and allocator fragmentation come on top
+        reserve = float(os.environ.get("AREAL_BENCH_RESERVE_GB", "0") or 0) or (10.0 + mb_tokens * 2.0e-3)
+        infer = dict(reserve_free_gb=reserve, max_running_requests=256)
     else:
         infer = dict(mem_fraction_static=0.8, max_running_requests=512)   # the rest: CUDA graphs' pools, the broadcast path's staging buffer
     return GRPOConfig(
@@ -142,6 +147,34 @@ def _cap_micro_batch(args, actor) -> None:
         args._resolved["max_tokens_per_mb_capped_by_memory"] = True
 
 
+def _pick_recompute(args, actor, model_cfg) -> None:
+    """The activation policy, one rule at every N (``--grad-ckpt -1``): keep the activations of as
+    many layers as the memory left after parameters, gradients and optimizer state holds, recompute
+    the rest in backward (``memory_budget`` checkpointing; the kept layers are the last ones, whose
+    activations live shortest). Estimate per token of a rank's micro-batch slice: 0.30 MB per kept
+    layer (bf16 activations of attention and MLP plus what autograd saves), 8 KB per recomputed
+    layer (its input), one layer's working set, 5 GB for the LM-head chunks and 12 GB of slack."""
+    if args.grad_ckpt >= 0:
+        return
+    free, _ = torch.cuda.mem_get_info()
+    sp = max(1, getattr(actor, "sp_size", 1))
+    t = actor.config.mb_spec.max_tokens_per_mb // sp
+    n = model_cfg.num_layers
+    per_layer_gb = t * 0.30e-3 * (model_cfg.hidden_size / 4096.0)
+    avail = free / 2 ** 30 - 12.0 - 5.0 - per_layer_gb - n * t * 8e-6
+    keep = max(0, min(n, int(avail / per_layer_gb)))
+    if actor.cpu_group is not None:
+        tt = torch.tensor([keep], dtype=torch.int64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MIN, group=actor.cpu_group)
+        keep = int(tt[0])
+    frac = 1.0 - keep / n
+    actor.model.set_activation_checkpointing("memory_budget", frac)
+    args._resolved["gradient_checkpointing"] = f"memory_budget: {n - keep} of {n} layers recomputed"
+    args._resolved["free_gb_before_activations"] = round(free / 2 ** 30, 1)
+    logger.info("activation policy: %d of %d layers recomputed (%.1f GB free, %d tokens per rank and micro-batch)", n - keep, n,
+                free / 2 ** 30, t)
+
+
 def _dataset(args, model_cfg, seed: int):
     return RandomTokenDataset(size=4096, prompt_len=args.prompt_len, vocab_size=model_cfg.vocab_size, seed=seed,
                               median_len=args.median_len, max_len=args.max_len, min_len=16, n_samples=args.group_size)
@@ -185,6 +218,7 @@ def run_async_grpo_bench(args, clock_sampler_cls) -> Optional[dict]:
         trainer = make_split_trainer(cfg, model_cfg, split, groups, bus, ds, seed=1)
         _instrument_transfers(trainer.actor)
         _cap_micro_batch(args, trainer.actor)
+        _pick_recompute(args, trainer.actor, model_cfg)
         res = _timed_loop(args, trainer, None, clock_sampler_cls, world, rank, model_cfg, lay, parallelism=par, groups=groups)
         if rank == 0:
             bus.put("exit", 1)
@@ -218,6 +252,8 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, la
             dist.barrier(group=cpu_group)
         torch.cuda.synchronize()
 
+    mem_base = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
     trainer.train(workflow=wf, max_steps=W)
     trainer.start_step += W
     # ---- region A: device-timed
@@ -305,6 +341,8 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, la
             "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms, "weight_sync_device_ms": push_dev_ms,
             "tokens_counted": "prompt + response tokens of the trained sequences",
             "response_tokens_per_s": resp_a / (ms_a / 1e3),
+            "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+            "peak_memory_over_resident_gb": round((torch.cuda.max_memory_allocated() - mem_base) / 2 ** 30, 1),
             "trainer_busy_fraction": round(1.0 - phases.get("rollout", 0.0) / step_s, 3),
             "staleness_avg": round(sum(stale) / len(stale), 3) if stale else None,
             "staleness_max": max(stale_max) if stale_max else None,

@@ -87,6 +87,14 @@ def bench_gemm(a):
     fl = 2.0 * a.m * a.n * a.k
     by = 2.0 * (a.m * a.k + a.n * a.k) + C.element_size() * a.m * a.n
     res = report("gemm_bf16_tcgen05", ms, fl, by, m=a.m, n=a.n, k=a.k, layout=a.layout, epi=a.epi)
+    if a.bn == 0:
+        old = OF.GEMM_2SM
+        OF.GEMM_2SM = True
+        try:
+            ms3 = timeit(lambda: OF.gemm(Aop, Bop, a_mn=a_mn, b_mn=b_mn, out=C, epi=a.epi), a.iters, a.warmup)
+            report("gemm_bf16_tcgen05_2sm (cta_group::2, 256x256 per CTA pair)", ms3, fl, by, m=a.m, n=a.n, k=a.k, layout=a.layout, epi=a.epi)
+        finally:
+            OF.GEMM_2SM = old
     if a.compare:
         ref = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
         ms2 = timeit(lambda: torch.matmul(A, B.t(), out=ref), a.iters, a.warmup)

@@ -29,10 +29,23 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned 
   return v;
 }
 
-// slots: [P][M][H] bf16 (this rank's receive buffer of the current set), one CTA per row.
-// H % 8 == 0 and H <= 8 * VEC_PER_THREAD * blockDim.x.
-template <int VEC_PER_THREAD>
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ float block_sum_tp(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// slots: [P][M][H] bf16 (this rank's receive buffer of the current set), one CTA of TPR threads per
+// row. H % 8 == 0 and H <= 8 * VEC_PER_THREAD * TPR. The thread-to-column mapping and the order of
+// the sum of squares are those of rmsnorm_fwd_kernel (elementwise.cu) for the same H, so the result
+// is bit-identical to  all-reduce in bf16 -> residual add + RMSNorm  with the unfused kernels.
+template <int TPR, int VEC_PER_THREAD>
+__global__ void __launch_bounds__(TPR)
 tp_reduce_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int P, long long slot_stride,
                          const __nv_bfloat16* __restrict__ resid_in, __nv_bfloat16* __restrict__ resid_out,
                          __nv_bfloat16* __restrict__ x_out, const __nv_bfloat16* __restrict__ w, float eps, int M, int H,
@@ -40,7 +53,7 @@ tp_reduce_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int P, long lo
                          unsigned long long expected, long long limit_cycles, int* err) {
   pdl_wait();
   pdl_trigger();
-  __shared__ float red[8];
+  __shared__ float red[32];
   __shared__ int proceed;
   const int row = blockIdx.x;
   if (threadIdx.x == 0) {
@@ -66,7 +79,7 @@ tp_reduce_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int P, long lo
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < VEC_PER_THREAD; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
+    const int c = threadIdx.x + i * TPR;
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
     if (c < nvec) {
@@ -111,15 +124,11 @@ tp_reduce_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int P, long lo
       reinterpret_cast<uint4*>(resid_out + (size_t)row * H)[c] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
   }
-  ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  float tot = 0.f;
-  for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+  const float tot = (TPR == 32) ? warp_sum(ss) : block_sum_tp(ss, red);
   const float rs = rsqrtf(tot / (float)H + eps);
 #pragma unroll
   for (int i = 0; i < VEC_PER_THREAD; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
+    const int c = threadIdx.x + i * TPR;
     if (c < nvec) {
       const uint4 wr = reinterpret_cast<const uint4*>(w)[c];
       const uint32_t q[4] = {wr.x, wr.y, wr.z, wr.w};
@@ -158,23 +167,27 @@ int ab2_tp_reduce_rmsnorm(const void* slots, int P, long long slot_stride, const
                           const void* w, float eps, int M, int H, const void* counter, void* state, int timeout_ms, void* stream) {
   using namespace ab2;
   if (M <= 0) return 0;
-  if (P < 1 || (H & 7) || H > 8 * 4 * 256) return 10;
+  if (P < 1 || (H & 7) || H > 8192) return 10;
   int* err = ab2host::error_flag();
   if (!err) return 301;
   const unsigned long long expected = (unsigned long long)P * (unsigned long long)M * (unsigned long long)((H + 31) / 32);
   const long long limit = (long long)timeout_ms * 1900000LL;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int nvec = H / 8;
-  if (nvec <= 256) {
-    launch_pdl(tp_reduce_rmsnorm_kernel<1>, dim3(M), dim3(256), 0, s, (const __nv_bfloat16*)slots, P, slot_stride,
+  // same (threads per row, vectors per thread) as ab2_rmsnorm_fwd picks for this H
+  if (H <= 256) {
+    launch_pdl(tp_reduce_rmsnorm_kernel<32, 1>, dim3(M), dim3(32), 0, s, (const __nv_bfloat16*)slots, P, slot_stride,
                (const __nv_bfloat16*)resid_in, (__nv_bfloat16*)resid_out, (__nv_bfloat16*)x_out, (const __nv_bfloat16*)w, eps, M, H,
                (const unsigned long long*)counter, (unsigned long long*)state, expected, limit, err);
-  } else if (nvec <= 512) {
-    launch_pdl(tp_reduce_rmsnorm_kernel<2>, dim3(M), dim3(256), 0, s, (const __nv_bfloat16*)slots, P, slot_stride,
+  } else if (H <= 2048) {
+    launch_pdl(tp_reduce_rmsnorm_kernel<128, 2>, dim3(M), dim3(128), 0, s, (const __nv_bfloat16*)slots, P, slot_stride,
+               (const __nv_bfloat16*)resid_in, (__nv_bfloat16*)resid_out, (__nv_bfloat16*)x_out, (const __nv_bfloat16*)w, eps, M, H,
+               (const unsigned long long*)counter, (unsigned long long*)state, expected, limit, err);
+  } else if (H <= 4096) {
+    launch_pdl(tp_reduce_rmsnorm_kernel<128, 4>, dim3(M), dim3(128), 0, s, (const __nv_bfloat16*)slots, P, slot_stride,
                (const __nv_bfloat16*)resid_in, (__nv_bfloat16*)resid_out, (__nv_bfloat16*)x_out, (const __nv_bfloat16*)w, eps, M, H,
                (const unsigned long long*)counter, (unsigned long long*)state, expected, limit, err);
   } else {
-    launch_pdl(tp_reduce_rmsnorm_kernel<4>, dim3(M), dim3(256), 0, s, (const __nv_bfloat16*)slots, P, slot_stride,
+    launch_pdl(tp_reduce_rmsnorm_kernel<256, 4>, dim3(M), dim3(256), 0, s, (const __nv_bfloat16*)slots, P, slot_stride,
                (const __nv_bfloat16*)resid_in, (__nv_bfloat16*)resid_out, (__nv_bfloat16*)x_out, (const __nv_bfloat16*)w, eps, M, H,
                (const unsigned long long*)counter, (unsigned long long*)state, expected, limit, err);
   }

@@ -22,6 +22,9 @@ import torch.nn.functional as F
 from . import lib as _lib
 
 EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_BF16_RESID = 0, 1, 2, 3
+# 2-CTA (cta_group::2) GEMM for large products: AB2_GEMM_2SM=0 keeps everything on the one-CTA kernel
+GEMM_2SM = __import__("os").environ.get("AB2_GEMM_2SM", "0") == "1"
+GEMM_2SM_MIN_M = 1024
 
 
 def _L():
@@ -64,6 +67,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         return out
     if epi == EPI_BF16_RESID:
         assert resid is not None and resid.shape == out.shape and resid.stride() == out.stride()
+    if GEMM_2SM and bn == 0 and M >= GEMM_2SM_MIN_M and N >= 512 and K >= 256:
+        # large products: 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2), half the B traffic per SM
+        rc = _L().ab2_gemm_bf16_2sm(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(resid), M, N, K, a.stride(0), b.stride(0),
+                                    out.stride(0), int(a_mn), int(b_mn), epi, _s())
+        _lib.check(rc, "ab2_gemm_bf16_2sm")
+        return out
     rc = _L().ab2_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(resid), M, N, K, a.stride(0),
                             b.stride(0), out.stride(0), int(a_mn), int(b_mn), epi, bn, _s())
     _lib.check(rc, "ab2_gemm_bf16")
@@ -1193,8 +1202,10 @@ def gae_scan(rewards: torch.Tensor, values: torch.Tensor, loss_mask: torch.Tenso
     lam = gae_lambda.float().to(dev).contiguous() if torch.is_tensor(gae_lambda) else torch.full((B,), float(gae_lambda), device=dev)
     adv = torch.empty(B, L, dtype=torch.float32, device=dev)
     ret = torch.empty(B, L, dtype=torch.float32, device=dev)
-    rc = _L().ab2_gae_scan(rewards.float().contiguous().data_ptr(), values.float().contiguous().data_ptr(),
-                           loss_mask.to(torch.uint8).contiguous().data_ptr(), seq_no_eos_mask.to(torch.uint8).contiguous().data_ptr(),
-                           lam.data_ptr(), float(discount), B, L, adv.data_ptr(), ret.data_ptr(), _s())
+    # converted copies stay referenced until the launch is queued (a freed block could be handed to the next conversion)
+    r32, v32 = rewards.float().contiguous(), values.float().contiguous()
+    m8, e8 = loss_mask.to(torch.uint8).contiguous(), seq_no_eos_mask.to(torch.uint8).contiguous()
+    rc = _L().ab2_gae_scan(r32.data_ptr(), v32.data_ptr(), m8.data_ptr(), e8.data_ptr(), lam.data_ptr(), float(discount), B, L,
+                           adv.data_ptr(), ret.data_ptr(), _s())
     _lib.check(rc, "ab2_gae_scan")
     return adv, ret

@@ -32,6 +32,7 @@ _SIGS = {
     "ab2_push_plan": ([c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "ab2_num_sms": ([], c_int),
     "ab2_gemm_bf16": ([c_void_p] * 4 + [c_int] * 10 + [c_void_p], c_int),
+    "ab2_gemm_bf16_2sm": ([c_void_p] * 4 + [c_int] * 9 + [c_void_p], c_int),
     "ab2_qknorm_rope_fwd": ([c_void_p] * 8 + [c_int] * 4 + [c_ll, c_float, c_void_p], c_int),
     "ab2_qknorm_rope_bwd": ([c_void_p] * 11 + [c_int] * 4 + [c_ll, c_ll, c_void_p], c_int),
     "ab2_gemm_grouped": ([c_void_p] * 4 + [c_int] * 9 + [c_void_p], c_int),

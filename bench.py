@@ -62,7 +62,9 @@ def parse_args():
     ap.add_argument("--median-len", type=int, default=None)
     ap.add_argument("--max-len", type=int, default=None)
     ap.add_argument("--max-tokens-per-mb", type=int, default=None, help="packed micro-batch size in tokens (0: from the memory policy)")
-    ap.add_argument("--grad-ckpt", type=int, default=1, help="1: activations are recomputed in backward (the same policy at every N), 0: kept")
+    ap.add_argument("--grad-ckpt", type=int, default=-1,
+                    help="-1: one memory rule at every N (keep as many layers' activations as the memory left after parameters, "
+                         "gradients and optimizer state holds, recompute the rest), 1: recompute every layer, 0: keep everything")
     ap.add_argument("--prox-logp-method", type=str, default=None,
                     help="recompute (decoupled PPO's own forward pass for the proximal log-probs, the reference's default) | "
                          "reuse_train_logp | loglinear")

@@ -559,3 +559,35 @@ def test_gae_scan_kernel_matches_the_loop(lam):
     assert torch.allclose(ret.cpu(), want_ret, rtol=1e-4, atol=1e-5)
     got_adv, _ = token_level_gae(rewards, values, lm, no_eos, 0.99, gl)      # CUDA inputs take the kernel
     assert torch.allclose(got_adv, adv)
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 512, 256), (2048, 1024, 512), (1100, 776, 328), (4096, 4096, 1024)])
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn", "tt"])
+def test_gemm_2sm_pair_kernel_matches_fp32(M, N, K, layout):
+    """256 x 256 tiles on CTA pairs (tcgen05 cta_group::2): all operand layouts, ragged edges, every
+    epilogue, against fp32 matmul; and bit-identical to the one-CTA kernel (same accumulation order)."""
+    torch.manual_seed(M + N + K)
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    a_mn, b_mn = layout[0] == "t", layout[1] == "n"
+    Aop = A.t().contiguous() if a_mn else A
+    Bop = B.t().contiguous() if b_mn else B
+    ref = A.float() @ B.float().t()
+    old = OF.GEMM_2SM
+    try:
+        OF.GEMM_2SM = False
+        base = OF.gemm(Aop, Bop, a_mn=a_mn, b_mn=b_mn)
+        OF.GEMM_2SM = True
+        out = OF.gemm(Aop, Bop, a_mn=a_mn, b_mn=b_mn)
+        assert oplib.kernel_error() == 0
+        assert _rel_err(out, ref) < 4e-3
+        assert torch.equal(out, base)
+        acc = torch.ones(M, N, device="cuda")
+        OF.gemm(Aop, Bop, a_mn=a_mn, b_mn=b_mn, out=acc, epi=OF.EPI_F32_ACC)
+        assert _rel_err(acc, ref + 1.0) < 1e-4
+        resid = torch.randn(M, N, device="cuda").bfloat16()
+        y = OF.gemm(Aop, Bop, a_mn=a_mn, b_mn=b_mn, epi=OF.EPI_BF16_RESID, resid=resid)
+        assert _rel_err(y, ref + resid.float()) < 4e-3
+        assert oplib.kernel_error() == 0
+    finally:
+        OF.GEMM_2SM = old
