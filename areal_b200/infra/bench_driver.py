@@ -285,6 +285,7 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, la
     h2d_b, d2h_b = float(_ByteCounter.h2d), float(actor.d2h_bytes)
     push_ms = getattr(getattr(actor, "_weight_pusher", None), "last_ms", None)
     push_dev_ms = getattr(getattr(actor, "_weight_pusher", None), "last_dev_ms", None)
+    push_gbs = getattr(getattr(actor, "_weight_pusher", None), "last_gbps", None)
     # ---- region C: the same job on the library-collective path (NCCL), a few steps
     Kc = args.nccl_steps if args.nccl_steps >= 0 else (max(2, K // 5) if world >= 2 else 0)
     ms_c = tok_c = 0.0
@@ -339,6 +340,7 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, la
             "decode_switches": {k_: os.environ.get(k_, "0") for k_ in ("AB2_PDL", "AB2_DECODE_SPLITK")},
             "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
             "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms, "weight_sync_device_ms": push_dev_ms,
+            "weight_sync_gbs_per_trainer_gpu": round(push_gbs, 1) if push_gbs else None,
             "tokens_counted": "prompt + response tokens of the trained sequences",
             "response_tokens_per_s": resp_a / (ms_a / 1e3),
             "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),

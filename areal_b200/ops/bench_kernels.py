@@ -335,10 +335,44 @@ def bench_ep(a):
     return report("ep_dispatch_bwd", ms, bytes_=2 * N * H * 2 + T * H * 2, rows=N, hidden=H, note="scaled rows out + gate-weight gradients (reads the saved rows)")
 
 
+def bench_push_plan(a):
+    """The one-launch re-shard of ONE trainer shard (1 of ``--shards`` FSDP ranks) of ``--model`` into the
+    tensor-parallel layout (``--tp``) of ``--replicas`` rollout replicas. On one GPU the "replicas" are local
+    buffers, so this times the kernel against HBM (read the shard once, write it ``replicas`` times); over
+    NVLink the same launch is timed inside ``bench.py`` (``weight_sync_device_ms``)."""
+    from ..engine.flat_params import flat_layout
+    from ..models.config import preset
+    from ..models.decoder import build_model
+    from ..parallel import tp as TP
+    from ..parallel.weight_push import TPPushPlan, build_push_plan, tp_dst_layout
+
+    cfg = preset(a.model)
+    meta = build_model(cfg, dtype=torch.bfloat16, device="meta")
+    names = [n for n, _ in meta.named_parameters()]
+    shapes = [tuple(p.shape) for _, p in meta.named_parameters()]
+    offs, padded = flat_layout([p.numel() for _, p in meta.named_parameters()], a.shards)
+    lo = padded // a.shards * (a.shards - 1)                     # the last shard (has the LM head and the last layers)
+    layout = tp_dst_layout(cfg, a.tp)
+    ops = build_push_plan(cfg, names, offs, shapes, (lo, lo + padded // a.shards), a.tp, layout)
+    plan = TPPushPlan(ops, a.tp, "cuda")
+    src = torch.randn(padded // a.shards, device="cuda").bfloat16()
+    for op in plan.ops:                                          # the source buffer here holds the shard only
+        op.src_off -= lo
+    plan = TPPushPlan(plan.ops, a.tp, "cuda")
+    local = build_model(TP.local_config(cfg, a.tp), dtype=torch.bfloat16, device="meta")
+    _, n_local = flat_layout([p.numel() for _, p in local.named_parameters()], 1)
+    dst = [torch.empty(n_local, dtype=torch.bfloat16, device="cuda") for _ in range(a.replicas * a.tp)]
+    ptrs = [t.data_ptr() for t in dst]
+    ms = timeit(lambda: plan.run(src, ptrs, a.replicas), a.iters, a.warmup)
+    return report("push_plan (FSDP shard -> TP layout, one launch)", ms, bytes_=plan.bytes * (1 + a.replicas), ops=len(plan.ops), tp=a.tp,
+                  replicas=a.replicas, shard_gb=round(plan.bytes / 1e9, 2), note="local destinations: HBM-bound form of the NVLink push")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_decode", "gemm_fp8", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
-                                           "engine_decode", "ep"])
+                                           "engine_decode", "ep", "push_plan"])
+    ap.add_argument("--shards", type=int, default=4); ap.add_argument("--tp", type=int, default=2); ap.add_argument("--replicas", type=int, default=2)
     ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
@@ -357,7 +391,7 @@ def main(argv=None):
         a.rows = 2048
     return {"gemm": bench_gemm, "gemm_decode": bench_gemm_decode, "gemm_fp8": bench_gemm_fp8, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
             "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
-            "engine_decode": bench_engine_decode, "ep": bench_ep}[a.kernel](a)
+            "engine_decode": bench_engine_decode, "ep": bench_ep, "push_plan": bench_push_plan}[a.kernel](a)
 
 
 if __name__ == "__main__":

@@ -93,7 +93,7 @@ def parse_args():
     if args.staleness is None:
         args.staleness = pre.get("staleness", 8)
     if args.prompts_per_gpu is None:
-        args.prompts_per_gpu = pre.get("prompts_per_gpu", 1.0)
+        args.prompts_per_gpu = pre.get("prompts_per_gpu", 2.0)
     if args.prox_logp_method is None:
         args.prox_logp_method = pre.get("prox_logp_method", "recompute")
     if not args.sp and "sp" in pre:
