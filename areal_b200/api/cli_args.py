@@ -128,6 +128,7 @@ class FSDPEngineConfig:
     fuse_reduce_scatter_adamw: bool = True   # fused RS + cast/scale + sharded AdamW kernel
     fuse_allgather_gemm: bool = True         # param all-gather fused into the consuming GEMM
     fuse_ulysses_projections: bool = True    # sequence-parallel all-to-alls folded into the QKV / output projection kernels
+    reduce_in_switch: bool = False           # gradient reduce-scatter by multimem.ld_reduce (NVLS) when a multicast mapping exists
     bucket_mb: int = 256
     per_layer_optim_step: bool = False        # accepted for compatibility (the flat sharded optimizer steps once)
     optim_step_prefetch_layers: int = 1
@@ -412,6 +413,9 @@ class NativeInferConfig:
     # Colocated engines: size the KV pool as (free memory - reserve_free_gb) instead of a fraction, so
     # the trainer sharing the GPU keeps a known amount for its activations. 0 = use the fraction.
     reserve_free_gb: float = 0.0
+    # KV pool in pausable memory (addresses survive while the physical pages leave the GPU): offload() then
+    # really returns the pool's memory to the device and onload() takes it back without re-capturing CUDA graphs
+    pausable_kv_cache: bool = False
     kv_cache_dtype: str = "bfloat16"
     use_cuda_graph: bool = True
     weight_dtype: str = "bfloat16"  # or float8_e4m3fn (block-scaled)

@@ -77,10 +77,22 @@ class _Seq:
 class PagedKVCache:
     """K and V pages for all layers: ``[layers, 2, num_pages * page_size, Hkv, D]``."""
 
-    def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int, device, dtype):
+    def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int, device, dtype, pausable: bool = False):
         self.page_size, self.num_pages = page_size, num_pages
-        self.data = torch.zeros(cfg.num_layers, 2, num_pages * page_size, cfg.num_kv_heads, cfg.head_dim,
-                                device=device, dtype=dtype)
+        shape = (cfg.num_layers, 2, num_pages * page_size, cfg.num_kv_heads, cfg.head_dim)
+        self.pausable = None
+        if pausable:
+            from ..ops import vmm
+
+            if vmm.available():
+                n = 1
+                for d in shape:
+                    n *= d
+                self.pausable = vmm.PausableBuffer(n * torch.empty(0, dtype=dtype).element_size(), device, keep_contents=False)
+                self.data = self.pausable.tensor(dtype, shape)
+                self.data.zero_()
+        if self.pausable is None:
+            self.data = torch.zeros(*shape, device=device, dtype=dtype)
         self.free = list(range(num_pages - 1, -1, -1))
         self.ref = [0] * num_pages          # users of a page: its sequence, plus the prefix cache and other sequences when shared
 
@@ -245,7 +257,8 @@ class NativeInferenceEngine(InferenceEngine):
         n_pages = max(16, min(want, budget // per_page))
         if getattr(ic, "num_pages", None):
             n_pages = ic.num_pages
-        self.cache = PagedKVCache(cfg, n_pages, ic.page_size, self.device, torch.bfloat16)
+        self.cache = PagedKVCache(cfg, n_pages, ic.page_size, self.device, torch.bfloat16,
+                                  pausable=bool(getattr(ic, "pausable_kv_cache", False)))
         self.max_pages_per_seq = ic.context_length // ic.page_size + 1
         B = max(b for b in DECODE_BUCKETS if b <= max(1, ic.max_running_requests)) if ic.max_running_requests >= 1 else 1
         self.max_batch = B
@@ -384,15 +397,34 @@ class NativeInferenceEngine(InferenceEngine):
         return fut
 
     def offload(self, tags=None):
-        """Drops the KV cache (and CUDA graphs that point into it); weights stay."""
+        """Gives the KV pool's memory back to the device. With a pausable pool the addresses (and the
+        CUDA graphs that point into them) survive; otherwise the pool and the graphs are dropped."""
         self.pause_generation()
+        if self.cache is not None and self.cache.pausable is not None:
+            self._abort_all_now()
+            self._prefix.clear()
+            self.cache.free = list(range(self.cache.num_pages - 1, -1, -1))
+            self.cache.ref = [0] * self.cache.num_pages
+            torch.cuda.synchronize(self.device)
+            self.cache.pausable.pause()
+            return
         self._graphs.clear()
         if self.cache is not None:
             self._saved_cache_shape = (self.cache.num_pages, self.cache.page_size)
             self.cache = None
             torch.cuda.empty_cache()
 
+    def _abort_all_now(self):
+        """Requests in flight lose their KV pages: they return what they have and their clients resubmit."""
+        self._abort_all()
+
     def onload(self, tags=None):
+        if self.cache is not None and self.cache.pausable is not None:
+            if self.cache.pausable.paused:
+                self.cache.pausable.resume()
+                self.cache.data.zero_()
+            self.continue_generation()
+            return
         if self.cache is None and self.device.type == "cuda" and not self._recompute_decode:
             n, ps = self._saved_cache_shape
             self.cache = PagedKVCache(self.model_config, n, ps, self.device, torch.bfloat16)

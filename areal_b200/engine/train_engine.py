@@ -451,9 +451,14 @@ class B200TrainEngine(TrainEngine):
         if alloc is not None:
             from ..parallel.fused_zero import FusedGradReducer
 
+            mc = 0
+            if cfg.fsdp.reduce_in_switch or os.environ.get("AREAL_NVLS_REDUCE", "0") == "1":
+                # in-switch reduction (NVLS) when the symmetric allocation came with a multicast mapping
+                mc = int(getattr(self._symm_handles[self.store.flat_grad.data_ptr()][0], "multicast_ptr", 0) or 0)
+                logger.info("gradient reduce-scatter through the NVLink switch: %s", "on" if mc else "no multicast mapping, peer loads")
             self._grad_reducer = FusedGradReducer(self.store, self._shard_group,
                                                   self.peer_ptrs(self.store.flat_grad, self._shard_ranks),
-                                                  self.peer_ptrs(self.store.flat_param, self._shard_ranks))
+                                                  self.peer_ptrs(self.store.flat_param, self._shard_ranks), grad_multicast_ptr=mc)
         self._initialized = True
         logger.info("initialised %s: %.2fB params, dtype %s, dp=%d sp=%d, %.1fs", model_config.arch,
                     model_config.num_params() / 1e9, dtype, self.dp_size, self.sp_size, time.time() - t0)

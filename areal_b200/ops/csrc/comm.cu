@@ -4,6 +4,7 @@
 //
 //   signal_barrier     all-to-all flag exchange with a bounded wait (error status, no trap)
 //   rs_sumsq           gradient reduce-scatter by peer loads + squared-norm partial of the shard
+//   rs_sumsq_multimem  the same through the NVLink switch: multimem.ld_reduce on the multicast address
 //   norm_allreduce     exchanges the per-shard partials through peer stores -> global sum
 //   adamw_push         sharded AdamW whose bf16 result is written straight into every
 //                      destination buffer (trainer peers = parameter all-gather, rollout
@@ -70,6 +71,36 @@ __global__ void rs_sumsq_kernel(PeerPtrs grads, int world, long long lo, long lo
       const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
     }
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    reinterpret_cast<float4*>(out)[i] = s;
+    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  acc = warp_sum(acc);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = acc;
+  __syncthreads();
+  if (w == 0) {
+    float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+    t = warp_sum(t);
+    if (l == 0) atomicAdd(state, t);
+  }
+}
+
+// The same reduce-scatter through the NVLink switch (NVLS): `mc` is the MULTICAST address of the
+// symmetric gradient buffer; one multimem.ld_reduce returns the sum over all ranks of 16 bytes, so a
+// rank issues one load per element group instead of one per peer and the addition happens in the
+// switch. Ordering is the caller's: a barrier after every rank's gradient writes, before this kernel.
+__global__ void rs_sumsq_multimem_kernel(const float* __restrict__ mc, long long lo, long long n, float* __restrict__ out,
+                                         float* __restrict__ state, float scale) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 s;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(s.x), "=f"(s.y), "=f"(s.z), "=f"(s.w)
+                 : "l"(mc + lo + 4 * i)
+                 : "memory");
     s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
     reinterpret_cast<float4*>(out)[i] = s;
     acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
@@ -339,6 +370,14 @@ int ab2_rs_sumsq(void* const* grads, int world, long long lo, long long n, float
   if (n <= 0) return 0;
   rs_sumsq_kernel<<<grid_of(n / 4), 256, 0, (cudaStream_t)stream>>>(make_ptrs(grads, world), world, lo, n, out, state,
                                                                     scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+// mc_grads: multicast (NVLS) address of the symmetric fp32 gradient buffer.
+int ab2_rs_sumsq_multimem(const void* mc_grads, long long lo, long long n, float* out, float* state, float scale, void* stream) {
+  if (!mc_grads || (n & 3) || (lo & 3)) return 10;
+  if (n <= 0) return 0;
+  rs_sumsq_multimem_kernel<<<grid_of(n / 4), 256, 0, (cudaStream_t)stream>>>((const float*)mc_grads, lo, n, out, state, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

@@ -27,6 +27,8 @@ oplib.declare("ab2_signal_barrier", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int
                                      ctypes.c_void_p])
 oplib.declare("ab2_rs_sumsq", [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_void_p,
                                ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p])
+oplib.declare("ab2_rs_sumsq_multimem", [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_float, ctypes.c_void_p])
 oplib.declare("ab2_norm_allreduce", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                      ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p])
 oplib.declare("ab2_adamw_push", [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_longlong] +

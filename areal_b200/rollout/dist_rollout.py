@@ -51,8 +51,9 @@ class DistRolloutCoordinator:
             batch = redistribute_trajectories(batch, te.data_parallel_group, self.granularity)
         g = te.context_and_model_parallel_group
         if g is not None and dist.get_world_size(g) > 1:
-            batch = D.broadcast_tensor_container(batch, src=te.current_data_parallel_head(), group=g,
-                                                 device=getattr(te, "device", None) if dist.get_backend(g) == "nccl" else None)
+            # the batch stays a host batch on every rank (the engine stages micro-batches itself); an NCCL
+            # group only carries the pickled bytes through device memory
+            batch = D.broadcast_tensor_container(batch, src=te.current_data_parallel_head(), group=g)
         return batch
 
     def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None) -> dict:

@@ -1,7 +1,8 @@
 """Key-value rendezvous: ``add / get / wait / get_subtree / delete / watch`` with in-memory and
 shared-filesystem (NFS) backends and optional TTL keep-alive. Reference:
 ``areal/utils/name_resolve.py`` (Memory / NFS / Etcd3 / Ray repositories) and ``utils/names.py``.
-Etcd and Ray are not available here; selecting them raises a clear error."""
+The etcd backend speaks etcd's JSON gateway over HTTP (no client package), the Ray backend keeps
+the records in a named detached actor."""
 from __future__ import annotations
 
 import os
@@ -198,6 +199,200 @@ class NfsNameRecordRepository(NameRecordRepository):
                 pass
 
 
+class Etcd3NameRecordRepository(NameRecordRepository):
+    """Records in an etcd v3 cluster, spoken to through etcd's own JSON gateway (``/v3/kv/put``,
+    ``/v3/kv/range``, ``/v3/kv/deleterange``, ``/v3/lease/grant``, ``/v3/lease/keepalive``): no
+    client package is needed. ``keepalive_ttl`` attaches a lease that a background thread renews
+    until the entry is deleted, so entries of a process that died disappear on their own
+    (reference: ``areal/utils/name_resolve.py:414`` Etcd3NameRecordRepository)."""
+
+    def __init__(self, addr: str = "localhost:2379", timeout: float = 5.0):
+        import base64
+        import json as _json
+        import urllib.request
+
+        self._b64 = lambda s_: base64.b64encode(s_.encode()).decode()
+        self._unb64 = lambda s_: base64.b64decode(s_).decode()
+        self._json, self._req = _json, urllib.request
+        self.base = addr if addr.startswith("http") else f"http://{addr}"
+        self.timeout = timeout
+        self._mine: set[str] = set()
+        self._leases: dict[str, tuple[str, float, float]] = {}    # name -> (lease id, ttl, next renewal)
+        self._lock = threading.Lock()
+        self._stop = threading.Event()
+        self._keeper: Optional[threading.Thread] = None
+
+    def _call(self, path: str, body: dict) -> dict:
+        req = self._req.Request(self.base + path, data=self._json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+        with self._req.urlopen(req, timeout=self.timeout) as r:
+            return self._json.loads(r.read().decode() or "{}")
+
+    @staticmethod
+    def _range_end(prefix: str) -> str:
+        b = bytearray(prefix.encode())
+        b[-1] += 1
+        return bytes(b).decode("latin-1")
+
+    def _keepalive_loop(self):
+        while not self._stop.wait(0.2):
+            now = time.monotonic()
+            with self._lock:
+                due = [(n, lid, ttl) for n, (lid, ttl, nxt) in self._leases.items() if now >= nxt]
+            for n, lid, ttl in due:
+                try:
+                    self._call("/v3/lease/keepalive", {"ID": lid})
+                except Exception:
+                    pass
+                with self._lock:
+                    if n in self._leases:
+                        self._leases[n] = (lid, ttl, now + max(0.2, ttl / 3))
+
+    def add(self, name, value, delete_on_exit=True, keepalive_ttl=None, replace=False):
+        name = name.rstrip("/")
+        if not replace:
+            try:
+                self.get(name)
+                raise NameEntryExistsError(name)
+            except NameEntryNotFoundError:
+                pass
+        body = {"key": self._b64(name), "value": self._b64(str(value))}
+        if keepalive_ttl:
+            lease = self._call("/v3/lease/grant", {"TTL": int(max(1, keepalive_ttl))})
+            body["lease"] = lease["ID"]
+            with self._lock:
+                self._leases[name] = (lease["ID"], float(keepalive_ttl), time.monotonic() + keepalive_ttl / 3)
+            if self._keeper is None:
+                self._keeper = threading.Thread(target=self._keepalive_loop, name="etcd-keepalive", daemon=True)
+                self._keeper.start()
+        self._call("/v3/kv/put", body)
+        if delete_on_exit:
+            self._mine.add(name)
+        return name
+
+    def delete(self, name):
+        name = name.rstrip("/")
+        res = self._call("/v3/kv/deleterange", {"key": self._b64(name)})
+        with self._lock:
+            self._leases.pop(name, None)
+        self._mine.discard(name)
+        if int(res.get("deleted", 0) or 0) == 0:
+            raise NameEntryNotFoundError(name)
+
+    def clear_subtree(self, name_root):
+        root = name_root.rstrip("/") + "/"
+        self._call("/v3/kv/deleterange", {"key": self._b64(root), "range_end": self._b64(self._range_end(root))})
+        try:
+            self._call("/v3/kv/deleterange", {"key": self._b64(name_root.rstrip("/"))})
+        except Exception:
+            pass
+
+    def get(self, name):
+        res = self._call("/v3/kv/range", {"key": self._b64(name.rstrip("/"))})
+        kvs = res.get("kvs") or []
+        if not kvs:
+            raise NameEntryNotFoundError(name)
+        return self._unb64(kvs[0]["value"])
+
+    def _range(self, name_root):
+        root = name_root.rstrip("/") + "/"
+        res = self._call("/v3/kv/range", {"key": self._b64(root), "range_end": self._b64(self._range_end(root))})
+        return sorted((self._unb64(kv["key"]), self._unb64(kv["value"])) for kv in (res.get("kvs") or []))
+
+    def get_subtree(self, name_root):
+        return [v for _, v in self._range(name_root)]
+
+    def find_subtree(self, name_root):
+        return [k for k, _ in self._range(name_root)]
+
+    def reset(self):
+        self._stop.set()
+        for n in list(self._mine):
+            try:
+                self.delete(n)
+            except Exception:
+                pass
+
+
+class RayNameRecordRepository(NameRecordRepository):
+    """Records in a named, detached Ray actor that every process of the job can look up (reference:
+    ``areal/utils/name_resolve.py:885`` RayNameResolveRepository). ``ray_module`` lets tests hand in a
+    stand-in for the ``ray`` package."""
+
+    class _Store:
+        def __init__(self):
+            self.kv: dict[str, str] = {}
+
+        def put(self, k, v, replace):
+            if k in self.kv and not replace:
+                return False
+            self.kv[k] = v
+            return True
+
+        def get(self, k):
+            return self.kv.get(k)
+
+        def delete(self, k):
+            return self.kv.pop(k, None) is not None
+
+        def prefix(self, root):
+            return sorted((k, v) for k, v in self.kv.items() if k.startswith(root))
+
+        def clear(self, root):
+            for k in [k for k in self.kv if k == root.rstrip("/") or k.startswith(root)]:
+                del self.kv[k]
+
+    def __init__(self, actor_name: str = "ray_kv_store", ray_module=None):
+        if ray_module is None:
+            import ray as ray_module  # noqa: F811  (only needed for this backend)
+        self.ray = ray_module
+        if not self.ray.is_initialized():
+            self.ray.init(ignore_reinit_error=True)
+        try:
+            self.actor = self.ray.get_actor(actor_name)
+        except Exception:
+            self.actor = self.ray.remote(self._Store).options(name=actor_name, lifetime="detached", get_if_exists=True).remote()
+        self._mine: set[str] = set()
+
+    def _do(self, method: str, *a):
+        return self.ray.get(getattr(self.actor, method).remote(*a))
+
+    def add(self, name, value, delete_on_exit=True, keepalive_ttl=None, replace=False):
+        name = name.rstrip("/")
+        if not self._do("put", name, str(value), bool(replace)):
+            raise NameEntryExistsError(name)
+        if delete_on_exit:
+            self._mine.add(name)
+        return name
+
+    def delete(self, name):
+        name = name.rstrip("/")
+        self._mine.discard(name)
+        if not self._do("delete", name):
+            raise NameEntryNotFoundError(name)
+
+    def clear_subtree(self, name_root):
+        self._do("clear", name_root.rstrip("/") + "/")
+
+    def get(self, name):
+        v = self._do("get", name.rstrip("/"))
+        if v is None:
+            raise NameEntryNotFoundError(name)
+        return v
+
+    def get_subtree(self, name_root):
+        return [v for _, v in self._do("prefix", name_root.rstrip("/") + "/")]
+
+    def find_subtree(self, name_root):
+        return [k for k, _ in self._do("prefix", name_root.rstrip("/") + "/")]
+
+    def reset(self):
+        for n in list(self._mine):
+            try:
+                self.delete(n)
+            except Exception:
+                pass
+
+
 # Processes started by a scheduler / launcher inherit the rendezvous location through the
 # environment: AREAL_NAME_RESOLVE_ROOT selects the shared-filesystem backend.
 _DEFAULT: NameRecordRepository = (NfsNameRecordRepository(os.environ["AREAL_NAME_RESOLVE_ROOT"])
@@ -205,15 +400,18 @@ _DEFAULT: NameRecordRepository = (NfsNameRecordRepository(os.environ["AREAL_NAME
 
 
 def reconfigure(config=None, **kwargs) -> NameRecordRepository:
-    """Selects the backend from a ``NameResolveConfig`` (``type``: memory | nfs)."""
+    """Selects the backend from a ``NameResolveConfig`` (``type``: memory | nfs | etcd3 | ray)."""
     global _DEFAULT
     t = getattr(config, "type", None) or kwargs.get("type", "memory")
     if t == "memory":
         _DEFAULT = MemoryNameRecordRepository()
     elif t == "nfs":
         _DEFAULT = NfsNameRecordRepository(getattr(config, "nfs_record_root", None) or kwargs.get("record_root", "/tmp/areal/name_resolve"))
-    elif t in ("etcd3", "ray"):
-        raise RuntimeError(f"name_resolve backend '{t}' needs a package that is not installed in this image; use memory or nfs")
+    elif t == "etcd3":
+        _DEFAULT = Etcd3NameRecordRepository(getattr(config, "etcd3_addr", None) or kwargs.get("addr", "localhost:2379"))
+    elif t == "ray":
+        _DEFAULT = RayNameRecordRepository(getattr(config, "ray_actor_name", None) or kwargs.get("actor_name", "ray_kv_store"),
+                                           ray_module=kwargs.get("ray_module"))
     else:
         raise ValueError(f"unknown name_resolve backend '{t}'")
     return _DEFAULT

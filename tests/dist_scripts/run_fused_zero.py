@@ -32,11 +32,12 @@ def batch(rank, B=4, L=200, V=1024):
                 versions=torch.zeros(B, L, dtype=torch.int32), rewards=torch.randn(B, generator=g))
 
 
-def run(fused: bool):
+def run(fused: bool, in_switch: bool = False):
     cfg = PPOActorConfig(init_from_scratch=True, dtype="bfloat16", optimizer=OptimizerConfig(lr=1e-3, gradient_clipping=0.5),
                          mb_spec=MicroBatchSpec(max_tokens_per_mb=1024), use_decoupled_loss=True, recompute_logprob=True,
                          kl_ctl=0.0, ppo_n_minibatches=1)
     cfg.fsdp.fuse_reduce_scatter_adamw = fused
+    cfg.fsdp.reduce_in_switch = in_switch
     e = B200PPOActor(cfg)
     e.create_process_group()
     e.initialize(model_config=preset("tiny-qwen3"), seed=7)
@@ -69,6 +70,15 @@ def main():
     assert same
     for a, b in gn:
         assert abs(a - b) / max(b, 1e-6) < 2e-2
+    if os.environ.get("AREAL_TEST_NVLS_REDUCE", "0") == "1":
+        # the same step with the gradient reduce-scatter formed inside the NVLink switch (multimem.ld_reduce)
+        ps, ss, es = run(True, in_switch=True)
+        used = bool(es._grad_reducer.grad_mc)
+        rel_s = ((ps - pf).norm() / pf.norm()).item()
+        print(f"rank {dist.get_rank()} in-switch reduce used {used} rel_diff_vs_peer_loads {rel_s:.3e} "
+              f"grad_norms {[(a['grad_norm'], b['grad_norm']) for a, b in zip(ss, sf)]}", flush=True)
+        assert oplib.kernel_error() == 0
+        assert rel_s < 2e-3, rel_s
     dist.barrier()
     dist.destroy_process_group()
 

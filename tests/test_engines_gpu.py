@@ -462,3 +462,88 @@ def test_colocated_loop_runs_sixty_steps_on_gpu(tmp_path):
         assert eng._exc is None
     assert len(hist) == 60 and all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
     assert oplib.kernel_error() == 0
+
+
+def test_pausable_memory_keeps_addresses_and_contents():
+    """A pausable buffer gives its physical memory back (free memory grows by about its size), keeps its
+    address, and holds the same bytes after resume; a CUDA graph captured on it replays correctly
+    afterwards; a buffer that does not keep its contents comes back usable."""
+    from areal_b200.ops import vmm
+
+    if not vmm.available():
+        pytest.skip("driver without the virtual-memory API")
+    n = 64 << 20
+    buf = vmm.PausableBuffer(n, "cuda", keep_contents=True)
+    t = buf.tensor(torch.float32)
+    t.copy_(torch.arange(t.numel(), device="cuda", dtype=torch.float32))
+    out = torch.zeros(1, device="cuda")
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        out.copy_(t[:1024].sum().reshape(1))
+        s.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            out.copy_(t[:1024].sum().reshape(1))
+    g.replay()
+    torch.cuda.synchronize()
+    want = float(out)
+    ptr = t.data_ptr()
+    free0, _ = torch.cuda.mem_get_info()
+    buf.pause()
+    assert buf.paused
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 - free0 >= n * 0.9
+    buf.resume()
+    torch.cuda.synchronize()
+    assert not buf.paused and t.data_ptr() == ptr
+    assert float(t[12345]) == 12345.0 and float(t[-1]) == float(t.numel() - 1)
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert float(out) == want
+    scratch = vmm.PausableBuffer(8 << 20, "cuda", keep_contents=False)
+    scratch.pause()
+    scratch.resume()
+    scratch.tensor(torch.int32).fill_(7)
+    assert int(scratch.tensor(torch.int32)[100]) == 7
+    pool = vmm.MemoryPool()
+    a = pool.empty((1024, 1024), torch.bfloat16, tag="weights")
+    b = pool.empty((1 << 20,), torch.uint8, tag="kv_cache", keep_contents=False)
+    a.fill_(1.5)
+    assert pool.pause(["kv_cache"]) == b.numel() and pool.resume(["kv_cache"]) == b.numel()
+    assert pool.pause() == a.numel() * 2 + b.numel()
+    pool.resume()
+    torch.cuda.synchronize()
+    assert float(a[5, 5]) == 1.5
+
+
+def test_engine_offload_returns_the_kv_pool_and_keeps_its_graphs():
+    """Rollout engine with a pausable KV pool: offload() hands the pool's memory back to the device,
+    onload() takes it again; the decode graphs captured before keep working (same greedy outputs)."""
+    from areal_b200.ops import vmm
+
+    if not vmm.available():
+        pytest.skip("driver without the virtual-memory API")
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=21)
+    ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=256, pausable_kv_cache=True)
+    ic.num_pages = 4096                                     # 4096 x 16 tokens x 4 layers x 2 x 2 kv heads x 64 x 2 B = 134 MB
+    eng = NativeInferenceEngine(InferenceEngineConfig(), ic, model=model, eos_token_id=None).initialize(device="cuda", start_executor=False)
+    g = GenerationHyperparameters(max_new_tokens=16, max_tokens=200, greedy=True, ignore_eos=True)
+
+    async def run():
+        return await asyncio.gather(*[eng.agenerate(ModelRequest(rid=f"o{i}", input_ids=list(range(5 + i, 45 + i)), gconfig=g)) for i in range(4)])
+
+    first = asyncio.run(run())
+    n_graphs = len(eng._graphs)
+    assert n_graphs > 0
+    free0, _ = torch.cuda.mem_get_info()
+    eng.offload()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 - free0 > 100 << 20
+    eng.onload()
+    again = asyncio.run(run())
+    assert [r.output_tokens for r in again] == [r.output_tokens for r in first]
+    assert len(eng._graphs) == n_graphs                    # nothing was re-captured
+    assert oplib.kernel_error() == 0
+    eng.destroy()

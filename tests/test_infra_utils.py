@@ -240,3 +240,155 @@ def test_slurm_and_ray_launcher_plans(tmp_path, capsys):
 
     assert ray_launcher.launch("train.py", [], cfg, ray_module=_Ray()) == 0
     assert calls["cancel"] == 2 and sum(1 for n, _ in calls["run"] if n.startswith("trainer_")) == 12
+
+
+# --------------------------------------------------------------------------- name_resolve: etcd and Ray backends
+class _FakeEtcd:
+    """The five JSON-gateway routes of etcd v3 that the backend uses, with lease expiry."""
+
+    def __init__(self):
+        import base64
+        import http.server
+        import json
+        import threading
+        import time
+
+        kv, leases, lock = {}, {}, threading.Lock()
+        self.kv, self.leases, self.keepalives = kv, leases, []
+        outer = self
+
+        class H(http.server.BaseHTTPRequestHandler):
+            def log_message(self, *a):
+                pass
+
+            def do_POST(self):
+                body = json.loads(self.rfile.read(int(self.headers["Content-Length"])) or b"{}")
+                dec = lambda s: base64.b64decode(s).decode("latin-1")
+                enc = lambda s: base64.b64encode(s.encode("latin-1")).decode()
+                out = {}
+                with lock:
+                    now = time.monotonic()
+                    for k in [k for k, (_, lid) in kv.items() if lid and leases.get(lid, 0) < now]:
+                        del kv[k]                                   # lease ran out
+                    if self.path == "/v3/kv/put":
+                        kv[dec(body["key"])] = (dec(body["value"]), body.get("lease"))
+                    elif self.path == "/v3/kv/range":
+                        k, end = dec(body["key"]), dec(body["range_end"]) if "range_end" in body else None
+                        hits = [x for x in sorted(kv) if (x == k if end is None else k <= x < end)]
+                        out = {"kvs": [{"key": enc(x), "value": enc(kv[x][0])} for x in hits], "count": str(len(hits))}
+                    elif self.path == "/v3/kv/deleterange":
+                        k, end = dec(body["key"]), dec(body["range_end"]) if "range_end" in body else None
+                        hits = [x for x in list(kv) if (x == k if end is None else k <= x < end)]
+                        for x in hits:
+                            del kv[x]
+                        out = {"deleted": str(len(hits))}
+                    elif self.path == "/v3/lease/grant":
+                        lid = str(len(leases) + 1000)
+                        leases[lid] = now + int(body["TTL"])
+                        out = {"ID": lid, "TTL": str(body["TTL"])}
+                    elif self.path == "/v3/lease/keepalive":
+                        leases[body["ID"]] = now + 2
+                        outer.keepalives.append(body["ID"])
+                        out = {"result": {"ID": body["ID"]}}
+                data = json.dumps(out).encode()
+                self.send_response(200)
+                self.send_header("Content-Length", str(len(data)))
+                self.end_headers()
+                self.wfile.write(data)
+
+        self.server = http.server.ThreadingHTTPServer(("127.0.0.1", 0), H)
+        self.addr = f"127.0.0.1:{self.server.server_address[1]}"
+        threading.Thread(target=self.server.serve_forever, daemon=True).start()
+
+    def close(self):
+        self.server.shutdown()
+
+
+def test_etcd_name_resolve_backend_against_a_fake_gateway():
+    import time
+
+    from areal_b200.utils import name_resolve as nr
+
+    etcd = _FakeEtcd()
+    try:
+        repo = nr.Etcd3NameRecordRepository(etcd.addr)
+        repo.add("exp/t0/workers/0", "10.0.0.1:7000")
+        repo.add("exp/t0/workers/1", "10.0.0.2:7000")
+        repo.add("exp/t0/worker", "not-in-subtree")
+        with pytest.raises(nr.NameEntryExistsError):
+            repo.add("exp/t0/workers/0", "other")
+        repo.add("exp/t0/workers/0", "10.0.0.9:7000", replace=True)
+        assert repo.get("exp/t0/workers/0") == "10.0.0.9:7000"
+        assert repo.get_subtree("exp/t0/workers") == ["10.0.0.9:7000", "10.0.0.2:7000"]
+        assert repo.find_subtree("exp/t0/workers") == ["exp/t0/workers/0", "exp/t0/workers/1"]
+        assert repo.wait("exp/t0/workers/1", timeout=1) == "10.0.0.2:7000"
+        with pytest.raises(nr.NameEntryNotFoundError):
+            repo.get("exp/t0/nobody")
+        repo.delete("exp/t0/workers/1")
+        with pytest.raises(nr.NameEntryNotFoundError):
+            repo.delete("exp/t0/workers/1")
+        # an entry with a TTL stays alive only while its lease is renewed
+        repo.add("exp/t0/alive", "x", keepalive_ttl=1)
+        time.sleep(1.6)
+        assert repo.get("exp/t0/alive") == "x" and etcd.keepalives
+        repo.clear_subtree("exp/t0")
+        assert repo.find_subtree("exp/t0") == []
+        # the module-level selector
+        assert isinstance(nr.reconfigure(type="etcd3", addr=etcd.addr), nr.Etcd3NameRecordRepository)
+        nr.add("a/b", "1")
+        assert nr.get("a/b") == "1"
+        nr.reset()
+        with pytest.raises(nr.NameEntryNotFoundError):
+            nr.get("a/b")
+    finally:
+        nr.reconfigure(type="memory")
+        etcd.close()
+
+
+def test_ray_name_resolve_backend_against_a_fake_ray():
+    import types
+
+    from areal_b200.utils import name_resolve as nr
+
+    class _Ref:
+        def __init__(self, v):
+            self.v = v
+
+    class _Handle:
+        def __init__(self, obj):
+            self._obj = obj
+
+        def __getattr__(self, name):
+            fn = getattr(self._obj, name)
+            return types.SimpleNamespace(remote=lambda *a: _Ref(fn(*a)))
+
+    actors = {}
+
+    def remote(cls):
+        def options(name=None, **kw):
+            def make():
+                if name not in actors:
+                    actors[name] = _Handle(cls())
+                return actors[name]
+            return types.SimpleNamespace(remote=make)
+        return types.SimpleNamespace(options=options)
+
+    def get_actor(name):
+        if name not in actors:
+            raise ValueError("no such actor")
+        return actors[name]
+
+    fake = types.SimpleNamespace(is_initialized=lambda: True, init=lambda **kw: None, remote=remote, get_actor=get_actor,
+                                 get=lambda ref: ref.v)
+    a = nr.RayNameRecordRepository("kv", ray_module=fake)
+    b = nr.RayNameRecordRepository("kv", ray_module=fake)          # a second process finds the same actor
+    a.add("job/servers/0", "h0:1")
+    b.add("job/servers/1", "h1:1")
+    assert a.get_subtree("job/servers") == ["h0:1", "h1:1"] and b.get("job/servers/0") == "h0:1"
+    with pytest.raises(nr.NameEntryExistsError):
+        b.add("job/servers/0", "dup")
+    a.reset()
+    with pytest.raises(nr.NameEntryNotFoundError):
+        b.get("job/servers/0")
+    b.clear_subtree("job")
+    assert b.find_subtree("job") == []
