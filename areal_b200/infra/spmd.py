@@ -152,28 +152,50 @@ class MessageBus:
                                    wait_for_workers=False)
         self.rank = rank
 
+    # The store refuses values above a few MB (its server closes the connection), and a training batch
+    # of long sequences is larger: values travel in pieces, announced by a small header under the key.
+    CHUNK = 2 << 20
+
     def put(self, key: str, obj: Any) -> None:
         buf = io.BytesIO()
         pickle.dump(obj, buf, protocol=pickle.HIGHEST_PROTOCOL)
-        self.store.set(key, buf.getvalue())
+        data = buf.getvalue()
+        if len(data) <= self.CHUNK:
+            self.store.set(key, b"\x00" + data)
+            return
+        n = (len(data) + self.CHUNK - 1) // self.CHUNK
+        for i in range(n):
+            self.store.set(f"{key}#{i}", data[i * self.CHUNK:(i + 1) * self.CHUNK])
+        self.store.set(key, b"\x01" + str(n).encode())          # the header goes last: readers wait on it
+
+    def _read(self, key: str) -> Any:
+        head = self.store.get(key)
+        if head[:1] == b"\x00":
+            return pickle.loads(head[1:])
+        n = int(head[1:].decode())
+        return pickle.loads(b"".join(self.store.get(f"{key}#{i}") for i in range(n)))
 
     def get(self, key: str, timeout_s: Optional[float] = None) -> Any:
         if timeout_s is not None:
             self.store.wait([key], timedelta(seconds=timeout_s))
         else:
             self.store.wait([key])
-        return pickle.loads(self.store.get(key))
+        return self._read(key)
 
     def poll(self, key: str) -> Optional[Any]:
         try:
             if self.store.check([key]):
-                return pickle.loads(self.store.get(key))
+                return self._read(key)
         except Exception:
             return None
         return None
 
     def delete(self, key: str) -> None:
         try:
+            head = self.store.get(key) if self.store.check([key]) else b""
+            if head[:1] == b"\x01":
+                for i in range(int(head[1:].decode())):
+                    self.store.delete_key(f"{key}#{i}")
             self.store.delete_key(key)
         except Exception:
             pass

@@ -83,6 +83,9 @@ class PPOTrainer:
         self.stats_logger = StatsLogger(config.stats_logger, self.ft_spec, rank=getattr(self.actor, "rank", 0))
         if config.perf_tracer is not None:
             perf_tracer.configure(config.perf_tracer, rank=getattr(self.actor, "rank", 0), role="trainer")
+        from ..utils.memory_profiler import MemoryProfiler
+
+        self.memory_profiler = MemoryProfiler(getattr(config, "memory_profiler", None), rank=getattr(self.actor, "rank", 0))
         self.start_step = 0
         info = self.recover_handler.load(self._engines(), self.saver, self.evaluator, self.stats_logger,
                                          self.train_dataloader, self.rollout, self.weight_update_meta)
@@ -229,6 +232,8 @@ class PPOTrainer:
             t_step = time.perf_counter()
             epoch, step = divmod(global_step, steps_per_epoch)
             si = StepInfo(epoch=epoch, epoch_step=step, global_step=global_step, steps_per_epoch=steps_per_epoch)
+            perf_tracer.set_step(global_step)
+            self.memory_profiler.start(global_step)
             with stats_tracker.record_timing("rollout"), perf_tracer.trace_scope("train.rollout", category="scheduler"):
                 batch = self.actor.prepare_batch(self.train_dataloader, workflow=workflow, workflow_kwargs=workflow_kwargs,
                                                  should_accept_fn=should_accept_fn, dynamic_bs=cfg.dynamic_bs)
@@ -253,8 +258,8 @@ class PPOTrainer:
             with stats_tracker.record_timing("compute_advantage"), perf_tracer.trace_scope("train.compute_advantage"):
                 self.actor.compute_advantages(batch, group_sizes=group_sizes)
             self.saver.maybe_wait_for_staging()
-            with stats_tracker.record_timing("train_step"), perf_tracer.trace_scope("train.ppo_update"):
-                self.actor.ppo_update(batch)
+            with stats_tracker.record_timing("train_step"), perf_tracer.profile_scope("train.ppo_update"):
+                self.actor.ppo_update(batch)      # on the steps listed in perf_tracer.profile_steps every kernel of the update is traced
                 self.actor.step_lr_scheduler()
             if self.critic is not None:
                 with stats_tracker.record_timing("critic_train_step"), perf_tracer.trace_scope("train.critic_update"):
@@ -278,6 +283,9 @@ class PPOTrainer:
                 with stats_tracker.record_timing("eval"):
                     self.evaluator.evaluate(lambda: self._evaluate(eval_workflow, eval_workflow_kwargs), epoch, step, global_step)
             self.actor.clear_batches(batch)
+            if self.memory_profiler.active_step is not None:
+                self.memory_profiler.stop(os.path.join(cfg.cluster.fileroot or "/tmp/areal", "logs", cfg.experiment_name or "exp",
+                                                       cfg.trial_name or "trial", "memory_snapshots"))
             stats = self._export_stats()
             stats["timeperf/step"] = time.perf_counter() - t_step
             self.step_times.append(stats["timeperf/step"])

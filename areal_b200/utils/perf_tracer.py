@@ -37,6 +37,10 @@ class PerfTracer:
         self.session_tracer = SessionTracer(config, rank) if self.enabled and getattr(config, "session_tracer", None) and \
             config.session_tracer.enabled else None
         self._save_interval = max(1, getattr(config, "save_interval", 1)) if config is not None else 1
+        self.profile_steps = self._normalize_profile_steps(getattr(config, "profile_steps", None) if config is not None else None)
+        self.current_step: Optional[int] = None
+        self._virtual_tids: dict = {}
+        self._profiling = False
 
     def _out_dir(self) -> str:
         c = self.config
@@ -93,6 +97,103 @@ class PerfTracer:
             yield
         finally:
             self.add_complete(name, category, start, self._now_us() - start, args)
+
+    # ------------------------------------------------------------------ kernel-level traces
+    @staticmethod
+    def _normalize_profile_steps(steps) -> frozenset:
+        out = set()
+        for raw in steps or ():
+            try:
+                out.add(int(raw))
+            except (TypeError, ValueError):
+                continue
+        return frozenset(out)
+
+    def set_step(self, step: Optional[int]) -> None:
+        """The trainer's current global step: scopes opened with ``profile=True`` run under the
+        PyTorch profiler when this step is listed in ``profile_steps``."""
+        self.current_step = step
+
+    def should_profile(self, requested: bool = True) -> bool:
+        return bool(self.enabled and requested and self.profile_steps and self.current_step is not None
+                    and self.current_step in self.profile_steps and not self._profiling)
+
+    @contextmanager
+    def profile_scope(self, name: str, category: str = "compute"):
+        """``trace_scope`` that additionally records every CPU op and GPU kernel inside it with
+        ``torch.profiler`` on the steps listed in ``profile_steps`` and merges those events into
+        this rank's trace (reference: areal/utils/perf_tracer.py:1454 merge_profiler_trace)."""
+        if not self.should_profile():
+            with self.trace_scope(name, category):
+                yield
+            return
+        import tempfile
+
+        import torch
+        from torch.profiler import ProfilerActivity, profile
+
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+        self._profiling = True
+        base_us = self._now_us()
+        try:
+            with profile(activities=acts) as prof, self.trace_scope(name, category, args={"profiled": True}):
+                yield
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            with tempfile.NamedTemporaryFile(suffix=".json", delete=False) as f:
+                path = f.name
+            try:
+                prof.export_chrome_trace(path)
+                with open(path) as fh:
+                    self.merge_profiler_trace(json.load(fh), base_us)
+            finally:
+                try:
+                    os.unlink(path)
+                except OSError:
+                    pass
+        finally:
+            self._profiling = False
+
+    def merge_profiler_trace(self, profiler_trace: dict, base_us: float) -> int:
+        """Merges a PyTorch-profiler Chrome trace (the loaded JSON) into this rank's event stream:
+        timestamps are shifted so the earliest profiler event lands at ``base_us`` on this tracer's
+        clock, every event is attributed to this rank's process id, and each (profiler pid, tid)
+        pair (CPU threads, ``GPU d stream s`` lanes) gets its own virtual, negative thread id with a
+        ``thread_name`` record, so kernels show up as extra lanes under the rank's own scopes.
+        Returns the number of events merged."""
+        if not self.enabled:
+            return 0
+        events = profiler_trace.get("traceEvents") or []
+        stamps = [e["ts"] for e in events if "ts" in e and e.get("ph") != "M"]
+        if not stamps:
+            return 0
+        shift = base_us - min(stamps)
+        names = {}
+        for e in events:
+            if e.get("ph") == "M" and e.get("name") == "thread_name":
+                names[(str(e.get("pid")), str(e.get("tid")))] = (e.get("args") or {}).get("name")
+        ignored_meta = {"process_name", "process_sort_index", "process_labels", "thread_name", "thread_sort_index"}
+        ignored_pids = {"Spans", "Traces", ""}
+        merged = []
+        for e in events:
+            if e.get("ph") == "M" and e.get("name") in ignored_meta:
+                continue
+            if str(e.get("pid")) in ignored_pids or "ts" not in e:
+                continue
+            key = (str(e.get("pid")), str(e.get("tid")))
+            vt = self._virtual_tids.get(key)
+            if vt is None:
+                vt = self._virtual_tids[key] = -(len(self._virtual_tids) + 1)
+                label = names.get(key) or (f"GPU {e.get('pid')} stream {e.get('tid')}" if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset")
+                                           else f"profiler thread {e.get('tid')}")
+                merged.append(dict(name="thread_name", ph="M", pid=self.rank, tid=vt, args={"name": label}))
+            ev = dict(e)
+            ev["ts"] = e["ts"] + shift
+            ev["pid"], ev["tid"] = self.rank, vt
+            merged.append(ev)
+        with self._lock:
+            self._events.extend(merged)
+        return sum(1 for m in merged if m.get("ph") != "M")
 
     def _flush_device_events(self):
         if not self._device_events:
@@ -183,6 +284,14 @@ def atrace_scope(name: str, category: str = "compute", args: Optional[dict] = No
 
 def instant(name: str, category: str = "misc", args: Optional[dict] = None):
     _GLOBAL.instant(name, category, args)
+
+
+def set_step(step: Optional[int]) -> None:
+    get_tracer().set_step(step)
+
+
+def profile_scope(name: str, category: str = "compute"):
+    return get_tracer().profile_scope(name, category)
 
 
 def save(step: Optional[int] = None, force: bool = False):

@@ -1,8 +1,10 @@
 """name_resolve backends, ports, seeding, distributed lock, timing controls."""
+import os
 import threading
 import time
 
 import pytest
+import torch
 
 from areal_b200.utils import name_resolve, network, seeding
 from areal_b200.utils.lock import DistributedLock
@@ -392,3 +394,54 @@ def test_ray_name_resolve_backend_against_a_fake_ray():
         b.get("job/servers/0")
     b.clear_subtree("job")
     assert b.find_subtree("job") == []
+
+
+def test_perf_tracer_merges_a_profiler_trace_and_profiles_listed_steps(tmp_path):
+    """Kernel-level events of a PyTorch-profiler trace land in the rank's trace: shifted onto the
+    tracer's clock, attributed to the rank, on virtual (negative) thread ids with names; a
+    ``profile_scope`` runs the profiler only on the listed steps."""
+    import json
+
+    from areal_b200.api.cli_args import PerfTracerConfig
+    from areal_b200.utils.perf_tracer import PerfTracer
+
+    cfg = PerfTracerConfig(experiment_name="e", trial_name="t", fileroot=str(tmp_path), enabled=True, profile_steps=[2])
+    tr = PerfTracer(cfg, rank=3, role="trainer")
+    fake = {"traceEvents": [
+        {"ph": "M", "name": "thread_name", "pid": 0, "tid": 7, "args": {"name": "stream 7"}},
+        {"ph": "M", "name": "process_name", "pid": 0, "tid": 0, "args": {"name": "python"}},
+        {"ph": "X", "name": "ab2::gemm_bf16_kernel", "cat": "kernel", "pid": 0, "tid": 7, "ts": 5_000_100.0, "dur": 40.0},
+        {"ph": "X", "name": "aten::mm", "cat": "cpu_op", "pid": 1234, "tid": 99, "ts": 5_000_000.0, "dur": 60.0},
+        {"ph": "X", "name": "internal", "cat": "x", "pid": "Spans", "tid": 1, "ts": 5_000_000.0, "dur": 1.0}]}
+    n = tr.merge_profiler_trace(fake, base_us=1000.0)
+    assert n == 2
+    evs = {e["name"]: e for e in tr._events if e.get("ph") == "X"}
+    assert evs["aten::mm"]["ts"] == 1000.0 and evs["ab2::gemm_bf16_kernel"]["ts"] == 1100.0
+    assert all(e["pid"] == 3 and e["tid"] < 0 for e in evs.values())
+    names = {e["tid"]: e["args"]["name"] for e in tr._events if e.get("ph") == "M"}
+    assert names[evs["ab2::gemm_bf16_kernel"]["tid"]] == "stream 7"
+    # profile_scope: a plain scope on step 1, profiler events merged on step 2
+    tr.set_step(1)
+    with tr.profile_scope("update"):
+        torch.ones(8).sum()
+    before = len(tr._events)
+    tr.set_step(2)
+    with tr.profile_scope("update"):
+        (torch.ones(64, 64) @ torch.ones(64, 64)).sum()
+    added = tr._events[before:]
+    assert any(e.get("args", {}).get("profiled") for e in added if e.get("name") == "update")
+    assert any("mm" in str(e.get("name")) or "matmul" in str(e.get("name")) for e in added)
+    tr.save(force=True)
+    lines = [json.loads(l) for l in open(os.path.join(tr._out_dir(), "traces-r3.jsonl"))]
+    assert len(lines) >= len(added)
+
+
+def test_memory_profiler_is_inert_without_cuda_and_respects_its_step_list(tmp_path):
+    from areal_b200.api.cli_args import MemoryProfilerConfig
+    from areal_b200.utils.memory_profiler import MemoryProfiler
+
+    mp = MemoryProfiler(MemoryProfilerConfig(enabled=True, profile_steps=[3], max_entries=1000), rank=0)
+    assert mp.wants(3) and not mp.wants(2)
+    if not torch.cuda.is_available():
+        assert mp.start(3) is False and mp.stop(str(tmp_path)) is None
+    assert MemoryProfiler(MemoryProfilerConfig(enabled=False, profile_steps=[3])).wants(3) is False
