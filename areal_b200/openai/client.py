@@ -102,7 +102,7 @@ class _Completions:
         eos = getattr(c.tokenizer, "eos_token_id", None)
         text = c.tokenizer.decode(out_ids[:-1] if out_ids and out_ids[-1] == eos else out_ids)
         reasoning, visible = split_reasoning(text)
-        content, calls = parse_tool_calls(visible, tools) if tools else (visible, [])
+        content, calls = parse_tool_calls(visible, tools, c.tool_call_parser) if tools else (visible, [])
         finish = "tool_calls" if calls else ("length" if resp.stop_reason == "length" else "stop")
         msg = ChatMessage(role="assistant", content=content, tool_calls=calls or None, reasoning_content=reasoning)
         comp = ChatCompletion(id=cid, model=model, choices=[Choice(0, msg, finish)],
@@ -154,7 +154,7 @@ class _Responses:
 
 class ArealOpenAI:
     def __init__(self, engine, tokenizer, gconfig: Optional[GenerationHyperparameters] = None, chat_template_type: str = "hf",
-                 enable_thinking: Optional[bool] = None, max_total_tokens: Optional[int] = None, **_):
+                 enable_thinking: Optional[bool] = None, max_total_tokens: Optional[int] = None, tool_call_parser: str = "auto", **_):
         if chat_template_type not in ("hf", "concat"):
             raise ValueError("chat_template_type must be 'hf' or 'concat'")
         self.engine, self.tokenizer = engine, tokenizer
@@ -162,6 +162,7 @@ class ArealOpenAI:
         self.chat_template_type = chat_template_type
         self.enable_thinking = enable_thinking
         self.max_total_tokens = max_total_tokens
+        self.tool_call_parser = tool_call_parser
         self._cache = InteractionCache()
         self.chat = _Chat(self)
         self.responses = _Responses(self)

@@ -73,6 +73,50 @@ def openai_to_anthropic(comp) -> dict:
             "usage": {"input_tokens": comp.usage.prompt_tokens, "output_tokens": comp.usage.completion_tokens}}
 
 
+def chat_completion_chunks(comp, piece_chars: int = 64):
+    """Server-sent-event payloads of a finished completion in the ``chat.completion.chunk`` wire
+    format: a role delta, content (and reasoning) deltas of at most ``piece_chars`` characters,
+    one delta per tool call, then the finish reason with the usage. The model call itself is not
+    incremental (the trajectory is recorded whole), so the stream starts once generation ended."""
+    base = {"id": comp.id, "object": "chat.completion.chunk", "created": comp.created, "model": comp.model}
+    m = comp.choices[0].message
+
+    def ev(delta: dict, finish=None, **extra) -> dict:
+        return {**base, "choices": [{"index": 0, "delta": delta, "finish_reason": finish}], **extra}
+
+    yield ev({"role": "assistant", "content": ""})
+    for field, text in (("reasoning_content", m.reasoning_content), ("content", m.content)):
+        for i in range(0, len(text or ""), piece_chars):
+            yield ev({field: text[i:i + piece_chars]})
+    for i, t in enumerate(m.tool_calls or []):
+        yield ev({"tool_calls": [{"index": i, "id": t.id, "type": "function",
+                                  "function": {"name": t.function.name, "arguments": t.function.arguments}}]})
+    u = comp.usage
+    yield ev({}, comp.choices[0].finish_reason,
+             usage={"prompt_tokens": u.prompt_tokens, "completion_tokens": u.completion_tokens, "total_tokens": u.total_tokens})
+
+
+def anthropic_message_events(msg: dict, piece_chars: int = 64):
+    """(event name, payload) pairs of the ``/v1/messages`` streaming protocol for a finished message."""
+    head = {k: v for k, v in msg.items() if k not in ("content", "stop_reason")}
+    yield "message_start", {"type": "message_start", "message": {**head, "content": [], "stop_reason": None}}
+    for i, blk in enumerate(msg["content"]):
+        if blk["type"] == "text":
+            yield "content_block_start", {"type": "content_block_start", "index": i, "content_block": {"type": "text", "text": ""}}
+            for j in range(0, len(blk["text"]), piece_chars):
+                yield "content_block_delta", {"type": "content_block_delta", "index": i,
+                                              "delta": {"type": "text_delta", "text": blk["text"][j:j + piece_chars]}}
+        else:
+            yield "content_block_start", {"type": "content_block_start", "index": i,
+                                          "content_block": {"type": "tool_use", "id": blk["id"], "name": blk["name"], "input": {}}}
+            yield "content_block_delta", {"type": "content_block_delta", "index": i,
+                                          "delta": {"type": "input_json_delta", "partial_json": json.dumps(blk["input"])}}
+        yield "content_block_stop", {"type": "content_block_stop", "index": i}
+    yield "message_delta", {"type": "message_delta", "delta": {"stop_reason": msg["stop_reason"]},
+                            "usage": {"output_tokens": msg["usage"]["output_tokens"]}}
+    yield "message_stop", {"type": "message_stop"}
+
+
 class _Session:
     def __init__(self, client: ArealOpenAI):
         self.client = client
@@ -154,6 +198,24 @@ class OpenAIProxyServer:
                 self.end_headers()
                 self.wfile.write(body)
 
+            def _stream(self, events):
+                """Server-sent events over chunked transfer encoding; ``events`` yields payload dicts or
+                (event name, payload) pairs; a bare string is sent as is (the ``[DONE]`` sentinel)."""
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Transfer-Encoding", "chunked")
+                self.end_headers()
+                for e in events:
+                    if isinstance(e, tuple):
+                        data = f"event: {e[0]}\ndata: {json.dumps(e[1])}\n\n"
+                    else:
+                        data = f"data: {e if isinstance(e, str) else json.dumps(e)}\n\n"
+                    raw = data.encode()
+                    self.wfile.write(f"{len(raw):x}\r\n".encode() + raw + b"\r\n")
+                    self.wfile.flush()
+                self.wfile.write(b"0\r\n\r\n")
+
             def do_GET(self):
                 if self.path in ("/health", "/v1/health"):
                     return self._reply(200, {"status": "ok", "sessions": len(proxy._sessions)})
@@ -171,11 +233,25 @@ class OpenAIProxyServer:
                         kw = {k: body[k] for k in ("messages", "model", "temperature", "top_p", "max_tokens", "max_completion_tokens",
                                                     "stop", "tools", "tool_choice", "frequency_penalty", "extra_body", "metadata") if k in body}
                         comp = proxy._run(s.client.chat.completions.create(**kw))
+                        if body.get("stream"):
+                            return self._stream(list(chat_completion_chunks(comp)) + ["[DONE]"])
                         return self._reply(200, comp.to_dict())
+                    if path.endswith("/responses"):
+                        s = proxy._session(self._key())
+                        kw = {k: body[k] for k in ("input", "instructions", "model", "max_output_tokens", "temperature", "top_p",
+                                                    "tools") if k in body}
+                        r = proxy._run(s.client.responses.create(**kw))
+                        u = r.usage
+                        return self._reply(200, {"id": r.id, "object": "response", "created_at": r.created_at, "model": r.model,
+                                                 "status": "completed", "output": r.output, "output_text": r.output_text,
+                                                 "usage": {"input_tokens": u.prompt_tokens, "output_tokens": u.completion_tokens,
+                                                           "total_tokens": u.total_tokens}})
                     if path.endswith("/v1/messages") or path == "/messages":
                         s = proxy._session(self._key())
                         kw = {k: v for k, v in anthropic_to_openai(body).items() if v is not None}
                         comp = proxy._run(s.client.chat.completions.create(**kw))
+                        if body.get("stream"):
+                            return self._stream(anthropic_message_events(openai_to_anthropic(comp)))
                         return self._reply(200, openai_to_anthropic(comp))
                     if path == "/rl/start_session":
                         if proxy.admin_key and self._key() != proxy.admin_key:

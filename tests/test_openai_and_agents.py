@@ -158,6 +158,73 @@ def test_http_proxy_sessions_rewards_export_and_anthropic_route():
     assert o["messages"][0] == {"role": "tool", "tool_call_id": "t1", "content": "42"} and o["tools"][0]["function"]["name"] == "calc"
 
 
+def _sse(url, body, key):
+    req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json",
+                                                                                "Authorization": f"Bearer {key}"})
+    with urllib.request.urlopen(req, timeout=20) as r:
+        assert r.headers["Content-Type"] == "text/event-stream"
+        return r.read().decode()
+
+
+def test_http_proxy_streams_chat_and_anthropic_events_and_serves_responses():
+    call = '<tool_call>{"name": "calc", "arguments": {"x": 1}}</tool_call>'
+    eng = ScriptedEngine(["<think>hm</think>" + "a" * 150, "let me see " + call, "plain", "resp"])
+    px = OpenAIProxyServer(eng, ByteTok(), GenerationHyperparameters(max_new_tokens=512)).start()
+    tools = [{"type": "function", "function": {"name": "calc", "parameters": {"type": "object"}}}]
+    try:
+        root = px.base_url[:-3]
+        key = px.start_session()
+        raw = _sse(f"{px.base_url}/chat/completions", {"messages": [{"role": "user", "content": "q"}], "stream": True}, key)
+        evs = [l[6:] for l in raw.split("\n") if l.startswith("data: ")]
+        assert evs[-1] == "[DONE]"
+        chunks = [json.loads(e) for e in evs[:-1]]
+        assert all(c["object"] == "chat.completion.chunk" and c["id"] == chunks[0]["id"] for c in chunks)
+        assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+        assert "".join(c["choices"][0]["delta"].get("content", "") for c in chunks) == "a" * 150
+        assert "".join(c["choices"][0]["delta"].get("reasoning_content", "") for c in chunks) == "hm"
+        assert sum("content" in c["choices"][0]["delta"] and c["choices"][0]["delta"]["content"] != "" for c in chunks) == 3
+        assert chunks[-1]["choices"][0]["finish_reason"] == "stop" and chunks[-1]["usage"]["completion_tokens"] > 0
+        raw = _sse(f"{px.base_url}/chat/completions", {"messages": [{"role": "user", "content": "q"}], "stream": True, "tools": tools}, key)
+        chunks = [json.loads(l[6:]) for l in raw.split("\n") if l.startswith("data: {")]
+        tc = [c["choices"][0]["delta"]["tool_calls"][0] for c in chunks if "tool_calls" in c["choices"][0]["delta"]]
+        assert len(tc) == 1 and tc[0]["function"]["name"] == "calc" and json.loads(tc[0]["function"]["arguments"]) == {"x": 1}
+        assert chunks[-1]["choices"][0]["finish_reason"] == "tool_calls"
+        raw = _sse(f"{root}/v1/messages", {"max_tokens": 8, "stream": True, "messages": [{"role": "user", "content": "hi"}]}, key)
+        names = [l[7:] for l in raw.split("\n") if l.startswith("event: ")]
+        assert names[0] == "message_start" and names[-2:] == ["message_delta", "message_stop"] and "content_block_delta" in names
+        text = "".join(json.loads(l[6:])["delta"]["text"] for l in raw.split("\n")
+                       if l.startswith("data: ") and json.loads(l[6:]).get("type") == "content_block_delta")
+        assert text == "plain"
+        code, r = _post(f"{px.base_url}/responses", {"input": "hello", "instructions": "be brief", "max_output_tokens": 16}, key)
+        assert code == 200 and r["object"] == "response" and r["output_text"] == "resp" and r["output"][0]["type"] == "message"
+        # the four calls were all recorded for training
+        assert len(px.pop_session(key).client.export_interactions("individual")) == 4
+    finally:
+        px.stop()
+
+
+def test_tool_call_parsers_by_format():
+    from areal_b200.openai.tool_call_parser import parse_tool_calls
+
+    tools = [{"type": "function", "function": {"name": "run", "parameters": {"type": "object", "properties": {
+        "code": {"type": "string"}, "n": {"type": "integer"}, "ok": {"type": "boolean"}, "xs": {"type": "array"}, "r": {"type": "number"}}}}}]
+    coder = ("I will run it\n<tool_call>\n<function=run>\n<parameter=code>\nprint(1)\n</parameter>\n<parameter=n>3</parameter>\n"
+             "<parameter=ok>True</parameter><parameter=xs>[1, 2]</parameter><parameter=r>0.5</parameter>\n</function>\n</tool_call>")
+    rest, calls = parse_tool_calls(coder, tools, "qwen3_coder")
+    assert rest == "I will run it" and len(calls) == 1 and calls[0].function.name == "run"
+    assert json.loads(calls[0].function.arguments) == {"code": "print(1)", "n": 3, "ok": True, "xs": [1, 2], "r": 0.5}
+    # unknown tool: left in the text; auto picks the format that matches
+    assert parse_tool_calls(coder.replace("function=run", "function=zzz"), tools, "qwen3_coder") == (coder.replace("function=run", "function=zzz"), [])
+    assert parse_tool_calls(coder, tools, "auto")[1][0].function.name == "run"
+    assert parse_tool_calls('<tool_call>{"name": "run", "arguments": {"n": 1}}</tool_call>', tools, "auto")[1][0].function.name == "run"
+    rest, calls = parse_tool_calls('```json\n[{"name": "run", "parameters": {"n": 2}}, {"name": "run", "arguments": {"n": 3}}]\n```', tools, "json")
+    assert rest == "" and [json.loads(c.function.arguments)["n"] for c in calls] == [2, 3]
+    assert parse_tool_calls('{"name": "other", "arguments": {}}', tools, "json")[1] == []
+    assert parse_tool_calls("no call here", tools, "auto") == ("no call here", [])
+    with pytest.raises(ValueError):
+        parse_tool_calls("x", tools, "nope")
+
+
 class EchoAgent:
     tokenizer = ByteTok()
     gconfig = GenerationHyperparameters(max_new_tokens=8)
