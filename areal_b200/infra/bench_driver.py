@@ -338,6 +338,7 @@ def _timed_loop(args, trainer, wf, clock_sampler_cls, world, rank, model_cfg, la
             "inflight_weight_update": "running requests keep their KV cache" if args.retain_kv else "running requests are re-prefilled",
             "prefix_sharing": bool(args.prefix_sharing),
             "decode_switches": {k_: os.environ.get(k_, "0") for k_ in ("AB2_PDL", "AB2_DECODE_SPLITK")},
+            "nccl_nvls": os.environ.get("NCCL_NVLS_ENABLE", "default"),
             "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
             "params_b": model_cfg.num_params() / 1e9, "weight_sync_ms": push_ms, "weight_sync_device_ms": push_dev_ms,
             "weight_sync_gbs_per_trainer_gpu": round(push_gbs, 1) if push_gbs else None,

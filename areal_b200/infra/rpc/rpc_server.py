@@ -7,11 +7,20 @@ Routes (JSON bodies in the envelope of :mod:`serialization`):
     GET  /health                      liveness + hosted engines
     POST /configure  {env, seed}      process-level settings
     POST /set_env    {env}            environment variables (RANK, MASTER_ADDR, ...)
-    POST /alloc_ports {count}         free ports on this host
+    POST /alloc_ports {count}         free ports on this host (never handed out twice by one server)
+    POST /fork {role, worker_index, raw_cmd, env}   start a sibling process on this node (one per role/index)
+    POST /kill_forked_worker {role, worker_index}   end it (its whole process group)
+    GET  /forked                      the children this server started, with their state
+    POST /data/batch {shard_ids}      several shards in one reply
     POST /create_engine {name, cls, args, kwargs}
     POST /call {name, method, args, kwargs, return_rtensor, direct}   run ``engine.method`` in the engine thread
     PUT  /data/<shard_id>  (torch.save bytes)   GET /data/<shard_id>   POST /data/clear {shard_ids}
-    POST /kill                        exit the process
+    POST /kill                        exit the process (children started by /fork are ended first)
+
+The fork / kill / port routes are the node-guard role of the reference
+(``areal/infra/rpc/guard/app.py:193-416``): a controller that colocates a second role with a
+worker (a reference model beside the actor, a proxy beside a rollout server) asks the worker's
+server to start it, so that it lands on the same node and shares its GPU visibility.
 
 All engine calls are executed by ONE engine thread in arrival order, which serialises
 collectives exactly like the reference's guard (``areal/infra/rpc/guard/engine_blueprint.py:115-181``).
@@ -25,7 +34,10 @@ import argparse
 import json
 import os
 import queue
+import signal
+import subprocess
 import sys
+import tempfile
 import threading
 import traceback
 from concurrent.futures import Future
@@ -103,7 +115,80 @@ class EngineHost:
         return do() if direct else self.run(do)
 
 
-def make_handler(host: EngineHost, stop_event: threading.Event):
+class ForkedWorkers:
+    """Children started on behalf of a controller, keyed by (role, index)."""
+
+    def __init__(self, log_dir: str | None = None):
+        self._procs: dict[tuple[str, int], subprocess.Popen] = {}
+        self._lock = threading.Lock()
+        self.log_dir = log_dir or os.path.join(tempfile.gettempdir(), f"areal_forked_{os.getpid()}")
+        self.ports: set[int] = set()
+
+    def alloc_ports(self, count: int) -> list[int]:
+        if not isinstance(count, int) or count <= 0:
+            raise ValueError("'count' must be a positive integer")
+        with self._lock:
+            got = find_free_ports(count, exclude=self.ports)
+            self.ports.update(got)
+        return got
+
+    def fork(self, role: str, index: int, raw_cmd: list, env: dict | None = None) -> int:
+        if not role or not isinstance(raw_cmd, list) or not raw_cmd:
+            raise ValueError("'role' and a non-empty 'raw_cmd' list are required")
+        key = (str(role), int(index))
+        with self._lock:
+            old = self._procs.get(key)
+            if old is not None and old.poll() is None:
+                raise ValueError(f"worker {role}/{index} is already running (pid {old.pid})")
+            os.makedirs(self.log_dir, exist_ok=True)
+            log = open(os.path.join(self.log_dir, f"{role}_{index}.log"), "ab")
+            child_env = dict(os.environ)
+            child_env.update({str(k): str(v) for k, v in (env or {}).items()})
+            # its own session: ending the child ends what the child started, and nothing else
+            p = subprocess.Popen([str(c) for c in raw_cmd], env=child_env, stdout=log, stderr=subprocess.STDOUT,
+                                 stdin=subprocess.DEVNULL, start_new_session=True)
+            log.close()
+            self._procs[key] = p
+        logger.info("forked %s/%d as pid %d: %s", role, index, p.pid, " ".join(map(str, raw_cmd)))
+        return p.pid
+
+    @staticmethod
+    def _end(p: subprocess.Popen, grace_s: float = 5.0) -> None:
+        if p.poll() is not None:
+            return
+        for sig in (signal.SIGTERM, signal.SIGKILL):
+            try:
+                os.killpg(p.pid, sig)         # the child leads its own process group (start_new_session)
+            except ProcessLookupError:
+                return
+            try:
+                p.wait(timeout=grace_s)
+                return
+            except subprocess.TimeoutExpired:
+                continue
+
+    def kill(self, role: str, index: int) -> bool:
+        with self._lock:
+            p = self._procs.pop((str(role), int(index)), None)
+        if p is None:
+            return False
+        self._end(p)
+        return True
+
+    def kill_all(self) -> None:
+        with self._lock:
+            procs, self._procs = list(self._procs.values()), {}
+        for p in procs:
+            self._end(p)
+
+    def status(self) -> list[dict]:
+        with self._lock:
+            return [{"role": r, "worker_index": i, "pid": p.pid, "returncode": p.poll()} for (r, i), p in sorted(self._procs.items())]
+
+
+def make_handler(host: EngineHost, stop_event: threading.Event, forked: "ForkedWorkers | None" = None):
+    forked = forked or ForkedWorkers()
+
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
 
@@ -127,6 +212,8 @@ def make_handler(host: EngineHost, stop_event: threading.Event):
         def do_GET(self):
             if self.path == "/health":
                 return self._json(200, {"status": "ok", "engines": sorted(host.engines), "pid": os.getpid(), "shards": len(RT.LOCAL_STORE)})
+            if self.path == "/forked":
+                return self._json(200, {"workers": forked.status()})
             if self.path.startswith("/data/"):
                 sid = self.path[len("/data/"):]
                 try:
@@ -155,7 +242,32 @@ def make_handler(host: EngineHost, stop_event: threading.Event):
                         set_random_seed(int(req["seed"]), req.get("seed_key", ""))
                     return self._json(200, {"ok": True})
                 if self.path == "/alloc_ports":
-                    return self._json(200, {"ports": find_free_ports(int(req.get("count", 1))), "host": gethostip()})
+                    try:
+                        return self._json(200, {"status": "success", "ports": forked.alloc_ports(req.get("count", 1)), "host": gethostip()})
+                    except ValueError as e:
+                        return self._json(400, {"error": str(e)})
+                if self.path == "/fork":
+                    try:
+                        pid = forked.fork(req.get("role"), req.get("worker_index", 0), req.get("raw_cmd"), req.get("env"))
+                    except ValueError as e:
+                        return self._json(400, {"error": str(e)})
+                    return self._json(200, {"status": "success", "host": gethostip(), "pid": pid})
+                if self.path == "/kill_forked_worker":
+                    if req.get("role") is None:
+                        return self._json(400, {"error": "Missing 'role' field in request"})
+                    if not forked.kill(req["role"], req.get("worker_index", 0)):
+                        return self._json(404, {"error": f"no forked worker {req['role']}/{req.get('worker_index', 0)}"})
+                    return self._json(200, {"status": "success"})
+                if self.path == "/data/batch":
+                    out, missing = {}, []
+                    for sid in req.get("shard_ids", []):
+                        try:
+                            out[sid] = RT.LOCAL_STORE.get(sid)
+                        except KeyError:
+                            missing.append(sid)
+                    if missing:
+                        return self._json(404, {"error": "shards not found", "missing": missing})
+                    return self._send(200, RT.dumps_batch(out), "application/octet-stream")
                 if self.path == "/create_engine":
                     host.create_engine(req["name"], req["cls"], req.get("args", []), req.get("kwargs", {}))
                     return self._json(200, {"ok": True})
@@ -170,6 +282,7 @@ def make_handler(host: EngineHost, stop_event: threading.Event):
                         return self._json(200, {"deleted": "all"})
                     return self._json(200, {"deleted": RT.LOCAL_STORE.delete(ids)})
                 if self.path == "/kill":
+                    forked.kill_all()
                     self._json(200, {"ok": True})
                     stop_event.set()
                     return

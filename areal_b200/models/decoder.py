@@ -182,21 +182,29 @@ class MoEMLP(nn.Module):
             gidx = gscore.topk(keep, dim=-1).indices
             gmask = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, gidx, True)
             choice = grouped.masked_fill(~gmask.unsqueeze(-1), float("-inf")).view(-1, E)
-        tope = torch.topk(choice, k, dim=-1).indices
+        # the choice, its stable sort by expert, the group sizes and the GEMM tile list come from one
+        # device-side routing pass (no host read); the weights stay a differentiable gather of ``probs``
+        if cfg.num_expert_groups > 0:
+            tope = torch.topk(choice, k, dim=-1).indices
+            routing = OF.moe_route(logits.detach(), k, tope=tope)
+        else:
+            routing = OF.moe_route(logits.detach(), k, bias=self.expert_bias, sigmoid=cfg.router_score_func == "sigmoid",
+                                   norm=cfg.norm_topk_prob, scale=cfg.router_scale, want_probs=False)
+            tope = routing.tope.long()
         topw = probs.gather(1, tope)
         if cfg.norm_topk_prob:
             topw = topw / topw.sum(-1, keepdim=True).clamp(min=1e-20)
         if cfg.router_scale != 1.0:
             topw = topw * cfg.router_scale
         if self.training and (cfg.router_aux_loss_coef > 0 or self.expert_bias is not None):
-            load = torch.zeros(E, device=x.device).scatter_add_(0, tope.reshape(-1), torch.ones(tope.numel(), device=x.device))
+            load = routing.counts.float()
             if self.expert_bias is not None:
                 self.tokens_per_expert.add_(load)
             if cfg.router_aux_loss_coef > 0:
                 mean_p = probs.mean(0) if cfg.router_score_func != "sigmoid" else (probs / probs.sum(-1, keepdim=True).clamp(min=1e-20)).mean(0)
                 self.last_aux_loss = E * (load / tope.numel() * mean_p).sum() * cfg.router_aux_loss_coef
         self.last_routed_experts = tope
-        return topw, tope
+        return topw, tope, routing
 
     @torch.no_grad()
     def update_expert_bias(self, group=None) -> None:
@@ -212,8 +220,14 @@ class MoEMLP(nn.Module):
         self.expert_bias.sub_(self.expert_bias.mean())
         load.zero_()
 
-    def experts_forward(self, xs: torch.Tensor, counts: list[int], first_expert: int = 0) -> torch.Tensor:
-        """xs: tokens sorted by (local) expert; counts[e] tokens for expert first_expert+e."""
+    def experts_forward(self, xs: torch.Tensor, counts, first_expert: int = 0) -> torch.Tensor:
+        """xs: tokens sorted by (local) expert; counts[e] tokens for expert first_expert+e, or the
+        device-made routing of all experts (then nothing is read back to the host)."""
+        if isinstance(counts, OF.Routing):
+            if xs.is_cuda and xs.shape[0] > 0 and getattr(self, "use_grouped_gemm", True):
+                h = OF.grouped_linear(xs, self.w_gate_up, counts)
+                return OF.grouped_linear(OF.swiglu(h), self.w_down, counts)
+            counts = counts.host_counts()
         if xs.is_cuda and xs.shape[0] > 0 and getattr(self, "use_grouped_gemm", True):
             # one grouped kernel per projection instead of a launch per expert
             E_local = self.w_gate_up.shape[0]
@@ -247,24 +261,25 @@ class MoEMLP(nn.Module):
     def forward(self, x):
         T, H = x.shape
         k = self.cfg.num_experts_per_tok
-        topw, tope = self.route(x)
-        flat_e = tope.reshape(-1)
-        order = torch.argsort(flat_e, stable=True)
-        token_of = order // k
+        topw, tope, routing = self.route(x)
         out = None
-        if x.is_cuda and hasattr(self.ep_dispatcher, "fused_forward"):
-            # dispatch and combine as one peer-memory kernel each (parallel/ep_fused.py)
-            out = self.ep_dispatcher.fused_forward(self, x, order, flat_e, topw)
-        if out is None:
-            xs = x[token_of]
-            if self.ep_dispatcher is not None:
-                ys = self.ep_dispatcher(self, xs, flat_e[order])
-            else:
-                counts = torch.bincount(flat_e, minlength=self.cfg.num_experts).tolist()
-                ys = self.experts_forward(xs, counts)
-            w = topw.reshape(-1)[order].to(ys.dtype).unsqueeze(-1)
-            out = torch.zeros(T, H, dtype=ys.dtype, device=x.device)
-            out.index_add_(0, token_of, ys * w)
+        if self.ep_dispatcher is not None:
+            flat_e = tope.reshape(-1)
+            order = routing.order.long()
+            if x.is_cuda and hasattr(self.ep_dispatcher, "fused_forward"):
+                # dispatch and combine as one peer-memory kernel each (parallel/ep_fused.py)
+                out = self.ep_dispatcher.fused_forward(self, x, order, flat_e, topw)
+            if out is None:
+                token_of = routing.token_of.long()
+                ys = self.ep_dispatcher(self, x[token_of], flat_e[order])
+                w = topw.reshape(-1)[order].to(ys.dtype).unsqueeze(-1)
+                out = torch.zeros(T, H, dtype=ys.dtype, device=x.device)
+                out.index_add_(0, token_of, ys * w)
+        else:
+            ys = self.experts_forward(x.index_select(0, routing.token_of), routing)
+            # every (token, slot) entry reads its row back: a gather and one sum over the k slots, the same
+            # bits run after run (no atomics)
+            out = (ys.index_select(0, routing.inv).view(T, k, H) * topw.to(ys.dtype).unsqueeze(-1)).sum(1)
         if self.shared_gate_up is not None:
             # the shared expert sees every token; its output is scaled by a per-token sigmoid gate
             sh = OF.linear(OF.swiglu(OF.linear(x, self.shared_gate_up)), self.shared_down)

@@ -36,8 +36,23 @@ template <int BN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     __nv_bfloat16* __restrict__ Cptr, const int4* __restrict__ tiles, int num_tiles, int N,
-                    int K, int ldc, int* err) {
+                    int K, int ldc, int* err, const int* __restrict__ num_rt_dev, int nblk) {
   constexpr bool A_MN = false;
+  // Row-tile mode (nblk > 0): `tiles` lists 128-row tiles only, written by the routing kernel together with
+  // their number; output tile i covers row tile i / nblk and n-block i % nblk, and the grid was sized for
+  // an upper bound of the row tiles.
+  if (nblk > 0) {
+    const int have = *num_rt_dev * nblk;
+    num_tiles = have < num_tiles ? have : num_tiles;
+  }
+  auto tile_info = [&](int tile) -> int4 {
+    if (nblk > 0) {
+      int4 t = tiles[tile / nblk];
+      t.w = tile % nblk;
+      return t;
+    }
+    return tiles[tile];
+  };
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -85,7 +100,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       int issued = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int4 ti = tiles[tile];
+        const int4 ti = tile_info(tile);
         const int expert = ti.x, m0 = ti.y, n0 = ti.w * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, err, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -161,7 +176,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-      const int4 ti = tiles[tile];
+      const int4 ti = tile_info(tile);
       const int m0 = ti.y, rows_valid = ti.z, n0 = ti.w * BN;
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
@@ -207,7 +222,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 template <int BN, bool B_MN>
 static int launch_grouped(const void* A, const void* B, void* C, const void* tiles, int num_tiles, int R, int N, int K, int E,
-                          int lda, int ldc, cudaStream_t stream) {
+                          int lda, int ldc, cudaStream_t stream, const int* num_rt_dev = nullptr, int nblk = 0) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmA, tmB;
   int rc = ab2host::encode_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)R, (uint64_t)lda * 2, BK, BM, true, 0);
@@ -226,7 +241,7 @@ static int launch_grouped(const void* A, const void* B, void* C, const void* til
   int* err = ab2host::error_flag();
   if (!err) return 301;
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const int4*>(tiles),
-                                               num_tiles, N, K, ldc, err);
+                                               num_tiles, N, K, ldc, err, num_rt_dev, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : 302;
 }
 
@@ -248,5 +263,24 @@ int ab2_gemm_grouped(const void* A, const void* B, void* C, const void* tiles, i
   if (bn == 128) return b_mn ? launch_grouped<128, true>(A, B, C, tiles, num_tiles, R, N, K, E, lda, ldc, s)
                              : launch_grouped<128, false>(A, B, C, tiles, num_tiles, R, N, K, E, lda, ldc, s);
   return 12;
+}
+
+// Same product with the tile list made on the device: row_tiles [max_row_tiles] int4 = (expert, first row,
+// valid rows, -) and *num_row_tiles as written by ab2_moe_route; no host copy of the group sizes is needed.
+int ab2_gemm_grouped_rt(const void* A, const void* B, void* C, const void* row_tiles, const void* num_row_tiles, int max_row_tiles,
+                        int R, int N, int K, int E, int lda, int ldc, int b_mn, int bn, void* stream) {
+  using namespace ab2;
+  if (max_row_tiles <= 0 || R <= 0) return 0;
+  if ((lda & 7) || (ldc & 7) || (K & 7) || (N & 7)) return 10;
+  if (bn != 128 && bn != 256) return 12;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nblk = (N + bn - 1) / bn;
+  const long long max_tiles = (long long)max_row_tiles * nblk;
+  if (max_tiles > 0x7fffffffLL) return 13;
+  const int* nrt = reinterpret_cast<const int*>(num_row_tiles);
+  if (bn == 256) return b_mn ? launch_grouped<256, true>(A, B, C, row_tiles, (int)max_tiles, R, N, K, E, lda, ldc, s, nrt, nblk)
+                             : launch_grouped<256, false>(A, B, C, row_tiles, (int)max_tiles, R, N, K, E, lda, ldc, s, nrt, nblk);
+  return b_mn ? launch_grouped<128, true>(A, B, C, row_tiles, (int)max_tiles, R, N, K, E, lda, ldc, s, nrt, nblk)
+              : launch_grouped<128, false>(A, B, C, row_tiles, (int)max_tiles, R, N, K, E, lda, ldc, s, nrt, nblk);
 }
 }

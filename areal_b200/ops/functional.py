@@ -132,6 +132,110 @@ def grouped_gemm(x: torch.Tensor, w: torch.Tensor, counts, b_mn: bool = False, t
     return y
 
 
+class Routing:
+    """Expert assignment of a batch of tokens, made on the device (:func:`moe_route`).
+
+    ``order[r]`` is the (token * k + slot) entry on row ``r`` of the expert-sorted layout, ``token_of[r]``
+    its token, ``inv`` the inverse of ``order``; ``counts`` / ``offs`` are the group sizes and starts;
+    ``row_tiles`` / ``num_row_tiles`` feed the grouped GEMM. ``host_counts()`` gives the group sizes as
+    a list; the copy was started when the routing was made, so a caller that asks late (the weight
+    gradients in backward) does not stall the stream."""
+
+    def __init__(self, tope, topw, probs, counts, offs, order, token_of, inv, row_tiles, num_row_tiles, k):
+        self.tope, self.topw, self.probs = tope, topw, probs
+        self.counts, self.offs, self.order, self.token_of, self.inv = counts, offs, order, token_of, inv
+        self.row_tiles, self.num_row_tiles, self.k = row_tiles, num_row_tiles, k
+        self.rows = order.shape[0]
+        self._host = None
+        self._event = None
+        if counts.is_cuda:
+            self._host = torch.empty(counts.shape, dtype=counts.dtype, pin_memory=True)
+            self._host.copy_(counts, non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record()
+
+    def host_counts(self) -> list:
+        if self._host is None:
+            return self.counts.tolist()
+        self._event.synchronize()
+        return self._host.tolist()
+
+
+def moe_route_ref(logits, k: int, bias=None, sigmoid: bool = False, norm: bool = True, scale: float = 1.0, tope=None):
+    """PyTorch statement of :func:`moe_route` (ties between equal scores may resolve differently)."""
+    T, E = logits.shape
+    probs = torch.sigmoid(logits.float()) if sigmoid else torch.softmax(logits.float(), dim=-1)
+    topw = None
+    if tope is None:
+        choice = probs if bias is None else probs + bias
+        tope = torch.topk(choice, k, dim=-1).indices
+        topw = probs.gather(1, tope)
+        if norm:
+            topw = topw / topw.sum(-1, keepdim=True).clamp(min=1e-20)
+        topw = topw * scale
+    flat = tope.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=E)
+    offs = torch.cat([counts.new_zeros(1), counts.cumsum(0)])
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device=order.device)
+    tiles = [(e, int(offs[e]) + r0, min(128, int(counts[e]) - r0), 0) for e in range(E) for r0 in range(0, int(counts[e]), 128)]
+    rt = torch.tensor(tiles, dtype=torch.int32, device=logits.device).view(-1, 4)
+    return Routing(tope.int(), topw, probs, counts.int(), offs.int(), order.int(), (order // k).int(), inv.int(), rt,
+                   torch.tensor([rt.shape[0]], dtype=torch.int32, device=logits.device), k)
+
+
+def moe_route(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor] = None, sigmoid: bool = False, norm: bool = True,
+              scale: float = 1.0, tope: Optional[torch.Tensor] = None, want_probs: bool = True) -> Routing:
+    """Scores, top-k choice, stable sort by expert, group sizes and the grouped-GEMM tile list from fp32
+    router logits [T, E], in four small launches and without a host read. With ``tope`` given (the choice
+    was made elsewhere, e.g. group-limited routing) only the sort / counts / tiles are produced."""
+    T, E = logits.shape
+    if not logits.is_cuda or E > 256 or k > 16:
+        return moe_route_ref(logits, k, bias, sigmoid, norm, scale, tope)
+    dev = logits.device
+    logits = logits.float().contiguous()
+    n = T * k
+    i32 = dict(dtype=torch.int32, device=dev)
+    given = tope is not None
+    tope_ = tope.to(torch.int32).contiguous() if given else torch.empty(T, k, **i32)
+    topw = None if given else torch.empty(T, k, dtype=torch.float32, device=dev)
+    probs = None if (given or not want_probs) else torch.empty(T, E, dtype=torch.float32, device=dev)
+    counts, offs = torch.empty(E, **i32), torch.empty(E + 1, **i32)
+    order, token_of, inv = torch.empty(n, **i32), torch.empty(n, **i32), torch.empty(n, **i32)
+    max_rt = n // 128 + E
+    row_tiles = torch.empty(max_rt, 4, **i32)
+    num_rt = torch.empty(1, **i32)
+    L = _L()
+    ws = torch.empty(int(L.ab2_moe_route_workspace(n, E)), **i32)
+    b = bias.float().contiguous() if bias is not None else None
+    flags = (1 if sigmoid else 0) | (2 if norm else 0) | (4 if given else 0)
+    rc = L.ab2_moe_route(logits.data_ptr(), _lib.ptr(b), T, E, k, flags, float(scale), _lib.ptr(probs), _lib.ptr(topw),
+                         tope_.data_ptr(), counts.data_ptr(), offs.data_ptr(), order.data_ptr(), token_of.data_ptr(),
+                         inv.data_ptr(), row_tiles.data_ptr(), num_rt.data_ptr(), max_rt, ws.data_ptr(), _s())
+    _lib.check(rc, "ab2_moe_route")
+    return Routing(tope_, topw, probs, counts, offs, order, token_of, inv, row_tiles, num_rt, k)
+
+
+def grouped_gemm_rt(x: torch.Tensor, w: torch.Tensor, routing: Routing, b_mn: bool = False) -> torch.Tensor:
+    """:func:`grouped_gemm` with the tile list of a device-made :class:`Routing` (no host copy of the group sizes)."""
+    if not x.is_cuda:
+        return grouped_gemm_ref(x, w, routing.host_counts(), b_mn)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()
+    R, K = x.shape
+    E = w.shape[0]
+    N = w.shape[2] if b_mn else w.shape[1]
+    assert (w.shape[1] if b_mn else w.shape[2]) == K and R == routing.rows
+    bn = 256 if N % 256 == 0 else 128
+    y = torch.empty(R, N, device=x.device, dtype=torch.bfloat16)
+    if R:
+        rc = _L().ab2_gemm_grouped_rt(x.data_ptr(), w.data_ptr(), y.data_ptr(), routing.row_tiles.data_ptr(),
+                                      routing.num_row_tiles.data_ptr(), routing.row_tiles.shape[0], R, N, K, E, x.stride(0),
+                                      y.stride(0), int(b_mn), bn, _s())
+        _lib.check(rc, "ab2_gemm_grouped_rt")
+    return y
+
+
 class _GroupedLinear(torch.autograd.Function):
     """``y[group e] = x[group e] @ W[e]^T`` for stacked expert weights ``W`` [E, N, K]. Forward and
     input gradient are one grouped kernel each; weight gradients accumulate per expert in fp32
@@ -139,16 +243,23 @@ class _GroupedLinear(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, counts):
-        ctx.counts = [int(c) for c in counts]
+        ctx.routing = counts if isinstance(counts, Routing) else None
+        ctx.counts = None if ctx.routing is not None else [int(c) for c in counts]
         ctx.save_for_backward(x, w)
+        if ctx.routing is not None:
+            return grouped_gemm_rt(x, w, ctx.routing)
         return grouped_gemm(x, w, ctx.counts)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        counts = ctx.counts
         dy = dy.contiguous()
-        dx = grouped_gemm(dy, w, counts, b_mn=True) if ctx.needs_input_grad[0] else None
+        if ctx.routing is not None:
+            dx = grouped_gemm_rt(dy, w, ctx.routing, b_mn=True) if ctx.needs_input_grad[0] else None
+            counts = ctx.routing.host_counts()      # copied to the host since the forward pass: no stall here
+        else:
+            counts = ctx.counts
+            dx = grouped_gemm(dy, w, counts, b_mn=True) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
@@ -174,6 +285,7 @@ class _GroupedLinear(torch.autograd.Function):
 
 
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts) -> torch.Tensor:
+    """``counts``: group sizes as a list of ints, or a :class:`Routing` made on the device."""
     return _GroupedLinear.apply(x, w, counts)
 
 

@@ -36,6 +36,9 @@ _SIGS = {
     "ab2_qknorm_rope_fwd": ([c_void_p] * 8 + [c_int] * 4 + [c_ll, c_float, c_void_p], c_int),
     "ab2_qknorm_rope_bwd": ([c_void_p] * 11 + [c_int] * 4 + [c_ll, c_ll, c_void_p], c_int),
     "ab2_gemm_grouped": ([c_void_p] * 4 + [c_int] * 9 + [c_void_p], c_int),
+    "ab2_gemm_grouped_rt": ([c_void_p] * 5 + [c_int] * 9 + [c_void_p], c_int),
+    "ab2_moe_route_workspace": ([c_ll, c_int], c_ll),
+    "ab2_moe_route": ([c_void_p] * 2 + [c_int] * 4 + [ctypes.c_float] + [c_void_p] * 10 + [c_int] + [c_void_p] * 2, c_int),
     "ab2_gemm_splitk": ([c_void_p] * 5 + [c_int] * 7 + [c_void_p], c_int),
     "ab2_gemm_fp8": ([c_void_p] * 5 + [c_int] * 8 + [c_void_p], c_int),
     "ab2_quant_fp8": ([c_void_p] * 3 + [c_int, c_int, c_ll, c_ll, c_int, c_int, c_void_p], c_int),

@@ -190,6 +190,12 @@ def main():
     # decode-sized projections (measured +4.7% tokens/s on one GPU with both on)
     os.environ.setdefault("AB2_PDL", "1")
     os.environ.setdefault("AB2_DECODE_SPLITK", "1")
+    # no step of this benchmark reduces through NVLink multicast (the fused kernels use plain peer loads and
+    # stores unless AREAL_NVLS_REDUCE=1), so no buffer is bound to a multicast object: a rank that ends early
+    # then cannot disturb its peers' GPUs through one
+    if os.environ.get("AREAL_NVLS_REDUCE", "0") != "1":
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
     import torch
     import torch.distributed as dist

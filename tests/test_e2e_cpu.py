@@ -238,7 +238,7 @@ def test_moe_router_variants():
         torch.nn.init.normal_(p, std=0.05)
     m.train()
     x = torch.randn(64, cfg.hidden_size)
-    w, e = m.route(x)
+    w, e, _ = m.route(x)
     assert w.shape == (64, 2) and e.shape == (64, 2)
     # weights: normalised sigmoid gates of the chosen experts times the scale
     probs = torch.sigmoid(x @ m.router.t())
@@ -259,7 +259,7 @@ def test_moe_router_variants():
     # the bias changes the choice only, not the weights
     m.expert_bias[:] = 0
     m.expert_bias[3] = 10.0
-    w2, e2 = m.route(x)
+    w2, e2, _ = m.route(x)
     assert (e2 == 3).any(dim=-1).float().mean() > 0.4   # expert 3 is picked whenever its group is among the chosen ones
     p2 = probs.gather(1, e2)
     assert torch.allclose(w2, p2 / p2.sum(-1, keepdim=True) * 2.5, atol=1e-6)

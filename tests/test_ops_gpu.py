@@ -357,6 +357,75 @@ def test_grouped_gemm_matches_fp32(counts):
     assert _rel_err(y, ref) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(w.grad, wr.grad) < 1e-2
 
 
+@pytest.mark.parametrize("T,E,k,sigmoid,bias", [(3000, 128, 8, False, False), (517, 64, 6, True, True), (40, 32, 1, False, False),
+                                                (5000, 96, 4, False, True)])
+def test_moe_route_kernels_match_pytorch(T, E, k, sigmoid, bias):
+    """Device-side routing (scores, top-k, stable sort by expert, group sizes, GEMM tile list) against
+    softmax / topk / argsort / bincount in PyTorch, and the same bits when run twice."""
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    logits = torch.randn(T, E, device="cuda", generator=g) * 2.0
+    b = torch.randn(E, device="cuda", generator=g) * 0.05 if bias else None
+    r = OF.moe_route(logits, k, bias=b, sigmoid=sigmoid, norm=True, scale=1.5)
+    torch.cuda.synchronize()
+    _no_kernel_error()
+    ref = OF.moe_route_ref(logits, k, bias=b, sigmoid=sigmoid, norm=True, scale=1.5)
+    assert torch.allclose(r.probs, ref.probs, atol=1e-6, rtol=1e-5)
+    # random fp32 scores have no ties: the chosen sets and their order agree
+    assert torch.equal(r.tope, ref.tope) and torch.allclose(r.topw, ref.topw, atol=1e-6, rtol=1e-5)
+    assert torch.equal(r.counts, ref.counts) and torch.equal(r.offs, ref.offs)
+    assert torch.equal(r.order, ref.order) and torch.equal(r.token_of, ref.token_of) and torch.equal(r.inv, ref.inv)
+    n = int(r.num_row_tiles.item())
+    assert n == ref.row_tiles.shape[0] and torch.equal(r.row_tiles[:n], ref.row_tiles)
+    assert r.host_counts() == ref.counts.tolist()
+    r2 = OF.moe_route(logits, k, bias=b, sigmoid=sigmoid, norm=True, scale=1.5)
+    assert torch.equal(r2.order, r.order) and torch.equal(r2.topw, r.topw)
+    # a choice made elsewhere: only the sort and the tables are produced
+    r3 = OF.moe_route(logits, k, tope=ref.tope)
+    assert torch.equal(r3.order, ref.order) and torch.equal(r3.counts, ref.counts) and r3.topw is None
+
+
+def test_grouped_linear_with_device_routing_matches_host_tile_table():
+    """The grouped GEMM fed by the device-made tile list (grid sized for an upper bound of the tiles) gives the
+    bits of the host-built table, forward and backward; the MoE layer on top of it matches fp32."""
+    torch.manual_seed(8)
+    T, E, k, K, N = 1500, 16, 4, 256, 384
+    logits = torch.randn(T, E, device="cuda")
+    logits[:, 3] = -30.0                                    # one expert without tokens
+    r = OF.moe_route(logits, k)
+    counts = r.host_counts()
+    assert counts[3] == 0 and sum(counts) == T * k
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(E, N, K, device="cuda") / K ** 0.5).bfloat16()
+    xs = x.index_select(0, r.token_of)
+    xa, wa = xs.clone().requires_grad_(), w.clone().requires_grad_()
+    xb, wb = xs.clone().requires_grad_(), w.clone().requires_grad_()
+    ya, yb = OF.grouped_linear(xa, wa, r), OF.grouped_linear(xb, wb, counts)
+    gy = torch.randn_like(ya)
+    ya.backward(gy)
+    yb.backward(gy)
+    _no_kernel_error()
+    assert torch.equal(ya, yb) and torch.equal(xa.grad, xb.grad) and torch.equal(wa.grad, wb.grad)
+
+    from areal_b200.models.config import ModelConfig
+    from areal_b200.models.decoder import MoEMLP
+
+    cfg = ModelConfig(hidden_size=256, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128, norm_topk_prob=True)
+    m = MoEMLP(cfg, torch.bfloat16, "cuda")
+    for p_ in m.parameters():
+        torch.nn.init.normal_(p_, std=0.05)
+    xin = torch.randn(700, 256, device="cuda").bfloat16().requires_grad_()
+    out = m(xin)
+    out.float().pow(2).sum().backward()
+    m32 = MoEMLP(cfg, torch.float32, "cuda")
+    m32.load_state_dict({k_: v.float() for k_, v in m.state_dict().items()})
+    m32.use_grouped_gemm = False
+    x32 = xin.detach().float().requires_grad_()
+    o32 = m32(x32)
+    o32.pow(2).sum().backward()
+    assert _rel_err(out, o32) < 2e-2 and _rel_err(xin.grad, x32.grad) < 3e-2
+    assert _rel_err(m.w_down.grad, m32.w_down.grad) < 3e-2 and _rel_err(m.router.grad, m32.router.grad) < 5e-2
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,page_size,splits", [(128, 32, 8, 64, 4), (128, 8, 1, 16, 3), (128, 12, 2, 64, 1), (64, 4, 2, 16, 4),
                                                        (64, 16, 2, 32, 2)])
 def test_paged_decode_attention_matches_fp32(D, Hq, Hkv, page_size, splits):

@@ -97,6 +97,38 @@ def rpc_worker():
     RT.LOCAL_STORE.clear()
 
 
+def test_rpc_guard_forks_and_ends_sibling_workers_and_never_repeats_a_port(rpc_worker, tmp_path):
+    import os
+    import sys
+
+    addr = rpc_worker
+    a = http_json(f"http://{addr}/alloc_ports", {"count": 3})
+    b = http_json(f"http://{addr}/alloc_ports", {"count": 3})
+    assert a["status"] == "success" and len(set(a["ports"]) | set(b["ports"])) == 6
+    assert http_json(f"http://{addr}/alloc_ports", {"count": 0})["__http_error__"] == 400
+    mark = tmp_path / "mark.txt"
+    code = f"import os,time; open(r'{mark}','w').write(os.environ['WHO']); time.sleep(120)"
+    r = http_json(f"http://{addr}/fork", {"role": "ref", "worker_index": 0, "raw_cmd": [sys.executable, "-c", code], "env": {"WHO": "ref0"}})
+    assert r["status"] == "success" and r["pid"] > 0
+    for _ in range(100):
+        if mark.exists() and mark.read_text() == "ref0":
+            break
+        time.sleep(0.05)
+    assert mark.read_text() == "ref0"
+    # a second fork under the same name is refused while the first one lives
+    assert http_json(f"http://{addr}/fork", {"role": "ref", "worker_index": 0, "raw_cmd": [sys.executable, "-c", "pass"]})["__http_error__"] == 400
+    assert http_json(f"http://{addr}/fork", {"role": "ref", "raw_cmd": []})["__http_error__"] == 400
+    st = http_json(f"http://{addr}/forked")["workers"]
+    assert st == [{"role": "ref", "worker_index": 0, "pid": r["pid"], "returncode": None}]
+    assert http_json(f"http://{addr}/kill_forked_worker", {"role": "ref", "worker_index": 0})["status"] == "success"
+    with pytest.raises(ProcessLookupError):
+        for _ in range(100):
+            os.kill(r["pid"], 0)
+            time.sleep(0.05)
+    assert http_json(f"http://{addr}/kill_forked_worker", {"role": "ref", "worker_index": 0})["__http_error__"] == 404
+    assert http_json(f"http://{addr}/forked")["workers"] == []
+
+
 def test_rpc_worker_engine_calls_and_remote_tensors(rpc_worker):
     addr = rpc_worker
     assert http_json(f"http://{addr}/health")["status"] == "ok"
