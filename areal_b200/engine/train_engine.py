@@ -604,6 +604,19 @@ class B200TrainEngine(TrainEngine):
             pos = D.positions_from_cu_seqlens(cu, T)
         labels = torch.roll(ids, shifts=-1, dims=0)
         pb = PackedBatch(cu, pos, T, int(mb.get("max_seqlen", 0)))
+        if getattr(self.config, "enable_tree_training", False):
+            # prefix sharing: sequences of the micro-batch that start alike (the samples of a group share their
+            # prompt) are merged into a trie, every distinct (prefix, token) runs through the layers once, and
+            # the per-token hidden states are read back from the trie nodes (reference:
+            # areal/engine/fsdp_engine.py tree-training branch over areal/models/tree_attn/*)
+            if self.sp_size > 1 or getattr(self, "pp_size", 1) > 1 or getattr(self, "tp_size", 1) > 1:
+                raise NotImplementedError("tree training runs with data parallelism only")
+            from ..models.tree_attn import tree_hidden_for_packed_batch
+
+            hidden, saving = tree_hidden_for_packed_batch(self.model, ids, cu, pad_to=self._align())
+            self._tree_saving = saving
+            stats_tracker.scalar(tree_token_saving=saving)
+            return hidden, labels, slice(0, T)
         if self.sp_size > 1:
             chunk = T // self.sp_size
             sl = slice(self.sp_rank * chunk, (self.sp_rank + 1) * chunk)

@@ -3,7 +3,8 @@ import torch
 
 from areal_b200.models.config import preset
 from areal_b200.models.decoder import build_model
-from areal_b200.models.tree_attn import ancestor_mask, build_tree, tree_logprobs
+from areal_b200.models.tree_attn import (ancestor_mask, build_tree, tree_forward_hidden, tree_hidden_for_packed_batch,
+                                         tree_logprobs)
 
 
 def test_trie_packing_and_mask():
@@ -35,3 +36,82 @@ def test_tree_logprobs_match_per_sequence_forward():
             ref, _ = model.logprobs_entropy(h[:-1].contiguous(), ids[1:])
             assert torch.allclose(lp, ref, atol=2e-5), (lp - ref).abs().max()
     assert build_tree(seqs).saving > 0.45                         # the shared prompt is computed once
+
+
+def test_flash_form_matches_masked_form_and_carries_gradients_of_shared_nodes():
+    """Gather-to-sequences attention (the form the flash kernels run) against the ancestor-mask oracle on a trie
+    with nested branching, forward and parameter gradients; node padding changes nothing."""
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=5)
+    g = torch.Generator().manual_seed(1)
+    r = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()   # noqa: E731
+    p, mid = r(9), r(4)
+    seqs = [p + mid + r(5), p + mid + r(2), p + r(6), r(3)]
+    tree = build_tree(seqs)
+    assert tree.depth.tolist() == [int(ancestor_mask(tree.parent)[i].sum()) - 1 for i in range(tree.num_nodes)]
+    outs = {}
+    for form, pad in (("masked", 1), ("flash", 1), ("flash", 16)):
+        model.zero_grad()
+        h = tree_forward_hidden(model, tree, form, pad)
+        assert h.shape[0] == tree.num_nodes
+        w = torch.linspace(0.5, 1.5, h.shape[0])[:, None]
+        (h * w).pow(2).sum().backward()
+        outs[(form, pad)] = (h.detach(), model.layers[0].self_attn.qkv_proj.grad.clone(), model.embed_tokens.grad.clone())
+    ref = outs[("masked", 1)]
+    for key in (("flash", 1), ("flash", 16)):
+        for a, b in zip(outs[key], ref):
+            assert torch.allclose(a, b, atol=2e-4, rtol=1e-3), (key, (a - b).abs().max())
+
+
+def test_packed_batch_entry_equals_plain_forward():
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=6).eval()
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab_size, (10,), generator=g).tolist()
+    seqs = [prompt + torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (4, 6, 3)] + [[0] * 5]
+    ids = torch.tensor([t for s in seqs for t in s])
+    cu = torch.tensor([0] + [len(s) for s in seqs]).cumsum(0).to(torch.int32)
+    with torch.no_grad():
+        h, saving = tree_hidden_for_packed_batch(model, ids, cu, pad_to=8)
+        ref = model(ids, cu, max_seqlen=16)
+    assert saving > 0.4 and torch.allclose(h, ref, atol=2e-5)
+
+
+def test_engine_trains_the_same_with_and_without_prefix_sharing():
+    """``enable_tree_training`` changes how a micro-batch is computed, not what: log-probs of a batch whose samples
+    share their prompts and the parameters after one SFT-style step agree with the plain path."""
+    from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, PPOActorConfig
+    from areal_b200.engine.train_engine import B200PPOActor
+
+    cfgm = preset("tiny-qwen3")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(1, cfgm.vocab_size, (11,), generator=g).tolist() for _ in range(2)]
+    seqs = [p + torch.randint(1, cfgm.vocab_size, (n,), generator=g).tolist() for p in prompts for n in (5, 8, 3)]
+    L = max(len(s) for s in seqs)
+    ids = torch.zeros(len(seqs), L, dtype=torch.long)
+    am = torch.zeros(len(seqs), L, dtype=torch.long)
+    for i, s in enumerate(seqs):
+        ids[i, :len(s)] = torch.tensor(s)
+        am[i, :len(s)] = 1
+    loss_mask = am.clone()
+    loss_mask[:, :11] = 0
+    batch = {"input_ids": ids, "attention_mask": am, "loss_mask": loss_mask}
+
+    def run(tree: bool):
+        cfg = PPOActorConfig(init_from_scratch=True, dtype="float32", optimizer=OptimizerConfig(type="sgd", lr=1e-1, weight_decay=0.0),
+                             mb_spec=MicroBatchSpec(max_tokens_per_mb=4096), enable_tree_training=tree)
+        e = B200PPOActor(cfg)
+        e.create_process_group()
+        e.initialize(model_config=cfgm, seed=11)
+        lp = e.forward_batch(dict(batch), output="logprobs")
+
+        def loss_fn(logp, entropy, mb):
+            m = torch.roll(mb["loss_mask"], -1, 0).float()
+            return -(logp * m).sum() / m.sum().clamp(min=1)
+        e.train_batch(dict(batch), loss_fn, lambda mb: torch.roll(mb["loss_mask"], -1, 0).float().sum())
+        return lp, e.store.flat_param.clone(), getattr(e, "_tree_saving", None)
+
+    lp0, p0, s0 = run(False)
+    lp1, p1, s1 = run(True)
+    assert s0 is None and s1 > 0.3
+    assert torch.allclose(lp0, lp1, atol=2e-5) and torch.allclose(p0, p1, atol=2e-5)
