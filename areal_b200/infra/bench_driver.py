@@ -158,15 +158,34 @@ def _pick_recompute(args, actor, model_cfg) -> None:
         return
     free, _ = torch.cuda.mem_get_info()
     sp = max(1, getattr(actor, "sp_size", 1))
-    t = actor.config.mb_spec.max_tokens_per_mb // sp
     n = model_cfg.num_layers
-    per_layer_gb = t * 0.30e-3 * (model_cfg.hidden_size / 4096.0)
-    avail = free / 2 ** 30 - 12.0 - 5.0 - per_layer_gb - n * t * 8e-6
-    keep = max(0, min(n, int(avail / per_layer_gb)))
-    if actor.cpu_group is not None:
-        tt = torch.tensor([keep], dtype=torch.int64)
+
+    def kept_layers(t: int) -> int:
+        per_layer_gb = t * 0.30e-3 * (model_cfg.hidden_size / 4096.0)
+        avail = free / 2 ** 30 - 12.0 - 5.0 - per_layer_gb - n * t * 8e-6
+        return max(0, min(n, int(avail / per_layer_gb)))
+
+    # Recomputing a layer costs a third of its forward + backward time; a smaller micro-batch costs next to
+    # nothing as long as its GEMMs still have thousands of rows (gradients accumulate locally, no collective per
+    # micro-batch). So the micro-batch shrinks (by halves, not below 4096 tokens per rank nor below the longest
+    # sequence) until every layer's activations fit, and only what then still does not fit is recomputed.
+    t = actor.config.mb_spec.max_tokens_per_mb // sp
+    longest = -(-(args.prompt_len + args.max_len) // 1024) * 1024
+    floor_t = max(4096, -(-longest // sp))
+    while kept_layers(t) < n and t // 2 >= floor_t:
+        t //= 2
+    keep = kept_layers(t)
+    if actor.cpu_group is not None:               # every trainer rank must split the batch the same way
+        tt = torch.tensor([t], dtype=torch.int64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MIN, group=actor.cpu_group)
+        t = int(tt[0])
+        tt = torch.tensor([kept_layers(t)], dtype=torch.int64)
         dist.all_reduce(tt, op=dist.ReduceOp.MIN, group=actor.cpu_group)
         keep = int(tt[0])
+    if t * sp != actor.config.mb_spec.max_tokens_per_mb:
+        actor.config.mb_spec.max_tokens_per_mb = t * sp
+        args._resolved["max_tokens_per_mb"] = t * sp
+        args._resolved["max_tokens_per_mb_shrunk_to_keep_activations"] = True
     frac = 1.0 - keep / n
     actor.model.set_activation_checkpointing("memory_budget", frac)
     args._resolved["gradient_checkpointing"] = f"memory_budget: {n - keep} of {n} layers recomputed"

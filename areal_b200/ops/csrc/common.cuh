@@ -14,8 +14,15 @@
 
 namespace ab2 {
 
-// ~1.5 s at 1.9 GHz; generous for any tile wait, short enough to return control.
-static constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;
+// Limit of one wait inside a kernel. A wait on a tile of the kernel's own pipeline (a TMA stage, a TMEM
+// buffer) lasts microseconds: ~0.5 s at 1.9 GHz leaves room for a context switched out by another process
+// and still returns control quickly. A file whose pipeline waits transitively on another GPU (its producer
+// spins on a peer's flag before it fills the stage) defines AB2_WAIT_LIMIT_CYCLES = 3e9 (~1.5 s, the
+// tolerated arrival skew between ranks) before including this header.
+#ifndef AB2_WAIT_LIMIT_CYCLES
+#define AB2_WAIT_LIMIT_CYCLES 1000000000LL
+#endif
+static constexpr long long WAIT_LIMIT_CYCLES = AB2_WAIT_LIMIT_CYCLES;
 
 enum KernelError : int {
   ERR_NONE = 0,

@@ -41,6 +41,7 @@
 // Takes the place of the all_gather / reduce_scatter + cuBLAS pairs behind the reference's
 // tensor-parallel linear layers (areal/engine/fsdp_utils/parallel.py:227-385, DTensor
 // Colwise/Rowwise plans) and of SGLang's TP all-reduce on the rollout side.
+#define AB2_WAIT_LIMIT_CYCLES 3000000000LL   // stages here are filled after a peer's flag arrived: allow the ranks' skew
 #include "common.cuh"
 
 namespace ab2 {

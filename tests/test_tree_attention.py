@@ -1,4 +1,5 @@
 """Prefix-sharing training: trie packing, ancestor mask, parity with per-sequence forward."""
+import pytest
 import torch
 
 from areal_b200.models.config import preset
@@ -115,3 +116,32 @@ def test_engine_trains_the_same_with_and_without_prefix_sharing():
     lp1, p1, s1 = run(True)
     assert s0 is None and s1 > 0.3
     assert torch.allclose(lp0, lp1, atol=2e-5) and torch.allclose(p0, p1, atol=2e-5)
+
+
+@pytest.mark.gpu
+def test_tree_training_on_the_flash_kernels_matches_the_plain_packed_forward():
+    """bf16 model on the device: hidden states and parameter gradients of a batch whose groups share long prompts,
+    computed over the trie (flash kernels on the gathered layout), against the plain packed forward + backward."""
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=7)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(1, cfg.vocab_size, (n,), generator=g).tolist() for n in (300, 170)]
+    seqs = [p + torch.randint(1, cfg.vocab_size, (n,), generator=g).tolist() for p in prompts for n in (90, 260, 33, 140)]
+    ids = torch.tensor([t for s in seqs for t in s], device="cuda", dtype=torch.int32)
+    cu = torch.tensor([0] + [len(s) for s in seqs]).cumsum(0).to(torch.int32).cuda()
+    w = torch.linspace(0.5, 1.5, ids.numel(), device="cuda")[:, None]
+    grads = []
+    outs = []
+    for tree in (False, True):
+        model.zero_grad()
+        if tree:
+            h, saving = tree_hidden_for_packed_batch(model, ids, cu, pad_to=128)
+            assert saving > 0.5
+        else:
+            h = model(ids, cu, max_seqlen=600)
+        (h.float() * w).pow(2).mean().backward()
+        outs.append(h.detach().float())
+        grads.append([p.grad.detach().float().clone() for p in model.parameters() if p.grad is not None])
+    rel = lambda a, b: ((a - b).norm() / b.norm().clamp(min=1e-12)).item()   # noqa: E731
+    assert rel(outs[1], outs[0]) < 2e-2
+    assert len(grads[0]) == len(grads[1]) and max(rel(a, b) for a, b in zip(grads[1], grads[0])) < 5e-2
