@@ -81,6 +81,8 @@ class RolloutController:
         self._executor: Optional[WorkflowExecutor] = None
         self._cb_server = None
         self.callback_addr: Optional[str] = None
+        self.proxy_addrs: list[str] = []
+        self._gateway = None
 
     # ------------------------------------------------------------------ lifecycle
     def initialize(self, n_workers: int = 1, gpus_per_worker: int = 0, engine_args: tuple = (), engine_kwargs: Optional[dict] = None,
@@ -107,7 +109,59 @@ class RolloutController:
             self._start_callback_server()
         return self
 
+    # ------------------------------------------------------------------ agent mode
+    def start_proxy(self, tokenizer: str, tokenizer_kwargs: Optional[dict] = None, gconfig: Optional[dict] = None,
+                    admin_key: Optional[str] = None, chat_template_type: str = "hf") -> list[str]:
+        """One OpenAI-compatible proxy beside every rollout worker, over that worker's engine (``tokenizer``: dotted
+        path of a callable that returns the tokenizer). Returns their base urls (reference
+        ``rollout_controller.py:406-471``)."""
+        if self.proxy_addrs:
+            return self.proxy_addrs
+        if not self.workers:
+            raise RuntimeError("initialize() first: the proxies sit beside the rollout workers")
+        name = f"{self.role}-proxy"
+        futs = [self._pool.submit(self.scheduler.create_engine, w.id, "areal_b200.openai.proxy.HostedProxy", name=name,
+                                  engine_name=self.role, tokenizer=tokenizer, tokenizer_kwargs=tokenizer_kwargs, gconfig=gconfig,
+                                  admin_key=admin_key, host=w.ip, chat_template_type=chat_template_type) for w in self.workers]
+        [f.result() for f in futs]
+        futs = [self._pool.submit(self.scheduler.call_engine, w.id, "initialize", engine_name=name, direct=True) for w in self.workers]
+        self.proxy_addrs = [f.result() for f in futs]
+        self._proxy_admin_key = admin_key
+        return self.proxy_addrs
+
+    def get_proxy_addr(self, rank: int) -> str:
+        if not self.proxy_addrs:
+            raise RuntimeError("start_proxy() first")
+        return self.proxy_addrs[rank]
+
+    def start_proxy_gateway(self, host: str = "127.0.0.1", port: Optional[int] = None) -> str:
+        """One address for agents outside the job, in front of all proxies (sessions stick to the proxy that
+        opened them). Reference ``rollout_controller.py:496-577``."""
+        if self._gateway is None:
+            from ...openai.proxy_gateway import ProxyGateway
+
+            if not self.proxy_addrs:
+                raise RuntimeError("start_proxy() first")
+            self._gateway = ProxyGateway(self.proxy_addrs, getattr(self, "_proxy_admin_key", None), host=host, port=port).start()
+        return self._gateway.addr
+
+    @property
+    def proxy_gateway_addr(self) -> str:
+        if self._gateway is None:
+            raise RuntimeError("proxy gateway not started")
+        return self._gateway.addr
+
     def destroy(self):
+        if self._gateway is not None:
+            self._gateway.stop()
+            self._gateway = None
+        if self.proxy_addrs and self._pool is not None:
+            for w in self.workers:
+                try:
+                    self.scheduler.call_engine(w.id, "destroy", engine_name=f"{self.role}-proxy", direct=True)
+                except Exception as e:
+                    logger.warning("stopping the proxy on %s failed: %r", w.id, e)
+            self.proxy_addrs = []
         if self._executor is not None:
             self._executor.destroy()
             self._executor = None

@@ -50,6 +50,7 @@ from ...utils import logging as alog
 from ...utils.dynamic_import import import_from_string
 from ...utils.network import find_free_ports, gethostip
 from . import rtensor as RT
+from .hosted import HOSTED_ENGINES
 from .serialization import deserialize_value, serialize_value
 
 logger = alog.getLogger("rpc_server")
@@ -82,6 +83,7 @@ class EngineHost:
         def make():
             cls = import_from_string(cls_path)
             self.engines[name] = cls(*args, **kwargs)
+            HOSTED_ENGINES[name] = self.engines[name]
             return True
         return self.run(make)
 

@@ -298,3 +298,37 @@ class OpenAIProxyServer:
             self._srv.server_close()
             self._srv = None
         self._loop.call_soon_threadsafe(self._loop.stop)
+
+
+class HostedProxy:
+    """An :class:`OpenAIProxyServer` created inside an RPC worker over an engine that the worker already hosts
+    (agents reach the rollout engine of that worker over HTTP; the trajectories stay on the worker until they
+    are exported). The role of the reference's forked proxy rollout server
+    (``areal/infra/controller/rollout_controller.py:406-471``); here the engine lives in the worker process, so
+    the proxy is a set of threads beside it instead of a second process."""
+
+    def __init__(self, engine_name: str, tokenizer: str, tokenizer_kwargs: Optional[dict] = None, gconfig: Optional[dict] = None,
+                 admin_key: Optional[str] = None, host: str = "127.0.0.1", chat_template_type: str = "hf"):
+        from ..api.cli_args import GenerationHyperparameters
+        from ..infra.rpc.hosted import HOSTED_ENGINES
+        from ..utils.dynamic_import import import_from_string
+
+        if engine_name not in HOSTED_ENGINES:
+            raise KeyError(f"no engine '{engine_name}' is hosted by this worker (have: {sorted(HOSTED_ENGINES)})")
+        tok = import_from_string(tokenizer)(**(tokenizer_kwargs or {}))
+        g = GenerationHyperparameters(**gconfig) if isinstance(gconfig, dict) else (gconfig or GenerationHyperparameters())
+        self.server = OpenAIProxyServer(HOSTED_ENGINES[engine_name], tok, g, host=host, admin_key=admin_key,
+                                        chat_template_type=chat_template_type)
+
+    def initialize(self) -> str:
+        self.server.start()
+        return self.server.base_url
+
+    def base_url(self) -> str:
+        return self.server.base_url
+
+    def n_sessions(self) -> int:
+        return len(self.server._sessions)
+
+    def destroy(self) -> None:
+        self.server.stop()

@@ -47,7 +47,7 @@ class PausableBuffer:
     def __init__(self, nbytes: int, device=None, keep_contents: bool = True):
         """``keep_contents``: a pause saves the buffer to pinned host memory and a resume restores
         it (weights, optimizer state); False discards the contents (KV cache)."""
-        if device is not None:
+        if device is not None and torch.device(device).index is not None:
             torch.cuda.set_device(device)
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.nbytes, self.keep_contents = int(nbytes), keep_contents

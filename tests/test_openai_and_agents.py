@@ -384,3 +384,40 @@ def test_openai_agents_example_runs_a_function_call_round_trip():
     traj = asyncio.run(ad.arun_episode(eng, {"question": "What is 17+72?", "answer": 89}))
     assert traj["input_ids"].shape[0] == 2 and traj["rewards"].tolist()[-1] == 1.0
     assert "89" in ByteTok().decode(eng.requests[1].input_ids)            # the tool result reached the second call
+
+
+def test_proxy_gateway_spreads_sessions_and_relays_to_the_owner():
+    """Two proxies behind one address: sessions open on the emptier proxy, later requests (streamed ones too) reach
+    the proxy that owns the key, exporting closes the mapping, unknown keys and a wrong admin key are refused."""
+    from areal_b200.openai.proxy_gateway import ProxyGateway
+
+    g = GenerationHyperparameters(max_new_tokens=16)
+    pa = OpenAIProxyServer(ScriptedEngine(["from-a"] * 4), ByteTok(), g, admin_key="adm").start()
+    pb = OpenAIProxyServer(ScriptedEngine(["from-b"] * 4), ByteTok(), g, admin_key="adm").start()
+    gw = ProxyGateway([pa.base_url, pb.base_url], admin_api_key="adm").start()
+    try:
+        assert _post(f"{gw.addr}/rl/start_session", {}, "nope")[0] == 401
+        k1 = _post(f"{gw.addr}/rl/start_session", {}, "adm")[1]
+        k2 = _post(f"{gw.addr}/rl/start_session", {}, "adm")[1]
+        assert k1["base_url"] == gw.base_url and gw.sessions() == [1, 1]
+        msg = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 8}
+        r1 = _post(f"{gw.base_url}/chat/completions", msg, k1["api_key"])[1]["choices"][0]["message"]["content"]
+        r2 = _post(f"{gw.base_url}/chat/completions", msg, k2["api_key"])[1]["choices"][0]["message"]["content"]
+        assert {r1, r2} == {"from-a", "from-b"}
+        raw = _sse(f"{gw.base_url}/chat/completions", {**msg, "stream": True}, k1["api_key"])
+        text = "".join(json.loads(l[6:])["choices"][0]["delta"].get("content", "") for l in raw.split("\n") if l.startswith("data: {"))
+        assert text == r1 and raw.rstrip().endswith("data: [DONE]")
+        assert _post(f"{gw.base_url}/chat/completions", msg, "sk-unknown")[0] == 401
+        assert _post(f"{gw.addr}/rl/set_reward", {"reward": 1.0}, k1["api_key"])[0] == 200
+        assert _post(f"{gw.addr}/rl/end_session", {}, k1["api_key"])[0] == 200
+        code, ex = _post(f"{gw.addr}/rl/export_trajectories", {"api_key": k1["api_key"], "discount": 1.0}, "adm")
+        assert code == 200 and len(ex["interactions"]) == 2 and all(v["rewards"] == [1.0] for v in ex["interactions"].values())
+        assert sorted(gw.sessions()) == [0, 1]
+        assert _post(f"{gw.addr}/rl/export_trajectories", {"api_key": k1["api_key"]}, "adm")[0] == 401
+        k3 = _post(f"{gw.addr}/rl/start_session", {}, "adm")[1]     # lands on the proxy that just emptied
+        r3 = _post(f"{gw.base_url}/chat/completions", msg, k3["api_key"])[1]["choices"][0]["message"]["content"]
+        assert r3 == r1
+        code, h = 200, json.loads(urllib.request.urlopen(f"{gw.addr}/health", timeout=10).read())
+        assert h["open_sessions"] == [1, 1]
+    finally:
+        gw.stop(); pa.stop(); pb.stop()

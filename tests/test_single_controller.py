@@ -266,6 +266,51 @@ def test_slurm_scheduler_against_mocked_commands(tmp_path, monkeypatch):
     name_resolve.reconfigure(type="memory")
 
 
+@pytest.mark.timeout(300)
+def test_rollout_controller_starts_proxies_beside_workers_and_a_gateway(tmp_path):
+    """Agent mode: one OpenAI-compatible proxy inside every rollout worker (over the engine the worker hosts) and one
+    gateway address in front of them; a session opened through the gateway generates on a worker's engine and its
+    trajectory comes back with the reward."""
+    cfg = _grpo_cfg(str(tmp_path))
+    mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+    sched = LocalScheduler(gpu_devices=[], log_dir=str(tmp_path / "sched"))
+    rollout = RolloutController("areal_b200.engine.infer_engine.NativeInferenceEngine", cfg.rollout, sched, role="rollout")
+    try:
+        rollout.initialize(n_workers=2, engine_kwargs={"model_config": mc}, init_kwargs={"seed": 1})
+        with pytest.raises(RuntimeError):
+            rollout.start_proxy_gateway()
+        addrs = rollout.start_proxy("areal_b200.dataset.CharTokenizer", gconfig={"max_new_tokens": 6}, admin_key="adm")
+        assert len(addrs) == 2 and len(set(addrs)) == 2 and rollout.get_proxy_addr(1) == addrs[1]
+        gw = rollout.start_proxy_gateway()
+        assert rollout.proxy_gateway_addr == gw
+        keys = [http_json(f"{gw}/rl/start_session", {}, timeout=30)  # no admin key: refused
+                ]
+        assert keys[0]["__http_error__"] == 401
+        import json
+        import urllib.request
+
+        def post(path, body, key):
+            req = urllib.request.Request(gw + path, data=json.dumps(body).encode(),
+                                         headers={"Content-Type": "application/json", "Authorization": f"Bearer {key}"})
+            with urllib.request.urlopen(req, timeout=120) as r:
+                return json.loads(r.read())
+        sess = [post("/rl/start_session", {}, "adm") for _ in range(2)]
+        for s_ in sess:
+            c = post("/v1/chat/completions", {"messages": [{"role": "user", "content": "1+2="}], "max_tokens": 6}, s_["api_key"])
+            assert c["usage"]["completion_tokens"] >= 1 and c["choices"][0]["finish_reason"] in ("stop", "length")
+            post("/rl/set_reward", {"reward": 0.5}, s_["api_key"])
+            post("/rl/end_session", {}, s_["api_key"])
+        # one session per worker: each proxy served one
+        n = [sched.call_engine(w.id, "n_sessions", engine_name="rollout-proxy", direct=True) for w in rollout.workers]
+        assert n == [1, 1]
+        ex = post("/rl/export_trajectories", {"api_key": sess[0]["api_key"]}, "adm")
+        (traj,) = ex["interactions"].values()
+        assert traj["rewards"] == [0.5] and sum(traj["loss_mask"]) >= 1 and len(traj["input_ids"]) == len(traj["logprobs"])
+    finally:
+        rollout.destroy()
+        sched.delete_workers()
+
+
 def test_ray_scheduler_against_fake_ray(tmp_path):
     """A stand-in ``ray`` module: actors run in-process, placement groups are records."""
     import types
