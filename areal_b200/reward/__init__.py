@@ -40,7 +40,8 @@ def gsm8k_reward_fn(prompt, completions, prompt_ids, completion_ids, answer=None
     return 1.0 if gold is not None and pred == gold else 0.0
 
 
-math_verify_reward_fn = gsm8k_reward_fn
+from .math_verify import (MathVerifyWorker, clevr_count_70k_reward_fn, extract_final_answer, geometry3k_reward_fn,  # noqa: E402,F401
+                          get_math_verify_worker, math_verify_reward_fn)
 
 
 def countdown_reward_fn(prompt, completions, prompt_ids, completion_ids, numbers=None, target=None, **kwargs) -> float:

@@ -253,3 +253,41 @@ def test_adam_with_bf16_state_tracks_fp32_adamw():
     assert float((moved - want).abs().max()) < 0.1 * float(want.abs().max())
     stalled = (w0.to(torch.bfloat16).float() - w0).abs().max()          # scale of one bf16 rounding error, for reference
     assert float((m.weight.float() - ref.detach()).abs().max()) <= 2 * float(stalled) + 1e-3
+
+
+@pytest.mark.parametrize("resp,gold,want", [
+    ("so we get \\boxed{\\frac{3}{4}}", "0.75", 1.0),
+    ("The answer is 1,234.", "#### 1234", 1.0),
+    ("thus \\boxed{\\dfrac{\\sqrt{2}}{2}} is the value", "\\frac{\\sqrt{2}}{2}", 1.0),
+    ("<answer> 45% </answer>", "0.45", 1.0),
+    ("it costs $12.50", "12.5", 1.0),
+    ("\\boxed{12 \\text{ cm}}", "12", 1.0),
+    ("\\boxed{(1, 2)}", "(1,2)", 1.0),
+    ("\\boxed{\\{3, 1\\}}".replace("\\{", "{").replace("\\}", "}"), "{1, 3}", 1.0),
+    ("\\boxed{x^2+1}", "x^2 + 1", 1.0),
+    ("\\boxed{2\\pi}", "6.283185", 1.0),
+    ("the result is 7", "8", 0.0),
+    ("\\boxed{(1, 3)}", "(1,2)", 0.0),
+    ("no number here", "5", 0.0),
+    ("\\boxed{3.14159}", "3.14160", 0.0),
+    ("1e3", "1000", 1.0),
+])
+def test_math_verifier_equivalences(resp, gold, want):
+    from areal_b200.reward import get_math_verify_worker
+
+    assert get_math_verify_worker().verify(resp, gold) == want
+
+
+def test_named_dataset_rewards():
+    from areal_b200.reward import MathVerifyWorker, clevr_count_70k_reward_fn, geometry3k_reward_fn, gsm8k_reward_fn, math_verify_reward_fn
+    from areal_b200.reward.math_verify import last_boxed
+
+    assert last_boxed("a \\boxed{1} b \\boxed{\\frac{a}{b{c}}} c") == "\\frac{a}{b{c}}" and last_boxed("\\boxed{unclosed") is None
+    assert geometry3k_reward_fn("", "angle is [45]", [], [], answer="45") == 1.0
+    assert geometry3k_reward_fn("", "i think 44.9", [], [], answer="[45]") == 0.0
+    assert clevr_count_70k_reward_fn("", "there are [3] cubes", [], [], answer="3") == 1.0
+    assert clevr_count_70k_reward_fn("", "maybe four", [], [], answer="4") == 0.0
+    assert math_verify_reward_fn("", "x = \\boxed{-\\frac{1}{2}}", [], [], answer="-0.5") == 1.0
+    assert gsm8k_reward_fn("", "... #### 72", [], [], answer="blah #### 72") == 1.0
+    strict = MathVerifyWorker(try_extract_without_anchor=False)
+    assert strict.verify("the number 5 appears", "5") == 0.0 and strict.verify("answer: 5", "5") == 1.0

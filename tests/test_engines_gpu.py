@@ -527,7 +527,7 @@ def test_engine_offload_returns_the_kv_pool_and_keeps_its_graphs():
     cfg = preset("tiny-qwen3")
     model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=21)
     ic = NativeInferConfig(max_running_requests=8, page_size=16, context_length=256, pausable_kv_cache=True)
-    ic.num_pages = 4096                                     # 4096 x 16 tokens x 4 layers x 2 x 2 kv heads x 64 x 2 B = 134 MB
+    ic.num_pages = 4096                                     # 4096 x 16 tokens x 2 layers x 2 (K, V) x 2 kv heads x 64 x 2 B = 64 MiB
     eng = NativeInferenceEngine(InferenceEngineConfig(), ic, model=model, eos_token_id=None).initialize(device="cuda", start_executor=False)
     g = GenerationHyperparameters(max_new_tokens=16, max_tokens=200, greedy=True, ignore_eos=True)
 
@@ -540,7 +540,7 @@ def test_engine_offload_returns_the_kv_pool_and_keeps_its_graphs():
     free0, _ = torch.cuda.mem_get_info()
     eng.offload()
     free1, _ = torch.cuda.mem_get_info()
-    assert free1 - free0 > 100 << 20
+    assert free1 - free0 > 48 << 20
     eng.onload()
     again = asyncio.run(run())
     assert [r.output_tokens for r in again] == [r.output_tokens for r in first]

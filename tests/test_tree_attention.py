@@ -136,7 +136,7 @@ def test_tree_training_on_the_flash_kernels_matches_the_plain_packed_forward():
         model.zero_grad()
         if tree:
             h, saving = tree_hidden_for_packed_batch(model, ids, cu, pad_to=128)
-            assert saving > 0.5
+            assert saving > 0.4
         else:
             h = model(ids, cu, max_seqlen=600)
         (h.float() * w).pow(2).mean().backward()
