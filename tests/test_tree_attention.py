@@ -121,17 +121,28 @@ def test_engine_trains_the_same_with_and_without_prefix_sharing():
 @pytest.mark.gpu
 def test_tree_training_on_the_flash_kernels_matches_the_plain_packed_forward():
     """bf16 model on the device: hidden states and parameter gradients of a batch whose groups share long prompts,
-    computed over the trie (flash kernels on the gathered layout), against the plain packed forward + backward."""
+    computed over the trie (flash kernels on the gathered layout) and by the plain packed forward + backward, both
+    judged against an fp32 oracle on the host: the trie path is no further from fp32 than bf16 rounding puts the
+    plain path (the loss sits behind a norm, so several gradients are sums of nearly cancelling terms)."""
     cfg = preset("tiny-qwen3")
     model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=7)
+    oracle = build_model(cfg, dtype=torch.float32, device="cpu", seed=7)
+    with torch.no_grad():
+        for p, q in zip(model.parameters(), oracle.parameters()):
+            q.copy_(p.float().cpu())
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(1, cfg.vocab_size, (n,), generator=g).tolist() for n in (300, 170)]
     seqs = [p + torch.randint(1, cfg.vocab_size, (n,), generator=g).tolist() for p in prompts for n in (90, 260, 33, 140)]
-    ids = torch.tensor([t for s in seqs for t in s], device="cuda", dtype=torch.int32)
-    cu = torch.tensor([0] + [len(s) for s in seqs]).cumsum(0).to(torch.int32).cuda()
-    w = torch.linspace(0.5, 1.5, ids.numel(), device="cuda")[:, None]
-    grads = []
-    outs = []
+    flat = [t for s in seqs for t in s]
+    cu_host = torch.tensor([0] + [len(s) for s in seqs]).cumsum(0).to(torch.int32)
+    ids, cu = torch.tensor(flat, device="cuda", dtype=torch.int32), cu_host.cuda()
+    w = torch.linspace(0.5, 1.5, len(flat))[:, None]
+    ho = oracle(torch.tensor(flat), cu_host, max_seqlen=600)
+    (ho * w).pow(2).mean().backward()
+    named = [n for n, p in oracle.named_parameters() if p.grad is not None]
+    want = {n: p.grad for n, p in oracle.named_parameters() if p.grad is not None}
+    rel = lambda a, b: ((a - b).norm() / b.norm().clamp(min=1e-12)).item()   # noqa: E731
+    errs = {}
     for tree in (False, True):
         model.zero_grad()
         if tree:
@@ -139,9 +150,10 @@ def test_tree_training_on_the_flash_kernels_matches_the_plain_packed_forward():
             assert saving > 0.4
         else:
             h = model(ids, cu, max_seqlen=600)
-        (h.float() * w).pow(2).mean().backward()
-        outs.append(h.detach().float())
-        grads.append([p.grad.detach().float().clone() for p in model.parameters() if p.grad is not None])
-    rel = lambda a, b: ((a - b).norm() / b.norm().clamp(min=1e-12)).item()   # noqa: E731
-    assert rel(outs[1], outs[0]) < 2e-2
-    assert len(grads[0]) == len(grads[1]) and max(rel(a, b) for a, b in zip(grads[1], grads[0])) < 5e-2
+        (h.float() * w.cuda()).pow(2).mean().backward()
+        got = {n: p.grad.float().cpu() for n, p in model.named_parameters() if p.grad is not None}
+        assert sorted(got) == sorted(named)
+        errs[tree] = (rel(h.detach().float().cpu(), ho.detach()), {n: rel(got[n], want[n]) for n in named})
+    assert errs[True][0] < max(2e-2, 2 * errs[False][0])
+    worst = {n: (errs[True][1][n], errs[False][1][n]) for n in named if errs[True][1][n] > max(5e-2, 3 * errs[False][1][n])}
+    assert not worst, worst
