@@ -268,6 +268,24 @@ class RejectionSamplingConfig:
             raise ValueError("rejection_sampling.agg must be sum|mean|max")
         if self.upper is None and self.lower is None:
             raise ValueError("rejection sampling needs at least one bound")
+        if self.action == "clamp":
+            if self.metric != "ratio":
+                raise ValueError("action='clamp' only supports metric='ratio' (a divergence cannot be truncated into a weight)")
+            if self.lower is None:
+                self.lower = 0.0
+        if self.metric == "ratio":
+            if self.upper is not None and self.upper <= 1.0:
+                raise ValueError("ratio metric: upper must be > 1.0 (an on-policy token has ratio 1)")
+            if self.lower is not None and (self.lower < 0.0 or (self.lower == 0.0 and self.action == "mask")):
+                raise ValueError("ratio metric: lower must be positive")
+        elif self.metric in ("kl_k2", "kl_k3", "binary_kl") and self.upper is not None and self.upper <= 0.0:
+            raise ValueError(f"{self.metric}: upper must be positive (the estimator is non-negative)")
+        if self.lower is not None and self.upper is not None and self.lower > self.upper:
+            raise ValueError("rejection sampling: lower must not exceed upper")
+        if self.level == "token" and self.agg != "mean":
+            import warnings
+
+            warnings.warn(f"rejection_sampling.agg='{self.agg}' is ignored at token level", UserWarning, stacklevel=2)
 
 
 @dataclass
