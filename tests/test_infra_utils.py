@@ -37,8 +37,8 @@ def test_name_resolve_backends(tmp_path, kind):
     sub = name_resolve.add_subentry("a/servers", "h:1")
     assert name_resolve.get(sub) == "h:1"
     repo.reset()
-    with pytest.raises(RuntimeError):
-        name_resolve.reconfigure(type="etcd3")
+    with pytest.raises(ValueError, match="unknown name_resolve backend"):
+        name_resolve.reconfigure(type="zookeeper")
     name_resolve.reconfigure(type="memory")
 
 

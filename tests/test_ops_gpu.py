@@ -659,3 +659,42 @@ def test_gemm_2sm_pair_kernel_matches_fp32(M, N, K, layout):
         assert oplib.kernel_error() == 0
     finally:
         OF.GEMM_2SM = old
+
+
+@pytest.mark.parametrize("cp,D,Hq,Hkv", [(2, 128, 8, 2), (4, 64, 4, 4)])
+def test_context_parallel_blockwise_attention_on_flash_kernels(cp, D, Hq, Hkv):
+    """Zig-zag context parallelism with emulated ranks on one device: every rank's chunk-pair calls of the flash
+    kernels, merged through their log-sum-exp, give causal attention over the whole sequences; the per-rank
+    gradient contributions add up to the gradients of the unsplit attention."""
+    from areal_b200.parallel import cp as CP
+
+    torch.manual_seed(cp + D)
+    lens = [700, 1130, 64, 333]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    T = int(cu[-1])
+    q = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(T, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(T, Hkv, D, device="cuda").bfloat16()
+    do = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    scale = D ** -0.5
+    o_ref, lse_ref = OF.attention_ref(q, k, v, cu.cuda(), True, scale)
+    dq_ref, dk_ref, dv_ref = OF.attention_bwd_ref(q, k, v, o_ref, lse_ref, do, cu.cuda(), True, scale)
+    parts = [[CP.zigzag_split(t, cu, cp, r) for r in range(cp)] for t in (q, k, v, do)]
+    k_all, v_all = torch.stack(parts[1]), torch.stack(parts[2])
+    dk_sum, dv_sum = torch.zeros_like(k_all, dtype=torch.float32), torch.zeros_like(v_all, dtype=torch.float32)
+    for r in range(cp):
+        src, _, local_lens = CP.zigzag_indices(cu, cp, r)
+        valid = (src >= 0).cuda()
+        o, lse = CP.cp_block_forward(parts[0][r], k_all, v_all, local_lens, r, scale)
+        want = CP.zigzag_split(o_ref, cu, cp, r)
+        assert _rel_err(o[valid], want[valid]) < 1e-2
+        dq, dk_c, dv_c = CP.cp_block_backward(parts[0][r], k_all, v_all, o, lse, parts[3][r], local_lens, r, scale)
+        assert _rel_err(dq[valid], CP.zigzag_split(dq_ref, cu, cp, r)[valid]) < 2e-2
+        dk_sum += dk_c
+        dv_sum += dv_c
+    _no_kernel_error()
+    for r in range(cp):
+        src, _, _ = CP.zigzag_indices(cu, cp, r)
+        valid = (src >= 0).cuda()
+        assert _rel_err(dk_sum[r][valid], CP.zigzag_split(dk_ref, cu, cp, r)[valid]) < 2e-2
+        assert _rel_err(dv_sum[r][valid], CP.zigzag_split(dv_ref, cu, cp, r)[valid]) < 2e-2
