@@ -431,7 +431,15 @@ class B200TrainEngine(TrainEngine):
                 self.expert_optimizer = ShardedAdamW(self.expert_store, cfg.optimizer, total_steps=total, group=self._edp_group)
         if self.sp_size * tp > 1 and model_config.is_vlm:
             raise NotImplementedError("vision-language models run data-parallel only (no sequence / tensor parallelism yet)")
-        if self.sp_size > 1:
+        self._cp_zigzag = self.sp_size > 1 and getattr(cfg.fsdp, "context_parallel", "ulysses") == "zigzag"
+        self._zz_perm = None
+        if getattr(cfg.fsdp, "context_parallel", "ulysses") not in ("ulysses", "zigzag"):
+            raise ValueError("fsdp.context_parallel must be ulysses or zigzag")
+        if self._cp_zigzag:
+            self._sp_fused = None
+            if tp > 1 or getattr(self, "pp_size", 1) > 1:
+                raise NotImplementedError("zig-zag context parallelism combines with data parallelism only")
+        elif self.sp_size > 1:
             from ..parallel.ulysses import install_ulysses
 
             install_ulysses(self.model, self._sp_group, self.sp_size, self.sp_rank)
@@ -617,6 +625,8 @@ class B200TrainEngine(TrainEngine):
             self._tree_saving = saving
             stats_tracker.scalar(tree_token_saving=saving)
             return hidden, labels, slice(0, T)
+        if self.sp_size > 1 and self._cp_zigzag:
+            return self._forward_mb_zigzag(ids, labels, cu, T)
         if self.sp_size > 1:
             chunk = T // self.sp_size
             sl = slice(self.sp_rank * chunk, (self.sp_rank + 1) * chunk)
@@ -635,6 +645,39 @@ class B200TrainEngine(TrainEngine):
         else:
             hidden = self.model.forward_hidden(ids, pb)
         return hidden, labels, slice(0, T)
+
+    def _forward_mb_zigzag(self, ids, labels, cu, T):
+        """Context parallelism by sequence chunks: every sequence is cut into ``2 * cp`` chunks, this rank runs the
+        layers on chunks ``r`` and ``2 cp - 1 - r`` of every sequence and attends to the gathered keys / values chunk
+        pair by chunk pair (``parallel/cp.py``). Per-token outputs are gathered and put back into the packed order
+        by :meth:`_sp_gather`, so the loss sees whole sequences exactly as under Ulysses."""
+        import math
+
+        from ..parallel import cp as CP
+
+        sp, r = self.sp_size, self.sp_rank
+        cu_host = cu.cpu()
+        src, pos_l, local_lens = CP.zigzag_indices(cu_host, sp, r)
+        T_local = int(src.numel())
+        srcd = src.to(self.device)
+        pad = srcd < 0
+        ids_l = ids[srcd.clamp(min=0)].masked_fill(pad, 0)
+        labels_l = labels[srcd.clamp(min=0)].masked_fill(pad, 0)
+        cu_l = torch.tensor([0] + list(torch.tensor(local_lens).cumsum(0)), dtype=torch.int32, device=self.device)
+        pb_l = PackedBatch(cu_l, pos_l.to(self.device).int(), T_local, max(CP.padded_lengths(cu_host, sp)))
+        scale = 1.0 / math.sqrt(self.model.cfg.head_dim)
+        group = self._sp_group
+
+        def attn(q, k, v):
+            return CP.cp_attention(q, k, v, cu_host, sp, r, group, scale)
+        hidden = self.model.forward_hidden(ids_l, pb_l, attn_fns=[attn] * len(self.model.layers))
+        perm = torch.full((T,), -1, dtype=torch.long)
+        for peer in range(sp):
+            s_p = src if peer == r else CP.zigzag_indices(cu_host, sp, peer)[0]
+            ok = s_p >= 0
+            perm[s_p[ok]] = (peer * T_local + torch.arange(T_local))[ok]
+        self._zz_perm = perm.to(self.device)
+        return hidden, labels_l, slice(0, T_local)
 
     # ------------------------------------------------------------------ train / eval / forward
     def optimizer_zero_grad(self):
@@ -711,7 +754,15 @@ class B200TrainEngine(TrainEngine):
     def _sp_gather(self, t: torch.Tensor) -> torch.Tensor:
         if self.sp_size <= 1:
             return t
-        return _GatherOverSP.apply(t, self._sp_group, self.sp_rank, self.sp_size)
+        full = _GatherOverSP.apply(t, self._sp_group, self.sp_rank, self.sp_size)
+        return self._sp_restore(full)
+
+    def _sp_restore(self, full: torch.Tensor) -> torch.Tensor:
+        """Rank-major concatenation of the ranks' local outputs -> packed order of the micro-batch (the identity
+        under Ulysses, whose ranks hold consecutive slices)."""
+        if getattr(self, "_cp_zigzag", False) and self._zz_perm is not None:
+            return full.index_select(0, self._zz_perm)
+        return full
 
     def _actor_outputs(self, hidden, labels, temperature=None):
         t = self.config.temperature if temperature is None else temperature
@@ -978,7 +1029,7 @@ class B200TrainEngine(TrainEngine):
                 for r in res:
                     parts = [torch.empty_like(r) for _ in range(self.sp_size)]
                     dist.all_gather(parts, r.contiguous(), group=self._sp_group)
-                    full.append(torch.cat(parts))
+                    full.append(self._sp_restore(torch.cat(parts)))
                 res = tuple(full)
             host = tuple(D.unpad_logits(r, pad).float().cpu() for r in res)
             self.d2h_bytes += sum(h.numel() * 4 for h in host)

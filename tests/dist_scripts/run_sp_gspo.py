@@ -1,4 +1,5 @@
-"""GSPO (sequence-level importance ratios) under Ulysses sp=2 equals the single-rank result."""
+"""GSPO (sequence-level importance ratios) under sequence parallelism over all ranks (Ulysses, or zig-zag context
+parallelism with AREAL_TEST_CP_MODE=zigzag) equals the single-rank result."""
 import os, sys
 sys.path.insert(0, os.getcwd())
 os.environ["AREAL_FORCE_CPU"] = "1"
@@ -13,6 +14,7 @@ def run(sp):
     cfg = PPOActorConfig(init_from_scratch=True, dtype="float32", optimizer=OptimizerConfig(lr=1e-3, gradient_clipping=1.0),
                          mb_spec=MicroBatchSpec(max_tokens_per_mb=512), use_decoupled_loss=True, recompute_logprob=True, kl_ctl=0.0,
                          ppo_n_minibatches=1, importance_sampling_level="sequence", prox_logp_method="recompute")
+    cfg.fsdp.context_parallel = os.environ.get("AREAL_TEST_CP_MODE", "ulysses")
     eng = B200PPOActor(cfg)
     if sp == 1:
         eng.set_train_ranks([rank], None)
@@ -32,7 +34,7 @@ def run(sp):
     eng.compute_advantages(data)
     st = eng.ppo_update(data)
     return st[0], eng.store.flat_param[:eng.store.numel].clone() - p0
-s2, p2 = run(2)
+s2, p2 = run(world)
 s1, p1 = run(1)
 assert abs(s1["grad_norm"] - s2["grad_norm"]) < 1e-4 * max(1, s1["grad_norm"]), (s1, s2)
 # Adam divides by sqrt(v): elements whose gradient is numerically zero move by rounding noise, so compare the update as a whole

@@ -3,6 +3,7 @@ import os
 import subprocess
 import sys
 
+import pytest
 import torch
 
 from areal_b200.models.config import preset
@@ -90,3 +91,16 @@ def test_sequence_level_loss_under_ulysses_equals_single_rank():
                        env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("SP_GSPO_OK") == 2
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_zigzag_context_parallel_engine_matches_single_rank(world):
+    """The engine with ``fsdp.context_parallel=zigzag``: sequence chunks per rank, blockwise attention against the
+    gathered keys / values, outputs restored to the packed order before the (sequence-level) loss. Three ranks show
+    that no head count has to divide (the tiny model has 4 query and 2 key / value heads)."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", AREAL_TEST_CP_MODE="zigzag")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+                        "127.0.0.1", "--master-port", str(29985 + world), os.path.join(ROOT, "tests", "dist_scripts", "run_sp_gspo.py")],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("SP_GSPO_OK") == world
