@@ -128,6 +128,8 @@ class FSDPEngineConfig:
     fuse_reduce_scatter_adamw: bool = True   # fused RS + cast/scale + sharded AdamW kernel
     fuse_allgather_gemm: bool = True         # param all-gather fused into the consuming GEMM
     fuse_ulysses_projections: bool = True    # sequence-parallel all-to-alls folded into the QKV / output projection kernels
+    tp_sequence_parallel: bool = False       # tensor parallel with the residual stream split by rows (gather -> GEMM, GEMM -> reduce-scatter)
+    fuse_tp_projections: bool = True         # ... those pairs as one peer-memory kernel each on CUDA
     context_parallel: str = "ulysses"  # ulysses (heads exchanged by all-to-all) | zigzag (sequence chunks, K/V gathered; any head count)
     reduce_in_switch: bool = False           # gradient reduce-scatter by multimem.ld_reduce (NVLS) when a multicast mapping exists
     bucket_mb: int = 256

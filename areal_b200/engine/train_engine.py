@@ -336,7 +336,18 @@ class B200TrainEngine(TrainEngine):
             self.local_model_config = TP.local_config(model_config, tp)
             self.model = build_model(self.local_model_config, dtype=dtype, device=self.device, seed=seed)
             TP.load_sharded_from_full(self.model, model_config, {n_: p_.detach() for n_, p_ in full.named_parameters()}, tp, self.tp_rank)
-            TP.install_tp(self.model, self._tp_group, tp, self.tp_rank)
+            tp_sp = bool(cfg.fsdp.tp_sequence_parallel) and not model_config.is_moe
+            fused_tp = None
+            if tp_sp and self.device.type == "cuda" and cfg.fsdp.fuse_tp_projections and model_config.head_dim in (64, 128):
+                from ..parallel.tp_fused import FusedTPLinear
+
+                unit = 128 * tp
+                max_t = (max(int(cfg.mb_spec.max_tokens_per_mb or 0), unit) + unit - 1) // unit * unit
+                lc = self.local_model_config
+                widest = max(model_config.hidden_size, 2 * lc.intermediate_size, (lc.num_heads + 2 * lc.num_kv_heads) * lc.head_dim)
+                fused_tp = FusedTPLinear(self._tp_group, self.device, max_t // tp, widest, widest)
+            self._tp_fused = fused_tp
+            TP.install_tp(self.model, self._tp_group, tp, self.tp_rank, sequence_parallel=tp_sp, fused=fused_tp)
             del full
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
@@ -572,6 +583,10 @@ class B200TrainEngine(TrainEngine):
         base = D.N_TOKENS_PER_PAGE if self.device.type == "cuda" else 1
         if getattr(self, "_sp_fused", None) is not None:
             return max(base, 128 * self.sp_size)   # the fused projections work on 128-row blocks per rank
+        if getattr(self.model, "tp_sequence_parallel", False):
+            import math
+
+            return math.lcm(base, (128 if getattr(self, "_tp_fused", None) is not None else 1) * self.tp_size)
         return base * self.sp_size if self.sp_size > 1 and base % self.sp_size else max(base, self.sp_size)
 
     def _prepare_mb_list(self, input_: dict[str, Any]) -> D.MicroBatchList:
@@ -627,6 +642,12 @@ class B200TrainEngine(TrainEngine):
             return hidden, labels, slice(0, T)
         if self.sp_size > 1 and self._cp_zigzag:
             return self._forward_mb_zigzag(ids, labels, cu, T)
+        if self.sp_size == 1 and getattr(self.model, "tp_sequence_parallel", False):
+            # the layers keep this rank's rows of the residual stream; attention sees all tokens (its heads)
+            chunk = T // self.tp_size
+            sl = slice(self.tp_rank * chunk, (self.tp_rank + 1) * chunk)
+            hidden = self.model.forward_hidden(ids[sl], pb)
+            return hidden, labels[sl], sl
         if self.sp_size > 1:
             chunk = T // self.sp_size
             sl = slice(self.sp_rank * chunk, (self.sp_rank + 1) * chunk)
@@ -751,7 +772,19 @@ class B200TrainEngine(TrainEngine):
                 out[k] = v
         return out
 
+    def _row_split(self):
+        """(group, size, rank) over which a micro-batch's tokens are split by rows: the Ulysses / context-parallel
+        group, or the tensor-parallel group when its residual stream is sequence parallel; size 1 otherwise."""
+        if self.sp_size > 1:
+            return self._sp_group, self.sp_size, self.sp_rank
+        if getattr(self.model, "tp_sequence_parallel", False):
+            return self._tp_group, self.tp_size, self.tp_rank
+        return None, 1, 0
+
     def _sp_gather(self, t: torch.Tensor) -> torch.Tensor:
+        g, n, r = self._row_split()
+        if self.sp_size <= 1 and n > 1:
+            return _GatherOverSP.apply(t, g, r, n)
         if self.sp_size <= 1:
             return t
         full = _GatherOverSP.apply(t, self._sp_group, self.sp_rank, self.sp_size)
@@ -1024,11 +1057,12 @@ class B200TrainEngine(TrainEngine):
             else:
                 logp, ent = self._actor_outputs(hidden, labels, temperature)
                 res = (logp, ent) if output == "logprobs_entropy" else ((ent,) if output == "entropy" else (logp,))
-            if self.sp_size > 1:
+            row_group, row_n, _ = self._row_split()
+            if row_n > 1:
                 full = []
                 for r in res:
-                    parts = [torch.empty_like(r) for _ in range(self.sp_size)]
-                    dist.all_gather(parts, r.contiguous(), group=self._sp_group)
+                    parts = [torch.empty_like(r) for _ in range(row_n)]
+                    dist.all_gather(parts, r.contiguous(), group=row_group)
                     full.append(self._sp_restore(torch.cat(parts)))
                 res = tuple(full)
             host = tuple(D.unpad_logits(r, pad).float().cpu() for r in res)

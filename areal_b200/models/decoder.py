@@ -48,6 +48,17 @@ def _lin(mod, name: str, x: torch.Tensor, resid: Optional[torch.Tensor] = None) 
         # tensor-parallel inference: the partial product goes straight into every rank's receive
         # slots from the GEMM epilogue; the caller gets a handle that the next norm kernel sums
         return ex.linear_bcast(x if x.stride(-1) == 1 else x.contiguous(), getattr(mod, name))
+    sp = getattr(mod, "tp_sp", None)
+    if sp is not None:
+        # tensor parallel with the residual stream split by rows: gather rows -> product, product -> reduce-scatter rows
+        from ..parallel.tp import column_parallel_sp, row_parallel_sp
+
+        if getattr(mod, "lora", None) is not None or getattr(mod, "use_fp8", False):
+            raise NotImplementedError("LoRA / fp8 projections with sequence-parallel tensor parallelism")
+        if name in ("qkv_proj", "gate_up_proj"):
+            return column_parallel_sp(x, getattr(mod, name), sp[0], sp[1])
+        y = row_parallel_sp(x if x.stride(-1) == 1 else x.contiguous(), getattr(mod, name), sp[0], sp[1])
+        return y + resid if resid is not None else y
     if getattr(mod, "use_fp8", False):
         # block-scaled e4m3 operands in forward and input gradient, fp32 accumulation
         y = OF.fp8_linear(x, getattr(mod, name))
@@ -79,9 +90,9 @@ class Attention(nn.Module):
 
     def project_qkv(self, x: torch.Tensor, pb_positions: torch.Tensor, cos, sin):
         """Returns q [T,nq,D], k [T,nkv,D], v [T,nkv,D] with QK-norm and RoPE applied."""
-        T = x.shape[0]
         D, nq, nkv = self.D, self.nq, self.nkv
         qkv = _lin(self, "qkv_proj", x)
+        T = qkv.shape[0]               # all tokens, also when x holds this rank's rows only (sequence-parallel TP)
         if self.qkv_bias is not None:
             qkv = qkv + self.qkv_bias
         if qkv.is_cuda and not torch.is_grad_enabled() and D in (64, 128):
@@ -107,7 +118,7 @@ class Attention(nn.Module):
                 qkv = qkv + self.qkv_bias
             o = OF.qknorm_rope_attention(qkv, self.q_norm, self.k_norm, pb.position_ids, cos, sin, pb.cu_seqlens, self.nq,
                                          self.nkv, self.D, self.cfg.rms_norm_eps, 1.0 / math.sqrt(self.D), pb.tile_info)
-            return _lin(self, "o_proj", o.reshape(T, self.nq * self.D))
+            return _lin(self, "o_proj", o.reshape(qkv.shape[0], self.nq * self.D))
         if attn_fn is None and getattr(self, "sp_fused", None) is not None and x.is_cuda:
             from ..parallel.ulysses import fused_ulysses_attention_block
 
@@ -122,7 +133,7 @@ class Attention(nn.Module):
         else:
             o = OF.attention(q, k.contiguous() if not k.is_cuda else k, v.contiguous() if not v.is_cuda else v,
                              pb.cu_seqlens, True, 1.0 / math.sqrt(self.D), pb.tile_info)
-        return _lin(self, "o_proj", o.reshape(T, self.nq * self.D))
+        return _lin(self, "o_proj", o.reshape(o.shape[0], self.nq * self.D))
 
 
 class DenseMLP(nn.Module):

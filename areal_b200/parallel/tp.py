@@ -131,12 +131,25 @@ def reduce_from_tp(x, group):
     return _ReduceFromTP.apply(x, group) if group is not None else x
 
 
-def install_tp(model, group, tp_size: int, tp_rank: int):
-    """Marks every decoder layer of a rank-local model as tensor parallel (the layer's forward
-    then brackets attention and MLP with the conjugate pair)."""
+def install_tp(model, group, tp_size: int, tp_rank: int, sequence_parallel: bool = False, fused=None):
+    """Marks every decoder layer of a rank-local model as tensor parallel. Default: the layer's forward brackets
+    attention and MLP with the conjugate pair (identity / all-reduce) and every rank carries all tokens.
+    ``sequence_parallel``: the residual stream is split by rows over the group as well (each rank holds ``T / P``
+    tokens between the blocks; norms, residual adds and the LM head run on local rows only); the QKV and gate/up
+    projections gather the rows in front of their product and the output / down projections reduce-scatter their
+    result, as ONE kernel each when ``fused`` (a ``tp_fused.FusedTPLinear``) is given. Reference: Megatron's
+    sequence-parallel linear layers, which ``areal/engine/megatron_engine.py`` turns on with tensor parallelism."""
+    on = tp_size > 1
     for layer in model.layers:
-        layer.tp_group = group if tp_size > 1 else None
-    model.tp_group, model.tp_size, model.tp_rank = (group if tp_size > 1 else None), tp_size, tp_rank
+        if sequence_parallel and on:
+            if type(layer.mlp).__name__ != "DenseMLP":
+                raise NotImplementedError("sequence-parallel tensor parallelism covers dense MLP layers")
+            layer.tp_group = None
+            layer.self_attn.tp_sp = layer.mlp.tp_sp = (group, fused)
+        else:
+            layer.tp_group = group if on else None
+    model.tp_group, model.tp_size, model.tp_rank = (group if on else None), tp_size, tp_rank
+    model.tp_sequence_parallel = bool(sequence_parallel and on)
     return model
 
 
@@ -161,9 +174,11 @@ def allreduce_replicated_grads(model, group, grad_of=lambda p: getattr(p, "main_
     if group is None:
         return
     params = dict(model.named_parameters())
+    # with the residual stream split by rows every replicated parameter saw only this rank's tokens (or heads)
+    all_partial = getattr(model, "tp_sequence_parallel", False)
     for n in replicated_parameter_names(model):
         leaf = n.rsplit(".", 1)[-1]
-        if leaf in ("q_norm", "k_norm", "router"):
+        if all_partial or leaf in ("q_norm", "k_norm", "router"):
             g = grad_of(params[n])
             if g is not None:
                 dist.all_reduce(g, group=group)
@@ -204,6 +219,32 @@ def _rs_rows(x, group):
     return x.chunk(P, 0)[r].clone()
 
 
+def _mm(a, b, b_mn: bool = False):
+    """``a @ b^T`` (``b_mn``: ``a @ b``): the library GEMM on CUDA, plain matmul in the tensors' precision elsewhere."""
+    if a.is_cuda:
+        from ..ops import functional as OF
+
+        return OF.gemm(a, b, b_mn=b_mn)
+    return a @ (b if b_mn else b.t())
+
+
+def _wgrad(w, dy_full, x_full):
+    """dW = dy^T x, accumulated in fp32 into ``w.main_grad`` when the parameter carries one (returns None then)."""
+    from ..ops import functional as OF
+
+    mg = getattr(w, "main_grad", None)
+    if not dy_full.is_cuda:
+        g = dy_full.t() @ x_full
+        if mg is not None:
+            mg.add_(g.to(mg.dtype))
+            return None
+        return g
+    if mg is not None:
+        OF.gemm(dy_full, x_full, a_mn=True, b_mn=True, out=mg, epi=OF.EPI_F32_ACC)
+        return None
+    return OF.gemm(dy_full, x_full, a_mn=True, b_mn=True)
+
+
 class _ColumnParallelSP(torch.autograd.Function):
     """``y[T, N/P] = gather_rows(x[T/P, K]) @ W[N/P, K]^T``."""
 
@@ -213,7 +254,7 @@ class _ColumnParallelSP(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         if fused is not None and x.is_cuda:
             return fused.allgather_gemm(x, w)
-        return _ag_rows(x, group) @ w.t()
+        return _mm(_ag_rows(x, group), w)
 
     @staticmethod
     def backward(ctx, dy):
@@ -223,8 +264,8 @@ class _ColumnParallelSP(torch.autograd.Function):
         if fused is not None and dy.is_cuda:
             dx = fused.gemm_reduce_scatter(dy, w, b_mn=True)           # rows of dy @ W that this rank owns
         else:
-            dx = _rs_rows(dy @ w, g)
-        dw = dy.t() @ _ag_rows(x, g) if ctx.needs_input_grad[1] else None
+            dx = _rs_rows(_mm(dy, w, b_mn=True), g)
+        dw = _wgrad(w, dy, _ag_rows(x, g)) if ctx.needs_input_grad[1] else None
         return dx, dw, None, None
 
 
@@ -237,7 +278,7 @@ class _RowParallelSP(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         if fused is not None and x.is_cuda:
             return fused.gemm_reduce_scatter(x, w)
-        return _rs_rows(x @ w.t(), group)
+        return _rs_rows(_mm(x, w), group)
 
     @staticmethod
     def backward(ctx, dy):
@@ -249,11 +290,11 @@ class _RowParallelSP(torch.autograd.Function):
             dy_full = None
         else:
             dy_full = _ag_rows(dy, g)
-            dx = dy_full @ w
+            dx = _mm(dy_full, w, b_mn=True)
         dw = None
         if ctx.needs_input_grad[1]:
             dy_full = dy_full if dy_full is not None else _ag_rows(dy, g)
-            dw = dy_full.t() @ x
+            dw = _wgrad(w, dy_full, x)
         return dx, dw, None, None
 
 

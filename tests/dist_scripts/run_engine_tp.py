@@ -40,6 +40,12 @@ def make_batch(vocab):
 
 
 def cfg_of(backend):
+    c = _cfg_of(backend)
+    c.fsdp.tp_sequence_parallel = os.environ.get("AREAL_TEST_TP_SP", "0") == "1"
+    return c
+
+
+def _cfg_of(backend):
     return TrainEngineConfig(init_from_scratch=True, dtype="float32", backend=backend, optimizer=OptimizerConfig(lr=1e-2, gradient_clipping=0.5),
                              mb_spec=MicroBatchSpec(max_tokens_per_mb=64))
 
@@ -51,6 +57,7 @@ def main():
     eng = B200TrainEngine(cfg_of("d2t2"))
     eng.create_process_group()
     eng.initialize(model_config=mc, seed=5)
+    assert getattr(eng.model, "tp_sequence_parallel", False) == (os.environ.get("AREAL_TEST_TP_SP", "0") == "1")
     assert (eng.dp_size, eng.tp_size, eng.sp_size) == (2, 2, 1) and eng.tp_rank == rank % 2 and eng.dp_rank == rank // 2
     assert eng.is_data_parallel_head() == (rank % 2 == 0) and eng.current_data_parallel_head() == (rank // 2) * 2
     batch = make_batch(mc.vocab_size)
