@@ -97,3 +97,13 @@ def test_engine_pipeline_zero_bubble_matches_1f1b_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_pp_gpu.py"), 2, 29791, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("ENGINE_PP_GPU_OK") == 2
+
+
+def test_engine_tensor_parallel_sequence_parallel_fused_two_gpus():
+    """``native:d1t2`` train engine in bf16 with the residual stream split by rows: fused gather->GEMM /
+    GEMM->reduce-scatter kernels and their NCCL form reproduce losses and gradient norms of all-reduce tensor
+    parallelism over three optimizer steps."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_tp_sp_gpu.py"), 2, 29793, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("ENGINE_TP_SP_GPU_OK") == 2
