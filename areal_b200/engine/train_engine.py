@@ -293,8 +293,10 @@ class B200TrainEngine(TrainEngine):
         seed = kwargs.get("seed", 1)
         t0 = time.time()
         tp = getattr(self, "tp_size", 1)
-        if getattr(model_config, "is_hybrid", False) and (tp > 1 or getattr(self, "sp_size", 1) > 1 or getattr(self, "pp_size", 1) > 1):
-            raise NotImplementedError("linear-attention (hybrid) models train data-parallel only: no tensor / sequence / pipeline split yet")
+        if getattr(model_config, "is_hybrid", False) and (tp > 1 or getattr(self, "pp_size", 1) > 1):
+            raise NotImplementedError("linear-attention (hybrid) models train with data and Ulysses sequence parallelism: no tensor / pipeline split yet")
+        if getattr(model_config, "is_hybrid", False) and getattr(cfg.fsdp, "context_parallel", "ulysses") != "ulysses" and getattr(self, "sp_size", 1) > 1:
+            raise NotImplementedError("hybrid models split sequences by heads (Ulysses); the delta rule needs whole sequences")
         has_ckpt = (not cfg.init_from_scratch and cfg.path and os.path.isdir(cfg.path)
                     and any(f.endswith(".safetensors") for f in os.listdir(cfg.path)))
         if getattr(self, "pp_size", 1) > 1:
@@ -456,7 +458,7 @@ class B200TrainEngine(TrainEngine):
             install_ulysses(self.model, self._sp_group, self.sp_size, self.sp_rank)
             self._sp_fused = None
             mc = model_config
-            if (on_gpu and cfg.fsdp.fuse_ulysses_projections and not self.use_lora and tp == 1 and self.sp_size <= 8
+            if (on_gpu and cfg.fsdp.fuse_ulysses_projections and not self.use_lora and tp == 1 and self.sp_size <= 8 and not getattr(mc, "is_hybrid", False)
                     and mc.num_heads % sp == 0 and mc.num_kv_heads % sp == 0 and not mc.attention_bias and mc.head_dim in (64, 128)
                     and ((mc.num_heads + 2 * mc.num_kv_heads) // sp * mc.head_dim) % 64 == 0):
                 from ..parallel.tp_fused import FusedUlyssesLinear

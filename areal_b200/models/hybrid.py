@@ -186,16 +186,46 @@ class GatedDeltaNet(nn.Module):
         g = -self.A_log.float().exp() * F.softplus(ba[:, self.nv:] + self.dt_bias.float())
         return OF.linear(x, self.in_proj_qkv), OF.linear(x, self.in_proj_z), beta, g
 
-    def _heads(self, mixed: torch.Tensor):
-        """Post-convolution q|k|v [T, C] -> unit-norm q, k [T, nv, dk] and v [T, nv, dv] (fp32)."""
+    def _heads(self, mixed: torch.Tensor, nk: Optional[int] = None, nv: Optional[int] = None):
+        """Post-convolution q|k|v [T, C] -> unit-norm q, k [T, nv, dk] and v [T, nv, dv] (fp32); ``nk`` / ``nv``:
+        the head counts present in ``mixed`` (a slice of the heads under sequence parallelism)."""
+        nk, nv = nk or self.nk, nv or self.nv
         T = mixed.shape[0]
-        q, k, v = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
-        q = l2norm(q.reshape(T, self.nk, self.dk))
-        k = l2norm(k.reshape(T, self.nk, self.dk))
-        rep = self.nv // self.nk
+        q, k, v = torch.split(mixed, [nk * self.dk, nk * self.dk, nv * self.dv], dim=-1)
+        q = l2norm(q.reshape(T, nk, self.dk))
+        k = l2norm(k.reshape(T, nk, self.dk))
+        rep = nv // nk
         if rep > 1:
             q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
-        return q, k, v.reshape(T, self.nv, self.dv).float()
+        return q, k, v.reshape(T, nv, self.dv).float()
+
+    sp_group = None     # set by parallel.ulysses.install_ulysses: tokens split over the group outside this block
+    sp_size = 1
+    sp_rank = 0
+
+    def _to_heads(self, pre, beta, g):
+        """Sequence-parallel exchange in front of the rule: local rows, all heads -> all rows, this rank's heads
+        (``[t, C] -> [n t, C / n]`` for q | k | v, ``[t, nv] -> [n t, nv / n]`` for beta and g) plus the
+        convolution taps of the local channels. The convolution and the recurrence run along the sequence, so they
+        need whole sequences; heads are independent (role of the cp2hp all-to-all of the reference's linear
+        attention, areal/models/mcore/lightning_attention.py:134-172)."""
+        from ..parallel.ulysses import SeqToHead
+
+        n, r, grp = self.sp_size, self.sp_rank, self.sp_group
+        t = pre.shape[0]
+        q, k, v = torch.split(pre, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        qf = SeqToHead.apply(q.reshape(t, self.nk, self.dk), grp, n)
+        kf = SeqToHead.apply(k.reshape(t, self.nk, self.dk), grp, n)
+        vf = SeqToHead.apply(v.reshape(t, self.nv, self.dv), grp, n)
+        T = qf.shape[0]
+        mixed = torch.cat([qf.reshape(T, -1), kf.reshape(T, -1), vf.reshape(T, -1)], dim=-1)
+        bf = SeqToHead.apply(beta.reshape(t, self.nv, 1), grp, n).reshape(T, -1)
+        gf = SeqToHead.apply(g.reshape(t, self.nv, 1), grp, n).reshape(T, -1)
+        kq, kv_ = self.key_dim // n, self.value_dim // n
+        w = self.conv1d
+        taps = torch.cat([w[r * kq:(r + 1) * kq], w[self.key_dim + r * kq: self.key_dim + (r + 1) * kq],
+                          w[2 * self.key_dim + r * kv_: 2 * self.key_dim + (r + 1) * kv_]], dim=0)
+        return mixed, bf, gf, taps
 
     def _output(self, o: torch.Tensor, z: torch.Tensor, dtype) -> torch.Tensor:
         """Per-head RMSNorm of the rule's output [T, nv, dv] (fp32), gate by silu(z), project back."""
@@ -205,7 +235,7 @@ class GatedDeltaNet(nn.Module):
         return OF.linear(o.to(dtype).reshape(T, self.value_dim), self.out_proj)
 
     def forward(self, x: torch.Tensor, pb) -> torch.Tensor:
-        T = x.shape[0]
+        T = x.shape[0] * (self.sp_size if self.sp_group is not None else 1)      # tokens the rule sees
         max_len = int(pb.max_seqlen) or int((pb.cu_seqlens[1:] - pb.cu_seqlens[:-1]).max())
         key = (T, max_len)
         idx = getattr(pb, "_pad_index", None)
@@ -214,7 +244,11 @@ class GatedDeltaNet(nn.Module):
             pb._pad_index = idx
         gather, scatter, pis = idx[1]
         pre, z, beta, g = self._inputs(x)
-        q, k, v = self._heads(causal_conv_packed(pre, self.conv1d, pis))
+        nk, nv, taps = self.nk, self.nv, self.conv1d
+        if self.sp_group is not None:
+            pre, beta, g, taps = self._to_heads(pre, beta, g)
+            nk, nv = self.nk // self.sp_size, self.nv // self.sp_size
+        q, k, v = self._heads(causal_conv_packed(pre, taps, pis), nk, nv)
 
         def padded(t):                                            # [T, ...] -> [B, max_len, ...]
             zero = torch.zeros((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
@@ -223,7 +257,12 @@ class GatedDeltaNet(nn.Module):
         o, S = gated_delta_rule_chunked(padded(q), padded(k), padded(v), padded(g), padded(beta))
         if self.capture is not None:
             self.capture.append((pre, S))
-        return self._output(o.reshape(-1, self.nv, self.dv)[scatter], z, x.dtype)
+        o = o.reshape(-1, nv, self.dv)[scatter]
+        if self.sp_group is not None:
+            from ..parallel.ulysses import HeadToSeq
+
+            o = HeadToSeq.apply(o.contiguous(), self.sp_group, self.sp_size)      # back to local rows, all heads
+        return self._output(o, z, x.dtype)
 
     def step(self, x: torch.Tensor, conv_state: torch.Tensor, S: torch.Tensor):
         """One new token per sequence: x [B, H], conv_state [B, K-1, C] (the last pre-convolution
@@ -288,6 +327,11 @@ class GatedAttention(nn.Module):
         scale = 1.0 / math.sqrt(D)
         if attn_fn is not None:
             o = attn_fn(q, k, v)
+        elif getattr(self, "sp_size", 1) > 1:
+            from ..parallel.ulysses import ulysses_attention
+
+            impl = OF.attention if (not x.is_cuda or D in (64, 128)) else (lambda q_, k_, v_, cu, causal, sc, ti: sdpa_varlen(q_, k_, v_, cu, sc))
+            o = ulysses_attention(self, q.contiguous(), k.contiguous(), v.contiguous(), pb.cu_seqlens, True, scale, pb.tile_info, impl)
         elif x.is_cuda and D in (64, 128):
             o = OF.attention(q.contiguous(), k.contiguous(), v.contiguous(), pb.cu_seqlens, True, scale, pb.tile_info)
         elif x.is_cuda:

@@ -66,7 +66,12 @@ def install_ulysses(model, group, sp_size: int, sp_rank: int) -> None:
     if nq % sp_size != 0:
         raise ValueError(f"sequence-parallel degree {sp_size} must divide the number of query heads {nq}")
     for layer in model.layers:
-        a = layer.self_attn
+        a = getattr(layer, "self_attn", None)
+        if a is None:
+            # linear-attention layer of a hybrid stack: the same exchange pair around the delta rule
+            a = layer.linear_attn
+            if a.nk % sp_size or a.nv % sp_size:
+                raise ValueError(f"sequence-parallel degree {sp_size} must divide the linear-attention head counts ({a.nk}, {a.nv})")
         a.sp_group, a.sp_size, a.sp_rank = group, sp_size, sp_rank
 
 

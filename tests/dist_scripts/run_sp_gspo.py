@@ -19,7 +19,8 @@ def run(sp):
     if sp == 1:
         eng.set_train_ranks([rank], None)
     eng.create_process_group(FSDPParallelStrategy(data_parallel_size=1, context_parallel_size=sp) if sp > 1 else FSDPParallelStrategy())
-    eng.initialize(model_config=preset("tiny-qwen2", vocab_size=64, num_layers=2), seed=3)
+    name = os.environ.get("AREAL_TEST_MODEL", "tiny-qwen2")
+    eng.initialize(model_config=preset(name, vocab_size=64, **({"num_layers": 2} if name == "tiny-qwen2" else {})), seed=3)
     g = torch.Generator().manual_seed(0)
     B, L = 6, 40
     ids = torch.randint(0, 64, (B, L), generator=g)

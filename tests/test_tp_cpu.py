@@ -107,3 +107,15 @@ def test_zigzag_context_parallel_engine_matches_single_rank(world):
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("SP_GSPO_OK") == world
+
+
+def test_hybrid_linear_attention_stack_under_ulysses_matches_single_rank():
+    """Gated-delta-rule layers under sequence parallelism: local rows -> (all rows, local heads) in front of the causal
+    convolution and the recurrence, back afterwards; the gated full-attention layer uses the same exchange. Update and
+    gradient norm of a sequence-level loss equal the single-rank run."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", AREAL_TEST_MODEL="tiny-qwen3.5")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29991", os.path.join(ROOT, "tests", "dist_scripts", "run_sp_gspo.py")],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("SP_GSPO_OK") == 2
