@@ -322,7 +322,7 @@ class PPOActorConfig(TrainEngineConfig):
     rejection_sampling: Optional[RejectionSamplingConfig] = None
     behave_imp_weight_cap: Optional[float] = None  # legacy alias -> rejection_sampling.upper
     importance_sampling_level: str = "token"  # token | sequence (GSPO)
-    prox_logp_method: str = "recompute"  # recompute | loglinear | linear | reuse_train_logp
+    prox_logp_method: str = "recompute"  # recompute | loglinear | linear | reuse_train_logp | metrics (recompute + approximation errors logged)
     log_agent_stats: bool = False
     log_agent_stats_keys: list[str] = field(default_factory=list)
     max_new_tokens: int = 1024
@@ -339,7 +339,7 @@ class PPOActorConfig(TrainEngineConfig):
             raise ValueError("SAPO loss requires use_decoupled_loss=false")
         if self.use_sapo_loss and self.use_cispo_loss:
             raise ValueError("choose at most one of SAPO / CISPO")
-        if self.prox_logp_method not in ("recompute", "loglinear", "linear", "reuse_train_logp"):
+        if self.prox_logp_method not in ("recompute", "loglinear", "linear", "reuse_train_logp", "metrics"):
             raise ValueError(f"unknown prox_logp_method {self.prox_logp_method}")
         if self.prox_logp_method == "reuse_train_logp" and self.ppo_n_minibatches != 1:
             raise ValueError("prox_logp_method='reuse_train_logp' requires ppo_n_minibatches=1: only then are the update "

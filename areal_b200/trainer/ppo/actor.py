@@ -89,6 +89,8 @@ class PPOActor:
 def resolve_proximal_logp(prox_logp_gt, method: str, old_logp, logprobs, versions, current_version):
     """Which proximal log-probs the loss uses (recomputed forward, an approximation, or the
     training log-probs themselves)."""
+    if method == "metrics":
+        method = "recompute"            # the loss uses the recomputed log-probs; the approximations are only measured
     if method == "reuse_train_logp":
         return logprobs.detach()
     if method in ("loglinear", "linear"):
@@ -159,6 +161,16 @@ def grpo_loss_fn(logprobs: torch.Tensor, entropy: torch.Tensor, input_data: dict
     if "filtered_fraction" in stat:
         stats_tracker.scalar(rs_filtered_fraction=stat["filtered_fraction"])
     versions = input_data.get("versions")
+    if prox_logp_method == "metrics" and versions is not None and current_version is not None and input_data.get("prox_logp") is not None:
+        # how far each approximation of the proximal policy is from the recomputed one, on the trained tokens
+        # (reference: the 'metrics' method of areal/api/cli_args.py:1832-1845 and its logging in the actor)
+        gt = input_data["prox_logp"].float()
+        for name in ("loglinear", "linear"):
+            ap = ADV.compute_prox_logp_approximation(old_logp, logprobs.detach(), versions, current_version, name)
+            err = (ap - gt) * loss_mask
+            stats_tracker.stat(**{f"prox_approx/{name}/abs_error": err.abs(), f"prox_approx/{name}/error": err,
+                                  f"prox_approx/{name}/ratio_error": (torch.exp(err) - 1).abs() * loss_mask},
+                               denominator="n_valid_tokens")
     if versions is not None and current_version is not None:
         m = stat.get("behave_mask", loss_mask) & (versions >= 0)
         stale = (current_version - versions).float()

@@ -138,3 +138,27 @@ def test_actor_skips_the_forward_pass_exactly_when_the_method_needs_none():
         PPOActorConfig(prox_logp_method="guess")
     with pytest.raises(ValueError, match="requires ppo_n_minibatches=1"):
         PPOActorConfig(prox_logp_method="reuse_train_logp", ppo_n_minibatches=4)
+
+
+def test_metrics_method_trains_on_recomputed_log_probs_and_logs_approximation_errors():
+    from areal_b200.utils import stats_tracker
+
+    mb = _mb()
+    lp = (mb["logprobs"] + 0.3).clone().requires_grad_()
+    gt = mb["logprobs"] + 0.12
+    stats_tracker.export_all()                                    # drop what earlier tests left
+    a = grpo_loss_fn(lp, torch.zeros(6), dict(mb, prox_logp=gt), 0.2, None, None, current_version=3, prox_logp_method="metrics",
+                     use_decoupled_loss=True)
+    st = stats_tracker.export_all()
+    b = grpo_loss_fn(lp, torch.zeros(6), dict(mb, prox_logp=gt), 0.2, None, None, current_version=3, prox_logp_method="recompute",
+                     use_decoupled_loss=True)
+    plain = stats_tracker.export_all()
+    assert torch.allclose(a, b)
+    keys = [k for k in st if "prox_approx/" in k]
+    assert any("loglinear/abs_error" in k for k in keys) and any("linear/ratio_error" in k for k in keys)
+    assert not [k for k in plain if "prox_approx/" in k]
+    ll = ADV.compute_prox_logp_approximation(mb["logprobs"], lp.detach(), mb["versions"], 3, "loglinear")
+    m = mb["loss_mask"].bool()
+    want = float(((ll - gt).abs() * m).sum() / m.sum())
+    got = next(v for k, v in st.items() if k.endswith("prox_approx/loglinear/abs_error/avg"))
+    assert got == pytest.approx(want, rel=1e-5)
