@@ -211,7 +211,8 @@ print("SPLIT_OK", split.rank, flush=True)
     (1, 2, 29811, "tiny-qwen2", 1, 1), (2, 4, 29821, "tiny-qwen2", 1, 1), (1, 2, 29831, "tiny-qwen3.5", 1, 1),
     (2, 4, 29841, "tiny-qwen2", 2, 2),        # one Ulysses pair of trainers, one tensor-parallel rollout replica
     (2, 4, 29851, "tiny-qwen2", 1, 2),        # two data-parallel trainers share one tensor-parallel replica
-    (1, 3, 29861, "tiny-qwen2", 1, 1)])       # one trainer merges the batches of two replicas
+    (1, 3, 29861, "tiny-qwen2", 1, 1),        # one trainer merges the batches of two replicas
+    (4, 8, 29871, "tiny-qwen2", 4, 2)])       # the 8-GPU benchmark layout: one Ulysses group of four trainers, two TP = 2 replicas
 def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port, model, sp, rtp):
     script = tmp_path / "split.py"
     script.write_text(SPLIT_SCRIPT % dict(root=ROOT, tmp=str(tmp_path)))
