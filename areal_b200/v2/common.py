@@ -35,6 +35,39 @@ class RequestCtx:
     headers: Any
 
 
+class SSE:
+    """A handler's answer that is streamed as server-sent events over chunked transfer encoding. ``events``
+    yields payload dicts, raw strings (sent as they are, e.g. ``[DONE]``) or ``(event name, payload)`` pairs."""
+
+    def __init__(self, events):
+        self.events = events
+
+
+def sse_lines(url: str, body: dict, api_key: Optional[str] = None, timeout: float = 600.0):
+    """POSTs ``body`` and yields the events of the streamed answer as ``(event name or None, data string)``."""
+    headers = {"Content-Type": "application/json", "Accept": "text/event-stream"}
+    if api_key:
+        headers["Authorization"] = f"Bearer {api_key}"
+    req = urllib.request.Request(url, data=json.dumps(body).encode(), headers=headers, method="POST")
+    try:
+        r = urllib.request.urlopen(req, timeout=timeout)
+    except urllib.error.HTTPError as e:
+        try:
+            msg = json.loads(e.read()).get("error", "")
+        except Exception:
+            msg = ""
+        raise HTTPError(e.code, msg)
+    with r:
+        name = None
+        for raw in r:
+            line = raw.decode().rstrip("\r\n")
+            if line.startswith("event: "):
+                name = line[7:]
+            elif line.startswith("data: "):
+                yield name, line[6:]
+                name = None
+
+
 class JsonService:
     """``svc.route("POST", "/x")(fn)``; path segments ``{name}`` capture into ``ctx.params``."""
 
@@ -93,6 +126,24 @@ class JsonService:
                 self.end_headers()
                 self.wfile.write(b)
 
+            def _stream(self, events):
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Transfer-Encoding", "chunked")
+                self.end_headers()
+                for e in events:
+                    if isinstance(e, tuple) and e[0] is not None:
+                        data = f"event: {e[0]}\ndata: {e[1] if isinstance(e[1], str) else json.dumps(e[1])}\n\n"
+                    else:
+                        if isinstance(e, tuple):
+                            e = e[1]
+                        data = f"data: {e if isinstance(e, str) else json.dumps(e)}\n\n"
+                    raw = data.encode()
+                    self.wfile.write(f"{len(raw):x}\r\n".encode() + raw + b"\r\n")
+                    self.wfile.flush()
+                self.wfile.write(b"0\r\n\r\n")
+
             def _handle(self, method):
                 fn, params = svc._match(method, self.path)
                 if fn is None:
@@ -101,6 +152,8 @@ class JsonService:
                     n = int(self.headers.get("Content-Length", "0"))
                     body = json.loads(self.rfile.read(n)) if n else {}
                     res = fn(body, RequestCtx(self._key(), self.path, params, self.headers))
+                    if isinstance(res, SSE):
+                        return self._stream(res.events)
                     if isinstance(res, tuple):
                         return self._reply(res[0], res[1])
                     return self._reply(200, res if res is not None else {"ok": True})

@@ -82,7 +82,14 @@ class DataProxy:
             s = self._get(ctx.api_key)
             kw = {k: body[k] for k in ("messages", "model", "temperature", "top_p", "max_tokens", "max_completion_tokens", "stop",
                                         "tools", "tool_choice", "frequency_penalty", "extra_body", "metadata") if k in body}
-            return self._run(s.client.chat.completions.create(**kw)).to_dict()
+            comp = self._run(s.client.chat.completions.create(**kw))
+            if body.get("stream"):
+                # the completion is recorded whole (the trajectory needs it); the client gets it as chunk events
+                from ...openai.proxy import chat_completion_chunks
+                from ..common import SSE
+
+                return SSE(list(chat_completion_chunks(comp)) + ["[DONE]"])
+            return comp.to_dict()
 
         @svc.route("POST", "/rl/set_reward")
         def set_reward(body, ctx):

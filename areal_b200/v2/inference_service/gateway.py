@@ -46,6 +46,11 @@ class Gateway:
         def forward(path):
             def fn(body, ctx):
                 a = call(f"http://{self.router}/route/lookup", {"session_id": ctx.api_key})["address"]
+                if body.get("stream"):
+                    # relay the worker's event stream as it arrives (reference: areal/v2/inference_service/gateway/streaming.py)
+                    from ..common import SSE, sse_lines
+
+                    return SSE(sse_lines(f"http://{a}{path}", body, api_key=ctx.api_key))
                 return call(f"http://{a}{path}", body, api_key=ctx.api_key)
             return fn
         svc.route("POST", "/v1/chat/completions")(forward("/chat/completions"))

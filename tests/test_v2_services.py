@@ -88,6 +88,37 @@ def test_inference_service_sessions_affinity_export_and_control():
         ctl.stop()
 
 
+def test_inference_service_streams_completions_through_the_gateway():
+    """``stream: true`` at the gateway: the worker's server-sent events are relayed as they are; the concatenated deltas
+    equal the non-streamed answer and the turn is recorded for training like any other."""
+    import json
+
+    from areal_b200.v2.common import sse_lines
+
+    engines = [CtlEngine(["x" * 150, "plain"])]
+    ctl = InferenceServiceController(admin_key="adm").start(engines, ByteTok(), GenerationHyperparameters(max_new_tokens=256))
+    try:
+        s = ctl.start_session("t1")
+        evs = list(sse_lines(f"{ctl.base_url}/chat/completions", {"messages": [{"role": "user", "content": "q"}], "stream": True},
+                             api_key=s["api_key"]))
+        assert evs[-1] == (None, "[DONE]")
+        chunks = [json.loads(d) for _, d in evs[:-1]]
+        assert all(c["object"] == "chat.completion.chunk" for c in chunks) and len(chunks) >= 5
+        assert "".join(c["choices"][0]["delta"].get("content", "") for c in chunks) == "x" * 150
+        assert chunks[-1]["choices"][0]["finish_reason"] == "stop" and chunks[-1]["usage"]["completion_tokens"] > 0
+        c = call(f"{ctl.base_url}/chat/completions", {"messages": [{"role": "user", "content": "q"}]}, api_key=s["api_key"])
+        assert c["choices"][0]["message"]["content"] == "plain"
+        with pytest.raises(HTTPError) as e:
+            list(sse_lines(f"{ctl.base_url}/chat/completions", {"messages": [], "stream": True}, api_key="sk-unknown"))
+        assert e.value.status in (401, 404)
+        call(f"{ctl.gateway.svc.url}/rl/set_reward", {"reward": 1.0}, api_key=s["api_key"])
+        call(f"{ctl.gateway.svc.url}/rl/end_session", {}, api_key=s["api_key"])
+        batch = ctl.export_batch(style="individual", discount=1.0)
+        assert batch["input_ids"].shape[0] == 2
+    finally:
+        ctl.stop()
+
+
 class FakeTrainEngine:
     """CPU stand-in for a train engine: deterministic functions of the batch."""
 
