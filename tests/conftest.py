@@ -25,3 +25,20 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords or "multi_gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _clear_kernel_error_word(request):
+    """A GPU test that fails after a bounded device wait gave up must not leave the error word set for the tests
+    that follow it in the same process."""
+    yield
+    if "gpu" in request.keywords or "multi_gpu" in request.keywords:
+        try:
+            import torch
+
+            if torch.cuda.is_available():
+                from areal_b200.ops import lib as oplib
+
+                oplib.kernel_error()
+        except Exception:
+            pass

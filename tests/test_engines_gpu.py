@@ -395,15 +395,15 @@ def test_optimizer_step_raises_when_a_device_wait_gave_up():
     data = _batch()
     data["prox_logp"] = eng.compute_logp(data)
     eng.compute_advantages(data)
-    eng.ppo_update(data)                                     # a normal step first
+    eng.ppo_update(dict(data))                               # a normal step first (the update consumes keys of its batch)
     exs = TPDecodeExchange.emulated(2, "cuda", 256, 64, timeout_ms=50)
     x = torch.randn(16, 128, device="cuda").bfloat16()
     w = torch.randn(256, 128, device="cuda").bfloat16()
     p0 = exs[0].linear_bcast(x, w)                           # the second rank never produces
     exs[0].reduce_rmsnorm(p0, torch.ones(256, device="cuda").bfloat16(), 1e-6, torch.zeros(16, 256, device="cuda").bfloat16())
     with pytest.raises(oplib.KernelWaitTimeout):
-        eng.ppo_update(data)
-    stats = eng.ppo_update(data)                             # the word was cleared: training continues
+        eng.ppo_update(dict(data))
+    stats = eng.ppo_update(dict(data))                       # the word was cleared: training continues
     assert stats[0]["update_successful"] == 1.0
     eng.destroy()
 
