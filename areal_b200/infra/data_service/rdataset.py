@@ -49,9 +49,13 @@ class DatasetWorker:
 
 
 class RDataset(Dataset):
-    def __init__(self, address: str, prefetch: int = 64, timeout: float = 60.0):
+    def __init__(self, address: str, prefetch: int = 64, timeout: float = 60.0, token: Optional[str] = None,
+                 length: Optional[int] = None, dataset_id: Optional[str] = None):
+        """``address``: a :class:`DatasetWorker` (no token) or the gateway of the data service (``token``: the key the
+        gateway handed out when the dataset was registered)."""
         self.address, self.timeout = address, timeout
-        self._len = int(call(f"http://{address}/len", timeout=timeout)["len"])
+        self.token, self.dataset_id = token, dataset_id
+        self._len = int(length) if length is not None else int(call(f"http://{address}/len", timeout=timeout)["len"])
         self.prefetch = prefetch
         self._cache: "collections.OrderedDict[int, Any]" = collections.OrderedDict()
         self._lock = threading.Lock()
@@ -63,7 +67,11 @@ class RDataset(Dataset):
 
     def _fetch(self, indices: Sequence[int]) -> None:
         try:
-            items = call(f"http://{self.address}/items", {"indices": list(indices)}, timeout=self.timeout)["items"]
+            if self.token is not None:
+                items = call(f"http://{self.address}/v1/samples/fetch", {"indices": list(indices)}, api_key=self.token,
+                             timeout=self.timeout)["samples"]
+            else:
+                items = call(f"http://{self.address}/items", {"indices": list(indices)}, timeout=self.timeout)["items"]
             with self._cv:
                 for i, it in zip(indices, items):
                     self._cache[i] = deserialize_value(it)
@@ -77,6 +85,19 @@ class RDataset(Dataset):
                     self._pending.discard(i)
                 self._cv.notify_all()
             raise
+
+    def advance_epoch(self, epoch: Optional[int] = None) -> int:
+        """Tells the service that a new epoch starts (datasets that reshuffle or re-augment per epoch follow)."""
+        if self.token is None:
+            return 0
+        body = {} if epoch is None else {"epoch": int(epoch)}
+        return int(call(f"http://{self.address}/v1/epochs/advance", body, api_key=self.token, timeout=self.timeout)["epoch"])
+
+    def save_state(self, path: str) -> list:
+        return call(f"http://{self.address}/v1/state/save", {"path": path}, api_key=self.token, timeout=self.timeout)["files"]
+
+    def load_state(self, path: str) -> dict:
+        return call(f"http://{self.address}/v1/state/load", {"path": path}, api_key=self.token, timeout=self.timeout)
 
     def hint(self, upcoming: Iterable[int]) -> None:
         """Announces indices that will be requested soon; they are fetched in the background."""

@@ -42,3 +42,53 @@ def test_remote_dataset_with_prefetch():
             pass
     finally:
         w.stop()
+
+
+def test_data_service_registers_fans_out_and_keeps_state(tmp_path):
+    """Three workers behind one gateway: a dataset registered once is loaded everywhere, a fetch is served by the
+    owners of its indices and comes back in request order, epoch / state travel to every worker, tokens and the admin
+    key are enforced, and a DataLoader over the remote dataset sees the same samples as the local one."""
+    import pytest
+
+    from areal_b200.infra.data_service.service import DataController
+    from areal_b200.v2.common import HTTPError, call
+
+    ctl = DataController(n_workers=3).start()
+    try:
+        ds = ArithmeticDataset(size=50, seed=9)
+        rd = ctl.register_dataset(factory="areal_b200.dataset.ArithmeticDataset", kwargs={"size": 50, "seed": 9}, prefetch=16)
+        assert len(rd) == 50 and rd.token.startswith("sk-data-")
+        order = [49, 0, 7, 7, 23, 1, 2]
+        got = call(f"http://{ctl.gateway.address}/v1/samples/fetch", {"indices": order}, api_key=rd.token)["samples"]
+        from areal_b200.infra.rpc.serialization import deserialize_value
+
+        assert [deserialize_value(g) for g in got] == [ds[i] for i in order]
+        served = [h["datasets"] for h in (call(f"http://{w.address}/health") for w in ctl.workers)]
+        assert all(list(s.values()) == [50] for s in served)            # every worker loaded the whole set
+        sampler = PrefetchAwareSampler(SequentialSampler(rd), rd, lookahead=16)
+        batches = [b for b in DataLoader(rd, batch_size=10, sampler=sampler, collate_fn=list)]
+        assert [x for b in batches for x in b] == [ds[i] for i in range(50)]
+        assert rd.advance_epoch() == 1 and rd.advance_epoch(5) == 5
+        files = rd.save_state(str(tmp_path / "state"))
+        assert len(files) == 3
+        rd.advance_epoch(9)
+        st = rd.load_state(str(tmp_path / "state"))
+        assert st["epoch"] == 5 and st["served"] >= 50 + len(order)
+        with pytest.raises(HTTPError) as e:
+            call(f"http://{ctl.gateway.address}/v1/samples/fetch", {"indices": [0]}, api_key="sk-data-wrong")
+        assert e.value.status == 401
+        with pytest.raises(HTTPError) as e:
+            call(f"http://{ctl.gateway.address}/v1/datasets/register", {"factory": "x.y"}, api_key="nope")
+        assert e.value.status == 401
+        with pytest.raises(HTTPError) as e:
+            call(f"http://{ctl.gateway.address}/v1/samples/fetch", {"indices": [50]}, api_key=rd.token)
+        assert e.value.status == 400
+        stat = ctl.status()
+        assert stat["datasets"][rd.dataset_id]["len"] == 50 and len(stat["workers"]) == 3
+        # a worker that went away is marked unhealthy and no longer routed to
+        ctl.workers[2].stop()
+        ctl.router.check_health()
+        assert [w["healthy"] for w in call(f"http://{ctl.router.address}/workers", api_key=ctl.admin_key)["workers"]] == [True, True, False]
+        assert call(f"http://{ctl.router.address}/route", {}, api_key=ctl.admin_key)["address"] in (ctl.workers[0].address, ctl.workers[1].address)
+    finally:
+        ctl.stop()
