@@ -262,8 +262,10 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
 }
 
 // ------------------------------------------------------------------ embedding
+// A token id outside [0, V) is clamped (the kernel stays inside W) and reported in the error word, which the
+// engines read once per optimizer step / decode iteration: a bad id is a loud failure, not a silent row 0.
 __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ W, const int* __restrict__ ids,
-                                 __nv_bfloat16* __restrict__ out, int T, int H, int V) {
+                                 __nv_bfloat16* __restrict__ out, int T, int H, int V, int* __restrict__ err) {
   pdl_wait();
   pdl_trigger();
   const int vec = H >> 3;
@@ -272,7 +274,10 @@ __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ W, const int*
        i += (long long)gridDim.x * blockDim.x) {
     const int t = (int)(i / vec), c = (int)(i - (long long)t * vec);
     int id = ids[t];
-    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    if (id < 0 || id >= V) {
+      if (c == 0 && err != nullptr) set_error(err, ERR_BOUNDS);
+      id = id < 0 ? 0 : V - 1;
+    }
     reinterpret_cast<uint4*>(out + (size_t)t * H)[c] = reinterpret_cast<const uint4*>(W + (size_t)id * H)[c];
   }
 }
@@ -427,7 +432,7 @@ int ab2_embed_fwd(const void* W, const int* ids, void* out, int T, int H, int V,
   if (H % 8) return 10;
   if (T <= 0) return 0;
   launch_pdl(embed_fwd_kernel, dim3(grid_for((long long)T * (H / 8), 256)), dim3(256), 0, (cudaStream_t)stream,
-             (const __nv_bfloat16*)W, ids, (__nv_bfloat16*)out, T, H, V);
+             (const __nv_bfloat16*)W, ids, (__nv_bfloat16*)out, T, H, V, ab2host::error_flag());
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 int ab2_embed_bwd(const void* dy, const int* ids, float* dW, int T, int H, int V, void* stream) {

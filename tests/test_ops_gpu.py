@@ -698,3 +698,45 @@ def test_context_parallel_blockwise_attention_on_flash_kernels(cp, D, Hq, Hkv):
         valid = (src >= 0).cuda()
         assert _rel_err(dk_sum[r][valid], CP.zigzag_split(dk_ref, cu, cp, r)[valid]) < 2e-2
         assert _rel_err(dv_sum[r][valid], CP.zigzag_split(dv_ref, cu, cp, r)[valid]) < 2e-2
+
+
+def test_embedding_reports_an_out_of_range_token_id():
+    """A token id outside the vocabulary is clamped (no stray read) and sets the device error word with the bounds
+    code, which the engines turn into an exception at their next poll; in-range ids leave the word alone."""
+    W = torch.randn(100, 64, device="cuda").bfloat16()
+    ok = OF.embedding(torch.tensor([0, 5, 99], device="cuda", dtype=torch.int32), W)
+    torch.cuda.synchronize()
+    assert oplib.kernel_error() == 0 and torch.equal(ok, W[[0, 5, 99]])
+    bad = OF.embedding(torch.tensor([3, 100, -1], device="cuda", dtype=torch.int32), W)
+    torch.cuda.synchronize()
+    assert oplib.kernel_error() == 6                              # ERR_BOUNDS; reading clears the word
+    assert torch.equal(bad, W[[3, 99, 0]]) and oplib.kernel_error() == 0
+
+
+def test_forward_and_decode_are_bitwise_reproducible_and_training_is_close():
+    """Run-twice check: the forward pass (log-probs of a packed batch) and greedy decoding give the same bits when
+    repeated; a training step uses float atomics (attention dQ, embedding rows), so two runs from one state agree to
+    rounding, not to the bit."""
+    from areal_b200.models.config import preset
+    from areal_b200.models.decoder import build_model
+
+    cfg = preset("tiny-qwen3")
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=3)
+    ids = torch.randint(0, cfg.vocab_size, (900,), device="cuda", dtype=torch.int32)
+    cu = torch.tensor([0, 300, 420, 900], dtype=torch.int32, device="cuda")
+    labels = torch.roll(ids, -1).long()
+    outs = []
+    for _ in range(2):
+        with torch.no_grad():
+            h = model(ids, cu, max_seqlen=480)
+            outs.append(model.logprobs_entropy(h, labels))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    grads = []
+    for _ in range(2):
+        model.zero_grad()
+        h = model(ids, cu, max_seqlen=480)
+        lp, _ = model.logprobs_entropy(h, labels)
+        (-lp.mean()).backward()
+        grads.append(torch.cat([p.grad.float().flatten() for p in model.parameters() if p.grad is not None]))
+    assert _rel_err(grads[0], grads[1]) < 1e-3
+    _no_kernel_error()
