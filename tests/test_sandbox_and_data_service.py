@@ -92,3 +92,29 @@ def test_data_service_registers_fans_out_and_keeps_state(tmp_path):
         assert call(f"http://{ctl.router.address}/route", {}, api_key=ctl.admin_key)["address"] in (ctl.workers[0].address, ctl.workers[1].address)
     finally:
         ctl.stop()
+
+
+def test_remote_sandbox_runs_code_on_a_server_with_its_limits():
+    import pytest
+
+    from areal_b200.infra.sandbox import DaytonaRunner, RemoteSandbox, SandboxConfig, SandboxServer
+    from areal_b200.infra.sandbox.local import run_python_tool
+    from areal_b200.v2.common import HTTPError
+
+    srv = SandboxServer(SandboxConfig(timeout_s=2.0), api_key="k", max_concurrent=2).start()
+    try:
+        sb = RemoteSandbox(srv.address, api_key="k")
+        r = sb.run("import sys; print(sys.stdin.read().upper() + open('d.txt').read())", stdin="ab", files={"d.txt": "!"})
+        assert r.ok and r.stdout.strip() == "AB!"
+        r = sb.run("raise SystemExit(3)")
+        assert not r.ok and r.returncode == 3
+        slow = RemoteSandbox(srv.address, api_key="k", timeout_s=50.0).run("import time; time.sleep(30)")
+        assert slow.timed_out and slow.seconds < 10                 # the server's own limit (2 s) wins over the request's 50 s
+        assert "exit code" not in run_python_tool({"code": "print(6*7)"}, sandbox=sb) and "42" in run_python_tool({"code": "print(6*7)"}, sandbox=sb)
+        with pytest.raises(HTTPError) as e:
+            RemoteSandbox(srv.address, api_key="wrong", retries=1).run("print(1)")
+        assert e.value.status == 401
+    finally:
+        srv.stop()
+    with pytest.raises(ImportError, match="daytona"):
+        DaytonaRunner()
