@@ -340,6 +340,30 @@ def bench_ep(a):
     return report("ep_dispatch_bwd", ms, bytes_=2 * N * H * 2 + T * H * 2, rows=N, hidden=H, note="scaled rows out + gate-weight gradients (reads the saved rows)")
 
 
+def bench_moe_route(a):
+    """Device-side routing (scores, top-k, stable sort by expert, group sizes, GEMM tile list; four small launches, no
+    host read) against the eager statement of the same step (softmax, topk, argsort, bincount and the host copy of
+    the counts that the tile table needs). ``--rows`` tokens, ``--experts`` experts, ``--topk`` choices."""
+    T, E, k = a.rows, a.experts, a.topk
+    logits = torch.randn(T, E, device="cuda") * 2.0
+
+    def eager():
+        probs = torch.softmax(logits, -1)
+        tope = torch.topk(probs, k, -1).indices
+        w = probs.gather(1, tope)
+        w = w / w.sum(-1, keepdim=True)
+        flat = tope.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=E).tolist()          # the host needs them to build the tile table
+        return order, w, counts
+    ms = timeit(lambda: OF.moe_route(logits, k, want_probs=False), a.iters, a.warmup)
+    by = 4.0 * T * E + 4.0 * T * k * 5
+    res = report("moe_route (topk + stable sort + counts + tile list, 4 launches)", ms, 0.0, by, tokens=T, experts=E, topk=k)
+    ms2 = timeit(eager, a.iters, a.warmup)
+    report("eager routing (softmax, topk, argsort, bincount, counts to host)", ms2, 0.0, by, tokens=T, experts=E, topk=k)
+    return res
+
+
 def bench_push_plan(a):
     """The one-launch re-shard of ONE trainer shard (1 of ``--shards`` FSDP ranks) of ``--model`` into the
     tensor-parallel layout (``--tp``) of ``--replicas`` rollout replicas. On one GPU the "replicas" are local
@@ -376,7 +400,8 @@ def bench_push_plan(a):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_decode", "gemm_fp8", "gemm_skinny", "qknorm_rope", "attn_fwd", "attn_bwd", "decode", "rmsnorm", "swiglu", "adamw", "logprob",
-                                           "engine_decode", "ep", "push_plan"])
+                                           "engine_decode", "ep", "push_plan", "moe_route"])
+    ap.add_argument("--experts", type=int, default=128); ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--shards", type=int, default=4); ap.add_argument("--tp", type=int, default=2); ap.add_argument("--replicas", type=int, default=2)
     ap.add_argument("--model", type=str, default="qwen3-8b"); ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--new", type=int, default=128)
@@ -396,7 +421,7 @@ def main(argv=None):
         a.rows = 2048
     return {"gemm": bench_gemm, "gemm_decode": bench_gemm_decode, "gemm_fp8": bench_gemm_fp8, "gemm_skinny": bench_gemm_skinny, "qknorm_rope": bench_qknorm_rope, "attn_fwd": bench_attn_fwd, "attn_bwd": bench_attn_bwd, "decode": bench_decode,
             "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "logprob": bench_logprob,
-            "engine_decode": bench_engine_decode, "ep": bench_ep, "push_plan": bench_push_plan}[a.kernel](a)
+            "engine_decode": bench_engine_decode, "ep": bench_ep, "push_plan": bench_push_plan, "moe_route": bench_moe_route}[a.kernel](a)
 
 
 if __name__ == "__main__":
