@@ -223,9 +223,58 @@ def test_cli_state_roundtrip(tmp_path, monkeypatch, capsys):
         out = capsys.readouterr().out
         assert "ok" in out and "DOWN" in out
         assert len(json.load(open(tmp_path / "st.json"))["services"]) == 2
+        assert cli.main(["inference", "ps"]) == 0 and "PID" in capsys.readouterr().out
+        assert cli.main(["inference", "models"]) == 1                  # the stub has no /v1/models route
+        log = tmp_path / "svc.log"
+        log.write_text("a\nb\nc\n")
+        cli.record("sandbox", "127.0.0.1:7", log=str(log), name="sbx0")
+        capsys.readouterr()
+        assert cli.main(["logs", "sbx0", "-n", "2"]) == 0 and capsys.readouterr().out == "b\nc\n"
+        assert cli.main(["logs", "nobody"]) == 1
+        assert cli.main(["sandbox", "stop", "--address", "127.0.0.1:7"]) == 0      # recorded by this very process: only forgotten
+        assert cli.main(["sandbox", "stop"]) == 1
+        assert [s_["kind"] for s_ in cli.load_state()["services"]] == ["inference", "inference"]
         assert cli.main(["state", "clear"]) == 0 and cli.load_state() == {"services": []}
     finally:
         svc.stop()
+
+
+def test_cli_serves_a_sandbox_and_a_data_worker(tmp_path):
+    """``python -m areal_b200.v2.cli sandbox serve`` / ``data serve worker`` as real child processes: they print their
+    address, answer, are listed in the state file, and ``stop`` ends them by their recorded pid."""
+    import os
+    import subprocess
+    import sys
+    import time
+
+    from areal_b200.infra.sandbox import RemoteSandbox
+
+    env = dict(os.environ, AREAL_V2_STATE=str(tmp_path / "st.json"), PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    procs = []
+    try:
+        addrs = {}
+        for args, tag in ((["sandbox", "serve", "--api-key", "k"], "SANDBOX_READY"), (["data", "serve", "worker"], "DATA_WORKER_READY")):
+            p = subprocess.Popen([sys.executable, "-m", "areal_b200.v2.cli"] + args, env=env, stdout=subprocess.PIPE, text=True)
+            procs.append(p)
+            line = p.stdout.readline()
+            assert line.startswith(tag), line
+            addrs[tag] = line.split()[1]
+        assert RemoteSandbox(addrs["SANDBOX_READY"], api_key="k").run("print(1+1)").stdout.strip() == "2"
+        assert call(f"http://{addrs['DATA_WORKER_READY']}/health")["status"] == "ok"
+        st = json.load(open(tmp_path / "st.json"))["services"]
+        assert sorted(s_["kind"] for s_ in st) == ["data", "sandbox"] and {s_["pid"] for s_ in st} == {p.pid for p in procs}
+        r = subprocess.run([sys.executable, "-m", "areal_b200.v2.cli", "sandbox", "stop"], env=env, capture_output=True, text=True)
+        assert r.returncode == 0 and "stopped 1" in r.stdout
+        for _ in range(100):
+            if procs[0].poll() is not None:
+                break
+            time.sleep(0.05)
+        assert procs[0].poll() is not None and procs[1].poll() is None
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.terminate()
+            p.wait(timeout=10)
 
 
 def test_agent_service_runs_queues_and_ends_sessions():
