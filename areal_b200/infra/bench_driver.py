@@ -147,6 +147,26 @@ def _cap_micro_batch(args, actor) -> None:
         args._resolved["max_tokens_per_mb_capped_by_memory"] = True
 
 
+def kept_layers_for(free_gb: float, tokens: int, n_layers: int, hidden: int) -> int:
+    """Layers whose activations fit: 0.30 MB per token and kept layer at hidden 4096 (bf16 activations of attention and
+    MLP plus what autograd saves), 8 KB per token and layer for the recomputed layers' inputs, one layer's working set,
+    5 GB for the LM-head chunks and 12 GB of slack."""
+    per_layer_gb = tokens * 0.30e-3 * (hidden / 4096.0)
+    avail = free_gb - 12.0 - 5.0 - per_layer_gb - n_layers * tokens * 8e-6
+    return max(0, min(n_layers, int(avail / per_layer_gb)))
+
+
+def plan_activation_policy(free_gb: float, tokens: int, n_layers: int, hidden: int, floor_tokens: int) -> tuple[int, int]:
+    """(tokens per rank and micro-batch, kept layers). Recomputing a layer costs a third of its forward + backward time;
+    a smaller micro-batch costs next to nothing as long as its GEMMs still have thousands of rows (gradients accumulate
+    locally, no collective per micro-batch). So the micro-batch shrinks by halves, not below ``floor_tokens`` (4096 per
+    rank, and the longest sequence), until every layer's activations fit; what then still does not fit is recomputed."""
+    t = tokens
+    while kept_layers_for(free_gb, t, n_layers, hidden) < n_layers and t // 2 >= floor_tokens:
+        t //= 2
+    return t, kept_layers_for(free_gb, t, n_layers, hidden)
+
+
 def _pick_recompute(args, actor, model_cfg) -> None:
     """The activation policy, one rule at every N (``--grad-ckpt -1``): keep the activations of as
     many layers as the memory left after parameters, gradients and optimizer state holds, recompute
@@ -161,20 +181,11 @@ def _pick_recompute(args, actor, model_cfg) -> None:
     n = model_cfg.num_layers
 
     def kept_layers(t: int) -> int:
-        per_layer_gb = t * 0.30e-3 * (model_cfg.hidden_size / 4096.0)
-        avail = free / 2 ** 30 - 12.0 - 5.0 - per_layer_gb - n * t * 8e-6
-        return max(0, min(n, int(avail / per_layer_gb)))
+        return kept_layers_for(free / 2 ** 30, t, n, model_cfg.hidden_size)
 
-    # Recomputing a layer costs a third of its forward + backward time; a smaller micro-batch costs next to
-    # nothing as long as its GEMMs still have thousands of rows (gradients accumulate locally, no collective per
-    # micro-batch). So the micro-batch shrinks (by halves, not below 4096 tokens per rank nor below the longest
-    # sequence) until every layer's activations fit, and only what then still does not fit is recomputed.
     t = actor.config.mb_spec.max_tokens_per_mb // sp
     longest = -(-(args.prompt_len + args.max_len) // 1024) * 1024
-    floor_t = max(4096, -(-longest // sp))
-    while kept_layers(t) < n and t // 2 >= floor_t:
-        t //= 2
-    keep = kept_layers(t)
+    t, keep = plan_activation_policy(free / 2 ** 30, t, n, model_cfg.hidden_size, max(4096, -(-longest // sp)))
     if actor.cpu_group is not None:               # every trainer rank must split the batch the same way
         tt = torch.tensor([t], dtype=torch.int64)
         dist.all_reduce(tt, op=dist.ReduceOp.MIN, group=actor.cpu_group)

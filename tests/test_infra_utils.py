@@ -445,3 +445,20 @@ def test_memory_profiler_is_inert_without_cuda_and_respects_its_step_list(tmp_pa
     if not torch.cuda.is_available():
         assert mp.start(3) is False and mp.stop(str(tmp_path)) is None
     assert MemoryProfiler(MemoryProfilerConfig(enabled=False, profile_steps=[3])).wants(3) is False
+
+
+def test_bench_activation_policy_shrinks_the_micro_batch_before_it_recomputes():
+    from areal_b200.infra.bench_driver import kept_layers_for, plan_activation_policy
+
+    # Qwen3-8B trainer rank of the 4-GPU layout: 68.7 GB free, 16384 tokens per rank asked for
+    assert kept_layers_for(68.7, 16384, 36, 4096) == 8
+    assert plan_activation_policy(68.7, 16384, 36, 4096, 4096) == (4096, 36)
+    # 8-GPU layout: more room, still 4096 per rank (8192 would keep 29 of 36)
+    assert plan_activation_policy(99.5, 8192, 36, 4096, 4096) == (4096, 36)
+    # a lone trainer holding all optimizer state: the floor (longest sequence) stops the shrinking, the rest is recomputed
+    t, keep = plan_activation_policy(30.0, 29696, 36, 4096, 5120)
+    assert t == 7424 and 0 < keep < 8
+    # plenty of memory: nothing changes
+    assert plan_activation_policy(150.0, 8192, 36, 4096, 4096) == (8192, 36)
+    # no memory at all: floor and full recompute
+    assert plan_activation_policy(10.0, 8192, 36, 4096, 4096) == (4096, 0)
