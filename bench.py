@@ -204,7 +204,8 @@ def main():
 
     # a rank that stops making progress prints every thread's stack and exits instead of
     # holding the other ranks (and the GPUs) until an outer limit
-    wd = float(os.environ.get("AREAL_BENCH_WATCHDOG_S", "0") or 0)
+    # (default: shortly before the 870 s a benchmark run is given, so that a stall leaves stacks behind, not just a kill)
+    wd = float(os.environ.get("AREAL_BENCH_WATCHDOG_S", "850") or 0)
     if wd > 0:
         faulthandler.dump_traceback_later(wd, exit=True)
 
