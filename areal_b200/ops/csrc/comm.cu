@@ -10,7 +10,6 @@
 //                      destination buffer (trainer peers = parameter all-gather, rollout
 //                      replicas = weight update)
 //   push_copy          shard-direct copy of a bf16 range to several destinations (weight push)
-//   push_cast_fp8      same, with an in-kernel block-scaled (1x128) e4m3 cast
 //   push_plan          a whole FSDP-shard -> tensor-parallel re-shard plan (row / column slices of
 //                      q/k/v/o, gate/up/down) in ONE launch, bf16 or cast to block-scaled e4m3
 //
@@ -195,46 +194,6 @@ __global__ void push_copy_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs
   }
 }
 
-// 2-D strided copy: rows x cols bf16 from a row-major source (ld_src) into destination k at
-// element offset dst_off[k] with leading dimension ld_dst (tensor-parallel re-sharding: a
-// row or column slice of a weight lands in the replica's TP-local tensor).
-__global__ void push_copy2d_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src, PeerPtrs dst, int ndst,
-                                   long long dst_off, long long ld_dst, int rows, int cols) {
-  const int c8 = cols >> 3;
-  const long long total = (long long)rows * c8;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / c8), c = (int)(i - (long long)r * c8);
-    const uint4 v = reinterpret_cast<const uint4*>(src + (size_t)r * ld_src)[c];
-    for (int k = 0; k < ndst; ++k)
-      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[k]) + dst_off + (size_t)r * ld_dst)[c] = v;
-  }
-}
-
-// Block-scaled fp8 cast fused into the push: one warp per 128-element block of the source
-// range; amax -> scale (optionally rounded up to a power of two, UE8M0 style) -> e4m3 values
-// to dstq[k] + off and the fp32 scale to dsts[k] + off / 128.
-__global__ void push_cast_fp8_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dstq, PeerPtrs dsts, int ndst,
-                                     long long dst_off, long long n_blocks, int pow2) {
-  const int lane = threadIdx.x & 31;
-  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long b = warp; b < n_blocks; b += nwarps) {
-    const uint2 raw = reinterpret_cast<const uint2*>(src + b * 128)[lane];
-    const float2 a = unpack_bf16(raw.x), c = unpack_bf16(raw.y);
-    float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(c.x), fabsf(c.y)));
-    amax = warp_max(amax);
-    float scale = fmaxf(amax, 1e-12f) / 448.f;
-    if (pow2) scale = exp2f(ceilf(log2f(scale)));
-    const float inv = 1.f / scale;
-    __nv_fp8x4_e4m3 q(make_float4(a.x * inv, a.y * inv, c.x * inv, c.y * inv));
-    for (int k = 0; k < ndst; ++k) {
-      reinterpret_cast<__nv_fp8x4_e4m3*>(reinterpret_cast<uint8_t*>(dstq.p[k]) + dst_off + b * 128)[lane] = q;
-      if (lane == 0) reinterpret_cast<float*>(dsts.p[k])[dst_off / 128 + b] = scale;
-    }
-  }
-}
-
 // One launch for a whole re-shard plan (tensor-parallel rollout replicas). Every op is a 2-D strided
 // copy of bf16 (rows x cols, 16-byte vectors) from this rank's flat parameter buffer into the flat
 // buffer of TP rank `dst` of EVERY replica: the source vector is loaded once and stored n_rep times.
@@ -411,15 +370,6 @@ int ab2_push_copy(const void* src, void* const* dst, int ndst, long long dst_off
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
-int ab2_push_copy2d(const void* src, long long ld_src, void* const* dst, int ndst, long long dst_off, long long ld_dst,
-                    int rows, int cols, void* stream) {
-  if (ndst > MAX_PEERS || (cols & 7) || (dst_off & 7) || (ld_src & 7) || (ld_dst & 7)) return 10;
-  if (rows <= 0 || cols <= 0 || ndst <= 0) return 0;
-  push_copy2d_kernel<<<grid_of((long long)rows * (cols / 8)), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)src, ld_src, make_ptrs(dst, ndst), ndst, dst_off, ld_dst, rows, cols);
-  return cudaGetLastError() == cudaSuccess ? 0 : 1;
-}
-
 // Executes a re-shard plan in one launch. ops / chunk_start / dst tables live in device memory:
 // ops[n_ops] (PushOp, 40 bytes each), chunk_start[n_ops] (int32, exclusive prefix sum of
 // ceil(rows * cols / 8 / 4096)), dst_ptrs[n_rep * tp] (destination flat buffers, replica-major).
@@ -444,15 +394,4 @@ int ab2_push_plan(const void* src, const void* ops, int n_ops, const void* chunk
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
-// n must be a multiple of 128. dst_off is in elements for the fp8 buffers (scales at off/128).
-int ab2_push_cast_fp8(const void* src, void* const* dstq, void* const* dsts, int ndst, long long dst_off, long long n,
-                      int pow2_scales, void* stream) {
-  if (ndst > MAX_PEERS || (n & 127) || (dst_off & 127)) return 10;
-  if (n <= 0 || ndst <= 0) return 0;
-  const long long nb = n / 128;
-  push_cast_fp8_kernel<<<grid_of(nb * 32), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src,
-                                                                           make_ptrs(dstq, ndst), make_ptrs(dsts, ndst),
-                                                                           ndst, dst_off, nb, pow2_scales);
-  return cudaGetLastError() == cudaSuccess ? 0 : 1;
-}
 }

@@ -35,10 +35,6 @@ oplib.declare("ab2_adamw_push", [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_
               [ctypes.c_float] * 5 + [ctypes.c_int, ctypes.c_void_p])
 oplib.declare("ab2_push_copy", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong,
                                 ctypes.c_void_p])
-oplib.declare("ab2_push_copy2d", [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
-                                  ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_void_p])
-oplib.declare("ab2_push_cast_fp8", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
-                                    ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p])
 
 
 def ptr_array(ptrs) -> ctypes.Array:

@@ -2,11 +2,10 @@
 
 Every trainer rank owns a contiguous shard of the flat bf16 parameter space. On an update it
 writes exactly that shard into the parameter buffers of every rollout replica with one kernel
-(:func:`ab2_push_copy`, or :func:`ab2_push_cast_fp8` for block-scaled fp8 rollout weights), so
-all trainer GPUs push concurrently, nothing is gathered to rank 0 and no tensor is touched
-twice. For tensor-parallel rollout replicas the plan below cuts every parameter into the row /
-column slices each TP rank owns and emits 1-D or 2-D strided copies
-(:func:`ab2_push_copy2d`).
+(:func:`ab2_push_copy`), so all trainer GPUs push concurrently, nothing is gathered to rank 0 and
+no tensor is touched twice. For tensor-parallel rollout replicas the plan below cuts every
+parameter into the row / column slices each TP rank owns; the whole plan (1-D and 2-D strided
+copies, optionally cast to block-scaled e4m3 on the way) runs as ONE launch (:func:`ab2_push_plan`).
 
 Compared with the reference's ``xccl`` path (``areal/engine/fsdp_engine.py:1596-1692``: full
 ``full_tensor()`` all-gather on every trainer rank, then per-tensor NCCL broadcast from rank 0
