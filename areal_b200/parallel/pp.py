@@ -314,20 +314,41 @@ class PipelineRunner:
 
 
 # --------------------------------------------------------------------------- virtual stages
+def stage_of(rank: int, chunk: int, n_ranks: int, placement: str = "loop") -> int:
+    """Global stage of chunk ``chunk`` on rank ``rank``: ``loop`` walks the ranks once per chunk (stage
+    ``chunk * P + rank``); ``v`` (two chunks) goes down the ranks and back up, so rank 0 holds the first AND the
+    last stage and rank ``P - 1`` two consecutive ones."""
+    if placement == "v":
+        return rank if chunk == 0 else 2 * n_ranks - 1 - rank
+    return chunk * n_ranks + rank
+
+
+def owner_of(stage: int, n_ranks: int, placement: str = "loop") -> tuple[int, int]:
+    """(rank, chunk) that holds ``stage``."""
+    if placement == "v":
+        return (stage, 0) if stage < n_ranks else (2 * n_ranks - 1 - stage, 1)
+    return stage % n_ranks, stage // n_ranks
+
+
 class InterleavedStages(nn.Module):
-    """``V`` model chunks of one pipeline rank (virtual pipeline): chunk ``v`` on rank ``r`` of
-    ``P`` is global stage ``v * P + r``. Presents the attributes the engine reads from a stage
-    (first / last flags, embedding, heads, native parameter names)."""
+    """``V`` model chunks of one pipeline rank (virtual pipeline), placed by :func:`stage_of`. Presents the
+    attributes the engine reads from a stage (first / last flags, embedding, heads, native parameter names)."""
 
     def __init__(self, cfg: ModelConfig, rank: int, n_ranks: int, n_chunks: int, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None,
-                 init_full: Optional[Callable] = None):
+                 init_full: Optional[Callable] = None, placement: str = "loop"):
         super().__init__()
+        if placement == "v" and n_chunks != 2:
+            raise ValueError("the V-shaped placement has exactly two chunks per rank")
         self.cfg, self.dtype, self.stage, self.n_stages = cfg, dtype, rank, n_ranks
-        self.n_chunks = n_chunks
+        self.n_chunks, self.placement = n_chunks, placement
         total = n_ranks * n_chunks
-        self.chunks = nn.ModuleList([PipelineStage(cfg, v * n_ranks + rank, total, dtype=dtype, device=device, seed=seed, init_full=init_full)
-                                     for v in range(n_chunks)])
-        self.is_first, self.is_last = rank == 0, rank == n_ranks - 1
+        self.chunks = nn.ModuleList([PipelineStage(cfg, stage_of(rank, v, n_ranks, placement), total, dtype=dtype, device=device, seed=seed,
+                                                   init_full=init_full) for v in range(n_chunks)])
+        self.is_first = any(c.is_first for c in self.chunks)
+        self.is_last = any(c.is_last for c in self.chunks)
+        if self.is_first and self.is_last and n_ranks > 1 and cfg.tie_word_embeddings and not cfg.is_critic:
+            # first and last stage on one rank (V placement): the tied embedding is ONE parameter used twice
+            self.chunks[-1].embed_tokens = self.chunks[0].embed_tokens
         self.gradient_checkpointing = False
 
     @property
@@ -395,13 +416,18 @@ def interleaved_order(n_ranks: int, n_chunks: int, n_micro: int, rank: int) -> l
     return ops
 
 
-def build_timetable(n_ranks: int, n_chunks: int, n_micro: int, schedule: str = "Interleaved1F1B", forward_only: bool = False):
+def build_timetable(n_ranks: int, n_chunks: int, n_micro: int, schedule: str = "Interleaved1F1B", forward_only: bool = False,
+                    placement: str = "loop"):
     """Lock-step timetable every rank derives identically: per tick, the operation each rank runs
     (or None) and the messages ``(src, dst, kind, micro-batch, destination stage)`` delivered at the
     tick's start. An operation runs once its input has been delivered; a message is delivered the
-    tick after it was produced."""
+    tick after it was produced. ``schedule="ZBV"`` (V placement) has no fixed order per rank: every tick a
+    rank runs the ready backward of the oldest micro-batch, else a ready forward (the deeper chunk first, since it
+    leads to a backward sooner) while fewer than ``2 P`` chunk activations are alive on it."""
     P, V, M = n_ranks, n_chunks, n_micro
     S = P * V
+    if schedule == "ZBV" and not forward_only:
+        return _greedy_timetable(P, V, M, placement)
     if forward_only or schedule == "GPipe":
         orders = [[("F", m, v) for v in range(V) for m in range(M)] + ([] if forward_only else [("B", m, v) for v in reversed(range(V)) for m in range(M)])
                   for _ in range(P)]
@@ -421,7 +447,7 @@ def build_timetable(n_ranks: int, n_chunks: int, n_micro: int, schedule: str = "
             op = orders[r][ptr[r]] if ptr[r] < len(orders[r]) else None
             if op is not None:
                 kind, mb, v = op
-                s = v * P + r
+                s = stage_of(r, v, P, placement)
                 ready = (s == 0 or ("act", mb, s) in have) if kind == "F" else \
                     (("F", mb, s) in done and (s == S - 1 or ("grad", mb, s) in have))
                 if not ready:
@@ -433,13 +459,67 @@ def build_timetable(n_ranks: int, n_chunks: int, n_micro: int, schedule: str = "
             if op is None:
                 continue
             kind, mb, v = op
-            s = v * P + r
+            s = stage_of(r, v, P, placement)
             ptr[r] += 1
             done.add((kind, mb, s))
             if kind == "F" and s < S - 1:
-                pending.append((r, (r + 1) % P, "act", mb, s + 1))
+                pending.append((r, owner_of(s + 1, P, placement)[0], "act", mb, s + 1))
             if kind == "B" and s > 0:
-                pending.append((r, (r - 1) % P, "grad", mb, s - 1))
+                pending.append((r, owner_of(s - 1, P, placement)[0], "grad", mb, s - 1))
+        ticks.append((row, delivered))
+    if pending:
+        ticks.append(([None] * P, pending))
+    return ticks
+
+
+def _greedy_timetable(P: int, V: int, M: int, placement: str):
+    S = P * V
+    todo = [{(k, m, v) for k in "FB" for m in range(M) for v in range(V)} for _ in range(P)]
+    have: set = set()
+    done: set = set()
+    alive = [0] * P                  # chunk activations held (forwards run minus backwards run)
+    cap = 2 * P
+    ticks, pending = [], []
+    while any(todo):
+        for msg in pending:
+            have.add((msg[2], msg[3], msg[4]))
+        delivered, pending = pending, []
+        row = []
+        for r in range(P):
+            best = None
+            for (kind, mb, v) in todo[r]:
+                s = stage_of(r, v, P, placement)
+                if kind == "B":
+                    if ("F", mb, s) in done and (s == S - 1 or ("grad", mb, s) in have):
+                        key = (0, mb, -s)
+                    else:
+                        continue
+                else:
+                    if (s == 0 or ("act", mb, s) in have) and alive[r] < cap:
+                        key = (1, -v, mb)
+                    else:
+                        continue
+                if best is None or key < best[0]:
+                    best = (key, (kind, mb, v))
+            row.append(best[1] if best else None)
+        if not delivered and all(o is None for o in row):
+            cap += 1                 # the activation bound was the only obstacle: let one more forward in
+            if cap > 2 * M * V + 2 * P:
+                raise RuntimeError(f"pipeline schedule cannot make progress (P={P}, V={V}, M={M})")
+            ticks.append(([None] * P, []))
+            continue
+        for r, op in enumerate(row):
+            if op is None:
+                continue
+            kind, mb, v = op
+            s = stage_of(r, v, P, placement)
+            todo[r].discard(op)
+            done.add((kind, mb, s))
+            alive[r] += 1 if kind == "F" else -1
+            if kind == "F" and s < S - 1:
+                pending.append((r, owner_of(s + 1, P, placement)[0], "act", mb, s + 1))
+            if kind == "B" and s > 0:
+                pending.append((r, owner_of(s - 1, P, placement)[0], "grad", mb, s - 1))
         ticks.append((row, delivered))
     if pending:
         ticks.append(([None] * P, pending))
@@ -461,19 +541,25 @@ class ScheduledPipelineRunner:
         self.ranks = dist.get_process_group_ranks(group)
         self.first_rank, self.last_rank = self.ranks[0], self.ranks[-1]
         self.schedule = {"1f1b": "Interleaved1F1B", "interleaved1f1b": "Interleaved1F1B", "gpipe": "GPipe",
-                         "interleavedzerobubble": "Interleaved1F1B", "zbh1": "Interleaved1F1B"}.get(schedule.lower())
+                         "interleavedzerobubble": "Interleaved1F1B", "zbh1": "Interleaved1F1B", "zbv": "ZBV",
+                         "zbvzerobubble": "ZBV"}.get(schedule.lower())
         if self.schedule is None:
             raise ValueError(f"unknown pipeline schedule '{schedule}'")
+        self.placement = getattr(stages, "placement", "loop")
+        if (self.schedule == "ZBV") != (self.placement == "v"):
+            raise ValueError("the ZBV schedule runs on the V-shaped placement (two chunks per rank), and only it does")
+        # the rank that holds the last stage computes the loss (rank 0 under the V placement)
+        self.loss_rank = owner_of(self.n * self.V - 1, self.n, self.placement)[0]
         # zero-bubble variant: same timetable, every backward leaves its weight-gradient products in a queue
         # that runs while the next tick's exchange (which carries this backward's input gradient) is in flight
-        self.split_backward = schedule.lower() in ("interleavedzerobubble", "zbh1")
+        self.split_backward = schedule.lower() in ("interleavedzerobubble", "zbh1", "zbv", "zbvzerobubble")
         p = next(self.chunks[0].parameters())
         self.device, self.dtype, self.H = p.device, p.dtype, stages.cfg.hidden_size
 
     def run(self, microbatches: list[dict[str, Any]], loss_fn: Optional[Callable] = None, forward_only: bool = False) -> list:
         P, V, M = self.n, self.V, len(microbatches)
         S = P * V
-        table = build_timetable(P, V, M, self.schedule, forward_only)
+        table = build_timetable(P, V, M, self.schedule, forward_only, self.placement)
         Ts = [mb["input_ids"].shape[0] for mb in microbatches]
         inbox: dict = {}             # (kind, mb, stage) -> tensor
         outbox: dict = {}
@@ -510,7 +596,7 @@ class ScheduledPipelineRunner:
             if op is None:
                 continue
             kind, mb, v = op
-            s = v * P + self.rank
+            s = stage_of(self.rank, v, P, self.placement)
             chunk, data = self.chunks[v], microbatches[mb]
             if kind == "F":
                 with torch.set_grad_enabled(not forward_only):
@@ -551,13 +637,15 @@ class ScheduledPipelineRunner:
         if pending:
             OF.flush_wgrad(pending)
         self.sync_tied_embedding_grads()
-        return results if self.rank == P - 1 else []
+        return results if self.rank == self.loss_rank else []
 
     def sync_tied_embedding_grads(self):
         cfg = self.m.cfg
-        if self.n * self.V == 1 or not cfg.tie_word_embeddings or cfg.is_critic or self.rank not in (0, self.n - 1):
+        if self.n * self.V == 1 or not cfg.tie_word_embeddings or cfg.is_critic or self.rank not in (0, self.loss_rank):
             return
         emb = self.chunks[0].embed_tokens if self.rank == 0 else self.chunks[-1].embed_tokens
+        if self.loss_rank == 0 and self.n > 1:
+            return                   # V placement: both uses share one parameter on rank 0, its gradient is already whole
         if self.n == 1:
             # first and last chunk live on the same rank: the two copies are one gradient
             a, b = self.chunks[0].embed_tokens, self.chunks[-1].embed_tokens
@@ -578,6 +666,7 @@ class ScheduledPipelineRunner:
         g.add_(other)
 
     def broadcast_loss(self, loss: Optional[torch.Tensor]) -> torch.Tensor:
-        t = loss.detach().float().reshape(1).to(self.device) if self.rank == self.n - 1 else torch.zeros(1, device=self.device)
-        dist.broadcast(t, src=self.last_rank, group=self.group)
+        lr = getattr(self, "loss_rank", self.n - 1)
+        t = loss.detach().float().reshape(1).to(self.device) if self.rank == lr else torch.zeros(1, device=self.device)
+        dist.broadcast(t, src=self.ranks[lr] if hasattr(self, "ranks") else self.last_rank, group=self.group)
         return t[0]
