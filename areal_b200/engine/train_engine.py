@@ -255,10 +255,13 @@ class B200TrainEngine(TrainEngine):
                 self._pp_group, self._pp_cpu_group = g, gc
         self._mp_group = self._pp_group
         self._cpu_group = dist.new_group(tr, backend="gloo") if use_cuda else self._all_train_group
-        # losses and statistics exist on the last stage only
-        last = [tr[(pp - 1) * dp + d] for d in range(dp)]
+        # losses and statistics exist only on the rank that holds the last stage: the last pipeline rank, or rank 0
+        # under the V-shaped placement of the ZBV schedule (two chunks per rank, down the ranks and back up)
+        sched = str(getattr(self.config.archon, "pp_schedule", "1F1B")).lower()
+        self._pp_loss_rank = 0 if sched in ("zbv", "zbvzerobubble") else pp - 1
+        last = [tr[self._pp_loss_rank * dp + d] for d in range(dp)]
         g = dist.new_group(last, backend="gloo") if dp > 1 else None
-        self._stats_group = g if self.pp_rank == pp - 1 else None
+        self._stats_group = g if self.pp_rank == self._pp_loss_rank else None
         t_ = torch.zeros(1, device=self.device)
         dist.all_reduce(t_, group=self._all_train_group)
         return self
@@ -308,22 +311,25 @@ class B200TrainEngine(TrainEngine):
             self.local_model_config = model_config
             vpp = max(int(getattr(self.parallel, "virtual_pipeline_parallel_size", 0) or 0), int(cfg.megatron.virtual_pipeline_parallel_size or 1), 1)
             sched_name = str(getattr(cfg.archon, "pp_schedule", "1F1B"))
-            if vpp > 1 or sched_name.lower() in ("interleaved1f1b", "interleavedzerobubble"):
-                # virtual stages: several model chunks per rank, interleaved 1F1B on the timetable runner
+            zbv = sched_name.lower() in ("zbv", "zbvzerobubble")
+            if zbv or vpp > 1 or sched_name.lower() in ("interleaved1f1b", "interleavedzerobubble"):
+                # virtual stages: several model chunks per rank, interleaved 1F1B on the timetable runner; ZBV places
+                # its two chunks in a V (first and last stage on rank 0) and orders the operations greedily
                 from ..parallel.pp import InterleavedStages, ScheduledPipelineRunner
 
-                vpp = max(vpp, 2)
+                vpp = 2 if zbv else max(vpp, 2)
                 self.model = InterleavedStages(model_config, self.pp_rank, self.pp_size, vpp, dtype=dtype, device=self.device, seed=seed,
-                                               init_full=loader)
+                                               init_full=loader, placement="v" if zbv else "loop")
                 self._pp_runner = ScheduledPipelineRunner(self.model, self._pp_group,
+                                                          "ZBV" if zbv else
                                                           "GPipe" if sched_name.lower() == "gpipe" else
                                                           "InterleavedZeroBubble" if "zero" in sched_name.lower() or sched_name.lower() == "zbh1"
                                                           else "Interleaved1F1B")
             else:
                 self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader)
                 # zero-bubble names of the reference map to the split-backward 1F1B (input gradients sent on first,
-                # weight gradients in the wait that follows); the V-shaped variant needs virtual stages and is not built
-                sched = {"1f1b": "1F1B", "gpipe": "GPipe", "zbh1": "ZBH1", "zerobubble": "ZBH1", "zbvzerobubble": "ZBH1"}.get(sched_name.lower(), "1F1B")
+                # weight gradients in the wait that follows); the V-shaped variant (ZBV) is the branch above
+                sched = {"1f1b": "1F1B", "gpipe": "GPipe", "zbh1": "ZBH1", "zerobubble": "ZBH1"}.get(sched_name.lower(), "1F1B")
                 self._pp_runner = PipelineRunner(self.model, self._pp_group, schedule=sched)
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
@@ -555,7 +561,7 @@ class B200TrainEngine(TrainEngine):
         return getattr(self, "_pp_group", None)
 
     def is_pipeline_last_stage(self) -> bool:
-        return getattr(self, "pp_size", 1) == 1 or self.pp_rank == self.pp_size - 1
+        return getattr(self, "pp_size", 1) == 1 or self.pp_rank == getattr(self, "_pp_loss_rank", self.pp_size - 1)
 
     @property
     def context_and_model_parallel_group(self):
@@ -759,7 +765,7 @@ class B200TrainEngine(TrainEngine):
         if getattr(self, "pp_size", 1) == 1:
             return outs
         box = [outs if self.is_pipeline_last_stage() else None]
-        src = self._train_ranks[(self.pp_size - 1) * self.dp_size + self.dp_rank]
+        src = self._train_ranks[getattr(self, "_pp_loss_rank", self.pp_size - 1) * self.dp_size + self.dp_rank]
         dist.broadcast_object_list(box, src=src, group=self._pp_cpu_group)
         return box[0]
 

@@ -578,6 +578,10 @@ class ScheduledPipelineRunner:
         for row, delivered in table:
             ops, keep = [], []
             for (src, dst, kind, mb, s) in delivered:
+                if src == self.rank and dst == self.rank:
+                    # consecutive stages on one rank (the turn of the V placement): handed over in place
+                    inbox[(kind, mb, s)] = outbox.pop((kind, mb, s)).contiguous()
+                    continue
                 if src == self.rank:
                     t = outbox.pop((kind, mb, s)).contiguous()
                     keep.append(t)

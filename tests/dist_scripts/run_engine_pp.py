@@ -47,13 +47,14 @@ def cfg_of(backend, vpp=1, schedule="1F1B"):
     return c
 
 
-def check(mc, tag, vpp=1, schedule="1F1B"):
+def check(mc, tag, vpp=1, schedule="1F1B", loss_rank=1):
     rank = dist.get_rank()
     eng = B200TrainEngine(cfg_of("native:d2p2", vpp, schedule))
     eng.create_process_group()
     eng.initialize(model_config=mc, seed=5)
     assert (eng.dp_size, eng.pp_size) == (2, 2) and eng.pp_rank == rank // 2 and eng.dp_rank == rank % 2
     assert eng.is_data_parallel_head() == (rank < 2) and eng.current_data_parallel_head() == rank % 2
+    assert eng.is_pipeline_last_stage() == (eng.pp_rank == loss_rank)
     batch = make_batch(mc.vocab_size)
     d = eng.dp_rank
     mine = {k: v[d * 4:(d + 1) * 4] for k, v in batch.items()}
@@ -106,6 +107,9 @@ def main():
     check(preset("tiny-qwen3", tie_word_embeddings=True), "zero-bubble-tied", schedule="ZBH1")   # split backward, weight gradients deferred
     check(preset("tiny-qwen3", num_layers=4), "interleaved", vpp=2)            # 2 ranks x 2 chunks, one layer each
     check(preset("tiny-qwen3", num_layers=4, tie_word_embeddings=True), "interleaved-tied", vpp=2)
+    # two chunks per rank placed in a V (rank 0 holds the first and the last stage, so the loss lives there), greedy order
+    check(preset("tiny-qwen3", num_layers=4), "zbv", schedule="ZBV", loss_rank=0)
+    check(preset("tiny-qwen3", num_layers=4, tie_word_embeddings=True), "zbv-tied", schedule="ZBV", loss_rank=0)
     print("ENGINE_PP_OK", flush=True)
     dist.barrier()
     dist.destroy_process_group()

@@ -104,3 +104,40 @@ def test_deferred_weight_gradients_match_plain_backward():
     finally:
         OF.SPLIT_BACKWARD = False
     assert w1.grad is None and torch.allclose(w1.main_grad, ref[1], atol=1e-4)
+
+
+@pytest.mark.parametrize("P,M", [(2, 4), (4, 8), (4, 5), (8, 16)])
+def test_zbv_timetable_is_complete_and_respects_dependencies(P, M):
+    """V placement + greedy order: every forward and backward of every (micro-batch, stage) runs exactly once, on the
+    rank that owns the stage, after its input arrived; at most 2 P chunk activations are alive on a rank unless the
+    bound had to be lifted; the table is no longer than the interleaved 1F1B one for the same problem."""
+    from areal_b200.parallel.pp import build_timetable, owner_of, stage_of
+
+    V, S = 2, 2 * P
+    assert [owner_of(s, P, "v") for s in (0, P - 1, P, S - 1)] == [(0, 0), (P - 1, 0), (P - 1, 1), (0, 1)]
+    assert all(owner_of(stage_of(r, v, P, "v"), P, "v") == (r, v) for r in range(P) for v in range(V))
+    table = build_timetable(P, V, M, "ZBV", False, "v")
+    done, have, alive, peak = {}, set(), [0] * P, 0
+    for tick, (row, delivered) in enumerate(table):
+        for (src, dst, kind, mb, s) in delivered:
+            assert owner_of(s, P, "v")[0] == dst
+            have.add((kind, mb, s))
+        for r, op in enumerate(row):
+            if op is None:
+                continue
+            kind, mb, v = op
+            s = stage_of(r, v, P, "v")
+            assert (kind, mb, s) not in done
+            if kind == "F":
+                assert s == 0 or ("act", mb, s) in have
+                alive[r] += 1
+            else:
+                assert ("F", mb, s) in done and (s == S - 1 or ("grad", mb, s) in have)
+                alive[r] -= 1
+            done[(kind, mb, s)] = tick
+            peak = max(peak, alive[r])
+    assert len(done) == 2 * M * S and all(a == 0 for a in alive)
+    assert peak <= 2 * P + 1
+    if M % P == 0:
+        loop = build_timetable(P, V, M, "Interleaved1F1B", False, "loop")
+        assert len(table) <= len(loop) + P
