@@ -52,7 +52,7 @@ def test_forward_logprob_parity_with_cpu(name):
     d_lp = (lp[:699].float().cpu() - lp_ref[:699]).abs()
     d_ent = (ent[:699].float().cpu() - ent_ref[:699]).abs()
     if cfg.is_moe:
-        # a near-tie in the router may pick a different expert in bf16: judge the bulk, not the worst token
+        # a near-tie in the router may pick a different expert in bf16: compare the bulk, not the worst token
         assert d_lp.median().item() < 0.02 and d_lp.mean().item() < 0.05
         assert d_ent.mean().item() < 0.05
     else:

@@ -122,7 +122,7 @@ def test_engine_trains_the_same_with_and_without_prefix_sharing():
 def test_tree_training_on_the_flash_kernels_matches_the_plain_packed_forward():
     """bf16 model on the device: hidden states and parameter gradients of a batch whose groups share long prompts,
     computed over the trie (flash kernels on the gathered layout) and by the plain packed forward + backward, both
-    judged against an fp32 oracle on the host: the trie path is no further from fp32 than bf16 rounding puts the
+    compared with an fp32 oracle on the host: the trie path is no further from fp32 than bf16 rounding puts the
     plain path (the loss sits behind a norm, so several gradients are sums of nearly cancelling terms)."""
     cfg = preset("tiny-qwen3")
     model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=7)
