@@ -8,7 +8,10 @@ partials -> combine (``ab2_logprob_combine``). Backward: local logits are recomp
 into bf16 dlogits with the *global* lse / entropy (``ab2_logprob_bwd`` with the shard's vocab
 offset), fed to the dgrad / wgrad GEMMs; the hidden-state gradient is summed over the group.
 Reference: ``areal/utils/functional/vocab_parallel.py:120-195`` (2-4 all-reduces per chunk:
-MAX, SUM(exp), SUM(target), SUM(exp*z)); here one gather of 16 bytes per row.
+MAX, SUM(exp), SUM(target), SUM(exp*z)); here one gather of 16 bytes per row. With a
+:class:`PartialsExchange` the gather is not a library collective either: every rank stores its
+partials straight into every peer's slot (peer memory over NVLink), a flag barrier follows, and the
+combine kernel reads the slots in place.
 """
 from __future__ import annotations
 
@@ -43,9 +46,45 @@ def combine_partials(parts: torch.Tensor):
     return tz - lse, lse - sz / s, lse
 
 
+class PartialsExchange:
+    """Peer-memory gather of the ``[rows, 4]`` partials of one chunk. Every rank owns a symmetric buffer of
+    ``2 x P x max_rows x 4`` floats; ``gather`` stores this rank's partials into slot ``rank`` of the current half
+    on every peer (one ``push_copy`` launch, 16-byte stores over NVLink), passes a bounded flag barrier and returns
+    the local half ``[P, max_rows, 4]``. The halves alternate: a rank that runs ahead writes the other half while a
+    slower peer still reads this one, and it cannot come back to this half before that peer has reached the next
+    barrier, i.e. finished reading."""
+
+    def __init__(self, group, device, max_rows: int = 4096):
+        from .symm import SymmComm, ptr_array, symm_empty
+
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.max_rows = int(max_rows)
+        self.half = self.world * self.max_rows * 4
+        self.buf, hdl = symm_empty(2 * self.half, torch.float32, device, group)
+        self.buf.zero_()
+        self.comm = SymmComm(group, device)
+        self.ptrs = ptr_array(list(hdl.buffer_ptrs))
+        self.parity = 0
+
+    def gather(self, part: torch.Tensor) -> tuple[torch.Tensor, int]:
+        """part: [n, 4] fp32 (n <= max_rows). Returns (slots [P, max_rows, 4] of this chunk, floats between ranks)."""
+        n = part.shape[0]
+        if n > self.max_rows:
+            raise ValueError(f"chunk of {n} rows exceeds the exchange's {self.max_rows}")
+        off = self.parity * self.half + self.rank * self.max_rows * 4          # in floats
+        # the copy kernel moves 16-byte vectors of 2-byte elements: a float is two of them
+        rc = oplib.get_lib().ab2_push_copy(part.contiguous().data_ptr(), self.ptrs, self.world, 2 * off, 2 * n * 4, oplib.stream_ptr())
+        oplib.check(rc, "ab2_push_copy(partials)")
+        self.comm.barrier(3)
+        view = self.buf[self.parity * self.half:(self.parity + 1) * self.half].view(self.world, self.max_rows, 4)
+        self.parity ^= 1
+        return view, self.max_rows * 4
+
+
 class _VocabParallelLogprob(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, W_shard, labels, temperature, chunk, group, vocab_start):
+    def forward(ctx, h, W_shard, labels, temperature, chunk, group, vocab_start, exchange=None):
         T = h.shape[0]
         Vl = W_shard.shape[0]
         P = dist.get_world_size(group)
@@ -68,15 +107,19 @@ class _VocabParallelLogprob(torch.autograd.Function):
             else:
                 z = (h[a:b].float() @ W_shard.float().t()) / temperature
                 part = _partials_ref(z, lab[a:b], vocab_start)
-            allp = torch.empty(P, n, 4, device=h.device, dtype=torch.float32)
-            if cuda:
+            stride = n * 4
+            allp = None
+            if cuda and exchange is not None:
+                allp, stride = exchange.gather(part)
+            elif cuda:
+                allp = torch.empty(P, n, 4, device=h.device, dtype=torch.float32)
                 dist.all_gather_into_tensor(allp.view(P * n, 4), part, group=group)
             else:
                 gathered = [torch.empty_like(part) for _ in range(P)]
                 dist.all_gather(gathered, part.contiguous(), group=group)
                 allp = torch.stack(gathered)
             if cuda:
-                oplib.check(L.ab2_logprob_combine(allp.data_ptr(), P, n * 4, logp[a:b].data_ptr(), ent[a:b].data_ptr(),
+                oplib.check(L.ab2_logprob_combine(allp.data_ptr(), P, stride, logp[a:b].data_ptr(), ent[a:b].data_ptr(),
                                                   lse[a:b].data_ptr(), n, oplib.stream_ptr()), "ab2_logprob_combine")
             else:
                 logp[a:b], ent[a:b], lse[a:b] = combine_partials(allp)
@@ -125,14 +168,16 @@ class _VocabParallelLogprob(torch.autograd.Function):
                 dW += dz.t() @ h[a:b].float()
         dist.all_reduce(dh, group=group)                    # every shard contributes to d hidden
         dW_ret = None if mg is not None else dW.to(W.dtype)
-        return dh.to(h.dtype), dW_ret, None, None, None, None, None
+        return dh.to(h.dtype), dW_ret, None, None, None, None, None, None
 
 
 def vocab_parallel_lm_head_logprob(h: torch.Tensor, W_shard: torch.Tensor, labels: torch.Tensor, group, temperature: float = 1.0,
-                                   chunk: int = 2048, vocab_start: Optional[int] = None):
+                                   chunk: int = 2048, vocab_start: Optional[int] = None, exchange: Optional[PartialsExchange] = None):
     """``(logp[label], entropy)`` of ``softmax(h @ W^T / temperature)`` with ``W`` split by rows
     over ``group`` (rank r holds rows ``[r * V/P, (r+1) * V/P)`` unless ``vocab_start`` says
     otherwise). ``h`` and ``labels`` are identical on every rank of the group."""
     if vocab_start is None:
         vocab_start = dist.get_rank(group) * W_shard.shape[0]
-    return _VocabParallelLogprob.apply(h, W_shard, labels, temperature, chunk, group, vocab_start)
+    if exchange is not None and chunk > exchange.max_rows:
+        chunk = exchange.max_rows
+    return _VocabParallelLogprob.apply(h, W_shard, labels, temperature, chunk, group, vocab_start, exchange)

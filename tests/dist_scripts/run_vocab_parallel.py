@@ -8,7 +8,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 from areal_b200.ops import functional as OF  # noqa: E402
-from areal_b200.parallel.vocab_parallel import vocab_parallel_lm_head_logprob  # noqa: E402
+from areal_b200.parallel.vocab_parallel import PartialsExchange, vocab_parallel_lm_head_logprob  # noqa: E402
 
 
 def main():
@@ -42,6 +42,18 @@ def main():
     rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item()
     assert rel(h.grad, h2.grad) < (3e-2 if use_cuda else 1e-4), rel(h.grad, h2.grad)
     assert rel(Ws.grad, W2.grad[rank * Vl:(rank + 1) * Vl]) < (3e-2 if use_cuda else 1e-4)
+    if use_cuda:
+        # the same with the partials exchanged through peer memory instead of an NCCL all-gather: same bits
+        from areal_b200.ops import lib as oplib
+
+        ex = PartialsExchange(dist.group.WORLD, dev, max_rows=128)
+        lp3, ent3 = vocab_parallel_lm_head_logprob(h.detach(), Ws.detach(), labels, dist.group.WORLD, temperature=0.7, chunk=128, exchange=ex)
+        torch.cuda.synchronize()
+        assert oplib.kernel_error() == 0
+        assert torch.equal(lp3, lp.detach()) and torch.equal(ent3, ent.detach())
+        lp4, _ = vocab_parallel_lm_head_logprob(h.detach(), Ws.detach(), labels, dist.group.WORLD, temperature=0.7, chunk=100, exchange=ex)
+        assert (lp4.float() - lp2).abs().max() < tol
+        print("VP_PEER_OK", flush=True)
     print("VP_OK", flush=True)
     dist.destroy_process_group()
 

@@ -107,3 +107,12 @@ def test_engine_tensor_parallel_sequence_parallel_fused_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_tp_sp_gpu.py"), 2, 29793, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("ENGINE_TP_SP_GPU_OK") == 2
+
+
+def test_vocab_parallel_head_partials_over_peer_memory_two_gpus():
+    """Vocabulary-parallel log-probs and entropy on 2 GPUs against the fp32 full-softmax oracle, with the per-row
+    partials gathered by NCCL and by peer stores + flag barrier (``PartialsExchange``): both forms give the same bits."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_vocab_parallel.py"), 2, 29795, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("VP_OK") == 2 and r.stdout.count("VP_PEER_OK") == 2
