@@ -448,8 +448,8 @@ class B200TrainEngine(TrainEngine):
             self.optimizer = ShardedAdamW(self.store, cfg.optimizer, total_steps=total, group=self._shard_group)
             if self.expert_store is not None:
                 self.expert_optimizer = ShardedAdamW(self.expert_store, cfg.optimizer, total_steps=total, group=self._edp_group)
-        if self.sp_size * tp > 1 and model_config.is_vlm:
-            raise NotImplementedError("vision-language models run data-parallel only (no sequence / tensor parallelism yet)")
+        if model_config.is_vlm and (tp > 1 or (self.sp_size > 1 and getattr(cfg.fsdp, "context_parallel", "ulysses") != "ulysses")):
+            raise NotImplementedError("vision-language models run with data and Ulysses sequence parallelism (no tensor / zig-zag split yet)")
         self._cp_zigzag = self.sp_size > 1 and getattr(cfg.fsdp, "context_parallel", "ulysses") == "zigzag"
         self._zz_perm = None
         if getattr(cfg.fsdp, "context_parallel", "ulysses") not in ("ulysses", "zigzag"):
@@ -464,7 +464,7 @@ class B200TrainEngine(TrainEngine):
             install_ulysses(self.model, self._sp_group, self.sp_size, self.sp_rank)
             self._sp_fused = None
             mc = model_config
-            if (on_gpu and cfg.fsdp.fuse_ulysses_projections and not self.use_lora and tp == 1 and self.sp_size <= 8 and not getattr(mc, "is_hybrid", False)
+            if (on_gpu and cfg.fsdp.fuse_ulysses_projections and not self.use_lora and tp == 1 and self.sp_size <= 8 and not getattr(mc, "is_hybrid", False) and not mc.is_vlm
                     and mc.num_heads % sp == 0 and mc.num_kv_heads % sp == 0 and not mc.attention_bias and mc.head_dim in (64, 128)
                     and ((mc.num_heads + 2 * mc.num_kv_heads) // sp * mc.head_dim) % 64 == 0):
                 from ..parallel.tp_fused import FusedUlyssesLinear
@@ -662,7 +662,15 @@ class B200TrainEngine(TrainEngine):
             pb_local = PackedBatch(cu, pos[sl], T, pb.max_seqlen)
             pb_local.tile_info = pb.tile_info
             pb_local.full_position_ids = pb.position_ids
-            hidden = self.model.forward_hidden(ids[sl], pb_local)
+            if getattr(self.model.cfg, "is_vlm", False):
+                from ..models.vlm import collect_multi_modal
+
+                mm = collect_multi_modal(mb.get("multi_modal_input"))
+                if mm is not None:
+                    mm = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mm.items()}
+                hidden = self.model.forward_hidden(ids, pb_local, mm=mm, row_slice=sl)
+            else:
+                hidden = self.model.forward_hidden(ids[sl], pb_local)
             return hidden, labels[sl], sl
         if getattr(self.model.cfg, "is_vlm", False):
             from ..models.vlm import collect_multi_modal

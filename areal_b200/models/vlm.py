@@ -96,10 +96,16 @@ class VisionLanguageModel(CausalLM):
         out = h.index_copy(0, positions, feats.to(h.dtype))
         return (out, (positions, taps) if taps else None) if with_deepstack else out
 
-    def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None, mm: Optional[dict[str, Any]] = None, **kw) -> torch.Tensor:
+    def forward_hidden(self, input_ids: torch.Tensor, pb: PackedBatch, attn_fns=None, mm: Optional[dict[str, Any]] = None,
+                       row_slice: Optional[slice] = None, **kw) -> torch.Tensor:
+        """``row_slice`` (sequence parallelism): ``input_ids`` holds ALL tokens of the micro-batch, the layers run on
+        rows ``row_slice`` only. Embeddings, image features and the per-token rotary tables are made for the whole
+        micro-batch on every rank (the image tower is small beside the language model) and cut to the rows; ``pb`` is
+        the local batch descriptor (full ``cu_seqlens``)."""
+        sl = row_slice
         if mm is None or mm.get("pixel_values") is None or mm["pixel_values"].numel() == 0:
             # text only: the three streams coincide and M-RoPE is ordinary RoPE
-            return super().forward_hidden(input_ids, pb, attn_fns, **kw)
+            return super().forward_hidden(input_ids if sl is None else input_ids[sl], pb, attn_fns, **kw)
         T = input_ids.shape[0]
         pos3, where = mm.get("mrope_position_ids"), mm.get("image_positions")
         if pos3 is None:
@@ -108,6 +114,13 @@ class VisionLanguageModel(CausalLM):
         sections = self.cfg.mrope_section or [self.cfg.head_dim // 2, 0, 0]
         cos, sin = mrope_tables(pos3, self.cfg.head_dim, self.cfg.rope_theta, sections, input_ids.device, self.cfg.mrope_interleaved)
         pb2 = copy.copy(pb)
-        pb2.position_ids = torch.arange(T, dtype=torch.int32, device=input_ids.device)   # row t of the per-token tables
+        rows = torch.arange(T, dtype=torch.int32, device=input_ids.device)   # row t of the per-token tables
         embeds, deep = self.embed_multimodal(input_ids, mm, where, with_deepstack=True)
+        if sl is not None:
+            rows, embeds, input_ids = rows[sl], embeds[sl], input_ids[sl]
+            if deep is not None:
+                idx, feats = deep
+                keep = (idx >= sl.start) & (idx < sl.stop)
+                deep = (idx[keep] - sl.start, [f[keep] for f in feats])
+        pb2.position_ids = rows
         return super().forward_hidden(input_ids, pb2, attn_fns, inputs_embeds=embeds, rope=(cos, sin), deepstack=deep)

@@ -119,3 +119,15 @@ def test_hybrid_linear_attention_stack_under_ulysses_matches_single_rank():
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("SP_GSPO_OK") == 2
+
+
+def test_vision_language_model_under_ulysses_matches_single_rank():
+    """Qwen2.5-VL and Qwen3-VL (deep-stack features) with the tokens of a micro-batch split over two ranks: image
+    features and per-token rotary tables are made for the whole micro-batch and cut to the local rows; losses, gradient
+    norms, the update and forward-only log-probs equal the single-rank engine."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29993", os.path.join(ROOT, "tests", "dist_scripts", "run_vlm_sp.py")],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=500)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("VLM_SP_OK") == 2
