@@ -1,7 +1,9 @@
 """Sharded engine checkpoints for recovery: every rank writes its own slice of the flat
 parameter space (weights in compute dtype, fp32 master, Adam moments) as one safetensors file
 plus a small JSON manifest; loading re-assembles by flat offsets, so a checkpoint can be read
-back under the same sharding without any gather. HF export is separate
+back under the same sharding without any gather, and under ANOTHER data-parallel world size by
+reading, from every saved shard, the part of its range that overlaps the new rank's range (tensor
+offsets in the flat space do not depend on the world size; only the tail padding does). HF export is separate
 (:mod:`areal_b200.models.hf_io`). Plays the role of the DCP checkpoints of the reference
 (``areal/engine/fsdp_engine.py:1834-1881``)."""
 from __future__ import annotations
@@ -42,15 +44,69 @@ def save_sharded(engine, path: str, with_optim: bool = True) -> None:
         dist.barrier(group=engine.cpu_group)
 
 
+def _load_resharded(engine, path: str, with_optim: bool) -> None:
+    """The checkpoint was written by another number of data-parallel ranks: every rank fills its range of the flat
+    space from the saved shards that overlap it."""
+    import glob
+
+    from safetensors.torch import load_file
+
+    st = engine.store
+    if getattr(engine, "expert_store", None) is not None:
+        raise ValueError("an expert-parallel checkpoint must be reloaded under the layout that wrote it; export to HF instead")
+    metas = []
+    for fn in sorted(glob.glob(os.path.join(path, "shard-*.json"))):
+        with open(fn) as f:
+            metas.append((int(os.path.basename(fn)[6:11]), json.load(f)))
+    if not metas:
+        raise FileNotFoundError(f"no sharded checkpoint under {path}")
+    m0 = metas[0][1]
+    if m0["names"] != st.names or m0["offsets"] != st.offsets or m0["numel"] != st.numel:
+        raise ValueError("sharded checkpoint holds another model or another model-parallel slice; export to HF and reload instead")
+    if len(metas) != m0["world_size"]:
+        raise ValueError(f"sharded checkpoint is incomplete: {len(metas)} of {m0['world_size']} shards")
+    lo, hi = st.shard_range
+    opt = engine.optimizer
+    want_opt = with_optim and opt is not None
+    st.param_shard.zero_()
+    got_opt = True
+    if want_opt:
+        for t in (opt.master, opt.exp_avg, opt.exp_avg_sq):
+            t.zero_()
+    for r, meta in metas:
+        a, b = meta["shard_range"]
+        x, y = max(a, lo), min(b, hi)
+        if x >= y:
+            continue
+        tensors = load_file(os.path.join(path, f"shard-{r:05d}-of-{meta['world_size']:05d}.safetensors"))
+        st.param_shard[x - lo:y - lo].copy_(tensors["param_shard"][x - a:y - a].to(st.dtype))
+        if want_opt and "master" in tensors:
+            for name, dst in (("master", opt.master), ("exp_avg", opt.exp_avg), ("exp_avg_sq", opt.exp_avg_sq)):
+                dst[x - lo:y - lo].copy_(tensors[name][x - a:y - a].to(dst.dtype))
+        else:
+            got_opt = False
+    if st.world_size > 1:
+        dist.all_gather_into_tensor(st.flat_param, st.param_shard.clone(), group=engine._shard_group)
+    if opt is not None:
+        if want_opt and got_opt:
+            opt.step_count, opt.sched_step = int(m0.get("step_count", 0)), int(m0.get("sched_step", 0))
+        else:
+            opt.resync_master()
+    engine.set_version(int(m0.get("version", 0)))
+
+
 def load_sharded(engine, path: str, with_optim: bool = True) -> None:
     from safetensors.torch import load_file
 
     st = engine.store
     r = max(engine.local_index, 0)
-    with open(os.path.join(path, f"shard-{r:05d}.json")) as f:
+    mine = os.path.join(path, f"shard-{r:05d}.json")
+    if not os.path.exists(mine):
+        return _load_resharded(engine, path, with_optim)          # more ranks now than wrote the checkpoint
+    with open(mine) as f:
         meta = json.load(f)
     if meta["world_size"] != st.world_size or meta["padded"] != st.padded:
-        raise ValueError("sharded checkpoint was written with a different layout; export to HF and reload instead")
+        return _load_resharded(engine, path, with_optim)
     tensors = load_file(os.path.join(path, f"shard-{r:05d}-of-{st.world_size:05d}.safetensors"))
     st.param_shard.copy_(tensors["param_shard"].to(st.dtype))
     if st.world_size > 1:

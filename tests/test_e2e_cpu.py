@@ -368,3 +368,16 @@ def test_colocated_loop_runs_a_hundred_steps_within_the_staleness_bound(tmp_path
     assert max(h["ppo_actor/update/staleness/max"] for h in hist) <= 2 + 1e-6
     lens = {round(h["ppo_actor/seq_len/avg"], 2) for h in hist}
     assert len(lens) > 5                                           # the samples of a group really have different lengths
+
+
+@pytest.mark.parametrize("n_load", [1, 3])
+def test_sharded_checkpoint_reloads_under_another_world_size(tmp_path, n_load):
+    """A recovery checkpoint written by two data-parallel ranks is read back by one and by three: parameters, fp32
+    master weights, both Adam moments, step count and version arrive bit for bit, and training carries on."""
+    script = os.path.join(ROOT, "tests", "dist_scripts", "run_reshard_ckpt.py")
+    for phase, n, port in (("save", 2, 29961), ("load", n_load, 29963 + n_load)):
+        env = dict(os.environ, OMP_NUM_THREADS="1", CKPT_DIR=str(tmp_path), PHASE=phase)
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+                            "--master-port", str(port), script], cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert r.stdout.count("RESHARD_OK") == n
