@@ -79,13 +79,59 @@ class VisionLanguageModel(CausalLM):
             img += k
         return pos, deltas, torch.tensor(where, dtype=torch.long)
 
+    vision_sp = None     # (group, size, rank) set by the train engine: the pictures of a micro-batch are split over the group
+
+    def _image_features(self, px: torch.Tensor, grid: torch.Tensor):
+        """Features of all pictures ``[n_tokens, H]`` (+ deep-stack taps). Under sequence parallelism every rank of
+        the group runs the tower on a contiguous share of the pictures (balanced by patch count) and the features are
+        all-gathered; the backward pass sums the feature gradients of all ranks onto the rank that made them (role of
+        the reference's ``vision_sp_shard.py``, which all-gathers the tower's outputs over the SP group)."""
+        want_taps = bool(self.vcfg.deepstack_visual_indexes)
+
+        def tower(p, g):
+            if want_taps:
+                return self.visual(p, g, return_deepstack=True)
+            return self.visual(p, g), None
+        sp = self.vision_sp
+        n_img = int(grid.shape[0])
+        if sp is None or sp[1] <= 1 or n_img < 2:
+            return tower(px, grid)
+        from ..parallel.cp import _AllGatherCat
+
+        group, size, rank = sp
+        patches = grid.long().prod(-1).tolist()
+        merge = self.vcfg.spatial_merge_size ** 2
+        # contiguous shares with about equal patch counts
+        total, bounds, acc = sum(patches), [0], 0
+        for i, n in enumerate(patches):
+            acc += n
+            while len(bounds) < size and acc >= total * len(bounds) / size:
+                bounds.append(i + 1)
+        bounds += [n_img] * (size + 1 - len(bounds))
+        bounds[-1] = n_img
+        tok = [sum(patches[bounds[r]:bounds[r + 1]]) // merge for r in range(size)]
+        i0, i1 = bounds[rank], bounds[rank + 1]
+        pa = sum(patches[:i0])
+        H = self.embed_tokens.shape[1]
+        if i1 > i0:
+            f, t = tower(px[pa:pa + sum(patches[i0:i1])], grid[i0:i1])
+        else:
+            # no picture for this rank: an empty slice of a parameter keeps the gather below inside this rank's autograd
+            # graph, so its backward (a collective) runs here as it does on the peers
+            f = self.embed_tokens[:0]
+            t = [self.embed_tokens[:0] for _ in self.vcfg.deepstack_visual_indexes] if want_taps else None
+        Lmax = max(tok)
+
+        def gather(x):
+            pad = x.new_zeros(Lmax, x.shape[1])
+            pad = torch.cat([x, pad[: Lmax - x.shape[0]]], 0) if x.shape[0] < Lmax else x
+            full = _AllGatherCat.apply(pad.contiguous(), group)
+            return torch.cat([full[r * Lmax: r * Lmax + tok[r]] for r in range(size)], 0)
+        return gather(f), ([gather(x) for x in t] if want_taps else None)
+
     def embed_multimodal(self, input_ids: torch.Tensor, mm: dict[str, Any], positions: Optional[torch.Tensor] = None,
                          with_deepstack: bool = False):
-        taps = None
-        if self.vcfg.deepstack_visual_indexes:
-            feats, taps = self.visual(mm["pixel_values"].to(self.embed_tokens.dtype), mm["image_grid_thw"], return_deepstack=True)
-        else:
-            feats = self.visual(mm["pixel_values"].to(self.embed_tokens.dtype), mm["image_grid_thw"])
+        feats, taps = self._image_features(mm["pixel_values"].to(self.embed_tokens.dtype), mm["image_grid_thw"])
         h = OF.embedding(input_ids, self.embed_tokens)
         if positions is None:
             mask = (input_ids == self.cfg.image_token_id) | (input_ids == self.cfg.video_token_id)
