@@ -68,6 +68,24 @@ def sse_lines(url: str, body: dict, api_key: Optional[str] = None, timeout: floa
                 name = None
 
 
+class Raw:
+    """A handler's answer sent as bytes (``application/octet-stream`` unless told otherwise)."""
+
+    def __init__(self, body: bytes, ctype: str = "application/octet-stream"):
+        self.body, self.ctype = body, ctype
+
+
+def fetch_bytes(url: str, api_key: Optional[str] = None, timeout: float = 600.0) -> bytes:
+    req = urllib.request.Request(url, headers={"Authorization": f"Bearer {api_key}"} if api_key else {})
+    try:
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return r.read()
+    except urllib.error.HTTPError as e:
+        raise HTTPError(e.code, e.read().decode(errors="replace")[:200])
+    except (urllib.error.URLError, ConnectionError, OSError) as e:
+        raise HTTPError(503, f"{url} unreachable: {e!r}")
+
+
 class JsonService:
     """``svc.route("POST", "/x")(fn)``; path segments ``{name}`` capture into ``ctx.params``."""
 
@@ -154,6 +172,13 @@ class JsonService:
                     res = fn(body, RequestCtx(self._key(), self.path, params, self.headers))
                     if isinstance(res, SSE):
                         return self._stream(res.events)
+                    if isinstance(res, Raw):
+                        self.send_response(200)
+                        self.send_header("Content-Type", res.ctype)
+                        self.send_header("Content-Length", str(len(res.body)))
+                        self.end_headers()
+                        self.wfile.write(res.body)
+                        return
                     if isinstance(res, tuple):
                         return self._reply(res[0], res[1])
                     return self._reply(200, res if res is not None else {"ok": True})

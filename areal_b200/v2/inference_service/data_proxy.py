@@ -137,6 +137,24 @@ class DataProxy:
             self.engine.set_version(int(body["version"]))
             return {"ok": True}
 
+        @svc.route("POST", "/update_weights_from_http")
+        def update_http(body, ctx):
+            # pulls the trainer's weight dictionary (torch.save bytes) and hands it to the engine; the caller has paused
+            # generation, or the engine swaps at its next step boundary
+            import io
+
+            import torch
+
+            from ..common import fetch_bytes
+
+            named = torch.load(io.BytesIO(fetch_bytes(body["url"], timeout=float(body.get("timeout_s", 600)))), map_location="cpu", weights_only=True)
+            res = self.engine.update_weights_from_tensors(named)
+            if hasattr(res, "result"):
+                res.result()
+            if body.get("version") is not None:
+                self.engine.set_version(int(body["version"]))
+            return {"ok": True, "tensors": len(named)}
+
         @svc.route("POST", "/release_memory")
         def release(body, ctx):
             self.engine.offload(body.get("tags"))

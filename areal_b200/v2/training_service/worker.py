@@ -97,6 +97,25 @@ class TrainingWorker:
             self._run(lambda: eng.load(deserialize_value(body)["meta"]))
             return {"ok": True}
 
+        @svc.route("GET", "/weights")
+        def weights(body, ctx):
+            # the complete weight dictionary by parameter name (gathered over the model-parallel ranks by the engine),
+            # serialised once per version: every inference worker of a pair pulls the same bytes
+            import io
+
+            import torch
+
+            from ..common import Raw
+
+            v = eng.get_version()
+            cached = getattr(self, "_weights_cache", None)
+            if cached is None or cached[0] != v:
+                w = self._run(eng.export_weights)
+                buf = io.BytesIO()
+                torch.save({k: t.detach().cpu() for k, t in w.items()}, buf)
+                cached = self._weights_cache = (v, buf.getvalue())
+            return Raw(cached[1])
+
         @svc.route("POST", "/set_version")
         def set_version(body, ctx):
             self._run(lambda: eng.set_version(int(body["version"])))

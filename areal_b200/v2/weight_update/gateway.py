@@ -6,8 +6,8 @@
     GET  /weight_meta/{pair}/{key}
 
 ``disk``: trainers ``/save`` a Hugging Face checkpoint under ``path/v{version}``, inference
-workers load it. ``http``: inference RPC workers pull the exported tensors of trainer 0 through
-the remote-tensor store. Generation is paused around the swap and the new version is
+workers load it. ``http``: inference workers pull the weight dictionary that trainer 0 exports
+(``GET /weights``, serialised once per version) and hand it to their engine; no shared file system is needed. Generation is paused around the swap and the new version is
 published to both sides. Shard-direct GPU transfers (peer-memory push) are driven in-process
 by ``areal_b200.parallel.weight_push`` when trainer and rollout ranks share a world.
 Reference: ``areal/v2/weight_update/{gateway/app.py, controller.py}``."""
@@ -47,7 +47,7 @@ class WeightUpdateGateway:
         @svc.route("POST", "/connect")
         def connect(body, ctx):
             mode = body.get("mode", "disk")
-            if mode not in ("disk",):
+            if mode not in ("disk", "http"):
                 raise HTTPError(400, f"mode '{mode}' is not served by the gateway (GPU-direct modes run inside the shared world)")
             if mode == "disk" and not body.get("path"):
                 raise HTTPError(400, "disk mode needs a shared 'path'")
@@ -80,6 +80,22 @@ class WeightUpdateGateway:
             p = self._pair(body["pair"])
             version = int(body["version"])
             t0 = time.time()
+            if p["mode"] == "http":
+                for a in p["infer_workers"]:
+                    call(f"http://{a}/pause_generation", {})
+                try:
+                    src = p["train_workers"][0]                # export_weights gathers the whole model on every trainer
+                    for a in p["train_workers"]:
+                        call(f"http://{a}/set_version", {"version": version})
+                    n = [call(f"http://{a}/update_weights_from_http", {"url": f"http://{src}/weights", "version": version})["tensors"]
+                         for a in p["infer_workers"]]
+                finally:
+                    for a in p["infer_workers"]:
+                        call(f"http://{a}/continue_generation", {})
+                p["version"] = version
+                p["history"].append({"version": version, "seconds": time.time() - t0})
+                p["meta"]["tensors"] = n[0] if n else 0
+                return {"ok": True, "version": version, "seconds": time.time() - t0}
             ckpt = os.path.join(p["path"], f"v{version}")
             for a in p["infer_workers"]:
                 call(f"http://{a}/pause_generation", {})

@@ -211,6 +211,41 @@ def test_weight_update_gateway_disk_flow(tmp_path):
         gw.stop(); infer.stop(); tw.stop()
 
 
+def test_weight_update_gateway_http_flow_moves_real_weights():
+    """``mode: http``: the inference worker pulls the trainer's weight dictionary over HTTP and its engine swaps it in;
+    a real train engine and a real inference engine (tiny model, CPU) end up with identical parameters and versions."""
+    import torch
+
+    from areal_b200.api.cli_args import InferenceEngineConfig, MicroBatchSpec, NativeInferConfig, OptimizerConfig, TrainEngineConfig
+    from areal_b200.engine.infer_engine import NativeInferenceEngine
+    from areal_b200.engine.train_engine import B200TrainEngine
+    from areal_b200.models.config import preset
+    from areal_b200.v2.inference_service.data_proxy import DataProxy
+
+    mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+    tr = B200TrainEngine(TrainEngineConfig(init_from_scratch=True, dtype="float32", optimizer=OptimizerConfig(lr=1e-2),
+                                           mb_spec=MicroBatchSpec(max_tokens_per_mb=128)))
+    tr.create_process_group()
+    tr.initialize(model_config=mc, seed=1)
+    inf = NativeInferenceEngine(InferenceEngineConfig(), NativeInferConfig(max_running_requests=4, page_size=16, context_length=64, num_pages=32),
+                                model_config=mc).initialize(seed=2, start_executor=False)
+    name = "layers.0.mlp.down_proj"
+    assert not torch.equal(dict(inf.model.named_parameters())[name], dict(tr.model.named_parameters())[name])
+    tw = TrainingWorker(tr).start()
+    dp = DataProxy(inf, ByteTok(), GenerationHyperparameters(max_new_tokens=4)).start()
+    gw = WeightUpdateGateway().start()
+    try:
+        call(f"{gw.svc.url}/connect", {"pair": "p", "train_workers": [tw.address], "infer_workers": [dp.address], "mode": "http"})
+        r = call(f"{gw.svc.url}/update_weights", {"pair": "p", "version": 5})
+        assert r["ok"] and r["version"] == 5
+        for (n, a), (_, b) in zip(tr.model.named_parameters(), inf.model.named_parameters()):
+            assert torch.equal(a.detach(), b.detach()), n
+        assert tr.get_version() == 5 and inf.get_version() == 5
+        assert call(f"{gw.svc.url}/weight_meta/p/tensors")["tensors"] == len(list(tr.model.named_parameters()))
+    finally:
+        gw.stop(); dp.stop(); tw.stop(); inf.destroy(); tr.destroy()
+
+
 def test_cli_state_roundtrip(tmp_path, monkeypatch, capsys):
     monkeypatch.setattr(cli, "STATE", str(tmp_path / "st.json"))
     svc = JsonService("x")
