@@ -421,3 +421,31 @@ def test_proxy_gateway_spreads_sessions_and_relays_to_the_owner():
         assert h["open_sessions"] == [1, 1]
     finally:
         gw.stop(); pa.stop(); pb.stop()
+
+
+def test_anthropic_shaped_client_records_turns_with_tools():
+    from areal_b200.openai.anthropic_client import ArealAnthropic
+
+    call_text = 'sure <tool_call>{"name": "calc", "arguments": {"x": 2}}</tool_call>'
+    eng = ScriptedEngine([call_text, "the answer is 4"])
+    cl = ArealAnthropic(eng, ByteTok(), gconfig=GenerationHyperparameters(max_new_tokens=64))
+    tools = [{"name": "calc", "description": "doubles", "input_schema": {"type": "object", "properties": {"x": {"type": "integer"}}}}]
+
+    async def episode():
+        r1 = await cl.messages.create(model="m", max_tokens=128, system="be terse", tools=tools,
+                                      messages=[{"role": "user", "content": "double 2"}])
+        assert r1.stop_reason == "tool_use" and r1.content[-1].type == "tool_use" and r1.content[-1].input == {"x": 2}
+        r2 = await cl.messages.create(model="m", max_tokens=32, system="be terse", tools=tools, messages=[
+            {"role": "user", "content": "double 2"},
+            {"role": "assistant", "content": [{"type": "tool_use", "id": r1.content[-1].id, "name": "calc", "input": {"x": 2}}]},
+            {"role": "user", "content": [{"type": "tool_result", "tool_use_id": r1.content[-1].id, "content": "4"}]}])
+        assert r2.stop_reason == "end_turn" and r2.content[0].text == "the answer is 4" and r2.usage.output_tokens > 0
+        cl.set_last_reward(1.0)
+        return r1, r2
+    r1, r2 = asyncio.run(episode())
+    inter = cl.export_interactions("individual", reward_discount=0.5)
+    assert set(inter) == {r1.id, r2.id} and inter[r2.id].reward == 1.0 and inter[r1.id].reward == 0.5
+    batch = cl.to_trajectory("individual")
+    assert batch["input_ids"].shape[0] == 2 and batch["loss_mask"].sum() > 0
+    with pytest.raises(NotImplementedError):
+        asyncio.run(cl.messages.create(messages=[], max_tokens=1, stream=True))
