@@ -117,3 +117,11 @@ def test_example_configs_parse_and_backend_extras_are_kept():
     cfg = to_structured_cfg(raw, GRPOConfig)
     assert cfg.sglang.extra == {"enable_dp_attention": True} and cfg.actor.megatron.extra == {"recompute_method": "uniform"}
     assert cfg.actor.use_kernels is False and cfg.rollout.poll_interval == 0.1
+
+
+def test_config_reference_is_generated_from_the_dataclasses():
+    from areal_b200.tools import generate_cli_docs as G
+
+    text = G.render()
+    assert "## PPOActorConfig" in text and "`prox_logp_method`" in text and "`context_parallel`" in text
+    assert G.main(["--check"]) == 0, "docs/config_reference.md is out of date: python -m areal_b200.tools.generate_cli_docs"
