@@ -51,8 +51,14 @@ async def arequest_with_retry(session, addr: str, endpoint: str, payload: Option
 
 
 class RemoteInfEngine(InferenceEngine):
-    def __init__(self, config: InferenceEngineConfig, addresses: Optional[list[str]] = None):
+    def __init__(self, config: InferenceEngineConfig, addresses: Optional[list[str]] = None, backend: Optional[str] = None):
+        """``backend``: wire format of the servers (``native`` | ``sglang`` | ``vllm``, see ``remote_backends.py``);
+        default: ``config.backend`` if it names one, else this repository's server."""
+        from .remote_backends import BACKENDS, get_backend
+
         self.config = config
+        name = backend if backend is not None else (getattr(config, "backend", "") or "")
+        self.backend = get_backend(name.split(":")[0] if name.split(":")[0].lower() in BACKENDS else "native")
         self.addresses: list[str] = list(addresses or [])
         self._version = 0
         self._rr = 0
@@ -199,21 +205,19 @@ class RemoteInfEngine(InferenceEngine):
         while stop not in ("stop", "length", "tool_calls") and len(out_tok) < budget:
             while self._paused.is_set():
                 await asyncio.sleep(0.01)
-            payload = {"rid": req.rid, "input_ids": prompt + out_tok, "return_logprob": True,
-                       "sampling_params": {"max_new_tokens": budget - len(out_tok), "min_new_tokens": max(0, g.min_new_tokens - len(out_tok)),
-                                           "temperature": 0.0 if g.greedy else g.temperature, "top_p": g.top_p,
-                                           "top_k": -1 if g.top_k >= 10 ** 7 else g.top_k, "stop_token_ids": g.stop_token_ids,
-                                           "ignore_eos": g.ignore_eos, "seed": g.seed}}
-            r = await arequest_with_retry(session, addr, "/generate", payload, max_retries=self.config.request_retries,
+            version_sent = self._version          # a weight update may land while the request is in flight
+            hr = self.backend.build_generation(req.rid, prompt + out_tok, g, budget, len(out_tok))
+            r = await arequest_with_retry(session, addr, hr.endpoint, hr.payload, method=hr.method, max_retries=self.config.request_retries,
                                           timeout=self.config.request_timeout)
-            seg = r.get("output_ids", [])
+            res = self.backend.parse_generation(r)
+            seg = res.tokens
             if seg and ttft == float("inf"):
                 ttft = time.perf_counter() - t0
-            vers = r.get("output_versions") or [self._version] * len(seg)
             out_tok += seg
-            out_lp += r.get("output_logprobs", [0.0] * len(seg))
-            out_ver += vers
-            stop = r["meta_info"]["finish_reason"]["type"]
+            out_lp += res.logprobs if len(res.logprobs) == len(seg) else [0.0] * len(seg)
+            # servers that do not tag tokens: the version that was current when the request left served it
+            out_ver += res.versions or [version_sent] * len(seg)
+            stop = res.stop_reason
             if stop == "abort" and not seg:
                 await asyncio.sleep(0.02)     # server is paused for a weight update
         if stop == "abort":
@@ -257,50 +261,65 @@ class RemoteInfEngine(InferenceEngine):
         threading.Thread(target=run, daemon=True).start()
         return fut
 
+    def _requests_future(self, request_fns: list, after=None) -> Future:
+        """Sends, one after the other, the requests ``request_fns[k](server index)`` to every server."""
+        fut: Future = Future()
+
+        def run():
+            try:
+                out = []
+                for fn in request_fns:
+                    first = fn(0)
+                    out = self._fanout_future(first.endpoint, lambda i, fn=fn: fn(i).payload).result()
+                if after:
+                    after()
+                fut.set_result(out)
+            except BaseException as e:
+                fut.set_exception(e)
+        threading.Thread(target=run, daemon=True).start()
+        return fut
+
     def set_version(self, version: int) -> None:
         self._version = version
-        self._fanout("/set_version", {"version": version})
+        hr = self.backend.set_version(version)
+        if hr is not None:
+            self._fanout(hr.endpoint, hr.payload)
 
     def get_version(self) -> int:
         return self._version
 
     def pause_generation(self):
         self._paused.set()
-        self._fanout("/pause_generation")
+        self._fanout(self.backend.pause_endpoint)
 
     def continue_generation(self):
-        self._fanout("/continue_generation")
+        self._fanout(self.backend.continue_endpoint)
         self._paused.clear()
 
     def update_weights_from_disk(self, meta: WeightUpdateMeta) -> Future:
         def done():
             if meta.version is not None:
                 self._version = meta.version
-        return self._fanout_future("/update_weights_from_disk", lambda i: {"model_path": meta.path, "version": meta.version}, done)
+        return self._requests_future([lambda i, r=r: r for r in self.backend.disk_update(meta)], done)
 
     def init_weights_update_group(self, meta: WeightUpdateMeta) -> Future:
         n = len(self.addresses)
-        return self._fanout_future("/init_weights_update_group", lambda i: {
-            "master_address": meta.nccl_master_address, "master_port": meta.nccl_master_port, "rank_offset": 1 + i,
-            "world_size": n + 1, "group_name": meta.nccl_group_name})
+        return self._requests_future([lambda i: self.backend.init_group(meta, i, n)])
 
     def update_weights_from_distributed(self, meta: WeightUpdateMeta, param_specs: list[ParamSpec]) -> Future:
-        body = {"names": [p.name for p in param_specs], "dtypes": [p.dtype for p in param_specs],
-                "shapes": [list(p.shape) for p in param_specs], "group_name": meta.nccl_group_name, "version": meta.version}
-
         def done():
             if meta.version is not None:
                 self._version = meta.version
-        return self._fanout_future("/update_weights_from_distributed", lambda i: body, done)
+        return self._requests_future([lambda i, r=r: r for r in self.backend.distributed_update(meta, param_specs)], done)
 
     def update_weights_from_tensors(self, named_tensors, meta: Optional[WeightUpdateMeta] = None) -> Future:
         raise NotImplementedError("tensors cannot be handed to another process; use disk, xccl or p2p weight updates")
 
     def offload(self, tags: Optional[list[str]] = None):
-        self._fanout("/release_memory_occupation", {"tags": tags})
+        self._fanout(self.backend.offload_endpoint, {"tags": tags})
 
     def onload(self, tags: Optional[list[str]] = None):
-        self._fanout("/resume_memory_occupation", {"tags": tags})
+        self._fanout(self.backend.onload_endpoint, {"tags": tags})
 
     # ------------------------------------------------------------------ executor passthrough
     def submit(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, task_id=None, is_eval=False) -> int:

@@ -90,3 +90,123 @@ def test_generation_interrupted_by_pause_is_resumed_with_new_version(served):
     assert r.output_len == 48 and len(r.output_versions) == 48 and r.stop_reason == "length"
     assert set(r.output_versions) <= {0, 9} and r.output_versions == sorted(r.output_versions)
     cl.destroy()
+
+
+def _fake_server(routes):
+    """A tiny HTTP server: ``routes[path](body) -> dict``; records every (path, body)."""
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+    from areal_b200.utils.network import find_free_ports
+
+    seen = []
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def _do(self):
+            n = int(self.headers.get("Content-Length", "0"))
+            body = json.loads(self.rfile.read(n)) if n else {}
+            seen.append((self.path, body))
+            fn = routes.get(self.path)
+            out = json.dumps(fn(body) if fn else {"error": "no route"}).encode()
+            self.send_response(200 if fn else 404)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+        do_POST = do_GET = _do
+
+    port = find_free_ports(1)[0]
+    srv = ThreadingHTTPServer(("127.0.0.1", port), H)
+    srv.daemon_threads = True
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return srv, f"127.0.0.1:{port}", seen
+
+
+def test_sglang_wire_format_and_version_of_the_request_in_flight():
+    """An SGLang-style server: the request carries ``sampling_params`` / ``sampling_seed`` / ``stop``, the answer's
+    (logprob, token, text) triples are read back, an abort before prefill is retried, and the tokens are tagged with the
+    weight version that was current when the request LEFT, although an update lands while it is in flight."""
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.engine.remote_engine import RemoteInfEngine
+
+    state = {"calls": 0}
+    box = {}
+
+    def generate(body):
+        state["calls"] += 1
+        if state["calls"] == 1:
+            return {"meta_info": {"finish_reason": {"type": "abort", "message": "Abort before prefill: paused"}}}
+        box["eng"]._version = 11                      # the weight update lands while this request is being served
+        return {"meta_info": {"finish_reason": {"type": "stop", "matched": 7},
+                              "output_token_logprobs": [[-0.5, 4, "a"], [-0.25, 5, "b"], [-1.0, 7, None]]}}
+    srv, addr, seen = _fake_server({"/generate": generate, "/pause_generation": lambda b: {}, "/continue_generation": lambda b: {},
+                                    "/release_memory_occupation": lambda b: {}, "/update_weights_from_disk": lambda b: {"success": True}})
+    try:
+        eng = RemoteInfEngine(InferenceEngineConfig(request_retries=1), [addr], backend="sglang")
+        box["eng"] = eng
+        eng._version = 10
+        g = GenerationHyperparameters(max_new_tokens=8, max_tokens=64, temperature=0.7, top_p=0.9, seed=3, stop=["\n\n"])
+        r = asyncio.run(eng.agenerate(ModelRequest(rid="r0", input_ids=[1, 2], gconfig=g)))
+        assert r.output_tokens == [4, 5, 7] and r.output_logprobs == [-0.5, -0.25, -1.0] and r.stop_reason == "stop"
+        assert r.output_versions == [10, 10, 10] and eng.get_version() == 11
+        body = [b for p, b in seen if p == "/generate"][-1]
+        assert body["input_ids"] == [1, 2] and body["return_logprob"] is True and body["stream"] is False
+        sp = body["sampling_params"]
+        assert sp["temperature"] == 0.7 and sp["top_p"] == 0.9 and sp["sampling_seed"] == 3 and sp["stop"] == ["\n\n"] and sp["max_new_tokens"] == 8
+        eng.set_version(12)                            # no such route on an SGLang server: nothing is sent
+        assert not [p for p, _ in seen if p == "/set_version"] and eng.get_version() == 12
+        eng.pause_generation(); eng.continue_generation(); eng.offload()
+        assert [p for p, _ in seen][-3:] == ["/pause_generation", "/continue_generation", "/release_memory_occupation"]
+    finally:
+        srv.shutdown()
+
+
+def test_vllm_wire_format_and_control_routes():
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig
+    from areal_b200.api.io_struct import ModelRequest, ParamSpec, WeightUpdateMeta
+    from areal_b200.engine.remote_backends import get_backend
+    from areal_b200.engine.remote_engine import RemoteInfEngine
+
+    def completions(body):
+        n = body["max_tokens"]
+        toks = [40, 41, 42][:n]
+        return {"choices": [{"finish_reason": "length" if n <= 3 else "stop",
+                             "logprobs": {"tokens": [f"token_id:{t}" for t in toks], "token_logprobs": [-0.1 * (i + 1) for i in range(len(toks))]}}]}
+    ok = lambda b: {"status": "ok"}                      # noqa: E731
+    srv, addr, seen = _fake_server({"/v1/completions": completions, "/areal_pause_generation": ok, "/areal_continue_generation": ok,
+                                    "/areal_update_weights": ok, "/areal_set_update_weight_meta": ok, "/areal_update_weights_xccl": ok,
+                                    "/areal_init_weights_update_group": ok, "/sleep": ok, "/wake_up": ok})
+    try:
+        eng = RemoteInfEngine(InferenceEngineConfig(request_retries=1), [addr], backend="vllm")
+        g = GenerationHyperparameters(max_new_tokens=2, max_tokens=64, greedy=True)
+        r = asyncio.run(eng.agenerate(ModelRequest(rid="q", input_ids=[9, 8, 7], gconfig=g)))
+        assert r.output_tokens == [40, 41] and r.stop_reason == "length" and r.output_logprobs == pytest.approx([-0.1, -0.2])
+        body = seen[0][1]
+        assert body["prompt"] == [9, 8, 7] and body["return_tokens_as_token_ids"] is True and body["temperature"] == 0.0 and body["max_tokens"] == 2
+        eng.pause_generation(); eng.continue_generation(); eng.offload(); eng.onload()
+        meta = WeightUpdateMeta(type="disk", path="/ckpt/v3", version=3)
+        eng.update_weights_from_disk(meta).result(timeout=30)
+        assert eng.get_version() == 3
+        xm = WeightUpdateMeta(type="xccl", version=4, nccl_master_address="127.0.0.1", nccl_master_port=1234, nccl_group_name="g")
+        eng.init_weights_update_group(xm).result(timeout=30)
+        eng.update_weights_from_distributed(xm, [ParamSpec(name="w", shape=(2, 2), dtype="bfloat16")]).result(timeout=30)
+        paths = [p for p, _ in seen]
+        assert paths[1:] == ["/areal_pause_generation", "/areal_continue_generation", "/sleep", "/wake_up", "/areal_update_weights",
+                             "/areal_init_weights_update_group", "/areal_set_update_weight_meta", "/areal_update_weights_xccl"]
+        init = [b for p, b in seen if p == "/areal_init_weights_update_group"][0]
+        assert init["rank_offset"] == 1 and init["world_size"] == 2 and init["group_name"] == "g"
+        with pytest.raises(ValueError, match="return_tokens_as_token_ids"):
+            get_backend("vllm").parse_generation({"choices": [{"finish_reason": "stop", "logprobs": {"tokens": ["hello"], "token_logprobs": [0.0]}}]})
+        with pytest.raises(ValueError, match="unknown generation-server backend"):
+            get_backend("tgi")
+    finally:
+        srv.shutdown()
