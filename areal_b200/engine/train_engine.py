@@ -214,18 +214,50 @@ class B200TrainEngine(TrainEngine):
         self.ep_rank, self._ep_group, self._edp_group = 0, None, None
         if self.ep_size > 1:
             ep = self.ep_size
-            if sp * tp > 1 or dp % ep or preset is not None:
-                raise NotImplementedError("expert parallelism folds into plain data parallelism (ep must divide dp; no tp / sp, no trainer-rollout split)")
-            self.ep_rank = self.dp_rank % ep
-            for blk in range(dp // ep):                       # experts are spread over consecutive data-parallel ranks
-                g = dist.new_group([tr[blk * ep + e] for e in range(ep)])
-                if blk == self.dp_rank // ep:
-                    self._ep_group = g
-            for e in range(ep):                               # replicas of the same experts: their gradients are summed
-                ranks = [tr[blk * ep + e] for blk in range(dp // ep)]
-                g = dist.new_group(ranks) if len(ranks) > 1 else None
-                if e == self.ep_rank:
-                    self._edp_group = g
+            self.etp_size = int(getattr(p, "etp_size", tp) or tp) if tp > 1 else 1
+            if sp > 1 or preset is not None:
+                raise NotImplementedError("expert parallelism folds into data (and tensor) parallelism: no sequence parallelism, no trainer-rollout split")
+            if self.etp_size not in (1, tp):
+                raise NotImplementedError(f"expert tensor parallelism must equal the attention tensor parallelism ({tp}) or 1, got {self.etp_size}")
+            if self.etp_size == tp:
+                # experts are sliced over the tensor-parallel group like a dense MLP and spread over consecutive
+                # data-parallel ranks: an EP group holds the ranks of one tensor-parallel slice
+                if dp % ep:
+                    raise ValueError(f"ep={ep} must divide dp={dp}")
+                self.ep_rank = self.dp_rank % ep
+                for t in range(tp):
+                    for blk in range(dp // ep):
+                        g = dist.new_group([gid(blk * ep + e, 0, t) for e in range(ep)])
+                        if blk == self.dp_rank // ep and t == self.tp_rank:
+                            self._ep_group = g
+                    for e in range(ep):                           # replicas of the same experts: their gradients are summed
+                        ranks = [gid(blk * ep + e, 0, t) for blk in range(dp // ep)]
+                        g = dist.new_group(ranks) if len(ranks) > 1 else None
+                        if e == self.ep_rank and t == self.tp_rank:
+                            self._edp_group = g
+                self._edp_index, self._n_edp = self.dp_rank // ep, dp // ep
+                self._export_member = self.dp_rank < ep
+            else:
+                # whole experts spread over data x tensor ranks (attention keeps its tensor split): the tensor-parallel
+                # peers of a replica hold the same tokens, so each routes its own 1 / tp of them
+                flat = dp * tp
+                if flat % ep:
+                    raise ValueError(f"ep={ep} must divide dp * tp = {flat}")
+                me = self.dp_rank * tp + self.tp_rank
+                self.ep_rank = me % ep
+                for blk in range(flat // ep):
+                    g = dist.new_group([tr[blk * ep + e] for e in range(ep)])
+                    if blk == me // ep:
+                        self._ep_group = g
+                for e in range(ep):
+                    ranks = [tr[blk * ep + e] for blk in range(flat // ep)]
+                    g = dist.new_group(ranks) if len(ranks) > 1 else None
+                    if e == self.ep_rank:
+                        self._edp_group = g
+                self._edp_index, self._n_edp = me // ep, flat // ep
+                import math
+
+                self._export_member = me < math.lcm(ep, tp)       # whole EP groups and whole TP groups: an export gathers over both
         return self
 
     def _create_pp_groups(self, li: int, use_cuda: bool):
@@ -341,9 +373,11 @@ class B200TrainEngine(TrainEngine):
             full = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
             if has_ckpt:
                 hf_io.load_model_hf(full, cfg.path, strict=not cfg.is_critic)
-            self.local_model_config = TP.local_config(model_config, tp)
+            xtp = getattr(self, "ep_size", 1) == 1 or getattr(self, "etp_size", 1) == tp      # experts sliced over the TP group too
+            self.local_model_config = TP.local_config(model_config, tp, expert_tp=xtp)
             self.model = build_model(self.local_model_config, dtype=dtype, device=self.device, seed=seed)
-            TP.load_sharded_from_full(self.model, model_config, {n_: p_.detach() for n_, p_ in full.named_parameters()}, tp, self.tp_rank)
+            TP.load_sharded_from_full(self.model, model_config, {n_: p_.detach() for n_, p_ in full.named_parameters()}, tp, self.tp_rank,
+                                      expert_tp=xtp)
             tp_sp = bool(cfg.fsdp.tp_sequence_parallel) and not model_config.is_moe
             fused_tp = None
             if tp_sp and self.device.type == "cuda" and cfg.fsdp.fuse_tp_projections and model_config.head_dim in (64, 128):
@@ -355,7 +389,7 @@ class B200TrainEngine(TrainEngine):
                 widest = max(model_config.hidden_size, 2 * lc.intermediate_size, (lc.num_heads + 2 * lc.num_kv_heads) * lc.head_dim)
                 fused_tp = FusedTPLinear(self._tp_group, self.device, max_t // tp, widest, widest)
             self._tp_fused = fused_tp
-            TP.install_tp(self.model, self._tp_group, tp, self.tp_rank, sequence_parallel=tp_sp, fused=fused_tp)
+            TP.install_tp(self.model, self._tp_group, tp, self.tp_rank, sequence_parallel=tp_sp, fused=fused_tp, expert_tp=xtp)
             del full
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
@@ -376,7 +410,7 @@ class B200TrainEngine(TrainEngine):
             if not model_config.is_moe:
                 raise ValueError("expert parallelism needs a mixture-of-experts model")
             fused_ep = (self.device.type == "cuda" and (cfg.archon.fuse_ep_dispatch or cfg.megatron.moe_enable_deepep)
-                        and os.environ.get("AREAL_EP_FUSED", "1") != "0")
+                        and os.environ.get("AREAL_EP_FUSED", "1") != "0" and tp == 1)
             self._expert_param_names = shard_experts(self.model, self.ep_rank, self.ep_size, self._ep_group, fused=fused_ep,
                                                      device=self.device)
         self.model.gradient_checkpointing = cfg.gradient_checkpointing
@@ -418,8 +452,7 @@ class B200TrainEngine(TrainEngine):
             # the ranks that hold the SAME experts; everything else is sharded over all ranks
             fused, alloc_g, alloc_p, alloc = False, None, None, None
             expert = set(self._expert_param_names)
-            n_edp = self.dp_size // self.ep_size
-            self.expert_store = FlatParamStore(self.model, n_edp, self.dp_rank // self.ep_size, torch.float32,
+            self.expert_store = FlatParamStore(self.model, self._n_edp, self._edp_index, torch.float32,
                                                with_grads=cfg.optimizer is not None, include=lambda n: n in expert)
         _expert_set = frozenset(self._expert_param_names)
         dense_only = (lambda n: n not in _expert_set) if _expert_set else None
@@ -1012,9 +1045,21 @@ class B200TrainEngine(TrainEngine):
         experts' over the replicas of the same experts; one global norm clips both."""
         es = self.expert_store
         es.fold_autograd_grads()
+        tp = getattr(self, "tp_size", 1)
+        if tp > 1:
+            from ..parallel.tp import allreduce_replicated_grads
+
+            allreduce_replicated_grads(self.model, self._tp_group)
         g_dense = self._reduce_scatter_flat(self.store, self._shard_group)
         g_exp = self._reduce_scatter_flat(es, self._edp_group)
-        pre = (g_dense.float().pow(2).sum() + g_exp.float().pow(2).sum()).reshape(1)
+        d32 = g_dense.float()
+        dense_sq = d32.pow(2).sum()
+        if tp > 1:
+            # parameters that every tensor-parallel rank holds in full count once; every expert element (whole or
+            # sliced) lives in exactly one rank's shard
+            rep = sum((d32[a:b].pow(2).sum() for a, b in self._replicated_ranges), torch.zeros((), device=self.device))
+            dense_sq = dense_sq - rep + rep / tp
+        pre = (dense_sq + g_exp.float().pow(2).sum()).reshape(1)
         if self._all_train_group is not None:
             dist.all_reduce(pre, group=self._all_train_group)     # every shard of either kind lives on exactly one rank
         res = self.optimizer.step(g_dense, precomputed_sumsq=pre)
@@ -1025,7 +1070,8 @@ class B200TrainEngine(TrainEngine):
             for layer in self.model.layers:
                 upd = getattr(layer.mlp, "update_expert_bias", None)
                 if upd is not None:
-                    upd(self._shard_group)
+                    # whole experts under tensor-parallel attention: every rank counted its own share of the tokens
+                    upd(self._all_train_group if tp > 1 and getattr(self, "etp_size", 1) != tp else self._shard_group)
         st = self._read_step_state(res["state"])
         self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
         return dict(self.last_step_stats)
@@ -1122,7 +1168,7 @@ class B200TrainEngine(TrainEngine):
                 if meta.tokenizer is not None:
                     meta.tokenizer.save_pretrained(meta.path)
         elif meta.weight_format == "hf" and getattr(self, "ep_size", 1) > 1:
-            if self.dp_rank < self.ep_size:                   # the first EP group gathers its experts; its head writes
+            if self._export_member:                           # the first EP (and TP) groups gather their slices; the head writes
                 named = self._ep_full_named_tensors()
                 if head:
                     hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named))
@@ -1168,14 +1214,22 @@ class B200TrainEngine(TrainEngine):
             dist.barrier(group=self._cpu_group)
 
     def _ep_full_named_tensors(self, to_cpu: bool = False):
-        """(name, tensor) with every expert stack gathered over the EP group (a collective of that group)."""
+        """(name, full tensor): expert stacks gathered over the EP group, tensor-parallel slices over the TP group
+        (collectives of those groups: every rank of both must iterate)."""
+        from ..parallel import tp as TP
+
         expert = set(self._expert_param_names)
+        tp, xtp = getattr(self, "tp_size", 1), getattr(self, "etp_size", 1) == getattr(self, "tp_size", 1)
         for n_, p_ in self.model.named_parameters():
             t = p_.detach()
             if n_ in expert:
                 parts = [torch.empty_like(t) for _ in range(self.ep_size)]
                 dist.all_gather(parts, t.contiguous(), group=self._ep_group)
                 t = torch.cat(parts, dim=0)
+            if tp > 1 and (n_ not in expert or xtp):
+                parts = [torch.empty_like(t) for _ in range(tp)]
+                dist.all_gather(parts, t.contiguous(), group=self._tp_group)
+                t = TP.unshard_tensors(self.model_config, n_, parts, expert_tp=xtp)
             yield n_, (t.to("cpu", copy=True) if to_cpu else t)
 
     def _gathered_full_tensors(self):
@@ -1197,12 +1251,16 @@ class B200TrainEngine(TrainEngine):
         elif meta.weight_format == "hf" and getattr(self, "ep_size", 1) > 1:
             full = build_model(self.model_config, dtype=self.model.dtype, device=self.device, seed=0)
             hf_io.load_model_hf(full, meta.path, strict=not self.config.is_critic)
+            from ..parallel import tp as TP
+
             src = dict(full.named_parameters())
             El = self.model_config.num_experts // self.ep_size
+            tp_, xtp = getattr(self, "tp_size", 1), getattr(self, "etp_size", 1) == getattr(self, "tp_size", 1)
+            expert = set(self._expert_param_names)
             with torch.no_grad():
                 for n_, p_ in self.model.named_parameters():
-                    t = src[n_].detach()
-                    p_.copy_(t[self.ep_rank * El:(self.ep_rank + 1) * El] if n_ in set(self._expert_param_names) else t)
+                    t = TP.shard_tensor(self.model_config, n_, src[n_].detach(), tp_, getattr(self, "tp_rank", 0), expert_tp=xtp)
+                    p_.copy_(t[self.ep_rank * El:(self.ep_rank + 1) * El] if n_ in expert else t)
             del full, src
         elif meta.weight_format == "hf":
             if getattr(self, "tp_size", 1) > 1:

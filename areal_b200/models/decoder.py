@@ -213,7 +213,7 @@ class MoEMLP(nn.Module):
                 self.tokens_per_expert.add_(load)
             if cfg.router_aux_loss_coef > 0:
                 mean_p = probs.mean(0) if cfg.router_score_func != "sigmoid" else (probs / probs.sum(-1, keepdim=True).clamp(min=1e-20)).mean(0)
-                self.last_aux_loss = E * (load / tope.numel() * mean_p).sum() * cfg.router_aux_loss_coef
+                self.last_aux_loss = E * (load / tope.numel() * mean_p).sum() * (cfg.router_aux_loss_coef * getattr(self, "aux_scale", 1.0))
         self.last_routed_experts = tope
         return topw, tope, routing
 
@@ -318,6 +318,7 @@ class DecoderLayer(nn.Module):
         self.mlp = MoEMLP(cfg, dtype, device) if cfg.layer_is_moe(idx) else DenseMLP(H, cfg.intermediate_size, dtype, device)
 
     tp_group = None  # set by parallel.tp.install_tp
+    moe_row_share = None  # (group, tp, rank): whole experts under tensor-parallel attention (parallel.tp.moe_on_row_share)
     tp_exchange = None  # set by parallel.tp_decode.install_tp_decode (inference: fused partial-sum exchange)
 
     def forward(self, h, resid, pb: PackedBatch, cos, sin, attn_fn=None):
@@ -341,6 +342,10 @@ class DecoderLayer(nn.Module):
 
         h = reduce_from_tp(self.self_attn(copy_to_tp(x, g), pb, cos, sin, attn_fn), g)
         x, resid = OF.rmsnorm(h, self.post_attention_layernorm, self.cfg.rms_norm_eps, resid)
+        if self.moe_row_share is not None:
+            from ..parallel.tp import moe_on_row_share
+
+            return moe_on_row_share(self.mlp, x, *self.moe_row_share), resid
         h = reduce_from_tp(self.mlp(copy_to_tp(x, g)), g)
         return h, resid
 

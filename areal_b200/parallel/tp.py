@@ -25,8 +25,9 @@ from ..models.config import ModelConfig
 from .weight_push import tp_layout_of
 
 
-def local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
-    """Architecture of one TP rank."""
+def local_config(cfg: ModelConfig, tp: int, expert_tp: bool = True) -> ModelConfig:
+    """Architecture of one TP rank. ``expert_tp=False``: routed experts keep their full width (they are spread whole
+    over an expert-parallel group instead; attention and dense MLPs are still sliced)."""
     if tp == 1:
         return cfg
     if getattr(cfg, "shared_expert_intermediate_size", 0):
@@ -35,15 +36,15 @@ def local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
         raise ValueError(f"num_heads={cfg.num_heads} is not divisible by tp={tp}")
     if cfg.num_kv_heads % tp:
         raise ValueError(f"num_kv_heads={cfg.num_kv_heads} is not divisible by tp={tp} (kv-head replication is not supported)")
-    if cfg.intermediate_size % tp or (cfg.num_experts and cfg.moe_intermediate_size % tp):
+    if cfg.intermediate_size % tp or (cfg.num_experts and expert_tp and cfg.moe_intermediate_size % tp):
         raise ValueError("MLP width is not divisible by tp")
     kw = dict(num_heads=cfg.num_heads // tp, num_kv_heads=cfg.num_kv_heads // tp, intermediate_size=cfg.intermediate_size // tp)
-    if cfg.num_experts:
+    if cfg.num_experts and expert_tp:
         kw["moe_intermediate_size"] = cfg.moe_intermediate_size // tp
     return dataclasses.replace(cfg, **kw)
 
 
-def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank: int, expert_tp: bool = True) -> torch.Tensor:
     """Rank-local slice of a full (native-named) parameter."""
     if tp == 1:
         return full
@@ -51,6 +52,8 @@ def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank:
     if leaf in ("embed_tokens", "lm_head"):       # replicated here (vocab parallelism is separate)
         return full
     if full.dim() == 3:                             # stacked experts [E, rows, cols]
+        if not expert_tp:
+            return full
         if leaf == "w_gate_up":
             I = full.shape[1] // 2
             a, b = rank * I // tp, (rank + 1) * I // tp
@@ -66,13 +69,15 @@ def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank:
     return torch.cat([full[r0:r1, c0:c1] for (r0, r1, c0, c1) in blocks], dim=0).contiguous()
 
 
-def unshard_tensors(cfg: ModelConfig, name: str, parts: list[torch.Tensor]) -> torch.Tensor:
+def unshard_tensors(cfg: ModelConfig, name: str, parts: list[torch.Tensor], expert_tp: bool = True) -> torch.Tensor:
     """Inverse of :func:`shard_tensor` (checkpoint export, weight push to a TP=1 consumer)."""
     tp = len(parts)
     if tp == 1:
         return parts[0]
     leaf = name.rsplit(".", 1)[-1]
     p0 = parts[0]
+    if p0.dim() == 3 and not expert_tp:
+        return p0
     if leaf in ("embed_tokens", "lm_head") or (p0.dim() == 1 and leaf != "qkv_bias") or leaf in ("router",):
         return p0
     if p0.dim() == 3:
@@ -131,7 +136,53 @@ def reduce_from_tp(x, group):
     return _ReduceFromTP.apply(x, group) if group is not None else x
 
 
-def install_tp(model, group, tp_size: int, tp_rank: int, sequence_parallel: bool = False, fused=None):
+def _gather_rows_uneven(x: torch.Tensor, T: int, group, tp: int) -> torch.Tensor:
+    """Rank r holds rows [T r // tp, T (r + 1) // tp) of a [T, ...] tensor; returns all of it."""
+    per = -(-T // tp)
+    pad = x.new_zeros((per,) + tuple(x.shape[1:]))
+    pad[: x.shape[0]] = x
+    parts = [torch.empty_like(pad) for _ in range(tp)]
+    dist.all_gather(parts, pad, group=group)
+    return torch.cat([parts[r][: T * (r + 1) // tp - T * r // tp] for r in range(tp)], dim=0)
+
+
+class _SliceRows(torch.autograd.Function):
+    """This rank's share of rows that every TP rank holds (forward); the shares' gradients gathered back (backward)."""
+
+    @staticmethod
+    def forward(ctx, x, group, tp, rank):
+        ctx.group, ctx.tp, ctx.T = group, tp, x.shape[0]
+        return x[x.shape[0] * rank // tp: x.shape[0] * (rank + 1) // tp]
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather_rows_uneven(g.contiguous(), ctx.T, ctx.group, ctx.tp), None, None, None
+
+
+class _GatherRows(torch.autograd.Function):
+    """Inverse of :class:`_SliceRows`: every rank ends up with all rows; each keeps its own rows' gradient (the
+    gradient of the gathered tensor is the same on every TP rank)."""
+
+    @staticmethod
+    def forward(ctx, x, group, tp, rank, T):
+        ctx.a, ctx.b = T * rank // tp, T * (rank + 1) // tp
+        return _gather_rows_uneven(x.contiguous(), T, group, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g[ctx.a:ctx.b], None, None, None, None
+
+
+def moe_on_row_share(mlp, x: torch.Tensor, group, tp: int, rank: int) -> torch.Tensor:
+    """A mixture-of-experts block whose experts are NOT sliced over the TP group: the group's ranks hold the same
+    ``x``, so each routes its own share of the rows through the (expert-parallel) block and the outputs are gathered.
+    Role of the attention-TP / expert-EP folding of the reference's hybrid layouts
+    (``areal/api/alloc_mode.py:955-1054``, Megatron's ``expert_tensor_parallel_size=1``)."""
+    T = x.shape[0]
+    return _GatherRows.apply(mlp(_SliceRows.apply(x, group, tp, rank)), group, tp, rank, T)
+
+
+def install_tp(model, group, tp_size: int, tp_rank: int, sequence_parallel: bool = False, fused=None, expert_tp: bool = True):
     """Marks every decoder layer of a rank-local model as tensor parallel. Default: the layer's forward brackets
     attention and MLP with the conjugate pair (identity / all-reduce) and every rank carries all tokens.
     ``sequence_parallel``: the residual stream is split by rows over the group as well (each rank holds ``T / P``
@@ -148,6 +199,9 @@ def install_tp(model, group, tp_size: int, tp_rank: int, sequence_parallel: bool
             layer.self_attn.tp_sp = layer.mlp.tp_sp = (group, fused)
         else:
             layer.tp_group = group if on else None
+            if on and not expert_tp and hasattr(layer.mlp, "w_gate_up"):
+                layer.moe_row_share = (group, tp_size, tp_rank)
+                layer.mlp.aux_scale = 1.0 / tp_size         # every TP rank adds the balancing loss of its own share
     model.tp_group, model.tp_size, model.tp_rank = (group if on else None), tp_size, tp_rank
     model.tp_sequence_parallel = bool(sequence_parallel and on)
     return model
@@ -184,11 +238,11 @@ def allreduce_replicated_grads(model, group, grad_of=lambda p: getattr(p, "main_
                 dist.all_reduce(g, group=group)
 
 
-def load_sharded_from_full(model, cfg: ModelConfig, full_state: dict, tp: int, rank: int):
+def load_sharded_from_full(model, cfg: ModelConfig, full_state: dict, tp: int, rank: int, expert_tp: bool = True):
     """Copies the rank-local slices of a full state dict into a rank-local model."""
     with torch.no_grad():
         for n, p in model.named_parameters():
-            p.copy_(shard_tensor(cfg, n, full_state[n], tp, rank).to(p.dtype))
+            p.copy_(shard_tensor(cfg, n, full_state[n], tp, rank, expert_tp).to(p.dtype))
     return model
 
 
