@@ -125,6 +125,7 @@ class FSDPEngineConfig:
     offload_params: bool = False
     memory_efficient_load: bool = False
     reshard_after_forward: bool = True
+    shard_parameters: bool = False           # ZeRO-3: weights and gradients sharded too, decoder layers gathered one at a time (for models that do not fit replicated)
     fuse_reduce_scatter_adamw: bool = True   # fused RS + cast/scale + sharded AdamW kernel
     fuse_allgather_gemm: bool = True         # param all-gather fused into the consuming GEMM
     fuse_ulysses_projections: bool = True    # sequence-parallel all-to-alls folded into the QKV / output projection kernels

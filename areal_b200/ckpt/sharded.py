@@ -85,7 +85,7 @@ def _load_resharded(engine, path: str, with_optim: bool) -> None:
                 dst[x - lo:y - lo].copy_(tensors[name][x - a:y - a].to(dst.dtype))
         else:
             got_opt = False
-    if st.world_size > 1:
+    if st.world_size > 1 and st.flat_param is not None:         # (sharded parameters have no replicated copy to refresh)
         dist.all_gather_into_tensor(st.flat_param, st.param_shard.clone(), group=engine._shard_group)
     if opt is not None:
         if want_opt and got_opt:
@@ -109,7 +109,7 @@ def load_sharded(engine, path: str, with_optim: bool = True) -> None:
         return _load_resharded(engine, path, with_optim)
     tensors = load_file(os.path.join(path, f"shard-{r:05d}-of-{st.world_size:05d}.safetensors"))
     st.param_shard.copy_(tensors["param_shard"].to(st.dtype))
-    if st.world_size > 1:
+    if st.world_size > 1 and st.flat_param is not None:         # (sharded parameters have no replicated copy to refresh)
         dist.all_gather_into_tensor(st.flat_param, st.param_shard.clone(), group=engine._shard_group)
     opt = engine.optimizer
     if opt is not None:

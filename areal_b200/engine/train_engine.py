@@ -395,7 +395,9 @@ class B200TrainEngine(TrainEngine):
                 torch.cuda.empty_cache()
         else:
             self.local_model_config = model_config
-            self.model = build_model(model_config, dtype=dtype, device=self.device, seed=seed)
+            # sharded parameters with memory_efficient_load: the model is built on the host and only shards reach the device
+            on_host = bool(getattr(cfg.fsdp, "shard_parameters", False)) and bool(cfg.fsdp.memory_efficient_load)
+            self.model = build_model(model_config, dtype=dtype, device="cpu" if on_host else self.device, seed=seed)
             if has_ckpt:
                 hf_io.load_model_hf(self.model, cfg.path, strict=not cfg.is_critic)
         f8 = cfg.archon.fp8 if cfg.archon.fp8.enabled else cfg.megatron.fp8
@@ -456,13 +458,27 @@ class B200TrainEngine(TrainEngine):
                                                with_grads=cfg.optimizer is not None, include=lambda n: n in expert)
         _expert_set = frozenset(self._expert_param_names)
         dense_only = (lambda n: n not in _expert_set) if _expert_set else None
-        self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
-                                    with_grads=cfg.optimizer is not None, only_trainable=self.use_lora, include=dense_only)
+        self._z3 = None
+        if bool(getattr(cfg.fsdp, "shard_parameters", False)):
+            # ZeRO-3: parameters and gradients sharded as well, decoder layers materialised one at a time
+            if tp > 1 or getattr(self, "pp_size", 1) > 1 or getattr(self, "ep_size", 1) > 1 or self.use_lora or model_config.is_vlm:
+                raise NotImplementedError("fsdp.shard_parameters covers data / sequence parallel text models (no tp / pp / ep, LoRA or image tower)")
+            from .sharded_params import ShardedParamStore
+
+            fused, alloc = False, None
+            self.store = self._z3 = ShardedParamStore(self.model, n_shards, shard_rank, self._shard_group if n_shards > 1 else None,
+                                                      self._shard_ranks if n_shards > 1 else None, torch.float32,
+                                                      with_grads=cfg.optimizer is not None, device=self.device)
+            self.model.param_units = self.store
+        else:
+            self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
+                                        with_grads=cfg.optimizer is not None, only_trainable=self.use_lora, include=dense_only)
         if on_gpu:
             torch.cuda.empty_cache()        # the parameters' first home (before the flat buffer) goes back to the driver
         if n_shards > 1:
             # identical initial weights on every rank of the shard group
-            dist.broadcast(self.store.flat_param, src=self._shard_ranks[0], group=self._shard_group)
+            if self._z3 is None:
+                dist.broadcast(self.store.flat_param, src=self._shard_ranks[0], group=self._shard_group)
         if tp > 1 and cfg.optimizer is not None:
             self._replicated_ranges = self._find_replicated_ranges()
         if getattr(self, "pp_size", 1) > 1 and cfg.optimizer is not None:
@@ -763,20 +779,27 @@ class B200TrainEngine(TrainEngine):
         if getattr(self, "pp_size", 1) > 1:
             return self._pp_forward_backward(mb_list, process_output_fn, forward_only)
         outs = []
+        z3 = getattr(self, "_z3", None)
         for mb, pad in zip(mb_list.padded_mbs, mb_list.padding_lengths):
             mbd = self._mb_to_device(mb)
-            if forward_only:
-                with torch.no_grad():
+            if z3 is not None:
+                z3.begin(train=not forward_only)     # embedding / head stay for the micro-batch, layers come and go
+            try:
+                if forward_only:
+                    with torch.no_grad():
+                        hidden, labels, sl = self._forward_mb(mbd)
+                        outs.append(process_output_fn(hidden, labels, mbd, pad, sl))
+                else:
                     hidden, labels, sl = self._forward_mb(mbd)
-                    outs.append(process_output_fn(hidden, labels, mbd, pad, sl))
-            else:
-                hidden, labels, sl = self._forward_mb(mbd)
-                loss = process_output_fn(hidden, labels, mbd, pad, sl)
-                aux = self.model.aux_loss()
-                if aux is not None:
-                    loss = loss + aux
-                loss.backward()
-                outs.append(loss.detach())
+                    loss = process_output_fn(hidden, labels, mbd, pad, sl)
+                    aux = self.model.aux_loss()
+                    if aux is not None:
+                        loss = loss + aux
+                    loss.backward()
+                    outs.append(loss.detach())
+            finally:
+                if z3 is not None:
+                    z3.end(train=not forward_only)
         return outs
 
     def _pp_forward_backward(self, mb_list: D.MicroBatchList, process_output_fn: Callable, forward_only: bool):
@@ -897,6 +920,17 @@ class B200TrainEngine(TrainEngine):
         if getattr(self, "expert_store", None) is not None:
             return self._ep_optimizer_step()
         opt = self.optimizer
+        if getattr(self, "_z3", None) is not None:
+            # gradients were reduced to their owners unit by unit during the backward; the updated shard stays put
+            res = opt.step(self.store.grad_shard)
+            if self.model.cfg.is_moe and self.model.cfg.router_bias_update_rate > 0:
+                for layer in self.model.layers:
+                    upd = getattr(layer.mlp, "update_expert_bias", None)
+                    if upd is not None:
+                        upd(self._shard_group)
+            st = self._read_step_state(res["state"])
+            self.last_step_stats = dict(update_successful=float(st[2]), grad_norm=float(st[3]), lr=float(res["lr"]))
+            return dict(self.last_step_stats)
         tp = getattr(self, "tp_size", 1)
         if tp > 1:
             from ..parallel.tp import allreduce_replicated_grads
@@ -1167,6 +1201,16 @@ class B200TrainEngine(TrainEngine):
                 self.model_config.save_pretrained(meta.path)
                 if meta.tokenizer is not None:
                     meta.tokenizer.save_pretrained(meta.path)
+        elif meta.weight_format == "hf" and getattr(self, "_z3", None) is not None:
+            # every rank takes part in the unit-by-unit gather; the head writes tensor by tensor
+            named = self._z3.full_tensors()
+            if head:
+                hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named))
+                if meta.tokenizer is not None:
+                    meta.tokenizer.save_pretrained(meta.path)
+            else:
+                for _ in named:
+                    pass
         elif meta.weight_format == "hf" and getattr(self, "ep_size", 1) > 1:
             if self._export_member:                           # the first EP (and TP) groups gather their slices; the head writes
                 named = self._ep_full_named_tensors()
@@ -1248,6 +1292,10 @@ class B200TrainEngine(TrainEngine):
             wanted = {hf for n in mine for hf, _, _ in plan[n]}
             hf_io.load_hf_tensors_into(self.model_config, {n: p.data for n, p in mine.items()},
                                        ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
+        elif meta.weight_format == "hf" and getattr(self, "_z3", None) is not None:
+            # tensors stream from the files; every rank keeps what falls into its shard
+            hf_io.load_hf_tensors_into(self.model_config, None, hf_io.iter_safetensors(meta.path), strict=not self.config.is_critic,
+                                       writer=self._z3.write_piece)
         elif meta.weight_format == "hf" and getattr(self, "ep_size", 1) > 1:
             full = build_model(self.model_config, dtype=self.model.dtype, device=self.device, seed=0)
             hf_io.load_model_hf(full, meta.path, strict=not self.config.is_critic)
@@ -1331,7 +1379,7 @@ class B200TrainEngine(TrainEngine):
                 t = getattr(self.optimizer, name)
                 self._offloaded[name] = t.to("cpu", non_blocking=False).pin_memory()
                 setattr(self.optimizer, name, torch.empty(0, device=self.device))
-        if self.store.flat_grad is not None:
+        if getattr(self.store, "flat_grad", None) is not None:
             self._offloaded["grad_shape"] = self.store.flat_grad.numel()
         torch.cuda.empty_cache()
 
@@ -1356,6 +1404,8 @@ class B200TrainEngine(TrainEngine):
                 return {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_parameters() if "_lora_" not in n}
             finally:
                 unmerge_lora_(self.model)
+        if getattr(self, "_z3", None) is not None:
+            return dict(self._z3.full_tensors(to_cpu=True))
         if getattr(self, "ep_size", 1) > 1:
             return dict(self._ep_full_named_tensors(to_cpu=True))
         if getattr(self, "tp_size", 1) > 1:

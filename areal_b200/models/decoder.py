@@ -419,12 +419,17 @@ class CausalLM(nn.Module):
         cos, sin = rope if rope is not None else self.rope(input_ids.device, max(self.cfg.max_position_embeddings, pb.max_seqlen + 1))
         h = inputs_embeds if inputs_embeds is not None else OF.embedding(input_ids, self.embed_tokens)
         resid = None
+        units = getattr(self, "param_units", None)      # sharded parameters: a layer's weights exist only between enter and leave
         for i, layer in enumerate(self.layers):
             fn = attn_fns[i] if attn_fns is not None else None
+            if units is not None:
+                h, resid = units.enter(i, h, resid)
             if self.training and torch.is_grad_enabled() and self._recompute_layer(i):
                 h, resid = checkpoint(layer, h, resid, pb, cos, sin, fn, use_reentrant=False)
             else:
                 h, resid = layer(h, resid, pb, cos, sin, fn)
+            if units is not None:
+                h, resid = units.leave(i, h, resid)
             if deepstack is not None and i < len(deepstack[1]):
                 # deep-stack features of the image tower join the hidden state (= resid + h) after the first layers
                 h = h.index_add(0, deepstack[0], deepstack[1][i].to(h.dtype))

@@ -131,9 +131,11 @@ def native_to_hf_tensors(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tens
 
 
 @torch.no_grad()
-def load_hf_tensors_into(cfg: ModelConfig, params: dict[str, torch.Tensor], hf_tensors: Iterable[tuple[str, torch.Tensor]],
-                         strict: bool = True) -> set[str]:
-    """Copies HF-named tensors into native parameters. Returns the set of HF names consumed."""
+def load_hf_tensors_into(cfg: ModelConfig, params: Optional[dict[str, torch.Tensor]], hf_tensors: Iterable[tuple[str, torch.Tensor]],
+                         strict: bool = True, writer=None) -> set[str]:
+    """Copies HF-named tensors into native parameters. Returns the set of HF names consumed. ``writer(native name,
+    expert index or None, row range or None, tensor)`` takes the pieces instead when the native tensors do not exist
+    as a whole (sharded parameters)."""
     plan = hf_to_native_plan(cfg)
     inverse: dict[str, tuple[str, Optional[tuple[int, int]], Optional[int]]] = {}
     for native, parts in plan.items():
@@ -155,6 +157,10 @@ def load_hf_tensors_into(cfg: ModelConfig, params: dict[str, torch.Tensor], hf_t
         native, rows, expert = inverse[hf_name]
         if hf_name.endswith("linear_attn.conv1d.weight") and t.dim() == 3:
             t = t.squeeze(1)
+        if writer is not None:
+            writer(native, expert, rows, t)
+            seen.add(hf_name)
+            continue
         dst = params[native]
         dst = dst if expert is None else dst[expert]
         dst = dst if rows is None else dst[rows[0]:rows[1]]

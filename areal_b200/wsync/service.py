@@ -105,6 +105,9 @@ class DiskPusher:
 def make_weight_pusher(train_engine, infer_engine, meta: WeightUpdateMeta):
     if meta.type == "disk":
         return DiskPusher(train_engine, infer_engine)
+    if getattr(train_engine, "_z3", None) is not None:
+        # sharded parameters: the full tensors are gathered unit by unit and handed over (or written to disk above)
+        return GatheredPusher(train_engine, infer_engine)
     if meta.type in ("p2p", "xccl", "awex") and hasattr(infer_engine, "remote_ranks"):
         from ..parallel.weight_push import BroadcastWeightPusher, DistributedWeightPusher, TPWeightPusher
 
