@@ -261,39 +261,60 @@ class B200TrainEngine(TrainEngine):
         return self
 
     def _create_pp_groups(self, li: int, use_cuda: bool):
-        """Pipeline x data parallel layout: index = stage * dp + d (stages outermost). Every stage
-        shards its optimizer state over its own data-parallel ranks; the ranks of one pipeline see
-        the same data (they are each other's model-parallel peers)."""
-        pp, dp, tr = self.pp_size, self.dp_size, self._train_ranks
-        if self.sp_size * self.tp_size > 1:
-            raise NotImplementedError("pipeline parallelism combines with data parallelism only (no tp / sp inside a stage yet)")
+        """Pipeline x data x tensor parallel layout: index = (stage * dp + d) * tp + t (stages outermost, tensor-parallel
+        peers adjacent). Every (stage, tensor slice) shards its optimizer state over its own data-parallel ranks; the
+        ranks of one pipeline (all stages and slices of one ``d``) see the same data. Activations travel between the
+        ranks that hold the same slice of neighbouring stages: with plain tensor parallelism every slice holds the whole
+        hidden state, so no exchange crosses slices."""
+        pp, dp, tp, tr = self.pp_size, self.dp_size, self.tp_size, self._train_ranks
+        if self.sp_size > 1:
+            raise NotImplementedError("pipeline parallelism combines with data and tensor parallelism (no sequence parallelism inside a stage)")
         if getattr(self, "_preset_groups", None) is not None:
             raise NotImplementedError("pipeline parallelism inside a trainer / rollout split")
-        self.pp_rank, self.dp_rank = li // dp, li % dp
-        self.tp_rank = self.sp_rank = 0
+        self.tp_rank, self.dp_rank, self.pp_rank = li % tp, (li // tp) % dp, li // (tp * dp)
+        self.sp_rank = 0
         self._tp_group = self._sp_group = None
+
+        def gid(s_, d, t):
+            return tr[(s_ * dp + d) * tp + t]
         self._all_train_group = dist.group.WORLD if len(tr) == self.world_size else dist.new_group(tr)
         self._shard_group = self._dp_group = None
         for s_ in range(pp):
-            ranks = [tr[s_ * dp + d] for d in range(dp)]
-            g = dist.new_group(ranks) if dp > 1 else None
-            if s_ == self.pp_rank:
-                self._shard_group = self._dp_group = g
+            for t in range(tp):
+                ranks = [gid(s_, d, t) for d in range(dp)]
+                g = dist.new_group(ranks) if dp > 1 else None
+                if s_ == self.pp_rank and t == self.tp_rank:
+                    self._shard_group = self._dp_group = g
         for d in range(dp):
-            ranks = [tr[s_ * dp + d] for s_ in range(pp)]
-            g = dist.new_group(ranks)
-            gc = dist.new_group(ranks, backend="gloo") if use_cuda else g
-            if d == self.dp_rank:
-                self._pp_group, self._pp_cpu_group = g, gc
+            for t in range(tp):
+                ranks = [gid(s_, d, t) for s_ in range(pp)]
+                g = dist.new_group(ranks)
+                gc = dist.new_group(ranks, backend="gloo") if use_cuda else g
+                if d == self.dp_rank and t == self.tp_rank:
+                    self._pp_group, self._pp_cpu_group = g, gc
         self._mp_group = self._pp_group
+        if tp > 1:
+            for s_ in range(pp):
+                for d in range(dp):
+                    g = dist.new_group([gid(s_, d, t) for t in range(tp)])
+                    if s_ == self.pp_rank and d == self.dp_rank:
+                        self._tp_group = g
+            for d in range(dp):                                  # every stage and slice of one replica
+                g = dist.new_group([gid(s_, d, t) for s_ in range(pp) for t in range(tp)])
+                if d == self.dp_rank:
+                    self._mp_group = g
         self._cpu_group = dist.new_group(tr, backend="gloo") if use_cuda else self._all_train_group
-        # losses and statistics exist only on the rank that holds the last stage: the last pipeline rank, or rank 0
-        # under the V-shaped placement of the ZBV schedule (two chunks per rank, down the ranks and back up)
+        # losses and statistics exist only on the ranks that hold the last stage: the last pipeline rank, or rank 0
+        # under the V-shaped placement of the ZBV schedule (two chunks per rank, down the ranks and back up); tensor-
+        # parallel peers hold copies, so each slice reduces over its own data-parallel peers
         sched = str(getattr(self.config.archon, "pp_schedule", "1F1B")).lower()
         self._pp_loss_rank = 0 if sched in ("zbv", "zbvzerobubble") else pp - 1
-        last = [tr[self._pp_loss_rank * dp + d] for d in range(dp)]
-        g = dist.new_group(last, backend="gloo") if dp > 1 else None
-        self._stats_group = g if self.pp_rank == self._pp_loss_rank else None
+        self._stats_group = None
+        for t in range(tp):
+            last = [gid(self._pp_loss_rank, d, t) for d in range(dp)]
+            g = dist.new_group(last, backend="gloo") if dp > 1 else None
+            if self.pp_rank == self._pp_loss_rank and t == self.tp_rank:
+                self._stats_group = g
         t_ = torch.zeros(1, device=self.device)
         dist.all_reduce(t_, group=self._all_train_group)
         return self
@@ -351,18 +372,25 @@ class B200TrainEngine(TrainEngine):
 
                 vpp = 2 if zbv else max(vpp, 2)
                 self.model = InterleavedStages(model_config, self.pp_rank, self.pp_size, vpp, dtype=dtype, device=self.device, seed=seed,
-                                               init_full=loader, placement="v" if zbv else "loop")
+                                               init_full=loader, placement="v" if zbv else "loop", tp=tp, tp_rank=self.tp_rank)
                 self._pp_runner = ScheduledPipelineRunner(self.model, self._pp_group,
                                                           "ZBV" if zbv else
                                                           "GPipe" if sched_name.lower() == "gpipe" else
                                                           "InterleavedZeroBubble" if "zero" in sched_name.lower() or sched_name.lower() == "zbh1"
                                                           else "Interleaved1F1B")
             else:
-                self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader)
+                self.model = PipelineStage(model_config, self.pp_rank, self.pp_size, dtype=dtype, device=self.device, seed=seed, init_full=loader,
+                                           tp=tp, tp_rank=self.tp_rank)
                 # zero-bubble names of the reference map to the split-backward 1F1B (input gradients sent on first,
                 # weight gradients in the wait that follows); the V-shaped variant (ZBV) is the branch above
                 sched = {"1f1b": "1F1B", "gpipe": "GPipe", "zbh1": "ZBH1", "zerobubble": "ZBH1"}.get(sched_name.lower(), "1F1B")
                 self._pp_runner = PipelineRunner(self.model, self._pp_group, schedule=sched)
+            if tp > 1:
+                from ..parallel import tp as TP
+
+                if model_config.is_moe:
+                    raise NotImplementedError("pipeline x tensor parallelism covers dense models")
+                TP.install_tp(self.model, self._tp_group, tp, self.tp_rank)
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
         elif tp > 1:
@@ -434,7 +462,7 @@ class B200TrainEngine(TrainEngine):
         self._shard_ranks = [self._train_ranks[(d * sp + s_) * tp + self.tp_rank] for d in range(self.dp_size) for s_ in range(sp)] \
             if self.local_index >= 0 else list(self._train_ranks)
         if getattr(self, "pp_size", 1) > 1:
-            self._shard_ranks = [self._train_ranks[self.pp_rank * self.dp_size + d] for d in range(self.dp_size)]
+            self._shard_ranks = [self._train_ranks[(self.pp_rank * self.dp_size + d) * tp + self.tp_rank] for d in range(self.dp_size)]
         n_shards = len(self._shard_ranks) if self._shard_group is not None else 1
         shard_rank = (self.dp_rank * sp + self.sp_rank) if n_shards > 1 else 0
         on_gpu = self.device.type == "cuda"
@@ -483,6 +511,7 @@ class B200TrainEngine(TrainEngine):
             self._replicated_ranges = self._find_replicated_ranges()
         if getattr(self, "pp_size", 1) > 1 and cfg.optimizer is not None:
             # the last stage's copy of a tied embedding must not count twice in the global norm
+            self._tp_replicated_ranges = self._replicated_ranges if tp > 1 else []
             self._replicated_ranges = []
             m = self.model
             if m.is_last and not m.is_first and m.embed_tokens is not None and m.lm_head is None and not model_config.is_critic:
@@ -601,7 +630,7 @@ class B200TrainEngine(TrainEngine):
 
     def current_data_parallel_head(self) -> int:
         if getattr(self, "pp_size", 1) > 1:
-            return self._train_ranks[self.dp_rank]          # first stage of this rank's pipeline
+            return self._train_ranks[self.dp_rank * getattr(self, "tp_size", 1)]          # first stage (first slice) of this rank's pipeline
         return self._train_ranks[self.dp_rank * self.sp_size * getattr(self, "tp_size", 1)]
 
     def is_data_parallel_head(self) -> bool:
@@ -831,7 +860,8 @@ class B200TrainEngine(TrainEngine):
         if getattr(self, "pp_size", 1) == 1:
             return outs
         box = [outs if self.is_pipeline_last_stage() else None]
-        src = self._train_ranks[getattr(self, "_pp_loss_rank", self.pp_size - 1) * self.dp_size + self.dp_rank]
+        tp = getattr(self, "tp_size", 1)
+        src = self._train_ranks[(getattr(self, "_pp_loss_rank", self.pp_size - 1) * self.dp_size + self.dp_rank) * tp + getattr(self, "tp_rank", 0)]
         dist.broadcast_object_list(box, src=src, group=self._pp_cpu_group)
         return box[0]
 
@@ -967,7 +997,18 @@ class B200TrainEngine(TrainEngine):
                 # global norm^2 = sum over every stage's shards; a tied embedding's second copy is left out
                 pre = torch.zeros(1, dtype=torch.float32, device=self.device)
                 g32 = gshard.float()
-                pre[0] = g32.pow(2).sum() - sum((g32[a:b].pow(2).sum() for a, b in self._replicated_ranges), torch.zeros((), device=self.device))
+                zero = torch.zeros((), device=self.device)
+                if tp > 1:
+                    # parameters that every tensor-parallel slice holds in full count once (1 / tp from each slice); the
+                    # tied copy is left out first, whether sliced or not
+                    keep = torch.ones_like(g32)
+                    for a, b in self._tp_replicated_ranges:
+                        keep[a:b] = 1.0 / tp
+                    for a, b in self._replicated_ranges:
+                        keep[a:b] = 0.0
+                    pre[0] = (g32.pow(2) * keep).sum()
+                else:
+                    pre[0] = g32.pow(2).sum() - sum((g32[a:b].pow(2).sum() for a, b in self._replicated_ranges), zero)
                 dist.all_reduce(pre, group=self._all_train_group)
             elif tp > 1:
                 # global norm^2 = sum over TP ranks of the sliced parameters' part + the replicated
@@ -1188,9 +1229,11 @@ class B200TrainEngine(TrainEngine):
             # the stages of the first pipeline write their own tensors; the head merges the index
             maps = [None] * self.pp_size
             if self.dp_rank == 0:
-                named = [(n, p.detach()) for n, p in self.model.named_native_parameters()]
-                mine = hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named),
-                                             rank_tag=f"pp{self.pp_rank}", write_index=False)
+                named = list(self._pp_native_full())
+                mine = {}
+                if getattr(self, "tp_rank", 0) == 0:          # one writer per stage
+                    mine = hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named),
+                                                 rank_tag=f"pp{self.pp_rank}", write_index=False)
                 dist.all_gather_object(maps, mine, group=self._pp_cpu_group)
             if head:
                 merged = {}
@@ -1276,6 +1319,20 @@ class B200TrainEngine(TrainEngine):
                 t = TP.unshard_tensors(self.model_config, n_, parts, expert_tp=xtp)
             yield n_, (t.to("cpu", copy=True) if to_cpu else t)
 
+    def _pp_native_full(self, skip_tied_copy: bool = True):
+        """(native name, full tensor) of this stage's parameters; tensor-parallel slices are gathered over the TP group
+        first (then a collective of that group: all its ranks must iterate)."""
+        from ..parallel import tp as TP
+
+        tp = getattr(self, "tp_size", 1)
+        for n_, p_ in self.model.named_native_parameters(skip_tied_copy=skip_tied_copy):
+            t = p_.detach()
+            if tp > 1:
+                parts = [torch.empty_like(t) for _ in range(tp)]
+                dist.all_gather(parts, t.contiguous(), group=self._tp_group)
+                t = TP.unshard_tensors(self.model_config, n_, parts)
+            yield n_, t
+
     def _gathered_full_tensors(self):
         """Yields (name, full tensor) for a tensor-parallel model; a collective over the TP group."""
         from ..parallel import tp as TP
@@ -1290,8 +1347,21 @@ class B200TrainEngine(TrainEngine):
             mine = {n: p for n, p in self.model.named_native_parameters(skip_tied_copy=False)}
             plan = hf_io.hf_to_native_plan(self.model_config)
             wanted = {hf for n in mine for hf, _, _ in plan[n]}
-            hf_io.load_hf_tensors_into(self.model_config, {n: p.data for n, p in mine.items()},
-                                       ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
+            tp_ = getattr(self, "tp_size", 1)
+            if tp_ > 1:
+                # full-size staging tensors for this stage's names, sliced into the local parameters afterwards
+                from ..parallel import tp as TP
+
+                shapes = {n: tuple(p.shape) for n, p in build_model(self.model_config, dtype=self.model.dtype, device="meta").named_parameters()}
+                stage = {n: torch.empty(shapes[n], dtype=p.dtype, device=p.device) for n, p in mine.items()}
+                hf_io.load_hf_tensors_into(self.model_config, stage, ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
+                with torch.no_grad():
+                    for n, p in mine.items():
+                        p.copy_(TP.shard_tensor(self.model_config, n, stage[n], tp_, self.tp_rank))
+                del stage
+            else:
+                hf_io.load_hf_tensors_into(self.model_config, {n: p.data for n, p in mine.items()},
+                                           ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
         elif meta.weight_format == "hf" and getattr(self, "_z3", None) is not None:
             # tensors stream from the files; every rank keeps what falls into its shard
             hf_io.load_hf_tensors_into(self.model_config, None, hf_io.iter_safetensors(meta.path), strict=not self.config.is_critic,
@@ -1408,12 +1478,12 @@ class B200TrainEngine(TrainEngine):
             return dict(self._z3.full_tensors(to_cpu=True))
         if getattr(self, "ep_size", 1) > 1:
             return dict(self._ep_full_named_tensors(to_cpu=True))
-        if getattr(self, "tp_size", 1) > 1:
+        if getattr(self, "tp_size", 1) > 1 and getattr(self, "pp_size", 1) == 1:
             return {n: t.to("cpu", copy=True) for n, t in self._gathered_full_tensors()}
         if getattr(self, "pp_size", 1) > 1:
             # every stage contributes its own tensors; all stages end up with the full dictionary
             parts = [None] * self.pp_size
-            mine = {n: p.detach().to("cpu", copy=True) for n, p in self.model.named_native_parameters()}
+            mine = {n: t.to("cpu", copy=True) for n, t in self._pp_native_full()}
             dist.all_gather_object(parts, mine, group=self._pp_cpu_group)
             out = {}
             for d_ in parts:

@@ -47,9 +47,10 @@ class PipelineStage(nn.Module):
     """The slice of a :class:`CausalLM` one pipeline rank owns."""
 
     def __init__(self, cfg: ModelConfig, stage: int, n_stages: int, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None,
-                 layer_ranges: Optional[list[range]] = None, init_full: Optional[Callable] = None):
+                 layer_ranges: Optional[list[range]] = None, init_full: Optional[Callable] = None, tp: int = 1, tp_rank: int = 0):
         super().__init__()
         self.cfg, self.stage, self.n_stages = cfg, stage, n_stages
+        self.tp, self.tp_rank = tp, tp_rank
         self.dtype = dtype
         self.is_first, self.is_last = stage == 0, stage == n_stages - 1
         ranges = layer_ranges or split_layers(cfg.num_layers, n_stages)
@@ -59,6 +60,13 @@ class PipelineStage(nn.Module):
         full = build_model(cfg, dtype=dtype, device=device, seed=seed)
         if init_full is not None:
             init_full(full)
+        if tp > 1:
+            # tensor parallelism inside the stage: the same weights, sliced (heads / MLP columns) for this TP rank
+            from . import tp as TP
+
+            local = build_model(TP.local_config(cfg, tp), dtype=dtype, device=device, seed=seed)
+            TP.load_sharded_from_full(local, cfg, {n: p.detach() for n, p in full.named_parameters()}, tp, tp_rank)
+            full = local
         self.layers = nn.ModuleList([full.layers[i] for i in self.layer_range])
         self.embed_tokens = full.embed_tokens if (self.is_first or (self.is_last and cfg.tie_word_embeddings and not cfg.is_critic)) else None
         self.norm = full.norm if self.is_last else None
@@ -335,7 +343,7 @@ class InterleavedStages(nn.Module):
     attributes the engine reads from a stage (first / last flags, embedding, heads, native parameter names)."""
 
     def __init__(self, cfg: ModelConfig, rank: int, n_ranks: int, n_chunks: int, dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None,
-                 init_full: Optional[Callable] = None, placement: str = "loop"):
+                 init_full: Optional[Callable] = None, placement: str = "loop", tp: int = 1, tp_rank: int = 0):
         super().__init__()
         if placement == "v" and n_chunks != 2:
             raise ValueError("the V-shaped placement has exactly two chunks per rank")
@@ -343,7 +351,7 @@ class InterleavedStages(nn.Module):
         self.n_chunks, self.placement = n_chunks, placement
         total = n_ranks * n_chunks
         self.chunks = nn.ModuleList([PipelineStage(cfg, stage_of(rank, v, n_ranks, placement), total, dtype=dtype, device=device, seed=seed,
-                                                   init_full=init_full) for v in range(n_chunks)])
+                                                   init_full=init_full, tp=tp, tp_rank=tp_rank) for v in range(n_chunks)])
         self.is_first = any(c.is_first for c in self.chunks)
         self.is_last = any(c.is_last for c in self.chunks)
         if self.is_first and self.is_last and n_ranks > 1 and cfg.tie_word_embeddings and not cfg.is_critic:

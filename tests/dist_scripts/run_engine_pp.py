@@ -47,17 +47,23 @@ def cfg_of(backend, vpp=1, schedule="1F1B"):
     return c
 
 
-def check(mc, tag, vpp=1, schedule="1F1B", loss_rank=1):
+def check(mc, tag, vpp=1, schedule="1F1B", loss_rank=1, backend="native:d2p2"):
     rank = dist.get_rank()
-    eng = B200TrainEngine(cfg_of("native:d2p2", vpp, schedule))
+    eng = B200TrainEngine(cfg_of(backend, vpp, schedule))
     eng.create_process_group()
     eng.initialize(model_config=mc, seed=5)
-    assert (eng.dp_size, eng.pp_size) == (2, 2) and eng.pp_rank == rank // 2 and eng.dp_rank == rank % 2
-    assert eng.is_data_parallel_head() == (rank < 2) and eng.current_data_parallel_head() == rank % 2
+    if backend == "native:d2p2":
+        assert (eng.dp_size, eng.pp_size) == (2, 2) and eng.pp_rank == rank // 2 and eng.dp_rank == rank % 2
+        assert eng.is_data_parallel_head() == (rank < 2) and eng.current_data_parallel_head() == rank % 2
+    else:       # d{1,2}p2t2: index = (stage * dp + d) * tp + t
+        dp_ = eng.dp_size
+        assert (eng.pp_size, eng.tp_size) == (2, 2) and eng.pp_rank == rank // (2 * dp_) and eng.tp_rank == rank % 2 and eng.dp_rank == (rank // 2) % dp_
+        assert eng.is_data_parallel_head() == (rank in (0, 2)[:dp_]) and eng.current_data_parallel_head() == 2 * eng.dp_rank
+        assert eng.model.layers[0].self_attn.qkv_proj.shape[0] * 2 == (mc.num_heads + 2 * mc.num_kv_heads) * mc.head_dim
     assert eng.is_pipeline_last_stage() == (eng.pp_rank == loss_rank)
     batch = make_batch(mc.vocab_size)
-    d = eng.dp_rank
-    mine = {k: v[d * 4:(d + 1) * 4] for k, v in batch.items()}
+    d, per = eng.dp_rank, 8 // eng.dp_size
+    mine = {k: v[d * per:(d + 1) * per] for k, v in batch.items()}
     stats = [eng.train_batch(mine, loss_fn, weight_fn) for _ in range(2)]
     ref = B200TrainEngine(cfg_of("d1"))
     ref.set_train_ranks([rank])
@@ -68,13 +74,15 @@ def check(mc, tag, vpp=1, schedule="1F1B", loss_rank=1):
         assert abs(a["grad_norm"] - b["grad_norm"]) < 2e-3 * max(1.0, b["grad_norm"]), (tag, a, b)
     full = {n: p.detach() for n, p in ref.model.named_parameters()}
     worst = 0.0
+    from areal_b200.parallel import tp as TP
+
     for n, p in eng.model.named_native_parameters(skip_tied_copy=False):
-        diff = (p.detach() - full[n]).abs()
+        diff = (p.detach() - TP.shard_tensor(mc, n, full[n], getattr(eng, "tp_size", 1), getattr(eng, "tp_rank", 0))).abs()
         worst = max(worst, diff.max().item())
         assert diff.mean().item() < 2e-5 and diff.max().item() < 5e-3, f"{tag}: weights diverged for {n}: max {diff.max().item()}"
     # forward-only outputs reach every stage and match the unsplit engine
     lp = eng.forward_batch(mine)
-    lref = ref.forward_batch(batch)[d * 4:(d + 1) * 4]
+    lref = ref.forward_batch(batch)[d * per:(d + 1) * per]
     assert lp.shape == mine["input_ids"].shape, (lp.shape, mine["input_ids"].shape)
     # a sequence's last position is scored against its packing neighbour's first token: compare inside the loss mask
     err = ((lp - lref[:, : lp.shape[1]]).abs() * mine["loss_mask"]).max().item()
@@ -102,6 +110,12 @@ def check(mc, tag, vpp=1, schedule="1F1B", loss_rank=1):
 
 def main():
     dist.init_process_group("gloo")
+    if os.environ.get("PP_LAYOUT"):           # one layout on its own world size (8 ranks: 2 replicas x 2 stages x 2 slices)
+        check(preset("tiny-qwen3", tie_word_embeddings=True), "pp-tp-dp", backend=os.environ["PP_LAYOUT"])
+        print("ENGINE_PP_OK", flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     check(preset("tiny-qwen3"), "untied")
     check(preset("tiny-qwen3", tie_word_embeddings=True), "tied")
     check(preset("tiny-qwen3", tie_word_embeddings=True), "zero-bubble-tied", schedule="ZBH1")   # split backward, weight gradients deferred
@@ -110,6 +124,10 @@ def main():
     # two chunks per rank placed in a V (rank 0 holds the first and the last stage, so the loss lives there), greedy order
     check(preset("tiny-qwen3", num_layers=4), "zbv", schedule="ZBV", loss_rank=0)
     check(preset("tiny-qwen3", num_layers=4, tie_word_embeddings=True), "zbv-tied", schedule="ZBV", loss_rank=0)
+    # tensor parallelism inside the stages: 2 stages x 2 slices
+    check(preset("tiny-qwen3"), "pp-tp", backend="native:d1p2t2")
+    check(preset("tiny-qwen3", tie_word_embeddings=True), "pp-tp-tied-zbh1", schedule="ZBH1", backend="native:d1p2t2")
+    check(preset("tiny-qwen3", num_layers=4, tie_word_embeddings=True), "pp-tp-interleaved", vpp=2, backend="native:d1p2t2")
     print("ENGINE_PP_OK", flush=True)
     dist.barrier()
     dist.destroy_process_group()

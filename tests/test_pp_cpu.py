@@ -50,6 +50,17 @@ def test_train_engine_pipeline_x_data_parallel(tmp_path):
     assert r.stdout.count("ENGINE_PP_OK") == 4
 
 
+def test_train_engine_data_pipeline_tensor_parallel_8_ranks(tmp_path):
+    """``native:d2p2t2``: two replicas x two stages x two tensor-parallel slices per stage against one rank (tied
+    embedding: its last-stage copy and the slices' replicated parameters each count once in the global norm)."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", PP_SAVE_DIR=str(tmp_path), PP_LAYOUT="native:d2p2t2")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=8", "--master-addr",
+                        "127.0.0.1", "--master-port", "29933", os.path.join(ROOT, "tests", "dist_scripts", "run_engine_pp.py")], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ENGINE_PP_OK") == 8
+
+
 @pytest.mark.parametrize("ranks,port", [(2, 29941), (4, 29943)])
 def test_train_engine_expert_parallel(tmp_path, ranks, port):
     """d{N}e2 engine on a tiny MoE model (dense parameters sharded over all ranks, experts over the
