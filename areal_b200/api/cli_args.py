@@ -392,6 +392,53 @@ class vLLMConfig:
     extra: dict = field(default_factory=dict)   # server flags of the reference's backend, accepted and kept
     __allow_extra__ = True
 
+    @staticmethod
+    def build_args(cfg: "vLLMConfig", tp_size: int = 1, pp_size: int = 1, host: Optional[str] = None, port: Optional[int] = None,
+                   dist_init_addr: Optional[str] = None, n_nodes: int = 1, node_rank: int = 0) -> dict:
+        """Flags of a vLLM OpenAI-compatible server for this configuration (reference: ``areal/api/cli_args.py:2081-2117``)."""
+        a = {k: v for k, v in dataclasses.asdict(cfg).items() if k != "extra"}
+        a.update(cfg.extra or {})
+        a.update(tokenizer=cfg.model, load_format="auto", trust_remote_code=True, tensor_parallel_size=tp_size, pipeline_parallel_size=pp_size)
+        if host is not None:
+            a["host"] = host
+        if port is not None:
+            a["port"] = port
+        if n_nodes > 1:
+            a.update(nnodes=n_nodes, node_rank=node_rank)
+            if dist_init_addr:
+                h, _, p_ = dist_init_addr.rpartition(":")
+                a.update(master_addr=h, master_port=p_)
+            if node_rank > 0:
+                a["headless"] = True
+        return a
+
+    @staticmethod
+    def build_cmd(cfg: "vLLMConfig", tp_size: int = 1, pp_size: int = 1, module: str = "vllm.entrypoints.openai.api_server", **kw) -> list[str]:
+        return server_cmd(module, vLLMConfig.build_args(cfg, tp_size, pp_size, **kw))
+
+
+def server_cmd(module: str, args: dict) -> list[str]:
+    """``python -m module --flag value ...``: booleans become bare flags (left out when false), ``None`` is left out,
+    lists repeat their values after the flag."""
+    import sys
+
+    cmd = [sys.executable, "-m", module]
+    for k, v in args.items():
+        flag = "--" + k.replace("_", "-")
+        if v is None or v is False or v == "":
+            continue
+        if v is True:
+            cmd.append(flag)
+        elif isinstance(v, (list, tuple)):
+            cmd += [flag] + [str(x) for x in v]
+        elif isinstance(v, dict):
+            import json
+
+            cmd += [flag, json.dumps(v)]
+        else:
+            cmd += [flag, str(v)]
+    return cmd
+
 
 @dataclass
 class SGLangConfig:
@@ -421,6 +468,25 @@ class SGLangConfig:
     max_lora_rank: Optional[int] = None
     extra: dict = field(default_factory=dict)   # server flags of the reference's backend, accepted and kept
     __allow_extra__ = True
+
+    @staticmethod
+    def build_args(cfg: "SGLangConfig", tp_size: int = 1, base_gpu_id: int = 0, host: Optional[str] = None, port: Optional[int] = None,
+                   dist_init_addr: Optional[str] = None, n_nodes: int = 1, node_rank: int = 0, pp_size: int = 1) -> dict:
+        """Flags of ``sglang.launch_server`` for this configuration (reference: ``areal/api/cli_args.py:2258-2330``)."""
+        a = {k: v for k, v in dataclasses.asdict(cfg).items() if k != "extra"}
+        a.update(cfg.extra or {})
+        a.update(tokenizer_path=cfg.model_path, tokenizer_mode="auto", load_format="auto", trust_remote_code=True, device="cuda",
+                 is_embedding=False, tp_size=tp_size, pp_size=pp_size, base_gpu_id=base_gpu_id, nnodes=n_nodes, node_rank=node_rank,
+                 dist_init_addr=dist_init_addr)
+        if host is not None:
+            a["host"] = host
+        if port is not None:
+            a["port"] = port
+        return a
+
+    @staticmethod
+    def build_cmd(cfg: "SGLangConfig", tp_size: int = 1, base_gpu_id: int = 0, module: str = "sglang.launch_server", **kw) -> list[str]:
+        return server_cmd(module, SGLangConfig.build_args(cfg, tp_size, base_gpu_id, **kw))
 
 
 @dataclass

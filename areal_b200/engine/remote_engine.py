@@ -127,6 +127,8 @@ class RemoteInfEngine(InferenceEngine):
     def launch_server(self, server_args: dict[str, Any]) -> str:
         """Starts a local server process (``python -m areal_b200.engine.server``) and returns
         its address once it reports ready."""
+        if self.backend.name != "native" or "cmd" in server_args:
+            return self._launch_external_server(dict(server_args))
         cmd = [sys.executable, "-m", "areal_b200.engine.server"]
         for k, v in server_args.items():
             cmd += [f"--{k.replace('_', '-')}", str(v)]
@@ -146,6 +148,42 @@ class RemoteInfEngine(InferenceEngine):
         if addr is None:
             raise TimeoutError("inference server did not become ready")
         threading.Thread(target=lambda: [None for _ in p.stdout], daemon=True).start()  # keep draining the pipe
+        self.addresses.append(addr)
+        return addr
+
+    def _launch_external_server(self, server_args: dict[str, Any]) -> str:
+        """An SGLang / vLLM server as a child process: ``server_args`` are the server's own flags (``host`` and ``port``
+        among them; see ``SGLangConfig.build_args`` / ``vLLMConfig.build_args``) or carry a ready command line under
+        ``cmd``. Ready when its health route answers. Reference: ``areal/engine/sglang_remote.py:394-420``,
+        ``areal/engine/vllm_remote.py`` (``launch_server``)."""
+        import urllib.request
+
+        from ..api.cli_args import server_cmd
+        from ..utils.network import find_free_ports
+
+        host = server_args.get("host") or "127.0.0.1"
+        port = server_args.get("port") or find_free_ports(1)[0]
+        cmd = server_args.pop("cmd", None)
+        if cmd is None:
+            server_args.update(host=host, port=port)
+            module = {"sglang": "sglang.launch_server", "vllm": "vllm.entrypoints.openai.api_server"}[self.backend.name]
+            cmd = server_cmd(module, server_args)
+        p = subprocess.Popen([str(c) for c in cmd], stdout=subprocess.DEVNULL, stderr=subprocess.STDOUT, start_new_session=True)
+        self._server_procs.append(p)
+        addr = f"{host}:{port}"
+        deadline = time.monotonic() + self.config.setup_timeout
+        while True:
+            if p.poll() is not None:
+                raise RuntimeError(f"{self.backend.name} server exited with code {p.returncode}")
+            try:
+                with urllib.request.urlopen(f"http://{addr}{self.backend.health_endpoint}", timeout=2) as r:
+                    if r.status == 200:
+                        break
+            except OSError:
+                pass
+            if time.monotonic() > deadline:
+                raise TimeoutError(f"{self.backend.name} server {addr} not healthy after {self.config.setup_timeout}s")
+            time.sleep(0.2)
         self.addresses.append(addr)
         return addr
 

@@ -1,5 +1,6 @@
 """HTTP inference server + remote client engine on CPU (tiny model)."""
 import asyncio
+import sys
 import threading
 import time
 
@@ -210,3 +211,45 @@ def test_vllm_wire_format_and_control_routes():
             get_backend("tgi")
     finally:
         srv.shutdown()
+
+
+def test_server_command_builders_and_external_launch(tmp_path):
+    """Flag lists for SGLang / vLLM servers from their config sections, and the launch of an external server process
+    (a stand-in that answers the health route) that the engine waits for and tears down."""
+    import textwrap
+
+    from areal_b200.api.cli_args import InferenceEngineConfig, SGLangConfig, server_cmd, vLLMConfig
+    from areal_b200.engine.remote_engine import RemoteInfEngine
+    from areal_b200.utils.network import find_free_ports
+
+    c = SGLangConfig.build_cmd(SGLangConfig(model_path="/m", attention_backend=None, extra={"enable_deterministic_inference": True}), 2, 4,
+                               host="127.0.0.1", port=3000, dist_init_addr="10.0.0.1:99", n_nodes=2, node_rank=1)
+    assert c[1:3] == ["-m", "sglang.launch_server"] and c[c.index("--tp-size") + 1] == "2" and c[c.index("--base-gpu-id") + 1] == "4"
+    assert "--disable-radix-cache" in c and "--enable-deterministic-inference" in c and "--disable-cuda-graph" not in c and "--attention-backend" not in c
+    assert c[c.index("--dist-init-addr") + 1] == "10.0.0.1:99" and c[c.index("--node-rank") + 1] == "1"
+    v = vLLMConfig.build_cmd(vLLMConfig(model="/m"), 2, 1, port=8000, n_nodes=2, node_rank=1, dist_init_addr="10.0.0.1:555")
+    assert v[v.index("--tensor-parallel-size") + 1] == "2" and "--headless" in v and v[v.index("--master-port") + 1] == "555" and "--enforce-eager" not in v
+    assert server_cmd("m", {"a_b": [1, 2], "c": {"k": 1}, "d": None, "e": False, "f": True})[3:] == ["--a-b", "1", "2", "--c", '{"k": 1}', "--f"]
+    fake = tmp_path / "fake_server.py"
+    fake.write_text(textwrap.dedent("""
+        import sys
+        from http.server import BaseHTTPRequestHandler, HTTPServer
+        port = int(sys.argv[sys.argv.index("--port") + 1])
+        class H(BaseHTTPRequestHandler):
+            def log_message(self, *a): pass
+            def do_GET(self):
+                self.send_response(200 if self.path == "/health" else 404); self.send_header("Content-Length", "0"); self.end_headers()
+        HTTPServer(("127.0.0.1", port), H).serve_forever()
+    """))
+    port = find_free_ports(1)[0]
+    eng = RemoteInfEngine(InferenceEngineConfig(setup_timeout=30), [], backend="sglang")
+    addr = eng.launch_server({"cmd": [sys.executable, str(fake), "--port", port], "host": "127.0.0.1", "port": port})
+    try:
+        assert addr == f"127.0.0.1:{port}" and eng.addresses == [addr] and eng._server_procs[0].poll() is None
+    finally:
+        proc = eng._server_procs[0]
+        eng.teardown_server()
+    assert proc.poll() is not None
+    bad = RemoteInfEngine(InferenceEngineConfig(setup_timeout=10), [], backend="vllm")
+    with pytest.raises(RuntimeError, match="exited with code"):
+        bad.launch_server({"cmd": [sys.executable, "-c", "raise SystemExit(3)"], "port": find_free_ports(1)[0]})
