@@ -647,8 +647,14 @@ class TensorBoardConfig:
 
 @dataclass
 class TrackioConfig:
-    mode: str = "disabled"
-    project: Optional[str] = None
+    mode: str = "disabled"            # disabled | online | local
+    project: Optional[str] = None     # defaults to the experiment name
+    name: Optional[str] = None        # defaults to the trial name
+    space_id: Optional[str] = None    # Hugging Face Space that also receives the metrics
+
+    def __post_init__(self):
+        if self.mode not in ("disabled", "online", "local"):
+            raise ValueError(f"trackio.mode must be disabled, online or local, got '{self.mode}'")
 
 
 @dataclass

@@ -203,21 +203,23 @@ class WorkflowExecutor:
                     self._expected_keys = set(traj.keys())
             ok = True if should_accept_fn is None else bool(should_accept_fn(traj))
             if ok and self.config.dump_to_file:
-                self._dump(traj, task_id)
+                self._dump(traj, task_id, is_eval)
             return traj, ok
         return run
 
-    def _dump(self, traj, task_id):
-        root = os.path.join(self.config.fileroot or "/tmp/areal", "rollout_dump")
-        os.makedirs(root, exist_ok=True)
-        if self._dump_fh is None:
-            self._dump_fh = open(os.path.join(root, f"v{self.engine.get_version()}_{os.getpid()}.jsonl"), "a")
-        rec = {"task_id": task_id, "version": self.engine.get_version()}
-        for k, v in traj.items():
-            if torch.is_tensor(v):
-                rec[k] = v.tolist()
-        self._dump_fh.write(json.dumps(rec) + "\n")
-        self._dump_fh.flush()
+    def _dump(self, traj, task_id, is_eval: bool = False):
+        """One readable line per sample (see ``rollout/dump.py``); a failure here never fails the episode."""
+        from . import dump as D
+
+        try:
+            root = D.dump_dir(self.config, is_eval) or os.path.join("/tmp/areal", "eval-rollout" if is_eval else "rollout")
+            if getattr(self, "_dump_tokenizer", None) is None and getattr(self.config, "tokenizer_path", ""):
+                from transformers import AutoTokenizer
+
+                self._dump_tokenizer = AutoTokenizer.from_pretrained(self.config.tokenizer_path)
+            D.dump_trajectory(traj, task_id, root, getattr(self, "_dump_tokenizer", None), self.engine.get_version())
+        except Exception as e:  # noqa: BLE001
+            logger.warning("trajectory of task %s not dumped: %s", task_id, e)
 
     # ------------------------------------------------------------------ public API
     def submit(self, data: dict[str, Any], workflow=None, workflow_kwargs=None, should_accept_fn=None,

@@ -52,6 +52,28 @@ class StatsLogger:
             except Exception as e:  # pragma: no cover
                 logger.warning("wandb unavailable: %r", e)
 
+        # swanlab and trackio share wandb's call shape: init(project, name, config) / log(dict, step) / finish()
+        self._trackers = []
+        sw = c.swanlab
+        if (sw.mode or "disabled") != "disabled":
+            self._open_tracker("swanlab", project=sw.project or c.experiment_name, experiment_name=sw.name or c.trial_name,
+                               config={**(sw.config or {}), **(exp_config if isinstance(exp_config, dict) else {})} or None,
+                               logdir=sw.logdir or os.path.join(d, "swanlab"), mode=sw.mode)
+        tk = c.trackio
+        if tk.mode != "disabled":
+            self._open_tracker("trackio", project=tk.project or c.experiment_name, name=tk.name or c.trial_name,
+                               config=exp_config if isinstance(exp_config, dict) else None, space_id=tk.space_id)
+
+    def _open_tracker(self, module: str, **init_kw):
+        try:
+            import importlib
+
+            m = importlib.import_module(module)
+            m.init(**{k: v for k, v in init_kw.items() if v is not None})
+            self._trackers.append(m)
+        except Exception as e:
+            logger.warning("%s unavailable: %r", module, e)
+
     def commit(self, epoch: int, step: int, global_step: int, data):
         if self.rank != 0:
             return
@@ -74,6 +96,8 @@ class StatsLogger:
                 self._tb.add_scalar(k, v, global_step)
         if self._wandb:
             self._wandb.log(merged, step=global_step)
+        for m in getattr(self, "_trackers", ()):
+            m.log(merged, step=global_step)
         self._last_commit_step = global_step
 
     def close(self):
@@ -83,6 +107,8 @@ class StatsLogger:
             self._tb.close()
         if self._wandb:
             self._wandb.finish()
+        for m in getattr(self, "_trackers", ()):
+            m.finish()
 
     def state_dict(self):
         return {"last_commit_step": self._last_commit_step}
