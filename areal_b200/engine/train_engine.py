@@ -526,8 +526,10 @@ class B200TrainEngine(TrainEngine):
             self.optimizer = ShardedAdamW(self.store, cfg.optimizer, total_steps=total, group=self._shard_group)
             if self.expert_store is not None:
                 self.expert_optimizer = ShardedAdamW(self.expert_store, cfg.optimizer, total_steps=total, group=self._edp_group)
-        if model_config.is_vlm and (tp > 1 or (self.sp_size > 1 and getattr(cfg.fsdp, "context_parallel", "ulysses") != "ulysses")):
-            raise NotImplementedError("vision-language models run with data and Ulysses sequence parallelism (no tensor / zig-zag split yet)")
+        if model_config.is_vlm and ((tp > 1 and (self.sp_size > 1 or getattr(self, "pp_size", 1) > 1 or bool(cfg.fsdp.tp_sequence_parallel)))
+                                    or (self.sp_size > 1 and getattr(cfg.fsdp, "context_parallel", "ulysses") != "ulysses")):
+            raise NotImplementedError("vision-language models run with data parallelism plus either Ulysses sequence parallelism or plain "
+                                      "tensor parallelism of the language model (the image tower stays whole; no zig-zag / pipeline split)")
         self._cp_zigzag = self.sp_size > 1 and getattr(cfg.fsdp, "context_parallel", "ulysses") == "zigzag"
         self._zz_perm = None
         if getattr(cfg.fsdp, "context_parallel", "ulysses") not in ("ulysses", "zigzag"):

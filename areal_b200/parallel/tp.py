@@ -49,7 +49,7 @@ def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank:
     if tp == 1:
         return full
     leaf = name.rsplit(".", 1)[-1]
-    if leaf in ("embed_tokens", "lm_head"):       # replicated here (vocab parallelism is separate)
+    if leaf in ("embed_tokens", "lm_head") or name.startswith("visual."):       # replicated here (vocab parallelism is separate)
         return full
     if full.dim() == 3:                             # stacked experts [E, rows, cols]
         if not expert_tp:
@@ -76,7 +76,7 @@ def unshard_tensors(cfg: ModelConfig, name: str, parts: list[torch.Tensor], expe
         return parts[0]
     leaf = name.rsplit(".", 1)[-1]
     p0 = parts[0]
-    if p0.dim() == 3 and not expert_tp:
+    if (p0.dim() == 3 and not expert_tp) or name.startswith("visual."):
         return p0
     if leaf in ("embed_tokens", "lm_head") or (p0.dim() == 1 and leaf != "qkv_bias") or leaf in ("router",):
         return p0
@@ -212,8 +212,8 @@ def replicated_parameter_names(model) -> list[str]:
     out = []
     for n, p in model.named_parameters():
         leaf = n.rsplit(".", 1)[-1]
-        if p.dim() == 1 and leaf != "qkv_bias" or leaf in ("embed_tokens", "lm_head", "router", "value_head"):
-            out.append(n)
+        if p.dim() == 1 and leaf != "qkv_bias" or leaf in ("embed_tokens", "lm_head", "router", "value_head") or n.startswith("visual."):
+            out.append(n)            # (the image tower of a vision-language model is not sliced: every rank runs all of it)
     return out
 
 

@@ -131,3 +131,15 @@ def test_vision_language_model_under_ulysses_matches_single_rank():
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=500)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("VLM_SP_OK") == 2
+
+
+def test_vision_language_model_with_tensor_parallel_language_model():
+    """Qwen2.5-VL and Qwen3-VL with the language model sliced over two ranks and the image tower whole on both (its
+    parameters count once in the global norm): losses, gradient norms, gathered weights after two steps and
+    forward-only log-probs equal the single-rank engine."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29995", os.path.join(ROOT, "tests", "dist_scripts", "run_vlm_tp.py")],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=500)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("VLM_TP_OK") == 2
