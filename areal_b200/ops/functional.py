@@ -435,16 +435,21 @@ class _LinearSplit(torch.autograd.Function):
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dx = (dy @ w) if ctx.needs_input_grad[0] else None
+        dw = None
         if ctx.needs_input_grad[1]:
             dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
-
-            def wgrad(dy2=dy2, x2=x2, w=w):
-                _accumulate_wgrad(w, dy2.float().t() @ x2.float())
-            if _WGRAD_QUEUE is not None:
-                _WGRAD_QUEUE.append(wgrad)
+            if not w.is_leaf and getattr(w, "main_grad", None) is None:
+                # a view of a parameter (one expert of a stack): its gradient has to travel on through autograd, so it
+                # cannot wait in the queue
+                dw = (dy2.float().t() @ x2.float()).to(w.dtype)
             else:
-                wgrad()
-        return dx, None, (dy if ctx.has_resid else None)
+                def wgrad(dy2=dy2, x2=x2, w=w):
+                    _accumulate_wgrad(w, dy2.float().t() @ x2.float())
+                if _WGRAD_QUEUE is not None:
+                    _WGRAD_QUEUE.append(wgrad)
+                else:
+                    wgrad()
+        return dx, dw, (dy if ctx.has_resid else None)
 
 
 class _Linear(torch.autograd.Function):
@@ -477,8 +482,9 @@ class _Linear(torch.autograd.Function):
             gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.grad_buf, epi=EPI_F32_ACC)
         elif ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
-            if _WGRAD_QUEUE is not None:
-                # split backward: the product runs when the caller flushes the queue
+            if _WGRAD_QUEUE is not None and (mg is not None or w.is_leaf):
+                # split backward: the product runs when the caller flushes the queue (a view of a parameter without
+                # its own gradient buffer cannot wait: its gradient travels on through autograd)
                 def wgrad(dy2=dy2, x2=x2, w=w, mg=mg):
                     if mg is not None:
                         gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, epi=EPI_F32_ACC)

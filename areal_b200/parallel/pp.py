@@ -101,7 +101,12 @@ class PipelineStage(nn.Module):
             else:
                 h, resid = layer(h, resid, pb, cos, sin, None)
         if self.is_last:
-            out, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
+            if self.cfg.rms_norm_offset:           # (1 + w) norms of the hybrid linear-attention family
+                from ..models.hybrid import rmsnorm_offset
+
+                out, _ = rmsnorm_offset(h, self.norm, self.cfg.rms_norm_eps, resid)
+            else:
+                out, _ = OF.rmsnorm(h, self.norm, self.cfg.rms_norm_eps, resid)
             return out
         return h + resid if resid is not None else h
 

@@ -124,6 +124,10 @@ def main():
     # two chunks per rank placed in a V (rank 0 holds the first and the last stage, so the loss lives there), greedy order
     check(preset("tiny-qwen3", num_layers=4), "zbv", schedule="ZBV", loss_rank=0)
     check(preset("tiny-qwen3", num_layers=4, tie_word_embeddings=True), "zbv-tied", schedule="ZBV", loss_rank=0)
+    # linear-attention (gated delta rule) layers in the stages, dense and MoE
+    check(preset("tiny-qwen3.5"), "hybrid")
+    check(preset("tiny-qwen3.5-moe"), "hybrid-moe", schedule="ZBH1")     # split backward with per-expert weight views
+    check(preset("tiny-qwen3-moe"), "moe-zbh1", schedule="ZBH1")
     # tensor parallelism inside the stages: 2 stages x 2 slices
     check(preset("tiny-qwen3"), "pp-tp", backend="native:d1p2t2")
     check(preset("tiny-qwen3", tie_word_embeddings=True), "pp-tp-tied-zbh1", schedule="ZBH1", backend="native:d1p2t2")

@@ -128,6 +128,21 @@ def test_deferred_weight_gradients_match_plain_backward():
     finally:
         OF.SPLIT_BACKWARD = False
     assert w1.grad is None and torch.allclose(w1.main_grad, ref[1], atol=1e-4)
+    # a weight that is a VIEW of a parameter (one expert of a stack, the per-expert loop of the CPU path): its gradient
+    # has to reach the parameter through autograd, so it is computed at once instead of waiting in the queue
+    w3 = torch.nn.Parameter(torch.randn(3, 5, 8))
+    xs = torch.randn(4, 8)
+    OF.linear(xs, w3[1]).square().sum().backward()
+    want = w3.grad.clone()
+    w3.grad = None
+    OF.SPLIT_BACKWARD = True
+    try:
+        with OF.deferred_wgrad() as q:
+            OF.linear(xs, w3[1]).square().sum().backward()
+        assert len(q) == 0
+    finally:
+        OF.SPLIT_BACKWARD = False
+    assert torch.allclose(w3.grad, want, atol=1e-5) and w3.grad[0].abs().max() == 0
 
 
 @pytest.mark.parametrize("P,M", [(2, 4), (4, 8), (4, 5), (8, 16)])
