@@ -315,6 +315,27 @@ class B200TrainEngine(TrainEngine):
             g = dist.new_group(last, backend="gloo") if dp > 1 else None
             if self.pp_rank == self._pp_loss_rank and t == self.tp_rank:
                 self._stats_group = g
+        self.ep_size = getattr(self.parallel, "ep_size", 1) or 1
+        self.ep_rank, self._ep_group, self._edp_group = 0, None, None
+        if self.ep_size > 1:
+            # experts of a stage's MoE layers spread over consecutive data-parallel ranks of that stage
+            ep = self.ep_size
+            if tp > 1 or dp % ep:
+                raise NotImplementedError(f"expert parallelism inside pipeline stages: ep={ep} must divide dp={dp}, no tensor parallelism")
+            self.etp_size = 1
+            self.ep_rank = self.dp_rank % ep
+            for s_ in range(pp):
+                for blk in range(dp // ep):
+                    g = dist.new_group([gid(s_, blk * ep + e, 0) for e in range(ep)])
+                    if s_ == self.pp_rank and blk == self.dp_rank // ep:
+                        self._ep_group = g
+                for e in range(ep):
+                    ranks = [gid(s_, blk * ep + e, 0) for blk in range(dp // ep)]
+                    g = dist.new_group(ranks) if len(ranks) > 1 else None
+                    if s_ == self.pp_rank and e == self.ep_rank:
+                        self._edp_group = g
+            self._edp_index, self._n_edp = self.dp_rank // ep, dp // ep
+            self._export_member = self.dp_rank < ep
         t_ = torch.zeros(1, device=self.device)
         dist.all_reduce(t_, group=self._all_train_group)
         return self
@@ -365,6 +386,8 @@ class B200TrainEngine(TrainEngine):
             vpp = max(int(getattr(self.parallel, "virtual_pipeline_parallel_size", 0) or 0), int(cfg.megatron.virtual_pipeline_parallel_size or 1), 1)
             sched_name = str(getattr(cfg.archon, "pp_schedule", "1F1B"))
             zbv = sched_name.lower() in ("zbv", "zbvzerobubble")
+            if getattr(self, "ep_size", 1) > 1 and (zbv or vpp > 1 or sched_name.lower() in ("interleaved1f1b", "interleavedzerobubble")):
+                raise NotImplementedError("expert parallelism inside pipeline stages runs the one-chunk schedules (1F1B, GPipe, ZBH1)")
             if zbv or vpp > 1 or sched_name.lower() in ("interleaved1f1b", "interleavedzerobubble"):
                 # virtual stages: several model chunks per rank, interleaved 1F1B on the timetable runner; ZBV places
                 # its two chunks in a V (first and last stage on rank 0) and orders the operations greedily
@@ -440,7 +463,7 @@ class B200TrainEngine(TrainEngine):
             if not model_config.is_moe:
                 raise ValueError("expert parallelism needs a mixture-of-experts model")
             fused_ep = (self.device.type == "cuda" and (cfg.archon.fuse_ep_dispatch or cfg.megatron.moe_enable_deepep)
-                        and os.environ.get("AREAL_EP_FUSED", "1") != "0" and tp == 1)
+                        and os.environ.get("AREAL_EP_FUSED", "1") != "0" and tp == 1 and getattr(self, "pp_size", 1) == 1)
             self._expert_param_names = shard_experts(self.model, self.ep_rank, self.ep_size, self._ep_group, fused=fused_ep,
                                                      device=self.device)
         self.model.gradient_checkpointing = cfg.gradient_checkpointing
@@ -1136,6 +1159,9 @@ class B200TrainEngine(TrainEngine):
             # sliced) lives in exactly one rank's shard
             rep = sum((d32[a:b].pow(2).sum() for a, b in self._replicated_ranges), torch.zeros((), device=self.device))
             dense_sq = dense_sq - rep + rep / tp
+        elif getattr(self, "pp_size", 1) > 1:
+            # the last stage's copy of a tied embedding is left out
+            dense_sq = dense_sq - sum((d32[a:b].pow(2).sum() for a, b in self._replicated_ranges), torch.zeros((), device=self.device))
         pre = (dense_sq + g_exp.float().pow(2).sum()).reshape(1)
         if self._all_train_group is not None:
             dist.all_reduce(pre, group=self._all_train_group)     # every shard of either kind lives on exactly one rank
@@ -1230,10 +1256,10 @@ class B200TrainEngine(TrainEngine):
         if meta.weight_format == "hf" and getattr(self, "pp_size", 1) > 1:
             # the stages of the first pipeline write their own tensors; the head merges the index
             maps = [None] * self.pp_size
-            if self.dp_rank == 0:
+            if self.dp_rank == 0 or (getattr(self, "ep_size", 1) > 1 and self._export_member):
                 named = list(self._pp_native_full())
                 mine = {}
-                if getattr(self, "tp_rank", 0) == 0:          # one writer per stage
+                if getattr(self, "tp_rank", 0) == 0 and self.dp_rank == 0:          # one writer per stage
                     mine = hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named),
                                                  rank_tag=f"pp{self.pp_rank}", write_index=False)
                 dist.all_gather_object(maps, mine, group=self._pp_cpu_group)
@@ -1327,8 +1353,13 @@ class B200TrainEngine(TrainEngine):
         from ..parallel import tp as TP
 
         tp = getattr(self, "tp_size", 1)
+        expert = {self.model.native_name(n) for n in self._expert_param_names}
         for n_, p_ in self.model.named_native_parameters(skip_tied_copy=skip_tied_copy):
             t = p_.detach()
+            if n_ in expert:                      # expert stacks: gathered over the stage's EP group
+                parts = [torch.empty_like(t) for _ in range(self.ep_size)]
+                dist.all_gather(parts, t.contiguous(), group=self._ep_group)
+                t = torch.cat(parts, dim=0)
             if tp > 1:
                 parts = [torch.empty_like(t) for _ in range(tp)]
                 dist.all_gather(parts, t.contiguous(), group=self._tp_group)
@@ -1350,7 +1381,19 @@ class B200TrainEngine(TrainEngine):
             plan = hf_io.hf_to_native_plan(self.model_config)
             wanted = {hf for n in mine for hf, _, _ in plan[n]}
             tp_ = getattr(self, "tp_size", 1)
-            if tp_ > 1:
+            ep_ = getattr(self, "ep_size", 1)
+            if ep_ > 1:
+                # full expert stacks staged per stage, this rank's experts kept
+                expert = {self.model.native_name(n) for n in self._expert_param_names}
+                shapes = {n: tuple(p.shape) for n, p in build_model(self.model_config, dtype=self.model.dtype, device="meta").named_parameters()}
+                stage = {n: (torch.empty(shapes[n], dtype=p.dtype, device=p.device) if n in expert else p.data) for n, p in mine.items()}
+                hf_io.load_hf_tensors_into(self.model_config, stage, ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
+                El = self.model_config.num_experts // ep_
+                with torch.no_grad():
+                    for n in expert:
+                        mine[n].copy_(stage[n][self.ep_rank * El:(self.ep_rank + 1) * El])
+                del stage
+            elif tp_ > 1:
                 # full-size staging tensors for this stage's names, sliced into the local parameters afterwards
                 from ..parallel import tp as TP
 
@@ -1478,7 +1521,7 @@ class B200TrainEngine(TrainEngine):
                 unmerge_lora_(self.model)
         if getattr(self, "_z3", None) is not None:
             return dict(self._z3.full_tensors(to_cpu=True))
-        if getattr(self, "ep_size", 1) > 1:
+        if getattr(self, "ep_size", 1) > 1 and getattr(self, "pp_size", 1) == 1:
             return dict(self._ep_full_named_tensors(to_cpu=True))
         if getattr(self, "tp_size", 1) > 1 and getattr(self, "pp_size", 1) == 1:
             return {n: t.to("cpu", copy=True) for n, t in self._gathered_full_tensors()}

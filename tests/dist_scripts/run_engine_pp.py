@@ -52,7 +52,10 @@ def check(mc, tag, vpp=1, schedule="1F1B", loss_rank=1, backend="native:d2p2"):
     eng = B200TrainEngine(cfg_of(backend, vpp, schedule))
     eng.create_process_group()
     eng.initialize(model_config=mc, seed=5)
-    if backend == "native:d2p2":
+    if backend == "native:d2p2e2":
+        assert (eng.dp_size, eng.pp_size, eng.ep_size) == (2, 2, 2) and eng.pp_rank == rank // 2 and eng.ep_rank == rank % 2 and eng.expert_store is not None
+        assert eng.model.layers[0].mlp.w_gate_up.shape[0] == mc.num_experts // 2
+    elif backend == "native:d2p2":
         assert (eng.dp_size, eng.pp_size) == (2, 2) and eng.pp_rank == rank // 2 and eng.dp_rank == rank % 2
         assert eng.is_data_parallel_head() == (rank < 2) and eng.current_data_parallel_head() == rank % 2
     else:       # d{1,2}p2t2: index = (stage * dp + d) * tp + t
@@ -76,8 +79,13 @@ def check(mc, tag, vpp=1, schedule="1F1B", loss_rank=1, backend="native:d2p2"):
     worst = 0.0
     from areal_b200.parallel import tp as TP
 
+    experts = {eng.model.native_name(n) for n in getattr(eng, "_expert_param_names", [])}
     for n, p in eng.model.named_native_parameters(skip_tied_copy=False):
-        diff = (p.detach() - TP.shard_tensor(mc, n, full[n], getattr(eng, "tp_size", 1), getattr(eng, "tp_rank", 0))).abs()
+        want = TP.shard_tensor(mc, n, full[n], getattr(eng, "tp_size", 1), getattr(eng, "tp_rank", 0))
+        if n in experts:
+            El = mc.num_experts // eng.ep_size
+            want = want[eng.ep_rank * El:(eng.ep_rank + 1) * El]
+        diff = (p.detach() - want).abs()
         worst = max(worst, diff.max().item())
         assert diff.mean().item() < 2e-5 and diff.max().item() < 5e-3, f"{tag}: weights diverged for {n}: max {diff.max().item()}"
     # forward-only outputs reach every stage and match the unsplit engine
@@ -128,6 +136,9 @@ def main():
     check(preset("tiny-qwen3.5"), "hybrid")
     check(preset("tiny-qwen3.5-moe"), "hybrid-moe", schedule="ZBH1")     # split backward with per-expert weight views
     check(preset("tiny-qwen3-moe"), "moe-zbh1", schedule="ZBH1")
+    # expert parallelism inside the stages: each stage's experts spread over its two data-parallel ranks
+    check(preset("tiny-qwen3-moe"), "pp-ep", backend="native:d2p2e2")
+    check(preset("tiny-qwen3-moe"), "pp-ep-zbh1", schedule="ZBH1", backend="native:d2p2e2")
     # tensor parallelism inside the stages: 2 stages x 2 slices
     check(preset("tiny-qwen3"), "pp-tp", backend="native:d1p2t2")
     check(preset("tiny-qwen3", tie_word_embeddings=True), "pp-tp-tied-zbh1", schedule="ZBH1", backend="native:d1p2t2")
