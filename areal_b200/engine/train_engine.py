@@ -370,8 +370,8 @@ class B200TrainEngine(TrainEngine):
         seed = kwargs.get("seed", 1)
         t0 = time.time()
         tp = getattr(self, "tp_size", 1)
-        if getattr(model_config, "is_hybrid", False) and tp > 1:
-            raise NotImplementedError("linear-attention (hybrid) models train with data, pipeline and Ulysses sequence parallelism: no tensor split yet")
+        if getattr(model_config, "is_hybrid", False) and tp > 1 and (getattr(self, "sp_size", 1) > 1 or bool(cfg.fsdp.tp_sequence_parallel)):
+            raise NotImplementedError("linear-attention (hybrid) models: tensor parallelism does not combine with sequence parallelism")
         if getattr(model_config, "is_hybrid", False) and getattr(cfg.fsdp, "context_parallel", "ulysses") != "ulysses" and getattr(self, "sp_size", 1) > 1:
             raise NotImplementedError("hybrid models split sequences by heads (Ulysses); the delta rule needs whole sequences")
         has_ckpt = (not cfg.init_from_scratch and cfg.path and os.path.isdir(cfg.path)

@@ -370,6 +370,15 @@ class HybridDecoderLayer(nn.Module):
     def forward(self, h, resid, pb, cos, sin, attn_fn=None):
         eps = self.cfg.rms_norm_eps
         x, resid = rmsnorm_offset(h, self.input_layernorm, eps, resid)
+        g = self.tp_group
+        if g is not None:
+            # tensor parallel: this rank holds a slice of the heads (of either mixer) and of the MLP columns
+            from ..parallel.tp import copy_to_tp, reduce_from_tp
+
+            x = copy_to_tp(x, g)
+            h = reduce_from_tp(self.linear_attn(x, pb) if self.is_linear else self.self_attn(x, pb, cos, sin, attn_fn), g)
+            x, resid = rmsnorm_offset(h, self.post_attention_layernorm, eps, resid)
+            return reduce_from_tp(self.mlp(copy_to_tp(x, g)), g), resid
         h = self.linear_attn(x, pb) if self.is_linear else self.self_attn(x, pb, cos, sin, attn_fn)
         x, resid = rmsnorm_offset(h, self.post_attention_layernorm, eps, resid)
         return self.mlp(x), resid

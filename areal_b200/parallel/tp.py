@@ -41,7 +41,49 @@ def local_config(cfg: ModelConfig, tp: int, expert_tp: bool = True) -> ModelConf
     kw = dict(num_heads=cfg.num_heads // tp, num_kv_heads=cfg.num_kv_heads // tp, intermediate_size=cfg.intermediate_size // tp)
     if cfg.num_experts and expert_tp:
         kw["moe_intermediate_size"] = cfg.moe_intermediate_size // tp
+    if getattr(cfg, "layer_types", None):
+        # linear-attention layers split by heads as well (key heads and value heads keep their grouping)
+        nk, nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        if nk % tp or nv % tp:
+            raise ValueError(f"linear-attention heads ({nk} key, {nv} value) are not divisible by tp={tp}")
+        kw.update(linear_num_key_heads=nk // tp, linear_num_value_heads=nv // tp)
     return dataclasses.replace(cfg, **kw)
+
+
+def _block_rows(full: torch.Tensor, sizes: list[int], tp: int, rank: int) -> torch.Tensor:
+    """``full`` is a stack of row blocks of ``sizes`` rows (q | k | v ...): rank ``rank``'s ``1 / tp`` of every block."""
+    out, off = [], 0
+    for n in sizes:
+        out.append(full[off + rank * n // tp: off + (rank + 1) * n // tp])
+        off += n
+    return torch.cat(out, dim=0).contiguous()
+
+
+def _unblock_rows(parts: list[torch.Tensor], sizes: list[int]) -> torch.Tensor:
+    tp = len(parts)
+    out = []
+    off = 0
+    for n in sizes:
+        out += [p[off:off + n // tp] for p in parts]
+        off += n // tp
+    return torch.cat(out, dim=0)
+
+
+def _hybrid_blocks(cfg: ModelConfig, name: str) -> Optional[list[int]]:
+    """Row-block sizes (in the FULL model) of the head-sliced parameters of the hybrid (linear / gated attention)
+    layers, ``None`` for every other parameter."""
+    leaf = name.rsplit(".", 1)[-1]
+    if ".linear_attn." in name:
+        kd = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+        vd = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+        nv = cfg.linear_num_value_heads
+        return {"in_proj_qkv": [kd, kd, vd], "conv1d": [kd, kd, vd], "in_proj_z": [vd], "in_proj_ba": [nv, nv], "dt_bias": [nv],
+                "A_log": [nv]}.get(leaf)
+    if leaf == "q_proj" and ".self_attn." in name:
+        return [cfg.num_heads * 2 * cfg.head_dim]
+    if leaf == "kv_proj" and ".self_attn." in name:
+        return [cfg.num_kv_heads * cfg.head_dim] * 2
+    return None
 
 
 def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank: int, expert_tp: bool = True) -> torch.Tensor:
@@ -51,6 +93,13 @@ def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank:
     leaf = name.rsplit(".", 1)[-1]
     if leaf in ("embed_tokens", "lm_head") or name.startswith("visual."):       # replicated here (vocab parallelism is separate)
         return full
+    if getattr(cfg, "layer_types", None):
+        blocks = _hybrid_blocks(cfg, name)
+        if blocks is not None:
+            return _block_rows(full, blocks, tp, rank)
+        if leaf == "out_proj" and ".linear_attn." in name:
+            C = full.shape[1]
+            return full[:, rank * C // tp:(rank + 1) * C // tp].contiguous()
     if full.dim() == 3:                             # stacked experts [E, rows, cols]
         if not expert_tp:
             return full
@@ -78,6 +127,12 @@ def unshard_tensors(cfg: ModelConfig, name: str, parts: list[torch.Tensor], expe
     p0 = parts[0]
     if (p0.dim() == 3 and not expert_tp) or name.startswith("visual."):
         return p0
+    if getattr(cfg, "layer_types", None):
+        blocks = _hybrid_blocks(cfg, name)
+        if blocks is not None:
+            return _unblock_rows(parts, blocks)
+        if leaf == "out_proj" and ".linear_attn." in name:
+            return torch.cat(parts, dim=1)
     if leaf in ("embed_tokens", "lm_head") or (p0.dim() == 1 and leaf != "qkv_bias") or leaf in ("router",):
         return p0
     if p0.dim() == 3:
@@ -212,7 +267,7 @@ def replicated_parameter_names(model) -> list[str]:
     out = []
     for n, p in model.named_parameters():
         leaf = n.rsplit(".", 1)[-1]
-        if p.dim() == 1 and leaf != "qkv_bias" or leaf in ("embed_tokens", "lm_head", "router", "value_head") or n.startswith("visual."):
+        if p.dim() == 1 and leaf not in ("qkv_bias", "dt_bias", "A_log") or leaf in ("embed_tokens", "lm_head", "router", "value_head") or n.startswith("visual."):
             out.append(n)            # (the image tower of a vision-language model is not sliced: every rank runs all of it)
     return out
 
@@ -232,7 +287,7 @@ def allreduce_replicated_grads(model, group, grad_of=lambda p: getattr(p, "main_
     all_partial = getattr(model, "tp_sequence_parallel", False)
     for n in replicated_parameter_names(model):
         leaf = n.rsplit(".", 1)[-1]
-        if all_partial or leaf in ("q_norm", "k_norm", "router"):
+        if all_partial or leaf in ("q_norm", "k_norm", "router") or n.endswith("linear_attn.norm"):     # (per-head norms saw the local heads only)
             g = grad_of(params[n])
             if g is not None:
                 dist.all_reduce(g, group=group)

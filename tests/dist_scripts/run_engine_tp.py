@@ -53,7 +53,7 @@ def _cfg_of(backend):
 def main():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    mc = preset("tiny-qwen3")
+    mc = preset(os.environ.get("AREAL_TEST_MODEL", "tiny-qwen3"))
     eng = B200TrainEngine(cfg_of("d2t2"))
     eng.create_process_group()
     eng.initialize(model_config=mc, seed=5)

@@ -43,11 +43,12 @@ def test_tensor_parallel_matches_unsharded_model_gloo():
     assert r.stdout.count("TP_OK") == 2
 
 
-@pytest.mark.parametrize("seq_par", ["0", "1"])
-def test_train_engine_dp2_tp2_matches_single_rank(tmp_path, seq_par):
+@pytest.mark.parametrize("seq_par,model", [("0", "tiny-qwen3"), ("1", "tiny-qwen3"), ("0", "tiny-qwen3.5")])
+def test_train_engine_dp2_tp2_matches_single_rank(tmp_path, seq_par, model):
     """``seq_par`` = 1: the residual stream is split by rows over the tensor-parallel group as well (gather -> product,
-    product -> reduce-scatter around attention and MLP; norms and LM head on local rows; outputs gathered for the loss)."""
-    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", TP_SAVE_DIR=str(tmp_path / "hf"), AREAL_TEST_TP_SP=seq_par)
+    product -> reduce-scatter around attention and MLP; norms and LM head on local rows; outputs gathered for the loss).
+    ``tiny-qwen3.5``: linear-attention (gated delta rule) and gated full-attention layers sliced by heads."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", TP_SAVE_DIR=str(tmp_path / "hf"), AREAL_TEST_TP_SP=seq_par, AREAL_TEST_MODEL=model)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
                         "--master-port", "29873", os.path.join(ROOT, "tests", "dist_scripts", "run_engine_tp.py")], cwd=ROOT, env=env,
                        capture_output=True, text=True, timeout=400)
