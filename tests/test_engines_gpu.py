@@ -436,6 +436,42 @@ def test_offloaded_and_bf16_state_optimizers_follow_the_default_on_gpu():
     assert oplib.kernel_error() == 0
 
 
+def test_sharded_parameters_follow_the_replicated_store_on_gpu():
+    """``fsdp.shard_parameters`` on the GPU kernels (one rank: the unit protocol alone): layers live in transient
+    buffers between enter and leave, weight gradients accumulate into per-unit fp32 buffers opened in the backward;
+    three PPO steps move the weights like the replicated store does."""
+    data = _batch()
+    outs = {}
+    for name in ("replicated", "sharded"):
+        cfg = PPOActorConfig(init_from_scratch=True, dtype="bfloat16", optimizer=OptimizerConfig(lr=1e-4),
+                             mb_spec=MicroBatchSpec(max_tokens_per_mb=1024), use_decoupled_loss=True, recompute_logprob=True,
+                             kl_ctl=0.0, ppo_n_minibatches=1)
+        cfg.fsdp.shard_parameters = name == "sharded"
+        eng = B200PPOActor(cfg)
+        eng.create_process_group()
+        eng.initialize(model_config=preset("tiny-qwen3"), seed=1)
+        init = {n: t.double() for n, t in eng.export_weights().items()}
+        d = dict(data)
+        d["prox_logp"] = eng.compute_logp(d)
+        eng.compute_advantages(d)
+        norms = []
+        for _ in range(3):
+            st = eng.ppo_update(dict(d))
+            assert st[0]["update_successful"] == 1.0
+            norms.append(st[0]["grad_norm"])
+        after = eng.export_weights()
+        outs[name] = (torch.cat([(after[n].double() - init[n]).reshape(-1) for n in sorted(init)]), norms)
+        if name == "sharded":
+            st_ = eng.store
+            assert st_.flat_param is None and not st_._live and not st_._gbuf and all(p.data.stride() == (0,) * p.dim() for p in eng.model.parameters())
+        eng.destroy()
+    (ur, nr), (us, ns) = outs["replicated"], outs["sharded"]
+    cos = float((ur * us).sum() / (ur.norm() * us.norm()).clamp(min=1e-30))
+    assert float(ur.norm()) > 0 and cos > 0.98 and abs(float(us.norm() / ur.norm()) - 1.0) < 0.05, (cos, float(us.norm()), float(ur.norm()))
+    assert all(abs(a - b) <= 0.05 * abs(b) + 0.05 for a, b in zip(ns, nr)), (ns, nr)
+    assert oplib.kernel_error() == 0
+
+
 def test_colocated_loop_runs_sixty_steps_on_gpu(tmp_path):
     """Trainer and rollout engine sharing one GPU (shared weights, CUDA graphs, prefix sharing, pages
     on demand in a small pool) for 60 steps: the configuration whose long runs used to die."""
