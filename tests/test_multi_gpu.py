@@ -116,3 +116,13 @@ def test_vocab_parallel_head_partials_over_peer_memory_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_vocab_parallel.py"), 2, 29795, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("VP_OK") == 2 and r.stdout.count("VP_PEER_OK") == 2
+
+
+def test_engine_layouts_sharded_hybrid_tp_vlm_tp_two_gpus():
+    """Sharded parameters (ZeRO-3 on NCCL broadcasts / reductions), a tensor-parallel linear-attention model and a
+    vision-language model with a tensor-parallel language model on 2 GPUs in bf16: gradient norms and the three-step
+    update follow a single-rank engine with replicated parameters."""
+    _need(2)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_layouts_gpu.py"), 2, 29797, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0
+    assert r.stdout.count("ENGINE_LAYOUTS_GPU_OK") == 2
