@@ -3,7 +3,11 @@ engine (replicated parameters) on the same batch:
 
 * ``sharded``   ``d2`` with ``fsdp.shard_parameters`` (ZeRO-3: asynchronous broadcasts / reductions on NCCL),
 * ``hybrid-tp`` ``native:d1t2`` of a linear-attention (gated delta rule) model, heads of both mixers sliced,
-* ``vlm-tp``    ``native:d1t2`` of a vision-language model, language model sliced, image tower whole.
+* ``vlm-tp``    ``native:d1t2`` of a vision-language model, language model sliced, image tower whole;
+
+and with 4 ranks (``LAYOUTS=ep-tp,ep-etp,pp-tp,pp-ep``): whole experts over data x tensor ranks (``native:d2t2e2``), experts
+sliced over the tensor-parallel group (``native:(attn:d2t2|ffn:e2t2)``), tensor parallelism inside pipeline stages
+(``native:d1p2t2``), expert parallelism inside pipeline stages (``native:d2p2e2``).
 
 Prints ``LAYOUT_OK <name>`` per rank and layout, then ENGINE_LAYOUTS_GPU_OK."""
 import faulthandler
@@ -100,6 +104,15 @@ def main():
 
         batch = _vlm_batch(mc, mc.vision_config())
         compare("vlm-tp", run(mc, batch, f"native:d1t{world}", on_gpu, rank), run(mc, batch, "d1", on_gpu, rank, alone=True), on_gpu, rank)
+    four = {"ep-tp": ("tiny-qwen3-moe", "native:d2t2e2"), "ep-etp": ("tiny-qwen3-moe", "native:(attn:d2t2|ffn:e2t2)"),
+            "pp-tp": ("tiny-qwen3", "native:d1p2t2"), "pp-ep": ("tiny-qwen3-moe", "native:d2p2e2")}
+    for name, (model, backend) in four.items():
+        if name in only:
+            assert world == 4, "these layouts are written for 4 ranks"
+            mc = preset(model)
+            batch = make_batch(mc.vocab_size)
+            share = lambda eng: {k: v[eng.dp_rank * (8 // eng.dp_size):(eng.dp_rank + 1) * (8 // eng.dp_size)] for k, v in batch.items()}   # noqa: E731
+            compare(name, run(mc, batch, backend, on_gpu, rank, mine=share), run(mc, batch, "d1", on_gpu, rank, alone=True), on_gpu, rank)
     print("ENGINE_LAYOUTS_GPU_OK", flush=True)
     dist.barrier()
     dist.destroy_process_group()
