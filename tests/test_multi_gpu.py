@@ -126,3 +126,14 @@ def test_engine_layouts_sharded_hybrid_tp_vlm_tp_two_gpus():
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_layouts_gpu.py"), 2, 29797, timeout=300, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0
     assert r.stdout.count("ENGINE_LAYOUTS_GPU_OK") == 2
+
+
+def test_engine_layouts_expert_tensor_pipeline_four_gpus():
+    """Whole and sliced experts under tensor-parallel attention (``native:d2t2e2``, ``native:(attn:d2t2|ffn:e2t2)``) and
+    tensor / expert parallelism inside pipeline stages (``native:d1p2t2``, ``native:d2p2e2``) on 4 GPUs in bf16: gradient
+    norms and the three-step update follow a single-rank engine."""
+    _need(4)
+    r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_layouts_gpu.py"), 4, 29799, timeout=300,
+                  env={"NCCL_NVLS_ENABLE": "0", "LAYOUTS": "ep-tp,ep-etp,pp-tp,pp-ep"})
+    assert r.returncode == 0
+    assert r.stdout.count("ENGINE_LAYOUTS_GPU_OK") == 4
