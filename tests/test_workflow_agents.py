@@ -1,0 +1,91 @@
+"""Ready-made agents (``areal_b200.workflow``): in-process through the adapter, and with the ecosystems' own SDKs
+(openai, anthropic, agents) over the HTTP proxy; every model call is recorded and the reward lands on the trajectory."""
+import asyncio
+import os
+
+import pytest
+
+from areal_b200.api.cli_args import GenerationHyperparameters
+from areal_b200.openai.proxy import OpenAIProxyServer
+from areal_b200.rollout.workflows.agent import AgentRolloutAdapter
+from areal_b200.workflow import AnthropicMathAgent, LangChainMathAgent, MathAgent, MultiTurnMathAgent, OpenAIAgentsMathAgent, math_reward
+from tests.test_openai_and_agents import ByteTok, ScriptedEngine
+
+G = GenerationHyperparameters(max_new_tokens=256)
+DATA = {"messages": [{"role": "user", "content": "What is 6 * 7?"}], "answer": "42"}
+
+
+def test_math_reward_reads_boxed_and_plain_answers():
+    assert math_reward("so the answer is \\boxed{42}", "42") == 1.0
+    assert math_reward("I think 41", "42") == 0.0 and math_reward("", "42") == 0.0 and math_reward(None, "42") == 0.0
+
+
+def test_one_shot_and_multi_turn_agents_in_process():
+    eng = ScriptedEngine(["The answer is \\boxed{42}"])
+    traj = asyncio.run(AgentRolloutAdapter(MathAgent(max_new_tokens=32, temperature=0.5), tokenizer=ByteTok(), gconfig=G).arun_episode(eng, DATA))
+    assert float(traj["rewards"][0]) == 1.0 and eng.requests[0].gconfig.max_new_tokens == 32
+    # wrong, wrong, right: three calls, the feedback joins the conversation, the last attempt's reward counts
+    eng = ScriptedEngine(["\\boxed{40}", "\\boxed{41}", "\\boxed{42}"])
+    ad = AgentRolloutAdapter(MultiTurnMathAgent(max_turns=5, max_new_tokens=32), tokenizer=ByteTok(), gconfig=G, turn_discount=0.5)
+    traj = asyncio.run(ad.arun_episode(eng, DATA))
+    assert len(eng.requests) == 3 and traj["rewards"].tolist() == [0.25, 0.5, 1.0]
+    assert b"carefully read the original question" in bytes(eng.requests[2].input_ids)
+    eng = ScriptedEngine(["\\boxed{1}"])                      # never right: stops at max_turns with reward 0
+    traj = asyncio.run(AgentRolloutAdapter(MultiTurnMathAgent(max_turns=2), tokenizer=ByteTok(), gconfig=G).arun_episode(eng, DATA))
+    assert len(eng.requests) == 2 and float(traj["rewards"].sum()) == 0.0
+
+
+def test_anthropic_agent_in_process():
+    eng = ScriptedEngine(["\\boxed{42}"])
+    traj = asyncio.run(AgentRolloutAdapter(AnthropicMathAgent(max_tokens=16, system="Be brief."), tokenizer=ByteTok(), gconfig=G).arun_episode(eng, DATA))
+    assert float(traj["rewards"][0]) == 1.0 and b"Be brief." in bytes(eng.requests[0].input_ids)
+
+
+def _with_proxy(eng, fn):
+    px = OpenAIProxyServer(eng, ByteTok(), G, admin_key="adm").start()
+    try:
+        return fn(px)
+    finally:
+        px.stop()
+
+
+def test_openai_and_anthropic_sdks_over_the_http_proxy(monkeypatch):
+    pytest.importorskip("openai")
+    pytest.importorskip("anthropic")
+    monkeypatch.setenv("AREAL_AGENT_HTTP", "1")
+    eng = ScriptedEngine(["\\boxed{41}", "\\boxed{42}", "\\boxed{42}"])
+
+    def go(px):
+        ad = AgentRolloutAdapter(MultiTurnMathAgent(max_turns=4, max_new_tokens=32), tokenizer=ByteTok(), gconfig=G, proxy=px)
+        t1 = asyncio.run(ad.arun_episode(eng, DATA))
+        ad2 = AgentRolloutAdapter(AnthropicMathAgent(max_tokens=16), tokenizer=ByteTok(), gconfig=G, proxy=px)
+        t2 = asyncio.run(ad2.arun_episode(eng, DATA))
+        return t1, t2
+    t1, t2 = _with_proxy(eng, go)
+    assert len(eng.requests) == 3 and t1["rewards"].tolist() == [1.0, 1.0] and t2["rewards"].tolist() == [1.0]
+
+
+def test_openai_agents_sdk_drives_a_tool_loop_over_the_proxy():
+    pytest.importorskip("agents")
+    call = '<tool_call>\n{"name": "multiply", "arguments": {"a": 6, "b": 7}}\n</tool_call>'
+    eng = ScriptedEngine([call, "The product is \\boxed{42}"])
+
+    def go(px):
+        ad = AgentRolloutAdapter(OpenAIAgentsMathAgent(max_turns=4, max_new_tokens=256), tokenizer=ByteTok(), gconfig=G, proxy=px)
+        return asyncio.run(ad.arun_episode(eng, DATA))
+    traj = _with_proxy(eng, go)
+    assert len(eng.requests) == 2 and float(traj["rewards"][-1]) == 1.0
+    assert b"42" in bytes(eng.requests[1].input_ids)                   # the tool's result went back to the model
+    with pytest.raises(ValueError, match="proxy mode"):
+        os.environ.pop("OPENAI_BASE_URL", None)
+        asyncio.run(OpenAIAgentsMathAgent().run(DATA))
+
+
+def test_langchain_agent_names_its_missing_package():
+    try:
+        import langchain_openai  # noqa: F401
+        pytest.skip("langchain-openai is installed")
+    except ImportError:
+        pass
+    with pytest.raises(ImportError, match="langchain-openai"):
+        asyncio.run(LangChainMathAgent().run(DATA, base_url="http://127.0.0.1:1/v1", api_key="k"))
