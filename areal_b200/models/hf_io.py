@@ -176,16 +176,65 @@ def load_hf_tensors_into(cfg: ModelConfig, params: Optional[dict[str, torch.Tens
 
 
 # --------------------------------------------------------------------------- safetensors IO
-def iter_safetensors(path: str, device: str = "cpu") -> Iterator[tuple[str, torch.Tensor]]:
+def dequant_block_fp8(w8: torch.Tensor, scale_inv: torch.Tensor, block: tuple[int, int] = (128, 128), dtype=torch.bfloat16) -> torch.Tensor:
+    """``w[i, j] = fp8[i, j] * scale_inv[i // bm, j // bn]`` (block-quantised checkpoints keep one fp32 multiplier per
+    ``bm x bn`` block under ``<name>_scale_inv``). Stacked tensors ``[E, R, C]`` carry scales ``[E, R / bm, C / bn]``."""
+    bm, bn = block
+    R, C = w8.shape[-2:]
+    if tuple(scale_inv.shape[-2:]) != (-(-R // bm), -(-C // bn)):
+        raise ValueError(f"scale grid {tuple(scale_inv.shape)} does not fit a {R} x {C} tensor in {bm} x {bn} blocks")
+    s = scale_inv.float().repeat_interleave(bm, dim=-2)[..., :R, :].repeat_interleave(bn, dim=-1)[..., :C]
+    return (w8.float() * s).to(dtype)
+
+
+def _fp8_block_of(path: str) -> Optional[tuple[int, int]]:
+    """Block shape from ``config.json`` (``quantization_config.weight_block_size``) when the checkpoint is fp8."""
+    cj = os.path.join(path, "config.json")
+    if not os.path.exists(cj):
+        return None
+    with open(cj) as f:
+        q = (json.load(f).get("quantization_config") or {})
+    if str(q.get("quant_method", "")).lower() != "fp8" and "weight_block_size" not in q:
+        return None
+    b = q.get("weight_block_size") or [128, 128]
+    return int(b[0]), int(b[1])
+
+
+def iter_safetensors(path: str, device: str = "cpu", dequant_fp8: bool = True) -> Iterator[tuple[str, torch.Tensor]]:
+    """(name, tensor) of every tensor under ``path``. Block-quantised fp8 weights (a ``float8_e4m3fn`` tensor with a
+    ``<name>_scale_inv`` companion, as written for DeepSeek-V3 / Qwen3-FP8 style checkpoints) come out dequantised to
+    bf16 and their scale tensors are not listed: the loaders above see an ordinary checkpoint. Reference:
+    ``areal/experimental/models/archon/fp8_checkpoint.py:36-330`` (dequantise on load)."""
     from safetensors import safe_open
 
     files = sorted(f for f in os.listdir(path) if f.endswith(".safetensors"))
     if not files:
         raise FileNotFoundError(f"no .safetensors files under {path}")
+    block = _fp8_block_of(path) if dequant_fp8 else None
+    where: dict[str, str] = {}
+    ij = os.path.join(path, "model.safetensors.index.json")
+    if dequant_fp8 and os.path.exists(ij):
+        with open(ij) as f:
+            where = json.load(f).get("weight_map", {})
+    fp8 = getattr(torch, "float8_e4m3fn", None)
     for fn in files:
         with safe_open(os.path.join(path, fn), framework="pt", device=device) as f:
-            for k in f.keys():
-                yield k, f.get_tensor(k)
+            keys = list(f.keys())
+            for k in keys:
+                if dequant_fp8 and k.endswith("_scale_inv"):
+                    continue
+                t = f.get_tensor(k)
+                if dequant_fp8 and fp8 is not None and t.dtype == fp8:
+                    sk = k + "_scale_inv"
+                    if sk in keys:
+                        sc = f.get_tensor(sk)
+                    elif sk in where:                  # the scale lives in another shard
+                        with safe_open(os.path.join(path, where[sk]), framework="pt", device=device) as g:
+                            sc = g.get_tensor(sk)
+                    else:
+                        raise KeyError(f"fp8 tensor '{k}' has no '{sk}' in the checkpoint")
+                    t = dequant_block_fp8(t, sc, block or (128, 128))
+                yield k, t
 
 
 def save_hf_sharded(path: str, cfg: ModelConfig, hf_named: Iterable[tuple[str, torch.Tensor]],

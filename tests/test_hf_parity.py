@@ -87,3 +87,70 @@ def test_logits_match_hf(family):
         theirs = torch.cat([hf(input_ids=s[None]).logits[0] for s in seqs])
     assert ours.shape == theirs.shape
     assert (ours - theirs).abs().max().item() < 2e-4, (ours - theirs).abs().max().item()
+
+
+def test_block_quantised_fp8_checkpoint_is_dequantised_on_load(tmp_path):
+    """A checkpoint whose projection weights are ``float8_e4m3fn`` with one fp32 multiplier per 128 x 128 block
+    (``<name>_scale_inv``, ``quantization_config`` in ``config.json``) loads like an ordinary one: weights come out within
+    fp8 rounding of the originals, scale tensors are not reported as unexpected, a scale kept in another shard is found
+    through the index."""
+    import json
+
+    import torch
+    from safetensors.torch import save_file
+
+    from areal_b200.models import hf_io
+    from areal_b200.models.config import preset
+    from areal_b200.models.decoder import build_model
+
+    cfg = preset("tiny-qwen3")
+    src = build_model(cfg, dtype=torch.bfloat16, device="cpu", seed=4)
+    named = dict(hf_io.native_to_hf_tensors(cfg, [(n, p.detach()) for n, p in src.named_parameters()]))
+
+    def quant(w, bm=128, bn=128):
+        R, C = w.shape
+        gr, gc = -(-R // bm), -(-C // bn)
+        pad = torch.zeros(gr * bm, gc * bn)
+        pad[:R, :C] = w.float()
+        amax = pad.view(gr, bm, gc, bn).abs().amax(dim=(1, 3)).clamp(min=1e-12)
+        scale = amax / 448.0
+        q = (pad.view(gr, bm, gc, bn) / scale[:, None, :, None]).view(gr * bm, gc * bn)[:R, :C].to(torch.float8_e4m3fn)
+        return q, scale
+
+    a, b = {}, {}
+    for k, t in named.items():
+        if k.endswith("proj.weight") and t.dim() == 2:
+            q, sc = quant(t)
+            a[k] = q
+            (b if "layers.1." in k else a)[k + "_scale_inv"] = sc            # layer 1's scales go to the other shard
+        else:
+            a[k] = t.contiguous()
+    save_file(a, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file(b, str(tmp_path / "model-00002-of-00002.safetensors"))
+    wm = {k: "model-00001-of-00002.safetensors" for k in a}
+    wm.update({k: "model-00002-of-00002.safetensors" for k in b})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": wm}))
+    cfg.save_pretrained(str(tmp_path))
+    cj = json.loads((tmp_path / "config.json").read_text())
+    cj["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128]}
+    (tmp_path / "config.json").write_text(json.dumps(cj))
+    dst = build_model(cfg, dtype=torch.bfloat16, device="cpu", seed=9)
+    hf_io.load_model_hf(dst, str(tmp_path))
+    n_q = 0
+    for (n, p), (_, q) in zip(src.named_parameters(), dst.named_parameters()):
+        if n.endswith("_proj"):
+            n_q += 1
+            rel = float((p.detach().float() - q.detach().float()).norm() / p.detach().float().norm())
+            assert 0 < rel < 0.05, (n, rel)                                   # e4m3 keeps 3 mantissa bits
+        else:
+            assert torch.equal(p, q), n
+    assert n_q >= 4 * cfg.num_layers
+    raw = dict(hf_io.iter_safetensors(str(tmp_path), dequant_fp8=False))
+    assert any(k.endswith("_scale_inv") for k in raw) and any(t.dtype == torch.float8_e4m3fn for t in raw.values())
+    w = torch.randn(200, 300)
+    q, sc = quant(w)
+    assert float((hf_io.dequant_block_fp8(q, sc).float() - w).norm() / w.norm()) < 0.05        # ragged last blocks
+    import pytest
+
+    with pytest.raises(ValueError, match="scale grid"):
+        hf_io.dequant_block_fp8(q, sc[:1])
