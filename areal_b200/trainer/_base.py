@@ -48,6 +48,12 @@ class SupervisedTrainer:
         self.evaluator = Evaluator(config.evaluator, self.ft_spec)
         self.recover_handler = RecoverHandler(config.recover, self.ft_spec)
         self.stats_logger = StatsLogger(config.stats_logger, self.ft_spec, rank=getattr(self.engine, "rank", 0))
+        if getattr(self.engine, "rank", 0) == 0 and config.stats_logger.fileroot:
+            from ..infra.utils.exp_metadata import save_experiment_metadata
+
+            # which source state produced this run, kept beside its logs
+            save_experiment_metadata(config.stats_logger.fileroot, config.stats_logger.experiment_name or "exp", config.stats_logger.trial_name or "trial",
+                                     {"allocation_mode": getattr(config, "allocation_mode", None)})
         self.start_step = 0
         info = self.recover_handler.load({self.role: self.engine}, self.saver, self.evaluator, self.stats_logger,
                                          self.train_dataloader)

@@ -81,6 +81,12 @@ class PPOTrainer:
         self.evaluator = Evaluator(config.evaluator, self.ft_spec)
         self.recover_handler = RecoverHandler(config.recover, self.ft_spec)
         self.stats_logger = StatsLogger(config.stats_logger, self.ft_spec, rank=getattr(self.actor, "rank", 0))
+        if getattr(self.actor, "rank", 0) == 0 and config.stats_logger.fileroot:
+            from ..infra.utils.exp_metadata import save_experiment_metadata
+
+            # which source state produced this run, kept beside its logs
+            save_experiment_metadata(config.stats_logger.fileroot, config.stats_logger.experiment_name or "exp", config.stats_logger.trial_name or "trial",
+                                     {"allocation_mode": getattr(config, "allocation_mode", None)})
         if config.perf_tracer is not None:
             perf_tracer.configure(config.perf_tracer, rank=getattr(self.actor, "rank", 0), role="trainer")
         from ..utils.memory_profiler import MemoryProfiler

@@ -90,3 +90,34 @@ class ValueScheduler:
         if self.kind == "cosine":
             return self.end + (self.init - self.end) * 0.5 * (1 + math.cos(math.pi * p))
         raise ValueError(f"unknown scheduler {self.kind}")
+
+
+class ChainedValueScheduler:
+    """Several schedules one after another: each runs for its own ``total`` steps from where the previous one ended in
+    time (values need not be continuous). Reference: ``areal/utils/timeutil.py`` (``ChainedScheduler``)."""
+
+    def __init__(self, schedulers: list[ValueScheduler]):
+        if not schedulers:
+            raise ValueError("a chained schedule needs at least one part")
+        self.parts = list(schedulers)
+
+    @property
+    def total_iters(self) -> int:
+        return sum(p.total for p in self.parts)
+
+    @property
+    def init_value(self) -> float:
+        return self.parts[0].init
+
+    @property
+    def final_value(self) -> float:
+        return self.parts[-1].get(self.parts[-1].total)
+
+    def get(self, step: int) -> float:
+        if step < 0:
+            raise ValueError("step must be non-negative")
+        for p in self.parts:
+            if step < p.total:
+                return p.get(step)
+            step -= p.total
+        return self.final_value

@@ -462,3 +462,29 @@ def test_bench_activation_policy_shrinks_the_micro_batch_before_it_recomputes():
     assert plan_activation_policy(150.0, 8192, 36, 4096, 4096) == (8192, 36)
     # no memory at all: floor and full recompute
     assert plan_activation_policy(10.0, 8192, 36, 4096, 4096) == (4096, 0)
+
+
+def test_version_info_experiment_metadata_and_chained_schedule(tmp_path):
+    import areal_b200
+    from areal_b200.infra.utils.exp_metadata import load_experiment_metadata, save_experiment_metadata
+    from areal_b200.utils.timeutil import ChainedValueScheduler, ValueScheduler
+
+    v = areal_b200.version_info
+    assert areal_b200.__version__ == v.version and v.full_version_with_dirty_description.startswith(v.version)
+    assert (v.commit == "unknown") == (v.full_version == v.version)
+    p = save_experiment_metadata(str(tmp_path), "exp", "t0", {"allocation_mode": "d4"})
+    m = load_experiment_metadata(str(tmp_path), "exp", "t0")
+    assert p.endswith("version.json") and m["commit_id"] == v.commit and m["allocation_mode"] == "d4" and m["trial_name"] == "t0"
+    assert load_experiment_metadata(str(tmp_path), "exp", "other") is None
+    # warm-up 0 -> 1 over 10 steps, then cosine 1 -> 0.1 over 90, then whatever the last part ends at
+    sch = ChainedValueScheduler([ValueScheduler("linear", 0.0, 10, 1.0), ValueScheduler("cosine", 1.0, 90, 0.1)])
+    assert sch.total_iters == 100 and sch.init_value == 0.0 and abs(sch.final_value - 0.1) < 1e-12
+    assert sch.get(0) == 0.0 and abs(sch.get(5) - 0.5) < 1e-12 and sch.get(10) == 1.0 and abs(sch.get(55) - 0.55) < 1e-9 and abs(sch.get(1000) - 0.1) < 1e-12
+    import pytest
+
+    with pytest.raises(ValueError):
+        ChainedValueScheduler([])
+    # the package's public names resolve lazily
+    assert areal_b200.StalenessManager.__name__ == "StalenessManager" and "PPOTrainer" in dir(areal_b200)
+    with pytest.raises(AttributeError):
+        areal_b200.no_such_name
