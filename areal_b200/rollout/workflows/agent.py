@@ -39,6 +39,10 @@ class AgentRolloutAdapter(RolloutWorkflow):
         if self.proxy is not None:
             session = self.proxy.start_session(client)
             extra.update(base_url=self.proxy.base_url, api_key=session)
+            try:
+                extra["http_client"] = wctx.get_httpx_client()      # one connection pool per event loop, not per episode
+            except ImportError:
+                pass
         try:
             params = inspect.signature(self.agent.run).parameters
             if not any(p.kind == inspect.Parameter.VAR_KEYWORD for p in params.values()):

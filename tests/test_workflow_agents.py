@@ -89,3 +89,23 @@ def test_langchain_agent_names_its_missing_package():
         pass
     with pytest.raises(ImportError, match="langchain-openai"):
         asyncio.run(LangChainMathAgent().run(DATA, base_url="http://127.0.0.1:1/v1", api_key="k"))
+
+
+def test_http_clients_are_shared_per_event_loop():
+    from areal_b200.rollout import workflow_context as wctx
+
+    async def two():
+        a, b = wctx.get_httpx_client(), wctx.get_httpx_client()
+        s, t = wctx.get_aiohttp_session(), wctx.get_aiohttp_session()
+        return a, b, s, t
+
+    a, b, s, t = asyncio.run(two())
+    assert a is b and s is t
+    a2, _, s2, _ = asyncio.run(two())                       # another loop: the old clients died with theirs
+    assert a2 is not a and s2 is not s and len(wctx._HTTP._httpx) == 1 and len(wctx._HTTP._aio) == 1
+
+    async def closing():
+        c, s_ = wctx.get_httpx_client(), wctx.get_aiohttp_session()
+        await wctx.close_http_clients()
+        return c.is_closed, s_.closed, wctx.get_httpx_client() is not c
+    assert asyncio.run(closing()) == (True, True, True)
