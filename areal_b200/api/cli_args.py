@@ -748,7 +748,7 @@ class LauncherConfig:
 
 @dataclass
 class BaseExperimentConfig:
-    post_exit_hook: Optional[str] = None      # import path of a callable run after training ends
+    post_exit_hook: Optional[str] = None      # shell command (LOG_DIR set) or `module:function` run by the launcher after the job ended
     experiment_name: str = "default-experiment"
     trial_name: str = "trial0"
     cluster: ClusterSpecConfig = field(default_factory=ClusterSpecConfig)

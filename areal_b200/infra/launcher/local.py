@@ -87,6 +87,9 @@ class LocalLauncher:
 
 
 def launch(script: str, script_args: list[str], cfg: BaseExperimentConfig, n_gpus: Optional[int] = None, max_restarts: Optional[int] = None) -> int:
+    from ..utils.launcher import run_post_exit_hook, validate_config_for_launcher
+
+    validate_config_for_launcher(cfg, n_gpus_available=n_gpus)
     alloc = AllocationMode.from_str(cfg.allocation_mode) if cfg.allocation_mode else None
     la = LocalLauncher(cfg.experiment_name, cfg.trial_name, cfg.cluster.fileroot, n_gpus)
     os.environ.setdefault("AREAL_NAME_RESOLVE_ROOT", os.path.join(cfg.cluster.fileroot, "name_resolve", cfg.experiment_name, cfg.trial_name))
@@ -117,12 +120,14 @@ def launch(script: str, script_args: list[str], cfg: BaseExperimentConfig, n_gpu
             la.submit("trainer", torchrun_cmd(script, script_args, n_train, master_port=find_free_ports(1)[0]), gpus=n_train, env=env)
             la.wait(["trainer"])
             la.stop_all()
+            run_post_exit_hook(cfg)
             return 0
         except JobFailed as e:
             la.stop_all()
             attempt += 1
             if cfg.recover.mode in ("disabled", "off") or attempt > retries:
                 logger.error("%s; giving up after %d attempt(s)", e, attempt)
+                run_post_exit_hook(cfg)
                 return e.code or 1
             logger.warning("%s; restarting the job (attempt %d of %d)", e, attempt, retries)
             time.sleep(1.0)

@@ -488,3 +488,53 @@ def test_version_info_experiment_metadata_and_chained_schedule(tmp_path):
     assert areal_b200.StalenessManager.__name__ == "StalenessManager" and "PPOTrainer" in dir(areal_b200)
     with pytest.raises(AttributeError):
         areal_b200.no_such_name
+
+
+def test_launcher_helpers_validate_wait_and_run_the_post_exit_hook(tmp_path):
+    import threading
+    import time
+
+    import pytest
+
+    from areal_b200.api.cli_args import BaseExperimentConfig, GRPOConfig
+    from areal_b200.infra.utils.launcher import (JobException, JobInfo, JobState, run_post_exit_hook, validate_config_for_launcher,
+                                                 wait_llm_server_addrs)
+    from areal_b200.utils import name_resolve, names
+
+    assert JobState.RUNNING.active() and JobState.PENDING.active() and not any(s.active() for s in (JobState.COMPLETED, JobState.FAILED, JobState.CANCELLED))
+    assert "FAILED" in str(JobException("run", "trainer", "node3", JobState.FAILED)) and JobInfo("x", JobState.PENDING).slurm_id is None
+    # an RL layout on a config without actor / rollout sections, and a layout larger than the cluster
+    base = BaseExperimentConfig(allocation_mode="native:d2+d2")
+    base.cluster.fileroot = str(tmp_path / "root")
+    with pytest.raises(RuntimeError, match="`actor` is required"):
+        validate_config_for_launcher(base)
+    g = GRPOConfig(allocation_mode="native:d4+d8")
+    g.cluster.fileroot = str(tmp_path / "root")
+    with pytest.raises(ValueError, match="needs 12 GPUs"):
+        validate_config_for_launcher(g)
+    g.allocation_mode = "native:d4+d4"
+    validate_config_for_launcher(g)
+    validate_config_for_launcher(g, n_gpus_available=0)              # CPU launch: no device count to hold against
+    # servers announce themselves; the wait returns once enough have
+    name_resolve.reconfigure(type="memory")
+    key = names.gen_servers("e", "t")
+    threading.Timer(0.3, lambda: [name_resolve.add_subentry(key, a) for a in ("h:1", "h:2")]).start()
+    t0 = time.time()
+    assert sorted(wait_llm_server_addrs("e", "t", 2, timeout=10, poll=0.05)) == ["h:1", "h:2"] and time.time() - t0 >= 0.25
+    with pytest.raises(TimeoutError, match="found 2"):
+        wait_llm_server_addrs("e", "t", 3, timeout=0.2, poll=0.05)
+    # the hook: a shell command that sees LOG_DIR, a failing one, a module:function, none
+    out = tmp_path / "hook.txt"
+    g.experiment_name, g.trial_name = "e", "t"
+    g.post_exit_hook = f'echo "$LOG_DIR" > {out}'
+    assert run_post_exit_hook(g) == 0 and out.read_text().strip().endswith(os.path.join("e", "t"))
+    g.post_exit_hook = "exit 7"
+    assert run_post_exit_hook(g) == 7
+    g.post_exit_hook = "sleep 5"
+    assert run_post_exit_hook(g, timeout=0.2) == -1
+    g.post_exit_hook = "os:getcwd"
+    assert run_post_exit_hook(g) == -1                                # getcwd(config) raises: logged, not propagated
+    g.post_exit_hook = "builtins:repr"
+    assert run_post_exit_hook(g) == 0
+    g.post_exit_hook = None
+    assert run_post_exit_hook(g) is None
