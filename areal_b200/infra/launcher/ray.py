@@ -63,6 +63,9 @@ def launch(script: str, script_args: list[str], cfg: BaseExperimentConfig, ray_m
     codes = ray.get(runs)
     for f in futures:
         ray.cancel(f, force=True)
+    from ..utils.launcher import run_post_exit_hook
+
+    run_post_exit_hook(cfg)
     return 0 if all(c == 0 for c in codes) else 1
 
 

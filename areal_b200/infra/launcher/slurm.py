@@ -49,6 +49,9 @@ def plan_jobs(script: str, script_args: list[str], cfg: BaseExperimentConfig, gp
 
 def launch(script: str, script_args: list[str], cfg: BaseExperimentConfig, gpus_per_node: int = 8, dry_run: bool = False,
            sbatch: str = "sbatch", poll_s: float = 10.0) -> int:
+    from ..utils.launcher import validate_config_for_launcher
+
+    validate_config_for_launcher(cfg)
     log_dir = os.path.join(cfg.cluster.fileroot, "logs", cfg.experiment_name, cfg.trial_name)
     os.makedirs(log_dir, exist_ok=True)
     ids = []
@@ -78,6 +81,9 @@ def launch(script: str, script_args: list[str], cfg: BaseExperimentConfig, gpus_
     for j in ids[:-1]:
         subprocess.run(["scancel", j])
     acct = subprocess.run(["sacct", "-n", "-j", trainer, "-o", "State", "-X"], capture_output=True, text=True).stdout
+    from ..utils.launcher import run_post_exit_hook
+
+    run_post_exit_hook(cfg)
     return 0 if "COMPLETED" in acct or not acct.strip() else 1
 
 

@@ -197,11 +197,11 @@ def test_stateful_dataloader_resumes_and_partitions():
 
 
 def test_slurm_and_ray_launcher_plans(tmp_path, capsys):
-    from areal_b200.api.cli_args import BaseExperimentConfig, ClusterSpecConfig
+    from areal_b200.api.cli_args import ClusterSpecConfig, GRPOConfig
     from areal_b200.infra.launcher import ray as ray_launcher
     from areal_b200.infra.launcher import slurm as slurm_launcher
 
-    cfg = BaseExperimentConfig(experiment_name="e", trial_name="t", allocation_mode="native:d2+d12", cluster=ClusterSpecConfig(fileroot=str(tmp_path)))
+    cfg = GRPOConfig(experiment_name="e", trial_name="t", allocation_mode="native:d2+d12", cluster=ClusterSpecConfig(fileroot=str(tmp_path), n_nodes=2))
     jobs = slurm_launcher.plan_jobs("train.py", ["--config", "c.yaml"], cfg, gpus_per_node=8)
     assert [j["name"] for j in jobs] == ["llm_server", "trainer"]
     assert jobs[0]["nodes"] == 1 and jobs[0]["gpus_per_node"] == 2 and jobs[1]["nodes"] == 2 and jobs[1]["gpus_per_node"] == 8
