@@ -61,6 +61,10 @@ class TrainingWorker:
         def health(body, ctx):
             return {"status": "ok", "engine": type(eng).__name__, "version": eng.get_version()}
 
+        @svc.route("GET", "/topology")
+        def topology(body, ctx):
+            return self.topology()
+
         @svc.route("GET", "/version")
         def version(body, ctx):
             return {"version": eng.get_version()}
@@ -126,12 +130,38 @@ class TrainingWorker:
             self._run(eng.step_lr_scheduler)
             return {"ok": True}
 
+    def topology(self) -> dict:
+        """This worker's place in the parallel layout, as its engine reports it (a single-process engine is its own
+        data-parallel group of one)."""
+        eng = self.engine
+        g = lambda name, default: getattr(eng, name, default)      # noqa: E731
+        head = eng.is_data_parallel_head() if hasattr(eng, "is_data_parallel_head") else True
+        return {"address": self.address, "rank": int(g("rank", 0) or 0), "dp_rank": int(g("dp_rank", g("data_parallel_rank", 0)) or 0),
+                "dp_size": int(g("dp_size", g("data_parallel_world_size", 1)) or 1), "is_dp_head": bool(head)}
+
+    def register(self, router_address: str, heartbeat_s: float = 5.0) -> None:
+        """Announces this worker to a training router and keeps the entry alive from a daemon thread."""
+        from ..common import call
+
+        call(f"http://{router_address}/register", self.topology(), retries=5)
+
+        def beat():
+            while not self._stopped.wait(heartbeat_s):
+                try:
+                    call(f"http://{router_address}/heartbeat", {"address": self.address})
+                except Exception:  # noqa: BLE001  (the router may be restarting; the next beat tries again)
+                    pass
+        self._stopped = threading.Event()
+        threading.Thread(target=beat, daemon=True, name="train-worker-heartbeat").start()
+
     def start(self):
         self.svc.start()
         return self
 
     def stop(self):
         self.svc.stop()
+        if getattr(self, "_stopped", None) is not None:
+            self._stopped.set()
         self._q.put((None, None))
 
     @property

@@ -2,6 +2,7 @@
 service with a fake engine, weight-update gateway, CLI state."""
 import json
 import os
+import time
 
 import pytest
 import torch
@@ -439,3 +440,69 @@ def test_control_plane_fault_injection_5xx_drop_and_delay():
         asyncio.run(go())
     finally:
         svc.stop()
+
+
+def test_training_gateway_dispatches_by_topology_and_heads_answer(tmp_path):
+    """Two data-parallel groups of two model-parallel ranks each: every rank of a group receives the group's share of the
+    batch, the head's answer is merged; control calls reach all four workers; a group with a missing rank degrades the
+    gateway instead of dispatching to half a group."""
+    from areal_b200.api.io_struct import SaveLoadMeta
+    from areal_b200.v2.training_service.gateway import GatewayTrainingClient, TrainingGateway, TrainingRouter
+
+    class Eng(FakeTrainEngine):
+        def __init__(self, rank, dp_rank, head):
+            super().__init__()
+            self.rank, self.dp_rank, self.dp_size, self._head, self.seen = rank, dp_rank, 2, head, []
+
+        def is_data_parallel_head(self):
+            return self._head
+
+        def compute_logp(self, batch):
+            self.seen.append(batch["input_ids"].shape[0])
+            return batch["input_ids"].float() * (-0.5 if self._head else 99.0)      # only the head's answer may come back
+
+    engs = [Eng(0, 0, True), Eng(1, 0, False), Eng(2, 1, True), Eng(3, 1, False)]
+    workers = [TrainingWorker(e).start() for e in engs]
+    router = TrainingRouter(heartbeat_timeout=1.0).start()
+    gw = TrainingGateway(router, admin_key="adm", group_size=2).start()
+    try:
+        with pytest.raises(HTTPError) as e:                     # nobody registered yet: the gateway says so with a 503
+            call(f"{gw.svc.url}/health", method="GET")
+        assert e.value.status == 503
+        for w in workers[:3]:
+            w.register(router.svc.address, heartbeat_s=0.2)
+        cl = GatewayTrainingClient(gw.svc.address, "adm")
+        lens = torch.tensor([9, 3, 5, 7, 2, 8, 6, 4])
+        am = torch.arange(9)[None] < lens[:, None]
+        batch = {"attention_mask": am, "input_ids": torch.randint(1, 9, (8, 9)) * am, "rewards": torch.arange(8).float()}
+        with pytest.raises(HTTPError) as e:                     # rank 3 has not registered: group 1 is incomplete
+            cl.compute_logp(batch)
+        assert e.value.status == 503
+        workers[3].register(router.svc.address, heartbeat_s=0.2)
+        with pytest.raises(HTTPError) as e:
+            GatewayTrainingClient(gw.svc.address, "wrong").compute_logp(batch)
+        assert e.value.status == 401
+        topo = cl.topology()
+        assert [[w["rank"] for w in g] for g in topo] == [[0, 1], [2, 3]] and all(g[0]["is_dp_head"] and not g[1]["is_dp_head"] for g in topo)
+        lp = cl.compute_logp(batch)
+        assert torch.equal(lp, batch["input_ids"].float() * -0.5)
+        assert engs[0].seen == engs[1].seen == [4] and engs[2].seen == engs[3].seen == [4]      # peers saw their head's share
+        out = cl.compute_advantages(batch)
+        assert out is batch and torch.equal(batch["advantages"], batch["rewards"][:, None].expand(8, 9) * am)
+        cl.set_version(7)
+        cl.step_lr_scheduler()
+        cl.save(SaveLoadMeta(path=str(tmp_path / "ck"), weight_format="hf", with_optim=False))
+        assert [e_.version for e_ in engs] == [7] * 4 and [e_.lr_steps for e_ in engs] == [1] * 4 and all(e_.saved for e_ in engs)
+        # a worker that stops beating drops out of the live set after the timeout
+        workers[1].stop()
+        time.sleep(1.5)
+        assert call(f"{router.svc.url}/workers")["workers"].__len__() == 3
+        with pytest.raises(HTTPError):
+            cl.compute_logp(batch)
+    finally:
+        gw.stop(); router.stop()
+        for w in workers:
+            try:
+                w.stop()
+            except Exception:
+                pass
