@@ -300,8 +300,19 @@ class RolloutWorker:
                 if self.staging is not None and self.staging.get("flat") is None:     # allocated on first use
                     self.staging["flat"] = torch.zeros(self.staging["padded"], dtype=self.flat_param.dtype, device=self.flat_param.device)
                 flat = self.staging["flat"] if self.staging is not None else self.flat_param
-                for a in range(0, flat.numel(), cmd["bucket"]):
-                    dist.broadcast(flat[a:a + cmd["bucket"]], src=cmd["src"], group=self.wu_group)
+                if cmd.get("sparse") is not None:
+                    # delta push: (index, value) pairs of the elements that changed since the last push
+                    k = int(cmd["sparse"])
+                    idx = torch.empty(k, dtype=getattr(torch, cmd.get("index_dtype", "int32")), device=flat.device)
+                    vals = torch.empty(k, dtype=flat.dtype, device=flat.device)
+                    for a in range(0, k, cmd["bucket"]):
+                        dist.broadcast(idx[a:a + cmd["bucket"]], src=cmd["src"], group=self.wu_group)
+                        dist.broadcast(vals[a:a + cmd["bucket"]], src=cmd["src"], group=self.wu_group)
+                    flat[idx.long()] = vals
+                    self.delta_pushes = getattr(self, "delta_pushes", 0) + 1
+                else:
+                    for a in range(0, flat.numel(), cmd["bucket"]):
+                        dist.broadcast(flat[a:a + cmd["bucket"]], src=cmd["src"], group=self.wu_group)
                 if self.staging is not None:
                     self._reshard_from_staging()
             done = self.bus.get(f"wu/{self.push_seq}/done")

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import asyncio
 import json
+import queue
 import secrets
 import threading
 import time
@@ -134,6 +135,9 @@ class OpenAIProxyServer:
         self.admin_key = admin_key
         self._sessions: dict[str, _Session] = {}
         self._lock = threading.Lock()
+        # online training: sessions opened over HTTP by an outside user are queued here when that user ends them
+        self._external: set[str] = set()
+        self._completed: "queue.Queue[str]" = queue.Queue()
         self._loop = asyncio.new_event_loop()
         self._loop_thread = threading.Thread(target=self._loop.run_forever, daemon=True, name="openai-proxy-loop")
         self._srv: Optional[ThreadingHTTPServer] = None
@@ -154,11 +158,25 @@ class OpenAIProxyServer:
     def end_session(self, key: str) -> None:
         with self._lock:
             s = self._sessions.get(key)
+            done = s is not None and not s.ended and key in self._external
             if s is not None:
                 s.ended = True
+        if done:
+            self._completed.put(key)
+
+    def wait_for_completed_session(self, timeout: Optional[float] = None) -> Optional[str]:
+        """Blocks until an outside user has finished a session it opened through ``/rl/start_session`` (start ->
+        chat -> set_reward -> end_session); returns that session's key, ``None`` on timeout. The caller pops and exports
+        it. Reference: the wait-for-session route of ``areal/experimental/openai/proxy/proxy_gateway.py`` used by
+        ``online_agent.py``."""
+        try:
+            return self._completed.get(timeout=timeout)
+        except queue.Empty:
+            return None
 
     def pop_session(self, key: str) -> Optional[_Session]:
         with self._lock:
+            self._external.discard(key)
             return self._sessions.pop(key, None)
 
     def _session(self, key: Optional[str]) -> _Session:
@@ -256,7 +274,10 @@ class OpenAIProxyServer:
                     if path == "/rl/start_session":
                         if proxy.admin_key and self._key() != proxy.admin_key:
                             raise PermissionError("admin key required")
-                        return self._reply(200, {"api_key": proxy.start_session(), "base_url": proxy.base_url})
+                        key = proxy.start_session()
+                        with proxy._lock:
+                            proxy._external.add(key)
+                        return self._reply(200, {"api_key": key, "base_url": proxy.base_url})
                     if path == "/rl/set_reward":
                         s = proxy._session(self._key())
                         if body.get("interaction_id"):

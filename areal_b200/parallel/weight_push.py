@@ -319,27 +319,68 @@ class DistributedWeightPusher:
 class BroadcastWeightPusher:
     """Collective baseline: the trainer head broadcasts the whole flat parameter buffer to the
     rollout ranks in buckets (the data movement of the reference's xccl path, minus its HTTP
-    round trips). Works on NCCL and on gloo (CPU deployments)."""
+    round trips). Works on NCCL and on gloo (CPU deployments).
+
+    Delta transfer (``actor.enable_delta_weight_update`` or ``weight_update_delta_method: exact``): after a
+    small-learning-rate step most bf16 values keep their bit pattern, so from the second push on the head compares the
+    buffer with a snapshot of what the receivers hold and, when fewer than a third of the elements changed, broadcasts
+    only (index, value) pairs: 6 bytes per changed element instead of 2 per element. Every
+    ``weight_update_anchor_interval``-th push (default 20) is a full one again. Reference:
+    ``areal/v2/weight_update/awex/delta_detect.py``, the ``dte`` example (sparse deltas with periodic anchors)."""
 
     def __init__(self, train_engine, rollout_client, group, bucket_mb: int = 1024):
         self.train, self.client, self.group = train_engine, rollout_client, group
         self.bucket = bucket_mb * 1024 * 1024 // max(1, train_engine.store.flat_param.element_size())
         self.bus, self.split, self.seq = rollout_client.bus, rollout_client.split, 0
         self.last_ms = 0.0
+        cfg = getattr(train_engine, "config", None)
+        self.delta = bool(getattr(cfg, "enable_delta_weight_update", False)) or getattr(cfg, "weight_update_delta_method", "none") == "exact"
+        self.anchor_every = int(getattr(cfg, "weight_update_anchor_interval", 0) or 20)
+        self.snapshot: Optional[torch.Tensor] = None
+        self.deltas_since_anchor = 0
+        self.last_fraction = 1.0               # bytes sent / bytes of a full push
+
+    def _sparse_update(self, flat: torch.Tensor):
+        """(indices, values) of the elements whose bits differ from the receivers' copy, or ``None`` for a full push."""
+        if not self.delta or self.snapshot is None or self.deltas_since_anchor >= self.anchor_every:
+            return None
+        view = {2: torch.int16, 4: torch.int32, 1: torch.int8}[flat.element_size()]
+        idx = (flat.view(view) != self.snapshot.view(view)).nonzero().flatten()
+        isz = 4 if flat.numel() < 2 ** 31 else 8
+        if idx.numel() * (isz + flat.element_size()) >= flat.numel() * flat.element_size():
+            return None                        # dense is cheaper
+        return (idx.to(torch.int32) if isz == 4 else idx), flat[idx]
 
     def push(self, meta: Optional[WeightUpdateMeta] = None) -> float:
         eng = self.train
         head = eng.local_index <= 0
         t0 = time.perf_counter()
         src = self.split.train_ranks[0]
+        flat = eng.store.flat_param
+        sparse = self._sparse_update(flat) if head else None
         if head:
-            self.bus.put(f"wu/{self.seq}/pause", {"mode": "broadcast", "bucket": self.bucket, "src": src})
+            cmd = {"mode": "broadcast", "bucket": self.bucket, "src": src}
+            if sparse is not None:
+                cmd.update(sparse=int(sparse[0].numel()), index_dtype=str(sparse[0].dtype).replace("torch.", ""))
+            self.bus.put(f"wu/{self.seq}/pause", cmd)
         for r in self.split.rollout_ranks:
             self.bus.get(f"wu/{self.seq}/ack/{r}")
-        flat = eng.store.flat_param
         if head:
-            for a in range(0, flat.numel(), self.bucket):
-                dist.broadcast(flat[a:a + self.bucket], src=src, group=self.group)
+            if sparse is not None:
+                idx, vals = sparse
+                for a in range(0, idx.numel(), self.bucket):
+                    dist.broadcast(idx[a:a + self.bucket], src=src, group=self.group)
+                    dist.broadcast(vals[a:a + self.bucket], src=src, group=self.group)
+                self.snapshot[idx.long()] = vals
+                self.deltas_since_anchor += 1
+                self.last_fraction = idx.numel() * (idx.element_size() + vals.element_size()) / max(1, flat.numel() * flat.element_size())
+            else:
+                for a in range(0, flat.numel(), self.bucket):
+                    dist.broadcast(flat[a:a + self.bucket], src=src, group=self.group)
+                if self.delta:
+                    self.snapshot = flat.detach().clone()
+                    self.deltas_since_anchor = 0
+                self.last_fraction = 1.0
             if flat.is_cuda:
                 torch.cuda.current_stream().synchronize()
         if eng.cpu_group is not None:

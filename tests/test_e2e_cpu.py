@@ -170,6 +170,9 @@ from areal_b200.models.config import preset
 from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
 from areal_b200.infra.spmd import init_split_world, make_split_trainer, run_rollout_rank
 cfg = _cfg(%(tmp)r)
+if os.environ.get("SPLIT_DELTA") == "1":
+    cfg.actor.enable_delta_weight_update = True           # sparse (index, value) pushes after the first full one
+    cfg.actor.optimizer.lr = 1e-10                         # fp32 weights here: a step far below half an ulp leaves most bit patterns alone
 mc = preset(os.environ.get("SPLIT_MODEL", "tiny-qwen2"), vocab_size=64, num_layers=2, **({"layer_types": ["linear_attention", "full_attention"]} if "qwen3.5" in os.environ.get("SPLIT_MODEL", "") else {}))
 split, groups, bus = init_split_world(int(os.environ["N_TRAIN"]), None, sp=int(os.environ.get("SPLIT_SP", "1")), rollout_tp=int(os.environ.get("SPLIT_RTP", "1")))
 ds = ArithmeticDataset(size=128)
@@ -183,6 +186,10 @@ if split.is_trainer:
         dist.broadcast(ref, src=0, group=groups["shard"])
         assert torch.equal(ref, tr.actor.store.flat_param), "trainer replicas diverged"
     if split.rank == 0:
+        if os.environ.get("SPLIT_DELTA") == "1":
+            p_ = tr.actor._weight_pusher
+            assert p_.delta and p_.deltas_since_anchor == 3 and p_.last_fraction < 1.0, (p_.deltas_since_anchor, p_.last_fraction)
+            print("DELTA_FRACTION", round(p_.last_fraction, 4), flush=True)
         bus.put("final_sum", float(tr.actor.store.flat_param.double().sum()))
         bus.put("exit", 1)
     tr.close()
@@ -190,6 +197,7 @@ else:
     wf = RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True)
     w = run_rollout_rank(cfg, mc, split, groups, bus, ds, wf, torch.device("cpu"))
     assert w.engine.get_version() == 3, w.engine.get_version()
+    assert getattr(w, "delta_pushes", 0) == (3 if os.environ.get("SPLIT_DELTA") == "1" else 0)     # the start-up push is full, the three step pushes are deltas
     if split.rollout_tp == 1:
         got = float(w.flat_param.double().sum())
         assert abs(got - bus.get("final_sum")) < 1e-6, "rollout replica does not hold the trainer's final weights"
@@ -212,11 +220,15 @@ print("SPLIT_OK", split.rank, flush=True)
     (2, 4, 29841, "tiny-qwen2", 2, 2),        # one Ulysses pair of trainers, one tensor-parallel rollout replica
     (2, 4, 29851, "tiny-qwen2", 1, 2),        # two data-parallel trainers share one tensor-parallel replica
     (1, 3, 29861, "tiny-qwen2", 1, 1),        # one trainer merges the batches of two replicas
-    (4, 8, 29871, "tiny-qwen2", 4, 2)])       # the 8-GPU benchmark layout: one Ulysses group of four trainers, two TP = 2 replicas
+    (4, 8, 29871, "tiny-qwen2", 4, 2),        # the 8-GPU benchmark layout: one Ulysses group of four trainers, two TP = 2 replicas
+    (2, 4, 29881, "tiny-qwen2-delta", 1, 1),  # delta weight transfer: a full push, then (index, value) pairs of changed elements
+    (2, 4, 29891, "tiny-qwen2-delta", 1, 2)]) # ... into the staging buffer of a tensor-parallel replica
 def test_trainer_rollout_split_over_gloo(tmp_path, n_train, world, port, model, sp, rtp):
     script = tmp_path / "split.py"
     script.write_text(SPLIT_SCRIPT % dict(root=ROOT, tmp=str(tmp_path)))
-    env = dict(os.environ, N_TRAIN=str(n_train), OMP_NUM_THREADS="1", SPLIT_MODEL=model, SPLIT_SP=str(sp), SPLIT_RTP=str(rtp))
+    delta = model.endswith("-delta")
+    model = model[: -len("-delta")] if delta else model
+    env = dict(os.environ, N_TRAIN=str(n_train), OMP_NUM_THREADS="1", SPLIT_MODEL=model, SPLIT_SP=str(sp), SPLIT_RTP=str(rtp), SPLIT_DELTA="1" if delta else "0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)], cwd=ROOT, env=env,
                        capture_output=True, text=True, timeout=400)

@@ -109,3 +109,68 @@ def test_http_clients_are_shared_per_event_loop():
         await wctx.close_http_clients()
         return c.is_closed, s_.closed, wctx.get_httpx_client() is not c
     assert asyncio.run(closing()) == (True, True, True)
+
+
+def test_online_workflow_turns_an_outside_users_session_into_a_trajectory():
+    """Online mode: the episode is whatever an outside user did between start_session and end_session on the proxy."""
+    import json
+    import threading
+    import urllib.request
+
+    from areal_b200.rollout.workflows.online import OnlineSessionWorkflow
+
+    def post(url, body, key):
+        req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json", "Authorization": f"Bearer {key}"})
+        with urllib.request.urlopen(req, timeout=30) as r:
+            return json.loads(r.read())
+
+    eng = ScriptedEngine(["first answer", "second answer", "third"])
+    px = OpenAIProxyServer(eng, ByteTok(), G, admin_key="adm").start()
+    try:
+        wf = OnlineSessionWorkflow(px, turn_discount=0.5, timeout=20)
+        box = {}
+        t = threading.Thread(target=lambda: box.setdefault("traj", asyncio.run(wf.arun_episode(eng, {}))))
+        t.start()
+        root = px.base_url[:-3]
+        key = post(f"{root}/rl/start_session", {}, "adm")["api_key"]
+        for q in ("one", "two"):
+            post(f"{px.base_url}/chat/completions", {"messages": [{"role": "user", "content": q}], "max_tokens": 32}, key)
+        assert t.is_alive()                                           # still waiting: the user has not closed the session
+        post(f"{root}/rl/set_reward", {"reward": 2.0}, key)
+        post(f"{root}/rl/end_session", {}, key)
+        t.join(timeout=20)
+        traj = box["traj"]
+        assert traj["rewards"].tolist() == [1.0, 2.0] and traj["input_ids"].shape[0] == 2 and len(px._sessions) == 0
+        # a session that ended without a reward is dropped unless a default is configured; in-process sessions never queue
+        k2 = post(f"{root}/rl/start_session", {}, "adm")["api_key"]
+        post(f"{px.base_url}/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 8}, k2)
+        post(f"{root}/rl/end_session", {}, k2)
+        assert asyncio.run(OnlineSessionWorkflow(px, timeout=5).arun_episode(eng, {})) is None
+        px.end_session(px.start_session())
+        assert asyncio.run(OnlineSessionWorkflow(px, timeout=0.2, default_reward=0.0).arun_episode(eng, {})) is None      # timeout
+    finally:
+        px.stop()
+
+
+def test_example_reward_runs_code_in_a_remote_sandbox(monkeypatch):
+    """``examples/sandbox_remote``: the completion's last python block plus the record's tests decide the reward."""
+    import importlib.util
+
+    from areal_b200.infra.sandbox import SandboxServer
+
+    srv = SandboxServer(api_key="k").start()
+    try:
+        monkeypatch.setenv("AREAL_SANDBOX_ADDR", srv.address)
+        monkeypatch.setenv("AREAL_SANDBOX_KEY", "k")
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        spec = importlib.util.spec_from_file_location("sandbox_reward_example", os.path.join(root, "examples", "sandbox_remote", "reward_example.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        good = "Here you go:\n```python\ndef add(a, b):\n    return a + b\n```"
+        bad = "```python\ndef add(a, b):\n    return a - b\n```"
+        tests = "assert add(2, 3) == 5"
+        assert mod.code_reward_fn("", good, [], [], tests=tests) == 1.0
+        assert mod.code_reward_fn("", bad, [], [], tests=tests) == 0.0
+        assert mod.code_reward_fn("", "no code here", [], [], tests=tests) == 0.0
+    finally:
+        srv.stop()
