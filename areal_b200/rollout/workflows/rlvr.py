@@ -19,6 +19,7 @@ from ...api.io_struct import ModelRequest
 from ...api.reward_api import AsyncRewardWrapper
 from ...api.workflow_api import RolloutWorkflow
 from ...utils import data as D
+from ...utils import logging as alog
 from ...utils import stats_tracker
 from .. import workflow_context as wctx
 
@@ -33,6 +34,9 @@ def default_get_input_ids(data: dict[str, Any], tokenizer, enable_thinking: bool
         return list(tokenizer.apply_chat_template(data["messages"], tokenize=True, add_generation_prompt=True,
                                                   enable_thinking=enable_thinking))
     return list(tokenizer.encode(data["prompt"]))
+
+
+logger = alog.getLogger("workflow")
 
 
 class RLVRWorkflow(RolloutWorkflow):
@@ -98,13 +102,48 @@ class RLVRWorkflow(RolloutWorkflow):
 
 
 class GroupedRolloutWorkflow(RolloutWorkflow):
-    """Runs ``group_size`` episodes of an inner workflow concurrently and concatenates them
-    (reference ``areal/infra/remote_inf_engine.py:70``)."""
+    """Runs ``group_size`` episodes of an inner workflow concurrently (each with its own ``sample_idx`` in the workflow
+    context) and concatenates them.
 
-    def __init__(self, workflow: RolloutWorkflow, group_size: int):
+    * ``drop_incomplete_group``: a group in which any episode failed (returned ``None``) is dropped as a whole, so
+      group-level baselines always see ``group_size`` samples; the trainer's batch preparation then takes another prompt.
+      Otherwise the remaining episodes are kept (variable group size).
+    * ``reward_normalization``: every episode's reward (its last one, when an episode exports several sequences) is
+      replaced by its z-score inside the group; the raw values stay in ``original_rewards``. A group with a missing reward
+      is dropped, so the normalisation base is always the configured size.
+
+    Reference: ``areal/infra/remote_inf_engine.py:70-206``; the two switches are ``gconfig.drop_incomplete_group`` and
+    ``gconfig.reward_normalization`` (see :meth:`from_gconfig`)."""
+
+    def __init__(self, workflow: RolloutWorkflow, group_size: int, reward_normalization: bool = False, drop_incomplete_group: bool = False):
+        if group_size < 1:
+            raise ValueError(f"group_size must be >= 1, got {group_size}")
         self.workflow, self.group_size = workflow, group_size
+        self.reward_normalization, self.drop_incomplete_group = reward_normalization, drop_incomplete_group
+
+    @classmethod
+    def from_gconfig(cls, workflow: RolloutWorkflow, gconfig: GenerationHyperparameters) -> "GroupedRolloutWorkflow":
+        return cls(workflow, max(1, gconfig.n_samples), bool(getattr(gconfig, "reward_normalization", False)),
+                   bool(getattr(gconfig, "drop_incomplete_group", False)))
 
     async def arun_episode(self, engine, data):
-        res = await asyncio.gather(*[self.workflow.arun_episode(engine, data) for _ in range(self.group_size)])
-        res = [r for r in res if r is not None]
-        return D.concat_padded_tensors(res) if res else None
+        parent = wctx.get()
+
+        async def one(i: int):
+            with wctx.scoped(is_eval=parent.is_eval, task_id=parent.task_id, sample_idx=i):
+                return await self.workflow.arun_episode(engine, data)
+
+        res = await asyncio.gather(*[one(i) for i in range(self.group_size)])
+        ok = [r for r in res if r is not None]
+        if not ok:
+            return None
+        if len(ok) < len(res) and (self.drop_incomplete_group or self.reward_normalization):
+            logger.warning("grouped rollout: %d of %d episodes failed, dropping the group", len(res) - len(ok), len(res))
+            return None
+        if self.reward_normalization and self.group_size > 1:
+            last = torch.stack([r["rewards"].float().reshape(-1)[-1] for r in ok])
+            z = (last - last.mean()) / (last.std(unbiased=False) + 1e-8)
+            for r, v in zip(ok, z):
+                r["original_rewards"] = r["rewards"].clone()
+                r["rewards"] = torch.full_like(r["rewards"].float(), float(v))
+        return D.concat_padded_tensors(ok)

@@ -60,6 +60,19 @@ class PPOActor:
                                final_reward=data["tot_rewards"], denominator="n_valid_tokens")
             prompt_lens = (attn.long().sum(-1) - data["loss_mask"].long().sum(-1)).float()
             stats_tracker.stat(prompt_len=prompt_lens, denominator="n_seqs")
+            reward_pos = reward > 0
+            stats_tracker.denominator(correct_n_seqs=reward_pos, incorrect_n_seqs=~reward_pos)
+            stats_tracker.stat(correct_seq_len=seqlens.float(), denominator="correct_n_seqs")
+            stats_tracker.stat(incorrect_seq_len=seqlens.float(), denominator="incorrect_n_seqs")
+            if getattr(cfg, "log_agent_stats", False):
+                # per-trajectory quantities an agent workflow attached to its first exported sequence (tool calls, turns ...):
+                # averaged over the rows that begin a trajectory (reference: areal/trainer/ppo/actor.py:385-444)
+                if "begin_of_trajectory" not in data:
+                    raise RuntimeError("'begin_of_trajectory' is expected in the batch to log agent statistics")
+                if not cfg.log_agent_stats_keys:
+                    raise RuntimeError("`log_agent_stats_keys` must not be empty when log_agent_stats=True")
+                stats_tracker.denominator(agent=(data["begin_of_trajectory"] > 0).bool())
+                stats_tracker.stat(**{k: data[k].float() for k in cfg.log_agent_stats_keys}, denominator="agent")
         for k in ("rewards", "tot_rewards", "kl_rewards"):
             data.pop(k, None)
         self.engine.train()

@@ -36,7 +36,7 @@ def main(argv):
     train = get_custom_dataset(config.train_dataset.path, type="rl", split="train", tokenizer=tok, max_length=config.train_dataset.max_length)
     one = AgentRolloutAdapter(ReflectingMathAgent(), tokenizer=tok, gconfig=config.gconfig, export_style="individual", turn_discount=0.9)
     with PPOTrainer(config, train, tokenizer=tok) as trainer:
-        trainer.train(workflow=GroupedRolloutWorkflow(one, config.gconfig.n_samples))
+        trainer.train(workflow=GroupedRolloutWorkflow.from_gconfig(one, config.gconfig))
 
 
 if __name__ == "__main__":

@@ -19,7 +19,7 @@ def main(argv):
     train = get_custom_dataset(config.train_dataset.path, type="rl", split="train", tokenizer=tok, max_length=config.train_dataset.max_length)
     one = MultiTurnWorkflow(gsm8k_reward_fn, config.gconfig, tok, max_turns=int(os.environ.get("MAX_TURNS", 3)),
                             turn_discount=float(os.environ.get("TURN_DISCOUNT", 0.9)))
-    wf = GroupedRolloutWorkflow(one, config.gconfig.n_samples)
+    wf = GroupedRolloutWorkflow.from_gconfig(one, config.gconfig)
     with PPOTrainer(config, train, tokenizer=tok) as trainer:
         trainer.train(workflow=wf)
 

@@ -68,7 +68,7 @@ def main(argv):
     data = [{"question": "What is " + d["prompt"].strip().rstrip("=") + "?", "answer": d["answer"]} for d in ArithmeticDataset(size=512)]
     one = AgentRolloutAdapter(CalculatorAgent(), tokenizer=tok, gconfig=config.gconfig, export_style="individual", turn_discount=0.9)
     with PPOTrainer(config, data, tokenizer=tok) as trainer:
-        trainer.train(workflow=GroupedRolloutWorkflow(one, config.gconfig.n_samples))
+        trainer.train(workflow=GroupedRolloutWorkflow.from_gconfig(one, config.gconfig))
 
 
 if __name__ == "__main__":

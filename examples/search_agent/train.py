@@ -91,7 +91,7 @@ def main(argv):
     tok = load_hf_tokenizer(config.tokenizer_path)
     one = AgentRolloutAdapter(SearchAgent(), tokenizer=tok, gconfig=config.gconfig, export_style="individual", turn_discount=0.9)
     with PPOTrainer(config, dataset(), tokenizer=tok) as trainer:
-        trainer.train(workflow=GroupedRolloutWorkflow(one, config.gconfig.n_samples))
+        trainer.train(workflow=GroupedRolloutWorkflow.from_gconfig(one, config.gconfig))
 
 
 if __name__ == "__main__":

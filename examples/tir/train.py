@@ -23,7 +23,7 @@ def main(argv):
     one = TIRWorkflow(gsm8k_reward_fn, config.gconfig, tok, max_tool_calls=int(os.environ.get("MAX_TOOL_CALLS", 4)),
                       sandbox=LocalSandbox(SandboxConfig(timeout_s=5.0, memory_mb=512)))
     with PPOTrainer(config, train, tokenizer=tok) as trainer:
-        trainer.train(workflow=GroupedRolloutWorkflow(one, config.gconfig.n_samples))
+        trainer.train(workflow=GroupedRolloutWorkflow.from_gconfig(one, config.gconfig))
 
 
 if __name__ == "__main__":

@@ -174,3 +174,38 @@ def test_example_reward_runs_code_in_a_remote_sandbox(monkeypatch):
         assert mod.code_reward_fn("", "no code here", [], [], tests=tests) == 0.0
     finally:
         srv.stop()
+
+
+def test_grouped_workflow_drops_or_keeps_incomplete_groups_and_normalises_rewards():
+    import torch
+
+    from areal_b200.api.workflow_api import RolloutWorkflow
+    from areal_b200.rollout import workflow_context as wctx
+    from areal_b200.rollout.workflows.rlvr import GroupedRolloutWorkflow
+
+    class Inner(RolloutWorkflow):
+        def __init__(self, rewards):
+            self.rewards, self.seen = rewards, []
+
+        async def arun_episode(self, engine, data):
+            i = wctx.get().sample_idx
+            self.seen.append(i)
+            r = self.rewards[i]
+            if r is None:
+                return None
+            return dict(input_ids=torch.tensor([[1, 2, 3]]), attention_mask=torch.ones(1, 3, dtype=torch.bool), loss_mask=torch.tensor([[0, 1, 1]]),
+                        rewards=torch.tensor([float(r)]))
+
+    inner = Inner([1.0, None, 3.0, 0.0])
+    out = asyncio.run(GroupedRolloutWorkflow(inner, 4).arun_episode(None, {}))
+    assert sorted(inner.seen) == [0, 1, 2, 3] and out["rewards"].tolist() == [1.0, 3.0, 0.0]           # variable group size
+    assert asyncio.run(GroupedRolloutWorkflow(Inner([1.0, None, 3.0, 0.0]), 4, drop_incomplete_group=True).arun_episode(None, {})) is None
+    assert asyncio.run(GroupedRolloutWorkflow(Inner([None] * 3), 3).arun_episode(None, {})) is None
+    out = asyncio.run(GroupedRolloutWorkflow(Inner([1.0, 3.0, 1.0, 3.0]), 4, reward_normalization=True).arun_episode(None, {}))
+    assert torch.allclose(out["rewards"], torch.tensor([-1.0, 1.0, -1.0, 1.0]), atol=1e-5) and out["original_rewards"].tolist() == [1.0, 3.0, 1.0, 3.0]
+    assert asyncio.run(GroupedRolloutWorkflow(Inner([1.0, None]), 2, reward_normalization=True).arun_episode(None, {})) is None
+    g = G.new(n_samples=3, drop_incomplete_group=True)
+    w = GroupedRolloutWorkflow.from_gconfig(Inner([0.0] * 3), g)
+    assert (w.group_size, w.drop_incomplete_group, w.reward_normalization) == (3, True, False)
+    with pytest.raises(ValueError):
+        GroupedRolloutWorkflow(Inner([]), 0)
