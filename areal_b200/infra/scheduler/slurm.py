@@ -26,8 +26,14 @@ _FAILED_STATES = {"FAILED", "CANCELLED", "TIMEOUT", "NODE_FAIL", "OUT_OF_MEMORY"
 def render_sbatch_script(job_name: str, n_tasks: int, gpus_per_task: int, cpus_per_task: int, mem_gb: int, log_path: str,
                          command: str, partition: Optional[str] = None, nodelist: Optional[str] = None, exclude: Optional[str] = None,
                          time_limit: Optional[str] = None, container_image: str = "", container_mounts: str = "",
-                         env: Optional[dict[str, str]] = None, extra_bash: Optional[list[str]] = None, tasks_per_node: Optional[int] = None) -> str:
-    """Text of the batch script (pure function: unit-testable without Slurm)."""
+                         env: Optional[dict[str, str]] = None, extra_bash: Optional[list[str]] = None, tasks_per_node: Optional[int] = None,
+                         reservation: Optional[str] = None, exclusive: bool = False, srun_additional_args: str = "",
+                         container_type: str = "none") -> str:
+    """Text of the batch script (pure function: unit-testable without Slurm). ``reservation`` / ``exclusive`` become
+    ``#SBATCH`` options; ``srun_additional_args`` is appended to the ``srun`` line; ``container_type``: ``none`` /
+    ``pyxis`` use srun's ``--container-image`` / ``--container-mounts``, ``apptainer`` (``singularity``) wraps the
+    command in ``apptainer exec --nv --bind <mounts> <image>`` instead (reference:
+    ``areal/infra/utils/slurm.py`` sbatch / srun templates, ``tests/test_slurm_reservation_and_env.py``)."""
     L = ["#!/bin/bash", f"#SBATCH --job-name={job_name}", f"#SBATCH --output={log_path}", "#SBATCH --open-mode=append",
          f"#SBATCH --ntasks={n_tasks}", f"#SBATCH --cpus-per-task={cpus_per_task}", f"#SBATCH --mem-per-cpu={max(1, mem_gb * 1024 // max(1, cpus_per_task))}M"]
     if gpus_per_task:
@@ -42,6 +48,10 @@ def render_sbatch_script(job_name: str, n_tasks: int, gpus_per_task: int, cpus_p
         L.append(f"#SBATCH --exclude={exclude}")
     if time_limit:
         L.append(f"#SBATCH --time={time_limit}")
+    if reservation:
+        L.append(f"#SBATCH --reservation={reservation}")
+    if exclusive:
+        L.append("#SBATCH --exclusive")
     L.append("")
     for k, v in (env or {}).items():
         L.append(f"export {k}={shlex.quote(str(v))}")
@@ -49,8 +59,14 @@ def render_sbatch_script(job_name: str, n_tasks: int, gpus_per_task: int, cpus_p
     srun = ["srun", "--kill-on-bad-exit=1", f"--ntasks={n_tasks}", f"--cpus-per-task={cpus_per_task}"]
     if gpus_per_task:
         srun.append(f"--gpus-per-task={gpus_per_task}")
-    if container_image:
+    ctype = (container_type or "none").lower()
+    if container_image and ctype in ("apptainer", "singularity"):
+        bind = f"--bind {container_mounts} " if container_mounts else ""
+        command = f"{ctype} exec --nv {bind}{shlex.quote(container_image)} bash -c {shlex.quote(command)}"
+    elif container_image:
         srun += [f"--container-image={container_image}"] + ([f"--container-mounts={container_mounts}"] if container_mounts else [])
+    if srun_additional_args:
+        srun += shlex.split(srun_additional_args)
     L.append(" ".join(srun) + " bash -c " + shlex.quote(command))
     return "\n".join(L) + "\n"
 
@@ -85,9 +101,10 @@ class SlurmScheduler(LocalScheduler):
         script = render_sbatch_script(
             f"{self.experiment_name}_{self.trial_name}:{role}", job.replicas, spec.gpu, spec.cpu, spec.mem,
             os.path.join(self.log_dir, f"{role}.log"), worker_cmd, spec.partition, spec.nodelist, spec.exclude, spec.time_limit,
-            spec.image or self.container_image, self.container_mounts,
+            spec.image or self.container_image, spec.mount or self.container_mounts,
             {**spec.env_vars, "AREAL_NAME_RESOLVE_ROOT": os.path.join(self.fileroot, "name_resolve")}, spec.additional_bash_cmds,
-            tasks_per_node=min(tpn, job.replicas) if tpn else None)
+            tasks_per_node=min(tpn, job.replicas) if tpn else None, reservation=spec.reservation, exclusive=spec.exclusive,
+            srun_additional_args=spec.srun_additional_args, container_type=spec.container_type)
         path = os.path.join(self.log_dir, f"{role}.sbatch")
         with open(path, "w") as f:
             f.write(script)

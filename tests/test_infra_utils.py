@@ -538,3 +538,23 @@ def test_launcher_helpers_validate_wait_and_run_the_post_exit_hook(tmp_path):
     assert run_post_exit_hook(g) == 0
     g.post_exit_hook = None
     assert run_post_exit_hook(g) is None
+
+
+@pytest.mark.parametrize("reservation,exclusive,present,absent", [
+    (None, False, [], ["--reservation", "--exclusive"]), ("shanghai", False, ["#SBATCH --reservation=shanghai"], ["--exclusive"]),
+    (None, True, ["#SBATCH --exclusive"], ["--reservation"]), ("r1", True, ["#SBATCH --reservation=r1", "#SBATCH --exclusive"], [])])
+def test_sbatch_script_reservation_exclusive_and_container_kinds(reservation, exclusive, present, absent):
+    from areal_b200.api.cli_args import SchedulingSpec
+    from areal_b200.infra.scheduler.slurm import render_sbatch_script
+
+    spec = SchedulingSpec()
+    assert spec.reservation is None and spec.exclusive is False
+    txt = render_sbatch_script("j", 2, 1, 4, 8, "/tmp/j.log", "echo hi", reservation=reservation, exclusive=exclusive)
+    assert all(p in txt for p in present) and not any(a in txt for a in absent)
+    # extra srun arguments and the two container styles
+    t2 = render_sbatch_script("j", 1, 1, 4, 8, "/tmp/j.log", "python x.py", container_image="/img.sif", container_mounts="/data:/data",
+                              srun_additional_args="--mpi=pmix --label", container_type="apptainer")
+    line = [l for l in t2.splitlines() if l.startswith("srun")][0]
+    assert "--mpi=pmix --label" in line and "apptainer exec --nv --bind /data:/data /img.sif" in line and "--container-image" not in line
+    t3 = render_sbatch_script("j", 1, 1, 4, 8, "/tmp/j.log", "python x.py", container_image="nvcr.io/x:1", container_mounts="/data:/data", container_type="pyxis")
+    assert "--container-image=nvcr.io/x:1 --container-mounts=/data:/data" in t3 and "apptainer" not in t3
