@@ -161,6 +161,7 @@ class WorkflowExecutor:
             traj, accepted = r.data
             if accepted:
                 self.staleness.on_rollout_accepted()
+                self._trace("finish and accept rollout", r.task_id)
                 with self._results_lock:
                     if r.task_id in self._tracked:      # handed out by ``wait_for_task`` only, never by ``wait``
                         self._task_results[r.task_id] = traj
@@ -169,9 +170,18 @@ class WorkflowExecutor:
             else:
                 self.staleness.on_rollout_rejected()
                 self.rejected_count += 1
+                self._trace("finish but reject rollout", r.task_id)
                 with self._results_lock:
                     if r.task_id in self._tracked:
                         self._task_results[r.task_id] = None
+
+    def _trace(self, what: str, task_id=None) -> None:
+        """``rollout.enable_rollout_tracing``: one log line per life-cycle event with the admission counters
+        (reference: ``areal/infra/workflow_executor.py:1239-1322``)."""
+        if getattr(self.config, "enable_rollout_tracing", False):
+            st = self.staleness.get_stats()
+            logger.info("%s (task %s): enqueued %d, running %d, accepted %d, rejected %d, engine version %d", what, task_id,
+                        st.enqueued, st.running, st.accepted, st.rejected, self.engine.get_version())
 
     # ------------------------------------------------------------------ workflow resolution
     def _resolve_workflow(self, workflow, workflow_kwargs) -> RolloutWorkflow:
@@ -260,6 +270,7 @@ class WorkflowExecutor:
             time.sleep(0.005)
         if not self.config.deterministic_sampling:
             random.shuffle(take)
+        self._trace(f"{count} rollout results are ready")
         return [r.data for r in take]
 
     def wait_for_task(self, task_id: int, timeout: Optional[float] = None, raise_timeout: bool = True):

@@ -46,8 +46,17 @@ class StatsLogger:
             try:
                 import wandb
 
-                wandb.init(mode=c.wandb.mode, entity=c.wandb.entity, project=c.wandb.project or c.experiment_name,
-                           name=c.wandb.name or c.trial_name, config=exp_config, dir=d)
+                w = c.wandb
+                if w.wandb_base_url:
+                    os.environ["WANDB_BASE_URL"] = w.wandb_base_url
+                if w.wandb_api_key:
+                    os.environ["WANDB_API_KEY"] = w.wandb_api_key
+                cfg = {**(w.config or {}), **(exp_config if isinstance(exp_config, dict) else {})} or exp_config
+                # a stable run id (experiment, trial, suffix): a recovered run resumes its own curves
+                run_id = f"{c.experiment_name}_{c.trial_name}_{w.id_suffix}" if w.id_suffix else None
+                wandb.init(mode=w.mode, entity=w.entity, project=w.project or c.experiment_name, name=w.name or c.trial_name, job_type=w.job_type,
+                           group=w.group or f"{c.experiment_name}_{c.trial_name}", notes=w.notes, tags=w.tags, config=cfg, dir=d, id=run_id,
+                           resume="allow", force=True)
                 self._wandb = wandb
             except Exception as e:  # pragma: no cover
                 logger.warning("wandb unavailable: %r", e)

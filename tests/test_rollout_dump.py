@@ -122,3 +122,27 @@ def test_stats_logger_feeds_trackio_and_swanlab_when_importable(tmp_path, monkey
     assert calls[1] == ("log", {"loss": 1.5}, 0) and calls[2] == ("log", {"loss": 1.25, "lr": 0.1}, 1) and calls[3] == ("finish",)
     with pytest.raises(ValueError, match="trackio.mode"):
         TrackioConfig(mode="cloud")
+
+
+def test_stats_logger_passes_the_wandb_section_through(tmp_path, monkeypatch):
+    import sys
+    import types
+
+    from areal_b200.api.cli_args import StatsLoggerConfig
+    from areal_b200.utils.stats_logger import StatsLogger
+
+    calls = {}
+    fake = types.ModuleType("wandb")
+    fake.init = lambda **kw: calls.update(init=kw)
+    fake.log = lambda d, step=None: calls.setdefault("log", []).append((dict(d), step))
+    fake.finish = lambda: calls.update(finished=True)
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    monkeypatch.delenv("WANDB_BASE_URL", raising=False)
+    cfg = StatsLoggerConfig(experiment_name="exp", trial_name="t1", fileroot=str(tmp_path))
+    cfg.wandb.mode, cfg.wandb.wandb_base_url, cfg.wandb.job_type, cfg.wandb.tags, cfg.wandb.config = "offline", "http://wb.local", "rl", ["a"], {"k": 1}
+    lg = StatsLogger(cfg, None, exp_config={"lr": 0.1})
+    lg.commit(0, 0, 0, {"loss": 1.0})
+    lg.close()
+    i = calls["init"]
+    assert i["id"] == "exp_t1_train" and i["resume"] == "allow" and i["job_type"] == "rl" and i["tags"] == ["a"] and i["config"] == {"k": 1, "lr": 0.1}
+    assert i["group"] == "exp_t1" and os.environ["WANDB_BASE_URL"] == "http://wb.local" and calls["log"] == [({"loss": 1.0}, 0)] and calls["finished"]
