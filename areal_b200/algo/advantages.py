@@ -159,7 +159,7 @@ class AdvantageComputer:
             lengths = torch.tensor([len(set(r[r >= 0].tolist())) for r in tid], device=loss_mask.device)
         else:
             lengths = loss_mask.sum(-1).long()
-        return self.gae_lambda_fn(lengths)
+        return self.gae_lambda_fn(lengths, **dict(getattr(self.config, "gae_lambda_kwargs", None) or {}))
 
     @torch.no_grad()
     def __call__(self, data: dict[str, Any], group_sizes: Optional[list[int]] = None) -> dict[str, Any]:

@@ -127,7 +127,6 @@ class FSDPEngineConfig:
     reshard_after_forward: bool = True
     shard_parameters: bool = False           # ZeRO-3: weights and gradients sharded too, decoder layers gathered one at a time (for models that do not fit replicated)
     fuse_reduce_scatter_adamw: bool = True   # fused RS + cast/scale + sharded AdamW kernel
-    fuse_allgather_gemm: bool = True         # param all-gather fused into the consuming GEMM
     fuse_ulysses_projections: bool = True    # sequence-parallel all-to-alls folded into the QKV / output projection kernels
     tp_sequence_parallel: bool = False       # tensor parallel with the residual stream split by rows (gather -> GEMM, GEMM -> reduce-scatter)
     fuse_tp_projections: bool = True         # ... those pairs as one peer-memory kernel each on CUDA
@@ -136,7 +135,7 @@ class FSDPEngineConfig:
     bucket_mb: int = 256
     per_layer_optim_step: bool = False        # accepted for compatibility (the flat sharded optimizer steps once)
     optim_step_prefetch_layers: int = 1
-    shard_vision_across_sp: bool = False
+    shard_vision_across_sp: bool = True       # Ulysses + image tower: each rank encodes its share of the pictures (False: every rank encodes all of them)
 
 
 @dataclass
@@ -146,7 +145,6 @@ class FP8Config:
     enabled: bool = False
     include_experts: bool = True
     include_dense: bool = False
-    pow2_scales: bool = True  # UE8M0-style power-of-two scales
 
 
 @dataclass
@@ -327,9 +325,6 @@ class PPOActorConfig(TrainEngineConfig):
     log_agent_stats: bool = False
     log_agent_stats_keys: list[str] = field(default_factory=list)
     max_new_tokens: int = 1024
-    dynamic_sampling: bool = False
-    distill_beta: float = 0.0
-    distill_rl_weight: float = 1.0
 
     def __post_init__(self):
         if self.c_clip is not None and self.c_clip <= 1.0:

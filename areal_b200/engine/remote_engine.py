@@ -329,6 +329,9 @@ class RemoteInfEngine(InferenceEngine):
     def pause_generation(self):
         self._paused.set()
         self._fanout(self.backend.pause_endpoint)
+        grace = float(getattr(self.config, "pause_grace_period", 0.0) or 0.0)
+        if grace > 0:
+            time.sleep(grace)          # lets requests that were already on their way to a server reach it and be aborted there
 
     def continue_generation(self):
         self._fanout(self.backend.continue_endpoint)

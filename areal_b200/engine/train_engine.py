@@ -566,7 +566,8 @@ class B200TrainEngine(TrainEngine):
 
             install_ulysses(self.model, self._sp_group, self.sp_size, self.sp_rank)
             if model_config.is_vlm:
-                self.model.vision_sp = (self._sp_group, self.sp_size, self.sp_rank)    # pictures split over the group too
+                if getattr(cfg.fsdp, "shard_vision_across_sp", True):
+                    self.model.vision_sp = (self._sp_group, self.sp_size, self.sp_rank)    # pictures split over the group too
             self._sp_fused = None
             mc = model_config
             if (on_gpu and cfg.fsdp.fuse_ulysses_projections and not self.use_lora and tp == 1 and self.sp_size <= 8 and not getattr(mc, "is_hybrid", False) and not mc.is_vlm

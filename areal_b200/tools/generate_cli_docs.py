@@ -4,7 +4,8 @@
     python -m areal_b200.tools.generate_cli_docs --check    # exit 1 when the committed file is out of date
 
 One section per dataclass (alphabetical), one table row per field with its type and default; the trailing comment
-of a field's line in the source becomes its note. Reference: ``docs/generate_cli_docs.py`` of the reference, which
+of a field's line in the source becomes its note; a field whose name occurs nowhere else in the package is marked as
+accepted for compatibility only. Reference: ``docs/generate_cli_docs.py`` of the reference, which
 renders its ``cli_args.py`` the same way."""
 from __future__ import annotations
 
@@ -64,8 +65,36 @@ def _notes(cls) -> dict[str, str]:
     return out
 
 
+COMPAT_NOTE = "accepted so that configuration files of the reference load unchanged; not read by this implementation"
+
+
+def _package_text() -> str:
+    """All source text of the package (and the benchmark entry point) except the configuration module itself."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    chunks = []
+    for dp, dns, fs in os.walk(root):
+        dns[:] = sorted(d for d in dns if d != "__pycache__")
+        for f in sorted(fs):
+            if f.endswith(".py") and not (dp.endswith(os.sep + "api") and f == "cli_args.py"):
+                with open(os.path.join(dp, f)) as fh:
+                    chunks.append(fh.read())
+    bench = os.path.join(os.path.dirname(root), "bench.py")
+    if os.path.exists(bench):
+        with open(bench) as fh:
+            chunks.append(fh.read())
+    return "\n".join(chunks)
+
+
 def render() -> str:
     from ..api import cli_args as C
+
+    text = _package_text()
+    used_cache: dict[str, bool] = {}
+
+    def used(name: str) -> bool:
+        if name not in used_cache:
+            used_cache[name] = re.search(r"\b%s\b" % re.escape(name), text) is not None
+        return used_cache[name]
 
     classes = sorted((c for _, c in inspect.getmembers(C, inspect.isclass)
                       if dataclasses.is_dataclass(c) and c.__module__ == C.__name__ and not c.__name__.startswith("_")),
@@ -83,8 +112,12 @@ def render() -> str:
         except Exception:
             pass
         parts.append("| field | type | default | note |\n|---|---|---|---|\n")
+        passthrough = cls.__name__ in ("SGLangConfig", "vLLMConfig")       # every field becomes a flag of the external server's command line
         for f in dataclasses.fields(cls):
-            parts.append(f"| `{f.name}` | `{_type_name(hints.get(f.name, f.type))}` | `{_default(f)}` | {notes.get(f.name, '')} |\n")
+            note = notes.get(f.name, "")
+            if not passthrough and not dataclasses.is_dataclass(f.type) and not used(f.name):
+                note = (note + "; " if note else "") + COMPAT_NOTE
+            parts.append(f"| `{f.name}` | `{_type_name(hints.get(f.name, f.type))}` | `{_default(f)}` | {note} |\n")
     return "".join(parts)
 
 

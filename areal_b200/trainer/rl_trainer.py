@@ -234,6 +234,9 @@ class PPOTrainer:
         if max_steps is not None:
             total = min(total, self.start_step + max_steps)
         history = []
+        if self.start_step == 0 and self.valid_dataloader is not None and eval_workflow is not None:
+            # ``evaluator.eval_before_train``: the initial policy's score, before any update
+            self.evaluator.evaluate(lambda: self._evaluate(eval_workflow, eval_workflow_kwargs), 0, -1, -1)
         for global_step in range(self.start_step, total):
             t_step = time.perf_counter()
             epoch, step = divmod(global_step, steps_per_epoch)

@@ -12,6 +12,9 @@ class Evaluator:
         self.freq_ctl = EpochStepTimeFreqCtl(config.freq_epochs, config.freq_steps, config.freq_secs)
 
     def evaluate(self, evaluate_fn: Callable, epoch: int, step: int, global_step: int):
+        if global_step < 0:
+            # the call before the first training step: only with ``eval_before_train`` (a baseline of the initial policy)
+            return evaluate_fn() if getattr(self.config, "eval_before_train", False) else None
         steps_per_epoch = self.ft_spec.steps_per_epoch if self.ft_spec is not None else 1 << 30
         if not self.freq_ctl.check(epochs=int(step == steps_per_epoch - 1), steps=1):
             return None

@@ -34,8 +34,11 @@ class PerfTracer:
         self._lock = threading.Lock()
         self._t0 = time.perf_counter()
         self._device_events: list[tuple] = []
-        self.session_tracer = SessionTracer(config, rank) if self.enabled and getattr(config, "session_tracer", None) and \
-            config.session_tracer.enabled else None
+        self.session_tracer = None
+        if self.enabled and getattr(config, "session_tracer", None) and config.session_tracer.enabled:
+            d = self._out_dir()
+            os.makedirs(d, exist_ok=True)
+            self.session_tracer = SessionTracer(config.session_tracer, rank, out_dir=d)
         self._save_interval = max(1, getattr(config, "save_interval", 1)) if config is not None else 1
         self.profile_steps = self._normalize_profile_steps(getattr(config, "profile_steps", None) if config is not None else None)
         self.current_step: Optional[int] = None
@@ -225,8 +228,12 @@ class PerfTracer:
 class SessionTracer:
     """Lifecycle of rollout sessions: phases with wall-clock stamps and a final status."""
 
-    def __init__(self, config=None, rank: int = 0):
+    def __init__(self, config=None, rank: int = 0, out_dir: Optional[str] = None):
         self.rank = rank
+        # finished sessions are written out once this many are waiting (``session_tracer.flush_threshold``), not only at
+        # the periodic save: a long run keeps a bounded list in memory
+        self.flush_threshold = max(1, int(getattr(config, "flush_threshold", 256) or 256))
+        self.out_dir = out_dir
         self._sessions: dict[Any, dict] = {}
         self._done: list[dict] = []
         self._lock = threading.Lock()
@@ -251,6 +258,9 @@ class SessionTracer:
             if s is not None:
                 s["status"], s["end_ts"] = status, time.time()
                 self._done.append(s)
+            pending = len(self._done)
+        if self.out_dir is not None and pending >= self.flush_threshold:
+            self.flush(self.out_dir)
 
     def flush(self, out_dir: str):
         with self._lock:

@@ -213,3 +213,51 @@ def test_num_params_matches_the_built_model(name):
 def test_published_sizes_are_in_the_right_ballpark():
     assert 7.5e9 < preset("qwen3-8b").num_params() < 8.5e9
     assert 1.4e9 < preset("qwen2.5-1.5b").num_params() < 1.9e9
+
+
+def test_small_config_switches_take_effect(tmp_path):
+    """Fields that used to be accepted and ignored: evaluation before training, extra arguments of a custom lambda
+    schedule, the session tracer's flush threshold, the pause grace period."""
+    import json
+    import os
+    import time
+    import types
+
+    import torch
+
+    from areal_b200.api.cli_args import EvaluatorConfig, InferenceEngineConfig, PPOActorConfig, SessionTracerConfig
+    from areal_b200.algo.advantages import AdvantageComputer
+    from areal_b200.engine.remote_engine import RemoteInfEngine
+    from areal_b200.utils.evaluator import Evaluator
+    from areal_b200.utils.perf_tracer import SessionTracer
+
+    calls = []
+    ev = Evaluator(EvaluatorConfig(freq_steps=100, eval_before_train=True))
+    assert ev.evaluate(lambda: calls.append("pre") or 1, 0, -1, -1) == 1 and calls == ["pre"]
+    assert Evaluator(EvaluatorConfig(freq_steps=100)).evaluate(lambda: calls.append("no"), 0, -1, -1) is None and calls == ["pre"]
+    # a custom lambda schedule gets its configured keyword arguments
+    mod = types.ModuleType("my_lambda_mod")
+    mod.fn = lambda lengths, floor=0.0, scale=1.0: torch.full((lengths.numel(),), floor + scale)
+    import sys
+
+    sys.modules["my_lambda_mod"] = mod
+    cfg = PPOActorConfig(gae_lambda="my_lambda_mod.fn", gae_lambda_kwargs={"floor": 0.5, "scale": 0.25})
+    pipe = AdvantageComputer(cfg)
+    lam = pipe._lambda(torch.ones(3, 4, dtype=torch.bool), torch.zeros(3, 4, dtype=torch.long))
+    assert torch.allclose(lam, torch.full((3,), 0.75))
+    # finished sessions reach the file as soon as the threshold is met
+    st = SessionTracer(SessionTracerConfig(enabled=True, flush_threshold=2), rank=0, out_dir=str(tmp_path))
+    a, b, c = st.register(1), st.register(2), st.register(3)
+    st.finish(a, "accepted")
+    assert not os.path.exists(tmp_path / "sessions.jsonl")
+    st.finish(b, "rejected")
+    rows = [json.loads(l) for l in open(tmp_path / "sessions.jsonl")]
+    assert [r["status"] for r in rows] == ["accepted", "rejected"] and st._done == []
+    st.finish(c, "accepted")
+    assert len(st._done) == 1
+    # the grace period after pausing
+    eng = RemoteInfEngine(InferenceEngineConfig(pause_grace_period=0.3), [])
+    t0 = time.time()
+    eng.pause_generation()
+    assert time.time() - t0 >= 0.3
+    eng.continue_generation()
