@@ -115,16 +115,21 @@ class GroupedRolloutWorkflow(RolloutWorkflow):
     Reference: ``areal/infra/remote_inf_engine.py:70-206``; the two switches are ``gconfig.drop_incomplete_group`` and
     ``gconfig.reward_normalization`` (see :meth:`from_gconfig`)."""
 
-    def __init__(self, workflow: RolloutWorkflow, group_size: int, reward_normalization: bool = False, drop_incomplete_group: bool = False):
+    def __init__(self, workflow: RolloutWorkflow, group_size: int, reward_normalization: bool = False, drop_incomplete_group: bool = False,
+                 serialize_group_samples: bool = False):
+        """``serialize_group_samples``: the episodes of a group run one after another instead of concurrently (an agent
+        whose tools hold per-prompt state, or a server whose prefix cache should see the first sample finish before
+        the others start; ``rollout.serialize_group_samples``)."""
         if group_size < 1:
             raise ValueError(f"group_size must be >= 1, got {group_size}")
         self.workflow, self.group_size = workflow, group_size
         self.reward_normalization, self.drop_incomplete_group = reward_normalization, drop_incomplete_group
+        self.serialize_group_samples = serialize_group_samples
 
     @classmethod
-    def from_gconfig(cls, workflow: RolloutWorkflow, gconfig: GenerationHyperparameters) -> "GroupedRolloutWorkflow":
+    def from_gconfig(cls, workflow: RolloutWorkflow, gconfig: GenerationHyperparameters, rollout_config=None) -> "GroupedRolloutWorkflow":
         return cls(workflow, max(1, gconfig.n_samples), bool(getattr(gconfig, "reward_normalization", False)),
-                   bool(getattr(gconfig, "drop_incomplete_group", False)))
+                   bool(getattr(gconfig, "drop_incomplete_group", False)), bool(getattr(rollout_config, "serialize_group_samples", False)))
 
     async def arun_episode(self, engine, data):
         parent = wctx.get()
@@ -133,7 +138,10 @@ class GroupedRolloutWorkflow(RolloutWorkflow):
             with wctx.scoped(is_eval=parent.is_eval, task_id=parent.task_id, sample_idx=i):
                 return await self.workflow.arun_episode(engine, data)
 
-        res = await asyncio.gather(*[one(i) for i in range(self.group_size)])
+        if self.serialize_group_samples:
+            res = [await one(i) for i in range(self.group_size)]
+        else:
+            res = await asyncio.gather(*[one(i) for i in range(self.group_size)])
         ok = [r for r in res if r is not None]
         if not ok:
             return None

@@ -209,3 +209,19 @@ def test_grouped_workflow_drops_or_keeps_incomplete_groups_and_normalises_reward
     assert (w.group_size, w.drop_incomplete_group, w.reward_normalization) == (3, True, False)
     with pytest.raises(ValueError):
         GroupedRolloutWorkflow(Inner([]), 0)
+    # serial groups start their samples strictly in order
+    order = []
+
+    class Slow(RolloutWorkflow):
+        async def arun_episode(self, engine, data):
+            i = wctx.get().sample_idx
+            order.append(("start", i))
+            await asyncio.sleep(0.01 * (3 - i))
+            order.append(("end", i))
+            return dict(input_ids=torch.tensor([[1]]), attention_mask=torch.ones(1, 1, dtype=torch.bool), loss_mask=torch.tensor([[1]]), rewards=torch.tensor([0.0]))
+
+    asyncio.run(GroupedRolloutWorkflow(Slow(), 3, serialize_group_samples=True).arun_episode(None, {}))
+    assert order == [("start", 0), ("end", 0), ("start", 1), ("end", 1), ("start", 2), ("end", 2)]
+    order.clear()
+    asyncio.run(GroupedRolloutWorkflow(Slow(), 3).arun_episode(None, {}))
+    assert [o for o in order if o[0] == "start"] == [("start", 0), ("start", 1), ("start", 2)] and order[3] == ("end", 2)
