@@ -485,7 +485,9 @@ class NativeInferenceEngine(InferenceEngine):
                        min_new=max(0, g.min_new_tokens - len(out_tok)), temperature=0.0 if g.greedy else g.temperature,
                        greedy=bool(g.greedy) or g.temperature == 0.0,
                        stop_ids=set(g.stop_token_ids or []), ignore_eos=g.ignore_eos,
-                       seed=(g.seed if g.seed is not None else zlib.crc32(req.rid.encode())) & 0x7FFFFFFF, future=(loop, fut),
+                       # a request without its own seed: its id hashed with the engine's seed (``native_infer.random_seed``)
+                       seed=(g.seed if g.seed is not None else zlib.crc32(req.rid.encode()) ^ (int(self.icfg.random_seed) * 0x9E3779B1)) & 0x7FFFFFFF,
+                       future=(loop, fut),
                        t_submit=time.perf_counter(), top_p=g.top_p, top_k=0 if g.top_k >= 10 ** 7 else int(g.top_k),
                        mm=mm, rope_delta=rope_delta, stop_strs=tuple(g.stop or ()), tokenizer=getattr(req, "tokenizer", None),
                        stop_window=max(8, 2 * max((len(x) for x in (g.stop or [""])), default=0)))
