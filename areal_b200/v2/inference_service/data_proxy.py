@@ -91,6 +91,42 @@ class DataProxy:
                 return SSE(list(chat_completion_chunks(comp)) + ["[DONE]"])
             return comp.to_dict()
 
+        @svc.route("POST", "/v1/messages")
+        def messages(body, ctx):
+            # Anthropic Messages shape over the same recorded chat call (system prompt, content blocks, tools translated both ways)
+            from ...openai.proxy import anthropic_message_events, anthropic_to_openai, openai_to_anthropic
+            from ..common import SSE
+
+            s = self._get(ctx.api_key)
+            kw = {k: v for k, v in anthropic_to_openai(body).items() if v is not None}
+            msg = openai_to_anthropic(self._run(s.client.chat.completions.create(**kw)))
+            return SSE(list(anthropic_message_events(msg))) if body.get("stream") else msg
+
+        @svc.route("POST", "/v1/responses")
+        def responses(body, ctx):
+            s = self._get(ctx.api_key)
+            kw = {k: body[k] for k in ("input", "instructions", "model", "max_output_tokens", "temperature", "top_p", "tools") if k in body}
+            r = self._run(s.client.responses.create(**kw))
+            u = r.usage
+            return {"id": r.id, "object": "response", "created_at": r.created_at, "model": r.model, "status": "completed", "output": r.output,
+                    "output_text": r.output_text, "usage": {"input_tokens": u.prompt_tokens, "output_tokens": u.completion_tokens,
+                                                            "total_tokens": u.total_tokens}}
+
+        # tokenizer service: agents and evaluators that count or cut tokens use the policy's own tokenizer without
+        # loading it (reference: areal/v2/inference_service/data_proxy/tokenizer_proxy.py)
+        @svc.route("POST", "/tokenize")
+        def tokenize(body, ctx):
+            if "messages" in body:
+                ids = self.tokenizer.apply_chat_template(body["messages"], tokenize=True, add_generation_prompt=bool(body.get("add_generation_prompt", True)))
+            else:
+                ids = self.tokenizer.encode(body["text"])
+            ids = [int(i) for i in ids]
+            return {"input_ids": ids, "count": len(ids)}
+
+        @svc.route("POST", "/detokenize")
+        def detokenize(body, ctx):
+            return {"text": self.tokenizer.decode([int(i) for i in body["input_ids"]])}
+
         @svc.route("POST", "/rl/set_reward")
         def set_reward(body, ctx):
             s = self._get(ctx.api_key)

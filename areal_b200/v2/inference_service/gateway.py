@@ -56,6 +56,18 @@ class Gateway:
         svc.route("POST", "/v1/chat/completions")(forward("/chat/completions"))
         svc.route("POST", "/chat/completions")(forward("/chat/completions"))
         svc.route("POST", "/rl/set_reward")(forward("/rl/set_reward"))
+        svc.route("POST", "/v1/messages")(forward("/v1/messages"))
+        svc.route("POST", "/v1/responses")(forward("/v1/responses"))
+
+        def any_worker(path):
+            def fn(body, ctx):
+                ws = self._workers()
+                if not ws:
+                    raise HTTPError(503, "no inference worker registered")
+                return call(f"http://{ws[0]}{path}", body)
+            return fn
+        svc.route("POST", "/tokenize")(any_worker("/tokenize"))
+        svc.route("POST", "/detokenize")(any_worker("/detokenize"))
 
         @svc.route("POST", "/rl/end_session")
         def end(body, ctx):

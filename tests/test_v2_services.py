@@ -506,3 +506,30 @@ def test_training_gateway_dispatches_by_topology_and_heads_answer(tmp_path):
                 w.stop()
             except Exception:
                 pass
+
+
+def test_inference_service_serves_messages_responses_and_the_tokenizer():
+    """Anthropic Messages and Responses shapes through the gateway land in the same recorded session as chat
+    completions; the tokenizer routes answer with the policy's own tokenizer."""
+    from areal_b200.v2.common import sse_lines
+
+    engines = [CtlEngine(["alpha", "beta", "gamma"])]
+    ctl = InferenceServiceController(admin_key="adm").start(engines, ByteTok(), GenerationHyperparameters(max_new_tokens=16))
+    try:
+        s = ctl.start_session("t")
+        root = ctl.gateway.svc.url
+        m = call(f"{root}/v1/messages", {"system": "be brief", "max_tokens": 8, "messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}]},
+                 api_key=s["api_key"])
+        assert m["type"] == "message" and m["content"][0]["text"] == "alpha" and m["stop_reason"] == "end_turn"
+        r = call(f"{root}/v1/responses", {"input": "and again", "max_output_tokens": 8}, api_key=s["api_key"])
+        assert r["object"] == "response" and r["output_text"] == "beta" and r["usage"]["output_tokens"] > 0
+        evs = list(sse_lines(f"{root}/v1/messages", {"max_tokens": 8, "stream": True, "messages": [{"role": "user", "content": "more"}]}, api_key=s["api_key"]))
+        kinds = [e for e, _ in evs]
+        assert kinds[0] == "message_start" and kinds[-1] == "message_stop" and "content_block_delta" in kinds
+        t = call(f"{root}/tokenize", {"text": "abc"})
+        assert t == {"input_ids": [97, 98, 99], "count": 3} and call(f"{root}/detokenize", {"input_ids": [97, 98]}) == {"text": "ab"}
+        call(f"{root}/rl/set_reward", {"reward": 1.0}, api_key=s["api_key"])
+        call(f"{root}/rl/end_session", {}, api_key=s["api_key"])
+        assert ctl.export_batch(style="individual", discount=1.0)["input_ids"].shape[0] == 3          # three recorded model calls
+    finally:
+        ctl.stop()
