@@ -67,6 +67,18 @@ def main():
             assert err < (0.08 if use_cuda else 2e-3), f"{name}: grad mismatch for {n}: {err}"
         if rank == 0:
             print(f"{name}: loss {l_full.item():.5f} vs {l_tp.item():.5f}, worst grad rel err {worst:.2e}", flush=True)
+    # row shares of a tensor that every rank holds, with a row count the group does not divide (7 rows over the ranks):
+    # slice -> per-share function -> gather equals the function of the whole, forward and backward
+    if not use_cuda:
+        torch.manual_seed(3)
+        x = torch.randn(7, 5, requires_grad=True)
+        w = torch.randn(5, 5)
+        y = TP._GatherRows.apply(torch.tanh(TP._SliceRows.apply(x, dist.group.WORLD, world, rank) @ w), dist.group.WORLD, world, rank, 7)
+        (y * torch.arange(7.0)[:, None]).sum().backward()
+        x2 = x.detach().clone().requires_grad_(True)
+        y2 = torch.tanh(x2 @ w)
+        (y2 * torch.arange(7.0)[:, None]).sum().backward()
+        assert y.shape == (7, 5) and torch.allclose(y, y2, atol=1e-6) and torch.allclose(x.grad, x2.grad, atol=1e-6)
     print("TP_OK", flush=True)
     dist.destroy_process_group()
 
