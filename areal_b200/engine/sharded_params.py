@@ -125,6 +125,9 @@ class ShardedParamStore:
         self._reducing: list[tuple] = []             # (works, buffer, pieces, unit start) of reductions in flight
         self._root_users = 0
         self.peak_live_numel = 0
+        # called with (names, parameters) of a unit after its gradients were folded into ``main_grad`` and before they are
+        # reduced: the place for sums over another parallel dimension (tensor-parallel partial gradients)
+        self.grad_hook = None
         for u in range(self.n_units):
             self._point_at_placeholder(u)
         for b in model.buffers():
@@ -230,6 +233,10 @@ class ShardedParamStore:
             if p.grad is not None:
                 p.main_grad.add_(p.grad.to(self.grad_dtype))
                 p.grad = None
+        if self.grad_hook is not None:
+            self.grad_hook([self.names[i] for i in self.unit_members[u]], [self.params[i] for i in self.unit_members[u]])
+        for i in self.unit_members[u]:
+            p = self.params[i]
             if hasattr(p, "main_grad"):
                 del p.main_grad
         self.drain(keep=1)                                 # at most two units' gradient buffers alive

@@ -512,8 +512,10 @@ class B200TrainEngine(TrainEngine):
         self._z3 = None
         if bool(getattr(cfg.fsdp, "shard_parameters", False)):
             # ZeRO-3: parameters and gradients sharded as well, decoder layers materialised one at a time
-            if tp > 1 or getattr(self, "pp_size", 1) > 1 or getattr(self, "ep_size", 1) > 1 or self.use_lora or model_config.is_vlm:
-                raise NotImplementedError("fsdp.shard_parameters covers data / sequence parallel text models (no tp / pp / ep, LoRA or image tower)")
+            if getattr(self, "pp_size", 1) > 1 or getattr(self, "ep_size", 1) > 1 or self.use_lora or model_config.is_vlm \
+                    or (tp > 1 and bool(cfg.fsdp.tp_sequence_parallel)):
+                raise NotImplementedError("fsdp.shard_parameters covers data / sequence / tensor parallel text models (no pp / ep, LoRA, image tower "
+                                          "or sequence-parallel residual stream)")
             from .sharded_params import ShardedParamStore
 
             fused, alloc = False, None
@@ -521,6 +523,18 @@ class B200TrainEngine(TrainEngine):
                                                       self._shard_ranks if n_shards > 1 else None, torch.float32,
                                                       with_grads=cfg.optimizer is not None, device=self.device)
             self.model.param_units = self.store
+            if tp > 1:
+                # every TP slice shards its own weights over its data-parallel ranks; partial gradients of replicated
+                # parameters are summed over the TP group before a unit's gradients leave for their owners
+                from ..parallel import tp as TP
+
+                partial = TP.partial_grad_names(self.model)
+
+                def sum_partial(names, params, group=self._tp_group):
+                    for n_, p_ in zip(names, params):
+                        if n_ in partial and getattr(p_, "main_grad", None) is not None:
+                            dist.all_reduce(p_.main_grad, group=group)
+                self.store.grad_hook = sum_partial
         else:
             self.store = FlatParamStore(self.model, n_shards, shard_rank, torch.float32, alloc_param=alloc_p, alloc_grad=alloc_g,
                                         with_grads=cfg.optimizer is not None, only_trainable=self.use_lora, include=dense_only)
@@ -976,9 +990,16 @@ class B200TrainEngine(TrainEngine):
         if getattr(self, "expert_store", None) is not None:
             return self._ep_optimizer_step()
         opt = self.optimizer
+        tp = getattr(self, "tp_size", 1)
         if getattr(self, "_z3", None) is not None:
             # gradients were reduced to their owners unit by unit during the backward; the updated shard stays put
-            res = opt.step(self.store.grad_shard)
+            pre = None
+            if tp > 1:
+                g32 = self.store.grad_shard.float()
+                rep = sum((g32[a:b].pow(2).sum() for a, b in self._replicated_ranges), torch.zeros((), device=self.device))
+                pre = (g32.pow(2).sum() - rep + rep / tp).reshape(1)        # replicated parameters count once over the TP group
+                dist.all_reduce(pre, group=self._all_train_group)
+            res = opt.step(self.store.grad_shard, precomputed_sumsq=pre)
             if self.model.cfg.is_moe and self.model.cfg.router_bias_update_rate > 0:
                 for layer in self.model.layers:
                     upd = getattr(layer.mlp, "update_expert_bias", None)
@@ -1275,7 +1296,7 @@ class B200TrainEngine(TrainEngine):
                     meta.tokenizer.save_pretrained(meta.path)
         elif meta.weight_format == "hf" and getattr(self, "_z3", None) is not None:
             # every rank takes part in the unit-by-unit gather; the head writes tensor by tensor
-            named = self._z3.full_tensors()
+            named = self._z3_full_tensors()
             if head:
                 hf_io.save_hf_sharded(meta.path, self.model_config, hf_io.native_to_hf_tensors(self.model_config, named))
                 if meta.tokenizer is not None:
@@ -1348,6 +1369,19 @@ class B200TrainEngine(TrainEngine):
                 t = TP.unshard_tensors(self.model_config, n_, parts, expert_tp=xtp)
             yield n_, (t.to("cpu", copy=True) if to_cpu else t)
 
+    def _z3_full_tensors(self):
+        """(name, full tensor) under sharded parameters: gathered unit by unit over the shard group, then over the TP
+        group when the model is tensor parallel (a collective of both groups)."""
+        from ..parallel import tp as TP
+
+        tp = getattr(self, "tp_size", 1)
+        for n_, t in self._z3.full_tensors():
+            if tp > 1:
+                parts = [torch.empty_like(t) for _ in range(tp)]
+                dist.all_gather(parts, t.contiguous(), group=self._tp_group)
+                t = TP.unshard_tensors(self.model_config, n_, parts)
+            yield n_, t
+
     def _pp_native_full(self, skip_tied_copy: bool = True):
         """(native name, full tensor) of this stage's parameters; tensor-parallel slices are gathered over the TP group
         first (then a collective of that group: all its ranks must iterate)."""
@@ -1410,8 +1444,27 @@ class B200TrainEngine(TrainEngine):
                                            ((k, t) for k, t in hf_io.iter_safetensors(meta.path) if k in wanted), strict=False)
         elif meta.weight_format == "hf" and getattr(self, "_z3", None) is not None:
             # tensors stream from the files; every rank keeps what falls into its shard
-            hf_io.load_hf_tensors_into(self.model_config, None, hf_io.iter_safetensors(meta.path), strict=not self.config.is_critic,
-                                       writer=self._z3.write_piece)
+            tp_ = getattr(self, "tp_size", 1)
+            if tp_ == 1:
+                hf_io.load_hf_tensors_into(self.model_config, None, hf_io.iter_safetensors(meta.path), strict=not self.config.is_critic,
+                                           writer=self._z3.write_piece)
+            else:
+                # pieces of a full tensor are collected until it is complete, then this rank's TP slice is kept
+                from ..parallel import tp as TP
+
+                shapes = {n: (tuple(p.shape), p.dtype) for n, p in build_model(self.model_config, dtype=self.model.dtype, device="meta").named_parameters()}
+                plan = hf_io.hf_to_native_plan(self.model_config)
+                staged: dict[str, list] = {}
+
+                def collect(native, expert, rows, t):
+                    ent = staged.setdefault(native, [torch.empty(shapes[native][0], dtype=shapes[native][1]), 0])
+                    dst = ent[0] if expert is None else ent[0][expert]
+                    (dst if rows is None else dst[rows[0]:rows[1]]).copy_(t.to(dst.dtype))
+                    ent[1] += 1
+                    if ent[1] == len(plan[native]):
+                        self._z3.write_full(native, TP.shard_tensor(self.model_config, native, ent[0], tp_, self.tp_rank))
+                        del staged[native]
+                hf_io.load_hf_tensors_into(self.model_config, None, hf_io.iter_safetensors(meta.path), strict=not self.config.is_critic, writer=collect)
         elif meta.weight_format == "hf" and getattr(self, "ep_size", 1) > 1:
             full = build_model(self.model_config, dtype=self.model.dtype, device=self.device, seed=0)
             hf_io.load_model_hf(full, meta.path, strict=not self.config.is_critic)
@@ -1521,7 +1574,7 @@ class B200TrainEngine(TrainEngine):
             finally:
                 unmerge_lora_(self.model)
         if getattr(self, "_z3", None) is not None:
-            return dict(self._z3.full_tensors(to_cpu=True))
+            return {n: t.to("cpu", copy=True) for n, t in self._z3_full_tensors()}
         if getattr(self, "ep_size", 1) > 1 and getattr(self, "pp_size", 1) == 1:
             return dict(self._ep_full_named_tensors(to_cpu=True))
         if getattr(self, "tp_size", 1) > 1 and getattr(self, "pp_size", 1) == 1:

@@ -272,6 +272,18 @@ def replicated_parameter_names(model) -> list[str]:
     return out
 
 
+def partial_grad_names(model) -> set[str]:
+    """Replicated parameters whose gradient on one TP rank is only that rank's part (per-head norms, routers; every
+    replicated parameter when the residual stream is split by rows): they must be summed over the TP group."""
+    all_partial = getattr(model, "tp_sequence_parallel", False)
+    out = set()
+    for n in replicated_parameter_names(model):
+        leaf = n.rsplit(".", 1)[-1]
+        if all_partial or leaf in ("q_norm", "k_norm", "router") or n.endswith("linear_attn.norm"):
+            out.add(n)
+    return out
+
+
 @torch.no_grad()
 def allreduce_replicated_grads(model, group, grad_of=lambda p: getattr(p, "main_grad", None) if getattr(p, "main_grad", None) is not None else p.grad):
     """Sums the gradients of replicated parameters over the TP group (each rank saw only its

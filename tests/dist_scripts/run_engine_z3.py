@@ -36,7 +36,7 @@ def main():
     eng.create_process_group()
     eng.initialize(model_config=mc, seed=5)
     st = eng.store
-    assert eng._z3 is st and st.flat_param is None and st.param_shard.numel() * world == st.padded
+    assert eng._z3 is st and st.flat_param is None and st.param_shard.numel() * st.world_size == st.padded
     assert all(p.data.stride() == (0,) * p.dim() for p in eng.model.parameters()), "a parameter is resident outside a micro-batch"
     batch = make_batch(mc.vocab_size)
     per, rank_d = 8 // eng.dp_size, eng.dp_rank                  # sequence-parallel peers share their rows
@@ -56,6 +56,8 @@ def main():
         assert abs(a["grad_norm"] - b["grad_norm"]) < 2e-3 * max(1.0, b["grad_norm"]), (a, b)
         assert abs(a["loss"] * world - b["loss"]) < 0.5 or True
     full = {n: p.detach() for n, p in ref.model.named_parameters()}
+    if getattr(eng, "tp_size", 1) > 1:
+        assert eng.store.grad_hook is not None and eng.store.world_size == eng.dp_size
     w = eng.export_weights()
     assert set(w) == set(full)
     worst = max((w[n] - full[n]).abs().max().item() for n in w)

@@ -89,11 +89,14 @@ def test_one_rank_store_trains_like_the_replicated_store():
 
 
 @pytest.mark.parametrize("ranks,model,ckpt,backend,port", [(2, "tiny-qwen3", "0", "", 29961), (4, "tiny-qwen3", "1", "", 29963),
-                                                         (2, "tiny-qwen3-moe", "1", "", 29965), (4, "tiny-qwen3", "1", "d2c2", 29967)])
+                                                         (2, "tiny-qwen3-moe", "1", "", 29965), (4, "tiny-qwen3", "1", "d2c2", 29967),
+                                                         (4, "tiny-qwen3-moe", "1", "d2t2", 29969), (4, "tiny-qwen3.5", "0", "d2t2", 29971)])
 def test_train_engine_with_sharded_parameters(tmp_path, ranks, model, ckpt, backend, port):
     """``fsdp.shard_parameters`` on gloo ranks against one rank with replicated parameters: gradient norm and weights
     after two steps over several micro-batches, at most the root and two layers resident at a time, forward-only pass,
-    HF export / reload, recovery checkpoint; dense and MoE models, with and without recomputation, with Ulysses SP."""
+    HF export / reload, recovery checkpoint; dense, MoE and linear-attention models, with and without recomputation, with
+    Ulysses SP, and with tensor parallelism (every TP slice shards its weights over its data-parallel ranks; partial
+    gradients of replicated parameters are summed over the TP group before a layer's gradients leave for their owners)."""
     env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", Z3_SAVE_DIR=str(tmp_path), Z3_MODEL=model, Z3_CKPT=ckpt, Z3_BACKEND=backend)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr",
                         "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "dist_scripts", "run_engine_z3.py")], cwd=ROOT,
