@@ -346,6 +346,7 @@ class HybridDecoderLayer(nn.Module):
     """Drop-in for ``DecoderLayer`` (same call signature) with the token mixer chosen per layer."""
 
     tp_group = None
+    moe_row_share = None     # (group, tp, rank), see DecoderLayer
 
     def __init__(self, cfg: ModelConfig, idx: int, dtype, device):
         super().__init__()
@@ -378,6 +379,10 @@ class HybridDecoderLayer(nn.Module):
             x = copy_to_tp(x, g)
             h = reduce_from_tp(self.linear_attn(x, pb) if self.is_linear else self.self_attn(x, pb, cos, sin, attn_fn), g)
             x, resid = rmsnorm_offset(h, self.post_attention_layernorm, eps, resid)
+            if self.moe_row_share is not None:     # whole experts: each TP rank routes its own share of the rows
+                from ..parallel.tp import moe_on_row_share
+
+                return moe_on_row_share(self.mlp, x, *self.moe_row_share), resid
             return reduce_from_tp(self.mlp(copy_to_tp(x, g)), g), resid
         h = self.linear_attn(x, pb) if self.is_linear else self.self_attn(x, pb, cos, sin, attn_fn)
         x, resid = rmsnorm_offset(h, self.post_attention_layernorm, eps, resid)

@@ -30,8 +30,6 @@ def local_config(cfg: ModelConfig, tp: int, expert_tp: bool = True) -> ModelConf
     over an expert-parallel group instead; attention and dense MLPs are still sliced)."""
     if tp == 1:
         return cfg
-    if getattr(cfg, "shared_expert_intermediate_size", 0):
-        raise NotImplementedError("tensor parallelism for models with a shared expert (use expert / data parallelism)")
     if cfg.num_heads % tp:
         raise ValueError(f"num_heads={cfg.num_heads} is not divisible by tp={tp}")
     if cfg.num_kv_heads % tp:
@@ -41,6 +39,11 @@ def local_config(cfg: ModelConfig, tp: int, expert_tp: bool = True) -> ModelConf
     kw = dict(num_heads=cfg.num_heads // tp, num_kv_heads=cfg.num_kv_heads // tp, intermediate_size=cfg.intermediate_size // tp)
     if cfg.num_experts and expert_tp:
         kw["moe_intermediate_size"] = cfg.moe_intermediate_size // tp
+        Is = getattr(cfg, "shared_expert_intermediate_size", 0) or 0
+        if Is:                                   # the shared expert is a dense MLP beside the routed ones: sliced the same way
+            if Is % tp:
+                raise ValueError("shared expert width is not divisible by tp")
+            kw["shared_expert_intermediate_size"] = Is // tp
     if getattr(cfg, "layer_types", None):
         # linear-attention layers split by heads as well (key heads and value heads keep their grouping)
         nk, nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
@@ -100,6 +103,15 @@ def shard_tensor(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank:
         if leaf == "out_proj" and ".linear_attn." in name:
             C = full.shape[1]
             return full[:, rank * C // tp:(rank + 1) * C // tp].contiguous()
+    if leaf in ("shared_gate_up", "shared_down", "shared_expert_gate"):
+        if not expert_tp or leaf == "shared_expert_gate":
+            return full                             # whole experts (row shares): the shared expert stays whole as well
+        if leaf == "shared_gate_up":
+            I = full.shape[0] // 2
+            a, b = rank * I // tp, (rank + 1) * I // tp
+            return torch.cat([full[a:b], full[I + a:I + b]], dim=0).contiguous()
+        C = full.shape[1]
+        return full[:, rank * C // tp:(rank + 1) * C // tp].contiguous()
     if full.dim() == 3:                             # stacked experts [E, rows, cols]
         if not expert_tp:
             return full
@@ -127,6 +139,13 @@ def unshard_tensors(cfg: ModelConfig, name: str, parts: list[torch.Tensor], expe
     p0 = parts[0]
     if (p0.dim() == 3 and not expert_tp) or name.startswith("visual."):
         return p0
+    if leaf in ("shared_gate_up", "shared_down", "shared_expert_gate"):
+        if not expert_tp or leaf == "shared_expert_gate":
+            return p0
+        if leaf == "shared_gate_up":
+            h = p0.shape[0] // 2
+            return torch.cat([p[:h] for p in parts] + [p[h:] for p in parts], dim=0)
+        return torch.cat(parts, dim=1)
     if getattr(cfg, "layer_types", None):
         blocks = _hybrid_blocks(cfg, name)
         if blocks is not None:
@@ -257,6 +276,7 @@ def install_tp(model, group, tp_size: int, tp_rank: int, sequence_parallel: bool
             if on and not expert_tp and hasattr(layer.mlp, "w_gate_up"):
                 layer.moe_row_share = (group, tp_size, tp_rank)
                 layer.mlp.aux_scale = 1.0 / tp_size         # every TP rank adds the balancing loss of its own share
+    model.tp_expert_tp = bool(expert_tp)
     model.tp_group, model.tp_size, model.tp_rank = (group if on else None), tp_size, tp_rank
     model.tp_sequence_parallel = bool(sequence_parallel and on)
     return model
@@ -267,7 +287,9 @@ def replicated_parameter_names(model) -> list[str]:
     out = []
     for n, p in model.named_parameters():
         leaf = n.rsplit(".", 1)[-1]
-        if p.dim() == 1 and leaf not in ("qkv_bias", "dt_bias", "A_log") or leaf in ("embed_tokens", "lm_head", "router", "value_head") or n.startswith("visual."):
+        whole_shared = not getattr(model, "tp_expert_tp", True) and leaf in ("shared_gate_up", "shared_down")
+        if p.dim() == 1 and leaf not in ("qkv_bias", "dt_bias", "A_log") or leaf in ("embed_tokens", "lm_head", "router", "value_head", "shared_expert_gate") \
+                or n.startswith("visual.") or whole_shared:
             out.append(n)            # (the image tower of a vision-language model is not sliced: every rank runs all of it)
     return out
 
@@ -279,8 +301,8 @@ def partial_grad_names(model) -> set[str]:
     out = set()
     for n in replicated_parameter_names(model):
         leaf = n.rsplit(".", 1)[-1]
-        if all_partial or leaf in ("q_norm", "k_norm", "router") or n.endswith("linear_attn.norm"):
-            out.add(n)
+        if all_partial or leaf in ("q_norm", "k_norm", "router", "shared_expert_gate", "shared_gate_up", "shared_down") or n.endswith("linear_attn.norm"):
+            out.add(n)             # (a whole shared expert is listed as replicated only when each TP rank ran it on its own row share)
     return out
 
 
@@ -299,7 +321,7 @@ def allreduce_replicated_grads(model, group, grad_of=lambda p: getattr(p, "main_
     all_partial = getattr(model, "tp_sequence_parallel", False)
     for n in replicated_parameter_names(model):
         leaf = n.rsplit(".", 1)[-1]
-        if all_partial or leaf in ("q_norm", "k_norm", "router") or n.endswith("linear_attn.norm"):     # (per-head norms saw the local heads only)
+        if all_partial or leaf in ("q_norm", "k_norm", "router", "shared_expert_gate", "shared_gate_up", "shared_down") or n.endswith("linear_attn.norm"):     # (per-head norms saw the local heads only)
             g = grad_of(params[n])
             if g is not None:
                 dist.all_reduce(g, group=group)

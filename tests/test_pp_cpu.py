@@ -74,12 +74,15 @@ def test_train_engine_expert_parallel(tmp_path, ranks, port):
     assert r.stdout.count("ENGINE_EP_OK") == ranks
 
 
-@pytest.mark.parametrize("backend,port", [("native:d2t2e2", 29945), ("native:(attn:d2t2|ffn:e2t2)", 29947)])
-def test_train_engine_expert_parallel_with_tensor_parallel_attention(tmp_path, backend, port):
+@pytest.mark.parametrize("backend,port,model", [("native:d2t2e2", 29945, "tiny-qwen3-moe"), ("native:(attn:d2t2|ffn:e2t2)", 29947, "tiny-qwen3-moe"),
+                                                ("native:d2t2e2", 29949, "tiny-qwen3.5-moe"), ("native:(attn:d2t2|ffn:e2t2)", 29951, "tiny-qwen3.5-moe")])
+def test_train_engine_expert_parallel_with_tensor_parallel_attention(tmp_path, backend, port, model):
     """Hybrid attention / expert layouts on 4 ranks against one rank: tensor-parallel attention with whole experts
     spread over data x tensor ranks (each TP rank routes its share of the tokens), and experts sliced over the TP group
-    and spread over the data ranks. Weights after two steps, the global gradient norm, HF export / reload."""
-    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", EP_SAVE_DIR=str(tmp_path), EP_TP_BACKEND=backend)
+    and spread over the data ranks. Weights after two steps, the global gradient norm, HF export / reload.
+    ``tiny-qwen3.5-moe``: linear-attention layers and a sigmoid-gated shared expert (sliced with the experts, or whole on
+    each rank's row share)."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", AREAL_FORCE_CPU="1", EP_SAVE_DIR=str(tmp_path), EP_TP_BACKEND=backend, EP_TP_MODEL=model)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
                         "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "dist_scripts", "run_engine_ep_tp.py")], cwd=ROOT,
                        env=env, capture_output=True, text=True, timeout=400)

@@ -43,7 +43,7 @@ def test_tensor_parallel_matches_unsharded_model_gloo():
     assert r.stdout.count("TP_OK") == 2
 
 
-@pytest.mark.parametrize("seq_par,model", [("0", "tiny-qwen3"), ("1", "tiny-qwen3"), ("0", "tiny-qwen3.5")])
+@pytest.mark.parametrize("seq_par,model", [("0", "tiny-qwen3"), ("1", "tiny-qwen3"), ("0", "tiny-qwen3.5"), ("0", "tiny-qwen3.5-moe")])
 def test_train_engine_dp2_tp2_matches_single_rank(tmp_path, seq_par, model):
     """``seq_par`` = 1: the residual stream is split by rows over the tensor-parallel group as well (gather -> product,
     product -> reduce-scatter around attention and MLP; norms and LM head on local rows; outputs gathered for the loss).
