@@ -107,6 +107,9 @@ def make_weight_pusher(train_engine, infer_engine, meta: WeightUpdateMeta):
         return DiskPusher(train_engine, infer_engine)
     if getattr(train_engine, "_z3", None) is not None:
         # sharded parameters: the full tensors are gathered unit by unit and handed over (or written to disk above)
+        if hasattr(infer_engine, "remote_ranks"):
+            raise NotImplementedError("fsdp.shard_parameters with rollout ranks in other processes: use actor.weight_update_mode=disk "
+                                      "(the peer-memory and broadcast paths read a replicated parameter buffer)")
         return GatheredPusher(train_engine, infer_engine)
     if meta.type in ("p2p", "xccl", "awex") and hasattr(infer_engine, "remote_ranks"):
         from ..parallel.weight_push import BroadcastWeightPusher, DistributedWeightPusher, TPWeightPusher
