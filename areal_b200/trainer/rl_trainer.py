@@ -189,7 +189,7 @@ class PPOTrainer:
         eos = getattr(self.tokenizer, "eos_token_id", None)
         # a trainer rank that holds only part of the model (pipeline stage, expert or tensor slice)
         # cannot lend its parameters to the engine: the engine keeps a full copy, fed by gathers
-        partial = any(getattr(self.actor, a, 1) > 1 for a in ("pp_size", "ep_size", "tp_size"))
+        partial = any(getattr(self.actor, a, 1) > 1 for a in ("pp_size", "ep_size", "tp_size")) or getattr(self.actor, "_z3", None) is not None
         share = self.actor.device.type == "cuda" and getattr(c.native_infer, "share_trainer_weights", True) and not partial
         if share:
             # colocated on one GPU: the rollout engine reads the trainer's bf16 parameters in

@@ -103,3 +103,27 @@ def test_train_engine_with_sharded_parameters(tmp_path, ranks, model, ckpt, back
                        env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("ENGINE_Z3_OK") == ranks
+
+
+def test_colocated_grpo_loop_with_sharded_parameters(tmp_path):
+    """The whole async GRPO loop on one CPU process with ``fsdp.shard_parameters``: the rollout engine keeps its own copy
+    of the weights (the trainer's parameters exist only layer by layer), fed by the gathered tensors after every step."""
+    os.environ["AREAL_FORCE_CPU"] = "1"
+    from areal_b200.dataset import ArithmeticDataset
+    from areal_b200.models.config import preset
+    from areal_b200.rollout.workflows.rlvr import RLVRWorkflow
+    from areal_b200.trainer import PPOTrainer
+    from tests.test_e2e_cpu import _cfg, digit_reward
+
+    cfg = _cfg(str(tmp_path), steps=5)
+    cfg.actor.fsdp.shard_parameters = True
+    mc = preset("tiny-qwen2", vocab_size=64, num_layers=2)
+    with PPOTrainer(cfg, ArithmeticDataset(size=128), tokenizer=None, model_config=mc) as tr:
+        assert tr.actor._z3 is not None and tr.rollout.model is not tr.actor.model
+        hist = tr.train(workflow=RLVRWorkflow(digit_reward, cfg.gconfig, reward_in_process=True))
+        assert tr.rollout.get_version() == 5
+        # the engine's copy equals the trainer's gathered weights after the last update
+        w = tr.actor.export_weights()
+        for n, p in tr.rollout.model.named_parameters():
+            assert torch.allclose(p.detach().float().cpu(), w[n].float(), atol=1e-6), n
+    assert len(hist) == 5 and all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
