@@ -512,10 +512,9 @@ class B200TrainEngine(TrainEngine):
         self._z3 = None
         if bool(getattr(cfg.fsdp, "shard_parameters", False)):
             # ZeRO-3: parameters and gradients sharded as well, decoder layers materialised one at a time
-            if getattr(self, "pp_size", 1) > 1 or getattr(self, "ep_size", 1) > 1 or self.use_lora or model_config.is_vlm \
-                    or (tp > 1 and bool(cfg.fsdp.tp_sequence_parallel)):
-                raise NotImplementedError("fsdp.shard_parameters covers data / sequence / tensor parallel text models (no pp / ep, LoRA, image tower "
-                                          "or sequence-parallel residual stream)")
+            if getattr(self, "pp_size", 1) > 1 or getattr(self, "ep_size", 1) > 1 or self.use_lora or (tp > 1 and bool(cfg.fsdp.tp_sequence_parallel)):
+                raise NotImplementedError("fsdp.shard_parameters covers data / sequence / tensor parallel models (no pp / ep, LoRA or "
+                                          "sequence-parallel residual stream); an image tower stays resident with the embedding for a micro-batch")
             from .sharded_params import ShardedParamStore
 
             fused, alloc = False, None

@@ -127,3 +127,35 @@ def test_colocated_grpo_loop_with_sharded_parameters(tmp_path):
         for n, p in tr.rollout.model.named_parameters():
             assert torch.allclose(p.detach().float().cpu(), w[n].float(), atol=1e-6), n
     assert len(hist) == 5 and all(h["ppo_actor/update/update_successful"] == 1.0 for h in hist)
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen2.5-vl", "tiny-qwen3-vl"])
+def test_vision_language_model_with_sharded_parameters(name):
+    """The image tower belongs to the root unit (resident with the embedding for a micro-batch), the decoder layers come
+    and go: two steps move the weights exactly as with replicated parameters."""
+    os.environ["AREAL_FORCE_CPU"] = "1"
+    from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, TrainEngineConfig
+    from areal_b200.engine.train_engine import B200TrainEngine
+    from areal_b200.models.config import preset
+    from tests.test_vlm import _vlm_batch
+
+    def loss_fn(logp, ent, mb):
+        m = mb["loss_mask"].bool()
+        return -(logp * m).sum() / m.sum().clamp(min=1)
+
+    res = []
+    for shard in (False, True):
+        cfg = TrainEngineConfig(init_from_scratch=True, dtype="float32", backend="d1", optimizer=OptimizerConfig(lr=1e-2, gradient_clipping=1.0),
+                                mb_spec=MicroBatchSpec(max_tokens_per_mb=256))
+        cfg.fsdp.shard_parameters = shard
+        eng = B200TrainEngine(cfg)
+        eng.create_process_group()
+        mc = preset(name)
+        eng.initialize(model_config=mc, seed=3)
+        batch = _vlm_batch(mc, mc.vision_config())
+        st = [eng.train_batch(dict(batch), loss_fn, lambda mb: mb["loss_mask"].count_nonzero()) for _ in range(2)]
+        if shard:
+            assert any(n.startswith("visual.") for n, u in zip(eng.store.names, eng.store.units_of) if u == 0)
+        res.append(([s["grad_norm"] for s in st], eng.export_weights()))
+    (g0, w0), (g1, w1) = res
+    assert all(abs(a - b) < 1e-4 * max(1.0, a) for a, b in zip(g0, g1)) and all(torch.allclose(w0[n], w1[n], atol=1e-5) for n in w0)
