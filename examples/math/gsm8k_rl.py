@@ -23,7 +23,9 @@ def main(argv):
     if config.valid_dataset is not None:
         valid = get_custom_dataset(config.valid_dataset.path, type="rl", split="test", tokenizer=tokenizer)
     workflow = RLVRWorkflow(gsm8k_reward_fn, config.gconfig, tokenizer=tokenizer)
-    eval_workflow = RLVRWorkflow(gsm8k_reward_fn, config.gconfig.new(temperature=0.6, n_samples=1), tokenizer=tokenizer)
+    # evaluation samples with its own generation settings when the config has an ``eval_gconfig`` section
+    eval_g = config.eval_gconfig if config.eval_gconfig is not None else config.gconfig.new(temperature=0.6, n_samples=1)
+    eval_workflow = RLVRWorkflow(gsm8k_reward_fn, eval_g, tokenizer=tokenizer)
     with PPOTrainer(config, train_dataset=train, valid_dataset=valid, tokenizer=tokenizer) as trainer:
         trainer.train(workflow=workflow, eval_workflow=eval_workflow)
 
