@@ -82,6 +82,12 @@ def _package_text() -> str:
     if os.path.exists(bench):
         with open(bench) as fh:
             chunks.append(fh.read())
+    for dp, dns, fs in os.walk(os.path.join(os.path.dirname(root), "examples")):      # example scripts read config fields too
+        dns[:] = sorted(d for d in dns if d != "__pycache__")
+        for f in sorted(fs):
+            if f.endswith(".py"):
+                with open(os.path.join(dp, f)) as fh:
+                    chunks.append(fh.read())
     return "\n".join(chunks)
 
 
