@@ -401,8 +401,10 @@ class vLLMConfig:
         if n_nodes > 1:
             a.update(nnodes=n_nodes, node_rank=node_rank)
             if dist_init_addr:
-                h, _, p_ = dist_init_addr.rpartition(":")
-                a.update(master_addr=h, master_port=p_)
+                from ..utils.network import split_hostport
+
+                h, p_ = split_hostport(dist_init_addr)            # (IPv6 literals with or without brackets)
+                a.update(master_addr=h, master_port=str(p_))
             if node_rank > 0:
                 a["headless"] = True
         return a

@@ -170,7 +170,9 @@ class RemoteInfEngine(InferenceEngine):
             cmd = server_cmd(module, server_args)
         p = subprocess.Popen([str(c) for c in cmd], stdout=subprocess.DEVNULL, stderr=subprocess.STDOUT, start_new_session=True)
         self._server_procs.append(p)
-        addr = f"{host}:{port}"
+        from ..utils.network import format_hostport
+
+        addr = format_hostport(host, port)
         deadline = time.monotonic() + self.config.setup_timeout
         while True:
             if p.poll() is not None:

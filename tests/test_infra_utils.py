@@ -558,3 +558,19 @@ def test_sbatch_script_reservation_exclusive_and_container_kinds(reservation, ex
     assert "--mpi=pmix --label" in line and "apptainer exec --nv --bind /data:/data /img.sif" in line and "--container-image" not in line
     t3 = render_sbatch_script("j", 1, 1, 4, 8, "/tmp/j.log", "python x.py", container_image="nvcr.io/x:1", container_mounts="/data:/data", container_type="pyxis")
     assert "--container-image=nvcr.io/x:1 --container-mounts=/data:/data" in t3 and "apptainer" not in t3
+
+
+def test_hostport_helpers_handle_ipv6():
+    from areal_b200.utils.network import format_hostport, gethostip_any, is_ipv6_literal, split_hostport
+
+    assert format_hostport("node3", 80) == "node3:80" and format_hostport("10.0.0.1", 80) == "10.0.0.1:80"
+    assert format_hostport("fe80::1", 8000) == "[fe80::1]:8000" and format_hostport("[fe80::1]", 8000) == "[fe80::1]:8000"
+    assert split_hostport("node3:80") == ("node3", 80) and split_hostport("[fe80::1%eth0]:9") == ("fe80::1%eth0", 9)
+    assert split_hostport("2001:db8::5:7000") == ("2001:db8::5", 7000)            # unbracketed, as some launchers write it
+    assert split_hostport(format_hostport("::1", 1234)) == ("::1", 1234)
+    for bad in ("node3", ":80", "[fe80::1]80", "[nonsense]:80", "1.2.3.4:99999", "zz::zz:80", "[fe80::1"):
+        with pytest.raises(ValueError):
+            split_hostport(bad)
+    assert is_ipv6_literal("::1") and is_ipv6_literal("[::1]") and not is_ipv6_literal("127.0.0.1") and not is_ipv6_literal("host")
+    ip = gethostip_any()
+    assert isinstance(ip, str) and ip
