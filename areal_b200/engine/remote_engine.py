@@ -64,6 +64,7 @@ class RemoteInfEngine(InferenceEngine):
         self._rr = 0
         self._rid_to_addr: dict[str, str] = {}
         self._rid_order: list[str] = []
+        self._inflight: dict[str, int] = {}          # address -> requests of this client being served there
         self._lock = threading.Lock()
         self._executor = None
         self._paused = threading.Event()
@@ -204,7 +205,11 @@ class RemoteInfEngine(InferenceEngine):
         with self._lock:
             if rid is not None and rid in self._rid_to_addr:
                 return self._rid_to_addr[rid]          # KV-cache affinity for resumed / multi-turn requests
-            a = self.addresses[self._rr % len(self.addresses)]
+            if getattr(self.config, "schedule_policy", "round_robin") in ("least_requests", "least_loaded") and self._inflight:
+                # the server with the fewest requests of this client in flight (ties: the earliest in the list)
+                a = min(self.addresses, key=lambda x: (self._inflight.get(x, 0), self.addresses.index(x)))
+            else:
+                a = self.addresses[self._rr % len(self.addresses)]
             self._rr += 1
             if rid is not None:
                 self._rid_to_addr[rid] = a
@@ -242,6 +247,15 @@ class RemoteInfEngine(InferenceEngine):
         ttft = float("inf")
         addr = self.choose_server(req.rid)
         session = await self._session()
+        with self._lock:
+            self._inflight[addr] = self._inflight.get(addr, 0) + 1
+        try:
+            return await self._generate_on(addr, session, req, g, prompt, budget, out_tok, out_lp, out_ver, stop, t0, ttft)
+        finally:
+            with self._lock:
+                self._inflight[addr] = max(0, self._inflight.get(addr, 1) - 1)
+
+    async def _generate_on(self, addr, session, req, g, prompt, budget, out_tok, out_lp, out_ver, stop, t0, ttft) -> ModelResponse:
         while stop not in ("stop", "length", "tool_calls") and len(out_tok) < budget:
             while self._paused.is_set():
                 await asyncio.sleep(0.01)

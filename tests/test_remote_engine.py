@@ -253,3 +253,16 @@ def test_server_command_builders_and_external_launch(tmp_path):
     bad = RemoteInfEngine(InferenceEngineConfig(setup_timeout=10), [], backend="vllm")
     with pytest.raises(RuntimeError, match="exited with code"):
         bad.launch_server({"cmd": [sys.executable, "-c", "raise SystemExit(3)"], "port": find_free_ports(1)[0]})
+
+
+def test_least_requests_policy_prefers_the_idle_server():
+    from areal_b200.api.cli_args import InferenceEngineConfig
+    from areal_b200.engine.remote_engine import RemoteInfEngine
+
+    eng = RemoteInfEngine(InferenceEngineConfig(schedule_policy="least_requests"), ["a:1", "b:1", "c:1"])
+    eng._inflight.update({"a:1": 3, "b:1": 0, "c:1": 2})
+    assert eng.choose_server("r1") == "b:1" and eng.choose_server("r1") == "b:1"          # and a request id stays where it went
+    eng._inflight["b:1"] = 5
+    assert eng.choose_server("r2") == "c:1"
+    rr = RemoteInfEngine(InferenceEngineConfig(), ["a:1", "b:1"])
+    assert [rr.choose_server() for _ in range(4)] == ["a:1", "b:1", "a:1", "b:1"]
