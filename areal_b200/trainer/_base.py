@@ -35,8 +35,9 @@ class SupervisedTrainer:
         self.collate_fn = collate_fn or pad_collate
         g = torch.Generator().manual_seed(config.seed)
         dc = config.train_dataset
+        # ``train_dataset.num_workers``: worker processes that tokenise / collate ahead of the training loop (0: in the loop)
         self.train_dataloader = DataLoader(train_dataset, batch_size=dc.batch_size, shuffle=dc.shuffle, drop_last=dc.drop_last,
-                                           collate_fn=self.collate_fn, generator=g)
+                                           collate_fn=self.collate_fn, generator=g, num_workers=max(0, int(getattr(dc, "num_workers", 0) or 0)))
         self.valid_dataloader = None
         if valid_dataset is not None:
             vb = config.valid_dataset.batch_size if config.valid_dataset else dc.batch_size
