@@ -5,9 +5,10 @@ engine (replicated parameters) on the same batch:
 * ``hybrid-tp`` ``native:d1t2`` of a linear-attention (gated delta rule) model, heads of both mixers sliced,
 * ``vlm-tp``    ``native:d1t2`` of a vision-language model, language model sliced, image tower whole;
 
-and with 4 ranks (``LAYOUTS=ep-tp,ep-etp,pp-tp,pp-ep``): whole experts over data x tensor ranks (``native:d2t2e2``), experts
+and with 4 ranks (``LAYOUTS=ep-tp,ep-etp,pp-tp,pp-ep,sharded-tp``): whole experts over data x tensor ranks (``native:d2t2e2``), experts
 sliced over the tensor-parallel group (``native:(attn:d2t2|ffn:e2t2)``), tensor parallelism inside pipeline stages
-(``native:d1p2t2``), expert parallelism inside pipeline stages (``native:d2p2e2``).
+(``native:d1p2t2``), expert parallelism inside pipeline stages (``native:d2p2e2``), sharded parameters under tensor
+parallelism (``d2t2`` with ``fsdp.shard_parameters``, a hybrid MoE model with a shared expert).
 
 Prints ``LAYOUT_OK <name>`` per rank and layout, then ENGINE_LAYOUTS_GPU_OK."""
 import faulthandler
@@ -104,15 +105,16 @@ def main():
 
         batch = _vlm_batch(mc, mc.vision_config())
         compare("vlm-tp", run(mc, batch, f"native:d1t{world}", on_gpu, rank), run(mc, batch, "d1", on_gpu, rank, alone=True), on_gpu, rank)
-    four = {"ep-tp": ("tiny-qwen3-moe", "native:d2t2e2"), "ep-etp": ("tiny-qwen3-moe", "native:(attn:d2t2|ffn:e2t2)"),
-            "pp-tp": ("tiny-qwen3", "native:d1p2t2"), "pp-ep": ("tiny-qwen3-moe", "native:d2p2e2")}
-    for name, (model, backend) in four.items():
+    four = {"ep-tp": ("tiny-qwen3-moe", "native:d2t2e2", False), "ep-etp": ("tiny-qwen3-moe", "native:(attn:d2t2|ffn:e2t2)", False),
+            "pp-tp": ("tiny-qwen3", "native:d1p2t2", False), "pp-ep": ("tiny-qwen3-moe", "native:d2p2e2", False),
+            "sharded-tp": ("tiny-qwen3.5-moe", "d2t2", True)}        # sharded parameters under tensor parallelism, shared expert sliced
+    for name, (model, backend, shard) in four.items():
         if name in only:
             assert world == 4, "these layouts are written for 4 ranks"
             mc = preset(model)
             batch = make_batch(mc.vocab_size)
             share = lambda eng: {k: v[eng.dp_rank * (8 // eng.dp_size):(eng.dp_rank + 1) * (8 // eng.dp_size)] for k, v in batch.items()}   # noqa: E731
-            compare(name, run(mc, batch, backend, on_gpu, rank, mine=share), run(mc, batch, "d1", on_gpu, rank, alone=True), on_gpu, rank)
+            compare(name, run(mc, batch, backend, on_gpu, rank, mine=share, shard=shard), run(mc, batch, "d1", on_gpu, rank, alone=True), on_gpu, rank)
     print("ENGINE_LAYOUTS_GPU_OK", flush=True)
     dist.barrier()
     dist.destroy_process_group()
