@@ -134,6 +134,6 @@ def test_engine_layouts_expert_tensor_pipeline_four_gpus():
     norms and the three-step update follow a single-rank engine."""
     _need(4)
     r = _torchrun(os.path.join(HERE, "dist_scripts", "run_engine_layouts_gpu.py"), 4, 29799, timeout=300,
-                  env={"NCCL_NVLS_ENABLE": "0", "LAYOUTS": "ep-tp,ep-etp,pp-tp,pp-ep,sharded-tp"})
+                  env={"NCCL_NVLS_ENABLE": "0", "LAYOUTS": "ep-tp,ep-etp,pp-tp,pp-ep"})
     assert r.returncode == 0
     assert r.stdout.count("ENGINE_LAYOUTS_GPU_OK") == 4
